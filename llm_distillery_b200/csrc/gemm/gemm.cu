@@ -1,0 +1,197 @@
+// Plain GEMM entry points on the tcgen05 mainloop (gemm_core.cuh):
+//   C[M,N] = alpha * A * B^T (+ C) (+ residual)     bf16/fp16 operands, fp32 accumulate,
+// with A and B each either K-major or MN-major, so forward (NT), dgrad (NN) and wgrad (TN)
+// GEMMs of a linear layer all run without a transpose pass.
+#include "gemm_core.cuh"
+#include "../common/host.cuh"
+
+namespace b200 {
+namespace gemm {
+
+struct StoreParams {
+  void* C;
+  long long ldc;               // elements
+  const __nv_bfloat16* resid;  // optional residual added to the result (bf16, same shape as C), may be null
+  long long ldr;
+  float alpha;
+  int out_f32;     // 1: C is fp32, 0: C is 16-bit (bf16 or fp16 according to fmt)
+  int accumulate;  // 1: C += result
+  int fmt;         // 0 fp16, 1 bf16 (16-bit output type)
+};
+
+template <int BN>
+struct EpiStore {
+  using Params = StoreParams;
+  static constexpr int SMEM_BYTES = 0;
+
+  static __device__ __forceinline__ void tile(const Params& p, uint32_t taddr, int m0, int n0, int M, int N, int quad,
+                                              int lane, uint8_t*) {
+    const int row = m0 + quad * 32 + lane;
+    const bool row_ok = row < M;
+#pragma unroll 1
+    for (int c = 0; c < BN / 32; ++c) {
+      uint32_t r[32];
+      tmem_ld_32x32b_x32(taddr + c * 32, r);
+      tmem_ld_wait();
+      const int col0 = n0 + c * 32;
+      if (!row_ok || col0 >= N) continue;
+      float v[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+      const int ncols = min(32, N - col0);
+      if (p.resid) {
+        const __nv_bfloat16* rp = p.resid + (long long)row * p.ldr + col0;
+        if (ncols == 32 && ((reinterpret_cast<uintptr_t>(rp) & 15) == 0)) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 q = *reinterpret_cast<const uint4*>(rp + j * 8);
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+              float2 f = __bfloat1622float2(h[t]);
+              v[j * 8 + t * 2] += f.x;
+              v[j * 8 + t * 2 + 1] += f.y;
+            }
+          }
+        } else {
+          for (int j = 0; j < ncols; ++j) v[j] += __bfloat162float(rp[j]);
+        }
+      }
+      if (p.out_f32) {
+        float* cp = reinterpret_cast<float*>(p.C) + (long long)row * p.ldc + col0;
+        if (ncols == 32 && ((reinterpret_cast<uintptr_t>(cp) & 15) == 0)) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            float4 o = make_float4(v[j * 4], v[j * 4 + 1], v[j * 4 + 2], v[j * 4 + 3]);
+            if (p.accumulate) {
+              float4 old = *reinterpret_cast<float4*>(cp + j * 4);
+              o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+            }
+            *reinterpret_cast<float4*>(cp + j * 4) = o;
+          }
+        } else {
+          for (int j = 0; j < ncols; ++j) cp[j] = p.accumulate ? cp[j] + v[j] : v[j];
+        }
+      } else if (p.fmt == 1) {
+        __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col0;
+        if (ncols == 32 && ((reinterpret_cast<uintptr_t>(cp) & 15) == 0)) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            if (p.accumulate) {
+              uint4 q = *reinterpret_cast<const uint4*>(cp + j * 8);
+              const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+              for (int t = 0; t < 4; ++t) {
+                float2 f = __bfloat1622float2(h[t]);
+                v[j * 8 + t * 2] += f.x;
+                v[j * 8 + t * 2 + 1] += f.y;
+              }
+            }
+            uint4 o;
+            o.x = pack_bf16x2(v[j * 8 + 0], v[j * 8 + 1]);
+            o.y = pack_bf16x2(v[j * 8 + 2], v[j * 8 + 3]);
+            o.z = pack_bf16x2(v[j * 8 + 4], v[j * 8 + 5]);
+            o.w = pack_bf16x2(v[j * 8 + 6], v[j * 8 + 7]);
+            *reinterpret_cast<uint4*>(cp + j * 8) = o;
+          }
+        } else {
+          for (int j = 0; j < ncols; ++j) {
+            float x = v[j] + (p.accumulate ? __bfloat162float(cp[j]) : 0.f);
+            cp[j] = __float2bfloat16(x);
+          }
+        }
+      } else {
+        __half* cp = reinterpret_cast<__half*>(p.C) + (long long)row * p.ldc + col0;
+        for (int j = 0; j < ncols; ++j) {
+          float x = v[j] + (p.accumulate ? __half2float(cp[j]) : 0.f);
+          cp[j] = __float2half(x);
+        }
+      }
+    }
+  }
+};
+
+template <int BN, int STAGES, bool A_MN, bool B_MN>
+static int launch_store(const void* A, const void* B, int M, int N, int K, long long lda, long long ldb, int fmt,
+                        const StoreParams& sp, const DescCfg* dc_override, cudaStream_t stream) {
+  using Epi = EpiStore<BN>;
+  using S = Smem<BN, STAGES>;
+  CUtensorMap tmA, tmB;
+  const CUtensorMapDataType dt = fmt == 1 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  int rc;
+  if (!A_MN)
+    rc = make_tmap_2d(&tmA, A, dt, 2, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B);
+  else
+    rc = make_tmap_2d(&tmA, A, dt, 2, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, 64, BK, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != B200_OK) return rc;
+  if (!B_MN)
+    rc = make_tmap_2d(&tmB, B, dt, 2, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, BK, BN, CU_TENSOR_MAP_SWIZZLE_128B);
+  else
+    rc = make_tmap_2d(&tmB, B, dt, 2, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, 64, BK, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != B200_OK) return rc;
+
+  auto kern = gemm_kernel<BN, STAGES, A_MN, B_MN, Epi>;
+  const int smem_bytes = S::bytes(Epi::SMEM_BYTES);
+  static bool attr_set = false;
+  if (!attr_set) {
+    B200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+    attr_set = true;
+  }
+  const int tiles = ceil_div(M, BM) * ceil_div(N, BN);
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  DescCfg dc = dc_override ? *dc_override : default_desc_cfg<BN, A_MN, B_MN>();
+  kern<<<grid, NUM_THREADS, smem_bytes, stream>>>(tmA, tmB, M, N, K, fmt, dc, sp, device_err_word());
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200_OK;
+}
+
+}  // namespace gemm
+}  // namespace b200
+
+extern "C" {
+
+// C[M,N] = alpha * op(A) * op(B)^T (+ C if accumulate) (+ residual)
+//   a_mn = 0: A is [M,K] with row stride lda;   a_mn = 1: A is stored [K,M] with row stride lda
+//   b_mn = 0: B is [N,K] with row stride ldb;   b_mn = 1: B is stored [K,N] with row stride ldb
+//   fmt: 1 = bf16 operands, 0 = fp16.  out_f32: C is fp32, else the operand type.
+// Strides are in elements and must be multiples of 8 (16 bytes); base pointers 16-byte aligned.
+// desc_cfg: optional 6 x uint32 override of the matrix-descriptor byte offsets (testing hook), else null.
+int b200_gemm(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+              long long ldc, int a_mn, int b_mn, int fmt, int out_f32, int accumulate, float alpha,
+              const void* residual, long long ldr, const unsigned int* desc_cfg, cudaStream_t stream) {
+  using namespace b200;
+  using namespace b200::gemm;
+  if (!A || !B || !C || M <= 0 || N <= 0 || K <= 0) return B200_ERR_ARG;
+  if ((lda & 7) || (ldb & 7)) return B200_ERR_ARG;
+  StoreParams sp;
+  sp.C = C;
+  sp.ldc = ldc;
+  sp.resid = reinterpret_cast<const __nv_bfloat16*>(residual);
+  sp.ldr = ldr;
+  sp.alpha = alpha;
+  sp.out_f32 = out_f32;
+  sp.accumulate = accumulate;
+  sp.fmt = fmt;
+  DescCfg dco;
+  const DescCfg* dcp = nullptr;
+  if (desc_cfg) {
+    dco.a_lbo = desc_cfg[0]; dco.a_sbo = desc_cfg[1]; dco.a_kadv = desc_cfg[2];
+    dco.b_lbo = desc_cfg[3]; dco.b_sbo = desc_cfg[4]; dco.b_kadv = desc_cfg[5];
+    dcp = &dco;
+  }
+  const bool small_n = N <= 128;
+  if (!a_mn && !b_mn) {
+    return small_n ? launch_store<128, 6, false, false>(A, B, M, N, K, lda, ldb, fmt, sp, dcp, stream)
+                   : launch_store<256, 4, false, false>(A, B, M, N, K, lda, ldb, fmt, sp, dcp, stream);
+  } else if (!a_mn && b_mn) {
+    return small_n ? launch_store<128, 6, false, true>(A, B, M, N, K, lda, ldb, fmt, sp, dcp, stream)
+                   : launch_store<256, 4, false, true>(A, B, M, N, K, lda, ldb, fmt, sp, dcp, stream);
+  } else if (a_mn && b_mn) {
+    return small_n ? launch_store<128, 6, true, true>(A, B, M, N, K, lda, ldb, fmt, sp, dcp, stream)
+                   : launch_store<256, 4, true, true>(A, B, M, N, K, lda, ldb, fmt, sp, dcp, stream);
+  } else {
+    return small_n ? launch_store<128, 6, true, false>(A, B, M, N, K, lda, ldb, fmt, sp, dcp, stream)
+                   : launch_store<256, 4, true, false>(A, B, M, N, K, lda, ldb, fmt, sp, dcp, stream);
+  }
+}
+}

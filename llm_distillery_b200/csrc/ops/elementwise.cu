@@ -1,0 +1,428 @@
+// Bandwidth-bound transformer ops for sm_100a: RMSNorm (+ fused residual add) fwd/bwd, rotary
+// embedding fwd/bwd (in place), SwiGLU fwd/bwd, embedding gather / scatter-add, dtype casts.
+// All tensors are bf16 unless stated; statistics and weight gradients are fp32.
+// Every kernel moves 16-byte vectors and keeps the row it works on in registers between passes,
+// so each element crosses HBM once per direction.
+#include "../common/ptx.cuh"
+#include "../common/host.cuh"
+
+namespace b200 {
+namespace ew {
+
+constexpr int NT = 256;
+constexpr int MAX_VEC = 4;  // 16-byte vectors cached per thread: rows up to NT*MAX_VEC*8 = 8192 elements
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  __syncthreads();
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = (threadIdx.x < (NT / 32)) ? red[threadIdx.x] : 0.f;
+  if (w == 0) {
+    t = warp_sum(t);
+    if (l == 0) red[0] = t;
+  }
+  __syncthreads();
+  return red[0];
+}
+
+__device__ __forceinline__ void unpack8(const uint4& q, float (&f)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+  for (int t = 0; t < 4; ++t) {
+    float2 x = __bfloat1622float2(h[t]);
+    f[2 * t] = x.x;
+    f[2 * t + 1] = x.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 o;
+  o.x = pack_bf16x2(f[0], f[1]);
+  o.y = pack_bf16x2(f[2], f[3]);
+  o.z = pack_bf16x2(f[4], f[5]);
+  o.w = pack_bf16x2(f[6], f[7]);
+  return o;
+}
+
+// y = rmsnorm(x (+ res)) * w ; if res != null also writes h = x + res to `hout`. rstd[row] saved for backward.
+__global__ void __launch_bounds__(NT) rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x,
+                                                        const __nv_bfloat16* __restrict__ res,
+                                                        const __nv_bfloat16* __restrict__ w,
+                                                        __nv_bfloat16* __restrict__ y, __nv_bfloat16* __restrict__ hout,
+                                                        float* __restrict__ rstd, int rows, int h, float eps) {
+  __shared__ float red[NT / 32];
+  const int nvec = h >> 3;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * h);
+    const uint4* rr = res ? reinterpret_cast<const uint4*>(res + (size_t)row * h) : nullptr;
+    float vals[MAX_VEC][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAX_VEC; ++i) {
+      const int v = threadIdx.x + i * NT;
+      if (v < nvec) {
+        unpack8(xr[v], vals[i]);
+        if (rr) {
+          float r8[8];
+          unpack8(rr[v], r8);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) vals[i][j] += r8[j];
+          if (hout) {
+            // the residual stream is stored in bf16: normalise what is stored, not the fp32 sum
+            uint4 hq = pack8(vals[i]);
+            reinterpret_cast<uint4*>(hout + (size_t)row * h)[v] = hq;
+            unpack8(hq, vals[i]);
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss += vals[i][j] * vals[i][j];
+      }
+    }
+    const float tot = block_sum(ss, red);
+    const float rs = rsqrtf(tot / (float)h + eps);
+    if (threadIdx.x == 0 && rstd) rstd[row] = rs;
+#pragma unroll
+    for (int i = 0; i < MAX_VEC; ++i) {
+      const int v = threadIdx.x + i * NT;
+      if (v < nvec) {
+        float w8[8], o[8];
+        unpack8(reinterpret_cast<const uint4*>(w)[v], w8);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = vals[i][j] * rs * w8[j];
+        reinterpret_cast<uint4*>(y + (size_t)row * h)[v] = pack8(o);
+      }
+    }
+  }
+}
+
+// dx = rstd * (dy*w - xhat * mean(dy*w*xhat)) (+ dres) ; dw partial sums per block in fp32.
+__global__ void __launch_bounds__(NT) rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
+                                                        const __nv_bfloat16* __restrict__ x,
+                                                        const __nv_bfloat16* __restrict__ w,
+                                                        const float* __restrict__ rstd,
+                                                        const __nv_bfloat16* __restrict__ dres,
+                                                        __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_partial,
+                                                        int rows, int h) {
+  __shared__ float red[NT / 32];
+  const int nvec = h >> 3;
+  float dwacc[MAX_VEC][8];
+  float w8[MAX_VEC][8];
+#pragma unroll
+  for (int i = 0; i < MAX_VEC; ++i) {
+    const int v = threadIdx.x + i * NT;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dwacc[i][j] = 0.f;
+    if (v < nvec) unpack8(reinterpret_cast<const uint4*>(w)[v], w8[i]);
+  }
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float rs = rstd[row];
+    float xh[MAX_VEC][8], g[MAX_VEC][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAX_VEC; ++i) {
+      const int v = threadIdx.x + i * NT;
+      if (v < nvec) {
+        float d8[8];
+        unpack8(reinterpret_cast<const uint4*>(x + (size_t)row * h)[v], xh[i]);
+        unpack8(reinterpret_cast<const uint4*>(dy + (size_t)row * h)[v], d8);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          xh[i][j] *= rs;
+          dwacc[i][j] += d8[j] * xh[i][j];
+          g[i][j] = d8[j] * w8[i][j];
+          dot += g[i][j] * xh[i][j];
+        }
+      }
+    }
+    const float c = block_sum(dot, red) / (float)h;
+#pragma unroll
+    for (int i = 0; i < MAX_VEC; ++i) {
+      const int v = threadIdx.x + i * NT;
+      if (v < nvec) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = rs * (g[i][j] - xh[i][j] * c);
+        if (dres) {
+          float r8[8];
+          unpack8(reinterpret_cast<const uint4*>(dres + (size_t)row * h)[v], r8);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] += r8[j];
+        }
+        reinterpret_cast<uint4*>(dx + (size_t)row * h)[v] = pack8(o);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < MAX_VEC; ++i) {
+    const int v = threadIdx.x + i * NT;
+    if (v < nvec) {
+      float* p = dw_partial + (size_t)blockIdx.x * h + (size_t)v * 8;
+      *reinterpret_cast<float4*>(p) = make_float4(dwacc[i][0], dwacc[i][1], dwacc[i][2], dwacc[i][3]);
+      *reinterpret_cast<float4*>(p + 4) = make_float4(dwacc[i][4], dwacc[i][5], dwacc[i][6], dwacc[i][7]);
+    }
+  }
+}
+
+// out[j] (+)= sum_b partial[b][j]
+__global__ void colsum_kernel(const float* __restrict__ partial, float* __restrict__ out, int nblk, int h,
+                              int accumulate) {
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= h) return;
+  float s = 0.f;
+  for (int b = 0; b < nblk; ++b) s += partial[(size_t)b * h + j];
+  out[j] = accumulate ? out[j] + s : s;
+}
+
+// Rotary embedding, HF Llama convention (pairs (i, i + d/2)), in place on x[T, nh, d].
+// cos/sin tables are fp32 [max_pos, d/2]; pos[t] gives the position of token t. sign = -1 runs the inverse rotation
+// (the backward pass).
+__global__ void rope_kernel(__nv_bfloat16* __restrict__ x, const int* __restrict__ pos, const float* __restrict__ cs,
+                            const float* __restrict__ sn, long long T, int nh, int d, long long row_stride,
+                            float sign) {
+  const int half = d >> 1;
+  const int pairs_per_tok = nh * (half >> 1);  // two pairs per thread (bf16x2 on each half)
+  const long long total = T * pairs_per_tok;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / pairs_per_tok;
+    const int r = (int)(i - t * pairs_per_tok);
+    const int hd = r / (half >> 1);
+    const int j = (r - hd * (half >> 1)) * 2;
+    const int p = pos[t];
+    __nv_bfloat16* base = x + t * row_stride + (long long)hd * d;
+    __nv_bfloat162 a = *reinterpret_cast<__nv_bfloat162*>(base + j);
+    __nv_bfloat162 b = *reinterpret_cast<__nv_bfloat162*>(base + j + half);
+    const float2 c = *reinterpret_cast<const float2*>(cs + (size_t)p * half + j);
+    float2 s = *reinterpret_cast<const float2*>(sn + (size_t)p * half + j);
+    s.x *= sign;
+    s.y *= sign;
+    const float2 fa = __bfloat1622float2(a), fb = __bfloat1622float2(b);
+    float2 oa, ob;
+    oa.x = fa.x * c.x - fb.x * s.x;
+    oa.y = fa.y * c.y - fb.y * s.y;
+    ob.x = fb.x * c.x + fa.x * s.x;
+    ob.y = fb.y * c.y + fa.y * s.y;
+    *reinterpret_cast<__nv_bfloat162*>(base + j) = __floats2bfloat162_rn(oa.x, oa.y);
+    *reinterpret_cast<__nv_bfloat162*>(base + j + half) = __floats2bfloat162_rn(ob.x, ob.y);
+  }
+}
+
+// act[t, j] = silu(gu[t, j]) * gu[t, f + j]      gu is [T, 2f]
+__global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ act, long long T,
+                                  int f) {
+  const int fv = f >> 3;
+  const long long total = T * fv;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / fv;
+    const int v = (int)(i - t * fv);
+    const uint4* row = reinterpret_cast<const uint4*>(gu + t * 2 * f);
+    float g[8], u[8], o[8];
+    unpack8(row[v], g);
+    unpack8(row[fv + v], u);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = g[j] / (1.f + __expf(-g[j])) * u[j];
+    reinterpret_cast<uint4*>(act + t * f)[v] = pack8(o);
+  }
+}
+
+// dgu[t, j] = dact * u * dsilu(g) ; dgu[t, f + j] = dact * silu(g)
+__global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gu, const __nv_bfloat16* __restrict__ dact,
+                                  __nv_bfloat16* __restrict__ dgu, long long T, int f) {
+  const int fv = f >> 3;
+  const long long total = T * fv;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / fv;
+    const int v = (int)(i - t * fv);
+    const uint4* row = reinterpret_cast<const uint4*>(gu + t * 2 * f);
+    float g[8], u[8], d[8], dg[8], du[8];
+    unpack8(row[v], g);
+    unpack8(row[fv + v], u);
+    unpack8(reinterpret_cast<const uint4*>(dact + t * f)[v], d);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float sg = 1.f / (1.f + __expf(-g[j]));
+      const float silu = g[j] * sg;
+      dg[j] = d[j] * u[j] * (sg + silu * (1.f - sg));
+      du[j] = d[j] * silu;
+    }
+    uint4* orow = reinterpret_cast<uint4*>(dgu + t * 2 * f);
+    orow[v] = pack8(dg);
+    orow[fv + v] = pack8(du);
+  }
+}
+
+__global__ void embed_fwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ W,
+                                 __nv_bfloat16* __restrict__ out, long long T, int h, int vocab) {
+  const int hv = h >> 3;
+  const long long total = T * hv;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / hv;
+    const int v = (int)(i - t * hv);
+    long long id = ids[t];
+    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+    reinterpret_cast<uint4*>(out + t * h)[v] = reinterpret_cast<const uint4*>(W + id * h)[v];
+  }
+}
+
+// dW[ids[t], :] += dout[t, :]   (fp32 gradient buffer, atomics: rows repeat)
+__global__ void embed_bwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ dout,
+                                 float* __restrict__ dW, long long T, int h, int vocab) {
+  const int hv = h >> 3;
+  const long long total = T * hv;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / hv;
+    const int v = (int)(i - t * hv);
+    long long id = ids[t];
+    if (id < 0 || id >= vocab) continue;
+    float d[8];
+    unpack8(reinterpret_cast<const uint4*>(dout + t * h)[v], d);
+    float* dst = dW + id * h + (long long)v * 8;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) atomicAdd(dst + j, d[j]);
+  }
+}
+
+// bf16 <-> fp32 conversions over flat buffers (n elements), with optional scale / accumulate.
+__global__ void cast_f32_to_bf16_kernel(const float* __restrict__ in, __nv_bfloat16* __restrict__ out, long long n,
+                                        float scale) {
+  const long long nv = n >> 3;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nv;
+       i += (long long)gridDim.x * blockDim.x) {
+    const float4 a = reinterpret_cast<const float4*>(in)[2 * i];
+    const float4 b = reinterpret_cast<const float4*>(in)[2 * i + 1];
+    float f[8] = {a.x * scale, a.y * scale, a.z * scale, a.w * scale, b.x * scale, b.y * scale, b.z * scale, b.w * scale};
+    reinterpret_cast<uint4*>(out)[i] = pack8(f);
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0)
+    for (long long i = nv << 3; i < n; ++i) out[i] = __float2bfloat16(in[i] * scale);
+}
+__global__ void cast_bf16_to_f32_kernel(const __nv_bfloat16* __restrict__ in, float* __restrict__ out, long long n,
+                                        float scale, int accumulate) {
+  const long long nv = n >> 3;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nv;
+       i += (long long)gridDim.x * blockDim.x) {
+    float f[8];
+    unpack8(reinterpret_cast<const uint4*>(in)[i], f);
+    float4 a = make_float4(f[0] * scale, f[1] * scale, f[2] * scale, f[3] * scale);
+    float4 b = make_float4(f[4] * scale, f[5] * scale, f[6] * scale, f[7] * scale);
+    if (accumulate) {
+      const float4 oa = reinterpret_cast<float4*>(out)[2 * i], ob = reinterpret_cast<float4*>(out)[2 * i + 1];
+      a.x += oa.x; a.y += oa.y; a.z += oa.z; a.w += oa.w;
+      b.x += ob.x; b.y += ob.y; b.z += ob.z; b.w += ob.w;
+    }
+    reinterpret_cast<float4*>(out)[2 * i] = a;
+    reinterpret_cast<float4*>(out)[2 * i + 1] = b;
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0)
+    for (long long i = nv << 3; i < n; ++i) {
+      const float v = __bfloat162float(in[i]) * scale;
+      out[i] = accumulate ? out[i] + v : v;
+    }
+}
+
+static inline int grid_for(long long work_items, int threads, int per_sm = 8) {
+  long long b = (work_items + threads - 1) / threads;
+  const long long cap = (long long)sm_count() * per_sm;
+  if (b > cap) b = cap;
+  if (b < 1) b = 1;
+  return (int)b;
+}
+
+}  // namespace ew
+}  // namespace b200
+
+extern "C" {
+using namespace b200;
+using namespace b200::ew;
+
+// Number of fp32 partial rows rmsnorm_bwd needs in `dw_partial` ([blocks, h]).
+int b200_rmsnorm_bwd_blocks(int rows) {
+  const int cap = sm_count() * 2;
+  return rows < cap ? rows : cap;
+}
+
+int b200_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* hout, float* rstd, int rows, int h,
+                     float eps, cudaStream_t st) {
+  if (!x || !w || !y || rows <= 0 || (h & 7) || h > NT * MAX_VEC * 8) return B200_ERR_ARG;
+  const int grid = rows < sm_count() * 8 ? rows : sm_count() * 8;
+  rmsnorm_fwd_kernel<<<grid, NT, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)res, (const __nv_bfloat16*)w,
+                                          (__nv_bfloat16*)y, (__nv_bfloat16*)hout, rstd, rows, h, eps);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200_OK;
+}
+
+// dw_out (+)= column sums; dw_partial is scratch of b200_rmsnorm_bwd_blocks(rows) * h floats.
+int b200_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dres, void* dx,
+                     float* dw_partial, float* dw_out, int dw_accumulate, int rows, int h, cudaStream_t st) {
+  if (!dy || !x || !w || !rstd || !dx || !dw_partial || !dw_out || rows <= 0 || (h & 7) || h > NT * MAX_VEC * 8)
+    return B200_ERR_ARG;
+  const int grid = b200_rmsnorm_bwd_blocks(rows);
+  rmsnorm_bwd_kernel<<<grid, NT, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
+                                          rstd, (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, dw_partial, rows, h);
+  B200_CUDA_CHECK(cudaGetLastError());
+  colsum_kernel<<<ceil_div(h, 128), 128, 0, st>>>(dw_partial, dw_out, grid, h, dw_accumulate);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200_OK;
+}
+
+int b200_rope(void* x, const int* pos, const float* cos_tab, const float* sin_tab, long long T, int nh, int d,
+              long long row_stride, int inverse, cudaStream_t st) {
+  if (!x || !pos || !cos_tab || !sin_tab || T <= 0 || (d & 3)) return B200_ERR_ARG;
+  const long long total = T * nh * (d >> 2);
+  rope_kernel<<<grid_for(total, 256), 256, 0, st>>>((__nv_bfloat16*)x, pos, cos_tab, sin_tab, T, nh, d, row_stride,
+                                                   inverse ? -1.f : 1.f);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200_OK;
+}
+
+int b200_swiglu_fwd(const void* gu, void* act, long long T, int f, cudaStream_t st) {
+  if (!gu || !act || T <= 0 || (f & 7)) return B200_ERR_ARG;
+  swiglu_fwd_kernel<<<grid_for(T * (f >> 3), 256), 256, 0, st>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)act, T, f);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200_OK;
+}
+
+int b200_swiglu_bwd(const void* gu, const void* dact, void* dgu, long long T, int f, cudaStream_t st) {
+  if (!gu || !dact || !dgu || T <= 0 || (f & 7)) return B200_ERR_ARG;
+  swiglu_bwd_kernel<<<grid_for(T * (f >> 3), 256), 256, 0, st>>>((const __nv_bfloat16*)gu, (const __nv_bfloat16*)dact,
+                                                                (__nv_bfloat16*)dgu, T, f);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200_OK;
+}
+
+int b200_embed_fwd(const long long* ids, const void* W, void* out, long long T, int h, int vocab, cudaStream_t st) {
+  if (!ids || !W || !out || T <= 0 || (h & 7)) return B200_ERR_ARG;
+  embed_fwd_kernel<<<grid_for(T * (h >> 3), 256), 256, 0, st>>>(ids, (const __nv_bfloat16*)W, (__nv_bfloat16*)out, T, h,
+                                                               vocab);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200_OK;
+}
+
+int b200_embed_bwd(const long long* ids, const void* dout, float* dW, long long T, int h, int vocab, cudaStream_t st) {
+  if (!ids || !dout || !dW || T <= 0 || (h & 7)) return B200_ERR_ARG;
+  embed_bwd_kernel<<<grid_for(T * (h >> 3), 256), 256, 0, st>>>(ids, (const __nv_bfloat16*)dout, dW, T, h, vocab);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200_OK;
+}
+
+int b200_cast_f32_to_bf16(const float* in, void* out, long long n, float scale, cudaStream_t st) {
+  if (!in || !out || n <= 0) return B200_ERR_ARG;
+  if ((reinterpret_cast<uintptr_t>(in) & 15) || (reinterpret_cast<uintptr_t>(out) & 15)) return B200_ERR_ARG;
+  cast_f32_to_bf16_kernel<<<grid_for(n >> 3, 256), 256, 0, st>>>(in, (__nv_bfloat16*)out, n, scale);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200_OK;
+}
+
+int b200_cast_bf16_to_f32(const void* in, float* out, long long n, float scale, int accumulate, cudaStream_t st) {
+  if (!in || !out || n <= 0) return B200_ERR_ARG;
+  if ((reinterpret_cast<uintptr_t>(in) & 15) || (reinterpret_cast<uintptr_t>(out) & 15)) return B200_ERR_ARG;
+  cast_bf16_to_f32_kernel<<<grid_for(n >> 3, 256), 256, 0, st>>>((const __nv_bfloat16*)in, out, n, scale, accumulate);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200_OK;
+}
+}

@@ -1,0 +1,250 @@
+"""Low-level ops: each function runs the sm_100a kernel when its tensors are on a CUDA device and the
+plain-PyTorch restatement (the test oracle, also the CPU plumbing path) otherwise. There is no silent
+fallback on a GPU: if the native library cannot be loaded the call raises.
+
+Shapes use T = tokens (batch*seq flattened), h = hidden, f = FFN width.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_void_p
+
+import torch
+import torch.nn.functional as F
+
+from . import _lib
+
+_BF16 = torch.bfloat16
+
+
+def _native(*ts: torch.Tensor) -> bool:
+    return any(t is not None and t.is_cuda for t in ts)
+
+
+def _fmt(dtype: torch.dtype) -> int:
+    if dtype == torch.bfloat16:
+        return 1
+    if dtype == torch.float16:
+        return 0
+    raise TypeError(f"tensor-core GEMM operands must be bf16 or fp16, got {dtype}")
+
+
+# ------------------------------------------------------------------------------------------------ GEMM
+def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, out: torch.Tensor | None = None,
+         out_dtype: torch.dtype | None = None, accumulate: bool = False, alpha: float = 1.0,
+         residual: torch.Tensor | None = None, desc_cfg: list[int] | None = None) -> torch.Tensor:
+    """C[M,N] = alpha * A @ B^T (+ C) (+ residual).
+
+    ``a`` is [M,K] (``a_mn=False``) or stored transposed as [K,M] (``a_mn=True``); ``b`` is [N,K] or stored as [K,N].
+    Rows must be contiguous (stride(1) == 1); row strides must be multiples of 8 elements.
+    """
+    if a_mn:
+        K, M = a.shape
+    else:
+        M, K = a.shape
+    if b_mn:
+        Kb, N = b.shape
+    else:
+        N, Kb = b.shape
+    if K != Kb:
+        raise ValueError(f"gemm: reduction dims differ ({K} vs {Kb})")
+    out_dtype = out_dtype or (out.dtype if out is not None else a.dtype)
+    if out is None:
+        if accumulate:
+            raise ValueError("gemm: accumulate=True needs out")
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    if not _native(a, b):
+        A = (a.t() if a_mn else a).float()
+        B = (b if b_mn else b.t()).float()
+        r = alpha * (A @ B)
+        if residual is not None:
+            r = r + residual.float()
+        if accumulate:
+            r = r + out.float()
+        out.copy_(r.to(out.dtype))
+        return out
+    if a.stride(-1) != 1 or b.stride(-1) != 1 or out.stride(-1) != 1:
+        raise ValueError("gemm: innermost stride must be 1")
+    if a.dtype != b.dtype:
+        raise TypeError("gemm: operand dtypes differ")
+    fmt = _fmt(a.dtype)
+    out_f32 = 1 if out.dtype == torch.float32 else 0
+    if not out_f32 and out.dtype != a.dtype:
+        raise TypeError("gemm: 16-bit output must match the operand dtype")
+    if residual is not None and (residual.dtype != _BF16 or residual.stride(-1) != 1):
+        raise TypeError("gemm: residual must be bf16 with contiguous rows")
+    cfg = None
+    if desc_cfg is not None:
+        cfg = (ctypes.c_uint * 6)(*desc_cfg)
+    rc = _lib.kernels().b200_gemm(
+        _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), M, N, K, a.stride(0), b.stride(0), out.stride(0), int(a_mn), int(b_mn),
+        fmt, out_f32, int(accumulate), float(alpha), _lib.ptr(residual), residual.stride(0) if residual is not None else 0,
+        ctypes.cast(cfg, c_void_p) if cfg is not None else c_void_p(0), _lib.stream())
+    _lib.check(rc, "b200_gemm")
+    return out
+
+
+def linear_fwd(x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
+    """y[T,N] = x[T,K] @ w[N,K]^T (+ residual)."""
+    return gemm(x, w, residual=residual)
+
+
+def linear_dgrad(dy: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """dx[T,K] = dy[T,N] @ w[N,K]  (w is read as an MN-major B operand: no transpose copy)."""
+    return gemm(dy, w, b_mn=True)
+
+
+def linear_wgrad(dy: torch.Tensor, x: torch.Tensor, out: torch.Tensor | None = None, accumulate: bool = False,
+                 out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """dW[N,K] (+)= dy[T,N]^T @ x[T,K]  (both operands MN-major)."""
+    return gemm(dy, x, a_mn=True, b_mn=True, out=out, accumulate=accumulate, out_dtype=out_dtype)
+
+
+# ------------------------------------------------------------------------------------------------ RMSNorm
+def rmsnorm_fwd(x: torch.Tensor, w: torch.Tensor, eps: float, residual: torch.Tensor | None = None):
+    """Returns (y, h, rstd): h = x + residual (or x itself), y = h * rsqrt(mean(h^2) + eps) * w."""
+    rows, hdim = x.shape
+    if not _native(x):
+        h = x if residual is None else (x.float() + residual.float()).to(x.dtype)
+        hf = h.float()
+        rstd = torch.rsqrt(hf.pow(2).mean(-1) + eps)
+        y = (hf * rstd[:, None] * w.float()).to(x.dtype)
+        return y, h, rstd
+    y = torch.empty_like(x)
+    h = torch.empty_like(x) if residual is not None else x
+    rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+    rc = _lib.kernels().b200_rmsnorm_fwd(_lib.ptr(x), _lib.ptr(residual), _lib.ptr(w), _lib.ptr(y),
+                                         _lib.ptr(h if residual is not None else None), _lib.ptr(rstd), rows, hdim,
+                                         float(eps), _lib.stream())
+    _lib.check(rc, "b200_rmsnorm_fwd")
+    return y, h, rstd
+
+
+def rmsnorm_bwd(dy: torch.Tensor, h: torch.Tensor, w: torch.Tensor, rstd: torch.Tensor,
+                dres: torch.Tensor | None = None, dw_out: torch.Tensor | None = None, dw_accumulate: bool = False):
+    """Returns (dh, dw). dh includes ``dres`` (gradient arriving through the residual branch) when given.
+    ``dw_out`` (fp32 [h]) is written or accumulated in place when supplied."""
+    rows, hdim = h.shape
+    if not _native(h):
+        xh = h.float() * rstd[:, None]
+        g = dy.float() * w.float()
+        c = (g * xh).mean(-1, keepdim=True)
+        dh = rstd[:, None] * (g - xh * c)
+        if dres is not None:
+            dh = dh + dres.float()
+        dw = (dy.float() * xh).sum(0)
+        if dw_out is not None:
+            dw_out.copy_(dw_out + dw if dw_accumulate else dw)
+            dw = dw_out
+        return dh.to(h.dtype), dw
+    dh = torch.empty_like(h)
+    nblk = _lib.kernels().b200_rmsnorm_bwd_blocks(rows)
+    partial = torch.empty((nblk, hdim), dtype=torch.float32, device=h.device)
+    if dw_out is None:
+        dw_out = torch.empty(hdim, dtype=torch.float32, device=h.device)
+        dw_accumulate = False
+    rc = _lib.kernels().b200_rmsnorm_bwd(_lib.ptr(dy), _lib.ptr(h), _lib.ptr(w), _lib.ptr(rstd), _lib.ptr(dres),
+                                         _lib.ptr(dh), _lib.ptr(partial), _lib.ptr(dw_out), int(dw_accumulate), rows,
+                                         hdim, _lib.stream())
+    _lib.check(rc, "b200_rmsnorm_bwd")
+    return dh, dw_out
+
+
+# ------------------------------------------------------------------------------------------------ RoPE
+def rope_tables(max_pos: int, head_dim: int, theta: float, device) -> tuple[torch.Tensor, torch.Tensor]:
+    """fp32 cos/sin tables [max_pos, head_dim/2] (HF Llama convention: pairs (i, i + d/2))."""
+    inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32, device=device) / head_dim))
+    ang = torch.arange(max_pos, dtype=torch.float32, device=device)[:, None] * inv[None, :]
+    return ang.cos().contiguous(), ang.sin().contiguous()
+
+
+def rope_(x: torch.Tensor, pos: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, n_heads: int, head_dim: int,
+          inverse: bool = False) -> torch.Tensor:
+    """Rotate x[T, >= n_heads*head_dim] in place (only the first n_heads*head_dim columns of each row).
+    ``pos`` is int32 [T]. ``inverse=True`` applies the transposed rotation (the backward pass)."""
+    T = x.shape[0]
+    if not _native(x):
+        half = head_dim // 2
+        v = x[:, : n_heads * head_dim].reshape(T, n_heads, head_dim).float()
+        c = cos[pos.long()][:, None, :]
+        s = sin[pos.long()][:, None, :] * (-1.0 if inverse else 1.0)
+        a, b = v[..., :half], v[..., half:]
+        out = torch.cat([a * c - b * s, b * c + a * s], dim=-1)
+        x[:, : n_heads * head_dim] = out.reshape(T, n_heads * head_dim).to(x.dtype)
+        return x
+    if x.stride(-1) != 1 or pos.dtype != torch.int32:
+        raise ValueError("rope_: x rows must be contiguous and pos int32")
+    rc = _lib.kernels().b200_rope(_lib.ptr(x), _lib.ptr(pos), _lib.ptr(cos), _lib.ptr(sin), T, n_heads, head_dim,
+                                  x.stride(0), int(inverse), _lib.stream())
+    _lib.check(rc, "b200_rope")
+    return x
+
+
+# ------------------------------------------------------------------------------------------------ SwiGLU
+def swiglu_fwd(gu: torch.Tensor) -> torch.Tensor:
+    """act[T,f] = silu(gu[:, :f]) * gu[:, f:]"""
+    T, f2 = gu.shape
+    f = f2 // 2
+    if not _native(gu):
+        g, u = gu[:, :f].float(), gu[:, f:].float()
+        return (F.silu(g) * u).to(gu.dtype)
+    act = torch.empty((T, f), dtype=gu.dtype, device=gu.device)
+    _lib.check(_lib.kernels().b200_swiglu_fwd(_lib.ptr(gu), _lib.ptr(act), T, f, _lib.stream()), "b200_swiglu_fwd")
+    return act
+
+
+def swiglu_bwd(gu: torch.Tensor, dact: torch.Tensor) -> torch.Tensor:
+    T, f2 = gu.shape
+    f = f2 // 2
+    if not _native(gu):
+        g, u, d = gu[:, :f].float(), gu[:, f:].float(), dact.float()
+        sg = torch.sigmoid(g)
+        silu = g * sg
+        return torch.cat([d * u * (sg + silu * (1 - sg)), d * silu], dim=1).to(gu.dtype)
+    dgu = torch.empty_like(gu)
+    _lib.check(_lib.kernels().b200_swiglu_bwd(_lib.ptr(gu), _lib.ptr(dact), _lib.ptr(dgu), T, f, _lib.stream()),
+               "b200_swiglu_bwd")
+    return dgu
+
+
+# ------------------------------------------------------------------------------------------------ embedding
+def embed_fwd(ids: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """out[T,h] = w[ids]; ids int64 [T]."""
+    if not _native(w):
+        return w[ids.clamp(0, w.shape[0] - 1)]
+    T = ids.numel()
+    out = torch.empty((T, w.shape[1]), dtype=w.dtype, device=w.device)
+    _lib.check(_lib.kernels().b200_embed_fwd(_lib.ptr(ids), _lib.ptr(w), _lib.ptr(out), T, w.shape[1], w.shape[0],
+                                             _lib.stream()), "b200_embed_fwd")
+    return out
+
+
+def embed_bwd(ids: torch.Tensor, dout: torch.Tensor, dw: torch.Tensor) -> torch.Tensor:
+    """dw[ids[t]] += dout[t]   (dw fp32 [V,h], accumulated in place)."""
+    if not _native(dw):
+        dw.index_add_(0, ids, dout.float())
+        return dw
+    T = ids.numel()
+    _lib.check(_lib.kernels().b200_embed_bwd(_lib.ptr(ids), _lib.ptr(dout), _lib.ptr(dw), T, dw.shape[1], dw.shape[0],
+                                             _lib.stream()), "b200_embed_bwd")
+    return dw
+
+
+# ------------------------------------------------------------------------------------------------ casts
+def cast_to_bf16(src_f32: torch.Tensor, dst_bf16: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    if not _native(src_f32):
+        dst_bf16.copy_((src_f32 * scale).to(dst_bf16.dtype))
+        return dst_bf16
+    _lib.check(_lib.kernels().b200_cast_f32_to_bf16(_lib.ptr(src_f32), _lib.ptr(dst_bf16), src_f32.numel(), float(scale),
+                                                    _lib.stream()), "b200_cast_f32_to_bf16")
+    return dst_bf16
+
+
+def cast_to_f32(src_bf16: torch.Tensor, dst_f32: torch.Tensor, scale: float = 1.0, accumulate: bool = False):
+    if not _native(src_bf16):
+        v = src_bf16.float() * scale
+        dst_f32.copy_(dst_f32 + v if accumulate else v)
+        return dst_f32
+    _lib.check(_lib.kernels().b200_cast_bf16_to_f32(_lib.ptr(src_bf16), _lib.ptr(dst_f32), src_bf16.numel(), float(scale),
+                                                    int(accumulate), _lib.stream()), "b200_cast_bf16_to_f32")
+    return dst_f32
