@@ -79,7 +79,10 @@ def register(name: str, argtypes: list) -> None:
     """Declare the signature of one more exported launcher (used by ops modules that own their kernels)."""
     _SIGS[name] = argtypes
     if _KERNELS is not None:
-        fn = getattr(_KERNELS, name)
+        try:
+            fn = getattr(_KERNELS, name)
+        except AttributeError:  # declared by Python but not built into the library yet: calling it will raise
+            return
         fn.argtypes = argtypes
         fn.restype = c_int
 

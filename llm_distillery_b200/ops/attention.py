@@ -1,0 +1,77 @@
+"""Causal grouped-query attention over the fused QKV activation.
+
+Layout: ``qkv`` is [T, (H + 2*Hkv) * d] with T = B * L tokens (sequence-major inside each batch row); columns
+[0, H*d) hold Q, then K, then V. Output is [T, H*d]; ``lse`` is fp32 [H, T] (log-sum-exp of the scaled scores,
+natural log), the only statistic the backward pass needs.
+
+CUDA tensors run the sm_100a flash-attention kernels (csrc/ops/flash_attn.cu); CPU tensors run the plain
+restatement below, which is also the oracle of the GPU tests.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import _lib
+
+
+def _split(qkv: torch.Tensor, B: int, L: int, H: int, Hkv: int, d: int):
+    q = qkv[:, : H * d].reshape(B, L, H, d)
+    k = qkv[:, H * d: (H + Hkv) * d].reshape(B, L, Hkv, d)
+    v = qkv[:, (H + Hkv) * d:].reshape(B, L, Hkv, d)
+    return q, k, v
+
+
+def attention_reference_fwd(qkv, B, L, H, Hkv, d):
+    q, k, v = _split(qkv.float(), B, L, H, Hkv, d)
+    g = H // Hkv
+    k = k.repeat_interleave(g, dim=2)
+    v = v.repeat_interleave(g, dim=2)
+    s = torch.einsum("blhd,bmhd->bhlm", q, k) / math.sqrt(d)
+    mask = torch.ones(L, L, dtype=torch.bool, device=qkv.device).tril()
+    s = s.masked_fill(~mask, float("-inf"))
+    lse = torch.logsumexp(s, dim=-1)  # [B,H,L]
+    p = torch.exp(s - lse[..., None])
+    o = torch.einsum("bhlm,bmhd->blhd", p, v).reshape(B * L, H * d)
+    return o.to(qkv.dtype), lse.permute(1, 0, 2).reshape(H, B * L).contiguous()
+
+
+def attention_reference_bwd(dout, qkv, out, lse, B, L, H, Hkv, d):
+    q, k, v = _split(qkv.float(), B, L, H, Hkv, d)
+    g = H // Hkv
+    kk = k.repeat_interleave(g, dim=2)
+    vv = v.repeat_interleave(g, dim=2)
+    do = dout.float().reshape(B, L, H, d)
+    o = out.float().reshape(B, L, H, d)
+    scale = 1.0 / math.sqrt(d)
+    s = torch.einsum("blhd,bmhd->bhlm", q, kk) * scale
+    mask = torch.ones(L, L, dtype=torch.bool, device=qkv.device).tril()
+    s = s.masked_fill(~mask, float("-inf"))
+    p = torch.exp(s - lse.reshape(H, B, L).permute(1, 0, 2)[..., None])
+    dv = torch.einsum("bhlm,blhd->bmhd", p, do)
+    dp = torch.einsum("blhd,bmhd->bhlm", do, vv)
+    delta = (do * o).sum(-1).permute(0, 2, 1)  # [B,H,L]
+    ds = p * (dp - delta[..., None]) * scale
+    dq = torch.einsum("bhlm,bmhd->blhd", ds, kk)
+    dk = torch.einsum("bhlm,blhd->bmhd", ds, q)
+    dk = dk.reshape(B, L, Hkv, g, d).sum(3)
+    dv = dv.reshape(B, L, Hkv, g, d).sum(3)
+    dqkv = torch.cat([dq.reshape(B * L, H * d), dk.reshape(B * L, Hkv * d), dv.reshape(B * L, Hkv * d)], dim=1)
+    return dqkv.to(qkv.dtype)
+
+
+def attention_fwd(qkv: torch.Tensor, B: int, L: int, H: int, Hkv: int, d: int):
+    """Returns (out [T, H*d], lse [H, T] fp32)."""
+    if not qkv.is_cuda:
+        return attention_reference_fwd(qkv, B, L, H, Hkv, d)
+    from . import flash
+    return flash.flash_attn_fwd(qkv, B, L, H, Hkv, d)
+
+
+def attention_bwd(dout, qkv, out, lse, B, L, H, Hkv, d):
+    """Returns dqkv with the layout of qkv."""
+    if not qkv.is_cuda:
+        return attention_reference_bwd(dout, qkv, out, lse, B, L, H, Hkv, d)
+    from . import flash
+    return flash.flash_attn_bwd(dout, qkv, out, lse, B, L, H, Hkv, d)

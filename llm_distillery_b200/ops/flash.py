@@ -1,0 +1,33 @@
+"""Bindings of the sm_100a flash-attention kernels (csrc/ops/flash_attn_fwd.cu, flash_attn_bwd.cu)."""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from ._lib import _VP, _I
+
+_lib.register("b200_flash_attn_fwd", [_VP, _VP, _VP, _I, _I, _I, _I, _I, _VP])
+_lib.register("b200_flash_attn_bwd", [_VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _VP])
+
+
+def flash_attn_fwd(qkv: torch.Tensor, B: int, L: int, H: int, Hkv: int, d: int):
+    if qkv.dtype != torch.bfloat16 or not qkv.is_contiguous():
+        raise TypeError("flash_attn_fwd: qkv must be contiguous bf16")
+    T = B * L
+    out = torch.empty((T, H * d), dtype=qkv.dtype, device=qkv.device)
+    lse = torch.empty((H, T), dtype=torch.float32, device=qkv.device)
+    rc = _lib.kernels().b200_flash_attn_fwd(_lib.ptr(qkv), _lib.ptr(out), _lib.ptr(lse), B, L, H, Hkv, d, _lib.stream())
+    _lib.check(rc, "b200_flash_attn_fwd")
+    return out, lse
+
+
+def flash_attn_bwd(dout, qkv, out, lse, B, L, H, Hkv, d):
+    if not dout.is_contiguous():
+        dout = dout.contiguous()
+    dqkv = torch.empty_like(qkv)
+    # delta[h, t] = sum_d dout * out, computed inside the launcher's pre-pass
+    delta = torch.empty_like(lse)
+    rc = _lib.kernels().b200_flash_attn_bwd(_lib.ptr(dout), _lib.ptr(qkv), _lib.ptr(out), _lib.ptr(lse), _lib.ptr(delta),
+                                            _lib.ptr(dqkv), B, L, H, Hkv, d, _lib.stream())
+    _lib.check(rc, "b200_flash_attn_bwd")
+    return dqkv

@@ -1,0 +1,71 @@
+"""tcgen05 GEMM (all three operand layouts, epilogue options) against fp32 PyTorch matmul."""
+import pytest
+import torch
+
+from llm_distillery_b200.ops import basic, _lib
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _ref(a, b, a_mn, b_mn):
+    A = (a.t() if a_mn else a).float()
+    B = (b if b_mn else b.t()).float()
+    return A @ B
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 128, 128), (384, 640, 200), (1000, 1000, 1000), (2048, 2560, 2048),
+                                   (130, 72, 8)])
+def test_gemm_layouts(M, N, K, a_mn, b_mn):
+    torch.manual_seed(M * 7 + N * 3 + K)
+    if (a_mn and M % 8) or (b_mn and N % 8):
+        pytest.skip("MN-major operands need a 16-byte aligned row stride")
+    a = torch.randn((K, M) if a_mn else (M, K), device=DEV).bfloat16()
+    b = torch.randn((K, N) if b_mn else (N, K), device=DEV).bfloat16()
+    out = basic.gemm(a, b, a_mn=a_mn, b_mn=b_mn)
+    assert _lib.take_device_error() == 0
+    r = _ref(a, b, a_mn, b_mn)
+    tol = 1e-2 * max(1.0, r.abs().max().item())
+    assert (out.float() - r).abs().max().item() <= tol
+
+
+def test_gemm_epilogues():
+    torch.manual_seed(5)
+    a = torch.randn(300, 136, device=DEV).bfloat16()
+    b = torch.randn(520, 136, device=DEV).bfloat16()
+    r = a.float() @ b.float().t()
+    # fp32 output, overwrite then accumulate
+    c = torch.empty(300, 520, device=DEV)
+    basic.gemm(a, b, out=c)
+    assert torch.allclose(c, r, atol=1e-3, rtol=1e-3)
+    basic.gemm(a, b, out=c, accumulate=True, alpha=0.5)
+    assert torch.allclose(c, 1.5 * r, atol=2e-3, rtol=1e-3)
+    # bf16 accumulate and residual
+    rsd = torch.randn(300, 520, device=DEV).bfloat16()
+    o = basic.gemm(a, b, residual=rsd)
+    assert torch.allclose(o.float(), (r + rsd.float()), atol=0.15, rtol=2e-2)
+    # fp16 operands
+    o16 = basic.gemm(a.half(), b.half())
+    assert torch.allclose(o16.float(), a.half().float() @ b.half().float().t(), atol=0.1, rtol=1e-2)
+    # strided (row-padded) operands and output
+    big = torch.randn(300, 256, device=DEV).bfloat16()
+    outbig = torch.zeros(300, 1024, device=DEV, dtype=torch.bfloat16)
+    basic.gemm(big[:, :136], b, out=outbig[:, 8:528])
+    assert torch.allclose(outbig[:, 8:528].float(), big[:, :136].float() @ b.float().t(), atol=0.15, rtol=2e-2)
+    assert outbig[:, :8].abs().max() == 0 and outbig[:, 528:].abs().max() == 0
+    assert _lib.take_device_error() == 0
+
+
+def test_linear_helpers_match_autograd():
+    torch.manual_seed(6)
+    x = torch.randn(512, 256, device=DEV).bfloat16()
+    w = torch.randn(384, 256, device=DEV).bfloat16() * 0.05
+    dy = torch.randn(512, 384, device=DEV).bfloat16()
+    xf, wf = x.float().requires_grad_(), w.float().requires_grad_()
+    (xf @ wf.t()).backward(dy.float())
+    assert torch.allclose(basic.linear_fwd(x, w).float(), (x.float() @ w.float().t()), atol=5e-2, rtol=2e-2)
+    assert torch.allclose(basic.linear_dgrad(dy, w).float(), xf.grad, atol=5e-2, rtol=2e-2)
+    g = torch.zeros(384, 256, device=DEV)
+    basic.linear_wgrad(dy, x, out=g, accumulate=True)
+    assert torch.allclose(g, wf.grad, atol=0.5, rtol=2e-2)
