@@ -1,0 +1,442 @@
+// Causal GQA flash-attention backward for sm_100a on tcgen05 tensor cores.
+//
+// One CTA owns one (batch, kv-head, 128-key block): K_j and V_j stay resident in shared memory, dK_j and dV_j
+// accumulate in TMEM over every query head of the group and every query block at or after the diagonal, and
+// are written once. dQ is produced per (query block, key block) pair and reduced into an fp32 buffer with
+// vector red.global.add (the same scheme as FlashAttention-2), then converted to bf16 by a small kernel.
+//
+// Per iteration (query head hq, query block i), five tcgen05.mma groups:
+//   S  = Q_i K_j^T                 (A K-major, B K-major)        -> TMEM
+//   dP = dO_i V_j^T                (A K-major, B K-major)        -> TMEM
+//   softmax warps: P = exp2(S*c - lse), dS = P * (dP - delta) * scale, both written to smem in bf16
+//   dV += P^T  dO_i                (A = P  read MN-major, B = dO MN-major)
+//   dK += dS^T Q_i                 (A = dS read MN-major, B = Q  MN-major)
+//   dQ  = dS   K_j                 (A = dS K-major,       B = K  MN-major)
+// A [q x k] tile written row-per-thread in the 128B-swizzled K-major layout is, byte for byte, also the
+// MN-major layout of its transpose, so P and dS are stored once and read both ways.
+//
+// Roles: warp 0 TMA producer (Q_i / dO_i ring), warp 1 MMA issuer, warps 2-5 softmax + dQ drain + epilogue.
+#include "../common/ptx.cuh"
+#include "../common/host.cuh"
+
+namespace b200 {
+namespace fab {
+
+constexpr int BM = 128;  // queries per block
+constexpr int BN = 128;  // keys per block
+constexpr int NTHREADS = 192;
+
+template <int D>
+struct Cfg {
+  static constexpr int STAGES = (D == 64) ? 2 : 1;
+  static constexpr int KV_BYTES = BN * D * 2;   // one of K or V
+  static constexpr int QDO_BYTES = BM * D * 2;  // one of Q or dO
+  static constexpr int STAGE_BYTES = 2 * QDO_BYTES;
+  static constexpr int P_BYTES = BM * BN * 2;
+  static constexpr int OFF_K = 0;
+  static constexpr int OFF_V = KV_BYTES;
+  static constexpr int OFF_QDO = 2 * KV_BYTES;
+  static constexpr int OFF_P = OFF_QDO + STAGES * STAGE_BYTES;
+  static constexpr int OFF_DS = OFF_P + P_BYTES;
+  static constexpr int OFF_BAR = OFF_DS + P_BYTES;
+  static constexpr int SMEM_BYTES = OFF_BAR + 256;
+  static constexpr bool ALIAS = (D == 128);  // dQ shares TMEM columns with S
+  static constexpr uint32_t S_COL = 0;
+  static constexpr uint32_t DP_COL = 128;
+  static constexpr uint32_t DV_COL = 256;
+  static constexpr uint32_t DK_COL = 256 + D;
+  static constexpr uint32_t DQ_COL = ALIAS ? 0 : 256 + 2 * D;
+  static constexpr uint32_t TMEM_COLS = 512;
+};
+
+struct BwdParams {
+  const float* lse;    // [H, T]
+  const float* delta;  // [H, T]
+  float* dq_acc;       // [T, H*D] fp32, zeroed by the launcher
+  __nv_bfloat16* dqkv; // [T, (H+2Hkv)*D]
+  int B, L, H, Hkv;
+  float scale;
+};
+
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
+               : "memory");
+}
+
+template <int D>
+__global__ void __launch_bounds__(NTHREADS, 1)
+    flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmDO, BwdParams p,
+                     unsigned int* err_word) {
+  using C = Cfg<D>;
+  constexpr int ST = C::STAGES;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
+  uint64_t* kv_full = bars + 0;
+  uint64_t* qdo_full = bars + 1;   // [2]
+  uint64_t* qdo_empty = bars + 3;  // [2]
+  uint64_t* sdp_full = bars + 5;
+  uint64_t* pds_ready = bars + 6;
+  uint64_t* dq_full = bars + 7;
+  uint64_t* dq_empty = bars + 8;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nkb = (p.L + BN - 1) / BN;
+  const int jb = blockIdx.x;  // key block; block 0 has the most work and is scheduled first
+  const int hkv = blockIdx.y, b = blockIdx.z;
+  const int g = p.H / p.Hkv;
+  const int kv0 = jb * BN;
+  const int nqb = (p.L + BM - 1) / BM;
+  const int i_start = kv0 / BM;
+  const int nqi = nqb - i_start;
+  const int n_it = g * nqi;
+  const long long T = (long long)p.B * p.L;
+  (void)nkb;
+
+  if ((smem_u32(smem) & 1023u) != 0u) {
+    if (threadIdx.x == 0 && err_word) atomicCAS(err_word, 0u, (unsigned)ERR_BAD_ARG);
+    return;
+  }
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmQKV);
+    tma_prefetch_desc(&tmDO);
+    mbar_init(kv_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&qdo_full[s], 1);
+      mbar_init(&qdo_empty[s], 1);
+    }
+    mbar_init(sdp_full, 1);
+    mbar_init(pds_ready, 128);
+    mbar_init(dq_full, 1);
+    mbar_init(dq_empty, 128);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int colK = p.H * D + hkv * D;
+  const int colV = (p.H + p.Hkv) * D + hkv * D;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_arrive_expect_tx(kv_full, 2 * C::KV_BYTES);
+#pragma unroll
+      for (int c = 0; c < D / 64; ++c) {
+        tma_load_3d(smem + C::OFF_K + c * (BN * 128), &tmQKV, kv_full, colK + c * 64, kv0, b);
+        tma_load_3d(smem + C::OFF_V + c * (BN * 128), &tmQKV, kv_full, colV + c * 64, kv0, b);
+      }
+      for (int it = 0; it < n_it; ++it) {
+        const int s = it % ST;
+        const uint32_t ph = (it / ST) & 1u;
+        const int hq = hkv * g + it / nqi;
+        const int q0 = (i_start + it % nqi) * BM;
+        if (!mbar_wait_bounded(&qdo_empty[s], ph ^ 1u, abort_flag, err_word, ERR_WAIT_EMPTY)) break;
+        uint8_t* sQ = smem + C::OFF_QDO + s * C::STAGE_BYTES;
+        uint8_t* sDO = sQ + C::QDO_BYTES;
+        mbar_arrive_expect_tx(&qdo_full[s], C::STAGE_BYTES);
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c) {
+          tma_load_3d(sQ + c * (BM * 128), &tmQKV, &qdo_full[s], hq * D + c * 64, q0, b);
+          tma_load_3d(sDO + c * (BM * 128), &tmDO, &qdo_full[s], hq * D + c * 64, q0, b);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_kk = make_idesc_f16(1, BM, BN, 0, 0);  // S, dP
+      const uint32_t idesc_tt = make_idesc_f16(1, BN, D, 1, 1);   // dV, dK
+      const uint32_t idesc_kt = make_idesc_f16(1, BM, D, 0, 1);   // dQ
+      const uint32_t sK = smem_u32(smem + C::OFF_K);
+      const uint32_t sV = smem_u32(smem + C::OFF_V);
+      const uint32_t sP = smem_u32(smem + C::OFF_P);
+      const uint32_t sDS = smem_u32(smem + C::OFF_DS);
+      bool ok = mbar_wait_bounded(kv_full, 0, abort_flag, err_word, ERR_WAIT_FULL);
+      for (int it = 0; ok && it < n_it; ++it) {
+        const int s = it % ST;
+        const uint32_t ph = (it / ST) & 1u;
+        if (!mbar_wait_bounded(&qdo_full[s], ph, abort_flag, err_word, ERR_WAIT_FULL)) break;
+        if (C::ALIAS && it > 0) {
+          if (!mbar_wait_bounded(dq_empty, (it - 1) & 1u, abort_flag, err_word, ERR_WAIT_AUX)) break;
+        }
+        tc_fence_after_sync();
+        const uint32_t sQ = smem_u32(smem + C::OFF_QDO + s * C::STAGE_BYTES);
+        const uint32_t sDO = sQ + C::QDO_BYTES;
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t sub = k >> 2, kk = k & 3;
+          const uint64_t da = make_smem_desc_sw128(sQ + sub * (BM * 128) + kk * 32, 16, 1024);
+          const uint64_t db = make_smem_desc_sw128(sK + sub * (BN * 128) + kk * 32, 16, 1024);
+          umma_f16_ss(tmem_base + C::S_COL, da, db, idesc_kk, k != 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t sub = k >> 2, kk = k & 3;
+          const uint64_t da = make_smem_desc_sw128(sDO + sub * (BM * 128) + kk * 32, 16, 1024);
+          const uint64_t db = make_smem_desc_sw128(sV + sub * (BN * 128) + kk * 32, 16, 1024);
+          umma_f16_ss(tmem_base + C::DP_COL, da, db, idesc_kk, k != 0 ? 1u : 0u);
+        }
+        umma_commit(sdp_full);
+        if (!mbar_wait_bounded(pds_ready, it & 1u, abort_flag, err_word, ERR_WAIT_AUX)) break;
+        if (!C::ALIAS && it > 0) {
+          if (!mbar_wait_bounded(dq_empty, (it - 1) & 1u, abort_flag, err_word, ERR_WAIT_AUX)) break;
+        }
+        tc_fence_after_sync();
+        // dV += P^T dO ; dK += dS^T Q : reduction over the 128 queries, 16 per step (2048 B per step in both tiles)
+#pragma unroll
+        for (int k = 0; k < BM / 16; ++k) {
+          const uint64_t da = make_smem_desc_sw128(sP + k * 2048, BM * 128, 1024);
+          const uint64_t db = make_smem_desc_sw128(sDO + k * 2048, BM * 128, 1024);
+          umma_f16_ss(tmem_base + C::DV_COL, da, db, idesc_tt, (it | k) != 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < BM / 16; ++k) {
+          const uint64_t da = make_smem_desc_sw128(sDS + k * 2048, BM * 128, 1024);
+          const uint64_t db = make_smem_desc_sw128(sQ + k * 2048, BM * 128, 1024);
+          umma_f16_ss(tmem_base + C::DK_COL, da, db, idesc_tt, (it | k) != 0 ? 1u : 0u);
+        }
+        // dQ = dS K : reduction over the 128 keys
+#pragma unroll
+        for (int k = 0; k < BN / 16; ++k) {
+          const uint32_t sub = k >> 2, kk = k & 3;
+          const uint64_t da = make_smem_desc_sw128(sDS + sub * (BM * 128) + kk * 32, 16, 1024);
+          const uint64_t db = make_smem_desc_sw128(sK + k * 2048, BN * 128, 1024);
+          umma_f16_ss(tmem_base + C::DQ_COL, da, db, idesc_kt, k != 0 ? 1u : 0u);
+        }
+        umma_commit(&qdo_empty[s]);
+        umma_commit(dq_full);
+      }
+    }
+  } else {
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;
+    const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+    const float c2 = p.scale * 1.4426950408889634f;
+    uint8_t* sP = smem + C::OFF_P;
+    uint8_t* sDS = smem + C::OFF_DS;
+    bool ok = true;
+    for (int it = 0; it < n_it; ++it) {
+      const int hq = hkv * g + it / nqi;
+      const int q0 = (i_start + it % nqi) * BM;
+      const int qi = q0 + r;
+      const bool row_ok = qi < p.L;
+      const long long t = (long long)b * p.L + qi;
+      const float lse2 = row_ok ? p.lse[(long long)hq * T + t] * 1.4426950408889634f : 0.f;
+      const float dlt = row_ok ? p.delta[(long long)hq * T + t] : 0.f;
+      const bool diag = (kv0 + BN - 1) > q0;
+      int w = mbar_wait_bounded(sdp_full, it & 1u, abort_flag, err_word, ERR_WAIT_TMEM_FULL) ? 1 : 0;
+      if (!__all_sync(0xffffffffu, w)) { ok = false; break; }
+      tc_fence_after_sync();
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t sv[32], dv[32];
+        tmem_ld_32x32b_x32(tmem_base + lane_addr + C::S_COL + c * 32, sv);
+        tmem_ld_32x32b_x32(tmem_base + lane_addr + C::DP_COL + c * 32, dv);
+        tmem_ld_wait();
+        uint32_t pkP[16], pkS[16];
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          float p0 = fast_exp2(__uint_as_float(sv[e]) * c2 - lse2);
+          float p1 = fast_exp2(__uint_as_float(sv[e + 1]) * c2 - lse2);
+          const int kvi = kv0 + c * 32 + e;
+          if (!row_ok || (diag && kvi > qi)) p0 = 0.f;
+          if (!row_ok || (diag && kvi + 1 > qi)) p1 = 0.f;
+          const float d0 = p0 * (__uint_as_float(dv[e]) - dlt) * p.scale;
+          const float d1 = p1 * (__uint_as_float(dv[e + 1]) - dlt) * p.scale;
+          pkP[e >> 1] = pack_bf16x2(p0, p1);
+          pkS[e >> 1] = pack_bf16x2(d0, d1);
+        }
+        const int sub = (c * 32) >> 6;
+        const int chunk0 = ((c * 32) & 63) >> 3;
+        const int off = sub * (BM * 128) + r * 128;
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const int ch = (chunk0 + q4) ^ (r & 7);
+          *reinterpret_cast<uint4*>(sP + off + ch * 16) =
+              make_uint4(pkP[q4 * 4], pkP[q4 * 4 + 1], pkP[q4 * 4 + 2], pkP[q4 * 4 + 3]);
+          *reinterpret_cast<uint4*>(sDS + off + ch * 16) =
+              make_uint4(pkS[q4 * 4], pkS[q4 * 4 + 1], pkS[q4 * 4 + 2], pkS[q4 * 4 + 3]);
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      mbar_arrive(pds_ready);
+      // drain dQ of this pair into the fp32 accumulator
+      int w2 = mbar_wait_bounded(dq_full, it & 1u, abort_flag, err_word, ERR_WAIT_AUX) ? 1 : 0;
+      if (!__all_sync(0xffffffffu, w2)) { ok = false; break; }
+      tc_fence_after_sync();
+      float* dq_row = p.dq_acc + t * (long long)(p.H * D) + hq * D;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(tmem_base + lane_addr + C::DQ_COL + c * 32, v);
+        tmem_ld_wait();
+        if (row_ok) {
+#pragma unroll
+          for (int q4 = 0; q4 < 8; ++q4)
+            red_add_v4(dq_row + c * 32 + q4 * 4, __uint_as_float(v[q4 * 4]), __uint_as_float(v[q4 * 4 + 1]),
+                       __uint_as_float(v[q4 * 4 + 2]), __uint_as_float(v[q4 * 4 + 3]));
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(dq_empty);
+    }
+    // epilogue: dK_j, dV_j (thread = key row). The last dq_full wait covered every MMA of this CTA.
+    if (ok && n_it > 0) {
+      const int kvi = kv0 + r;
+      const bool row_ok = kvi < p.L;
+      const long long width = (long long)(p.H + 2 * p.Hkv) * D;
+      __nv_bfloat16* krow = p.dqkv + ((long long)b * p.L + kvi) * width + colK;
+      __nv_bfloat16* vrow = p.dqkv + ((long long)b * p.L + kvi) * width + colV;
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {
+        const uint32_t col = which == 0 ? C::DK_COL : C::DV_COL;
+        __nv_bfloat16* dst = which == 0 ? krow : vrow;
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(tmem_base + lane_addr + col + c * 32, v);
+          tmem_ld_wait();
+          if (row_ok) {
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              uint4 o;
+              o.x = pack_bf16x2(__uint_as_float(v[q4 * 8 + 0]), __uint_as_float(v[q4 * 8 + 1]));
+              o.y = pack_bf16x2(__uint_as_float(v[q4 * 8 + 2]), __uint_as_float(v[q4 * 8 + 3]));
+              o.z = pack_bf16x2(__uint_as_float(v[q4 * 8 + 4]), __uint_as_float(v[q4 * 8 + 5]));
+              o.w = pack_bf16x2(__uint_as_float(v[q4 * 8 + 6]), __uint_as_float(v[q4 * 8 + 7]));
+              *reinterpret_cast<uint4*>(dst + c * 32 + q4 * 8) = o;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  __syncwarp();
+  if (*abort_flag) {
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+}
+
+// delta[h, t] = sum_d dout[t, h*D + d] * out[t, h*D + d]; one group of D/8 lanes per (t, h).
+template <int D>
+__global__ void delta_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ out,
+                             float* __restrict__ delta, long long T, int H) {
+  constexpr int LPG = D / 8;  // lanes per (t,h)
+  const long long gid = (blockIdx.x * (long long)blockDim.x + threadIdx.x);
+  const long long grp = gid / LPG;
+  const int sub = (int)(gid % LPG);
+  float s = 0.f;
+  const bool ok = grp < T * H;
+  long long t = 0;
+  int h = 0;
+  if (ok) {
+    t = grp / H;
+    h = (int)(grp - t * H);
+    const size_t off = (size_t)t * H * D + (size_t)h * D + sub * 8;
+    uint4 a = *reinterpret_cast<const uint4*>(dout + off);
+    uint4 b = *reinterpret_cast<const uint4*>(out + off);
+    const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&a);
+    const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&b);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float2 x = __bfloat1622float2(pa[i]), y = __bfloat1622float2(pb[i]);
+      s += x.x * y.x + x.y * y.y;
+    }
+  }
+#pragma unroll
+  for (int o = LPG / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if (ok && sub == 0) delta[(size_t)h * T + t] = s;
+}
+
+// dqkv[t, 0:H*D] = bf16(dq_acc[t, :])
+__global__ void dq_convert_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dqkv, long long T, int HD,
+                                  long long width) {
+  const int hv = HD >> 3;
+  const long long total = T * hv;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / hv;
+    const int v = (int)(i - t * hv);
+    const float4 a = reinterpret_cast<const float4*>(acc + t * HD)[2 * v];
+    const float4 b = reinterpret_cast<const float4*>(acc + t * HD)[2 * v + 1];
+    uint4 o;
+    o.x = pack_bf16x2(a.x, a.y);
+    o.y = pack_bf16x2(a.z, a.w);
+    o.z = pack_bf16x2(b.x, b.y);
+    o.w = pack_bf16x2(b.z, b.w);
+    reinterpret_cast<uint4*>(dqkv + t * width)[v] = o;
+  }
+}
+
+template <int D>
+static int launch_bwd(const void* dout, const void* qkv, const void* out, const float* lse, float* delta, void* dqkv,
+                      float* dq_acc, int B, int L, int H, int Hkv, cudaStream_t st) {
+  using C = Cfg<D>;
+  const long long width = (long long)(H + 2 * Hkv) * D;
+  const long long T = (long long)B * L;
+  const long long HD = (long long)H * D;
+  CUtensorMap tmQKV, tmDO;
+  int rc = make_tmap_3d(&tmQKV, qkv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)width, (uint64_t)L, (uint64_t)B,
+                        (uint64_t)width * 2, (uint64_t)L * width * 2, 64, 128, 1, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != B200_OK) return rc;
+  rc = make_tmap_3d(&tmDO, dout, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)HD, (uint64_t)L, (uint64_t)B,
+                    (uint64_t)HD * 2, (uint64_t)L * HD * 2, 64, 128, 1, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != B200_OK) return rc;
+  {
+    const long long threads = T * H * (D / 8);
+    delta_kernel<D><<<(unsigned)((threads + 255) / 256), 256, 0, st>>>((const __nv_bfloat16*)dout,
+                                                                      (const __nv_bfloat16*)out, delta, T, H);
+    B200_CUDA_CHECK(cudaGetLastError());
+  }
+  B200_CUDA_CHECK(cudaMemsetAsync(dq_acc, 0, (size_t)T * HD * sizeof(float), st));
+  auto kern = flash_bwd_kernel<D>;
+  static bool attr = false;
+  if (!attr) {
+    B200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+    attr = true;
+  }
+  BwdParams p{lse, delta, dq_acc, (__nv_bfloat16*)dqkv, B, L, H, Hkv, 1.0f / sqrtf((float)D)};
+  dim3 grid((L + BN - 1) / BN, Hkv, B);
+  kern<<<grid, NTHREADS, C::SMEM_BYTES, st>>>(tmQKV, tmDO, p, device_err_word());
+  B200_CUDA_CHECK(cudaGetLastError());
+  {
+    long long work = T * (HD >> 3);
+    long long blocks = (work + 255) / 256;
+    const long long cap = (long long)sm_count() * 8;
+    if (blocks > cap) blocks = cap;
+    dq_convert_kernel<<<(unsigned)blocks, 256, 0, st>>>(dq_acc, (__nv_bfloat16*)dqkv, T, (int)HD, width);
+    B200_CUDA_CHECK(cudaGetLastError());
+  }
+  return B200_OK;
+}
+
+}  // namespace fab
+}  // namespace b200
+
+// dq_acc: fp32 scratch [T, H*D] (zeroed here); delta: fp32 scratch [H, T]. dqkv receives dQ | dK | dV.
+extern "C" int b200_flash_attn_bwd(const void* dout, const void* qkv, const void* out, const float* lse, float* delta,
+                                   void* dqkv, float* dq_acc, int B, int L, int H, int Hkv, int D, cudaStream_t st) {
+  using namespace b200;
+  if (!dout || !qkv || !out || !lse || !delta || !dqkv || !dq_acc || B <= 0 || L <= 0 || H <= 0 || Hkv <= 0 ||
+      (H % Hkv) != 0)
+    return B200_ERR_ARG;
+  if (D == 64) return fab::launch_bwd<64>(dout, qkv, out, lse, delta, dqkv, dq_acc, B, L, H, Hkv, st);
+  if (D == 128) return fab::launch_bwd<128>(dout, qkv, out, lse, delta, dqkv, dq_acc, B, L, H, Hkv, st);
+  return B200_ERR_ARG;
+}

@@ -7,7 +7,7 @@ from . import _lib
 from ._lib import _VP, _I
 
 _lib.register("b200_flash_attn_fwd", [_VP, _VP, _VP, _I, _I, _I, _I, _I, _VP])
-_lib.register("b200_flash_attn_bwd", [_VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _VP])
+_lib.register("b200_flash_attn_bwd", [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _VP])
 
 
 def flash_attn_fwd(qkv: torch.Tensor, B: int, L: int, H: int, Hkv: int, d: int):
@@ -25,9 +25,10 @@ def flash_attn_bwd(dout, qkv, out, lse, B, L, H, Hkv, d):
     if not dout.is_contiguous():
         dout = dout.contiguous()
     dqkv = torch.empty_like(qkv)
-    # delta[h, t] = sum_d dout * out, computed inside the launcher's pre-pass
+    # scratch: delta[h, t] = sum_d dout * out (pre-pass) and the fp32 dQ accumulator the key-block CTAs reduce into
     delta = torch.empty_like(lse)
+    dq_acc = torch.empty((B * L, H * d), dtype=torch.float32, device=qkv.device)
     rc = _lib.kernels().b200_flash_attn_bwd(_lib.ptr(dout), _lib.ptr(qkv), _lib.ptr(out), _lib.ptr(lse), _lib.ptr(delta),
-                                            _lib.ptr(dqkv), B, L, H, Hkv, d, _lib.stream())
+                                            _lib.ptr(dqkv), _lib.ptr(dq_acc), B, L, H, Hkv, d, _lib.stream())
     _lib.check(rc, "b200_flash_attn_bwd")
     return dqkv
