@@ -31,6 +31,7 @@ struct EpiStore {
 #pragma unroll 1
     for (int c = 0; c < BN / 32; ++c) {
       uint32_t r[32];
+      __syncwarp();  // lanes may have diverged in the previous chunk; tcgen05.ld is warp-collective
       tmem_ld_32x32b_x32(taddr + c * 32, r);
       tmem_ld_wait();
       const int col0 = n0 + c * 32;

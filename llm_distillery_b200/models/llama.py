@@ -1,0 +1,408 @@
+"""Llama-family decoder (Llama 1/2/3, TinyLlama, Mistral: RMSNorm, RoPE, GQA, SwiGLU, optional tied embeddings)
+for both roles: student training (forward + hand-written backward) and teacher inference.
+
+Design. Each decoder layer is ONE autograd node (``DecoderLayerFn``) whose forward and backward are explicit
+sequences of the kernels in ``ops`` - 7 GEMMs, 2 RMSNorms, RoPE, flash attention, SwiGLU - so residual adds ride
+in GEMM epilogues, the residual-branch gradient is added inside the RMSNorm backward, weight gradients are
+accumulated by the wgrad GEMM epilogue straight into fp32 ``main_grad`` buffers, and no autograd bookkeeping or
+library elementwise kernel sits between them. QKV and gate/up projections are stored fused ([(H+2Hkv)d, h] and
+[2f, h]); HuggingFace checkpoints are split / concatenated at load / save time (``to_hf_state_dict``).
+
+The same code runs on CPU tensors through the PyTorch restatements in ``ops`` (fp32 plumbing runs and tests).
+"""
+from __future__ import annotations
+
+import json
+import math
+import os
+from dataclasses import dataclass, asdict
+
+import torch
+import torch.nn as nn
+
+from ..ops import basic, attention
+
+
+@dataclass
+class LlamaConfig:
+    vocab_size: int = 32000
+    hidden_size: int = 2048
+    intermediate_size: int = 5632
+    num_hidden_layers: int = 22
+    num_attention_heads: int = 32
+    num_key_value_heads: int = 4
+    rms_norm_eps: float = 1e-5
+    rope_theta: float = 10000.0
+    max_position_embeddings: int = 2048
+    tie_word_embeddings: bool = False
+    bos_token_id: int = 1
+    eos_token_id: int = 2
+    model_type: str = "llama"
+
+    @property
+    def head_dim(self) -> int:
+        return self.hidden_size // self.num_attention_heads
+
+    @property
+    def q_size(self) -> int:
+        return self.num_attention_heads * self.head_dim
+
+    @property
+    def kv_size(self) -> int:
+        return self.num_key_value_heads * self.head_dim
+
+    def num_params(self) -> int:
+        h, f, V, Lr = self.hidden_size, self.intermediate_size, self.vocab_size, self.num_hidden_layers
+        per_layer = h * (self.q_size + 2 * self.kv_size) + self.q_size * h + 3 * h * f + 2 * h
+        return Lr * per_layer + V * h * (1 if self.tie_word_embeddings else 2) + h
+
+    def flops_per_token_fwd(self, seq_len: int) -> float:
+        h, f, V, Lr = self.hidden_size, self.intermediate_size, self.vocab_size, self.num_hidden_layers
+        lin = 2 * (Lr * (h * (self.q_size + 2 * self.kv_size) + self.q_size * h + 3 * h * f) + V * h)
+        attn = Lr * 4 * self.q_size * seq_len / 2  # causal
+        return lin + attn
+
+    def to_hf_dict(self) -> dict:
+        d = asdict(self)
+        d.update(architectures=["LlamaForCausalLM"], hidden_act="silu", torch_dtype="bfloat16", attention_bias=False,
+                 mlp_bias=False)
+        return d
+
+    @classmethod
+    def from_hf_dict(cls, d: dict) -> "LlamaConfig":
+        keys = {f for f in cls.__dataclass_fields__}
+        kw = {k: v for k, v in d.items() if k in keys}
+        if "num_key_value_heads" not in kw or kw["num_key_value_heads"] is None:
+            kw["num_key_value_heads"] = kw.get("num_attention_heads", 32)
+        return cls(**kw)
+
+    @classmethod
+    def from_pretrained(cls, path: str) -> "LlamaConfig":
+        with open(os.path.join(path, "config.json"), "r", encoding="utf-8") as f:
+            return cls.from_hf_dict(json.load(f))
+
+
+PRESETS = {
+    # name: (layers, hidden, heads, kv_heads, ffn, vocab, theta, eps, tied, max_pos)
+    "tinyllama-1.1b": (22, 2048, 32, 4, 5632, 32000, 10000.0, 1e-5, False, 2048),
+    "llama-3.2-1b": (16, 2048, 32, 8, 8192, 128256, 500000.0, 1e-5, True, 131072),
+    "llama-3-8b": (32, 4096, 32, 8, 14336, 128256, 500000.0, 1e-5, False, 8192),
+    "mistral-7b": (32, 4096, 32, 8, 14336, 32000, 10000.0, 1e-5, False, 32768),
+    "llama-3-70b": (80, 8192, 64, 8, 28672, 128256, 500000.0, 1e-5, False, 8192),
+    "plumbing-teacher": (2, 256, 4, 4, 688, 32000, 10000.0, 1e-6, False, 2048),
+    "plumbing-student": (4, 256, 4, 4, 688, 32000, 10000.0, 1e-6, False, 2048),
+}
+
+
+def preset(name: str, **over) -> LlamaConfig:
+    Lr, h, H, Hkv, f, V, theta, eps, tied, mp = PRESETS[name]
+    cfg = LlamaConfig(vocab_size=V, hidden_size=h, intermediate_size=f, num_hidden_layers=Lr, num_attention_heads=H,
+                      num_key_value_heads=Hkv, rms_norm_eps=eps, rope_theta=theta, max_position_embeddings=mp,
+                      tie_word_embeddings=tied)
+    for k, v in over.items():
+        setattr(cfg, k, v)
+    return cfg
+
+
+# ---------------------------------------------------------------------------------------------- gradient slots
+class GradSlot:
+    """fp32 accumulation target of one parameter (a view into the engine's flat gradient buffer). ``fresh`` means
+    nothing has been accumulated since the last optimizer step: the next wgrad overwrites instead of adding."""
+    __slots__ = ("buf", "fresh")
+
+    def __init__(self, buf: torch.Tensor):
+        self.buf = buf
+        self.fresh = True
+
+
+def _slot(p: torch.Tensor):
+    return getattr(p, "grad_slot", None) if p.requires_grad else None
+
+
+def _wgrad(dy: torch.Tensor, x: torch.Tensor, w: torch.Tensor, slot):
+    """Weight gradient of y = x w^T. With a slot: accumulated in place (fp32), returns None. Else returns dW."""
+    if not w.requires_grad:
+        return None
+    if slot is not None:
+        basic.linear_wgrad(dy, x, out=slot.buf, accumulate=not slot.fresh)
+        slot.fresh = False
+        return None
+    return basic.linear_wgrad(dy, x, out_dtype=w.dtype)
+
+
+def _vec_grad(dw: torch.Tensor, w: torch.Tensor, slot):
+    if not w.requires_grad:
+        return None
+    if slot is not None:
+        if slot.fresh:
+            slot.buf.copy_(dw)
+            slot.fresh = False
+        else:
+            slot.buf.add_(dw)
+        return None
+    return dw.to(w.dtype)
+
+
+# ---------------------------------------------------------------------------------------------- autograd nodes
+class EmbeddingFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, ids, w):
+        ctx.save_for_backward(ids)
+        ctx.w = w
+        ctx.slot = _slot(w)
+        return basic.embed_fwd(ids, w)
+
+    @staticmethod
+    def backward(ctx, dout):
+        (ids,) = ctx.saved_tensors
+        w, slot = ctx.w, ctx.slot
+        if not w.requires_grad:
+            return None, None
+        if slot is not None:
+            if slot.fresh:
+                slot.buf.zero_()
+                slot.fresh = False
+            basic.embed_bwd(ids, dout.contiguous(), slot.buf)
+            return None, None
+        dw = torch.zeros(w.shape, dtype=torch.float32, device=w.device)
+        basic.embed_bwd(ids, dout.contiguous(), dw)
+        return None, dw.to(w.dtype)
+
+
+class DecoderLayerFn(torch.autograd.Function):
+    """h_out = h + Attn(RMSNorm(h)) ; then + MLP(RMSNorm(.)) - one node, explicit backward."""
+
+    @staticmethod
+    def forward(ctx, h, pos, cos, sin, w_ln1, w_qkv, w_o, w_ln2, w_gu, w_d, meta):
+        B, L, H, Hkv, d, eps, recompute = meta
+        n1, _, rstd1 = basic.rmsnorm_fwd(h, w_ln1, eps)
+        qkv = basic.linear_fwd(n1, w_qkv)
+        basic.rope_(qkv, pos, cos, sin, H + Hkv, d)          # q and k heads are adjacent columns
+        att, lse = attention.attention_fwd(qkv, B, L, H, Hkv, d)
+        h1 = basic.linear_fwd(att, w_o, residual=h)
+        n2, _, rstd2 = basic.rmsnorm_fwd(h1, w_ln2, eps)
+        gu = basic.linear_fwd(n2, w_gu)
+        act = basic.swiglu_fwd(gu)
+        h2 = basic.linear_fwd(act, w_d, residual=h1)
+        ctx.meta = meta
+        ctx.weights = (w_ln1, w_qkv, w_o, w_ln2, w_gu, w_d)
+        ctx.slots = tuple(_slot(w) for w in ctx.weights)
+        if recompute:   # gradient checkpointing: keep only the layer input
+            ctx.save_for_backward(h, pos, cos, sin)
+        else:
+            ctx.save_for_backward(h, pos, cos, sin, rstd1, n1, qkv, att, lse, h1, rstd2, n2, gu)
+        return h2
+
+    @staticmethod
+    def backward(ctx, dh2):
+        B, L, H, Hkv, d, eps, recompute = ctx.meta
+        w_ln1, w_qkv, w_o, w_ln2, w_gu, w_d = ctx.weights
+        s_ln1, s_qkv, s_o, s_ln2, s_gu, s_d = ctx.slots
+        if recompute:
+            h, pos, cos, sin = ctx.saved_tensors
+            n1, _, rstd1 = basic.rmsnorm_fwd(h, w_ln1, eps)
+            qkv = basic.linear_fwd(n1, w_qkv)
+            basic.rope_(qkv, pos, cos, sin, H + Hkv, d)
+            att, lse = attention.attention_fwd(qkv, B, L, H, Hkv, d)
+            h1 = basic.linear_fwd(att, w_o, residual=h)
+            n2, _, rstd2 = basic.rmsnorm_fwd(h1, w_ln2, eps)
+            gu = basic.linear_fwd(n2, w_gu)
+        else:
+            h, pos, cos, sin, rstd1, n1, qkv, att, lse, h1, rstd2, n2, gu = ctx.saved_tensors
+        dh2 = dh2.contiguous()
+        # MLP branch
+        act = basic.swiglu_fwd(gu)
+        g_d = _wgrad(dh2, act, w_d, s_d)
+        dact = basic.linear_dgrad(dh2, w_d)
+        del act
+        dgu = basic.swiglu_bwd(gu, dact)
+        del dact
+        g_gu = _wgrad(dgu, n2, w_gu, s_gu)
+        dn2 = basic.linear_dgrad(dgu, w_gu)
+        del dgu
+        dh1, dw2 = basic.rmsnorm_bwd(dn2, h1, w_ln2, rstd2, dres=dh2)
+        g_ln2 = _vec_grad(dw2, w_ln2, s_ln2)
+        # attention branch
+        g_o = _wgrad(dh1, att, w_o, s_o)
+        datt = basic.linear_dgrad(dh1, w_o)
+        dqkv = attention.attention_bwd(datt, qkv, att, lse, B, L, H, Hkv, d)
+        del datt
+        basic.rope_(dqkv, pos, cos, sin, H + Hkv, d, inverse=True)
+        g_qkv = _wgrad(dqkv, n1, w_qkv, s_qkv)
+        dn1 = basic.linear_dgrad(dqkv, w_qkv)
+        del dqkv
+        dh, dw1 = basic.rmsnorm_bwd(dn1, h, w_ln1, rstd1, dres=dh1)
+        g_ln1 = _vec_grad(dw1, w_ln1, s_ln1)
+        return dh, None, None, None, g_ln1, g_qkv, g_o, g_ln2, g_gu, g_d, None
+
+
+class FinalNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, h, w, eps):
+        y, _, rstd = basic.rmsnorm_fwd(h, w, eps)
+        ctx.save_for_backward(h, rstd)
+        ctx.w, ctx.slot = w, _slot(w)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        h, rstd = ctx.saved_tensors
+        dh, dw = basic.rmsnorm_bwd(dy.contiguous(), h, ctx.w, rstd)
+        return dh, _vec_grad(dw, ctx.w, ctx.slot), None
+
+
+class LinearFn(torch.autograd.Function):
+    """y = x w^T, used for the LM head when full logits are requested (teacher collection, CPU oracle)."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        ctx.save_for_backward(x)
+        ctx.w, ctx.slot = w, _slot(w)
+        return basic.linear_fwd(x, w)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (x,) = ctx.saved_tensors
+        dy = dy.contiguous()
+        return basic.linear_dgrad(dy, ctx.w), _wgrad(dy, x, ctx.w, ctx.slot)
+
+
+# ---------------------------------------------------------------------------------------------- modules
+class LlamaDecoderLayer(nn.Module):
+    def __init__(self, cfg: LlamaConfig, dtype, device):
+        super().__init__()
+        h, f = cfg.hidden_size, cfg.intermediate_size
+        kw = dict(dtype=dtype, device=device)
+        self.input_layernorm = nn.Parameter(torch.ones(h, **kw))
+        self.qkv_proj = nn.Parameter(torch.empty(cfg.q_size + 2 * cfg.kv_size, h, **kw))
+        self.o_proj = nn.Parameter(torch.empty(h, cfg.q_size, **kw))
+        self.post_attention_layernorm = nn.Parameter(torch.ones(h, **kw))
+        self.gate_up_proj = nn.Parameter(torch.empty(2 * f, h, **kw))
+        self.down_proj = nn.Parameter(torch.empty(h, f, **kw))
+
+
+class LlamaModel(nn.Module):
+    """Parameters use fused projection names; ``named_hf_parameters`` / ``to_hf_state_dict`` expose the HF names
+    (``model.layers.N.self_attn.q_proj.weight`` ...), which is also what ``freeze_layers`` substrings match."""
+
+    def __init__(self, cfg: LlamaConfig, dtype=torch.bfloat16, device="cpu"):
+        super().__init__()
+        self.cfg = cfg
+        kw = dict(dtype=dtype, device=device)
+        self.embed_tokens = nn.Parameter(torch.empty(cfg.vocab_size, cfg.hidden_size, **kw))
+        self.layers = nn.ModuleList([LlamaDecoderLayer(cfg, dtype, device) for _ in range(cfg.num_hidden_layers)])
+        self.norm = nn.Parameter(torch.ones(cfg.hidden_size, **kw))
+        if cfg.tie_word_embeddings:
+            self.lm_head = self.embed_tokens
+        else:
+            self.lm_head = nn.Parameter(torch.empty(cfg.vocab_size, cfg.hidden_size, **kw))
+        self.grad_checkpointing = False
+        self._rope = None
+
+    # ---- init / tables
+    @torch.no_grad()
+    def init_weights(self, seed: int = 0, std: float = 0.02) -> "LlamaModel":
+        gens: dict = {}
+        for name, p in self.named_parameters():
+            if p.dim() == 1:
+                p.fill_(1.0)
+            else:
+                dev = p.device
+                if dev not in gens:
+                    gens[dev] = torch.Generator(device=dev).manual_seed(seed)
+                p.normal_(mean=0.0, std=std, generator=gens[dev])   # generated where the weights live
+        return self
+
+    def rope(self, device, max_pos: int | None = None):
+        need = max_pos or self.cfg.max_position_embeddings
+        if self._rope is None or self._rope[0].device != torch.device(device) or self._rope[0].shape[0] < need:
+            n = max(need, min(self.cfg.max_position_embeddings, 8192))
+            self._rope = basic.rope_tables(n, self.cfg.head_dim, self.cfg.rope_theta, device)
+        return self._rope
+
+    # ---- forward
+    def hidden_states(self, input_ids: torch.Tensor) -> torch.Tensor:
+        """input_ids [B, L] int64 -> final-norm hidden states [B*L, h]."""
+        cfg = self.cfg
+        B, L = input_ids.shape
+        dev = self.embed_tokens.device
+        ids = input_ids.reshape(-1).to(dev)
+        pos = torch.arange(L, dtype=torch.int32, device=dev).repeat(B)
+        cos, sin = self.rope(dev, L)
+        h = EmbeddingFn.apply(ids, self.embed_tokens)
+        meta = (B, L, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.rms_norm_eps,
+                bool(self.grad_checkpointing and torch.is_grad_enabled()))
+        for layer in self.layers:
+            h = DecoderLayerFn.apply(h, pos, cos, sin, layer.input_layernorm, layer.qkv_proj, layer.o_proj,
+                                     layer.post_attention_layernorm, layer.gate_up_proj, layer.down_proj, meta)
+        return FinalNormFn.apply(h, self.norm, cfg.rms_norm_eps)
+
+    def forward(self, input_ids: torch.Tensor) -> torch.Tensor:
+        """Full logits [B, L, V] (collection without the fused top-K head, tests). Training never calls this."""
+        B, L = input_ids.shape
+        hs = self.hidden_states(input_ids)
+        return LinearFn.apply(hs, self.lm_head).reshape(B, L, -1)
+
+    # ---- HF naming
+    def named_hf_parameters(self):
+        """Yields (hf_name, parameter, row_slice or None) - fused tensors appear once per HF tensor they hold."""
+        cfg = self.cfg
+        yield "model.embed_tokens.weight", self.embed_tokens, None
+        q, kv, f = cfg.q_size, cfg.kv_size, cfg.intermediate_size
+        for i, l in enumerate(self.layers):
+            pre = f"model.layers.{i}."
+            yield pre + "input_layernorm.weight", l.input_layernorm, None
+            yield pre + "self_attn.q_proj.weight", l.qkv_proj, slice(0, q)
+            yield pre + "self_attn.k_proj.weight", l.qkv_proj, slice(q, q + kv)
+            yield pre + "self_attn.v_proj.weight", l.qkv_proj, slice(q + kv, q + 2 * kv)
+            yield pre + "self_attn.o_proj.weight", l.o_proj, None
+            yield pre + "post_attention_layernorm.weight", l.post_attention_layernorm, None
+            yield pre + "mlp.gate_proj.weight", l.gate_up_proj, slice(0, f)
+            yield pre + "mlp.up_proj.weight", l.gate_up_proj, slice(f, 2 * f)
+            yield pre + "mlp.down_proj.weight", l.down_proj, None
+        yield "model.norm.weight", self.norm, None
+        if not cfg.tie_word_embeddings:
+            yield "lm_head.weight", self.lm_head, None
+
+    def to_hf_state_dict(self) -> dict[str, torch.Tensor]:
+        return {n: (p.data if sl is None else p.data[sl]) for n, p, sl in self.named_hf_parameters()}
+
+    @torch.no_grad()
+    def load_hf_state_dict(self, sd: dict[str, torch.Tensor], strict: bool = True) -> None:
+        seen = set()
+        for n, p, sl in self.named_hf_parameters():
+            if n not in sd:
+                if n == "lm_head.weight" and "model.embed_tokens.weight" in sd:
+                    p.copy_(sd["model.embed_tokens.weight"].to(p.dtype))
+                    continue
+                if strict:
+                    raise KeyError(f"missing tensor {n}")
+                continue
+            (p if sl is None else p[sl]).copy_(sd[n].to(p.dtype))
+            seen.add(n)
+        extra = [k for k in sd if k not in seen and k != "lm_head.weight" and not k.endswith("rotary_emb.inv_freq")]
+        if strict and extra:
+            raise KeyError(f"unexpected tensors {extra[:5]}")
+
+    def apply_freeze(self, freeze_layers: list[str]) -> list[str]:
+        """requires_grad=False for every parameter one of whose HF names contains a listed substring
+        (reference: classes/student/model.py:214-218). A fused tensor freezes only if all its parts match."""
+        by_param: dict[int, list[bool]] = {}
+        params = {}
+        for n, p, _ in self.named_hf_parameters():
+            hit = any(s in n for s in (freeze_layers or []))
+            by_param.setdefault(id(p), []).append(hit)
+            params[id(p)] = (p, n)
+        frozen = []
+        for pid, hits in by_param.items():
+            if hits and all(hits):
+                params[pid][0].requires_grad = False
+                frozen.append(params[pid][1])
+        return frozen
+
+
+def build_model(cfg: LlamaConfig, dtype=torch.bfloat16, device="cpu", seed: int | None = 0) -> LlamaModel:
+    m = LlamaModel(cfg, dtype=dtype, device=device)
+    if seed is not None:
+        m.init_weights(seed)
+    return m
