@@ -287,6 +287,21 @@ __global__ void embed_bwd_kernel(const long long* __restrict__ ids, const __nv_b
   }
 }
 
+// dst[rows[i], :] = src[i, :]   (rows unique; dst pre-zeroed by the launcher). Backward of a row gather.
+__global__ void scatter_rows_kernel(const long long* __restrict__ rows, const __nv_bfloat16* __restrict__ src,
+                                    __nv_bfloat16* __restrict__ dst, long long n, int h, long long dst_rows) {
+  const int hv = h >> 3;
+  const long long total = n * hv;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / hv;
+    const int v = (int)(i - t * hv);
+    const long long r = rows[t];
+    if (r < 0 || r >= dst_rows) continue;
+    reinterpret_cast<uint4*>(dst + r * h)[v] = reinterpret_cast<const uint4*>(src + t * h)[v];
+  }
+}
+
 // bf16 <-> fp32 conversions over flat buffers (n elements), with optional scale / accumulate.
 __global__ void cast_f32_to_bf16_kernel(const float* __restrict__ in, __nv_bfloat16* __restrict__ out, long long n,
                                         float scale) {
@@ -406,6 +421,16 @@ int b200_embed_fwd(const long long* ids, const void* W, void* out, long long T, 
 int b200_embed_bwd(const long long* ids, const void* dout, float* dW, long long T, int h, int vocab, cudaStream_t st) {
   if (!ids || !dout || !dW || T <= 0 || (h & 7)) return B200_ERR_ARG;
   embed_bwd_kernel<<<grid_for(T * (h >> 3), 256), 256, 0, st>>>(ids, (const __nv_bfloat16*)dout, dW, T, h, vocab);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200_OK;
+}
+
+int b200_scatter_rows(const long long* rows, const void* src, void* dst, long long n, int h, long long dst_rows,
+                      cudaStream_t st) {
+  if (!rows || !src || !dst || n <= 0 || (h & 7) || dst_rows <= 0) return B200_ERR_ARG;
+  B200_CUDA_CHECK(cudaMemsetAsync(dst, 0, (size_t)dst_rows * h * 2, st));
+  scatter_rows_kernel<<<grid_for(n * (h >> 3), 256), 256, 0, st>>>(rows, (const __nv_bfloat16*)src, (__nv_bfloat16*)dst,
+                                                                  n, h, dst_rows);
   B200_CUDA_CHECK(cudaGetLastError());
   return B200_OK;
 }

@@ -86,7 +86,9 @@ def reference_loss_segments(s: torch.Tensor, t: torch.Tensor, ids: torch.Tensor,
     def ce(x):
         picked = torch.where(hit, x, torch.zeros_like(x)).sum(-1)                       # value at the label slot
         n_valid = _seg_sum(valid.to(x.dtype), seg, n_seg)
-        mean_valid = _seg_sum(torch.where(valid, picked, torch.zeros_like(picked)), seg, n_seg) / n_valid
+        # a conversation none of whose labels is inside the teacher's top-K has no CE signal: use 0 there (the
+        # reference divides by zero and turns the whole step into NaN)
+        mean_valid = _seg_sum(torch.where(valid, picked, torch.zeros_like(picked)), seg, n_seg) / n_valid.clamp_min(1)
         filled = torch.where(valid, picked, mean_valid[seg])
         return -filled
 

@@ -46,6 +46,7 @@ _SIGS = {
     "b200_swiglu_bwd": [_VP, _VP, _VP, _LL, _I, _VP],
     "b200_embed_fwd": [_VP, _VP, _VP, _LL, _I, _I, _VP],
     "b200_embed_bwd": [_VP, _VP, _VP, _LL, _I, _I, _VP],
+    "b200_scatter_rows": [_VP, _VP, _VP, _LL, _I, _LL, _VP],
     "b200_cast_f32_to_bf16": [_VP, _VP, _LL, _F, _VP],
     "b200_cast_bf16_to_f32": [_VP, _VP, _LL, _F, _I, _VP],
     "b200_adam_step": [_VP, _VP, _VP, _VP, _VP, _LL, _F, _F, _F, _F, _F, _I, _F, _I, _VP],
@@ -56,7 +57,36 @@ _SIGS = {
 }
 
 
-def kernels() -> ctypes.CDLL:
+# device kernels launched by one call of each exported launcher (default 1); used to count launches
+KERNELS_PER_CALL = {"b200_rmsnorm_bwd": 2, "b200_flash_attn_bwd": 3, "b200_head_num_tiles": 0, "b200_sm_count": 0,
+                    "b200_rmsnorm_bwd_blocks": 0, "b200_last_cuda_error": 0, "b200_take_device_error": 0}
+LAUNCH_COUNT = [0]
+
+
+class _CountingLib:
+    """Attribute proxy over the CDLL that counts kernel launches (``LAUNCH_COUNT[0]``)."""
+
+    def __init__(self, lib):
+        object.__setattr__(self, "_lib", lib)
+        object.__setattr__(self, "_cache", {})
+
+    def __getattr__(self, name):
+        cache = object.__getattribute__(self, "_cache")
+        fn = cache.get(name)
+        if fn is None:
+            raw = getattr(object.__getattribute__(self, "_lib"), name)
+            n = KERNELS_PER_CALL.get(name, 1)
+            if n == 0:
+                fn = raw
+            else:
+                def fn(*a, _raw=raw, _n=n):
+                    LAUNCH_COUNT[0] += _n
+                    return _raw(*a)
+            cache[name] = fn
+        return fn
+
+
+def kernels():
     global _KERNELS
     if _KERNELS is None:
         lib = _load("libb200_kernels.so")
@@ -71,7 +101,7 @@ def kernels() -> ctypes.CDLL:
                 continue
             fn.argtypes = args
             fn.restype = c_int
-        _KERNELS = lib
+        _KERNELS = _CountingLib(lib)
     return _KERNELS
 
 
@@ -80,7 +110,7 @@ def register(name: str, argtypes: list) -> None:
     _SIGS[name] = argtypes
     if _KERNELS is not None:
         try:
-            fn = getattr(_KERNELS, name)
+            fn = getattr(object.__getattribute__(_KERNELS, "_lib"), name)
         except AttributeError:  # declared by Python but not built into the library yet: calling it will raise
             return
         fn.argtypes = argtypes

@@ -230,6 +230,36 @@ def embed_bwd(ids: torch.Tensor, dout: torch.Tensor, dw: torch.Tensor) -> torch.
     return dw
 
 
+def gather_rows(x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
+    """out[i] = x[rows[i]] (rows int64)."""
+    return embed_fwd(rows, x)
+
+
+def scatter_rows(src: torch.Tensor, rows: torch.Tensor, n_rows: int) -> torch.Tensor:
+    """out [n_rows, h] zero except out[rows[i]] = src[i] (rows unique): the backward of ``gather_rows``."""
+    if not _native(src):
+        out = torch.zeros((n_rows, src.shape[1]), dtype=src.dtype, device=src.device)
+        out[rows] = src
+        return out
+    out = torch.empty((n_rows, src.shape[1]), dtype=src.dtype, device=src.device)
+    _lib.check(_lib.kernels().b200_scatter_rows(_lib.ptr(rows), _lib.ptr(src), _lib.ptr(out), rows.numel(), src.shape[1],
+                                                n_rows, _lib.stream()), "b200_scatter_rows")
+    return out
+
+
+class GatherRowsFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, rows):
+        ctx.save_for_backward(rows)
+        ctx.n = x.shape[0]
+        return gather_rows(x, rows)
+
+    @staticmethod
+    def backward(ctx, dout):
+        (rows,) = ctx.saved_tensors
+        return scatter_rows(dout.contiguous(), rows, ctx.n), None
+
+
 # ------------------------------------------------------------------------------------------------ casts
 def cast_to_bf16(src_f32: torch.Tensor, dst_bf16: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
     if not _native(src_f32):
