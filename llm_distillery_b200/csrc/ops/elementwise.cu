@@ -164,14 +164,23 @@ __global__ void __launch_bounds__(NT) rmsnorm_bwd_kernel(const __nv_bfloat16* __
   }
 }
 
-// out[j] (+)= sum_b partial[b][j]
-__global__ void colsum_kernel(const float* __restrict__ partial, float* __restrict__ out, int nblk, int h,
-                              int accumulate) {
-  const int j = blockIdx.x * blockDim.x + threadIdx.x;
-  if (j >= h) return;
+// out[j] (+)= sum_b partial[b][j]; block = 32 columns x 8 row groups, reduced through shared memory
+__global__ void __launch_bounds__(256) colsum_kernel(const float* __restrict__ partial, float* __restrict__ out,
+                                                     int nblk, int h, int accumulate) {
+  __shared__ float red[8][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int j = blockIdx.x * 32 + tx;
   float s = 0.f;
-  for (int b = 0; b < nblk; ++b) s += partial[(size_t)b * h + j];
-  out[j] = accumulate ? out[j] + s : s;
+  if (j < h)
+    for (int b = ty; b < nblk; b += 8) s += partial[(size_t)b * h + j];
+  red[ty][tx] = s;
+  __syncthreads();
+  if (ty == 0 && j < h) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) t += red[k][tx];
+    out[j] = accumulate ? out[j] + t : t;
+  }
 }
 
 // Rotary embedding, HF Llama convention (pairs (i, i + d/2)), in place on x[T, nh, d].
@@ -357,7 +366,7 @@ using namespace b200::ew;
 
 // Number of fp32 partial rows rmsnorm_bwd needs in `dw_partial` ([blocks, h]).
 int b200_rmsnorm_bwd_blocks(int rows) {
-  const int cap = sm_count() * 2;
+  const int cap = sm_count() * 8;  // 8 resident 256-thread CTAs per SM keep HBM busy; partial rows stay small
   return rows < cap ? rows : cap;
 }
 
@@ -380,7 +389,7 @@ int b200_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* 
   rmsnorm_bwd_kernel<<<grid, NT, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
                                           rstd, (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, dw_partial, rows, h);
   B200_CUDA_CHECK(cudaGetLastError());
-  colsum_kernel<<<ceil_div(h, 128), 128, 0, st>>>(dw_partial, dw_out, grid, h, dw_accumulate);
+  colsum_kernel<<<ceil_div(h, 32), 256, 0, st>>>(dw_partial, dw_out, grid, h, dw_accumulate);
   B200_CUDA_CHECK(cudaGetLastError());
   return B200_OK;
 }

@@ -190,7 +190,7 @@ class DecoderLayerFn(torch.autograd.Function):
         if recompute:   # gradient checkpointing: keep only the layer input
             ctx.save_for_backward(h, pos, cos, sin)
         else:
-            ctx.save_for_backward(h, pos, cos, sin, rstd1, n1, qkv, att, lse, h1, rstd2, n2, gu)
+            ctx.save_for_backward(h, pos, cos, sin, rstd1, n1, qkv, att, lse, h1, rstd2, n2, gu, act)
         return h2
 
     @staticmethod
@@ -207,11 +207,11 @@ class DecoderLayerFn(torch.autograd.Function):
             h1 = basic.linear_fwd(att, w_o, residual=h)
             n2, _, rstd2 = basic.rmsnorm_fwd(h1, w_ln2, eps)
             gu = basic.linear_fwd(n2, w_gu)
+            act = basic.swiglu_fwd(gu)
         else:
-            h, pos, cos, sin, rstd1, n1, qkv, att, lse, h1, rstd2, n2, gu = ctx.saved_tensors
+            h, pos, cos, sin, rstd1, n1, qkv, att, lse, h1, rstd2, n2, gu, act = ctx.saved_tensors
         dh2 = dh2.contiguous()
         # MLP branch
-        act = basic.swiglu_fwd(gu)
         g_d = _wgrad(dh2, act, w_d, s_d)
         dact = basic.linear_dgrad(dh2, w_d)
         del act

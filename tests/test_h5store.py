@@ -1,0 +1,148 @@
+"""C++ HDF5 store: round trips, metadata, rename/delete/merge, crash consistency, and a byte-level check of the
+emitted structures with an independent reader."""
+import os
+import shutil
+
+import numpy as np
+import pytest
+
+from llm_distillery_b200.data.convo import TeacherRows
+from llm_distillery_b200.data.h5store import H5Store, merge_topk
+from tests.h5_spec_reader import SpecReader
+
+
+def _rows(cid, n=37, K=16, V=500, seed=0, sample="s"):
+    rng = np.random.default_rng(seed + cid)
+    logits = rng.normal(size=(n, V)).astype(np.float32) * 3
+    lp = logits - np.log(np.exp(logits).sum(-1, keepdims=True))
+    idx = np.argsort(-lp, axis=1)[:, :K]
+    return TeacherRows(cid, np.take_along_axis(lp, idx, 1), idx.astype(np.int64), f"sha{cid:04d}" * 8, f"{sample}-{cid} é")
+
+
+def test_roundtrip_reopen_and_spec_reader(tmp_path):
+    st = H5Store(str(tmp_path))
+    data = {i: _rows(i, n=5 + 3 * i) for i in [0, 1, 2, 10, 33, 7]}
+    st.write_batch(list(data.values()))
+    st.set_vocab_family("llama_3")
+    st.set_topk(16)
+    st.wait()
+    assert sorted(st.get_dataset_ids()) == sorted(data)
+    for i, r in data.items():
+        v, ix = st.load_id(i)
+        assert v.dtype == np.float32 and ix.dtype == np.int64
+        assert np.array_equal(v, r.values.astype(np.float16).astype(np.float32)) and np.array_equal(ix, r.indices)
+    assert st.get_available_shas()[10] == data[10].content_sha
+    st.close()
+    st2 = H5Store(str(tmp_path))
+    assert st2.get_vocab_family() == "llama_3" and st2.get_topk() == 16 and st2.has_data()
+    v, ix = st2.load_id(33)
+    assert np.array_equal(ix, data[33].indices)
+    st2.close()
+    sr = SpecReader(os.path.join(str(tmp_path), "distributions.hdf5"))
+    root = sr.group(sr.root_hdr)
+    assert sorted(root) == sorted(f"convo_{i}" for i in data)
+    assert sr.attrs(sr.root_hdr) == {"vocab_family": "llama_3", "topk": 16}
+    g = sr.group(root["convo_10"])
+    assert sorted(g) == ["distributions", "indices"]
+    assert sr.attrs(root["convo_10"]) == {"content_sha": data[10].content_sha, "sample": data[10].sample}
+    assert np.array_equal(sr.dataset(g["distributions"]), data[10].values.astype(np.float16))
+    assert np.array_equal(sr.dataset(g["indices"]), data[10].indices.astype(np.uint32))
+
+
+def test_many_groups_multilevel_btree(tmp_path):
+    st = H5Store(str(tmp_path))
+    n = 1300   # > 32 * 32 links: forces a two-level group B-tree
+    st.write_batch([_rows(i, n=2, K=4, V=50) for i in range(n)])
+    st.close()
+    sr = SpecReader(os.path.join(str(tmp_path), "distributions.hdf5"))
+    assert len(sr.group(sr.root_hdr)) == n
+    st = H5Store(str(tmp_path))
+    assert sorted(st.get_dataset_ids()) == list(range(n))
+    v, ix = st.load_id(1299)
+    assert v.shape == (2, 4)
+    st.close()
+
+
+def test_delete_rename_swap_purge_update_sha(tmp_path):
+    st = H5Store(str(tmp_path))
+    st.write_batch([_rows(i) for i in range(6)])
+    st.wait()
+    ref = {i: st.load_id(i)[1] for i in range(6)}
+    st.sync([4, 5], {0: 1, 1: 0, 2: 9})        # swap 0<->1, move 2->9
+    assert sorted(st.get_dataset_ids()) == [0, 1, 3, 9]
+    assert np.array_equal(st.load_id(0)[1], ref[1]) and np.array_equal(st.load_id(1)[1], ref[0])
+    assert np.array_equal(st.load_id(9)[1], ref[2])
+    st.update_shas({3: "f" * 64, 77: "ignored"})
+    assert st.get_sha(3) == "f" * 64 and np.array_equal(st.load_id(3)[1], ref[3])
+    before = st.file_bytes()
+    st.repack()
+    assert st.file_bytes() < before and sorted(st.get_dataset_ids()) == [0, 1, 3, 9]
+    st.set_vocab_family("x"); st.set_topk(3)
+    st.purge_dataset(ask_confirmation=False)
+    assert not st.has_data() and st.get_vocab_family() is None and st.get_topk() is None
+    with pytest.raises(ValueError):
+        st.load_id(0)
+    st.close()
+
+
+def test_multi_teacher_merge_sums_probabilities(tmp_path):
+    a, b = _rows(0, n=9, seed=1), _rows(0, n=12, seed=2)
+    st = H5Store(str(tmp_path))
+    st.write_batch([a]); st.wait()
+    st.write_batch([b]); st.wait()
+    v, ix = st.load_id(0)
+    assert v.shape == (12, 16)
+    for r in range(9):
+        acc = {}
+        for src in (a, b):
+            for i, lp in zip(src.indices[r], src.values[r].astype(np.float16).astype(np.float32)):
+                acc[int(i)] = acc.get(int(i), 0.0) + float(np.exp(lp))
+        best = sorted(acc.items(), key=lambda kv: -kv[1])[:16]
+        assert set(int(x) for x in ix[r]) == {k for k, _ in best} or abs(best[15][1] - sorted(acc.values())[-17]) < 1e-6
+        got = dict(zip(ix[r].tolist(), np.exp(v[r]).tolist()))
+        for k, p in best[:8]:
+            assert abs(got[k] - p) < 3e-3 * max(p, 1e-3)
+    assert np.array_equal(ix[9:], b.indices[9:])
+    assert st.get_sha(0) == b.content_sha
+    st.close()
+    l, i = merge_topk(a.values, a.indices, a.values, a.indices)   # same teacher twice = doubled probabilities
+    assert np.allclose(np.sort(np.exp(l), 1), np.sort(2 * np.exp(a.values), 1), rtol=1e-5)
+
+
+def test_killed_before_flush_keeps_last_consistent_state(tmp_path):
+    st = H5Store(str(tmp_path))
+    st.write_batch([_rows(i) for i in range(3)])
+    st.wait()                                     # consistent state with 3 conversations
+    snap = str(tmp_path / "snap.hdf5")
+    st._put_one(_rows(3), True)                   # data appended, root not yet rewritten
+    shutil.copy(st.file_path, snap)               # what a kill -9 right now leaves on disk
+    st.close()
+    rec = H5Store(snap)
+    assert sorted(rec.get_dataset_ids()) == [0, 1, 2]
+    assert rec.load_id(2)[0].shape == (37, 16)
+    rec.write_batch([_rows(3)]); rec.wait()       # and the file keeps working
+    assert sorted(rec.get_dataset_ids()) == [0, 1, 2, 3]
+    rec.close()
+    # truncated tail (torn write) is also survivable: the superblock still points at the old root
+    with open(snap, "r+b") as f:
+        f.truncate(os.path.getsize(snap) - 0)
+    SpecReader(snap)
+
+
+def test_prefetch_batches_padded_sorted(tmp_path):
+    st = H5Store(str(tmp_path))
+    st.write_batch([_rows(i, n=4 + i) for i in range(8)])
+    st.wait()
+    st.enqueue_get_batches([[0, 1, 2], [3, 4]], sort_ids=True)
+    st.enqueue_get_batches([[5, 6, 7]], sort_ids=True)
+    b0, b1, b2 = st.read_next_batch(), st.read_next_batch(), st.read_next_batch()
+    assert b0["values"].shape == (3, 6, 16) and b0["lengths"] == [4, 5, 6] and b1["ids"] == [3, 4] and b2["ids"] == [5, 6, 7]
+    assert (b0["values"][0, 4:] == 0).all()
+    assert all((np.diff(ix, axis=1) > 0).all() for ix in b0["indices"])
+    v, ix = st.load_id(1)
+    o = np.argsort(ix, 1)
+    assert np.array_equal(b0["values"][1, :5], np.take_along_axis(v, o, 1))
+    st.read_only_mode([[0], [1]])
+    seen = [st.read_next_batch()["ids"][0] for _ in range(5)]
+    assert seen == [0, 1, 0, 1, 0]
+    st.close()
