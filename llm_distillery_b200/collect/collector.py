@@ -1,0 +1,85 @@
+"""Teacher collection on device: forward -> content rows -> LM head -> log-softmax -> top-K -> pinned host.
+
+What the reference does per batch (classes/teacher/inference_worker.py:66-85, result_processor_worker.py:27-58):
+full forward, ``[:, :, :crop].float()``, log_softmax over the cropped vocabulary, ``torch.topk``, copy EVERYTHING to
+the host, then keep the content positions on the CPU. Here the content rows are gathered on the device before
+the LM head, so the vocabulary-sized work is done only for rows that are kept; logits exist only for one row
+chunk at a time (fp32, sized to stay L2-resident) between the tcgen05 GEMM and the exact top-K kernel; fp16
+log-probs + int32 ids go to pinned host memory with an asynchronous copy.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from ..data.convo import ConvoTokenized, TeacherRows
+from ..ops import basic, topk as topk_ops
+
+
+class TeacherCollector:
+    def __init__(self, model, *, topk: int, crop_to_size: int, enable_topk: bool = True, logits_chunk_bytes: int = 96 << 20):
+        self.model = model
+        self.K = int(topk)
+        self.vocab = min(int(crop_to_size or model.cfg.vocab_size), model.cfg.vocab_size)
+        self.enable_topk = bool(enable_topk)
+        self.device = model.embed_tokens.device
+        self.chunk_rows = max(128, (logits_chunk_bytes // (4 * self.vocab)) // 128 * 128)
+
+    @torch.no_grad()
+    def content_logprobs(self, tokens: np.ndarray, convos: list[ConvoTokenized]):
+        """tokens [B, L] int64 (cropped to the longest member). Returns (values fp16 [M, K or Vc], ids int32 [M, K] or
+        None, rows_per_convo) as host tensors; M = total content rows of the batch."""
+        B, L = tokens.shape
+        ids = torch.from_numpy(np.ascontiguousarray(tokens)).to(self.device, non_blocking=True)
+        hs = self.model.hidden_states(ids)
+        rows, counts = [], []
+        for b, c in enumerate(convos):
+            ci = c.content_indices()
+            ci = ci[ci < min(c.length, L)]
+            rows.append(ci + b * L)
+            counts.append(len(ci))
+        rows_np = np.concatenate(rows) if rows else np.zeros(0, dtype=np.int64)
+        M = len(rows_np)
+        if M == 0:
+            return None, None, counts
+        rows_t = torch.from_numpy(rows_np).to(self.device, non_blocking=True)
+        Hc = basic.gather_rows(hs, rows_t)
+        W = self.model.lm_head[: self.vocab]
+        width = self.K if self.enable_topk else self.vocab
+        out_v = torch.empty((M, width), dtype=torch.float16, device=self.device)
+        out_i = torch.empty((M, self.K), dtype=torch.int32, device=self.device) if self.enable_topk else None
+        logits = torch.empty((min(self.chunk_rows, M), self.vocab), dtype=torch.float32, device=self.device)
+        for r0 in range(0, M, self.chunk_rows):
+            r1 = min(M, r0 + self.chunk_rows)
+            lg = logits[: r1 - r0]
+            if Hc.is_cuda and Hc.dtype in (torch.bfloat16, torch.float16):
+                basic.gemm(Hc[r0:r1], W, out=lg)
+            else:
+                lg.copy_(Hc[r0:r1].float() @ W.float().t())
+            if self.enable_topk:
+                v, i = topk_ops.topk_logprob(lg, self.vocab, self.K)
+                out_v[r0:r1], out_i[r0:r1] = v, i
+            else:
+                out_v[r0:r1] = topk_ops.logprob_full(lg, self.vocab)
+        pin = self.device.type == "cuda"
+        hv = torch.empty(out_v.shape, dtype=out_v.dtype, pin_memory=pin)
+        hv.copy_(out_v, non_blocking=True)
+        hi = None
+        if out_i is not None:
+            hi = torch.empty(out_i.shape, dtype=out_i.dtype, pin_memory=pin)
+            hi.copy_(out_i, non_blocking=True)
+        if pin:
+            torch.cuda.current_stream().synchronize()
+        return hv, hi, counts
+
+    def collect_batch(self, tokens: np.ndarray, convos: list[ConvoTokenized]) -> list[TeacherRows]:
+        hv, hi, counts = self.content_logprobs(tokens, convos)
+        out, r = [], 0
+        for c, n in zip(convos, counts):
+            if n == 0:
+                continue
+            vals = hv[r:r + n].numpy()
+            idx = None if hi is None else hi[r:r + n].numpy().astype(np.int64)
+            out.append(TeacherRows(c.origin_convo_id, vals, idx, c.content_sha, c.sample))
+            r += n
+        return out

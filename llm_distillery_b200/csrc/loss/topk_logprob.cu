@@ -1,0 +1,278 @@
+// Exact per-row top-K of log_softmax(logits[:, :V]) for teacher collection, and the multi-teacher top-K merge.
+//
+// topk_logprob: one CTA per row over fp32 logits (the row chunk just written by the LM-head GEMM, L2 resident):
+//   1. max and sum-exp                                  -> lse
+//   2. 4-pass 8-bit radix select on order-preserving keys -> exact K-th largest value and how many ties to keep
+//   3. gather: everything above the threshold, plus the lowest-index ties
+//   4. bitonic sort in shared memory by (value desc, index asc) - the order torch.topk users expect
+//   5. write fp16 log-probs (value - lse) and int32 ids
+// Output layout matches the HDF5 datasets: [rows, K] fp16 + [rows, K] int32.
+//
+// topk_merge: per row, union of two top-K lists with probabilities of equal ids summed, best K kept, log stored
+// (the multi-teacher rule of the data store), sorted by value.
+#include "../common/ptx.cuh"
+#include "../common/host.cuh"
+
+namespace b200 {
+namespace topk {
+
+constexpr int NT = 256;
+constexpr int MAX_K = 1024;
+constexpr int TIE_CAP = 1024;
+
+__device__ __forceinline__ uint32_t fkey(float x) {
+  uint32_t k = __float_as_uint(x);
+  return (k & 0x80000000u) ? ~k : (k | 0x80000000u);
+}
+__device__ __forceinline__ float kfloat(uint32_t k) {
+  return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+}
+
+// descending bitonic sort of n (power of two) 64-bit keys in shared memory
+__device__ void bitonic_desc(unsigned long long* s, int n) {
+  for (int k = 2; k <= n; k <<= 1) {
+    for (int j = k >> 1; j > 0; j >>= 1) {
+      for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const int ixj = i ^ j;
+        if (ixj > i) {
+          const unsigned long long a = s[i], b = s[ixj];
+          const bool desc = ((i & k) == 0);
+          if (desc ? (a < b) : (a > b)) { s[i] = b; s[ixj] = a; }
+        }
+      }
+      __syncthreads();
+    }
+  }
+}
+
+__global__ void __launch_bounds__(NT) topk_logprob_kernel(const float* __restrict__ logits, long long ld, int V, int K,
+                                                         __half* __restrict__ out_logp, int* __restrict__ out_idx) {
+  __shared__ unsigned long long sel[MAX_K];
+  __shared__ unsigned int hist[256];
+  __shared__ unsigned int ties[TIE_CAP];
+  __shared__ float redf[NT / 32];
+  __shared__ unsigned int s_prefix, s_remaining, s_nsel, s_nties;
+  __shared__ float s_max, s_lse;
+  const long long row = blockIdx.x;
+  const float* x = logits + row * ld;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+  // 1. max, sum-exp
+  float mx = -INFINITY;
+  for (int i = tid; i < V; i += NT) mx = fmaxf(mx, x[i]);
+  mx = warp_max(mx);
+  if (lane == 0) redf[warp] = mx;
+  __syncthreads();
+  if (tid == 0) { float m = redf[0]; for (int w = 1; w < NT / 32; ++w) m = fmaxf(m, redf[w]); s_max = m; }
+  __syncthreads();
+  mx = s_max;
+  float sm = 0.f;
+  for (int i = tid; i < V; i += NT) sm += __expf(x[i] - mx);
+  sm = warp_sum(sm);
+  __syncthreads();
+  if (lane == 0) redf[warp] = sm;
+  __syncthreads();
+  if (tid == 0) {
+    float t = 0.f;
+    for (int w = 0; w < NT / 32; ++w) t += redf[w];
+    s_lse = mx + __logf(t);
+    s_prefix = 0; s_remaining = (unsigned)K; s_nsel = 0; s_nties = 0;
+  }
+  __syncthreads();
+
+  // 2. radix select: after the loop s_prefix is the key of the K-th largest element and s_remaining (>= 1) is
+  //    how many elements equal to it belong to the top K
+  for (int pass = 0; pass < 4; ++pass) {
+    const int shift = 24 - 8 * pass;
+    const uint32_t mask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
+    const uint32_t prefix = s_prefix;
+    hist[tid] = 0;
+    __syncthreads();
+    for (int i = tid; i < V; i += NT) {
+      const uint32_t k = fkey(x[i]);
+      if ((k & mask) == prefix) atomicAdd(&hist[(k >> shift) & 0xffu], 1u);
+    }
+    __syncthreads();
+    if (tid == 0) {
+      unsigned rem = s_remaining, cum = 0;
+      int b = 255;
+      for (; b > 0; --b) {
+        if (cum + hist[b] >= rem) break;
+        cum += hist[b];
+      }
+      s_prefix = prefix | ((uint32_t)b << shift);
+      s_remaining = rem - cum;
+    }
+    __syncthreads();
+  }
+  const uint32_t thr = s_prefix;
+  const unsigned need_eq = s_remaining;
+
+  // 3. gather
+  for (int i = tid; i < V; i += NT) {
+    const uint32_t k = fkey(x[i]);
+    if (k > thr) {
+      const unsigned p = atomicAdd(&s_nsel, 1u);
+      if (p < MAX_K) sel[p] = ((unsigned long long)k << 32) | (0xffffffffu - (uint32_t)i);
+    } else if (k == thr) {
+      const unsigned p = atomicAdd(&s_nties, 1u);
+      if (p < TIE_CAP) ties[p] = (uint32_t)i;
+    }
+  }
+  __syncthreads();
+  const unsigned ngt = s_nsel;
+  unsigned nt = s_nties;
+  if (nt > TIE_CAP) {
+    // pathological row (more than TIE_CAP equal values at the threshold): ordered sequential pick
+    if (tid == 0) {
+      unsigned got = 0;
+      for (int i = 0; i < V && got < need_eq; ++i)
+        if (fkey(x[i]) == thr) sel[ngt + got++] = ((unsigned long long)thr << 32) | (0xffffffffu - (uint32_t)i);
+    }
+  } else {
+    // keep the need_eq lowest indices among the ties: rank each tie by counting smaller indices
+    for (unsigned t = tid; t < nt; t += NT) {
+      const uint32_t me = ties[t];
+      unsigned rank = 0;
+      for (unsigned u = 0; u < nt; ++u) rank += (ties[u] < me) ? 1u : 0u;
+      if (rank < need_eq) sel[ngt + rank] = ((unsigned long long)thr << 32) | (0xffffffffu - me);
+    }
+  }
+  __syncthreads();
+
+  // 4. sort (pad to a power of two with zeros, which sort last)
+  int n2 = 1;
+  while (n2 < K) n2 <<= 1;
+  for (int i = K + tid; i < n2; i += NT) sel[i] = 0ull;
+  __syncthreads();
+  bitonic_desc(sel, n2);
+
+  // 5. write
+  const float lse = s_lse;
+  for (int i = tid; i < K; i += NT) {
+    const unsigned long long e = sel[i];
+    out_logp[row * K + i] = __float2half(kfloat((uint32_t)(e >> 32)) - lse);
+    out_idx[row * K + i] = (int)(0xffffffffu - (uint32_t)(e & 0xffffffffu));
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- merge
+// a_*, b_*: [rows, K] (log-prob fp32, id int32). out: union with summed probabilities, best K, sorted by value desc.
+__global__ void __launch_bounds__(NT) topk_merge_kernel(const float* __restrict__ a_lp, const int* __restrict__ a_id,
+                                                       const float* __restrict__ b_lp, const int* __restrict__ b_id,
+                                                       int K, float* __restrict__ o_lp, int* __restrict__ o_id) {
+  __shared__ unsigned long long s[2 * MAX_K];
+  __shared__ float pv[2 * MAX_K];
+  const long long row = blockIdx.x;
+  const int n = 2 * K;
+  int n2 = 1;
+  while (n2 < n) n2 <<= 1;
+  // sort by id (key = id << 32 | slot), carrying probabilities in pv[slot]
+  for (int i = threadIdx.x; i < n2; i += NT) {
+    if (i < n) {
+      const bool first = i < K;
+      const int id = first ? a_id[row * K + i] : b_id[row * K + i - K];
+      pv[i] = __expf(first ? a_lp[row * K + i] : b_lp[row * K + i - K]);
+      s[i] = ((unsigned long long)(uint32_t)id << 32) | (uint32_t)i;
+    } else {
+      s[i] = 0ull;
+    }
+  }
+  __syncthreads();
+  bitonic_desc(s, n2);  // equal ids are now adjacent (descending id), padding zeros last... id 0 handled via slot
+  __syncthreads();
+  // combine duplicates: the first of an equal-id pair takes the sum, the second is dropped
+  __shared__ float comb[2 * MAX_K];
+  for (int i = threadIdx.x; i < n; i += NT) {
+    const uint32_t id = (uint32_t)(s[i] >> 32);
+    const float p = pv[(uint32_t)s[i]];
+    const bool dup_prev = (i > 0) && ((uint32_t)(s[i - 1] >> 32) == id);
+    const bool dup_next = (i + 1 < n) && ((uint32_t)(s[i + 1] >> 32) == id);
+    comb[i] = dup_prev ? -1.f : (dup_next ? p + pv[(uint32_t)s[i + 1]] : p);
+  }
+  __syncthreads();
+  // re-key by probability (desc), tie-break by lower id
+  for (int i = threadIdx.x; i < n2; i += NT) {
+    if (i < n && comb[i] >= 0.f) {
+      const uint32_t id = (uint32_t)(s[i] >> 32);
+      s[i] = ((unsigned long long)fkey(comb[i]) << 32) | (0xffffffffu - id);
+    } else {
+      s[i] = 0ull;
+    }
+  }
+  __syncthreads();
+  bitonic_desc(s, n2);
+  for (int i = threadIdx.x; i < K; i += NT) {
+    const unsigned long long e = s[i];
+    const float p = e ? kfloat((uint32_t)(e >> 32)) : 0.f;
+    o_lp[row * K + i] = __logf(p);
+    o_id[row * K + i] = e ? (int)(0xffffffffu - (uint32_t)e) : 0;
+  }
+}
+
+}  // namespace topk
+}  // namespace b200
+
+extern "C" {
+using namespace b200;
+
+// logits: fp32 [rows, >=V] with row stride ld (elements). out_logp fp16 [rows, K], out_idx int32 [rows, K].
+int b200_topk_logprob(const float* logits, long long ld, int rows, int V, int K, void* out_logp, int* out_idx,
+                      cudaStream_t st) {
+  if (!logits || !out_logp || !out_idx || rows <= 0 || V <= 0 || K <= 0 || K > topk::MAX_K || K > V)
+    return K > topk::MAX_K ? B200_ERR_TOO_BIG : B200_ERR_ARG;
+  topk::topk_logprob_kernel<<<rows, topk::NT, 0, st>>>(logits, ld, V, K, (__half*)out_logp, out_idx);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200_OK;
+}
+
+int b200_topk_merge(const float* a_lp, const int* a_id, const float* b_lp, const int* b_id, int rows, int K,
+                    float* o_lp, int* o_id, cudaStream_t st) {
+  if (!a_lp || !a_id || !b_lp || !b_id || !o_lp || !o_id || rows <= 0 || K <= 0 || K > topk::MAX_K)
+    return K > topk::MAX_K ? B200_ERR_TOO_BIG : B200_ERR_ARG;
+  topk::topk_merge_kernel<<<rows, topk::NT, 0, st>>>(a_lp, a_id, b_lp, b_id, K, o_lp, o_id);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200_OK;
+}
+}
+
+namespace b200 {
+namespace topk {
+// out[row, j] = fp16(x[row, j] - lse(row))  for j < V : full-vocabulary log-probabilities (top-K storage disabled)
+__global__ void __launch_bounds__(NT) logprob_full_kernel(const float* __restrict__ logits, long long ld, int V,
+                                                         __half* __restrict__ out, long long ldo) {
+  __shared__ float redf[NT / 32];
+  __shared__ float s_max, s_lse;
+  const long long row = blockIdx.x;
+  const float* x = logits + row * ld;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  float mx = -INFINITY;
+  for (int i = tid; i < V; i += NT) mx = fmaxf(mx, x[i]);
+  mx = warp_max(mx);
+  if (lane == 0) redf[warp] = mx;
+  __syncthreads();
+  if (tid == 0) { float m = redf[0]; for (int w = 1; w < NT / 32; ++w) m = fmaxf(m, redf[w]); s_max = m; }
+  __syncthreads();
+  mx = s_max;
+  float sm = 0.f;
+  for (int i = tid; i < V; i += NT) sm += __expf(x[i] - mx);
+  sm = warp_sum(sm);
+  __syncthreads();
+  if (lane == 0) redf[warp] = sm;
+  __syncthreads();
+  if (tid == 0) { float t = 0.f; for (int w = 0; w < NT / 32; ++w) t += redf[w]; s_lse = mx + __logf(t); }
+  __syncthreads();
+  const float lse = s_lse;
+  for (int i = tid; i < V; i += NT) out[row * ldo + i] = __float2half(x[i] - lse);
+}
+}  // namespace topk
+}  // namespace b200
+
+extern "C" int b200_logprob_full(const float* logits, long long ld, int rows, int V, void* out, long long ldo,
+                                 cudaStream_t st) {
+  using namespace b200;
+  if (!logits || !out || rows <= 0 || V <= 0) return B200_ERR_ARG;
+  topk::logprob_full_kernel<<<rows, topk::NT, 0, st>>>(logits, ld, V, (__half*)out, ldo);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200_OK;
+}

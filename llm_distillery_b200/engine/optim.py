@@ -80,6 +80,18 @@ class FlatParams:
                 self.slots.append(slot)
         self.master = self.model[self.shard_lo:self.shard_lo + self.shard_size].float().clone()
 
+    def absorb_autograd_grads(self) -> None:
+        """Fold gradients that autograd left in ``p.grad`` (ops without a fused wgrad epilogue, e.g. the PyTorch
+        restatement of the loss head on CPU) into the flat fp32 gradient."""
+        for p, s in zip(self.params, self.slots):
+            if p.grad is not None:
+                if s.fresh:
+                    s.buf.copy_(p.grad)
+                    s.fresh = False
+                else:
+                    s.buf.add_(p.grad)
+                p.grad = None
+
     def mark_fresh(self) -> None:
         for s in self.slots:
             s.fresh = True

@@ -89,6 +89,7 @@ class DistillEngine:
     def micro_step(self, mb: HostBatch):
         loss, logs = self.loss_on_batch(mb)
         loss.backward()
+        self.flat.absorb_autograd_grads()
         self.micro_in_step += 1
         return loss.detach(), logs
 

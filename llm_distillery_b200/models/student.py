@@ -1,0 +1,321 @@
+"""Student role: trains the student against the stored teacher distributions.
+
+Bookkeeping follows the reference exactly (collect_and_finetune.py:178-208, classes/student/model.py:319-532):
+every "step" counter is in SAMPLES (conversations), an optimizer step happens whenever the number of trained
+samples reaches the next multiple of ``grad_accum * batch_size``, validation runs at step 0 and every
+``validate_every_n_epochs * dataset_len`` samples on an endlessly cycling validation reader, checkpoints are
+HF folders ``<cache>/student/trained/<model>_step_<N|final>``, and in chunked mode the trainer state is saved
+after every chunk and restored at the next one.
+
+What differs: the model, loss head and optimizer are this package's kernels driven by ``DistillEngine``; the
+per-conversation Python loss loop is one fused head call per micro-batch; teacher batches arrive from a prefetch
+thread in pinned memory; with several ranks each rank trains a different batch of the same global step and the
+engine's communicator reduces the gradients; trainer state also resumes across process restarts.
+"""
+from __future__ import annotations
+
+import math
+import os
+import time
+
+import numpy as np
+import torch
+
+from ..ckpt import hf as ckpt
+from ..engine.schedule import set_lr_scheduler
+from ..engine.trainer import DistillEngine, HostBatch
+from ..obs.console import progress
+from ..obs.metrics import Losses, MetricsLogger
+from .base_model import BaseModel
+
+
+class StudentModel(BaseModel):
+    def __init__(self, model_path: str, paths, add_bos: bool, prompt_format: dict, batch_size: int,
+                 interactive: bool = False):
+        super().__init__(model_path, student=True, interactive=interactive)
+        self.model = None
+        self.engine: DistillEngine | None = None
+        self.tokenizer_dir = self.model_path
+        self.add_bos = add_bos
+        self.prompt_format = prompt_format
+        self.batch_size = batch_size
+        self.paths = paths
+        self.losses: Losses | None = None
+        self.logger: MetricsLogger | None = None
+        # hyper-parameters (set by cli.set_training_params)
+        self.optimizer_name = "adamw"
+        self.lr_scheduler_name = "wsd"
+        self.lr = 0.0
+        self.decay_start = 0.9
+        self.final_lr = 5e-7
+        self.alpha = 2.0
+        self.loss_kind = "reference"
+        self.num_epochs = 0
+        self.total_training_steps = 0
+        self.num_warmup_steps = 0
+        self.grad_accum = 1
+        self.num_grad_accum_batches = 0
+        self.eff_batch_size = 0
+        self.validation_every_steps = 0
+        self.save_every_steps = 0
+        # progress
+        self.next_save_step = 0
+        self.num_trained_steps = 0
+        self.next_val_step = 0
+        self.next_accum_step = 0
+        self.saved_state = False
+        self.val_batch_order_ids: list = []
+        # misc
+        self.freeze_layers: list = []
+        self.training_precision_name = "bf16"
+        self.data_order = "sorted"
+        self.save_final_state = False
+        self.grad_checkpointing = False
+        self.multi_gpu = False
+        self.use_fa2 = True
+        self.wandb_comment = ""
+        self.device_map_name = ""
+        self.max_memory: dict = {}
+        self.num_gpu0_layers = 0
+        self.metrics_backend = "jsonl"
+        self.comm = None           # parallel communicator (None = single GPU)
+        self.rank, self.world = 0, 1
+        self.seed = 0
+        self.tokens_trained = 0
+        self.train_seconds = 0.0
+        self._rng = np.random.default_rng(0)
+
+    # ------------------------------------------------------------------ model / optimizer
+    def _dtype(self, device: torch.device) -> torch.dtype:
+        """Compute dtype. On a GPU every precision name runs the bf16 tensor-core kernels with fp32 master
+        weights and optimizer state (fp16 / bitsandbytes 4-bit / 8-bit weights have no counterpart here);
+        on CPU everything is fp32."""
+        return torch.bfloat16 if device.type == "cuda" else torch.float32
+
+    def _load_model(self) -> None:
+        dev = torch.device(self.device)
+        self.model = ckpt.load_hf_model(self.model_path, dtype=self._dtype(dev), device=dev)
+        self.model.grad_checkpointing = bool(self.grad_checkpointing)
+        if self.freeze_layers:
+            self.model.apply_freeze(self.freeze_layers)
+        schedule = set_lr_scheduler(self.lr_scheduler_name, self.lr, self.num_warmup_steps, self.num_grad_accum_batches,
+                                    self.decay_start, self.final_lr)
+        self.engine = DistillEngine(self.model, loss=self.loss_kind, temperature=self.temperature, alpha=self.alpha,
+                                    crop_to_size=self.crop_to_size, optimizer=self.optimizer_name, lr=self.lr,
+                                    betas=(0.9, 0.99), weight_decay=2e-8, grad_accum=self.grad_accum, schedule=schedule,
+                                    comm=self.comm)
+
+    def _unload_model(self) -> None:
+        self.model = None
+        self.engine = None
+        if torch.cuda.is_available():
+            torch.cuda.empty_cache()
+
+    # ------------------------------------------------------------------ data order / batching
+    def reorder_dataset(self) -> None:
+        if self.dataset_sorted:
+            return
+        if self.data_order == "shuffle":
+            self._rng.shuffle(self.dataset)
+        elif self.data_order == "sorted":
+            self.dataset.sort(key=lambda c: c.length, reverse=True)
+            self.dataset_sorted = True
+        elif self.data_order == "native":
+            self.dataset_sorted = True
+
+    def _construct_batches(self, dataset_chunk):
+        n = math.ceil(len(dataset_chunk) / self.batch_size)
+        convo_batches = [dataset_chunk[i * self.batch_size:(i + 1) * self.batch_size] for i in range(n)]
+        return convo_batches, [[c.origin_convo_id for c in b] for b in convo_batches]
+
+    def _my_share(self, convo_batches, id_batches):
+        """Global step t trains batches t*world .. t*world+world-1, one per rank. Returns this rank's batches (None
+        where the last global step has no batch for it) and the sample count of every global step."""
+        w = self.world
+        steps = math.ceil(len(convo_batches) / w)
+        mine, mine_ids, sizes = [], [], []
+        for t in range(steps):
+            group = convo_batches[t * w:(t + 1) * w]
+            sizes.append(sum(len(b) for b in group))
+            mine.append(group[self.rank] if self.rank < len(group) else None)
+            if self.rank < len(group):
+                mine_ids.append(id_batches[t * w + self.rank])
+        return mine, mine_ids, sizes
+
+    def build_host_batch(self, convos, teacher: dict) -> HostBatch:
+        """Assemble one micro-batch from tokenised conversations and their stored teacher rows."""
+        L = max(c.length for c in convos)
+        tokens = np.stack([c.tokenized[:L] for c in convos])
+        rows, ids, logp, seg, labels, avoid = [], [], [], [], [], []
+        need_ce = self.loss_kind == "reference"
+        for b, c in enumerate(convos):
+            ci = c.content_indices()
+            ci = ci[ci < L]
+            t_ids = teacher["indices"][b]
+            n = min(len(ci), teacher["lengths"][b], len(t_ids) if t_ids is not None else len(ci))
+            if n <= 0:
+                continue
+            rows.append(ci[:n] + b * L)
+            vals = teacher["values"][b][:n]
+            if t_ids is None:                      # full-distribution dataset: every id of the cropped vocabulary
+                t_ids = np.broadcast_to(np.arange(vals.shape[1], dtype=np.int64), vals.shape)
+            ids.append(np.asarray(t_ids[:n], dtype=np.int32))
+            logp.append(vals.astype(np.float32))
+            seg.append(np.full(n, b, dtype=np.int64))
+            if need_ce:
+                ce_idx, av = c.ce_indices(self.context_len)
+                lab = np.full(n, -1, dtype=np.int64)
+                m = min(n, len(ce_idx))
+                ok = ce_idx[:m] < L
+                lab[:m][ok] = c.tokenized[ce_idx[:m][ok]]
+                labels.append(lab)
+                a = np.zeros(n, dtype=bool)
+                a[av[av < n]] = True
+                avoid.append(a)
+        cat = lambda xs, dt: torch.from_numpy(np.ascontiguousarray(np.concatenate(xs)).astype(dt, copy=False))  # noqa: E731
+        hb = HostBatch(input_ids=torch.from_numpy(np.ascontiguousarray(tokens)), ids=cat(ids, np.int32),
+                       logp=cat(logp, np.float32), seg=cat(seg, np.int64), n_seg=len(convos),
+                       rows=cat(rows, np.int64), labels=cat(labels, np.int64) if need_ce else None,
+                       avoid=cat(avoid, bool) if need_ce else None, n_tokens=int(tokens.size))
+        return hb.pin() if torch.device(self.device).type == "cuda" else hb
+
+    # ------------------------------------------------------------------ checkpoints
+    def _save_model(self, step) -> None:
+        if self.rank != 0:
+            return
+        folder = os.path.join(self.paths.student_trained, f"{self.model_name}_step_{step}")
+        ckpt.save_hf_model(self.model, folder, tokenizer_src=self.tokenizer_dir)
+
+    def _counters(self) -> dict:
+        return {"num_trained_steps": self.num_trained_steps, "next_save_step": self.next_save_step,
+                "next_val_step": self.next_val_step, "next_accum_step": self.next_accum_step,
+                "total_training_steps": self.total_training_steps, "seed": self.seed, "world": self.world}
+
+    def _save_state(self) -> None:
+        if self.num_trained_steps < self.total_training_steps and self.rank == 0:
+            self.paths.empty_student_states()
+        if self.comm is not None:
+            self.comm.barrier()
+        if self.rank == 0 or (self.comm is not None and self.comm.shards_optimizer):
+            ckpt.save_trainer_state(self.paths.student_states, self.model, self.engine.opt, self.engine.schedule,
+                                    self._counters())
+
+    def _load_state(self) -> None:
+        self._load_model()
+        c = ckpt.load_trainer_state(self.paths.student_states, self.model, self.engine.opt, self.engine.schedule)
+        for k in ("num_trained_steps", "next_save_step", "next_val_step", "next_accum_step"):
+            if k in c:
+                setattr(self, k, c[k])
+
+    # ------------------------------------------------------------------ training
+    def _prefetch_dataset_chunk(self, data_manager, data_list, full_collect, trainable_ids):
+        self.reorder_dataset()
+        chunk = self.dataset if full_collect else [c for c in self.dataset if c.origin_convo_id in trainable_ids]
+        convo_batches, id_batches = self._construct_batches(chunk)
+        mine, mine_ids, sizes = self._my_share(convo_batches, id_batches)
+        data_list.append((mine, sizes))
+        data_manager.enqueue_get_batches(mine_ids, sort_ids=True)
+        return data_list
+
+    def train_chunk(self, data_manager, validation_data_manager, full_collect: bool) -> None:
+        trainable_ids = set(data_manager.get_dataset_ids())
+        if not self.validation_dataset_sorted:
+            self.validation_dataset.sort(key=lambda c: c.length, reverse=True)
+            self.validation_dataset_sorted = True
+            self.validation_dataset_batched, self.val_batch_order_ids = self._construct_batches(self.validation_dataset)
+            if self.val_batch_order_ids:
+                validation_data_manager.read_only_mode(self.val_batch_order_ids, sort_ids=True)
+        if self.logger is None and self.rank == 0:
+            name = f"{self.wandb_comment} " if self.wandb_comment else ""
+            short = self.model_name if len(self.model_name) <= 20 else f"{self.model_name[:20]}..."
+            name += f"{short} lr({self.lr}) ({time.strftime('%d.%m.%Y / %H:%M:%S')})"
+            cfg = {k: v for k, v in self.__dict__.items() if isinstance(v, (int, float, str, bool, list, dict))}
+            self.logger = MetricsLogger(self.paths.cache, self.metrics_backend, run_name=name, config=cfg,
+                                        group=self.model_name)
+        resume = self.saved_state or (self.num_trained_steps == 0 and ckpt.has_trainer_state(self.paths.student_states)
+                                      and os.environ.get("B200_RESUME", "1") == "1")
+        if resume:
+            self._load_state()
+            self.saved_state = False
+        else:
+            self._load_model()
+        if self.losses is None:
+            self.losses = Losses(self.logger)
+        self.progress_bar = progress(total=self.total_training_steps, initial=self.num_trained_steps, desc="Training",
+                                     leave=False)
+        if self.num_trained_steps == 0:
+            self._validate_distillation(validation_data_manager)
+        t0 = time.time()
+        data_list = self._prefetch_dataset_chunk(data_manager, [], full_collect, trainable_ids)
+        updated = True
+        if full_collect:
+            epochs_left = max(0, math.ceil((self.total_training_steps - self.num_trained_steps) / max(1, self.dataset_len)))
+            for e in range(epochs_left):
+                if e + 1 < epochs_left:
+                    data_list = self._prefetch_dataset_chunk(data_manager, data_list, full_collect, trainable_ids)
+                updated = self._run_distillation_cycle(data_list.pop(0), data_manager, validation_data_manager)
+        else:
+            updated = self._run_distillation_cycle(data_list.pop(0), data_manager, validation_data_manager)
+        if not updated:
+            self._optimizer_step()
+        self.train_seconds += time.time() - t0
+        if not full_collect:
+            self._save_state()
+            self.saved_state = True
+        if self.num_trained_steps >= self.total_training_steps:
+            self._save_model("final")
+            if self.save_final_state:
+                self._save_state()
+                self.saved_state = True
+        self.progress_bar.close()
+        self._unload_model()
+
+    def _optimizer_step(self) -> None:
+        lr = self.engine.lr
+        self.engine.optimizer_step()
+        if self.logger is not None:
+            self.logger.log({"Learning Rate": lr}, self.num_trained_steps)
+        self.losses.log(self.num_trained_steps)
+        self.losses.empty()
+
+    def _run_distillation_cycle(self, cycle, data_manager, validation_data_manager) -> bool:
+        batches, sizes = cycle
+        updated = False
+        for convos, n_samples in zip(batches, sizes):
+            updated = False
+            if convos is not None:
+                teacher = data_manager.read_next_batch()
+                hb = self.build_host_batch(convos, teacher)
+                mb = hb.to_device(self.engine.device)
+                loss, logs = self.engine.micro_step(mb)
+                self.losses.add_losses(logs, count=len(convos))
+                self.tokens_trained += hb.n_tokens
+            self.progress_bar.update(n_samples)
+            self.num_trained_steps += n_samples
+            if self.num_trained_steps >= self.next_accum_step:
+                self._optimizer_step()
+                updated = True
+                self.next_accum_step += self.eff_batch_size
+            if self.num_trained_steps >= self.next_save_step and self.num_trained_steps < self.total_training_steps:
+                self._save_model(self.num_trained_steps)
+                self.next_save_step += self.save_every_steps
+            if self.num_trained_steps >= self.next_val_step:
+                self._validate_distillation(validation_data_manager)
+        return updated
+
+    @torch.no_grad()
+    def _validate_distillation(self, validation_data_manager) -> None:
+        losses = Losses(self.logger, validation=True)
+        for convos in self.validation_dataset_batched:
+            teacher = validation_data_manager.read_next_batch()
+            hb = self.build_host_batch(convos, teacher)
+            _, logs = self.engine.eval_batch(hb)
+            losses.add_losses(logs, count=len(convos))
+        losses.log(self.num_trained_steps)
+        self.last_validation = losses.averages()
+        self.next_val_step += self.validation_every_steps if self.validation_every_steps > 0 else float("inf")
+
+    def close(self) -> None:
+        if self.logger is not None:
+            self.logger.finish()
+            self.logger = None

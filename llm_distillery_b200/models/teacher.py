@@ -1,0 +1,101 @@
+"""Teacher role: collects next-token distributions for the conversations that are missing from the HDF5 store.
+
+Reference (classes/teacher/model.py + the three worker files): a batch-creator process, N spawned inference
+processes each holding an ExLlamaV2 replica, a result-processor process and the HDF5 server process, connected by
+Manager queues and POSIX shared memory. Here one process per GPU does all of it: batches are planned up front
+(length-sorted, cropped to the longest member, reference: batch_creator_worker.py:16-33), the model runs on the
+sm_100a kernels, content rows are selected on the device, and finished conversations go straight into the
+store's writer pool while the GPU computes the next batch. With several ranks, ``num_inference_workers`` becomes
+the number of data-parallel replicas: rank r takes batches r, r+world, ... and rank-local stores are not shared -
+each rank writes through the same HDF5 store only when it is rank 0 of its node (others send rows over the
+process group).
+"""
+from __future__ import annotations
+
+import math
+import time
+
+import numpy as np
+import torch
+
+from ..ckpt.hf import load_hf_model
+from ..collect.collector import TeacherCollector
+from ..obs.console import progress
+from .base_model import BaseModel
+
+
+def plan_batches(dataset_chunk, batch_size: int):
+    """Consecutive batches of a length-sorted chunk; every batch is cropped to its longest non-padded member."""
+    out = []
+    for i in range(0, len(dataset_chunk), batch_size):
+        convos = dataset_chunk[i:i + batch_size]
+        longest = max(c.length for c in convos)
+        out.append((np.stack([c.tokenized[:longest] for c in convos]), convos))
+    return out
+
+
+class TeacherModel(BaseModel):
+    def __init__(self, model_path: str, max_queue_size: int = 3, interactive: bool = False):
+        super().__init__(model_path, student=False, interactive=interactive)
+        self.max_queue_size = max_queue_size
+        self.model = None
+        self.dtype = torch.bfloat16
+        self.tokens_collected = 0
+        self.collect_seconds = 0.0
+
+    def _sort_datasets_by_len(self) -> None:
+        if not self.dataset_sorted:
+            self.dataset.sort(key=lambda c: c.length, reverse=True)
+            self.dataset_sorted = True
+        if not self.validation_dataset_sorted:
+            self.validation_dataset.sort(key=lambda c: c.length, reverse=True)
+            self.validation_dataset_sorted = True
+
+    def load(self, device=None):
+        if self.model is None:
+            dev = torch.device(device or self.device)
+            dtype = self.dtype if dev.type == "cuda" else torch.float32
+            self.model = load_hf_model(self.model_path, dtype=dtype, device=dev)
+            for p in self.model.parameters():
+                p.requires_grad_(False)
+        return self.model
+
+    def unload(self) -> None:
+        self.model = None
+        if torch.cuda.is_available():
+            torch.cuda.empty_cache()
+
+    def process_chunk(self, reserve_vram_gb=None, num_inference_workers: int = 1, ids_to_collect=None,
+                      data_manager=None, validation: bool = False, rank: int = 0, world: int = 1,
+                      sha_by_id: dict | None = None) -> int:
+        """Collect ``ids_to_collect`` into ``data_manager``. Returns the number of conversations written."""
+        self._sort_datasets_by_len()
+        wanted = set(ids_to_collect or [])
+        chunk = [c for c in (self.validation_dataset if validation else self.dataset) if c.origin_convo_id in wanted]
+        if not chunk:
+            return 0
+        model = self.load()
+        collector = TeacherCollector(model, topk=self.topK, crop_to_size=self.crop_to_size, enable_topk=self.enable_topK)
+        batches = plan_batches(chunk, max(1, self.batch_size))[rank::max(1, world)]
+        done = 0
+        t0 = time.time()
+        with progress(total=len(chunk), desc="Convos", leave=False) as bar:
+            bar.set_postfix_str("Generating...")
+            for tokens, convos in batches:
+                rows = collector.collect_batch(tokens, convos)
+                if sha_by_id:   # the store is keyed by the STUDENT's view of the text (that is what sync compares)
+                    for r in rows:
+                        r.content_sha = sha_by_id.get(r.convo_id, r.content_sha)
+                data_manager.write_batch(rows)          # asynchronous: compression + file IO overlap the next batch
+                self.tokens_collected += int(sum(c.length for c in convos))
+                done += len(rows)
+                bar.update(len(convos))
+        data_manager.wait()
+        self.collect_seconds += time.time() - t0
+        return done
+
+    def close(self) -> None:
+        self.unload()
+        self.dataset, self.validation_dataset = [], []
+        self.dataset_len = 0
+        self.dataset_sorted = self.validation_dataset_sorted = False

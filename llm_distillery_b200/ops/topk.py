@@ -1,0 +1,59 @@
+"""Top-K log-prob extraction and multi-teacher top-K merge (csrc/loss/topk_logprob.cu) with PyTorch restatements."""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from ._lib import _VP, _I, _LL
+
+_lib.register("b200_topk_logprob", [_VP, _LL, _I, _I, _I, _VP, _VP, _VP])
+_lib.register("b200_topk_merge", [_VP, _VP, _VP, _VP, _I, _I, _VP, _VP, _VP])
+_lib.register("b200_logprob_full", [_VP, _LL, _I, _I, _VP, _LL, _VP])
+
+
+def topk_logprob(logits: torch.Tensor, vocab: int, k: int):
+    """(fp16 log-probs [rows, k] sorted descending, int32 ids [rows, k]) of log_softmax(logits[:, :vocab])."""
+    rows = logits.shape[0]
+    if not logits.is_cuda:
+        lp = torch.log_softmax(logits[:, :vocab].float(), dim=-1)
+        v, i = torch.sort(lp, dim=-1, descending=True, stable=True)
+        return v[:, :k].to(torch.float16), i[:, :k].to(torch.int32)
+    if logits.dtype != torch.float32 or logits.stride(-1) != 1:
+        raise TypeError("topk_logprob: logits must be fp32 with contiguous rows")
+    out_lp = torch.empty((rows, k), dtype=torch.float16, device=logits.device)
+    out_ix = torch.empty((rows, k), dtype=torch.int32, device=logits.device)
+    _lib.check(_lib.kernels().b200_topk_logprob(_lib.ptr(logits), logits.stride(0), rows, vocab, k, _lib.ptr(out_lp),
+                                                _lib.ptr(out_ix), _lib.stream()), "b200_topk_logprob")
+    return out_lp, out_ix
+
+
+def logprob_full(logits: torch.Tensor, vocab: int) -> torch.Tensor:
+    """fp16 log_softmax(logits[:, :vocab]) (full-distribution storage)."""
+    rows = logits.shape[0]
+    if not logits.is_cuda:
+        return torch.log_softmax(logits[:, :vocab].float(), dim=-1).to(torch.float16)
+    out = torch.empty((rows, vocab), dtype=torch.float16, device=logits.device)
+    _lib.check(_lib.kernels().b200_logprob_full(_lib.ptr(logits), logits.stride(0), rows, vocab, _lib.ptr(out),
+                                                out.stride(0), _lib.stream()), "b200_logprob_full")
+    return out
+
+
+def topk_merge(a_lp: torch.Tensor, a_id: torch.Tensor, b_lp: torch.Tensor, b_id: torch.Tensor):
+    """Union of two top-K lists per row with probabilities of equal ids summed; best K; (fp32 log, int32 id)."""
+    rows, K = a_lp.shape
+    if not a_lp.is_cuda:
+        ids = torch.cat([a_id, b_id], 1).long()
+        p = torch.cat([a_lp, b_lp], 1).float().exp()
+        o_lp = torch.empty((rows, K)); o_id = torch.empty((rows, K), dtype=torch.int32)
+        for r in range(rows):
+            u, inv = torch.unique(ids[r], return_inverse=True)
+            acc = torch.zeros(len(u)).index_add_(0, inv, p[r])
+            v, j = torch.sort(acc, descending=True, stable=True)
+            o_lp[r] = v[:K].log(); o_id[r] = u[j[:K]].to(torch.int32)
+        return o_lp, o_id
+    o_lp = torch.empty((rows, K), dtype=torch.float32, device=a_lp.device)
+    o_id = torch.empty((rows, K), dtype=torch.int32, device=a_lp.device)
+    _lib.check(_lib.kernels().b200_topk_merge(_lib.ptr(a_lp.float().contiguous()), _lib.ptr(a_id.int().contiguous()),
+                                              _lib.ptr(b_lp.float().contiguous()), _lib.ptr(b_id.int().contiguous()), rows, K,
+                                              _lib.ptr(o_lp), _lib.ptr(o_id), _lib.stream()), "b200_topk_merge")
+    return o_lp, o_id

@@ -1,0 +1,92 @@
+"""End-to-end CPU plumbing run: synthetic tokenizer + random-init teacher (2 layers) and student (4 layers),
+collect top-K into HDF5, train a few optimizer steps, checkpoint; rerun collects nothing and resumes."""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from llm_distillery_b200 import cli
+from llm_distillery_b200.ckpt.hf import load_hf_model
+from llm_distillery_b200.data.h5store import H5Store
+from llm_distillery_b200.models.llama import preset
+from llm_distillery_b200.utils import synthetic
+
+
+@pytest.fixture(scope="module")
+def workspace(tmp_path_factory):
+    root = tmp_path_factory.mktemp("plumbing")
+    tok = str(root / "tok")
+    synthetic.make_tokenizer(tok, 400)
+    tcfg = preset("plumbing-teacher", vocab_size=512, hidden_size=64, intermediate_size=176, max_position_embeddings=128)
+    scfg = preset("plumbing-student", vocab_size=512, hidden_size=64, intermediate_size=176, max_position_embeddings=128)
+    synthetic.make_model_dir(str(root / "teachers" / "teacher_a"), tcfg, tok, seed=1, batch_size=4)
+    synthetic.make_model_dir(str(root / "student"), scfg, tok, seed=2)
+    synthetic.make_dataset(str(root / "train.jsonl"), 24, seed=3)
+    synthetic.make_dataset(str(root / "val.jsonl"), 6, seed=4)
+    conf = {"cache_folder": str(root / "cache"), "dataset_path": str(root / "train.jsonl"),
+            "validation_dataset_path": str(root / "val.jsonl"), "teacher_models_folder": str(root / "teachers"),
+            "student_path": str(root / "student"), "context_len": 96, "crop_distr_to_size": 400, "save_topK": 20,
+            "enable_topK": True, "device": "cpu", "num_epochs": 2, "num_warmup_steps": 4, "batch_size": 2,
+            "grad_accum_batches": 2, "temperature": 1.0, "lr": 2e-3, "optimizer": "adamw", "data_order": "sorted",
+            "training_precision": "fp32", "validate_every_n_epochs": 1, "save_student_every_n_epochs": 1,
+            "freeze_layers": [], "loss": "reference", "max_cache_size_gb": 320}
+    with open(root / "config.json", "w") as f:
+        json.dump(conf, f)
+    return root
+
+
+def test_collect_train_checkpoint_then_rerun_skips_collection(workspace):
+    os.environ["B200_NO_PROGRESS"] = "1"
+    out = cli.main(["--config", str(workspace / "config.json")])
+    assert out["trained_samples"] == 48 and out["tokens_collected"] > 0
+    st = H5Store(str(workspace / "cache" / "dataset"))
+    ids = st.get_dataset_ids()
+    assert len(ids) == 24 and st.get_topk() == 20 and st.get_vocab_family() == "Unknown"
+    v, ix = st.load_id(ids[0])
+    assert v.shape[1] == 20 and ix.max() < 400 and (np.diff(v, axis=1) <= 1e-3).all()     # sorted descending
+    assert abs(np.exp(v[0]).sum()) <= 1.0 + 1e-2
+    st.close()
+    trained = workspace / "cache" / "student" / "trained"
+    folders = sorted(os.listdir(trained))
+    assert "student_step_final" in folders and any(f.startswith("student_step_24") for f in folders)
+    m = load_hf_model(str(trained / "student_step_final"), dtype=torch.float32)
+    m0 = load_hf_model(str(workspace / "student"), dtype=torch.float32)
+    assert not torch.equal(m.lm_head, m0.lm_head)
+    lines = [json.loads(x) for x in open(workspace / "cache" / "metrics.jsonl") if "step" in x]
+    val = [r["Val Loss/custom loss"] for r in lines if "Val Loss/custom loss" in r]
+    assert len(val) >= 3 and val[-1] < val[0]
+    assert any("Learning Rate" in r for r in lines) and any("Loss/kl_div" in r for r in lines)
+    # HF transformers reads the checkpoint folder
+    from transformers import AutoModelForCausalLM
+    hf = AutoModelForCausalLM.from_pretrained(str(trained / "student_step_final"), torch_dtype=torch.float32)
+    x = torch.randint(0, 400, (1, 12))
+    assert torch.allclose(hf(x).logits, m(x), atol=2e-4, rtol=1e-3)
+
+    # rerun: nothing to collect (SHA sync), training runs from the data on disk
+    out2 = cli.main(["--config", str(workspace / "config.json"), "--num_epochs", "1", "--loss", "kl"])
+    assert out2["tokens_collected"] == 0 and out2["trained_samples"] == 24
+
+
+def test_chunked_mode_and_dataset_edit(workspace):
+    os.environ["B200_NO_PROGRESS"] = "1"
+    # drop two samples and add one: the store renames / removes / collects only what changed
+    rows = [json.loads(x) for x in open(workspace / "train.jsonl")]
+    rows = rows[2:] + [{"init": "", "conversations": [{"from": "human", "value": "brand new sample about foxes"},
+                                                     {"from": "gpt", "value": "and wizards too"}], "source": "s", "tags": []}]
+    with open(workspace / "train2.jsonl", "w") as f:
+        for r in rows:
+            f.write(json.dumps(r) + "\n")
+    out = cli.main(["--config", str(workspace / "config.json"), "--dataset_path", str(workspace / "train2.jsonl"),
+                    "--num_epochs", "1", "--loss", "kl"])
+    assert out["tokens_collected"] > 0 and out["trained_samples"] == 23
+    st = H5Store(str(workspace / "cache" / "dataset"))
+    assert sorted(st.get_dataset_ids()) == list(range(23))
+    st.close()
+    # tiny cache limit: alternate collect-chunk / train-chunk, trainer state handed over between chunks
+    out = cli.main(["--config", str(workspace / "config.json"), "--dataset_path", str(workspace / "train2.jsonl"),
+                    "--max_cache_size_gb", "0.00002", "--num_epochs", "1", "--loss", "jsd",
+                    "--cache_folder", str(workspace / "cache_chunked")])
+    assert out["trained_samples"] == 23
+    assert os.path.exists(workspace / "cache_chunked" / "student" / "states" / "trainer_state.json")
