@@ -15,9 +15,11 @@ def topk_logprob(logits: torch.Tensor, vocab: int, k: int):
     """(fp16 log-probs [rows, k] sorted descending, int32 ids [rows, k]) of log_softmax(logits[:, :vocab])."""
     rows = logits.shape[0]
     if not logits.is_cuda:
-        lp = torch.log_softmax(logits[:, :vocab].float(), dim=-1)
-        v, i = torch.sort(lp, dim=-1, descending=True, stable=True)
-        return v[:, :k].to(torch.float16), i[:, :k].to(torch.int32)
+        z = logits[:, :vocab].float()
+        _, i = torch.sort(z, dim=-1, descending=True, stable=True)   # rank on the logits: subtraction can merge values
+        i = i[:, :k]
+        lp = torch.gather(z, 1, i) - torch.logsumexp(z, dim=-1, keepdim=True)
+        return lp.to(torch.float16), i.to(torch.int32)
     if logits.dtype != torch.float32 or logits.stride(-1) != 1:
         raise TypeError("topk_logprob: logits must be fp32 with contiguous rows")
     out_lp = torch.empty((rows, k), dtype=torch.float16, device=logits.device)
