@@ -460,3 +460,65 @@ int b200_cast_bf16_to_f32(const void* in, float* out, long long n, float scale, 
   return B200_OK;
 }
 }
+
+// ------------------------------------------------------------------------------------------------------------
+// Allocation-free RMSNorm backward (declared and documented in rmsnorm_noalloc.h).
+#include "rmsnorm_noalloc.h"
+
+#include <mutex>
+
+namespace b200 {
+namespace ew {
+
+// Workspace for the per-block weight-gradient partial sums. In host code this name is only a handle for the
+// runtime: the kernels get the device address obtained once per device by scratch_for_current_device().
+static __device__ __align__(256) float g_rmsnorm_noalloc_scratch[B200_RMSNORM_NOALLOC_MAX_BLOCKS * B200_RMSNORM_NOALLOC_MAX_H];
+
+static float* g_noalloc_ptr[64] = {nullptr};
+static std::mutex g_noalloc_mu;
+
+// Device address of the workspace on the current device (looked up on the first call per device).
+static int scratch_for_current_device(float** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return set_last_cuda_error(e, "cudaGetDevice");
+  if (dev < 0 || dev >= 64) return B200_ERR_ARG;
+  std::lock_guard<std::mutex> lk(g_noalloc_mu);
+  if (!g_noalloc_ptr[dev]) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_rmsnorm_noalloc_scratch);
+    if (e != cudaSuccess) return set_last_cuda_error(e, "cudaGetSymbolAddress(g_rmsnorm_noalloc_scratch)");
+    g_noalloc_ptr[dev] = p;
+  }
+  *out = g_noalloc_ptr[dev];
+  return B200_OK;
+}
+
+}  // namespace ew
+}  // namespace b200
+
+extern "C" int b200_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const float* rstd,
+                                        const void* dres, void* dx, float* dw_out, int dw_accumulate, int rows, int h,
+                                        cudaStream_t st) {
+  using namespace b200;
+  using namespace b200::ew;
+  if (!dy || !x || !w || !rstd || !dx || !dw_out || rows <= 0 || h <= 0 || (h & 7)) return B200_ERR_ARG;
+  if (h > B200_RMSNORM_NOALLOC_MAX_H) {
+    set_last_cuda_error(cudaErrorInvalidValue,
+                        "b200_rmsnorm_bwd_noalloc: h exceeds B200_RMSNORM_NOALLOC_MAX_H (4096); use b200_rmsnorm_bwd "
+                        "with a caller-provided workspace");
+    return B200_ERR_TOO_BIG;
+  }
+  float* scratch = nullptr;
+  const int rc = scratch_for_current_device(&scratch);
+  if (rc != B200_OK) return rc;
+  const int grid = rows < B200_RMSNORM_NOALLOC_MAX_BLOCKS ? rows : B200_RMSNORM_NOALLOC_MAX_BLOCKS;
+  // every block writes its own partial row (all h columns) before the column sum reads rows [0, grid):
+  // nothing left over from an earlier call is ever read
+  rmsnorm_bwd_kernel<<<grid, NT, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
+                                          rstd, (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, scratch, rows, h);
+  B200_CUDA_CHECK(cudaGetLastError());
+  colsum_kernel<<<ceil_div(h, 32), 256, 0, st>>>(scratch, dw_out, grid, h, dw_accumulate);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200_OK;
+}
