@@ -1,0 +1,203 @@
+// NVLink peer-to-peer collectives over symmetric memory (every rank's buffer mapped into every rank's address
+// space). Kernels here use plain peer loads / stores and system-scope release/acquire flags; nothing uses TMA
+// multicast or multimem. One process drives one GPU, so kernels that wait on a peer's flag always run on a
+// different GPU than the kernel that sets it.
+//
+//   p2p_barrier        epoch-numbered flag exchange; every wait is bounded (2 s) and reports ERR_WAIT_PEER
+//   rs_adamw_ag        THE data-parallel optimizer step: for this rank's shard of the flat parameter space, sum
+//                      the fp32 gradients of all ranks straight out of their memory (reduce-scatter by peer loads),
+//                      apply AdamW to the local fp32 master / moments, and store the new bf16 weights into every
+//                      rank's weight buffer (all-gather by peer stores) - one pass, no staging buffers
+//   reduce_scatter_f32 / allgather_16 / allreduce_f32   stand-alone pieces for the other optimizers and for tests
+#include "../common/ptx.cuh"
+#include "../common/host.cuh"
+
+namespace b200 {
+namespace comm {
+
+constexpr int MAX_RANKS = 16;
+struct Peers { void* p[MAX_RANKS]; };
+
+__device__ __forceinline__ void st_release_sys(unsigned int* addr, unsigned int v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* addr) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
+
+// sig[r] points at rank r's flag array (MAX_RANKS words). Thread t tells rank t "rank `rank` reached `epoch`" and
+// waits until rank t has told us the same. Epochs only grow, so a late reader never sees a stale match.
+__global__ void barrier_kernel(Peers sig, int rank, int world, unsigned int epoch, unsigned int* err_word) {
+  const int t = threadIdx.x;
+  if (t >= world) return;
+  __threadfence_system();
+  st_release_sys(reinterpret_cast<unsigned int*>(sig.p[t]) + rank, epoch);
+  const unsigned int* mine = reinterpret_cast<const unsigned int*>(sig.p[rank]) + t;
+  const unsigned long long t0 = globaltimer_ns();
+  unsigned int spins = 0;
+  while (static_cast<int>(ld_acquire_sys(mine) - epoch) < 0) {
+    if (((++spins) & 0xffu) == 0u && globaltimer_ns() - t0 > kWaitTimeoutNs) {
+      if (err_word) atomicCAS(err_word, 0u, (unsigned)ERR_WAIT_PEER);
+      return;
+    }
+    __nanosleep(64);
+  }
+}
+
+struct AdamArgs {
+  float lr, beta1, beta2, eps, weight_decay, bias1, bias2, grad_scale;
+  int decoupled;
+};
+
+// 8 elements per thread: two float4 gradient loads per peer, one 16-byte bf16 store per peer.
+__global__ void __launch_bounds__(256) rs_adamw_ag_kernel(Peers grads, Peers models, float* __restrict__ master,
+                                                         float* __restrict__ m, float* __restrict__ v,
+                                                         long long shard_lo, long long shard_n, int rank, int world,
+                                                         AdamArgs a) {
+  const long long nv = shard_n >> 3;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nv;
+       i += (long long)gridDim.x * blockDim.x) {
+    float g[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int k = 0; k < world; ++k) {
+      const int p = (rank + k) % world;  // start with the local copy, spread peers over time
+      const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(grads.p[p]) + shard_lo) + 2 * i;
+      const float4 x = src[0], y = src[1];
+      g[0] += x.x; g[1] += x.y; g[2] += x.z; g[3] += x.w;
+      g[4] += y.x; g[5] += y.y; g[6] += y.z; g[7] += y.w;
+    }
+    float pm[8], mm[8], vv[8];
+    *reinterpret_cast<float4*>(pm) = reinterpret_cast<float4*>(master)[2 * i];
+    *reinterpret_cast<float4*>(pm + 4) = reinterpret_cast<float4*>(master)[2 * i + 1];
+    *reinterpret_cast<float4*>(mm) = reinterpret_cast<float4*>(m)[2 * i];
+    *reinterpret_cast<float4*>(mm + 4) = reinterpret_cast<float4*>(m)[2 * i + 1];
+    *reinterpret_cast<float4*>(vv) = reinterpret_cast<float4*>(v)[2 * i];
+    *reinterpret_cast<float4*>(vv + 4) = reinterpret_cast<float4*>(v)[2 * i + 1];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float gj = g[j] * a.grad_scale;
+      if (a.decoupled) pm[j] *= (1.f - a.lr * a.weight_decay);
+      else gj += a.weight_decay * pm[j];
+      mm[j] = a.beta1 * mm[j] + (1.f - a.beta1) * gj;
+      vv[j] = a.beta2 * vv[j] + (1.f - a.beta2) * gj * gj;
+      pm[j] -= (a.lr / a.bias1) * mm[j] / (sqrtf(vv[j] / a.bias2) + a.eps);
+    }
+    reinterpret_cast<float4*>(master)[2 * i] = *reinterpret_cast<float4*>(pm);
+    reinterpret_cast<float4*>(master)[2 * i + 1] = *reinterpret_cast<float4*>(pm + 4);
+    reinterpret_cast<float4*>(m)[2 * i] = *reinterpret_cast<float4*>(mm);
+    reinterpret_cast<float4*>(m)[2 * i + 1] = *reinterpret_cast<float4*>(mm + 4);
+    reinterpret_cast<float4*>(v)[2 * i] = *reinterpret_cast<float4*>(vv);
+    reinterpret_cast<float4*>(v)[2 * i + 1] = *reinterpret_cast<float4*>(vv + 4);
+    uint4 o;
+    o.x = pack_bf16x2(pm[0], pm[1]);
+    o.y = pack_bf16x2(pm[2], pm[3]);
+    o.z = pack_bf16x2(pm[4], pm[5]);
+    o.w = pack_bf16x2(pm[6], pm[7]);
+    for (int k = 0; k < world; ++k) {
+      const int p = (rank + k) % world;
+      reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(models.p[p]) + shard_lo)[i] = o;
+    }
+  }
+  __threadfence_system();
+}
+
+// out[i] = scale * sum_p src_p[lo + i]   (fp32), i < n, n % 4 == 0
+__global__ void __launch_bounds__(256) reduce_scatter_kernel(Peers src, float* __restrict__ out, long long lo,
+                                                            long long n, int rank, int world, float scale) {
+  const long long nv = n >> 2;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nv;
+       i += (long long)gridDim.x * blockDim.x) {
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int k = 0; k < world; ++k) {
+      const int p = (rank + k) % world;
+      const float4 x = (reinterpret_cast<const float4*>(reinterpret_cast<const float*>(src.p[p]) + lo))[i];
+      s.x += x.x; s.y += x.y; s.z += x.z; s.w += x.w;
+    }
+    s.x *= scale; s.y *= scale; s.z *= scale; s.w *= scale;
+    reinterpret_cast<float4*>(out)[i] = s;
+  }
+}
+
+// dst_p[lo_bytes + ...] = local[...] for every rank p: all-gather by peer stores, 16-byte granules
+__global__ void __launch_bounds__(256) allgather_kernel(Peers dst, const uint4* __restrict__ local, long long lo_vec,
+                                                       long long nvec, int rank, int world, int skip_self) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
+       i += (long long)gridDim.x * blockDim.x) {
+    const uint4 x = local[i];
+    for (int k = skip_self ? 1 : 0; k < world; ++k) {
+      const int p = (rank + k) % world;
+      (reinterpret_cast<uint4*>(dst.p[p]) + lo_vec)[i] = x;
+    }
+  }
+  __threadfence_system();
+}
+
+static int grid_for(long long items) {
+  long long b = (items + 255) / 256;
+  const long long cap = (long long)sm_count() * 8;
+  if (b > cap) b = cap;
+  if (b < 1) b = 1;
+  return (int)b;
+}
+static bool fill(Peers& P, const void* const* ptrs, int world) {
+  if (!ptrs || world < 1 || world > MAX_RANKS) return false;
+  for (int i = 0; i < MAX_RANKS; ++i) P.p[i] = i < world ? const_cast<void*>(ptrs[i]) : nullptr;
+  for (int i = 0; i < world; ++i)
+    if (!P.p[i]) return false;
+  return true;
+}
+
+}  // namespace comm
+}  // namespace b200
+
+extern "C" {
+using namespace b200;
+using namespace b200::comm;
+
+int b200_p2p_max_ranks() { return MAX_RANKS; }
+
+// sig_ptrs[r]: rank r's flag array (>= 16 uint32, zero-initialised once). epoch must grow by one per barrier.
+int b200_p2p_barrier(const void* const* sig_ptrs, int rank, int world, unsigned int epoch, cudaStream_t st) {
+  Peers S;
+  if (!fill(S, sig_ptrs, world) || rank < 0 || rank >= world) return B200_ERR_ARG;
+  barrier_kernel<<<1, 32, 0, st>>>(S, rank, world, epoch, device_err_word());
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200_OK;
+}
+
+// grad_ptrs[r]: rank r's full fp32 gradient; model_ptrs[r]: rank r's full bf16 weights; master/m/v: local shard.
+int b200_p2p_rs_adamw_ag(const void* const* grad_ptrs, const void* const* model_ptrs, float* master, float* m, float* v,
+                         long long shard_lo, long long shard_n, int rank, int world, float lr, float beta1, float beta2,
+                         float eps, float weight_decay, int step, float grad_scale, int decoupled, cudaStream_t st) {
+  Peers G, M;
+  if (!fill(G, grad_ptrs, world) || !fill(M, model_ptrs, world) || !master || !m || !v || shard_n <= 0 ||
+      (shard_n & 7) || (shard_lo & 7) || step < 1)
+    return B200_ERR_ARG;
+  AdamArgs a{lr, beta1, beta2, eps, weight_decay, 1.f - powf(beta1, (float)step), 1.f - powf(beta2, (float)step),
+             grad_scale, decoupled};
+  rs_adamw_ag_kernel<<<grid_for(shard_n >> 3), 256, 0, st>>>(G, M, master, m, v, shard_lo, shard_n, rank, world, a);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200_OK;
+}
+
+int b200_p2p_reduce_scatter_f32(const void* const* src_ptrs, float* out, long long lo, long long n, int rank, int world,
+                                float scale, cudaStream_t st) {
+  Peers S;
+  if (!fill(S, src_ptrs, world) || !out || n <= 0 || (n & 3) || (lo & 3)) return B200_ERR_ARG;
+  reduce_scatter_kernel<<<grid_for(n >> 2), 256, 0, st>>>(S, out, lo, n, rank, world, scale);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200_OK;
+}
+
+// Copies nbytes (multiple of 16) from `local` into every rank's buffer at byte offset lo_bytes.
+int b200_p2p_allgather(const void* const* dst_ptrs, const void* local, long long lo_bytes, long long nbytes, int rank,
+                       int world, int skip_self, cudaStream_t st) {
+  Peers D;
+  if (!fill(D, dst_ptrs, world) || !local || nbytes <= 0 || (nbytes & 15) || (lo_bytes & 15)) return B200_ERR_ARG;
+  allgather_kernel<<<grid_for(nbytes >> 4), 256, 0, st>>>(D, (const uint4*)local, lo_bytes >> 4, nbytes >> 4, rank, world,
+                                                         skip_self);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200_OK;
+}
+}

@@ -1,0 +1,145 @@
+"""NVLink peer-to-peer communicator for the flat parameter space (kernels: csrc/comm/p2p.cu).
+
+The flat fp32 gradient and the flat bf16 weights are allocated in symmetric memory, so every rank holds device
+pointers to every other rank's copies. One optimizer step is then
+
+    barrier (all backward passes done)  ->  rs_adamw_ag kernel  ->  barrier (all weight stores landed)
+
+where the middle kernel, for this rank's 1/world shard, sums all ranks' gradients with peer loads, applies AdamW to
+the local fp32 master weights / moments and writes the new bf16 weights into every rank's weight buffer with peer
+stores. Optimizer state is therefore sharded (ZeRO-1) for ``ddp`` and ``fsdp`` alike. Optimizers other than the
+fp32-state Adam family run reduce-scatter kernel -> local optimizer kernel -> all-gather kernel.
+
+Barriers are flag exchanges with growing epoch numbers; every device-side wait is bounded and reports through the
+error word (``ops._lib.take_device_error``). ``check()`` turns a reported time-out into a Python exception.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_void_p
+
+import torch
+import torch.distributed as dist
+
+from ..engine.optim import ALIGN, _round_up
+from ..ops import _lib
+from ..ops._lib import _VP, _I, _LL, _F
+
+_U = ctypes.c_uint
+_lib.register("b200_p2p_barrier", [_VP, _I, _I, _U, _VP])
+_lib.register("b200_p2p_rs_adamw_ag", [_VP, _VP, _VP, _VP, _VP, _LL, _LL, _I, _I, _F, _F, _F, _F, _F, _I, _F, _I, _VP])
+_lib.register("b200_p2p_reduce_scatter_f32", [_VP, _VP, _LL, _LL, _I, _I, _F, _VP])
+_lib.register("b200_p2p_allgather", [_VP, _VP, _LL, _LL, _I, _I, _I, _VP])
+
+
+def _ptr_array(ptrs) -> ctypes.Array:
+    return (c_void_p * len(ptrs))(*[c_void_p(int(p)) for p in ptrs])
+
+
+class SymmetricBuffer:
+    """A tensor allocated in symmetric memory plus the device pointers of every rank's copy."""
+
+    def __init__(self, numel: int, dtype: torch.dtype, device, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        group = group or dist.group.WORLD
+        self.tensor = symm_mem.empty(numel, dtype=dtype, device=device)
+        self.tensor.zero_()
+        self.handle = symm_mem.rendezvous(self.tensor, group)
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.c_ptrs = _ptr_array(self.ptrs)
+
+
+class P2PComm:
+    shards_optimizer = True
+
+    def __init__(self, device, shard_strategy: str = "ddp"):
+        self.device = torch.device(device)
+        self.rank = dist.get_rank()
+        self.world = dist.get_world_size()
+        self.shard_strategy = shard_strategy
+        self.flat = None
+        self.opt = None
+        self.epoch = 0
+        self.sig = SymmetricBuffer(64, torch.int32, self.device)
+        self.grad_buf = None
+        self.model_buf = None
+        torch.cuda.synchronize(self.device)
+        dist.barrier()
+
+    # ---- buffers for FlatParams (same layout rule as engine.optim.FlatParams)
+    def allocate_flat_buffers(self, model) -> dict:
+        seen, total = set(), 0
+        dtype = None
+        for p in model.parameters():
+            if p.requires_grad and id(p) not in seen:
+                seen.add(id(p))
+                total += _round_up(p.numel(), ALIGN)
+                dtype = dtype or p.dtype
+        total = _round_up(total, 256 * self.world)
+        self.grad_buf = SymmetricBuffer(total, torch.float32, self.device)
+        self.model_buf = SymmetricBuffer(total, dtype, self.device)
+        return {"grad": self.grad_buf.tensor, "model": self.model_buf.tensor}
+
+    def attach(self, flat, opt) -> None:
+        self.flat, self.opt = flat, opt
+        if flat.grad.data_ptr() != self.grad_buf.tensor.data_ptr() or flat.model.data_ptr() != self.model_buf.tensor.data_ptr():
+            raise RuntimeError("flat buffers are not the symmetric allocations")
+        self.barrier()
+
+    # ---- primitives
+    def barrier(self) -> None:
+        self.epoch += 1
+        _lib.check(_lib.kernels().b200_p2p_barrier(self.sig.c_ptrs, self.rank, self.world, self.epoch, _lib.stream()),
+                   "b200_p2p_barrier")
+
+    def check(self) -> None:
+        err = _lib.take_device_error()
+        if err:
+            raise RuntimeError(f"peer-to-peer wait timed out on rank {self.rank} (device error code {err})")
+
+    def reduce_scatter(self, src: SymmetricBuffer, out: torch.Tensor, lo: int, scale: float = 1.0) -> None:
+        """out[i] = scale * sum over ranks of src[lo + i]; callers bracket this with barriers."""
+        _lib.check(_lib.kernels().b200_p2p_reduce_scatter_f32(src.c_ptrs, _lib.ptr(out), lo, out.numel(), self.rank,
+                                                              self.world, float(scale), _lib.stream()), "p2p reduce_scatter")
+
+    def allgather(self, dst: SymmetricBuffer, local: torch.Tensor, lo_elems: int, skip_self: bool = False) -> None:
+        es = local.element_size()
+        _lib.check(_lib.kernels().b200_p2p_allgather(dst.c_ptrs, _lib.ptr(local), lo_elems * es, local.numel() * es,
+                                                     self.rank, self.world, int(skip_self), _lib.stream()), "p2p allgather")
+
+    def allreduce_(self, buf: SymmetricBuffer, scale: float = 1.0) -> torch.Tensor:
+        """In-place sum of a symmetric fp32 buffer over all ranks (reduce-scatter + all-gather by peer access)."""
+        n = buf.tensor.numel()
+        per = _round_up(-(-n // self.world), 4)
+        lo = min(self.rank * per, n)
+        cnt = max(0, min(per, n - lo))
+        self.barrier()
+        tmp = torch.empty(max(cnt, 4), dtype=torch.float32, device=self.device)
+        if cnt:
+            self.reduce_scatter(buf, tmp[:cnt], lo, scale)
+        self.barrier()          # everyone has finished reading before anyone overwrites
+        if cnt:
+            self.allgather(buf, tmp[:cnt], lo)
+        self.barrier()
+        return buf.tensor
+
+    # ---- the optimizer step
+    def reduce_and_step(self, lr: float, grad_scale: float) -> None:
+        f, opt = self.flat, self.opt
+        gs = grad_scale / self.world
+        self.barrier()
+        fused = opt.name in ("adam", "adamw", "adamw32bit", "paged_adamw", "paged_adamw32bit") and f.dtype == torch.bfloat16
+        if fused:
+            opt.step_count += 1
+            b1, b2 = opt.betas
+            st = opt.state
+            _lib.check(_lib.kernels().b200_p2p_rs_adamw_ag(
+                self.grad_buf.c_ptrs, self.model_buf.c_ptrs, _lib.ptr(f.master), _lib.ptr(st["m"]), _lib.ptr(st["v"]),
+                f.shard_lo, f.shard_size, self.rank, self.world, lr, b1, b2, opt.eps, opt.weight_decay, opt.step_count,
+                gs, int(opt.decoupled), _lib.stream()), "b200_p2p_rs_adamw_ag")
+        else:
+            shard = torch.empty(f.shard_size, dtype=torch.float32, device=self.device)
+            self.reduce_scatter(self.grad_buf, shard, f.shard_lo, 1.0)
+            opt.step(lr, grad_scale=gs, grad=shard)
+            self.allgather(self.model_buf, f.model_shard(), f.shard_lo, skip_self=True)
+        self.barrier()

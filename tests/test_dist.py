@@ -1,0 +1,35 @@
+"""Multi-rank paths: gloo ranks on CPU (always), NCCL + NVLink P2P ranks when two or more GPUs are visible."""
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _launch(mode, nproc, timeout=600, env=None):
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr",
+           "127.0.0.1", "--master-port", str(_free_port()), os.path.join(HERE, "dist_worker.py"), mode]
+    e = dict(os.environ, B200_NO_PROGRESS="1", OMP_NUM_THREADS="2", **(env or {}))
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=e)
+    assert r.returncode == 0 and "WORKER_OK" in r.stdout, (r.stdout[-2000:], r.stderr[-4000:])
+
+
+def test_cpu_ranks_ddp_and_fsdp_match_single_process():
+    _launch("cpu_engine", 2)
+
+
+@pytest.mark.gpu
+def test_p2p_collectives_and_training_match_nccl():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least 2 GPUs")
+    _launch("gpu_p2p", min(4, torch.cuda.device_count()), env={"NCCL_NVLS_ENABLE": "0"})
