@@ -1,0 +1,189 @@
+#!/usr/bin/env python
+"""Kernel micro-benchmarks with roofline fractions against the measured box peaks (MEASURED_PEAKS.json when
+present, else the documented fallback of 6.65 TB/s and 1.59 PFLOP/s).
+
+    python bench_kernels.py gemm --m 16384 --n 2048 --k 2048 [--layout nt|nn|tn] [--iters 20]
+    python bench_kernels.py attn --batch 8 --seq 2048 --heads 32 --kv-heads 4 --dim 64 [--bwd]
+    python bench_kernels.py head --rows 16384 --hidden 2048 --vocab 32000 --topk 200
+    python bench_kernels.py elementwise --rows 16384 --hidden 2048 --ffn 5632
+    python bench_kernels.py all            (the model shapes of the headline benchmark)
+
+Timing: CUDA events on the launching stream, warm-up first, L2 flushed between timed iterations by writing a
+256 MB buffer (its time is excluded: one event pair per iteration). One JSON line per case.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+from llm_distillery_b200.ops import basic, attention, _lib  # noqa: E402
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "tflops": d["bf16_tflops"], "tflops_sustained": d.get("bf16_tflops_sustained"),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops": 1590.0, "tflops_sustained": 1400.0, "source": "fallback"}
+
+
+_FLUSH = None
+
+
+def timed(fn, iters: int, warmup: int = 3, flush: bool = True) -> float:
+    """Median milliseconds per call."""
+    global _FLUSH
+    if flush and _FLUSH is None:
+        _FLUSH = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        if flush:
+            _FLUSH.fill_(1)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def report(name, ms, flops=None, bytes_=None, **extra):
+    pk = peaks()
+    out = {"kernel": name, "ms": round(ms, 4), **extra}
+    if flops:
+        tf = flops / ms / 1e9
+        out.update(tflops=round(tf, 1), frac_of_peak=round(tf / pk["tflops"], 3), peak=f"{pk['tflops']} TF/s of {pk['source']}")
+    if bytes_:
+        gbs = bytes_ / ms / 1e6
+        out.update(gbs=round(gbs, 1), frac_of_hbm=round(gbs / pk["hbm_gbs"], 3), hbm=f"{pk['hbm_gbs']} GB/s of {pk['source']}")
+    err = _lib.take_device_error()
+    if err:
+        out["device_error"] = err
+    print(json.dumps(out), flush=True)
+
+
+def bench_gemm(M, N, K, layout, iters, compare=True):
+    a_mn, b_mn = {"nt": (False, False), "nn": (False, True), "tn": (True, True)}[layout]
+    a = torch.randn((K, M) if a_mn else (M, K), device="cuda").bfloat16()
+    b = torch.randn((K, N) if b_mn else (N, K), device="cuda").bfloat16()
+    out = torch.empty((M, N), device="cuda", dtype=torch.bfloat16)
+    ms = timed(lambda: basic.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=out), iters)
+    extra = {}
+    if compare:
+        A, B = (a.t() if a_mn else a), (b if b_mn else b.t())
+        extra["cublas_ms"] = round(timed(lambda: torch.matmul(A, B, out=out), iters), 4)
+    report(f"gemm_{layout}", ms, flops=2.0 * M * N * K, shape=[M, N, K], **extra)
+
+
+def bench_attn(B, L, H, Hkv, d, iters, bwd):
+    qkv = torch.randn(B * L, (H + 2 * Hkv) * d, device="cuda").bfloat16()
+    out, lse = attention.attention_fwd(qkv, B, L, H, Hkv, d)
+    fl = 4.0 * B * H * L * L * d / 2
+    ms = timed(lambda: attention.attention_fwd(qkv, B, L, H, Hkv, d), iters)
+    report("flash_attn_fwd", ms, flops=fl, shape=[B, L, H, Hkv, d])
+    if bwd:
+        dout = torch.randn_like(out)
+        ms = timed(lambda: attention.attention_bwd(dout, qkv, out, lse, B, L, H, Hkv, d), iters)
+        report("flash_attn_bwd", ms, flops=2.5 * fl, shape=[B, L, H, Hkv, d])
+
+
+def bench_head(M, h, V, K, iters, T=2.0):
+    from llm_distillery_b200.loss import head
+    from llm_distillery_b200.models.llama import GradSlot
+    Hc = torch.randn(M, h, device="cuda").bfloat16().requires_grad_()
+    W = (torch.randn(V, h, device="cuda") * 0.02).bfloat16().requires_grad_()
+    W.grad_slot = GradSlot(torch.zeros(V, h, device="cuda"))
+    ids = torch.rand(M, V, device="cuda").topk(K, -1).indices.sort(-1).values.int() if V * M < 2 ** 30 else \
+        torch.stack([torch.randperm(V, device="cuda")[:K].sort().values for _ in range(M)]).int()
+    u = torch.log_softmax(torch.randn(M, K, device="cuda") * 3, -1)
+
+    def fwd():
+        return head.fused_distill_rows(Hc, W, ids, u, "kl", T, V)
+
+    def fwd_bwd():
+        Hc.grad = None
+        fwd().sum().backward()
+
+    gemm_fl = 2.0 * M * V * h
+    with torch.no_grad():
+        report("distill_head_fwd", timed(fwd, iters), flops=gemm_fl, shape=[M, h, V, K])
+    report("distill_head_fwd_bwd", timed(fwd_bwd, iters), flops=4 * gemm_fl, shape=[M, h, V, K],
+           note="4 GEMM-equivalents: stats, recompute, dH, dW")
+
+
+def bench_elementwise(rows, h, f, iters):
+    x = torch.randn(rows, h, device="cuda").bfloat16()
+    w = torch.ones(h, device="cuda").bfloat16()
+    y, _, rstd = basic.rmsnorm_fwd(x, w, 1e-5)
+    report("rmsnorm_fwd", timed(lambda: basic.rmsnorm_fwd(x, w, 1e-5), iters), bytes_=2 * rows * h * 2, shape=[rows, h])
+    report("rmsnorm_bwd", timed(lambda: basic.rmsnorm_bwd(y, x, w, rstd, x), iters), bytes_=4 * rows * h * 2, shape=[rows, h])
+    gu = torch.randn(rows, 2 * f, device="cuda").bfloat16()
+    act = basic.swiglu_fwd(gu)
+    report("swiglu_fwd", timed(lambda: basic.swiglu_fwd(gu), iters), bytes_=3 * rows * f * 2, shape=[rows, f])
+    report("swiglu_bwd", timed(lambda: basic.swiglu_bwd(gu, act), iters), bytes_=5 * rows * f * 2, shape=[rows, f])
+    pos = torch.arange(rows, device="cuda", dtype=torch.int32) % 2048
+    cos, sin = basic.rope_tables(2048, 64, 10000.0, "cuda")
+    q = torch.randn(rows, h + 512, device="cuda").bfloat16()
+    report("rope", timed(lambda: basic.rope_(q, pos, cos, sin, (h + 256) // 64, 64), iters), bytes_=2 * rows * (h + 256) * 2,
+           shape=[rows, h + 256])
+    n = 64 << 20
+    from llm_distillery_b200.engine.optim import FlatOptimizer, FlatParams
+    p = torch.nn.Parameter(torch.randn(n, device="cuda").bfloat16())
+    opt = FlatOptimizer(FlatParams([p]), "adamw", lr=1e-4)
+    report("adamw", timed(lambda: opt.step(), iters), bytes_=n * 30, shape=[n])
+
+
+def main():
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    g = sub.add_parser("gemm")
+    g.add_argument("--m", type=int, default=8192); g.add_argument("--n", type=int, default=8192)
+    g.add_argument("--k", type=int, default=8192); g.add_argument("--layout", default="nt", choices=["nt", "nn", "tn"])
+    a = sub.add_parser("attn")
+    a.add_argument("--batch", type=int, default=8); a.add_argument("--seq", type=int, default=2048)
+    a.add_argument("--heads", type=int, default=32); a.add_argument("--kv-heads", type=int, default=4)
+    a.add_argument("--dim", type=int, default=64); a.add_argument("--bwd", action="store_true")
+    h = sub.add_parser("head")
+    h.add_argument("--rows", type=int, default=16384); h.add_argument("--hidden", type=int, default=2048)
+    h.add_argument("--vocab", type=int, default=32000); h.add_argument("--topk", type=int, default=200)
+    e = sub.add_parser("elementwise")
+    e.add_argument("--rows", type=int, default=16384); e.add_argument("--hidden", type=int, default=2048)
+    e.add_argument("--ffn", type=int, default=5632)
+    sub.add_parser("all")
+    for s in (g, a, h, e, sub.choices["all"]):
+        s.add_argument("--iters", type=int, default=20)
+    args = ap.parse_args()
+    if args.cmd == "gemm":
+        bench_gemm(args.m, args.n, args.k, args.layout, args.iters)
+    elif args.cmd == "attn":
+        bench_attn(args.batch, args.seq, args.heads, args.kv_heads, args.dim, args.iters, args.bwd)
+    elif args.cmd == "head":
+        bench_head(args.rows, args.hidden, args.vocab, args.topk, args.iters)
+    elif args.cmd == "elementwise":
+        bench_elementwise(args.rows, args.hidden, args.ffn, args.iters)
+    else:
+        for shp, lay in [((8192, 8192, 8192), "nt"), ((16384, 2560, 2048), "nt"), ((16384, 2048, 2048), "nt"),
+                         ((16384, 11264, 2048), "nt"), ((16384, 2048, 5632), "nt"), ((16384, 2048, 2560), "nn"),
+                         ((16384, 2048, 11264), "nn"), ((16384, 5632, 2048), "nn"), ((2560, 2048, 16384), "tn"),
+                         ((11264, 2048, 16384), "tn"), ((2048, 5632, 16384), "tn"), ((2048, 2048, 16384), "tn")]:
+            bench_gemm(*shp, lay, args.iters)
+        bench_attn(8, 2048, 32, 4, 64, args.iters, True)
+        bench_attn(2, 4096, 32, 8, 128, args.iters, True)
+        bench_head(16384, 2048, 32000, 200, max(3, args.iters // 4))
+        bench_elementwise(16384, 2048, 5632, args.iters)
+
+
+if __name__ == "__main__":
+    main()

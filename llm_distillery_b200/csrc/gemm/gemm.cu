@@ -2,7 +2,8 @@
 //   C[M,N] = alpha * A * B^T (+ C) (+ residual)     bf16/fp16 operands, fp32 accumulate,
 // with A and B each either K-major or MN-major, so forward (NT), dgrad (NN) and wgrad (TN)
 // GEMMs of a linear layer all run without a transpose pass.
-#include "gemm_core.cuh"
+#include "gemm_pair.cuh"
+#include <stdlib.h>
 #include "../common/host.cuh"
 
 namespace b200 {
@@ -146,6 +147,60 @@ static int launch_store(const void* A, const void* B, int M, int N, int K, long 
   return B200_OK;
 }
 
+// Two-SM (cta_group::2) launch: 256 x 256 tiles, one CTA pair per tile.
+template <bool A_MN, bool B_MN>
+static int launch_store_pair(const void* A, const void* B, int M, int N, int K, long long lda, long long ldb, int fmt,
+                             const StoreParams& sp, cudaStream_t stream) {
+  using Epi = EpiStore<PAIR_BN>;
+  constexpr int STAGES = 6;
+  using S = SmemPair<STAGES>;
+  CUtensorMap tmA, tmB;
+  const CUtensorMapDataType dt = fmt == 1 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  int rc;
+  if (!A_MN)
+    rc = make_tmap_2d(&tmA, A, dt, 2, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B);
+  else
+    rc = make_tmap_2d(&tmA, A, dt, 2, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, 64, BK, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != B200_OK) return rc;
+  if (!B_MN)
+    rc = make_tmap_2d(&tmB, B, dt, 2, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, BK, PAIR_HALF_N,
+                      CU_TENSOR_MAP_SWIZZLE_128B);
+  else
+    rc = make_tmap_2d(&tmB, B, dt, 2, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, 64, BK, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != B200_OK) return rc;
+  auto kern = gemm_pair_kernel<STAGES, A_MN, B_MN, Epi>;
+  const int smem_bytes = S::bytes(Epi::SMEM_BYTES);
+  static bool attr_set = false;
+  if (!attr_set) {
+    B200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+    attr_set = true;
+  }
+  const int tiles = ceil_div(M, PAIR_BM) * ceil_div(N, PAIR_BN);
+  const int max_pairs = sm_count() / 2;
+  const int pairs = tiles < max_pairs ? tiles : max_pairs;
+  kern<<<2 * pairs, NUM_THREADS, smem_bytes, stream>>>(tmA, tmB, M, N, K, fmt, sp, device_err_word());
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200_OK;
+}
+
+// 0 = never, 1 = whenever the shape allows, unset = heuristic (enough 256 x 256 tiles to fill the SM pairs)
+static int pair_mode() {
+  static int mode = -2;
+  if (mode == -2) {
+    const char* e = getenv("B200_GEMM_PAIR");
+    mode = e ? atoi(e) : -1;
+  }
+  return mode;
+}
+
+static bool use_pair(int M, int N, int K) {
+  const int mode = pair_mode();
+  if (mode == 0 || N <= 128) return false;
+  if (mode == 1) return true;
+  const long long tiles = (long long)ceil_div(M, PAIR_BM) * ceil_div(N, PAIR_BN);
+  return tiles >= sm_count() / 2 && K >= 256;
+}
+
 }  // namespace gemm
 }  // namespace b200
 
@@ -179,6 +234,12 @@ int b200_gemm(const void* A, const void* B, void* C, int M, int N, int K, long l
     dco.a_lbo = desc_cfg[0]; dco.a_sbo = desc_cfg[1]; dco.a_kadv = desc_cfg[2];
     dco.b_lbo = desc_cfg[3]; dco.b_sbo = desc_cfg[4]; dco.b_kadv = desc_cfg[5];
     dcp = &dco;
+  }
+  if (!dcp && use_pair(M, N, K)) {
+    if (!a_mn && !b_mn) return launch_store_pair<false, false>(A, B, M, N, K, lda, ldb, fmt, sp, stream);
+    if (!a_mn && b_mn) return launch_store_pair<false, true>(A, B, M, N, K, lda, ldb, fmt, sp, stream);
+    if (a_mn && b_mn) return launch_store_pair<true, true>(A, B, M, N, K, lda, ldb, fmt, sp, stream);
+    return launch_store_pair<true, false>(A, B, M, N, K, lda, ldb, fmt, sp, stream);
   }
   const bool small_n = N <= 128;
   if (!a_mn && !b_mn) {
