@@ -26,7 +26,7 @@ class TeacherCollector:
         self.chunk_rows = max(128, (logits_chunk_bytes // (4 * self.vocab)) // 128 * 128)
 
     @torch.no_grad()
-    def content_logprobs(self, tokens: np.ndarray, convos: list[ConvoTokenized]):
+    def content_logprobs(self, tokens: np.ndarray, convos: list[ConvoTokenized], positions=None):
         """tokens [B, L] int64 (cropped to the longest member). Returns (values fp16 [M, K or Vc], ids int32 [M, K] or
         None, rows_per_convo) as host tensors; M = total content rows of the batch."""
         B, L = tokens.shape
@@ -34,7 +34,7 @@ class TeacherCollector:
         hs = self.model.hidden_states(ids)
         rows, counts = [], []
         for b, c in enumerate(convos):
-            ci = c.content_indices()
+            ci = c.content_indices() if positions is None else np.asarray(positions[b], dtype=np.int64)
             ci = ci[ci < min(c.length, L)]
             rows.append(ci + b * L)
             counts.append(len(ci))
@@ -72,7 +72,10 @@ class TeacherCollector:
             torch.cuda.current_stream().synchronize()
         return hv, hi, counts
 
-    def collect_batch(self, tokens: np.ndarray, convos: list[ConvoTokenized]) -> list[TeacherRows]:
+    def collect_batch(self, tokens: np.ndarray, convos: list[ConvoTokenized], aligner=None,
+                      validation: bool = False) -> list[TeacherRows]:
+        if aligner is not None:
+            return self._collect_aligned(tokens, convos, aligner, validation)
         hv, hi, counts = self.content_logprobs(tokens, convos)
         out, r = [], 0
         for c, n in zip(convos, counts):
@@ -82,4 +85,36 @@ class TeacherCollector:
             idx = None if hi is None else hi[r:r + n].numpy().astype(np.int64)
             out.append(TeacherRows(c.origin_convo_id, vals, idx, c.content_sha, c.sample))
             r += n
+        return out
+
+    def _collect_aligned(self, tokens, convos, aligner, validation) -> list[TeacherRows]:
+        """Teacher of another vocabulary: collect at the teacher positions that share a token boundary with the
+        student's content rows, map the ids onto the student vocabulary, and lay the rows out in student order
+        (rows without a counterpart are all -inf)."""
+        if not self.enable_topk:
+            raise ValueError("cross-tokenizer teachers need top-K storage (enable_topK)")
+        maps = [aligner.positions_for(c, validation) for c in convos]
+        wanted = [np.unique(m[m >= 0]) if m is not None else np.zeros(0, dtype=np.int64) for m in maps]
+        hv, hi, counts = self.content_logprobs(tokens, convos, positions=wanted)
+        out, r = [], 0
+        for c, m, w, n in zip(convos, maps, wanted, counts):
+            if m is None or len(m) == 0:
+                r += n
+                continue
+            vals = np.full((len(m), self.K), -np.inf, dtype=np.float16)
+            idx = np.tile(np.arange(self.K, dtype=np.int64), (len(m), 1))
+            if n:
+                lp, ids = aligner.remap(hv[r:r + n].to(self.device), hi[r:r + n].to(self.device), self.K)
+                lp, ids = lp.cpu().numpy().astype(np.float16), ids.cpu().numpy().astype(np.int64)
+                where = {int(p): j for j, p in enumerate(w[:n])}
+                for row, p in enumerate(m):
+                    j = where.get(int(p), -1) if p >= 0 else -1
+                    if j >= 0:
+                        vals[row], idx[row] = lp[j], ids[j]
+                # rows whose remapped list is shorter than K keep -inf tails with placeholder ids: make the ids unique
+                empty = ~np.isfinite(vals.astype(np.float32))
+                idx[empty] = (np.arange(self.K, dtype=np.int64)[None, :].repeat(len(m), 0))[empty]
+            r += n
+            s = (aligner.student_val_convos if validation else aligner.student_convos)[c.origin_convo_id]
+            out.append(TeacherRows(c.origin_convo_id, vals, idx, s.content_sha, s.sample))
         return out

@@ -11,7 +11,7 @@
 //
 // The custom per-conversation loss of the reference implementation is a function of the same (lse, z_k, U_k):
 // it is evaluated in PyTorch on the [rows, K] tensors and enters pass 2 through the same a_k / A interface.
-#include "../gemm/gemm_core.cuh"
+#include "../gemm/gemm_pair.cuh"
 #include "../common/host.cuh"
 
 namespace b200 {
@@ -176,14 +176,31 @@ struct EpiDz {
 template <class Epi>
 static int launch_head(const void* Hc, const void* W, int M, int N, int Kdim, long long ldh, long long ldw,
                        const typename Epi::Params& ep, cudaStream_t stream) {
-  using S = Smem<BN, STAGES>;
+  // enough 256 x 256 tiles: run on SM pairs (cta_group::2), else one CTA per 128 x 256 tile
+  const bool pair = (long long)ceil_div(M, PAIR_BM) * ceil_div(N, PAIR_BN) >= sm_count() / 2 && Kdim >= 256;
   CUtensorMap tmA, tmB;
   int rc = make_tmap_2d(&tmA, Hc, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)Kdim, (uint64_t)M, (uint64_t)ldh * 2,
                         BK, BM, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != B200_OK) return rc;
   rc = make_tmap_2d(&tmB, W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)Kdim, (uint64_t)N, (uint64_t)ldw * 2, BK,
-                    BN, CU_TENSOR_MAP_SWIZZLE_128B);
+                    pair ? PAIR_HALF_N : BN, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != B200_OK) return rc;
+  if (pair) {
+    constexpr int PSTAGES = 6;
+    auto kern = gemm_pair_kernel<PSTAGES, false, false, Epi>;
+    const int smem_bytes = SmemPair<PSTAGES>::bytes(Epi::SMEM_BYTES);
+    static bool attr = false;
+    if (!attr) {
+      B200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+      attr = true;
+    }
+    const int tiles = ceil_div(M, PAIR_BM) * ceil_div(N, PAIR_BN);
+    const int pairs = tiles < sm_count() / 2 ? tiles : sm_count() / 2;
+    kern<<<2 * pairs, NUM_THREADS, smem_bytes, stream>>>(tmA, tmB, M, N, Kdim, 1, ep, device_err_word());
+    B200_CUDA_CHECK(cudaGetLastError());
+    return B200_OK;
+  }
+  using S = Smem<BN, STAGES>;
   auto kern = gemm_kernel<BN, STAGES, false, false, Epi>;
   const int smem_bytes = S::bytes(Epi::SMEM_BYTES);
   static bool attr = false;
@@ -235,9 +252,11 @@ __global__ void __launch_bounds__(128) distill_rows_kernel(RowParams p) {
   const float* u = p.u + (long long)row * p.K;
   const int* ids = p.ids + (long long)row * p.K;
   // teacher log-softmax over the support at temperature T
+  // an entry takes part when its id is inside the cropped vocabulary and the teacher gave it a finite log-prob
+#define B200_ENTRY_OK(k) (ids[k] < p.vocab && u[k] > -1e30f)
   float umax = -INFINITY, zmax = -INFINITY;
   for (int k = lane; k < p.K; k += 32) {
-    const bool ok = ids[k] < p.vocab;
+    const bool ok = B200_ENTRY_OK(k);
     if (ok) {
       umax = fmaxf(umax, u[k] * p.inv_T);
       zmax = fmaxf(zmax, zk[k]);
@@ -247,19 +266,24 @@ __global__ void __launch_bounds__(128) distill_rows_kernel(RowParams p) {
   zmax = warp_max(zmax);
   float us = 0.f, zs = 0.f;
   for (int k = lane; k < p.K; k += 32) {
-    if (ids[k] < p.vocab) {
+    if (B200_ENTRY_OK(k)) {
       us += __expf(u[k] * p.inv_T - umax);
       zs += __expf(zk[k] - zmax);
     }
   }
   us = warp_sum(us);
   zs = warp_sum(zs);
+  if (!(us > 0.f)) {  // no teacher target on this row (e.g. no shared token boundary): zero loss, zero gradient
+    for (int k = lane; k < p.K; k += 32) p.a[(long long)row * p.K + k] = 0.f;
+    if (lane == 0) { p.loss[row] = 0.f; p.A[row] = 0.f; }
+    return;
+  }
   const float ulse = umax + __logf(us);  // teacher normaliser over the support
   const float zlse = zmax + __logf(zs);  // student normaliser over the support
   float loss = 0.f;
   // first sweep: the loss itself (reverse KL and renormalised JSD need it before the gradient)
   for (int k = lane; k < p.K; k += 32) {
-    if (ids[k] >= p.vocab) continue;
+    if (!B200_ENTRY_OK(k)) continue;
     const float t = u[k] * p.inv_T - ulse;
     const float pt = __expf(t);
     if (p.kind == 0) {
@@ -279,7 +303,7 @@ __global__ void __launch_bounds__(128) distill_rows_kernel(RowParams p) {
   float asum = 0.f, inner = 0.f;
   if (p.kind == 3) {
     for (int k = lane; k < p.K; k += 32) {
-      if (ids[k] >= p.vocab) continue;
+      if (!B200_ENTRY_OK(k)) continue;
       const float t = u[k] * p.inv_T - ulse;
       const float s1 = zk[k] - zlse;
       const float q = __expf(s1);
@@ -289,7 +313,7 @@ __global__ void __launch_bounds__(128) distill_rows_kernel(RowParams p) {
   }
   for (int k = lane; k < p.K; k += 32) {
     float ak = 0.f;
-    if (ids[k] < p.vocab) {
+    if (B200_ENTRY_OK(k)) {
       const float t = u[k] * p.inv_T - ulse;
       const float pt = __expf(t);
       if (p.kind == 0) {

@@ -276,3 +276,75 @@ extern "C" int b200_logprob_full(const float* logits, long long ld, int rows, in
   B200_CUDA_CHECK(cudaGetLastError());
   return B200_OK;
 }
+
+// ---------------------------------------------------------------------------------------------- vocabulary remap
+// Cross-tokenizer marginalisation of one teacher's top-K rows onto the student vocabulary: every teacher id is
+// sent through `table` (teacher id -> student id, -1 = no image), probabilities that land on the same student id
+// are summed, the best K_out are kept and written as (log-prob, id) sorted by probability. Entries without an image
+// (or with a non-finite log-prob) drop out; unused output slots get -inf and id 0.
+namespace b200 {
+namespace topk {
+__global__ void __launch_bounds__(NT) remap_topk_kernel(const float* __restrict__ lp, const int* __restrict__ ids,
+                                                       const int* __restrict__ table, int table_size, int K, int K_out,
+                                                       float* __restrict__ o_lp, int* __restrict__ o_id) {
+  __shared__ unsigned long long s[MAX_K];
+  __shared__ float pv[MAX_K];
+  __shared__ float comb[MAX_K];
+  const long long row = blockIdx.x;
+  int n2 = 1;
+  while (n2 < K) n2 <<= 1;
+  for (int i = threadIdx.x; i < n2; i += NT) {
+    unsigned long long key = 0ull;
+    if (i < K) {
+      const int t = ids[row * K + i];
+      const float l = lp[row * K + i];
+      const int sid = (t >= 0 && t < table_size) ? table[t] : -1;
+      pv[i] = (sid >= 0 && l > -1e30f) ? __expf(l) : 0.f;
+      // key: (student id + 1) so that "no image" (0) sorts last together with the padding
+      key = (sid >= 0 && l > -1e30f) ? (((unsigned long long)(uint32_t)(sid + 1) << 32) | (uint32_t)i) : 0ull;
+    }
+    s[i] = key;
+  }
+  __syncthreads();
+  bitonic_desc(s, n2);
+  // run heads take the sum of their run (runs can be longer than two here)
+  for (int i = threadIdx.x; i < n2; i += NT) {
+    const unsigned long long e = s[i];
+    float c = -1.f;
+    if (e != 0ull) {
+      const uint32_t id = (uint32_t)(e >> 32);
+      if (i == 0 || (uint32_t)(s[i - 1] >> 32) != id) {
+        c = 0.f;
+        for (int j = i; j < n2 && (uint32_t)(s[j] >> 32) == id; ++j) c += pv[(uint32_t)s[j]];
+      }
+    }
+    comb[i] = c;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < n2; i += NT) {
+    const unsigned long long e = s[i];
+    const float c = comb[i];
+    __syncwarp();
+    s[i] = (c >= 0.f) ? (((unsigned long long)fkey(c) << 32) | (0xffffffffu - ((uint32_t)(e >> 32) - 1u))) : 0ull;
+  }
+  __syncthreads();
+  bitonic_desc(s, n2);
+  for (int i = threadIdx.x; i < K_out; i += NT) {
+    const unsigned long long e = i < n2 ? s[i] : 0ull;
+    o_lp[row * K_out + i] = e ? __logf(kfloat((uint32_t)(e >> 32))) : -INFINITY;
+    o_id[row * K_out + i] = e ? (int)(0xffffffffu - (uint32_t)e) : 0;
+  }
+}
+}  // namespace topk
+}  // namespace b200
+
+extern "C" int b200_remap_topk(const float* lp, const int* ids, const int* table, int table_size, int rows, int K,
+                               int K_out, float* o_lp, int* o_id, cudaStream_t st) {
+  using namespace b200;
+  if (!lp || !ids || !table || !o_lp || !o_id || rows <= 0 || K <= 0 || K_out <= 0 || table_size <= 0)
+    return B200_ERR_ARG;
+  if (K > topk::MAX_K || K_out > topk::MAX_K) return B200_ERR_TOO_BIG;
+  topk::remap_topk_kernel<<<rows, topk::NT, 0, st>>>(lp, ids, table, table_size, K, K_out, o_lp, o_id);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200_OK;
+}

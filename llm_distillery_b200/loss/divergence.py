@@ -30,10 +30,14 @@ def student_teacher_logprobs(lse: torch.Tensor, zk: torch.Tensor, u: torch.Tenso
     ``valid`` [M,K] bool marks usable entries (ids inside the cropped vocabulary)."""
     s = zk - lse[:, None]
     ut = u / temperature
+    finite = torch.isfinite(ut)
+    valid = finite if valid is None else (valid & finite)      # -inf entries (no teacher target) are outside the support
     if valid is not None:
         ut = ut.masked_fill(~valid, float("-inf"))
         s = s.masked_fill(~valid, float("-inf"))
-    t = F.log_softmax(ut, dim=-1)
+    row_ok = valid.any(-1, keepdim=True)                       # rows without any target stay finite (and unused)
+    t = F.log_softmax(torch.where(row_ok, ut, torch.zeros_like(ut)), dim=-1)
+    t = torch.where(valid, t, torch.full_like(t, float("-inf")))
     return s, t
 
 
@@ -46,7 +50,9 @@ def loss_rows(kind: str, s: torch.Tensor, t: torch.Tensor, jsd_renorm: bool = Fa
     if kind == "kl":
         s0 = torch.where(valid, s, zero)
         return torch.where(valid, t0.exp() * (t0 - s0), zero).sum(-1)
-    s1 = torch.where(valid, F.log_softmax(torch.where(valid, s, torch.full_like(s, float("-inf"))), dim=-1), zero)
+    row_ok = valid.any(-1, keepdim=True)
+    s_in = torch.where(valid, s, torch.full_like(s, float("-inf")))
+    s1 = torch.where(valid, F.log_softmax(torch.where(row_ok, s_in, zero), dim=-1), zero)
     if kind == "rkl":
         return torch.where(valid, s1.exp() * (s1 - t0), zero).sum(-1)
     if kind == "jsd":

@@ -75,14 +75,16 @@ class TeacherModel(BaseModel):
         if not chunk:
             return 0
         model = self.load()
-        collector = TeacherCollector(model, topk=self.topK, crop_to_size=self.crop_to_size, enable_topk=self.enable_topK)
+        aligner = getattr(self, "aligner", None)
+        crop = model.cfg.vocab_size if aligner is not None else self.crop_to_size   # own vocabulary when remapping
+        collector = TeacherCollector(model, topk=self.topK, crop_to_size=crop, enable_topk=self.enable_topK)
         batches = plan_batches(chunk, max(1, self.batch_size))[rank::max(1, world)]
         done = 0
         t0 = time.time()
         with progress(total=len(chunk), desc="Convos", leave=False) as bar:
             bar.set_postfix_str("Generating...")
             for tokens, convos in batches:
-                rows = collector.collect_batch(tokens, convos)
+                rows = collector.collect_batch(tokens, convos, aligner=aligner, validation=validation)
                 if sha_by_id:   # the store is keyed by the STUDENT's view of the text (that is what sync compares)
                     for r in rows:
                         r.content_sha = sha_by_id.get(r.convo_id, r.content_sha)

@@ -8,6 +8,7 @@ from ._lib import _VP, _I, _LL
 
 _lib.register("b200_topk_logprob", [_VP, _LL, _I, _I, _I, _VP, _VP, _VP])
 _lib.register("b200_topk_merge", [_VP, _VP, _VP, _VP, _I, _I, _VP, _VP, _VP])
+_lib.register("b200_remap_topk", [_VP, _VP, _VP, _I, _I, _I, _I, _VP, _VP, _VP])
 _lib.register("b200_logprob_full", [_VP, _LL, _I, _I, _VP, _LL, _VP])
 
 
@@ -58,4 +59,32 @@ def topk_merge(a_lp: torch.Tensor, a_id: torch.Tensor, b_lp: torch.Tensor, b_id:
     _lib.check(_lib.kernels().b200_topk_merge(_lib.ptr(a_lp.float().contiguous()), _lib.ptr(a_id.int().contiguous()),
                                               _lib.ptr(b_lp.float().contiguous()), _lib.ptr(b_id.int().contiguous()), rows, K,
                                               _lib.ptr(o_lp), _lib.ptr(o_id), _lib.stream()), "b200_topk_merge")
+    return o_lp, o_id
+
+
+def remap_topk(lp: torch.Tensor, ids: torch.Tensor, table: torch.Tensor, k_out: int):
+    """Send top-K rows through a teacher-id -> student-id table (-1 = no image), sum probabilities that meet on one
+    student id, keep the best ``k_out``. Returns (fp32 log-prob [rows, k_out], int32 id); empty slots are -inf / 0."""
+    rows, K = lp.shape
+    if not lp.is_cuda:
+        o_lp = torch.full((rows, k_out), float("-inf"))
+        o_id = torch.zeros((rows, k_out), dtype=torch.int32)
+        tab = table.long()
+        for r in range(rows):
+            sid = tab[ids[r].long().clamp(0, len(tab) - 1)]
+            ok = (sid >= 0) & torch.isfinite(lp[r]) & (ids[r] >= 0) & (ids[r] < len(tab))
+            if not ok.any():
+                continue
+            u, inv = torch.unique(sid[ok], return_inverse=True)
+            acc = torch.zeros(len(u)).index_add_(0, inv, lp[r][ok].float().exp())
+            v, j = torch.sort(acc, descending=True, stable=True)
+            n = min(k_out, len(u))
+            o_lp[r, :n] = v[:n].log()
+            o_id[r, :n] = u[j[:n]].to(torch.int32)
+        return o_lp, o_id
+    o_lp = torch.empty((rows, k_out), dtype=torch.float32, device=lp.device)
+    o_id = torch.empty((rows, k_out), dtype=torch.int32, device=lp.device)
+    _lib.check(_lib.kernels().b200_remap_topk(_lib.ptr(lp.float().contiguous()), _lib.ptr(ids.int().contiguous()),
+                                              _lib.ptr(table.int().contiguous()), table.numel(), rows, K, k_out,
+                                              _lib.ptr(o_lp), _lib.ptr(o_id), _lib.stream()), "b200_remap_topk")
     return o_lp, o_id

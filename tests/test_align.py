@@ -1,0 +1,137 @@
+"""Cross-tokenizer alignment: byte trie, vocabulary map, position pairing, mass remap, two-teacher end-to-end run."""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from llm_distillery_b200 import cli
+from llm_distillery_b200.align import aligner as al
+from llm_distillery_b200.data.h5store import H5Store
+from llm_distillery_b200.models.llama import preset
+from llm_distillery_b200.ops import topk
+from llm_distillery_b200.utils import synthetic
+
+
+@pytest.fixture(scope="module")
+def toks(tmp_path_factory):
+    root = tmp_path_factory.mktemp("toks")
+    a = synthetic.make_tokenizer(str(root / "a"), 400, seed=0)
+    b = synthetic.make_tokenizer(str(root / "b"), 700, seed=5, extra_merges_text="quartz sphinx wizard " * 50)
+    return root, a, b
+
+
+def test_trie_and_vocab_map(toks):
+    _, a, b = toks
+    t = al.ByteTrie()
+    for i, k in enumerate([b"a", b"ab", b"abc", b"b", b"abd"]):
+        t.insert(k, i)
+    assert t.longest_prefix(b"abcd") == 2 and t.longest_prefix(b"abx") == 1 and t.longest_prefix(b"zz") == -1
+    ident = al.build_vocab_map(a, a)
+    tb = al.token_bytes(a)
+    real = [i for i, x in enumerate(tb) if x]
+    dup = {}
+    for i in real:
+        dup.setdefault(tb[i], i)
+    assert all(ident[i] == dup[tb[i]] for i in real)                  # same vocabulary -> identity (lowest id of equal strings)
+    m = al.build_vocab_map(b, a)
+    sb, tbb = al.token_bytes(a), al.token_bytes(b)
+    for t_id in np.random.default_rng(0).choice(len(tbb), 200):
+        if not tbb[t_id]:
+            assert m[t_id] == -1
+            continue
+        assert m[t_id] >= 0                                            # byte fallback: every token has an image
+        img = sb[m[t_id]]
+        assert tbb[t_id].startswith(img)
+        assert not any(tbb[t_id].startswith(x) and len(x) > len(img) for x in sb if x)   # and it is the longest
+
+
+def test_remap_conserves_mass_and_matches_bruteforce(toks):
+    _, a, b = toks
+    table = torch.from_numpy(al.build_vocab_map(b, a))
+    g = torch.Generator().manual_seed(0)
+    V, K = len(table), 40
+    lp, ids = torch.log_softmax(torch.randn(30, V, generator=g) * 3, -1).topk(K, -1)
+    o_lp, o_id = topk.remap_topk(lp, ids.int(), table, K)
+    for r in range(30):
+        acc = {}
+        for l, i in zip(lp[r].tolist(), ids[r].tolist()):
+            s = int(table[i])
+            if s >= 0:
+                acc[s] = acc.get(s, 0.0) + float(np.exp(l))
+        got = {int(i): float(np.exp(l)) for l, i in zip(o_lp[r].tolist(), o_id[r].tolist()) if np.isfinite(l)}
+        assert got.keys() == acc.keys()
+        assert all(abs(got[k] - acc[k]) < 1e-5 for k in acc)
+        assert abs(sum(got.values()) - sum(acc.values())) < 1e-5 and sum(got.values()) <= lp[r].exp().sum() + 1e-5
+        vals = o_lp[r][torch.isfinite(o_lp[r])]
+        assert (vals[:-1] >= vals[1:] - 1e-6).all()
+
+
+def test_position_alignment_on_shared_text(toks):
+    _, a, b = toks
+    from llm_distillery_b200.data.tokenize import TokenizeSpec, encode_prompt_format, tokenize_sample
+    from llm_distillery_b200.data.convo import ConvoTokenized
+    from llm_distillery_b200.config import DEFAULT_PROMPT_FORMAT
+    item = {"init": "", "conversations": [{"from": "human", "value": "the quick brown fox jumps over wizard quartz 42"},
+                                          {"from": "gpt", "value": "sphinx of black quartz judge my vow"}], "tags": []}
+    convs = []
+    for tk in (a, b):
+        spec = TokenizeSpec(128, model_student=True, model_add_bos=True, bos_token_id=1)
+        _, t, ranges, n, empty = tokenize_sample(0, item, tk, encode_prompt_format(DEFAULT_PROMPT_FORMAT, tk), spec)
+        convs.append(ConvoTokenized(t, ranges, 128 - n, False, 0))
+    s, t = convs
+    sb, tb = al.token_bytes(a), al.token_bytes(b)
+    pos = al.align_positions(s, t, sb, tb)
+    so, to = al.start_offsets(s.tokenized, s.length, sb), al.start_offsets(t.tokenized, t.length, tb)
+    assert so[-1] == to[-1]                                   # both token streams spell the same bytes
+    ci = s.content_indices(); ci = ci[ci < s.length]
+    assert (pos >= 0).mean() > 0.2       # the finer tokenizer has many boundaries the coarser one lacks
+    for r, p in enumerate(pos):
+        if p >= 0:
+            assert so[ci[r] + 1] == to[p + 1]
+
+
+def test_two_teachers_one_with_another_tokenizer(toks, tmp_path):
+    root, a, b = toks
+    os.environ["B200_NO_PROGRESS"] = "1"
+    cfg_t = preset("plumbing-teacher", vocab_size=768, hidden_size=64, intermediate_size=176, max_position_embeddings=128)
+    cfg_s = preset("plumbing-student", vocab_size=512, hidden_size=64, intermediate_size=176, max_position_embeddings=128,
+                   num_hidden_layers=2)
+    synthetic.make_model_dir(str(tmp_path / "teachers" / "t_same"), preset("plumbing-teacher", vocab_size=512, hidden_size=64,
+                             intermediate_size=176, max_position_embeddings=128), str(root / "a"), seed=1, batch_size=4, add_bos=False)
+    synthetic.make_model_dir(str(tmp_path / "teachers" / "t_other"), cfg_t, str(root / "b"), seed=2, batch_size=4, add_bos=False)
+    synthetic.make_model_dir(str(tmp_path / "student"), cfg_s, str(root / "a"), seed=3)
+    synthetic.make_dataset(str(tmp_path / "train.jsonl"), 10, seed=3)
+    synthetic.make_dataset(str(tmp_path / "val.jsonl"), 3, seed=4)
+    conf = {"cache_folder": str(tmp_path / "cache"), "dataset_path": str(tmp_path / "train.jsonl"),
+            "validation_dataset_path": str(tmp_path / "val.jsonl"), "teacher_models_folder": str(tmp_path / "teachers"),
+            "student_path": str(tmp_path / "student"), "context_len": 96, "crop_distr_to_size": 400, "save_topK": 16,
+            "device": "cpu", "num_epochs": 1, "batch_size": 2, "grad_accum_batches": 1, "lr": 1e-3, "optimizer": "adamw",
+            "training_precision": "fp32", "freeze_layers": [], "loss": "jsd", "cross_tokenizer": True}
+    (tmp_path / "config.json").write_text(json.dumps(conf))
+    with pytest.raises(ValueError):
+        cli.main(["--config", str(tmp_path / "config.json"), "--cross_tokenizer", "false"])
+    out = cli.main(["--config", str(tmp_path / "config.json")])
+    assert out["trained_samples"] == 10
+    st = H5Store(str(tmp_path / "cache" / "dataset"))
+    v, ix = st.load_id(st.get_dataset_ids()[0])
+    mass = np.exp(v).sum(-1)
+    assert ix.max() < 400 and (mass > 0.03).all() and (mass <= 2.0 + 1e-2).all()
+    st.close()
+    # the other-vocabulary teacher alone: aligned rows carry remapped mass on student ids, unaligned rows are empty
+    conf2 = dict(conf, teacher_models_folder=str(tmp_path / "teachers" / "t_other"), cache_folder=str(tmp_path / "cache2"),
+                 loss="kl")
+    (tmp_path / "config2.json").write_text(json.dumps(conf2))
+    out = cli.main(["--config", str(tmp_path / "config2.json")])
+    assert out["trained_samples"] == 10 and np.isfinite(out["last_validation"]["kl_div"])
+    st = H5Store(str(tmp_path / "cache2" / "dataset"))
+    got_rows = empty_rows = 0
+    for cid in st.get_dataset_ids():
+        v, ix = st.load_id(cid)
+        fin = np.isfinite(v)
+        got_rows += int(fin.any(1).sum())
+        empty_rows += int((~fin.any(1)).sum())
+        assert ix[fin].max() < 400 and (np.exp(v[fin.any(1)]).sum(-1) <= 1.0 + 1e-2).all()
+    assert got_rows > 0 and empty_rows > 0
+    st.close()
