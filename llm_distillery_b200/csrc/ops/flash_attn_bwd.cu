@@ -2,8 +2,9 @@
 //
 // One CTA owns one (batch, kv-head, 128-key block): K_j and V_j stay resident in shared memory, dK_j and dV_j
 // accumulate in TMEM over every query head of the group and every query block at or after the diagonal, and
-// are written once. dQ is produced per (query block, key block) pair and reduced into an fp32 buffer with
-// vector red.global.add (the same scheme as FlashAttention-2), then converted to bf16 by a small kernel.
+// are written once. dQ is produced per (query block, key block) pair, staged in shared memory and added into an fp32
+// buffer by TMA reduce-add (whole 32-byte sectors per request instead of scattered per-thread atomics, which bound
+// an earlier version of this kernel), then converted to bf16 by a small kernel.
 //
 // Per iteration (query head hq, query block i), five tcgen05.mma groups:
 //   S  = Q_i K_j^T                 (A K-major, B K-major)        -> TMEM
@@ -15,7 +16,8 @@
 // A [q x k] tile written row-per-thread in the 128B-swizzled K-major layout is, byte for byte, also the
 // MN-major layout of its transpose, so P and dS are stored once and read both ways.
 //
-// Roles: warp 0 TMA producer (Q_i / dO_i ring), warp 1 MMA issuer, warps 2-5 softmax + dQ drain + epilogue.
+// Roles: warp 0 TMA producer (Q_i / dO_i ring), warp 1 MMA issuer, warps 2-9 softmax + dQ drain + epilogue: each TMEM
+// lane quadrant is served by two warps that split the tile's columns, so every SM sub-partition has two warps to issue from.
 #include "../common/ptx.cuh"
 #include "../common/host.cuh"
 
@@ -24,7 +26,7 @@ namespace fab {
 
 constexpr int BM = 128;  // queries per block
 constexpr int BN = 128;  // keys per block
-constexpr int NTHREADS = 192;
+constexpr int NTHREADS = 320;  // TMA warp, MMA warp, 8 softmax/drain warps (two per TMEM lane quadrant)
 
 template <int D>
 struct Cfg {
@@ -38,7 +40,9 @@ struct Cfg {
   static constexpr int OFF_QDO = 2 * KV_BYTES;
   static constexpr int OFF_P = OFF_QDO + STAGES * STAGE_BYTES;
   static constexpr int OFF_DS = OFF_P + P_BYTES;
-  static constexpr int OFF_BAR = OFF_DS + P_BYTES;
+  static constexpr int OFF_DQS = OFF_DS + P_BYTES;  // dQ staging: two [128 x 32] fp32 sub-tiles, 128B-swizzled
+  static constexpr int DQS_BYTES = 2 * BM * 128;
+  static constexpr int OFF_BAR = OFF_DQS + DQS_BYTES;
   static constexpr int SMEM_BYTES = OFF_BAR + 256;
   static constexpr bool ALIAS = (D == 128);  // dQ shares TMEM columns with S
   static constexpr uint32_t S_COL = 0;
@@ -58,15 +62,10 @@ struct BwdParams {
   float scale;
 };
 
-__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
-               : "memory");
-}
-
 template <int D>
 __global__ void __launch_bounds__(NTHREADS, 1)
-    flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmDO, BwdParams p,
-                     unsigned int* err_word) {
+    flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmDO,
+                     const __grid_constant__ CUtensorMap tmDQ, BwdParams p, unsigned int* err_word) {
   using C = Cfg<D>;
   constexpr int ST = C::STAGES;
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -78,7 +77,9 @@ __global__ void __launch_bounds__(NTHREADS, 1)
   uint64_t* pds_ready = bars + 6;
   uint64_t* dq_full = bars + 7;
   uint64_t* dq_empty = bars + 8;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  uint64_t* stage_full = bars + 9;   // dQ staging tile written by all 256 drain threads
+  uint64_t* stage_free = bars + 10;  // ... and read out by the TMA reduce
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -101,15 +102,18 @@ __global__ void __launch_bounds__(NTHREADS, 1)
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tmQKV);
     tma_prefetch_desc(&tmDO);
+    tma_prefetch_desc(&tmDQ);
     mbar_init(kv_full, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(&qdo_full[s], 1);
       mbar_init(&qdo_empty[s], 1);
     }
     mbar_init(sdp_full, 1);
-    mbar_init(pds_ready, 128);
+    mbar_init(pds_ready, 256);
     mbar_init(dq_full, 1);
-    mbar_init(dq_empty, 128);
+    mbar_init(dq_empty, 256);
+    mbar_init(stage_full, 256);
+    mbar_init(stage_free, 1);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -216,42 +220,60 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     }
   } else {
     const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;  // which half of the columns this warp handles
     const int r = quad * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
     const float c2 = p.scale * 1.4426950408889634f;
     uint8_t* sP = smem + C::OFF_P;
     uint8_t* sDS = smem + C::OFF_DS;
+    constexpr int SCH = BN / 64;  // 32-column chunks of S / dP per warp
+    constexpr int DCH = D / 64;   // 32-column chunks of dQ / dK / dV per warp
     bool ok = true;
-    for (int it = 0; it < n_it; ++it) {
+    uint32_t rd = 0;  // staging rounds so far
+    for (int it = 0; ok && it < n_it; ++it) {
       const int hq = hkv * g + it / nqi;
       const int q0 = (i_start + it % nqi) * BM;
       const int qi = q0 + r;
       const bool row_ok = qi < p.L;
       const long long t = (long long)b * p.L + qi;
-      const float lse2 = row_ok ? p.lse[(long long)hq * T + t] * 1.4426950408889634f : 0.f;
-      const float dlt = row_ok ? p.delta[(long long)hq * T + t] : 0.f;
+      // a row past the end of the sequence gets lse = +inf: exp2(s - inf) = 0, so P and dS vanish without a mask
+      const float lse2 = row_ok ? p.lse[(long long)hq * T + t] * 1.4426950408889634f : INFINITY;
+      const float dlts = row_ok ? p.delta[(long long)hq * T + t] * p.scale : 0.f;
       const bool diag = (kv0 + BN - 1) > q0;
+      const int lim = diag ? (qi - kv0) : 0x7fffffff;  // tile columns <= lim are visible to this row
       int w = mbar_wait_bounded(sdp_full, it & 1u, abort_flag, err_word, ERR_WAIT_TMEM_FULL) ? 1 : 0;
       if (!__all_sync(0xffffffffu, w)) { ok = false; break; }
       tc_fence_after_sync();
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+#pragma unroll
+      for (int cc = 0; cc < SCH; ++cc) {
+        const int c = half * SCH + cc;
         uint32_t sv[32], dv[32];
         tmem_ld_32x32b_x32(tmem_base + lane_addr + C::S_COL + c * 32, sv);
         tmem_ld_32x32b_x32(tmem_base + lane_addr + C::DP_COL + c * 32, dv);
         tmem_ld_wait();
         uint32_t pkP[16], pkS[16];
+        if (!diag) {
 #pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          float p0 = fast_exp2(__uint_as_float(sv[e]) * c2 - lse2);
-          float p1 = fast_exp2(__uint_as_float(sv[e + 1]) * c2 - lse2);
-          const int kvi = kv0 + c * 32 + e;
-          if (!row_ok || (diag && kvi > qi)) p0 = 0.f;
-          if (!row_ok || (diag && kvi + 1 > qi)) p1 = 0.f;
-          const float d0 = p0 * (__uint_as_float(dv[e]) - dlt) * p.scale;
-          const float d1 = p1 * (__uint_as_float(dv[e + 1]) - dlt) * p.scale;
-          pkP[e >> 1] = pack_bf16x2(p0, p1);
-          pkS[e >> 1] = pack_bf16x2(d0, d1);
+          for (int e = 0; e < 32; e += 2) {
+            const float p0 = fast_exp2(fmaf(__uint_as_float(sv[e]), c2, -lse2));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(sv[e + 1]), c2, -lse2));
+            const float d0 = p0 * fmaf(__uint_as_float(dv[e]), p.scale, -dlts);
+            const float d1 = p1 * fmaf(__uint_as_float(dv[e + 1]), p.scale, -dlts);
+            pkP[e >> 1] = pack_bf16x2(p0, p1);
+            pkS[e >> 1] = pack_bf16x2(d0, d1);
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            float p0 = fast_exp2(fmaf(__uint_as_float(sv[e]), c2, -lse2));
+            float p1 = fast_exp2(fmaf(__uint_as_float(sv[e + 1]), c2, -lse2));
+            if ((c * 32 + e) > lim) p0 = 0.f;
+            if ((c * 32 + e + 1) > lim) p1 = 0.f;
+            const float d0 = p0 * fmaf(__uint_as_float(dv[e]), p.scale, -dlts);
+            const float d1 = p1 * fmaf(__uint_as_float(dv[e + 1]), p.scale, -dlts);
+            pkP[e >> 1] = pack_bf16x2(p0, p1);
+            pkS[e >> 1] = pack_bf16x2(d0, d1);
+          }
         }
         const int sub = (c * 32) >> 6;
         const int chunk0 = ((c * 32) & 63) >> 3;
@@ -272,22 +294,43 @@ __global__ void __launch_bounds__(NTHREADS, 1)
       int w2 = mbar_wait_bounded(dq_full, it & 1u, abort_flag, err_word, ERR_WAIT_AUX) ? 1 : 0;
       if (!__all_sync(0xffffffffu, w2)) { ok = false; break; }
       tc_fence_after_sync();
-      float* dq_row = p.dq_acc + t * (long long)(p.H * D) + hq * D;
+      // stage the fp32 tile in shared memory (row r, 128-byte rows of 32 floats, 16-byte chunks XOR-swizzled like
+      // every other tile here) and let one thread hand it to the TMA reduce engine. D = 128 takes two rounds.
+      uint8_t* sDQ = smem + C::OFF_DQS;
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
+      for (int cc = 0; cc < DCH; ++cc) {
+        const int c = half * DCH + cc;  // 32-column chunk of dQ
         uint32_t v[32];
         tmem_ld_32x32b_x32(tmem_base + lane_addr + C::DQ_COL + c * 32, v);
         tmem_ld_wait();
-        if (row_ok) {
+        // the previous round's reduce has finished reading the staging tile (bounded wait, like every wait here)
+        int w3 = mbar_wait_bounded(stage_free, (rd & 1u) ^ 1u, abort_flag, err_word, ERR_WAIT_AUX) ? 1 : 0;
+        if (!__all_sync(0xffffffffu, w3)) { ok = false; break; }
+        uint8_t* rowp = sDQ + half * (BM * 128) + r * 128;
 #pragma unroll
-          for (int q4 = 0; q4 < 8; ++q4)
-            red_add_v4(dq_row + c * 32 + q4 * 4, __uint_as_float(v[q4 * 4]), __uint_as_float(v[q4 * 4 + 1]),
-                       __uint_as_float(v[q4 * 4 + 2]), __uint_as_float(v[q4 * 4 + 3]));
+        for (int q4 = 0; q4 < 8; ++q4)
+          *reinterpret_cast<uint4*>(rowp + ((q4 ^ (r & 7)) * 16)) =
+              make_uint4(v[q4 * 4], v[q4 * 4 + 1], v[q4 * 4 + 2], v[q4 * 4 + 3]);
+        fence_proxy_async_smem();
+        mbar_arrive(stage_full);
+        if (warp == 2 && lane == 0) {
+          if (mbar_wait_bounded(stage_full, rd & 1u, abort_flag, err_word, ERR_WAIT_AUX)) {
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh)
+              tma_reduce_add_3d(&tmDQ, sDQ + hh * (BM * 128), hq * D + (hh * DCH + cc) * 32, q0, b);
+            tma_store_commit();
+            tma_store_wait_read0();
+            mbar_arrive(stage_free);
+          }
         }
+        __syncwarp();
+        ++rd;
       }
+      if (!ok) break;
       tc_fence_before_sync();
       mbar_arrive(dq_empty);
     }
+    if (warp == 2 && lane == 0) tma_store_wait_all0();
     // epilogue: dK_j, dV_j (thread = key row). The last dq_full wait covered every MMA of this CTA.
     if (ok && n_it > 0) {
       const int kvi = kv0 + r;
@@ -300,7 +343,8 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         const uint32_t col = which == 0 ? C::DK_COL : C::DV_COL;
         __nv_bfloat16* dst = which == 0 ? krow : vrow;
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
+        for (int cc = 0; cc < DCH; ++cc) {
+          const int c = half * DCH + cc;
           uint32_t v[32];
           tmem_ld_32x32b_x32(tmem_base + lane_addr + col + c * 32, v);
           tmem_ld_wait();
@@ -398,6 +442,10 @@ static int launch_bwd(const void* dout, const void* qkv, const void* out, const 
   rc = make_tmap_3d(&tmDO, dout, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)HD, (uint64_t)L, (uint64_t)B,
                     (uint64_t)HD * 2, (uint64_t)L * HD * 2, 64, 128, 1, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != B200_OK) return rc;
+  CUtensorMap tmDQ;
+  rc = make_tmap_3d(&tmDQ, dq_acc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (uint64_t)HD, (uint64_t)L, (uint64_t)B,
+                    (uint64_t)HD * 4, (uint64_t)L * HD * 4, 32, 128, 1, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != B200_OK) return rc;
   {
     const long long threads = T * H * (D / 8);
     delta_kernel<D><<<(unsigned)((threads + 255) / 256), 256, 0, st>>>((const __nv_bfloat16*)dout,
@@ -413,7 +461,7 @@ static int launch_bwd(const void* dout, const void* qkv, const void* out, const 
   }
   BwdParams p{lse, delta, dq_acc, (__nv_bfloat16*)dqkv, B, L, H, Hkv, 1.0f / sqrtf((float)D)};
   dim3 grid((L + BN - 1) / BN, Hkv, B);
-  kern<<<grid, NTHREADS, C::SMEM_BYTES, st>>>(tmQKV, tmDO, p, device_err_word());
+  kern<<<grid, NTHREADS, C::SMEM_BYTES, st>>>(tmQKV, tmDO, tmDQ, p, device_err_word());
   B200_CUDA_CHECK(cudaGetLastError());
   {
     long long work = T * (HD >> 3);

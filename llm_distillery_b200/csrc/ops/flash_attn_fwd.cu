@@ -177,18 +177,32 @@ __global__ void __launch_bounds__(NTHREADS, 2)
       tc_fence_after_sync();
       const int kv0 = j * BN;
       const bool diag = (kv0 + BN - 1) > q0;  // some keys of this tile may be masked for some rows
-      // pass 1: row max
+      // pass 1: row max (the masked variant only runs on tiles that cross the diagonal)
       float mx = -INFINITY;
+      if (!diag) {
 #pragma unroll
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(tmem_base + lane_addr + C::S_COL + c * 32, v);
-        tmem_ld_wait();
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(tmem_base + lane_addr + C::S_COL + c * 32, v);
+          tmem_ld_wait();
+          float m0 = -INFINITY, m1 = -INFINITY;
 #pragma unroll
-        for (int t = 0; t < 32; ++t) {
-          float x = __uint_as_float(v[t]);
-          if (diag && (kv0 + c * 32 + t) > qi) x = -INFINITY;
-          mx = fmaxf(mx, x);
+          for (int t = 0; t < 32; t += 2) {
+            m0 = fmaxf(m0, __uint_as_float(v[t]));
+            m1 = fmaxf(m1, __uint_as_float(v[t + 1]));
+          }
+          mx = fmaxf(mx, fmaxf(m0, m1));
+        }
+      } else {
+        const int lim = qi - kv0;  // columns <= lim are visible
+#pragma unroll
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(tmem_base + lane_addr + C::S_COL + c * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int t = 0; t < 32; ++t)
+            mx = fmaxf(mx, (c * 32 + t) <= lim ? __uint_as_float(v[t]) : -INFINITY);
         }
       }
       float alpha = 1.f;
@@ -213,26 +227,34 @@ __global__ void __launch_bounds__(NTHREADS, 2)
       }
       // pass 2: p = exp2((s - m) * c2) -> bf16 -> swizzled smem ; l += sum(p)
       const float mb = (m_used == -INFINITY) ? 0.f : m_used * c2;
-      float lsum = 0.f;
+      float lsum = 0.f, lsum1 = 0.f;
+      const int lim2 = diag ? (qi - kv0) : 0x7fffffff;
 #pragma unroll
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t v[32];
         tmem_ld_32x32b_x32(tmem_base + lane_addr + C::S_COL + c * 32, v);
         tmem_ld_wait();
         uint32_t pk[16];
+        if (!diag) {
 #pragma unroll
-        for (int t = 0; t < 32; t += 2) {
-          float x0 = __uint_as_float(v[t]), x1 = __uint_as_float(v[t + 1]);
-          float p0 = fast_exp2(x0 * c2 - mb), p1 = fast_exp2(x1 * c2 - mb);
-          if (diag) {
-            if ((kv0 + c * 32 + t) > qi) p0 = 0.f;
-            if ((kv0 + c * 32 + t + 1) > qi) p1 = 0.f;
+          for (int t = 0; t < 32; t += 2) {
+            const float p0 = fast_exp2(fmaf(__uint_as_float(v[t]), c2, -mb));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(v[t + 1]), c2, -mb));
+            lsum += p0;
+            lsum1 += p1;
+            pk[t >> 1] = pack_bf16x2(p0, p1);
           }
-          // accumulate what the tensor core will see (bf16-rounded), so O / l is a true average
-          __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
-          float2 back = __bfloat1622float2(h2);
-          lsum += back.x + back.y;
-          pk[t >> 1] = *reinterpret_cast<uint32_t*>(&h2);
+        } else {
+#pragma unroll
+          for (int t = 0; t < 32; t += 2) {
+            float p0 = fast_exp2(fmaf(__uint_as_float(v[t]), c2, -mb));
+            float p1 = fast_exp2(fmaf(__uint_as_float(v[t + 1]), c2, -mb));
+            if ((c * 32 + t) > lim2) p0 = 0.f;
+            if ((c * 32 + t + 1) > lim2) p1 = 0.f;
+            lsum += p0;
+            lsum1 += p1;
+            pk[t >> 1] = pack_bf16x2(p0, p1);
+          }
         }
         // columns c*32 .. c*32+31 of row r: sub-tile (c*32)/64, 16-byte chunks ((c*32)%64)/8 + {0..3}
         const int sub = (c * 32) >> 6;
@@ -245,6 +267,7 @@ __global__ void __launch_bounds__(NTHREADS, 2)
               make_uint4(pk[q4 * 4], pk[q4 * 4 + 1], pk[q4 * 4 + 2], pk[q4 * 4 + 3]);
         }
       }
+      lsum += lsum1;
       l += lsum;
       // lazy rescale of the O accumulator (warp-uniform decision: tcgen05.ld/st are warp-collective)
       if (__any_sync(0xffffffffu, need)) {
