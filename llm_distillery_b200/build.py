@@ -4,7 +4,10 @@
 No GPU is needed to build (nvcc cross-compiles). Objects are cached under ``build/`` keyed by a hash of
 the source, its local includes and the flags, so rebuilding after a one-file edit takes seconds.
 
-    python -m llm_distillery_b200.build [--force] [--verbose] [--jobs N]
+    python -m llm_distillery_b200.build [--force] [--verbose] [--jobs N] [--sanitize]
+
+``--sanitize`` additionally builds ``_C/libb200_host_asan.so`` (the HDF5 store with AddressSanitizer and UBSan) for
+use from an instrumented host program or with ``LD_PRELOAD`` of the sanitizer runtime.
 """
 from __future__ import annotations
 
@@ -103,7 +106,7 @@ def host_sources() -> list[Path]:
     return sorted(p for p in CSRC.rglob("*.cc"))
 
 
-def build(force: bool = False, verbose: bool = False, jobs: int | None = None) -> dict:
+def build(force: bool = False, verbose: bool = False, jobs: int | None = None, sanitize: bool = False) -> dict:
     """Build both native libraries (no-op when up to date). Returns {"kernels": path, "host": path}."""
     jobs = jobs or (os.cpu_count() or 4)
     nvcc = _nvcc()
@@ -115,7 +118,14 @@ def build(force: bool = False, verbose: bool = False, jobs: int | None = None) -
     if ccs:
         _build_lib(ccs, CXX_FLAGS, ["g++"], ["g++", "-shared", "-pthread", "-Wl,--no-undefined"], HOST_LIB, force,
                    verbose, jobs, link_tail=["-lz"])
-    return {"kernels": str(KERNEL_LIB), "host": str(HOST_LIB)}
+    out = {"kernels": str(KERNEL_LIB), "host": str(HOST_LIB)}
+    if sanitize and ccs:
+        san = ["-fsanitize=address,undefined", "-fno-omit-frame-pointer", "-g"]
+        asan_lib = OUT / "libb200_host_asan.so"
+        _build_lib(ccs, CXX_FLAGS + san, ["g++"], ["g++", "-shared", "-pthread"] + san, asan_lib, force, verbose, jobs,
+                   link_tail=["-lz"])
+        out["host_asan"] = str(asan_lib)
+    return out
 
 
 def main(argv=None) -> int:
@@ -123,8 +133,9 @@ def main(argv=None) -> int:
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
     ap.add_argument("--jobs", type=int, default=None)
+    ap.add_argument("--sanitize", action="store_true")
     a = ap.parse_args(argv)
-    out = build(a.force, a.verbose, a.jobs)
+    out = build(a.force, a.verbose, a.jobs, a.sanitize)
     print(out)
     return 0
 
