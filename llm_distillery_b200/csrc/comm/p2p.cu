@@ -9,23 +9,11 @@
 //                      apply AdamW to the local fp32 master / moments, and store the new bf16 weights into every
 //                      rank's weight buffer (all-gather by peer stores) - one pass, no staging buffers
 //   reduce_scatter_f32 / allgather_16 / allreduce_f32   stand-alone pieces for the other optimizers and for tests
-#include "../common/ptx.cuh"
+#include "peer.cuh"
 #include "../common/host.cuh"
 
 namespace b200 {
 namespace comm {
-
-constexpr int MAX_RANKS = 16;
-struct Peers { void* p[MAX_RANKS]; };
-
-__device__ __forceinline__ void st_release_sys(unsigned int* addr, unsigned int v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
-}
-__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* addr) {
-  unsigned int v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
-  return v;
-}
 
 // sig[r] points at rank r's flag array (MAX_RANKS words). Thread t tells rank t "rank `rank` reached `epoch`" and
 // waits until rank t has told us the same. Epochs only grow, so a late reader never sees a stale match.

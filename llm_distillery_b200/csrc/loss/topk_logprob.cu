@@ -45,8 +45,13 @@ __device__ void bitonic_desc(unsigned long long* s, int n) {
   }
 }
 
+// Vocabulary-shard mode (out_raw != null): the row is one rank's slice of the vocabulary; the kernel writes the raw
+// fp32 logits of the slice's top K, their GLOBAL ids (index + id_offset) and the slice's log-sum-exp, which
+// topk_combine_kernel turns into the exact top-K log-probs of the whole vocabulary.
 __global__ void __launch_bounds__(NT) topk_logprob_kernel(const float* __restrict__ logits, long long ld, int V, int K,
-                                                         __half* __restrict__ out_logp, int* __restrict__ out_idx) {
+                                                         __half* __restrict__ out_logp, int* __restrict__ out_idx,
+                                                         float* __restrict__ out_raw, float* __restrict__ out_lse,
+                                                         int id_offset) {
   __shared__ unsigned long long sel[MAX_K];
   __shared__ unsigned int hist[256];
   __shared__ unsigned int ties[TIE_CAP];
@@ -151,7 +156,50 @@ __global__ void __launch_bounds__(NT) topk_logprob_kernel(const float* __restric
   const float lse = s_lse;
   for (int i = tid; i < K; i += NT) {
     const unsigned long long e = sel[i];
-    out_logp[row * K + i] = __float2half(kfloat((uint32_t)(e >> 32)) - lse);
+    const float z = kfloat((uint32_t)(e >> 32));
+    if (out_raw) out_raw[row * K + i] = z;
+    else out_logp[row * K + i] = __float2half(z - lse);
+    out_idx[row * K + i] = (int)(0xffffffffu - (uint32_t)(e & 0xffffffffu)) + id_offset;
+  }
+  if (out_lse && tid == 0) out_lse[row] = lse;
+}
+
+// Per row: `parts` vocabulary shards each delivered K (raw logit, global id) candidates and the shard's log-sum-exp
+// (layout [parts][rows][K] and [parts][rows], part stride given in elements). Output: the K best of the parts*K
+// candidates as fp16 log-probs under the whole-vocabulary log-sum-exp, ids int32; ties by lower id.
+__global__ void __launch_bounds__(NT) topk_combine_kernel(const float* __restrict__ z, const int* __restrict__ ids,
+                                                         const float* __restrict__ lse, long long zk_stride,
+                                                         long long lse_stride, int parts, int K,
+                                                         __half* __restrict__ out_logp, int* __restrict__ out_idx) {
+  extern __shared__ unsigned long long cs[];
+  __shared__ float s_glse;
+  const long long row = blockIdx.x;
+  const int n = parts * K;
+  int n2 = 1;
+  while (n2 < n) n2 <<= 1;
+  if (threadIdx.x == 0) {
+    float m = -INFINITY;
+    for (int q = 0; q < parts; ++q) m = fmaxf(m, lse[q * lse_stride + row]);
+    float t = 0.f;
+    for (int q = 0; q < parts; ++q) t += __expf(lse[q * lse_stride + row] - m);
+    s_glse = m + __logf(t);
+  }
+  for (int i = threadIdx.x; i < n2; i += NT) {
+    unsigned long long e = 0ull;
+    if (i < n) {
+      const int q = i / K, j = i - q * K;
+      const float v = z[q * zk_stride + row * K + j];
+      const int id = ids[q * zk_stride + row * K + j];
+      e = ((unsigned long long)fkey(v) << 32) | (0xffffffffu - (uint32_t)id);
+    }
+    cs[i] = e;
+  }
+  __syncthreads();
+  bitonic_desc(cs, n2);
+  const float g = s_glse;
+  for (int i = threadIdx.x; i < K; i += NT) {
+    const unsigned long long e = cs[i];
+    out_logp[row * K + i] = __float2half(kfloat((uint32_t)(e >> 32)) - g);
     out_idx[row * K + i] = (int)(0xffffffffu - (uint32_t)(e & 0xffffffffu));
   }
 }
@@ -221,7 +269,33 @@ int b200_topk_logprob(const float* logits, long long ld, int rows, int V, int K,
                       cudaStream_t st) {
   if (!logits || !out_logp || !out_idx || rows <= 0 || V <= 0 || K <= 0 || K > topk::MAX_K || K > V)
     return K > topk::MAX_K ? B200_ERR_TOO_BIG : B200_ERR_ARG;
-  topk::topk_logprob_kernel<<<rows, topk::NT, 0, st>>>(logits, ld, V, K, (__half*)out_logp, out_idx);
+  topk::topk_logprob_kernel<<<rows, topk::NT, 0, st>>>(logits, ld, V, K, (__half*)out_logp, out_idx, nullptr, nullptr, 0);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200_OK;
+}
+
+// One vocabulary shard of a vocabulary-parallel LM head: raw top-K logits fp32 [rows, K], global ids, shard lse [rows].
+int b200_topk_partial(const float* logits, long long ld, int rows, int V, int K, int id_offset, float* out_raw,
+                      int* out_idx, float* out_lse, cudaStream_t st) {
+  if (!logits || !out_raw || !out_idx || !out_lse || rows <= 0 || V <= 0 || K <= 0 || K > topk::MAX_K || K > V)
+    return K > topk::MAX_K ? B200_ERR_TOO_BIG : B200_ERR_ARG;
+  topk::topk_logprob_kernel<<<rows, topk::NT, 0, st>>>(logits, ld, V, K, nullptr, out_idx, out_raw, out_lse, id_offset);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200_OK;
+}
+
+// Merge of `parts` shard results (see topk_combine_kernel). zk_stride / lse_stride: elements between parts.
+int b200_topk_combine(const float* z, const int* ids, const float* lse, long long zk_stride, long long lse_stride,
+                      int parts, int rows, int K, void* out_logp, int* out_idx, cudaStream_t st) {
+  if (!z || !ids || !lse || !out_logp || !out_idx || parts <= 0 || rows <= 0 || K <= 0) return B200_ERR_ARG;
+  int n2 = 1;
+  while (n2 < parts * K) n2 <<= 1;
+  const int smem = n2 * 8;
+  if (smem > 200 * 1024) return B200_ERR_TOO_BIG;
+  if (smem > 48 * 1024)
+    B200_CUDA_CHECK(cudaFuncSetAttribute(topk::topk_combine_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  topk::topk_combine_kernel<<<rows, topk::NT, smem, st>>>(z, ids, lse, zk_stride, lse_stride, parts, K,
+                                                         (__half*)out_logp, out_idx);
   B200_CUDA_CHECK(cudaGetLastError());
   return B200_OK;
 }

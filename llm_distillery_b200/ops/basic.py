@@ -101,16 +101,23 @@ def linear_wgrad(dy: torch.Tensor, x: torch.Tensor, out: torch.Tensor | None = N
 
 
 # ------------------------------------------------------------------------------------------------ RMSNorm
-def rmsnorm_fwd(x: torch.Tensor, w: torch.Tensor, eps: float, residual: torch.Tensor | None = None):
-    """Returns (y, h, rstd): h = x + residual (or x itself), y = h * rsqrt(mean(h^2) + eps) * w."""
+def rmsnorm_fwd(x: torch.Tensor, w: torch.Tensor, eps: float, residual: torch.Tensor | None = None,
+                out: torch.Tensor | None = None):
+    """Returns (y, h, rstd): h = x + residual (or x itself), y = h * rsqrt(mean(h^2) + eps) * w.
+    ``out`` (contiguous, same shape and dtype as x) receives y when given."""
     rows, hdim = x.shape
     if not _native(x):
         h = x if residual is None else (x.float() + residual.float()).to(x.dtype)
         hf = h.float()
         rstd = torch.rsqrt(hf.pow(2).mean(-1) + eps)
         y = (hf * rstd[:, None] * w.float()).to(x.dtype)
+        if out is not None:
+            out.copy_(y)
+            y = out
         return y, h, rstd
-    y = torch.empty_like(x)
+    if out is not None and (out.shape != x.shape or out.dtype != x.dtype or not out.is_contiguous()):
+        raise ValueError("rmsnorm_fwd: out must be contiguous with x's shape and dtype")
+    y = out if out is not None else torch.empty_like(x)
     h = torch.empty_like(x) if residual is not None else x
     rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
     rc = _lib.kernels().b200_rmsnorm_fwd(_lib.ptr(x), _lib.ptr(residual), _lib.ptr(w), _lib.ptr(y),

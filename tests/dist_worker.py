@@ -3,6 +3,9 @@
               concatenated micro-batches
   gpu_p2p     NCCL + NVLink P2P ranks: P2P all-reduce equals NCCL all-reduce; a P2P-communicated training run equals
               the NCCL-communicated one
+  cpu_tp      gloo ranks on CPU: the tensor-parallel teacher's top-K log-probs equal the unsharded model's
+  gpu_tp      NVLink ranks: fused all-gather->GEMM and GEMM->reduce-scatter equal NCCL + matmul; the tensor-parallel
+              teacher's top-K log-probs equal the single-GPU model's
 Prints "WORKER_OK" on rank 0 when every check passed."""
 import os
 import sys
@@ -92,5 +95,98 @@ def gpu_p2p():
     dist.destroy_process_group()
 
 
+def _tp_model_check(dev, dtype, rank, world, k, atol):
+    from llm_distillery_b200.ops import topk as topk_ops
+    from llm_distillery_b200.parallel.tp import TPGroup, TPLlama, padded_seq_len
+    cfg = LlamaConfig(vocab_size=1000, hidden_size=256, intermediate_size=512, num_hidden_layers=2,
+                      num_attention_heads=4, num_key_value_heads=2 if world <= 2 else 4, max_position_embeddings=1024)
+    if world > 2:
+        cfg.num_attention_heads = 2 * world
+        cfg.num_key_value_heads = world
+        cfg.hidden_size = 64 * cfg.num_attention_heads
+    full = build_model(cfg, dtype=dtype, device=dev, seed=11)
+    B = 2
+    L = padded_seq_len(B, 100, world)
+    g = torch.Generator().manual_seed(3)
+    ids = torch.randint(0, cfg.vocab_size, (B, L), generator=g)
+    vocab = 990          # cropped vocabulary that does not divide evenly
+    grp = TPGroup(dev, B * L, cfg.hidden_size, topk=k, dtype=dtype)
+    tpm = TPLlama.from_full(full, grp, vocab=vocab)
+    for _ in range(2):   # twice: buffers and epochs are reused
+        lp, ix = tpm.topk_logprobs(ids, k)
+    with torch.no_grad():
+        hs = full.hidden_states(ids.to(dev))
+        logits = hs.float() @ full.lm_head[:vocab].float().t()
+    ref_lp, ref_ix = topk_ops.topk_logprob(logits.contiguous(), vocab, k)
+    if dev != "cpu":
+        torch.cuda.synchronize()
+        from llm_distillery_b200.ops import _lib
+        assert _lib.take_device_error() == 0
+    # compare as sparse distributions: probability mass per id
+    full_lp = torch.log_softmax(logits[:, :vocab], -1)
+    got = torch.gather(full_lp, 1, ix.long().to(full_lp.device))
+    err = (got - lp.float().to(got.device)).abs().max().item()
+    assert err < atol, ("tp log-probs vs unsharded log-softmax at the returned ids", err)
+    top_ref = ref_lp.float()[:, -1]
+    assert (lp.float()[:, -1].to(top_ref.device) - top_ref).abs().max().item() < atol, "K-th value differs"
+    return err
+
+
+def cpu_tp():
+    dist.init_process_group("gloo")
+    rank, world = dist.get_rank(), dist.get_world_size()
+    _tp_model_check("cpu", torch.float32, rank, world, 16, 1e-2)
+    if rank == 0:
+        print("WORKER_OK")
+    dist.destroy_process_group()
+
+
+def gpu_tp():
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    rank, world = dist.get_rank(), dist.get_world_size()
+    from llm_distillery_b200.ops import _lib
+    from llm_distillery_b200.parallel.tp import TPGroup
+    T, h, n_col, k_row = 512 * world, 512, 768, 640
+    grp = TPGroup(dev, T, h)
+    Ts = T // world
+    gen = torch.Generator(device=dev).manual_seed(100 + rank)
+    for it in range(3):
+        x_shard = torch.randn((Ts, h), device=dev, generator=gen).to(torch.bfloat16)
+        w_col = (torch.randn((n_col, h), device=dev, generator=gen) * 0.05).to(torch.bfloat16)
+        grp.slab(T, h).copy_(x_shard)
+        y = grp.ag_gemm(w_col, T)
+        parts = [torch.empty_like(x_shard) for _ in range(world)]
+        dist.all_gather(parts, x_shard)
+        ref = (torch.cat(parts).float() @ w_col.float().t())
+        torch.cuda.synchronize()
+        assert _lib.take_device_error() == 0
+        err = (y.float() - ref).abs().max().item()
+        assert err < 0.06, ("ag_gemm", it, err)
+        grp.slab(T, h).copy_(x_shard)
+        y32 = grp.ag_gemm(w_col, T, out_f32=True)
+        assert (y32 - ref).abs().max().item() < 2e-3, "ag_gemm fp32 output"
+        xa = torch.randn((T, k_row), device=dev, generator=gen).to(torch.bfloat16)
+        w_row = (torch.randn((h, k_row), device=dev, generator=gen) * 0.05).to(torch.bfloat16)
+        res = torch.randn((Ts, h), device=dev, generator=gen).to(torch.bfloat16)
+        out = grp.gemm_rs(xa, w_row, residual=res)
+        # every rank's partial is rounded to bf16 before the sum, like the kernel's staging
+        part = (xa.float() @ w_row.float().t()).to(torch.bfloat16).float()
+        dist.all_reduce(part)
+        ref2 = part[rank * Ts:(rank + 1) * Ts] + res.float()
+        torch.cuda.synchronize()
+        assert _lib.take_device_error() == 0
+        err2 = (out.float() - ref2).abs().max().item()
+        assert err2 < 0.08, ("gemm_rs", it, err2)
+    del grp
+    _tp_model_check(dev, torch.bfloat16, rank, world, 32, 0.05)
+    if rank == 0:
+        print("WORKER_OK")
+    dist.destroy_process_group()
+
+
 if __name__ == "__main__":
-    {"cpu_engine": cpu_engine, "gpu_p2p": gpu_p2p}[sys.argv[1]]()
+    {"cpu_engine": cpu_engine, "gpu_p2p": gpu_p2p, "cpu_tp": cpu_tp, "gpu_tp": gpu_tp}[sys.argv[1]]()

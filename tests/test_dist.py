@@ -33,3 +33,14 @@ def test_p2p_collectives_and_training_match_nccl():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs at least 2 GPUs")
     _launch("gpu_p2p", min(4, torch.cuda.device_count()), env={"NCCL_NVLS_ENABLE": "0"})
+
+
+def test_cpu_ranks_tensor_parallel_teacher_matches_unsharded():
+    _launch("cpu_tp", 2)
+
+
+@pytest.mark.gpu
+def test_fused_tp_gemms_and_tp_teacher_match_references():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least 2 GPUs")
+    _launch("gpu_tp", min(4, torch.cuda.device_count()), env={"NCCL_NVLS_ENABLE": "0"})
