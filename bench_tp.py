@@ -1,0 +1,211 @@
+#!/usr/bin/env python
+"""Multi-GPU benchmarks of the tensor-parallel path (one rank per GPU, launched by torch.distributed.run):
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \\
+        bench_tp.py gemms   [--tokens 8192] [--model llama-3-70b] [--iters 10]
+        bench_tp.py collect [--model llama-3-70b] [--seq 8192] [--batch 1] [--topk 128] [--steps 3] [--layers N]
+        bench_tp.py p2p     [--iters 10]
+
+gemms    the four linear layers of one decoder block at tensor-parallel width N: fused all-gather->GEMM and
+         GEMM->reduce-scatter kernels against NCCL all_gather / reduce_scatter + torch.matmul (cuBLAS), with the
+         roofline  max(FLOPs / measured bf16 peak, bytes over NVLink / 770 GB/s per direction).
+collect  teacher collection throughput (tokens/s) of the tensor-parallel forward + vocabulary-parallel top-K,
+         random-init weights, synthetic token ids (``--layers`` below the model's depth is a smoke run, flagged in the
+         output and not a benchmark number).
+p2p      peer-to-peer all-reduce (reduce-scatter + all-gather kernels) against NCCL all_reduce, bus bandwidth.
+
+Timing: CUDA events on the launching stream after warm-up, a barrier before each timed call, median per rank, MAX
+over ranks. Inputs of the GEMM cases are far larger than L2. One JSON line per case from rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+from llm_distillery_b200.models.llama import preset  # noqa: E402
+from llm_distillery_b200.ops import _lib  # noqa: E402
+from llm_distillery_b200.parallel.tp import TPGroup, TPLlama, padded_seq_len  # noqa: E402
+
+NVLINK_GBS = 770.0   # measured peer copy bandwidth per direction on this pool
+
+
+def peak_tflops() -> tuple[float, str]:
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        return float(json.load(open(p))["bf16_tflops"]), "measured"
+    return 1590.0, "fallback"
+
+
+def timed_max(fn, iters: int, warmup: int = 3) -> float:
+    """Median ms per call on this rank, then the maximum over ranks."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    ts.sort()
+    t = torch.tensor([ts[len(ts) // 2]], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def emit(rank: int, **kw) -> None:
+    err = _lib.take_device_error()
+    if err:
+        kw["device_error"] = err
+    if rank == 0:
+        print(json.dumps(kw), flush=True)
+
+
+def bench_gemms(args, dev, rank, world) -> None:
+    cfg = preset(args.model)
+    T, h = args.tokens, cfg.hidden_size
+    d, H, Hkv, f = cfg.head_dim, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.intermediate_size
+    Ts = T // world
+    grp = TPGroup(dev, T, h)
+    pk, src = peak_tflops()
+    gen = torch.Generator(device=dev).manual_seed(rank)
+
+    def rnd(*shape):
+        return (torch.randn(shape, device=dev, generator=gen) * 0.05).to(torch.bfloat16)
+
+    link_bytes = T * h * 2 * (world - 1) / world      # what one rank must receive (AG) or send (RS)
+    for name, n_local in (("qkv", (H + 2 * Hkv) * d // world), ("gate_up", 2 * f // world)):
+        w = rnd(n_local, h)
+        x_shard = rnd(Ts, h)
+        full = torch.empty((T, h), dtype=torch.bfloat16, device=dev)
+
+        def fused():
+            grp.slab(T, h).copy_(x_shard)
+            return grp.ag_gemm(w, T)
+
+        def copy_only():
+            grp.slab(T, h).copy_(x_shard)
+
+        def nccl():
+            dist.all_gather_into_tensor(full, x_shard)
+            return full @ w.t()
+
+        ms_f = timed_max(fused, args.iters) - timed_max(copy_only, args.iters)
+        ms_n = timed_max(nccl, args.iters)
+        flops = 2.0 * T * n_local * h
+        ideal = max(flops / (pk * 1e9), link_bytes / (NVLINK_GBS * 1e6))
+        emit(rank, case=f"ag_gemm {name}", tp=world, shape=[T, n_local, h], ms_fused=round(ms_f, 4), ms_nccl_cublas=round(ms_n, 4),
+             speedup=round(ms_n / ms_f, 3), tflops=round(flops / ms_f / 1e9, 1), roofline_ms=round(ideal, 4),
+             frac_of_roofline=round(ideal / ms_f, 3), roofline=f"max(FLOPs/{pk} TF/s of {src}, bytes/{NVLINK_GBS} GB/s)")
+    for name, k_local in (("o_proj", H * d // world), ("down", f // world)):
+        w = rnd(h, k_local)
+        x = rnd(T, k_local)
+        res = rnd(Ts, h)
+        out = torch.empty((Ts, h), dtype=torch.bfloat16, device=dev)
+
+        def fused():
+            return grp.gemm_rs(x, w, residual=res)
+
+        def nccl():
+            y = x @ w.t()
+            dist.reduce_scatter_tensor(out, y)
+            return out.add_(res)
+
+        ms_f = timed_max(fused, args.iters)
+        ms_n = timed_max(nccl, args.iters)
+        flops = 2.0 * T * h * k_local
+        ideal = max(flops / (pk * 1e9), link_bytes / (NVLINK_GBS * 1e6))
+        emit(rank, case=f"gemm_rs {name}", tp=world, shape=[T, h, k_local], ms_fused=round(ms_f, 4), ms_nccl_cublas=round(ms_n, 4),
+             speedup=round(ms_n / ms_f, 3), tflops=round(flops / ms_f / 1e9, 1), roofline_ms=round(ideal, 4),
+             frac_of_roofline=round(ideal / ms_f, 3), roofline=f"max(FLOPs/{pk} TF/s of {src}, bytes/{NVLINK_GBS} GB/s)")
+
+
+def bench_collect(args, dev, rank, world) -> None:
+    over = {"num_hidden_layers": args.layers} if args.layers else {}
+    cfg = preset(args.model, **over)
+    full_depth = preset(args.model).num_hidden_layers
+    B = args.batch
+    L = padded_seq_len(B, args.seq, world)
+    grp = TPGroup(dev, B * L, cfg.hidden_size, topk=args.topk)
+    model = TPLlama.random_init(cfg, grp, seed=0)
+    g = torch.Generator().manual_seed(1)
+    ids = torch.randint(0, cfg.vocab_size, (B, L), generator=g)
+    pin = ids.pin_memory()
+    host_lp = torch.empty((B * L, args.topk), dtype=torch.float16).pin_memory()
+    host_ix = torch.empty((B * L, args.topk), dtype=torch.int32).pin_memory()
+
+    def step():
+        dev_ids = pin.to(dev, non_blocking=True)
+        lp, ix = model.topk_logprobs(dev_ids, args.topk)
+        if rank == 0:   # the writer rank takes the rows to pinned host memory, as the collector does
+            host_lp.copy_(lp, non_blocking=True)
+            host_ix.copy_(ix, non_blocking=True)
+
+    n0 = _lib.LAUNCH_COUNT[0]
+    ms = timed_max(step, args.steps, warmup=max(1, args.warmup))
+    launches = (_lib.LAUNCH_COUNT[0] - n0) // (args.steps + max(1, args.warmup))
+    toks = B * L
+    emit(rank, metric="teacher collect tokens/s", value=round(toks / ms * 1e3, 1), unit="tokens/s", n_gpus=world,
+         ms_per_step=round(ms, 3), dtype="bf16", data="synthetic token ids, random-init weights",
+         config={"model": args.model, "layers": cfg.num_hidden_layers, "parallelism": f"tp{world}", "batch": B,
+                 "seq_len": L, "topk": args.topk},
+         smoke_only=bool(cfg.num_hidden_layers != full_depth), gpu_launches_per_step=int(launches),
+         fwd_tflops_per_gpu=round(cfg.flops_per_token_fwd(L) * toks / ms / 1e9 / world, 1))
+
+
+def bench_p2p(args, dev, rank, world) -> None:
+    from llm_distillery_b200.parallel.p2p import P2PComm, SymmetricBuffer
+    comm = P2PComm(dev)
+    for mib in (1, 16, 128, 1024):
+        n = mib * (1 << 20) // 4
+        buf = SymmetricBuffer(n, torch.float32, dev)
+        ref = torch.zeros(n, dtype=torch.float32, device=dev)
+        ms_p = timed_max(lambda: comm.allreduce_(buf, 1.0 / world), args.iters)
+        ms_n = timed_max(lambda: dist.all_reduce(ref), args.iters)
+        bus = lambda ms: 2.0 * (world - 1) / world * n * 4 / ms / 1e6
+        emit(rank, case="allreduce fp32", mib=mib, tp=world, ms_p2p=round(ms_p, 4), ms_nccl=round(ms_n, 4),
+             busbw_p2p_gbs=round(bus(ms_p), 1), busbw_nccl_gbs=round(bus(ms_n), 1))
+        del buf
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
+    ap.add_argument("cmd", choices=["gemms", "collect", "p2p"])
+    ap.add_argument("--model", default="llama-3-70b")
+    ap.add_argument("--tokens", type=int, default=8192)
+    ap.add_argument("--seq", type=int, default=8192)
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--topk", type=int, default=128)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=2)
+    ap.add_argument("--layers", type=int, default=0)
+    ap.add_argument("--iters", type=int, default=10)
+    args = ap.parse_args()
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29511")
+    os.environ.setdefault("RANK", "0")
+    os.environ.setdefault("WORLD_SIZE", "1")
+    dist.init_process_group("nccl", device_id=dev)
+    rank, world = dist.get_rank(), dist.get_world_size()
+    {"gemms": bench_gemms, "collect": bench_collect, "p2p": bench_p2p}[args.cmd](args, dev, rank, world)
+    torch.cuda.synchronize()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

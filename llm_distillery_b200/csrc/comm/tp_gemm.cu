@@ -78,18 +78,20 @@ __device__ __forceinline__ void acc_bf16x8(float (&a)[8], const uint4& q) {
   }
 }
 
-// Store the 128 x 256 accumulator tile as bf16 rows at `dst_row` (row stride ld elements), columns n0...
-__device__ __forceinline__ void store_tile_bf16(uint32_t taddr, __nv_bfloat16* dst_row, bool row_ok, int n0, int N) {
+// Store this warp's 32 x 256 slice of the accumulator tile as bf16. The slice goes through a per-warp shared-memory
+// stage (32 rows x 256 B, 16-byte chunks XOR-swizzled by row) so that every global store instruction writes two
+// whole 256-byte row segments: stores that cross NVLink then travel as full sectors instead of 16-byte fragments.
+// dst points at the slice's first row (row stride ld elements); rows_valid of its 32 rows exist; N % 8 == 0.
+constexpr int EPI_STAGE_BYTES = 32 * 256;
+__device__ __forceinline__ void store_tile_bf16(uint32_t taddr, uint8_t* stage, __nv_bfloat16* dst, long long ld,
+                                                int rows_valid, int n0, int N, int lane) {
 #pragma unroll 1
-  for (int c = 0; c < TBN / 32; ++c) {
-    uint32_t r[32];
-    __syncwarp();
-    tmem_ld_32x32b_x32(taddr + c * 32, r);
-    tmem_ld_wait();
-    const int col0 = n0 + c * 32;
-    if (!row_ok || col0 >= N) continue;
-    __nv_bfloat16* cp = dst_row + col0;
-    if (col0 + 32 <= N) {
+  for (int half = 0; half < TBN / 128; ++half) {
+#pragma unroll 1
+    for (int c4 = 0; c4 < 4; ++c4) {
+      uint32_t r[32];
+      tmem_ld_32x32b_x32(taddr + half * 128 + c4 * 32, r);
+      tmem_ld_wait();
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         uint4 o;
@@ -97,11 +99,20 @@ __device__ __forceinline__ void store_tile_bf16(uint32_t taddr, __nv_bfloat16* d
         o.y = pack_bf16x2(__uint_as_float(r[j * 8 + 2]), __uint_as_float(r[j * 8 + 3]));
         o.z = pack_bf16x2(__uint_as_float(r[j * 8 + 4]), __uint_as_float(r[j * 8 + 5]));
         o.w = pack_bf16x2(__uint_as_float(r[j * 8 + 6]), __uint_as_float(r[j * 8 + 7]));
-        *reinterpret_cast<uint4*>(cp + j * 8) = o;
+        const int chunk = c4 * 4 + j;
+        *reinterpret_cast<uint4*>(stage + lane * 256 + ((chunk ^ (lane & 15)) << 4)) = o;
       }
-    } else {
-      for (int j = 0; j < N - col0; ++j) cp[j] = __float2bfloat16(__uint_as_float(r[j]));
     }
+    __syncwarp();
+    const int chunk = lane & 15;
+    const int col = n0 + half * 128 + chunk * 8;
+#pragma unroll 4
+    for (int j = 0; j < 16; ++j) {
+      const int row = 2 * j + (lane >> 4);
+      const uint4 v = *reinterpret_cast<const uint4*>(stage + row * 256 + ((chunk ^ (row & 15)) << 4));
+      if (row < rows_valid && col < N) *reinterpret_cast<uint4*>(dst + (long long)row * ld + col) = v;
+    }
+    __syncwarp();
   }
 }
 
@@ -138,6 +149,7 @@ __global__ void __launch_bounds__(MODE == MODE_AG ? AG_THREADS : RS_THREADS, 1)
   uint64_t* tempty_bar = tfull_bar + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint8_t* epi_smem = smem + S::RING_BYTES + S::BAR_BYTES;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -257,17 +269,21 @@ __global__ void __launch_bounds__(MODE == MODE_AG ? AG_THREADS : RS_THREADS, 1)
       }
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + acc * TBN + (static_cast<uint32_t>(quad * 32) << 16);
-      const int row = m_blk * BM + quad * 32 + lane;
+      const int row0 = m_blk * BM + quad * 32;  // first row of this warp's slice
+      const int rows_valid = min(32, M - row0);
+      uint8_t* stage = epi_smem + (warp - 2) * EPI_STAGE_BYTES;
       if (MODE == MODE_AG) {
         if (p.out_f32)
-          store_tile_f32(taddr, reinterpret_cast<float*>(p.C) + (long long)row * p.ldc, row < M, n_blk * TBN, N);
+          store_tile_f32(taddr, reinterpret_cast<float*>(p.C) + (long long)(row0 + lane) * p.ldc, lane < rows_valid,
+                         n_blk * TBN, N);
         else
-          store_tile_bf16(taddr, reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc, row < M, n_blk * TBN, N);
+          store_tile_bf16(taddr, stage, reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row0 * p.ldc, p.ldc,
+                          rows_valid, n_blk * TBN, N, lane);
       } else {
         const int owner = m_blk / bps;
         __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(p.stg.p[owner]);
-        const long long lrow = (long long)p.rank * Ts + (row - (long long)owner * Ts);
-        store_tile_bf16(taddr, base + lrow * N, row < M, n_blk * TBN, N);
+        const long long lrow0 = (long long)p.rank * Ts + (row0 - (long long)owner * Ts);
+        store_tile_bf16(taddr, stage, base + lrow0 * N, N, rows_valid, n_blk * TBN, N, lane);
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -296,16 +312,39 @@ __global__ void __launch_bounds__(MODE == MODE_AG ? AG_THREADS : RS_THREADS, 1)
         const uint4* rs = reinterpret_cast<const uint4*>(p.resid);
         uint4* out = reinterpret_cast<uint4*>(p.out);
         const long long step = (long long)gridDim.x * (NUM_EPI_WARPS * 32);
-        for (long long i = (long long)blockIdx.x * (NUM_EPI_WARPS * 32) + (warp - 2) * 32 + lane; i < nvec; i += step) {
-          float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-          if (rs) acc_bf16x8(a, rs[i]);
-          for (int q = 0; q < p.world; ++q) acc_bf16x8(a, ld_cg_v4(st + q * nvec + i));
-          uint4 o;
-          o.x = pack_bf16x2(a[0], a[1]);
-          o.y = pack_bf16x2(a[2], a[3]);
-          o.z = pack_bf16x2(a[4], a[5]);
-          o.w = pack_bf16x2(a[6], a[7]);
-          out[i] = o;
+        constexpr int U = 4;  // independent 16-byte streams per thread: enough loads in flight to fill HBM
+        for (long long i0 = (long long)blockIdx.x * (NUM_EPI_WARPS * 32) + (warp - 2) * 32 + lane; i0 < nvec;
+             i0 += U * step) {
+          float a[U][8];
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) a[u][e] = 0.f;
+            const long long i = i0 + u * step;
+            if (rs && i < nvec) acc_bf16x8(a[u], ld_cg_v4(rs + i));
+          }
+          for (int q = 0; q < p.world; ++q) {
+            uint4 v[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+              const long long i = i0 + u * step;
+              v[u] = i < nvec ? ld_cg_v4(st + q * nvec + i) : make_uint4(0u, 0u, 0u, 0u);
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) acc_bf16x8(a[u], v[u]);
+          }
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            const long long i = i0 + u * step;
+            if (i < nvec) {
+              uint4 o;
+              o.x = pack_bf16x2(a[u][0], a[u][1]);
+              o.y = pack_bf16x2(a[u][2], a[u][3]);
+              o.z = pack_bf16x2(a[u][4], a[u][5]);
+              o.w = pack_bf16x2(a[u][6], a[u][7]);
+              out[i] = o;
+            }
+          }
         }
       }
     }
@@ -396,7 +435,7 @@ int launch(const void* A, long long lda, const void* W, long long ldw, int T, in
                     gemm::BK, TBN, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != B200_OK) return rc;
   auto kern = tp_gemm_kernel<MODE>;
-  const int smem_bytes = S::bytes(0);
+  const int smem_bytes = S::bytes(gemm::NUM_EPI_WARPS * EPI_STAGE_BYTES);
   static bool attr_set = false;
   if (!attr_set) {
     B200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
@@ -426,7 +465,7 @@ int b200_tp_ag_gemm(const void* const* xf_ptrs, const void* const* flag_ptrs, co
   if (!W || !C || !blk_count || T <= 0 || N <= 0 || K <= 0 || world < 1 || world > comm::MAX_RANKS || rank < 0 ||
       rank >= world)
     return B200_ERR_ARG;
-  if (T % (world * gemm::BM) != 0 || (K & 7) || (!out_f32 && (ldc & 7))) return B200_ERR_ARG;
+  if (T % (world * gemm::BM) != 0 || (K & 7) || (!out_f32 && ((ldc & 7) || (N & 7)))) return B200_ERR_ARG;
   TpParams p{};
   p.rank = rank;
   p.world = world;
