@@ -19,8 +19,9 @@
 // ERR_WAIT_AUX through the error word. A kernel here needs all its CTAs resident at once (they wait on one another
 // through the block counters): the grid never exceeds the SM count and the kernel takes a whole SM per CTA.
 #include "peer.cuh"
-#include "../gemm/gemm_core.cuh"
+#include "../gemm/gemm_pair.cuh"
 #include "../common/host.cuh"
+#include <stdlib.h>
 
 namespace b200 {
 namespace tp {
@@ -133,6 +134,131 @@ __device__ __forceinline__ void store_tile_f32(uint32_t taddr, float* dst_row, b
     } else {
       for (int j = 0; j < min(32, N - col0); ++j) cp[j] = __uint_as_float(r[j]);
     }
+  }
+}
+
+// gemm_rs, after a warp's last tile: publish "this rank's partials have landed" once every epilogue warp of the grid
+// is through, wait for every rank's message, then sum the staged partials (+ residual) of the own shard.
+// ew = epilogue warp index 0..3.
+__device__ __forceinline__ void rs_tail(const TpParams& p, int N, bool ok_all, int ew, int lane,
+                                        volatile int* abort_flag, unsigned int* err_word) {
+  const long long Ts = (long long)p.blocks_per_shard * BM;
+  __threadfence_system();
+  __syncwarp();
+  if (lane == 0) {
+    const unsigned int old = atomicAdd(p.done_count, 1u);
+    if (old + 1u == gridDim.x * NUM_EPI_WARPS) {
+      __threadfence_system();
+      for (int q = 0; q < p.world; ++q)
+        comm::st_release_sys(reinterpret_cast<unsigned int*>(p.flags.p[q]) + p.rank, p.epoch);
+    }
+  }
+  int okw = 1;
+  if (ok_all && lane < p.world)
+    okw = comm::wait_reached_bounded<true>(reinterpret_cast<const unsigned int*>(p.flags.p[p.rank]) + lane, p.epoch,
+                                           abort_flag, err_word, ERR_WAIT_PEER) ? 1 : 0;
+  okw = __all_sync(0xffffffffu, okw);
+  if (!(ok_all && okw)) return;
+  const long long nvec = Ts * N / 8;
+  const uint4* st = reinterpret_cast<const uint4*>(p.stg.p[p.rank]);
+  const uint4* rs = reinterpret_cast<const uint4*>(p.resid);
+  uint4* out = reinterpret_cast<uint4*>(p.out);
+  const long long step = (long long)gridDim.x * (NUM_EPI_WARPS * 32);
+  constexpr int U = 4;  // independent 16-byte streams per thread: enough loads in flight to fill HBM
+  for (long long i0 = (long long)blockIdx.x * (NUM_EPI_WARPS * 32) + ew * 32 + lane; i0 < nvec; i0 += U * step) {
+    float a[U][8];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) a[u][e] = 0.f;
+      const long long i = i0 + u * step;
+      if (rs && i < nvec) acc_bf16x8(a[u], ld_cg_v4(rs + i));
+    }
+    for (int q = 0; q < p.world; ++q) {
+      uint4 v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + u * step;
+        v[u] = i < nvec ? ld_cg_v4(st + q * nvec + i) : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) acc_bf16x8(a[u], v[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * step;
+      if (i < nvec) {
+        uint4 o;
+        o.x = pack_bf16x2(a[u][0], a[u][1]);
+        o.y = pack_bf16x2(a[u][2], a[u][3]);
+        o.z = pack_bf16x2(a[u][4], a[u][5]);
+        o.w = pack_bf16x2(a[u][6], a[u][7]);
+        out[i] = o;
+      }
+    }
+  }
+}
+
+// ag_gemm copy warps (ct = 0..63 inside the CTA): announce the own slab, then pull the other ranks' slabs into the
+// local gathered buffer, one 128-row block at a time, and count each finished block.
+__device__ __forceinline__ void ag_copy_warps(const TpParams& p, int ct, int lane, volatile int* abort_flag,
+                                              unsigned int* err_word) {
+  const int bps = p.blocks_per_shard;
+  if (blockIdx.x == 0 && ct == 0) {
+    // the own slab was written by the kernel before this one on the stream: tell the peers it is ready
+    __threadfence_system();
+    for (int q = 0; q < p.world; ++q)
+      if (q != p.rank) comm::st_release_sys(reinterpret_cast<unsigned int*>(p.flags.p[q]) + p.rank, p.epoch);
+  }
+  const long long blk_vecs = (long long)BM * p.row_bytes / 16;
+  const long long step = (long long)gridDim.x * (COPY_WARPS * 32);
+  uint4* dst_base = reinterpret_cast<uint4*>(p.xf.p[p.rank]);
+  for (int j = 1; j < p.world; ++j) {
+    const int src = (p.rank + j) % p.world;
+    int w = comm::wait_reached_bounded<true>(reinterpret_cast<const unsigned int*>(p.flags.p[p.rank]) + src, p.epoch,
+                                             abort_flag, err_word, ERR_WAIT_PEER) ? 1 : 0;
+    if (!__all_sync(0xffffffffu, w)) break;
+    const uint4* src_base = reinterpret_cast<const uint4*>(p.xf.p[src]);
+    for (int b = 0; b < bps; ++b) {
+      const int m_blk = src * bps + b;
+      const long long off = (long long)m_blk * blk_vecs;
+      long long i = (long long)blockIdx.x * (COPY_WARPS * 32) + ct;
+      for (; i + 3 * step < blk_vecs; i += 4 * step) {
+        const uint4 v0 = ld_peer_v4(src_base + off + i);
+        const uint4 v1 = ld_peer_v4(src_base + off + i + step);
+        const uint4 v2 = ld_peer_v4(src_base + off + i + 2 * step);
+        const uint4 v3 = ld_peer_v4(src_base + off + i + 3 * step);
+        dst_base[off + i] = v0;
+        dst_base[off + i + step] = v1;
+        dst_base[off + i + 2 * step] = v2;
+        dst_base[off + i + 3 * step] = v3;
+      }
+      for (; i < blk_vecs; i += step) dst_base[off + i] = ld_peer_v4(src_base + off + i);
+      fence_proxy_async_all();
+      __threadfence();
+      __syncwarp();
+      if (lane == 0) comm::red_release_gpu_add(p.blk_count + m_blk, 1u);
+    }
+  }
+}
+
+// One warp's share of a finished accumulator tile: rows row0 .. row0+31 of the GEMM, columns n0 .. n0+255.
+template <int MODE>
+__device__ __forceinline__ void epilogue_slice(const TpParams& p, uint32_t taddr, uint8_t* stage, int row0, int n0,
+                                               int M, int N, int lane) {
+  const int rows_valid = min(32, M - row0);
+  if (MODE == MODE_AG) {
+    if (p.out_f32)
+      store_tile_f32(taddr, reinterpret_cast<float*>(p.C) + (long long)(row0 + lane) * p.ldc, lane < rows_valid, n0, N);
+    else
+      store_tile_bf16(taddr, stage, reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row0 * p.ldc, p.ldc, rows_valid,
+                      n0, N, lane);
+  } else {
+    const long long Ts = (long long)p.blocks_per_shard * BM;
+    const int owner = row0 / (int)Ts;
+    __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(p.stg.p[owner]);
+    const long long lrow0 = (long long)p.rank * Ts + (row0 - (long long)owner * Ts);
+    store_tile_bf16(taddr, stage, base + lrow0 * N, N, rows_valid, n0, N, lane);
   }
 }
 
@@ -252,7 +378,6 @@ __global__ void __launch_bounds__(MODE == MODE_AG ? AG_THREADS : RS_THREADS, 1)
   } else if (warp < 2 + NUM_EPI_WARPS) {
     // ------------------------------------------------------------ epilogue warps (2..5)
     const int quad = warp & 3;
-    const long long Ts = (long long)bps * BM;
     uint32_t tl = 0;
     bool ok_all = true;
     for (int tile = blockIdx.x; tile < tm.num_tiles; tile += gridDim.x, ++tl) {
@@ -269,127 +394,16 @@ __global__ void __launch_bounds__(MODE == MODE_AG ? AG_THREADS : RS_THREADS, 1)
       }
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + acc * TBN + (static_cast<uint32_t>(quad * 32) << 16);
-      const int row0 = m_blk * BM + quad * 32;  // first row of this warp's slice
-      const int rows_valid = min(32, M - row0);
-      uint8_t* stage = epi_smem + (warp - 2) * EPI_STAGE_BYTES;
-      if (MODE == MODE_AG) {
-        if (p.out_f32)
-          store_tile_f32(taddr, reinterpret_cast<float*>(p.C) + (long long)(row0 + lane) * p.ldc, lane < rows_valid,
-                         n_blk * TBN, N);
-        else
-          store_tile_bf16(taddr, stage, reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row0 * p.ldc, p.ldc,
-                          rows_valid, n_blk * TBN, N, lane);
-      } else {
-        const int owner = m_blk / bps;
-        __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(p.stg.p[owner]);
-        const long long lrow0 = (long long)p.rank * Ts + (row0 - (long long)owner * Ts);
-        store_tile_bf16(taddr, stage, base + lrow0 * N, N, rows_valid, n_blk * TBN, N, lane);
-      }
+      epilogue_slice<MODE>(p, taddr, epi_smem + (warp - 2) * EPI_STAGE_BYTES, m_blk * BM + quad * 32, n_blk * TBN, M, N,
+                           lane);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[acc]);
     }
-    if (MODE == MODE_RS) {
-      // ---- all partial tiles of this warp are on their way: publish, then reduce the own shard
-      __threadfence_system();
-      __syncwarp();
-      if (lane == 0) {
-        const unsigned int old = atomicAdd(p.done_count, 1u);
-        if (old + 1u == gridDim.x * NUM_EPI_WARPS) {
-          __threadfence_system();
-          for (int q = 0; q < p.world; ++q)
-            comm::st_release_sys(reinterpret_cast<unsigned int*>(p.flags.p[q]) + p.rank, p.epoch);
-        }
-      }
-      int okw = 1;
-      if (ok_all && lane < p.world)
-        okw = comm::wait_reached_bounded<true>(reinterpret_cast<const unsigned int*>(p.flags.p[p.rank]) + lane,
-                                               p.epoch, abort_flag, err_word, ERR_WAIT_PEER) ? 1 : 0;
-      okw = __all_sync(0xffffffffu, okw);
-      if (ok_all && okw) {
-        const long long nvec = Ts * N / 8;
-        const uint4* st = reinterpret_cast<const uint4*>(p.stg.p[p.rank]);
-        const uint4* rs = reinterpret_cast<const uint4*>(p.resid);
-        uint4* out = reinterpret_cast<uint4*>(p.out);
-        const long long step = (long long)gridDim.x * (NUM_EPI_WARPS * 32);
-        constexpr int U = 4;  // independent 16-byte streams per thread: enough loads in flight to fill HBM
-        for (long long i0 = (long long)blockIdx.x * (NUM_EPI_WARPS * 32) + (warp - 2) * 32 + lane; i0 < nvec;
-             i0 += U * step) {
-          float a[U][8];
-#pragma unroll
-          for (int u = 0; u < U; ++u) {
-#pragma unroll
-            for (int e = 0; e < 8; ++e) a[u][e] = 0.f;
-            const long long i = i0 + u * step;
-            if (rs && i < nvec) acc_bf16x8(a[u], ld_cg_v4(rs + i));
-          }
-          for (int q = 0; q < p.world; ++q) {
-            uint4 v[U];
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-              const long long i = i0 + u * step;
-              v[u] = i < nvec ? ld_cg_v4(st + q * nvec + i) : make_uint4(0u, 0u, 0u, 0u);
-            }
-#pragma unroll
-            for (int u = 0; u < U; ++u) acc_bf16x8(a[u], v[u]);
-          }
-#pragma unroll
-          for (int u = 0; u < U; ++u) {
-            const long long i = i0 + u * step;
-            if (i < nvec) {
-              uint4 o;
-              o.x = pack_bf16x2(a[u][0], a[u][1]);
-              o.y = pack_bf16x2(a[u][2], a[u][3]);
-              o.z = pack_bf16x2(a[u][4], a[u][5]);
-              o.w = pack_bf16x2(a[u][6], a[u][7]);
-              out[i] = o;
-            }
-          }
-        }
-      }
-    }
+    if (MODE == MODE_RS) rs_tail(p, N, ok_all, warp - 2, lane, abort_flag, err_word);
   } else {
     // ------------------------------------------------------------ copy warps (ag_gemm only)
-    if (MODE == MODE_AG) {
-      const int ct = threadIdx.x - (2 + NUM_EPI_WARPS) * 32;  // 0..63
-      if (blockIdx.x == 0 && ct == 0) {
-        // the own slab was written by the kernel before this one on the stream: tell the peers it is ready
-        __threadfence_system();
-        for (int q = 0; q < p.world; ++q)
-          if (q != p.rank) comm::st_release_sys(reinterpret_cast<unsigned int*>(p.flags.p[q]) + p.rank, p.epoch);
-      }
-      const long long blk_vecs = (long long)BM * p.row_bytes / 16;
-      const long long step = (long long)gridDim.x * (COPY_WARPS * 32);
-      uint4* dst_base = reinterpret_cast<uint4*>(p.xf.p[p.rank]);
-      bool ok = true;
-      for (int j = 1; ok && j < p.world; ++j) {
-        const int src = (p.rank + j) % p.world;
-        int w = comm::wait_reached_bounded<true>(reinterpret_cast<const unsigned int*>(p.flags.p[p.rank]) + src,
-                                                 p.epoch, abort_flag, err_word, ERR_WAIT_PEER) ? 1 : 0;
-        if (!__all_sync(0xffffffffu, w)) break;
-        const uint4* src_base = reinterpret_cast<const uint4*>(p.xf.p[src]);
-        for (int b = 0; b < bps; ++b) {
-          const int m_blk = src * bps + b;
-          const long long off = (long long)m_blk * blk_vecs;
-          long long i = (long long)blockIdx.x * (COPY_WARPS * 32) + ct;
-          for (; i + 3 * step < blk_vecs; i += 4 * step) {
-            const uint4 v0 = ld_peer_v4(src_base + off + i);
-            const uint4 v1 = ld_peer_v4(src_base + off + i + step);
-            const uint4 v2 = ld_peer_v4(src_base + off + i + 2 * step);
-            const uint4 v3 = ld_peer_v4(src_base + off + i + 3 * step);
-            dst_base[off + i] = v0;
-            dst_base[off + i + step] = v1;
-            dst_base[off + i + 2 * step] = v2;
-            dst_base[off + i + 3 * step] = v3;
-          }
-          for (; i < blk_vecs; i += step) dst_base[off + i] = ld_peer_v4(src_base + off + i);
-          fence_proxy_async_all();
-          __threadfence();
-          __syncwarp();
-          if (lane == 0) comm::red_release_gpu_add(p.blk_count + m_blk, 1u);
-        }
-      }
-    }
+    if (MODE == MODE_AG) ag_copy_warps(p, threadIdx.x - (2 + NUM_EPI_WARPS) * 32, lane, abort_flag, err_word);
   }
 
   __syncwarp();
@@ -402,6 +416,188 @@ __global__ void __launch_bounds__(MODE == MODE_AG ? AG_THREADS : RS_THREADS, 1)
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+
+// ---------------------------------------------------------------------------------------------- CTA-pair variant
+// Same two fused layers on the cta_group::2 mainloop (gemm_pair.cuh): a cluster of two CTAs per 256 x 256 tile, each
+// CTA loading its own 128 rows of A and its own half of B (no multicast), 6 stages. Used when every rank's slab is a
+// whole number of 256-row tiles. Block counters stay per 128 rows: each CTA's producer waits for its own rows.
+constexpr int PSTAGES = 6;
+
+template <int MODE>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(MODE == MODE_AG ? AG_THREADS : RS_THREADS, 1)
+    tp_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, int M, int N,
+                        int K, TpParams p, unsigned int* err_word) {
+  using S = SmemPair<PSTAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + S::RING_BYTES);
+  uint64_t* empty_bar = full_bar + PSTAGES;
+  uint64_t* tfull_bar = empty_bar + PSTAGES;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint8_t* epi_smem = smem + S::RING_BYTES + S::BAR_BYTES;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta = cluster_ctarank();  // 0 = leader
+  constexpr uint32_t TMEM_COLS = 2 * PAIR_BN;
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+    for (int s = 0; s < PSTAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], 2 * NUM_EPI_WARPS);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int m_tiles = (M + PAIR_BM - 1) / PAIR_BM;
+  const int n_tiles = (N + PAIR_BN - 1) / PAIR_BN;
+  const int num_tiles = m_tiles * n_tiles;
+  const int num_kb = (K + BK - 1) / BK;
+  const int pair_id = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+  const int bps2 = p.blocks_per_shard / 2;  // 256-row tiles per slab
+  const int group_m = bps2 < 8 ? bps2 : 8;
+  const int rot = (MODE == MODE_AG ? p.rank : (p.rank + 1) % p.world) * bps2;
+  auto tile_coords = [&](int tile, int& m_blk, int& n_blk) {
+    const int per_group = group_m * n_tiles;
+    const int g = tile / per_group;
+    const int first_m = g * group_m;
+    const int gsz = min(group_m, m_tiles - first_m);
+    const int r = tile - g * per_group;
+    m_blk = (first_m + (r % gsz) + rot) % m_tiles;  // physical tile row: own slab first (ag) or last (rs)
+    n_blk = r / gsz;
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      const unsigned int arrivals = gridDim.x * COPY_WARPS;
+      for (int tile = pair_id; ok && tile < num_tiles; tile += num_pairs) {
+        int m_blk, n_blk;
+        tile_coords(tile, m_blk, n_blk);
+        const int m0 = m_blk * PAIR_BM + (int)cta * BM;
+        const int n0 = n_blk * PAIR_BN + (int)cta * PAIR_HALF_N;
+        if (MODE == MODE_AG && m_blk / bps2 != p.rank) {
+          if (!comm::wait_reached_bounded<false>(p.blk_count + m0 / BM, arrivals, abort_flag, err_word, ERR_WAIT_AUX)) break;
+          fence_proxy_async_all();
+        }
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const uint32_t s = it % PSTAGES;
+          const uint32_t ph = (it / PSTAGES) & 1u;
+          if (!mbar_wait_bounded(&empty_bar[s], ph ^ 1u, abort_flag, err_word, ERR_WAIT_EMPTY)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sA = smem + s * S::STAGE_BYTES;
+          uint8_t* sB = sA + S::A_BYTES;
+          if (cta == 0) mbar_arrive_expect_tx(&full_bar[s], 2 * S::STAGE_BYTES);
+          tma_load_2d_pair(sA, &tmA, &full_bar[s], kb * BK, m0);
+          tma_load_2d_pair(sB, &tmB, &full_bar[s], kb * BK, n0);
+        }
+      }
+      for (uint32_t d = 0; ok && d < (uint32_t)PSTAGES && d < it; ++d) {
+        const uint32_t j = it - 1 - d;
+        if (!mbar_wait_bounded(&empty_bar[j % PSTAGES], (j / PSTAGES) & 1u, abort_flag, err_word, ERR_WAIT_EMPTY)) break;
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (leader only)
+    if (lane == 0 && cta == 0) {
+      const uint32_t idesc = make_idesc_f16(1, PAIR_BM, PAIR_BN, 0, 0);
+      uint32_t it = 0, tl = 0;
+      bool ok = true;
+      for (int tile = pair_id; ok && tile < num_tiles; tile += num_pairs, ++tl) {
+        const uint32_t acc = tl & 1u;
+        const uint32_t aph = (tl >> 1) & 1u;
+        if (!mbar_wait_bounded(&tempty_bar[acc], aph ^ 1u, abort_flag, err_word, ERR_WAIT_TMEM_EMPTY)) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * PAIR_BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const uint32_t s = it % PSTAGES;
+          const uint32_t ph = (it / PSTAGES) & 1u;
+          if (!mbar_wait_bounded(&full_bar[s], ph, abort_flag, err_word, ERR_WAIT_FULL)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t a_base = smem_u32(smem + s * S::STAGE_BYTES);
+          const uint32_t b_base = a_base + S::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t da = make_smem_desc_sw128(a_base + k * (UMMA_K * 2), 16, 1024);
+            const uint64_t db = make_smem_desc_sw128(b_base + k * (UMMA_K * 2), 16, 1024);
+            umma_f16_ss_pair(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit_pair(&empty_bar[s], 0x3);
+        }
+        if (ok) umma_commit_pair(&tfull_bar[acc], 0x3);
+      }
+    }
+  } else if (warp < 2 + NUM_EPI_WARPS) {
+    // ------------------------------------------------------------ epilogue warps (both CTAs)
+    const int quad = warp & 3;
+    const uint32_t leader_tempty0 = mapa_shared(smem_u32(&tempty_bar[0]), 0);
+    uint32_t tl = 0;
+    bool ok_all = true;
+    for (int tile = pair_id; tile < num_tiles; tile += num_pairs, ++tl) {
+      int m_blk, n_blk;
+      tile_coords(tile, m_blk, n_blk);
+      const uint32_t acc = tl & 1u;
+      const uint32_t aph = (tl >> 1) & 1u;
+      int ok = mbar_wait_bounded(&tfull_bar[acc], aph, abort_flag, err_word, ERR_WAIT_TMEM_FULL) ? 1 : 0;
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        ok_all = false;
+        break;
+      }
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + acc * PAIR_BN + (static_cast<uint32_t>(quad * 32) << 16);
+      epilogue_slice<MODE>(p, taddr, epi_smem + (warp - 2) * EPI_STAGE_BYTES,
+                           m_blk * PAIR_BM + (int)cta * BM + quad * 32, n_blk * PAIR_BN, M, N, lane);
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(leader_tempty0 + acc * 8);
+    }
+    if (MODE == MODE_RS) rs_tail(p, N, ok_all, warp - 2, lane, abort_flag, err_word);
+  } else {
+    // ------------------------------------------------------------ copy warps (ag_gemm only)
+    if (MODE == MODE_AG) ag_copy_warps(p, threadIdx.x - (2 + NUM_EPI_WARPS) * 32, lane, abort_flag, err_word);
+  }
+
+  __syncwarp();
+  if (*abort_flag) {
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
   }
 }
 
@@ -423,28 +619,59 @@ int fill_peers(comm::Peers& dst, const void* const* src, int world) {
   return B200_OK;
 }
 
+static int pair_mode() {
+  static int mode = -2;
+  if (mode == -2) {
+    const char* e = getenv("B200_TP_PAIR");
+    mode = e ? atoi(e) : -1;
+  }
+  return mode;
+}
+
 template <int MODE>
 int launch(const void* A, long long lda, const void* W, long long ldw, int T, int N, int K, const TpParams& p,
            cudaStream_t stream) {
-  using S = gemm::Smem<TBN, TSTAGES>;
   CUtensorMap tmA, tmB;
   int rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)K, (uint64_t)T, (uint64_t)lda * 2,
                         gemm::BK, gemm::BM, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != B200_OK) return rc;
-  rc = make_tmap_2d(&tmB, W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)K, (uint64_t)N, (uint64_t)ldw * 2,
-                    gemm::BK, TBN, CU_TENSOR_MAP_SWIZZLE_128B);
-  if (rc != B200_OK) return rc;
-  auto kern = tp_gemm_kernel<MODE>;
-  const int smem_bytes = S::bytes(gemm::NUM_EPI_WARPS * EPI_STAGE_BYTES);
-  static bool attr_set = false;
-  if (!attr_set) {
-    B200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
-    attr_set = true;
+  const int threads = MODE == MODE_AG ? AG_THREADS : RS_THREADS;
+  const int epi_bytes = gemm::NUM_EPI_WARPS * EPI_STAGE_BYTES;
+  // CTA pairs when every slab is whole 256-row tiles and there are enough tiles for all SM pairs
+  const long long ptiles = (long long)(T / gemm::PAIR_BM) * ceil_div(N, gemm::PAIR_BN);
+  const bool pair = pair_mode() != 0 && (p.blocks_per_shard % 2 == 0) && N > 128 &&
+                    (pair_mode() == 1 || ptiles >= sm_count() / 2);
+  if (pair) {
+    using S = gemm::SmemPair<PSTAGES>;
+    rc = make_tmap_2d(&tmB, W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)K, (uint64_t)N, (uint64_t)ldw * 2,
+                      gemm::BK, gemm::PAIR_HALF_N, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != B200_OK) return rc;
+    auto kern = tp_gemm_pair_kernel<MODE>;
+    const int smem_bytes = S::bytes(epi_bytes);
+    static bool attr_set = false;
+    if (!attr_set) {
+      B200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+      attr_set = true;
+    }
+    const int max_pairs = sm_count() / 2;
+    const int pairs = ptiles < max_pairs ? (int)ptiles : max_pairs;
+    kern<<<2 * pairs, threads, smem_bytes, stream>>>(tmA, tmB, T, N, K, p, device_err_word());
+  } else {
+    using S = gemm::Smem<TBN, TSTAGES>;
+    rc = make_tmap_2d(&tmB, W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)K, (uint64_t)N, (uint64_t)ldw * 2,
+                      gemm::BK, TBN, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != B200_OK) return rc;
+    auto kern = tp_gemm_kernel<MODE>;
+    const int smem_bytes = S::bytes(epi_bytes);
+    static bool attr_set = false;
+    if (!attr_set) {
+      B200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+      attr_set = true;
+    }
+    const int tiles = ceil_div(T, gemm::BM) * ceil_div(N, TBN);
+    const int grid = tiles < sm_count() ? tiles : sm_count();
+    kern<<<grid, threads, smem_bytes, stream>>>(tmA, tmB, T, N, K, p, device_err_word());
   }
-  const int tiles = ceil_div(T, gemm::BM) * ceil_div(N, TBN);
-  const int grid = tiles < sm_count() ? tiles : sm_count();
-  kern<<<grid, MODE == MODE_AG ? AG_THREADS : RS_THREADS, smem_bytes, stream>>>(tmA, tmB, T, N, K, p,
-                                                                                 device_err_word());
   B200_CUDA_CHECK(cudaGetLastError());
   return B200_OK;
 }

@@ -44,3 +44,10 @@ def test_fused_tp_gemms_and_tp_teacher_match_references():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs at least 2 GPUs")
     _launch("gpu_tp", min(4, torch.cuda.device_count()), env={"NCCL_NVLS_ENABLE": "0"})
+
+
+@pytest.mark.gpu
+def test_fused_tp_gemms_on_cta_pairs_match_references():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least 2 GPUs")
+    _launch("gpu_tp", min(4, torch.cuda.device_count()), env={"NCCL_NVLS_ENABLE": "0", "B200_TP_PAIR": "1"})
