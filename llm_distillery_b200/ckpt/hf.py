@@ -123,3 +123,65 @@ def load_trainer_state(states_dir: str, model: LlamaModel, optimizer, schedule) 
 def has_trainer_state(states_dir: str) -> bool:
     return os.path.exists(os.path.join(states_dir, "model_state.pt")) and \
         os.path.exists(os.path.join(states_dir, "trainer_state.json"))
+
+
+# ------------------------------------------------------------------------------------------------- tensor-parallel load
+def load_tp_weights(path: str, rank: int, tp: int, vocab: int | None = None, dtype: torch.dtype = torch.bfloat16,
+                    device="cpu") -> tuple[LlamaConfig, dict]:
+    """Read ONE tensor-parallel rank's slices straight out of a HF safetensors checkpoint (no rank ever holds the
+    whole model): q/k/v and gate/up rows, o_proj / down_proj columns, an equal slice of the (cropped) LM head,
+    replicated embedding and norms. Returns (config, weights) in the layout of ``parallel.tp.shard_llama_weights``."""
+    from safetensors import safe_open
+    cfg = LlamaConfig.from_pretrained(path)
+    H, Hkv, d, f = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.intermediate_size
+    if H % tp or Hkv % tp or f % tp:
+        raise ValueError(f"tp={tp} must divide heads ({H}), kv heads ({Hkv}) and the FFN width ({f})")
+    idx = os.path.join(path, "model.safetensors.index.json")
+    if os.path.exists(idx):
+        with open(idx, encoding="utf-8") as fh:
+            where = json.load(fh)["weight_map"]
+    else:
+        files = sorted(x for x in os.listdir(path) if x.endswith(".safetensors"))
+        where = {}
+        for fn in files:
+            with safe_open(os.path.join(path, fn), "pt") as sf:
+                for k in sf.keys():
+                    where[k] = fn
+    handles: dict = {}
+
+    def sl(name: str, rows=None, cols=None) -> torch.Tensor:
+        fn = where[name]
+        if fn not in handles:
+            handles[fn] = safe_open(os.path.join(path, fn), "pt")
+        s = handles[fn].get_slice(name)
+        if rows is not None:
+            t = s[rows[0]:rows[1]]
+        elif cols is not None:
+            t = s[:, cols[0]:cols[1]]
+        else:
+            t = s[:]
+        return t.to(device=device, dtype=dtype)
+
+    Hl, Hkvl, fl = H // tp, Hkv // tp, f // tp
+    w = {"embed_tokens": sl("model.embed_tokens.weight"), "norm": sl("model.norm.weight")}
+    for i in range(cfg.num_hidden_layers):
+        hp, p = f"model.layers.{i}.", f"layers.{i}."
+        w[p + "qkv_proj"] = torch.cat([sl(hp + "self_attn.q_proj.weight", rows=(rank * Hl * d, (rank + 1) * Hl * d)),
+                                       sl(hp + "self_attn.k_proj.weight", rows=(rank * Hkvl * d, (rank + 1) * Hkvl * d)),
+                                       sl(hp + "self_attn.v_proj.weight", rows=(rank * Hkvl * d, (rank + 1) * Hkvl * d))], 0)
+        w[p + "o_proj"] = sl(hp + "self_attn.o_proj.weight", cols=(rank * Hl * d, (rank + 1) * Hl * d)).contiguous()
+        w[p + "gate_up_proj"] = torch.cat([sl(hp + "mlp.gate_proj.weight", rows=(rank * fl, (rank + 1) * fl)),
+                                           sl(hp + "mlp.up_proj.weight", rows=(rank * fl, (rank + 1) * fl))], 0)
+        w[p + "down_proj"] = sl(hp + "mlp.down_proj.weight", cols=(rank * fl, (rank + 1) * fl)).contiguous()
+        w[p + "input_layernorm"] = sl(hp + "input_layernorm.weight")
+        w[p + "post_attention_layernorm"] = sl(hp + "post_attention_layernorm.weight")
+    head_name = "lm_head.weight" if "lm_head.weight" in where else "model.embed_tokens.weight"
+    V = min(vocab or cfg.vocab_size, cfg.vocab_size)
+    Vl = -(-(-(-V // tp)) // 8) * 8
+    lo, hi = min(rank * Vl, V), min((rank + 1) * Vl, V)
+    piece = torch.zeros((Vl, cfg.hidden_size), dtype=dtype, device=device)
+    if hi > lo:
+        piece[: hi - lo] = sl(head_name, rows=(lo, hi))
+    w["lm_head"] = piece
+    w["_vocab"] = (V, Vl, lo, hi - lo)
+    return cfg, w

@@ -196,6 +196,52 @@ def _init_distributed(cfg: DistillConfig):
     return rank, world, make_comm(kind, torch.device(cfg.device), shard_strategy=cfg.shard_strategy)
 
 
+def refresh_stores(rank: int, world: int, *stores) -> None:
+    """Rank 0 is the only writer of the HDF5 files: make its writes visible to the other ranks' handles."""
+    if world == 1:
+        return
+    import torch.distributed as dist
+    if rank == 0:
+        for st in stores:
+            st.wait()
+            st.flush()
+    dist.barrier()
+    if rank != 0:
+        for st in stores:
+            st.reopen()
+    dist.barrier()
+
+
+_TP_GROUPS: dict = {}
+
+
+def _tp_group(cfg, teacher, rank: int, world: int, tp: int):
+    """The tensor-parallel group of this rank (consecutive ranks), with symmetric buffers sized for the teacher's
+    largest batch. Process groups are created once (every rank takes part in every ``new_group`` call)."""
+    import torch
+    import torch.distributed as dist
+    from .models.llama import LlamaConfig
+    from .parallel.tp import TPGroup, padded_seq_len
+    if "pg" not in _TP_GROUPS:
+        if tp == world:
+            _TP_GROUPS["pg"] = dist.group.WORLD
+        else:
+            mine = None
+            for g0 in range(0, world, tp):
+                pg = dist.new_group(list(range(g0, g0 + tp)))
+                if g0 <= rank < g0 + tp:
+                    mine = pg
+            _TP_GROUPS["pg"] = mine
+    mcfg = LlamaConfig.from_pretrained(teacher.model_path)
+    B = max(1, teacher.batch_size)
+    tokens = B * padded_seq_len(B, cfg.context_len, tp)
+    key = (mcfg.hidden_size, tokens, int(teacher.topK))
+    if key not in _TP_GROUPS:
+        _TP_GROUPS[key] = TPGroup(torch.device(cfg.device), tokens, mcfg.hidden_size, topk=int(teacher.topK),
+                                  group=_TP_GROUPS["pg"], dtype=torch.float32)
+    return _TP_GROUPS[key]
+
+
 def collect(teachers, cfg, store, ids, validation, rank, world, student=None) -> None:
     """Every teacher in turn collects ``ids`` into ``store`` (teachers after the first merge into the same
     conversations). With several ranks each rank collects a strided share into its own shard file and rank 0
@@ -206,11 +252,16 @@ def collect(teachers, cfg, store, ids, validation, rank, world, student=None) ->
     shas = None
     if student is not None:
         shas = {c.origin_convo_id: c.content_sha for c in (student.validation_dataset if validation else student.dataset)}
+    tp = max(1, min(int(cfg.tp_size), world))
+    if world % tp:
+        raise ValueError(f"tp_size={tp} must divide the number of ranks ({world})")
+    dp_rank, dp_world = rank // tp, world // tp
     if world > 1:
         target = H5Store(store.file_path.replace(".hdf5", f".rank{rank}.hdf5"))
     for t in progress(teachers, desc="Teachers", leave=False, disable=len(teachers) == 1):
+        tp_group = _tp_group(cfg, t, rank, world, tp) if tp > 1 else None
         t.process_chunk(cfg.reserve_vram, cfg.num_inference_workers, ids_to_collect=ids, data_manager=target,
-                        validation=validation, rank=rank, world=world, sha_by_id=shas)
+                        validation=validation, rank=dp_rank, world=dp_world, sha_by_id=shas, tp_group=tp_group)
         t.unload()
     if world > 1:
         import torch.distributed as dist
@@ -288,6 +339,7 @@ def main(argv=None, default_config_path: str | None = None) -> dict:
             for t in teachers:
                 t.topK = k
             collect(teachers, cfg, data_manager, ids_collect, False, rank, world, student)
+            refresh_stores(rank, world, data_manager, validation_data_manager)
             student.train_chunk(data_manager, validation_data_manager, full_collect)
         else:
             print(f"WARNING: The calculated size of the h5 dataset is too large for the specified cache size "
@@ -306,9 +358,11 @@ def main(argv=None, default_config_path: str | None = None) -> dict:
                         data_manager.set_topk(cfg.save_topK)
                         data_manager.set_vocab_family(student.vocab_family)
                     collect(teachers, cfg, data_manager, chunk_ids, False, rank, world, student)
+                    refresh_stores(rank, world, data_manager, validation_data_manager)
                     student.train_chunk(data_manager, validation_data_manager, full_collect)
     else:
         print("Using data on disk for training...")
+        refresh_stores(rank, world, data_manager, validation_data_manager)
         student.train_chunk(data_manager, validation_data_manager, True)
 
     print("Done!")

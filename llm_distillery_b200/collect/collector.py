@@ -118,3 +118,55 @@ class TeacherCollector:
             s = (aligner.student_val_convos if validation else aligner.student_convos)[c.origin_convo_id]
             out.append(TeacherRows(c.origin_convo_id, vals, idx, s.content_sha, s.sample))
         return out
+
+
+class TPTeacherCollector(TeacherCollector):
+    """Collector over a tensor-parallel teacher (``parallel.tp.TPLlama``): every rank of the group calls
+    ``content_logprobs`` with the same batch; the vocabulary-parallel head returns the exact top-K of the whole
+    vocabulary on every rank and only the group's first rank copies the content rows to the host."""
+
+    def __init__(self, tp_model, *, topk: int, crop_to_size: int, enable_topk: bool = True):
+        if not enable_topk:
+            raise NotImplementedError("full-distribution storage is not offered with a tensor-parallel teacher: "
+                                      "use top-K storage (enable_topK) or tp_size = 1")
+        self.model = tp_model
+        self.K = int(topk)
+        self.vocab = tp_model.V
+        self.enable_topk = True
+        self.device = tp_model.device
+        self.is_writer = tp_model.g.rank == 0
+
+    @torch.no_grad()
+    def content_logprobs(self, tokens: np.ndarray, convos: list[ConvoTokenized], positions=None):
+        from ..parallel.tp import padded_seq_len
+        B, L = tokens.shape
+        Lp = padded_seq_len(B, L, self.model.g.world)
+        padded = np.zeros((B, Lp), dtype=np.int64)      # causal attention: trailing padding cannot reach real rows
+        padded[:, :L] = tokens
+        ids = torch.from_numpy(padded).to(self.device, non_blocking=True)
+        lp, ix = self.model.topk_logprobs(ids, self.K)
+        rows, counts = [], []
+        for b, c in enumerate(convos):
+            ci = c.content_indices() if positions is None else np.asarray(positions[b], dtype=np.int64)
+            ci = ci[ci < min(c.length, L)]
+            rows.append(ci + b * Lp)
+            counts.append(len(ci))
+        rows_np = np.concatenate(rows) if rows else np.zeros(0, dtype=np.int64)
+        if len(rows_np) == 0 or not self.is_writer:
+            return None, None, counts
+        rows_t = torch.from_numpy(rows_np).to(self.device, non_blocking=True)
+        out_v, out_i = lp[rows_t], ix[rows_t]
+        pin = self.device.type == "cuda"
+        hv = torch.empty(out_v.shape, dtype=out_v.dtype, pin_memory=pin)
+        hi = torch.empty(out_i.shape, dtype=out_i.dtype, pin_memory=pin)
+        hv.copy_(out_v, non_blocking=True)
+        hi.copy_(out_i, non_blocking=True)
+        if pin:
+            torch.cuda.current_stream().synchronize()
+        return hv, hi, counts
+
+    def collect_batch(self, tokens, convos, aligner=None, validation: bool = False):
+        if self.is_writer:
+            return super().collect_batch(tokens, convos, aligner=aligner, validation=validation)
+        self.content_logprobs(tokens, convos)     # take part in the forward; the rows stay on the writer rank
+        return []

@@ -434,6 +434,16 @@ class H5Store:
         if self.lib.h5s_count(self.h) == 0 and self.file_bytes() > min_bytes:
             self.repack()
 
+    def reopen(self) -> None:
+        """Drop this handle's view of the file and read it again (another process has written to it)."""
+        self.stop_prefetch()
+        self.wait()
+        self.lib.h5s_close(self.h)
+        err = ctypes.create_string_buffer(512)
+        self.h = self.lib.h5s_open(self.file_path.encode(), 1, err, 512)
+        if not self.h:
+            raise IOError(f"cannot reopen {self.file_path}: {err.value.decode()}")
+
     def close(self) -> None:
         if self.closed:
             return

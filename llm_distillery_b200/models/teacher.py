@@ -60,6 +60,18 @@ class TeacherModel(BaseModel):
                 p.requires_grad_(False)
         return self.model
 
+    def load_tp(self, tp_group, max_tokens_hint: int | None = None):
+        """Tensor-parallel load: this rank reads only its slices of the checkpoint (``ckpt.hf.load_tp_weights``)."""
+        from ..ckpt.hf import load_tp_weights
+        from ..parallel.tp import TPLlama
+        if self.model is None:
+            dev = tp_group.device
+            dtype = self.dtype if dev.type == "cuda" else torch.float32
+            crop = None if getattr(self, "aligner", None) is not None else (self.crop_to_size or None)
+            cfg, w = load_tp_weights(self.model_path, tp_group.rank, tp_group.world, vocab=crop, dtype=dtype, device=dev)
+            self.model = TPLlama(cfg, w, tp_group)
+        return self.model
+
     def unload(self) -> None:
         self.model = None
         if torch.cuda.is_available():
@@ -67,17 +79,24 @@ class TeacherModel(BaseModel):
 
     def process_chunk(self, reserve_vram_gb=None, num_inference_workers: int = 1, ids_to_collect=None,
                       data_manager=None, validation: bool = False, rank: int = 0, world: int = 1,
-                      sha_by_id: dict | None = None) -> int:
-        """Collect ``ids_to_collect`` into ``data_manager``. Returns the number of conversations written."""
+                      sha_by_id: dict | None = None, tp_group=None) -> int:
+        """Collect ``ids_to_collect`` into ``data_manager``. Returns the number of conversations written.
+        ``rank`` / ``world`` index the data-parallel replicas (each takes a strided share of the batches); with
+        ``tp_group`` the replica is a tensor-parallel group whose ranks all call this with the same arguments."""
         self._sort_datasets_by_len()
         wanted = set(ids_to_collect or [])
         chunk = [c for c in (self.validation_dataset if validation else self.dataset) if c.origin_convo_id in wanted]
         if not chunk:
             return 0
-        model = self.load()
         aligner = getattr(self, "aligner", None)
-        crop = model.cfg.vocab_size if aligner is not None else self.crop_to_size   # own vocabulary when remapping
-        collector = TeacherCollector(model, topk=self.topK, crop_to_size=crop, enable_topk=self.enable_topK)
+        if tp_group is not None:
+            from ..collect.collector import TPTeacherCollector
+            model = self.load_tp(tp_group)
+            collector = TPTeacherCollector(model, topk=self.topK, crop_to_size=model.V, enable_topk=self.enable_topK)
+        else:
+            model = self.load()
+            crop = model.cfg.vocab_size if aligner is not None else self.crop_to_size   # own vocabulary when remapping
+            collector = TeacherCollector(model, topk=self.topK, crop_to_size=crop, enable_topk=self.enable_topK)
         batches = plan_batches(chunk, max(1, self.batch_size))[rank::max(1, world)]
         done = 0
         t0 = time.time()

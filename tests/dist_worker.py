@@ -4,6 +4,7 @@
   gpu_p2p     NCCL + NVLink P2P ranks: P2P all-reduce equals NCCL all-reduce; a P2P-communicated training run equals
               the NCCL-communicated one
   cpu_tp      gloo ranks on CPU: the tensor-parallel teacher's top-K log-probs equal the unsharded model's
+  cpu_cli_tp  gloo ranks on CPU: the command-line pipeline with tp_size = 2 stores what a single process stores
   gpu_tp      NVLink ranks: fused all-gather->GEMM and GEMM->reduce-scatter equal NCCL + matmul; the tensor-parallel
               teacher's top-K log-probs equal the single-GPU model's
 Prints "WORKER_OK" on rank 0 when every check passed."""
@@ -141,6 +142,59 @@ def cpu_tp():
     dist.destroy_process_group()
 
 
+def cpu_cli_tp():
+    """The whole pipeline under two gloo ranks with a tensor-parallel teacher (tp_size = 2): what lands in the HDF5
+    store equals a single-process collection of the same teacher."""
+    import json
+    import numpy as np
+    from llm_distillery_b200 import cli
+    from llm_distillery_b200.data.h5store import H5Store
+    from llm_distillery_b200.models.llama import preset
+    from llm_distillery_b200.utils import synthetic
+    root = sys.argv[2]
+    rank = int(os.environ["RANK"])
+    conf = {"cache_folder": os.path.join(root, "cache"), "dataset_path": os.path.join(root, "train.jsonl"),
+            "validation_dataset_path": os.path.join(root, "val.jsonl"), "teacher_models_folder": os.path.join(root, "teachers"),
+            "student_path": os.path.join(root, "student"), "context_len": 96, "crop_distr_to_size": 400, "save_topK": 20,
+            "enable_topK": True, "device": "cpu", "num_epochs": 1, "num_warmup_steps": 2, "batch_size": 2,
+            "grad_accum_batches": 1, "temperature": 1.0, "lr": 1e-3, "optimizer": "adamw", "data_order": "sorted",
+            "training_precision": "fp32", "validate_every_n_epochs": 1, "save_student_every_n_epochs": 1,
+            "freeze_layers": [], "loss": "kl", "max_cache_size_gb": 320, "tp_size": 2}
+    if rank == 0:
+        tok = os.path.join(root, "tok")
+        synthetic.make_tokenizer(tok, 400)
+        tcfg = preset("plumbing-teacher", vocab_size=512, hidden_size=64, intermediate_size=176, max_position_embeddings=512)
+        scfg = preset("plumbing-student", vocab_size=512, hidden_size=64, intermediate_size=176, max_position_embeddings=512)
+        synthetic.make_model_dir(os.path.join(root, "teachers", "teacher_a"), tcfg, tok, seed=1, batch_size=4)
+        synthetic.make_model_dir(os.path.join(root, "student"), scfg, tok, seed=2)
+        synthetic.make_dataset(os.path.join(root, "train.jsonl"), 10, seed=3)
+        synthetic.make_dataset(os.path.join(root, "val.jsonl"), 4, seed=4)
+        with open(os.path.join(root, "config.json"), "w") as f:
+            json.dump(conf, f)
+    dist.init_process_group("gloo")
+    dist.barrier()
+    out = cli.main(["--config", os.path.join(root, "config.json")])
+    assert out["trained_samples"] == 10, out
+    if rank == 0:
+        # single-process collection of the same data into another cache folder
+        os.environ["WORLD_SIZE"] = "1"
+        conf1 = dict(conf, cache_folder=os.path.join(root, "cache1"), tp_size=1)
+        with open(os.path.join(root, "config1.json"), "w") as f:
+            json.dump(conf1, f)
+        cli.main(["--config", os.path.join(root, "config1.json")])
+        a = H5Store(os.path.join(root, "cache", "dataset"))
+        b = H5Store(os.path.join(root, "cache1", "dataset"))
+        ids = a.get_dataset_ids()
+        assert sorted(ids) == sorted(b.get_dataset_ids()) and len(ids) == 10
+        for cid in ids:
+            va, ia = a.load_id(cid)
+            vb, ib = b.load_id(cid)
+            assert va.shape == vb.shape and a.get_sha(cid) == b.get_sha(cid)
+            assert np.abs(va.astype(np.float32) - vb.astype(np.float32)).max() < 2e-2
+            assert (ia == ib).mean() > 0.97      # near-ties may swap under another summation order
+        print("WORKER_OK")
+
+
 def gpu_tp():
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -189,4 +243,4 @@ def gpu_tp():
 
 
 if __name__ == "__main__":
-    {"cpu_engine": cpu_engine, "gpu_p2p": gpu_p2p, "cpu_tp": cpu_tp, "gpu_tp": gpu_tp}[sys.argv[1]]()
+    {"cpu_engine": cpu_engine, "gpu_p2p": gpu_p2p, "cpu_tp": cpu_tp, "gpu_tp": gpu_tp, "cpu_cli_tp": cpu_cli_tp}[sys.argv[1]]()

@@ -16,9 +16,9 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _launch(mode, nproc, timeout=600, env=None):
+def _launch(mode, nproc, timeout=600, env=None, extra=()):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr",
-           "127.0.0.1", "--master-port", str(_free_port()), os.path.join(HERE, "dist_worker.py"), mode]
+           "127.0.0.1", "--master-port", str(_free_port()), os.path.join(HERE, "dist_worker.py"), mode, *extra]
     e = dict(os.environ, B200_NO_PROGRESS="1", OMP_NUM_THREADS="2", **(env or {}))
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=e)
     assert r.returncode == 0 and "WORKER_OK" in r.stdout, (r.stdout[-2000:], r.stderr[-4000:])
@@ -37,6 +37,10 @@ def test_p2p_collectives_and_training_match_nccl():
 
 def test_cpu_ranks_tensor_parallel_teacher_matches_unsharded():
     _launch("cpu_tp", 2)
+
+
+def test_cpu_ranks_pipeline_with_tensor_parallel_teacher(tmp_path):
+    _launch("cpu_cli_tp", 2, extra=(str(tmp_path),))
 
 
 @pytest.mark.gpu
