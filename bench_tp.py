@@ -5,6 +5,7 @@
         bench_tp.py gemms   [--tokens 8192] [--model llama-3-70b] [--iters 10]
         bench_tp.py collect [--model llama-3-70b] [--seq 8192] [--batch 1] [--topk 128] [--steps 3] [--layers N]
         bench_tp.py p2p     [--iters 10]
+        bench_tp.py head    [--rows 32768] [--hidden 4096] [--vocab 128256] [--topk 200] [--iters 10]
 
 gemms    the four linear layers of one decoder block at tensor-parallel width N: fused all-gather->GEMM and
          GEMM->reduce-scatter kernels against NCCL all_gather / reduce_scatter + torch.matmul (cuBLAS), with the
@@ -12,6 +13,8 @@ gemms    the four linear layers of one decoder block at tensor-parallel width N:
 collect  teacher collection throughput (tokens/s) of the tensor-parallel forward + vocabulary-parallel top-K,
          random-init weights, synthetic token ids (``--layers`` below the model's depth is a smoke run, flagged in the
          output and not a benchmark number).
+head     the fused vocabulary-parallel LM head + distillation loss (forward and backward) over N vocabulary slices
+         against cuBLAS + PyTorch ops + NCCL all-reduce, KL and JSD at T = 1 and 2.
 p2p      peer-to-peer all-reduce (reduce-scatter + all-gather kernels) against NCCL all_reduce, bus bandwidth.
 
 Timing: CUDA events on the launching stream after warm-up, a barrier before each timed call, median per rank, MAX
@@ -164,6 +167,63 @@ def bench_collect(args, dev, rank, world) -> None:
          fwd_tflops_per_gpu=round(cfg.flops_per_token_fwd(L) * toks / ms / 1e9 / world, 1))
 
 
+def bench_head(args, dev, rank, world) -> None:
+    """Fused vocabulary-parallel loss head (forward + backward) against the unfused library path: cuBLAS logits of
+    the slice, fp32 softmax statistics with NCCL all-reduces, the loss in PyTorch ops, autograd backward, NCCL
+    all-reduce of dH."""
+    from llm_distillery_b200.loss import divergence as dv
+    from llm_distillery_b200.loss.head import sort_teacher_rows
+    from llm_distillery_b200.parallel.vp_head import VocabParallelHead
+    M, h, V, K = args.rows, args.hidden, args.vocab, args.topk
+    g = torch.Generator(device=dev).manual_seed(5)          # same stream on every rank: replicated inputs
+    Hc = (torch.randn((M, h), device=dev, generator=g) * 0.5).to(torch.bfloat16)
+    ids = torch.randint(0, V, (M, K), device=dev, generator=g, dtype=torch.int32)
+    u = torch.log_softmax(torch.randn((M, K), device=dev, generator=g) * 2, -1)
+    ids, u = sort_teacher_rows(ids, u)
+    grp = TPGroup(dev, M, h)
+    head = VocabParallelHead(grp, M, h, K, V)
+    gw = torch.Generator(device=dev).manual_seed(100 + rank)
+    Ws = (torch.randn((head.vl, h), device=dev, generator=gw) * 0.02).to(torch.bfloat16)
+    dW = torch.zeros((head.vl, h), dtype=torch.float32, device=dev)
+    pk, src = peak_tflops()
+    for kind in ("kl", "jsd"):
+        for T in (1.0, 2.0):
+            def fused():
+                return head.loss_and_grads(Hc, Ws, ids, u, kind, T, dW=dW)
+
+            def unfused():
+                Hr = Hc.detach().requires_grad_(True)
+                Wr = Ws.detach().requires_grad_(True)
+                z = (Hr @ Wr.t()).float() / T
+                m = z.detach().max(-1).values
+                dist.all_reduce(m, op=dist.ReduceOp.MAX)
+                se = torch.exp(z - m[:, None]).sum(-1)
+                se_all = se.detach().clone()
+                dist.all_reduce(se_all)
+                lse = m + torch.log(se + (se_all - se.detach()))
+                local = ids.long() - head.lo
+                inside = (local >= 0) & (local < head.valid)
+                zk_part = torch.where(inside, torch.gather(z, 1, local.clamp(0, head.valid - 1)), torch.zeros((), device=dev))
+                zk_all = zk_part.detach().clone()
+                dist.all_reduce(zk_all)
+                zk = zk_part + (zk_all - zk_part.detach())
+                s, t = dv.student_teacher_logprobs(lse, zk, u, ids.long() < V, T)
+                rows = dv.loss_rows(kind, s, t)
+                rows.mean().backward()
+                dist.all_reduce(Hr.grad)
+                return rows
+
+            ms_f = timed_max(fused, args.iters)
+            ms_u = timed_max(unfused, max(3, args.iters // 2))
+            flops = 4 * 2.0 * M * head.vl * h       # pass 1, pass 2, dgrad, wgrad on the slice
+            link = M * h * 2 * (world - 1) / world * 2 + (world - 1) * M * K * 4
+            ideal = max(flops / (pk * 1e9), link / (NVLINK_GBS * 1e6))
+            emit(rank, case=f"vocab-parallel head {kind} T={T}", tp=world, shape=[M, h, V, K], ms_fused=round(ms_f, 3),
+                 ms_unfused=round(ms_u, 3), speedup=round(ms_u / ms_f, 2), tflops_per_gpu=round(flops / ms_f / 1e9, 1),
+                 roofline_ms=round(ideal, 3), frac_of_roofline=round(ideal / ms_f, 3),
+                 roofline=f"max(4 GEMMs/{pk} TF/s of {src}, link bytes/{NVLINK_GBS} GB/s)")
+
+
 def bench_p2p(args, dev, rank, world) -> None:
     from llm_distillery_b200.parallel.p2p import P2PComm, SymmetricBuffer
     comm = P2PComm(dev)
@@ -181,7 +241,10 @@ def bench_p2p(args, dev, rank, world) -> None:
 
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
-    ap.add_argument("cmd", choices=["gemms", "collect", "p2p"])
+    ap.add_argument("cmd", choices=["gemms", "collect", "p2p", "head"])
+    ap.add_argument("--rows", type=int, default=32768)
+    ap.add_argument("--hidden", type=int, default=4096)
+    ap.add_argument("--vocab", type=int, default=128256)
     ap.add_argument("--model", default="llama-3-70b")
     ap.add_argument("--tokens", type=int, default=8192)
     ap.add_argument("--seq", type=int, default=8192)
@@ -201,7 +264,7 @@ def main() -> None:
     os.environ.setdefault("WORLD_SIZE", "1")
     dist.init_process_group("nccl", device_id=dev)
     rank, world = dist.get_rank(), dist.get_world_size()
-    {"gemms": bench_gemms, "collect": bench_collect, "p2p": bench_p2p}[args.cmd](args, dev, rank, world)
+    {"gemms": bench_gemms, "collect": bench_collect, "p2p": bench_p2p, "head": bench_head}[args.cmd](args, dev, rank, world)
     torch.cuda.synchronize()
     dist.barrier()
     dist.destroy_process_group()

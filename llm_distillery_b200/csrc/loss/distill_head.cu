@@ -30,6 +30,7 @@ struct LseParams {
   float* psum;      // [n_tiles, M] out: sum_j exp(z_j/T - pmax)
   int K;
   float inv_T;
+  int id_off;       // vocabulary-parallel shard: this GEMM's column j is token id j + id_off (0 when unsharded)
 };
 
 struct EpiLse {
@@ -46,11 +47,11 @@ struct EpiLse {
       int lo = 0, hi = p.K;
       while (lo < hi) {
         const int mid = (lo + hi) >> 1;
-        if (__ldg(ids + mid) < n0) lo = mid + 1; else hi = mid;
+        if (__ldg(ids + mid) - p.id_off < n0) lo = mid + 1; else hi = mid;
       }
       pos = lo;
     }
-    int next_id = (row_ok && pos < p.K) ? __ldg(ids + pos) : 0x7fffffff;
+    int next_id = (row_ok && pos < p.K) ? __ldg(ids + pos) - p.id_off : 0x7fffffff;
     float mx = -INFINITY, sm = 0.f;
     const float c2 = p.inv_T * LOG2E;
 #pragma unroll 1
@@ -69,7 +70,7 @@ struct EpiLse {
         for (int j = 0; j < 32; ++j) v = (sel == j) ? __uint_as_float(r[j]) : v;
         if (next_id < N) p.zk[(long long)row * p.K + pos] = v * p.inv_T;
         ++pos;
-        next_id = pos < p.K ? __ldg(ids + pos) : 0x7fffffff;
+        next_id = pos < p.K ? __ldg(ids + pos) - p.id_off : 0x7fffffff;
       }
       // online max / sum-exp (log2 domain internally)
       float cm = -INFINITY;
@@ -108,6 +109,7 @@ struct DzParams {
   long long ldz;
   int K;
   float inv_T;
+  int id_off;          // see LseParams
 };
 
 struct EpiDz {
@@ -124,14 +126,14 @@ struct EpiDz {
       int lo = 0, hi = p.K;
       while (lo < hi) {
         const int mid = (lo + hi) >> 1;
-        if (__ldg(ids + mid) < n0) lo = mid + 1; else hi = mid;
+        if (__ldg(ids + mid) - p.id_off < n0) lo = mid + 1; else hi = mid;
       }
       pos = lo;
       gs = p.g[row] * p.inv_T;
       coef = -gs * p.A[row];
       lse2 = p.lse[row] * LOG2E;
     }
-    int next_id = (row_ok && pos < p.K) ? __ldg(ids + pos) : 0x7fffffff;
+    int next_id = (row_ok && pos < p.K) ? __ldg(ids + pos) - p.id_off : 0x7fffffff;
     const float c2 = p.inv_T * LOG2E;
 #pragma unroll 1
     for (int c = 0; c < BN / 32; ++c) {
@@ -150,7 +152,7 @@ struct EpiDz {
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] += (sel == j) ? add : 0.f;
         ++pos;
-        next_id = pos < p.K ? __ldg(ids + pos) : 0x7fffffff;
+        next_id = pos < p.K ? __ldg(ids + pos) - p.id_off : 0x7fffffff;
       }
       __nv_bfloat16* dst = p.dz + (long long)row * p.ldz + col0;
       const int ncols = min(32, N - col0);
@@ -341,6 +343,43 @@ __global__ void __launch_bounds__(128) distill_rows_kernel(RowParams p) {
   }
 }
 
+
+// Vocabulary-parallel head: every rank ran pass 1 on its slice of the vocabulary. One warp per row reads ALL ranks'
+// partial statistics straight out of their memory (peer loads over NVLink) and leaves, locally, one combined
+// (max, sum-exp) pair per row and the summed z_k (an id lives in exactly one slice; the other ranks hold zeros),
+// which distill_rows_kernel then consumes as a single column tile.
+struct VpPeers { const void* p[16]; };
+__global__ void __launch_bounds__(128) vp_combine_kernel(VpPeers pmax, VpPeers psum, VpPeers zk, int world,
+                                                        int n_tiles, int M, int K, float* __restrict__ out_pmax,
+                                                        float* __restrict__ out_psum, float* __restrict__ out_zk) {
+  const int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (row >= M) return;
+  const int n = world * n_tiles;
+  float mx = -INFINITY;
+  for (int i = lane; i < n; i += 32) {
+    const int q = i / n_tiles, t = i - q * n_tiles;
+    mx = fmaxf(mx, reinterpret_cast<const float*>(pmax.p[q])[(long long)t * M + row]);
+  }
+  mx = warp_max(mx);
+  float sm = 0.f;
+  for (int i = lane; i < n; i += 32) {
+    const int q = i / n_tiles, t = i - q * n_tiles;
+    const long long o = (long long)t * M + row;
+    sm += reinterpret_cast<const float*>(psum.p[q])[o] * __expf(reinterpret_cast<const float*>(pmax.p[q])[o] - mx);
+  }
+  sm = warp_sum(sm);
+  if (lane == 0) {
+    out_pmax[row] = mx;
+    out_psum[row] = sm;
+  }
+  for (int k = lane; k < K; k += 32) {
+    float z = 0.f;
+    for (int q = 0; q < world; ++q) z += reinterpret_cast<const float*>(zk.p[q])[(long long)row * K + k];
+    out_zk[(long long)row * K + k] = z;
+  }
+}
+
 }  // namespace head
 }  // namespace b200
 
@@ -358,8 +397,35 @@ int b200_lmhead_lse_gather(const void* Hc, const void* W, int M, int N, int h, l
                            cudaStream_t st) {
   if (!Hc || !W || !ids || !zk || !pmax || !psum || M <= 0 || N <= 0 || h <= 0 || K <= 0 || (ldh & 7) || (ldw & 7))
     return B200_ERR_ARG;
-  LseParams ep{ids, zk, pmax, psum, K, inv_T};
+  LseParams ep{ids, zk, pmax, psum, K, inv_T, 0};
   return launch_head<EpiLse>(Hc, W, M, N, h, ldh, ldw, ep, st);
+}
+
+// Pass 1 on one vocabulary slice: W holds the rows [id_off, id_off + N) of the LM head; ids stay global.
+int b200_lmhead_lse_gather_shard(const void* Hc, const void* W, int M, int N, int h, long long ldh, long long ldw,
+                                 const int* ids, int K, float inv_T, int id_off, float* zk, float* pmax, float* psum,
+                                 cudaStream_t st) {
+  if (!Hc || !W || !ids || !zk || !pmax || !psum || M <= 0 || N <= 0 || h <= 0 || K <= 0 || (ldh & 7) || (ldw & 7))
+    return B200_ERR_ARG;
+  LseParams ep{ids, zk, pmax, psum, K, inv_T, id_off};
+  return launch_head<EpiLse>(Hc, W, M, N, h, ldh, ldw, ep, st);
+}
+
+// Combine the slices' statistics (arrays of `world` device pointers, peers' memory included) into one local tile.
+int b200_vp_combine(const void* const* pmax_ptrs, const void* const* psum_ptrs, const void* const* zk_ptrs, int world,
+                    int n_tiles, int M, int K, float* out_pmax, float* out_psum, float* out_zk, cudaStream_t st) {
+  if (!pmax_ptrs || !psum_ptrs || !zk_ptrs || world < 1 || world > 16 || n_tiles <= 0 || M <= 0 || K <= 0 ||
+      !out_pmax || !out_psum || !out_zk)
+    return B200_ERR_ARG;
+  VpPeers a{}, b{}, c{};
+  for (int i = 0; i < world; ++i) {
+    a.p[i] = pmax_ptrs[i];
+    b.p[i] = psum_ptrs[i];
+    c.p[i] = zk_ptrs[i];
+  }
+  vp_combine_kernel<<<ceil_div(M, 4), 128, 0, st>>>(a, b, c, world, n_tiles, M, K, out_pmax, out_psum, out_zk);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200_OK;
 }
 
 int b200_distill_rows(const float* pmax, const float* psum, const float* zk, const float* u, const int* ids,
@@ -381,7 +447,18 @@ int b200_lmhead_dlogits(const void* Hc, const void* W, int M, int N, int h, long
   if (!Hc || !W || !ids || !a || !A || !lse || !g || !dz || M <= 0 || N <= 0 || h <= 0 || K <= 0 || (ldh & 7) ||
       (ldw & 7))
     return B200_ERR_ARG;
-  DzParams ep{ids, a, A, lse, g, (__nv_bfloat16*)dz, ldz, K, inv_T};
+  DzParams ep{ids, a, A, lse, g, (__nv_bfloat16*)dz, ldz, K, inv_T, 0};
+  return launch_head<EpiDz>(Hc, W, M, N, h, ldh, ldw, ep, st);
+}
+
+// Pass 2 on one vocabulary slice (see b200_lmhead_lse_gather_shard).
+int b200_lmhead_dlogits_shard(const void* Hc, const void* W, int M, int N, int h, long long ldh, long long ldw,
+                              const int* ids, const float* a, const float* A, const float* lse, const float* g, int K,
+                              float inv_T, int id_off, void* dz, long long ldz, cudaStream_t st) {
+  if (!Hc || !W || !ids || !a || !A || !lse || !g || !dz || M <= 0 || N <= 0 || h <= 0 || K <= 0 || (ldh & 7) ||
+      (ldw & 7))
+    return B200_ERR_ARG;
+  DzParams ep{ids, a, A, lse, g, (__nv_bfloat16*)dz, ldz, K, inv_T, id_off};
   return launch_head<EpiDz>(Hc, W, M, N, h, ldh, ldw, ep, st);
 }
 }

@@ -4,6 +4,7 @@
   gpu_p2p     NCCL + NVLink P2P ranks: P2P all-reduce equals NCCL all-reduce; a P2P-communicated training run equals
               the NCCL-communicated one
   cpu_tp      gloo ranks on CPU: the tensor-parallel teacher's top-K log-probs equal the unsharded model's
+  cpu_vp_head gloo ranks on CPU: the vocabulary-parallel loss head equals the unsharded head (loss, dH, dW)
   cpu_cli_tp  gloo ranks on CPU: the command-line pipeline with tp_size = 2 stores what a single process stores
   gpu_tp      NVLink ranks: fused all-gather->GEMM and GEMM->reduce-scatter equal NCCL + matmul; the tensor-parallel
               teacher's top-K log-probs equal the single-GPU model's
@@ -142,6 +143,48 @@ def cpu_tp():
     dist.destroy_process_group()
 
 
+def _vp_head_check(dev, dtype, rank, world, atol):
+    """Vocabulary-parallel head against the unsharded head on every rank: per-row loss, dH, this rank's dW rows."""
+    from llm_distillery_b200.loss.head import fused_distill_rows, sort_teacher_rows
+    from llm_distillery_b200.parallel.tp import TPGroup
+    from llm_distillery_b200.parallel.vp_head import VocabParallelHead
+    M, h, V, K = 256 * world, 256, 1000, 24
+    g = torch.Generator().manual_seed(7)
+    Hc = (torch.randn((M, h), generator=g) * 0.5).to(dtype).to(dev)
+    W = (torch.randn((V + 24, h), generator=g) * 0.05).to(dtype).to(dev)
+    ids = torch.stack([torch.randperm(V + 20, generator=g)[:K] for _ in range(M)]).to(torch.int32)   # some ids >= vocab
+    u = torch.log_softmax(torch.randn((M, K), generator=g) * 2, -1)
+    ids, u = sort_teacher_rows(ids, u)
+    ids, u = ids.to(dev), u.to(dev)
+    grp = TPGroup(dev, M, h, dtype=dtype)
+    head = VocabParallelHead(grp, M, h, K, V)
+    for kind, T in (("kl", 2.0), ("jsd", 1.0), ("rkl", 1.0)):
+        Ws = torch.zeros((head.vl, h), dtype=dtype, device=dev)
+        Ws[: head.valid] = W[head.lo: head.lo + head.valid]
+        loss, dH, dW = head.loss_and_grads(Hc, Ws, ids, u, kind, T)
+        Hr = Hc.detach().clone().requires_grad_(True)
+        Wr = W.detach().clone().requires_grad_(True)
+        ref = fused_distill_rows(Hr, Wr, ids, u, kind, T, vocab=V)
+        ref.mean().backward()
+        if dev != "cpu":
+            torch.cuda.synchronize()
+            from llm_distillery_b200.ops import _lib
+            assert _lib.take_device_error() == 0
+        e1 = (loss - ref.detach()).abs().max().item()
+        e2 = (dH.float() - Hr.grad.float()).abs().max().item() / max(Hr.grad.float().abs().max().item(), 1e-12)
+        wref = Wr.grad.float()[head.lo: head.lo + head.valid]
+        e3 = (dW[: head.valid] - wref).abs().max().item() / max(wref.abs().max().item(), 1e-12)
+        assert e1 < atol and e2 < 10 * atol and e3 < 10 * atol, (kind, e1, e2, e3)
+
+
+def cpu_vp_head():
+    dist.init_process_group("gloo")
+    _vp_head_check("cpu", torch.float32, dist.get_rank(), dist.get_world_size(), 1e-4)
+    if dist.get_rank() == 0:
+        print("WORKER_OK")
+    dist.destroy_process_group()
+
+
 def cpu_cli_tp():
     """The whole pipeline under two gloo ranks with a tensor-parallel teacher (tp_size = 2): what lands in the HDF5
     store equals a single-process collection of the same teacher."""
@@ -237,10 +280,12 @@ def gpu_tp():
         assert err2 < 0.08, ("gemm_rs", it, err2)
     del grp
     _tp_model_check(dev, torch.bfloat16, rank, world, 32, 0.05)
+    _vp_head_check(dev, torch.bfloat16, rank, world, 5e-3)
     if rank == 0:
         print("WORKER_OK")
     dist.destroy_process_group()
 
 
 if __name__ == "__main__":
-    {"cpu_engine": cpu_engine, "gpu_p2p": gpu_p2p, "cpu_tp": cpu_tp, "gpu_tp": gpu_tp, "cpu_cli_tp": cpu_cli_tp}[sys.argv[1]]()
+    {"cpu_engine": cpu_engine, "gpu_p2p": gpu_p2p, "cpu_tp": cpu_tp, "gpu_tp": gpu_tp, "cpu_cli_tp": cpu_cli_tp,
+     "cpu_vp_head": cpu_vp_head}[sys.argv[1]]()

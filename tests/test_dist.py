@@ -39,6 +39,10 @@ def test_cpu_ranks_tensor_parallel_teacher_matches_unsharded():
     _launch("cpu_tp", 2)
 
 
+def test_cpu_ranks_vocabulary_parallel_head_matches_unsharded():
+    _launch("cpu_vp_head", 2)
+
+
 def test_cpu_ranks_pipeline_with_tensor_parallel_teacher(tmp_path):
     _launch("cpu_cli_tp", 2, extra=(str(tmp_path),))
 
