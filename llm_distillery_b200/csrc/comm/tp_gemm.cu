@@ -2,7 +2,7 @@
 // gemm_core.cuh, peer loads/stores over NVLink on symmetric buffers; no NCCL, no multimem, no TMA multicast).
 //
 //   ag_gemm   Y[T, N_local] = gather_rows(X)[T, K] * W[N_local, K]^T          (column-parallel: QKV, gate/up, lm_head)
-//     X lives token-sharded: rank q produced rows [q*Ts, (q+1)*Ts) of ITS copy of the gathered buffer XF. Two extra
+//     X lives token-sharded: rank q produced rows [q*Ts, (q+1)*Ts) of ITS copy of the gathered buffer XF. Four extra
 //     "copy warps" per CTA pull the other ranks' slabs into the local XF, 128-row block by block, in the order
 //     rank+1, rank+2, ...; the tile loop runs over the same order starting with the rank's own slab, and the TMA
 //     producer starts a tile only when the block's arrival counter says that all copy warps have delivered it.
@@ -30,9 +30,10 @@ using comm::Peers;
 
 constexpr int TBN = 256;
 constexpr int TSTAGES = 4;
-constexpr int AG_THREADS = 256;  // TMA warp, MMA warp, 4 epilogue warps, 2 copy warps
+constexpr int AG_THREADS = 320;  // TMA warp, MMA warp, 4 epilogue warps, 4 copy warps
 constexpr int RS_THREADS = 192;
-constexpr int COPY_WARPS = 2;
+constexpr int COPY_WARPS = 4;
+constexpr int COPY_UNROLL = 8;  // 16-byte peer loads in flight per copy thread: NVLink latency needs MBs in flight
 
 enum Mode { MODE_AG = 0, MODE_RS = 1 };
 
@@ -199,7 +200,7 @@ __device__ __forceinline__ void rs_tail(const TpParams& p, int N, bool ok_all, i
   }
 }
 
-// ag_gemm copy warps (ct = 0..63 inside the CTA): announce the own slab, then pull the other ranks' slabs into the
+// ag_gemm copy warps (ct = 0..127 inside the CTA): announce the own slab, then pull the other ranks' slabs into the
 // local gathered buffer, one 128-row block at a time, and count each finished block.
 __device__ __forceinline__ void ag_copy_warps(const TpParams& p, int ct, int lane, volatile int* abort_flag,
                                               unsigned int* err_word) {
@@ -223,15 +224,12 @@ __device__ __forceinline__ void ag_copy_warps(const TpParams& p, int ct, int lan
       const int m_blk = src * bps + b;
       const long long off = (long long)m_blk * blk_vecs;
       long long i = (long long)blockIdx.x * (COPY_WARPS * 32) + ct;
-      for (; i + 3 * step < blk_vecs; i += 4 * step) {
-        const uint4 v0 = ld_peer_v4(src_base + off + i);
-        const uint4 v1 = ld_peer_v4(src_base + off + i + step);
-        const uint4 v2 = ld_peer_v4(src_base + off + i + 2 * step);
-        const uint4 v3 = ld_peer_v4(src_base + off + i + 3 * step);
-        dst_base[off + i] = v0;
-        dst_base[off + i + step] = v1;
-        dst_base[off + i + 2 * step] = v2;
-        dst_base[off + i + 3 * step] = v3;
+      for (; i + (COPY_UNROLL - 1) * step < blk_vecs; i += COPY_UNROLL * step) {
+        uint4 v[COPY_UNROLL];
+#pragma unroll
+        for (int u = 0; u < COPY_UNROLL; ++u) v[u] = ld_peer_v4(src_base + off + i + u * step);
+#pragma unroll
+        for (int u = 0; u < COPY_UNROLL; ++u) dst_base[off + i + u * step] = v[u];
       }
       for (; i < blk_vecs; i += step) dst_base[off + i] = ld_peer_v4(src_base + off + i);
       fence_proxy_async_all();
