@@ -172,6 +172,9 @@ def handle_termination(signum, frame) -> None:
         t.close()
     if _STATE.get("student") is not None:
         _STATE["student"].close()
+    if _STATE.get("heartbeat") is not None:
+        _STATE["heartbeat"].close("done")
+        _STATE["heartbeat"] = None
     if signum is not None:
         os._exit(0)
 
@@ -282,8 +285,42 @@ def collect(teachers, cfg, store, ids, validation, rank, world, student=None) ->
 
 
 def main(argv=None, default_config_path: str | None = None) -> dict:
+    """Run the pipeline. With several ranks a heartbeat / watchdog pair runs beside it: when a peer stops beating,
+    the surviving ranks find out between two steps, save their trainer state without any collective and exit with
+    status 3; running the same command again resumes (SHA sync for collection, trainer state for training)."""
+    from .obs import watchdog
+    try:
+        return _main(argv, default_config_path)
+    except watchdog.RankFailure as e:
+        print(f"[watchdog] {e}: saving state and leaving", flush=True)
+        student, hb = _STATE.get("student"), _STATE.get("heartbeat")
+        if student is not None and getattr(student, "engine", None) is not None:
+            try:
+                student._save_state(collective=False)
+            except Exception as ex:  # noqa: BLE001
+                print(f"[watchdog] emergency save failed: {ex}", flush=True)
+        if hb is not None:
+            hb.close("failed")
+        for key in ("data_manager", "validation_data_manager"):
+            if _STATE.get(key) is not None:
+                _STATE[key].close()
+        os._exit(3)
+
+
+def _main(argv=None, default_config_path: str | None = None) -> dict:
+    from .obs import watchdog
     cfg = get_params(argv, default_config_path)
     rank, world, comm = _init_distributed(cfg)
+    def _escalate(failed):      # watchdog thread: the main thread is stuck (e.g. inside a collective with a dead peer)
+        print(f"[watchdog] {failed}; the main thread did not return from its step: leaving without a state save "
+              f"(the last checkpoint and the HDF5 cache stay valid)", flush=True)
+        os._exit(3)
+
+    stall = os.environ.get("B200_STALL_TIMEOUT")
+    heartbeat = watchdog.from_env(rank, world, timeout=float(os.environ.get("B200_HEARTBEAT_TIMEOUT", "60")),
+                                  stall_timeout=float(stall) if stall else None, on_failure=_escalate)
+    _STATE["heartbeat"] = heartbeat
+
     signal.signal(signal.SIGTERM, handle_termination)
     signal.signal(signal.SIGINT, handle_termination)
 
@@ -291,6 +328,9 @@ def main(argv=None, default_config_path: str | None = None) -> dict:
     teachers = get_teachers(cfg.teacher_models_folder, cfg.use_teachers, cfg.interactive)
     student = StudentModel(cfg.student_path, paths, cfg.add_bos, cfg.prompt_format, cfg.batch_size, cfg.interactive)
     student.comm, student.rank, student.world = comm, rank, world
+    student.heartbeat = heartbeat
+    for t in teachers:
+        t.heartbeat = heartbeat
     print("Opening data stores...")
     data_manager = H5Store(paths.dataset, cfg.device, manager_name="main", interactive=cfg.interactive)
     validation_data_manager = H5Store(paths.dataset_validation, cfg.device, manager_name="validation",

@@ -164,6 +164,100 @@ __global__ void __launch_bounds__(NT) rmsnorm_bwd_kernel(const __nv_bfloat16* __
   }
 }
 
+// 16-byte read-only load that the compiler may not hoist out of a loop (keeps loop-invariant vectors in L1, not in
+// registers).
+__device__ __forceinline__ uint4 ld_nc_v4_nohoist(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+
+// Second read of a vector this thread loaded a moment ago (volatile: the compiler may not merge it with the first).
+__device__ __forceinline__ uint4 ld_cg_v4_again(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.global.ca.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+
+// Same computation with one WARP per row (h = VPL * 256): no block barriers, 2 * VPL 16-byte loads in flight per
+// lane, the second sweep re-reading the row through the caches, and the warp's running weight-gradient sums
+// in shared memory (h floats per warp, split into two planes so that every access is a conflict-free float4).
+// Each warp owns one row of dw_partial.
+template <int VPL>
+__global__ void __launch_bounds__(128, 5) rmsnorm_bwd_warp_kernel(const __nv_bfloat16* __restrict__ dy,
+                                                              const __nv_bfloat16* __restrict__ x,
+                                                              const __nv_bfloat16* __restrict__ w,
+                                                              const float* __restrict__ rstd,
+                                                              const __nv_bfloat16* __restrict__ dres,
+                                                              __nv_bfloat16* __restrict__ dx,
+                                                              float* __restrict__ dw_partial, int rows, int nwarps) {
+  constexpr int h = VPL * 256;
+  extern __shared__ float4 sdw_all[];
+  const int lane = threadIdx.x & 31;
+  const int gw = blockIdx.x * 4 + (threadIdx.x >> 5);
+  float4* lo = sdw_all + (threadIdx.x >> 5) * (h / 4);  // plane 0: elements 0-3 of every 8-vector
+  float4* hi = lo + h / 8;                                // plane 1: elements 4-7
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    lo[lane + 32 * i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    hi[lane + 32 * i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  if (gw >= nwarps) return;
+  const uint4* wv = reinterpret_cast<const uint4*>(w);
+  for (int row = gw; row < rows; row += nwarps) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * h);
+    const uint4* dr = reinterpret_cast<const uint4*>(dy + (size_t)row * h);
+    const float rs = rstd[row];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      float xf[8], df[8], wf[8];
+      unpack8(xr[lane + 32 * i], xf);
+      unpack8(dr[lane + 32 * i], df);
+      unpack8(ld_nc_v4_nohoist(wv + lane + 32 * i), wf);
+      float4 a = lo[lane + 32 * i], b = hi[lane + 32 * i];
+      float t[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float xh = xf[j] * rs;
+        t[j] = df[j] * xh;
+        dot += df[j] * wf[j] * xh;
+      }
+      a.x += t[0]; a.y += t[1]; a.z += t[2]; a.w += t[3];
+      b.x += t[4]; b.y += t[5]; b.z += t[6]; b.w += t[7];
+      lo[lane + 32 * i] = a;
+      hi[lane + 32 * i] = b;
+    }
+    const float c = warp_sum(dot) * (1.f / (float)h);
+    // second sweep: the row comes back from L1/L2 (it was read a moment ago), which costs no HBM traffic and keeps
+    // the register count low enough for many rows in flight per SM
+    const uint4* rr = dres ? reinterpret_cast<const uint4*>(dres + (size_t)row * h) : nullptr;
+    uint4* outr = reinterpret_cast<uint4*>(dx + (size_t)row * h);
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      float xf[8], df[8], wf[8], o[8];
+      unpack8(ld_cg_v4_again(xr + lane + 32 * i), xf);
+      unpack8(ld_cg_v4_again(dr + lane + 32 * i), df);
+      unpack8(ld_nc_v4_nohoist(wv + lane + 32 * i), wf);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = rs * (df[j] * wf[j] - xf[j] * rs * c);
+      if (rr) {
+        float r8[8];
+        unpack8(rr[lane + 32 * i], r8);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] += r8[j];
+      }
+      outr[lane + 32 * i] = pack8(o);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    float4* p = reinterpret_cast<float4*>(dw_partial + (size_t)gw * h + (size_t)(lane + 32 * i) * 8);
+    p[0] = lo[lane + 32 * i];
+    p[1] = hi[lane + 32 * i];
+  }
+}
+
 // out[j] (+)= sum_b partial[b][j]; block = 32 columns x 8 row groups, reduced through shared memory
 __global__ void __launch_bounds__(256) colsum_kernel(const float* __restrict__ partial, float* __restrict__ out,
                                                      int nblk, int h, int accumulate) {
@@ -366,7 +460,7 @@ using namespace b200::ew;
 
 // Number of fp32 partial rows rmsnorm_bwd needs in `dw_partial` ([blocks, h]).
 int b200_rmsnorm_bwd_blocks(int rows) {
-  const int cap = sm_count() * 8;  // 8 resident 256-thread CTAs per SM keep HBM busy; partial rows stay small
+  const int cap = sm_count() * 16;  // enough rows in flight per SM to keep HBM busy; partial rows stay small
   return rows < cap ? rows : cap;
 }
 
@@ -385,9 +479,19 @@ int b200_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* 
                      float* dw_partial, float* dw_out, int dw_accumulate, int rows, int h, cudaStream_t st) {
   if (!dy || !x || !w || !rstd || !dx || !dw_partial || !dw_out || rows <= 0 || (h & 7) || h > NT * MAX_VEC * 8)
     return B200_ERR_ARG;
-  const int grid = b200_rmsnorm_bwd_blocks(rows);
-  rmsnorm_bwd_kernel<<<grid, NT, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
-                                          rstd, (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, dw_partial, rows, h);
+  const int grid = b200_rmsnorm_bwd_blocks(rows);  // partial rows: one per block, or one per warp in the warp kernels
+#define B200_RMS_BWD_WARP(VPL)                                                                                       \
+  rmsnorm_bwd_warp_kernel<VPL><<<ceil_div(grid, 4), 128, 4 * (VPL) * 256 * 4, st>>>(                                                   \
+      (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, rstd, (const __nv_bfloat16*)dres,   \
+      (__nv_bfloat16*)dx, dw_partial, rows, grid)
+  if (h == 2048) B200_RMS_BWD_WARP(8);
+  else if (h == 1024) B200_RMS_BWD_WARP(4);
+  else if (h == 512) B200_RMS_BWD_WARP(2);
+  else if (h == 256) B200_RMS_BWD_WARP(1);
+  else
+    rmsnorm_bwd_kernel<<<grid, NT, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
+                                            rstd, (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, dw_partial, rows, h);
+#undef B200_RMS_BWD_WARP
   B200_CUDA_CHECK(cudaGetLastError());
   colsum_kernel<<<ceil_div(h, 32), 256, 0, st>>>(dw_partial, dw_out, grid, h, dw_accumulate);
   B200_CUDA_CHECK(cudaGetLastError());

@@ -191,10 +191,11 @@ class StudentModel(BaseModel):
                 "next_val_step": self.next_val_step, "next_accum_step": self.next_accum_step,
                 "total_training_steps": self.total_training_steps, "seed": self.seed, "world": self.world}
 
-    def _save_state(self) -> None:
-        if self.num_trained_steps < self.total_training_steps and self.rank == 0:
+    def _save_state(self, collective: bool = True) -> None:
+        """``collective=False``: emergency save after a peer failed - no barrier, files of this rank only."""
+        if collective and self.num_trained_steps < self.total_training_steps and self.rank == 0:
             self.paths.empty_student_states()
-        if self.comm is not None:
+        if collective and self.comm is not None:
             self.comm.barrier()
         if self.rank == 0 or (self.comm is not None and self.comm.shards_optimizer):
             ckpt.save_trainer_state(self.paths.student_states, self.model, self.engine.opt, self.engine.schedule,
@@ -277,12 +278,18 @@ class StudentModel(BaseModel):
             self.logger.log({"Learning Rate": lr}, self.num_trained_steps)
         self.losses.log(self.num_trained_steps)
         self.losses.empty()
+        if self.comm is not None and hasattr(self.comm, "check"):
+            self.comm.check()      # a bounded device-side wait that ran out (lost peer) surfaces here, not as a hang
 
     def _run_distillation_cycle(self, cycle, data_manager, validation_data_manager) -> bool:
         batches, sizes = cycle
         updated = False
         for convos, n_samples in zip(batches, sizes):
             updated = False
+            hbt = getattr(self, "heartbeat", None)
+            if hbt is not None:      # between steps, nothing in flight: learn about a lost peer BEFORE the next launch
+                hbt.beat(self.num_trained_steps, "train")
+                hbt.check()
             if convos is not None:
                 teacher = data_manager.read_next_batch()
                 hb = self.build_host_batch(convos, teacher)

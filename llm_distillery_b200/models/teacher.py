@@ -102,7 +102,11 @@ class TeacherModel(BaseModel):
         t0 = time.time()
         with progress(total=len(chunk), desc="Convos", leave=False) as bar:
             bar.set_postfix_str("Generating...")
+            hbt = getattr(self, "heartbeat", None)
             for tokens, convos in batches:
+                if hbt is not None:      # between batches: a lost peer is noticed before the next launch
+                    hbt.beat(done, "collect")
+                    hbt.check()
                 rows = collector.collect_batch(tokens, convos, aligner=aligner, validation=validation)
                 if sha_by_id:   # the store is keyed by the STUDENT's view of the text (that is what sync compares)
                     for r in rows:

@@ -5,6 +5,7 @@
               the NCCL-communicated one
   cpu_tp      gloo ranks on CPU: the tensor-parallel teacher's top-K log-probs equal the unsharded model's
   cpu_vp_head gloo ranks on CPU: the vocabulary-parallel loss head equals the unsharded head (loss, dH, dW)
+  cpu_rank_loss  three gloo ranks, one leaves between steps: the others find out through the heartbeat and leave
   cpu_cli_tp  gloo ranks on CPU: the command-line pipeline with tp_size = 2 stores what a single process stores
   gpu_tp      NVLink ranks: fused all-gather->GEMM and GEMM->reduce-scatter equal NCCL + matmul; the tensor-parallel
               teacher's top-K log-probs equal the single-GPU model's
@@ -185,6 +186,38 @@ def cpu_vp_head():
     dist.destroy_process_group()
 
 
+def cpu_rank_loss():
+    """Rank 2 leaves between steps (no kernel or collective of its own in flight) without marking its record."""
+    import datetime
+    import time
+    from llm_distillery_b200.obs.watchdog import Heartbeat, RankFailure
+    dist.init_process_group("gloo", timeout=datetime.timedelta(seconds=20))
+    rank, world = dist.get_rank(), dist.get_world_size()
+    hb = Heartbeat(os.path.join(sys.argv[2], "hb"), rank, world, interval=0.1, timeout=1.5)
+    x = torch.ones(4)
+    try:
+        for step in range(200):
+            hb.beat(step, "train")
+            hb.check()
+            if rank == 2 and step == 3:
+                os._exit(0)
+            try:
+                dist.all_reduce(x)
+            except RuntimeError as e:      # the collective ended with an error: ask the heartbeat who is gone
+                deadline = time.time() + 5.0
+                while time.time() < deadline and not hb.scan():
+                    time.sleep(0.1)
+                hb.check()
+                raise e
+            time.sleep(0.05)
+        raise AssertionError("the lost rank was never noticed")
+    except RankFailure as e:
+        assert e.ranks == [2], e
+        print(f"SURVIVOR_OK rank {rank}: {e}", flush=True)
+        hb.close("done")
+        os._exit(0)
+
+
 def cpu_cli_tp():
     """The whole pipeline under two gloo ranks with a tensor-parallel teacher (tp_size = 2): what lands in the HDF5
     store equals a single-process collection of the same teacher."""
@@ -288,4 +321,4 @@ def gpu_tp():
 
 if __name__ == "__main__":
     {"cpu_engine": cpu_engine, "gpu_p2p": gpu_p2p, "cpu_tp": cpu_tp, "gpu_tp": gpu_tp, "cpu_cli_tp": cpu_cli_tp,
-     "cpu_vp_head": cpu_vp_head}[sys.argv[1]]()
+     "cpu_vp_head": cpu_vp_head, "cpu_rank_loss": cpu_rank_loss}[sys.argv[1]]()

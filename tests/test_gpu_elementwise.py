@@ -15,7 +15,7 @@ def _cpu(fn, *args, **kw):
     return fn(*conv, **kwc)
 
 
-@pytest.mark.parametrize("rows,h", [(7, 256), (300, 2048), (64, 4096), (33, 8192)])
+@pytest.mark.parametrize("rows,h", [(7, 256), (300, 2048), (5000, 2048), (2500, 1024), (77, 512), (64, 4096), (33, 8192)])
 def test_rmsnorm_fwd_bwd(rows, h):
     torch.manual_seed(0)
     x = torch.randn(rows, h, device=DEV).bfloat16()
