@@ -96,6 +96,70 @@ __global__ void __launch_bounds__(NT) rmsnorm_fwd_kernel(const __nv_bfloat16* __
   }
 }
 
+// 16-byte read-only load that the compiler may not hoist out of a loop (keeps loop-invariant vectors in L1, not in
+// registers).
+__device__ __forceinline__ uint4 ld_nc_v4_nohoist(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+
+// One WARP per row (h = VPL * 256): the row stays in registers, the reduction is a warp shuffle, no block barrier.
+template <int VPL>
+__global__ void __launch_bounds__(128) rmsnorm_fwd_warp_kernel(const __nv_bfloat16* __restrict__ x,
+                                                              const __nv_bfloat16* __restrict__ res,
+                                                              const __nv_bfloat16* __restrict__ w,
+                                                              __nv_bfloat16* __restrict__ y,
+                                                              __nv_bfloat16* __restrict__ hout,
+                                                              float* __restrict__ rstd, int rows, float eps) {
+  constexpr int h = VPL * 256;
+  const int lane = threadIdx.x & 31;
+  const int nwarps = gridDim.x * 4;
+  const uint4* wv = reinterpret_cast<const uint4*>(w);
+  for (int row = blockIdx.x * 4 + (threadIdx.x >> 5); row < rows; row += nwarps) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * h);
+    const uint4* rr = res ? reinterpret_cast<const uint4*>(res + (size_t)row * h) : nullptr;
+    uint4 q[VPL];
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) q[i] = xr[lane + 32 * i];
+    if (rr) {
+      uint4 r[VPL];
+#pragma unroll
+      for (int i = 0; i < VPL; ++i) r[i] = rr[lane + 32 * i];
+#pragma unroll
+      for (int i = 0; i < VPL; ++i) {
+        float a[8], b[8];
+        unpack8(q[i], a);
+        unpack8(r[i], b);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) a[j] += b[j];
+        q[i] = pack8(a);  // the residual stream is stored in bf16: normalise what is stored, not the fp32 sum
+        if (hout) reinterpret_cast<uint4*>(hout + (size_t)row * h)[lane + 32 * i] = q[i];
+      }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      float a[8];
+      unpack8(q[i], a);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += a[j] * a[j];
+    }
+    const float rs = rsqrtf(warp_sum(ss) * (1.f / (float)h) + eps);
+    if (lane == 0 && rstd) rstd[row] = rs;
+    uint4* yr = reinterpret_cast<uint4*>(y + (size_t)row * h);
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      float a[8], w8[8], o[8];
+      unpack8(q[i], a);
+      unpack8(ld_nc_v4_nohoist(wv + lane + 32 * i), w8);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = a[j] * rs * w8[j];
+      yr[lane + 32 * i] = pack8(o);
+    }
+  }
+}
+
 // dx = rstd * (dy*w - xhat * mean(dy*w*xhat)) (+ dres) ; dw partial sums per block in fp32.
 __global__ void __launch_bounds__(NT) rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
                                                         const __nv_bfloat16* __restrict__ x,
@@ -162,14 +226,6 @@ __global__ void __launch_bounds__(NT) rmsnorm_bwd_kernel(const __nv_bfloat16* __
       *reinterpret_cast<float4*>(p + 4) = make_float4(dwacc[i][4], dwacc[i][5], dwacc[i][6], dwacc[i][7]);
     }
   }
-}
-
-// 16-byte read-only load that the compiler may not hoist out of a loop (keeps loop-invariant vectors in L1, not in
-// registers).
-__device__ __forceinline__ uint4 ld_nc_v4_nohoist(const uint4* p) {
-  uint4 v;
-  asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-  return v;
 }
 
 // Second read of a vector this thread loaded a moment ago (volatile: the compiler may not merge it with the first).
@@ -283,31 +339,36 @@ __global__ void __launch_bounds__(256) colsum_kernel(const float* __restrict__ p
 __global__ void rope_kernel(__nv_bfloat16* __restrict__ x, const int* __restrict__ pos, const float* __restrict__ cs,
                             const float* __restrict__ sn, long long T, int nh, int d, long long row_stride,
                             float sign) {
+  // one thread rotates 8 pairs: a 16-byte vector from each half of the head
   const int half = d >> 1;
-  const int pairs_per_tok = nh * (half >> 1);  // two pairs per thread (bf16x2 on each half)
-  const long long total = T * pairs_per_tok;
+  const int vecs_per_head = half >> 3;
+  const int vecs_per_tok = nh * vecs_per_head;
+  const long long total = T * vecs_per_tok;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
-    const long long t = i / pairs_per_tok;
-    const int r = (int)(i - t * pairs_per_tok);
-    const int hd = r / (half >> 1);
-    const int j = (r - hd * (half >> 1)) * 2;
+    const long long t = i / vecs_per_tok;
+    const int r = (int)(i - t * vecs_per_tok);
+    const int hd = r / vecs_per_head;
+    const int j = (r - hd * vecs_per_head) * 8;
     const int p = pos[t];
     __nv_bfloat16* base = x + t * row_stride + (long long)hd * d;
-    __nv_bfloat162 a = *reinterpret_cast<__nv_bfloat162*>(base + j);
-    __nv_bfloat162 b = *reinterpret_cast<__nv_bfloat162*>(base + j + half);
-    const float2 c = *reinterpret_cast<const float2*>(cs + (size_t)p * half + j);
-    float2 s = *reinterpret_cast<const float2*>(sn + (size_t)p * half + j);
-    s.x *= sign;
-    s.y *= sign;
-    const float2 fa = __bfloat1622float2(a), fb = __bfloat1622float2(b);
-    float2 oa, ob;
-    oa.x = fa.x * c.x - fb.x * s.x;
-    oa.y = fa.y * c.y - fb.y * s.y;
-    ob.x = fb.x * c.x + fa.x * s.x;
-    ob.y = fb.y * c.y + fa.y * s.y;
-    *reinterpret_cast<__nv_bfloat162*>(base + j) = __floats2bfloat162_rn(oa.x, oa.y);
-    *reinterpret_cast<__nv_bfloat162*>(base + j + half) = __floats2bfloat162_rn(ob.x, ob.y);
+    float fa[8], fb[8], oa[8], ob[8];
+    unpack8(*reinterpret_cast<const uint4*>(base + j), fa);
+    unpack8(*reinterpret_cast<const uint4*>(base + j + half), fb);
+    const float4 c0 = *reinterpret_cast<const float4*>(cs + (size_t)p * half + j);
+    const float4 c1 = *reinterpret_cast<const float4*>(cs + (size_t)p * half + j + 4);
+    const float4 s0 = *reinterpret_cast<const float4*>(sn + (size_t)p * half + j);
+    const float4 s1 = *reinterpret_cast<const float4*>(sn + (size_t)p * half + j + 4);
+    const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    const float sg[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float sk = sg[k] * sign;
+      oa[k] = fa[k] * c[k] - fb[k] * sk;
+      ob[k] = fb[k] * c[k] + fa[k] * sk;
+    }
+    *reinterpret_cast<uint4*>(base + j) = pack8(oa);
+    *reinterpret_cast<uint4*>(base + j + half) = pack8(ob);
   }
 }
 
@@ -325,7 +386,7 @@ __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfl
     unpack8(row[v], g);
     unpack8(row[fv + v], u);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) o[j] = g[j] / (1.f + __expf(-g[j])) * u[j];
+    for (int j = 0; j < 8; ++j) o[j] = __fdividef(g[j], 1.f + __expf(-g[j])) * u[j];
     reinterpret_cast<uint4*>(act + t * f)[v] = pack8(o);
   }
 }
@@ -346,7 +407,7 @@ __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gu, const __
     unpack8(reinterpret_cast<const uint4*>(dact + t * f)[v], d);
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      const float sg = 1.f / (1.f + __expf(-g[j]));
+      const float sg = __fdividef(1.f, 1.f + __expf(-g[j]));
       const float silu = g[j] * sg;
       dg[j] = d[j] * u[j] * (sg + silu * (1.f - sg));
       du[j] = d[j] * silu;
@@ -468,8 +529,19 @@ int b200_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, voi
                      float eps, cudaStream_t st) {
   if (!x || !w || !y || rows <= 0 || (h & 7) || h > NT * MAX_VEC * 8) return B200_ERR_ARG;
   const int grid = rows < sm_count() * 8 ? rows : sm_count() * 8;
-  rmsnorm_fwd_kernel<<<grid, NT, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)res, (const __nv_bfloat16*)w,
-                                          (__nv_bfloat16*)y, (__nv_bfloat16*)hout, rstd, rows, h, eps);
+  const int wblocks = ceil_div(rows, 4) < sm_count() * 5 ? ceil_div(rows, 4) : sm_count() * 5;  // 4 rows per 128-thread CTA
+#define B200_RMS_FWD_WARP(VPL)                                                                                        \
+  rmsnorm_fwd_warp_kernel<VPL><<<wblocks, 128, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)res,            \
+                                                        (const __nv_bfloat16*)w, (__nv_bfloat16*)y,                   \
+                                                        (__nv_bfloat16*)hout, rstd, rows, eps)
+  if (h == 2048) B200_RMS_FWD_WARP(8);
+  else if (h == 1024) B200_RMS_FWD_WARP(4);
+  else if (h == 512) B200_RMS_FWD_WARP(2);
+  else if (h == 256) B200_RMS_FWD_WARP(1);
+  else
+    rmsnorm_fwd_kernel<<<grid, NT, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)res, (const __nv_bfloat16*)w,
+                                            (__nv_bfloat16*)y, (__nv_bfloat16*)hout, rstd, rows, h, eps);
+#undef B200_RMS_FWD_WARP
   B200_CUDA_CHECK(cudaGetLastError());
   return B200_OK;
 }
@@ -500,8 +572,8 @@ int b200_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* 
 
 int b200_rope(void* x, const int* pos, const float* cos_tab, const float* sin_tab, long long T, int nh, int d,
               long long row_stride, int inverse, cudaStream_t st) {
-  if (!x || !pos || !cos_tab || !sin_tab || T <= 0 || (d & 3)) return B200_ERR_ARG;
-  const long long total = T * nh * (d >> 2);
+  if (!x || !pos || !cos_tab || !sin_tab || T <= 0 || (d & 15) || (row_stride & 7)) return B200_ERR_ARG;
+  const long long total = T * nh * (d >> 4);
   rope_kernel<<<grid_for(total, 256), 256, 0, st>>>((__nv_bfloat16*)x, pos, cos_tab, sin_tab, T, nh, d, row_stride,
                                                    inverse ? -1.f : 1.f);
   B200_CUDA_CHECK(cudaGetLastError());
