@@ -51,3 +51,34 @@ class BaselineRunner:
 
     def e2e_step(self, hb):
         return self._step(hb.to_device(self.device))
+
+    # ---- collection, restating classes/teacher/inference_worker.py:66-85 and result_processor_worker.py:27-58:
+    # full forward, crop + .float(), log_softmax over the vocabulary, torch.topk, everything to the host, content
+    # rows selected on the CPU
+    def collect_setup(self):
+        m = self.model.module if hasattr(self.model, "module") else self.model
+        m.eval()
+        self._teacher = m
+
+    @torch.no_grad()
+    def collect_step(self, tokens_np, convos):
+        import numpy as np
+        topk = int(getattr(self, "collect_topk", 200))
+        ids = torch.from_numpy(tokens_np).to(self.device)
+        B, L = ids.shape
+        # one sequence at a time keeps the fp32 log-softmax of this arm at the size the reference itself handles
+        vals, idx = [], []
+        for b in range(B):
+            logits = self._teacher(ids[b:b + 1]).logits[:, :, : self.vocab].float()
+            lp = F.log_softmax(logits, dim=-1)
+            v, i = torch.topk(lp, topk, dim=-1)
+            vals.append(v[0].to("cpu").numpy())
+            idx.append(i[0].to("cpu").numpy())
+        rows_v, rows_i = [], []
+        for b, c in enumerate(convos):
+            ci = c.content_indices()
+            rows_v.append(vals[b][ci].astype(np.float16))
+            rows_i.append(idx[b][ci])
+        hv = torch.from_numpy(np.concatenate(rows_v))
+        hi = torch.from_numpy(np.concatenate(rows_i).astype(np.int32))
+        return hv, hi, [len(c.content_indices()) for c in convos]

@@ -45,6 +45,7 @@ def parse_args():
     ap.add_argument("--loss", type=str, default="kl")
     ap.add_argument("--comm", type=str, default="p2p", choices=["p2p", "nccl"])
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--skip-collect", action="store_true")
     return ap.parse_args()
 
 
@@ -167,6 +168,14 @@ def main() -> int:
 
             def to_device(self, hb):
                 return hb.to_device(dev)
+
+            def collect_setup(self):
+                # self-distillation config: the teacher has the student's architecture (weights shared here)
+                from llm_distillery_b200.collect.collector import TeacherCollector
+                self.collector = TeacherCollector(model, topk=K, crop_to_size=cfg.vocab_size)
+
+            def collect_step(self, tokens_np, convos):
+                return self.collector.content_logprobs(tokens_np, convos)
         runner = Runner()
         launches_of = lambda: _lib.LAUNCH_COUNT[0]  # noqa: E731
 
@@ -220,6 +229,41 @@ def main() -> int:
                "d2h_bytes_per_step": 4}
     clocks = sampler.stop() if rank == 0 else None
 
+    # ---------------- teacher collection arm (second half of the metric): tokens in -> top-K rows in pinned host memory
+    collect = None
+    if not args.skip_collect and hasattr(runner, "collect_step"):
+        import numpy as np
+
+        class _Convo:      # every position of every sequence is a content row
+            length = L
+
+            @staticmethod
+            def content_indices():
+                return np.arange(L, dtype=np.int64)
+        convos = [_Convo() for _ in range(B)]
+        toks = [np.random.default_rng(50 + rank + i).integers(0, cfg.vocab_size, (B, L)).astype(np.int64) for i in range(2)]
+        with torch.no_grad():
+            runner.collect_topk = K
+            runner.collect_setup()
+            for i in range(2):
+                runner.collect_step(toks[i % 2], convos)
+            barrier()
+            t0 = time.perf_counter()
+            n_col = max(3, args.steps // 2)
+            d2h = 0
+            for i in range(n_col):
+                hv, hi, _ = runner.collect_step(toks[i % 2], convos)
+                d2h = hv.numel() * hv.element_size() + hi.numel() * hi.element_size()
+            barrier()
+        dt = torch.tensor([time.perf_counter() - t0], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+        collect = {"metric": "teacher collect tokens/s", "value": tokens_per_step * n_col / float(dt.item()),
+                   "unit": "tokens/s", "ms_per_batch": 1e3 * float(dt.item()) / n_col, "batches": n_col,
+                   "h2d_bytes_per_batch": B * L * 8, "d2h_bytes_per_batch": d2h,
+                   "config": {"teacher": args.model, "batch": B, "seq_len": L, "topk": K, "parallelism": f"dp{world}",
+                              "rows": "all positions are content rows"}}
+
     err = 0
     if args.impl == "ours":
         from llm_distillery_b200.ops import _lib
@@ -235,7 +279,7 @@ def main() -> int:
                        "parallelism": f"dp{world}", "loss": f"{args.loss} T={args.temperature}", "topk": K,
                        "optimizer": "adamw (fp32 master + state)", "comm": args.comm if world > 1 else "none",
                        "l2": "no flush: each step streams ~2.2 GB of weights and >20 GB of activations, far above the 126 MB L2"},
-            "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "final_loss": final_loss, "device_error": err,
+            "e2e": e2e, "collect": collect, "gpu_launches": launches, "clocks": clocks, "final_loss": final_loss, "device_error": err,
         }
         print(json.dumps(out))
     if world > 1:
