@@ -23,6 +23,7 @@ from ..loss.head import distill_head_loss
 from ..ops import basic
 from .optim import FlatOptimizer, FlatParams
 from .schedule import LRSchedule
+from ..obs.trace import PhaseTimer
 
 
 @dataclass
@@ -76,6 +77,7 @@ class DistillEngine:
         if comm is not None:
             comm.attach(self.flat, self.opt)
         self.micro_in_step = 0
+        self.timer = PhaseTimer(device=self.device)     # B200_TRACE=1 / B200_NVTX=1: device-timed phases, NVTX ranges
 
     # ---- forward of one micro-batch: (sum over conversations of per-conversation loss, logs)
     def loss_on_batch(self, mb: HostBatch):
@@ -87,9 +89,11 @@ class DistillEngine:
                                  avoid=mb.avoid, seg=mb.seg, n_seg=mb.n_seg, jsd_renorm=self.jsd_renorm)
 
     def micro_step(self, mb: HostBatch):
-        loss, logs = self.loss_on_batch(mb)
-        loss.backward()
-        self.flat.absorb_autograd_grads()
+        with self.timer.phase("forward+loss"):
+            loss, logs = self.loss_on_batch(mb)
+        with self.timer.phase("backward"):
+            loss.backward()
+            self.flat.absorb_autograd_grads()
         self.micro_in_step += 1
         return loss.detach(), logs
 
@@ -102,10 +106,11 @@ class DistillEngine:
         backward (classes/losses.py:77); here that factor rides in the optimizer kernel's gradient scale."""
         self.flat.untouched_to_zero()
         scale = 1.0 / self.grad_accum
-        if self.comm is not None:
-            self.comm.reduce_and_step(self.lr, scale)
-        else:
-            self.opt.step(self.lr, grad_scale=scale)
+        with self.timer.phase("reduce+optimizer"):
+            if self.comm is not None:
+                self.comm.reduce_and_step(self.lr, scale)
+            else:
+                self.opt.step(self.lr, grad_scale=scale)
         self.flat.mark_fresh()
         self.micro_in_step = 0
         if self.schedule is not None:

@@ -275,7 +275,19 @@ class StudentModel(BaseModel):
         lr = self.engine.lr
         self.engine.optimizer_step()
         if self.logger is not None:
-            self.logger.log({"Learning Rate": lr}, self.num_trained_steps)
+            perf = {"Learning Rate": lr}
+            now = time.time()
+            last_t, last_tok = getattr(self, "_perf_mark", (None, 0))
+            if last_t is not None and now > last_t:
+                perf["Perf/train tokens per s"] = (self.tokens_trained - last_tok) * self.world / (now - last_t)
+                perf["Perf/step ms"] = 1e3 * (now - last_t)
+            self._perf_mark = (now, self.tokens_trained)
+            if self.engine.timer.enabled:
+                for k, v in self.engine.timer.summary().items():
+                    perf[f"Perf/{k} ms"] = v
+                if torch.cuda.is_available():
+                    perf["Perf/HBM high-water GB"] = torch.cuda.max_memory_allocated() / 2 ** 30
+            self.logger.log(perf, self.num_trained_steps)
         self.losses.log(self.num_trained_steps)
         self.losses.empty()
         if self.comm is not None and hasattr(self.comm, "check"):
