@@ -95,9 +95,11 @@ def merge_full(disk_logp: np.ndarray, new_logp: np.ndarray) -> np.ndarray:
 
 class H5Store:
     def __init__(self, dataset_path: str, device: str = "cpu", max_queue_size: int = 7, manager_name: str = "",
-                 file_name: str = "distributions.hdf5", writers: int = 4, interactive: bool = False,
+                 file_name: str = "distributions.hdf5", writers: int | None = None, interactive: bool = False,
                  compression_level: int = 6):
         import os
+        if writers is None:      # deflate is the cost of a write (~9 MB/s per core at level 6): use the cores there are
+            writers = min(32, max(4, (os.cpu_count() or 8) // 2))
         self.lib = _bind()
         self.file_path = dataset_path if dataset_path.endswith((".hdf5", ".h5")) else os.path.join(dataset_path, file_name)
         os.makedirs(os.path.dirname(os.path.abspath(self.file_path)), exist_ok=True)
