@@ -6,6 +6,7 @@ present, else the documented fallback of 6.65 TB/s and 1.59 PFLOP/s).
     python bench_kernels.py attn --batch 8 --seq 2048 --heads 32 --kv-heads 4 --dim 64 [--bwd]
     python bench_kernels.py head --rows 16384 --hidden 2048 --vocab 32000 --topk 200
     python bench_kernels.py elementwise --rows 16384 --hidden 2048 --ffn 5632
+    python bench_kernels.py topk --rows 4096 --vocab 32000 --topk 200     (top-K extraction, merge, remap)
     python bench_kernels.py all            (the model shapes of the headline benchmark)
 
 Timing: CUDA events on the launching stream, warm-up first, L2 flushed between timed iterations by writing a
@@ -145,6 +146,38 @@ def bench_elementwise(rows, h, f, iters):
     report("adamw", timed(lambda: opt.step(), iters), bytes_=n * 30, shape=[n])
 
 
+def bench_topk_family(rows, V, K, iters):
+    """Exact top-K log-prob extraction, multi-teacher merge and cross-tokenizer remap against their library / CPU
+    statements (the CPU loops are timed on 256 rows and scaled)."""
+    import time
+    from llm_distillery_b200.ops import topk as tk
+    dev = "cuda"
+    g = torch.Generator(device=dev).manual_seed(0)
+    logits = torch.randn((rows, V), device=dev, generator=g) * 3
+    ms = timed(lambda: tk.topk_logprob(logits, V, K), iters)
+    ms_t = timed(lambda: torch.topk(torch.log_softmax(logits, -1), K, dim=-1), max(3, iters // 2))
+    report("topk_logprob", ms, bytes_=rows * V * 4.0, shape=[rows, V, K], torch_ms=round(ms_t, 4),
+           speedup_vs_torch=round(ms_t / ms, 2), note="torch = log_softmax + topk on the same fp32 logits")
+    a_lp, a_id = tk.topk_logprob(logits, V, K)
+    b_lp, b_id = tk.topk_logprob(logits.roll(1, 0) + 0.5 * torch.randn_like(logits), V, K)
+    a_lp, b_lp = a_lp.float(), b_lp.float()
+    ms = timed(lambda: tk.topk_merge(a_lp, a_id, b_lp, b_id), iters, flush=False)
+    sub = 256
+    ca = [t[:sub].cpu() for t in (a_lp, a_id, b_lp, b_id)]
+    t0 = time.perf_counter()
+    tk.topk_merge(*ca)
+    cpu_ms = (time.perf_counter() - t0) * 1e3 * rows / sub
+    report("topk_merge", ms, bytes_=rows * K * 8.0 * 3, shape=[rows, K], cpu_loop_ms=round(cpu_ms, 1),
+           speedup_vs_cpu_loop=round(cpu_ms / ms, 1), note="CPU = per-row unique + index_add + sort (the reference's merge rule)")
+    table = torch.randint(-1, 32000, (V,), device=dev, generator=g, dtype=torch.int32)
+    ms = timed(lambda: tk.remap_topk(a_lp, a_id, table, K), iters, flush=False)
+    t0 = time.perf_counter()
+    tk.remap_topk(ca[0], ca[1], table.cpu(), K)
+    cpu_ms = (time.perf_counter() - t0) * 1e3 * rows / sub
+    report("remap_topk", ms, bytes_=rows * K * 8.0 * 2, shape=[rows, K, V], cpu_loop_ms=round(cpu_ms, 1),
+           speedup_vs_cpu_loop=round(cpu_ms / ms, 1), note="CPU = per-row table lookup + unique + index_add + sort")
+
+
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -161,8 +194,11 @@ def main():
     e = sub.add_parser("elementwise")
     e.add_argument("--rows", type=int, default=16384); e.add_argument("--hidden", type=int, default=2048)
     e.add_argument("--ffn", type=int, default=5632)
+    t = sub.add_parser("topk")
+    t.add_argument("--rows", type=int, default=4096); t.add_argument("--vocab", type=int, default=32000)
+    t.add_argument("--topk", type=int, default=200)
     sub.add_parser("all")
-    for s in (g, a, h, e, sub.choices["all"]):
+    for s in (g, a, h, e, t, sub.choices["all"]):
         s.add_argument("--iters", type=int, default=20)
     args = ap.parse_args()
     if args.cmd == "gemm":
@@ -173,6 +209,8 @@ def main():
         bench_head(args.rows, args.hidden, args.vocab, args.topk, args.iters)
     elif args.cmd == "elementwise":
         bench_elementwise(args.rows, args.hidden, args.ffn, args.iters)
+    elif args.cmd == "topk":
+        bench_topk_family(args.rows, args.vocab, args.topk, args.iters)
     else:
         for shp, lay in [((8192, 8192, 8192), "nt"), ((16384, 2560, 2048), "nt"), ((16384, 2048, 2048), "nt"),
                          ((16384, 11264, 2048), "nt"), ((16384, 2048, 5632), "nt"), ((16384, 2048, 2560), "nn"),
@@ -183,6 +221,7 @@ def main():
         bench_attn(2, 4096, 32, 8, 128, args.iters, True)
         bench_head(16384, 2048, 32000, 200, max(3, args.iters // 4))
         bench_elementwise(16384, 2048, 5632, args.iters)
+        bench_topk_family(4096, 32000, 200, max(3, args.iters // 2))
 
 
 if __name__ == "__main__":
