@@ -11,9 +11,10 @@
 //
 //   gemm_rs   Y_shard[Ts, N] = reduce_scatter_rows( X[T, K_local] * W[N, K_local]^T ) (+ residual)   (row-parallel: O, down)
 //     The epilogue stores each bf16 partial tile straight into the OWNER rank's staging buffer (slot = this rank);
-//     tiles owned by other ranks come first, so their stores travel while the own tiles are computed. The last
-//     epilogue warp to finish tells every rank "my partials have landed"; then the epilogue warps of all CTAs wait for
-//     every rank's message and sum the `world` staged partials (+ residual) of their shard in fp32.
+//     tiles owned by other ranks come first, so their stores travel while the own tiles are computed. When the grid is
+//     through with one destination's tiles, that destination is told "my partials for you have landed"; after their
+//     last tile the epilogue warps of all CTAs wait for every rank's message and sum the `world` staged partials
+//     (+ residual) of their shard in fp32.
 //
 // Cross-rank flags are epoch numbers that only grow; each wait is bounded (2 s) and reports ERR_WAIT_PEER /
 // ERR_WAIT_AUX through the error word. A kernel here needs all its CTAs resident at once (they wait on one another
@@ -41,6 +42,8 @@ struct TpParams {
   // common
   int rank, world;
   int blocks_per_shard;  // 128-row blocks per rank slab (Ts / 128)
+  int group_m;           // row tiles per L2 tile group: a divisor of the tiles per slab, so that no group spans two
+                         // slabs and every CTA meets the slabs (= destinations, sources) in one monotonic order
   unsigned int epoch;    // this call's number on the flag words it uses
   Peers flags;           // every rank's flag array for this kind of call: flags.p[dst][src] = epoch
   // ag_gemm
@@ -52,7 +55,7 @@ struct TpParams {
   int out_f32;
   // gemm_rs
   Peers stg;                 // every rank's staging buffer [world][Ts][N] bf16
-  unsigned int* done_count;  // local counter of finished epilogue warps, zeroed before the launch
+  unsigned int* done_count;  // local [world] counters of epilogue warps through with each destination, zeroed before the launch
   const __nv_bfloat16* resid;  // [Ts, N] or null
   __nv_bfloat16* out;          // [Ts, N]
 };
@@ -138,22 +141,37 @@ __device__ __forceinline__ void store_tile_f32(uint32_t taddr, float* dst_row, b
   }
 }
 
-// gemm_rs, after a warp's last tile: publish "this rank's partials have landed" once every epilogue warp of the grid
-// is through, wait for every rank's message, then sum the staged partials (+ residual) of the own shard.
-// ew = epilogue warp index 0..3.
-__device__ __forceinline__ void rs_tail(const TpParams& p, int N, bool ok_all, int ew, int lane,
-                                        volatile int* abort_flag, unsigned int* err_word) {
-  const long long Ts = (long long)p.blocks_per_shard * BM;
+// gemm_rs signalling. The tile loop visits the destinations in phases: phase ph holds the tiles owned by rank
+// (rank + 1 + ph) % world, the own tiles come last. When a warp has moved past its tiles of a phase (stores fenced at
+// system scope) it counts itself on that destination's counter; the last of the grid's epilogue warps tells the
+// destination "rank `rank`'s partials for you have landed". A destination therefore hears from a source as soon as
+// that source is through with ITS rows, not when the source's whole GEMM is over.
+__device__ __forceinline__ void rs_signal_phases(const TpParams& p, int from_phase, int to_phase, int lane) {
+  if (to_phase <= from_phase) return;
   __threadfence_system();
   __syncwarp();
   if (lane == 0) {
-    const unsigned int old = atomicAdd(p.done_count, 1u);
-    if (old + 1u == gridDim.x * NUM_EPI_WARPS) {
-      __threadfence_system();
-      for (int q = 0; q < p.world; ++q)
-        comm::st_release_sys(reinterpret_cast<unsigned int*>(p.flags.p[q]) + p.rank, p.epoch);
+    for (int ph = from_phase; ph < to_phase; ++ph) {
+      const int dest = (p.rank + 1 + ph) % p.world;
+      const unsigned int old = atomicAdd(p.done_count + dest, 1u);
+      if (old + 1u == gridDim.x * NUM_EPI_WARPS) {
+        __threadfence_system();
+        comm::st_release_sys(reinterpret_cast<unsigned int*>(p.flags.p[dest]) + p.rank, p.epoch);
+      }
     }
   }
+  __syncwarp();
+}
+__device__ __forceinline__ int rs_phase_of(const TpParams& p, int owner) {
+  return (owner - p.rank - 1 + 2 * p.world) % p.world;
+}
+
+// gemm_rs, after a warp's last tile: signal the phases not yet signalled, wait for every rank's message to this rank,
+// then sum the staged partials (+ residual) of the own shard. ew = epilogue warp index 0..3.
+__device__ __forceinline__ void rs_tail(const TpParams& p, int N, bool ok_all, int phases_signalled, int ew, int lane,
+                                        volatile int* abort_flag, unsigned int* err_word) {
+  const long long Ts = (long long)p.blocks_per_shard * BM;
+  rs_signal_phases(p, phases_signalled, p.world, lane);
   int okw = 1;
   if (ok_all && lane < p.world)
     okw = comm::wait_reached_bounded<true>(reinterpret_cast<const unsigned int*>(p.flags.p[p.rank]) + lane, p.epoch,
@@ -165,7 +183,7 @@ __device__ __forceinline__ void rs_tail(const TpParams& p, int N, bool ok_all, i
   const uint4* rs = reinterpret_cast<const uint4*>(p.resid);
   uint4* out = reinterpret_cast<uint4*>(p.out);
   const long long step = (long long)gridDim.x * (NUM_EPI_WARPS * 32);
-  constexpr int U = 4;  // independent 16-byte streams per thread: enough loads in flight to fill HBM
+  constexpr int U = 8;  // independent 16-byte streams per thread: ~64 KB in flight per SM is what HBM latency needs
   for (long long i0 = (long long)blockIdx.x * (NUM_EPI_WARPS * 32) + ew * 32 + lane; i0 < nvec; i0 += U * step) {
     float a[U][8];
 #pragma unroll
@@ -223,15 +241,16 @@ __device__ __forceinline__ void ag_copy_warps(const TpParams& p, int ct, int lan
     for (int b = 0; b < bps; ++b) {
       const int m_blk = src * bps + b;
       const long long off = (long long)m_blk * blk_vecs;
-      long long i = (long long)blockIdx.x * (COPY_WARPS * 32) + ct;
-      for (; i + (COPY_UNROLL - 1) * step < blk_vecs; i += COPY_UNROLL * step) {
+      // every thread keeps COPY_UNROLL peer loads in flight (predicated at the block's end), then stores them
+      for (long long i0 = (long long)blockIdx.x * (COPY_WARPS * 32) + ct; i0 < blk_vecs; i0 += COPY_UNROLL * step) {
         uint4 v[COPY_UNROLL];
 #pragma unroll
-        for (int u = 0; u < COPY_UNROLL; ++u) v[u] = ld_peer_v4(src_base + off + i + u * step);
+        for (int u = 0; u < COPY_UNROLL; ++u)
+          if (i0 + u * step < blk_vecs) v[u] = ld_peer_v4(src_base + off + i0 + u * step);
 #pragma unroll
-        for (int u = 0; u < COPY_UNROLL; ++u) dst_base[off + i + u * step] = v[u];
+        for (int u = 0; u < COPY_UNROLL; ++u)
+          if (i0 + u * step < blk_vecs) dst_base[off + i0 + u * step] = v[u];
       }
-      for (; i < blk_vecs; i += step) dst_base[off + i] = ld_peer_v4(src_base + off + i);
       fence_proxy_async_all();
       __threadfence();
       __syncwarp();
@@ -303,7 +322,7 @@ __global__ void __launch_bounds__(MODE == MODE_AG ? AG_THREADS : RS_THREADS, 1)
   const uint32_t tmem_base = *tmem_slot;
 
   TileMap tm;
-  tm.init(M, N, TBN, p.blocks_per_shard < 16 ? p.blocks_per_shard : 16);
+  tm.init(M, N, TBN, p.group_m);
   const int num_kb = (K + BK - 1) / BK;
   const int bps = p.blocks_per_shard;
   // logical row-block order: ag_gemm starts with the own slab; gemm_rs ends with it
@@ -378,6 +397,7 @@ __global__ void __launch_bounds__(MODE == MODE_AG ? AG_THREADS : RS_THREADS, 1)
     const int quad = warp & 3;
     uint32_t tl = 0;
     bool ok_all = true;
+    int phases_signalled = 0;
     for (int tile = blockIdx.x; tile < tm.num_tiles; tile += gridDim.x, ++tl) {
       int lm, n_blk;
       tm.get(tile, lm, n_blk);
@@ -391,6 +411,11 @@ __global__ void __launch_bounds__(MODE == MODE_AG ? AG_THREADS : RS_THREADS, 1)
         break;
       }
       tc_fence_after_sync();
+      if (MODE == MODE_RS) {
+        const int ph = rs_phase_of(p, m_blk / bps);
+        rs_signal_phases(p, phases_signalled, ph, lane);
+        phases_signalled = max(phases_signalled, ph);
+      }
       const uint32_t taddr = tmem_base + acc * TBN + (static_cast<uint32_t>(quad * 32) << 16);
       epilogue_slice<MODE>(p, taddr, epi_smem + (warp - 2) * EPI_STAGE_BYTES, m_blk * BM + quad * 32, n_blk * TBN, M, N,
                            lane);
@@ -398,7 +423,7 @@ __global__ void __launch_bounds__(MODE == MODE_AG ? AG_THREADS : RS_THREADS, 1)
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[acc]);
     }
-    if (MODE == MODE_RS) rs_tail(p, N, ok_all, warp - 2, lane, abort_flag, err_word);
+    if (MODE == MODE_RS) rs_tail(p, N, ok_all, phases_signalled, warp - 2, lane, abort_flag, err_word);
   } else {
     // ------------------------------------------------------------ copy warps (ag_gemm only)
     if (MODE == MODE_AG) ag_copy_warps(p, threadIdx.x - (2 + NUM_EPI_WARPS) * 32, lane, abort_flag, err_word);
@@ -475,7 +500,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(MODE == MODE_AG ? AG
   const int pair_id = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
   const int bps2 = p.blocks_per_shard / 2;  // 256-row tiles per slab
-  const int group_m = bps2 < 8 ? bps2 : 8;
+  const int group_m = p.group_m;
   const int rot = (MODE == MODE_AG ? p.rank : (p.rank + 1) % p.world) * bps2;
   auto tile_coords = [&](int tile, int& m_blk, int& n_blk) {
     const int per_group = group_m * n_tiles;
@@ -560,6 +585,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(MODE == MODE_AG ? AG
     const uint32_t leader_tempty0 = mapa_shared(smem_u32(&tempty_bar[0]), 0);
     uint32_t tl = 0;
     bool ok_all = true;
+    int phases_signalled = 0;
     for (int tile = pair_id; tile < num_tiles; tile += num_pairs, ++tl) {
       int m_blk, n_blk;
       tile_coords(tile, m_blk, n_blk);
@@ -572,6 +598,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(MODE == MODE_AG ? AG
         break;
       }
       tc_fence_after_sync();
+      if (MODE == MODE_RS) {
+        const int ph = rs_phase_of(p, m_blk / bps2);
+        rs_signal_phases(p, phases_signalled, ph, lane);
+        phases_signalled = max(phases_signalled, ph);
+      }
       const uint32_t taddr = tmem_base + acc * PAIR_BN + (static_cast<uint32_t>(quad * 32) << 16);
       epilogue_slice<MODE>(p, taddr, epi_smem + (warp - 2) * EPI_STAGE_BYTES,
                            m_blk * PAIR_BM + (int)cta * BM + quad * 32, n_blk * PAIR_BN, M, N, lane);
@@ -579,7 +610,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(MODE == MODE_AG ? AG
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(leader_tempty0 + acc * 8);
     }
-    if (MODE == MODE_RS) rs_tail(p, N, ok_all, warp - 2, lane, abort_flag, err_word);
+    if (MODE == MODE_RS) rs_tail(p, N, ok_all, phases_signalled, warp - 2, lane, abort_flag, err_word);
   } else {
     // ------------------------------------------------------------ copy warps (ag_gemm only)
     if (MODE == MODE_AG) ag_copy_warps(p, threadIdx.x - (2 + NUM_EPI_WARPS) * 32, lane, abort_flag, err_word);
@@ -627,7 +658,7 @@ static int pair_mode() {
 }
 
 template <int MODE>
-int launch(const void* A, long long lda, const void* W, long long ldw, int T, int N, int K, const TpParams& p,
+int launch(const void* A, long long lda, const void* W, long long ldw, int T, int N, int K, const TpParams& p_in,
            cudaStream_t stream) {
   CUtensorMap tmA, tmB;
   int rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)K, (uint64_t)T, (uint64_t)lda * 2,
@@ -637,8 +668,16 @@ int launch(const void* A, long long lda, const void* W, long long ldw, int T, in
   const int epi_bytes = gemm::NUM_EPI_WARPS * EPI_STAGE_BYTES;
   // CTA pairs when every slab is whole 256-row tiles and there are enough tiles for all SM pairs
   const long long ptiles = (long long)(T / gemm::PAIR_BM) * ceil_div(N, gemm::PAIR_BN);
-  const bool pair = pair_mode() != 0 && (p.blocks_per_shard % 2 == 0) && N > 128 &&
+  const bool pair = pair_mode() != 0 && (p_in.blocks_per_shard % 2 == 0) && N > 128 &&
                     (pair_mode() == 1 || ptiles >= sm_count() / 2);
+  TpParams p = p_in;
+  {
+    const int per_slab = pair ? p.blocks_per_shard / 2 : p.blocks_per_shard;
+    const int cap = pair ? 8 : 16;
+    int g = per_slab < cap ? per_slab : cap;
+    while (per_slab % g) --g;
+    p.group_m = g;
+  }
   if (pair) {
     using S = gemm::SmemPair<PSTAGES>;
     rc = make_tmap_2d(&tmB, W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)K, (uint64_t)N, (uint64_t)ldw * 2,
@@ -711,7 +750,7 @@ int b200_tp_ag_gemm(const void* const* xf_ptrs, const void* const* flag_ptrs, co
 
 // Row-parallel linear with the reduce-scatter inside: out[T/world, N] = rows of this rank of
 // sum over ranks ( X[T, K] * W[N, K]^T ) + residual. stg_ptrs[q] = rank q's staging buffer [world][T/world][N] bf16;
-// flag_ptrs[q] = rank q's flag array reserved for gemm_rs calls; done_count: one word of scratch.
+// flag_ptrs[q] = rank q's flag array reserved for gemm_rs calls; done_count: `world` words of scratch.
 // Alternate between two staging buffers on consecutive calls.
 int b200_tp_gemm_rs(const void* X, long long ldx, const void* W, const void* const* stg_ptrs,
                     const void* const* flag_ptrs, const void* residual, void* out, unsigned int* done_count, int T,
@@ -732,7 +771,7 @@ int b200_tp_gemm_rs(const void* X, long long ldx, const void* W, const void* con
   p.done_count = done_count;
   p.resid = reinterpret_cast<const __nv_bfloat16*>(residual);
   p.out = reinterpret_cast<__nv_bfloat16*>(out);
-  B200_CUDA_CHECK(cudaMemsetAsync(done_count, 0, sizeof(unsigned int), stream));
+  B200_CUDA_CHECK(cudaMemsetAsync(done_count, 0, sizeof(unsigned int) * world, stream));
   return launch<MODE_RS>(X, ldx, W, K, T, N, K, p, stream);
 }
 }

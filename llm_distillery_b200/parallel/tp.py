@@ -70,7 +70,7 @@ class TPGroup:
         self.rs_flags = SymmetricBuffer(64, torch.int32, self.device, self.group)
         self.sig = SymmetricBuffer(64, torch.int32, self.device, self.group)
         self.blk_count = torch.zeros(self.max_tokens // ROW_BLOCK, dtype=torch.int32, device=self.device)
-        self.done_count = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.done_count = torch.zeros(16, dtype=torch.int32, device=self.device)
         if topk:
             w, t, k = self.world, self.max_tokens, topk
             self.cand_z = SymmetricBuffer(w * t * k, torch.float32, self.device, self.group)
