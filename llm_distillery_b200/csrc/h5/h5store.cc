@@ -171,7 +171,9 @@ struct Store {
   }
 
   // -------- one chunked+deflated dataset (single chunk). `comp` is the already-deflated payload.
-  uint64_t write_dataset(uint64_t rows, uint64_t cols, int elem, bool is_f16, const std::vector<uint8_t>& comp) {
+  // `shuffled`: the payload was byte-shuffled (HDF5 filter 2) before deflate; the filter pipeline message says so.
+  uint64_t write_dataset(uint64_t rows, uint64_t cols, int elem, bool is_f16, const std::vector<uint8_t>& comp,
+                         bool shuffled = false, int level = 6) {
     uint64_t chunk_addr = append(comp.data(), comp.size());
     if (chunk_addr == UNDEF) return UNDEF;
     // chunk B-tree: one leaf node with one entry
@@ -190,7 +192,9 @@ struct Store {
     { Buf m; ds_simple(m, {rows, cols}); add_msg(ms, 0x0001, m); }
     { Buf m; if (is_f16) dt_f16(m); else dt_uint(m, elem, false); add_msg(ms, 0x0003, m); }
     { Buf m; m.u8(2); m.u8(3); m.u8(2); m.u8(0); add_msg(ms, 0x0005, m); }
-    { Buf m; m.u8(1); m.u8(1); m.zeros(6); m.u16(1); m.u16(0); m.u16(1); m.u16(1); m.u32(6); m.u32(0);
+    { Buf m; m.u8(1); m.u8(shuffled ? 2 : 1); m.zeros(6);
+      if (shuffled) { m.u16(2); m.u16(0); m.u16(1); m.u16(1); m.u32((uint32_t)elem); m.u32(0); }   // shuffle(elem size)
+      m.u16(1); m.u16(0); m.u16(1); m.u16(1); m.u32((uint32_t)level); m.u32(0);                      // deflate(level)
       add_msg(ms, 0x000B, m); }
     { Buf m; m.u8(3); m.u8(2); m.u8(rank1); m.u64(tree_addr); m.u32((uint32_t)rows); m.u32((uint32_t)cols);
       m.u32((uint32_t)elem); add_msg(ms, 0x0008, m); }
@@ -632,6 +636,17 @@ struct Store {
   }
 };
 
+// Byte shuffle (HDF5 filter 2): all first bytes of the elements, then all second bytes, ... Slowly varying high
+// bytes (sorted fp16 log-probs, token ids below 2^17) then form long runs, which deflate packs better and faster.
+void shuffle_bytes(const uint8_t* src, size_t n_elem, int elem, std::vector<uint8_t>& out) {
+  out.resize(n_elem * (size_t)elem);
+  for (int b = 0; b < elem; ++b) {
+    uint8_t* d = out.data() + (size_t)b * n_elem;
+    const uint8_t* sp = src + b;
+    for (size_t i = 0; i < n_elem; ++i) d[i] = sp[i * (size_t)elem];
+  }
+}
+
 bool deflate_buf(const void* src, size_t n, int level, std::vector<uint8_t>& out) {
   uLongf cap = compressBound((uLong)n);
   out.resize(cap);
@@ -673,14 +688,30 @@ int h5s_put(void* h, long long id, const void* values_f16, const void* indices_u
             const char* sha, const char* sample, int level) {
   Store* s = (Store*)h;
   if (rows < 0 || cols <= 0 || !values_f16) return -1;
-  std::vector<uint8_t> cv, ci;
-  if (!deflate_buf(values_f16, (size_t)rows * cols * 2, level, cv)) return -1;
-  if (indices_u32 && !deflate_buf(indices_u32, (size_t)rows * cols * 4, level, ci)) return -1;
+  // level: deflate level in the low byte; bit 8 set = byte-shuffle before deflate
+  const bool shuf = (level & 0x100) != 0;
+  level &= 0xff;
+  std::vector<uint8_t> cv, ci, tmp;
+  const size_t n = (size_t)rows * cols;
+  if (shuf) {
+    shuffle_bytes((const uint8_t*)values_f16, n, 2, tmp);
+    if (!deflate_buf(tmp.data(), n * 2, level, cv)) return -1;
+    if (indices_u32) {
+      shuffle_bytes((const uint8_t*)indices_u32, n, 4, tmp);
+      if (!deflate_buf(tmp.data(), n * 4, level, ci)) return -1;
+    }
+  } else {
+    if (!deflate_buf(values_f16, n * 2, level, cv)) return -1;
+    if (indices_u32 && !deflate_buf(indices_u32, n * 4, level, ci)) return -1;
+  }
   std::lock_guard<std::mutex> lk(s->mu);
-  uint64_t dh = s->write_dataset((uint64_t)rows, (uint64_t)cols, 2, true, cv);
+  uint64_t dh = s->write_dataset((uint64_t)rows, (uint64_t)cols, 2, true, cv, shuf, level);
   if (dh == UNDEF) return -1;
   uint64_t ih = UNDEF;
-  if (indices_u32) { ih = s->write_dataset((uint64_t)rows, (uint64_t)cols, 4, false, ci); if (ih == UNDEF) return -1; }
+  if (indices_u32) {
+    ih = s->write_dataset((uint64_t)rows, (uint64_t)cols, 4, false, ci, shuf, level);
+    if (ih == UNDEF) return -1;
+  }
   return s->put_group(convo_name(id), dh, ih, sha ? sha : "", sample ? sample : "") ? 0 : -1;
 }
 

@@ -96,7 +96,10 @@ def merge_full(disk_logp: np.ndarray, new_logp: np.ndarray) -> np.ndarray:
 class H5Store:
     def __init__(self, dataset_path: str, device: str = "cpu", max_queue_size: int = 7, manager_name: str = "",
                  file_name: str = "distributions.hdf5", writers: int | None = None, interactive: bool = False,
-                 compression_level: int = 6):
+                 compression_level: int = 6, shuffle: bool = True):
+        """``shuffle``: put the HDF5 byte-shuffle filter in front of deflate for newly written datasets (read back
+        transparently by this store and by h5py). The reference writes plain gzip-6 (classes/data_manager.py:300-309);
+        ``shuffle=False`` reproduces that byte for byte in the filter pipeline."""
         import os
         if writers is None:      # deflate is the cost of a write (~9 MB/s per core at level 6): use the cores there are
             writers = min(32, max(4, (os.cpu_count() or 8) // 2))
@@ -110,7 +113,7 @@ class H5Store:
         self.device = device
         self.manager_name = manager_name + " " if manager_name else manager_name
         self.interactive = interactive
-        self.level = compression_level
+        self.level = int(compression_level) | (0x100 if shuffle else 0)
         self.max_queue_size = max_queue_size
         self._pool = ThreadPoolExecutor(max_workers=writers, thread_name_prefix="h5w")
         self._pending: list = []

@@ -121,6 +121,7 @@ class SpecReader:
         dims = dtype = None
         layout = None
         deflate = False
+        shuffle = 0
         for t, body in self.messages(hdr):
             if t == 1:
                 assert body[0] == 1
@@ -142,10 +143,19 @@ class SpecReader:
                 cd = struct.unpack_from("<%dI" % rank1, body, 11)
                 layout = (bt, cd)
             elif t == 0x0B:
-                assert body[0] == 1 and body[1] == 1
-                fid, nlen, flags, ncd = struct.unpack_from("<HHHH", body, 8)
-                assert fid == 1 and ncd == 1
-                deflate = True
+                assert body[0] == 1 and body[1] in (1, 2)
+                p = 8
+                for _ in range(body[1]):            # filters in the order they are applied on write
+                    fid, nlen, flags, ncd = struct.unpack_from("<HHHH", body, p)
+                    assert nlen == 0 and ncd == 1
+                    val = struct.unpack_from("<I", body, p + 8)[0]
+                    p += 16                         # header 8 + one client value 4 + padding 4
+                    if fid == 2:
+                        assert not deflate, "shuffle comes before deflate"
+                        shuffle = val               # element size
+                    else:
+                        assert fid == 1
+                        deflate = True
         bt, cd = layout
         assert cd[:2] == tuple(dims) and cd[2] == np.dtype(dtype).itemsize and deflate
         assert self.b[bt:bt + 4] == b"TREE" and self.b[bt + 4] == 1 and self.b[bt + 5] == 0
@@ -154,4 +164,8 @@ class SpecReader:
         csize, mask, o0, o1, o2, child = struct.unpack_from("<IIQQQQ", self.b, bt + 24)
         assert (mask, o0, o1, o2) == (0, 0, 0, 0)
         raw = zlib.decompress(self.b[child:child + csize])
+        if shuffle:
+            assert shuffle == np.dtype(dtype).itemsize
+            n = len(raw) // shuffle
+            raw = np.frombuffer(raw, dtype=np.uint8).reshape(shuffle, n).T.tobytes()
         return np.frombuffer(raw, dtype=dtype).reshape(dims)

@@ -19,8 +19,9 @@ def _rows(cid, n=37, K=16, V=500, seed=0, sample="s"):
     return TeacherRows(cid, np.take_along_axis(lp, idx, 1), idx.astype(np.int64), f"sha{cid:04d}" * 8, f"{sample}-{cid} é")
 
 
-def test_roundtrip_reopen_and_spec_reader(tmp_path):
-    st = H5Store(str(tmp_path))
+@pytest.mark.parametrize("shuffle", [True, False])
+def test_roundtrip_reopen_and_spec_reader(tmp_path, shuffle):
+    st = H5Store(str(tmp_path), shuffle=shuffle)
     data = {i: _rows(i, n=5 + 3 * i) for i in [0, 1, 2, 10, 33, 7]}
     st.write_batch(list(data.values()))
     st.set_vocab_family("llama_3")
