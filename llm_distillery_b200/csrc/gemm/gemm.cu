@@ -23,10 +23,82 @@ struct StoreParams {
 template <int BN>
 struct EpiStore {
   using Params = StoreParams;
-  static constexpr int SMEM_BYTES = 0;
+  static constexpr int STAGE_BYTES = 32 * 256;              // per epilogue warp: 32 rows x 128 bf16 columns
+  static constexpr int SMEM_BYTES = NUM_EPI_WARPS * STAGE_BYTES;
+
+  // bf16 output without accumulation (forward and dgrad GEMMs): the warp's 32 x 128 slice goes through a swizzled
+  // shared-memory stage so that each store instruction writes two whole 256-byte row segments instead of 32
+  // scattered 16-byte pieces. alpha and the residual are applied in fp32 before the rounding to bf16.
+  static __device__ __forceinline__ void tile_staged(const Params& p, uint32_t taddr, int m0, int n0, int M, int N,
+                                                     int quad, int lane, uint8_t* epi_smem) {
+    uint8_t* stage = epi_smem + quad * STAGE_BYTES;
+    const int row0 = m0 + quad * 32;
+    const int rows_valid = min(32, M - row0);
+    const bool my_row_ok = lane < rows_valid;
+    __nv_bfloat16* C = reinterpret_cast<__nv_bfloat16*>(p.C);
+#pragma unroll 1
+    for (int half = 0; half < BN / 128; ++half) {
+#pragma unroll 1
+      for (int c4 = 0; c4 < 4; ++c4) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(taddr + half * 128 + c4 * 32, r);
+        tmem_ld_wait();
+        const int col0 = n0 + half * 128 + c4 * 32;
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+        if (p.resid && my_row_ok && col0 < N) {
+          const __nv_bfloat16* rp = p.resid + (long long)(row0 + lane) * p.ldr + col0;
+          if (col0 + 32 <= N && ((reinterpret_cast<uintptr_t>(rp) & 15) == 0)) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint4 q = *reinterpret_cast<const uint4*>(rp + j * 8);
+              const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+              for (int t = 0; t < 4; ++t) {
+                const float2 f = __bfloat1622float2(h[t]);
+                v[j * 8 + t * 2] += f.x;
+                v[j * 8 + t * 2 + 1] += f.y;
+              }
+            }
+          } else {
+            const int ncols = min(32, N - col0);
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (j < ncols) v[j] += __bfloat162float(rp[j]);
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint4 o;
+          o.x = pack_bf16x2(v[j * 8 + 0], v[j * 8 + 1]);
+          o.y = pack_bf16x2(v[j * 8 + 2], v[j * 8 + 3]);
+          o.z = pack_bf16x2(v[j * 8 + 4], v[j * 8 + 5]);
+          o.w = pack_bf16x2(v[j * 8 + 6], v[j * 8 + 7]);
+          const int chunk = c4 * 4 + j;
+          *reinterpret_cast<uint4*>(stage + lane * 256 + ((chunk ^ (lane & 15)) << 4)) = o;
+        }
+      }
+      __syncwarp();
+      const int chunk = lane & 15;
+      const int col = n0 + half * 128 + chunk * 8;
+#pragma unroll 4
+      for (int j = 0; j < 16; ++j) {
+        const int row = 2 * j + (lane >> 4);
+        const uint4 o = *reinterpret_cast<const uint4*>(stage + row * 256 + ((chunk ^ (row & 15)) << 4));
+        if (row < rows_valid && col < N) *reinterpret_cast<uint4*>(C + (long long)(row0 + row) * p.ldc + col) = o;
+      }
+      __syncwarp();
+    }
+  }
 
   static __device__ __forceinline__ void tile(const Params& p, uint32_t taddr, int m0, int n0, int M, int N, int quad,
-                                              int lane, uint8_t*) {
+                                              int lane, uint8_t* epi_smem) {
+    if (!p.out_f32 && p.fmt == 1 && !p.accumulate && !(N & 7) && !(p.ldc & 7) &&
+        !(reinterpret_cast<uintptr_t>(p.C) & 15)) {
+      tile_staged(p, taddr, m0, n0, M, N, quad, lane, epi_smem);
+      return;
+    }
     const int row = m0 + quad * 32 + lane;
     const bool row_ok = row < M;
 #pragma unroll 1
