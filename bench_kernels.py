@@ -80,11 +80,19 @@ def bench_gemm(M, N, K, layout, iters, compare=True):
     a = torch.randn((K, M) if a_mn else (M, K), device="cuda").bfloat16()
     b = torch.randn((K, N) if b_mn else (N, K), device="cuda").bfloat16()
     out = torch.empty((M, N), device="cuda", dtype=torch.bfloat16)
-    ms = timed(lambda: basic.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=out), iters)
     extra = {}
+    if layout == "tn":
+        # the weight-gradient GEMM as the trainer runs it: fp32 accumulation into the gradient buffer
+        acc = torch.zeros((M, N), device="cuda", dtype=torch.float32)
+        ms = timed(lambda: basic.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=acc, accumulate=True), iters)
+        extra["output"] = "fp32 +="
+    else:
+        ms = timed(lambda: basic.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=out), iters)
     if compare:
         A, B = (a.t() if a_mn else a), (b if b_mn else b.t())
         extra["cublas_ms"] = round(timed(lambda: torch.matmul(A, B, out=out), iters), 4)
+        if layout == "tn":
+            extra["cublas_note"] = "bf16 output, no accumulation"
     report(f"gemm_{layout}", ms, flops=2.0 * M * N * K, shape=[M, N, K], **extra)
 
 

@@ -18,6 +18,7 @@ struct StoreParams {
   int out_f32;     // 1: C is fp32, 0: C is 16-bit (bf16 or fp16 according to fmt)
   int accumulate;  // 1: C += result
   int fmt;         // 0 fp16, 1 bf16 (16-bit output type)
+  int atomic;      // 1: fp32 C is updated with red.add (split-K: several CTAs add into one tile)
 };
 
 template <int BN>
@@ -131,7 +132,20 @@ struct EpiStore {
           for (int j = 0; j < ncols; ++j) v[j] += __bfloat162float(rp[j]);
         }
       }
-      if (p.out_f32) {
+      if (p.out_f32 && p.atomic) {
+        float* cp = reinterpret_cast<float*>(p.C) + (long long)row * p.ldc + col0;
+        if (ncols == 32 && ((reinterpret_cast<uintptr_t>(cp) & 15) == 0)) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(cp + j * 4), "f"(v[j * 4]),
+                         "f"(v[j * 4 + 1]), "f"(v[j * 4 + 2]), "f"(v[j * 4 + 3])
+                         : "memory");
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (j < ncols) atomicAdd(cp + j, v[j]);
+        }
+      } else if (p.out_f32) {
         float* cp = reinterpret_cast<float*>(p.C) + (long long)row * p.ldc + col0;
         if (ncols == 32 && ((reinterpret_cast<uintptr_t>(cp) & 15) == 0)) {
 #pragma unroll
@@ -219,6 +233,15 @@ static int launch_store(const void* A, const void* B, int M, int N, int K, long 
   return B200_OK;
 }
 
+static bool split_k_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("B200_GEMM_SPLITK");
+    on = e ? (atoi(e) != 0) : 1;
+  }
+  return on != 0;
+}
+
 // Two-SM (cta_group::2) launch: 256 x 256 tiles, one CTA pair per tile.
 template <bool A_MN, bool B_MN>
 static int launch_store_pair(const void* A, const void* B, int M, int N, int K, long long lda, long long ldb, int fmt,
@@ -249,8 +272,25 @@ static int launch_store_pair(const void* A, const void* B, int M, int N, int K, 
   }
   const int tiles = ceil_div(M, PAIR_BM) * ceil_div(N, PAIR_BN);
   const int max_pairs = sm_count() / 2;
-  const int pairs = tiles < max_pairs ? tiles : max_pairs;
-  kern<<<2 * pairs, NUM_THREADS, smem_bytes, stream>>>(tmA, tmB, M, N, K, fmt, sp, device_err_word());
+  // split-K for fp32 outputs with a long reduction and too few tiles for even waves (weight-gradient GEMMs):
+  // aim at about three units per CTA pair; the slices add atomically into a zeroed (or accumulated-into) C
+  int k_splits = 1;
+  StoreParams spl = sp;
+  if (sp.out_f32 && !sp.resid && K >= 4096 && tiles < 3 * max_pairs && split_k_enabled()) {
+    k_splits = (3 * max_pairs + tiles - 1) / tiles;
+    const int max_by_k = K / 1024;   // at least 16 k-blocks per slice
+    if (k_splits > max_by_k) k_splits = max_by_k;
+    if (k_splits > 8) k_splits = 8;
+    if (k_splits < 1) k_splits = 1;
+  }
+  if (k_splits > 1) {
+    spl.atomic = 1;
+    if (!sp.accumulate)
+      B200_CUDA_CHECK(cudaMemset2DAsync(sp.C, (size_t)sp.ldc * 4, 0, (size_t)N * 4, (size_t)M, stream));
+  }
+  const long long units = (long long)tiles * k_splits;
+  const int pairs = units < max_pairs ? (int)units : max_pairs;
+  kern<<<2 * pairs, NUM_THREADS, smem_bytes, stream>>>(tmA, tmB, M, N, K, fmt, spl, device_err_word(), k_splits);
   B200_CUDA_CHECK(cudaGetLastError());
   return B200_OK;
 }
@@ -270,7 +310,7 @@ static bool use_pair(int M, int N, int K) {
   if (mode == 0 || N <= 128) return false;
   if (mode == 1) return true;
   const long long tiles = (long long)ceil_div(M, PAIR_BM) * ceil_div(N, PAIR_BN);
-  return tiles >= sm_count() / 2 && K >= 256;
+  return (tiles >= sm_count() / 2 && K >= 256) || (tiles >= sm_count() / 8 && K >= 4096);
 }
 
 }  // namespace gemm
@@ -300,6 +340,7 @@ int b200_gemm(const void* A, const void* B, void* C, int M, int N, int K, long l
   sp.out_f32 = out_f32;
   sp.accumulate = accumulate;
   sp.fmt = fmt;
+  sp.atomic = 0;
   DescCfg dco;
   const DescCfg* dcp = nullptr;
   if (desc_cfg) {

@@ -32,7 +32,7 @@ struct SmemPair {
 template <int STAGES, bool A_MN, bool B_MN, class Epi>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
     gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, int M, int N,
-                     int K, int fmt, typename Epi::Params ep, unsigned int* err_word) {
+                     int K, int fmt, typename Epi::Params ep, unsigned int* err_word, int k_splits) {
   using S = SmemPair<STAGES>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -77,6 +77,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
   const int n_tiles = (N + PAIR_BN - 1) / PAIR_BN;
   const int num_tiles = m_tiles * n_tiles;
   const int num_kb = (K + BK - 1) / BK;
+  // split-K: a work unit is (tile, slice of the K loop); the slices of one tile run on different CTA pairs and the
+  // epilogue (which must add atomically then) combines them. k_splits = 1: one unit per tile.
+  const int num_units = num_tiles * k_splits;
+  auto unit_range = [&](int unit, int& tile, int& kb0, int& kb1) {
+    tile = unit / k_splits;
+    const int sp = unit - tile * k_splits;
+    kb0 = (int)((long long)num_kb * sp / k_splits);
+    kb1 = (int)((long long)num_kb * (sp + 1) / k_splits);
+  };
   const int pair_id = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
   constexpr int GROUP_M = 8;
@@ -95,12 +104,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = pair_id; ok && tile < num_tiles; tile += num_pairs) {
-        int m_blk, n_blk;
+      for (int unit = pair_id; ok && unit < num_units; unit += num_pairs) {
+        int tile, kb0, kb1, m_blk, n_blk;
+        unit_range(unit, tile, kb0, kb1);
         tile_coords(tile, m_blk, n_blk);
         const int m0 = m_blk * PAIR_BM + (int)cta * BM;
         const int n0 = n_blk * PAIR_BN + (int)cta * PAIR_HALF_N;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const uint32_t s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
           if (!mbar_wait_bounded(&empty_bar[s], ph ^ 1u, abort_flag, err_word, ERR_WAIT_EMPTY)) {
@@ -140,13 +150,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
       constexpr uint32_t b_lbo = B_MN ? BK * 128 : 16, b_kadv = B_MN ? UMMA_K * 128 : UMMA_K * 2;
       uint32_t it = 0, tl = 0;
       bool ok = true;
-      for (int tile = pair_id; ok && tile < num_tiles; tile += num_pairs, ++tl) {
+      for (int unit = pair_id; ok && unit < num_units; unit += num_pairs, ++tl) {
+        int tile, kb0, kb1;
+        unit_range(unit, tile, kb0, kb1);
         const uint32_t acc = tl & 1u;
         const uint32_t aph = (tl >> 1) & 1u;
         if (!mbar_wait_bounded(&tempty_bar[acc], aph ^ 1u, abort_flag, err_word, ERR_WAIT_TMEM_EMPTY)) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * PAIR_BN;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const uint32_t s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
           if (!mbar_wait_bounded(&full_bar[s], ph, abort_flag, err_word, ERR_WAIT_FULL)) {
@@ -160,7 +172,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
           for (int k = 0; k < BK / UMMA_K; ++k) {
             const uint64_t da = make_smem_desc_sw128(a_base + k * a_kadv, a_lbo, 1024);
             const uint64_t db = make_smem_desc_sw128(b_base + k * b_kadv, b_lbo, 1024);
-            umma_f16_ss_pair(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_f16_ss_pair(d_tmem, da, db, idesc, (kb != kb0 || k != 0) ? 1u : 0u);
           }
           umma_commit_pair(&empty_bar[s], 0x3);
         }
@@ -172,8 +184,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
     const int quad = warp & 3;
     const uint32_t leader_tempty0 = mapa_shared(smem_u32(&tempty_bar[0]), 0);
     uint32_t tl = 0;
-    for (int tile = pair_id; tile < num_tiles; tile += num_pairs, ++tl) {
-      int m_blk, n_blk;
+    for (int unit = pair_id; unit < num_units; unit += num_pairs, ++tl) {
+      int tile, kb0, kb1, m_blk, n_blk;
+      unit_range(unit, tile, kb0, kb1);
       tile_coords(tile, m_blk, n_blk);
       const uint32_t acc = tl & 1u;
       const uint32_t aph = (tl >> 1) & 1u;

@@ -57,6 +57,24 @@ def test_gemm_epilogues():
     assert _lib.take_device_error() == 0
 
 
+@pytest.mark.parametrize("a_mn,b_mn", [(True, True), (False, False)])
+def test_split_k_fp32_output_overwrite_accumulate_and_strided(a_mn, b_mn):
+    """Long reduction, few tiles, fp32 output: the CTA-pair kernel splits K and adds the slices atomically."""
+    torch.manual_seed(11)
+    M, N, K = 1280, 1000, 8192
+    a = (torch.randn((K, M) if a_mn else (M, K), device=DEV) * 0.1).bfloat16()
+    b = (torch.randn((K, N) if b_mn else (N, K), device=DEV) * 0.1).bfloat16()
+    r = _ref(a, b, a_mn, b_mn)
+    wide = torch.full((M, N + 24), 7.0, device=DEV)          # row-padded output: the memset must respect the stride
+    c = wide[:, 8:8 + N]
+    basic.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=c)
+    assert torch.allclose(c, r, atol=2e-2, rtol=2e-3), (c - r).abs().max()
+    assert (wide[:, :8] == 7).all() and (wide[:, 8 + N:] == 7).all()
+    basic.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=c, accumulate=True)
+    assert torch.allclose(c, 2 * r, atol=4e-2, rtol=2e-3)
+    assert _lib.take_device_error() == 0
+
+
 def test_linear_helpers_match_autograd():
     torch.manual_seed(6)
     x = torch.randn(512, 256, device=DEV).bfloat16()
