@@ -273,15 +273,20 @@ static int launch_store_pair(const void* A, const void* B, int M, int N, int K, 
   const int tiles = ceil_div(M, PAIR_BM) * ceil_div(N, PAIR_BN);
   const int max_pairs = sm_count() / 2;
   // split-K for fp32 outputs with a long reduction and too few tiles for even waves (weight-gradient GEMMs):
-  // aim at about three units per CTA pair; the slices add atomically into a zeroed (or accumulated-into) C
+  // the slices add atomically into a zeroed (or accumulated-into) C
   int k_splits = 1;
   StoreParams spl = sp;
   if (sp.out_f32 && !sp.resid && K >= 4096 && tiles < 3 * max_pairs && split_k_enabled()) {
-    k_splits = (3 * max_pairs + tiles - 1) / tiles;
-    const int max_by_k = K / 1024;   // at least 16 k-blocks per slice
-    if (k_splits > max_by_k) k_splits = max_by_k;
-    if (k_splits > 8) k_splits = 8;
-    if (k_splits < 1) k_splits = 1;
+    // rounds of the pair grid per unit of tile time: ceil(tiles * s / pairs) / s, plus 8 % per extra slice (measured) for the
+    // atomic epilogues; split only when that buys at least 5 %
+    const int max_s = K / 1024 < 8 ? K / 1024 : 8;   // at least 16 k-blocks per slice
+    double best = (double)((tiles + max_pairs - 1) / max_pairs);
+    const double unsplit = best;
+    for (int s2 = 2; s2 <= max_s; ++s2) {
+      const double c = (double)((tiles * s2 + max_pairs - 1) / max_pairs) / s2 * (1.0 + 0.08 * (s2 - 1));
+      if (c < best) { best = c; k_splits = s2; }
+    }
+    if (best > 0.95 * unsplit) k_splits = 1;
   }
   if (k_splits > 1) {
     spl.atomic = 1;
