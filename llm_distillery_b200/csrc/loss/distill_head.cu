@@ -114,10 +114,16 @@ struct DzParams {
 
 struct EpiDz {
   using Params = DzParams;
-  static constexpr int SMEM_BYTES = 0;
+  static constexpr int STAGE_BYTES = 32 * 256;   // per epilogue warp: 32 rows x 128 bf16 columns, chunks XOR-swizzled
+  static constexpr int SMEM_BYTES = NUM_EPI_WARPS * STAGE_BYTES;
   static __device__ __forceinline__ void tile(const Params& p, uint32_t taddr, int m0, int n0, int M, int N, int quad,
-                                              int lane, uint8_t*) {
-    const int row = m0 + quad * 32 + lane;
+                                              int lane, uint8_t* epi_smem) {
+    // bf16 dlogits leave through a shared-memory stage as whole 256-byte row segments when the layout allows it
+    const bool staged = !(N & 7) && !(p.ldz & 7) && !(reinterpret_cast<uintptr_t>(p.dz) & 15);
+    uint8_t* stage = epi_smem + quad * STAGE_BYTES;
+    const int row0 = m0 + quad * 32;
+    const int rows_valid = min(32, M - row0);
+    const int row = row0 + lane;
     const bool row_ok = row < M;
     const int* ids = p.ids + (long long)row * p.K;
     int pos = 0;
@@ -142,18 +148,47 @@ struct EpiDz {
       tmem_ld_32x32b_x32(taddr + c * 32, r);
       tmem_ld_wait();
       const int col0 = n0 + c * 32;
-      if (!row_ok || col0 >= N) continue;
+      const bool active = row_ok && col0 < N;
       float v[32];
 #pragma unroll
       for (int j = 0; j < 32; ++j) v[j] = coef * fast_exp2(__uint_as_float(r[j]) * c2 - lse2);
-      while (next_id < col0 + 32) {
-        const int sel = next_id - col0;
-        const float add = gs * __ldg(p.a + (long long)row * p.K + pos);
+      if (active) {
+        while (next_id < col0 + 32) {
+          const int sel = next_id - col0;
+          const float add = gs * __ldg(p.a + (long long)row * p.K + pos);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] += (sel == j) ? add : 0.f;
-        ++pos;
-        next_id = pos < p.K ? __ldg(ids + pos) - p.id_off : 0x7fffffff;
+          for (int j = 0; j < 32; ++j) v[j] += (sel == j) ? add : 0.f;
+          ++pos;
+          next_id = pos < p.K ? __ldg(ids + pos) - p.id_off : 0x7fffffff;
+        }
       }
+      if (staged) {
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          uint4 o;
+          o.x = pack_bf16x2(v[q4 * 8 + 0], v[q4 * 8 + 1]);
+          o.y = pack_bf16x2(v[q4 * 8 + 2], v[q4 * 8 + 3]);
+          o.z = pack_bf16x2(v[q4 * 8 + 4], v[q4 * 8 + 5]);
+          o.w = pack_bf16x2(v[q4 * 8 + 6], v[q4 * 8 + 7]);
+          const int chunk = (c & 3) * 4 + q4;
+          *reinterpret_cast<uint4*>(stage + lane * 256 + ((chunk ^ (lane & 15)) << 4)) = o;
+        }
+        if ((c & 3) == 3) {  // 128 columns staged: write them out, two 256-byte row segments per instruction
+          __syncwarp();
+          const int chunk = lane & 15;
+          const int col = n0 + (c >> 2) * 128 + chunk * 8;
+#pragma unroll 4
+          for (int j = 0; j < 16; ++j) {
+            const int rr = 2 * j + (lane >> 4);
+            const uint4 o = *reinterpret_cast<const uint4*>(stage + rr * 256 + ((chunk ^ (rr & 15)) << 4));
+            if (rr < rows_valid && col < N)
+              *reinterpret_cast<uint4*>(p.dz + (long long)(row0 + rr) * p.ldz + col) = o;
+          }
+          __syncwarp();
+        }
+        continue;
+      }
+      if (!active) continue;
       __nv_bfloat16* dst = p.dz + (long long)row * p.ldz + col0;
       const int ncols = min(32, N - col0);
       if (ncols == 32 && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
