@@ -95,18 +95,71 @@ def save_trainer_state(states_dir: str, model: LlamaModel, optimizer, schedule, 
         json.dump(counters, f, indent=2)
 
 
+def _saved_optimizer_shards(states_dir: str) -> list[dict] | None:
+    """All optimizer shard files of the state folder in rank order (CPU tensors), or None if the set is incomplete."""
+    single = os.path.join(states_dir, "optimizer_state.pt")
+    if os.path.exists(single):
+        return [torch.load(single, map_location="cpu")]
+    first = os.path.join(states_dir, "optimizer_state.rank0.pt")
+    if not os.path.exists(first):
+        return None
+    world = int(torch.load(first, map_location="cpu")["shard"][1])
+    out = []
+    for r in range(world):
+        p = os.path.join(states_dir, f"optimizer_state.rank{r}.pt")
+        if not os.path.exists(p):
+            return None
+        out.append(torch.load(p, map_location="cpu"))
+    return out
+
+
+def reshard_optimizer_state(shards: list[dict], optimizer) -> bool:
+    """Load a state saved under another world size: the flat parameter space is the same up to tail padding, so the
+    saved slices are concatenated in rank order and this rank's slice is cut out. Only element-wise fp32 state
+    (master weights and moments as long as a slice) can be cut this way; block-quantised 8-bit state cannot - the
+    function then returns False and the caller restarts the moments."""
+    flat = optimizer.flat
+    old_size = int(shards[0]["total"]) // len(shards)
+    if shards[0]["name"] != optimizer.name:
+        return False
+    keys = list(shards[0]["state"].keys())
+    for sd in shards:
+        if sd["master"].numel() != old_size or any(
+                (not torch.is_tensor(sd["state"][k])) or sd["state"][k].numel() != old_size or
+                sd["state"][k].dtype != torch.float32 for k in keys):
+            return False
+    if any(k not in optimizer.state or optimizer.state[k].numel() != flat.shard_size for k in keys):
+        return False
+
+    def cut(parts: list[torch.Tensor]) -> torch.Tensor:
+        full = torch.cat([t.reshape(-1).float() for t in parts])
+        if full.numel() < flat.total:       # the new layout pads further: zeros there (no parameter lives in padding)
+            full = torch.cat([full, torch.zeros(flat.total - full.numel())])
+        return full[flat.shard_lo: flat.shard_lo + flat.shard_size]
+
+    flat.master.copy_(cut([sd["master"] for sd in shards]))
+    for k in keys:
+        optimizer.state[k].copy_(cut([sd["state"][k] for sd in shards]))
+    optimizer.step_count = int(shards[0]["step_count"])
+    flat.model_shard().copy_(flat.master.to(flat.dtype))
+    return True
+
+
 def load_trainer_state(states_dir: str, model: LlamaModel, optimizer, schedule) -> dict:
     model.load_hf_state_dict(torch.load(os.path.join(states_dir, "model_state.pt"), map_location="cpu"), strict=False)
     shard = optimizer.state_dict()["shard"]
     name = "optimizer_state.pt" if shard[1] == 1 else f"optimizer_state.rank{shard[0]}.pt"
     p = os.path.join(states_dir, name)
+    done = False
     if os.path.exists(p):
         osd = torch.load(p, map_location=optimizer.flat.device)
         if tuple(osd["shard"]) == tuple(shard) and osd["total"] == optimizer.flat.total:
             optimizer.load_state_dict(osd)
-        else:   # different world size: optimizer moments restart, weights (above) carry over
-            optimizer.flat.master.copy_(optimizer.flat.model_shard().float())
-    else:
+            done = True
+    if not done:    # saved under another world size: cut this rank's slice out of the saved ones
+        shards = _saved_optimizer_shards(states_dir)
+        done = bool(shards) and reshard_optimizer_state(shards, optimizer)
+    if not done:    # nothing usable: optimizer moments restart, weights (above) carry over
         optimizer.flat.master.copy_(optimizer.flat.model_shard().float())
     sp = os.path.join(states_dir, "scheduler_state.pt")
     if schedule is not None and os.path.exists(sp):
