@@ -26,7 +26,9 @@ namespace fab {
 
 constexpr int BM = 128;  // queries per block
 constexpr int BN = 128;  // keys per block
-constexpr int NTHREADS = 320;  // TMA warp, MMA warp, 8 softmax/drain warps (two per TMEM lane quadrant)
+constexpr int NSPLIT = 4;        // softmax/drain warps per TMEM lane quadrant: each takes 1/4 of a tile's columns
+constexpr int NTHREADS = 64 + 4 * NSPLIT * 32;  // TMA warp, MMA warp, 16 softmax/drain warps
+constexpr int NWORK = 4 * NSPLIT * 32;          // threads that arrive on the softmax/drain barriers
 
 template <int D>
 struct Cfg {
@@ -77,7 +79,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
   uint64_t* pds_ready = bars + 6;
   uint64_t* dq_full = bars + 7;
   uint64_t* dq_empty = bars + 8;
-  uint64_t* stage_full = bars + 9;   // dQ staging tile written by all 256 drain threads
+  uint64_t* stage_full = bars + 9;   // dQ staging tile written by the drain threads (all of them arrive)
   uint64_t* stage_free = bars + 10;  // ... and read out by the TMA reduce
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -109,10 +111,10 @@ __global__ void __launch_bounds__(NTHREADS, 1)
       mbar_init(&qdo_empty[s], 1);
     }
     mbar_init(sdp_full, 1);
-    mbar_init(pds_ready, 256);
+    mbar_init(pds_ready, NWORK);
     mbar_init(dq_full, 1);
-    mbar_init(dq_empty, 256);
-    mbar_init(stage_full, 256);
+    mbar_init(dq_empty, NWORK);
+    mbar_init(stage_full, NWORK);
     mbar_init(stage_free, 1);
     *abort_flag = 0;
     fence_mbar_init();
@@ -220,14 +222,15 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     }
   } else {
     const int quad = warp & 3;
-    const int half = (warp - 2) >> 2;  // which half of the columns this warp handles
+    const int part = (warp - 2) >> 2;  // which quarter of the columns this warp handles
     const int r = quad * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
     const float c2 = p.scale * 1.4426950408889634f;
     uint8_t* sP = smem + C::OFF_P;
     uint8_t* sDS = smem + C::OFF_DS;
-    constexpr int SCH = BN / 64;  // 32-column chunks of S / dP per warp
-    constexpr int DCH = D / 64;   // 32-column chunks of dQ / dK / dV per warp
+    constexpr int DW = D / NSPLIT;     // columns of dQ / dK / dV per warp: 16 (D = 64) or 32 (D = 128)
+    constexpr int ROUNDS = D / 64;     // the dQ staging area holds two 32-column sub-tiles per round
+    const int dc0 = part * DW;         // first dQ / dK / dV column of this warp
     bool ok = true;
     uint32_t rd = 0;  // staging rounds so far
     for (int it = 0; ok && it < n_it; ++it) {
@@ -244,17 +247,18 @@ __global__ void __launch_bounds__(NTHREADS, 1)
       int w = mbar_wait_bounded(sdp_full, it & 1u, abort_flag, err_word, ERR_WAIT_TMEM_FULL) ? 1 : 0;
       if (!__all_sync(0xffffffffu, w)) { ok = false; break; }
       tc_fence_after_sync();
+      // this warp's 32 columns of S and dP, 16 at a time (keeps the register count under the 18-warp budget)
 #pragma unroll
-      for (int cc = 0; cc < SCH; ++cc) {
-        const int c = half * SCH + cc;
-        uint32_t sv[32], dv[32];
-        tmem_ld_32x32b_x32(tmem_base + lane_addr + C::S_COL + c * 32, sv);
-        tmem_ld_32x32b_x32(tmem_base + lane_addr + C::DP_COL + c * 32, dv);
+      for (int hf = 0; hf < 2; ++hf) {
+        const int col0 = part * 32 + hf * 16;
+        uint32_t sv[16], dv[16];
+        tmem_ld_32x32b_x16(tmem_base + lane_addr + C::S_COL + col0, sv);
+        tmem_ld_32x32b_x16(tmem_base + lane_addr + C::DP_COL + col0, dv);
         tmem_ld_wait();
-        uint32_t pkP[16], pkS[16];
+        uint32_t pkP[8], pkS[8];
         if (!diag) {
 #pragma unroll
-          for (int e = 0; e < 32; e += 2) {
+          for (int e = 0; e < 16; e += 2) {
             const float p0 = fast_exp2(fmaf(__uint_as_float(sv[e]), c2, -lse2));
             const float p1 = fast_exp2(fmaf(__uint_as_float(sv[e + 1]), c2, -lse2));
             const float d0 = p0 * fmaf(__uint_as_float(dv[e]), p.scale, -dlts);
@@ -264,22 +268,23 @@ __global__ void __launch_bounds__(NTHREADS, 1)
           }
         } else {
 #pragma unroll
-          for (int e = 0; e < 32; e += 2) {
+          for (int e = 0; e < 16; e += 2) {
             float p0 = fast_exp2(fmaf(__uint_as_float(sv[e]), c2, -lse2));
             float p1 = fast_exp2(fmaf(__uint_as_float(sv[e + 1]), c2, -lse2));
-            if ((c * 32 + e) > lim) p0 = 0.f;
-            if ((c * 32 + e + 1) > lim) p1 = 0.f;
+            if ((col0 + e) > lim) p0 = 0.f;
+            if ((col0 + e + 1) > lim) p1 = 0.f;
             const float d0 = p0 * fmaf(__uint_as_float(dv[e]), p.scale, -dlts);
             const float d1 = p1 * fmaf(__uint_as_float(dv[e + 1]), p.scale, -dlts);
             pkP[e >> 1] = pack_bf16x2(p0, p1);
             pkS[e >> 1] = pack_bf16x2(d0, d1);
           }
         }
-        const int sub = (c * 32) >> 6;
-        const int chunk0 = ((c * 32) & 63) >> 3;
+        // columns col0 .. col0+15 of row r: 64-column sub-tile col0/64, 16-byte chunks (col0 % 64)/8 + {0, 1}
+        const int sub = col0 >> 6;
+        const int chunk0 = (col0 & 63) >> 3;
         const int off = sub * (BM * 128) + r * 128;
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
+        for (int q4 = 0; q4 < 2; ++q4) {
           const int ch = (chunk0 + q4) ^ (r & 7);
           *reinterpret_cast<uint4*>(sP + off + ch * 16) =
               make_uint4(pkP[q4 * 4], pkP[q4 * 4 + 1], pkP[q4 * 4 + 2], pkP[q4 * 4 + 3]);
@@ -295,29 +300,35 @@ __global__ void __launch_bounds__(NTHREADS, 1)
       if (!__all_sync(0xffffffffu, w2)) { ok = false; break; }
       tc_fence_after_sync();
       // stage the fp32 tile in shared memory (row r, 128-byte rows of 32 floats, 16-byte chunks XOR-swizzled like
-      // every other tile here) and let one thread hand it to the TMA reduce engine. D = 128 takes two rounds.
+      // every other tile here) and let one thread hand it to the TMA reduce engine. The staging area holds two
+      // 32-column sub-tiles: D = 128 takes two rounds, and in each round only the warps whose columns belong to
+      // that round write (everybody arrives on the barriers).
       uint8_t* sDQ = smem + C::OFF_DQS;
+      uint32_t v[DW];
+      if constexpr (DW == 32) tmem_ld_32x32b_x32(tmem_base + lane_addr + C::DQ_COL + dc0, v);
+      else tmem_ld_32x32b_x16(tmem_base + lane_addr + C::DQ_COL + dc0, v);
+      tmem_ld_wait();
+      const int st = dc0 >> 5;               // 32-column sub-tile of dQ this warp contributes to
+      const int chunkbase = (dc0 & 31) >> 2;  // first 16-byte chunk (4 floats) inside the 128-byte row
 #pragma unroll
-      for (int cc = 0; cc < DCH; ++cc) {
-        const int c = half * DCH + cc;  // 32-column chunk of dQ
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(tmem_base + lane_addr + C::DQ_COL + c * 32, v);
-        tmem_ld_wait();
+      for (int rr = 0; rr < ROUNDS; ++rr) {
         // the previous round's reduce has finished reading the staging tile (bounded wait, like every wait here)
         int w3 = mbar_wait_bounded(stage_free, (rd & 1u) ^ 1u, abort_flag, err_word, ERR_WAIT_AUX) ? 1 : 0;
         if (!__all_sync(0xffffffffu, w3)) { ok = false; break; }
-        uint8_t* rowp = sDQ + half * (BM * 128) + r * 128;
+        if ((st >> 1) == rr) {
+          uint8_t* rowp = sDQ + (st & 1) * (BM * 128) + r * 128;
 #pragma unroll
-        for (int q4 = 0; q4 < 8; ++q4)
-          *reinterpret_cast<uint4*>(rowp + ((q4 ^ (r & 7)) * 16)) =
-              make_uint4(v[q4 * 4], v[q4 * 4 + 1], v[q4 * 4 + 2], v[q4 * 4 + 3]);
+          for (int q4 = 0; q4 < DW / 4; ++q4)
+            *reinterpret_cast<uint4*>(rowp + (((chunkbase + q4) ^ (r & 7)) * 16)) =
+                make_uint4(v[q4 * 4], v[q4 * 4 + 1], v[q4 * 4 + 2], v[q4 * 4 + 3]);
+        }
         fence_proxy_async_smem();
         mbar_arrive(stage_full);
         if (warp == 2 && lane == 0) {
           if (mbar_wait_bounded(stage_full, rd & 1u, abort_flag, err_word, ERR_WAIT_AUX)) {
 #pragma unroll
             for (int hh = 0; hh < 2; ++hh)
-              tma_reduce_add_3d(&tmDQ, sDQ + hh * (BM * 128), hq * D + (hh * DCH + cc) * 32, q0, b);
+              tma_reduce_add_3d(&tmDQ, sDQ + hh * (BM * 128), hq * D + (rr * 2 + hh) * 32, q0, b);
             tma_store_commit();
             tma_store_wait_read0();
             mbar_arrive(stage_free);
@@ -342,22 +353,19 @@ __global__ void __launch_bounds__(NTHREADS, 1)
       for (int which = 0; which < 2; ++which) {
         const uint32_t col = which == 0 ? C::DK_COL : C::DV_COL;
         __nv_bfloat16* dst = which == 0 ? krow : vrow;
+        uint32_t v[DW];
+        if constexpr (DW == 32) tmem_ld_32x32b_x32(tmem_base + lane_addr + col + dc0, v);
+        else tmem_ld_32x32b_x16(tmem_base + lane_addr + col + dc0, v);
+        tmem_ld_wait();
+        if (row_ok) {
 #pragma unroll
-        for (int cc = 0; cc < DCH; ++cc) {
-          const int c = half * DCH + cc;
-          uint32_t v[32];
-          tmem_ld_32x32b_x32(tmem_base + lane_addr + col + c * 32, v);
-          tmem_ld_wait();
-          if (row_ok) {
-#pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) {
-              uint4 o;
-              o.x = pack_bf16x2(__uint_as_float(v[q4 * 8 + 0]), __uint_as_float(v[q4 * 8 + 1]));
-              o.y = pack_bf16x2(__uint_as_float(v[q4 * 8 + 2]), __uint_as_float(v[q4 * 8 + 3]));
-              o.z = pack_bf16x2(__uint_as_float(v[q4 * 8 + 4]), __uint_as_float(v[q4 * 8 + 5]));
-              o.w = pack_bf16x2(__uint_as_float(v[q4 * 8 + 6]), __uint_as_float(v[q4 * 8 + 7]));
-              *reinterpret_cast<uint4*>(dst + c * 32 + q4 * 8) = o;
-            }
+          for (int q4 = 0; q4 < DW / 8; ++q4) {
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(v[q4 * 8 + 0]), __uint_as_float(v[q4 * 8 + 1]));
+            o.y = pack_bf16x2(__uint_as_float(v[q4 * 8 + 2]), __uint_as_float(v[q4 * 8 + 3]));
+            o.z = pack_bf16x2(__uint_as_float(v[q4 * 8 + 4]), __uint_as_float(v[q4 * 8 + 5]));
+            o.w = pack_bf16x2(__uint_as_float(v[q4 * 8 + 6]), __uint_as_float(v[q4 * 8 + 7]));
+            *reinterpret_cast<uint4*>(dst + dc0 + q4 * 8) = o;
           }
         }
       }
