@@ -52,6 +52,9 @@ struct Cfg {
   static constexpr uint32_t DV_COL = 256;
   static constexpr uint32_t DK_COL = 256 + D;
   static constexpr uint32_t DQ_COL = ALIAS ? 0 : 256 + 2 * D;
+  // head dim 64 leaves 64 TMEM columns free: a second dQ accumulator lets the pair loop run two pairs deep
+  static constexpr bool PIPE = !ALIAS;
+  static constexpr uint32_t DQ_COL1 = PIPE ? 256 + 3 * D : DQ_COL;
   static constexpr uint32_t TMEM_COLS = 512;
 };
 
@@ -81,7 +84,9 @@ __global__ void __launch_bounds__(NTHREADS, 1)
   uint64_t* dq_empty = bars + 8;
   uint64_t* stage_full = bars + 9;   // dQ staging tile written by the drain threads (all of them arrive)
   uint64_t* stage_free = bars + 10;  // ... and read out by the TMA reduce
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  uint64_t* dq_full1 = bars + 11;    // second dQ accumulator (pipelined variant)
+  uint64_t* dq_empty1 = bars + 12;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -116,6 +121,8 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     mbar_init(dq_empty, NWORK);
     mbar_init(stage_full, NWORK);
     mbar_init(stage_free, 1);
+    mbar_init(dq_full1, 1);
+    mbar_init(dq_empty1, NWORK);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -165,14 +172,8 @@ __global__ void __launch_bounds__(NTHREADS, 1)
       const uint32_t sP = smem_u32(smem + C::OFF_P);
       const uint32_t sDS = smem_u32(smem + C::OFF_DS);
       bool ok = mbar_wait_bounded(kv_full, 0, abort_flag, err_word, ERR_WAIT_FULL);
-      for (int it = 0; ok && it < n_it; ++it) {
-        const int s = it % ST;
-        const uint32_t ph = (it / ST) & 1u;
-        if (!mbar_wait_bounded(&qdo_full[s], ph, abort_flag, err_word, ERR_WAIT_FULL)) break;
-        if (C::ALIAS && it > 0) {
-          if (!mbar_wait_bounded(dq_empty, (it - 1) & 1u, abort_flag, err_word, ERR_WAIT_AUX)) break;
-        }
-        tc_fence_after_sync();
+      // S = Q K^T and dP = dO V^T of the pair whose Q / dO sit in stage s
+      auto issue_s_dp = [&](int s) {
         const uint32_t sQ = smem_u32(smem + C::OFF_QDO + s * C::STAGE_BYTES);
         const uint32_t sDO = sQ + C::QDO_BYTES;
 #pragma unroll
@@ -189,13 +190,12 @@ __global__ void __launch_bounds__(NTHREADS, 1)
           const uint64_t db = make_smem_desc_sw128(sV + sub * (BN * 128) + kk * 32, 16, 1024);
           umma_f16_ss(tmem_base + C::DP_COL, da, db, idesc_kk, k != 0 ? 1u : 0u);
         }
-        umma_commit(sdp_full);
-        if (!mbar_wait_bounded(pds_ready, it & 1u, abort_flag, err_word, ERR_WAIT_AUX)) break;
-        if (!C::ALIAS && it > 0) {
-          if (!mbar_wait_bounded(dq_empty, (it - 1) & 1u, abort_flag, err_word, ERR_WAIT_AUX)) break;
-        }
-        tc_fence_after_sync();
-        // dV += P^T dO ; dK += dS^T Q : reduction over the 128 queries, 16 per step (2048 B per step in both tiles)
+      };
+      // dV += P^T dO ; dK += dS^T Q (reduction over the 128 queries, 16 per step = 2048 B per step in both tiles);
+      // dQ = dS K (reduction over the 128 keys) into the accumulator at dq_col
+      auto issue_dv_dk_dq = [&](int s, int it, uint32_t dq_col) {
+        const uint32_t sQ = smem_u32(smem + C::OFF_QDO + s * C::STAGE_BYTES);
+        const uint32_t sDO = sQ + C::QDO_BYTES;
 #pragma unroll
         for (int k = 0; k < BM / 16; ++k) {
           const uint64_t da = make_smem_desc_sw128(sP + k * 2048, BM * 128, 1024);
@@ -208,16 +208,63 @@ __global__ void __launch_bounds__(NTHREADS, 1)
           const uint64_t db = make_smem_desc_sw128(sQ + k * 2048, BM * 128, 1024);
           umma_f16_ss(tmem_base + C::DK_COL, da, db, idesc_tt, (it | k) != 0 ? 1u : 0u);
         }
-        // dQ = dS K : reduction over the 128 keys
 #pragma unroll
         for (int k = 0; k < BN / 16; ++k) {
           const uint32_t sub = k >> 2, kk = k & 3;
           const uint64_t da = make_smem_desc_sw128(sDS + sub * (BM * 128) + kk * 32, 16, 1024);
           const uint64_t db = make_smem_desc_sw128(sK + k * 2048, BN * 128, 1024);
-          umma_f16_ss(tmem_base + C::DQ_COL, da, db, idesc_kt, k != 0 ? 1u : 0u);
+          umma_f16_ss(tmem_base + dq_col, da, db, idesc_kt, k != 0 ? 1u : 0u);
         }
-        umma_commit(&qdo_empty[s]);
-        umma_commit(dq_full);
+      };
+      if constexpr (C::PIPE) {
+        // Two pairs deep: as soon as the softmax warps have consumed S / dP of pair `it` (pds_ready), the S / dP MMAs
+        // of pair it+1 are issued AHEAD of pair it's dV / dK / dQ MMAs, so the warps never wait for the tensor core
+        // between pairs; dQ alternates between two accumulators because pair it-1's is drained during pair it.
+        if (ok && n_it > 0) {
+          ok = mbar_wait_bounded(&qdo_full[0], 0, abort_flag, err_word, ERR_WAIT_FULL);
+          if (ok) {
+            tc_fence_after_sync();
+            issue_s_dp(0);
+            umma_commit(sdp_full);
+          }
+        }
+        for (int it = 0; ok && it < n_it; ++it) {
+          const int s = it % ST;
+          if (!mbar_wait_bounded(pds_ready, it & 1u, abort_flag, err_word, ERR_WAIT_AUX)) break;
+          tc_fence_after_sync();
+          if (it + 1 < n_it) {
+            const int s1 = (it + 1) % ST;
+            if (!mbar_wait_bounded(&qdo_full[s1], ((it + 1) / ST) & 1u, abort_flag, err_word, ERR_WAIT_FULL)) break;
+            tc_fence_after_sync();
+            issue_s_dp(s1);
+            umma_commit(sdp_full);
+          }
+          const int bq = it & 1;
+          if (it >= 2) {  // the drain of pair it-2 has emptied this accumulator
+            if (!mbar_wait_bounded(bq ? dq_empty1 : dq_empty, ((it >> 1) - 1) & 1u, abort_flag, err_word, ERR_WAIT_AUX)) break;
+            tc_fence_after_sync();
+          }
+          issue_dv_dk_dq(s, it, bq ? C::DQ_COL1 : C::DQ_COL);
+          umma_commit(&qdo_empty[s]);
+          umma_commit(bq ? dq_full1 : dq_full);
+        }
+      } else {
+        for (int it = 0; ok && it < n_it; ++it) {
+          const int s = it % ST;
+          const uint32_t ph = (it / ST) & 1u;
+          if (!mbar_wait_bounded(&qdo_full[s], ph, abort_flag, err_word, ERR_WAIT_FULL)) break;
+          if (it > 0) {  // dQ shares its TMEM columns with S here
+            if (!mbar_wait_bounded(dq_empty, (it - 1) & 1u, abort_flag, err_word, ERR_WAIT_AUX)) break;
+          }
+          tc_fence_after_sync();
+          issue_s_dp(s);
+          umma_commit(sdp_full);
+          if (!mbar_wait_bounded(pds_ready, it & 1u, abort_flag, err_word, ERR_WAIT_AUX)) break;
+          tc_fence_after_sync();
+          issue_dv_dk_dq(s, it, C::DQ_COL);
+          umma_commit(&qdo_empty[s]);
+          umma_commit(dq_full);
+        }
       }
     }
   } else {
@@ -233,6 +280,68 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     const int dc0 = part * DW;         // first dQ / dK / dV column of this warp
     bool ok = true;
     uint32_t rd = 0;  // staging rounds so far
+    uint8_t* sDQ = smem + C::OFF_DQS;
+    const int st = dc0 >> 5;               // 32-column sub-tile of dQ this warp contributes to
+    const int chunkbase = (dc0 & 31) >> 2;  // first 16-byte chunk (4 floats) inside the 128-byte row
+    // Drain the dQ accumulator of pair `itd` into the fp32 gradient: TMEM -> registers -> swizzled staging tile in
+    // shared memory (row r, 128-byte rows of 32 floats) -> TMA reduce-add issued by one thread. The staging area holds
+    // two 32-column sub-tiles: D = 128 takes two rounds, and in each round only the warps whose columns belong to
+    // that round write (everybody arrives on the barriers). The caller has waited for the pair's dq_full barrier.
+    auto drain = [&](int itd) {
+      const int hq = hkv * g + itd / nqi;
+      const int q0 = (i_start + itd % nqi) * BM;
+      const uint32_t dq_col = (C::PIPE && (itd & 1)) ? C::DQ_COL1 : C::DQ_COL;
+      uint32_t v[DW];
+      if constexpr (DW == 32) tmem_ld_32x32b_x32(tmem_base + lane_addr + dq_col + dc0, v);
+      else tmem_ld_32x32b_x16(tmem_base + lane_addr + dq_col + dc0, v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int rr = 0; rr < ROUNDS; ++rr) {
+        // the previous round's reduce must have finished READING the staging tile. The thread that issued it checks
+        // that only now, a whole softmax phase later, so that the TMA engine's latency is off the critical path.
+        if (warp == 2 && lane == 0 && rd > 0) {
+          tma_store_wait_read0();
+          mbar_arrive(stage_free);
+        }
+        __syncwarp();
+        if (rd > 0) {
+          int w3 = mbar_wait_bounded(stage_free, (rd - 1) & 1u, abort_flag, err_word, ERR_WAIT_AUX) ? 1 : 0;
+          if (!__all_sync(0xffffffffu, w3)) { ok = false; break; }
+        }
+        if ((st >> 1) == rr) {
+          uint8_t* rowp = sDQ + (st & 1) * (BM * 128) + r * 128;
+#pragma unroll
+          for (int q4 = 0; q4 < DW / 4; ++q4)
+            *reinterpret_cast<uint4*>(rowp + (((chunkbase + q4) ^ (r & 7)) * 16)) =
+                make_uint4(v[q4 * 4], v[q4 * 4 + 1], v[q4 * 4 + 2], v[q4 * 4 + 3]);
+        }
+        fence_proxy_async_smem();
+        mbar_arrive(stage_full);
+        if (warp == 2 && lane == 0) {
+          if (mbar_wait_bounded(stage_full, rd & 1u, abort_flag, err_word, ERR_WAIT_AUX)) {
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh)
+              tma_reduce_add_3d(&tmDQ, sDQ + hh * (BM * 128), hq * D + (rr * 2 + hh) * 32, q0, b);
+            tma_store_commit();
+          }
+        }
+        __syncwarp();
+        ++rd;
+      }
+      if (ok) {
+        tc_fence_before_sync();
+        mbar_arrive((C::PIPE && (itd & 1)) ? dq_empty1 : dq_empty);
+      }
+    };
+    // dq_full of pair itd: one barrier per accumulator, each used by every second pair in the pipelined variant
+    auto wait_dq_full = [&](int itd) -> bool {
+      uint64_t* bar = (C::PIPE && (itd & 1)) ? dq_full1 : dq_full;
+      const uint32_t parity = C::PIPE ? ((itd >> 1) & 1u) : (itd & 1u);
+      int w2 = mbar_wait_bounded(bar, parity, abort_flag, err_word, ERR_WAIT_AUX) ? 1 : 0;
+      if (!__all_sync(0xffffffffu, w2)) return false;
+      tc_fence_after_sync();
+      return true;
+    };
     for (int it = 0; ok && it < n_it; ++it) {
       const int hq = hkv * g + it / nqi;
       const int q0 = (i_start + it % nqi) * BM;
@@ -279,6 +388,11 @@ __global__ void __launch_bounds__(NTHREADS, 1)
             pkS[e >> 1] = pack_bf16x2(d0, d1);
           }
         }
+        if (C::PIPE && hf == 0 && it > 0) {
+          // P / dS in shared memory still belong to pair it-1 until its dV / dK / dQ MMAs are done (they were issued
+          // behind this pair's S / dP MMAs); the first 16 columns above were computed while waiting for that
+          if (!wait_dq_full(it - 1)) { ok = false; break; }
+        }
         // columns col0 .. col0+15 of row r: 64-column sub-tile col0/64, 16-byte chunks (col0 % 64)/8 + {0, 1}
         const int sub = col0 >> 6;
         const int chunk0 = (col0 & 63) >> 3;
@@ -292,54 +406,20 @@ __global__ void __launch_bounds__(NTHREADS, 1)
               make_uint4(pkS[q4 * 4], pkS[q4 * 4 + 1], pkS[q4 * 4 + 2], pkS[q4 * 4 + 3]);
         }
       }
+      if (!ok) break;
       fence_proxy_async_smem();
       tc_fence_before_sync();
       mbar_arrive(pds_ready);
-      // drain dQ of this pair into the fp32 accumulator
-      int w2 = mbar_wait_bounded(dq_full, it & 1u, abort_flag, err_word, ERR_WAIT_AUX) ? 1 : 0;
-      if (!__all_sync(0xffffffffu, w2)) { ok = false; break; }
-      tc_fence_after_sync();
-      // stage the fp32 tile in shared memory (row r, 128-byte rows of 32 floats, 16-byte chunks XOR-swizzled like
-      // every other tile here) and let one thread hand it to the TMA reduce engine. The staging area holds two
-      // 32-column sub-tiles: D = 128 takes two rounds, and in each round only the warps whose columns belong to
-      // that round write (everybody arrives on the barriers).
-      uint8_t* sDQ = smem + C::OFF_DQS;
-      uint32_t v[DW];
-      if constexpr (DW == 32) tmem_ld_32x32b_x32(tmem_base + lane_addr + C::DQ_COL + dc0, v);
-      else tmem_ld_32x32b_x16(tmem_base + lane_addr + C::DQ_COL + dc0, v);
-      tmem_ld_wait();
-      const int st = dc0 >> 5;               // 32-column sub-tile of dQ this warp contributes to
-      const int chunkbase = (dc0 & 31) >> 2;  // first 16-byte chunk (4 floats) inside the 128-byte row
-#pragma unroll
-      for (int rr = 0; rr < ROUNDS; ++rr) {
-        // the previous round's reduce has finished reading the staging tile (bounded wait, like every wait here)
-        int w3 = mbar_wait_bounded(stage_free, (rd & 1u) ^ 1u, abort_flag, err_word, ERR_WAIT_AUX) ? 1 : 0;
-        if (!__all_sync(0xffffffffu, w3)) { ok = false; break; }
-        if ((st >> 1) == rr) {
-          uint8_t* rowp = sDQ + (st & 1) * (BM * 128) + r * 128;
-#pragma unroll
-          for (int q4 = 0; q4 < DW / 4; ++q4)
-            *reinterpret_cast<uint4*>(rowp + (((chunkbase + q4) ^ (r & 7)) * 16)) =
-                make_uint4(v[q4 * 4], v[q4 * 4 + 1], v[q4 * 4 + 2], v[q4 * 4 + 3]);
-        }
-        fence_proxy_async_smem();
-        mbar_arrive(stage_full);
-        if (warp == 2 && lane == 0) {
-          if (mbar_wait_bounded(stage_full, rd & 1u, abort_flag, err_word, ERR_WAIT_AUX)) {
-#pragma unroll
-            for (int hh = 0; hh < 2; ++hh)
-              tma_reduce_add_3d(&tmDQ, sDQ + hh * (BM * 128), hq * D + (rr * 2 + hh) * 32, q0, b);
-            tma_store_commit();
-            tma_store_wait_read0();
-            mbar_arrive(stage_free);
-          }
-        }
-        __syncwarp();
-        ++rd;
+      if constexpr (C::PIPE) {
+        if (it > 0) drain(it - 1);   // its dq_full was waited for above
+      } else {
+        if (!wait_dq_full(it)) { ok = false; break; }
+        drain(it);
       }
-      if (!ok) break;
-      tc_fence_before_sync();
-      mbar_arrive(dq_empty);
+    }
+    if (C::PIPE && ok && n_it > 0) {   // the last pair's dQ; this wait also covers every MMA of the CTA
+      if (wait_dq_full(n_it - 1)) drain(n_it - 1);
+      else ok = false;
     }
     if (warp == 2 && lane == 0) tma_store_wait_all0();
     // epilogue: dK_j, dV_j (thread = key row). The last dq_full wait covered every MMA of this CTA.
