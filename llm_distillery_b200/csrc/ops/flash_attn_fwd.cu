@@ -130,14 +130,9 @@ __global__ void __launch_bounds__(NTHREADS, 2)
       const uint32_t sQ = smem_u32(smem);
       const uint32_t sP = smem_u32(smem + C::OFF_P);
       bool ok = mbar_wait_bounded(q_full, 0, abort_flag, err_word, ERR_WAIT_FULL);
-      for (int j = 0; ok && j < n_kv; ++j) {
-        const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1u;
-        if (!mbar_wait_bounded(&kv_full[s], ph, abort_flag, err_word, ERR_WAIT_FULL)) break;
-        tc_fence_after_sync();
+      // S = Q K^T for the K tile in stage s: D/16 k-steps; 64-column sub-tiles are BM*128 (Q) / BN*128 (K) bytes apart
+      auto issue_s = [&](int s) {
         const uint32_t sK = smem_u32(smem + C::OFF_KV + s * C::STAGE_BYTES);
-        const uint32_t sV = sK + C::K_BYTES;
-        // S = Q K^T : D/16 k-steps; 64-column sub-tiles are BM*128 (Q) / BN*128 (K) bytes apart
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t sub = k >> 2, kk = k & 3;
@@ -145,10 +140,30 @@ __global__ void __launch_bounds__(NTHREADS, 2)
           const uint64_t db = make_smem_desc_sw128(sK + sub * (BN * 128) + kk * 32, 16, 1024);
           umma_f16_ss(tmem_base + C::S_COL, da, db, idesc_s, k != 0 ? 1u : 0u);
         }
-        umma_commit(s_full);
-        // wait for P_j (and the O rescale) from the softmax warps
+      };
+      if (ok && n_kv > 0) {
+        ok = mbar_wait_bounded(&kv_full[0], 0, abort_flag, err_word, ERR_WAIT_FULL);
+        if (ok) {
+          tc_fence_after_sync();
+          issue_s(0);
+          umma_commit(s_full);
+        }
+      }
+      for (int j = 0; ok && j < n_kv; ++j) {
+        const int s = j & 1;
+        // wait for P_j (and the O rescale) from the softmax warps: S is free again from here on
         if (!mbar_wait_bounded(p_ready, j & 1u, abort_flag, err_word, ERR_WAIT_AUX)) break;
         tc_fence_after_sync();
+        if (j + 1 < n_kv) {
+          // the next tile's scores go to the tensor core AHEAD of this tile's P V, so that the softmax warps find
+          // S_{j+1} ready as soon as they are done with tile j
+          const int s1 = (j + 1) & 1;
+          if (!mbar_wait_bounded(&kv_full[s1], ((j + 1) >> 1) & 1u, abort_flag, err_word, ERR_WAIT_FULL)) break;
+          tc_fence_after_sync();
+          issue_s(s1);
+          umma_commit(s_full);
+        }
+        const uint32_t sV = smem_u32(smem + C::OFF_KV + s * C::STAGE_BYTES) + C::K_BYTES;
         // O += P V : BN/16 k-steps over keys; V is MN-major (D contiguous), 64-wide D chunks BN*128 bytes apart
 #pragma unroll
         for (int k = 0; k < BN / 16; ++k) {
