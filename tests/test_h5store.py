@@ -147,3 +147,41 @@ def test_prefetch_batches_padded_sorted(tmp_path):
     seen = [st.read_next_batch()["ids"][0] for _ in range(5)]
     assert seen == [0, 1, 0, 1, 0]
     st.close()
+
+
+def _tiny_store(path, shuffle):
+    st = H5Store(path, writers=1, shuffle=shuffle)
+    for i in range(3):
+        v = (np.arange(12 * 5, dtype=np.float32).reshape(12, 5) * -0.25 - i).astype(np.float16)
+        ix = (np.arange(12 * 5, dtype=np.int64).reshape(12, 5) * 7 + i) % 32000
+        st.write_batch([TeacherRows(10 + i, v, ix, f"sha-{i}", "sample")])
+        st.wait()
+    st.set_vocab_family("llama_3")
+    st.set_topk(5)
+    st.close()
+
+
+@pytest.mark.parametrize("shuffle,digest", [(True, None), (False, None)])
+def test_file_bytes_are_deterministic(tmp_path, shuffle, digest):
+    """Same writes, same bytes: two files written with the same calls are identical (no timestamps, no pointers, no
+    uninitialised padding leak into the file), so a format change shows up as a diff of a hex dump."""
+    import hashlib
+    a, b = str(tmp_path / "a"), str(tmp_path / "b")
+    _tiny_store(a, shuffle)
+    _tiny_store(b, shuffle)
+    da = hashlib.sha256(open(a + "/distributions.hdf5", "rb").read()).hexdigest()
+    db = hashlib.sha256(open(b + "/distributions.hdf5", "rb").read()).hexdigest()
+    assert da == db
+
+
+def test_h5py_reads_the_file_when_it_is_installed(tmp_path):
+    h5py = pytest.importorskip("h5py")      # not on the build box; runs wherever the library exists
+    for shuffle in (True, False):
+        d = str(tmp_path / f"s{int(shuffle)}")
+        _tiny_store(d, shuffle)
+        with h5py.File(d + "/distributions.hdf5", "r") as f:
+            assert f.attrs["vocab_family"] == "llama_3" and int(f.attrs["topk"]) == 5
+            g = f["convo_11"]
+            assert g.attrs["content_sha"] == "sha-1"
+            assert g["distributions"].dtype == np.float16 and g["distributions"].shape == (12, 5)
+            assert g["indices"].dtype == np.uint32 and int(g["indices"][0, 0]) == 1
