@@ -222,6 +222,10 @@ def load_tp_weights(path: str, rank: int, tp: int, vocab: int | None = None, dty
         w[p + "qkv_proj"] = torch.cat([sl(hp + "self_attn.q_proj.weight", rows=(rank * Hl * d, (rank + 1) * Hl * d)),
                                        sl(hp + "self_attn.k_proj.weight", rows=(rank * Hkvl * d, (rank + 1) * Hkvl * d)),
                                        sl(hp + "self_attn.v_proj.weight", rows=(rank * Hkvl * d, (rank + 1) * Hkvl * d))], 0)
+        if cfg.attention_bias:
+            w[p + "qkv_bias"] = torch.cat([sl(hp + "self_attn.q_proj.bias", rows=(rank * Hl * d, (rank + 1) * Hl * d)),
+                                           sl(hp + "self_attn.k_proj.bias", rows=(rank * Hkvl * d, (rank + 1) * Hkvl * d)),
+                                           sl(hp + "self_attn.v_proj.bias", rows=(rank * Hkvl * d, (rank + 1) * Hkvl * d))])
         w[p + "o_proj"] = sl(hp + "self_attn.o_proj.weight", cols=(rank * Hl * d, (rank + 1) * Hl * d)).contiguous()
         w[p + "gate_up_proj"] = torch.cat([sl(hp + "mlp.gate_proj.weight", rows=(rank * fl, (rank + 1) * fl)),
                                            sl(hp + "mlp.up_proj.weight", rows=(rank * fl, (rank + 1) * fl))], 0)

@@ -372,6 +372,55 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ x, const int* __restrict
   }
 }
 
+// x[t, j] += bias[j] in place (bf16, 16-byte vectors): the q/k/v projection bias of Qwen2-style attention
+__global__ void bias_add_kernel(__nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ bias, long long T,
+                                int N, long long ld) {
+  const int nv = N >> 3;
+  const long long total = T * nv;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / nv;
+    const int v = (int)(i - t * nv);
+    uint4* px = reinterpret_cast<uint4*>(x + t * ld) + v;
+    float a[8], b8[8];
+    unpack8(*px, a);
+    unpack8(reinterpret_cast<const uint4*>(bias)[v], b8);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) a[j] += b8[j];
+    *px = pack8(a);
+  }
+}
+
+// out[j] += sum_t dy[t, j]  (fp32 atomics; the launcher zeroes `out` first when it must not accumulate).
+// Block = 32 column vectors (256 columns) x 8 row lanes; grid.y row groups stride over the rows.
+__global__ void __launch_bounds__(256) bias_grad_kernel(const __nv_bfloat16* __restrict__ dy, float* __restrict__ out,
+                                                        long long T, int N, long long ld) {
+  __shared__ float red[8][32][9];
+  const int cv = threadIdx.x & 31, rl = threadIdx.x >> 5;
+  const int v = blockIdx.x * 32 + cv;  // column vector index
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (v * 8 < N) {
+    for (long long t = (long long)blockIdx.y * 8 + rl; t < T; t += (long long)gridDim.y * 8) {
+      float a[8];
+      unpack8(reinterpret_cast<const uint4*>(dy + t * ld)[v], a);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += a[j];
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) red[rl][cv][j] = acc[j];
+  __syncthreads();
+  if (rl == 0 && v * 8 < N) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float s = 0.f;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) s += red[k][cv][j];
+      atomicAdd(out + v * 8 + j, s);
+    }
+  }
+}
+
 // act[t, j] = silu(gu[t, j]) * gu[t, f + j]      gu is [T, 2f]
 __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ act, long long T,
                                   int f) {
@@ -576,6 +625,26 @@ int b200_rope(void* x, const int* pos, const float* cos_tab, const float* sin_ta
   const long long total = T * nh * (d >> 4);
   rope_kernel<<<grid_for(total, 256), 256, 0, st>>>((__nv_bfloat16*)x, pos, cos_tab, sin_tab, T, nh, d, row_stride,
                                                    inverse ? -1.f : 1.f);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200_OK;
+}
+
+int b200_bias_add(void* x, const void* bias, long long T, int N, long long ld, cudaStream_t st) {
+  if (!x || !bias || T <= 0 || N <= 0 || (N & 7) || (ld & 7)) return B200_ERR_ARG;
+  bias_add_kernel<<<grid_for(T * (N >> 3), 256), 256, 0, st>>>((__nv_bfloat16*)x, (const __nv_bfloat16*)bias, T, N, ld);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200_OK;
+}
+
+// out[N] (fp32) (+)= column sums of dy[T, N] (bf16, row stride ld)
+int b200_bias_grad(const void* dy, float* out, long long T, int N, long long ld, int accumulate, cudaStream_t st) {
+  if (!dy || !out || T <= 0 || N <= 0 || (N & 7) || (ld & 7)) return B200_ERR_ARG;
+  if (!accumulate) B200_CUDA_CHECK(cudaMemsetAsync(out, 0, sizeof(float) * N, st));
+  long long gy = (T + 511) / 512;
+  if (gy > 64) gy = 64;
+  if (gy < 1) gy = 1;
+  dim3 grid((unsigned)ceil_div(N, 256), (unsigned)gy);
+  bias_grad_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)dy, out, T, N, ld);
   B200_CUDA_CHECK(cudaGetLastError());
   return B200_OK;
 }

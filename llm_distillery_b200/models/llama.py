@@ -38,6 +38,7 @@ class LlamaConfig:
     bos_token_id: int = 1
     eos_token_id: int = 2
     model_type: str = "llama"
+    attention_bias: bool = False      # bias on the q/k/v projections (Qwen2 family); o_proj and the MLP have none
 
     @property
     def head_dim(self) -> int:
@@ -54,6 +55,8 @@ class LlamaConfig:
     def num_params(self) -> int:
         h, f, V, Lr = self.hidden_size, self.intermediate_size, self.vocab_size, self.num_hidden_layers
         per_layer = h * (self.q_size + 2 * self.kv_size) + self.q_size * h + 3 * h * f + 2 * h
+        if self.attention_bias:
+            per_layer += self.q_size + 2 * self.kv_size
         return Lr * per_layer + V * h * (1 if self.tie_word_embeddings else 2) + h
 
     def flops_per_token_fwd(self, seq_len: int) -> float:
@@ -64,14 +67,27 @@ class LlamaConfig:
 
     def to_hf_dict(self) -> dict:
         d = asdict(self)
-        d.update(architectures=["LlamaForCausalLM"], hidden_act="silu", torch_dtype="bfloat16", attention_bias=False,
-                 mlp_bias=False)
+        if self.attention_bias:     # q/k/v bias without o_proj bias is the Qwen2 layout in HuggingFace terms
+            d.pop("attention_bias")
+            d.update(architectures=["Qwen2ForCausalLM"], model_type="qwen2", hidden_act="silu", torch_dtype="bfloat16",
+                     use_sliding_window=False)
+        else:
+            d.update(architectures=["LlamaForCausalLM"], hidden_act="silu", torch_dtype="bfloat16",
+                     attention_bias=False, mlp_bias=False)
         return d
 
     @classmethod
     def from_hf_dict(cls, d: dict) -> "LlamaConfig":
         keys = {f for f in cls.__dataclass_fields__}
         kw = {k: v for k, v in d.items() if k in keys}
+        mt = d.get("model_type", "llama")
+        if mt == "qwen2":
+            kw["attention_bias"] = True
+        elif kw.get("attention_bias"):
+            raise NotImplementedError("attention_bias on a Llama config also puts a bias on o_proj, which is not built; "
+                                      "q/k/v-only bias (model_type qwen2) is")
+        if d.get("mlp_bias"):
+            raise NotImplementedError("mlp_bias is not supported")
         if "num_key_value_heads" not in kw or kw["num_key_value_heads"] is None:
             kw["num_key_value_heads"] = kw.get("num_attention_heads", 32)
         return cls(**kw)
@@ -89,6 +105,10 @@ PRESETS = {
     "llama-3-8b": (32, 4096, 32, 8, 14336, 128256, 500000.0, 1e-5, False, 8192),
     "mistral-7b": (32, 4096, 32, 8, 14336, 32000, 10000.0, 1e-5, False, 32768),
     "llama-3-70b": (80, 8192, 64, 8, 28672, 128256, 500000.0, 1e-5, False, 8192),
+    # Qwen2 family: the same blocks with a bias on the q/k/v projections (attention_bias, set by preset())
+    "qwen2.5-0.5b": (24, 896, 14, 2, 4864, 151936, 1000000.0, 1e-6, True, 32768),
+    "qwen2.5-1.5b": (28, 1536, 12, 2, 8960, 151936, 1000000.0, 1e-6, True, 32768),
+    "qwen2.5-7b": (28, 3584, 28, 4, 18944, 152064, 1000000.0, 1e-6, False, 32768),
     "plumbing-teacher": (2, 256, 4, 4, 688, 32000, 10000.0, 1e-6, False, 2048),
     "plumbing-student": (4, 256, 4, 4, 688, 32000, 10000.0, 1e-6, False, 2048),
 }
@@ -99,6 +119,8 @@ def preset(name: str, **over) -> LlamaConfig:
     cfg = LlamaConfig(vocab_size=V, hidden_size=h, intermediate_size=f, num_hidden_layers=Lr, num_attention_heads=H,
                       num_key_value_heads=Hkv, rms_norm_eps=eps, rope_theta=theta, max_position_embeddings=mp,
                       tie_word_embeddings=tied)
+    if name.startswith("qwen2"):
+        cfg.attention_bias, cfg.model_type = True, "qwen2"
     for k, v in over.items():
         setattr(cfg, k, v)
     return cfg
@@ -173,10 +195,12 @@ class DecoderLayerFn(torch.autograd.Function):
     """h_out = h + Attn(RMSNorm(h)) ; then + MLP(RMSNorm(.)) - one node, explicit backward."""
 
     @staticmethod
-    def forward(ctx, h, pos, cos, sin, w_ln1, w_qkv, w_o, w_ln2, w_gu, w_d, meta):
+    def forward(ctx, h, pos, cos, sin, w_ln1, w_qkv, w_o, w_ln2, w_gu, w_d, meta, b_qkv=None):
         B, L, H, Hkv, d, eps, recompute = meta
         n1, _, rstd1 = basic.rmsnorm_fwd(h, w_ln1, eps)
         qkv = basic.linear_fwd(n1, w_qkv)
+        if b_qkv is not None:
+            basic.bias_add_(qkv, b_qkv)
         basic.rope_(qkv, pos, cos, sin, H + Hkv, d)          # q and k heads are adjacent columns
         att, lse = attention.attention_fwd(qkv, B, L, H, Hkv, d)
         h1 = basic.linear_fwd(att, w_o, residual=h)
@@ -187,6 +211,8 @@ class DecoderLayerFn(torch.autograd.Function):
         ctx.meta = meta
         ctx.weights = (w_ln1, w_qkv, w_o, w_ln2, w_gu, w_d)
         ctx.slots = tuple(_slot(w) for w in ctx.weights)
+        ctx.b_qkv = b_qkv
+        ctx.b_slot = _slot(b_qkv) if b_qkv is not None else None
         if recompute:   # gradient checkpointing: keep only the layer input
             ctx.save_for_backward(h, pos, cos, sin)
         else:
@@ -202,6 +228,8 @@ class DecoderLayerFn(torch.autograd.Function):
             h, pos, cos, sin = ctx.saved_tensors
             n1, _, rstd1 = basic.rmsnorm_fwd(h, w_ln1, eps)
             qkv = basic.linear_fwd(n1, w_qkv)
+            if ctx.b_qkv is not None:
+                basic.bias_add_(qkv, ctx.b_qkv)
             basic.rope_(qkv, pos, cos, sin, H + Hkv, d)
             att, lse = attention.attention_fwd(qkv, B, L, H, Hkv, d)
             h1 = basic.linear_fwd(att, w_o, residual=h)
@@ -228,12 +256,19 @@ class DecoderLayerFn(torch.autograd.Function):
         dqkv = attention.attention_bwd(datt, qkv, att, lse, B, L, H, Hkv, d)
         del datt
         basic.rope_(dqkv, pos, cos, sin, H + Hkv, d, inverse=True)
+        g_b = None
+        if ctx.b_qkv is not None and ctx.b_qkv.requires_grad:
+            if ctx.b_slot is not None:
+                basic.bias_grad(dqkv, out=ctx.b_slot.buf, accumulate=not ctx.b_slot.fresh)
+                ctx.b_slot.fresh = False
+            else:
+                g_b = basic.bias_grad(dqkv).to(ctx.b_qkv.dtype)
         g_qkv = _wgrad(dqkv, n1, w_qkv, s_qkv)
         dn1 = basic.linear_dgrad(dqkv, w_qkv)
         del dqkv
         dh, dw1 = basic.rmsnorm_bwd(dn1, h, w_ln1, rstd1, dres=dh1)
         g_ln1 = _vec_grad(dw1, w_ln1, s_ln1)
-        return dh, None, None, None, g_ln1, g_qkv, g_o, g_ln2, g_gu, g_d, None
+        return dh, None, None, None, g_ln1, g_qkv, g_o, g_ln2, g_gu, g_d, None, g_b
 
 
 class FinalNormFn(torch.autograd.Function):
@@ -275,6 +310,8 @@ class LlamaDecoderLayer(nn.Module):
         kw = dict(dtype=dtype, device=device)
         self.input_layernorm = nn.Parameter(torch.ones(h, **kw))
         self.qkv_proj = nn.Parameter(torch.empty(cfg.q_size + 2 * cfg.kv_size, h, **kw))
+        if cfg.attention_bias:
+            self.qkv_bias = nn.Parameter(torch.zeros(cfg.q_size + 2 * cfg.kv_size, **kw))
         self.o_proj = nn.Parameter(torch.empty(h, cfg.q_size, **kw))
         self.post_attention_layernorm = nn.Parameter(torch.ones(h, **kw))
         self.gate_up_proj = nn.Parameter(torch.empty(2 * f, h, **kw))
@@ -304,7 +341,12 @@ class LlamaModel(nn.Module):
     def init_weights(self, seed: int = 0, std: float = 0.02) -> "LlamaModel":
         gens: dict = {}
         for name, p in self.named_parameters():
-            if p.dim() == 1:
+            if name.endswith("qkv_bias"):
+                dev = p.device
+                if dev not in gens:
+                    gens[dev] = torch.Generator(device=dev).manual_seed(seed)
+                p.normal_(mean=0.0, std=std, generator=gens[dev])
+            elif p.dim() == 1:
                 p.fill_(1.0)
             else:
                 dev = p.device
@@ -334,7 +376,8 @@ class LlamaModel(nn.Module):
                 bool(self.grad_checkpointing and torch.is_grad_enabled()))
         for layer in self.layers:
             h = DecoderLayerFn.apply(h, pos, cos, sin, layer.input_layernorm, layer.qkv_proj, layer.o_proj,
-                                     layer.post_attention_layernorm, layer.gate_up_proj, layer.down_proj, meta)
+                                     layer.post_attention_layernorm, layer.gate_up_proj, layer.down_proj, meta,
+                                     getattr(layer, "qkv_bias", None))
         return FinalNormFn.apply(h, self.norm, cfg.rms_norm_eps)
 
     def forward(self, input_ids: torch.Tensor) -> torch.Tensor:
@@ -355,6 +398,10 @@ class LlamaModel(nn.Module):
             yield pre + "self_attn.q_proj.weight", l.qkv_proj, slice(0, q)
             yield pre + "self_attn.k_proj.weight", l.qkv_proj, slice(q, q + kv)
             yield pre + "self_attn.v_proj.weight", l.qkv_proj, slice(q + kv, q + 2 * kv)
+            if cfg.attention_bias:
+                yield pre + "self_attn.q_proj.bias", l.qkv_bias, slice(0, q)
+                yield pre + "self_attn.k_proj.bias", l.qkv_bias, slice(q, q + kv)
+                yield pre + "self_attn.v_proj.bias", l.qkv_bias, slice(q + kv, q + 2 * kv)
             yield pre + "self_attn.o_proj.weight", l.o_proj, None
             yield pre + "post_attention_layernorm.weight", l.post_attention_layernorm, None
             yield pre + "mlp.gate_proj.weight", l.gate_up_proj, slice(0, f)

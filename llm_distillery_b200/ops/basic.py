@@ -187,6 +187,37 @@ def rope_(x: torch.Tensor, pos: torch.Tensor, cos: torch.Tensor, sin: torch.Tens
     return x
 
 
+# ------------------------------------------------------------------------------------------------ bias
+_lib.register("b200_bias_add", [_lib._VP, _lib._VP, _lib._LL, _lib._I, _lib._LL, _lib._VP])
+_lib.register("b200_bias_grad", [_lib._VP, _lib._VP, _lib._LL, _lib._I, _lib._LL, _lib._I, _lib._VP])
+
+
+def bias_add_(x: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+    """x[T, N] += bias[N] in place (the q/k/v projection bias of Qwen2-style attention)."""
+    if not _native(x):
+        x.add_(bias.to(x.dtype))
+        return x
+    T, N = x.shape
+    _lib.check(_lib.kernels().b200_bias_add(_lib.ptr(x), _lib.ptr(bias), T, N, x.stride(0), _lib.stream()),
+               "b200_bias_add")
+    return x
+
+
+def bias_grad(dy: torch.Tensor, out: torch.Tensor | None = None, accumulate: bool = False) -> torch.Tensor:
+    """fp32 column sums of dy[T, N]; with ``out`` they are written (or added) there."""
+    T, N = dy.shape
+    if out is None:
+        out = torch.zeros(N, dtype=torch.float32, device=dy.device)
+        accumulate = True
+    if not _native(dy):
+        g = dy.float().sum(0)
+        out.copy_(out + g if accumulate else g)
+        return out
+    _lib.check(_lib.kernels().b200_bias_grad(_lib.ptr(dy), _lib.ptr(out), T, N, dy.stride(0), int(accumulate),
+                                             _lib.stream()), "b200_bias_grad")
+    return out
+
+
 # ------------------------------------------------------------------------------------------------ SwiGLU
 def swiglu_fwd(gu: torch.Tensor) -> torch.Tensor:
     """act[T,f] = silu(gu[:, :f]) * gu[:, f:]"""

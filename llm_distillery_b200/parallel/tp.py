@@ -222,6 +222,11 @@ def shard_llama_weights(cfg, sd: dict, rank: int, tp: int, vocab: int | None = N
         q, k, v = qkv[: H * d], qkv[H * d:(H + Hkv) * d], qkv[(H + Hkv) * d:]
         out[p + "qkv_proj"] = torch.cat([q[rank * Hl * d:(rank + 1) * Hl * d], k[rank * Hkvl * d:(rank + 1) * Hkvl * d],
                                          v[rank * Hkvl * d:(rank + 1) * Hkvl * d]], 0).contiguous()
+        if p + "qkv_bias" in sd:
+            bq = sd[p + "qkv_bias"]
+            out[p + "qkv_bias"] = torch.cat([bq[: H * d][rank * Hl * d:(rank + 1) * Hl * d],
+                                             bq[H * d:(H + Hkv) * d][rank * Hkvl * d:(rank + 1) * Hkvl * d],
+                                             bq[(H + Hkv) * d:][rank * Hkvl * d:(rank + 1) * Hkvl * d]]).contiguous()
         out[p + "o_proj"] = sd[p + "o_proj"][:, rank * Hl * d:(rank + 1) * Hl * d].contiguous()
         gu = sd[p + "gate_up_proj"]
         out[p + "gate_up_proj"] = torch.cat([gu[rank * fl:(rank + 1) * fl], gu[f + rank * fl: f + (rank + 1) * fl]],
@@ -315,6 +320,8 @@ class TPLlama:
             p = f"layers.{i}."
             basic.rmsnorm_fwd(x, w[p + "input_layernorm"], eps, out=g.slab(T, h))
             qkv = g.ag_gemm(w[p + "qkv_proj"], T)
+            if p + "qkv_bias" in w:
+                basic.bias_add_(qkv, w[p + "qkv_bias"])
             basic.rope_(qkv, pos, cos, sin, Hl + Hkvl, d)
             att, _ = attention.attention_fwd(qkv, B, L, Hl, Hkvl, d)
             x = g.gemm_rs(att, w[p + "o_proj"], residual=x)

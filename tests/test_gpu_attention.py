@@ -7,7 +7,7 @@ from llm_distillery_b200.ops import attention, _lib
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
-CASES = [(1, 128, 2, 1, 64), (2, 256, 4, 2, 64), (2, 384, 8, 2, 64), (1, 200, 4, 4, 64), (3, 1024, 4, 1, 64),
+CASES = [(1, 128, 1, 1, 64), (1, 128, 2, 1, 64), (2, 256, 4, 2, 64), (2, 384, 8, 2, 64), (1, 200, 4, 4, 64), (3, 1024, 4, 1, 64),
          (1, 128, 2, 1, 128), (2, 320, 4, 2, 128), (1, 1024, 8, 2, 128)]
 
 

@@ -91,3 +91,24 @@ def test_casts():
     basic.cast_to_f32(o, acc, 2.0, accumulate=True)
     assert torch.allclose(acc, 1 + o.float() * 2)
     assert _lib.take_device_error() == 0
+
+
+@pytest.mark.parametrize("T,N", [(5, 64), (1000, 2560), (4097, 1152)])
+def test_bias_add_and_grad(T, N):
+    torch.manual_seed(4)
+    wide = torch.randn(T, N + 16, device=DEV).bfloat16()       # row-padded view: the stride is not the width
+    x = wide[:, :N]
+    b = torch.randn(N, device=DEV).bfloat16()
+    ref = (x.float() + b.float()).bfloat16()
+    keep = wide[:, N:].clone()
+    basic.bias_add_(x, b)
+    assert torch.equal(x, ref) and torch.equal(wide[:, N:], keep)
+    dy = torch.randn(T, N, device=DEV).bfloat16()
+    g = basic.bias_grad(dy)
+    r = dy.float().sum(0)
+    assert torch.allclose(g, r, atol=2e-3 * T ** 0.5, rtol=1e-3)
+    acc = torch.full((N,), 2.0, device=DEV)
+    basic.bias_grad(dy, out=acc, accumulate=True)
+    assert torch.allclose(acc, r + 2.0, atol=2e-3 * T ** 0.5, rtol=1e-3)
+    basic.bias_grad(dy, out=acc, accumulate=False)
+    assert torch.allclose(acc, r, atol=2e-3 * T ** 0.5, rtol=1e-3)

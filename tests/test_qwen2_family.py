@@ -1,0 +1,91 @@
+"""Qwen2-style attention (bias on the q/k/v projections): the fused-QKV model equals HuggingFace's Qwen2ForCausalLM in
+logits and gradients, round-trips through the HF checkpoint layout, and trains through the engine."""
+import pytest
+import torch
+
+from llm_distillery_b200.ckpt.hf import load_hf_model, save_hf_model
+from llm_distillery_b200.engine.trainer import DistillEngine, synthetic_batch
+from llm_distillery_b200.models.llama import LlamaConfig, build_model
+
+CFG = LlamaConfig(vocab_size=320, hidden_size=64, intermediate_size=136, num_hidden_layers=2, num_attention_heads=4,
+                  num_key_value_heads=2, max_position_embeddings=64, rope_theta=1e6, rms_norm_eps=1e-6,
+                  attention_bias=True, model_type="qwen2", tie_word_embeddings=False)
+
+
+def _hf_twin(model):
+    tr = pytest.importorskip("transformers")
+    hf_cfg = tr.Qwen2Config(vocab_size=CFG.vocab_size, hidden_size=CFG.hidden_size, intermediate_size=CFG.intermediate_size,
+                            num_hidden_layers=CFG.num_hidden_layers, num_attention_heads=CFG.num_attention_heads,
+                            num_key_value_heads=CFG.num_key_value_heads, max_position_embeddings=64, rope_theta=1e6,
+                            rms_norm_eps=1e-6, tie_word_embeddings=False, use_sliding_window=False,
+                            attn_implementation="eager")
+    hf = tr.Qwen2ForCausalLM(hf_cfg).float()
+    missing = hf.load_state_dict({k: v.clone() for k, v in model.to_hf_state_dict().items()}, strict=False)
+    assert not [k for k in missing.missing_keys if "rotary" not in k], missing
+    return hf
+
+
+def test_logits_and_gradients_match_huggingface_qwen2():
+    torch.manual_seed(0)
+    model = build_model(CFG, dtype=torch.float32, device="cpu", seed=3)
+    hf = _hf_twin(model)
+    x = torch.randint(0, CFG.vocab_size, (2, 24))
+    ours = model(x)
+    ref = hf(x).logits
+    assert torch.allclose(ours, ref, atol=2e-4, rtol=1e-3), (ours - ref).abs().max()
+    ours.square().mean().backward()
+    ref.square().mean().backward()
+    b = model.layers[1].qkv_bias.grad
+    q = CFG.q_size
+    assert torch.allclose(b[:q], hf.model.layers[1].self_attn.q_proj.bias.grad, atol=1e-6, rtol=1e-3)
+    assert torch.allclose(b[q + CFG.kv_size:], hf.model.layers[1].self_attn.v_proj.bias.grad, atol=1e-6, rtol=1e-3)
+    w = model.layers[0].qkv_proj.grad
+    assert torch.allclose(w[:q], hf.model.layers[0].self_attn.q_proj.weight.grad, atol=1e-6, rtol=1e-3)
+
+
+def test_checkpoint_round_trip_and_config_say_qwen2(tmp_path):
+    model = build_model(CFG, dtype=torch.float32, device="cpu", seed=4)
+    save_hf_model(model, str(tmp_path / "m"))
+    import json
+    c = json.load(open(tmp_path / "m" / "config.json"))
+    assert c["model_type"] == "qwen2" and c["architectures"] == ["Qwen2ForCausalLM"]
+    back = load_hf_model(str(tmp_path / "m"), dtype=torch.float32)
+    assert back.cfg.attention_bias and torch.equal(back.layers[1].qkv_bias, model.layers[1].qkv_bias)
+    tr = pytest.importorskip("transformers")
+    hf = tr.AutoModelForCausalLM.from_pretrained(str(tmp_path / "m"), torch_dtype=torch.float32)
+    x = torch.randint(0, CFG.vocab_size, (1, 10))
+    assert torch.allclose(hf(x).logits, model(x), atol=2e-4, rtol=1e-3)
+
+
+def test_engine_trains_the_bias():
+    model = build_model(CFG, dtype=torch.float32, device="cpu", seed=5)
+    before = model.layers[0].qkv_bias.detach().clone()
+    eng = DistillEngine(model, loss="kl", temperature=1.0, optimizer="adamw", lr=1e-2)
+    hb = synthetic_batch(CFG.vocab_size, 2, 32, 8, seed=1)
+    l0 = float(eng.train_step([hb]))
+    for _ in range(5):
+        l1 = float(eng.train_step([hb]))
+    assert l1 < l0 and not torch.equal(model.layers[0].qkv_bias, before)
+
+
+@pytest.mark.gpu
+def test_gpu_kernels_follow_the_cpu_model():
+    """bf16 kernels (GEMM + bias add + RoPE + flash attention ...) against the fp32 CPU statement of the same model."""
+    cfg = LlamaConfig(vocab_size=512, hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=2, max_position_embeddings=256, rope_theta=1e6, rms_norm_eps=1e-6,
+                      attention_bias=True, model_type="qwen2")
+    cpu = build_model(cfg, dtype=torch.float32, device="cpu", seed=7)
+    gpu = build_model(cfg, dtype=torch.bfloat16, device="cuda", seed=7)
+    with torch.no_grad():
+        for a, b in zip(gpu.parameters(), cpu.parameters()):
+            a.copy_(b.to(torch.bfloat16))
+            b.copy_(a.float().cpu())          # both sides hold the bf16-rounded weights
+    x = torch.randint(0, cfg.vocab_size, (2, 128))
+    lc = cpu(x)
+    lg = gpu(x.cuda())
+    assert torch.allclose(lg.float().cpu(), lc, atol=6e-2, rtol=5e-2), (lg.float().cpu() - lc).abs().max()
+    lc.square().mean().backward()
+    lg.float().square().mean().backward()
+    gb_c = cpu.layers[0].qkv_bias.grad
+    gb_g = gpu.layers[0].qkv_bias.grad.float().cpu()
+    assert (gb_g - gb_c).abs().max() <= 0.05 * gb_c.abs().max() + 1e-4
