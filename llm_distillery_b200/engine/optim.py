@@ -79,6 +79,18 @@ class FlatParams:
                 p.grad_slot = slot
                 self.slots.append(slot)
         self.master = self.model[self.shard_lo:self.shard_lo + self.shard_size].float().clone()
+        self._offset_by_id = {id(p): o for p, o in zip(uniq, self.offsets)}
+
+    def offset_of(self, p) -> int | None:
+        """Offset of a parameter in the flat space (None: not a trainable parameter of this engine)."""
+        return self._offset_by_id.get(id(p))
+
+    def zero_untouched_in(self, lo: int, hi: int) -> None:
+        """``untouched_to_zero`` restricted to the parameters that start in [lo, hi)."""
+        for s, o in zip(self.slots, self.offsets):
+            if lo <= o < hi and s.fresh:
+                s.buf.zero_()
+                s.fresh = False
 
     def absorb_autograd_grads(self) -> None:
         """Fold gradients that autograd left in ``p.grad`` (ops without a fused wgrad epilogue, e.g. the PyTorch

@@ -91,11 +91,29 @@ class DistillEngine:
     def micro_step(self, mb: HostBatch):
         with self.timer.phase("forward+loss"):
             loss, logs = self.loss_on_batch(mb)
-        with self.timer.phase("backward"):
-            loss.backward()
-            self.flat.absorb_autograd_grads()
+        # last micro-batch of the step under a communicator that can do it: the gradient of each layer is reduced
+        # (and its shard of the weights updated) as soon as that layer's backward is through, behind the backward
+        # of the earlier layers
+        overlap = (self.comm is not None and getattr(self.comm, "supports_overlap", False)
+                   and self.micro_in_step + 1 == self.grad_accum)
+        if overlap:
+            from ..models import llama as _llama
+            self.comm.begin_overlap(self.lr, 1.0 / self.grad_accum)
+            _llama.LAYER_BACKWARD_DONE[0] = self._layer_done
+        try:
+            with self.timer.phase("backward"):
+                loss.backward()
+                self.flat.absorb_autograd_grads()
+        finally:
+            if overlap:
+                _llama.LAYER_BACKWARD_DONE[0] = None
         self.micro_in_step += 1
         return loss.detach(), logs
+
+    def _layer_done(self, first_param) -> None:
+        off = self.flat.offset_of(first_param)
+        if off is not None:
+            self.comm.range_ready(off)
 
     @property
     def lr(self) -> float:

@@ -191,6 +191,12 @@ class EmbeddingFn(torch.autograd.Function):
         return None, dw.to(w.dtype)
 
 
+# Called with a layer's first parameter when that layer's backward has produced all its weight gradients (and, since
+# backward runs from the last layer to the first, those of every later layer): the data-parallel engine starts
+# reducing that part of the gradient while the earlier layers are still in backward.
+LAYER_BACKWARD_DONE = [None]
+
+
 class DecoderLayerFn(torch.autograd.Function):
     """h_out = h + Attn(RMSNorm(h)) ; then + MLP(RMSNorm(.)) - one node, explicit backward."""
 
@@ -268,6 +274,8 @@ class DecoderLayerFn(torch.autograd.Function):
         del dqkv
         dh, dw1 = basic.rmsnorm_bwd(dn1, h, w_ln1, rstd1, dres=dh1)
         g_ln1 = _vec_grad(dw1, w_ln1, s_ln1)
+        if LAYER_BACKWARD_DONE[0] is not None:
+            LAYER_BACKWARD_DONE[0](w_ln1)
         return dh, None, None, None, g_ln1, g_qkv, g_o, g_ln2, g_gu, g_d, None, g_b
 
 

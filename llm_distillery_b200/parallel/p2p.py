@@ -61,6 +61,15 @@ class P2PComm:
         self.opt = None
         self.epoch = 0
         self.sig = SymmetricBuffer(64, torch.int32, self.device)
+        # gradient reduction behind backward: its own stream, flag words and epoch counter (barriers of the two
+        # streams must not share flags: a flag holds the latest epoch, and the streams run in no fixed order)
+        self.sig_side = SymmetricBuffer(64, torch.int32, self.device)
+        self.side_epoch = 0
+        self.side = torch.cuda.Stream(device=self.device)
+        self._ov = None
+        import os
+        self._overlap_enabled = os.environ.get("B200_NO_OVERLAP", "0") != "1"
+        self._buckets = max(1, int(os.environ.get("B200_OVERLAP_BUCKETS", "4")))   # ranges per step handed over early
         self.grad_buf = None
         self.model_buf = None
         torch.cuda.synchronize(self.device)
@@ -123,12 +132,68 @@ class P2PComm:
         self.barrier()
         return buf.tensor
 
+    # ---- gradient reduction overlapped with backward (fp32-state Adam family only)
+    def _fused(self) -> bool:
+        return (self.opt.name in ("adam", "adamw", "adamw32bit", "paged_adamw", "paged_adamw32bit")
+                and self.flat.dtype == torch.bfloat16)
+
+    @property
+    def supports_overlap(self) -> bool:
+        return self._overlap_enabled and self.world > 1 and self.flat is not None and self._fused()
+
+    def begin_overlap(self, lr: float, grad_scale: float) -> None:
+        """Before the last backward of a step: from now on ``range_ready(lo)`` may hand over finished gradients."""
+        self.opt.step_count += 1
+        self._ov = {"lr": lr, "gs": grad_scale / self.world, "hi": self.flat.total}
+
+    def range_ready(self, lo: int) -> None:
+        """Flat offsets >= lo hold final gradients on THIS rank. Every rank calls this with the same offsets in the
+        same order; the range [lo, previous lo) is reduced on the side stream once every rank has got there."""
+        ov = self._ov
+        if ov is None or lo >= ov["hi"]:
+            return
+        if ov["hi"] - lo < self.flat.total // (self._buckets + 1):
+            return          # too little for a launch of its own: goes with the next layer(s)
+        hi, ov["hi"] = ov["hi"], lo
+        self._launch_range(lo, hi)
+
+    def _launch_range(self, lo: int, hi: int) -> None:
+        f, opt, ov = self.flat, self.opt, self._ov
+        f.zero_untouched_in(lo, hi)
+        a, b = max(lo, f.shard_lo), min(hi, f.shard_lo + f.shard_size)
+        ev = torch.cuda.Event()
+        ev.record()                                   # this rank's gradients of the range are complete here
+        with torch.cuda.stream(self.side):
+            self.side.wait_event(ev)
+            self.side_epoch += 1                      # every rank takes part, also with an empty intersection
+            _lib.check(_lib.kernels().b200_p2p_barrier(self.sig_side.c_ptrs, self.rank, self.world, self.side_epoch,
+                                                       _lib.stream()), "b200_p2p_barrier")
+            if b > a:
+                o = a - f.shard_lo
+                b1, b2 = opt.betas
+                st = opt.state
+                _lib.check(_lib.kernels().b200_p2p_rs_adamw_ag(
+                    self.grad_buf.c_ptrs, self.model_buf.c_ptrs, _lib.ptr(f.master[o:]), _lib.ptr(st["m"][o:]),
+                    _lib.ptr(st["v"][o:]), a, b - a, self.rank, self.world, ov["lr"], b1, b2, opt.eps,
+                    opt.weight_decay, opt.step_count, ov["gs"], int(opt.decoupled), _lib.stream()),
+                    "b200_p2p_rs_adamw_ag")
+
     # ---- the optimizer step
     def reduce_and_step(self, lr: float, grad_scale: float) -> None:
         f, opt = self.flat, self.opt
         gs = grad_scale / self.world
+        if self._ov is not None:
+            # the tail of the flat space (first layers, embedding) and then: everything of the side stream is done,
+            # and every rank's weight stores have landed, before the next forward reads the weights
+            self._launch_range(0, self._ov["hi"])
+            self._ov = None
+            done = torch.cuda.Event()
+            done.record(self.side)
+            torch.cuda.current_stream().wait_event(done)
+            self.barrier()
+            return
         self.barrier()
-        fused = opt.name in ("adam", "adamw", "adamw32bit", "paged_adamw", "paged_adamw32bit") and f.dtype == torch.bfloat16
+        fused = self._fused()
         if fused:
             opt.step_count += 1
             b1, b2 = opt.betas
