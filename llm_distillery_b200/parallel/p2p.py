@@ -68,7 +68,10 @@ class P2PComm:
         self.side = torch.cuda.Stream(device=self.device)
         self._ov = None
         import os
-        self._overlap_enabled = os.environ.get("B200_NO_OVERLAP", "0") != "1"
+        # off by default: on 2 and 8 B200s the step was 1-2 % SLOWER with the reduction running beside backward (the
+        # side-stream kernel competes with the backward GEMMs for HBM and SM slots, and the reduction it hides is
+        # only ~4 % of the step); B200_OVERLAP=1 turns it on
+        self._overlap_enabled = os.environ.get("B200_OVERLAP", "0") == "1"
         self._buckets = max(1, int(os.environ.get("B200_OVERLAP_BUCKETS", "4")))   # ranges per step handed over early
         self.grad_buf = None
         self.model_buf = None

@@ -29,10 +29,12 @@ def test_cpu_ranks_ddp_and_fsdp_match_single_process():
 
 
 @pytest.mark.gpu
-def test_p2p_collectives_and_training_match_nccl():
+@pytest.mark.parametrize("overlap", ["0", "1"])
+def test_p2p_collectives_and_training_match_nccl(overlap):
+    """overlap = 1: the gradient reduction runs behind backward on a side stream (off by default)."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs at least 2 GPUs")
-    _launch("gpu_p2p", min(4, torch.cuda.device_count()), env={"NCCL_NVLS_ENABLE": "0"})
+    _launch("gpu_p2p", min(4, torch.cuda.device_count()), env={"NCCL_NVLS_ENABLE": "0", "B200_OVERLAP": overlap})
 
 
 def test_cpu_ranks_tensor_parallel_teacher_matches_unsharded():
