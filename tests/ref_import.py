@@ -8,8 +8,11 @@ import types
 
 import pytest
 
-_CANDIDATES = [os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "baseline", "_ref"),
-               "/root/reference"]
+# where a copy of the reference tree may be: the optional in-repo install, a directory named by the environment, or a
+# "reference" folder beside the repository
+_REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+_CANDIDATES = [os.path.join(_REPO, "baseline", "_ref"), os.environ.get("LLM_DISTILLERY_REFERENCE", ""),
+               os.path.join(os.path.dirname(_REPO), "reference")]
 
 
 def reference_root():
