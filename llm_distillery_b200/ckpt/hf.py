@@ -82,8 +82,11 @@ def load_hf_model(path: str, dtype: torch.dtype = torch.bfloat16, device="cpu") 
 
 # ------------------------------------------------------------------------------------------------- trainer state
 def save_trainer_state(states_dir: str, model: LlamaModel, optimizer, schedule, counters: dict) -> None:
+    """``model`` None: this rank writes no ``model_state.pt`` (another rank does, or the weights cannot be had)."""
     os.makedirs(states_dir, exist_ok=True)
-    torch.save({k: v.detach().cpu() for k, v in model.to_hf_state_dict().items()}, os.path.join(states_dir, "model_state.pt"))
+    if model is not None:
+        torch.save({k: v.detach().cpu() for k, v in model.to_hf_state_dict().items()},
+                   os.path.join(states_dir, "model_state.pt"))
     osd = optimizer.state_dict()
     osd = {k: (v.detach().cpu() if isinstance(v, torch.Tensor) else
                ({kk: vv.detach().cpu() for kk, vv in v.items()} if isinstance(v, dict) else v)) for k, v in osd.items()}
@@ -122,6 +125,8 @@ def reshard_optimizer_state(shards: list[dict], optimizer) -> bool:
     old_size = int(shards[0]["total"]) // len(shards)
     if shards[0]["name"] != optimizer.name:
         return False
+    if shards[0].get("layout", "contiguous") != "contiguous" or getattr(flat, "layout", "contiguous") != "contiguous":
+        return False        # per-unit pieces (full sharding) are not slices of one flat space
     keys = list(shards[0]["state"].keys())
     for sd in shards:
         if sd["master"].numel() != old_size or any(
@@ -145,15 +150,22 @@ def reshard_optimizer_state(shards: list[dict], optimizer) -> bool:
     return True
 
 
-def load_trainer_state(states_dir: str, model: LlamaModel, optimizer, schedule) -> dict:
+def load_model_state(states_dir: str, model: LlamaModel) -> None:
     model.load_hf_state_dict(torch.load(os.path.join(states_dir, "model_state.pt"), map_location="cpu"), strict=False)
+
+
+def load_trainer_state(states_dir: str, model: LlamaModel | None, optimizer, schedule) -> dict:
+    """``model`` None: the weights have been loaded already (``load_model_state``)."""
+    if model is not None:
+        load_model_state(states_dir, model)
     shard = optimizer.state_dict()["shard"]
     name = "optimizer_state.pt" if shard[1] == 1 else f"optimizer_state.rank{shard[0]}.pt"
     p = os.path.join(states_dir, name)
     done = False
     if os.path.exists(p):
         osd = torch.load(p, map_location=optimizer.flat.device)
-        if tuple(osd["shard"]) == tuple(shard) and osd["total"] == optimizer.flat.total:
+        if (tuple(osd["shard"]) == tuple(shard) and osd["total"] == optimizer.flat.total
+                and osd.get("layout", "contiguous") == getattr(optimizer.flat, "layout", "contiguous")):
             optimizer.load_state_dict(osd)
             done = True
     if not done:    # saved under another world size: cut this rank's slice out of the saved ones

@@ -228,7 +228,8 @@ class FlatOptimizer:
 
     def state_dict(self) -> dict:
         return {"name": self.name, "step_count": self.step_count, "lr": self.lr, "master": self.flat.master,
-                "state": dict(self.state), "shard": (self.flat.rank, self.flat.world), "total": self.flat.total}
+                "state": dict(self.state), "shard": (self.flat.rank, self.flat.world), "total": self.flat.total,
+                "layout": getattr(self.flat, "layout", "contiguous")}
 
     def load_state_dict(self, sd: dict) -> None:
         if sd["name"] != self.name:

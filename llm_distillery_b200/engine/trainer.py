@@ -70,9 +70,13 @@ class DistillEngine:
         self.comm = comm
         self.jsd_renorm = jsd_renorm
         self.device = model.embed_tokens.device
-        shard = (comm.rank, comm.world) if comm is not None and comm.shards_optimizer else (0, 1)
-        buffers = comm.allocate_flat_buffers(model) if comm is not None else None
-        self.flat = FlatParams([p for p in model.parameters() if p.requires_grad], shard=shard, buffers=buffers)
+        if comm is not None and getattr(comm, "full_shard", False):
+            # weights, gradients and optimizer state all sharded: the communicator owns the layout (parallel/fsdp.py)
+            self.flat = comm.build_flat(model)
+        else:
+            shard = (comm.rank, comm.world) if comm is not None and comm.shards_optimizer else (0, 1)
+            buffers = comm.allocate_flat_buffers(model) if comm is not None else None
+            self.flat = FlatParams([p for p in model.parameters() if p.requires_grad], shard=shard, buffers=buffers)
         self.opt = FlatOptimizer(self.flat, optimizer, lr=lr, betas=betas, weight_decay=weight_decay)
         if comm is not None:
             comm.attach(self.flat, self.opt)
@@ -114,6 +118,20 @@ class DistillEngine:
         off = self.flat.offset_of(first_param)
         if off is not None:
             self.comm.range_ready(off)
+
+    def idle_micro_step(self) -> None:
+        """This rank has no micro-batch where other ranks have one: under full sharding it still takes part in their
+        collectives; otherwise nothing to do."""
+        if self.comm is not None and hasattr(self.comm, "idle_micro_step"):
+            self.comm.idle_micro_step()
+
+    def full_parameters(self, writeback: bool = False):
+        """Context in which every parameter holds its whole current value (checkpoint save / load). All ranks enter
+        together under full sharding; a no-op otherwise."""
+        if self.comm is not None and hasattr(self.comm, "gathered"):
+            return self.comm.gathered(writeback=writeback)
+        import contextlib
+        return contextlib.nullcontext()
 
     @property
     def lr(self) -> float:

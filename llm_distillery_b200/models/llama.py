@@ -196,6 +196,11 @@ class EmbeddingFn(torch.autograd.Function):
 # reducing that part of the gradient while the earlier layers are still in backward.
 LAYER_BACKWARD_DONE = [None]
 
+# Called with (parameter, backward) just before a unit of the model - the embedding, a decoder layer, the final norm
+# + head - reads its parameters, in forward and again at the start of a layer's backward: the full-shard engine
+# (parallel/fsdp.py) gathers that unit's weights there and starts gathering the next one.
+UNIT_PRE = [None]
+
 
 class DecoderLayerFn(torch.autograd.Function):
     """h_out = h + Attn(RMSNorm(h)) ; then + MLP(RMSNorm(.)) - one node, explicit backward."""
@@ -230,6 +235,8 @@ class DecoderLayerFn(torch.autograd.Function):
         B, L, H, Hkv, d, eps, recompute = ctx.meta
         w_ln1, w_qkv, w_o, w_ln2, w_gu, w_d = ctx.weights
         s_ln1, s_qkv, s_o, s_ln2, s_gu, s_d = ctx.slots
+        if UNIT_PRE[0] is not None:
+            UNIT_PRE[0](w_ln1, True)
         if recompute:
             h, pos, cos, sin = ctx.saved_tensors
             n1, _, rstd1 = basic.rmsnorm_fwd(h, w_ln1, eps)
@@ -379,13 +386,20 @@ class LlamaModel(nn.Module):
         ids = input_ids.reshape(-1).to(dev)
         pos = torch.arange(L, dtype=torch.int32, device=dev).repeat(B)
         cos, sin = self.rope(dev, L)
+        pre = UNIT_PRE[0]
+        if pre is not None:
+            pre(self.embed_tokens, False)
         h = EmbeddingFn.apply(ids, self.embed_tokens)
         meta = (B, L, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.rms_norm_eps,
                 bool(self.grad_checkpointing and torch.is_grad_enabled()))
         for layer in self.layers:
+            if pre is not None:
+                pre(layer.input_layernorm, False)
             h = DecoderLayerFn.apply(h, pos, cos, sin, layer.input_layernorm, layer.qkv_proj, layer.o_proj,
                                      layer.post_attention_layernorm, layer.gate_up_proj, layer.down_proj, meta,
                                      getattr(layer, "qkv_bias", None))
+        if pre is not None:
+            pre(self.norm, False)
         return FinalNormFn.apply(h, self.norm, cfg.rms_norm_eps)
 
     def forward(self, input_ids: torch.Tensor) -> torch.Tensor:

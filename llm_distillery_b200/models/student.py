@@ -181,10 +181,10 @@ class StudentModel(BaseModel):
 
     # ------------------------------------------------------------------ checkpoints
     def _save_model(self, step) -> None:
-        if self.rank != 0:
-            return
         folder = os.path.join(self.paths.student_trained, f"{self.model_name}_step_{step}")
-        ckpt.save_hf_model(self.model, folder, tokenizer_src=self.tokenizer_dir)
+        with self.engine.full_parameters():       # every rank: under full sharding the weights are gathered first
+            if self.rank == 0:
+                ckpt.save_hf_model(self.model, folder, tokenizer_src=self.tokenizer_dir)
 
     def _counters(self) -> dict:
         return {"num_trained_steps": self.num_trained_steps, "next_save_step": self.next_save_step,
@@ -197,13 +197,22 @@ class StudentModel(BaseModel):
             self.paths.empty_student_states()
         if collective and self.comm is not None:
             self.comm.barrier()
-        if self.rank == 0 or (self.comm is not None and self.comm.shards_optimizer):
-            ckpt.save_trainer_state(self.paths.student_states, self.model, self.engine.opt, self.engine.schedule,
+        mine = self.rank == 0 or (self.comm is not None and self.comm.shards_optimizer)
+        if not collective and getattr(self.comm, "full_shard", False):
+            # no peer to gather the weights from: this rank's optimizer shard (with its fp32 master weights) only
+            ckpt.save_trainer_state(self.paths.student_states, None, self.engine.opt, self.engine.schedule,
                                     self._counters())
+            return
+        with self.engine.full_parameters():
+            if mine:
+                ckpt.save_trainer_state(self.paths.student_states, self.model if (self.rank == 0 or not collective) else None,
+                                        self.engine.opt, self.engine.schedule, self._counters())
 
     def _load_state(self) -> None:
         self._load_model()
-        c = ckpt.load_trainer_state(self.paths.student_states, self.model, self.engine.opt, self.engine.schedule)
+        with self.engine.full_parameters(writeback=True):
+            ckpt.load_model_state(self.paths.student_states, self.model)
+        c = ckpt.load_trainer_state(self.paths.student_states, None, self.engine.opt, self.engine.schedule)
         for k in ("num_trained_steps", "next_save_step", "next_val_step", "next_accum_step"):
             if k in c:
                 setattr(self, k, c[k])
@@ -309,6 +318,8 @@ class StudentModel(BaseModel):
                 loss, logs = self.engine.micro_step(mb)
                 self.losses.add_losses(logs, count=len(convos))
                 self.tokens_trained += hb.n_tokens
+            else:
+                self.engine.idle_micro_step()
             self.progress_bar.update(n_samples)
             self.num_trained_steps += n_samples
             if self.num_trained_steps >= self.next_accum_step:

@@ -5,6 +5,9 @@ rank runs the same full optimizer step (``ddp``) - or, with ``shard_strategy="fs
 gradient, update only the local 1/world shard of the fp32 master weights / optimizer state, and all-gather the
 updated weights (ZeRO-style sharding of optimizer state; the model-dtype weights stay replicated).
 
+``FullShardComm`` (``parallel/fsdp.py``, ``shard_strategy="zero3"``) also shards the weights and gradients: each unit
+of the model is all-gathered just before it runs and its gradient reduce-scattered right after its backward.
+
 ``P2PComm`` (``parallel/p2p.py``) is the NVLink path: gradient and weight buffers live in symmetric memory and ONE
 kernel per step reads every peer's gradient shard over NVLink, applies AdamW to the local shard and stores the new
 weights into every peer's weight buffer.
@@ -60,6 +63,9 @@ NcclComm = AllReduceComm
 def make_comm(kind: str, device, shard_strategy: str = "ddp"):
     if not dist.is_initialized() or dist.get_world_size() == 1:
         return None
+    if shard_strategy == "zero3":
+        from .fsdp import FullShardComm
+        return FullShardComm(device)
     if kind in ("nccl", "gloo") or torch.device(device).type != "cuda":
         return AllReduceComm(device, shard_strategy)
     from .p2p import P2PComm

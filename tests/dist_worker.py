@@ -1,6 +1,10 @@
 """Worker run under torch.distributed.run by tests/test_dist.py. Modes:
   cpu_engine  gloo ranks on CPU: ddp and fsdp(all-reduce comm) training equals single-process training on the
               concatenated micro-batches
+  cpu_zero3   gloo ranks on CPU: full parameter sharding (weights gathered per unit, gradients reduce-scattered per
+              layer) equals single-process training, with gradient accumulation, an evaluation between steps, a rank
+              without a micro-batch, tied embeddings, a frozen layer and a checkpoint taken through the gathered view
+  gpu_zero3   NCCL ranks: full parameter sharding equals the replicated NCCL run
   gpu_p2p     NCCL + NVLink P2P ranks: P2P all-reduce equals NCCL all-reduce; a P2P-communicated training run equals
               the NCCL-communicated one
   cpu_tp      gloo ranks on CPU: the tensor-parallel teacher's top-K log-probs equal the unsharded model's
@@ -57,6 +61,130 @@ def cpu_engine():
     gathered = [torch.empty_like(out["ddp"]) for _ in range(world)]
     dist.all_gather(gathered, out["fsdp"])
     assert all(torch.equal(g, gathered[0]) for g in gathered), "ranks diverged"
+    if rank == 0:
+        print("WORKER_OK")
+    dist.destroy_process_group()
+
+
+def _tiny3(dtype, device, tied):
+    cfg = LlamaConfig(vocab_size=512, hidden_size=128, intermediate_size=256, num_hidden_layers=3, num_attention_heads=2,
+                      num_key_value_heads=1, max_position_embeddings=128, tie_word_embeddings=tied)
+    return build_model(cfg, dtype=dtype, device=device, seed=7), cfg
+
+
+def _zero3_case(device, dtype, rank, world, tied, freeze, comm_factory, accum=2, steps=3, L=64):
+    """Returns (weights after training under the communicator, loss of an evaluation batch between the steps)."""
+    model, cfg = _tiny3(dtype, device, tied)
+    if freeze:
+        for p in model.layers[1].parameters():
+            p.requires_grad_(False)
+    comm = comm_factory()
+    eng = DistillEngine(model, loss="kl", temperature=2.0, optimizer="adamw", lr=1e-3, grad_accum=accum, comm=comm)
+    ev = None
+    for s in range(steps):
+        for m in range(accum):
+            if s == 1 and m == 1 and rank == world - 1 and world > 1:
+                eng.idle_micro_step()          # the last rank has no second micro-batch in step 1
+                continue
+            hb = synthetic_batch(cfg.vocab_size, 2, L, 16, seed=1000 * s + 10 * m + rank)
+            eng.micro_step(hb.to_device(device))
+        eng.optimizer_step()
+        if s == 0:
+            ev = float(eng.eval_batch(synthetic_batch(cfg.vocab_size, 2, L, 16, seed=77))[0])
+    with eng.full_parameters():
+        w = torch.cat([p.detach().float().reshape(-1).cpu() for p in model.parameters()])
+    if hasattr(comm, "close"):
+        comm.close()
+    return w, ev, eng
+
+
+def _zero3_reference(device, dtype, world, tied, freeze, accum=2, steps=3, L=64):
+    model, cfg = _tiny3(dtype, device, tied)
+    if freeze:
+        for p in model.layers[1].parameters():
+            p.requires_grad_(False)
+    eng = DistillEngine(model, loss="kl", temperature=2.0, optimizer="adamw", lr=1e-3, grad_accum=accum * world)
+    ev = None
+    for s in range(steps):
+        for m in range(accum):
+            for r in range(world):
+                if s == 1 and m == 1 and r == world - 1 and world > 1:
+                    continue
+                eng.micro_step(synthetic_batch(cfg.vocab_size, 2, L, 16, seed=1000 * s + 10 * m + r).to_device(device))
+        eng.optimizer_step()
+        if s == 0:
+            ev = float(eng.eval_batch(synthetic_batch(cfg.vocab_size, 2, L, 16, seed=77))[0])
+    return torch.cat([p.detach().float().reshape(-1).cpu() for p in model.parameters()]), ev
+
+
+def cpu_zero3():
+    dist.init_process_group("gloo")
+    rank, world = dist.get_rank(), dist.get_world_size()
+    from llm_distillery_b200.parallel.fsdp import FullShardComm
+    for tied, freeze in ((False, False), (True, False), (False, True)):
+        got, ev, eng = _zero3_case("cpu", torch.float32, rank, world, tied, freeze,
+                                   lambda: make_comm("gloo", "cpu", shard_strategy="zero3"))
+        assert isinstance(eng.comm, FullShardComm)
+        ref, ev_ref = _zero3_reference("cpu", torch.float32, world, tied, freeze)
+        err = (got - ref).abs().max().item()
+        assert err < 2e-5, (tied, freeze, err)
+        assert abs(ev - ev_ref) < 1e-4 * max(1.0, abs(ev_ref)), (ev, ev_ref)
+        flat = eng.flat
+        n_params = sum(p.numel() for p in flat.params)
+        # every rank keeps 1/world of the weights, master weights, gradient and moments
+        assert flat.master.numel() == flat.shard_size and flat.shard_size * world == flat.total
+        assert flat.shard_size < n_params / world * 1.2 + 4096
+        assert eng.opt.state["m"].numel() == flat.shard_size
+    # a checkpoint written through the gathered view loads into a fresh, differently initialised engine
+    import tempfile
+    from llm_distillery_b200.ckpt import hf as ckpt
+    d = [tempfile.mkdtemp() if rank == 0 else None]
+    dist.broadcast_object_list(d, src=0)
+    with eng.full_parameters():
+        ckpt.save_trainer_state(d[0], eng.model if rank == 0 else None, eng.opt, eng.schedule, {"k": 1})
+    dist.barrier()
+    model2, cfg = _tiny3(torch.float32, "cpu", False)
+    for p in model2.layers[1].parameters():
+        p.requires_grad_(False)
+    with torch.no_grad():
+        for p in model2.parameters():
+            p.add_(0.5)
+    eng2 = DistillEngine(model2, loss="kl", temperature=2.0, optimizer="adamw", lr=1e-3, grad_accum=2,
+                         comm=make_comm("gloo", "cpu", shard_strategy="zero3"))
+    with eng2.full_parameters(writeback=True):
+        ckpt.load_model_state(d[0], model2)
+    ckpt.load_trainer_state(d[0], None, eng2.opt, eng2.schedule)
+    assert torch.equal(eng2.flat.master, eng.flat.master) and eng2.opt.step_count == eng.opt.step_count
+    assert torch.equal(eng2.opt.state["v"], eng.opt.state["v"])
+    with eng2.full_parameters():
+        w2 = torch.cat([p.detach().float().reshape(-1) for p in model2.parameters()])
+    assert torch.equal(w2, got), (w2 - got).abs().max()
+    if rank == 0:
+        print("WORKER_OK")
+    dist.destroy_process_group()
+
+
+def gpu_zero3():
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    rank, world = dist.get_rank(), dist.get_world_size()
+    for tied in (False, True):
+        a, ev_a, eng = _zero3_case(dev, torch.bfloat16, rank, world, tied, False,
+                                   lambda: make_comm("nccl", dev, shard_strategy="zero3"), L=128)
+        b, ev_b, _ = _zero3_case(dev, torch.bfloat16, rank, world, tied, False,
+                                 lambda: make_comm("nccl", dev, shard_strategy="ddp"), L=128)
+        torch.cuda.synchronize()
+        err = (a - b).abs().max().item()
+        assert err < 2e-2, (tied, err)
+        assert abs(ev_a - ev_b) < 2e-2 * max(1.0, abs(ev_b)), (ev_a, ev_b)
+        assert eng.comm.stats["gathers"] > 0 and eng.comm.stats["reduces"] > 0
+        flat = a.to(dev)
+        parts = [torch.empty_like(flat) for _ in range(world)]
+        dist.all_gather(parts, flat)
+        assert all(torch.equal(p, parts[0]) for p in parts), "ranks hold different weights"
     if rank == 0:
         print("WORKER_OK")
     dist.destroy_process_group()
@@ -321,4 +449,4 @@ def gpu_tp():
 
 if __name__ == "__main__":
     {"cpu_engine": cpu_engine, "gpu_p2p": gpu_p2p, "cpu_tp": cpu_tp, "gpu_tp": gpu_tp, "cpu_cli_tp": cpu_cli_tp,
-     "cpu_vp_head": cpu_vp_head, "cpu_rank_loss": cpu_rank_loss}[sys.argv[1]]()
+     "cpu_vp_head": cpu_vp_head, "cpu_rank_loss": cpu_rank_loss, "cpu_zero3": cpu_zero3, "gpu_zero3": gpu_zero3}[sys.argv[1]]()

@@ -28,6 +28,18 @@ def test_cpu_ranks_ddp_and_fsdp_match_single_process():
     _launch("cpu_engine", 2)
 
 
+@pytest.mark.parametrize("world", [2, 3])
+def test_cpu_ranks_full_parameter_sharding_matches_single_process(world):
+    _launch("cpu_zero3", world)
+
+
+@pytest.mark.gpu
+def test_full_parameter_sharding_matches_replicated_training():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least 2 GPUs")
+    _launch("gpu_zero3", min(4, torch.cuda.device_count()), env={"NCCL_NVLS_ENABLE": "0"})
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("overlap", ["0", "1"])
 def test_p2p_collectives_and_training_match_nccl(overlap):
