@@ -44,6 +44,8 @@ def parse_args():
     ap.add_argument("--temperature", type=float, default=2.0)
     ap.add_argument("--loss", type=str, default="kl")
     ap.add_argument("--comm", type=str, default="p2p", choices=["p2p", "nccl"])
+    ap.add_argument("--shard", type=str, default="ddp", choices=["ddp", "fsdp", "zero3"],
+                    help="ddp/fsdp: weights replicated (fsdp shards the optimizer state); zero3: weights and gradients sharded too")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-collect", action="store_true")
     return ap.parse_args()
@@ -153,7 +155,7 @@ def main() -> int:
         from llm_distillery_b200.ops import _lib
         from llm_distillery_b200.parallel.ddp import make_comm
         model = build_model(cfg, dtype=torch.bfloat16, device=dev, seed=1234)
-        comm = make_comm(args.comm, dev) if world > 1 else None
+        comm = make_comm(args.comm, dev, shard_strategy=args.shard) if world > 1 else None
         eng = DistillEngine(model, loss=args.loss, temperature=args.temperature, optimizer="adamw", lr=1e-5,
                             crop_to_size=cfg.vocab_size, grad_accum=1, comm=comm)
 
@@ -276,7 +278,9 @@ def main() -> int:
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic token ids + synthetic top-K teacher targets, random-init weights",
             "impl": args.impl,
             "config": {"model": args.model, "global_batch": B * world, "micro_batch_per_gpu": B, "seq_len": L,
-                       "parallelism": f"dp{world}", "loss": f"{args.loss} T={args.temperature}", "topk": K,
+                       "parallelism": f"dp{world}" + ("" if args.shard == "ddp" or world == 1 else f"-{args.shard}"),
+                       "peak_mem_gb": round(torch.cuda.max_memory_allocated(dev) / 2 ** 30, 2),
+                       "loss": f"{args.loss} T={args.temperature}", "topk": K,
                        "optimizer": "adamw (fp32 master + state)", "comm": args.comm if world > 1 else "none",
                        "l2": "no flush: each step streams ~2.2 GB of weights and >20 GB of activations, far above the 126 MB L2"},
             "e2e": e2e, "collect": collect, "gpu_launches": launches, "clocks": clocks, "final_loss": final_loss, "device_error": err,

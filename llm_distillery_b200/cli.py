@@ -332,9 +332,18 @@ def _main(argv=None, default_config_path: str | None = None) -> dict:
     for t in teachers:
         t.heartbeat = heartbeat
     print("Opening data stores...")
-    data_manager = H5Store(paths.dataset, cfg.device, manager_name="main", interactive=cfg.interactive)
-    validation_data_manager = H5Store(paths.dataset_validation, cfg.device, manager_name="validation",
-                                      interactive=cfg.interactive)
+    def open_stores():
+        return (H5Store(paths.dataset, cfg.device, manager_name="main", interactive=cfg.interactive),
+                H5Store(paths.dataset_validation, cfg.device, manager_name="validation", interactive=cfg.interactive))
+    if world > 1:       # rank 0 creates missing files; the others open them only once they are complete
+        import torch.distributed as dist
+        if rank == 0:
+            data_manager, validation_data_manager = open_stores()
+        dist.barrier()
+        if rank != 0:
+            data_manager, validation_data_manager = open_stores()
+    else:
+        data_manager, validation_data_manager = open_stores()
     _STATE.update(data_manager=data_manager, validation_data_manager=validation_data_manager, teachers=teachers,
                   student=student)
 

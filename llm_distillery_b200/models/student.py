@@ -106,6 +106,8 @@ class StudentModel(BaseModel):
                                     comm=self.comm)
 
     def _unload_model(self) -> None:
+        if self.comm is not None and hasattr(self.comm, "close"):
+            self.comm.close()              # unit hooks of the full-shard engine leave with its model
         self.model = None
         self.engine = None
         if torch.cuda.is_available():

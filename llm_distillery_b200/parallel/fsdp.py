@@ -193,6 +193,8 @@ class FullShardComm:
     # ---- engine interface
     def build_flat(self, model) -> ShardedFlat:
         self.flat = ShardedFlat(model, self.rank, self.world)
+        self._ready.clear()
+        self._grads_free = [None, None]
         for layer in model.layers:          # frozen parameters of a partly trainable layer also identify its unit
             ps = list(layer.parameters())
             u = next((self.flat.unit_of[id(q)] for q in ps if id(q) in self.flat.unit_of), None)
@@ -217,6 +219,7 @@ class FullShardComm:
         _llama.LAYER_BACKWARD_DONE[0] = self._layer_done
 
     def close(self) -> None:
+        self.flat = self.opt = self._tmp = None
         if _llama.UNIT_PRE[0] == self._pre:
             _llama.UNIT_PRE[0] = None
         if _llama.LAYER_BACKWARD_DONE[0] == self._layer_done:

@@ -4,6 +4,7 @@
   cpu_zero3   gloo ranks on CPU: full parameter sharding (weights gathered per unit, gradients reduce-scattered per
               layer) equals single-process training, with gradient accumulation, an evaluation between steps, a rank
               without a micro-batch, tied embeddings, a frozen layer and a checkpoint taken through the gathered view
+  cpu_cli_zero3  gloo ranks on CPU: the command-line pipeline trains the same student replicated and fully sharded
   gpu_zero3   NCCL ranks: full parameter sharding equals the replicated NCCL run
   gpu_p2p     NCCL + NVLink P2P ranks: P2P all-reduce equals NCCL all-reduce; a P2P-communicated training run equals
               the NCCL-communicated one
@@ -72,7 +73,7 @@ def _tiny3(dtype, device, tied):
     return build_model(cfg, dtype=dtype, device=device, seed=7), cfg
 
 
-def _zero3_case(device, dtype, rank, world, tied, freeze, comm_factory, accum=2, steps=3, L=64):
+def _zero3_case(device, dtype, rank, world, tied, freeze, comm_factory, accum=2, steps=3, L=64, close=False):
     """Returns (weights after training under the communicator, loss of an evaluation batch between the steps)."""
     model, cfg = _tiny3(dtype, device, tied)
     if freeze:
@@ -93,9 +94,10 @@ def _zero3_case(device, dtype, rank, world, tied, freeze, comm_factory, accum=2,
             ev = float(eng.eval_batch(synthetic_batch(cfg.vocab_size, 2, L, 16, seed=77))[0])
     with eng.full_parameters():
         w = torch.cat([p.detach().float().reshape(-1).cpu() for p in model.parameters()])
-    if hasattr(comm, "close"):
+    stats = dict(getattr(comm, "stats", {}))
+    if close and hasattr(comm, "close"):
         comm.close()
-    return w, ev, eng
+    return w, ev, (stats if close else eng)
 
 
 def _zero3_reference(device, dtype, world, tied, freeze, accum=2, steps=3, L=64):
@@ -172,15 +174,15 @@ def gpu_zero3():
     dist.init_process_group("nccl", device_id=dev)
     rank, world = dist.get_rank(), dist.get_world_size()
     for tied in (False, True):
-        a, ev_a, eng = _zero3_case(dev, torch.bfloat16, rank, world, tied, False,
-                                   lambda: make_comm("nccl", dev, shard_strategy="zero3"), L=128)
+        a, ev_a, stats = _zero3_case(dev, torch.bfloat16, rank, world, tied, False,
+                                     lambda: make_comm("nccl", dev, shard_strategy="zero3"), L=128, close=True)
         b, ev_b, _ = _zero3_case(dev, torch.bfloat16, rank, world, tied, False,
-                                 lambda: make_comm("nccl", dev, shard_strategy="ddp"), L=128)
+                                 lambda: make_comm("nccl", dev, shard_strategy="ddp"), L=128, close=True)
         torch.cuda.synchronize()
         err = (a - b).abs().max().item()
         assert err < 2e-2, (tied, err)
         assert abs(ev_a - ev_b) < 2e-2 * max(1.0, abs(ev_b)), (ev_a, ev_b)
-        assert eng.comm.stats["gathers"] > 0 and eng.comm.stats["reduces"] > 0
+        assert stats["gathers"] > 0 and stats["reduces"] > 0
         flat = a.to(dev)
         parts = [torch.empty_like(flat) for _ in range(world)]
         dist.all_gather(parts, flat)
@@ -399,6 +401,58 @@ def cpu_cli_tp():
         print("WORKER_OK")
 
 
+def cpu_cli_zero3():
+    """The command-line pipeline under two gloo ranks, student trained once replicated and once fully sharded: five
+    batches over two ranks, so the last step has a rank without a micro-batch; the saved students are equal."""
+    import json
+    from llm_distillery_b200 import cli
+    from llm_distillery_b200.ckpt.hf import load_hf_state_dict
+    from llm_distillery_b200.models.llama import preset
+    from llm_distillery_b200.utils import synthetic
+    root = sys.argv[2]
+    rank = int(os.environ["RANK"])
+    conf = {"dataset_path": os.path.join(root, "train.jsonl"),
+            "validation_dataset_path": os.path.join(root, "val.jsonl"), "teacher_models_folder": os.path.join(root, "teachers"),
+            "student_path": os.path.join(root, "student"), "context_len": 96, "crop_distr_to_size": 400, "save_topK": 20,
+            "enable_topK": True, "device": "cpu", "num_epochs": 2, "num_warmup_steps": 2, "batch_size": 2,
+            "grad_accum_batches": 1, "temperature": 1.0, "lr": 1e-3, "optimizer": "adamw", "data_order": "sorted",
+            "training_precision": "fp32", "validate_every_n_epochs": 1, "save_student_every_n_epochs": 1,
+            "freeze_layers": [], "loss": "kl", "max_cache_size_gb": 320, "tp_size": 2}
+    if rank == 0:
+        tok = os.path.join(root, "tok")
+        synthetic.make_tokenizer(tok, 400)
+        tcfg = preset("plumbing-teacher", vocab_size=512, hidden_size=64, intermediate_size=176, max_position_embeddings=512)
+        scfg = preset("plumbing-student", vocab_size=512, hidden_size=64, intermediate_size=176, max_position_embeddings=512)
+        synthetic.make_model_dir(os.path.join(root, "teachers", "teacher_a"), tcfg, tok, seed=1, batch_size=4)
+        synthetic.make_model_dir(os.path.join(root, "student"), scfg, tok, seed=2)
+        synthetic.make_dataset(os.path.join(root, "train.jsonl"), 10, seed=3)
+        synthetic.make_dataset(os.path.join(root, "val.jsonl"), 4, seed=4)
+        for strat in ("ddp", "zero3"):
+            with open(os.path.join(root, f"config_{strat}.json"), "w") as f:
+                json.dump(dict(conf, cache_folder=os.path.join(root, f"cache_{strat}"), shard_strategy=strat), f)
+    dist.init_process_group("gloo")
+    dist.barrier()
+    finals = {}
+    for strat in ("ddp", "zero3"):
+        out = cli.main(["--config", os.path.join(root, f"config_{strat}.json")])
+        assert out["trained_samples"] == 20, out
+        dist.barrier()
+        if rank == 0:
+            base = os.path.join(root, f"cache_{strat}", "student", "trained")
+            final = [d for d in os.listdir(base) if d.endswith("final")]
+            assert len(final) == 1, os.listdir(base)
+            finals[strat] = load_hf_state_dict(os.path.join(base, final[0]))
+    if rank == 0:
+        init = load_hf_state_dict(os.path.join(root, "student"))
+        moved = 0.0
+        for k, v in finals["ddp"].items():
+            err = (v.float() - finals["zero3"][k].float()).abs().max().item()
+            assert err < 1e-5, (k, err)
+            moved = max(moved, (v.float() - init[k].float()).abs().max().item())
+        assert moved > 1e-4, "training did not change the student"
+        print("WORKER_OK")
+
+
 def gpu_tp():
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -449,4 +503,5 @@ def gpu_tp():
 
 if __name__ == "__main__":
     {"cpu_engine": cpu_engine, "gpu_p2p": gpu_p2p, "cpu_tp": cpu_tp, "gpu_tp": gpu_tp, "cpu_cli_tp": cpu_cli_tp,
-     "cpu_vp_head": cpu_vp_head, "cpu_rank_loss": cpu_rank_loss, "cpu_zero3": cpu_zero3, "gpu_zero3": gpu_zero3}[sys.argv[1]]()
+     "cpu_vp_head": cpu_vp_head, "cpu_rank_loss": cpu_rank_loss, "cpu_zero3": cpu_zero3, "gpu_zero3": gpu_zero3,
+     "cpu_cli_zero3": cpu_cli_zero3}[sys.argv[1]]()

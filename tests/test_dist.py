@@ -33,6 +33,10 @@ def test_cpu_ranks_full_parameter_sharding_matches_single_process(world):
     _launch("cpu_zero3", world)
 
 
+def test_cpu_ranks_pipeline_with_fully_sharded_student(tmp_path):
+    _launch("cpu_cli_zero3", 2, extra=(str(tmp_path),))
+
+
 @pytest.mark.gpu
 def test_full_parameter_sharding_matches_replicated_training():
     if torch.cuda.device_count() < 2:
