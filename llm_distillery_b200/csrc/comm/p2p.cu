@@ -9,6 +9,8 @@
 //                      apply AdamW to the local fp32 master / moments, and store the new bf16 weights into every
 //                      rank's weight buffer (all-gather by peer stores) - one pass, no staging buffers
 //   reduce_scatter_f32 / allgather_16 / allreduce_f32   stand-alone pieces for the other optimizers and for tests
+//   gather_pull / reduce_scatter_acc_f32   full parameter sharding: a unit's weights pulled from the ranks' shards
+//                      just before it runs; its gradients summed onto this rank's slice right after its backward
 #include "peer.cuh"
 #include "../common/host.cuh"
 
@@ -121,6 +123,50 @@ __global__ void __launch_bounds__(256) allgather_kernel(Peers dst, const uint4* 
   __threadfence_system();
 }
 
+// dst[p * piece + i] = src_p[src_off + i] for every rank p (16-byte granules): all-gather by peer LOADS. The sources
+// are read-only while this runs (weights between two optimizer steps), so no flags are exchanged. Eight loads per
+// thread are in flight before the first store: NVLink latency is hidden by independent requests, not by occupancy.
+__global__ void __launch_bounds__(256) gather_pull_kernel(Peers src, uint4* __restrict__ dst, long long src_off_vec,
+                                                         long long piece_vec, int rank, int world) {
+  constexpr int U = 8;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (int k = 0; k < world; ++k) {
+    const int p = (rank + k) % world;          // own piece first, then the peers starting at the next rank
+    const uint4* __restrict__ s = reinterpret_cast<const uint4*>(src.p[p]) + src_off_vec;
+    uint4* __restrict__ d = dst + (long long)p * piece_vec;
+    for (long long base = blockIdx.x * (long long)blockDim.x + threadIdx.x; base < piece_vec; base += stride * U) {
+      uint4 x[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = base + u * stride;
+        if (i < piece_vec) x[u] = s[i];
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = base + u * stride;
+        if (i < piece_vec) d[i] = x[u];
+      }
+    }
+  }
+}
+
+// out[i] (+)= sum_p src_p[lo + i]   (fp32), i < n, n % 4 == 0: reduce-scatter by peer loads into (or onto) a local slice
+__global__ void __launch_bounds__(256) reduce_scatter_acc_kernel(Peers src, float* __restrict__ out, long long lo,
+                                                                long long n, int rank, int world, int accumulate) {
+  const long long nv = n >> 2;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nv;
+       i += (long long)gridDim.x * blockDim.x) {
+    float4 s = accumulate ? reinterpret_cast<const float4*>(out)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+    for (int k = 0; k < world; ++k) {
+      const int p = (rank + k) % world;
+      const float4 x = (reinterpret_cast<const float4*>(reinterpret_cast<const float*>(src.p[p]) + lo))[i];
+      s.x += x.x; s.y += x.y; s.z += x.z; s.w += x.w;
+    }
+    reinterpret_cast<float4*>(out)[i] = s;
+  }
+}
+
 static int grid_for(long long items) {
   long long b = (items + 255) / 256;
   const long long cap = (long long)sm_count() * 8;
@@ -174,6 +220,30 @@ int b200_p2p_reduce_scatter_f32(const void* const* src_ptrs, float* out, long lo
   Peers S;
   if (!fill(S, src_ptrs, world) || !out || n <= 0 || (n & 3) || (lo & 3)) return B200_ERR_ARG;
   reduce_scatter_kernel<<<grid_for(n >> 2), 256, 0, st>>>(S, out, lo, n, rank, world, scale);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200_OK;
+}
+
+// dst (world * piece_bytes, local) = concatenation over ranks p of src_ptrs[p][src_off_bytes .. + piece_bytes).
+int b200_p2p_gather_pull(const void* const* src_ptrs, void* dst, long long src_off_bytes, long long piece_bytes, int rank,
+                         int world, cudaStream_t st) {
+  Peers S;
+  if (!fill(S, src_ptrs, world) || !dst || piece_bytes <= 0 || (piece_bytes & 15) || (src_off_bytes & 15) || rank < 0 ||
+      rank >= world)
+    return B200_ERR_ARG;
+  long long blocks = ((piece_bytes >> 4) + 256 * 8 - 1) / (256 * 8);
+  const long long cap = (long long)sm_count() * 2;
+  if (blocks > cap) blocks = cap;
+  gather_pull_kernel<<<(int)blocks, 256, 0, st>>>(S, (uint4*)dst, src_off_bytes >> 4, piece_bytes >> 4, rank, world);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200_OK;
+}
+
+int b200_p2p_reduce_scatter_acc_f32(const void* const* src_ptrs, float* out, long long lo, long long n, int rank,
+                                    int world, int accumulate, cudaStream_t st) {
+  Peers S;
+  if (!fill(S, src_ptrs, world) || !out || n <= 0 || (n & 3) || (lo & 3)) return B200_ERR_ARG;
+  reduce_scatter_acc_kernel<<<grid_for(n >> 2), 256, 0, st>>>(S, out, lo, n, rank, world, accumulate);
   B200_CUDA_CHECK(cudaGetLastError());
   return B200_OK;
 }

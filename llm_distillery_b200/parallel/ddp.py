@@ -64,7 +64,9 @@ def make_comm(kind: str, device, shard_strategy: str = "ddp"):
     if not dist.is_initialized() or dist.get_world_size() == 1:
         return None
     if shard_strategy == "zero3":
-        from .fsdp import FullShardComm
+        from .fsdp import FullShardComm, P2PFullShardComm
+        if kind == "p2p" and torch.device(device).type == "cuda":
+            return P2PFullShardComm(device)
         return FullShardComm(device)
     if kind in ("nccl", "gloo") or torch.device(device).type != "cuda":
         return AllReduceComm(device, shard_strategy)

@@ -76,7 +76,9 @@ class ShardedFlat:
 
     layout = "per_unit"
 
-    def __init__(self, model, rank: int, world: int):
+    def __init__(self, model, rank: int, world: int, alloc=None):
+        """``alloc(numel, dtype, role)`` returns a zeroed buffer; roles "shard" (this rank's weight pieces) and "grads"
+        (a unit-sized gradient buffer) are what peers read under the peer-to-peer communicator."""
         units = model_units(model)
         if not units:
             raise ValueError("no trainable parameters")
@@ -93,13 +95,15 @@ class ShardedFlat:
         self.shard_lo = rank * off             # nominal: the shard space is not a slice of one flat space
         self.total = off * world
         kw = dict(device=self.device)
-        self._model_shard = torch.zeros(off, dtype=self.dtype, **kw)
+        if alloc is None:
+            alloc = lambda n, dt, role: torch.zeros(n, dtype=dt, **kw)      # noqa: E731
+        self._model_shard = alloc(off, self.dtype, "shard")
         self._grad_shard = torch.zeros(off, dtype=torch.float32, **kw)
         # gather buffers: two shared by the layers, one each for the other units
         layers = [u for u in self.units if u.is_layer]
         big = max((u.numel for u in layers), default=0)
         self.rot_w = [torch.zeros(big, dtype=self.dtype, **kw) for _ in range(2 if layers else 0)]
-        self.rot_g = [torch.zeros(big, dtype=torch.float32, **kw) for _ in range(2 if layers else 0)]
+        self.rot_g = [alloc(big, torch.float32, "grads") for _ in range(2 if layers else 0)]
         self.rot_owner: list[int | None] = [None, None]
         for k, u in enumerate(layers):
             u.slot = k & 1
@@ -107,7 +111,7 @@ class ShardedFlat:
         for u in self.units:
             if not u.is_layer:
                 u.weights = torch.zeros(u.numel, dtype=self.dtype, **kw)
-                u.grads = torch.zeros(u.numel, dtype=torch.float32, **kw)
+                u.grads = alloc(u.numel, torch.float32, "grads")
         self.unit_of: dict[int, _Unit] = {}
         self.slots: list[GradSlot] = []
         with torch.no_grad():
@@ -192,7 +196,7 @@ class FullShardComm:
 
     # ---- engine interface
     def build_flat(self, model) -> ShardedFlat:
-        self.flat = ShardedFlat(model, self.rank, self.world)
+        self.flat = ShardedFlat(model, self.rank, self.world, alloc=self._alloc())
         self._ready.clear()
         self._grads_free = [None, None]
         for layer in model.layers:          # frozen parameters of a partly trainable layer also identify its unit
@@ -265,12 +269,18 @@ class FullShardComm:
                 return
             u.valid = True
         with self._on_side():
-            self._all_gather(u.weights, f.piece_of(u))
+            self._gather_unit(u)
             if self.cuda:
                 ev = torch.cuda.Event()
                 ev.record()
                 self._ready[u.index] = ev
         self.stats["gathers"] += 1
+
+    def _gather_unit(self, u: _Unit) -> None:
+        self._all_gather(u.weights, self.flat.piece_of(u))
+
+    def _alloc(self):
+        return None
 
     def _wait_ready(self, u: _Unit) -> None:
         ev = self._ready.pop(u.index, None)
@@ -289,10 +299,8 @@ class FullShardComm:
             return
         self._issue_gather(u)
         self._wait_ready(u)
-        if backward and u.is_layer and self._grads_free[u.slot] is not None:
-            # the previous owner's gradients must have left the buffer before this layer's wgrad kernels write it
-            torch.cuda.current_stream().wait_event(self._grads_free[u.slot])
-            self._grads_free[u.slot] = None
+        if backward and u.is_layer:
+            self._before_backward_writes(u)
         # next unit in execution order: gathered behind this unit's compute. Going backward only layers are needed
         # again (embedding backward reads no weights; the head ran just before)
         nxt = self._neighbour(u, -1 if backward else 1)
@@ -311,21 +319,38 @@ class FullShardComm:
             if s.fresh:                 # a parameter without a gradient this time
                 s.buf.zero_()
         with self._on_side():
-            dst = f.grad_piece_of(u)
-            if not u.reduced:
-                self._reduce_scatter(dst, u.grads)
-            else:
-                tmp = self._tmp[u.slot][:u.piece] if u.is_layer else torch.empty_like(dst)
-                self._reduce_scatter(tmp, u.grads)
-                dst.add_(tmp)
-            if self.cuda and u.is_layer:
-                ev = torch.cuda.Event()
-                ev.record()
-                self._grads_free[u.slot] = ev
+            self._reduce_op(u)
         u.reduced = True
         for s in u.slots:
             s.fresh = True
         self.stats["reduces"] += 1
+
+    def _reduce_op(self, u: _Unit) -> None:
+        """On the side stream: sum the unit's gradient buffers over the ranks onto this rank's piece."""
+        dst = self.flat.grad_piece_of(u)
+        if not u.reduced:
+            self._reduce_scatter(dst, u.grads)
+        else:
+            tmp = self._tmp[u.slot][:u.piece] if u.is_layer else torch.empty_like(dst)
+            self._reduce_scatter(tmp, u.grads)
+            dst.add_(tmp)
+        if self.cuda and u.is_layer:
+            ev = torch.cuda.Event()
+            ev.record()
+            self._grads_free[u.slot] = ev
+
+    def _before_backward_writes(self, u: _Unit) -> None:
+        """A layer's backward is about to write its gradient buffer."""
+        if self._grads_free[u.slot] is not None:
+            # the previous owner's gradients must have left the buffer before this layer's wgrad kernels write it
+            torch.cuda.current_stream().wait_event(self._grads_free[u.slot])
+            self._grads_free[u.slot] = None
+
+    def _step_begin(self) -> None:
+        pass
+
+    def _step_end(self) -> None:
+        pass
 
     def idle_micro_step(self) -> None:
         """The collectives of one micro-batch's forward + backward with a zero gradient contribution: for a rank
@@ -341,6 +366,7 @@ class FullShardComm:
     # ---- the optimizer step
     def reduce_and_step(self, lr: float, grad_scale: float) -> None:
         f = self.flat
+        self._step_begin()
         for u in f.units:
             if not u.is_layer:
                 self._reduce_unit(u)
@@ -356,6 +382,7 @@ class FullShardComm:
             u.reduced = False
         f.rot_owner = [None, None]
         self._ready.clear()
+        self._step_end()
 
     # ---- whole-model access (checkpoints)
     @contextlib.contextmanager
@@ -387,3 +414,110 @@ class FullShardComm:
                 if writeback:
                     f.master.copy_(f.model_shard().float())
             f.rot_owner = [None, None]
+
+
+class P2PFullShardComm(FullShardComm):
+    """Full sharding over NVLink peer access (kernels: csrc/comm/p2p.cu) instead of NCCL.
+
+    * This rank's weight pieces live in symmetric memory. A unit is gathered by ONE kernel that loads every rank's
+      piece straight out of its memory (``gather_pull``): the pieces do not change between two optimizer steps, so a
+      gather needs no handshake at all - only the optimizer step is bracketed by flag barriers.
+    * The unit-sized gradient buffers live in symmetric memory. After a layer's backward: flag barrier (every rank's
+      gradients of the layer are complete), then one kernel sums the ranks' buffers over this rank's slice onto the
+      gradient of the shard space (``reduce_scatter_acc``). The barrier of the NEXT reduction tells a rank that all
+      peers have finished reading the previous buffer, which is when its next owner may overwrite it.
+
+    All of it runs on the side stream, behind the compute of the neighbouring layer. Every device-side wait is
+    bounded and reports through the device error word (``check``).
+    """
+
+    def __init__(self, device, group=None):
+        super().__init__(device, group)
+        from ..ops import _lib
+        from ..ops._lib import _VP, _I, _LL
+        from .p2p import SymmetricBuffer
+        import ctypes
+        _lib.register("b200_p2p_barrier", [_VP, _I, _I, ctypes.c_uint, _VP])
+        _lib.register("b200_p2p_gather_pull", [_VP, _VP, _LL, _LL, _I, _I, _VP])
+        _lib.register("b200_p2p_reduce_scatter_acc_f32", [_VP, _VP, _LL, _LL, _I, _I, _I, _VP])
+        self._lib = _lib
+        self._SymmetricBuffer = SymmetricBuffer
+        self.sig = SymmetricBuffer(64, torch.int32, self.device)
+        self.epoch = 0
+        self._sym: dict[int, object] = {}
+        self._unprotected = None      # rotating gradient buffer read by the latest reduction, no barrier issued since
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)
+
+    def _alloc(self):
+        def alloc(n, dtype, role):
+            buf = self._SymmetricBuffer(max(int(n), 64), dtype, self.device)      # zero-filled, mapped on every rank
+            self._sym[buf.tensor.data_ptr()] = buf
+            return buf.tensor[:n]
+        self._sym.clear()
+        self._unprotected = None
+        return alloc
+
+    def close(self) -> None:
+        super().close()
+        self._sym.clear()
+
+    def _barrier(self) -> None:
+        self.epoch += 1
+        self._lib.check(self._lib.kernels().b200_p2p_barrier(self.sig.c_ptrs, self.rank, self.world, self.epoch,
+                                                             self._lib.stream()), "b200_p2p_barrier")
+
+    def check(self) -> None:
+        err = self._lib.take_device_error()
+        if err:
+            raise RuntimeError(f"peer-to-peer wait timed out on rank {self.rank} (device error code {err})")
+
+    def _gather_unit(self, u: _Unit) -> None:
+        f = self.flat
+        es = f.model_shard().element_size()
+        src = self._sym[f.model_shard().data_ptr()]
+        self._lib.check(self._lib.kernels().b200_p2p_gather_pull(
+            src.c_ptrs, self._lib.ptr(u.weights), u.shard_lo * es, u.piece * es, self.rank, self.world,
+            self._lib.stream()), "b200_p2p_gather_pull")
+
+    def _mark_protected(self) -> None:
+        """Call right after a barrier on the side stream: every peer has finished its earlier reductions."""
+        if self._unprotected is not None:
+            ev = torch.cuda.Event()
+            ev.record()
+            self._grads_free[self._unprotected] = ev
+            self._unprotected = None
+
+    def _reduce_op(self, u: _Unit) -> None:
+        self._barrier()
+        self._mark_protected()
+        src = self._sym[u.grads.data_ptr()]
+        dst = self.flat.grad_piece_of(u)
+        self._lib.check(self._lib.kernels().b200_p2p_reduce_scatter_acc_f32(
+            src.c_ptrs, self._lib.ptr(dst), self.rank * u.piece, u.piece, self.rank, self.world, int(u.reduced),
+            self._lib.stream()), "b200_p2p_reduce_scatter_acc_f32")
+        if u.is_layer:
+            self._unprotected = u.slot
+
+    def _before_backward_writes(self, u: _Unit) -> None:
+        if self._unprotected == u.slot:
+            # the latest reduction read this very buffer (first layer of the previous micro-batch's backward order):
+            # peers may still be reading it, and no later reduction's barrier has vouched for them yet
+            with self._on_side():
+                self._barrier()
+                self._mark_protected()
+        super()._before_backward_writes(u)
+
+    def _step_begin(self) -> None:
+        # peers may still be pulling weights for an evaluation pass: nobody's optimizer overwrites its pieces before
+        # every rank has got here
+        with self._on_side():
+            self._barrier()
+            self._mark_protected()
+
+    def _step_end(self) -> None:
+        # the new pieces of every rank are in place before anyone gathers them
+        with self._on_side():
+            self._barrier()
+            self._mark_protected()
+        self._grads_free = [None, None]

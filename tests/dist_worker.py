@@ -5,7 +5,7 @@
               layer) equals single-process training, with gradient accumulation, an evaluation between steps, a rank
               without a micro-batch, tied embeddings, a frozen layer and a checkpoint taken through the gathered view
   cpu_cli_zero3  gloo ranks on CPU: the command-line pipeline trains the same student replicated and fully sharded
-  gpu_zero3   NCCL ranks: full parameter sharding equals the replicated NCCL run
+  gpu_zero3   GPU ranks: full parameter sharding, over NCCL and over the peer-access kernels, equals the replicated run
   gpu_p2p     NCCL + NVLink P2P ranks: P2P all-reduce equals NCCL all-reduce; a P2P-communicated training run equals
               the NCCL-communicated one
   cpu_tp      gloo ranks on CPU: the tensor-parallel teacher's top-K log-probs equal the unsharded model's
@@ -173,20 +173,23 @@ def gpu_zero3():
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
     rank, world = dist.get_rank(), dist.get_world_size()
+    from llm_distillery_b200.ops import _lib
     for tied in (False, True):
-        a, ev_a, stats = _zero3_case(dev, torch.bfloat16, rank, world, tied, False,
-                                     lambda: make_comm("nccl", dev, shard_strategy="zero3"), L=128, close=True)
         b, ev_b, _ = _zero3_case(dev, torch.bfloat16, rank, world, tied, False,
                                  lambda: make_comm("nccl", dev, shard_strategy="ddp"), L=128, close=True)
-        torch.cuda.synchronize()
-        err = (a - b).abs().max().item()
-        assert err < 2e-2, (tied, err)
-        assert abs(ev_a - ev_b) < 2e-2 * max(1.0, abs(ev_b)), (ev_a, ev_b)
-        assert stats["gathers"] > 0 and stats["reduces"] > 0
-        flat = a.to(dev)
-        parts = [torch.empty_like(flat) for _ in range(world)]
-        dist.all_gather(parts, flat)
-        assert all(torch.equal(p, parts[0]) for p in parts), "ranks hold different weights"
+        for kind in ("nccl", "p2p"):        # library collectives, then the peer-access kernels
+            a, ev_a, stats = _zero3_case(dev, torch.bfloat16, rank, world, tied, False,
+                                         lambda: make_comm(kind, dev, shard_strategy="zero3"), L=128, close=True)
+            torch.cuda.synchronize()
+            assert _lib.take_device_error() == 0
+            err = (a - b).abs().max().item()
+            assert err < 2e-2, (kind, tied, err)
+            assert abs(ev_a - ev_b) < 2e-2 * max(1.0, abs(ev_b)), (kind, ev_a, ev_b)
+            assert stats["gathers"] > 0 and stats["reduces"] > 0
+            flat = a.to(dev)
+            parts = [torch.empty_like(flat) for _ in range(world)]
+            dist.all_gather(parts, flat)
+            assert all(torch.equal(p, parts[0]) for p in parts), "ranks hold different weights"
     if rank == 0:
         print("WORKER_OK")
     dist.destroy_process_group()
