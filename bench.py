@@ -161,7 +161,7 @@ def main() -> int:
 
         class Runner:
             def device_step(self, db):
-                loss, _ = eng.micro_step(db)
+                loss, _ = eng.micro_step(db, last=True)
                 eng.optimizer_step()
                 return loss
 
@@ -280,6 +280,8 @@ def main() -> int:
             "config": {"model": args.model, "global_batch": B * world, "micro_batch_per_gpu": B, "seq_len": L,
                        "parallelism": f"dp{world}" + ("" if args.shard == "ddp" or world == 1 else f"-{args.shard}"),
                        "peak_mem_gb": round(torch.cuda.max_memory_allocated(dev) / 2 ** 30, 2),
+                       # whole device, symmetric (peer-mapped) buffers included, which the allocator's peak does not see
+                       "device_mem_used_gb": round((lambda fr, tot: (tot - fr) / 2 ** 30)(*torch.cuda.mem_get_info(dev)), 2),
                        "loss": f"{args.loss} T={args.temperature}", "topk": K,
                        "optimizer": "adamw (fp32 master + state)", "comm": args.comm if world > 1 else "none",
                        "l2": "no flush: each step streams ~2.2 GB of weights and >20 GB of activations, far above the 126 MB L2"},

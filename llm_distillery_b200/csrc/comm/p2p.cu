@@ -92,6 +92,61 @@ __global__ void __launch_bounds__(256) rs_adamw_ag_kernel(Peers grads, Peers mod
   __threadfence_system();
 }
 
+// Full sharding, last micro-batch of a step: g = acc + sum_p grads_p[grad_lo + i] (acc: what earlier micro-batches left
+// in the local shard gradient, may be null), AdamW on the local piece of master / m / v, new bf16 weights into the
+// local weight piece (peers pull it when they next gather the unit). 8 elements per thread.
+__global__ void __launch_bounds__(256) rs_adamw_piece_kernel(Peers grads, long long grad_lo, const float* __restrict__ acc,
+                                                            __nv_bfloat16* __restrict__ model, float* __restrict__ master,
+                                                            float* __restrict__ m, float* __restrict__ v, long long n,
+                                                            int rank, int world, AdamArgs a) {
+  const long long nv = n >> 3;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nv;
+       i += (long long)gridDim.x * blockDim.x) {
+    float g[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (acc) {
+      *reinterpret_cast<float4*>(g) = reinterpret_cast<const float4*>(acc)[2 * i];
+      *reinterpret_cast<float4*>(g + 4) = reinterpret_cast<const float4*>(acc)[2 * i + 1];
+    }
+#pragma unroll 4
+    for (int k = 0; k < world; ++k) {
+      const int p = (rank + k) % world;
+      const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(grads.p[p]) + grad_lo) + 2 * i;
+      const float4 x = src[0], y = src[1];
+      g[0] += x.x; g[1] += x.y; g[2] += x.z; g[3] += x.w;
+      g[4] += y.x; g[5] += y.y; g[6] += y.z; g[7] += y.w;
+    }
+    float pm[8], mm[8], vv[8];
+    *reinterpret_cast<float4*>(pm) = reinterpret_cast<float4*>(master)[2 * i];
+    *reinterpret_cast<float4*>(pm + 4) = reinterpret_cast<float4*>(master)[2 * i + 1];
+    *reinterpret_cast<float4*>(mm) = reinterpret_cast<float4*>(m)[2 * i];
+    *reinterpret_cast<float4*>(mm + 4) = reinterpret_cast<float4*>(m)[2 * i + 1];
+    *reinterpret_cast<float4*>(vv) = reinterpret_cast<float4*>(v)[2 * i];
+    *reinterpret_cast<float4*>(vv + 4) = reinterpret_cast<float4*>(v)[2 * i + 1];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float gj = g[j] * a.grad_scale;
+      if (a.decoupled) pm[j] *= (1.f - a.lr * a.weight_decay);
+      else gj += a.weight_decay * pm[j];
+      mm[j] = a.beta1 * mm[j] + (1.f - a.beta1) * gj;
+      vv[j] = a.beta2 * vv[j] + (1.f - a.beta2) * gj * gj;
+      pm[j] -= (a.lr / a.bias1) * mm[j] / (sqrtf(vv[j] / a.bias2) + a.eps);
+    }
+    reinterpret_cast<float4*>(master)[2 * i] = *reinterpret_cast<float4*>(pm);
+    reinterpret_cast<float4*>(master)[2 * i + 1] = *reinterpret_cast<float4*>(pm + 4);
+    reinterpret_cast<float4*>(m)[2 * i] = *reinterpret_cast<float4*>(mm);
+    reinterpret_cast<float4*>(m)[2 * i + 1] = *reinterpret_cast<float4*>(mm + 4);
+    reinterpret_cast<float4*>(v)[2 * i] = *reinterpret_cast<float4*>(vv);
+    reinterpret_cast<float4*>(v)[2 * i + 1] = *reinterpret_cast<float4*>(vv + 4);
+    uint4 o;
+    o.x = pack_bf16x2(pm[0], pm[1]);
+    o.y = pack_bf16x2(pm[2], pm[3]);
+    o.z = pack_bf16x2(pm[4], pm[5]);
+    o.w = pack_bf16x2(pm[6], pm[7]);
+    reinterpret_cast<uint4*>(model)[i] = o;
+  }
+  __threadfence_system();
+}
+
 // out[i] = scale * sum_p src_p[lo + i]   (fp32), i < n, n % 4 == 0
 __global__ void __launch_bounds__(256) reduce_scatter_kernel(Peers src, float* __restrict__ out, long long lo,
                                                             long long n, int rank, int world, float scale) {
@@ -235,6 +290,22 @@ int b200_p2p_gather_pull(const void* const* src_ptrs, void* dst, long long src_o
   const long long cap = (long long)sm_count() * 2;
   if (blocks > cap) blocks = cap;
   gather_pull_kernel<<<(int)blocks, 256, 0, st>>>(S, (uint4*)dst, src_off_bytes >> 4, piece_bytes >> 4, rank, world);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200_OK;
+}
+
+// grad_ptrs[r]: rank r's unit-sized fp32 gradient buffer; this rank's slice of it starts at grad_lo. acc (nullable),
+// model (bf16), master, m, v: this rank's piece of the unit, n elements (multiple of 8).
+int b200_p2p_rs_adamw_piece(const void* const* grad_ptrs, long long grad_lo, const float* acc, void* model, float* master,
+                            float* m, float* v, long long n, int rank, int world, float lr, float beta1, float beta2,
+                            float eps, float weight_decay, int step, float grad_scale, int decoupled, cudaStream_t st) {
+  Peers G;
+  if (!fill(G, grad_ptrs, world) || !model || !master || !m || !v || n <= 0 || (n & 7) || (grad_lo & 7) || step < 1)
+    return B200_ERR_ARG;
+  AdamArgs a{lr, beta1, beta2, eps, weight_decay, 1.f - powf(beta1, (float)step), 1.f - powf(beta2, (float)step),
+             grad_scale, decoupled};
+  rs_adamw_piece_kernel<<<grid_for(n >> 3), 256, 0, st>>>(G, grad_lo, acc, (__nv_bfloat16*)model, master, m, v, n, rank,
+                                                         world, a);
   B200_CUDA_CHECK(cudaGetLastError());
   return B200_OK;
 }

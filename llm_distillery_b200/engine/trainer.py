@@ -92,14 +92,18 @@ class DistillEngine:
                                  temperature=self.temperature, vocab=self.vocab, alpha=self.alpha, labels=mb.labels,
                                  avoid=mb.avoid, seg=mb.seg, n_seg=mb.n_seg, jsd_renorm=self.jsd_renorm)
 
-    def micro_step(self, mb: HostBatch):
+    def micro_step(self, mb: HostBatch, last: bool | None = None):
+        """Forward + backward of one micro-batch. ``last``: the caller knows whether the optimizer step follows this
+        micro-batch (None: not known; then it is taken to be the ``grad_accum``-th micro-batch of the step)."""
         with self.timer.phase("forward+loss"):
             loss, logs = self.loss_on_batch(mb)
         # last micro-batch of the step under a communicator that can do it: the gradient of each layer is reduced
         # (and its shard of the weights updated) as soon as that layer's backward is through, behind the backward
         # of the earlier layers
-        overlap = (self.comm is not None and getattr(self.comm, "supports_overlap", False)
-                   and self.micro_in_step + 1 == self.grad_accum)
+        is_last = (self.micro_in_step + 1 == self.grad_accum) if last is None else bool(last)
+        overlap = self.comm is not None and getattr(self.comm, "supports_overlap", False) and is_last
+        if last and self.comm is not None and hasattr(self.comm, "last_micro_batch"):
+            self.comm.last_micro_batch(self.lr, 1.0 / self.grad_accum)
         if overlap:
             from ..models import llama as _llama
             self.comm.begin_overlap(self.lr, 1.0 / self.grad_accum)
@@ -119,10 +123,12 @@ class DistillEngine:
         if off is not None:
             self.comm.range_ready(off)
 
-    def idle_micro_step(self) -> None:
+    def idle_micro_step(self, last: bool | None = None) -> None:
         """This rank has no micro-batch where other ranks have one: under full sharding it still takes part in their
         collectives; otherwise nothing to do."""
         if self.comm is not None and hasattr(self.comm, "idle_micro_step"):
+            if last and hasattr(self.comm, "last_micro_batch"):
+                self.comm.last_micro_batch(self.lr, 1.0 / self.grad_accum)
             self.comm.idle_micro_step()
 
     def full_parameters(self, writeback: bool = False):
@@ -154,9 +160,9 @@ class DistillEngine:
 
     def train_step(self, host_batches: list[HostBatch]) -> torch.Tensor:
         total = None
-        for hb in host_batches:
+        for k, hb in enumerate(host_batches):
             mb = hb.to_device(self.device)
-            loss, _ = self.micro_step(mb)
+            loss, _ = self.micro_step(mb, last=(k + 1 == len(host_batches)))
             total = loss if total is None else total + loss
         self.optimizer_step()
         return total

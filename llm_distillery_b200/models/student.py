@@ -313,15 +313,18 @@ class StudentModel(BaseModel):
             if hbt is not None:      # between steps, nothing in flight: learn about a lost peer BEFORE the next launch
                 hbt.beat(self.num_trained_steps, "train")
                 hbt.check()
+            # known before the micro-batch runs: the optimizer step follows it (the sharded engines then fold the
+            # update of each layer into that layer's gradient reduction)
+            steps_after = self.num_trained_steps + n_samples >= self.next_accum_step
             if convos is not None:
                 teacher = data_manager.read_next_batch()
                 hb = self.build_host_batch(convos, teacher)
                 mb = hb.to_device(self.engine.device)
-                loss, logs = self.engine.micro_step(mb)
+                loss, logs = self.engine.micro_step(mb, last=steps_after)
                 self.losses.add_losses(logs, count=len(convos))
                 self.tokens_trained += hb.n_tokens
             else:
-                self.engine.idle_micro_step()
+                self.engine.idle_micro_step(last=steps_after)
             self.progress_bar.update(n_samples)
             self.num_trained_steps += n_samples
             if self.num_trained_steps >= self.next_accum_step:

@@ -69,6 +69,7 @@ class _Unit:
         self.slots: list[GradSlot] = []
         self.valid = False           # weights hold the current values (dedicated buffers only)
         self.reduced = False         # a reduce-scatter of this unit has already gone into the shard gradient this step
+        self.stepped = False         # the optimizer update of this unit's piece has been done with its last reduction
 
 
 class ShardedFlat:
@@ -440,6 +441,10 @@ class P2PFullShardComm(FullShardComm):
         _lib.register("b200_p2p_barrier", [_VP, _I, _I, ctypes.c_uint, _VP])
         _lib.register("b200_p2p_gather_pull", [_VP, _VP, _LL, _LL, _I, _I, _VP])
         _lib.register("b200_p2p_reduce_scatter_acc_f32", [_VP, _VP, _LL, _LL, _I, _I, _I, _VP])
+        _F = ctypes.c_float
+        _lib.register("b200_p2p_rs_adamw_piece", [_VP, _LL, _VP, _VP, _VP, _VP, _VP, _LL, _I, _I, _F, _F, _F, _F, _F, _I,
+                                                  _F, _I, _VP])
+        self._fused = None            # {"lr", "gs"} during the last micro-batch of a step and the step that follows
         self._lib = _lib
         self._SymmetricBuffer = SymmetricBuffer
         self.sig = SymmetricBuffer(64, torch.int32, self.device)
@@ -493,11 +498,51 @@ class P2PFullShardComm(FullShardComm):
         self._mark_protected()
         src = self._sym[u.grads.data_ptr()]
         dst = self.flat.grad_piece_of(u)
-        self._lib.check(self._lib.kernels().b200_p2p_reduce_scatter_acc_f32(
-            src.c_ptrs, self._lib.ptr(dst), self.rank * u.piece, u.piece, self.rank, self.world, int(u.reduced),
-            self._lib.stream()), "b200_p2p_reduce_scatter_acc_f32")
+        lib, ptr = self._lib.kernels(), self._lib.ptr
+        if self._fused is not None:
+            # the optimizer step follows this micro-batch: reduce + AdamW on this rank's piece in one kernel. Nobody
+            # gathers this unit again before the step is over, so its weight piece may change now
+            f, opt = self.flat, self.opt
+            lo, hi = u.shard_lo, u.shard_lo + u.piece
+            b1, b2 = opt.betas
+            self._lib.check(lib.b200_p2p_rs_adamw_piece(
+                src.c_ptrs, self.rank * u.piece, ptr(dst) if u.reduced else None, ptr(f.model_shard()[lo:hi]),
+                ptr(f.master[lo:hi]), ptr(opt.state["m"][lo:hi]), ptr(opt.state["v"][lo:hi]), u.piece, self.rank,
+                self.world, self._fused["lr"], b1, b2, opt.eps, opt.weight_decay, opt.step_count, self._fused["gs"],
+                int(opt.decoupled), self._lib.stream()), "b200_p2p_rs_adamw_piece")
+            u.stepped = True
+        else:
+            self._lib.check(lib.b200_p2p_reduce_scatter_acc_f32(
+                src.c_ptrs, ptr(dst), self.rank * u.piece, u.piece, self.rank, self.world, int(u.reduced),
+                self._lib.stream()), "b200_p2p_reduce_scatter_acc_f32")
         if u.is_layer:
             self._unprotected = u.slot
+
+    def last_micro_batch(self, lr: float, grad_scale: float) -> None:
+        """The optimizer step follows the micro-batch whose backward starts now (every rank is told the same)."""
+        opt = self.opt
+        if (opt.name in ("adam", "adamw", "adamw32bit", "paged_adamw", "paged_adamw32bit") and "m" in opt.state
+                and self.flat.dtype == torch.bfloat16 and self._fused is None):
+            opt.step_count += 1
+            self._fused = {"lr": float(lr), "gs": float(grad_scale) / self.world}
+
+    def reduce_and_step(self, lr: float, grad_scale: float) -> None:
+        if self._fused is None:
+            return super().reduce_and_step(lr, grad_scale)
+        f = self.flat
+        self._step_begin()
+        for u in f.units:
+            if not u.stepped:           # embedding and head (their gradients were still accumulating); a layer
+                self._reduce_unit(u)    # whose backward did not run contributes its zeroed buffer
+        done = torch.cuda.Event()
+        done.record(self.side)
+        torch.cuda.current_stream().wait_event(done)
+        for u in f.units:
+            u.valid = u.reduced = u.stepped = False
+        f.rot_owner = [None, None]
+        self._ready.clear()
+        self._fused = None
+        self._step_end()
 
     def _before_backward_writes(self, u: _Unit) -> None:
         if self._unprotected == u.slot:

@@ -85,10 +85,11 @@ def _zero3_case(device, dtype, rank, world, tied, freeze, comm_factory, accum=2,
     for s in range(steps):
         for m in range(accum):
             if s == 1 and m == 1 and rank == world - 1 and world > 1:
-                eng.idle_micro_step()          # the last rank has no second micro-batch in step 1
+                eng.idle_micro_step(last=(m + 1 == accum))   # the last rank has no second micro-batch in step 1
                 continue
             hb = synthetic_batch(cfg.vocab_size, 2, L, 16, seed=1000 * s + 10 * m + rank)
-            eng.micro_step(hb.to_device(device))
+            # step 2 leaves it to the engine's count whether this is the last micro-batch (unfused update)
+            eng.micro_step(hb.to_device(device), last=(m + 1 == accum) if s < 2 else None)
         eng.optimizer_step()
         if s == 0:
             ev = float(eng.eval_batch(synthetic_batch(cfg.vocab_size, 2, L, 16, seed=77))[0])
