@@ -44,6 +44,7 @@ def parse_args():
     ap.add_argument("--temperature", type=float, default=2.0)
     ap.add_argument("--loss", type=str, default="kl")
     ap.add_argument("--comm", type=str, default="p2p", choices=["p2p", "nccl"])
+    ap.add_argument("--grad-accum", type=int, default=1, help="micro-batches per optimizer step (ours only)")
     ap.add_argument("--shard", type=str, default="ddp", choices=["ddp", "fsdp", "zero3"],
                     help="ddp/fsdp: weights replicated (fsdp shards the optimizer state); zero3: weights and gradients sharded too")
     ap.add_argument("--skip-e2e", action="store_true")
@@ -143,7 +144,8 @@ def main() -> int:
     from llm_distillery_b200.models.llama import preset
     cfg = preset(args.model)
     B, L, K = args.micro_batch, args.seq_len, args.topk
-    tokens_per_step = B * L * world
+    A = max(1, args.grad_accum) if args.impl == "ours" else 1
+    tokens_per_step = B * L * world * A
 
     if args.impl == "baseline":
         from baseline.hf_baseline import BaselineRunner
@@ -157,16 +159,17 @@ def main() -> int:
         model = build_model(cfg, dtype=torch.bfloat16, device=dev, seed=1234)
         comm = make_comm(args.comm, dev, shard_strategy=args.shard) if world > 1 else None
         eng = DistillEngine(model, loss=args.loss, temperature=args.temperature, optimizer="adamw", lr=1e-5,
-                            crop_to_size=cfg.vocab_size, grad_accum=1, comm=comm)
+                            crop_to_size=cfg.vocab_size, grad_accum=A, comm=comm)
 
         class Runner:
             def device_step(self, db):
-                loss, _ = eng.micro_step(db, last=True)
+                for k in range(A):
+                    loss, _ = eng.micro_step(db, last=(k + 1 == A))
                 eng.optimizer_step()
                 return loss
 
             def e2e_step(self, hb):
-                return eng.train_step([hb])
+                return eng.train_step([hb] * A)
 
             def to_device(self, hb):
                 return hb.to_device(dev)
@@ -227,7 +230,7 @@ def main() -> int:
         if world > 1:
             dist.all_reduce(dt, op=dist.ReduceOp.MAX)
         e2e = {"value": tokens_per_step * args.steps / float(dt.item()), "unit": "tokens/s",
-               "ms_per_step": 1e3 * float(dt.item()) / args.steps, "h2d_bytes_per_step": h2d_bytes,
+               "ms_per_step": 1e3 * float(dt.item()) / args.steps, "h2d_bytes_per_step": h2d_bytes * A,
                "d2h_bytes_per_step": 4}
     clocks = sampler.stop() if rank == 0 else None
 
@@ -277,7 +280,7 @@ def main() -> int:
             "warmup": args.warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic token ids + synthetic top-K teacher targets, random-init weights",
             "impl": args.impl,
-            "config": {"model": args.model, "global_batch": B * world, "micro_batch_per_gpu": B, "seq_len": L,
+            "config": {"model": args.model, "global_batch": B * world * A, "micro_batch_per_gpu": B, "grad_accum": A, "seq_len": L,
                        "parallelism": f"dp{world}" + ("" if args.shard == "ddp" or world == 1 else f"-{args.shard}"),
                        "peak_mem_gb": round(torch.cuda.max_memory_allocated(dev) / 2 ** 30, 2),
                        # whole device, symmetric (peer-mapped) buffers included, which the allocator's peak does not see
