@@ -22,8 +22,10 @@ gradients, fp32 master weights and optimizer state over the data-parallel ranks:
 Per-rank memory is (2 + 4 + 4 + state) bytes x parameters / world plus two layers and the embedding / head in full,
 against (2 + 4) bytes x parameters replicated under ``ddp`` / ``fsdp`` (which shard only master weights and state).
 
-Collectives run through ``torch.distributed`` (NCCL on GPUs, on a side stream; gloo between CPU ranks). Every rank
-must issue the same sequence of them: a rank without a micro-batch in the last step of an epoch calls
+``FullShardComm`` runs the collectives through ``torch.distributed`` (NCCL on GPUs, on a side stream; gloo between
+CPU ranks). ``P2PFullShardComm`` replaces them by kernels over NVLink peer access: a handshake-free pull gather, and a
+reduction that on the last micro-batch of a step is fused with the AdamW update of the rank's piece. Every rank must
+issue the same sequence of collectives: a rank without a micro-batch in the last step of an epoch calls
 ``idle_micro_step`` instead of skipping.
 """
 from __future__ import annotations
