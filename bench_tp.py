@@ -6,6 +6,7 @@
         bench_tp.py collect [--model llama-3-70b] [--seq 8192] [--batch 1] [--topk 128] [--steps 3] [--layers N]
         bench_tp.py p2p     [--iters 10]
         bench_tp.py head    [--rows 32768] [--hidden 4096] [--vocab 128256] [--topk 200] [--iters 10]
+        bench_tp.py zero3   [--iters 10]
 
 gemms    the four linear layers of one decoder block at tensor-parallel width N: fused all-gather->GEMM and
          GEMM->reduce-scatter kernels against NCCL all_gather / reduce_scatter + torch.matmul (cuBLAS), with the
@@ -15,6 +16,8 @@ collect  teacher collection throughput (tokens/s) of the tensor-parallel forward
          output and not a benchmark number).
 head     the fused vocabulary-parallel LM head + distillation loss (forward and backward) over N vocabulary slices
          against cuBLAS + PyTorch ops + NCCL all-reduce, KL and JSD at T = 1 and 2.
+zero3    the kernels of full parameter sharding on one decoder layer of TinyLlama-1.1B and Llama-3-8B: pull gather,
+         reduce-scatter-accumulate and reduce-scatter + AdamW, against NCCL all_gather / reduce_scatter.
 p2p      peer-to-peer all-reduce (reduce-scatter + all-gather kernels) against NCCL all_reduce, bus bandwidth.
 
 Timing: CUDA events on the launching stream after warm-up, a barrier before each timed call, median per rank, MAX
@@ -239,9 +242,67 @@ def bench_p2p(args, dev, rank, world) -> None:
         del buf
 
 
+def bench_zero3(args, dev, rank, world) -> None:
+    """The three kernels of full parameter sharding on one decoder layer's worth of parameters, against the NCCL
+    collectives they replace: pull gather (bf16), reduce-scatter-accumulate (fp32), reduce-scatter + AdamW (fp32)."""
+    import ctypes
+    from llm_distillery_b200.ops._lib import _VP, _I, _LL
+    from llm_distillery_b200.parallel.p2p import P2PComm, SymmetricBuffer
+    _F = ctypes.c_float
+    _lib.register("b200_p2p_gather_pull", [_VP, _VP, _LL, _LL, _I, _I, _VP])
+    _lib.register("b200_p2p_reduce_scatter_acc_f32", [_VP, _VP, _LL, _LL, _I, _I, _I, _VP])
+    _lib.register("b200_p2p_rs_adamw_piece", [_VP, _LL, _VP, _VP, _VP, _VP, _VP, _LL, _I, _I, _F, _F, _F, _F, _F, _I, _F,
+                                              _I, _VP])
+    lib = _lib.kernels()
+    comm = P2PComm(dev)
+    for name in ("tinyllama-1.1b", "llama-3-8b"):
+        c = preset(name)
+        per_layer = (c.q_size + 2 * c.kv_size) * c.hidden_size + c.hidden_size * c.q_size + 3 * c.hidden_size * c.intermediate_size
+        numel = (per_layer + 256 * world - 1) // (256 * world) * (256 * world)
+        piece = numel // world
+        shard = SymmetricBuffer(piece, torch.bfloat16, dev)
+        grads = SymmetricBuffer(numel, torch.float32, dev)
+        full = torch.empty(numel, dtype=torch.bfloat16, device=dev)
+        out = torch.zeros(piece, dtype=torch.float32, device=dev)
+        master, m, v = (torch.zeros(piece, dtype=torch.float32, device=dev) for _ in range(3))
+        gfull = torch.zeros(numel, dtype=torch.float32, device=dev)
+
+        def pull():
+            _lib.check(lib.b200_p2p_gather_pull(shard.c_ptrs, _lib.ptr(full), 0, piece * 2, rank, world, _lib.stream()), "pull")
+
+        def rs_acc():
+            comm.barrier()
+            _lib.check(lib.b200_p2p_reduce_scatter_acc_f32(grads.c_ptrs, _lib.ptr(out), rank * piece, piece, rank, world, 1,
+                                                           _lib.stream()), "rs")
+
+        def rs_adam():
+            comm.barrier()
+            _lib.check(lib.b200_p2p_rs_adamw_piece(grads.c_ptrs, rank * piece, None, _lib.ptr(shard.tensor), _lib.ptr(master),
+                                                   _lib.ptr(m), _lib.ptr(v), piece, rank, world, 1e-5, 0.9, 0.99, 1e-8, 2e-8,
+                                                   1, 1.0 / world, 1, _lib.stream()), "rs_adamw")
+
+        def nccl_ag():
+            dist.all_gather_into_tensor(full, shard.tensor)
+
+        def nccl_rs():
+            dist.reduce_scatter_tensor(out, gfull)
+
+        ms = {k: timed_max(f, args.iters) for k, f in (("pull", pull), ("nccl_ag", nccl_ag), ("rs_acc", rs_acc),
+                                                       ("nccl_rs", nccl_rs), ("rs_adamw", rs_adam))}
+        link = (world - 1) / world          # share of the bytes that crosses NVLink
+        emit(rank, case="zero3 layer kernels", model=name, world=world, layer_params=numel,
+             ms={k: round(x, 4) for k, x in ms.items()},
+             gather_in_gbs=round(numel * 2 * link / ms["pull"] / 1e6, 1) if world > 1 else None,
+             gather_write_gbs=round(numel * 2 / ms["pull"] / 1e6, 1),
+             rs_in_gbs=round(piece * 4 * (world - 1) / ms["rs_acc"] / 1e6, 1) if world > 1 else None,
+             rs_adamw_hbm_gbs=round(piece * (4 * world + 24 + 2) / ms["rs_adamw"] / 1e6, 1))
+        del shard, grads, full, out, master, m, v, gfull
+    comm.check()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
-    ap.add_argument("cmd", choices=["gemms", "collect", "p2p", "head"])
+    ap.add_argument("cmd", choices=["gemms", "collect", "p2p", "head", "zero3"])
     ap.add_argument("--rows", type=int, default=32768)
     ap.add_argument("--hidden", type=int, default=4096)
     ap.add_argument("--vocab", type=int, default=128256)
@@ -264,7 +325,8 @@ def main() -> None:
     os.environ.setdefault("WORLD_SIZE", "1")
     dist.init_process_group("nccl", device_id=dev)
     rank, world = dist.get_rank(), dist.get_world_size()
-    {"gemms": bench_gemms, "collect": bench_collect, "p2p": bench_p2p, "head": bench_head}[args.cmd](args, dev, rank, world)
+    {"gemms": bench_gemms, "collect": bench_collect, "p2p": bench_p2p, "head": bench_head,
+     "zero3": bench_zero3}[args.cmd](args, dev, rank, world)
     torch.cuda.synchronize()
     dist.barrier()
     dist.destroy_process_group()

@@ -186,7 +186,8 @@ __global__ void __launch_bounds__(256) gather_pull_kernel(Peers src, uint4* __re
   constexpr int U = 8;
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (int k = 0; k < world; ++k) {
-    const int p = (rank + k) % world;          // own piece first, then the peers starting at the next rank
+    // CTAs start at different sources, so the local copy and the loads from every peer run side by side
+    const int p = (rank + k + (int)(blockIdx.x % (unsigned)world)) % world;
     const uint4* __restrict__ s = reinterpret_cast<const uint4*>(src.p[p]) + src_off_vec;
     uint4* __restrict__ d = dst + (long long)p * piece_vec;
     for (long long base = blockIdx.x * (long long)blockDim.x + threadIdx.x; base < piece_vec; base += stride * U) {
