@@ -188,10 +188,24 @@ class StudentModel(BaseModel):
             if self.rank == 0:
                 ckpt.save_hf_model(self.model, folder, tokenizer_src=self.tokenizer_dir)
 
+    _HASHED = ("model_name", "lr", "batch_size", "grad_accum", "loss_kind", "temperature", "alpha", "context_len",
+               "crop_to_size", "optimizer_name", "lr_scheduler_name", "num_warmup_steps", "decay_start", "final_lr",
+               "data_order", "freeze_layers", "seed")
+
+    def _config_hash(self) -> str:
+        """Fingerprint of what makes a resumed run the continuation of the saved one (not: paths, save / validation
+        intervals, world size)."""
+        import hashlib
+        import json
+        rec = {k: getattr(self, k, None) for k in self._HASHED}
+        return hashlib.sha256(json.dumps(rec, sort_keys=True, default=str).encode()).hexdigest()[:16]
+
     def _counters(self) -> dict:
         return {"num_trained_steps": self.num_trained_steps, "next_save_step": self.next_save_step,
                 "next_val_step": self.next_val_step, "next_accum_step": self.next_accum_step,
-                "total_training_steps": self.total_training_steps, "seed": self.seed, "world": self.world}
+                "total_training_steps": self.total_training_steps, "seed": self.seed, "world": self.world,
+                "tokens_trained": self.tokens_trained, "data_order": self.data_order,
+                "rng_state": self._rng.bit_generator.state, "config_hash": self._config_hash()}
 
     def _save_state(self, collective: bool = True) -> None:
         """``collective=False``: emergency save after a peer failed - no barrier, files of this rank only."""
@@ -215,9 +229,17 @@ class StudentModel(BaseModel):
         with self.engine.full_parameters(writeback=True):
             ckpt.load_model_state(self.paths.student_states, self.model)
         c = ckpt.load_trainer_state(self.paths.student_states, None, self.engine.opt, self.engine.schedule)
-        for k in ("num_trained_steps", "next_save_step", "next_val_step", "next_accum_step"):
+        for k in ("num_trained_steps", "next_save_step", "next_val_step", "next_accum_step", "tokens_trained"):
             if k in c:
                 setattr(self, k, c[k])
+        if "rng_state" in c:                 # the shuffle order of the epochs still to come continues where it stopped
+            try:
+                self._rng.bit_generator.state = c["rng_state"]
+            except (TypeError, ValueError, KeyError):
+                pass
+        if c.get("config_hash") not in (None, self._config_hash()) and self.rank == 0:
+            print("Note: the saved trainer state was written under different training settings "
+                  f"(fingerprint {c['config_hash']} != {self._config_hash()}); counters and optimizer state are reused as they are.")
 
     # ------------------------------------------------------------------ training
     def _prefetch_dataset_chunk(self, data_manager, data_list, full_collect, trainable_ids):
@@ -282,9 +304,33 @@ class StudentModel(BaseModel):
         self.progress_bar.close()
         self._unload_model()
 
+    def _phase_times(self) -> tuple[dict, dict]:
+        """(this rank's device-timed phases since the last step, cross-rank figures). With tracing on, every rank
+        takes part: the compute time (forward + loss + backward) of each rank is gathered, and the spread between the
+        slowest and the fastest rank is the time the fast ones spend waiting inside the gradient reduction."""
+        if not self.engine.timer.enabled:
+            return {}, {}
+        phases = self.engine.timer.summary()
+        cross = {}
+        if self.world > 1:
+            import torch.distributed as dist
+            if dist.is_initialized():
+                dev = self.engine.device if dist.get_backend() == "nccl" else "cpu"
+                mine = torch.tensor([phases.get("forward+loss", 0.0) + phases.get("backward", 0.0)],
+                                    dtype=torch.float64, device=dev)
+                parts = [torch.zeros_like(mine) for _ in range(self.world)]
+                dist.all_gather(parts, mine)
+                ts = [float(p.item()) for p in parts]
+                cross = {"Perf/rank skew ms": max(ts) - min(ts), "Perf/slowest rank": float(ts.index(max(ts)))}
+                step = sum(phases.values())
+                if step > 0:        # share of the step that is not compute: reduction + optimizer + waiting for peers
+                    cross["Perf/non-compute share"] = 1.0 - float(mine.item()) / step
+        return phases, cross
+
     def _optimizer_step(self) -> None:
         lr = self.engine.lr
         self.engine.optimizer_step()
+        phases, cross = self._phase_times()
         if self.logger is not None:
             perf = {"Learning Rate": lr}
             now = time.time()
@@ -294,8 +340,9 @@ class StudentModel(BaseModel):
                 perf["Perf/step ms"] = 1e3 * (now - last_t)
             self._perf_mark = (now, self.tokens_trained)
             if self.engine.timer.enabled:
-                for k, v in self.engine.timer.summary().items():
+                for k, v in phases.items():
                     perf[f"Perf/{k} ms"] = v
+                perf.update(cross)
                 if torch.cuda.is_available():
                     perf["Perf/HBM high-water GB"] = torch.cuda.max_memory_allocated() / 2 ** 30
             self.logger.log(perf, self.num_trained_steps)

@@ -421,7 +421,8 @@ def cpu_cli_zero3():
             "enable_topK": True, "device": "cpu", "num_epochs": 2, "num_warmup_steps": 2, "batch_size": 2,
             "grad_accum_batches": 1, "temperature": 1.0, "lr": 1e-3, "optimizer": "adamw", "data_order": "sorted",
             "training_precision": "fp32", "validate_every_n_epochs": 1, "save_student_every_n_epochs": 1,
-            "freeze_layers": [], "loss": "kl", "max_cache_size_gb": 320, "tp_size": 2}
+            "freeze_layers": [], "loss": "kl", "max_cache_size_gb": 320, "tp_size": 2, "save_final_state": True}
+    os.environ["B200_TRACE"] = "1"          # phase timers on: the per-rank skew figures are gathered and logged
     if rank == 0:
         tok = os.path.join(root, "tok")
         synthetic.make_tokenizer(tok, 400)
@@ -446,6 +447,12 @@ def cpu_cli_zero3():
             final = [d for d in os.listdir(base) if d.endswith("final")]
             assert len(final) == 1, os.listdir(base)
             finals[strat] = load_hf_state_dict(os.path.join(base, final[0]))
+            with open(os.path.join(root, f"cache_{strat}", "metrics.jsonl")) as f:
+                logged = [json.loads(line) for line in f if line.strip()]
+            assert any("Perf/rank skew ms" in rec for rec in logged), logged[:3]
+            with open(os.path.join(root, f"cache_{strat}", "student", "states", "trainer_state.json")) as f:
+                st = json.load(f)
+            assert len(st["config_hash"]) == 16 and "rng_state" in st and st["world"] == 2
     if rank == 0:
         init = load_hf_state_dict(os.path.join(root, "student"))
         moved = 0.0
