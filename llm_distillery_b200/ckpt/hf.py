@@ -125,8 +125,11 @@ def reshard_optimizer_state(shards: list[dict], optimizer) -> bool:
     old_size = int(shards[0]["total"]) // len(shards)
     if shards[0]["name"] != optimizer.name:
         return False
-    if shards[0].get("layout", "contiguous") != "contiguous" or getattr(flat, "layout", "contiguous") != "contiguous":
-        return False        # per-unit pieces (full sharding) are not slices of one flat space
+    saved_layout, layout = shards[0].get("layout", "contiguous"), getattr(flat, "layout", "contiguous")
+    if saved_layout != layout:
+        return False        # per-unit pieces (full sharding) and slices of one flat space do not convert
+    if layout == "per_unit":
+        return _reshard_per_unit(shards, optimizer)
     keys = list(shards[0]["state"].keys())
     for sd in shards:
         if sd["master"].numel() != old_size or any(
@@ -141,6 +144,44 @@ def reshard_optimizer_state(shards: list[dict], optimizer) -> bool:
         if full.numel() < flat.total:       # the new layout pads further: zeros there (no parameter lives in padding)
             full = torch.cat([full, torch.zeros(flat.total - full.numel())])
         return full[flat.shard_lo: flat.shard_lo + flat.shard_size]
+
+    flat.master.copy_(cut([sd["master"] for sd in shards]))
+    for k in keys:
+        optimizer.state[k].copy_(cut([sd["state"][k] for sd in shards]))
+    optimizer.step_count = int(shards[0]["step_count"])
+    flat.model_shard().copy_(flat.master.to(flat.dtype))
+    return True
+
+
+def _reshard_per_unit(shards: list[dict], optimizer) -> bool:
+    """Full sharding: every rank holds piece r of every unit. A unit's saved pieces, in rank order, are the unit up to
+    its (world-dependent) tail padding; the new rank's piece is cut out of that, unit by unit."""
+    flat = optimizer.flat
+    old_units, new_units = shards[0].get("units"), flat.unit_table()
+    if not old_units or len(old_units) != len(new_units):
+        return False
+    if any(o[0] != n[0] or int(o[1]) != int(n[1]) for o, n in zip(old_units, new_units)):
+        return False        # other units or other sizes: not the same model / freeze pattern
+    keys = list(shards[0]["state"].keys())
+    old_size = sum(int(u[2]) for u in old_units)
+    for sd in shards:
+        if sd["master"].numel() != old_size or any(
+                (not torch.is_tensor(sd["state"][k])) or sd["state"][k].numel() != old_size or
+                sd["state"][k].dtype != torch.float32 for k in keys):
+            return False
+    if any(k not in optimizer.state or optimizer.state[k].numel() != flat.shard_size for k in keys):
+        return False
+
+    def cut(parts: list[torch.Tensor]) -> torch.Tensor:
+        out, old_lo = [], 0
+        for (_, payload, old_piece), (_, _, new_piece) in zip(old_units, new_units):
+            full = torch.cat([t.reshape(-1)[old_lo:old_lo + old_piece].float().cpu() for t in parts])[:payload]
+            need = new_piece * flat.world
+            if full.numel() < need:
+                full = torch.cat([full, torch.zeros(need - full.numel())])
+            out.append(full[flat.rank * new_piece:(flat.rank + 1) * new_piece])
+            old_lo += old_piece
+        return torch.cat(out)
 
     flat.master.copy_(cut([sd["master"] for sd in shards]))
     for k in keys:

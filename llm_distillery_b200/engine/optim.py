@@ -229,7 +229,8 @@ class FlatOptimizer:
     def state_dict(self) -> dict:
         return {"name": self.name, "step_count": self.step_count, "lr": self.lr, "master": self.flat.master,
                 "state": dict(self.state), "shard": (self.flat.rank, self.flat.world), "total": self.flat.total,
-                "layout": getattr(self.flat, "layout", "contiguous")}
+                "layout": getattr(self.flat, "layout", "contiguous"),
+                "units": self.flat.unit_table() if hasattr(self.flat, "unit_table") else None}
 
     def load_state_dict(self, sd: dict) -> None:
         if sd["name"] != self.name:

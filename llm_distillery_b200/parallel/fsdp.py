@@ -61,6 +61,7 @@ class _Unit:
         for p in params:
             self.offsets.append(off)
             off += _round_up(p.numel(), ALIGN)
+        self.payload = off           # elements before the padding that depends on the world size
         self.numel = _round_up(off, 256 * world)
         self.piece = self.numel // world
         self.is_layer = name.startswith("layer")
@@ -133,6 +134,11 @@ class ShardedFlat:
                     self.slots.append(slot)
                     self.unit_of[id(p)] = u
         self.master = self._model_shard.float().clone()
+
+    def unit_table(self) -> list[tuple[str, int, int]]:
+        """(name, elements before padding, piece length) per unit in shard-space order: what a checkpoint needs to
+        re-cut the pieces for another world size."""
+        return [(u.name, u.payload, u.piece) for u in self.units]
 
     # ---- FlatParams surface
     def piece_of(self, u: _Unit) -> torch.Tensor:
