@@ -5,6 +5,7 @@
               layer) equals single-process training, with gradient accumulation, an evaluation between steps, a rank
               without a micro-batch, tied embeddings, a frozen layer and a checkpoint taken through the gathered view
   cpu_cli_zero3  gloo ranks on CPU: the command-line pipeline trains the same student replicated and fully sharded
+  gpu_cli_zero3  the same pipeline on two GPUs in bf16
   gpu_zero3   GPU ranks: full parameter sharding, over NCCL and over the peer-access kernels, equals the replicated run
   gpu_p2p     NCCL + NVLink P2P ranks: P2P all-reduce equals NCCL all-reduce; a P2P-communicated training run equals
               the NCCL-communicated one
@@ -405,8 +406,8 @@ def cpu_cli_tp():
         print("WORKER_OK")
 
 
-def cpu_cli_zero3():
-    """The command-line pipeline under two gloo ranks, student trained once replicated and once fully sharded: five
+def _cli_zero3(device: str, precision: str, tol: float, tp: int, hidden: int, ffn: int):
+    """The command-line pipeline under two ranks, student trained once replicated and once fully sharded: five
     batches over two ranks, so the last step has a rank without a micro-batch; the saved students are equal."""
     import json
     from llm_distillery_b200 import cli
@@ -418,24 +419,30 @@ def cpu_cli_zero3():
     conf = {"dataset_path": os.path.join(root, "train.jsonl"),
             "validation_dataset_path": os.path.join(root, "val.jsonl"), "teacher_models_folder": os.path.join(root, "teachers"),
             "student_path": os.path.join(root, "student"), "context_len": 96, "crop_distr_to_size": 400, "save_topK": 20,
-            "enable_topK": True, "device": "cpu", "num_epochs": 2, "num_warmup_steps": 2, "batch_size": 2,
+            "enable_topK": True, "device": device, "num_epochs": 2, "num_warmup_steps": 2, "batch_size": 2,
             "grad_accum_batches": 1, "temperature": 1.0, "lr": 1e-3, "optimizer": "adamw", "data_order": "sorted",
-            "training_precision": "fp32", "validate_every_n_epochs": 1, "save_student_every_n_epochs": 1,
-            "freeze_layers": [], "loss": "kl", "max_cache_size_gb": 320, "tp_size": 2, "save_final_state": True}
+            "training_precision": precision, "validate_every_n_epochs": 1, "save_student_every_n_epochs": 1,
+            "freeze_layers": [], "loss": "kl", "max_cache_size_gb": 320, "tp_size": tp, "save_final_state": True}
     os.environ["B200_TRACE"] = "1"          # phase timers on: the per-rank skew figures are gathered and logged
     if rank == 0:
         tok = os.path.join(root, "tok")
         synthetic.make_tokenizer(tok, 400)
-        tcfg = preset("plumbing-teacher", vocab_size=512, hidden_size=64, intermediate_size=176, max_position_embeddings=512)
-        scfg = preset("plumbing-student", vocab_size=512, hidden_size=64, intermediate_size=176, max_position_embeddings=512)
-        synthetic.make_model_dir(os.path.join(root, "teachers", "teacher_a"), tcfg, tok, seed=1, batch_size=4)
-        synthetic.make_model_dir(os.path.join(root, "student"), scfg, tok, seed=2)
+        kw = dict(vocab_size=512, hidden_size=hidden, intermediate_size=ffn, max_position_embeddings=512)
+        synthetic.make_model_dir(os.path.join(root, "teachers", "teacher_a"), preset("plumbing-teacher", **kw), tok, seed=1,
+                                 batch_size=4)
+        synthetic.make_model_dir(os.path.join(root, "student"), preset("plumbing-student", **kw), tok, seed=2)
         synthetic.make_dataset(os.path.join(root, "train.jsonl"), 10, seed=3)
         synthetic.make_dataset(os.path.join(root, "val.jsonl"), 4, seed=4)
         for strat in ("ddp", "zero3"):
             with open(os.path.join(root, f"config_{strat}.json"), "w") as f:
                 json.dump(dict(conf, cache_folder=os.path.join(root, f"cache_{strat}"), shard_strategy=strat), f)
-    dist.init_process_group("gloo")
+    if device == "cpu":
+        dist.init_process_group("gloo")
+    else:
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        local = int(os.environ.get("LOCAL_RANK", "0"))
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     dist.barrier()
     finals = {}
     for strat in ("ddp", "zero3"):
@@ -453,15 +460,29 @@ def cpu_cli_zero3():
             with open(os.path.join(root, f"cache_{strat}", "student", "states", "trainer_state.json")) as f:
                 st = json.load(f)
             assert len(st["config_hash"]) == 16 and "rng_state" in st and st["world"] == 2
+    if device != "cpu":
+        from llm_distillery_b200.ops import _lib
+        torch.cuda.synchronize()
+        assert _lib.take_device_error() == 0
     if rank == 0:
         init = load_hf_state_dict(os.path.join(root, "student"))
         moved = 0.0
         for k, v in finals["ddp"].items():
             err = (v.float() - finals["zero3"][k].float()).abs().max().item()
-            assert err < 1e-5, (k, err)
+            assert err < tol, (k, err)
+            assert torch.isfinite(v.float()).all(), k
             moved = max(moved, (v.float() - init[k].float()).abs().max().item())
         assert moved > 1e-4, "training did not change the student"
         print("WORKER_OK")
+
+
+def cpu_cli_zero3():
+    _cli_zero3("cpu", "fp32", 1e-5, tp=2, hidden=64, ffn=176)
+
+
+def gpu_cli_zero3():
+    """Same on two GPUs in bf16: data-parallel collection replicas, NVLink data parallelism / full sharding."""
+    _cli_zero3("cuda", "bf16", 3e-2, tp=1, hidden=256, ffn=688)
 
 
 def gpu_tp():
@@ -515,4 +536,4 @@ def gpu_tp():
 if __name__ == "__main__":
     {"cpu_engine": cpu_engine, "gpu_p2p": gpu_p2p, "cpu_tp": cpu_tp, "gpu_tp": gpu_tp, "cpu_cli_tp": cpu_cli_tp,
      "cpu_vp_head": cpu_vp_head, "cpu_rank_loss": cpu_rank_loss, "cpu_zero3": cpu_zero3, "gpu_zero3": gpu_zero3,
-     "cpu_cli_zero3": cpu_cli_zero3}[sys.argv[1]]()
+     "cpu_cli_zero3": cpu_cli_zero3, "gpu_cli_zero3": gpu_cli_zero3}[sys.argv[1]]()

@@ -38,6 +38,13 @@ def test_cpu_ranks_pipeline_with_fully_sharded_student(tmp_path):
 
 
 @pytest.mark.gpu
+def test_gpu_pipeline_with_replicated_and_fully_sharded_student(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least 2 GPUs")
+    _launch("gpu_cli_zero3", 2, env={"NCCL_NVLS_ENABLE": "0"}, extra=(str(tmp_path),))
+
+
+@pytest.mark.gpu
 def test_full_parameter_sharding_matches_replicated_training():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs at least 2 GPUs")
