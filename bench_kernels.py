@@ -186,6 +186,50 @@ def bench_topk_family(rows, V, K, iters):
            speedup_vs_cpu_loop=round(cpu_ms / ms, 1), note="CPU = per-row table lookup + unique + index_add + sort")
 
 
+def bench_trie_walk(iters):
+    """Teacher-vocabulary -> student-vocabulary table of a 32 000-token teacher against a 128 256-token student
+    (synthetic byte-fallback vocabularies): the trie-walk kernel against the per-token Python walk."""
+    import random
+    import time
+    from llm_distillery_b200.align.aligner import ByteTrie
+    from llm_distillery_b200.ops import topk as tk
+    rng = random.Random(0)
+    alpha = bytes(range(97, 123)) + b" \xc3\xa9"
+
+    def words(n):
+        return [bytes(rng.choice(alpha) for _ in range(rng.randint(2, 12))) for _ in range(n)]
+    student = [bytes([b]) for b in range(256)] + words(128256 - 256)
+    teacher = [bytes([b]) for b in range(256)] + words(32000 - 256)
+    trie = ByteTrie()
+    for i, b in enumerate(student):
+        trie.insert(b, i)
+    flat = trie.flatten()
+    t0 = time.perf_counter()
+    want = [trie.longest_prefix(b) for b in teacher]
+    cpu_ms = (time.perf_counter() - t0) * 1e3
+    got, _ = tk.trie_walk(flat, teacher, "cuda")
+    assert got.cpu().tolist() == want
+    # device-resident inputs: time the kernel, not the upload of the trie
+    g = {k: torch.from_numpy(v).cuda() for k, v in flat.items()}
+    import numpy as np
+    lens = np.fromiter((len(b) for b in teacher), dtype=np.int64, count=len(teacher))
+    off = np.zeros(len(teacher) + 1, dtype=np.int64)
+    np.cumsum(lens, out=off[1:])
+    tb = torch.from_numpy(np.frombuffer(b"".join(teacher), dtype=np.uint8).copy()).cuda()
+    to = torch.from_numpy(off).cuda()
+    out = torch.empty(len(teacher), dtype=torch.int32, device="cuda")
+    lib = _lib.kernels()
+
+    def run():
+        _lib.check(lib.b200_trie_walk(_lib.ptr(g["edge_start"]), _lib.ptr(g["edge_byte"]), _lib.ptr(g["edge_child"]),
+                                      _lib.ptr(g["node_value"]), g["node_value"].numel(), _lib.ptr(tb), _lib.ptr(to),
+                                      len(teacher), _lib.ptr(out), None, _lib.stream()), "b200_trie_walk")
+    ms = timed(run, iters)
+    report("trie_walk", ms, shape=[len(teacher), len(student), int(g["node_value"].numel())], cpu_loop_ms=round(cpu_ms, 1),
+           speedup_vs_cpu_loop=round(cpu_ms / ms, 1), bytes_walked=int(off[-1]),
+           note="shape = teacher tokens, student tokens, trie nodes; CPU = dictionary trie walked token by token in Python")
+
+
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -219,6 +263,7 @@ def main():
         bench_elementwise(args.rows, args.hidden, args.ffn, args.iters)
     elif args.cmd == "topk":
         bench_topk_family(args.rows, args.vocab, args.topk, args.iters)
+        bench_trie_walk(args.iters)
     else:
         for shp, lay in [((8192, 8192, 8192), "nt"), ((16384, 2560, 2048), "nt"), ((16384, 2048, 2048), "nt"),
                          ((16384, 11264, 2048), "nt"), ((16384, 2048, 5632), "nt"), ((16384, 2048, 2560), "nn"),
@@ -230,6 +275,7 @@ def main():
         bench_head(16384, 2048, 32000, 200, max(3, args.iters // 4))
         bench_elementwise(16384, 2048, 5632, args.iters)
         bench_topk_family(4096, 32000, 200, max(3, args.iters // 2))
+        bench_trie_walk(max(3, args.iters // 2))
 
 
 if __name__ == "__main__":

@@ -9,7 +9,8 @@ Here a teacher of another vocabulary family is mapped onto the student's vocabul
    ignores it).
 2. *Mass.* A byte-level trie over the student vocabulary gives every teacher token the student token that is the
    LONGEST prefix of its byte string (what a greedy longest-match tokenizer would emit first); the walk depends
-   only on the token, so it is tabulated once per tokenizer pair (``build_vocab_map``). Per position the teacher's
+   only on the token, so it is tabulated once per tokenizer pair (``build_vocab_map``; on a GPU the whole teacher
+   vocabulary is walked through the flattened trie by the ``trie_walk`` kernel, csrc/align/trie.cu). Per position the teacher's
    top-K probabilities are sent through the table, probabilities meeting on one student id are summed, the best K
    are kept (kernel ``remap_topk``; PyTorch restatement in ``ops.topk``). Total mass never grows; it is conserved
    exactly when every teacher token has an image (byte-fallback vocabularies always do).
@@ -80,6 +81,24 @@ class ByteTrie:
         if self.value[node] < 0 or value < self.value[node]:
             self.value[node] = value      # duplicates: keep the lowest id
 
+    def flatten(self) -> dict[str, np.ndarray]:
+        """The trie as flat arrays for the walk kernel: node n owns edges ``edge_start[n] .. edge_start[n+1]-1`` sorted
+        by byte; edge e leads to node ``edge_child[e]``; ``node_value[n]`` is the id stored at n (-1: none)."""
+        n = len(self.children)
+        counts = np.fromiter((len(c) for c in self.children), dtype=np.int32, count=n)
+        start = np.zeros(n + 1, dtype=np.int32)
+        np.cumsum(counts, out=start[1:])
+        edge_byte = np.zeros(max(1, int(start[-1])), dtype=np.uint8)
+        edge_child = np.zeros(max(1, int(start[-1])), dtype=np.int32)
+        for i, c in enumerate(self.children):
+            if c:
+                ks = sorted(c)
+                a = int(start[i])
+                edge_byte[a:a + len(ks)] = ks
+                edge_child[a:a + len(ks)] = [c[k] for k in ks]
+        return {"edge_start": start, "edge_byte": edge_byte, "edge_child": edge_child,
+                "node_value": np.asarray(self.value, dtype=np.int32)}
+
     def longest_prefix(self, key: bytes) -> int:
         node, best = 0, -1
         for ch in key:
@@ -91,15 +110,22 @@ class ByteTrie:
         return best
 
 
-def build_vocab_map(teacher_tokenizer, student_tokenizer, student_vocab_limit: int | None = None) -> np.ndarray:
-    """int32 [teacher vocab]: the student token that is the longest byte-prefix of each teacher token (-1: none)."""
-    sb = token_bytes(student_tokenizer)
+def vocab_map_from_bytes(teacher_bytes: list[bytes], student_bytes: list[bytes], student_vocab_limit: int | None = None,
+                         device=None) -> np.ndarray:
+    """int32 [teacher vocab]: the student token that is the longest byte-prefix of each teacher token (-1: none).
+    On a CUDA ``device`` the whole teacher vocabulary is walked through the flattened trie by one kernel launch
+    (``ops.topk.trie_walk``); otherwise token by token in Python."""
     trie = ByteTrie()
-    for i, b in enumerate(sb):
+    for i, b in enumerate(student_bytes):
         if b and (student_vocab_limit is None or i < student_vocab_limit):
             trie.insert(b, i)
-    tb = token_bytes(teacher_tokenizer)
-    return np.asarray([trie.longest_prefix(b) if b else -1 for b in tb], dtype=np.int32)
+    if device is not None and torch.device(device).type == "cuda" and teacher_bytes:
+        return topk_ops.trie_walk(trie.flatten(), teacher_bytes, device)[0].cpu().numpy()
+    return np.asarray([trie.longest_prefix(b) if b else -1 for b in teacher_bytes], dtype=np.int32)
+
+
+def build_vocab_map(teacher_tokenizer, student_tokenizer, student_vocab_limit: int | None = None, device=None) -> np.ndarray:
+    return vocab_map_from_bytes(token_bytes(teacher_tokenizer), token_bytes(student_tokenizer), student_vocab_limit, device)
 
 
 def start_offsets(tokens: np.ndarray, length: int, tok_bytes: list[bytes]) -> np.ndarray:
@@ -129,8 +155,8 @@ def align_positions(student_convo, teacher_convo, student_bytes, teacher_bytes) 
 
 class VocabAligner:
     def __init__(self, teacher_tokenizer, student_tokenizer, student_dataset, student_validation_dataset,
-                 student_vocab_limit: int | None = None):
-        self.table_np = build_vocab_map(teacher_tokenizer, student_tokenizer, student_vocab_limit)
+                 student_vocab_limit: int | None = None, device=None):
+        self.table_np = build_vocab_map(teacher_tokenizer, student_tokenizer, student_vocab_limit, device)
         self.table = torch.from_numpy(self.table_np)
         self.student_bytes = token_bytes(student_tokenizer)
         self.teacher_bytes = token_bytes(teacher_tokenizer)
@@ -156,6 +182,7 @@ def attach_aligners(teachers, student) -> None:
     for t in teachers:
         if getattr(t, "needs_alignment", False):
             t.aligner = VocabAligner(load_tokenizer(t.model_path), s_tok, student.dataset, student.validation_dataset,
-                                     student_vocab_limit=student.crop_to_size or None)
+                                     student_vocab_limit=student.crop_to_size or None,
+                                     device=getattr(student, "device", None))
             print(f"{t.model_name}: cross-tokenizer alignment, {100 * t.aligner.coverage:.1f}% of its tokens have an "
                   f"image in the student vocabulary")

@@ -9,6 +9,7 @@ from ._lib import _VP, _I, _LL
 _lib.register("b200_topk_logprob", [_VP, _LL, _I, _I, _I, _VP, _VP, _VP])
 _lib.register("b200_topk_merge", [_VP, _VP, _VP, _VP, _I, _I, _VP, _VP, _VP])
 _lib.register("b200_remap_topk", [_VP, _VP, _VP, _I, _I, _I, _I, _VP, _VP, _VP])
+_lib.register("b200_trie_walk", [_VP, _VP, _VP, _VP, _I, _VP, _VP, _I, _VP, _VP, _VP])
 _lib.register("b200_logprob_full", [_VP, _LL, _I, _I, _VP, _LL, _VP])
 
 
@@ -88,3 +89,40 @@ def remap_topk(lp: torch.Tensor, ids: torch.Tensor, table: torch.Tensor, k_out: 
                                               _lib.ptr(table.int().contiguous()), table.numel(), rows, K, k_out,
                                               _lib.ptr(o_lp), _lib.ptr(o_id), _lib.stream()), "b200_remap_topk")
     return o_lp, o_id
+
+
+def trie_walk(flat: dict, token_bytes: list[bytes], device):
+    """Longest-prefix lookup of every byte string in ``token_bytes`` in a flattened byte trie
+    (``align.aligner.ByteTrie.flatten``). Returns (int32 id per string, -1 = no prefix is stored; int32 number of bytes
+    the found prefix covers). CUDA devices run one thread per string (kernel ``trie_walk``); the CPU path walks the
+    same arrays in Python."""
+    import numpy as np
+    lens = np.fromiter((len(b) for b in token_bytes), dtype=np.int64, count=len(token_bytes))
+    off = np.zeros(len(token_bytes) + 1, dtype=np.int64)
+    np.cumsum(lens, out=off[1:])
+    blob = np.frombuffer(b"".join(token_bytes) or b"\0", dtype=np.uint8)
+    dev = torch.device(device)
+    if dev.type != "cuda":
+        es, eb, ec, nv = flat["edge_start"], flat["edge_byte"], flat["edge_child"], flat["node_value"]
+        out = np.full(len(token_bytes), -1, dtype=np.int32)
+        out_len = np.zeros(len(token_bytes), dtype=np.int32)
+        for t in range(len(token_bytes)):
+            node = 0
+            for i in range(int(off[t]), int(off[t + 1])):
+                a, e = int(es[node]), int(es[node + 1])
+                j = a + int(np.searchsorted(eb[a:e], blob[i]))
+                if j >= e or eb[j] != blob[i]:
+                    break
+                node = int(ec[j])
+                if nv[node] >= 0:
+                    out[t], out_len[t] = nv[node], i - int(off[t]) + 1
+        return torch.from_numpy(out), torch.from_numpy(out_len)
+    g = {k: torch.from_numpy(np.ascontiguousarray(v)).to(dev) for k, v in flat.items()}
+    tb, to = torch.from_numpy(blob.copy()).to(dev), torch.from_numpy(off).to(dev)
+    out = torch.empty(len(token_bytes), dtype=torch.int32, device=dev)
+    out_len = torch.empty(len(token_bytes), dtype=torch.int32, device=dev)
+    _lib.check(_lib.kernels().b200_trie_walk(_lib.ptr(g["edge_start"]), _lib.ptr(g["edge_byte"]), _lib.ptr(g["edge_child"]),
+                                             _lib.ptr(g["node_value"]), g["node_value"].numel(), _lib.ptr(tb), _lib.ptr(to),
+                                             len(token_bytes), _lib.ptr(out), _lib.ptr(out_len), _lib.stream()),
+               "b200_trie_walk")
+    return out, out_len

@@ -135,3 +135,67 @@ def test_two_teachers_one_with_another_tokenizer(toks, tmp_path):
         assert ix[fin].max() < 400 and (np.exp(v[fin.any(1)]).sum(-1) <= 1.0 + 1e-2).all()
     assert got_rows > 0 and empty_rows > 0
     st.close()
+
+
+def _random_vocabularies(seed, n_student=3000, n_teacher=4000):
+    """Byte-fallback style vocabularies: all 256 single bytes plus random multi-byte strings over a small alphabet
+    (so that prefixes collide often), some strings in both."""
+    import random
+    rng = random.Random(seed)
+    alpha = b"abcde \xc3\xa9"
+    def words(n):
+        return [bytes(rng.choice(alpha) for _ in range(rng.randint(1, 9))) for _ in range(n)]
+    student = [bytes([b]) for b in range(256)] + words(n_student) + [b""]
+    teacher = [b"", bytes([7])] + words(n_teacher) + student[300:600] + [b"\xff\xfe\xfd" * 5]
+    return teacher, student
+
+
+def test_flattened_trie_walk_equals_the_dictionary_trie():
+    import numpy as np
+    from llm_distillery_b200.align.aligner import ByteTrie, vocab_map_from_bytes
+    from llm_distillery_b200.ops.topk import trie_walk
+    teacher, student = _random_vocabularies(0, 400, 500)
+    trie = ByteTrie()
+    for i, b in enumerate(student):
+        if b:
+            trie.insert(b, i)
+    want = np.asarray([trie.longest_prefix(b) if b else -1 for b in teacher])
+    got, got_len = trie_walk(trie.flatten(), teacher, "cpu")
+    assert np.array_equal(got.numpy(), want)
+    for t, (sid, n) in enumerate(zip(got.tolist(), got_len.tolist())):
+        if sid >= 0:
+            assert student[sid] == teacher[t][:n] and n == len(student[sid])
+        else:
+            assert n == 0
+    # byte-fallback student vocabulary: every non-empty teacher token has an image
+    assert all(s >= 0 for s, b in zip(got.tolist(), teacher) if b)
+    assert np.array_equal(vocab_map_from_bytes(teacher, student), want)
+    # a vocabulary limit removes the longer tokens: images fall back to shorter prefixes, never disappear
+    lim = vocab_map_from_bytes(teacher, student, student_vocab_limit=256)
+    assert all(0 <= s < 256 for s, b in zip(lim.tolist(), teacher) if b)
+
+
+@pytest.mark.gpu
+def test_trie_walk_kernel_equals_the_dictionary_trie():
+    import numpy as np
+    from llm_distillery_b200.align.aligner import ByteTrie, vocab_map_from_bytes
+    from llm_distillery_b200.ops import _lib
+    from llm_distillery_b200.ops.topk import trie_walk
+    for seed, (ns, nt) in enumerate([(3000, 4000), (20000, 50000), (5, 3)]):
+        teacher, student = _random_vocabularies(seed, ns, nt)
+        trie = ByteTrie()
+        for i, b in enumerate(student):
+            if b:
+                trie.insert(b, i)
+        want = np.asarray([trie.longest_prefix(b) if b else -1 for b in teacher])
+        got, got_len = trie_walk(trie.flatten(), teacher, "cuda")
+        torch.cuda.synchronize()
+        assert _lib.take_device_error() == 0
+        assert np.array_equal(got.cpu().numpy(), want)
+        lens = got_len.cpu().tolist()
+        assert all((n == len(student[s])) if s >= 0 else n == 0 for s, n in zip(want.tolist(), lens))
+        assert np.array_equal(vocab_map_from_bytes(teacher, student, device="cuda"), want)
+    # a student vocabulary without any token: nothing has an image
+    empty = ByteTrie().flatten()
+    got, _ = trie_walk(empty, [b"abc", b""], "cuda")
+    assert got.cpu().tolist() == [-1, -1]
