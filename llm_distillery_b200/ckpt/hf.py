@@ -272,6 +272,20 @@ def load_tp_weights(path: str, rank: int, tp: int, vocab: int | None = None, dty
     w = {"embed_tokens": sl("model.embed_tokens.weight"), "norm": sl("model.norm.weight")}
     for i in range(cfg.num_hidden_layers):
         hp, p = f"model.layers.{i}.", f"layers.{i}."
+        if cfg.model_type == "phi3":        # fused tensors in the checkpoint: this rank's q / k / v and gate / up rows
+            qn, kn = H * d, Hkv * d
+            fused = hp + "self_attn.qkv_proj.weight"
+            w[p + "qkv_proj"] = torch.cat([sl(fused, rows=(rank * Hl * d, (rank + 1) * Hl * d)),
+                                           sl(fused, rows=(qn + rank * Hkvl * d, qn + (rank + 1) * Hkvl * d)),
+                                           sl(fused, rows=(qn + kn + rank * Hkvl * d, qn + kn + (rank + 1) * Hkvl * d))], 0)
+            w[p + "o_proj"] = sl(hp + "self_attn.o_proj.weight", cols=(rank * Hl * d, (rank + 1) * Hl * d)).contiguous()
+            gu = hp + "mlp.gate_up_proj.weight"
+            w[p + "gate_up_proj"] = torch.cat([sl(gu, rows=(rank * fl, (rank + 1) * fl)),
+                                               sl(gu, rows=(f + rank * fl, f + (rank + 1) * fl))], 0)
+            w[p + "down_proj"] = sl(hp + "mlp.down_proj.weight", cols=(rank * fl, (rank + 1) * fl)).contiguous()
+            w[p + "input_layernorm"] = sl(hp + "input_layernorm.weight")
+            w[p + "post_attention_layernorm"] = sl(hp + "post_attention_layernorm.weight")
+            continue
         w[p + "qkv_proj"] = torch.cat([sl(hp + "self_attn.q_proj.weight", rows=(rank * Hl * d, (rank + 1) * Hl * d)),
                                        sl(hp + "self_attn.k_proj.weight", rows=(rank * Hkvl * d, (rank + 1) * Hkvl * d)),
                                        sl(hp + "self_attn.v_proj.weight", rows=(rank * Hkvl * d, (rank + 1) * Hkvl * d))], 0)

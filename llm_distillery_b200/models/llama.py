@@ -15,7 +15,7 @@ from __future__ import annotations
 import json
 import math
 import os
-from dataclasses import dataclass, asdict
+from dataclasses import asdict, dataclass, field
 
 import torch
 import torch.nn as nn
@@ -37,8 +37,12 @@ class LlamaConfig:
     tie_word_embeddings: bool = False
     bos_token_id: int = 1
     eos_token_id: int = 2
-    model_type: str = "llama"
+    model_type: str = "llama"         # llama | mistral | qwen2 (q/k/v bias) | phi3 (fused projections in the checkpoint)
     attention_bias: bool = False      # bias on the q/k/v projections (Qwen2 family); o_proj and the MLP have none
+    rope_scaling: dict | None = None  # HuggingFace dict; types default / linear / llama3 (ops.basic.rope_tables)
+    sliding_window: int | None = None  # attention here is full causal: sequences longer than the window are refused
+    pad_token_id: int | None = None
+    extra: dict = field(default_factory=dict)   # other keys of the source config.json, written back unchanged
 
     @property
     def head_dim(self) -> int:
@@ -67,20 +71,34 @@ class LlamaConfig:
 
     def to_hf_dict(self) -> dict:
         d = asdict(self)
-        if self.attention_bias:     # q/k/v bias without o_proj bias is the Qwen2 layout in HuggingFace terms
+        extra = d.pop("extra") or {}
+        for k in ("rope_scaling", "sliding_window", "pad_token_id"):
+            if d[k] is None:
+                d.pop(k)
+        if self.model_type == "phi3":
+            d.pop("attention_bias")
+            d.update(architectures=["Phi3ForCausalLM"], hidden_act="silu", torch_dtype="bfloat16")
+        elif self.attention_bias:     # q/k/v bias without o_proj bias is the Qwen2 layout in HuggingFace terms
             d.pop("attention_bias")
             d.update(architectures=["Qwen2ForCausalLM"], model_type="qwen2", hidden_act="silu", torch_dtype="bfloat16",
                      use_sliding_window=False)
+        elif self.model_type == "mistral":
+            d.pop("attention_bias")
+            d.update(architectures=["MistralForCausalLM"], hidden_act="silu", torch_dtype="bfloat16")
         else:
             d.update(architectures=["LlamaForCausalLM"], hidden_act="silu", torch_dtype="bfloat16",
                      attention_bias=False, mlp_bias=False)
-        return d
+        return {**extra, **d}
+
+    _KNOWN_TYPES = ("llama", "mistral", "qwen2", "phi3")
 
     @classmethod
     def from_hf_dict(cls, d: dict) -> "LlamaConfig":
-        keys = {f for f in cls.__dataclass_fields__}
+        keys = {f for f in cls.__dataclass_fields__} - {"extra"}
         kw = {k: v for k, v in d.items() if k in keys}
         mt = d.get("model_type", "llama")
+        if mt not in cls._KNOWN_TYPES:
+            raise NotImplementedError(f"model_type {mt!r}: only Llama-shaped decoders are built {cls._KNOWN_TYPES}")
         if mt == "qwen2":
             kw["attention_bias"] = True
         elif kw.get("attention_bias"):
@@ -88,9 +106,25 @@ class LlamaConfig:
                                       "q/k/v-only bias (model_type qwen2) is")
         if d.get("mlp_bias"):
             raise NotImplementedError("mlp_bias is not supported")
+        if d.get("hidden_act", "silu") not in ("silu", "swish"):
+            raise NotImplementedError(f"hidden_act {d['hidden_act']!r}: only SwiGLU (silu) is built")
+        if float(d.get("partial_rotary_factor", 1.0) or 1.0) != 1.0:
+            raise NotImplementedError("partial rotary embeddings are not built")
         if "num_key_value_heads" not in kw or kw["num_key_value_heads"] is None:
             kw["num_key_value_heads"] = kw.get("num_attention_heads", 32)
-        return cls(**kw)
+        hd = d.get("head_dim")
+        if hd is not None and hd * kw.get("num_attention_heads", 32) != kw.get("hidden_size", 2048):
+            raise NotImplementedError("head_dim different from hidden_size / num_attention_heads is not built")
+        if mt == "qwen2" and not d.get("use_sliding_window", False):
+            kw["sliding_window"] = None        # Qwen2 configs carry a window that is switched off
+        cfg = cls(**kw)
+        if cfg.rope_scaling is not None:       # fail at load time, not at the first forward
+            kind = cfg.rope_scaling.get("rope_type", cfg.rope_scaling.get("type"))
+            if kind not in (None, "default", "linear", "llama3"):
+                raise NotImplementedError(f"rope_scaling type {kind!r} is not built (default, linear and llama3 are)")
+        generated = {"architectures", "hidden_act", "torch_dtype", "mlp_bias", "use_sliding_window", "head_dim"}
+        cfg.extra = {k: v for k, v in d.items() if k not in keys and k not in generated}
+        return cfg
 
     @classmethod
     def from_pretrained(cls, path: str) -> "LlamaConfig":
@@ -374,7 +408,7 @@ class LlamaModel(nn.Module):
         need = max_pos or self.cfg.max_position_embeddings
         if self._rope is None or self._rope[0].device != torch.device(device) or self._rope[0].shape[0] < need:
             n = max(need, min(self.cfg.max_position_embeddings, 8192))
-            self._rope = basic.rope_tables(n, self.cfg.head_dim, self.cfg.rope_theta, device)
+            self._rope = basic.rope_tables(n, self.cfg.head_dim, self.cfg.rope_theta, device, self.cfg.rope_scaling)
         return self._rope
 
     # ---- forward
@@ -382,6 +416,9 @@ class LlamaModel(nn.Module):
         """input_ids [B, L] int64 -> final-norm hidden states [B*L, h]."""
         cfg = self.cfg
         B, L = input_ids.shape
+        if cfg.sliding_window and L > cfg.sliding_window:
+            raise ValueError(f"sequence length {L} exceeds the model's attention window ({cfg.sliding_window}); windowed "
+                             "attention is not built - lower context_len")
         dev = self.embed_tokens.device
         ids = input_ids.reshape(-1).to(dev)
         pos = torch.arange(L, dtype=torch.int32, device=dev).repeat(B)
@@ -417,6 +454,13 @@ class LlamaModel(nn.Module):
         for i, l in enumerate(self.layers):
             pre = f"model.layers.{i}."
             yield pre + "input_layernorm.weight", l.input_layernorm, None
+            if cfg.model_type == "phi3":     # the checkpoint stores the fused projections, in this model's own order
+                yield pre + "self_attn.qkv_proj.weight", l.qkv_proj, None
+                yield pre + "self_attn.o_proj.weight", l.o_proj, None
+                yield pre + "post_attention_layernorm.weight", l.post_attention_layernorm, None
+                yield pre + "mlp.gate_up_proj.weight", l.gate_up_proj, None
+                yield pre + "mlp.down_proj.weight", l.down_proj, None
+                continue
             yield pre + "self_attn.q_proj.weight", l.qkv_proj, slice(0, q)
             yield pre + "self_attn.k_proj.weight", l.qkv_proj, slice(q, q + kv)
             yield pre + "self_attn.v_proj.weight", l.qkv_proj, slice(q + kv, q + 2 * kv)

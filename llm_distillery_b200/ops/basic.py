@@ -158,9 +158,30 @@ def rmsnorm_bwd(dy: torch.Tensor, h: torch.Tensor, w: torch.Tensor, rstd: torch.
 
 
 # ------------------------------------------------------------------------------------------------ RoPE
-def rope_tables(max_pos: int, head_dim: int, theta: float, device) -> tuple[torch.Tensor, torch.Tensor]:
-    """fp32 cos/sin tables [max_pos, head_dim/2] (HF Llama convention: pairs (i, i + d/2))."""
+def rope_tables(max_pos: int, head_dim: int, theta: float, device, scaling: dict | None = None
+                ) -> tuple[torch.Tensor, torch.Tensor]:
+    """fp32 cos/sin tables [max_pos, head_dim/2] (HF Llama convention: pairs (i, i + d/2)).
+
+    ``scaling`` is a HuggingFace ``rope_scaling`` dict: ``llama3`` (Llama 3.1 / 3.2: low frequencies divided by
+    ``factor``, a smooth blend between ``original_max_position_embeddings / low_freq_factor`` and ``/ high_freq_factor``
+    wavelengths) and ``linear`` (every frequency divided by ``factor``) are built; other types are refused."""
+    import math
     inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32, device=device) / head_dim))
+    kind = (scaling or {}).get("rope_type", (scaling or {}).get("type")) if scaling else None
+    if kind in (None, "default"):
+        pass
+    elif kind == "linear":
+        inv = inv / float(scaling["factor"])
+    elif kind == "llama3":
+        factor = float(scaling["factor"])
+        lo_f, hi_f = float(scaling.get("low_freq_factor", 1.0)), float(scaling.get("high_freq_factor", 4.0))
+        old = float(scaling.get("original_max_position_embeddings", 8192))
+        wavelen = 2.0 * math.pi / inv
+        smooth = ((old / wavelen - lo_f) / (hi_f - lo_f)).clamp(0.0, 1.0)
+        blended = (1.0 - smooth) * inv / factor + smooth * inv
+        inv = torch.where(wavelen > old / lo_f, inv / factor, torch.where(wavelen < old / hi_f, inv, blended))
+    else:
+        raise NotImplementedError(f"rope_scaling type {kind!r} is not built (default, linear and llama3 are)")
     ang = torch.arange(max_pos, dtype=torch.float32, device=device)[:, None] * inv[None, :]
     return ang.cos().contiguous(), ang.sin().contiguous()
 

@@ -1,0 +1,102 @@
+"""Checkpoint-level compatibility beyond plain Llama: Llama 3.1 / 3.2 rope scaling, the Phi-3 family (fused projections
+in the checkpoint), Mistral's attention window, and config keys that must survive a load / save round trip."""
+import json
+
+import pytest
+import torch
+
+from llm_distillery_b200.ckpt.hf import load_hf_model, load_tp_weights, save_hf_model
+from llm_distillery_b200.models.llama import LlamaConfig, build_model
+from llm_distillery_b200.ops import basic
+
+tr = pytest.importorskip("transformers")
+
+ROPE3 = {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+         "original_max_position_embeddings": 64}
+
+
+def _base(**kw):
+    d = dict(vocab_size=320, hidden_size=64, intermediate_size=136, num_hidden_layers=2, num_attention_heads=4,
+             num_key_value_heads=2, max_position_embeddings=256, rope_theta=10000.0, rms_norm_eps=1e-6)
+    d.update(kw)
+    return d
+
+
+def test_llama3_rope_scaling_matches_huggingface():
+    cfg = LlamaConfig(**_base(rope_scaling=ROPE3))
+    model = build_model(cfg, dtype=torch.float32, device="cpu", seed=1)
+    hf_cfg = tr.LlamaConfig(**_base(), rope_scaling=dict(ROPE3), attn_implementation="eager", tie_word_embeddings=False)
+    hf = tr.LlamaForCausalLM(hf_cfg).float()
+    hf.load_state_dict({k: v.clone() for k, v in model.to_hf_state_dict().items()}, strict=False)
+    x = torch.randint(0, 320, (2, 200))          # beyond original_max_position_embeddings: the scaled band matters
+    ours, ref = model(x), hf(x).logits
+    assert torch.allclose(ours, ref, atol=3e-4, rtol=1e-3), (ours - ref).abs().max()
+    plain = build_model(LlamaConfig(**_base()), dtype=torch.float32, device="cpu", seed=1)
+    assert (plain(x) - ref).abs().max() > 2e-3    # and it is not a no-op (ten times the tolerance above)
+    # linear scaling: every frequency divided by the factor
+    c1, s1 = basic.rope_tables(32, 16, 10000.0, "cpu", {"type": "linear", "factor": 4.0})
+    c0, s0 = basic.rope_tables(128, 16, 10000.0, "cpu")
+    assert torch.allclose(c1[4::4], c0[1:8], atol=1e-6) and torch.allclose(s1[4::4], s0[1:8], atol=1e-6)
+    with pytest.raises(NotImplementedError):
+        basic.rope_tables(8, 16, 10000.0, "cpu", {"rope_type": "yarn", "factor": 2.0})
+
+
+def test_phi3_checkpoint_layout_matches_huggingface(tmp_path):
+    cfg = LlamaConfig(**_base(model_type="phi3", pad_token_id=0, bos_token_id=1, eos_token_id=2))
+    model = build_model(cfg, dtype=torch.float32, device="cpu", seed=2)
+    sd = model.to_hf_state_dict()
+    assert "model.layers.0.self_attn.qkv_proj.weight" in sd and "model.layers.1.mlp.gate_up_proj.weight" in sd
+    assert not any("q_proj" in k or "gate_proj" in k for k in sd)
+    hf_cfg = tr.Phi3Config(**_base(), pad_token_id=0, bos_token_id=1, eos_token_id=2, attn_implementation="eager",
+                           tie_word_embeddings=False, sliding_window=None)
+    hf = tr.Phi3ForCausalLM(hf_cfg).float()
+    missing = hf.load_state_dict({k: v.clone() for k, v in sd.items()}, strict=False)
+    assert not [k for k in missing.missing_keys if "rotary" not in k] and not missing.unexpected_keys, missing
+    x = torch.randint(0, 320, (2, 40))
+    ours, ref = model(x), hf(x).logits
+    assert torch.allclose(ours, ref, atol=3e-4, rtol=1e-3), (ours - ref).abs().max()
+    # save -> HuggingFace reads it; HuggingFace saves -> this loader reads it
+    save_hf_model(model, str(tmp_path / "ours"))
+    c = json.load(open(tmp_path / "ours" / "config.json"))
+    assert c["model_type"] == "phi3" and c["architectures"] == ["Phi3ForCausalLM"] and c["pad_token_id"] == 0
+    hf2 = tr.AutoModelForCausalLM.from_pretrained(str(tmp_path / "ours"), torch_dtype=torch.float32,
+                                                  attn_implementation="eager")
+    assert torch.allclose(hf2(x).logits, ref, atol=3e-4, rtol=1e-3)
+    hf.save_pretrained(str(tmp_path / "theirs"), safe_serialization=True)
+    back = load_hf_model(str(tmp_path / "theirs"), dtype=torch.float32)
+    assert back.cfg.model_type == "phi3"
+    assert torch.allclose(back(x), ref, atol=3e-4, rtol=1e-3)
+    # tensor-parallel slices come out of the fused tensors
+    _, w0 = load_tp_weights(str(tmp_path / "theirs"), 0, 2, dtype=torch.float32)
+    _, w1 = load_tp_weights(str(tmp_path / "theirs"), 1, 2, dtype=torch.float32)
+    q, kv, f = cfg.q_size, cfg.kv_size, cfg.intermediate_size
+    full = back.layers[0].qkv_proj.data
+    want0 = torch.cat([full[: q // 2], full[q: q + kv // 2], full[q + kv: q + kv + kv // 2]])
+    want1 = torch.cat([full[q // 2: q], full[q + kv // 2: q + kv], full[q + kv + kv // 2:]])
+    assert torch.equal(w0["layers.0.qkv_proj"], want0) and torch.equal(w1["layers.0.qkv_proj"], want1)
+    gu = back.layers[1].gate_up_proj.data
+    assert torch.equal(w1["layers.1.gate_up_proj"], torch.cat([gu[f // 2: f], gu[f + f // 2:]]))
+
+
+def test_config_keys_survive_a_round_trip_and_unbuilt_variants_are_refused(tmp_path):
+    src = dict(_base(), model_type="mistral", architectures=["MistralForCausalLM"], sliding_window=128, bos_token_id=5,
+               eos_token_id=[6, 7], pad_token_id=9, rope_scaling=None, attention_dropout=0.0, initializer_range=0.02,
+               transformers_version="4.40.0", hidden_act="silu", tie_word_embeddings=False, some_future_key={"a": 1})
+    cfg = LlamaConfig.from_hf_dict(src)
+    assert cfg.sliding_window == 128 and cfg.extra["some_future_key"] == {"a": 1} and cfg.eos_token_id == [6, 7]
+    out = cfg.to_hf_dict()
+    for k in ("sliding_window", "bos_token_id", "eos_token_id", "pad_token_id", "attention_dropout", "initializer_range",
+              "some_future_key", "model_type"):
+        assert out[k] == src[k], k
+    assert out["architectures"] == ["MistralForCausalLM"]
+    model = build_model(cfg, dtype=torch.float32, device="cpu", seed=0)
+    model(torch.randint(0, 320, (1, 128)))                       # up to the window: full causal attention is exact
+    with pytest.raises(ValueError, match="attention window"):
+        model(torch.randint(0, 320, (1, 129)))
+    for bad in (dict(model_type="gemma2"), dict(hidden_act="gelu_pytorch_tanh"), dict(head_dim=32),
+                dict(partial_rotary_factor=0.5), dict(rope_scaling={"rope_type": "yarn", "factor": 4.0}), dict(mlp_bias=True)):
+        with pytest.raises(NotImplementedError):
+            LlamaConfig.from_hf_dict(dict(_base(), **bad))
+    # Qwen2 carries a window that is switched off
+    q = LlamaConfig.from_hf_dict(dict(_base(), model_type="qwen2", sliding_window=64, use_sliding_window=False))
+    assert q.sliding_window is None and q.attention_bias
