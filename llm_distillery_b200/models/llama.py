@@ -155,6 +155,9 @@ def preset(name: str, **over) -> LlamaConfig:
                       tie_word_embeddings=tied)
     if name.startswith("qwen2"):
         cfg.attention_bias, cfg.model_type = True, "qwen2"
+    if name.startswith("llama-3.2"):      # the published Llama 3.2 configs scale the low rope frequencies
+        cfg.rope_scaling = {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                            "original_max_position_embeddings": 8192}
     for k, v in over.items():
         setattr(cfg, k, v)
     return cfg
