@@ -453,6 +453,8 @@ class P2PFullShardComm(FullShardComm):
         _lib.register("b200_p2p_rs_adamw_piece", [_VP, _LL, _VP, _VP, _VP, _VP, _VP, _LL, _I, _I, _F, _F, _F, _F, _F, _I,
                                                   _F, _I, _VP])
         self._fused = None            # {"lr", "gs"} during the last micro-batch of a step and the step that follows
+        self._met = False             # an NCCL rendezvous has preceded the flag barriers since the last forward began
+        self._rdv = torch.zeros(1, dtype=torch.float32, device=self.device)
         self._lib = _lib
         self._SymmetricBuffer = SymmetricBuffer
         self.sig = SymmetricBuffer(64, torch.int32, self.device)
@@ -475,7 +477,17 @@ class P2PFullShardComm(FullShardComm):
         super().close()
         self._sym.clear()
 
+    def _pre(self, param, backward: bool = False) -> None:
+        if not backward:
+            self._met = False         # a new forward: this rank may have waited for its batch for any length of time
+        super()._pre(param, backward)
+
     def _barrier(self) -> None:
+        if not self._met:
+            # ranks can be seconds apart here (a checkpoint being written, a batch late from disk) while the flag
+            # barrier gives up after two: let NCCL, whose wait has no such bound, bring the streams together first
+            dist.all_reduce(self._rdv, group=self.group)
+            self._met = True
         self.epoch += 1
         self._lib.check(self._lib.kernels().b200_p2p_barrier(self.sig.c_ptrs, self.rank, self.world, self.epoch,
                                                              self._lib.stream()), "b200_p2p_barrier")

@@ -75,6 +75,7 @@ class P2PComm:
         self._buckets = max(1, int(os.environ.get("B200_OVERLAP_BUCKETS", "4")))   # ranges per step handed over early
         self.grad_buf = None
         self.model_buf = None
+        self._rdv = torch.zeros(1, dtype=torch.float32, device=self.device)
         torch.cuda.synchronize(self.device)
         dist.barrier()
 
@@ -99,6 +100,14 @@ class P2PComm:
         self.barrier()
 
     # ---- primitives
+    def rendezvous(self) -> None:
+        """A tiny NCCL all-reduce on the current stream: what is enqueued after it starts only once every rank's
+        stream has got here. The flag barriers of this module wait for at most two seconds and then report a lost peer;
+        ranks can be further apart than that for harmless reasons (rank 0 writing a checkpoint, one rank's batch coming
+        late from disk), so the first flag barrier of a step is preceded by this - NCCL's own wait has no such bound -
+        and the bounded waits only ever see the skew of a few kernels."""
+        dist.all_reduce(self._rdv)
+
     def barrier(self) -> None:
         self.epoch += 1
         _lib.check(_lib.kernels().b200_p2p_barrier(self.sig.c_ptrs, self.rank, self.world, self.epoch, _lib.stream()),
@@ -147,7 +156,7 @@ class P2PComm:
     def begin_overlap(self, lr: float, grad_scale: float) -> None:
         """Before the last backward of a step: from now on ``range_ready(lo)`` may hand over finished gradients."""
         self.opt.step_count += 1
-        self._ov = {"lr": lr, "gs": grad_scale / self.world, "hi": self.flat.total}
+        self._ov = {"lr": lr, "gs": grad_scale / self.world, "hi": self.flat.total, "met": False}
 
     def range_ready(self, lo: int) -> None:
         """Flat offsets >= lo hold final gradients on THIS rank. Every rank calls this with the same offsets in the
@@ -168,6 +177,9 @@ class P2PComm:
         ev.record()                                   # this rank's gradients of the range are complete here
         with torch.cuda.stream(self.side):
             self.side.wait_event(ev)
+            if not ov["met"]:
+                self.rendezvous()
+                ov["met"] = True
             self.side_epoch += 1                      # every rank takes part, also with an empty intersection
             _lib.check(_lib.kernels().b200_p2p_barrier(self.sig_side.c_ptrs, self.rank, self.world, self.side_epoch,
                                                        _lib.stream()), "b200_p2p_barrier")
@@ -195,6 +207,7 @@ class P2PComm:
             torch.cuda.current_stream().wait_event(done)
             self.barrier()
             return
+        self.rendezvous()
         self.barrier()
         fused = self._fused()
         if fused:

@@ -101,6 +101,16 @@ class TPGroup:
         if err:
             raise RuntimeError(f"tensor-parallel wait timed out on rank {self.rank} (device error code {err})")
 
+    def rendezvous(self) -> None:
+        """A tiny NCCL all-reduce on the current stream, once per forward: the fused kernels' waits on peers give up
+        after two seconds, and ranks can be further apart than that when a forward begins (the group's first rank also
+        hands rows to the HDF5 writer, batches come from the host at different times). NCCL's wait has no such bound;
+        after it the bounded waits only see the skew of a few kernels."""
+        if self.native and self.world > 1:
+            if getattr(self, "_rdv", None) is None:
+                self._rdv = torch.zeros(1, dtype=torch.float32, device=self.device)
+            dist.all_reduce(self._rdv, group=self.group)
+
     def barrier(self) -> None:
         if not self.native:
             dist.barrier(self.group)
@@ -316,6 +326,7 @@ class TPLlama:
         ids = input_ids.reshape(-1).to(self.device)
         pos = torch.arange(L, dtype=torch.int32, device=self.device).repeat(B)
         cos, sin = self.rope(L)
+        g.rendezvous()
         x = basic.embed_fwd(ids[r * Ts:(r + 1) * Ts].contiguous(), w["embed_tokens"])
         for i in range(cfg.num_hidden_layers):
             p = f"layers.{i}."

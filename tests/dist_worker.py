@@ -168,6 +168,25 @@ def cpu_zero3():
     dist.destroy_process_group()
 
 
+def _late_rank_step(dev, rank, world, comm_factory):
+    """One rank arrives three seconds late at a step - longer than the two seconds a device-side wait lasts. The
+    communicators bring the streams together through NCCL first, so no wait runs out."""
+    import time
+    from llm_distillery_b200.ops import _lib
+    model, cfg = _tiny3(torch.bfloat16, dev, False)
+    comm = comm_factory()
+    eng = DistillEngine(model, loss="kl", temperature=2.0, optimizer="adamw", lr=1e-3, comm=comm)
+    for s in range(3):
+        if s == 1 and rank == world - 1:
+            time.sleep(3.0)
+        loss = eng.train_step([synthetic_batch(cfg.vocab_size, 2, 128, 16, seed=50 + s + rank)])
+    torch.cuda.synchronize()
+    assert _lib.take_device_error() == 0, "a bounded wait ran out although every rank was alive"
+    assert torch.isfinite(loss).all()
+    if hasattr(comm, "close"):
+        comm.close()
+
+
 def gpu_zero3():
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -192,6 +211,7 @@ def gpu_zero3():
             parts = [torch.empty_like(flat) for _ in range(world)]
             dist.all_gather(parts, flat)
             assert all(torch.equal(p, parts[0]) for p in parts), "ranks hold different weights"
+    _late_rank_step(dev, rank, world, lambda: make_comm("p2p", dev, shard_strategy="zero3"))
     if rank == 0:
         print("WORKER_OK")
     dist.destroy_process_group()
@@ -228,6 +248,7 @@ def gpu_p2p():
         parts = [torch.empty_like(flat) for _ in range(world)]
         dist.all_gather(parts, flat)
         assert all(torch.equal(p, parts[0]) for p in parts), "ranks hold different weights"
+    _late_rank_step(dev, rank, world, lambda: P2PComm(dev))
     if rank == 0:
         print("WORKER_OK")
     dist.destroy_process_group()
