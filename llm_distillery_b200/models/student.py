@@ -229,6 +229,8 @@ class StudentModel(BaseModel):
         with self.engine.full_parameters(writeback=True):
             ckpt.load_model_state(self.paths.student_states, self.model)
         c = ckpt.load_trainer_state(self.paths.student_states, None, self.engine.opt, self.engine.schedule)
+        if self.comm is not None and hasattr(self.comm, "shards_written"):
+            self.comm.shards_written()      # the optimizer load rewrote this rank's weight pieces from its master copy
         for k in ("num_trained_steps", "next_save_step", "next_val_step", "next_accum_step", "tokens_trained"):
             if k in c:
                 setattr(self, k, c[k])

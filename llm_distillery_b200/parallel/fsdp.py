@@ -241,6 +241,10 @@ class FullShardComm:
     def barrier(self) -> None:
         dist.barrier(self.group)
 
+    def shards_written(self) -> None:
+        """This rank's weight pieces were written outside the step protocol (construction, a checkpoint load). Nothing
+        to do here: an all-gather reads the local piece in stream order and waits for the peers by itself."""
+
     # ---- collectives (every rank issues them in the same host order; on GPUs all of them on the side stream)
     def _all_gather(self, out: torch.Tensor, piece: torch.Tensor) -> None:
         if self.gloo:
@@ -423,6 +427,8 @@ class FullShardComm:
                 if writeback:
                     f.master.copy_(f.model_shard().float())
             f.rot_owner = [None, None]
+            if writeback:
+                self.shards_written()
 
 
 class P2PFullShardComm(FullShardComm):
@@ -476,6 +482,18 @@ class P2PFullShardComm(FullShardComm):
     def close(self) -> None:
         super().close()
         self._sym.clear()
+
+    def build_flat(self, model) -> ShardedFlat:
+        flat = super().build_flat(model)
+        self.shards_written()
+        return flat
+
+    def shards_written(self) -> None:
+        """Peers read this rank's pieces straight out of its memory, and a pull gather involves no handshake: after
+        writes outside the step protocol every rank waits until all of them have finished theirs (host barrier; these
+        are start-up and checkpoint-load moments, not the training loop)."""
+        torch.cuda.current_stream().synchronize()
+        dist.barrier(self.group)
 
     def _pre(self, param, backward: bool = False) -> None:
         if not backward:
