@@ -228,6 +228,11 @@ class FullShardComm:
         if flat is not self.flat:
             raise RuntimeError("the engine must use the flat space built by build_flat")
         self.opt = opt
+        # the model calls ONE pair of module-level hooks: a second fully sharded engine in the same process would
+        # silently take them away from the first
+        other = getattr(_llama.UNIT_PRE[0], "__self__", None)
+        if other is not None and other is not self and getattr(other, "flat", None) is not None:
+            raise RuntimeError("another fully sharded engine is active in this process: close() its communicator first")
         _llama.UNIT_PRE[0] = self._pre
         _llama.LAYER_BACKWARD_DONE[0] = self._layer_done
 

@@ -125,7 +125,10 @@ def cpu_zero3():
     dist.init_process_group("gloo")
     rank, world = dist.get_rank(), dist.get_world_size()
     from llm_distillery_b200.parallel.fsdp import FullShardComm
+    eng = None
     for tied, freeze in ((False, False), (True, False), (False, True)):
+        if eng is not None:
+            eng.comm.close()        # one fully sharded engine per process at a time
         got, ev, eng = _zero3_case("cpu", torch.float32, rank, world, tied, freeze,
                                    lambda: make_comm("gloo", "cpu", shard_strategy="zero3"))
         assert isinstance(eng.comm, FullShardComm)
@@ -153,13 +156,21 @@ def cpu_zero3():
     with torch.no_grad():
         for p in model2.parameters():
             p.add_(0.5)
+    try:        # a second fully sharded engine while the first is still active is refused
+        DistillEngine(_tiny3(torch.float32, "cpu", False)[0], loss="kl", optimizer="adamw",
+                      comm=make_comm("gloo", "cpu", shard_strategy="zero3"))
+        raise AssertionError("two active fully sharded engines were accepted")
+    except RuntimeError as e:
+        assert "close()" in str(e)
+    master1, v1, steps1 = eng.flat.master.clone(), eng.opt.state["v"].clone(), eng.opt.step_count
+    eng.comm.close()
     eng2 = DistillEngine(model2, loss="kl", temperature=2.0, optimizer="adamw", lr=1e-3, grad_accum=2,
                          comm=make_comm("gloo", "cpu", shard_strategy="zero3"))
     with eng2.full_parameters(writeback=True):
         ckpt.load_model_state(d[0], model2)
     ckpt.load_trainer_state(d[0], None, eng2.opt, eng2.schedule)
-    assert torch.equal(eng2.flat.master, eng.flat.master) and eng2.opt.step_count == eng.opt.step_count
-    assert torch.equal(eng2.opt.state["v"], eng.opt.state["v"])
+    assert torch.equal(eng2.flat.master, master1) and eng2.opt.step_count == steps1
+    assert torch.equal(eng2.opt.state["v"], v1)
     with eng2.full_parameters():
         w2 = torch.cat([p.detach().float().reshape(-1) for p in model2.parameters()])
     assert torch.equal(w2, got), (w2 - got).abs().max()
