@@ -110,17 +110,63 @@ class ByteTrie:
         return best
 
 
+def flat_trie(student_bytes: list[bytes], student_vocab_limit: int | None = None) -> dict[str, np.ndarray]:
+    """Flattened byte trie of a vocabulary (``ByteTrie.flatten`` layout), built by the native host library when it is
+    there (csrc/align/trie_build.cc: same node numbering, tens of milliseconds for 128k tokens) and by the dictionary
+    trie otherwise."""
+    import ctypes
+    from ..ops import _lib
+    n = len(student_bytes) if student_vocab_limit is None else min(len(student_bytes), student_vocab_limit)
+    toks = student_bytes[:n]
+    try:
+        lib = _lib.host()
+        build = lib.b200_trie_build
+    except (OSError, AttributeError):
+        lib = None
+    if lib is None:
+        trie = ByteTrie()
+        for i, b in enumerate(toks):
+            if b:
+                trie.insert(b, i)
+        return trie.flatten()
+    lens = np.fromiter((len(b) for b in toks), dtype=np.int64, count=n)
+    off = np.zeros(n + 1, dtype=np.int64)
+    np.cumsum(lens, out=off[1:])
+    blob = np.frombuffer(b"".join(toks) or b"\0", dtype=np.uint8)
+    ids = np.arange(n, dtype=np.int32)
+    vp = ctypes.c_void_p
+    build.restype = vp
+    build.argtypes = [vp, vp, vp, ctypes.c_int, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_longlong)]
+    lib.b200_trie_export.argtypes = [vp, vp, vp, vp, vp]
+    lib.b200_trie_free.argtypes = [vp]
+    n_nodes, n_edges = ctypes.c_int(0), ctypes.c_longlong(0)
+    h = build(blob.ctypes.data, off.ctypes.data, ids.ctypes.data, n, ctypes.byref(n_nodes), ctypes.byref(n_edges))
+    if not h:
+        raise RuntimeError("b200_trie_build refused its arguments")
+    try:
+        out = {"edge_start": np.zeros(n_nodes.value + 1, dtype=np.int32),
+               "edge_byte": np.zeros(max(1, n_edges.value), dtype=np.uint8),
+               "edge_child": np.zeros(max(1, n_edges.value), dtype=np.int32),
+               "node_value": np.zeros(n_nodes.value, dtype=np.int32)}
+        if lib.b200_trie_export(h, out["edge_start"].ctypes.data, out["edge_byte"].ctypes.data,
+                                out["edge_child"].ctypes.data, out["node_value"].ctypes.data) != 0:
+            raise RuntimeError("b200_trie_export failed")
+    finally:
+        lib.b200_trie_free(h)
+    return out
+
+
 def vocab_map_from_bytes(teacher_bytes: list[bytes], student_bytes: list[bytes], student_vocab_limit: int | None = None,
                          device=None) -> np.ndarray:
     """int32 [teacher vocab]: the student token that is the longest byte-prefix of each teacher token (-1: none).
     On a CUDA ``device`` the whole teacher vocabulary is walked through the flattened trie by one kernel launch
     (``ops.topk.trie_walk``); otherwise token by token in Python."""
+    if device is not None and torch.device(device).type == "cuda" and teacher_bytes:
+        return topk_ops.trie_walk(flat_trie(student_bytes, student_vocab_limit), teacher_bytes, device)[0].cpu().numpy()
     trie = ByteTrie()
     for i, b in enumerate(student_bytes):
         if b and (student_vocab_limit is None or i < student_vocab_limit):
             trie.insert(b, i)
-    if device is not None and torch.device(device).type == "cuda" and teacher_bytes:
-        return topk_ops.trie_walk(trie.flatten(), teacher_bytes, device)[0].cpu().numpy()
     return np.asarray([trie.longest_prefix(b) if b else -1 for b in teacher_bytes], dtype=np.int32)
 
 

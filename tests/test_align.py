@@ -199,3 +199,36 @@ def test_trie_walk_kernel_equals_the_dictionary_trie():
     empty = ByteTrie().flatten()
     got, _ = trie_walk(empty, [b"abc", b""], "cuda")
     assert got.cpu().tolist() == [-1, -1]
+
+
+def test_native_trie_builder_equals_the_dictionary_trie():
+    import time
+    from llm_distillery_b200.align.aligner import ByteTrie, flat_trie
+    from llm_distillery_b200.ops import _lib
+    try:
+        _lib.host().b200_trie_build
+    except (OSError, AttributeError):
+        pytest.skip("host library not built")
+    for seed, (ns, nt) in enumerate([(400, 10), (20000, 10), (0, 1)]):
+        _, student = _random_vocabularies(seed, ns, nt)
+        student = student + student[300:320]              # duplicates: the lowest id stays
+        for limit in (None, 256, 1000):
+            trie = ByteTrie()
+            for i, b in enumerate(student):
+                if b and (limit is None or i < limit):
+                    trie.insert(b, i)
+            want, got = trie.flatten(), flat_trie(student, limit)
+            assert sorted(want) == sorted(got)
+            for k in want:
+                assert got[k].dtype == want[k].dtype and np.array_equal(got[k], want[k]), (seed, limit, k)
+    empty = flat_trie([], None)
+    assert empty["node_value"].tolist() == [-1] and empty["edge_start"].tolist() == [0, 0]
+    # and it is the fast way: a 100k-token vocabulary
+    import random
+    rng = random.Random(1)
+    big = [bytes(rng.randrange(97, 123) for _ in range(rng.randint(2, 12))) for _ in range(100000)]
+    t0 = time.perf_counter()
+    ft = flat_trie(big)
+    native_s = time.perf_counter() - t0
+    assert ft["node_value"].max() == 99999 or len(set(big)) < len(big)
+    assert native_s < 1.5, native_s
