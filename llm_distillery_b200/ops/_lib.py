@@ -120,7 +120,9 @@ def register(name: str, argtypes: list) -> None:
 def host() -> ctypes.CDLL:
     global _HOST
     if _HOST is None:
-        _HOST = _load("libb200_host.so")
+        # B200_HOST_LIB: another build of the same library, e.g. the AddressSanitizer one of `build --sanitize`
+        override = os.environ.get("B200_HOST_LIB")
+        _HOST = ctypes.CDLL(override, mode=ctypes.RTLD_GLOBAL) if override else _load("libb200_host.so")
     return _HOST
 
 
