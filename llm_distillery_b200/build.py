@@ -6,7 +6,8 @@ the source, its local includes and the flags, so rebuilding after a one-file edi
 
     python -m llm_distillery_b200.build [--force] [--verbose] [--jobs N] [--sanitize]
 
-``--sanitize`` additionally builds ``_C/libb200_host_asan.so`` (the HDF5 store with AddressSanitizer and UBSan) for
+``--sanitize`` additionally builds ``_C/libb200_host_asan.so`` (the host library with AddressSanitizer and UBSan) and
+``_C/libb200_host_tsan.so`` (ThreadSanitizer) for
 use from an instrumented host program or with ``LD_PRELOAD`` of the sanitizer runtime.
 """
 from __future__ import annotations
@@ -125,6 +126,11 @@ def build(force: bool = False, verbose: bool = False, jobs: int | None = None, s
         _build_lib(ccs, CXX_FLAGS + san, ["g++"], ["g++", "-shared", "-pthread"] + san, asan_lib, force, verbose, jobs,
                    link_tail=["-lz"])
         out["host_asan"] = str(asan_lib)
+        tsan = ["-fsanitize=thread", "-fno-omit-frame-pointer", "-g"]
+        tsan_lib = OUT / "libb200_host_tsan.so"
+        _build_lib(ccs, CXX_FLAGS + tsan, ["g++"], ["g++", "-shared", "-pthread"] + tsan, tsan_lib, force, verbose, jobs,
+                   link_tail=["-lz"])
+        out["host_tsan"] = str(tsan_lib)
     return out
 
 

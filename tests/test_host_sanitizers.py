@@ -1,6 +1,7 @@
-"""The native host library (HDF5 store, byte-trie builder) under AddressSanitizer + UBSan.
+"""The native host library (HDF5 store, byte-trie builder) under AddressSanitizer + UBSan and under ThreadSanitizer.
 
-``build --sanitize`` compiles the same C++ sources with ``-fsanitize=address,undefined``; a child interpreter
+``build --sanitize`` compiles the same C++ sources with ``-fsanitize=address,undefined`` and with
+``-fsanitize=thread``; a child interpreter
 preloads the sanitizer runtime, loads that library instead of the regular one (``B200_HOST_LIB``) and drives the store
 through writes from several threads, merges, renames, deletes, a repack, a reopen and a prefetch, and the trie builder
 through a large vocabulary. Any heap overflow, use after free or undefined operation ends the child with the
@@ -22,7 +23,7 @@ from llm_distillery_b200.align.aligner import ByteTrie, flat_trie
 from llm_distillery_b200.data.convo import TeacherRows
 from llm_distillery_b200.data.h5store import H5Store
 from llm_distillery_b200.ops import _lib
-assert "asan" in os.environ["B200_HOST_LIB"] and _lib.host() is not None
+assert "san.so" in os.environ["B200_HOST_LIB"] and _lib.host() is not None
 
 def rows(cid, n, K=16, V=500):
     rng = np.random.default_rng(cid)
@@ -73,21 +74,25 @@ def _runtime(name: str) -> str | None:
     return p if os.path.isabs(p) and os.path.exists(p) else None
 
 
-def test_store_and_trie_builder_are_clean_under_address_and_ub_sanitizers(tmp_path):
-    asan = _runtime("libasan.so")
-    if asan is None:
-        pytest.skip("no AddressSanitizer runtime on this machine")
+@pytest.mark.parametrize("kind", ["asan", "tsan"])
+def test_store_and_trie_builder_are_clean_under_sanitizers(tmp_path, kind):
+    """asan: AddressSanitizer + UBSan; tsan: ThreadSanitizer (the store's writer pool and prefetch thread)."""
+    runtime = _runtime("libasan.so" if kind == "asan" else "libtsan.so")
+    if runtime is None:
+        pytest.skip(f"no {kind} runtime on this machine")
     from llm_distillery_b200 import build as native_build
     out = native_build.build(sanitize=True)
-    lib = out.get("host_asan")
+    lib = out.get(f"host_{kind}")
     assert lib and os.path.exists(lib)
     script = tmp_path / "child.py"
     script.write_text(CHILD)
-    env = dict(os.environ, LD_PRELOAD=asan, B200_HOST_LIB=lib, B200_NO_PROGRESS="1",
+    env = dict(os.environ, LD_PRELOAD=runtime, B200_HOST_LIB=lib, B200_NO_PROGRESS="1",
                ASAN_OPTIONS="detect_leaks=0:alloc_dealloc_mismatch=0:detect_odr_violation=0:halt_on_error=1:abort_on_error=0",
-               UBSAN_OPTIONS="halt_on_error=1:print_stacktrace=1")
+               UBSAN_OPTIONS="halt_on_error=1:print_stacktrace=1",
+               TSAN_OPTIONS="halt_on_error=0:report_signal_unsafe=0:exitcode=66")
     r = subprocess.run([sys.executable, str(script), ROOT, str(tmp_path)], capture_output=True, text=True, timeout=900,
                        env=env)
     report = r.stderr[-4000:]
-    assert "AddressSanitizer" not in r.stderr and "runtime error:" not in r.stderr, report
+    for marker in ("AddressSanitizer", "runtime error:", "ThreadSanitizer"):
+        assert marker not in r.stderr, report
     assert r.returncode == 0 and "CHILD_OK" in r.stdout, (r.stdout[-1000:], report)
