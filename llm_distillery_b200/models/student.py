@@ -100,10 +100,38 @@ class StudentModel(BaseModel):
             self.model.apply_freeze(self.freeze_layers)
         schedule = set_lr_scheduler(self.lr_scheduler_name, self.lr, self.num_warmup_steps, self.num_grad_accum_batches,
                                     self.decay_start, self.final_lr)
+        if self.rank == 0 and dev.type == "cuda" and not getattr(self, "_memory_note_done", False):
+            try:
+                print(self.memory_note())
+            except Exception as e:  # noqa: BLE001 - an estimate must never stop a run
+                print(f"(memory estimate unavailable: {e})")
+            self._memory_note_done = True
         self.engine = DistillEngine(self.model, loss=self.loss_kind, temperature=self.temperature, alpha=self.alpha,
                                     crop_to_size=self.crop_to_size, optimizer=self.optimizer_name, lr=self.lr,
                                     betas=(0.9, 0.99), weight_decay=2e-8, grad_accum=self.grad_accum, schedule=schedule,
                                     comm=self.comm)
+
+    def memory_note(self) -> str:
+        """One line on how the run sits in 180 GB of HBM per GPU under the configured sharding, and what would fit if
+        it does not (``parallel.memory``)."""
+        from ..parallel import memory
+        strategy = getattr(self.comm, "full_shard", False) and "zero3" or \
+            ("fsdp" if getattr(self.comm, "shards_optimizer", False) else "ddp")
+        tokens = int(self.batch_size) * int(self.context_len)
+        kw = dict(topk=200, optimizer=self.optimizer_name)
+        fp = memory.estimate(self.model.cfg, self.world, strategy, tokens, grad_checkpointing=bool(self.grad_checkpointing),
+                             comm="p2p" if type(self.comm).__name__.startswith("P2P") else "nccl", **kw)
+        note = (f"Estimated memory per GPU ({strategy}, {self.world} rank(s), up to {tokens} tokens per micro-batch): "
+                f"{fp.total_gb:.0f} GB of {memory.HBM_GB:.0f} GB (weights {fp.weights_gb:.1f}, gradients "
+                f"{fp.gradients_gb:.1f}, optimizer {fp.optimizer_gb:.1f}, activations {fp.activations_gb:.1f}).")
+        if not fp.fits():
+            pick, _ = memory.recommend(self.model.cfg, self.world, tokens, **kw)
+            hint = {"none": "no built-in plan fits: use more GPUs, an 8-bit optimizer, a smaller batch_size or context_len",
+                    "ddp": "it fits with replicated weights (shard_strategy ddp)"}.get(
+                        pick, f"it fits with shard_strategy {pick.split('+')[0]}" +
+                        (" and grad_checkpointing" if "checkpointing" in pick else ""))
+            note += f" This does NOT fit; {hint}."
+        return note
 
     def _unload_model(self) -> None:
         if self.comm is not None and hasattr(self.comm, "close"):
