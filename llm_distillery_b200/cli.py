@@ -179,9 +179,38 @@ def handle_termination(signum, frame) -> None:
         os._exit(0)
 
 
+def resolve_shard_strategy(cfg: DistillConfig, world: int) -> str:
+    """``shard_strategy = auto``: the first of replicated weights, full sharding, full sharding + gradient checkpointing
+    whose estimated footprint fits one GPU (``parallel.memory``); the config is updated in place (also
+    ``grad_checkpointing`` when the plan needs it). Other values pass through."""
+    if cfg.shard_strategy != "auto":
+        return cfg.shard_strategy
+    from .models.llama import LlamaConfig
+    from .parallel import memory
+    try:
+        mcfg = LlamaConfig.from_pretrained(cfg.student_path)
+    except (OSError, ValueError, NotImplementedError, KeyError):
+        cfg.shard_strategy = "ddp"
+        return cfg.shard_strategy
+    tokens = int(cfg.batch_size) * int(cfg.context_len)
+    pick, table = memory.recommend(mcfg, world, tokens, topk=int(cfg.save_topK) if cfg.enable_topK else 200,
+                                   optimizer=cfg.optimizer, grad_checkpointing=bool(cfg.grad_checkpointing))
+    if pick == "none":
+        pick = "zero3+checkpointing" if world > 1 else "ddp+checkpointing"
+        print("shard_strategy auto: no plan is estimated to fit 180 GB per GPU; using the smallest one")
+    cfg.shard_strategy = pick.split("+")[0]
+    if "checkpointing" in pick:
+        cfg.grad_checkpointing = True
+    fp = table.get(pick) or next(iter(table.values()))
+    print(f"shard_strategy auto -> {cfg.shard_strategy}" + (" with grad_checkpointing" if "checkpointing" in pick else "") +
+          f" (estimated {fp.total_gb:.0f} GB per GPU)")
+    return cfg.shard_strategy
+
+
 def _init_distributed(cfg: DistillConfig):
     """(rank, world, communicator) - communicator is None for a single process."""
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    resolve_shard_strategy(cfg, world)
     if world == 1:
         return 0, 1, None
     import torch

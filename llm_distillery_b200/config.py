@@ -104,7 +104,7 @@ class DistillConfig:
     loss: str = "reference"            # reference | kl | rkl | jsd
     tp_size: int = 1                   # tensor-parallel width for teacher collection
     dp_size: int = 0                   # 0 = world_size / tp_size
-    shard_strategy: str = "ddp"        # ddp | fsdp (optimizer state sharded) | zero3 (weights and gradients too)
+    shard_strategy: str = "ddp"        # ddp | fsdp (optimizer state sharded) | zero3 (weights and gradients too) | auto
     comm_backend: str = "p2p"          # p2p (in-kernel NVLink) | nccl
     cross_tokenizer: bool = False      # allow teachers of another vocab family (byte-trie alignment)
     seed: int = 0
@@ -131,8 +131,8 @@ class DistillConfig:
             raise ValueError(f"Invalid training_precision: {self.training_precision}; choose from {PRECISIONS}")
         if self.data_order.lower() not in DATA_ORDERS:
             raise ValueError(f"Invalid data_order: {self.data_order}; choose from {DATA_ORDERS}")
-        if self.shard_strategy not in ("ddp", "fsdp", "zero3"):
-            raise ValueError("shard_strategy must be ddp, fsdp or zero3")
+        if self.shard_strategy not in ("ddp", "fsdp", "zero3", "auto"):
+            raise ValueError("shard_strategy must be ddp, fsdp, zero3 or auto")
         if self.comm_backend not in ("p2p", "nccl"):
             raise ValueError("comm_backend must be p2p or nccl")
         if self.context_len <= 0 or self.batch_size <= 0 or self.grad_accum_batches <= 0:
@@ -220,7 +220,7 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--loss", type=str, help="reference | kl | rkl | jsd")
     g.add_argument("--tp_size", type=int)
     g.add_argument("--dp_size", type=int)
-    g.add_argument("--shard_strategy", type=str, help="ddp | fsdp | zero3")
+    g.add_argument("--shard_strategy", type=str, help="ddp | fsdp | zero3 | auto (the first plan that fits 180 GB per GPU)")
     g.add_argument("--comm_backend", type=str, help="p2p | nccl")
     g.add_argument("--cross_tokenizer", type=str2bool)
     g.add_argument("--seed", type=int)

@@ -62,3 +62,28 @@ def test_student_memory_note_names_a_plan_that_fits():
     z3 = SimpleNamespace(full_shard=True, shards_optimizer=True)
     assert "zero3, 8 rank(s)" in note("llama-3-8b", 8, z3, 2, 4096)
     assert "no built-in plan fits" in note("llama-3-70b", 8, z3, 1, 4096)
+
+
+def test_shard_strategy_auto_resolves_from_the_student_config(tmp_path):
+    import json
+    from types import SimpleNamespace
+    from llm_distillery_b200.cli import resolve_shard_strategy
+
+    def run(model, world, batch, ctx, optimizer="adamw", ck=False, strategy="auto"):
+        d = tmp_path / f"{model}-{world}-{batch}-{ctx}"
+        d.mkdir(exist_ok=True)
+        (d / "config.json").write_text(json.dumps(preset(model).to_hf_dict()))
+        cfg = SimpleNamespace(shard_strategy=strategy, student_path=str(d), batch_size=batch, context_len=ctx,
+                              save_topK=200, enable_topK=True, optimizer=optimizer, grad_checkpointing=ck)
+        return resolve_shard_strategy(cfg, world), cfg
+    assert run("tinyllama-1.1b", 8, 8, 2048)[0] == "ddp"
+    pick, cfg = run("llama-3-8b", 2, 8, 4096)
+    assert pick == "zero3" and cfg.shard_strategy == "zero3" and cfg.grad_checkpointing is True
+    pick, cfg = run("llama-3-70b", 8, 1, 4096)                # nothing fits: the smallest plan, with a notice
+    assert pick == "zero3" and cfg.grad_checkpointing is True
+    pick, cfg = run("llama-3-8b", 1, 8, 4096)                 # one GPU: checkpointing is the only lever
+    assert pick == "ddp" and cfg.grad_checkpointing is True
+    assert run("llama-3-8b", 2, 8, 4096, strategy="fsdp")[0] == "fsdp"        # explicit values pass through
+    cfg = SimpleNamespace(shard_strategy="auto", student_path=str(tmp_path / "missing"), batch_size=1, context_len=8,
+                          save_topK=1, enable_topK=True, optimizer="adamw", grad_checkpointing=False)
+    assert resolve_shard_strategy(cfg, 4) == "ddp"
