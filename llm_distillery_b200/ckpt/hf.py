@@ -27,31 +27,47 @@ def is_model_safetensors(model_path: str) -> bool:
 
 
 def save_hf_model(model: LlamaModel, folder: str, tokenizer_src: str | None = None,
-                  max_shard_bytes: int = 5 * 1024 ** 3, dtype: torch.dtype | None = None) -> None:
+                  max_shard_bytes: int = 5 * 1024 ** 3, dtype: torch.dtype | None = None,
+                  writer: tuple[int, int] = (0, 1)) -> None:
+    """HuggingFace folder layout: ``config.json``, ``model.safetensors`` or numbered shards + index, tokenizer files.
+
+    ``writer = (rank, world)``: several ranks that all hold the whole weights share the work - every rank cuts the
+    same shard list, rank r writes shards r, r + world, ...; rank 0 also writes the config, the index and the
+    tokenizer files. Only tensors this rank writes are copied to the host."""
     from safetensors.torch import save_file
+    rank, world = writer
     os.makedirs(folder, exist_ok=True)
     cfg = model.cfg.to_hf_dict()
-    sd = {k: v.detach().to("cpu", dtype or v.dtype).contiguous() for k, v in model.to_hf_state_dict().items()}
-    cfg["torch_dtype"] = str(next(iter(sd.values())).dtype).replace("torch.", "")
-    with open(os.path.join(folder, "config.json"), "w", encoding="utf-8") as f:
-        json.dump(cfg, f, indent=2)
-    shards, cur, cur_bytes = [], {}, 0
-    for k, v in sd.items():
-        n = v.numel() * v.element_size()
+    named = list(model.to_hf_state_dict().items())
+    out_dtype = dtype or named[0][1].dtype
+    cfg["torch_dtype"] = str(out_dtype).replace("torch.", "")
+    size = lambda v: v.numel() * torch.empty((), dtype=dtype or v.dtype).element_size()  # noqa: E731
+    shards, cur, cur_bytes = [], [], 0
+    for k, v in named:
+        n = size(v)
         if cur and cur_bytes + n > max_shard_bytes:
             shards.append(cur)
-            cur, cur_bytes = {}, 0
-        cur[k] = v
+            cur, cur_bytes = [], 0
+        cur.append(k)
         cur_bytes += n
     shards.append(cur)
+    by_name = dict(named)
+    to_host = lambda k: by_name[k].detach().to("cpu", dtype or by_name[k].dtype).contiguous()  # noqa: E731
     if len(shards) == 1:
-        save_file(shards[0], os.path.join(folder, "model.safetensors"), metadata={"format": "pt"})
+        names = ["model.safetensors"]
     else:
-        index = {"metadata": {"total_size": sum(v.numel() * v.element_size() for v in sd.values())}, "weight_map": {}}
-        for i, sh in enumerate(shards, 1):
-            name = f"model-{i:05d}-of-{len(shards):05d}.safetensors"
-            save_file(sh, os.path.join(folder, name), metadata={"format": "pt"})
-            for k in sh:
+        names = [f"model-{i:05d}-of-{len(shards):05d}.safetensors" for i in range(1, len(shards) + 1)]
+    for i, (name, keys) in enumerate(zip(names, shards)):
+        if i % world == rank:
+            save_file({k: to_host(k) for k in keys}, os.path.join(folder, name), metadata={"format": "pt"})
+    if rank != 0:
+        return
+    with open(os.path.join(folder, "config.json"), "w", encoding="utf-8") as f:
+        json.dump(cfg, f, indent=2)
+    if len(shards) > 1:
+        index = {"metadata": {"total_size": sum(size(v) for _, v in named)}, "weight_map": {}}
+        for name, keys in zip(names, shards):
+            for k in keys:
                 index["weight_map"][k] = name
         with open(os.path.join(folder, "model.safetensors.index.json"), "w", encoding="utf-8") as f:
             json.dump(index, f, indent=2)

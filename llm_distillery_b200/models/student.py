@@ -213,8 +213,10 @@ class StudentModel(BaseModel):
     def _save_model(self, step) -> None:
         folder = os.path.join(self.paths.student_trained, f"{self.model_name}_step_{step}")
         with self.engine.full_parameters():       # every rank: under full sharding the weights are gathered first
-            if self.rank == 0:
-                ckpt.save_hf_model(self.model, folder, tokenizer_src=self.tokenizer_dir)
+            # every rank holds the whole weights here: the shard files are written side by side, rank r taking shards
+            # r, r + world, ...; rank 0 adds the config, the index and the tokenizer
+            ckpt.save_hf_model(self.model, folder, tokenizer_src=self.tokenizer_dir, writer=(self.rank, self.world),
+                               max_shard_bytes=int(getattr(self, "max_shard_bytes", 5 * 1024 ** 3)))
 
     _HASHED = ("model_name", "lr", "batch_size", "grad_accum", "loss_kind", "temperature", "alpha", "context_len",
                "crop_to_size", "optimizer_name", "lr_scheduler_name", "num_warmup_steps", "decay_start", "final_lr",

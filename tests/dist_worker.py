@@ -174,6 +174,20 @@ def cpu_zero3():
     with eng2.full_parameters():
         w2 = torch.cat([p.detach().float().reshape(-1) for p in model2.parameters()])
     assert torch.equal(w2, got), (w2 - got).abs().max()
+    # HuggingFace-layout checkpoint with the shard files written by the ranks side by side
+    hf_dir = os.path.join(d[0], "hf")
+    with eng2.full_parameters():
+        ckpt.save_hf_model(model2, hf_dir, writer=(rank, world), max_shard_bytes=200_000)
+    dist.barrier()
+    if rank == 0:
+        import json
+        files = sorted(f for f in os.listdir(hf_dir) if f.endswith(".safetensors"))
+        assert len(files) >= world, files
+        index = json.load(open(os.path.join(hf_dir, "model.safetensors.index.json")))
+        assert set(index["weight_map"].values()) == set(files)
+        back = ckpt.load_hf_model(hf_dir, dtype=torch.float32)
+        wb = torch.cat([p.detach().float().reshape(-1) for p in back.parameters()])
+        assert torch.equal(wb, got)
     if rank == 0:
         print("WORKER_OK")
     dist.destroy_process_group()
