@@ -274,6 +274,30 @@ def _tp_group(cfg, teacher, rank: int, world: int, tp: int):
     return _TP_GROUPS[key]
 
 
+def resolve_tp_size(cfg, teachers, world: int) -> int:
+    """``tp_size`` > 0 is taken as given (capped at the number of ranks); 0 = the smallest width at which every teacher
+    fits one GPU (``parallel.memory.recommend_tp``) - the remaining ranks become data-parallel replicas."""
+    if int(cfg.tp_size) > 0 or world <= 1:
+        return max(1, min(int(cfg.tp_size), world))
+    cached = getattr(cfg, "_tp_auto", None)
+    if cached:
+        return cached
+    from .models.llama import LlamaConfig
+    from .parallel import memory
+    cfgs = []
+    for t in teachers:
+        try:
+            cfgs.append(LlamaConfig.from_pretrained(t.model_path))
+        except (OSError, ValueError, NotImplementedError, KeyError):
+            pass
+    tokens = int(cfg.context_len) * max([int(getattr(t, "batch_size", 1) or 1) for t in teachers] or [1])
+    tp = memory.recommend_tp(cfgs, world, tokens, int(cfg.save_topK) if cfg.enable_topK else 200,
+                             int(cfg.crop_distr_to_size) or None) if cfgs else 1
+    print(f"tp_size auto -> {tp} ({world // tp} data-parallel replica(s) of a {tp}-way tensor-parallel teacher)")
+    cfg._tp_auto = tp
+    return tp
+
+
 def collect(teachers, cfg, store, ids, validation, rank, world, student=None) -> None:
     """Every teacher in turn collects ``ids`` into ``store`` (teachers after the first merge into the same
     conversations). With several ranks each rank collects a strided share into its own shard file and rank 0
@@ -284,7 +308,7 @@ def collect(teachers, cfg, store, ids, validation, rank, world, student=None) ->
     shas = None
     if student is not None:
         shas = {c.origin_convo_id: c.content_sha for c in (student.validation_dataset if validation else student.dataset)}
-    tp = max(1, min(int(cfg.tp_size), world))
+    tp = resolve_tp_size(cfg, teachers, world)
     if world % tp:
         raise ValueError(f"tp_size={tp} must divide the number of ranks ({world})")
     dp_rank, dp_world = rank // tp, world // tp

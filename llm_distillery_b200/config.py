@@ -102,7 +102,7 @@ class DistillConfig:
     prompt_format: dict = field(default_factory=lambda: dict(DEFAULT_PROMPT_FORMAT))
     # ---- new in this framework (defaults = reference behaviour)
     loss: str = "reference"            # reference | kl | rkl | jsd
-    tp_size: int = 1                   # tensor-parallel width for teacher collection
+    tp_size: int = 1                   # tensor-parallel width for teacher collection; 0 = the smallest width that fits one GPU
     dp_size: int = 0                   # 0 = world_size / tp_size
     shard_strategy: str = "ddp"        # ddp | fsdp (optimizer state sharded) | zero3 (weights and gradients too) | auto
     comm_backend: str = "p2p"          # p2p (in-kernel NVLink) | nccl
@@ -218,7 +218,7 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--prompt_format", type=json.loads)
     g = p.add_argument_group("Parallelism / loss (new)")
     g.add_argument("--loss", type=str, help="reference | kl | rkl | jsd")
-    g.add_argument("--tp_size", type=int)
+    g.add_argument("--tp_size", type=int, help="tensor-parallel width of the teachers; 0 = smallest width that fits 180 GB per GPU")
     g.add_argument("--dp_size", type=int)
     g.add_argument("--shard_strategy", type=str, help="ddp | fsdp | zero3 | auto (the first plan that fits 180 GB per GPU)")
     g.add_argument("--comm_backend", type=str, help="p2p | nccl")

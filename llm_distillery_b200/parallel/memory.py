@@ -119,6 +119,33 @@ def recommend(cfg, world: int, tokens: int, **kw) -> tuple[str, dict[str, Footpr
     return "none", table
 
 
+def teacher_footprint_gb(cfg, tp: int, tokens: int, topk: int = 200, vocab: int | None = None) -> float:
+    """bf16 teacher collecting ``tokens`` positions per forward at tensor-parallel width ``tp``: the rank's slices of the
+    layers and of the (cropped) LM head, the replicated embedding and norms, the token-major working set of one layer
+    (gathered / staged activations are double-buffered), the fp32 logits of the rank's vocabulary slice and the top-K
+    candidates."""
+    tp = max(1, int(tp))
+    h, f, q, kv = cfg.hidden_size, cfg.intermediate_size, cfg.q_size, cfg.kv_size
+    V = min(vocab or cfg.vocab_size, cfg.vocab_size)
+    layer = _layer_params(cfg) - 2 * h
+    weights = 2 * (cfg.num_hidden_layers * (layer / tp + 2 * h) + cfg.vocab_size * h + V * h / tp + h)
+    work = tokens * ((8 * h + 2 * (q + 2 * kv) / tp + 4 * f / tp) * 2 + (V / tp) * 4 + tp * topk * 12)
+    return (weights + work) / GB
+
+
+def recommend_tp(cfgs, world: int, tokens: int, topk: int = 200, vocab: int | None = None) -> int:
+    """Smallest tensor-parallel width (a divisor of ``world`` that also divides every teacher's heads, KV heads and FFN
+    width) at which every teacher fits 180 GB per GPU. Smaller is better when it fits: the ranks that are not needed
+    for width become data-parallel replicas, which collect without any communication. Returns ``world``'s largest
+    valid width if nothing fits."""
+    valid = [t for t in range(1, max(1, world) + 1) if world % t == 0 and all(
+        c.num_attention_heads % t == 0 and c.num_key_value_heads % t == 0 and c.intermediate_size % t == 0 for c in cfgs)]
+    for t in valid:
+        if all(teacher_footprint_gb(c, t, tokens, topk, vocab) + HEADROOM_GB <= HBM_GB for c in cfgs):
+            return t
+    return valid[-1] if valid else 1
+
+
 def main(argv=None) -> int:
     from ..models.llama import LlamaConfig, preset
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawTextHelpFormatter)

@@ -87,3 +87,23 @@ def test_shard_strategy_auto_resolves_from_the_student_config(tmp_path):
     cfg = SimpleNamespace(shard_strategy="auto", student_path=str(tmp_path / "missing"), batch_size=1, context_len=8,
                           save_topK=1, enable_topK=True, optimizer="adamw", grad_checkpointing=False)
     assert resolve_shard_strategy(cfg, 4) == "ddp"
+
+
+def test_tensor_parallel_width_is_the_smallest_that_fits():
+    t70, t8, tiny = preset("llama-3-70b"), preset("llama-3-8b"), preset("tinyllama-1.1b")
+    # a 70 B teacher in bf16 is 131 GiB of weights: one B200 holds it, eight replicas collect without communication
+    assert memory.teacher_footprint_gb(t70, 1, 8192, 128) < memory.HBM_GB - memory.HEADROOM_GB
+    assert memory.recommend_tp([t70], 8, 8192, 128) == 1
+    assert memory.recommend_tp([t70], 8, 65536, 128) == 2          # eight sequences of 8192 per forward: no longer
+    assert memory.recommend_tp([t8, tiny], 8, 16384) == 1
+    big = preset("llama-3-70b", num_hidden_layers=240)             # three times deeper: needs the weights split
+    assert memory.recommend_tp([big], 8, 8192, 128) == 4
+    assert memory.teacher_footprint_gb(t70, 8, 8192, 128) < 0.2 * memory.teacher_footprint_gb(t70, 1, 8192, 128)
+    # only widths that divide the ranks, the heads, the KV heads and the FFN width are offered
+    odd = preset("llama-3-70b", num_hidden_layers=240, num_key_value_heads=2)   # nothing fits: the widest valid
+    assert memory.recommend_tp([odd], 8, 8192, 128) == 2
+
+    from types import SimpleNamespace
+    from llm_distillery_b200.cli import resolve_tp_size
+    cfg = SimpleNamespace(tp_size=4, context_len=8192, save_topK=128, enable_topK=True, crop_distr_to_size=128256)
+    assert resolve_tp_size(cfg, [], 8) == 4 and resolve_tp_size(cfg, [], 2) == 2 and resolve_tp_size(cfg, [], 1) == 1
