@@ -36,6 +36,7 @@ class Sim:
         self.unit = None
         self.window = None
         self.ncoll = {"nccl": 0, "host": 0}
+        self.nsym = 0
 
     def add(self, kind, stream=None, reads=(), writes=(), deps=(), coll=None, phase=None) -> int:
         stream = stream or self.cur
@@ -100,7 +101,8 @@ def fake_stream_ctx(s):
 class FakeSym:
     def __init__(self, numel, dtype, device, group=None):
         self.tensor = torch.zeros(numel, dtype=dtype)
-        self.ptrs, self.c_ptrs = [], None
+        SIM.nsym += 1                       # allocation order is the same on every rank: the count names the buffer
+        self.ptrs, self.c_ptrs = [], ("sym", SIM.nsym)
 
 
 def _weights_obj(rank, u):
@@ -115,7 +117,7 @@ class FakeKernels:
     """Stands in for the kernel library: every launcher records what its kernel touches, on the current stream."""
 
     def b200_p2p_barrier(self, sig, rank, world, epoch, stream):
-        SIM.collective(("flag", int(epoch)))
+        SIM.collective(("flag", sig, int(epoch)))          # flag words of one symmetric buffer, one epoch
         return 0
 
     def b200_p2p_gather_pull(self, src, dst, off, nbytes, rank, world, stream):
