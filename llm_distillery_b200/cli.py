@@ -325,15 +325,20 @@ def collect(teachers, cfg, store, ids, validation, rank, world, student=None) ->
         dist.barrier()
         if rank == 0:
             from .data.convo import TeacherRows
+            seen: set[int] = set()
             for r in range(world):
                 shard_path = store.file_path.replace(".hdf5", f".rank{r}.hdf5")
                 shard = H5Store(shard_path)
                 for cid in shard.get_dataset_ids():
                     v, ix = shard.load_id(cid)
-                    store.update_batch([TeacherRows(cid, v, ix, shard.get_sha(cid) or "", shard._attr(cid, "sample") or "")])
+                    rows = [TeacherRows(cid, v, ix, shard.get_sha(cid) or "", shard._attr(cid, "sample") or "")]
+                    # teachers batch the conversations differently, so one conversation can sit in several ranks' files,
+                    # each holding other teachers' rows: the first one replaces what the main file had, the others merge
+                    (store.write_batch if cid in seen else store.update_batch)(rows)
+                    seen.add(cid)
                 shard.close()
                 os.remove(shard_path)
-            store.wait()
+                store.wait()            # a replace must have landed before a later shard merges into it
         dist.barrier()
 
 

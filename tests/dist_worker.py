@@ -6,6 +6,7 @@
               without a micro-batch, tied embeddings, a frozen layer and a checkpoint taken through the gathered view
   cpu_cli_zero3  gloo ranks on CPU: the command-line pipeline trains the same student replicated and fully sharded
   gpu_cli_zero3  the same pipeline on two GPUs in bf16
+  cpu_cli_config3  two teachers (one cross-tokenizer), tied-embedding student, JSD, fully sharded, planner-chosen widths
   gpu_zero3   GPU ranks: full parameter sharding, over NCCL and over the peer-access kernels, equals the replicated run
   gpu_p2p     NCCL + NVLink P2P ranks: P2P all-reduce equals NCCL all-reduce; a P2P-communicated training run equals
               the NCCL-communicated one
@@ -526,6 +527,80 @@ def cpu_cli_zero3():
     _cli_zero3("cpu", "fp32", 1e-5, tp=2, hidden=64, ffn=176)
 
 
+def cpu_cli_config3():
+    """The multi-teacher cross-tokenizer configuration in small: two teachers, one with another tokenizer (mapped onto the
+    student vocabulary through the byte trie), a student with tied embeddings trained with JSD on the merged targets,
+    fully sharded over two gloo ranks; tensor-parallel width and sharding both left to the planner. The result equals
+    the single-process run of the same configuration."""
+    import json
+    import numpy as np
+    from llm_distillery_b200 import cli
+    from llm_distillery_b200.ckpt.hf import load_hf_state_dict
+    from llm_distillery_b200.data.h5store import H5Store
+    from llm_distillery_b200.models.llama import preset
+    from llm_distillery_b200.utils import synthetic
+    root = sys.argv[2]
+    rank = int(os.environ["RANK"])
+    if rank == 0:
+        synthetic.make_tokenizer(os.path.join(root, "tok_a"), 400, seed=0)
+        synthetic.make_tokenizer(os.path.join(root, "tok_b"), 700, seed=5, extra_merges_text="quartz sphinx wizard " * 50)
+        kw = dict(hidden_size=64, intermediate_size=176, max_position_embeddings=128)
+        synthetic.make_model_dir(os.path.join(root, "teachers", "t_same"), preset("plumbing-teacher", vocab_size=512, **kw),
+                                 os.path.join(root, "tok_a"), seed=1, batch_size=4, add_bos=False)
+        synthetic.make_model_dir(os.path.join(root, "teachers", "t_other"), preset("plumbing-teacher", vocab_size=768, **kw),
+                                 os.path.join(root, "tok_b"), seed=2, batch_size=4, add_bos=False)
+        synthetic.make_model_dir(os.path.join(root, "student"),
+                                 preset("plumbing-student", vocab_size=512, num_hidden_layers=3, tie_word_embeddings=True, **kw),
+                                 os.path.join(root, "tok_a"), seed=3)
+        synthetic.make_dataset(os.path.join(root, "train.jsonl"), 9, seed=3)
+        synthetic.make_dataset(os.path.join(root, "val.jsonl"), 3, seed=4)
+        conf = {"dataset_path": os.path.join(root, "train.jsonl"), "validation_dataset_path": os.path.join(root, "val.jsonl"),
+                "teacher_models_folder": os.path.join(root, "teachers"), "student_path": os.path.join(root, "student"),
+                "context_len": 96, "crop_distr_to_size": 400, "save_topK": 16, "device": "cpu", "num_epochs": 2,
+                "batch_size": 2, "grad_accum_batches": 2, "lr": 1e-3, "optimizer": "adamw", "training_precision": "fp32",
+                "freeze_layers": [], "loss": "jsd", "cross_tokenizer": True, "data_order": "sorted", "tp_size": 0}
+        for name, extra in (("sharded", {"shard_strategy": "zero3"}), ("auto", {"shard_strategy": "auto"}), ("single", {})):
+            with open(os.path.join(root, f"config_{name}.json"), "w") as f:
+                json.dump(dict(conf, cache_folder=os.path.join(root, f"cache_{name}"), **extra), f)
+    dist.init_process_group("gloo")
+    dist.barrier()
+    finals = {}
+    for name in ("sharded", "auto"):
+        out = cli.main(["--config", os.path.join(root, f"config_{name}.json")])
+        assert out["trained_samples"] == 18, out
+        dist.barrier()
+        if rank == 0:
+            base = os.path.join(root, f"cache_{name}", "student", "trained")
+            final = [d for d in os.listdir(base) if d.endswith("final")]
+            finals[name] = load_hf_state_dict(os.path.join(base, final[0]))
+    if rank == 0:
+        os.environ["WORLD_SIZE"] = "1"
+        out = cli.main(["--config", os.path.join(root, "config_single.json")])
+        assert out["trained_samples"] == 18
+        base = os.path.join(root, "cache_single", "student", "trained")
+        single = load_hf_state_dict(os.path.join(base, [d for d in os.listdir(base) if d.endswith("final")][0]))
+        assert "lm_head.weight" not in single                       # tied embeddings stay tied in the checkpoint
+        for k, v in single.items():
+            # same data, same schedule; one process sums the two batches of a step in another order than two ranks do,
+            # and AdamW turns a last-bit difference of a near-zero gradient into a visible one (lr = 1e-3)
+            for name, sd in finals.items():
+                err = (v.float() - sd[k].float()).abs().max().item()
+                assert err < 3e-4, (name, k, err)
+            err = (finals["sharded"][k].float() - finals["auto"][k].float()).abs().max().item()
+            assert err < 2e-5, ("sharded vs planner-chosen", k, err)
+        a, b = H5Store(os.path.join(root, "cache_sharded", "dataset")), H5Store(os.path.join(root, "cache_single", "dataset"))
+        assert sorted(a.get_dataset_ids()) == sorted(b.get_dataset_ids()) and len(a.get_dataset_ids()) == 9
+        for cid in a.get_dataset_ids():
+            va, ia = a.load_id(cid)
+            vb, ib = b.load_id(cid)
+            assert va.shape == vb.shape and ia.max() < 400
+            fin = np.isfinite(va) & np.isfinite(vb)
+            assert (np.isfinite(va) == np.isfinite(vb)).all() and np.abs(va[fin] - vb[fin]).max() < 2e-2
+            mass = np.exp(va).sum(-1)
+            assert (mass <= 2.0 + 1e-2).all()                       # two teachers' probabilities summed, never more
+        print("WORKER_OK")
+
+
 def gpu_cli_zero3():
     """Same on two GPUs in bf16: data-parallel collection replicas, NVLink data parallelism / full sharding."""
     _cli_zero3("cuda", "bf16", 3e-2, tp=1, hidden=256, ffn=688)
@@ -582,4 +657,4 @@ def gpu_tp():
 if __name__ == "__main__":
     {"cpu_engine": cpu_engine, "gpu_p2p": gpu_p2p, "cpu_tp": cpu_tp, "gpu_tp": gpu_tp, "cpu_cli_tp": cpu_cli_tp,
      "cpu_vp_head": cpu_vp_head, "cpu_rank_loss": cpu_rank_loss, "cpu_zero3": cpu_zero3, "gpu_zero3": gpu_zero3,
-     "cpu_cli_zero3": cpu_cli_zero3, "gpu_cli_zero3": gpu_cli_zero3}[sys.argv[1]]()
+     "cpu_cli_zero3": cpu_cli_zero3, "gpu_cli_zero3": gpu_cli_zero3, "cpu_cli_config3": cpu_cli_config3}[sys.argv[1]]()

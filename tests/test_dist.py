@@ -37,6 +37,10 @@ def test_cpu_ranks_pipeline_with_fully_sharded_student(tmp_path):
     _launch("cpu_cli_zero3", 2, extra=(str(tmp_path),))
 
 
+def test_cpu_ranks_multi_teacher_cross_tokenizer_pipeline_fully_sharded(tmp_path):
+    _launch("cpu_cli_config3", 2, extra=(str(tmp_path),))
+
+
 @pytest.mark.gpu
 def test_gpu_pipeline_with_replicated_and_fully_sharded_student(tmp_path):
     if torch.cuda.device_count() < 2:
