@@ -441,6 +441,7 @@ class H5Store:
 
     def reopen(self) -> None:
         """Drop this handle's view of the file and read it again (another process has written to it)."""
+        cycle = self._cycle              # a validation cycle set up earlier goes on after the reopen, from its first batch
         self.stop_prefetch()
         self.wait()
         self.lib.h5s_close(self.h)
@@ -448,6 +449,8 @@ class H5Store:
         self.h = self.lib.h5s_open(self.file_path.encode(), 1, err, 512)
         if not self.h:
             raise IOError(f"cannot reopen {self.file_path}: {err.value.decode()}")
+        if cycle is not None:
+            self.read_only_mode(cycle[0], **cycle[1])
 
     def close(self) -> None:
         if self.closed:

@@ -6,6 +6,7 @@
               without a micro-batch, tied embeddings, a frozen layer and a checkpoint taken through the gathered view
   cpu_cli_zero3  gloo ranks on CPU: the command-line pipeline trains the same student replicated and fully sharded
   gpu_cli_zero3  the same pipeline on two GPUs in bf16
+  cpu_cli_zero3_chunked  the same with a cache that holds only part of the data (collect / train / state per chunk)
   cpu_cli_config3  two teachers (one cross-tokenizer), tied-embedding student, JSD, fully sharded, planner-chosen widths
   gpu_zero3   GPU ranks: full parameter sharding, over NCCL and over the peer-access kernels, equals the replicated run
   gpu_p2p     NCCL + NVLink P2P ranks: P2P all-reduce equals NCCL all-reduce; a P2P-communicated training run equals
@@ -453,7 +454,7 @@ def cpu_cli_tp():
         print("WORKER_OK")
 
 
-def _cli_zero3(device: str, precision: str, tol: float, tp: int, hidden: int, ffn: int):
+def _cli_zero3(device: str, precision: str, tol: float, tp: int, hidden: int, ffn: int, extra: dict | None = None):
     """The command-line pipeline under two ranks, student trained once replicated and once fully sharded: five
     batches over two ranks, so the last step has a rank without a micro-batch; the saved students are equal."""
     import json
@@ -470,6 +471,7 @@ def _cli_zero3(device: str, precision: str, tol: float, tp: int, hidden: int, ff
             "grad_accum_batches": 1, "temperature": 1.0, "lr": 1e-3, "optimizer": "adamw", "data_order": "sorted",
             "training_precision": precision, "validate_every_n_epochs": 1, "save_student_every_n_epochs": 1,
             "freeze_layers": [], "loss": "kl", "max_cache_size_gb": 320, "tp_size": tp, "save_final_state": True}
+    conf.update(extra or {})
     os.environ["B200_TRACE"] = "1"          # phase timers on: the per-rank skew figures are gathered and logged
     if rank == 0:
         tok = os.path.join(root, "tok")
@@ -525,6 +527,12 @@ def _cli_zero3(device: str, precision: str, tol: float, tp: int, hidden: int, ff
 
 def cpu_cli_zero3():
     _cli_zero3("cpu", "fp32", 1e-5, tp=2, hidden=64, ffn=176)
+
+
+def cpu_cli_zero3_chunked():
+    """The cache holds only part of the data at a time: collect a chunk, train on it, save the trainer state, next chunk
+    (state loaded back) - replicated against fully sharded, whose state goes through the gathered view each time."""
+    _cli_zero3("cpu", "fp32", 1e-5, tp=1, hidden=64, ffn=176, extra={"max_cache_size_gb": 0.00002})
 
 
 def cpu_cli_config3():
@@ -657,4 +665,5 @@ def gpu_tp():
 if __name__ == "__main__":
     {"cpu_engine": cpu_engine, "gpu_p2p": gpu_p2p, "cpu_tp": cpu_tp, "gpu_tp": gpu_tp, "cpu_cli_tp": cpu_cli_tp,
      "cpu_vp_head": cpu_vp_head, "cpu_rank_loss": cpu_rank_loss, "cpu_zero3": cpu_zero3, "gpu_zero3": gpu_zero3,
-     "cpu_cli_zero3": cpu_cli_zero3, "gpu_cli_zero3": gpu_cli_zero3, "cpu_cli_config3": cpu_cli_config3}[sys.argv[1]]()
+     "cpu_cli_zero3": cpu_cli_zero3, "gpu_cli_zero3": gpu_cli_zero3, "cpu_cli_config3": cpu_cli_config3,
+     "cpu_cli_zero3_chunked": cpu_cli_zero3_chunked}[sys.argv[1]]()

@@ -37,6 +37,11 @@ def test_cpu_ranks_pipeline_with_fully_sharded_student(tmp_path):
     _launch("cpu_cli_zero3", 2, extra=(str(tmp_path),))
 
 
+def test_cpu_ranks_chunked_pipeline_replicated_and_fully_sharded(tmp_path):
+    """Cache smaller than the data: collect / train / save state / load state per chunk, on two ranks."""
+    _launch("cpu_cli_zero3_chunked", 2, extra=(str(tmp_path),))
+
+
 def test_cpu_ranks_multi_teacher_cross_tokenizer_pipeline_fully_sharded(tmp_path):
     _launch("cpu_cli_config3", 2, extra=(str(tmp_path),))
 

@@ -187,3 +187,22 @@ def test_h5py_reads_the_file_when_it_is_installed(tmp_path):
             assert g.attrs["content_sha"] == "sha-1"
             assert g["distributions"].dtype == np.float16 and g["distributions"].shape == (12, 5)
             assert g["indices"].dtype == np.uint32 and int(g["indices"][0, 0]) == 1
+
+
+def test_reopen_keeps_the_validation_cycle(tmp_path):
+    """Another process appends to the file; a reader that reopens it goes on cycling over its validation batches."""
+    st = H5Store(str(tmp_path))
+    st.write_batch([_rows(i) for i in range(4)])
+    st.wait()
+    reader = H5Store(str(tmp_path))
+    reader.read_only_mode([[0, 1], [2, 3]], sort_ids=True)
+    first = reader.read_next_batch(timeout=30)
+    st.write_batch([_rows(9)])
+    st.wait()
+    reader.reopen()
+    assert 9 in reader.get_dataset_ids()
+    again = [reader.read_next_batch(timeout=30) for _ in range(3)]       # the cycle starts over: [0,1], [2,3], [0,1]
+    assert np.array_equal(again[0]["values"][0], first["values"][0]) and np.array_equal(again[2]["values"][0], first["values"][0])
+    assert not np.array_equal(again[1]["values"][0], first["values"][0])
+    reader.close()
+    st.close()
