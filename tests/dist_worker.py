@@ -7,6 +7,7 @@
   cpu_cli_zero3  gloo ranks on CPU: the command-line pipeline trains the same student replicated and fully sharded
   gpu_cli_zero3  the same pipeline on two GPUs in bf16
   cpu_cli_zero3_chunked  the same with a cache that holds only part of the data (collect / train / state per chunk)
+  cpu_cli_resume  a fully sharded run stopped after one epoch and taken up again equals the uninterrupted run
   cpu_cli_config3  two teachers (one cross-tokenizer), tied-embedding student, JSD, fully sharded, planner-chosen widths
   gpu_zero3   GPU ranks: full parameter sharding, over NCCL and over the peer-access kernels, equals the replicated run
   gpu_p2p     NCCL + NVLink P2P ranks: P2P all-reduce equals NCCL all-reduce; a P2P-communicated training run equals
@@ -535,6 +536,65 @@ def cpu_cli_zero3_chunked():
     _cli_zero3("cpu", "fp32", 1e-5, tp=1, hidden=64, ffn=176, extra={"max_cache_size_gb": 0.00002})
 
 
+def cpu_cli_resume():
+    """A fully sharded two-rank run stops after one epoch with its trainer state saved; the same command asking for two
+    epochs picks the state up (weights through the gathered view, per-rank optimizer pieces, counters) and ends where
+    an uninterrupted two-epoch run ends."""
+    import json
+    from llm_distillery_b200 import cli
+    from llm_distillery_b200.ckpt.hf import load_hf_state_dict
+    from llm_distillery_b200.models.llama import preset
+    from llm_distillery_b200.utils import synthetic
+    root = sys.argv[2]
+    rank = int(os.environ["RANK"])
+    conf = {"dataset_path": os.path.join(root, "train.jsonl"), "validation_dataset_path": os.path.join(root, "val.jsonl"),
+            "teacher_models_folder": os.path.join(root, "teachers"), "student_path": os.path.join(root, "student"),
+            "context_len": 96, "crop_distr_to_size": 400, "save_topK": 20, "enable_topK": True, "device": "cpu",
+            "num_epochs": 1, "num_warmup_steps": 0, "lr_scheduler": "constant", "batch_size": 2, "grad_accum_batches": 1,
+            "temperature": 1.0, "lr": 1e-3, "optimizer": "adamw", "data_order": "sorted", "training_precision": "fp32",
+            "freeze_layers": [], "loss": "kl", "max_cache_size_gb": 320, "shard_strategy": "zero3", "save_final_state": True}
+    if rank == 0:
+        tok = os.path.join(root, "tok")
+        synthetic.make_tokenizer(tok, 400)
+        kw = dict(vocab_size=512, hidden_size=64, intermediate_size=176, max_position_embeddings=512)
+        synthetic.make_model_dir(os.path.join(root, "teachers", "teacher_a"), preset("plumbing-teacher", **kw), tok, seed=1,
+                                 batch_size=4)
+        synthetic.make_model_dir(os.path.join(root, "student"), preset("plumbing-student", **kw), tok, seed=2)
+        synthetic.make_dataset(os.path.join(root, "train.jsonl"), 8, seed=3)
+        synthetic.make_dataset(os.path.join(root, "val.jsonl"), 4, seed=4)
+        for name, extra in (("stop", {"cache_folder": os.path.join(root, "cache_a")}),
+                            ("go_on", {"cache_folder": os.path.join(root, "cache_a"), "num_epochs": 2}),
+                            ("whole", {"cache_folder": os.path.join(root, "cache_b"), "num_epochs": 2})):
+            with open(os.path.join(root, f"config_{name}.json"), "w") as f:
+                json.dump(dict(conf, **extra), f)
+    dist.init_process_group("gloo")
+    dist.barrier()
+
+    def final(cache):
+        base = os.path.join(root, cache, "student", "trained")
+        names = [d for d in os.listdir(base) if d.endswith("final")]
+        return {k: v.clone() for k, v in load_hf_state_dict(os.path.join(base, names[0])).items()}
+    out = cli.main(["--config", os.path.join(root, "config_stop.json")])
+    assert out["trained_samples"] == 8, out
+    dist.barrier()
+    first = final("cache_a") if rank == 0 else None
+    out = cli.main(["--config", os.path.join(root, "config_go_on.json")])
+    assert out["trained_samples"] == 16 and out["tokens_collected"] == 0, out      # nothing collected again; 8 more trained
+    dist.barrier()
+    resumed = final("cache_a") if rank == 0 else None
+    out = cli.main(["--config", os.path.join(root, "config_whole.json")])
+    assert out["trained_samples"] == 16, out
+    dist.barrier()
+    if rank == 0:
+        whole = final("cache_b")
+        for k, v in whole.items():
+            err = (v.float() - resumed[k].float()).abs().max().item()
+            assert err < 1e-5, (k, err)
+        moved = max((first[k].float() - resumed[k].float()).abs().max().item() for k in first)
+        assert moved > 1e-4, ("the second epoch changed nothing", moved)
+        print("WORKER_OK")
+
+
 def cpu_cli_config3():
     """The multi-teacher cross-tokenizer configuration in small: two teachers, one with another tokenizer (mapped onto the
     student vocabulary through the byte trie), a student with tied embeddings trained with JSD on the merged targets,
@@ -666,4 +726,4 @@ if __name__ == "__main__":
     {"cpu_engine": cpu_engine, "gpu_p2p": gpu_p2p, "cpu_tp": cpu_tp, "gpu_tp": gpu_tp, "cpu_cli_tp": cpu_cli_tp,
      "cpu_vp_head": cpu_vp_head, "cpu_rank_loss": cpu_rank_loss, "cpu_zero3": cpu_zero3, "gpu_zero3": gpu_zero3,
      "cpu_cli_zero3": cpu_cli_zero3, "gpu_cli_zero3": gpu_cli_zero3, "cpu_cli_config3": cpu_cli_config3,
-     "cpu_cli_zero3_chunked": cpu_cli_zero3_chunked}[sys.argv[1]]()
+     "cpu_cli_zero3_chunked": cpu_cli_zero3_chunked, "cpu_cli_resume": cpu_cli_resume}[sys.argv[1]]()

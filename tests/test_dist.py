@@ -42,6 +42,10 @@ def test_cpu_ranks_chunked_pipeline_replicated_and_fully_sharded(tmp_path):
     _launch("cpu_cli_zero3_chunked", 2, extra=(str(tmp_path),))
 
 
+def test_cpu_ranks_fully_sharded_run_resumes_where_it_stopped(tmp_path):
+    _launch("cpu_cli_resume", 2, extra=(str(tmp_path),))
+
+
 def test_cpu_ranks_multi_teacher_cross_tokenizer_pipeline_fully_sharded(tmp_path):
     _launch("cpu_cli_config3", 2, extra=(str(tmp_path),))
 
