@@ -7,6 +7,7 @@
   cpu_cli_zero3  gloo ranks on CPU: the command-line pipeline trains the same student replicated and fully sharded
   gpu_cli_zero3  the same pipeline on two GPUs in bf16
   cpu_cli_zero3_chunked  the same with a cache that holds only part of the data (collect / train / state per chunk)
+  cpu_cli_zero3_three / cpu_cli_zero3_accum  the same on three ranks / with an accumulation that straddles epochs
   cpu_cli_resume  a fully sharded run stopped after one epoch and taken up again equals the uninterrupted run
   cpu_cli_config3  two teachers (one cross-tokenizer), tied-embedding student, JSD, fully sharded, planner-chosen widths
   gpu_zero3   GPU ranks: full parameter sharding, over NCCL and over the peer-access kernels, equals the replicated run
@@ -509,7 +510,7 @@ def _cli_zero3(device: str, precision: str, tol: float, tp: int, hidden: int, ff
             assert any("Perf/rank skew ms" in rec for rec in logged), logged[:3]
             with open(os.path.join(root, f"cache_{strat}", "student", "states", "trainer_state.json")) as f:
                 st = json.load(f)
-            assert len(st["config_hash"]) == 16 and "rng_state" in st and st["world"] == 2
+            assert len(st["config_hash"]) == 16 and "rng_state" in st and st["world"] == int(os.environ["WORLD_SIZE"])
     if device != "cpu":
         from llm_distillery_b200.ops import _lib
         torch.cuda.synchronize()
@@ -528,6 +529,17 @@ def _cli_zero3(device: str, precision: str, tol: float, tp: int, hidden: int, ff
 
 def cpu_cli_zero3():
     _cli_zero3("cpu", "fp32", 1e-5, tp=2, hidden=64, ffn=176)
+
+
+def cpu_cli_zero3_three():
+    """Three ranks, five batches per epoch: the last step of an epoch has one rank without a batch."""
+    _cli_zero3("cpu", "fp32", 1e-5, tp=1, hidden=64, ffn=176)
+
+
+def cpu_cli_zero3_accum():
+    """Gradient accumulation whose step size (batch 2 x 2 micro-batches x 2 ranks = 8 samples) does not divide the ten
+    samples of an epoch: steps straddle epochs and the run ends with a partial step."""
+    _cli_zero3("cpu", "fp32", 1e-5, tp=1, hidden=64, ffn=176, extra={"grad_accum_batches": 2})
 
 
 def cpu_cli_zero3_chunked():
@@ -726,4 +738,5 @@ if __name__ == "__main__":
     {"cpu_engine": cpu_engine, "gpu_p2p": gpu_p2p, "cpu_tp": cpu_tp, "gpu_tp": gpu_tp, "cpu_cli_tp": cpu_cli_tp,
      "cpu_vp_head": cpu_vp_head, "cpu_rank_loss": cpu_rank_loss, "cpu_zero3": cpu_zero3, "gpu_zero3": gpu_zero3,
      "cpu_cli_zero3": cpu_cli_zero3, "gpu_cli_zero3": gpu_cli_zero3, "cpu_cli_config3": cpu_cli_config3,
-     "cpu_cli_zero3_chunked": cpu_cli_zero3_chunked, "cpu_cli_resume": cpu_cli_resume}[sys.argv[1]]()
+     "cpu_cli_zero3_chunked": cpu_cli_zero3_chunked, "cpu_cli_resume": cpu_cli_resume, "cpu_cli_zero3_three": cpu_cli_zero3_three,
+     "cpu_cli_zero3_accum": cpu_cli_zero3_accum}[sys.argv[1]]()

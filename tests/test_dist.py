@@ -42,6 +42,14 @@ def test_cpu_ranks_chunked_pipeline_replicated_and_fully_sharded(tmp_path):
     _launch("cpu_cli_zero3_chunked", 2, extra=(str(tmp_path),))
 
 
+def test_cpu_three_ranks_pipeline_with_a_rank_short_of_a_batch(tmp_path):
+    _launch("cpu_cli_zero3_three", 3, extra=(str(tmp_path),))
+
+
+def test_cpu_ranks_pipeline_with_accumulation_that_straddles_epochs(tmp_path):
+    _launch("cpu_cli_zero3_accum", 2, extra=(str(tmp_path),))
+
+
 def test_cpu_ranks_fully_sharded_run_resumes_where_it_stopped(tmp_path):
     _launch("cpu_cli_resume", 2, extra=(str(tmp_path),))
 
