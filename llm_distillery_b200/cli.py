@@ -266,7 +266,12 @@ def _tp_group(cfg, teacher, rank: int, world: int, tp: int):
             _TP_GROUPS["pg"] = mine
     mcfg = LlamaConfig.from_pretrained(teacher.model_path)
     B = max(1, teacher.batch_size)
-    tokens = B * padded_seq_len(B, cfg.context_len, tp)
+    # a teacher with another tokenizer can spell the same text in more tokens than the student's context length
+    longest = max([int(cfg.context_len)] + [int(c.length) for ds in (getattr(teacher, "dataset", None),
+                                                                      getattr(teacher, "validation_dataset", None))
+                                            for c in (ds or [])])
+    # the last batch of a share can hold fewer conversations, and an odd count pads each of them further
+    tokens = max(b * padded_seq_len(b, longest, tp) for b in range(1, B + 1))
     key = (mcfg.hidden_size, tokens, int(teacher.topK))
     if key not in _TP_GROUPS:
         _TP_GROUPS[key] = TPGroup(torch.device(cfg.device), tokens, mcfg.hidden_size, topk=int(teacher.topK),

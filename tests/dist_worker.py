@@ -638,7 +638,7 @@ def cpu_cli_config3():
                 "teacher_models_folder": os.path.join(root, "teachers"), "student_path": os.path.join(root, "student"),
                 "context_len": 96, "crop_distr_to_size": 400, "save_topK": 16, "device": "cpu", "num_epochs": 2,
                 "batch_size": 2, "grad_accum_batches": 2, "lr": 1e-3, "optimizer": "adamw", "training_precision": "fp32",
-                "freeze_layers": [], "loss": "jsd", "cross_tokenizer": True, "data_order": "sorted", "tp_size": 0}
+                "freeze_layers": [], "loss": "jsd", "cross_tokenizer": True, "data_order": "sorted", "tp_size": int(os.environ.get("C3_TP", "0"))}
         for name, extra in (("sharded", {"shard_strategy": "zero3"}), ("auto", {"shard_strategy": "auto"}), ("single", {})):
             with open(os.path.join(root, f"config_{name}.json"), "w") as f:
                 json.dump(dict(conf, cache_folder=os.path.join(root, f"cache_{name}"), **extra), f)

@@ -54,8 +54,10 @@ def test_cpu_ranks_fully_sharded_run_resumes_where_it_stopped(tmp_path):
     _launch("cpu_cli_resume", 2, extra=(str(tmp_path),))
 
 
-def test_cpu_ranks_multi_teacher_cross_tokenizer_pipeline_fully_sharded(tmp_path):
-    _launch("cpu_cli_config3", 2, extra=(str(tmp_path),))
+@pytest.mark.parametrize("tp", ["0", "2"])
+def test_cpu_ranks_multi_teacher_cross_tokenizer_pipeline_fully_sharded(tmp_path, tp):
+    """tp 0: the planner picks the width (1: two replicas); tp 2: both teachers run as one two-way group."""
+    _launch("cpu_cli_config3", 2, extra=(str(tmp_path),), env={"C3_TP": tp})
 
 
 @pytest.mark.gpu
