@@ -542,6 +542,14 @@ def cpu_cli_zero3_accum():
     _cli_zero3("cpu", "fp32", 1e-5, tp=1, hidden=64, ffn=176, extra={"grad_accum_batches": 2})
 
 
+def cpu_cli_zero3_variants():
+    """Gradient checkpointing (the layer is recomputed from gathered weights in backward), shuffled data order, the
+    reference's weighted loss, a frozen layer and an 8-bit optimizer name, replicated against fully sharded."""
+    _cli_zero3("cpu", "fp32", 1e-5, tp=1, hidden=64, ffn=176,
+               extra={"grad_checkpointing": True, "data_order": "shuffle", "loss": "reference", "temperature": 2.0,
+                      "freeze_layers": ["layers.1."], "optimizer": os.environ.get("Z3_OPT", "adamw")})
+
+
 def cpu_cli_zero3_chunked():
     """The cache holds only part of the data at a time: collect a chunk, train on it, save the trainer state, next chunk
     (state loaded back) - replicated against fully sharded, whose state goes through the gathered view each time."""
@@ -739,4 +747,4 @@ if __name__ == "__main__":
      "cpu_vp_head": cpu_vp_head, "cpu_rank_loss": cpu_rank_loss, "cpu_zero3": cpu_zero3, "gpu_zero3": gpu_zero3,
      "cpu_cli_zero3": cpu_cli_zero3, "gpu_cli_zero3": gpu_cli_zero3, "cpu_cli_config3": cpu_cli_config3,
      "cpu_cli_zero3_chunked": cpu_cli_zero3_chunked, "cpu_cli_resume": cpu_cli_resume, "cpu_cli_zero3_three": cpu_cli_zero3_three,
-     "cpu_cli_zero3_accum": cpu_cli_zero3_accum}[sys.argv[1]]()
+     "cpu_cli_zero3_accum": cpu_cli_zero3_accum, "cpu_cli_zero3_variants": cpu_cli_zero3_variants}[sys.argv[1]]()

@@ -50,6 +50,12 @@ def test_cpu_ranks_pipeline_with_accumulation_that_straddles_epochs(tmp_path):
     _launch("cpu_cli_zero3_accum", 2, extra=(str(tmp_path),))
 
 
+@pytest.mark.parametrize("optimizer", ["adamw", "sgd"])
+def test_cpu_ranks_pipeline_variants_replicated_and_fully_sharded(tmp_path, optimizer):
+    """Gradient checkpointing, shuffled order, the reference's weighted loss, a frozen layer."""
+    _launch("cpu_cli_zero3_variants", 2, extra=(str(tmp_path),), env={"Z3_OPT": optimizer})
+
+
 def test_cpu_ranks_fully_sharded_run_resumes_where_it_stopped(tmp_path):
     _launch("cpu_cli_resume", 2, extra=(str(tmp_path),))
 
