@@ -8,6 +8,8 @@
   gpu_cli_zero3  the same pipeline on two GPUs in bf16
   cpu_cli_zero3_chunked  the same with a cache that holds only part of the data (collect / train / state per chunk)
   cpu_cli_zero3_three / cpu_cli_zero3_accum  the same on three ranks / with an accumulation that straddles epochs
+  cpu_cli_zero3_variants  gradient checkpointing, shuffled order, reference loss, frozen layer, other optimizers
+  cpu_cli_sync  the dataset changes between two runs: only the new conversations are collected, the store is re-keyed
   cpu_cli_resume  a fully sharded run stopped after one epoch and taken up again equals the uninterrupted run
   cpu_cli_config3  two teachers (one cross-tokenizer), tied-embedding student, JSD, fully sharded, planner-chosen widths
   gpu_zero3   GPU ranks: full parameter sharding, over NCCL and over the peer-access kernels, equals the replicated run
@@ -615,6 +617,75 @@ def cpu_cli_resume():
         print("WORKER_OK")
 
 
+def cpu_cli_sync():
+    """The dataset changes between two runs on two ranks: two conversations are dropped, the rest is reordered, three
+    new ones arrive. The second run collects only the new ones, renames / removes the old entries by their content
+    SHA, and the store ends up equal to a fresh collection of the new dataset."""
+    import json
+    import numpy as np
+    from llm_distillery_b200 import cli
+    from llm_distillery_b200.data.h5store import H5Store
+    from llm_distillery_b200.models.llama import preset
+    from llm_distillery_b200.utils import synthetic
+    root = sys.argv[2]
+    rank = int(os.environ["RANK"])
+    conf = {"dataset_path": os.path.join(root, "train.jsonl"), "validation_dataset_path": os.path.join(root, "val.jsonl"),
+            "teacher_models_folder": os.path.join(root, "teachers"), "student_path": os.path.join(root, "student"),
+            "context_len": 96, "crop_distr_to_size": 400, "save_topK": 20, "enable_topK": True, "device": "cpu",
+            "num_epochs": 1, "num_warmup_steps": 0, "batch_size": 2, "grad_accum_batches": 1, "lr": 1e-3,
+            "optimizer": "adamw", "data_order": "sorted", "training_precision": "fp32", "freeze_layers": [], "loss": "kl",
+            "max_cache_size_gb": 320, "cache_folder": os.path.join(root, "cache")}
+    if rank == 0:
+        tok = os.path.join(root, "tok")
+        synthetic.make_tokenizer(tok, 400)
+        kw = dict(vocab_size=512, hidden_size=64, intermediate_size=176, max_position_embeddings=512)
+        synthetic.make_model_dir(os.path.join(root, "teachers", "teacher_a"), preset("plumbing-teacher", **kw), tok, seed=1,
+                                 batch_size=4)
+        synthetic.make_model_dir(os.path.join(root, "student"), preset("plumbing-student", **kw), tok, seed=2)
+        rows = synthetic.make_dataset(os.path.join(root, "all.jsonl"), 12, seed=3)
+        synthetic.make_dataset(os.path.join(root, "val.jsonl"), 4, seed=4)
+        with open(os.path.join(root, "train.jsonl"), "w", encoding="utf-8") as f:
+            for r in rows[:9]:
+                f.write(json.dumps(r, ensure_ascii=False) + "\n")
+        with open(os.path.join(root, "config.json"), "w") as f:
+            json.dump(conf, f)
+        with open(os.path.join(root, "config_fresh.json"), "w") as f:
+            json.dump(dict(conf, cache_folder=os.path.join(root, "cache_fresh")), f)
+    dist.init_process_group("gloo")
+    dist.barrier()
+    out = cli.main(["--config", os.path.join(root, "config.json")])
+    def total(n):           # tokens collected by all ranks together
+        t = torch.tensor([float(n)])
+        dist.all_reduce(t)
+        return float(t.item())
+    first_tokens = total(out["tokens_collected"])
+    assert out["trained_samples"] == 9 and first_tokens > 0
+    dist.barrier()
+    if rank == 0:
+        rows = [json.loads(line) for line in open(os.path.join(root, "all.jsonl"), encoding="utf-8")]
+        new = [rows[7], rows[9], rows[0], rows[10], rows[3], rows[4], rows[11], rows[5], rows[8], rows[6]]   # 1, 2 dropped
+        with open(os.path.join(root, "train.jsonl"), "w", encoding="utf-8") as f:
+            for r in new:
+                f.write(json.dumps(r, ensure_ascii=False) + "\n")
+    dist.barrier()
+    out = cli.main(["--config", os.path.join(root, "config.json")])
+    assert out["trained_samples"] == 10, out
+    again = total(out["tokens_collected"])
+    assert 0 < again < 0.6 * first_tokens, (again, first_tokens)                 # three conversations of ten
+    dist.barrier()
+    if rank == 0:
+        os.environ["WORLD_SIZE"] = "1"
+        cli.main(["--config", os.path.join(root, "config_fresh.json")])
+        a, b = H5Store(os.path.join(root, "cache", "dataset")), H5Store(os.path.join(root, "cache_fresh", "dataset"))
+        assert sorted(a.get_dataset_ids()) == sorted(b.get_dataset_ids()) == list(range(10))
+        for cid in range(10):
+            assert a.get_sha(cid) == b.get_sha(cid), cid
+            va, ia = a.load_id(cid)
+            vb, ib = b.load_id(cid)
+            assert va.shape == vb.shape and np.abs(va - vb).max() < 2e-2 and (ia == ib).mean() > 0.97
+        print("WORKER_OK")
+
+
 def cpu_cli_config3():
     """The multi-teacher cross-tokenizer configuration in small: two teachers, one with another tokenizer (mapped onto the
     student vocabulary through the byte trie), a student with tied embeddings trained with JSD on the merged targets,
@@ -747,4 +818,5 @@ if __name__ == "__main__":
      "cpu_vp_head": cpu_vp_head, "cpu_rank_loss": cpu_rank_loss, "cpu_zero3": cpu_zero3, "gpu_zero3": gpu_zero3,
      "cpu_cli_zero3": cpu_cli_zero3, "gpu_cli_zero3": gpu_cli_zero3, "cpu_cli_config3": cpu_cli_config3,
      "cpu_cli_zero3_chunked": cpu_cli_zero3_chunked, "cpu_cli_resume": cpu_cli_resume, "cpu_cli_zero3_three": cpu_cli_zero3_three,
-     "cpu_cli_zero3_accum": cpu_cli_zero3_accum, "cpu_cli_zero3_variants": cpu_cli_zero3_variants}[sys.argv[1]]()
+     "cpu_cli_zero3_accum": cpu_cli_zero3_accum, "cpu_cli_zero3_variants": cpu_cli_zero3_variants,
+     "cpu_cli_sync": cpu_cli_sync}[sys.argv[1]]()

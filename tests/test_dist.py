@@ -56,6 +56,10 @@ def test_cpu_ranks_pipeline_variants_replicated_and_fully_sharded(tmp_path, opti
     _launch("cpu_cli_zero3_variants", 2, extra=(str(tmp_path),), env={"Z3_OPT": optimizer})
 
 
+def test_cpu_ranks_changed_dataset_is_synced_not_recollected(tmp_path):
+    _launch("cpu_cli_sync", 2, extra=(str(tmp_path),))
+
+
 def test_cpu_ranks_fully_sharded_run_resumes_where_it_stopped(tmp_path):
     _launch("cpu_cli_resume", 2, extra=(str(tmp_path),))
 
