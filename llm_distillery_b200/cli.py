@@ -347,27 +347,55 @@ def collect(teachers, cfg, store, ids, validation, rank, world, student=None) ->
         dist.barrier()
 
 
+def _leave_after_rank_failure(e) -> None:
+    """Emergency exit of a surviving rank: trainer state of this rank without any collective, stores closed, status 3."""
+    print(f"[watchdog] {e}: saving state and leaving", flush=True)
+    student, hb = _STATE.get("student"), _STATE.get("heartbeat")
+    if student is not None and getattr(student, "engine", None) is not None:
+        try:
+            student._save_state(collective=False)
+        except Exception as ex:  # noqa: BLE001
+            print(f"[watchdog] emergency save failed: {ex}", flush=True)
+    if hb is not None:
+        hb.close("failed")
+    for key in ("data_manager", "validation_data_manager"):
+        if _STATE.get(key) is not None:
+            try:
+                _STATE[key].close()
+            except Exception:  # noqa: BLE001
+                pass
+    os._exit(3)
+
+
 def main(argv=None, default_config_path: str | None = None) -> dict:
     """Run the pipeline. With several ranks a heartbeat / watchdog pair runs beside it: when a peer stops beating,
     the surviving ranks find out between two steps, save their trainer state without any collective and exit with
-    status 3; running the same command again resumes (SHA sync for collection, trainer state for training)."""
+    status 3; running the same command again resumes (SHA sync for collection, trainer state for training).
+
+    A peer that leaves just before a collective is usually noticed the other way round: the collective ends with an
+    error before the heartbeat record is old enough. Any exception under several ranks is therefore followed by a
+    look at the heartbeats (for as long as a record takes to go stale): if a peer is gone, the exception is its
+    consequence and the rank leaves the same way; if every peer is alive, the exception is this rank's own."""
+    import time
     from .obs import watchdog
     try:
         return _main(argv, default_config_path)
     except watchdog.RankFailure as e:
-        print(f"[watchdog] {e}: saving state and leaving", flush=True)
-        student, hb = _STATE.get("student"), _STATE.get("heartbeat")
-        if student is not None and getattr(student, "engine", None) is not None:
-            try:
-                student._save_state(collective=False)
-            except Exception as ex:  # noqa: BLE001
-                print(f"[watchdog] emergency save failed: {ex}", flush=True)
-        if hb is not None:
-            hb.close("failed")
-        for key in ("data_manager", "validation_data_manager"):
-            if _STATE.get(key) is not None:
-                _STATE[key].close()
-        os._exit(3)
+        _leave_after_rank_failure(e)
+    except Exception as ex:  # noqa: BLE001
+        hb = _STATE.get("heartbeat")
+        if hb is None:
+            raise
+        deadline = time.time() + hb.timeout + 3 * hb.interval + 1.0
+        failed = hb.scan()
+        while not failed and time.time() < deadline:
+            time.sleep(hb.interval)
+            failed = hb.scan()
+        if not failed:
+            raise
+        ranks = sorted(failed)
+        _leave_after_rank_failure(watchdog.RankFailure(
+            ranks, "; ".join(f"rank {k}: {failed[k]}" for k in ranks) + f" (seen as {type(ex).__name__}: {str(ex)[:200]})"))
 
 
 def _main(argv=None, default_config_path: str | None = None) -> dict:

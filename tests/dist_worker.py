@@ -9,6 +9,7 @@
   cpu_cli_zero3_chunked  the same with a cache that holds only part of the data (collect / train / state per chunk)
   cpu_cli_zero3_three / cpu_cli_zero3_accum  the same on three ranks / with an accumulation that straddles epochs
   cpu_cli_zero3_variants  gradient checkpointing, shuffled order, reference loss, frozen layer, other optimizers
+  cpu_cli_rank_loss  a rank's process ends between two steps of the command-line run: the other saves state, status 3
   cpu_cli_sync  the dataset changes between two runs: only the new conversations are collected, the store is re-keyed
   cpu_cli_resume  a fully sharded run stopped after one epoch and taken up again equals the uninterrupted run
   cpu_cli_config3  two teachers (one cross-tokenizer), tied-embedding student, JSD, fully sharded, planner-chosen widths
@@ -686,6 +687,50 @@ def cpu_cli_sync():
         print("WORKER_OK")
 
 
+def cpu_cli_rank_loss():
+    """The command line on two ranks; rank 1's process ends right after its third optimizer step. Rank 0 meets the loss
+    as a failed collective, asks the heartbeats, saves what it can without a peer and leaves with status 3."""
+    import datetime
+    import json
+    from llm_distillery_b200 import cli
+    from llm_distillery_b200.models.llama import preset
+    from llm_distillery_b200.models.student import StudentModel
+    from llm_distillery_b200.utils import synthetic
+    root = sys.argv[2]
+    rank = int(os.environ["RANK"])
+    conf = {"dataset_path": os.path.join(root, "train.jsonl"), "validation_dataset_path": os.path.join(root, "val.jsonl"),
+            "teacher_models_folder": os.path.join(root, "teachers"), "student_path": os.path.join(root, "student"),
+            "context_len": 96, "crop_distr_to_size": 400, "save_topK": 20, "enable_topK": True, "device": "cpu",
+            "num_epochs": 3, "num_warmup_steps": 0, "batch_size": 2, "grad_accum_batches": 1, "lr": 1e-3,
+            "optimizer": "adamw", "data_order": "sorted", "training_precision": "fp32", "freeze_layers": [], "loss": "kl",
+            "max_cache_size_gb": 320, "cache_folder": os.path.join(root, "cache"),
+            "shard_strategy": os.environ.get("RL_STRATEGY", "ddp")}
+    if rank == 0:
+        tok = os.path.join(root, "tok")
+        synthetic.make_tokenizer(tok, 400)
+        kw = dict(vocab_size=512, hidden_size=64, intermediate_size=176, max_position_embeddings=512)
+        synthetic.make_model_dir(os.path.join(root, "teachers", "teacher_a"), preset("plumbing-teacher", **kw), tok, seed=1,
+                                 batch_size=4)
+        synthetic.make_model_dir(os.path.join(root, "student"), preset("plumbing-student", **kw), tok, seed=2)
+        synthetic.make_dataset(os.path.join(root, "train.jsonl"), 8, seed=3)
+        synthetic.make_dataset(os.path.join(root, "val.jsonl"), 2, seed=4)
+        with open(os.path.join(root, "config.json"), "w") as f:
+            json.dump(conf, f)
+    dist.init_process_group("gloo", timeout=datetime.timedelta(seconds=20))
+    dist.barrier()
+    real, count = StudentModel._optimizer_step, [0]
+
+    def step(self):
+        real(self)
+        count[0] += 1
+        if rank == 1 and count[0] == 3:       # between two steps: nothing of this rank is in flight
+            print("RANK 1 LEAVES", flush=True)
+            os._exit(0)
+    StudentModel._optimizer_step = step
+    cli.main(["--config", os.path.join(root, "config.json")])
+    print(f"rank {rank} finished the run although its peer left", flush=True)
+
+
 def cpu_cli_config3():
     """The multi-teacher cross-tokenizer configuration in small: two teachers, one with another tokenizer (mapped onto the
     student vocabulary through the byte trie), a student with tied embeddings trained with JSD on the merged targets,
@@ -819,4 +864,4 @@ if __name__ == "__main__":
      "cpu_cli_zero3": cpu_cli_zero3, "gpu_cli_zero3": gpu_cli_zero3, "cpu_cli_config3": cpu_cli_config3,
      "cpu_cli_zero3_chunked": cpu_cli_zero3_chunked, "cpu_cli_resume": cpu_cli_resume, "cpu_cli_zero3_three": cpu_cli_zero3_three,
      "cpu_cli_zero3_accum": cpu_cli_zero3_accum, "cpu_cli_zero3_variants": cpu_cli_zero3_variants,
-     "cpu_cli_sync": cpu_cli_sync}[sys.argv[1]]()
+     "cpu_cli_sync": cpu_cli_sync, "cpu_cli_rank_loss": cpu_cli_rank_loss}[sys.argv[1]]()

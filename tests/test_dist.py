@@ -56,6 +56,26 @@ def test_cpu_ranks_pipeline_variants_replicated_and_fully_sharded(tmp_path, opti
     _launch("cpu_cli_zero3_variants", 2, extra=(str(tmp_path),), env={"Z3_OPT": optimizer})
 
 
+@pytest.mark.parametrize("strategy", ["ddp", "zero3"])
+def test_cpu_ranks_lost_peer_in_the_command_line_run(tmp_path, strategy):
+    """The survivor meets the loss as a failed collective, learns from the heartbeats that a peer is gone, writes its
+    trainer state without any collective (under full sharding: its optimizer pieces with their master weights) and
+    exits with status 3."""
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(_free_port()), os.path.join(HERE, "dist_worker.py"), "cpu_cli_rank_loss", str(tmp_path)]
+    env = dict(os.environ, B200_NO_PROGRESS="1", OMP_NUM_THREADS="2", B200_HEARTBEAT_TIMEOUT="2", RL_STRATEGY=strategy)
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    log = r.stdout + r.stderr
+    assert "RANK 1 LEAVES" in log and "finished the run although" not in log, log[-3000:]
+    assert "[watchdog] rank(s) [1]" in log and "saving state and leaving" in log, log[-3000:]
+    assert "exitcode  : 3" in log or "exitcode: 3" in log, log[-3000:]
+    states = os.listdir(os.path.join(str(tmp_path), "cache", "student", "states"))
+    assert "trainer_state.json" in states
+    assert ("optimizer_state.rank0.pt" if strategy == "zero3" else "optimizer_state.pt") in states or \
+        "optimizer_state.rank0.pt" in states, states
+    assert ("model_state.pt" in states) == (strategy != "zero3")
+
+
 def test_cpu_ranks_changed_dataset_is_synced_not_recollected(tmp_path):
     _launch("cpu_cli_sync", 2, extra=(str(tmp_path),))
 
