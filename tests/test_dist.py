@@ -74,6 +74,8 @@ def test_cpu_ranks_lost_peer_in_the_command_line_run(tmp_path, strategy):
     assert ("optimizer_state.rank0.pt" if strategy == "zero3" else "optimizer_state.pt") in states or \
         "optimizer_state.rank0.pt" in states, states
     assert ("model_state.pt" in states) == (strategy != "zero3")
+    # the same command again, nobody leaves: nothing is collected a second time and the run completes
+    _launch("cpu_cli_rank_loss", 2, extra=(str(tmp_path),), env={"RL_LEAVE": "0", "RL_STRATEGY": strategy})
 
 
 def test_cpu_ranks_changed_dataset_is_synced_not_recollected(tmp_path):
