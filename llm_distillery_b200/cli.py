@@ -373,8 +373,8 @@ def main(argv=None, default_config_path: str | None = None) -> dict:
     status 3; running the same command again resumes (SHA sync for collection, trainer state for training).
 
     A peer that leaves just before a collective is usually noticed the other way round: the collective ends with an
-    error before the heartbeat record is old enough. Any exception under several ranks is therefore followed by a
-    look at the heartbeats (for as long as a record takes to go stale): if a peer is gone, the exception is its
+    error before the heartbeat record is old enough. A RuntimeError / OSError under several ranks (what collectives and
+    device-side waits raise) is therefore followed by a look at the heartbeats (for as long as a record takes to go stale): if a peer is gone, the exception is its
     consequence and the rank leaves the same way; if every peer is alive, the exception is this rank's own."""
     import time
     from .obs import watchdog
@@ -382,7 +382,7 @@ def main(argv=None, default_config_path: str | None = None) -> dict:
         return _main(argv, default_config_path)
     except watchdog.RankFailure as e:
         _leave_after_rank_failure(e)
-    except Exception as ex:  # noqa: BLE001
+    except (RuntimeError, OSError, TimeoutError) as ex:       # what a collective or a device-side wait raises
         hb = _STATE.get("heartbeat")
         if hb is None:
             raise
