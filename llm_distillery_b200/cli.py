@@ -65,15 +65,19 @@ def prepare_datasets(cfg: DistillConfig, data_manager, validation_data_manager, 
     print("Preparing datasets for the student...")
     all_not_add_bos = (not student.add_bos) and all(not t.add_bos for t in teachers)
     args = (cfg.context_len, cfg.save_sys_range, cfg.save_user_range, cfg.save_assistant_range)
+    has_val = bool(cfg.validation_dataset_path)       # the reference requires a validation set; here "" = train without one
+
+    def tokenize_val(model):
+        if not has_val:
+            return [], set()
+        return tokenize_dataset(cfg.validation_dataset_path, *args, model, cfg.ignore_model_type, all_not_add_bos)
     student.dataset, ids = tokenize_dataset(cfg.dataset_path, *args, student, cfg.ignore_model_type, all_not_add_bos)
-    student.validation_dataset, ids_val = tokenize_dataset(cfg.validation_dataset_path, *args, student,
-                                                           cfg.ignore_model_type, all_not_add_bos)
+    student.validation_dataset, ids_val = tokenize_val(student)
     t_ids, t_ids_val = set(), set()
     for t in teachers:
         print(f"Preparing datasets for {t.model_name}...")
         t.dataset, a = tokenize_dataset(cfg.dataset_path, *args, t, cfg.ignore_model_type, all_not_add_bos)
-        t.validation_dataset, b = tokenize_dataset(cfg.validation_dataset_path, *args, t, cfg.ignore_model_type,
-                                                   all_not_add_bos)
+        t.validation_dataset, b = tokenize_val(t)
         t_ids |= a
         t_ids_val |= b
     if cfg.use_teachers:

@@ -1,0 +1,90 @@
+"""The command line under many settings of its configuration keys, single process on CPU: every case collects, trains
+and validates without error; a few are checked further (full-vocabulary rows, frozen tensors, saved files)."""
+import json
+import math
+import os
+
+import numpy as np
+import pytest
+
+from llm_distillery_b200 import cli
+from llm_distillery_b200.ckpt.hf import load_hf_state_dict
+from llm_distillery_b200.data.h5store import H5Store
+from llm_distillery_b200.models.llama import preset
+from llm_distillery_b200.utils import synthetic
+
+CASES = {
+    "full distributions": {"enable_topK": False},
+    "full distributions, weighted reference loss": {"enable_topK": False, "loss": "reference"},
+    "8-bit AdamW, cosine": {"optimizer": "adamw8bit", "lr_scheduler": "cosine"},
+    "RMSprop, linear": {"optimizer": "rmsprop", "lr_scheduler": "linear"},
+    "Adagrad, constant with warm-up": {"optimizer": "adagrad", "lr_scheduler": "constant_with_warmup"},
+    "reverse KL at T = 3": {"loss": "rkl", "temperature": 3.0},
+    "JSD": {"loss": "jsd"},
+    "no validation set": {"validation_dataset_path": ""},
+    "frozen MLPs": {"freeze_layers": [".mlp."]},
+    "bf16 on CPU": {"training_precision": "bf16"},
+    "shuffled, checkpointing, accumulation of 3": {"data_order": "shuffle", "grad_checkpointing": True, "grad_accum_batches": 3},
+    "native order, context 48": {"data_order": "native", "context_len": 48},
+    "two epochs, checkpoint per epoch, final state": {"num_epochs": 2, "save_student_every_n_epochs": 1, "save_final_state": True},
+}
+
+
+@pytest.fixture(scope="module")
+def world(tmp_path_factory):
+    root = str(tmp_path_factory.mktemp("variants"))
+    os.environ["B200_NO_PROGRESS"] = "1"
+    tok = os.path.join(root, "tok")
+    synthetic.make_tokenizer(tok, 400)
+    kw = dict(vocab_size=512, hidden_size=64, intermediate_size=176, max_position_embeddings=512)
+    synthetic.make_model_dir(os.path.join(root, "teachers", "teacher_a"), preset("plumbing-teacher", **kw), tok, seed=1, batch_size=4)
+    synthetic.make_model_dir(os.path.join(root, "teachers", "teacher_b"), preset("plumbing-teacher", **kw), tok, seed=5, batch_size=3)
+    synthetic.make_model_dir(os.path.join(root, "student"), preset("plumbing-student", **kw), tok, seed=2)
+    synthetic.make_dataset(os.path.join(root, "train.jsonl"), 9, seed=3)
+    synthetic.make_dataset(os.path.join(root, "val.jsonl"), 3, seed=4)
+    base = {"dataset_path": os.path.join(root, "train.jsonl"), "validation_dataset_path": os.path.join(root, "val.jsonl"),
+            "teacher_models_folder": os.path.join(root, "teachers"), "student_path": os.path.join(root, "student"),
+            "context_len": 96, "crop_distr_to_size": 400, "save_topK": 20, "enable_topK": True, "device": "cpu",
+            "num_epochs": 1, "num_warmup_steps": 2, "batch_size": 2, "grad_accum_batches": 1, "lr": 1e-3,
+            "optimizer": "adamw", "data_order": "sorted", "training_precision": "fp32", "freeze_layers": [], "loss": "kl",
+            "max_cache_size_gb": 320}
+    return root, base
+
+
+@pytest.mark.parametrize("name", list(CASES))
+def test_cli_case(world, name):
+    root, base = world
+    cache = os.path.join(root, "cache_" + "".join(ch if ch.isalnum() else "_" for ch in name))
+    conf = dict(base, cache_folder=cache, **CASES[name])
+    path = cache + ".json"
+    with open(path, "w") as f:
+        json.dump(conf, f)
+    out = cli.main(["--config", path])
+    assert out["trained_samples"] == 9 * conf["num_epochs"] and out["tokens_collected"] > 0
+    val = out.get("last_validation") or {}
+    if conf["validation_dataset_path"]:
+        assert val and all(math.isfinite(v) for v in val.values()), val
+    else:
+        assert not val
+    st = H5Store(os.path.join(cache, "dataset"))
+    ids = st.get_dataset_ids()
+    assert len(ids) == 9
+    v, ix = st.load_id(ids[0])
+    if conf["enable_topK"]:
+        assert v.shape[1] == 20 and ix is not None and ix.max() < 400
+        assert (np.exp(v).sum(-1) <= 2.0 + 1e-2).all()                   # two teachers' probabilities summed
+    else:
+        assert v.shape[1] == 400 and ix is None                          # whole cropped distribution, no index table
+    st.close()
+    trained = os.path.join(cache, "student", "trained")
+    finals = [d for d in os.listdir(trained) if d.endswith("final")]
+    assert len(finals) == 1
+    sd, init = load_hf_state_dict(os.path.join(trained, finals[0])), load_hf_state_dict(os.path.join(root, "student"))
+    moved = {k: float((sd[k].float() - init[k].float()).abs().max()) for k in init}
+    assert max(moved.values()) > 1e-5
+    if name == "frozen MLPs":
+        assert all(m == 0.0 for k, m in moved.items() if ".mlp." in k) and any(m > 0 for k, m in moved.items() if "self_attn" in k)
+    if name.startswith("two epochs"):
+        assert len(os.listdir(trained)) == 2                              # the epoch-1 checkpoint and the final one
+        assert {"model_state.pt", "optimizer_state.pt", "scheduler_state.pt", "trainer_state.json"} <= set(
+            os.listdir(os.path.join(cache, "student", "states")))
