@@ -19,8 +19,8 @@ from ..ops import basic, topk as topk_ops
 class TeacherCollector:
     def __init__(self, model, *, topk: int, crop_to_size: int, enable_topk: bool = True, logits_chunk_bytes: int = 96 << 20):
         self.model = model
-        self.K = int(topk)
         self.vocab = min(int(crop_to_size or model.cfg.vocab_size), model.cfg.vocab_size)
+        self.K = min(int(topk), self.vocab)          # a vocabulary smaller than K: every token is kept
         self.enable_topk = bool(enable_topk)
         self.device = model.embed_tokens.device
         self.chunk_rows = max(128, (logits_chunk_bytes // (4 * self.vocab)) // 128 * 128)
@@ -130,8 +130,8 @@ class TPTeacherCollector(TeacherCollector):
             raise NotImplementedError("full-distribution storage is not offered with a tensor-parallel teacher: "
                                       "use top-K storage (enable_topK) or tp_size = 1")
         self.model = tp_model
-        self.K = int(topk)
         self.vocab = tp_model.V
+        self.K = min(int(topk), int(tp_model.V))
         self.enable_topk = True
         self.device = tp_model.device
         self.is_writer = tp_model.g.rank == 0

@@ -137,6 +137,10 @@ class DistillConfig:
             raise ValueError("comm_backend must be p2p or nccl")
         if self.context_len <= 0 or self.batch_size <= 0 or self.grad_accum_batches <= 0:
             raise ValueError("context_len, batch_size and grad_accum_batches must be positive")
+        if self.enable_topK and 0 < self.crop_distr_to_size < self.save_topK:
+            print(f"save_topK ({self.save_topK}) exceeds crop_distr_to_size ({self.crop_distr_to_size}): keeping "
+                  f"{self.crop_distr_to_size} values per token")
+            self.save_topK = int(self.crop_distr_to_size)
         if self.enable_topK and self.save_topK <= 0:
             raise ValueError("save_topK must be positive when enable_topK is set")
         if self.temperature <= 0:

@@ -26,6 +26,9 @@ CASES = {
     "bf16 on CPU": {"training_precision": "bf16"},
     "shuffled, checkpointing, accumulation of 3": {"data_order": "shuffle", "grad_checkpointing": True, "grad_accum_batches": 3},
     "native order, context 48": {"data_order": "native", "context_len": 48},
+    "top-K above the crop": {"save_topK": 600},
+    "crop and top-K above the vocabulary": {"crop_distr_to_size": 32000, "save_topK": 600},
+    "every range is content, one big batch": {"save_sys_range": True, "save_user_range": True, "batch_size": 64},
     "two epochs, checkpoint per epoch, final state": {"num_epochs": 2, "save_student_every_n_epochs": 1, "save_final_state": True},
 }
 
@@ -71,7 +74,8 @@ def test_cli_case(world, name):
     assert len(ids) == 9
     v, ix = st.load_id(ids[0])
     if conf["enable_topK"]:
-        assert v.shape[1] == 20 and ix is not None and ix.max() < 400
+        keep = min(conf["save_topK"], conf["crop_distr_to_size"], 512)      # never more values than the vocabulary has
+        assert v.shape[1] == keep and ix is not None and ix.max() < min(conf["crop_distr_to_size"], 512)
         assert (np.exp(v).sum(-1) <= 2.0 + 1e-2).all()                   # two teachers' probabilities summed
     else:
         assert v.shape[1] == 400 and ix is None                          # whole cropped distribution, no index table
