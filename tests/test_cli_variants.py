@@ -28,7 +28,8 @@ CASES = {
     "native order, context 48": {"data_order": "native", "context_len": 48},
     "top-K above the crop": {"save_topK": 600},
     "crop and top-K above the vocabulary": {"crop_distr_to_size": 32000, "save_topK": 600},
-    "every range is content, one big batch": {"save_sys_range": True, "save_user_range": True, "batch_size": 64},
+    "every range is content, one big batch": {"save_sys_range": True, "save_user_range": True, "batch_size": 64,
+                                              "num_warmup_steps": 0},      # the single step is not a warm-up step
     "two epochs, checkpoint per epoch, final state": {"num_epochs": 2, "save_student_every_n_epochs": 1, "save_final_state": True},
 }
 
