@@ -321,6 +321,8 @@ def collect(teachers, cfg, store, ids, validation, rank, world, student=None) ->
     if world % tp:
         raise ValueError(f"tp_size={tp} must divide the number of ranks ({world})")
     dp_rank, dp_world = rank // tp, world // tp
+    if int(getattr(cfg, "dp_size", 0) or 0) not in (0, dp_world):
+        raise ValueError(f"dp_size={cfg.dp_size} x tp_size={tp} does not match the {world} ranks of this run")
     if world > 1:
         target = H5Store(store.file_path.replace(".hdf5", f".rank{rank}.hdf5"))
     for t in progress(teachers, desc="Teachers", leave=False, disable=len(teachers) == 1):
