@@ -324,7 +324,10 @@ def collect(teachers, cfg, store, ids, validation, rank, world, student=None) ->
     if int(getattr(cfg, "dp_size", 0) or 0) not in (0, dp_world):
         raise ValueError(f"dp_size={cfg.dp_size} x tp_size={tp} does not match the {world} ranks of this run")
     if world > 1:
-        target = H5Store(store.file_path.replace(".hdf5", f".rank{rank}.hdf5"))
+        shard_path = store.file_path.replace(".hdf5", f".rank{rank}.hdf5")
+        if os.path.exists(shard_path):       # left behind by a run that was killed mid-collection: its rows are not
+            os.remove(shard_path)            # this run's, and folding them again would count their teachers twice
+        target = H5Store(shard_path)
     for t in progress(teachers, desc="Teachers", leave=False, disable=len(teachers) == 1):
         tp_group = _tp_group(cfg, t, rank, world, tp) if tp > 1 else None
         t.process_chunk(cfg.reserve_vram, cfg.num_inference_workers, ids_to_collect=ids, data_manager=target,
