@@ -244,15 +244,16 @@ class StudentModel(BaseModel):
         if collective and self.comm is not None:
             self.comm.barrier()
         mine = self.rank == 0 or (self.comm is not None and self.comm.shards_optimizer)
+        # an emergency save happens after a step that failed half-way: its samples were counted but never applied
+        counters = self._counters() if collective else (getattr(self, "_applied", None) or self._counters())
         if not collective and getattr(self.comm, "full_shard", False):
             # no peer to gather the weights from: this rank's optimizer shard (with its fp32 master weights) only
-            ckpt.save_trainer_state(self.paths.student_states, None, self.engine.opt, self.engine.schedule,
-                                    self._counters())
+            ckpt.save_trainer_state(self.paths.student_states, None, self.engine.opt, self.engine.schedule, counters)
             return
         with self.engine.full_parameters():
             if mine:
                 ckpt.save_trainer_state(self.paths.student_states, self.model if (self.rank == 0 or not collective) else None,
-                                        self.engine.opt, self.engine.schedule, self._counters())
+                                        self.engine.opt, self.engine.schedule, counters)
 
     def _load_state(self) -> None:
         self._load_model()
@@ -305,6 +306,7 @@ class StudentModel(BaseModel):
             self.saved_state = False
         else:
             self._load_model()
+        self._applied = self._counters()
         if self.losses is None:
             self.losses = Losses(self.logger)
         self.progress_bar = progress(total=self.total_training_steps, initial=self.num_trained_steps, desc="Training",
@@ -315,11 +317,16 @@ class StudentModel(BaseModel):
         data_list = self._prefetch_dataset_chunk(data_manager, [], full_collect, trainable_ids)
         updated = True
         if full_collect:
-            epochs_left = max(0, math.ceil((self.total_training_steps - self.num_trained_steps) / max(1, self.dataset_len)))
+            # a run taken up again in the middle of an epoch goes on where it stopped: the samples of that epoch that
+            # the saved state already counts are passed over
+            into_epoch = self.num_trained_steps % max(1, self.dataset_len) if resume else 0
+            left = self.total_training_steps - self.num_trained_steps + into_epoch
+            epochs_left = max(0, math.ceil(left / max(1, self.dataset_len)))
             for e in range(epochs_left):
                 if e + 1 < epochs_left:
                     data_list = self._prefetch_dataset_chunk(data_manager, data_list, full_collect, trainable_ids)
-                updated = self._run_distillation_cycle(data_list.pop(0), data_manager, validation_data_manager)
+                updated = self._run_distillation_cycle(data_list.pop(0), data_manager, validation_data_manager,
+                                                       skip_samples=into_epoch if e == 0 else 0)
         else:
             updated = self._run_distillation_cycle(data_list.pop(0), data_manager, validation_data_manager)
         if not updated:
@@ -383,10 +390,16 @@ class StudentModel(BaseModel):
         if self.comm is not None and hasattr(self.comm, "check"):
             self.comm.check()      # a bounded device-side wait that ran out (lost peer) surfaces here, not as a hang
 
-    def _run_distillation_cycle(self, cycle, data_manager, validation_data_manager) -> bool:
+    def _run_distillation_cycle(self, cycle, data_manager, validation_data_manager, skip_samples: int = 0) -> bool:
         batches, sizes = cycle
         updated = False
         for convos, n_samples in zip(batches, sizes):
+            if skip_samples >= n_samples > 0:        # trained before the interruption
+                skip_samples -= n_samples
+                if convos is not None:
+                    data_manager.read_next_batch()   # its rows were queued with the rest of the epoch: drop them
+                continue
+            skip_samples = 0
             updated = False
             hbt = getattr(self, "heartbeat", None)
             if hbt is not None:      # between steps, nothing in flight: learn about a lost peer BEFORE the next launch
@@ -410,6 +423,7 @@ class StudentModel(BaseModel):
                 self._optimizer_step()
                 updated = True
                 self.next_accum_step += self.eff_batch_size
+                self._applied = self._counters()     # what an emergency save may claim: nothing beyond this step
             if self.num_trained_steps >= self.next_save_step and self.num_trained_steps < self.total_training_steps:
                 self._save_model(self.num_trained_steps)
                 self.next_save_step += self.save_every_steps

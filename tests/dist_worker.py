@@ -688,7 +688,7 @@ def cpu_cli_sync():
 
 
 def cpu_cli_rank_loss():
-    """The command line on two ranks; rank 1's process ends right after its third optimizer step. Rank 0 meets the loss
+    """The command line on two ranks; rank 1's process ends right after its second optimizer step. Rank 0 meets the loss
     as a failed collective, asks the heartbeats, saves what it can without a peer and leaves with status 3."""
     import datetime
     import json
@@ -701,9 +701,9 @@ def cpu_cli_rank_loss():
     conf = {"dataset_path": os.path.join(root, "train.jsonl"), "validation_dataset_path": os.path.join(root, "val.jsonl"),
             "teacher_models_folder": os.path.join(root, "teachers"), "student_path": os.path.join(root, "student"),
             "context_len": 96, "crop_distr_to_size": 400, "save_topK": 20, "enable_topK": True, "device": "cpu",
-            "num_epochs": 3, "num_warmup_steps": 0, "batch_size": 2, "grad_accum_batches": 1, "lr": 1e-3,
+            "num_epochs": 2, "num_warmup_steps": 0, "batch_size": 2, "grad_accum_batches": 1, "lr": 1e-3,
             "optimizer": "adamw", "data_order": "sorted", "training_precision": "fp32", "freeze_layers": [], "loss": "kl",
-            "max_cache_size_gb": 320, "cache_folder": os.path.join(root, "cache"),
+            "max_cache_size_gb": 320, "cache_folder": os.path.join(root, os.environ.get("RL_CACHE", "cache")),
             "shard_strategy": os.environ.get("RL_STRATEGY", "ddp")}
     if rank == 0:
         tok = os.path.join(root, "tok")
@@ -714,6 +714,7 @@ def cpu_cli_rank_loss():
         synthetic.make_model_dir(os.path.join(root, "student"), preset("plumbing-student", **kw), tok, seed=2)
         synthetic.make_dataset(os.path.join(root, "train.jsonl"), 8, seed=3)
         synthetic.make_dataset(os.path.join(root, "val.jsonl"), 2, seed=4)
+    if rank == 0:
         with open(os.path.join(root, "config.json"), "w") as f:
             json.dump(conf, f)
     dist.init_process_group("gloo", timeout=datetime.timedelta(seconds=20))
@@ -723,7 +724,7 @@ def cpu_cli_rank_loss():
     def step(self):
         real(self)
         count[0] += 1
-        if rank == 1 and count[0] == 3 and os.environ.get("RL_LEAVE", "1") == "1":   # between two steps: nothing in flight
+        if rank == 1 and count[0] == int(os.environ.get("RL_AT", "2")) and os.environ.get("RL_LEAVE", "1") == "1":   # between two steps: nothing in flight
             print("RANK 1 LEAVES", flush=True)
             os._exit(0)
     StudentModel._optimizer_step = step
@@ -731,7 +732,9 @@ def cpu_cli_rank_loss():
     if os.environ.get("RL_LEAVE", "1") == "1":
         print(f"rank {rank} finished the run although its peer left", flush=True)
     else:
-        assert out["trained_samples"] == 24 and out["tokens_collected"] == 0, out     # the cache is reused as it is
+        assert out["trained_samples"] == 16, out
+        if "RL_CACHE" not in os.environ:
+            assert out["tokens_collected"] == 0, out                                  # the cache is reused as it is
         if rank == 0:
             print("WORKER_OK")
 

@@ -60,22 +60,40 @@ def test_cpu_ranks_pipeline_variants_replicated_and_fully_sharded(tmp_path, opti
 def test_cpu_ranks_lost_peer_in_the_command_line_run(tmp_path, strategy):
     """The survivor meets the loss as a failed collective, learns from the heartbeats that a peer is gone, writes its
     trainer state without any collective (under full sharding: its optimizer pieces with their master weights) and
-    exits with status 3."""
+    exits with status 3. Replicated case, peer lost in the middle of the second epoch: the same command again takes
+    the state up, passes over the samples it already counts, and ends where an undisturbed run ends."""
+    at = "3" if strategy == "ddp" else "2"
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
            "--master-port", str(_free_port()), os.path.join(HERE, "dist_worker.py"), "cpu_cli_rank_loss", str(tmp_path)]
-    env = dict(os.environ, B200_NO_PROGRESS="1", OMP_NUM_THREADS="2", B200_HEARTBEAT_TIMEOUT="2", RL_STRATEGY=strategy)
+    env = dict(os.environ, B200_NO_PROGRESS="1", OMP_NUM_THREADS="2", B200_HEARTBEAT_TIMEOUT="2", RL_STRATEGY=strategy,
+               RL_AT=at)
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     log = r.stdout + r.stderr
     assert "RANK 1 LEAVES" in log and "finished the run although" not in log, log[-3000:]
     assert "[watchdog] rank(s) [1]" in log and "saving state and leaving" in log, log[-3000:]
     assert "exitcode  : 3" in log or "exitcode: 3" in log, log[-3000:]
-    states = os.listdir(os.path.join(str(tmp_path), "cache", "student", "states"))
+    states_dir = os.path.join(str(tmp_path), "cache", "student", "states")
+    states = os.listdir(states_dir)
     assert "trainer_state.json" in states
-    assert ("optimizer_state.rank0.pt" if strategy == "zero3" else "optimizer_state.pt") in states or \
-        "optimizer_state.rank0.pt" in states, states
+    assert ("optimizer_state.rank0.pt" if strategy == "zero3" else "optimizer_state.pt") in states, states
     assert ("model_state.pt" in states) == (strategy != "zero3")
-    # the same command again, nobody leaves: nothing is collected a second time and the run completes
+    import json
+    with open(os.path.join(states_dir, "trainer_state.json")) as f:
+        counted = json.load(f)["num_trained_steps"]
+    assert counted == 4 * int(at)            # four samples per step; the step that failed is not claimed
+    if strategy != "ddp":
+        return
     _launch("cpu_cli_rank_loss", 2, extra=(str(tmp_path),), env={"RL_LEAVE": "0", "RL_STRATEGY": strategy})
+    _launch("cpu_cli_rank_loss", 2, extra=(str(tmp_path),), env={"RL_LEAVE": "0", "RL_STRATEGY": strategy,
+                                                                  "RL_CACHE": "cache_whole"})
+    from llm_distillery_b200.ckpt.hf import load_hf_state_dict
+
+    def final(cache):
+        base = os.path.join(str(tmp_path), cache, "student", "trained")
+        return load_hf_state_dict(os.path.join(base, [d for d in os.listdir(base) if d.endswith("final")][0]))
+    taken_up, whole = final("cache"), final("cache_whole")
+    for k, v in whole.items():
+        assert (v.float() - taken_up[k].float()).abs().max().item() < 1e-5, k
 
 
 def test_cpu_ranks_changed_dataset_is_synced_not_recollected(tmp_path):
