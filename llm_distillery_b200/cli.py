@@ -164,6 +164,15 @@ def check_topk(data_manager, enable_topk: bool, save_topk: int, validation: bool
 
 
 def handle_termination(signum, frame) -> None:
+    student = _STATE.get("student")
+    if (signum is not None and student is not None and getattr(student, "training_active", False)
+            and not getattr(student, "stop_requested", False)):
+        # in the middle of training: finish the step, save the trainer state (all ranks together), then leave; a
+        # second signal ends the process at once
+        student.stop_requested = True
+        print("\nStop requested: the run ends after the current step with its state saved "
+              "(signal again to end it at once).", flush=True)
+        return
     print("\nTerminating the script...")
     for key in ("data_manager", "validation_data_manager"):
         dm = _STATE.get(key)
@@ -387,8 +396,14 @@ def main(argv=None, default_config_path: str | None = None) -> dict:
     consequence and the rank leaves the same way; if every peer is alive, the exception is this rank's own."""
     import time
     from .obs import watchdog
+    from .models.student import StopRequested
     try:
         return _main(argv, default_config_path)
+    except StopRequested:
+        student = _STATE.get("student")
+        summary = {"stopped": True, "trained_samples": getattr(student, "num_trained_steps", 0)}
+        handle_termination(None, None)
+        return summary
     except watchdog.RankFailure as e:
         _leave_after_rank_failure(e)
     except (RuntimeError, OSError, TimeoutError) as ex:       # what a collective or a device-side wait raises

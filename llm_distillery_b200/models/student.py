@@ -29,6 +29,10 @@ from ..obs.metrics import Losses, MetricsLogger
 from .base_model import BaseModel
 
 
+class StopRequested(Exception):
+    """Raised out of the training loop after the trainer state has been saved on a stop request (SIGTERM / SIGINT)."""
+
+
 class StudentModel(BaseModel):
     def __init__(self, model_path: str, paths, add_bos: bool, prompt_format: dict, batch_size: int,
                  interactive: bool = False):
@@ -307,6 +311,7 @@ class StudentModel(BaseModel):
         else:
             self._load_model()
         self._applied = self._counters()
+        self.training_active = True
         if self.losses is None:
             self.losses = Losses(self.logger)
         self.progress_bar = progress(total=self.total_training_steps, initial=self.num_trained_steps, desc="Training",
@@ -341,7 +346,22 @@ class StudentModel(BaseModel):
                 self._save_state()
                 self.saved_state = True
         self.progress_bar.close()
+        self.training_active = False
         self._unload_model()
+
+    def _stop_agreed(self) -> bool:
+        """A stop request (``stop_requested``, set by the signal handler) reaches the ranks at different moments: they
+        agree after an optimizer step - a tiny MAX all-reduce - so that all of them save and leave at the same step."""
+        mine = bool(getattr(self, "stop_requested", False))
+        if self.world <= 1:
+            return mine
+        import torch.distributed as dist
+        if not dist.is_initialized():
+            return mine
+        dev = self.engine.device if dist.get_backend() == "nccl" else "cpu"
+        t = torch.tensor([1.0 if mine else 0.0], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return bool(t.item() > 0)
 
     def _phase_times(self) -> tuple[dict, dict]:
         """(this rank's device-timed phases since the last step, cross-rank figures). With tracing on, every rank
@@ -424,6 +444,11 @@ class StudentModel(BaseModel):
                 updated = True
                 self.next_accum_step += self.eff_batch_size
                 self._applied = self._counters()     # what an emergency save may claim: nothing beyond this step
+                if self._stop_agreed() and self.num_trained_steps < self.total_training_steps:
+                    print("Stop requested: saving the trainer state; the same command takes the run up again.", flush=True)
+                    self._save_state()
+                    self.training_active = False
+                    raise StopRequested()
             if self.num_trained_steps >= self.next_save_step and self.num_trained_steps < self.total_training_steps:
                 self._save_model(self.num_trained_steps)
                 self.next_save_step += self.save_every_steps

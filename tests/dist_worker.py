@@ -725,10 +725,20 @@ def cpu_cli_rank_loss():
         real(self)
         count[0] += 1
         if rank == 1 and count[0] == int(os.environ.get("RL_AT", "2")) and os.environ.get("RL_LEAVE", "1") == "1":   # between two steps: nothing in flight
+            if os.environ.get("RL_MODE") == "stop":      # a stop request that reaches only this rank (yet)
+                import signal
+                cli.handle_termination(signal.SIGTERM, None)
+                return
             print("RANK 1 LEAVES", flush=True)
             os._exit(0)
     StudentModel._optimizer_step = step
     out = cli.main(["--config", os.path.join(root, "config.json")])
+    if os.environ.get("RL_MODE") == "stop" and os.environ.get("RL_LEAVE", "1") == "1":
+        assert out == {"stopped": True, "trained_samples": 4 * int(os.environ.get("RL_AT", "2"))}, out
+        dist.barrier()
+        if rank == 0:
+            print("WORKER_OK")
+        return
     if os.environ.get("RL_LEAVE", "1") == "1":
         print(f"rank {rank} finished the run although its peer left", flush=True)
     else:

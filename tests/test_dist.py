@@ -96,6 +96,23 @@ def test_cpu_ranks_lost_peer_in_the_command_line_run(tmp_path, strategy):
         assert (v.float() - taken_up[k].float()).abs().max().item() < 1e-5, k
 
 
+def test_cpu_ranks_stop_request_at_one_rank_stops_all_and_the_run_resumes(tmp_path):
+    """SIGTERM reaches rank 1 during its third step of a fully sharded run: after the next step both ranks agree, save
+    the state together (weights through the gathered view) and return; the rerun ends like an undisturbed run."""
+    env = {"RL_STRATEGY": "zero3", "RL_MODE": "stop", "RL_AT": "3"}
+    _launch("cpu_cli_rank_loss", 2, extra=(str(tmp_path),), env=env)
+    _launch("cpu_cli_rank_loss", 2, extra=(str(tmp_path),), env=dict(env, RL_LEAVE="0"))
+    _launch("cpu_cli_rank_loss", 2, extra=(str(tmp_path),), env=dict(env, RL_LEAVE="0", RL_CACHE="cache_whole"))
+    from llm_distillery_b200.ckpt.hf import load_hf_state_dict
+
+    def final(cache):
+        base = os.path.join(str(tmp_path), cache, "student", "trained")
+        return load_hf_state_dict(os.path.join(base, [d for d in os.listdir(base) if d.endswith("final")][0]))
+    taken_up, whole = final("cache"), final("cache_whole")
+    for k, v in whole.items():
+        assert (v.float() - taken_up[k].float()).abs().max().item() < 1e-5, k
+
+
 def test_cpu_ranks_changed_dataset_is_synced_not_recollected(tmp_path):
     _launch("cpu_cli_sync", 2, extra=(str(tmp_path),))
 

@@ -90,3 +90,57 @@ def test_chunked_mode_and_dataset_edit(workspace):
                     "--cache_folder", str(workspace / "cache_chunked")])
     assert out["trained_samples"] == 23
     assert os.path.exists(workspace / "cache_chunked" / "student" / "states" / "trainer_state.json")
+
+
+def test_stop_request_saves_state_and_the_rerun_ends_like_an_undisturbed_run(tmp_path, monkeypatch):
+    """SIGTERM in the middle of training: the step is finished, the trainer state saved, the command returns; the same
+    command again takes the run up in the middle of its epoch and ends with the weights of a run that was never
+    stopped. A signal outside training still ends the process the old way (not exercised here)."""
+    import json
+    import signal
+    from llm_distillery_b200 import cli
+    from llm_distillery_b200.ckpt.hf import load_hf_state_dict
+    from llm_distillery_b200.models.llama import preset
+    from llm_distillery_b200.models.student import StudentModel
+    from llm_distillery_b200.utils import synthetic
+    monkeypatch.setenv("B200_NO_PROGRESS", "1")
+    root = str(tmp_path)
+    tok = os.path.join(root, "tok")
+    synthetic.make_tokenizer(tok, 400)
+    kw = dict(vocab_size=512, hidden_size=64, intermediate_size=176, max_position_embeddings=512)
+    synthetic.make_model_dir(os.path.join(root, "teachers", "teacher_a"), preset("plumbing-teacher", **kw), tok, seed=1, batch_size=4)
+    synthetic.make_model_dir(os.path.join(root, "student"), preset("plumbing-student", **kw), tok, seed=2)
+    synthetic.make_dataset(os.path.join(root, "train.jsonl"), 8, seed=3)
+    synthetic.make_dataset(os.path.join(root, "val.jsonl"), 2, seed=4)
+    conf = {"dataset_path": os.path.join(root, "train.jsonl"), "validation_dataset_path": os.path.join(root, "val.jsonl"),
+            "teacher_models_folder": os.path.join(root, "teachers"), "student_path": os.path.join(root, "student"),
+            "context_len": 96, "crop_distr_to_size": 400, "save_topK": 20, "enable_topK": True, "device": "cpu",
+            "num_epochs": 2, "num_warmup_steps": 4, "batch_size": 2, "grad_accum_batches": 1, "lr": 1e-3,
+            "optimizer": "adamw", "data_order": "sorted", "training_precision": "fp32", "freeze_layers": [], "loss": "kl"}
+    for name in ("stopped", "whole"):
+        with open(os.path.join(root, f"{name}.json"), "w") as f:
+            json.dump(dict(conf, cache_folder=os.path.join(root, "cache_" + name)), f)
+    real, count = StudentModel._optimizer_step, [0]
+
+    def step(self):
+        real(self)
+        count[0] += 1
+        if count[0] == 5:                       # the signal arrives during the fifth of eight steps (second epoch)
+            cli.handle_termination(signal.SIGTERM, None)
+    monkeypatch.setattr(StudentModel, "_optimizer_step", step)
+    out = cli.main(["--config", os.path.join(root, "stopped.json")])
+    assert out == {"stopped": True, "trained_samples": 10}
+    states = os.listdir(os.path.join(root, "cache_stopped", "student", "states"))
+    assert {"model_state.pt", "optimizer_state.pt", "trainer_state.json"} <= set(states)
+    monkeypatch.setattr(StudentModel, "_optimizer_step", real)
+    out = cli.main(["--config", os.path.join(root, "stopped.json")])
+    assert out["trained_samples"] == 16 and out["tokens_collected"] == 0
+    out = cli.main(["--config", os.path.join(root, "whole.json")])
+    assert out["trained_samples"] == 16
+
+    def final(cache):
+        base = os.path.join(root, cache, "student", "trained")
+        return load_hf_state_dict(os.path.join(base, [d for d in os.listdir(base) if d.endswith("final")][0]))
+    a, b = final("cache_stopped"), final("cache_whole")
+    for k in b:
+        assert (a[k].float() - b[k].float()).abs().max().item() < 1e-6, k
