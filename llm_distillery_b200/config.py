@@ -224,7 +224,8 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--loss", type=str, help="reference | kl | rkl | jsd")
     g.add_argument("--tp_size", type=int, help="tensor-parallel width of the teachers; 0 = smallest width that fits 180 GB per GPU")
     g.add_argument("--dp_size", type=int, help="data-parallel replicas of the teacher; 0 = ranks / tp_size")
-    g.add_argument("--shard_strategy", type=str, help="student sharding: ddp (replicated weights) | fsdp (optimizer state sharded) | zero3 (weights, gradients and state sharded) | auto (first plan that fits 180 GB per GPU)")")
+    g.add_argument("--shard_strategy", type=str, help="student sharding: ddp (replicated weights) | fsdp (optimizer state sharded) | "
+                   "zero3 (weights, gradients and state sharded) | auto (first plan that fits 180 GB per GPU)")
     g.add_argument("--comm_backend", type=str, help="p2p (NVLink peer-access kernels) | nccl (library collectives)")
     g.add_argument("--cross_tokenizer", type=str2bool)
     g.add_argument("--seed", type=int)
