@@ -144,3 +144,58 @@ def test_stop_request_saves_state_and_the_rerun_ends_like_an_undisturbed_run(tmp
     a, b = final("cache_stopped"), final("cache_whole")
     for k in b:
         assert (a[k].float() - b[k].float()).abs().max().item() < 1e-6, k
+
+
+def test_collection_killed_half_way_is_continued_not_repeated(tmp_path, monkeypatch):
+    """The process dies during collection (here: an exception out of the third batch). What had reached the HDF5 file
+    stays; the same command again collects only the conversations that are missing and the store equals a fresh one."""
+    import json
+    from llm_distillery_b200 import cli
+    from llm_distillery_b200.collect.collector import TeacherCollector
+    from llm_distillery_b200.models.llama import preset
+    from llm_distillery_b200.utils import synthetic
+    monkeypatch.setenv("B200_NO_PROGRESS", "1")
+    root = str(tmp_path)
+    tok = os.path.join(root, "tok")
+    synthetic.make_tokenizer(tok, 400)
+    kw = dict(vocab_size=512, hidden_size=64, intermediate_size=176, max_position_embeddings=512)
+    synthetic.make_model_dir(os.path.join(root, "teachers", "teacher_a"), preset("plumbing-teacher", **kw), tok, seed=1, batch_size=2)
+    synthetic.make_model_dir(os.path.join(root, "student"), preset("plumbing-student", **kw), tok, seed=2)
+    synthetic.make_dataset(os.path.join(root, "train.jsonl"), 10, seed=3)
+    synthetic.make_dataset(os.path.join(root, "val.jsonl"), 2, seed=4)
+    conf = {"dataset_path": os.path.join(root, "train.jsonl"), "validation_dataset_path": os.path.join(root, "val.jsonl"),
+            "teacher_models_folder": os.path.join(root, "teachers"), "student_path": os.path.join(root, "student"),
+            "context_len": 96, "crop_distr_to_size": 400, "save_topK": 20, "enable_topK": True, "device": "cpu",
+            "num_epochs": 1, "num_warmup_steps": 0, "batch_size": 2, "grad_accum_batches": 1, "lr": 1e-3,
+            "optimizer": "adamw", "data_order": "sorted", "training_precision": "fp32", "freeze_layers": [], "loss": "kl"}
+    for name in ("killed", "fresh"):
+        with open(os.path.join(root, f"{name}.json"), "w") as f:
+            json.dump(dict(conf, cache_folder=os.path.join(root, "cache_" + name)), f)
+    real, calls = TeacherCollector.collect_batch, [0]
+
+    def dying(self, *a, **k):
+        calls[0] += 1
+        if calls[0] == 4:          # the validation batch and two training batches are through
+            raise KeyboardInterrupt("killed")
+        return real(self, *a, **k)
+    monkeypatch.setattr(TeacherCollector, "collect_batch", dying)
+    with pytest.raises(KeyboardInterrupt):
+        cli.main(["--config", os.path.join(root, "killed.json")])
+    cli.handle_termination(None, None)                       # what the signal handler does on the way out
+    monkeypatch.setattr(TeacherCollector, "collect_batch", real)
+    partial = H5Store(os.path.join(root, "cache_killed", "dataset"))
+    have = len(partial.get_dataset_ids())
+    partial.close()
+    assert 0 < have < 10
+    out = cli.main(["--config", os.path.join(root, "killed.json")])
+    fresh = cli.main(["--config", os.path.join(root, "fresh.json")])
+    assert out["trained_samples"] == fresh["trained_samples"] == 10
+    assert 0 < out["tokens_collected"] < fresh["tokens_collected"]
+    a, b = H5Store(os.path.join(root, "cache_killed", "dataset")), H5Store(os.path.join(root, "cache_fresh", "dataset"))
+    assert sorted(a.get_dataset_ids()) == sorted(b.get_dataset_ids()) == list(range(10))
+    for cid in range(10):
+        va, ia = a.load_id(cid)
+        vb, ib = b.load_id(cid)
+        assert a.get_sha(cid) == b.get_sha(cid) and np.array_equal(va, vb) and np.array_equal(ia, ib)
+    a.close()
+    b.close()
