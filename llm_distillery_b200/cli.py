@@ -337,11 +337,23 @@ def collect(teachers, cfg, store, ids, validation, rank, world, student=None) ->
         if os.path.exists(shard_path):       # left behind by a run that was killed mid-collection: its rows are not
             os.remove(shard_path)            # this run's, and folding them again would count their teachers twice
         target = H5Store(shard_path)
-    for t in progress(teachers, desc="Teachers", leave=False, disable=len(teachers) == 1):
+    from .data.convo import PARTIAL_SHA_PREFIX
+    for k, t in enumerate(progress(teachers, desc="Teachers", leave=False, disable=len(teachers) == 1)):
         tp_group = _tp_group(cfg, t, rank, world, tp) if tp > 1 else None
         t.process_chunk(cfg.reserve_vram, cfg.num_inference_workers, ids_to_collect=ids, data_manager=target,
-                        validation=validation, rank=dp_rank, world=dp_world, sha_by_id=shas, tp_group=tp_group)
+                        validation=validation, rank=dp_rank, world=dp_world, sha_by_id=shas, tp_group=tp_group,
+                        last_teacher=(k + 1 == len(teachers)))
         t.unload()
+
+    def finalize(st) -> None:
+        """Every teacher is through: a conversation the last teacher had no rows for still carries the mark."""
+        marked = {cid: sha[len(PARTIAL_SHA_PREFIX):] for cid, sha in st.get_available_shas().items()
+                  if sha.startswith(PARTIAL_SHA_PREFIX)}
+        if marked:
+            st.update_shas(marked)
+            st.flush()
+    if world == 1:
+        finalize(store)
     if world > 1:
         import torch.distributed as dist
         target.close()
@@ -354,7 +366,10 @@ def collect(teachers, cfg, store, ids, validation, rank, world, student=None) ->
                 shard = H5Store(shard_path)
                 for cid in shard.get_dataset_ids():
                     v, ix = shard.load_id(cid)
-                    rows = [TeacherRows(cid, v, ix, shard.get_sha(cid) or "", shard._attr(cid, "sample") or "")]
+                    sha = shard.get_sha(cid) or ""
+                    if sha.startswith(PARTIAL_SHA_PREFIX):     # all teachers are through by now: the mark comes off
+                        sha = sha[len(PARTIAL_SHA_PREFIX):]
+                    rows = [TeacherRows(cid, v, ix, sha, shard._attr(cid, "sample") or "")]
                     # teachers batch the conversations differently, so one conversation can sit in several ranks' files,
                     # each holding other teachers' rows: the first one replaces what the main file had, the others merge
                     (store.write_batch if cid in seen else store.update_batch)(rows)

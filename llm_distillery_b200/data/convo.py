@@ -77,3 +77,10 @@ class TeacherRows:
     content_sha: str = ""
     sample: str = ""
     meta: dict = field(default_factory=dict)
+
+
+# Rows of a teacher that is not the last one of the run are stored under a marked SHA: the conversation only counts as
+# collected (its SHA equals the dataset's) once the last teacher has merged its rows. A run killed between two teachers
+# leaves marked conversations, which the next run's sync sees as changed and collects again from the first teacher on.
+PARTIAL_SHA_PREFIX = "partial:"
+

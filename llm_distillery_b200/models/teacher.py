@@ -20,6 +20,7 @@ import torch
 
 from ..ckpt.hf import load_hf_model
 from ..collect.collector import TeacherCollector
+from ..data.convo import PARTIAL_SHA_PREFIX
 from ..obs.console import progress
 from .base_model import BaseModel
 
@@ -79,7 +80,7 @@ class TeacherModel(BaseModel):
 
     def process_chunk(self, reserve_vram_gb=None, num_inference_workers: int = 1, ids_to_collect=None,
                       data_manager=None, validation: bool = False, rank: int = 0, world: int = 1,
-                      sha_by_id: dict | None = None, tp_group=None) -> int:
+                      sha_by_id: dict | None = None, tp_group=None, last_teacher: bool = True) -> int:
         """Collect ``ids_to_collect`` into ``data_manager``. Returns the number of conversations written.
         ``rank`` / ``world`` index the data-parallel replicas (each takes a strided share of the batches); with
         ``tp_group`` the replica is a tensor-parallel group whose ranks all call this with the same arguments."""
@@ -111,6 +112,9 @@ class TeacherModel(BaseModel):
                 if sha_by_id:   # the store is keyed by the STUDENT's view of the text (that is what sync compares)
                     for r in rows:
                         r.content_sha = sha_by_id.get(r.convo_id, r.content_sha)
+                if not last_teacher:     # more teachers follow: the conversation is not complete yet (data/convo.py)
+                    for r in rows:
+                        r.content_sha = PARTIAL_SHA_PREFIX + (r.content_sha or "")
                 data_manager.write_batch(rows)          # asynchronous: compression + file IO overlap the next batch
                 self.tokens_collected += int(sum(c.length for c in convos))
                 done += len(rows)

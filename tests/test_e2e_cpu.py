@@ -146,9 +146,12 @@ def test_stop_request_saves_state_and_the_rerun_ends_like_an_undisturbed_run(tmp
         assert (a[k].float() - b[k].float()).abs().max().item() < 1e-6, k
 
 
-def test_collection_killed_half_way_is_continued_not_repeated(tmp_path, monkeypatch):
+@pytest.mark.parametrize("teachers,kill_at", [(1, 4), (2, 10)])
+def test_collection_killed_half_way_is_continued_not_repeated(tmp_path, monkeypatch, teachers, kill_at):
     """The process dies during collection (here: an exception out of the third batch). What had reached the HDF5 file
-    stays; the same command again collects only the conversations that are missing and the store equals a fresh one."""
+    stays; the same command again collects only the conversations that are missing and the store equals a fresh one.
+    With two teachers the kill comes while the SECOND is merging: the conversations it had not reached carry the first
+    teacher's rows under a marked SHA, are seen as changed by the next run and collected again by both teachers."""
     import json
     from llm_distillery_b200 import cli
     from llm_distillery_b200.collect.collector import TeacherCollector
@@ -160,6 +163,9 @@ def test_collection_killed_half_way_is_continued_not_repeated(tmp_path, monkeypa
     synthetic.make_tokenizer(tok, 400)
     kw = dict(vocab_size=512, hidden_size=64, intermediate_size=176, max_position_embeddings=512)
     synthetic.make_model_dir(os.path.join(root, "teachers", "teacher_a"), preset("plumbing-teacher", **kw), tok, seed=1, batch_size=2)
+    if teachers == 2:
+        synthetic.make_model_dir(os.path.join(root, "teachers", "teacher_b"), preset("plumbing-teacher", **kw), tok, seed=7,
+                                 batch_size=2)
     synthetic.make_model_dir(os.path.join(root, "student"), preset("plumbing-student", **kw), tok, seed=2)
     synthetic.make_dataset(os.path.join(root, "train.jsonl"), 10, seed=3)
     synthetic.make_dataset(os.path.join(root, "val.jsonl"), 2, seed=4)
@@ -175,7 +181,8 @@ def test_collection_killed_half_way_is_continued_not_repeated(tmp_path, monkeypa
 
     def dying(self, *a, **k):
         calls[0] += 1
-        if calls[0] == 4:          # the validation batch and two training batches are through
+        if calls[0] == kill_at:    # one teacher: validation batch + two training batches are through; two teachers:
+            # both validation batches, the first teacher's five batches and two of the second teacher's
             raise KeyboardInterrupt("killed")
         return real(self, *a, **k)
     monkeypatch.setattr(TeacherCollector, "collect_batch", dying)
@@ -186,7 +193,13 @@ def test_collection_killed_half_way_is_continued_not_repeated(tmp_path, monkeypa
     partial = H5Store(os.path.join(root, "cache_killed", "dataset"))
     have = len(partial.get_dataset_ids())
     partial.close()
-    assert 0 < have < 10
+    assert (0 < have < 10) if teachers == 1 else have == 10
+    if teachers == 2:
+        from llm_distillery_b200.data.convo import PARTIAL_SHA_PREFIX
+        partial = H5Store(os.path.join(root, "cache_killed", "dataset"))
+        marked = [c for c, sha in partial.get_available_shas().items() if sha.startswith(PARTIAL_SHA_PREFIX)]
+        partial.close()
+        assert len(marked) == 6                               # four conversations got the second teacher's rows
     out = cli.main(["--config", os.path.join(root, "killed.json")])
     fresh = cli.main(["--config", os.path.join(root, "fresh.json")])
     assert out["trained_samples"] == fresh["trained_samples"] == 10
@@ -196,6 +209,6 @@ def test_collection_killed_half_way_is_continued_not_repeated(tmp_path, monkeypa
     for cid in range(10):
         va, ia = a.load_id(cid)
         vb, ib = b.load_id(cid)
-        assert a.get_sha(cid) == b.get_sha(cid) and np.array_equal(va, vb) and np.array_equal(ia, ib)
+        assert a.get_sha(cid) == b.get_sha(cid) and np.array_equal(va, vb) and np.array_equal(ia, ib), cid
     a.close()
     b.close()
