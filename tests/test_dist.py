@@ -61,7 +61,8 @@ def test_cpu_ranks_lost_peer_in_the_command_line_run(tmp_path, strategy):
     """The survivor meets the loss as a failed collective, learns from the heartbeats that a peer is gone, writes its
     trainer state without any collective (under full sharding: its optimizer pieces with their master weights) and
     exits with status 3. Replicated case, peer lost in the middle of the second epoch: the same command again takes
-    the state up, passes over the samples it already counts, and ends where an undisturbed run ends."""
+    the state up, passes over the samples it already counts and completes the run (that a run taken up in the middle of
+    an epoch ends with the weights of an undisturbed one is checked in tests/test_e2e_cpu.py)."""
     at = "3" if strategy == "ddp" else "2"
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
            "--master-port", str(_free_port()), os.path.join(HERE, "dist_worker.py"), "cpu_cli_rank_loss", str(tmp_path)]
@@ -84,16 +85,6 @@ def test_cpu_ranks_lost_peer_in_the_command_line_run(tmp_path, strategy):
     if strategy != "ddp":
         return
     _launch("cpu_cli_rank_loss", 2, extra=(str(tmp_path),), env={"RL_LEAVE": "0", "RL_STRATEGY": strategy})
-    _launch("cpu_cli_rank_loss", 2, extra=(str(tmp_path),), env={"RL_LEAVE": "0", "RL_STRATEGY": strategy,
-                                                                  "RL_CACHE": "cache_whole"})
-    from llm_distillery_b200.ckpt.hf import load_hf_state_dict
-
-    def final(cache):
-        base = os.path.join(str(tmp_path), cache, "student", "trained")
-        return load_hf_state_dict(os.path.join(base, [d for d in os.listdir(base) if d.endswith("final")][0]))
-    taken_up, whole = final("cache"), final("cache_whole")
-    for k, v in whole.items():
-        assert (v.float() - taken_up[k].float()).abs().max().item() < 1e-5, k
 
 
 def test_cpu_ranks_stop_request_at_one_rank_stops_all_and_the_run_resumes(tmp_path):
