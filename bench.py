@@ -9,8 +9,8 @@ over N GPUs of one node (weak scaling) - on synthetic token data and random-init
 
 Prints ONE JSON line from rank 0. ``value`` is device-timed (CUDA events, max over ranks) with the step's inputs
 already on the device; ``e2e`` repeats the measurement through the public per-step API with the inputs copied
-from pinned host memory and the loss read back every step. ``--impl reference`` reports the reference arm
-(unavailable on this image: see the printed reason); ``--impl baseline`` runs the reference's op sequence on the
+from pinned host memory and the loss read back every step. ``--impl reference`` runs the unmodified reference tree
+from ``baseline/_ref`` through its own ``StudentModel.train_chunk`` (``baseline/reference_arm.py``); ``--impl baseline`` runs the reference's op sequence on the
 libraries that are installed (HF Llama on cuBLAS/SDPA, full fp32 logits, torch AdamW, NCCL DDP).
 """
 from __future__ import annotations
@@ -101,23 +101,10 @@ class ClockSampler:
 
 
 def reference_arm(args) -> int:
-    """The unmodified reference cannot run on this image: it is not an installable package (no setup.py /
-    pyproject.toml) and its stock code path imports exllamav2, bitsandbytes, h5py and accelerate, none of which is
-    installed or present in the offline wheelhouse."""
-    why = ("reference is not pip-installable (no setup.py/pyproject.toml) and its stock path needs exllamav2, "
-           "bitsandbytes, h5py, accelerate, which are absent from the image and the offline wheelhouse")
-    ref_dir = os.path.join(ROOT, "baseline", "_ref")
-    try:
-        if os.path.exists(os.path.join(ref_dir, "collect_and_finetune.py")):
-            sys.path.insert(0, ref_dir)
-            import importlib
-            importlib.import_module("classes.student.model")  # raises on the first missing dependency
-            why = "reference imported but no GPU-free teacher/HDF5 stack exists to drive StudentModel.train_chunk"
-    except Exception as e:  # noqa: BLE001
-        why = f"reference import failed: {type(e).__name__}: {e}".replace("\n", " ")[:300]
-    if int(os.environ.get("RANK", "0")) == 0:
-        print(json.dumps({"impl": "reference", "unavailable": why}))
-    return 0
+    """Runs the unmodified reference tree kept under ``baseline/_ref`` (``baseline/reference_arm.py`` says what stands
+    in for the packages this image lacks), or prints the ``unavailable`` line when that cannot be done."""
+    from baseline import reference_arm as ra
+    return ra.run(args, ClockSampler(int(os.environ.get("LOCAL_RANK", "0"))))
 
 
 def main() -> int:

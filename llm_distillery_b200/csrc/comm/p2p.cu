@@ -11,17 +11,32 @@
 //   reduce_scatter_f32 / allgather_16 / allreduce_f32   stand-alone pieces for the other optimizers and for tests
 //   gather_pull / reduce_scatter_acc_f32   full parameter sharding: a unit's weights pulled from the ranks' shards
 //                      just before it runs; its gradients summed onto this rank's slice right after its backward
+//
+// Wire format of the data-parallel gradient exchange: every rank casts its fp32 gradient to a bf16 copy in symmetric
+// memory (cast_wire); the owner of a shard adds its OWN fp32 gradient and the peers' bf16 copies in fp32 registers.
+// Half the bytes cross NVLink, and the sum is still fp32.
+//
+// A barrier whose wait runs out poisons this GPU's collectives: it sets a device word that every kernel of this
+// file reads first, and a kernel that finds it set returns without touching anything. The reduction and optimizer
+// kernels queued behind a failed barrier therefore leave master weights, moments and every rank's weights as the
+// last good step wrote them. The host clears the word when it has taken note of the error (b200_p2p_clear_poison).
 #include "peer.cuh"
 #include "../common/host.cuh"
 
 namespace b200 {
 namespace comm {
 
+__device__ unsigned int g_poison = 0;
+__device__ __forceinline__ bool poisoned() { return *reinterpret_cast<volatile unsigned int*>(&g_poison) != 0u; }
+
 // sig[r] points at rank r's flag array (MAX_RANKS words). Thread t tells rank t "rank `rank` reached `epoch`" and
 // waits until rank t has told us the same. Epochs only grow, so a late reader never sees a stale match.
 __global__ void barrier_kernel(Peers sig, int rank, int world, unsigned int epoch, unsigned int* err_word) {
   const int t = threadIdx.x;
   if (t >= world) return;
+  // an earlier barrier already gave up: post nothing (the peers' waits run out too, so every survivor skips the
+  // step) and do not wait two more seconds
+  if (poisoned()) return;
   __threadfence_system();
   st_release_sys(reinterpret_cast<unsigned int*>(sig.p[t]) + rank, epoch);
   const unsigned int* mine = reinterpret_cast<const unsigned int*>(sig.p[rank]) + t;
@@ -29,10 +44,38 @@ __global__ void barrier_kernel(Peers sig, int rank, int world, unsigned int epoc
   unsigned int spins = 0;
   while (static_cast<int>(ld_acquire_sys(mine) - epoch) < 0) {
     if (((++spins) & 0xffu) == 0u && globaltimer_ns() - t0 > kWaitTimeoutNs) {
+      atomicExch(&g_poison, 1u);
       if (err_word) atomicCAS(err_word, 0u, (unsigned)ERR_WAIT_PEER);
       return;
     }
     __nanosleep(64);
+  }
+}
+
+__global__ void clear_poison_kernel() { g_poison = 0u; }
+
+// Counts the optimizer steps whose reduction really ran: queued right behind the reduction kernels, it adds one
+// unless the step's barrier gave up. The host compares the count with the steps it issued before it saves state.
+__global__ void mark_step_kernel(unsigned int* counter) {
+  if (!poisoned()) *counter += 1u;
+}
+
+// wire[lo + i] = bf16(grad[lo + i]), 8 elements per thread
+__global__ void __launch_bounds__(256) cast_wire_kernel(const float* __restrict__ grad, __nv_bfloat16* __restrict__ wire,
+                                                        long long lo, long long n) {
+  if (poisoned()) return;
+  const long long nv = n >> 3;
+  const float4* src = reinterpret_cast<const float4*>(grad + lo);
+  uint4* dst = reinterpret_cast<uint4*>(wire + lo);
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nv;
+       i += (long long)gridDim.x * blockDim.x) {
+    const float4 x = src[2 * i], y = src[2 * i + 1];
+    uint4 o;
+    o.x = pack_bf16x2(x.x, x.y);
+    o.y = pack_bf16x2(x.z, x.w);
+    o.z = pack_bf16x2(y.x, y.y);
+    o.w = pack_bf16x2(y.z, y.w);
+    dst[i] = o;
   }
 }
 
@@ -41,21 +84,53 @@ struct AdamArgs {
   int decoupled;
 };
 
-// 8 elements per thread: two float4 gradient loads per peer, one 16-byte bf16 store per peer.
-__global__ void __launch_bounds__(256) rs_adamw_ag_kernel(Peers grads, Peers models, float* __restrict__ master,
-                                                         float* __restrict__ m, float* __restrict__ v,
-                                                         long long shard_lo, long long shard_n, int rank, int world,
-                                                         AdamArgs a) {
+__device__ __forceinline__ void add_bf16x8(float (&g)[8], const uint4& q) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+  for (int t = 0; t < 4; ++t) {
+    const float2 x = __bfloat1622float2(h[t]);
+    g[2 * t] += x.x;
+    g[2 * t + 1] += x.y;
+  }
+}
+
+// 8 elements per thread. WIRE16 = false: `grads` are the ranks' fp32 gradients (two float4 loads per peer).
+// WIRE16 = true: `grads` are the ranks' bf16 wire copies (one 16-byte load per peer) and this rank's own
+// contribution comes from `own` (its fp32 gradient). One 16-byte bf16 store per peer either way.
+template <bool WIRE16>
+__global__ void __launch_bounds__(256) rs_adamw_ag_kernel(Peers grads, const float* __restrict__ own, Peers models,
+                                                         float* __restrict__ master, float* __restrict__ m,
+                                                         float* __restrict__ v, long long shard_lo, long long shard_n,
+                                                         long long state_off, int rank, int world, AdamArgs a) {
+  if (poisoned()) return;
   const long long nv = shard_n >> 3;
+  master += state_off; m += state_off; v += state_off;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nv;
        i += (long long)gridDim.x * blockDim.x) {
     float g[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (int k = 0; k < world; ++k) {
-      const int p = (rank + k) % world;  // start with the local copy, spread peers over time
-      const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(grads.p[p]) + shard_lo) + 2 * i;
+    if (WIRE16) {
+      uint4 q[MAX_RANKS];
+#pragma unroll
+      for (int k = 1; k < MAX_RANKS; ++k)   // all peer loads issued before the first use: their latencies overlap
+        if (k < world)
+          q[k] = (reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(grads.p[(rank + k) % world]) +
+                                                 shard_lo))[i];
+      const float4* src = reinterpret_cast<const float4*>(own + shard_lo) + 2 * i;
       const float4 x = src[0], y = src[1];
-      g[0] += x.x; g[1] += x.y; g[2] += x.z; g[3] += x.w;
-      g[4] += y.x; g[5] += y.y; g[6] += y.z; g[7] += y.w;
+      g[0] = x.x; g[1] = x.y; g[2] = x.z; g[3] = x.w;
+      g[4] = y.x; g[5] = y.y; g[6] = y.z; g[7] = y.w;
+#pragma unroll
+      for (int k = 1; k < MAX_RANKS; ++k)
+        if (k < world) add_bf16x8(g, q[k]);
+    } else {
+      for (int k = 0; k < world; ++k) {
+        const int p = (rank + k) % world;  // start with the local copy, spread peers over time
+        const float4* src =
+            reinterpret_cast<const float4*>(reinterpret_cast<const float*>(grads.p[p]) + shard_lo) + 2 * i;
+        const float4 x = src[0], y = src[1];
+        g[0] += x.x; g[1] += x.y; g[2] += x.z; g[3] += x.w;
+        g[4] += y.x; g[5] += y.y; g[6] += y.z; g[7] += y.w;
+      }
     }
     float pm[8], mm[8], vv[8];
     *reinterpret_cast<float4*>(pm) = reinterpret_cast<float4*>(master)[2 * i];
@@ -99,6 +174,7 @@ __global__ void __launch_bounds__(256) rs_adamw_piece_kernel(Peers grads, long l
                                                             __nv_bfloat16* __restrict__ model, float* __restrict__ master,
                                                             float* __restrict__ m, float* __restrict__ v, long long n,
                                                             int rank, int world, AdamArgs a) {
+  if (poisoned()) return;
   const long long nv = n >> 3;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nv;
        i += (long long)gridDim.x * blockDim.x) {
@@ -150,6 +226,7 @@ __global__ void __launch_bounds__(256) rs_adamw_piece_kernel(Peers grads, long l
 // out[i] = scale * sum_p src_p[lo + i]   (fp32), i < n, n % 4 == 0
 __global__ void __launch_bounds__(256) reduce_scatter_kernel(Peers src, float* __restrict__ out, long long lo,
                                                             long long n, int rank, int world, float scale) {
+  if (poisoned()) return;
   const long long nv = n >> 2;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nv;
        i += (long long)gridDim.x * blockDim.x) {
@@ -167,6 +244,7 @@ __global__ void __launch_bounds__(256) reduce_scatter_kernel(Peers src, float* _
 // dst_p[lo_bytes + ...] = local[...] for every rank p: all-gather by peer stores, 16-byte granules
 __global__ void __launch_bounds__(256) allgather_kernel(Peers dst, const uint4* __restrict__ local, long long lo_vec,
                                                        long long nvec, int rank, int world, int skip_self) {
+  if (poisoned()) return;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
        i += (long long)gridDim.x * blockDim.x) {
     const uint4 x = local[i];
@@ -183,6 +261,7 @@ __global__ void __launch_bounds__(256) allgather_kernel(Peers dst, const uint4* 
 // thread are in flight before the first store: NVLink latency is hidden by independent requests, not by occupancy.
 __global__ void __launch_bounds__(256) gather_pull_kernel(Peers src, uint4* __restrict__ dst, long long src_off_vec,
                                                          long long piece_vec, int rank, int world) {
+  if (poisoned()) return;
   constexpr int U = 8;
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (int k = 0; k < world; ++k) {
@@ -209,6 +288,7 @@ __global__ void __launch_bounds__(256) gather_pull_kernel(Peers src, uint4* __re
 // out[i] (+)= sum_p src_p[lo + i]   (fp32), i < n, n % 4 == 0: reduce-scatter by peer loads into (or onto) a local slice
 __global__ void __launch_bounds__(256) reduce_scatter_acc_kernel(Peers src, float* __restrict__ out, long long lo,
                                                                 long long n, int rank, int world, int accumulate) {
+  if (poisoned()) return;
   const long long nv = n >> 2;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nv;
        i += (long long)gridDim.x * blockDim.x) {
@@ -256,17 +336,50 @@ int b200_p2p_barrier(const void* const* sig_ptrs, int rank, int world, unsigned 
   return B200_OK;
 }
 
-// grad_ptrs[r]: rank r's full fp32 gradient; model_ptrs[r]: rank r's full bf16 weights; master/m/v: local shard.
-int b200_p2p_rs_adamw_ag(const void* const* grad_ptrs, const void* const* model_ptrs, float* master, float* m, float* v,
-                         long long shard_lo, long long shard_n, int rank, int world, float lr, float beta1, float beta2,
-                         float eps, float weight_decay, int step, float grad_scale, int decoupled, cudaStream_t st) {
+// Clears the poison word of the current device (after the host has read the error word and decided to go on).
+int b200_p2p_clear_poison(cudaStream_t st) {
+  clear_poison_kernel<<<1, 1, 0, st>>>();
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200_OK;
+}
+
+int b200_p2p_mark_step(unsigned int* counter, cudaStream_t st) {
+  if (!counter) return B200_ERR_ARG;
+  mark_step_kernel<<<1, 1, 0, st>>>(counter);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200_OK;
+}
+
+// wire[lo, lo + n) = bf16(grad[lo, lo + n)): this rank's gradient in the format the peers read. n, lo multiples of 8.
+int b200_p2p_cast_wire(const float* grad, void* wire, long long lo, long long n, cudaStream_t st) {
+  if (!grad || !wire || n <= 0 || (n & 7) || (lo & 7) || lo < 0) return B200_ERR_ARG;
+  cast_wire_kernel<<<grid_for(n >> 3), 256, 0, st>>>(grad, (__nv_bfloat16*)wire, lo, n);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200_OK;
+}
+
+// The data-parallel optimizer step on flat offsets [lo, lo + n) (inside this rank's shard):
+//   grad_ptrs[r]   rank r's gradient, fp32 (wire16 = 0) or its bf16 wire copy (wire16 = 1)
+//   own_grad       this rank's fp32 gradient (used with wire16 = 1; its own wire copy is never read)
+//   model_ptrs[r]  rank r's full bf16 weights
+//   master/m/v     local shard; state_off = lo - shard start
+//   max_ctas       > 0 caps the grid: a launch that runs beside the backward pass takes a few CTAs, not every SM
+int b200_p2p_rs_adamw_ag(const void* const* grad_ptrs, const float* own_grad, int wire16, const void* const* model_ptrs,
+                         float* master, float* m, float* v, long long lo, long long n, long long state_off, int rank,
+                         int world, float lr, float beta1, float beta2, float eps, float weight_decay, int step,
+                         float grad_scale, int decoupled, int max_ctas, cudaStream_t st) {
   Peers G, M;
-  if (!fill(G, grad_ptrs, world) || !fill(M, model_ptrs, world) || !master || !m || !v || shard_n <= 0 ||
-      (shard_n & 7) || (shard_lo & 7) || step < 1)
+  if (!fill(G, grad_ptrs, world) || !fill(M, model_ptrs, world) || !master || !m || !v || n <= 0 || (n & 7) ||
+      (lo & 7) || (state_off & 7) || state_off < 0 || step < 1 || (wire16 && !own_grad))
     return B200_ERR_ARG;
   AdamArgs a{lr, beta1, beta2, eps, weight_decay, 1.f - powf(beta1, (float)step), 1.f - powf(beta2, (float)step),
              grad_scale, decoupled};
-  rs_adamw_ag_kernel<<<grid_for(shard_n >> 3), 256, 0, st>>>(G, M, master, m, v, shard_lo, shard_n, rank, world, a);
+  int grid = grid_for(n >> 3);
+  if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
+  if (wire16)
+    rs_adamw_ag_kernel<true><<<grid, 256, 0, st>>>(G, own_grad, M, master, m, v, lo, n, state_off, rank, world, a);
+  else
+    rs_adamw_ag_kernel<false><<<grid, 256, 0, st>>>(G, own_grad, M, master, m, v, lo, n, state_off, rank, world, a);
   B200_CUDA_CHECK(cudaGetLastError());
   return B200_OK;
 }

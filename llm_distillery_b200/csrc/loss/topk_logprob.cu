@@ -219,8 +219,11 @@ __global__ void __launch_bounds__(NT) topk_merge_kernel(const float* __restrict_
   for (int i = threadIdx.x; i < n2; i += NT) {
     if (i < n) {
       const bool first = i < K;
-      const int id = first ? a_id[row * K + i] : b_id[row * K + i - K];
+      int id = first ? a_id[row * K + i] : b_id[row * K + i - K];
       pv[i] = __expf(first ? a_lp[row * K + i] : b_lp[row * K + i - K]);
+      // an empty slot (log-prob -inf, id 0) carries no mass; it gets an id of its own above every vocabulary so that
+      // it never sits between a real token 0 of one list and of the other (equal ids are summed in PAIRS below)
+      if (!(pv[i] > 0.f)) id = 0x7f000000 + i;
       s[i] = ((unsigned long long)(uint32_t)id << 32) | (uint32_t)i;
     } else {
       s[i] = 0ull;
@@ -254,7 +257,8 @@ __global__ void __launch_bounds__(NT) topk_merge_kernel(const float* __restrict_
     const unsigned long long e = s[i];
     const float p = e ? kfloat((uint32_t)(e >> 32)) : 0.f;
     o_lp[row * K + i] = __logf(p);
-    o_id[row * K + i] = e ? (int)(0xffffffffu - (uint32_t)e) : 0;
+    const int oid = e ? (int)(0xffffffffu - (uint32_t)e) : 0;
+    o_id[row * K + i] = (p > 0.f && oid < 0x7f000000) ? oid : 0;
   }
 }
 

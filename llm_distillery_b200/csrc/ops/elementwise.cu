@@ -727,7 +727,10 @@ static int scratch_for_current_device(float** out) {
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return set_last_cuda_error(e, "cudaGetDevice");
-  if (dev < 0 || dev >= 64) return B200_ERR_ARG;
+  if (dev < 0 || dev >= 64) {
+    set_last_cuda_error(cudaErrorInvalidDevice, "b200_rmsnorm_bwd_noalloc: device index outside the 64 this library tracks");
+    return B200_ERR_ARG;
+  }
   std::lock_guard<std::mutex> lk(g_noalloc_mu);
   if (!g_noalloc_ptr[dev]) {
     float* p = nullptr;

@@ -13,7 +13,9 @@
 //   * limit: h <= B200_RMSNORM_NOALLOC_MAX_H (and h % 8 == 0). Larger rows are refused with B200_ERR_TOO_BIG (-4) and
 //     a message readable through b200_last_cuda_error(); nothing is launched;
 //   * the first call on each device looks up the array's device address (cudaGetSymbolAddress) with that device
-//     current. Make that first call outside any stream capture;
+//     current. Make that first call outside any stream capture. The address is remembered per device for the life
+//     of the process and is not valid across cudaDeviceReset: a process that resets a device must not call this
+//     entry point on it afterwards;
 //   * every call on a device shares the one array. A call overwrites the rows it uses before reading them, so
 //     nothing has to be cleared between calls, but two calls that overlap in time on one GPU (different streams)
 //     would corrupt each other's partial sums: serialise them;

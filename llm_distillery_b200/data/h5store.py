@@ -66,6 +66,11 @@ def merge_topk(disk_logp: np.ndarray, disk_idx: np.ndarray, new_logp: np.ndarray
     n = min(len(disk_logp), len(new_logp))
     ids = np.concatenate([disk_idx[:n].astype(np.int64), new_idx[:n].astype(np.int64)], axis=1)
     p = np.exp(np.concatenate([disk_logp[:n].astype(np.float32), new_logp[:n].astype(np.float32)], axis=1))
+    # empty slots (log-prob -inf, id 0: what a cross-tokenizer remap leaves when fewer than K ids have an image) carry
+    # no mass but would sit next to a real token 0 and break the "duplicates come in pairs" rule below: give each of
+    # them an id of its own above every vocabulary; they sort last by probability and leave as id 0 again
+    empty = ~(p > 0)
+    ids = np.where(empty, (1 << 40) + np.arange(ids.shape[1], dtype=np.int64)[None, :], ids)
     order = np.argsort(ids, axis=1, kind="stable")
     ids = np.take_along_axis(ids, order, 1)
     p = np.take_along_axis(p, order, 1)
@@ -75,6 +80,7 @@ def merge_topk(disk_logp: np.ndarray, disk_idx: np.ndarray, new_logp: np.ndarray
     top = np.argsort(-p, axis=1, kind="stable")[:, :K]
     out_p = np.take_along_axis(p, top, 1)
     out_i = np.take_along_axis(ids, top, 1)
+    out_i = np.where(out_i >= (1 << 40), 0, out_i)
     with np.errstate(divide="ignore"):
         out_l = np.log(np.maximum(out_p, 0.0))
     rest_l, rest_i = (disk_logp[n:], disk_idx[n:]) if len(disk_logp) > n else (new_logp[n:], new_idx[n:])

@@ -62,8 +62,42 @@ def loss_rows(kind: str, s: torch.Tensor, t: torch.Tensor, jsd_renorm: bool = Fa
     raise ValueError(f"unknown loss kind {kind}")
 
 
+class _SegSumFn(torch.autograd.Function):
+    """Sum of ``x`` per conversation on CUDA with a fixed order of additions (csrc/loss/segment.cu): ``seg`` must be
+    non-decreasing, which is how micro-batches are laid out (one conversation's rows after the other's)."""
+
+    @staticmethod
+    def forward(ctx, x, seg, n):
+        from ..ops import _lib
+        out = torch.empty(n, dtype=torch.float32, device=x.device)
+        _lib.check(_lib.kernels().b200_segment_reduce(_lib.ptr(x), _lib.ptr(seg), _lib.ptr(out), x.numel(), n, 0,
+                                                      _lib.stream()), "b200_segment_reduce")
+        ctx.save_for_backward(seg)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        (seg,) = ctx.saved_tensors
+        return g.index_select(0, seg), None, None
+
+
 def _seg_sum(x, seg, n):
+    """out[c] = sum of x over the rows of conversation c. Bit-repeatable on both devices: an ordered loop on CPU, the
+    segment kernel on CUDA (``index_add_`` there is an atomic scatter whose order changes from run to run)."""
+    if x.is_cuda:
+        return _SegSumFn.apply(x.float().contiguous(), seg.contiguous(), n)
     return torch.zeros(n, dtype=x.dtype, device=x.device).index_add_(0, seg, x)
+
+
+def seg_count(seg, n, dtype=torch.float32):
+    """Number of rows of each conversation."""
+    if seg.is_cuda:
+        from ..ops import _lib
+        out = torch.empty(n, dtype=torch.float32, device=seg.device)
+        _lib.check(_lib.kernels().b200_segment_reduce(None, _lib.ptr(seg.contiguous()), _lib.ptr(out), seg.numel(), n, 2,
+                                                      _lib.stream()), "b200_segment_reduce")
+        return out.to(dtype)
+    return torch.zeros(n, dtype=dtype, device=seg.device).index_add_(0, seg, torch.ones(seg.numel(), dtype=dtype))
 
 
 def _seg_max(x, seg, n):
@@ -83,8 +117,6 @@ def reference_loss_segments(s: torch.Tensor, t: torch.Tensor, ids: torch.Tensor,
     seg       [M]   conversation index of each row, in [0, n_seg)
     Returns (train_loss_per_conversation [n_seg], dict of logged per-conversation scalars [n_seg] each).
     """
-    M = s.shape[0]
-    ones = torch.ones(M, dtype=s.dtype, device=s.device)
     has_label = labels >= 0
     hit = (ids == labels[:, None]) & has_label[:, None] & (~avoid)[:, None]
     valid = hit.any(-1)
@@ -103,7 +135,7 @@ def reference_loss_segments(s: torch.Tensor, t: torch.Tensor, ids: torch.Tensor,
     d = torch.where(has_label, torch.relu(ce_diff), torch.zeros_like(ce_diff))          # last row: padded 0
     kl = loss_rows("kl", s, t)
     rkl = loss_rows("rkl", s, t)
-    n_rows = _seg_sum(ones, seg, n_seg)
+    n_rows = seg_count(seg, n_seg, s.dtype)
     n_lab = _seg_sum(has_label.to(s.dtype), seg, n_seg)
 
     def weighted(x):

@@ -188,7 +188,6 @@ def distill_head_loss(Hc, W, ids, u, *, kind: str, temperature: float, vocab: in
         custom, logs = dv.reference_loss_segments(s, t, ids.long(), labels, avoid, seg, n_seg, alpha)
         return custom.sum(), {k: v.detach().sum() for k, v in logs.items()}
     rows = fused_distill_rows(Hc, W, ids, u, kind, temperature, vocab, jsd_renorm)
-    n_rows = torch.zeros(n_seg, dtype=rows.dtype, device=rows.device).index_add_(0, seg, torch.ones_like(rows))
-    per_convo = torch.zeros(n_seg, dtype=rows.dtype, device=rows.device).index_add_(0, seg, rows) / n_rows
+    per_convo = dv._seg_sum(rows, seg, n_seg) / dv.seg_count(seg, n_seg, rows.dtype)
     key = {"kl": "kl_div", "rkl": "reverse kl_div", "jsd": "jsd"}[kind]
     return per_convo.sum(), {key: per_convo.detach().sum(), "custom loss": per_convo.detach().sum()}

@@ -250,6 +250,14 @@ class StudentModel(BaseModel):
         mine = self.rank == 0 or (self.comm is not None and self.comm.shards_optimizer)
         # an emergency save happens after a step that failed half-way: its samples were counted but never applied
         counters = self._counters() if collective else (getattr(self, "_applied", None) or self._counters())
+        if not collective and hasattr(self.comm, "unapplied_steps"):
+            # the host may have issued one or two optimizer steps past the lost peer before it learnt of it; their
+            # kernels did nothing (csrc/comm/p2p.cu), so the saved step count and sample counters go back with them
+            lost = self.comm.unapplied_steps()
+            if lost > 0:
+                hist = self._applied_history
+                self.engine.opt.step_count = max(0, self.engine.opt.step_count - lost)
+                counters = hist[-1 - lost] if len(hist) > lost else (hist[0] if hist else counters)
         if not collective and getattr(self.comm, "full_shard", False):
             # no peer to gather the weights from: this rank's optimizer shard (with its fp32 master weights) only
             ckpt.save_trainer_state(self.paths.student_states, None, self.engine.opt, self.engine.schedule, counters)
@@ -311,6 +319,7 @@ class StudentModel(BaseModel):
         else:
             self._load_model()
         self._applied = self._counters()
+        self._applied_history = [self._applied]      # counters after each of the last few optimizer steps
         self.training_active = True
         if self.losses is None:
             self.losses = Losses(self.logger)
@@ -444,6 +453,8 @@ class StudentModel(BaseModel):
                 updated = True
                 self.next_accum_step += self.eff_batch_size
                 self._applied = self._counters()     # what an emergency save may claim: nothing beyond this step
+                self._applied_history.append(self._applied)
+                del self._applied_history[:-4]
                 if self._stop_agreed() and self.num_trained_steps < self.total_training_steps:
                     print("Stop requested: saving the trainer state; the same command takes the run up again.", flush=True)
                     self._save_state()

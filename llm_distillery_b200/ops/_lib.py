@@ -54,6 +54,7 @@ _SIGS = {
     "b200_simple_opt_step": [_VP, _VP, _VP, _VP, _VP, _LL, _I, _F, _F, _F, _F, _F, _I, _I, _F, _VP],
     "b200_sumsq": [_VP, _LL, _F, _VP, _VP],
     "b200_sm_count": [],
+    "b200_segment_reduce": [_VP, _VP, _VP, _LL, _I, _I, _VP],
 }
 
 
@@ -147,6 +148,11 @@ def check(rc: int, what: str) -> None:
 def take_device_error() -> int:
     """Synchronise and return (then clear) the in-kernel wait error word of the current device (0 = none)."""
     torch.cuda.synchronize()
+    return int(kernels().b200_take_device_error())
+
+
+def peek_device_error() -> int:
+    """The error word as it stands (pinned host memory), read and cleared WITHOUT synchronising the device."""
     return int(kernels().b200_take_device_error())
 
 

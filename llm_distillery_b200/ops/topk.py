@@ -48,12 +48,14 @@ def topk_merge(a_lp: torch.Tensor, a_id: torch.Tensor, b_lp: torch.Tensor, b_id:
     if not a_lp.is_cuda:
         ids = torch.cat([a_id, b_id], 1).long()
         p = torch.cat([a_lp, b_lp], 1).float().exp()
-        o_lp = torch.empty((rows, K)); o_id = torch.empty((rows, K), dtype=torch.int32)
+        o_lp = torch.full((rows, K), float("-inf")); o_id = torch.zeros((rows, K), dtype=torch.int32)
         for r in range(rows):
-            u, inv = torch.unique(ids[r], return_inverse=True)
-            acc = torch.zeros(len(u)).index_add_(0, inv, p[r])
+            ok = p[r] > 0                    # empty slots (id 0, log-prob -inf) take no part and come out as such
+            u, inv = torch.unique(ids[r][ok], return_inverse=True)
+            acc = torch.zeros(len(u)).index_add_(0, inv, p[r][ok])
             v, j = torch.sort(acc, descending=True, stable=True)
-            o_lp[r] = v[:K].log(); o_id[r] = u[j[:K]].to(torch.int32)
+            n = min(K, len(u))
+            o_lp[r, :n] = v[:n].log(); o_id[r, :n] = u[j[:n]].to(torch.int32)
         return o_lp, o_id
     o_lp = torch.empty((rows, K), dtype=torch.float32, device=a_lp.device)
     o_id = torch.empty((rows, K), dtype=torch.int32, device=a_lp.device)

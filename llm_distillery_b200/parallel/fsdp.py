@@ -518,6 +518,11 @@ class P2PFullShardComm(FullShardComm):
     def check(self) -> None:
         err = self._lib.take_device_error()
         if err:
+            # the barrier that gave up switched this GPU's peer kernels off (csrc/comm/p2p.cu): nothing behind it ran
+            from ..ops._lib import _VP
+            self._lib.register("b200_p2p_clear_poison", [_VP])
+            self._lib.check(self._lib.kernels().b200_p2p_clear_poison(self._lib.stream()), "b200_p2p_clear_poison")
+            torch.cuda.synchronize()
             raise RuntimeError(f"peer-to-peer wait timed out on rank {self.rank} (device error code {err})")
 
     def _gather_unit(self, u: _Unit) -> None:

@@ -7,7 +7,14 @@ pointers to every other rank's copies. One optimizer step is then
 
 where the middle kernel, for this rank's 1/world shard, sums all ranks' gradients with peer loads, applies AdamW to
 the local fp32 master weights / moments and writes the new bf16 weights into every rank's weight buffer with peer
-stores. Optimizer state is therefore sharded (ZeRO-1) for ``ddp`` and ``fsdp`` alike. Optimizers other than the
+stores. The peers' gradients cross NVLink as bf16 (each rank casts its fp32 gradient into a symmetric "wire" buffer
+first; the owner of a shard adds its own fp32 gradient and the peers' bf16 copies in fp32), which halves the bytes;
+``B200_WIRE=fp32`` keeps the fp32 exchange.
+
+With ``B200_OVERLAP=1`` (default when several GPUs train) the same kernel runs per finished layer range on a side
+stream behind the backward of the earlier layers, on a handful of CTAs (``B200_OVERLAP_CTAS``): the exchange needs a
+few tens of GB/s to keep up with backward, so it does not need the SMs the backward GEMMs are using, and only the
+last range (embedding and first layer) is left for after backward. Optimizer state is therefore sharded (ZeRO-1) for ``ddp`` and ``fsdp`` alike. Optimizers other than the
 fp32-state Adam family run reduce-scatter kernel -> local optimizer kernel -> all-gather kernel.
 
 Barriers are flag exchanges with growing epoch numbers; every device-side wait is bounded and reports through the
@@ -27,7 +34,11 @@ from ..ops._lib import _VP, _I, _LL, _F
 
 _U = ctypes.c_uint
 _lib.register("b200_p2p_barrier", [_VP, _I, _I, _U, _VP])
-_lib.register("b200_p2p_rs_adamw_ag", [_VP, _VP, _VP, _VP, _VP, _LL, _LL, _I, _I, _F, _F, _F, _F, _F, _I, _F, _I, _VP])
+_lib.register("b200_p2p_rs_adamw_ag", [_VP, _VP, _I, _VP, _VP, _VP, _VP, _LL, _LL, _LL, _I, _I, _F, _F, _F, _F, _F, _I, _F,
+                                        _I, _I, _VP])
+_lib.register("b200_p2p_cast_wire", [_VP, _VP, _LL, _LL, _VP])
+_lib.register("b200_p2p_clear_poison", [_VP])
+_lib.register("b200_p2p_mark_step", [_VP, _VP])
 _lib.register("b200_p2p_reduce_scatter_f32", [_VP, _VP, _LL, _LL, _I, _I, _F, _VP])
 _lib.register("b200_p2p_allgather", [_VP, _VP, _LL, _LL, _I, _I, _I, _VP])
 
@@ -68,14 +79,22 @@ class P2PComm:
         self.side = torch.cuda.Stream(device=self.device)
         self._ov = None
         import os
-        # off by default: on 2 and 8 B200s the step was 1-2 % SLOWER with the reduction running beside backward (the
-        # side-stream kernel competes with the backward GEMMs for HBM and SM slots, and the reduction it hides is
-        # only ~4 % of the step); B200_OVERLAP=1 turns it on
-        self._overlap_enabled = os.environ.get("B200_OVERLAP", "0") == "1"
-        self._buckets = max(1, int(os.environ.get("B200_OVERLAP_BUCKETS", "4")))   # ranges per step handed over early
+        # the reduction of finished layer ranges runs beside backward on a few CTAs (a full-size grid there took SM
+        # slots and HBM bandwidth from the backward GEMMs and made the step slower); B200_OVERLAP=0 does one
+        # reduction after backward instead
+        self._overlap_enabled = os.environ.get("B200_OVERLAP", "1") == "1"
+        self._buckets = max(1, int(os.environ.get("B200_OVERLAP_BUCKETS", "8")))   # ranges per step handed over early
+        self._overlap_ctas = max(1, int(os.environ.get("B200_OVERLAP_CTAS", "24")))
+        self._wire16 = os.environ.get("B200_WIRE", "bf16") != "fp32"
         self.grad_buf = None
         self.model_buf = None
+        self.wire_buf = None
         self._rdv = torch.zeros(1, dtype=torch.float32, device=self.device)
+        # optimizer steps issued by the host / steps whose reduction kernels really ran (a kernel behind a barrier
+        # that gave up does nothing): the difference is what an emergency save must not claim
+        self.steps_issued = 0
+        self._steps_applied = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.failed_step = False
         torch.cuda.synchronize(self.device)
         dist.barrier()
 
@@ -91,6 +110,8 @@ class P2PComm:
         total = _round_up(total, 256 * self.world)
         self.grad_buf = SymmetricBuffer(total, torch.float32, self.device)
         self.model_buf = SymmetricBuffer(total, dtype, self.device)
+        if self._wire16 and dtype == torch.bfloat16:
+            self.wire_buf = SymmetricBuffer(total, torch.bfloat16, self.device)
         return {"grad": self.grad_buf.tensor, "model": self.model_buf.tensor}
 
     def attach(self, flat, opt) -> None:
@@ -113,10 +134,44 @@ class P2PComm:
         _lib.check(_lib.kernels().b200_p2p_barrier(self.sig.c_ptrs, self.rank, self.world, self.epoch, _lib.stream()),
                    "b200_p2p_barrier")
 
-    def check(self) -> None:
-        err = _lib.take_device_error()
+    def check(self, sync: bool = False) -> None:
+        """Raises when a bounded device-side wait has run out. Without ``sync`` the error word is read where it lives,
+        in pinned host memory, with no device synchronisation: a wait that ran out in the step just queued may then
+        only be seen at the next call. That is safe, because the kernels behind a failed barrier change nothing (see
+        csrc/comm/p2p.cu); callers that are about to SAVE state pass ``sync=True``."""
+        err = _lib.take_device_error() if sync else _lib.peek_device_error()
         if err:
+            torch.cuda.synchronize(self.device)
+            _lib.take_device_error()
+            _lib.check(_lib.kernels().b200_p2p_clear_poison(_lib.stream()), "b200_p2p_clear_poison")
+            torch.cuda.synchronize(self.device)
+            self.failed_step = True
             raise RuntimeError(f"peer-to-peer wait timed out on rank {self.rank} (device error code {err})")
+
+    def _mark_step(self) -> None:
+        self.steps_issued += 1
+        _lib.check(_lib.kernels().b200_p2p_mark_step(_lib.ptr(self._steps_applied), _lib.stream()), "b200_p2p_mark_step")
+
+    def unapplied_steps(self) -> int:
+        """Optimizer steps the host issued whose kernels did NOT run because a peer was lost (synchronises)."""
+        torch.cuda.synchronize(self.device)
+        return self.steps_issued - int(self._steps_applied.item())
+
+    def _grad_sources(self):
+        """(pointer table of the gradients the peers are read from, this rank's fp32 gradient, wire flag)."""
+        if self.wire_buf is not None:
+            return self.wire_buf.c_ptrs, _lib.ptr(self.flat.grad), 1
+        return self.grad_buf.c_ptrs, None, 0
+
+    def _cast_wire(self, lo: int, hi: int) -> None:
+        """bf16 copy of this rank's gradient on [lo, hi) for the peers; its own shard is skipped (nobody reads it)."""
+        if self.wire_buf is None:
+            return
+        f = self.flat
+        for a, b in ((lo, min(hi, f.shard_lo)), (max(lo, f.shard_lo + f.shard_size), hi)):
+            if b > a:
+                _lib.check(_lib.kernels().b200_p2p_cast_wire(_lib.ptr(f.grad), _lib.ptr(self.wire_buf.tensor), a, b - a,
+                                                             _lib.stream()), "b200_p2p_cast_wire")
 
     def reduce_scatter(self, src: SymmetricBuffer, out: torch.Tensor, lo: int, scale: float = 1.0) -> None:
         """out[i] = scale * sum over ranks of src[lo + i]; callers bracket this with barriers."""
@@ -169,9 +224,10 @@ class P2PComm:
         hi, ov["hi"] = ov["hi"], lo
         self._launch_range(lo, hi)
 
-    def _launch_range(self, lo: int, hi: int) -> None:
+    def _launch_range(self, lo: int, hi: int, tail: bool = False) -> None:
         f, opt, ov = self.flat, self.opt, self._ov
         f.zero_untouched_in(lo, hi)
+        self._cast_wire(lo, hi)
         a, b = max(lo, f.shard_lo), min(hi, f.shard_lo + f.shard_size)
         ev = torch.cuda.Event()
         ev.record()                                   # this rank's gradients of the range are complete here
@@ -184,13 +240,14 @@ class P2PComm:
             _lib.check(_lib.kernels().b200_p2p_barrier(self.sig_side.c_ptrs, self.rank, self.world, self.side_epoch,
                                                        _lib.stream()), "b200_p2p_barrier")
             if b > a:
-                o = a - f.shard_lo
                 b1, b2 = opt.betas
                 st = opt.state
+                gp, own, w16 = self._grad_sources()
+                # ranges that run beside backward take a few CTAs; the last one has the GPU to itself
                 _lib.check(_lib.kernels().b200_p2p_rs_adamw_ag(
-                    self.grad_buf.c_ptrs, self.model_buf.c_ptrs, _lib.ptr(f.master[o:]), _lib.ptr(st["m"][o:]),
-                    _lib.ptr(st["v"][o:]), a, b - a, self.rank, self.world, ov["lr"], b1, b2, opt.eps,
-                    opt.weight_decay, opt.step_count, ov["gs"], int(opt.decoupled), _lib.stream()),
+                    gp, own, w16, self.model_buf.c_ptrs, _lib.ptr(f.master), _lib.ptr(st["m"]), _lib.ptr(st["v"]),
+                    a, b - a, a - f.shard_lo, self.rank, self.world, ov["lr"], b1, b2, opt.eps, opt.weight_decay,
+                    opt.step_count, ov["gs"], int(opt.decoupled), 0 if tail else self._overlap_ctas, _lib.stream()),
                     "b200_p2p_rs_adamw_ag")
 
     # ---- the optimizer step
@@ -200,27 +257,32 @@ class P2PComm:
         if self._ov is not None:
             # the tail of the flat space (first layers, embedding) and then: everything of the side stream is done,
             # and every rank's weight stores have landed, before the next forward reads the weights
-            self._launch_range(0, self._ov["hi"])
+            self._launch_range(0, self._ov["hi"], tail=True)
             self._ov = None
             done = torch.cuda.Event()
             done.record(self.side)
             torch.cuda.current_stream().wait_event(done)
+            self._mark_step()
             self.barrier()
             return
+        fused = self._fused()
+        if fused:
+            self._cast_wire(0, f.total)
         self.rendezvous()
         self.barrier()
-        fused = self._fused()
         if fused:
             opt.step_count += 1
             b1, b2 = opt.betas
             st = opt.state
+            gp, own, w16 = self._grad_sources()
             _lib.check(_lib.kernels().b200_p2p_rs_adamw_ag(
-                self.grad_buf.c_ptrs, self.model_buf.c_ptrs, _lib.ptr(f.master), _lib.ptr(st["m"]), _lib.ptr(st["v"]),
-                f.shard_lo, f.shard_size, self.rank, self.world, lr, b1, b2, opt.eps, opt.weight_decay, opt.step_count,
-                gs, int(opt.decoupled), _lib.stream()), "b200_p2p_rs_adamw_ag")
+                gp, own, w16, self.model_buf.c_ptrs, _lib.ptr(f.master), _lib.ptr(st["m"]), _lib.ptr(st["v"]),
+                f.shard_lo, f.shard_size, 0, self.rank, self.world, lr, b1, b2, opt.eps, opt.weight_decay,
+                opt.step_count, gs, int(opt.decoupled), 0, _lib.stream()), "b200_p2p_rs_adamw_ag")
         else:
             shard = torch.empty(f.shard_size, dtype=torch.float32, device=self.device)
             self.reduce_scatter(self.grad_buf, shard, f.shard_lo, 1.0)
             opt.step(lr, grad_scale=gs, grad=shard)
             self.allgather(self.model_buf, f.model_shard(), f.shard_lo, skip_self=True)
+        self._mark_step()
         self.barrier()

@@ -43,6 +43,21 @@ def test_logprob_full_and_merge():
     assert same > 0.99          # order may differ only between exactly equal probabilities
 
 
+def test_merge_keeps_the_mass_of_token_zero_beside_empty_slots():
+    """Empty slots are (id 0, -inf); a real token 0 in both lists must come out with both probabilities."""
+    ninf = float("-inf")
+    a_lp = torch.tensor([[0.5, 0.2, 0.0, 0.0, 0.0, 0.0]], device=DEV).log()
+    a_id = torch.tensor([[0, 7, 0, 0, 0, 0]], device=DEV, dtype=torch.int32)
+    b_lp = torch.tensor([[0.3, 0.25, 0.1, 0.0, 0.0, 0.0]], device=DEV).log()
+    b_id = torch.tensor([[0, 9, 7, 0, 0, 0]], device=DEV, dtype=torch.int32)
+    lp, ids = topk.topk_merge(a_lp, a_id, b_lp, b_id)
+    assert ids[0, :3].tolist() == [0, 7, 9]
+    assert torch.allclose(lp[0, :3].exp().cpu(), torch.tensor([0.8, 0.3, 0.25]), atol=1e-5)
+    assert ids[0, 3:].tolist() == [0, 0, 0] and bool((lp[0, 3:] == ninf).all())
+    rlp, rids = topk.topk_merge(a_lp.cpu(), a_id.cpu(), b_lp.cpu(), b_id.cpu())
+    assert rids[0, :3].tolist() == [0, 7, 9] and torch.allclose(rlp[0, :3].exp(), torch.tensor([0.8, 0.3, 0.25]), atol=1e-5)
+
+
 def test_collector_matches_full_logits_path():
     torch.manual_seed(1)
     cfg = LlamaConfig(vocab_size=2048, hidden_size=256, intermediate_size=512, num_hidden_layers=2,

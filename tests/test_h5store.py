@@ -110,6 +110,24 @@ def test_multi_teacher_merge_sums_probabilities(tmp_path):
     assert np.allclose(np.sort(np.exp(l), 1), np.sort(2 * np.exp(a.values), 1), rtol=1e-5)
 
 
+def test_merge_with_a_real_token_zero_next_to_empty_slots():
+    """Rows that came through a cross-tokenizer remap end in empty slots (id 0, log-prob -inf). A real token 0 in both
+    inputs must still have its two probabilities summed, whatever number of empty slots shares its id."""
+    ninf = -np.inf
+    disk_l = np.log(np.array([[0.5, 0.2, 0.0, 0.0, 0.0]], dtype=np.float32), where=[[True, True, False, False, False]],
+                    out=np.full((1, 5), ninf, dtype=np.float32))
+    disk_i = np.array([[0, 7, 0, 0, 0]], dtype=np.uint32)
+    new_l = np.log(np.array([[0.3, 0.25, 0.1, 0.0, 0.0]], dtype=np.float32), where=[[True, True, True, False, False]],
+                   out=np.full((1, 5), ninf, dtype=np.float32))
+    new_i = np.array([[0, 9, 7, 0, 0]], dtype=np.uint32)
+    l, i = merge_topk(disk_l, disk_i, new_l, new_i)
+    got = {int(k): float(np.exp(v)) for k, v in zip(i[0], l[0]) if np.isfinite(v)}
+    assert got.keys() == {0, 7, 9}
+    assert abs(got[0] - 0.8) < 1e-6 and abs(got[7] - 0.3) < 1e-6 and abs(got[9] - 0.25) < 1e-6
+    assert [int(x) for x in i[0][:3]] == [0, 7, 9]                  # by probability, descending
+    assert all(int(x) == 0 for x in i[0][3:]) and np.all(np.isneginf(l[0][3:]))   # what is left: empty slots again
+
+
 def test_killed_before_flush_keeps_last_consistent_state(tmp_path):
     st = H5Store(str(tmp_path))
     st.write_batch([_rows(i) for i in range(3)])

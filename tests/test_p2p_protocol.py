@@ -6,7 +6,9 @@ stored into EVERY rank's weight buffer) -> flag barrier. Overlapped schedule (``
 range is handed to the side stream (own flag words), behind the backward of the earlier layers. Memory is tracked per
 segment of the flat parameter space (cut at parameter and shard boundaries), per rank: the kernel's peer loads of a
 gradient segment must be ordered against the owner's weight-gradient writes of this and of the next step, and its peer
-stores of a weight segment against every rank's compute that reads it.
+stores of a weight segment against every rank's compute that reads it. With the bf16 wire format every rank first
+copies its gradient into a wire buffer that the peers read instead: the copy must follow the gradient writes, and the
+next step's copy must follow every peer's read of this step's.
 """
 import bisect
 
@@ -52,10 +54,24 @@ class P2PKernels:
         zp.SIM.collective(("flag", sig, int(epoch)))
         return 0
 
-    def b200_p2p_rs_adamw_ag(self, grads, models, master, m, v, lo, n, rank, world, *rest):
+    def b200_p2p_rs_adamw_ag(self, grads, own, wire16, models, master, m, v, lo, n, state_off, rank, world, *rest):
         segs = list(self.seg.span(lo, lo + n))
-        zp.SIM.add("reduce+adamw+allgather", reads={("grad", r, k) for r in range(world) for k in segs},
+        assert state_off == lo - self.shard_lo
+        if wire16:      # own fp32 gradient + the peers' wire copies
+            reads = {("grad", rank, k) for k in segs} | {("wire", r, k) for r in range(world) if r != rank for k in segs}
+        else:
+            reads = {("grad", r, k) for r in range(world) for k in segs}
+        zp.SIM.add("reduce+adamw+allgather", reads=reads,
                    writes={("model", r, k) for r in range(world) for k in segs} | {("state", rank, k) for k in segs})
+        return 0
+
+    def b200_p2p_mark_step(self, counter, stream):
+        return 0
+
+    def b200_p2p_cast_wire(self, grad, wire, lo, n, stream):
+        segs = list(self.seg.span(lo, lo + n))
+        rank = zp.SIM.rank
+        zp.SIM.add("cast wire", reads={("grad", rank, k) for k in segs}, writes={("wire", rank, k) for k in segs})
         return 0
 
     def b200_p2p_reduce_scatter_f32(self, src, out, lo, n, rank, world, scale, stream):
@@ -86,18 +102,21 @@ class TracedP2P(p2p.P2PComm):
             S.begin_window({("model", self.rank, k) for k in below}, {("grad", self.rank, k) for k in below})
 
 
-def trace_rank(monkeypatch, rank, world, layers, steps, overlap, optimizer="adamw"):
+def trace_rank(monkeypatch, rank, world, layers, steps, overlap, optimizer="adamw", wire=True):
     zp.SIM = S = zp.Sim(rank, world)
     cfg = LlamaConfig(vocab_size=64, hidden_size=32, intermediate_size=64, num_hidden_layers=layers,
                       num_attention_heads=2, num_key_value_heads=1, max_position_embeddings=32)
     model = build_model(cfg, dtype=torch.float32, device="cpu", seed=1)
     comm = TracedP2P("cpu")
+    comm._wire16 = wire
     comm._overlap_enabled = overlap
     comm._buckets = 64                # hand every layer over on its own
     comm.side = zp.FakeStream("S")
     accum = max(len(st) for st in steps)
     eng = DistillEngine(model, loss="kl", temperature=1.0, optimizer=optimizer, lr=1e-3, grad_accum=accum, comm=comm)
     flat = eng.flat
+    if wire:        # the traced model is fp32 (CPU); the schedule of the bf16 wire copy is the same
+        comm.wire_buf = zp.FakeSym(flat.total, torch.bfloat16, "cpu")
     comm.segments = seg = Segments(flat)
     monkeypatch.setattr(zp._lib, "kernels", lambda: P2PKernels(seg, flat.shard_lo, flat.shard_size))
     real_step = eng.opt.step
@@ -123,8 +142,8 @@ def trace_rank(monkeypatch, rank, world, layers, steps, overlap, optimizer="adam
     return S.ops
 
 
-def run(monkeypatch, world, layers, steps, overlap, optimizer="adamw"):
-    traces = [trace_rank(monkeypatch, r, world, layers, steps, overlap, optimizer) for r in range(world)]
+def run(monkeypatch, world, layers, steps, overlap, optimizer="adamw", wire=True):
+    traces = [trace_rank(monkeypatch, r, world, layers, steps, overlap, optimizer, wire) for r in range(world)]
     kinds = {op["kind"] for t in traces for op in t}
     assert "arrive" in kinds and ("reduce+adamw+allgather" in kinds or optimizer != "adamw")
     if overlap and optimizer == "adamw":
@@ -149,11 +168,19 @@ def test_three_ranks_and_the_unfused_optimizers(recorders, monkeypatch):  # noqa
     assert not run(monkeypatch, 2, 2, STEPS["plain"], False, optimizer="sgd")
 
 
+@pytest.mark.parametrize("overlap", [False, True])
+def test_fp32_exchange_without_the_wire_copy(recorders, monkeypatch, overlap):  # noqa: F811
+    assert not run(monkeypatch, 2, 3, STEPS["accumulation"], overlap, wire=False)
+
+
 @pytest.mark.parametrize("what", ["main-stream barriers", "side-stream wait for backward"])
 def test_the_checker_sees_a_removed_ordering(recorders, monkeypatch, what):  # noqa: F811
     if what == "main-stream barriers":
         monkeypatch.setattr(p2p.P2PComm, "barrier", lambda self: None)
         races = run(monkeypatch, 2, 2, STEPS["plain"], False)
+        # peers read the wire copy, not the fp32 gradient: without barriers those reads race with the owner's copy
+        assert any(r.startswith("('model'") for r in races) and any(r.startswith("('wire'") for r in races), races[:5]
+        races = run(monkeypatch, 2, 2, STEPS["plain"], False, wire=False)
         assert any(r.startswith("('model'") for r in races) and any(r.startswith("('grad'") for r in races), races[:5]
     else:
         monkeypatch.setattr(zp.FakeStream, "wait_event", lambda self, ev: None)
