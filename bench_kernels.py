@@ -96,16 +96,58 @@ def bench_gemm(M, N, K, layout, iters, compare=True):
     report(f"gemm_{layout}", ms, flops=2.0 * M * N * K, shape=[M, N, K], **extra)
 
 
-def bench_attn(B, L, H, Hkv, d, iters, bwd):
+def _sm_clock_mhz():
+    """SM clock right now (read through NVML; None when it is not available)."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(torch.cuda.current_device())
+        return int(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM))
+    except Exception:  # noqa: BLE001
+        return None
+
+
+def bench_attn(B, L, H, Hkv, d, iters, bwd, library=True):
+    """This repository's kernels, then the library kernels on the same tensors: flash_attn 2.8 (the reference's
+    ``attn_implementation="flash_attention_2"``) and torch SDPA (its fallback)."""
     qkv = torch.randn(B * L, (H + 2 * Hkv) * d, device="cuda").bfloat16()
     out, lse = attention.attention_fwd(qkv, B, L, H, Hkv, d)
     fl = 4.0 * B * H * L * L * d / 2
     ms = timed(lambda: attention.attention_fwd(qkv, B, L, H, Hkv, d), iters)
-    report("flash_attn_fwd", ms, flops=fl, shape=[B, L, H, Hkv, d])
+    report("flash_attn_fwd", ms, flops=fl, shape=[B, L, H, Hkv, d], sm_mhz=_sm_clock_mhz())
+    dout = torch.randn_like(out)
     if bwd:
-        dout = torch.randn_like(out)
         ms = timed(lambda: attention.attention_bwd(dout, qkv, out, lse, B, L, H, Hkv, d), iters)
-        report("flash_attn_bwd", ms, flops=2.5 * fl, shape=[B, L, H, Hkv, d])
+        report("flash_attn_bwd", ms, flops=2.5 * fl, shape=[B, L, H, Hkv, d], sm_mhz=_sm_clock_mhz())
+    if not library:
+        return
+    q4 = qkv.view(B, L, H + 2 * Hkv, d)
+    q, k, v = (q4[:, :, :H].contiguous().requires_grad_(bwd), q4[:, :, H:H + Hkv].contiguous().requires_grad_(bwd),
+               q4[:, :, H + Hkv:].contiguous().requires_grad_(bwd))
+    do4 = dout.view(B, L, H, d)
+    try:
+        from flash_attn import flash_attn_func
+        o = flash_attn_func(q, k, v, causal=True)
+        ms = timed(lambda: flash_attn_func(q, k, v, causal=True), iters)
+        report("library flash_attn 2 fwd", ms, flops=fl, shape=[B, L, H, Hkv, d], sm_mhz=_sm_clock_mhz())
+        if bwd:
+            ms = timed(lambda: torch.autograd.grad(o, (q, k, v), do4, retain_graph=True), iters)
+            report("library flash_attn 2 bwd", ms, flops=2.5 * fl, shape=[B, L, H, Hkv, d], sm_mhz=_sm_clock_mhz())
+    except Exception as e:  # noqa: BLE001
+        print(json.dumps({"kernel": "library flash_attn 2", "unavailable": f"{type(e).__name__}: {e}"[:200]}), flush=True)
+    try:
+        import torch.nn.functional as F
+        qs, ks, vs = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
+        f = lambda: F.scaled_dot_product_attention(qs, ks, vs, is_causal=True, enable_gqa=True)  # noqa: E731
+        o = f()
+        ms = timed(f, iters)
+        report("library torch sdpa fwd", ms, flops=fl, shape=[B, L, H, Hkv, d], sm_mhz=_sm_clock_mhz())
+        if bwd:
+            dos = do4.transpose(1, 2)
+            ms = timed(lambda: torch.autograd.grad(o, (q, k, v), dos, retain_graph=True), iters)
+            report("library torch sdpa bwd", ms, flops=2.5 * fl, shape=[B, L, H, Hkv, d], sm_mhz=_sm_clock_mhz())
+    except Exception as e:  # noqa: BLE001
+        print(json.dumps({"kernel": "library torch sdpa", "unavailable": f"{type(e).__name__}: {e}"[:200]}), flush=True)
 
 
 def bench_head(M, h, V, K, iters, T=2.0):

@@ -172,49 +172,46 @@ __global__ void __launch_bounds__(NTHREADS, 1)
       const uint32_t sP = smem_u32(smem + C::OFF_P);
       const uint32_t sDS = smem_u32(smem + C::OFF_DS);
       bool ok = mbar_wait_bounded(kv_full, 0, abort_flag, err_word, ERR_WAIT_FULL);
+      // Base descriptors, built once: inside the loop an MMA's operands are a base plus a constant (k-step) and a
+      // stage offset, i.e. one 64-bit add each. (Rebuilding both descriptors per MMA cost the issuing thread ~80
+      // cycles per instruction - more than most of these MMAs occupy the tensor core - and made it the bottleneck.)
+      // The address field counts 16-byte units and never carries out of its 14 bits below 256 KB.
+      const uint32_t sQ0 = smem_u32(smem + C::OFF_QDO), sDO0 = sQ0 + C::QDO_BYTES;
+      const uint64_t kQ = make_smem_desc_sw128(sQ0, 16, 1024), kDO = make_smem_desc_sw128(sDO0, 16, 1024);       // K-major
+      const uint64_t kK = make_smem_desc_sw128(sK, 16, 1024), kV = make_smem_desc_sw128(sV, 16, 1024);
+      const uint64_t kDS = make_smem_desc_sw128(sDS, 16, 1024);
+      const uint64_t tP = make_smem_desc_sw128(sP, BM * 128, 1024), tDS = make_smem_desc_sw128(sDS, BM * 128, 1024);  // MN-major
+      const uint64_t tDO = make_smem_desc_sw128(sDO0, BM * 128, 1024), tQ = make_smem_desc_sw128(sQ0, BM * 128, 1024);
+      const uint64_t tK = make_smem_desc_sw128(sK, BN * 128, 1024);
+      auto koff = [](int k) -> uint64_t {   // k-step inside a K-major tile: 64-column sub-tiles 16 KB apart, 32 B per step
+        return static_cast<uint64_t>(((k >> 2) * (128 * 128) + (k & 3) * 32) >> 4);
+      };
       // S = Q K^T and dP = dO V^T of the pair whose Q / dO sit in stage s
       auto issue_s_dp = [&](int s) {
-        const uint32_t sQ = smem_u32(smem + C::OFF_QDO + s * C::STAGE_BYTES);
-        const uint32_t sDO = sQ + C::QDO_BYTES;
+        const uint64_t stage = static_cast<uint64_t>((s * C::STAGE_BYTES) >> 4);
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k) {
-          const uint32_t sub = k >> 2, kk = k & 3;
-          const uint64_t da = make_smem_desc_sw128(sQ + sub * (BM * 128) + kk * 32, 16, 1024);
-          const uint64_t db = make_smem_desc_sw128(sK + sub * (BN * 128) + kk * 32, 16, 1024);
-          umma_f16_ss(tmem_base + C::S_COL, da, db, idesc_kk, k != 0 ? 1u : 0u);
-        }
+        for (int k = 0; k < D / 16; ++k)
+          umma_f16_ss(tmem_base + C::S_COL, kQ + stage + koff(k), kK + koff(k), idesc_kk, k != 0 ? 1u : 0u);
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k) {
-          const uint32_t sub = k >> 2, kk = k & 3;
-          const uint64_t da = make_smem_desc_sw128(sDO + sub * (BM * 128) + kk * 32, 16, 1024);
-          const uint64_t db = make_smem_desc_sw128(sV + sub * (BN * 128) + kk * 32, 16, 1024);
-          umma_f16_ss(tmem_base + C::DP_COL, da, db, idesc_kk, k != 0 ? 1u : 0u);
-        }
+        for (int k = 0; k < D / 16; ++k)
+          umma_f16_ss(tmem_base + C::DP_COL, kDO + stage + koff(k), kV + koff(k), idesc_kk, k != 0 ? 1u : 0u);
       };
       // dV += P^T dO ; dK += dS^T Q (reduction over the 128 queries, 16 per step = 2048 B per step in both tiles);
       // dQ = dS K (reduction over the 128 keys) into the accumulator at dq_col
       auto issue_dv_dk_dq = [&](int s, int it, uint32_t dq_col) {
-        const uint32_t sQ = smem_u32(smem + C::OFF_QDO + s * C::STAGE_BYTES);
-        const uint32_t sDO = sQ + C::QDO_BYTES;
+        const uint64_t stage = static_cast<uint64_t>((s * C::STAGE_BYTES) >> 4);
+        const uint32_t acc = it != 0 ? 1u : 0u;
 #pragma unroll
-        for (int k = 0; k < BM / 16; ++k) {
-          const uint64_t da = make_smem_desc_sw128(sP + k * 2048, BM * 128, 1024);
-          const uint64_t db = make_smem_desc_sw128(sDO + k * 2048, BM * 128, 1024);
-          umma_f16_ss(tmem_base + C::DV_COL, da, db, idesc_tt, (it | k) != 0 ? 1u : 0u);
-        }
+        for (int k = 0; k < BM / 16; ++k)
+          umma_f16_ss(tmem_base + C::DV_COL, tP + (uint64_t)(k * 128), tDO + stage + (uint64_t)(k * 128), idesc_tt,
+                      k != 0 ? 1u : acc);
 #pragma unroll
-        for (int k = 0; k < BM / 16; ++k) {
-          const uint64_t da = make_smem_desc_sw128(sDS + k * 2048, BM * 128, 1024);
-          const uint64_t db = make_smem_desc_sw128(sQ + k * 2048, BM * 128, 1024);
-          umma_f16_ss(tmem_base + C::DK_COL, da, db, idesc_tt, (it | k) != 0 ? 1u : 0u);
-        }
+        for (int k = 0; k < BM / 16; ++k)
+          umma_f16_ss(tmem_base + C::DK_COL, tDS + (uint64_t)(k * 128), tQ + stage + (uint64_t)(k * 128), idesc_tt,
+                      k != 0 ? 1u : acc);
 #pragma unroll
-        for (int k = 0; k < BN / 16; ++k) {
-          const uint32_t sub = k >> 2, kk = k & 3;
-          const uint64_t da = make_smem_desc_sw128(sDS + sub * (BM * 128) + kk * 32, 16, 1024);
-          const uint64_t db = make_smem_desc_sw128(sK + k * 2048, BN * 128, 1024);
-          umma_f16_ss(tmem_base + dq_col, da, db, idesc_kt, k != 0 ? 1u : 0u);
-        }
+        for (int k = 0; k < BN / 16; ++k)
+          umma_f16_ss(tmem_base + dq_col, kDS + koff(k), tK + (uint64_t)(k * 128), idesc_kt, k != 0 ? 1u : 0u);
       };
       if constexpr (C::PIPE) {
         // Two pairs deep: as soon as the softmax warps have consumed S / dP of pair `it` (pds_ready), the S / dP MMAs

@@ -1,15 +1,22 @@
 // Causal GQA flash-attention forward for sm_100a on tcgen05 tensor cores.
 //
-// One CTA = one (batch, q-head, 128-query block). Roles (192 threads):
-//   warp 0    TMA producer : Q once, then K/V tiles of BN keys through a 2-stage smem ring (3D tensor map
-//                            [B][L][width], so rows past the sequence end read zeros; no multicast)
-//   warp 1    MMA issuer   : S = Q K^T   (tcgen05.mma, both operands K-major, accumulator S in TMEM)
-//                            O += P V    (P from smem as K-major A, V as MN-major B, accumulator O in TMEM)
-//   warps 2-5 softmax      : thread = query row. Reads S from TMEM, causal mask, online softmax in the exp2
-//                            domain, writes P (bf16) into 128B-swizzled smem, rescales O in TMEM only when
-//                            the running max grew by more than 2^8 (lazy rescale), final O / l and lse.
-// S and O live in TMEM (BN + D <= 192 columns, 256 allocated) and smem is ~112 KB, so two CTAs share an SM
-// and overlap each other's MMA and softmax phases.
+// One CTA = one (batch, q-head, 128-query block); keys are walked in tiles of BN = 64. Roles (192 threads):
+//   warp 0    TMA producer : Q once, then K tiles through a 3-stage ring and V tiles through a 2-stage ring (3D tensor
+//                            map [B][L][width], so rows past the sequence end read zeros; no multicast)
+//   warp 1    MMA issuer   : S_j = Q K_j^T (tcgen05.mma, both operands K-major) into one of TWO score buffers in TMEM;
+//                            O += P_j V_j with A = P_j read from TMEM and V_j as MN-major B from shared memory
+//   warps 2-5 softmax      : thread = query row. Reads S_j from TMEM once (both 32-column loads in flight),
+//                            exponentiates against the maximum known so far (exp2 domain, packed f32x2 arithmetic,
+//                            part of the exponentials on the FMA pipe), writes P_j as bf16 pairs over the first half
+//                            of the same score buffer, and only when a score outgrew the maximum by more than 2^8
+//                            moves the maximum, rescales O in TMEM and redoes the tile; final O / l and lse.
+// The score buffers alternate: S_{j+1} is computed while the softmax warps work on S_j, and S_{j+2} goes into S_j's
+// buffer as soon as P_j V_j has been issued (MMAs of one thread execute in order), so in the steady state the
+// softmax warps never wait for the tensor core and the tensor core never waits for them.
+// P never touches shared memory: an N = D MMA fed from shared memory on both sides is bound by shared-memory
+// bandwidth, and the softmax warps issue no st.shared and no proxy fence.
+// TMEM: 2 x 64 score columns + D output columns (<= 256); shared memory 56 KB (D = 64) / 112 KB (D = 128): two CTAs
+// share an SM.
 //
 // Layout: qkv [T, (H + 2*Hkv) * D] bf16 with T = B*L; out [T, H*D] bf16; lse [H, T] fp32 (natural log).
 #include "../common/ptx.cuh"
@@ -19,25 +26,24 @@ namespace b200 {
 namespace fa {
 
 constexpr int BM = 128;
+constexpr int BN = 64;
 constexpr int NTHREADS = 192;
+constexpr int KS = 3;  // K ring
+constexpr int VS = 2;  // V ring
 constexpr float kRescaleThreshold = 8.0f;  // in log2 units
 
 template <int D>
 struct Cfg {
-  static constexpr int BN = (D == 64) ? 128 : 64;
   static constexpr int Q_BYTES = BM * D * 2;
-  static constexpr int K_BYTES = BN * D * 2;
-  static constexpr int V_BYTES = BN * D * 2;
-  static constexpr int STAGE_BYTES = K_BYTES + V_BYTES;
-  static constexpr int P_BYTES = BM * BN * 2;
-  static constexpr int STAGES = 2;
-  static constexpr int OFF_KV = Q_BYTES;
-  static constexpr int OFF_P = OFF_KV + STAGES * STAGE_BYTES;
-  static constexpr int OFF_BAR = OFF_P + P_BYTES;
+  static constexpr int T_BYTES = BN * D * 2;  // one K or V tile
+  static constexpr int OFF_K = Q_BYTES;
+  static constexpr int OFF_V = OFF_K + KS * T_BYTES;
+  static constexpr int OFF_BAR = OFF_V + VS * T_BYTES;
   static constexpr int SMEM_BYTES = OFF_BAR + 256;
   static constexpr uint32_t TMEM_COLS = 256;
-  static constexpr uint32_t S_COL = 0;
-  static constexpr uint32_t O_COL = BN;
+  static constexpr uint32_t S_COL = 0;        // two buffers of BN columns; P_j overwrites columns [0, BN/2) of S_j
+  static constexpr uint32_t O_COL = 2 * BN;
+  static_assert(2 * BN + D <= 256, "TMEM budget");
 };
 
 struct FwdParams {
@@ -47,21 +53,39 @@ struct FwdParams {
   float scale;  // 1/sqrt(D)
 };
 
+// 2^x for x <= 0 (and a little above) on the FMA pipe: round-to-nearest split x = n + f, f in [-0.5, 0.5], a quartic
+// for 2^f (relative error 4e-5, far below bf16 resolution), n added into the exponent field. The MUFU unit does 16
+// exponentials per clock and SM, which is what bounds this kernel; taking a share of them off it is worth the
+// extra FMA-pipe instructions.
+__device__ __forceinline__ float poly_exp2(float x) {
+  x = fmaxf(x, -126.f);
+  const float magic = 12582912.f;  // 1.5 * 2^23: adding it rounds to an integer in the low mantissa bits
+  const float xr = x + magic;
+  const float f = x - (xr - magic);
+  float pl = fmaf(f, 0.0096181291f, 0.0555041087f);
+  pl = fmaf(pl, f, 0.2402265070f);
+  pl = fmaf(pl, f, 0.6931471806f);
+  pl = fmaf(pl, f, 1.0f);
+  return __int_as_float(__float_as_int(pl) + (__float_as_int(xr) << 23));
+}
+
 template <int D>
 __global__ void __launch_bounds__(NTHREADS, 2)
     flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmKV, FwdParams p,
                      unsigned int* err_word) {
   using C = Cfg<D>;
-  constexpr int BN = C::BN;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
   uint64_t* q_full = bars + 0;
-  uint64_t* kv_full = bars + 1;   // [2]
-  uint64_t* kv_empty = bars + 3;  // [2]
-  uint64_t* s_full = bars + 5;
-  uint64_t* p_ready = bars + 6;
-  uint64_t* o_done = bars + 7;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  uint64_t* k_full = bars + 1;    // [KS]
+  uint64_t* k_empty = bars + 4;   // [KS]
+  uint64_t* v_full = bars + 7;    // [VS]
+  uint64_t* v_empty = bars + 9;   // [VS]
+  uint64_t* s_full = bars + 11;   // [2]
+  uint64_t* p_ready = bars + 13;  // [2]
+  uint64_t* o_done = bars + 15;
+  uint64_t* o_final = bars + 16;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -81,13 +105,20 @@ __global__ void __launch_bounds__(NTHREADS, 2)
     tma_prefetch_desc(&tmQ);
     tma_prefetch_desc(&tmKV);
     mbar_init(q_full, 1);
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(&kv_full[s], 1);
-      mbar_init(&kv_empty[s], 1);
+    for (int s = 0; s < KS; ++s) {
+      mbar_init(&k_full[s], 1);
+      mbar_init(&k_empty[s], 1);
     }
-    mbar_init(s_full, 1);
-    mbar_init(p_ready, 128);
+    for (int s = 0; s < VS; ++s) {
+      mbar_init(&v_full[s], 1);
+      mbar_init(&v_empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&s_full[s], 1);
+      mbar_init(&p_ready[s], 128);
+    }
     mbar_init(o_done, 1);
+    mbar_init(o_final, 1);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -110,71 +141,77 @@ __global__ void __launch_bounds__(NTHREADS, 2)
 #pragma unroll
       for (int c = 0; c < D / 64; ++c) tma_load_3d(smem + c * (BM * 128), &tmQ, q_full, colQ + c * 64, q0, b);
       for (int j = 0; j < n_kv; ++j) {
-        const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1u;
-        if (!mbar_wait_bounded(&kv_empty[s], ph ^ 1u, abort_flag, err_word, ERR_WAIT_EMPTY)) break;
-        uint8_t* sK = smem + C::OFF_KV + s * C::STAGE_BYTES;
-        uint8_t* sV = sK + C::K_BYTES;
-        mbar_arrive_expect_tx(&kv_full[s], C::STAGE_BYTES);
+        // K_j runs two tiles ahead of the softmax, V_j is only needed when P_j exists: separate rings
+        const int ks = j % KS, vs = j % VS;
+        if (!mbar_wait_bounded(&k_empty[ks], ((j / KS) & 1u) ^ 1u, abort_flag, err_word, ERR_WAIT_EMPTY)) break;
+        uint8_t* sK = smem + C::OFF_K + ks * C::T_BYTES;
+        mbar_arrive_expect_tx(&k_full[ks], C::T_BYTES);
 #pragma unroll
-        for (int c = 0; c < D / 64; ++c) {
-          tma_load_3d(sK + c * (BN * 128), &tmKV, &kv_full[s], colK + c * 64, j * BN, b);
-          tma_load_3d(sV + c * (BN * 128), &tmKV, &kv_full[s], colV + c * 64, j * BN, b);
-        }
+        for (int c = 0; c < D / 64; ++c) tma_load_3d(sK + c * (BN * 128), &tmKV, &k_full[ks], colK + c * 64, j * BN, b);
+        if (!mbar_wait_bounded(&v_empty[vs], ((j / VS) & 1u) ^ 1u, abort_flag, err_word, ERR_WAIT_EMPTY)) break;
+        uint8_t* sV = smem + C::OFF_V + vs * C::T_BYTES;
+        mbar_arrive_expect_tx(&v_full[vs], C::T_BYTES);
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c) tma_load_3d(sV + c * (BN * 128), &tmKV, &v_full[vs], colV + c * 64, j * BN, b);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t idesc_s = make_idesc_f16(1, BM, BN, 0, 0);
       const uint32_t idesc_o = make_idesc_f16(1, BM, D, 0, 1);
-      const uint32_t sQ = smem_u32(smem);
-      const uint32_t sP = smem_u32(smem + C::OFF_P);
+      // Every shared-memory descriptor of the loop is a constant plus a stage offset: they are built once here, so
+      // that issuing an MMA costs a 64-bit add and the instruction itself. (With the descriptors rebuilt per MMA the
+      // issuing thread needed ~80 cycles per instruction, more than a 128 x 64 x 16 MMA occupies the tensor core.)
+      uint64_t dQ[D / 16], dK[D / 16], dV[BN / 16];
+#pragma unroll
+      for (int k = 0; k < D / 16; ++k) {
+        const uint32_t sub = k >> 2, kk = k & 3;   // 64-column sub-tiles are BM*128 (Q) / BN*128 (K) bytes apart
+        dQ[k] = make_smem_desc_sw128(smem_u32(smem) + sub * (BM * 128) + kk * 32, 16, 1024);
+        dK[k] = make_smem_desc_sw128(smem_u32(smem + C::OFF_K) + sub * (BN * 128) + kk * 32, 16, 1024);
+      }
+#pragma unroll
+      for (int k = 0; k < BN / 16; ++k)   // V is MN-major (D contiguous), 64-wide D chunks BN*128 bytes apart
+        dV[k] = make_smem_desc_sw128(smem_u32(smem + C::OFF_V) + k * (16 * 128), BN * 128, 1024);
       bool ok = mbar_wait_bounded(q_full, 0, abort_flag, err_word, ERR_WAIT_FULL);
-      // S = Q K^T for the K tile in stage s: D/16 k-steps; 64-column sub-tiles are BM*128 (Q) / BN*128 (K) bytes apart
-      auto issue_s = [&](int s) {
-        const uint32_t sK = smem_u32(smem + C::OFF_KV + s * C::STAGE_BYTES);
-#pragma unroll
-        for (int k = 0; k < D / 16; ++k) {
-          const uint32_t sub = k >> 2, kk = k & 3;
-          const uint64_t da = make_smem_desc_sw128(sQ + sub * (BM * 128) + kk * 32, 16, 1024);
-          const uint64_t db = make_smem_desc_sw128(sK + sub * (BN * 128) + kk * 32, 16, 1024);
-          umma_f16_ss(tmem_base + C::S_COL, da, db, idesc_s, k != 0 ? 1u : 0u);
-        }
-      };
-      if (ok && n_kv > 0) {
-        ok = mbar_wait_bounded(&kv_full[0], 0, abort_flag, err_word, ERR_WAIT_FULL);
-        if (ok) {
-          tc_fence_after_sync();
-          issue_s(0);
-          umma_commit(s_full);
-        }
-      }
-      for (int j = 0; ok && j < n_kv; ++j) {
-        const int s = j & 1;
-        // wait for P_j (and the O rescale) from the softmax warps: S is free again from here on
-        if (!mbar_wait_bounded(p_ready, j & 1u, abort_flag, err_word, ERR_WAIT_AUX)) break;
+      // S_t = Q K_t^T into score buffer t & 1
+      auto issue_s = [&](int t) -> bool {
+        const int ks = t % KS;
+        if (!mbar_wait_bounded(&k_full[ks], (t / KS) & 1u, abort_flag, err_word, ERR_WAIT_FULL)) return false;
         tc_fence_after_sync();
-        if (j + 1 < n_kv) {
-          // the next tile's scores go to the tensor core AHEAD of this tile's P V, so that the softmax warps find
-          // S_{j+1} ready as soon as they are done with tile j
-          const int s1 = (j + 1) & 1;
-          if (!mbar_wait_bounded(&kv_full[s1], ((j + 1) >> 1) & 1u, abort_flag, err_word, ERR_WAIT_FULL)) break;
-          tc_fence_after_sync();
-          issue_s(s1);
-          umma_commit(s_full);
-        }
-        const uint32_t sV = smem_u32(smem + C::OFF_KV + s * C::STAGE_BYTES) + C::K_BYTES;
-        // O += P V : BN/16 k-steps over keys; V is MN-major (D contiguous), 64-wide D chunks BN*128 bytes apart
+        const uint64_t stage = static_cast<uint64_t>((ks * C::T_BYTES) >> 4);   // the address field counts 16-byte units
+        const uint32_t dcol = tmem_base + C::S_COL + (t & 1) * BN;
 #pragma unroll
-        for (int k = 0; k < BN / 16; ++k) {
-          const uint32_t sub = k >> 2, kk = k & 3;
-          const uint64_t da = make_smem_desc_sw128(sP + sub * (BM * 128) + kk * 32, 16, 1024);
-          const uint64_t db = make_smem_desc_sw128(sV + k * (16 * 128), BN * 128, 1024);
-          umma_f16_ss(tmem_base + C::O_COL, da, db, idesc_o, (j | k) != 0 ? 1u : 0u);
+        for (int k = 0; k < D / 16; ++k) umma_f16_ss(dcol, dQ[k], dK[k] + stage, idesc_s, k != 0 ? 1u : 0u);
+        umma_commit(&k_empty[ks]);
+        umma_commit(&s_full[t & 1]);
+        return true;
+      };
+      for (int t = 0; ok && t < 2 && t < n_kv; ++t) ok = issue_s(t);
+      for (int j = 0; ok && j < n_kv; ++j) {
+        const int bsel = j & 1, vs = j % VS;
+        // P_j is in TMEM (over the first half of S_j) once the softmax warps have arrived
+        if (!mbar_wait_bounded(&p_ready[bsel], (j >> 1) & 1u, abort_flag, err_word, ERR_WAIT_AUX)) break;
+        if (!mbar_wait_bounded(&v_full[vs], (j / VS) & 1u, abort_flag, err_word, ERR_WAIT_FULL)) break;
+        tc_fence_after_sync();
+        const uint64_t stage = static_cast<uint64_t>((vs * C::T_BYTES) >> 4);
+        const uint32_t pcol = tmem_base + C::S_COL + bsel * BN;
+        // O += P V : BN/16 k-steps over keys. A = P from TMEM (16 bf16 of a row = 8 columns per step)
+        if (j == 0) {
+#pragma unroll
+          for (int k = 0; k < BN / 16; ++k)
+            umma_f16_ts(tmem_base + C::O_COL, pcol + k * 8, dV[k] + stage, idesc_o, k != 0 ? 1u : 0u);
+        } else {
+#pragma unroll
+          for (int k = 0; k < BN / 16; ++k) umma_f16_ts(tmem_base + C::O_COL, pcol + k * 8, dV[k] + stage, idesc_o, 1u);
         }
-        umma_commit(&kv_empty[s]);
+        umma_commit(&v_empty[vs]);
         umma_commit(o_done);
+        // the buffer that held S_j / P_j takes S_{j+2}: it executes behind P_j V_j, which is what frees the buffer
+        if (j + 2 < n_kv) ok = issue_s(j + 2);
       }
+      // its own barrier for the very last P V: the softmax warps do not follow o_done tile by tile, so its parity
+      // alone would not tell them which of the last two tiles has completed
+      if (ok) umma_commit(o_final);
     }
   } else {
     // ------------------------------------------------------------------ softmax / epilogue
@@ -183,132 +220,124 @@ __global__ void __launch_bounds__(NTHREADS, 2)
     const int qi = q0 + r;           // position in the sequence
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
     const float c2 = p.scale * 1.4426950408889634f;  // scores -> log2 domain
+    const uint64_t c2p = pack_f32x2(c2, c2);
+    const uint32_t tO = tmem_base + lane_addr + C::O_COL;
     float m_used = -INFINITY, l = 0.f;
-    uint8_t* sP = smem + C::OFF_P;
     bool ok = true;
+
+    // One 32-column chunk of scores -> probabilities (bf16 pairs) with the running maximum and the row sum.
+    // `lim`: columns of this chunk with index <= lim are visible (>= 31: all of them). Every fourth pair of
+    // exponentials is evaluated on the FMA pipe.
+    auto chunk = [&](const uint32_t (&v)[32], const uint64_t nmb, const int lim, float& mx, uint64_t& sum2,
+                     uint32_t (&pk)[16]) {
+      if (lim >= 31) {
+#pragma unroll
+        for (int t = 0; t < 32; t += 2) {
+          const float s0 = __uint_as_float(v[t]), s1 = __uint_as_float(v[t + 1]);
+          mx = fmax3(mx, s0, s1);
+          float x0, x1;
+          unpack_f32x2(fma_f32x2(pack_f32x2(s0, s1), c2p, nmb), x0, x1);
+          const bool poly = (t & 6) == 6;
+          const float p0 = poly ? poly_exp2(x0) : fast_exp2(x0);
+          const float p1 = poly ? poly_exp2(x1) : fast_exp2(x1);
+          sum2 = add_f32x2(sum2, pack_f32x2(p0, p1));
+          pk[t >> 1] = pack_bf16x2(p0, p1);
+        }
+      } else {
+#pragma unroll
+        for (int t = 0; t < 32; t += 2) {
+          const float s0 = t <= lim ? __uint_as_float(v[t]) : -INFINITY;
+          const float s1 = (t + 1) <= lim ? __uint_as_float(v[t + 1]) : -INFINITY;
+          mx = fmax3(mx, s0, s1);
+          float x0, x1;
+          unpack_f32x2(fma_f32x2(pack_f32x2(s0, s1), c2p, nmb), x0, x1);
+          const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);   // exp2(-inf) = 0 for the masked columns
+          sum2 = add_f32x2(sum2, pack_f32x2(p0, p1));
+          pk[t >> 1] = pack_bf16x2(p0, p1);
+        }
+      }
+    };
+
     for (int j = 0; j < n_kv; ++j) {
-      int w = mbar_wait_bounded(s_full, j & 1u, abort_flag, err_word, ERR_WAIT_TMEM_FULL) ? 1 : 0;
+      const int bsel = j & 1;
+      const uint32_t tS = tmem_base + lane_addr + C::S_COL + bsel * BN;
+      int w = mbar_wait_bounded(&s_full[bsel], (j >> 1) & 1u, abort_flag, err_word, ERR_WAIT_TMEM_FULL) ? 1 : 0;
       if (!__all_sync(0xffffffffu, w)) { ok = false; break; }
       tc_fence_after_sync();
       const int kv0 = j * BN;
-      const bool diag = (kv0 + BN - 1) > q0;  // some keys of this tile may be masked for some rows
-      // pass 1: row max (the masked variant only runs on tiles that cross the diagonal)
-      float mx = -INFINITY;
-      if (!diag) {
+      const bool diag = (kv0 + BN - 1) > q0;                 // some keys of this tile are masked for some rows
+      const int lim = diag ? (qi - kv0) : 0x3fffffff;        // tile columns <= lim are visible to this row
+      uint32_t va[32], vb[32], pka[16], pkb[16];
+      tmem_ld_32x32b_x32(tS, va);
+      tmem_ld_32x32b_x32(tS + 32, vb);
+      tmem_ld_wait();
+      if (j == 0) {
+        // The first tile fixes the reference maximum (every row sees key 0, so it is finite). Later tiles are
+        // exponentiated against the maximum known so far and only redone when a score exceeds it by more than
+        // 2^kRescaleThreshold, which is rare once a row has seen a few hundred keys.
+        float mx0 = -INFINITY;
 #pragma unroll
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t v[32];
-          tmem_ld_32x32b_x32(tmem_base + lane_addr + C::S_COL + c * 32, v);
-          tmem_ld_wait();
-          float m0 = -INFINITY, m1 = -INFINITY;
-#pragma unroll
-          for (int t = 0; t < 32; t += 2) {
-            m0 = fmaxf(m0, __uint_as_float(v[t]));
-            m1 = fmaxf(m1, __uint_as_float(v[t + 1]));
-          }
-          mx = fmaxf(mx, fmaxf(m0, m1));
+        for (int t = 0; t < 32; t += 2) {
+          mx0 = fmax3(mx0, t <= lim ? __uint_as_float(va[t]) : -INFINITY,
+                      (t + 1) <= lim ? __uint_as_float(va[t + 1]) : -INFINITY);
+          mx0 = fmax3(mx0, (t + 32) <= lim ? __uint_as_float(vb[t]) : -INFINITY,
+                      (t + 33) <= lim ? __uint_as_float(vb[t + 1]) : -INFINITY);
         }
-      } else {
-        const int lim = qi - kv0;  // columns <= lim are visible
-#pragma unroll
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t v[32];
-          tmem_ld_32x32b_x32(tmem_base + lane_addr + C::S_COL + c * 32, v);
-          tmem_ld_wait();
-#pragma unroll
-          for (int t = 0; t < 32; ++t)
-            mx = fmaxf(mx, (c * 32 + t) <= lim ? __uint_as_float(v[t]) : -INFINITY);
-        }
+        m_used = mx0;
       }
-      float alpha = 1.f;
-      bool need = false;
-      if (mx > m_used) {
-        if (m_used == -INFINITY) {
-          m_used = mx;  // first tile with a visible key: nothing accumulated yet for this row
-          need = (j > 0);
-          alpha = 0.f;  // anything accumulated so far came from fully masked tiles (all-zero P)
-        } else if ((mx - m_used) * c2 > kRescaleThreshold) {
-          alpha = exp2f((m_used - mx) * c2);
-          m_used = mx;
-          need = true;
-        }
-      }
-      l *= alpha;
-      // P smem is single-buffered and O is about to be touched: the previous P*V must be complete
-      if (j > 0) {
-        int w2 = mbar_wait_bounded(o_done, (j - 1) & 1u, abort_flag, err_word, ERR_WAIT_AUX) ? 1 : 0;
-        if (!__all_sync(0xffffffffu, w2)) { ok = false; break; }
-        tc_fence_after_sync();
-      }
-      // pass 2: p = exp2((s - m) * c2) -> bf16 -> swizzled smem ; l += sum(p)
-      const float mb = (m_used == -INFINITY) ? 0.f : m_used * c2;
-      float lsum = 0.f, lsum1 = 0.f;
-      const int lim2 = diag ? (qi - kv0) : 0x7fffffff;
-#pragma unroll
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(tmem_base + lane_addr + C::S_COL + c * 32, v);
-        tmem_ld_wait();
-        uint32_t pk[16];
-        if (!diag) {
-#pragma unroll
-          for (int t = 0; t < 32; t += 2) {
-            const float p0 = fast_exp2(fmaf(__uint_as_float(v[t]), c2, -mb));
-            const float p1 = fast_exp2(fmaf(__uint_as_float(v[t + 1]), c2, -mb));
-            lsum += p0;
-            lsum1 += p1;
-            pk[t >> 1] = pack_bf16x2(p0, p1);
-          }
-        } else {
-#pragma unroll
-          for (int t = 0; t < 32; t += 2) {
-            float p0 = fast_exp2(fmaf(__uint_as_float(v[t]), c2, -mb));
-            float p1 = fast_exp2(fmaf(__uint_as_float(v[t + 1]), c2, -mb));
-            if ((c * 32 + t) > lim2) p0 = 0.f;
-            if ((c * 32 + t + 1) > lim2) p1 = 0.f;
-            lsum += p0;
-            lsum1 += p1;
-            pk[t >> 1] = pack_bf16x2(p0, p1);
-          }
-        }
-        // columns c*32 .. c*32+31 of row r: sub-tile (c*32)/64, 16-byte chunks ((c*32)%64)/8 + {0..3}
-        const int sub = (c * 32) >> 6;
-        const int chunk0 = ((c * 32) & 63) >> 3;
-        uint8_t* rowp = sP + sub * (BM * 128) + r * 128;
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          const int ch = (chunk0 + q4) ^ (r & 7);
-          *reinterpret_cast<uint4*>(rowp + ch * 16) =
-              make_uint4(pk[q4 * 4], pk[q4 * 4 + 1], pk[q4 * 4 + 2], pk[q4 * 4 + 3]);
-        }
-      }
-      lsum += lsum1;
-      l += lsum;
-      // lazy rescale of the O accumulator (warp-uniform decision: tcgen05.ld/st are warp-collective)
+      float mx = m_used;
+      uint64_t sum2 = 0ull;
+      uint64_t nmb = pack_f32x2(-m_used * c2, -m_used * c2);
+      chunk(va, nmb, lim, mx, sum2, pka);
+      chunk(vb, nmb, lim - 32, mx, sum2, pkb);
+      const bool need = (mx - m_used) * c2 > kRescaleThreshold;
       if (__any_sync(0xffffffffu, need)) {
+        // a score outgrew the reference maximum: move the maximum, rescale what is accumulated, redo the tile
+        // (warp-uniform: tcgen05.ld / st are warp-collective; rows that did not need it repeat their own values).
+        // O belongs to the previous tile's P V until that MMA is done.
+        const float alpha = need ? fast_exp2((m_used - mx) * c2) : 1.f;
+        if (need) m_used = mx;
+        l *= alpha;
+        if (j > 0) {
+          int w2 = mbar_wait_bounded(o_done, (j - 1) & 1u, abort_flag, err_word, ERR_WAIT_AUX) ? 1 : 0;
+          if (!__all_sync(0xffffffffu, w2)) { ok = false; break; }
+          tc_fence_after_sync();
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t v[32];
-          tmem_ld_32x32b_x32(tmem_base + lane_addr + C::O_COL + c * 32, v);
-          tmem_ld_wait();
-          uint32_t lo[16], hi[16];
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t v[32];
+            tmem_ld_32x32b_x32(tO + c * 32, v);
+            tmem_ld_wait();
+            uint32_t lo[16], hi[16];
 #pragma unroll
-          for (int t = 0; t < 16; ++t) {
-            lo[t] = __float_as_uint(__uint_as_float(v[t]) * alpha);
-            hi[t] = __float_as_uint(__uint_as_float(v[16 + t]) * alpha);
+            for (int t = 0; t < 16; ++t) {
+              lo[t] = __float_as_uint(__uint_as_float(v[t]) * alpha);
+              hi[t] = __float_as_uint(__uint_as_float(v[16 + t]) * alpha);
+            }
+            tmem_st_32x32b_x16(tO + c * 32, lo);
+            tmem_st_32x32b_x16(tO + c * 32 + 16, hi);
           }
-          tmem_st_32x32b_x16(tmem_base + lane_addr + C::O_COL + c * 32, lo);
-          tmem_st_32x32b_x16(tmem_base + lane_addr + C::O_COL + c * 32 + 16, hi);
         }
-        tmem_st_wait();
+        nmb = pack_f32x2(-m_used * c2, -m_used * c2);
+        sum2 = 0ull;
+        float mx2 = m_used;
+        chunk(va, nmb, lim, mx2, sum2, pka);
+        chunk(vb, nmb, lim - 32, mx2, sum2, pkb);
       }
-      fence_proxy_async_smem();  // generic-proxy smem writes -> visible to the tensor core (async proxy)
+      // P_j over the first half of S_j (both halves of S_j are in registers by now)
+      tmem_st_32x32b_x16(tS, pka);
+      tmem_st_32x32b_x16(tS + 16, pkb);
+      {
+        float s0, s1;
+        unpack_f32x2(sum2, s0, s1);
+        l += s0 + s1;
+      }
+      tmem_st_wait();
       tc_fence_before_sync();
-      mbar_arrive(p_ready);
+      mbar_arrive(&p_ready[bsel]);
     }
     // epilogue: O / l -> bf16, lse
     if (ok) {
-      int w3 = mbar_wait_bounded(o_done, (n_kv - 1) & 1u, abort_flag, err_word, ERR_WAIT_AUX) ? 1 : 0;
+      int w3 = mbar_wait_bounded(o_final, 0, abort_flag, err_word, ERR_WAIT_AUX) ? 1 : 0;
       if (__all_sync(0xffffffffu, w3)) {
         tc_fence_after_sync();
         const float inv = l > 0.f ? 1.f / l : 0.f;
@@ -318,7 +347,7 @@ __global__ void __launch_bounds__(NTHREADS, 2)
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
           uint32_t v[32];
-          tmem_ld_32x32b_x32(tmem_base + lane_addr + C::O_COL + c * 32, v);
+          tmem_ld_32x32b_x32(tO + c * 32, v);
           tmem_ld_wait();
           if (row_ok) {
 #pragma unroll
@@ -360,7 +389,7 @@ static int launch_fwd(const void* qkv, void* out, float* lse, int B, int L, int 
                         (uint64_t)width * 2, (uint64_t)L * width * 2, 64, BM, 1, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != B200_OK) return rc;
   rc = make_tmap_3d(&tmKV, qkv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)width, (uint64_t)L, (uint64_t)B,
-                    (uint64_t)width * 2, (uint64_t)L * width * 2, 64, C::BN, 1, CU_TENSOR_MAP_SWIZZLE_128B);
+                    (uint64_t)width * 2, (uint64_t)L * width * 2, 64, BN, 1, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != B200_OK) return rc;
   auto kern = flash_fwd_kernel<D>;
   static bool attr = false;
