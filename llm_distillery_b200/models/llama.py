@@ -237,6 +237,9 @@ LAYER_BACKWARD_DONE = [None]
 # + head - reads its parameters, in forward and again at the start of a layer's backward: the full-shard engine
 # (parallel/fsdp.py) gathers that unit's weights there and starts gathering the next one.
 UNIT_PRE = [None]
+# Called with a decoder layer's first parameter just before the layer's matrices are read, in forward and at the start
+# of its backward: frozen low-bit weights (ops/quant.py) are expanded into their bf16 buffer there.
+LAYER_WEIGHTS_PRE = [None]
 
 
 class DecoderLayerFn(torch.autograd.Function):
@@ -274,6 +277,8 @@ class DecoderLayerFn(torch.autograd.Function):
         s_ln1, s_qkv, s_o, s_ln2, s_gu, s_d = ctx.slots
         if UNIT_PRE[0] is not None:
             UNIT_PRE[0](w_ln1, True)
+        if LAYER_WEIGHTS_PRE[0] is not None:
+            LAYER_WEIGHTS_PRE[0](w_ln1)
         if recompute:
             h, pos, cos, sin = ctx.saved_tensors
             n1, _, rstd1 = basic.rmsnorm_fwd(h, w_ln1, eps)
@@ -387,6 +392,7 @@ class LlamaModel(nn.Module):
             self.lm_head = nn.Parameter(torch.empty(cfg.vocab_size, cfg.hidden_size, **kw))
         self.grad_checkpointing = False
         self._rope = None
+        self.quant = None          # FrozenQuantLinears when the decoder layers' matrices are frozen NF4 / int8
 
     # ---- init / tables
     @torch.no_grad()
@@ -435,6 +441,8 @@ class LlamaModel(nn.Module):
         for layer in self.layers:
             if pre is not None:
                 pre(layer.input_layernorm, False)
+            if LAYER_WEIGHTS_PRE[0] is not None:
+                LAYER_WEIGHTS_PRE[0](layer.input_layernorm)
             h = DecoderLayerFn.apply(h, pos, cos, sin, layer.input_layernorm, layer.qkv_proj, layer.o_proj,
                                      layer.post_attention_layernorm, layer.gate_up_proj, layer.down_proj, meta,
                                      getattr(layer, "qkv_bias", None))
@@ -481,7 +489,26 @@ class LlamaModel(nn.Module):
             yield "lm_head.weight", self.lm_head, None
 
     def to_hf_state_dict(self) -> dict[str, torch.Tensor]:
-        return {n: (p.data if sl is None else p.data[sl]) for n, p, sl in self.named_hf_parameters()}
+        if self.quant is None:
+            return {n: (p.data if sl is None else p.data[sl]) for n, p, sl in self.named_hf_parameters()}
+        # frozen low-bit matrices live packed; their parameters are views of a rotating buffer: export dequantised copies
+        out, fresh = {}, {}
+        for i, layer in enumerate(self.layers):
+            for name, t in self.quant.dequantized(i).items():
+                fresh[id(getattr(layer, name))] = t
+        for n, p, sl in self.named_hf_parameters():
+            src = fresh.get(id(p), p.data)
+            out[n] = src if sl is None else src[sl]
+        return out
+
+    def quantize_frozen_linears(self, kind: str) -> "LlamaModel":
+        """Turns the decoder layers' matrices into frozen NF4 (``"nf4"``) or int8 weights: what the reference's
+        ``training_precision`` 4bit / 8bit do through bitsandbytes (classes/student/model.py:138-148). Embeddings,
+        norms and the LM head stay in the compute dtype and keep training."""
+        from ..ops.quant import FrozenQuantLinears
+        self.quant = FrozenQuantLinears(self, kind)
+        LAYER_WEIGHTS_PRE[0] = self.quant.before_layer
+        return self
 
     @torch.no_grad()
     def load_hf_state_dict(self, sd: dict[str, torch.Tensor], strict: bool = True) -> None:

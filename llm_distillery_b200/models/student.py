@@ -91,15 +91,33 @@ class StudentModel(BaseModel):
 
     # ------------------------------------------------------------------ model / optimizer
     def _dtype(self, device: torch.device) -> torch.dtype:
-        """Compute dtype. On a GPU every precision name runs the bf16 tensor-core kernels with fp32 master
-        weights and optimizer state (fp16 / bitsandbytes 4-bit / 8-bit weights have no counterpart here);
-        on CPU everything is fp32."""
-        return torch.bfloat16 if device.type == "cuda" else torch.float32
+        """Compute dtype for ``training_precision`` (reference: classes/student/model.py:121-148).
+
+        ``bf16``: bf16 tensor-core kernels, fp32 master weights and optimizer state. ``4bit`` / ``8bit``: the same
+        compute, with the decoder layers' matrices frozen as NF4 / int8 weights (``_load_model``). ``fp32`` and
+        ``fp16`` name compute types these kernels do not have: on a GPU they are refused rather than silently run in
+        bf16. On CPU (the restatement that the tests and the plumbing configuration run) everything is fp32."""
+        if device.type != "cuda":
+            return torch.float32
+        name = (self.training_precision_name or "bf16").lower()
+        if name in ("fp32", "fp16"):
+            raise ValueError(f"training_precision = {name!r} is not available on GPUs here: the kernels compute in bf16 "
+                             "with fp32 accumulation, fp32 master weights and fp32 optimizer state. Set "
+                             "training_precision to 'bf16' (or to '4bit' / '8bit' for frozen low-bit base weights).")
+        return torch.bfloat16
 
     def _load_model(self) -> None:
         dev = torch.device(self.device)
         self.model = ckpt.load_hf_model(self.model_path, dtype=self._dtype(dev), device=dev)
         self.model.grad_checkpointing = bool(self.grad_checkpointing)
+        name = (self.training_precision_name or "bf16").lower()
+        if name in ("4bit", "8bit"):
+            self.model.quantize_frozen_linears("nf4" if name == "4bit" else "int8")
+            if self.rank == 0 and not getattr(self, "_quant_note_done", False):
+                q = self.model.quant
+                print(f"training_precision {name}: the decoder layers' matrices are frozen {q.kind} weights "
+                      f"({q.packed_bytes() / 2 ** 30:.2f} GiB packed); embeddings, norms and the LM head train.")
+                self._quant_note_done = True
         if self.freeze_layers:
             self.model.apply_freeze(self.freeze_layers)
         schedule = set_lr_scheduler(self.lr_scheduler_name, self.lr, self.num_warmup_steps, self.num_grad_accum_batches,

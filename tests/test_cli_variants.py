@@ -24,6 +24,8 @@ CASES = {
     "no validation set": {"validation_dataset_path": ""},
     "frozen MLPs": {"freeze_layers": [".mlp."]},
     "bf16 on CPU": {"training_precision": "bf16"},
+    "4bit: frozen NF4 decoder matrices": {"training_precision": "4bit"},
+    "8bit: frozen int8 decoder matrices": {"training_precision": "8bit"},
     "shuffled, checkpointing, accumulation of 3": {"data_order": "shuffle", "grad_checkpointing": True, "grad_accum_batches": 3},
     "native order, context 48": {"data_order": "native", "context_len": 48},
     "top-K above the crop": {"save_topK": 600},
@@ -87,6 +89,15 @@ def test_cli_case(world, name):
     sd, init = load_hf_state_dict(os.path.join(trained, finals[0])), load_hf_state_dict(os.path.join(root, "student"))
     moved = {k: float((sd[k].float() - init[k].float()).abs().max()) for k in init}
     assert max(moved.values()) > 1e-5
+    if name[:4] in ("4bit", "8bit"):
+        # the decoder matrices are frozen at their quantised values: what is saved differs from the checkpoint by the
+        # quantisation error only, and embeddings / norms / head are what trained
+        from llm_distillery_b200.ops import quant
+        w0 = init["model.layers.0.mlp.down_proj.weight"].float()
+        q = (quant.quantize_nf4 if name[0] == "4" else quant.quantize_int8)(w0)
+        assert np.allclose(sd["model.layers.0.mlp.down_proj.weight"].float().numpy(),
+                           quant.dequantize_reference(q).numpy(), atol=1e-6)
+        assert moved["model.embed_tokens.weight"] > 1e-5 and moved["model.norm.weight"] > 0
     if name == "frozen MLPs":
         assert all(m == 0.0 for k, m in moved.items() if ".mlp." in k) and any(m > 0 for k, m in moved.items() if "self_attn" in k)
     if name.startswith("two epochs"):
