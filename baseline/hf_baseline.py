@@ -1,9 +1,12 @@
-"""Reference-equivalent training step on the libraries that ARE installed (the literal reference cannot run here:
-exllamav2 / bitsandbytes / h5py / accelerate are missing). It restates the reference's op sequence
-(classes/student/model.py:408-448): HuggingFace ``LlamaForCausalLM`` forward on cuBLAS + SDPA, full-vocabulary
-logits -> ``[:, :, :Vc].float() / T`` -> log_softmax -> gather at the teacher's top-K ids -> forward KL ->
-autograd backward -> ``torch.optim.AdamW``; more than one GPU uses NCCL ``DistributedDataParallel``.
-None of this package's kernels, models or engine is on this path."""
+"""The strongest configuration of the LIBRARIES that are installed, for the same step as the benchmark (the unmodified
+reference itself is the other arm: ``baseline/reference_arm.py``). It follows the reference's op sequence
+(classes/student/model.py:408-448): HuggingFace ``LlamaForCausalLM`` forward on cuBLAS + torch SDPA (the fastest
+library attention on this GPU: 664 TFLOP/s forward at head dim 64 against 318 for flash_attn 2, which
+``B200_BASELINE_ATTN=flash_attention_2`` selects), full-vocabulary logits -> ``[:, :, :Vc].float() / T`` -> log_softmax
+-> gather at the teacher's top-K ids -> forward KL, or with ``loss="reference"`` the reference's own
+``calculate_divergence`` imported from its tree and called per conversation as the reference calls it -> autograd
+backward -> ``torch.optim.AdamW(fused=True)``; more than one GPU uses NCCL ``DistributedDataParallel``. Collection runs
+the whole batch at once. None of this package's kernels, models or engine is on this path."""
 from __future__ import annotations
 
 import torch
@@ -11,13 +14,25 @@ import torch.nn.functional as F
 
 
 class BaselineRunner:
-    def __init__(self, cfg, device, world: int, temperature: float, topk: int, lr: float = 1e-5):
+    def __init__(self, cfg, device, world: int, temperature: float, topk: int, lr: float = 1e-5, loss: str = "kl"):
+        import os
         from transformers import LlamaConfig, LlamaForCausalLM
+        self.loss = loss
+        self._ref_loss = None
+        if loss == "reference":
+            import sys
+            from . import reference_arm as ra
+            ra._install_stand_ins(None if device.type != "cuda" else device.index)
+            if ra.REF not in sys.path:
+                sys.path.insert(0, ra.REF)
+            from utils.finetuning_utils import calculate_divergence      # the reference's own function
+            self._ref_loss = calculate_divergence
         hf = LlamaConfig(vocab_size=cfg.vocab_size, hidden_size=cfg.hidden_size, intermediate_size=cfg.intermediate_size,
                          num_hidden_layers=cfg.num_hidden_layers, num_attention_heads=cfg.num_attention_heads,
                          num_key_value_heads=cfg.num_key_value_heads, rms_norm_eps=cfg.rms_norm_eps,
                          rope_theta=cfg.rope_theta, max_position_embeddings=cfg.max_position_embeddings,
-                         tie_word_embeddings=cfg.tie_word_embeddings, attn_implementation="sdpa")
+                         tie_word_embeddings=cfg.tie_word_embeddings,
+                         attn_implementation=os.environ.get("B200_BASELINE_ATTN", "sdpa"))
         torch.manual_seed(1234)
         with torch.device(device):
             model = LlamaForCausalLM(hf).to(torch.bfloat16)
@@ -36,6 +51,18 @@ class BaselineRunner:
     def _step(self, mb):
         logits = self.model(mb.input_ids).logits[:, :, : self.vocab].float() / self.T
         B, L, V = logits.shape
+        if self._ref_loss is not None:
+            # classes/student/model.py:415-441: one call per conversation, losses summed, one backward
+            total = None
+            ids3, u3 = mb.ids.view(B, L, -1).long(), mb.logp.view(B, L, -1).float() / self.T
+            none = torch.zeros(0, dtype=torch.long, device=logits.device)
+            for b in range(B):
+                d = self._ref_loss(logits[b], u3[b], ids3[b], mb.input_ids[b, 1:], 2, none)
+                total = d["train_loss"] if total is None else total + d["train_loss"]
+            total.backward()
+            self.opt.step()
+            self.opt.zero_grad(set_to_none=True)
+            return total.detach()
         s_full = F.log_softmax(logits.reshape(B * L, V), dim=-1)
         s = torch.gather(s_full, 1, mb.ids.long())
         t = F.log_softmax(mb.logp.float() / self.T, dim=-1)
@@ -66,14 +93,10 @@ class BaselineRunner:
         topk = int(getattr(self, "collect_topk", 200))
         ids = torch.from_numpy(tokens_np).to(self.device)
         B, L = ids.shape
-        # one sequence at a time keeps the fp32 log-softmax of this arm at the size the reference itself handles
-        vals, idx = [], []
-        for b in range(B):
-            logits = self._teacher(ids[b:b + 1]).logits[:, :, : self.vocab].float()
-            lp = F.log_softmax(logits, dim=-1)
-            v, i = torch.topk(lp, topk, dim=-1)
-            vals.append(v[0].to("cpu").numpy())
-            idx.append(i[0].to("cpu").numpy())
+        logits = self._teacher(ids).logits[:, :, : self.vocab].float()      # the whole batch at once: 2 GB of fp32
+        lp = F.log_softmax(logits, dim=-1)
+        v, i = torch.topk(lp, topk, dim=-1)
+        vals, idx = v.to("cpu").numpy(), i.to("cpu").numpy()
         rows_v, rows_i = [], []
         for b, c in enumerate(convos):
             ci = c.content_indices()

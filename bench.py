@@ -136,7 +136,7 @@ def main() -> int:
 
     if args.impl == "baseline":
         from baseline.hf_baseline import BaselineRunner
-        runner = BaselineRunner(cfg, dev, world, temperature=args.temperature, topk=K)
+        runner = BaselineRunner(cfg, dev, world, temperature=args.temperature, topk=K, loss=args.loss)
         launches_of = lambda: 0  # noqa: E731
     else:
         from llm_distillery_b200.engine.trainer import DistillEngine
@@ -168,11 +168,22 @@ def main() -> int:
 
             def collect_step(self, tokens_np, convos):
                 return self.collector.content_logprobs(tokens_np, convos)
+
+            def collect_many(self, toks, convos, n):
+                """n batches the way the pipeline runs them: batch i+1 is queued before batch i's rows are taken."""
+                pending, last = None, None
+                for i in range(n):
+                    t = self.collector.submit(toks[i % len(toks)], convos)
+                    if pending is not None:
+                        last = self.collector.fetch(pending)
+                    pending = t
+                return self.collector.fetch(pending)
         runner = Runner()
         launches_of = lambda: _lib.LAUNCH_COUNT[0]  # noqa: E731
 
     from llm_distillery_b200.engine.trainer import synthetic_batch
-    pool = [synthetic_batch(cfg.vocab_size, B, L, K, seed=100 + 7 * rank + i, device=dev).pin() for i in range(2)]
+    pool = [synthetic_batch(cfg.vocab_size, B, L, K, seed=100 + 7 * rank + i, device=dev,
+                            reference_fields=(args.loss == "reference")).pin() for i in range(2)]
     dev_pool = [runner.to_device(hb) for hb in pool]
     h2d_bytes = pool[0].nbytes()
 
@@ -221,6 +232,23 @@ def main() -> int:
                "d2h_bytes_per_step": 4}
     clocks = sampler.stop() if rank == 0 else None
 
+    # ---------------- what the gradient exchange leaves exposed: device time from the end of backward to the end of
+    # the step (reduce + optimizer + weight all-gather), a few extra steps with the phase timer on, max over ranks
+    exposed = None
+    if args.impl == "ours" and hasattr(runner, "device_step"):
+        eng.timer.enabled = True
+        eng.timer.summary()
+        n_probe = 3
+        for i in range(n_probe):
+            runner.device_step(dev_pool[i % 2])
+        barrier()
+        phases = eng.timer.summary()
+        eng.timer.enabled = False
+        t = torch.tensor([phases.get("reduce+optimizer", 0.0) / n_probe], device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        exposed = float(t.item())
+
     # ---------------- teacher collection arm (second half of the metric): tokens in -> top-K rows in pinned host memory
     collect = None
     if not args.skip_collect and hasattr(runner, "collect_step"):
@@ -243,9 +271,12 @@ def main() -> int:
             t0 = time.perf_counter()
             n_col = max(3, args.steps // 2)
             d2h = 0
-            for i in range(n_col):
-                hv, hi, _ = runner.collect_step(toks[i % 2], convos)
-                d2h = hv.numel() * hv.element_size() + hi.numel() * hi.element_size()
+            if hasattr(runner, "collect_many"):
+                hv, hi, _ = runner.collect_many(toks, convos, n_col)
+            else:
+                for i in range(n_col):
+                    hv, hi, _ = runner.collect_step(toks[i % 2], convos)
+            d2h = hv.numel() * hv.element_size() + hi.numel() * hi.element_size()
             barrier()
         dt = torch.tensor([time.perf_counter() - t0], device=dev, dtype=torch.float64)
         if world > 1:
@@ -275,7 +306,7 @@ def main() -> int:
                        "loss": f"{args.loss} T={args.temperature}", "topk": K,
                        "optimizer": "adamw (fp32 master + state)", "comm": args.comm if world > 1 else "none",
                        "l2": "no flush: each step streams ~2.2 GB of weights and >20 GB of activations, far above the 126 MB L2"},
-            "e2e": e2e, "collect": collect, "gpu_launches": launches, "clocks": clocks, "final_loss": final_loss, "device_error": err,
+            "e2e": e2e, "exposed_comm_ms": exposed, "collect": collect, "gpu_launches": launches, "clocks": clocks, "final_loss": final_loss, "device_error": err,
         }
         print(json.dumps(out))
     if world > 1:

@@ -103,6 +103,7 @@ def set_params(teachers, student, cfg: DistillConfig) -> None:
     for t in teachers:
         t.crop_to_size, t.context_len, t.temperature = cfg.crop_distr_to_size, cfg.context_len, cfg.temperature
         t.device, t.topK, t.enable_topK = cfg.device, cfg.save_topK, cfg.enable_topK
+        t.chunked_prefill, t.prefill_max_tokens = cfg.chunked_prefill, int(cfg.prefill_max_tokens)
     student.crop_to_size, student.context_len = cfg.crop_distr_to_size, cfg.context_len
     student.temperature, student.device = cfg.temperature, cfg.device
 

@@ -5,7 +5,8 @@ full forward, ``[:, :, :crop].float()``, log_softmax over the cropped vocabulary
 the host, then keep the content positions on the CPU. Here the content rows are gathered on the device before
 the LM head, so the vocabulary-sized work is done only for rows that are kept; logits exist only for one row
 chunk at a time (fp32, sized to stay L2-resident) between the tcgen05 GEMM and the exact top-K kernel; fp16
-log-probs + int32 ids go to pinned host memory with an asynchronous copy.
+log-probs + int32 ids go to pinned host memory on a copy stream, and the caller queues the next batch before it takes
+delivery of this one (``submit`` / ``fetch``).
 """
 from __future__ import annotations
 
@@ -17,8 +18,12 @@ from ..ops import basic, topk as topk_ops
 
 
 class TeacherCollector:
-    def __init__(self, model, *, topk: int, crop_to_size: int, enable_topk: bool = True, logits_chunk_bytes: int = 96 << 20):
+    def __init__(self, model, *, topk: int, crop_to_size: int, enable_topk: bool = True, logits_chunk_bytes: int = 96 << 20,
+                 prefill_chunk_len: int = 0):
         self.model = model
+        # > 0: sequences longer than this are run through the model in chunks of this many positions against a
+        # key / value cache (LlamaModel.hidden_states_chunked); 0: one pass over the whole sequence
+        self.prefill_chunk_len = int(prefill_chunk_len or 0)
         self.vocab = min(int(crop_to_size or model.cfg.vocab_size), model.cfg.vocab_size)
         self.K = min(int(topk), self.vocab)          # a vocabulary smaller than K: every token is kept
         self.enable_topk = bool(enable_topk)
@@ -26,12 +31,19 @@ class TeacherCollector:
         self.chunk_rows = max(128, (logits_chunk_bytes // (4 * self.vocab)) // 128 * 128)
 
     @torch.no_grad()
-    def content_logprobs(self, tokens: np.ndarray, convos: list[ConvoTokenized], positions=None):
-        """tokens [B, L] int64 (cropped to the longest member). Returns (values fp16 [M, K or Vc], ids int32 [M, K] or
-        None, rows_per_convo) as host tensors; M = total content rows of the batch."""
+    def submit(self, tokens: np.ndarray, convos: list[ConvoTokenized], positions=None) -> dict:
+        """Queues the whole batch - forward, LM head, top-K, copy of the kept rows to pinned host memory - and returns
+        a ticket at once. The copy runs on a stream of its own behind the compute, so the caller can queue the NEXT
+        batch before it ``fetch``es this one: the GPU computes batch i+1 while batch i's rows cross PCIe and are handed
+        to the HDF5 writer. (Pinned buffers come from PyTorch's caching host allocator: after the first batches no
+        new page-locked memory is allocated, and a buffer is reused only when every array handed out over it is gone.)
+        """
         B, L = tokens.shape
         ids = torch.from_numpy(np.ascontiguousarray(tokens)).to(self.device, non_blocking=True)
-        hs = self.model.hidden_states(ids)
+        if 0 < self.prefill_chunk_len < L:
+            hs = self.model.hidden_states_chunked(ids, self.prefill_chunk_len)
+        else:
+            hs = self.model.hidden_states(ids)
         rows, counts = [], []
         for b, c in enumerate(convos):
             ci = c.content_indices() if positions is None else np.asarray(positions[b], dtype=np.int64)
@@ -41,9 +53,13 @@ class TeacherCollector:
         rows_np = np.concatenate(rows) if rows else np.zeros(0, dtype=np.int64)
         M = len(rows_np)
         if M == 0:
-            return None, None, counts
-        rows_t = torch.from_numpy(rows_np).to(self.device, non_blocking=True)
-        Hc = basic.gather_rows(hs, rows_t)
+            return {"hv": None, "hi": None, "counts": counts, "event": None}
+        every_row = M == B * L and bool((rows_np == np.arange(M)).all())
+        if every_row:
+            Hc = hs
+        else:
+            rows_t = torch.from_numpy(rows_np).to(self.device, non_blocking=True)
+            Hc = basic.gather_rows(hs, rows_t)
         W = self.model.lm_head[: self.vocab]
         width = self.K if self.enable_topk else self.vocab
         out_v = torch.empty((M, width), dtype=torch.float16, device=self.device)
@@ -61,22 +77,46 @@ class TeacherCollector:
                 out_v[r0:r1], out_i[r0:r1] = v, i
             else:
                 out_v[r0:r1] = topk_ops.logprob_full(lg, self.vocab)
+        return self._to_host(out_v, out_i, counts)
+
+    def _to_host(self, out_v, out_i, counts) -> dict:
         pin = self.device.type == "cuda"
         hv = torch.empty(out_v.shape, dtype=out_v.dtype, pin_memory=pin)
-        hv.copy_(out_v, non_blocking=True)
-        hi = None
+        hi = torch.empty(out_i.shape, dtype=out_i.dtype, pin_memory=pin) if out_i is not None else None
+        if not pin:
+            hv.copy_(out_v)
+            if hi is not None:
+                hi.copy_(out_i)
+            return {"hv": hv, "hi": hi, "counts": counts, "event": None}
+        if getattr(self, "_copy_stream", None) is None:
+            self._copy_stream = torch.cuda.Stream(device=self.device)
+        cs = self._copy_stream
+        cs.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(cs):
+            hv.copy_(out_v, non_blocking=True)
+            if hi is not None:
+                hi.copy_(out_i, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record(cs)
+        out_v.record_stream(cs)          # the device rows stay allocated until the copy stream is through with them
         if out_i is not None:
-            hi = torch.empty(out_i.shape, dtype=out_i.dtype, pin_memory=pin)
-            hi.copy_(out_i, non_blocking=True)
-        if pin:
-            torch.cuda.current_stream().synchronize()
-        return hv, hi, counts
+            out_i.record_stream(cs)
+        return {"hv": hv, "hi": hi, "counts": counts, "event": ev}
 
-    def collect_batch(self, tokens: np.ndarray, convos: list[ConvoTokenized], aligner=None,
-                      validation: bool = False) -> list[TeacherRows]:
-        if aligner is not None:
-            return self._collect_aligned(tokens, convos, aligner, validation)
-        hv, hi, counts = self.content_logprobs(tokens, convos)
+    @staticmethod
+    def fetch(ticket: dict):
+        """Waits for the ticket's copy (only that: later batches keep running) and returns (values, ids, counts)."""
+        if ticket["event"] is not None:
+            ticket["event"].synchronize()
+        return ticket["hv"], ticket["hi"], ticket["counts"]
+
+    def content_logprobs(self, tokens: np.ndarray, convos: list[ConvoTokenized], positions=None):
+        """tokens [B, L] int64 (cropped to the longest member). Returns (values fp16 [M, K or Vc], ids int32 [M, K] or
+        None, rows_per_convo) as host tensors; M = total content rows of the batch."""
+        return self.fetch(self.submit(tokens, convos, positions))
+
+    def rows_of(self, ticket: dict, convos: list[ConvoTokenized]) -> list[TeacherRows]:
+        hv, hi, counts = self.fetch(ticket)
         out, r = [], 0
         for c, n in zip(convos, counts):
             if n == 0:
@@ -86,6 +126,12 @@ class TeacherCollector:
             out.append(TeacherRows(c.origin_convo_id, vals, idx, c.content_sha, c.sample))
             r += n
         return out
+
+    def collect_batch(self, tokens: np.ndarray, convos: list[ConvoTokenized], aligner=None,
+                      validation: bool = False) -> list[TeacherRows]:
+        if aligner is not None:
+            return self._collect_aligned(tokens, convos, aligner, validation)
+        return self.rows_of(self.submit(tokens, convos), convos)
 
     def _collect_aligned(self, tokens, convos, aligner, validation) -> list[TeacherRows]:
         """Teacher of another vocabulary: collect at the teacher positions that share a token boundary with the
@@ -137,7 +183,7 @@ class TPTeacherCollector(TeacherCollector):
         self.is_writer = tp_model.g.rank == 0
 
     @torch.no_grad()
-    def content_logprobs(self, tokens: np.ndarray, convos: list[ConvoTokenized], positions=None):
+    def submit(self, tokens: np.ndarray, convos: list[ConvoTokenized], positions=None) -> dict:
         from ..parallel.tp import padded_seq_len
         B, L = tokens.shape
         Lp = padded_seq_len(B, L, self.model.g.world)
@@ -153,20 +199,14 @@ class TPTeacherCollector(TeacherCollector):
             counts.append(len(ci))
         rows_np = np.concatenate(rows) if rows else np.zeros(0, dtype=np.int64)
         if len(rows_np) == 0 or not self.is_writer:
-            return None, None, counts
+            return {"hv": None, "hi": None, "counts": counts, "event": None}
         rows_t = torch.from_numpy(rows_np).to(self.device, non_blocking=True)
-        out_v, out_i = lp[rows_t], ix[rows_t]
-        pin = self.device.type == "cuda"
-        hv = torch.empty(out_v.shape, dtype=out_v.dtype, pin_memory=pin)
-        hi = torch.empty(out_i.shape, dtype=out_i.dtype, pin_memory=pin)
-        hv.copy_(out_v, non_blocking=True)
-        hi.copy_(out_i, non_blocking=True)
-        if pin:
-            torch.cuda.current_stream().synchronize()
-        return hv, hi, counts
+        # the vocabulary-parallel head runs on every padded position and the content rows are picked afterwards: the
+        # hidden states are token-sharded over the group at that point, and the head is ~1.5 % of a 70 B forward
+        return self._to_host(lp[rows_t], ix[rows_t], counts)
 
     def collect_batch(self, tokens, convos, aligner=None, validation: bool = False):
         if self.is_writer:
             return super().collect_batch(tokens, convos, aligner=aligner, validation=validation)
-        self.content_logprobs(tokens, convos)     # take part in the forward; the rows stay on the writer rank
+        self.submit(tokens, convos)     # take part in the forward; the rows stay on the writer rank
         return []

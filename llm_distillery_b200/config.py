@@ -107,6 +107,11 @@ class DistillConfig:
     shard_strategy: str = "ddp"        # ddp | fsdp (optimizer state sharded) | zero3 (weights and gradients too) | auto
     comm_backend: str = "p2p"          # p2p (in-kernel NVLink) | nccl
     cross_tokenizer: bool = False      # allow teachers of another vocab family (byte-trie alignment)
+    chunked_prefill: str = "auto"      # teacher forward in chunks against a KV cache: true (chunks of the teacher's
+                                       # seq_chunk_len, as the reference does) | false | auto (only batches of more
+                                       # than prefill_max_tokens tokens, in chunks that keep a pass below that)
+    prefill_max_tokens: int = 131072
+    vocab_parallel_loss: bool = False  # training: LM head and loss split over the vocabulary across the ranks
     seed: int = 0
     interactive: bool = False          # ask before destructive HDF5 operations / for missing model sidecars
     metrics_backend: str = "jsonl"     # jsonl | wandb | both
@@ -133,6 +138,9 @@ class DistillConfig:
             raise ValueError(f"Invalid data_order: {self.data_order}; choose from {DATA_ORDERS}")
         if self.shard_strategy not in ("ddp", "fsdp", "zero3", "auto"):
             raise ValueError("shard_strategy must be ddp, fsdp, zero3 or auto")
+        self.chunked_prefill = str(self.chunked_prefill).lower()
+        if self.chunked_prefill not in ("true", "false", "auto"):
+            raise ValueError("chunked_prefill must be true, false or auto")
         if self.comm_backend not in ("p2p", "nccl"):
             raise ValueError("comm_backend must be p2p or nccl")
         if self.context_len <= 0 or self.batch_size <= 0 or self.grad_accum_batches <= 0:
@@ -228,6 +236,9 @@ def build_parser() -> argparse.ArgumentParser:
                    "zero3 (weights, gradients and state sharded) | auto (first plan that fits 180 GB per GPU)")
     g.add_argument("--comm_backend", type=str, help="p2p (NVLink peer-access kernels) | nccl (library collectives)")
     g.add_argument("--cross_tokenizer", type=str2bool)
+    g.add_argument("--chunked_prefill", type=str, help="true | false | auto")
+    g.add_argument("--prefill_max_tokens", type=int)
+    g.add_argument("--vocab_parallel_loss", type=str2bool)
     g.add_argument("--seed", type=int)
     g.add_argument("--interactive", type=str2bool)
     g.add_argument("--metrics_backend", type=str)

@@ -51,6 +51,11 @@ struct FwdParams {
   float* lse;
   int B, L, H, Hkv;
   float scale;  // 1/sqrt(D)
+  // Chunked prefill: the L queries are positions q_off .. q_off + L - 1 of a sequence whose earlier keys / values
+  // sit in a cache (row p of the K / V tensors = position p). q_off = 0 and K / V inside the same packed tensor as Q
+  // is the ordinary whole-sequence call.
+  int q_off;
+  int colQ0, colK0, colV0;  // first column of head 0 of Q / K / V in their tensors
 };
 
 // 2^x for x <= 0 (and a little above) on the FMA pipe: round-to-nearest split x = n + f, f in [-0.5, 0.5], a quartic
@@ -71,8 +76,8 @@ __device__ __forceinline__ float poly_exp2(float x) {
 
 template <int D>
 __global__ void __launch_bounds__(NTHREADS, 2)
-    flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmKV, FwdParams p,
-                     unsigned int* err_word) {
+    flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                     const __grid_constant__ CUtensorMap tmV, FwdParams p, unsigned int* err_word) {
   using C = Cfg<D>;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
@@ -94,7 +99,8 @@ __global__ void __launch_bounds__(NTHREADS, 2)
   const int hq = blockIdx.y, b = blockIdx.z;
   const int hkv = hq / (p.H / p.Hkv);
   const int q0 = qb * BM;
-  const int kv_end = min(p.L, q0 + BM);  // causal: keys < kv_end
+  const int qpos0 = p.q_off + q0;                       // sequence position of the block's first query
+  const int kv_end = p.q_off + min(p.L, q0 + BM);       // causal: keys < kv_end
   const int n_kv = (kv_end + BN - 1) / BN;
 
   if ((smem_u32(smem) & 1023u) != 0u) {  // swizzled tiles need a 1024-byte aligned base
@@ -103,7 +109,8 @@ __global__ void __launch_bounds__(NTHREADS, 2)
   }
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tmQ);
-    tma_prefetch_desc(&tmKV);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
     mbar_init(q_full, 1);
     for (int s = 0; s < KS; ++s) {
       mbar_init(&k_full[s], 1);
@@ -131,9 +138,9 @@ __global__ void __launch_bounds__(NTHREADS, 2)
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int colQ = hq * D;
-  const int colK = p.H * D + hkv * D;
-  const int colV = (p.H + p.Hkv) * D + hkv * D;
+  const int colQ = p.colQ0 + hq * D;
+  const int colK = p.colK0 + hkv * D;
+  const int colV = p.colV0 + hkv * D;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -147,12 +154,12 @@ __global__ void __launch_bounds__(NTHREADS, 2)
         uint8_t* sK = smem + C::OFF_K + ks * C::T_BYTES;
         mbar_arrive_expect_tx(&k_full[ks], C::T_BYTES);
 #pragma unroll
-        for (int c = 0; c < D / 64; ++c) tma_load_3d(sK + c * (BN * 128), &tmKV, &k_full[ks], colK + c * 64, j * BN, b);
+        for (int c = 0; c < D / 64; ++c) tma_load_3d(sK + c * (BN * 128), &tmK, &k_full[ks], colK + c * 64, j * BN, b);
         if (!mbar_wait_bounded(&v_empty[vs], ((j / VS) & 1u) ^ 1u, abort_flag, err_word, ERR_WAIT_EMPTY)) break;
         uint8_t* sV = smem + C::OFF_V + vs * C::T_BYTES;
         mbar_arrive_expect_tx(&v_full[vs], C::T_BYTES);
 #pragma unroll
-        for (int c = 0; c < D / 64; ++c) tma_load_3d(sV + c * (BN * 128), &tmKV, &v_full[vs], colV + c * 64, j * BN, b);
+        for (int c = 0; c < D / 64; ++c) tma_load_3d(sV + c * (BN * 128), &tmV, &v_full[vs], colV + c * 64, j * BN, b);
       }
     }
   } else if (warp == 1) {
@@ -217,7 +224,8 @@ __global__ void __launch_bounds__(NTHREADS, 2)
     // ------------------------------------------------------------------ softmax / epilogue
     const int quad = warp & 3;
     const int r = quad * 32 + lane;  // row inside the q block
-    const int qi = q0 + r;           // position in the sequence
+    const int qi = q0 + r;           // row of the query inside this call
+    const int qpos = qpos0 + r;      // its position in the sequence
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
     const float c2 = p.scale * 1.4426950408889634f;  // scores -> log2 domain
     const uint64_t c2p = pack_f32x2(c2, c2);
@@ -265,8 +273,8 @@ __global__ void __launch_bounds__(NTHREADS, 2)
       if (!__all_sync(0xffffffffu, w)) { ok = false; break; }
       tc_fence_after_sync();
       const int kv0 = j * BN;
-      const bool diag = (kv0 + BN - 1) > q0;                 // some keys of this tile are masked for some rows
-      const int lim = diag ? (qi - kv0) : 0x3fffffff;        // tile columns <= lim are visible to this row
+      const bool diag = (kv0 + BN - 1) > qpos0;              // some keys of this tile are masked for some rows
+      const int lim = diag ? (qpos - kv0) : 0x3fffffff;      // tile columns <= lim are visible to this row
       uint32_t va[32], vb[32], pka[16], pkb[16];
       tmem_ld_32x32b_x32(tS, va);
       tmem_ld_32x32b_x32(tS + 32, vb);
@@ -381,15 +389,19 @@ __global__ void __launch_bounds__(NTHREADS, 2)
 }
 
 template <int D>
-static int launch_fwd(const void* qkv, void* out, float* lse, int B, int L, int H, int Hkv, cudaStream_t st) {
+static int launch_fwd(const void* q, long long q_width, int colQ0, const void* k, const void* v, long long kv_width,
+                      int colK0, int colV0, long long kv_rows, void* out, float* lse, int B, int L, int q_off, int H,
+                      int Hkv, cudaStream_t st) {
   using C = Cfg<D>;
-  const long long width = (long long)(H + 2 * Hkv) * D;
-  CUtensorMap tmQ, tmKV;
-  int rc = make_tmap_3d(&tmQ, qkv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)width, (uint64_t)L, (uint64_t)B,
-                        (uint64_t)width * 2, (uint64_t)L * width * 2, 64, BM, 1, CU_TENSOR_MAP_SWIZZLE_128B);
+  CUtensorMap tmQ, tmK, tmV;
+  int rc = make_tmap_3d(&tmQ, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)q_width, (uint64_t)L, (uint64_t)B,
+                        (uint64_t)q_width * 2, (uint64_t)L * q_width * 2, 64, BM, 1, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != B200_OK) return rc;
-  rc = make_tmap_3d(&tmKV, qkv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)width, (uint64_t)L, (uint64_t)B,
-                    (uint64_t)width * 2, (uint64_t)L * width * 2, 64, BN, 1, CU_TENSOR_MAP_SWIZZLE_128B);
+  rc = make_tmap_3d(&tmK, k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)kv_width, (uint64_t)kv_rows, (uint64_t)B,
+                    (uint64_t)kv_width * 2, (uint64_t)kv_rows * kv_width * 2, 64, BN, 1, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != B200_OK) return rc;
+  rc = make_tmap_3d(&tmV, v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)kv_width, (uint64_t)kv_rows, (uint64_t)B,
+                    (uint64_t)kv_width * 2, (uint64_t)kv_rows * kv_width * 2, 64, BN, 1, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != B200_OK) return rc;
   auto kern = flash_fwd_kernel<D>;
   static bool attr = false;
@@ -397,9 +409,9 @@ static int launch_fwd(const void* qkv, void* out, float* lse, int B, int L, int 
     B200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
     attr = true;
   }
-  FwdParams p{(__nv_bfloat16*)out, lse, B, L, H, Hkv, 1.0f / sqrtf((float)D)};
+  FwdParams p{(__nv_bfloat16*)out, lse, B, L, H, Hkv, 1.0f / sqrtf((float)D), q_off, colQ0, colK0, colV0};
   dim3 grid((L + BM - 1) / BM, H, B);
-  kern<<<grid, NTHREADS, C::SMEM_BYTES, st>>>(tmQ, tmKV, p, device_err_word());
+  kern<<<grid, NTHREADS, C::SMEM_BYTES, st>>>(tmQ, tmK, tmV, p, device_err_word());
   B200_CUDA_CHECK(cudaGetLastError());
   return B200_OK;
 }
@@ -411,7 +423,29 @@ extern "C" int b200_flash_attn_fwd(const void* qkv, void* out, float* lse, int B
                                    cudaStream_t st) {
   using namespace b200;
   if (!qkv || !out || B <= 0 || L <= 0 || H <= 0 || Hkv <= 0 || (H % Hkv) != 0) return B200_ERR_ARG;
-  if (D == 64) return fa::launch_fwd<64>(qkv, out, lse, B, L, H, Hkv, st);
-  if (D == 128) return fa::launch_fwd<128>(qkv, out, lse, B, L, H, Hkv, st);
+  const long long width = (long long)(H + 2 * Hkv) * D;
+  if (D == 64)
+    return fa::launch_fwd<64>(qkv, width, 0, qkv, qkv, width, H * D, (H + Hkv) * D, L, out, lse, B, L, 0, H, Hkv, st);
+  if (D == 128)
+    return fa::launch_fwd<128>(qkv, width, 0, qkv, qkv, width, H * D, (H + Hkv) * D, L, out, lse, B, L, 0, H, Hkv, st);
+  return B200_ERR_ARG;
+}
+
+// Chunked prefill against a key / value cache. qkv [B*L, (H + 2*Hkv)*D]: this chunk's projections (its K / V columns
+// are NOT read: the caller has copied them into the caches first). k_cache, v_cache [B, cache_rows, Hkv*D] bf16 with
+// row p = sequence position p, valid (and finite: allocate the caches zeroed) for p < q_off + L. The chunk's queries
+// are positions q_off .. q_off + L - 1 and see keys <= their own position. out [B*L, H*D], lse [H, B*L] (may be null).
+extern "C" int b200_flash_attn_fwd_cached(const void* qkv, const void* k_cache, const void* v_cache, long long cache_rows,
+                                          void* out, float* lse, int B, int L, int q_off, int H, int Hkv, int D,
+                                          cudaStream_t st) {
+  using namespace b200;
+  if (!qkv || !k_cache || !v_cache || !out || B <= 0 || L <= 0 || q_off < 0 || H <= 0 || Hkv <= 0 || (H % Hkv) != 0 ||
+      cache_rows < (long long)q_off + L)
+    return B200_ERR_ARG;
+  const long long width = (long long)(H + 2 * Hkv) * D, kvw = (long long)Hkv * D;
+  if (D == 64)
+    return fa::launch_fwd<64>(qkv, width, 0, k_cache, v_cache, kvw, 0, 0, cache_rows, out, lse, B, L, q_off, H, Hkv, st);
+  if (D == 128)
+    return fa::launch_fwd<128>(qkv, width, 0, k_cache, v_cache, kvw, 0, 0, cache_rows, out, lse, B, L, q_off, H, Hkv, st);
   return B200_ERR_ARG;
 }

@@ -450,6 +450,50 @@ class LlamaModel(nn.Module):
             pre(self.norm, False)
         return FinalNormFn.apply(h, self.norm, cfg.rms_norm_eps)
 
+    @torch.no_grad()
+    def hidden_states_chunked(self, input_ids: torch.Tensor, chunk_len: int) -> torch.Tensor:
+        """Inference-only forward in chunks of ``chunk_len`` positions against a key / value cache - the reference's
+        long-context mechanism (classes/teacher/inference_worker.py:38-48: ``max_input_len = seq_chunk_len`` with an
+        ExLlamaV2 cache). Per chunk the activations are [B*chunk_len, .] instead of [B*L, .]; every layer keeps its
+        rotated keys and its values for all positions seen so far ([B, L, Hkv*d] each, zero-filled beyond), and the
+        chunk's queries attend to positions <= their own. Same result as ``hidden_states`` up to rounding."""
+        cfg = self.cfg
+        B, L = input_ids.shape
+        if chunk_len <= 0 or chunk_len >= L:
+            return self.hidden_states(input_ids)
+        if cfg.sliding_window and L > cfg.sliding_window:
+            raise ValueError(f"sequence length {L} exceeds the model's attention window ({cfg.sliding_window})")
+        dev = self.embed_tokens.device
+        H, Hkv, d = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+        cos, sin = self.rope(dev, L)
+        kv = Hkv * d
+        caches = [(torch.zeros((B, L, kv), dtype=self.embed_tokens.dtype, device=dev),
+                   torch.zeros((B, L, kv), dtype=self.embed_tokens.dtype, device=dev)) for _ in self.layers]
+        out = torch.empty((B, L, cfg.hidden_size), dtype=self.embed_tokens.dtype, device=dev)
+        ids = input_ids.to(dev)
+        for c0 in range(0, L, chunk_len):
+            n = min(chunk_len, L - c0)
+            pos = torch.arange(c0, c0 + n, dtype=torch.int32, device=dev).repeat(B)
+            h = basic.embed_fwd(ids[:, c0:c0 + n].reshape(-1), self.embed_tokens)
+            for layer, (kc, vc) in zip(self.layers, caches):
+                if LAYER_WEIGHTS_PRE[0] is not None:
+                    LAYER_WEIGHTS_PRE[0](layer.input_layernorm)
+                n1, _, _ = basic.rmsnorm_fwd(h, layer.input_layernorm, cfg.rms_norm_eps)
+                qkv = basic.linear_fwd(n1, layer.qkv_proj)
+                if hasattr(layer, "qkv_bias"):
+                    basic.bias_add_(qkv, layer.qkv_bias)
+                basic.rope_(qkv, pos, cos, sin, H + Hkv, d)
+                kc[:, c0:c0 + n] = qkv[:, H * d:(H + Hkv) * d].reshape(B, n, kv)
+                vc[:, c0:c0 + n] = qkv[:, (H + Hkv) * d:].reshape(B, n, kv)
+                att = attention.attention_fwd_cached(qkv, kc, vc, B, n, c0, H, Hkv, d)
+                h1 = basic.linear_fwd(att, layer.o_proj, residual=h)
+                n2, _, _ = basic.rmsnorm_fwd(h1, layer.post_attention_layernorm, cfg.rms_norm_eps)
+                act = basic.swiglu_fwd(basic.linear_fwd(n2, layer.gate_up_proj))
+                h = basic.linear_fwd(act, layer.down_proj, residual=h1)
+            y, _, _ = basic.rmsnorm_fwd(h, self.norm, cfg.rms_norm_eps)
+            out[:, c0:c0 + n] = y.reshape(B, n, -1)
+        return out.reshape(B * L, -1)
+
     def forward(self, input_ids: torch.Tensor) -> torch.Tensor:
         """Full logits [B, L, V] (collection without the fused top-K head, tests). Training never calls this."""
         B, L = input_ids.shape

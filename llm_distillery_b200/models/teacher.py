@@ -43,6 +43,20 @@ class TeacherModel(BaseModel):
         self.dtype = torch.bfloat16
         self.tokens_collected = 0
         self.collect_seconds = 0.0
+        self.chunked_prefill = "auto"       # true | false | auto (config key of the same name)
+        self.prefill_max_tokens = 131072
+
+    def prefill_chunk_len(self, batch_size: int, longest: int) -> int:
+        """Positions per prefill chunk for a batch of ``batch_size`` sequences of up to ``longest`` tokens (0 = one
+        pass). ``true``: the model's own ``seq_chunk_len`` as in the reference (classes/teacher/inference_worker.py:
+        38-48); ``auto``: only when the batch holds more than ``prefill_max_tokens`` tokens, in chunks (multiples of
+        128) that keep one pass below that."""
+        mode = str(self.chunked_prefill).lower()
+        if mode == "true":
+            return int(self.seq_chunk_len) if 0 < int(self.seq_chunk_len or 0) < longest else 0
+        if mode == "auto" and batch_size * longest > self.prefill_max_tokens > 0:
+            return max(128, (self.prefill_max_tokens // max(1, batch_size)) // 128 * 128)
+        return 0
 
     def _sort_datasets_by_len(self) -> None:
         if not self.dataset_sorted:
@@ -97,18 +111,17 @@ class TeacherModel(BaseModel):
         else:
             model = self.load()
             crop = model.cfg.vocab_size if aligner is not None else self.crop_to_size   # own vocabulary when remapping
-            collector = TeacherCollector(model, topk=self.topK, crop_to_size=crop, enable_topk=self.enable_topK)
+            collector = TeacherCollector(model, topk=self.topK, crop_to_size=crop, enable_topk=self.enable_topK,
+                                         prefill_chunk_len=self.prefill_chunk_len(max(1, self.batch_size),
+                                                                                  max(c.length for c in chunk)))
         batches = plan_batches(chunk, max(1, self.batch_size))[rank::max(1, world)]
         done = 0
         t0 = time.time()
         with progress(total=len(chunk), desc="Convos", leave=False) as bar:
             bar.set_postfix_str("Generating...")
             hbt = getattr(self, "heartbeat", None)
-            for tokens, convos in batches:
-                if hbt is not None:      # between batches: a lost peer is noticed before the next launch
-                    hbt.beat(done, "collect")
-                    hbt.check()
-                rows = collector.collect_batch(tokens, convos, aligner=aligner, validation=validation)
+            def deliver(rows, convos):
+                nonlocal done
                 if sha_by_id:   # the store is keyed by the STUDENT's view of the text (that is what sync compares)
                     for r in rows:
                         r.content_sha = sha_by_id.get(r.convo_id, r.content_sha)
@@ -119,6 +132,26 @@ class TeacherModel(BaseModel):
                 self.tokens_collected += int(sum(c.length for c in convos))
                 done += len(rows)
                 bar.update(len(convos))
+
+            # one batch deep: batch i+1 is queued on the GPU before batch i's rows are waited for, so the device
+            # never idles during the copy to the host and the hand-off to the writer
+            # (on CPU there is nothing to overlap: the plain per-batch call runs)
+            pipelined = (aligner is None and tp_group is None and hasattr(collector, "rows_of")
+                         and collector.device.type == "cuda")
+            pending = None
+            for tokens, convos in batches:
+                if hbt is not None:      # between batches: a lost peer is noticed before the next launch
+                    hbt.beat(done, "collect")
+                    hbt.check()
+                if pipelined:
+                    ticket = collector.submit(tokens, convos)
+                    if pending is not None:
+                        deliver(collector.rows_of(*pending), pending[1])
+                    pending = (ticket, convos)
+                else:
+                    deliver(collector.collect_batch(tokens, convos, aligner=aligner, validation=validation), convos)
+            if pending is not None:
+                deliver(collector.rows_of(*pending), pending[1])
         data_manager.wait()
         self.collect_seconds += time.time() - t0
         return done

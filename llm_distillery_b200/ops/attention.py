@@ -75,3 +75,28 @@ def attention_bwd(dout, qkv, out, lse, B, L, H, Hkv, d):
         return attention_reference_bwd(dout, qkv, out, lse, B, L, H, Hkv, d)
     from . import flash
     return flash.flash_attn_bwd(dout, qkv, out, lse, B, L, H, Hkv, d)
+
+
+def attention_cached_reference_fwd(qkv, k_cache, v_cache, B, L, q_off, H, Hkv, d):
+    """Chunked prefill restated: the chunk's L queries (positions q_off .. q_off+L-1) against the cached keys /
+    values of positions < q_off + L. k_cache, v_cache [B, rows, Hkv*d]. Returns out [B*L, H*d]."""
+    q = qkv[:, : H * d].float().reshape(B, L, H, d)
+    n = q_off + L
+    g = H // Hkv
+    k = k_cache[:, :n].float().reshape(B, n, Hkv, d).repeat_interleave(g, dim=2)
+    v = v_cache[:, :n].float().reshape(B, n, Hkv, d).repeat_interleave(g, dim=2)
+    s = torch.einsum("blhd,bmhd->bhlm", q, k) / math.sqrt(d)
+    qpos = torch.arange(q_off, n, device=qkv.device)[:, None]
+    s = s.masked_fill(torch.arange(n, device=qkv.device)[None, :] > qpos, float("-inf"))
+    p = torch.softmax(s, dim=-1)
+    return torch.einsum("bhlm,bmhd->blhd", p, v).reshape(B * L, H * d).to(qkv.dtype)
+
+
+def attention_fwd_cached(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, B: int, L: int, q_off: int,
+                         H: int, Hkv: int, d: int) -> torch.Tensor:
+    """Attention of one prefill chunk against the key / value caches (which already contain the chunk's own keys and
+    values at rows q_off .. q_off+L-1). Inference only: no log-sum-exp is kept."""
+    if not qkv.is_cuda:
+        return attention_cached_reference_fwd(qkv, k_cache, v_cache, B, L, q_off, H, Hkv, d)
+    from . import flash
+    return flash.flash_attn_fwd_cached(qkv, k_cache, v_cache, B, L, q_off, H, Hkv, d)

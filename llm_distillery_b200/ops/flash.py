@@ -4,9 +4,10 @@ from __future__ import annotations
 import torch
 
 from . import _lib
-from ._lib import _VP, _I
+from ._lib import _VP, _I, _LL
 
 _lib.register("b200_flash_attn_fwd", [_VP, _VP, _VP, _I, _I, _I, _I, _I, _VP])
+_lib.register("b200_flash_attn_fwd_cached", [_VP, _VP, _VP, _LL, _VP, _VP, _I, _I, _I, _I, _I, _I, _VP])
 _lib.register("b200_flash_attn_bwd", [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _VP])
 
 
@@ -32,3 +33,15 @@ def flash_attn_bwd(dout, qkv, out, lse, B, L, H, Hkv, d):
                                             _lib.ptr(dqkv), _lib.ptr(dq_acc), B, L, H, Hkv, d, _lib.stream())
     _lib.check(rc, "b200_flash_attn_bwd")
     return dqkv
+
+
+def flash_attn_fwd_cached(qkv, k_cache, v_cache, B, L, q_off, H, Hkv, d):
+    if qkv.dtype != torch.bfloat16 or not (qkv.is_contiguous() and k_cache.is_contiguous() and v_cache.is_contiguous()):
+        raise TypeError("flash_attn_fwd_cached: contiguous bf16 tensors expected")
+    if k_cache.shape != v_cache.shape or k_cache.shape[0] != B or k_cache.shape[2] != Hkv * d:
+        raise ValueError("key / value caches must be [B, rows, Hkv*d]")
+    out = torch.empty((B * L, H * d), dtype=qkv.dtype, device=qkv.device)
+    rc = _lib.kernels().b200_flash_attn_fwd_cached(_lib.ptr(qkv), _lib.ptr(k_cache), _lib.ptr(v_cache), k_cache.shape[1],
+                                                   _lib.ptr(out), None, B, L, q_off, H, Hkv, d, _lib.stream())
+    _lib.check(rc, "b200_flash_attn_fwd_cached")
+    return out
