@@ -16,8 +16,11 @@
 // A [q x k] tile written row-per-thread in the 128B-swizzled K-major layout is, byte for byte, also the
 // MN-major layout of its transpose, so P and dS are stored once and read both ways.
 //
-// Roles: warp 0 TMA producer (Q_i / dO_i ring), warp 1 MMA issuer, warps 2-9 softmax + dQ drain + epilogue: each TMEM
-// lane quadrant is served by two warps that split the tile's columns, so every SM sub-partition has two warps to issue from.
+// Roles: warp 0 TMA producer (Q_i / dO_i ring); warps 1-4 issue the MMA groups, one group each (S and dP; dV; dK; dQ):
+// every tcgen05 instruction - an MMA, a commit, a completed mbarrier wait - costs its issuing thread on the order of a
+// hundred cycles here, so one thread issuing the 32 MMAs of a pair needed ~3.8 K cycles per pair and was what bound
+// the kernel (the tensor core needs ~1.3 K); warps 5-20 softmax + dQ drain + epilogue: each TMEM lane quadrant is
+// served by four warps that split the tile's columns.
 #include "../common/ptx.cuh"
 #include "../common/host.cuh"
 
@@ -27,7 +30,9 @@ namespace fab {
 constexpr int BM = 128;  // queries per block
 constexpr int BN = 128;  // keys per block
 constexpr int NSPLIT = 4;        // softmax/drain warps per TMEM lane quadrant: each takes 1/4 of a tile's columns
-constexpr int NTHREADS = 64 + 4 * NSPLIT * 32;  // TMA warp, MMA warp, 16 softmax/drain warps
+constexpr int NISSUE = 4;                        // MMA-issuing warps: S/dP, dV, dK, dQ
+constexpr int FIRST_WORK_WARP = 1 + NISSUE;      // warp 0 is the TMA producer
+constexpr int NTHREADS = 32 * FIRST_WORK_WARP + 4 * NSPLIT * 32;  // + 16 softmax/drain warps
 constexpr int NWORK = 4 * NSPLIT * 32;          // threads that arrive on the softmax/drain barriers
 
 template <int D>
@@ -91,8 +96,10 @@ __global__ void __launch_bounds__(NTHREADS, 1)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nkb = (p.L + BN - 1) / BN;
-  const int jb = blockIdx.x;  // key block; block 0 has the most work and is scheduled first
-  const int hkv = blockIdx.y, b = blockIdx.z;
+  // blockIdx.y = key block (block 0 has the most work), blockIdx.x = (kv head, batch): blocks are handed out x-fastest,
+  // so all the heavy key blocks of every head start first and the light ones fill the tail
+  const int jb = blockIdx.y;
+  const int hkv = blockIdx.x % p.Hkv, b = blockIdx.x / p.Hkv;
   const int g = p.H / p.Hkv;
   const int kv0 = jb * BN;
   const int nqb = (p.L + BM - 1) / BM;
@@ -117,11 +124,11 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     }
     mbar_init(sdp_full, 1);
     mbar_init(pds_ready, NWORK);
-    mbar_init(dq_full, 1);
+    mbar_init(dq_full, 3);     // "pair done": the dV, dK and dQ issuers each commit to it
     mbar_init(dq_empty, NWORK);
     mbar_init(stage_full, NWORK);
     mbar_init(stage_free, 1);
-    mbar_init(dq_full1, 1);
+    mbar_init(dq_full1, 3);
     mbar_init(dq_empty1, NWORK);
     *abort_flag = 0;
     fence_mbar_init();
@@ -151,7 +158,15 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         const uint32_t ph = (it / ST) & 1u;
         const int hq = hkv * g + it / nqi;
         const int q0 = (i_start + it % nqi) * BM;
-        if (!mbar_wait_bounded(&qdo_empty[s], ph ^ 1u, abort_flag, err_word, ERR_WAIT_EMPTY)) break;
+        (void)ph;
+        if (it >= ST) {
+          // the stage was read by pair it - ST: free once that pair's dV, dK and dQ MMAs are done (the S / dP MMAs of a
+          // pair complete before its softmax and so before these are even issued)
+          const int pd = it - ST;
+          uint64_t* done = (C::PIPE && (pd & 1)) ? dq_full1 : dq_full;
+          const uint32_t par = C::PIPE ? ((pd >> 1) & 1u) : (pd & 1u);
+          if (!mbar_wait_bounded(done, par, abort_flag, err_word, ERR_WAIT_EMPTY)) break;
+        }
         uint8_t* sQ = smem + C::OFF_QDO + s * C::STAGE_BYTES;
         uint8_t* sDO = sQ + C::QDO_BYTES;
         mbar_arrive_expect_tx(&qdo_full[s], C::STAGE_BYTES);
@@ -162,111 +177,98 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         }
       }
     }
-  } else if (warp == 1) {
+  } else if (warp < FIRST_WORK_WARP) {
+    // ------------------------------------------------------------------ MMA issuers (one elected thread per warp)
     if (lane == 0) {
-      const uint32_t idesc_kk = make_idesc_f16(1, BM, BN, 0, 0);  // S, dP
-      const uint32_t idesc_tt = make_idesc_f16(1, BN, D, 1, 1);   // dV, dK
-      const uint32_t idesc_kt = make_idesc_f16(1, BM, D, 0, 1);   // dQ
       const uint32_t sK = smem_u32(smem + C::OFF_K);
       const uint32_t sV = smem_u32(smem + C::OFF_V);
       const uint32_t sP = smem_u32(smem + C::OFF_P);
       const uint32_t sDS = smem_u32(smem + C::OFF_DS);
-      bool ok = mbar_wait_bounded(kv_full, 0, abort_flag, err_word, ERR_WAIT_FULL);
-      // Base descriptors, built once: inside the loop an MMA's operands are a base plus a constant (k-step) and a
-      // stage offset, i.e. one 64-bit add each. (Rebuilding both descriptors per MMA cost the issuing thread ~80
-      // cycles per instruction - more than most of these MMAs occupy the tensor core - and made it the bottleneck.)
-      // The address field counts 16-byte units and never carries out of its 14 bits below 256 KB.
+      // Base descriptors, built once: inside the loops an MMA's operands are a base plus a constant (k-step) and a
+      // stage offset. The address field counts 16-byte units and never carries out of its 14 bits below 256 KB.
       const uint32_t sQ0 = smem_u32(smem + C::OFF_QDO), sDO0 = sQ0 + C::QDO_BYTES;
-      const uint64_t kQ = make_smem_desc_sw128(sQ0, 16, 1024), kDO = make_smem_desc_sw128(sDO0, 16, 1024);       // K-major
-      const uint64_t kK = make_smem_desc_sw128(sK, 16, 1024), kV = make_smem_desc_sw128(sV, 16, 1024);
-      const uint64_t kDS = make_smem_desc_sw128(sDS, 16, 1024);
-      const uint64_t tP = make_smem_desc_sw128(sP, BM * 128, 1024), tDS = make_smem_desc_sw128(sDS, BM * 128, 1024);  // MN-major
-      const uint64_t tDO = make_smem_desc_sw128(sDO0, BM * 128, 1024), tQ = make_smem_desc_sw128(sQ0, BM * 128, 1024);
-      const uint64_t tK = make_smem_desc_sw128(sK, BN * 128, 1024);
       auto koff = [](int k) -> uint64_t {   // k-step inside a K-major tile: 64-column sub-tiles 16 KB apart, 32 B per step
         return static_cast<uint64_t>(((k >> 2) * (128 * 128) + (k & 3) * 32) >> 4);
       };
-      // S = Q K^T and dP = dO V^T of the pair whose Q / dO sit in stage s
-      auto issue_s_dp = [&](int s) {
-        const uint64_t stage = static_cast<uint64_t>((s * C::STAGE_BYTES) >> 4);
-#pragma unroll
-        for (int k = 0; k < D / 16; ++k)
-          umma_f16_ss(tmem_base + C::S_COL, kQ + stage + koff(k), kK + koff(k), idesc_kk, k != 0 ? 1u : 0u);
-#pragma unroll
-        for (int k = 0; k < D / 16; ++k)
-          umma_f16_ss(tmem_base + C::DP_COL, kDO + stage + koff(k), kV + koff(k), idesc_kk, k != 0 ? 1u : 0u);
-      };
-      // dV += P^T dO ; dK += dS^T Q (reduction over the 128 queries, 16 per step = 2048 B per step in both tiles);
-      // dQ = dS K (reduction over the 128 keys) into the accumulator at dq_col
-      auto issue_dv_dk_dq = [&](int s, int it, uint32_t dq_col) {
-        const uint64_t stage = static_cast<uint64_t>((s * C::STAGE_BYTES) >> 4);
-        const uint32_t acc = it != 0 ? 1u : 0u;
-#pragma unroll
-        for (int k = 0; k < BM / 16; ++k)
-          umma_f16_ss(tmem_base + C::DV_COL, tP + (uint64_t)(k * 128), tDO + stage + (uint64_t)(k * 128), idesc_tt,
-                      k != 0 ? 1u : acc);
-#pragma unroll
-        for (int k = 0; k < BM / 16; ++k)
-          umma_f16_ss(tmem_base + C::DK_COL, tDS + (uint64_t)(k * 128), tQ + stage + (uint64_t)(k * 128), idesc_tt,
-                      k != 0 ? 1u : acc);
-#pragma unroll
-        for (int k = 0; k < BN / 16; ++k)
-          umma_f16_ss(tmem_base + dq_col, kDS + koff(k), tK + (uint64_t)(k * 128), idesc_kt, k != 0 ? 1u : 0u);
-      };
-      if constexpr (C::PIPE) {
-        // Two pairs deep: as soon as the softmax warps have consumed S / dP of pair `it` (pds_ready), the S / dP MMAs
-        // of pair it+1 are issued AHEAD of pair it's dV / dK / dQ MMAs, so the warps never wait for the tensor core
-        // between pairs; dQ alternates between two accumulators because pair it-1's is drained during pair it.
-        if (ok && n_it > 0) {
-          ok = mbar_wait_bounded(&qdo_full[0], 0, abort_flag, err_word, ERR_WAIT_FULL);
-          if (ok) {
-            tc_fence_after_sync();
-            issue_s_dp(0);
-            umma_commit(sdp_full);
-          }
-        }
+      auto stage_off = [](int it) -> uint64_t { return static_cast<uint64_t>(((it % ST) * C::STAGE_BYTES) >> 4); };
+      // "pair done" barrier of pair `it` (count 3) and the parity of its phase
+      auto pair_bar = [&](int it) -> uint64_t* { return (C::PIPE && (it & 1)) ? dq_full1 : dq_full; };
+      if (warp == 1) {
+        // S = Q K^T and dP = dO V^T (both operands K-major) -> TMEM. Pair it + 1 is issued as soon as the softmax warps
+        // have read S / dP of pair it, i.e. AHEAD of pair it's dV / dK / dQ, which the other issuers handle.
+        const uint32_t idesc_kk = make_idesc_f16(1, BM, BN, 0, 0);
+        const uint64_t kQ = make_smem_desc_sw128(sQ0, 16, 1024), kDO = make_smem_desc_sw128(sDO0, 16, 1024);
+        const uint64_t kK = make_smem_desc_sw128(sK, 16, 1024), kV = make_smem_desc_sw128(sV, 16, 1024);
+        bool ok = mbar_wait_bounded(kv_full, 0, abort_flag, err_word, ERR_WAIT_FULL);
         for (int it = 0; ok && it < n_it; ++it) {
-          const int s = it % ST;
+          if (!mbar_wait_bounded(&qdo_full[it % ST], (it / ST) & 1u, abort_flag, err_word, ERR_WAIT_FULL)) break;
+          if (it > 0) {
+            if constexpr (C::PIPE) {
+              if (!mbar_wait_bounded(pds_ready, (it - 1) & 1u, abort_flag, err_word, ERR_WAIT_AUX)) break;
+            } else {  // dQ shares its TMEM columns with S: they are free when the drain of pair it - 1 is through
+              if (!mbar_wait_bounded(dq_empty, (it - 1) & 1u, abort_flag, err_word, ERR_WAIT_AUX)) break;
+            }
+          }
+          tc_fence_after_sync();
+          const uint64_t stage = stage_off(it);
+#pragma unroll
+          for (int k = 0; k < D / 16; ++k)
+            umma_f16_ss(tmem_base + C::S_COL, kQ + stage + koff(k), kK + koff(k), idesc_kk, k != 0 ? 1u : 0u);
+#pragma unroll
+          for (int k = 0; k < D / 16; ++k)
+            umma_f16_ss(tmem_base + C::DP_COL, kDO + stage + koff(k), kV + koff(k), idesc_kk, k != 0 ? 1u : 0u);
+          umma_commit(sdp_full);
+        }
+      } else if (warp == 2 || warp == 3) {
+        // dV += P^T dO (warp 2) ; dK += dS^T Q (warp 3): reduction over the 128 queries, 16 per step = 2048 B per step
+        // in both tiles, both operands MN-major
+        const uint32_t idesc_tt = make_idesc_f16(1, BN, D, 1, 1);
+        const uint64_t tA = make_smem_desc_sw128(warp == 2 ? sP : sDS, BM * 128, 1024);
+        const uint64_t tB = make_smem_desc_sw128(warp == 2 ? sDO0 : sQ0, BM * 128, 1024);
+        const uint32_t dcol = tmem_base + (warp == 2 ? C::DV_COL : C::DK_COL);
+        for (int it = 0; it < n_it; ++it) {
           if (!mbar_wait_bounded(pds_ready, it & 1u, abort_flag, err_word, ERR_WAIT_AUX)) break;
           tc_fence_after_sync();
-          if (it + 1 < n_it) {
-            const int s1 = (it + 1) % ST;
-            if (!mbar_wait_bounded(&qdo_full[s1], ((it + 1) / ST) & 1u, abort_flag, err_word, ERR_WAIT_FULL)) break;
-            tc_fence_after_sync();
-            issue_s_dp(s1);
-            umma_commit(sdp_full);
+          const uint64_t stage = stage_off(it);
+          if (it == 0) {
+#pragma unroll
+            for (int k = 0; k < BM / 16; ++k)
+              umma_f16_ss(dcol, tA + (uint64_t)(k * 128), tB + stage + (uint64_t)(k * 128), idesc_tt, k != 0 ? 1u : 0u);
+          } else {
+#pragma unroll
+            for (int k = 0; k < BM / 16; ++k)
+              umma_f16_ss(dcol, tA + (uint64_t)(k * 128), tB + stage + (uint64_t)(k * 128), idesc_tt, 1u);
           }
-          const int bq = it & 1;
-          if (it >= 2) {  // the drain of pair it-2 has emptied this accumulator
-            if (!mbar_wait_bounded(bq ? dq_empty1 : dq_empty, ((it >> 1) - 1) & 1u, abort_flag, err_word, ERR_WAIT_AUX)) break;
-            tc_fence_after_sync();
-          }
-          issue_dv_dk_dq(s, it, bq ? C::DQ_COL1 : C::DQ_COL);
-          umma_commit(&qdo_empty[s]);
-          umma_commit(bq ? dq_full1 : dq_full);
+          umma_commit(pair_bar(it));
         }
       } else {
+        // dQ = dS K (reduction over the 128 keys; dS K-major, K MN-major) into the pair's accumulator
+        const uint32_t idesc_kt = make_idesc_f16(1, BM, D, 0, 1);
+        const uint64_t kDS = make_smem_desc_sw128(sDS, 16, 1024);
+        const uint64_t tK = make_smem_desc_sw128(sK, BN * 128, 1024);
+        bool ok = mbar_wait_bounded(kv_full, 0, abort_flag, err_word, ERR_WAIT_FULL);
         for (int it = 0; ok && it < n_it; ++it) {
-          const int s = it % ST;
-          const uint32_t ph = (it / ST) & 1u;
-          if (!mbar_wait_bounded(&qdo_full[s], ph, abort_flag, err_word, ERR_WAIT_FULL)) break;
-          if (it > 0) {  // dQ shares its TMEM columns with S here
-            if (!mbar_wait_bounded(dq_empty, (it - 1) & 1u, abort_flag, err_word, ERR_WAIT_AUX)) break;
+          if (!mbar_wait_bounded(pds_ready, it & 1u, abort_flag, err_word, ERR_WAIT_AUX)) break;
+          uint32_t dq_col = C::DQ_COL;
+          if constexpr (C::PIPE) {
+            dq_col = (it & 1) ? C::DQ_COL1 : C::DQ_COL;
+            if (it >= 2) {  // the drain of pair it-2 has emptied this accumulator
+              if (!mbar_wait_bounded((it & 1) ? dq_empty1 : dq_empty, ((it >> 1) - 1) & 1u, abort_flag, err_word,
+                                     ERR_WAIT_AUX))
+                break;
+            }
           }
           tc_fence_after_sync();
-          issue_s_dp(s);
-          umma_commit(sdp_full);
-          if (!mbar_wait_bounded(pds_ready, it & 1u, abort_flag, err_word, ERR_WAIT_AUX)) break;
-          tc_fence_after_sync();
-          issue_dv_dk_dq(s, it, C::DQ_COL);
-          umma_commit(&qdo_empty[s]);
-          umma_commit(dq_full);
+#pragma unroll
+          for (int k = 0; k < BN / 16; ++k)
+            umma_f16_ss(tmem_base + dq_col, kDS + koff(k), tK + (uint64_t)(k * 128), idesc_kt, k != 0 ? 1u : 0u);
+          umma_commit(pair_bar(it));
         }
       }
     }
   } else {
     const int quad = warp & 3;
-    const int part = (warp - 2) >> 2;  // which quarter of the columns this warp handles
+    const int part = (warp - FIRST_WORK_WARP) >> 2;  // which quarter of the columns this warp handles
     const int r = quad * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
     const float c2 = p.scale * 1.4426950408889634f;
@@ -296,7 +298,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
       for (int rr = 0; rr < ROUNDS; ++rr) {
         // the previous round's reduce must have finished READING the staging tile. The thread that issued it checks
         // that only now, a whole softmax phase later, so that the TMA engine's latency is off the critical path.
-        if (warp == 2 && lane == 0 && rd > 0) {
+        if (warp == FIRST_WORK_WARP && lane == 0 && rd > 0) {
           tma_store_wait_read0();
           mbar_arrive(stage_free);
         }
@@ -314,7 +316,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         }
         fence_proxy_async_smem();
         mbar_arrive(stage_full);
-        if (warp == 2 && lane == 0) {
+        if (warp == FIRST_WORK_WARP && lane == 0) {
           if (mbar_wait_bounded(stage_full, rd & 1u, abort_flag, err_word, ERR_WAIT_AUX)) {
 #pragma unroll
             for (int hh = 0; hh < 2; ++hh)
@@ -418,7 +420,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
       if (wait_dq_full(n_it - 1)) drain(n_it - 1);
       else ok = false;
     }
-    if (warp == 2 && lane == 0) tma_store_wait_all0();
+    if (warp == FIRST_WORK_WARP && lane == 0) tma_store_wait_all0();
     // epilogue: dK_j, dV_j (thread = key row). The last dq_full wait covered every MMA of this CTA.
     if (ok && n_it > 0) {
       const int kvi = kv0 + r;
@@ -545,7 +547,7 @@ static int launch_bwd(const void* dout, const void* qkv, const void* out, const 
     attr = true;
   }
   BwdParams p{lse, delta, dq_acc, (__nv_bfloat16*)dqkv, B, L, H, Hkv, 1.0f / sqrtf((float)D)};
-  dim3 grid((L + BN - 1) / BN, Hkv, B);
+  dim3 grid(Hkv * B, (L + BN - 1) / BN);
   kern<<<grid, NTHREADS, C::SMEM_BYTES, st>>>(tmQKV, tmDO, tmDQ, p, device_err_word());
   B200_CUDA_CHECK(cudaGetLastError());
   {

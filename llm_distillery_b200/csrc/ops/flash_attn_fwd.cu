@@ -1,18 +1,20 @@
 // Causal GQA flash-attention forward for sm_100a on tcgen05 tensor cores.
 //
-// One CTA = one (batch, q-head, 128-query block); keys are walked in tiles of BN = 64. Roles (192 threads):
+// One CTA = one (batch, q-head, 128-query block); keys are walked in tiles of BN = 64. Roles (224 threads):
 //   warp 0    TMA producer : Q once, then K tiles through a 3-stage ring and V tiles through a 2-stage ring (3D tensor
 //                            map [B][L][width], so rows past the sequence end read zeros; no multicast)
-//   warp 1    MMA issuer   : S_j = Q K_j^T (tcgen05.mma, both operands K-major) into one of TWO score buffers in TMEM;
-//                            O += P_j V_j with A = P_j read from TMEM and V_j as MN-major B from shared memory
-//   warps 2-5 softmax      : thread = query row. Reads S_j from TMEM once (both 32-column loads in flight),
+//   warp 1    P V issuer   : O += P_j V_j with A = P_j read from TMEM and V_j as MN-major B from shared memory
+//   warp 2    S issuer     : S_j = Q K_j^T (tcgen05.mma, both operands K-major) into one of TWO score buffers in TMEM
+//                            (two issuing threads because every tcgen05 instruction - MMA, commit, a completed
+//                            mbarrier wait - costs its issuer on the order of a hundred cycles here: one thread
+//                            issuing both groups of a 64-key tile took longer than the softmax of that tile)
+//   warps 3-6 softmax      : thread = query row. Reads S_j from TMEM once (both 32-column loads in flight),
 //                            exponentiates against the maximum known so far (exp2 domain, packed f32x2 arithmetic,
 //                            part of the exponentials on the FMA pipe), writes P_j as bf16 pairs over the first half
 //                            of the same score buffer, and only when a score outgrew the maximum by more than 2^8
 //                            moves the maximum, rescales O in TMEM and redoes the tile; final O / l and lse.
 // The score buffers alternate: S_{j+1} is computed while the softmax warps work on S_j, and S_{j+2} goes into S_j's
-// buffer as soon as P_j V_j has been issued (MMAs of one thread execute in order), so in the steady state the
-// softmax warps never wait for the tensor core and the tensor core never waits for them.
+// buffer as soon as P_j V_j has completed, so in the steady state the softmax warps never wait for the tensor core.
 // P never touches shared memory: an N = D MMA fed from shared memory on both sides is bound by shared-memory
 // bandwidth, and the softmax warps issue no st.shared and no proxy fence.
 // TMEM: 2 x 64 score columns + D output columns (<= 256); shared memory 56 KB (D = 64) / 112 KB (D = 128): two CTAs
@@ -27,7 +29,7 @@ namespace fa {
 
 constexpr int BM = 128;
 constexpr int BN = 64;
-constexpr int NTHREADS = 192;
+constexpr int NTHREADS = 224;
 constexpr int KS = 3;  // K ring
 constexpr int VS = 2;  // V ring
 constexpr float kRescaleThreshold = 8.0f;  // in log2 units
@@ -86,17 +88,20 @@ __global__ void __launch_bounds__(NTHREADS, 2)
   uint64_t* k_empty = bars + 4;   // [KS]
   uint64_t* v_full = bars + 7;    // [VS]
   uint64_t* v_empty = bars + 9;   // [VS]
-  uint64_t* s_full = bars + 11;   // [2]
-  uint64_t* p_ready = bars + 13;  // [2]
-  uint64_t* o_done = bars + 15;
-  uint64_t* o_final = bars + 16;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
+  uint64_t* s_full = bars + 11;   // [2]  S_t complete (buffer t & 1)
+  uint64_t* p_ready = bars + 13;  // [2]  P_j written by the 128 softmax threads
+  uint64_t* pv_done = bars + 15;  // [2]  P_j V_j complete: buffer j & 1 and V stage j % 2 are free, O holds tile j
+  uint64_t* o_final = bars + 17;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nqb = (p.L + BM - 1) / BM;
-  const int qb = nqb - 1 - blockIdx.x;  // heaviest (longest causal span) blocks first
-  const int hq = blockIdx.y, b = blockIdx.z;
+  // blockIdx.x runs over (head, batch) and blockIdx.y over the query blocks, longest causal span first: the hardware
+  // hands out blocks x-fastest, so EVERY head's heaviest block starts before any light one and the light blocks fill
+  // the tail (with the query block fastest, the last head's heaviest block started when the grid was almost through)
+  const int qb = nqb - 1 - blockIdx.y;
+  const int hq = blockIdx.x % p.H, b = blockIdx.x / p.H;
   const int hkv = hq / (p.H / p.Hkv);
   const int q0 = qb * BM;
   const int qpos0 = p.q_off + q0;                       // sequence position of the block's first query
@@ -123,8 +128,8 @@ __global__ void __launch_bounds__(NTHREADS, 2)
     for (int s = 0; s < 2; ++s) {
       mbar_init(&s_full[s], 1);
       mbar_init(&p_ready[s], 128);
+      mbar_init(&pv_done[s], 1);
     }
-    mbar_init(o_done, 1);
     mbar_init(o_final, 1);
     *abort_flag = 0;
     fence_mbar_init();
@@ -155,7 +160,8 @@ __global__ void __launch_bounds__(NTHREADS, 2)
         mbar_arrive_expect_tx(&k_full[ks], C::T_BYTES);
 #pragma unroll
         for (int c = 0; c < D / 64; ++c) tma_load_3d(sK + c * (BN * 128), &tmK, &k_full[ks], colK + c * 64, j * BN, b);
-        if (!mbar_wait_bounded(&v_empty[vs], ((j / VS) & 1u) ^ 1u, abort_flag, err_word, ERR_WAIT_EMPTY)) break;
+        // V stage j % 2 was read by P_{j-2} V_{j-2} (VS == 2, so it shares its index with the score buffer)
+        if (j >= VS && !mbar_wait_bounded(&pv_done[vs], ((j - VS) >> 1) & 1u, abort_flag, err_word, ERR_WAIT_EMPTY)) break;
         uint8_t* sV = smem + C::OFF_V + vs * C::T_BYTES;
         mbar_arrive_expect_tx(&v_full[vs], C::T_BYTES);
 #pragma unroll
@@ -163,46 +169,24 @@ __global__ void __launch_bounds__(NTHREADS, 2)
       }
     }
   } else if (warp == 1) {
+    // ------------------------------------------------------------------ O += P_j V_j
     if (lane == 0) {
-      const uint32_t idesc_s = make_idesc_f16(1, BM, BN, 0, 0);
       const uint32_t idesc_o = make_idesc_f16(1, BM, D, 0, 1);
-      // Every shared-memory descriptor of the loop is a constant plus a stage offset: they are built once here, so
-      // that issuing an MMA costs a 64-bit add and the instruction itself. (With the descriptors rebuilt per MMA the
-      // issuing thread needed ~80 cycles per instruction, more than a 128 x 64 x 16 MMA occupies the tensor core.)
-      uint64_t dQ[D / 16], dK[D / 16], dV[BN / 16];
-#pragma unroll
-      for (int k = 0; k < D / 16; ++k) {
-        const uint32_t sub = k >> 2, kk = k & 3;   // 64-column sub-tiles are BM*128 (Q) / BN*128 (K) bytes apart
-        dQ[k] = make_smem_desc_sw128(smem_u32(smem) + sub * (BM * 128) + kk * 32, 16, 1024);
-        dK[k] = make_smem_desc_sw128(smem_u32(smem + C::OFF_K) + sub * (BN * 128) + kk * 32, 16, 1024);
-      }
+      // descriptors are constants plus a stage offset (the address field counts 16-byte units): built once
+      uint64_t dV[BN / 16];
 #pragma unroll
       for (int k = 0; k < BN / 16; ++k)   // V is MN-major (D contiguous), 64-wide D chunks BN*128 bytes apart
         dV[k] = make_smem_desc_sw128(smem_u32(smem + C::OFF_V) + k * (16 * 128), BN * 128, 1024);
-      bool ok = mbar_wait_bounded(q_full, 0, abort_flag, err_word, ERR_WAIT_FULL);
-      // S_t = Q K_t^T into score buffer t & 1
-      auto issue_s = [&](int t) -> bool {
-        const int ks = t % KS;
-        if (!mbar_wait_bounded(&k_full[ks], (t / KS) & 1u, abort_flag, err_word, ERR_WAIT_FULL)) return false;
-        tc_fence_after_sync();
-        const uint64_t stage = static_cast<uint64_t>((ks * C::T_BYTES) >> 4);   // the address field counts 16-byte units
-        const uint32_t dcol = tmem_base + C::S_COL + (t & 1) * BN;
-#pragma unroll
-        for (int k = 0; k < D / 16; ++k) umma_f16_ss(dcol, dQ[k], dK[k] + stage, idesc_s, k != 0 ? 1u : 0u);
-        umma_commit(&k_empty[ks]);
-        umma_commit(&s_full[t & 1]);
-        return true;
-      };
-      for (int t = 0; ok && t < 2 && t < n_kv; ++t) ok = issue_s(t);
-      for (int j = 0; ok && j < n_kv; ++j) {
+      bool ok = true;
+      for (int j = 0; j < n_kv; ++j) {
         const int bsel = j & 1, vs = j % VS;
         // P_j is in TMEM (over the first half of S_j) once the softmax warps have arrived
-        if (!mbar_wait_bounded(&p_ready[bsel], (j >> 1) & 1u, abort_flag, err_word, ERR_WAIT_AUX)) break;
-        if (!mbar_wait_bounded(&v_full[vs], (j / VS) & 1u, abort_flag, err_word, ERR_WAIT_FULL)) break;
+        if (!mbar_wait_bounded(&p_ready[bsel], (j >> 1) & 1u, abort_flag, err_word, ERR_WAIT_AUX)) { ok = false; break; }
+        if (!mbar_wait_bounded(&v_full[vs], (j / VS) & 1u, abort_flag, err_word, ERR_WAIT_FULL)) { ok = false; break; }
         tc_fence_after_sync();
         const uint64_t stage = static_cast<uint64_t>((vs * C::T_BYTES) >> 4);
         const uint32_t pcol = tmem_base + C::S_COL + bsel * BN;
-        // O += P V : BN/16 k-steps over keys. A = P from TMEM (16 bf16 of a row = 8 columns per step)
+        // BN/16 k-steps over keys. A = P from TMEM (16 bf16 of a row = 8 columns per step)
         if (j == 0) {
 #pragma unroll
           for (int k = 0; k < BN / 16; ++k)
@@ -211,14 +195,35 @@ __global__ void __launch_bounds__(NTHREADS, 2)
 #pragma unroll
           for (int k = 0; k < BN / 16; ++k) umma_f16_ts(tmem_base + C::O_COL, pcol + k * 8, dV[k] + stage, idesc_o, 1u);
         }
-        umma_commit(&v_empty[vs]);
-        umma_commit(o_done);
-        // the buffer that held S_j / P_j takes S_{j+2}: it executes behind P_j V_j, which is what frees the buffer
-        if (j + 2 < n_kv) ok = issue_s(j + 2);
+        umma_commit(&pv_done[bsel]);
       }
-      // its own barrier for the very last P V: the softmax warps do not follow o_done tile by tile, so its parity
-      // alone would not tell them which of the last two tiles has completed
-      if (ok) umma_commit(o_final);
+      if (ok) umma_commit(o_final);   // a barrier of its own for the last tile: the epilogue waits on nothing else
+    }
+  } else if (warp == 2) {
+    // ------------------------------------------------------------------ S_t = Q K_t^T
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc_f16(1, BM, BN, 0, 0);
+      uint64_t dQ[D / 16], dK[D / 16];
+#pragma unroll
+      for (int k = 0; k < D / 16; ++k) {
+        const uint32_t sub = k >> 2, kk = k & 3;   // 64-column sub-tiles are BM*128 (Q) / BN*128 (K) bytes apart
+        dQ[k] = make_smem_desc_sw128(smem_u32(smem) + sub * (BM * 128) + kk * 32, 16, 1024);
+        dK[k] = make_smem_desc_sw128(smem_u32(smem + C::OFF_K) + sub * (BN * 128) + kk * 32, 16, 1024);
+      }
+      bool ok = mbar_wait_bounded(q_full, 0, abort_flag, err_word, ERR_WAIT_FULL);
+      for (int t = 0; ok && t < n_kv; ++t) {
+        const int ks = t % KS;
+        // buffer t & 1 held S_{t-2} and then P_{t-2}: it is free when P_{t-2} V_{t-2} has completed
+        if (t >= 2 && !mbar_wait_bounded(&pv_done[t & 1], ((t - 2) >> 1) & 1u, abort_flag, err_word, ERR_WAIT_AUX)) break;
+        if (!mbar_wait_bounded(&k_full[ks], (t / KS) & 1u, abort_flag, err_word, ERR_WAIT_FULL)) break;
+        tc_fence_after_sync();
+        const uint64_t stage = static_cast<uint64_t>((ks * C::T_BYTES) >> 4);
+        const uint32_t dcol = tmem_base + C::S_COL + (t & 1) * BN;
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) umma_f16_ss(dcol, dQ[k], dK[k] + stage, idesc_s, k != 0 ? 1u : 0u);
+        umma_commit(&s_full[t & 1]);
+        umma_commit(&k_empty[ks]);
+      }
     }
   } else {
     // ------------------------------------------------------------------ softmax / epilogue
@@ -307,7 +312,7 @@ __global__ void __launch_bounds__(NTHREADS, 2)
         if (need) m_used = mx;
         l *= alpha;
         if (j > 0) {
-          int w2 = mbar_wait_bounded(o_done, (j - 1) & 1u, abort_flag, err_word, ERR_WAIT_AUX) ? 1 : 0;
+          int w2 = mbar_wait_bounded(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1u, abort_flag, err_word, ERR_WAIT_AUX) ? 1 : 0;
           if (!__all_sync(0xffffffffu, w2)) { ok = false; break; }
           tc_fence_after_sync();
 #pragma unroll
@@ -328,8 +333,13 @@ __global__ void __launch_bounds__(NTHREADS, 2)
         nmb = pack_f32x2(-m_used * c2, -m_used * c2);
         sum2 = 0ull;
         float mx2 = m_used;
+        // S_j is still intact in TMEM (P_j is stored below): read it again rather than keep it in registers
+        tmem_ld_32x32b_x32(tS, va);
+        tmem_ld_wait();
         chunk(va, nmb, lim, mx2, sum2, pka);
-        chunk(vb, nmb, lim - 32, mx2, sum2, pkb);
+        tmem_ld_32x32b_x32(tS + 32, va);
+        tmem_ld_wait();
+        chunk(va, nmb, lim - 32, mx2, sum2, pkb);
       }
       // P_j over the first half of S_j (both halves of S_j are in registers by now)
       tmem_st_32x32b_x16(tS, pka);
@@ -410,7 +420,7 @@ static int launch_fwd(const void* q, long long q_width, int colQ0, const void* k
     attr = true;
   }
   FwdParams p{(__nv_bfloat16*)out, lse, B, L, H, Hkv, 1.0f / sqrtf((float)D), q_off, colQ0, colK0, colV0};
-  dim3 grid((L + BM - 1) / BM, H, B);
+  dim3 grid(H * B, (L + BM - 1) / BM);
   kern<<<grid, NTHREADS, C::SMEM_BYTES, st>>>(tmQ, tmK, tmV, p, device_err_word());
   B200_CUDA_CHECK(cudaGetLastError());
   return B200_OK;

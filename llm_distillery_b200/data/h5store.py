@@ -90,6 +90,33 @@ def merge_topk(disk_logp: np.ndarray, disk_idx: np.ndarray, new_logp: np.ndarray
     return out_l, out_i
 
 
+def merge_topk_on(device: str, disk_logp: np.ndarray, disk_idx: np.ndarray, new_logp: np.ndarray, new_idx: np.ndarray):
+    """``merge_topk`` on the GPU the store was opened for (kernel ``topk_merge``: csrc/loss/topk_logprob.cu), or the
+    NumPy statement above when the store runs without a GPU or the rows do not fit the kernel (K above 1024, the two
+    teachers kept different K). Called from the store's writer threads: the merge of conversation i runs while the
+    model computes the next batch."""
+    K = disk_logp.shape[1]
+    n = min(len(disk_logp), len(new_logp))
+    dev = str(device or "cpu")
+    if not dev.startswith("cuda") or K > 1024 or new_logp.shape[1] != K or n == 0:
+        return merge_topk(disk_logp, disk_idx, new_logp, new_idx)
+    import torch
+    if not torch.cuda.is_available():
+        return merge_topk(disk_logp, disk_idx, new_logp, new_idx)
+    from ..ops import topk as topk_ops
+    d = torch.device(dev)
+    with torch.cuda.device(d):
+        up = lambda a, dt: torch.from_numpy(np.ascontiguousarray(a[:n]).astype(dt, copy=False)).to(d)   # noqa: E731
+        lp, ix = topk_ops.topk_merge(up(disk_logp, np.float32), up(disk_idx, np.int32), up(new_logp, np.float32),
+                                     up(new_idx, np.int32))
+        out_l, out_i = lp.cpu().numpy(), ix.cpu().numpy().astype(np.int64)
+    rest_l, rest_i = (disk_logp[n:], disk_idx[n:]) if len(disk_logp) > n else (new_logp[n:], new_idx[n:])
+    if len(rest_l):
+        out_l = np.concatenate([out_l, rest_l.astype(np.float32)])
+        out_i = np.concatenate([out_i, rest_i.astype(np.int64)])
+    return out_l, out_i
+
+
 def merge_full(disk_logp: np.ndarray, new_logp: np.ndarray) -> np.ndarray:
     n = max(len(disk_logp), len(new_logp))
     acc = np.zeros((n, disk_logp.shape[1]), dtype=np.float32)
@@ -155,7 +182,8 @@ class H5Store:
             if merge and self.lib.h5s_has(self.h, cid):
                 d_l, d_i = self.load_id(cid)
                 if indices is not None and d_i is not None:
-                    values, indices = merge_topk(d_l, d_i, np.asarray(values, dtype=np.float32), np.asarray(indices))
+                    values, indices = merge_topk_on(self.device, d_l, d_i, np.asarray(values, dtype=np.float32),
+                                                    np.asarray(indices))
                 else:
                     values = merge_full(d_l, np.asarray(values, dtype=np.float32))
                 sha = sha or (self.get_sha(cid) or "")

@@ -66,3 +66,57 @@ def test_cli_collect_train_checkpoint_on_gpu(tmp_path, monkeypatch):
     # second run: nothing to collect; training is already complete
     out2 = cli.main(["--config", path])
     assert out2["tokens_collected"] == 0, out2
+
+
+def test_two_teachers_are_merged_on_the_device(tmp_path, monkeypatch):
+    """Two teachers of one vocabulary: the second teacher's rows are merged into the stored ones by the
+    ``topk_merge`` kernel from the store's writer threads; the result equals the NumPy statement of the merge."""
+    import numpy as np
+    from llm_distillery_b200 import cli
+    from llm_distillery_b200.data import h5store
+    from llm_distillery_b200.data.h5store import H5Store
+    from llm_distillery_b200.models.llama import preset
+    from llm_distillery_b200.utils import synthetic
+    monkeypatch.setenv("B200_NO_PROGRESS", "1")
+    monkeypatch.delenv("WORLD_SIZE", raising=False)
+    root = str(tmp_path)
+    tok = os.path.join(root, "tok")
+    synthetic.make_tokenizer(tok, 400)
+    kw = dict(vocab_size=512, hidden_size=256, intermediate_size=688, max_position_embeddings=512)
+    for name, seed in (("teacher_a", 1), ("teacher_b", 7)):
+        synthetic.make_model_dir(os.path.join(root, "teachers", name), preset("plumbing-teacher", **kw), tok, seed=seed,
+                                 batch_size=4)
+    synthetic.make_model_dir(os.path.join(root, "student"), preset("plumbing-student", **kw), tok, seed=2)
+    synthetic.make_dataset(os.path.join(root, "train.jsonl"), 8, seed=3)
+    synthetic.make_dataset(os.path.join(root, "val.jsonl"), 2, seed=4)
+    calls = {"device": 0, "host": 0, "pairs": []}
+    real = h5store.merge_topk_on
+
+    def spy(device, d_l, d_i, n_l, n_i):
+        out = real(device, d_l, d_i, n_l, n_i)
+        calls["device" if str(device).startswith("cuda") else "host"] += 1
+        if len(calls["pairs"]) < 3:
+            calls["pairs"].append((out, h5store.merge_topk(d_l, d_i, n_l, n_i)))
+        return out
+    monkeypatch.setattr(h5store, "merge_topk_on", spy)
+    conf = {"cache_folder": os.path.join(root, "cache"), "dataset_path": os.path.join(root, "train.jsonl"),
+            "validation_dataset_path": os.path.join(root, "val.jsonl"), "teacher_models_folder": os.path.join(root, "teachers"),
+            "student_path": os.path.join(root, "student"), "context_len": 128, "crop_distr_to_size": 400, "save_topK": 32,
+            "enable_topK": True, "device": "cuda:0", "num_epochs": 1, "num_warmup_steps": 0, "batch_size": 2,
+            "grad_accum_batches": 1, "temperature": 1.0, "lr": 1e-3, "optimizer": "adamw", "data_order": "sorted",
+            "training_precision": "bf16", "validate_every_n_epochs": 1, "save_student_every_n_epochs": 1,
+            "freeze_layers": [], "loss": "kl", "max_cache_size_gb": 320}
+    path = os.path.join(root, "config.json")
+    with open(path, "w") as f:
+        json.dump(conf, f)
+    out = cli.main(["--config", path])
+    assert out["trained_samples"] == 8
+    assert calls["device"] >= 8 and calls["host"] == 0, calls          # every conversation of the second teacher
+    for (gl, gi), (hl, hi) in calls["pairs"]:
+        order_g, order_h = np.argsort(gi, axis=1), np.argsort(hi, axis=1)
+        assert np.array_equal(np.take_along_axis(gi, order_g, 1), np.take_along_axis(hi, order_h, 1))
+        assert np.allclose(np.take_along_axis(gl, order_g, 1), np.take_along_axis(hl, order_h, 1), atol=2e-3)
+    store = H5Store(os.path.join(root, "cache", "dataset"))
+    v, ix = store.load_id(store.get_dataset_ids()[0])
+    assert (np.exp(v.astype(np.float32)).sum(-1) > 1.0).any()              # two teachers' probabilities summed
+    store.close()
