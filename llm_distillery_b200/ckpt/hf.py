@@ -86,6 +86,10 @@ def load_hf_state_dict(path: str) -> dict[str, torch.Tensor]:
     sd = {}
     for f in files:
         sd.update(load_file(os.path.join(path, f)))
+    if any(k.endswith((".qweight", ".q_weight")) for k in sd):
+        # a quantised export (GPTQ): expanded to bf16 here, once (ckpt/gptq.py says why and which layouts are read)
+        from . import gptq
+        sd = gptq.dequantize_state_dict(sd, gptq.quantization_config(path) or {})
     return sd
 
 
@@ -254,6 +258,11 @@ def load_tp_weights(path: str, rank: int, tp: int, vocab: int | None = None, dty
     whole model): q/k/v and gate/up rows, o_proj / down_proj columns, an equal slice of the (cropped) LM head,
     replicated embedding and norms. Returns (config, weights) in the layout of ``parallel.tp.shard_llama_weights``."""
     from safetensors import safe_open
+    from . import gptq
+    if (gptq.quantization_config(path) or {}).get("quant_method") in ("gptq", "exl2"):
+        raise ValueError(f"{path} is a quantised checkpoint: the tensor-parallel loader reads slices of plain 16-bit "
+                         "tensors. Collect with tp_size = 1 (the dequantised model fits one GPU) or export the "
+                         "checkpoint to bf16 first.")
     cfg = LlamaConfig.from_pretrained(path)
     H, Hkv, d, f = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.intermediate_size
     if H % tp or Hkv % tp or f % tp:

@@ -85,6 +85,40 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
   }
 }
 
+// Non-suspending variant for the single threads that issue MMAs or TMA loads: mbarrier.test_wait returns at once, so
+// the waiter sees a completed phase within a few cycles (try_wait may park the thread, and waking it took 300+ cycles
+// in the attention kernels, where these hand-offs sit on the critical path). Same bound and abort protocol.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_spin_bounded(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                                  unsigned int* err_word, unsigned int code) {
+  if (mbar_test_wait(bar, parity)) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    if (mbar_test_wait(bar, parity)) return true;
+    if (((++spins) & 0xfffu) == 0u) {
+      if (*abort_flag) return false;
+      if (globaltimer_ns() - t0 > kWaitTimeoutNs) {
+        *abort_flag = 1;
+        if (err_word) atomicCAS(err_word, 0u, code);
+        return false;
+      }
+    }
+  }
+}
+
 // ---------------------------------------------------------------- fences
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

@@ -165,7 +165,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
           const int pd = it - ST;
           uint64_t* done = (C::PIPE && (pd & 1)) ? dq_full1 : dq_full;
           const uint32_t par = C::PIPE ? ((pd >> 1) & 1u) : (pd & 1u);
-          if (!mbar_wait_bounded(done, par, abort_flag, err_word, ERR_WAIT_EMPTY)) break;
+          if (!mbar_spin_bounded(done, par, abort_flag, err_word, ERR_WAIT_EMPTY)) break;
         }
         uint8_t* sQ = smem + C::OFF_QDO + s * C::STAGE_BYTES;
         uint8_t* sDO = sQ + C::QDO_BYTES;
@@ -199,14 +199,14 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         const uint32_t idesc_kk = make_idesc_f16(1, BM, BN, 0, 0);
         const uint64_t kQ = make_smem_desc_sw128(sQ0, 16, 1024), kDO = make_smem_desc_sw128(sDO0, 16, 1024);
         const uint64_t kK = make_smem_desc_sw128(sK, 16, 1024), kV = make_smem_desc_sw128(sV, 16, 1024);
-        bool ok = mbar_wait_bounded(kv_full, 0, abort_flag, err_word, ERR_WAIT_FULL);
+        bool ok = mbar_spin_bounded(kv_full, 0, abort_flag, err_word, ERR_WAIT_FULL);
         for (int it = 0; ok && it < n_it; ++it) {
-          if (!mbar_wait_bounded(&qdo_full[it % ST], (it / ST) & 1u, abort_flag, err_word, ERR_WAIT_FULL)) break;
+          if (!mbar_spin_bounded(&qdo_full[it % ST], (it / ST) & 1u, abort_flag, err_word, ERR_WAIT_FULL)) break;
           if (it > 0) {
             if constexpr (C::PIPE) {
-              if (!mbar_wait_bounded(pds_ready, (it - 1) & 1u, abort_flag, err_word, ERR_WAIT_AUX)) break;
+              if (!mbar_spin_bounded(pds_ready, (it - 1) & 1u, abort_flag, err_word, ERR_WAIT_AUX)) break;
             } else {  // dQ shares its TMEM columns with S: they are free when the drain of pair it - 1 is through
-              if (!mbar_wait_bounded(dq_empty, (it - 1) & 1u, abort_flag, err_word, ERR_WAIT_AUX)) break;
+              if (!mbar_spin_bounded(dq_empty, (it - 1) & 1u, abort_flag, err_word, ERR_WAIT_AUX)) break;
             }
           }
           tc_fence_after_sync();
@@ -227,7 +227,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         const uint64_t tB = make_smem_desc_sw128(warp == 2 ? sDO0 : sQ0, BM * 128, 1024);
         const uint32_t dcol = tmem_base + (warp == 2 ? C::DV_COL : C::DK_COL);
         for (int it = 0; it < n_it; ++it) {
-          if (!mbar_wait_bounded(pds_ready, it & 1u, abort_flag, err_word, ERR_WAIT_AUX)) break;
+          if (!mbar_spin_bounded(pds_ready, it & 1u, abort_flag, err_word, ERR_WAIT_AUX)) break;
           tc_fence_after_sync();
           const uint64_t stage = stage_off(it);
           if (it == 0) {
@@ -246,14 +246,14 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         const uint32_t idesc_kt = make_idesc_f16(1, BM, D, 0, 1);
         const uint64_t kDS = make_smem_desc_sw128(sDS, 16, 1024);
         const uint64_t tK = make_smem_desc_sw128(sK, BN * 128, 1024);
-        bool ok = mbar_wait_bounded(kv_full, 0, abort_flag, err_word, ERR_WAIT_FULL);
+        bool ok = mbar_spin_bounded(kv_full, 0, abort_flag, err_word, ERR_WAIT_FULL);
         for (int it = 0; ok && it < n_it; ++it) {
-          if (!mbar_wait_bounded(pds_ready, it & 1u, abort_flag, err_word, ERR_WAIT_AUX)) break;
+          if (!mbar_spin_bounded(pds_ready, it & 1u, abort_flag, err_word, ERR_WAIT_AUX)) break;
           uint32_t dq_col = C::DQ_COL;
           if constexpr (C::PIPE) {
             dq_col = (it & 1) ? C::DQ_COL1 : C::DQ_COL;
             if (it >= 2) {  // the drain of pair it-2 has emptied this accumulator
-              if (!mbar_wait_bounded((it & 1) ? dq_empty1 : dq_empty, ((it >> 1) - 1) & 1u, abort_flag, err_word,
+              if (!mbar_spin_bounded((it & 1) ? dq_empty1 : dq_empty, ((it >> 1) - 1) & 1u, abort_flag, err_word,
                                      ERR_WAIT_AUX))
                 break;
             }

@@ -30,22 +30,26 @@ namespace fa {
 constexpr int BM = 128;
 constexpr int BN = 64;
 constexpr int NTHREADS = 224;
-constexpr int KS = 3;  // K ring
 constexpr int VS = 2;  // V ring
 constexpr float kRescaleThreshold = 8.0f;  // in log2 units
 
 template <int D>
 struct Cfg {
+  // Score buffers in TMEM: S_{t} may be issued as soon as P_{t-NBUF} V_{t-NBUF} has completed. With two buffers that
+  // dependency (softmax_j -> P_j V_j -> S_{j+2}) is longer than one softmax and the softmax warps idle a third of
+  // the time; a third buffer (head dim 64: 3 x 64 + 64 columns = 256) takes it off the critical path.
+  static constexpr int NBUF = (3 * BN + D <= 256) ? 3 : 2;
+  static constexpr int KS = NBUF + 1;  // K ring: K runs NBUF tiles ahead of the softmax
   static constexpr int Q_BYTES = BM * D * 2;
   static constexpr int T_BYTES = BN * D * 2;  // one K or V tile
   static constexpr int OFF_K = Q_BYTES;
-  static constexpr int OFF_V = OFF_K + KS * T_BYTES;
+  static constexpr int OFF_V = OFF_K + KS * T_BYTES;   // KS declared above
   static constexpr int OFF_BAR = OFF_V + VS * T_BYTES;
   static constexpr int SMEM_BYTES = OFF_BAR + 256;
   static constexpr uint32_t TMEM_COLS = 256;
-  static constexpr uint32_t S_COL = 0;        // two buffers of BN columns; P_j overwrites columns [0, BN/2) of S_j
-  static constexpr uint32_t O_COL = 2 * BN;
-  static_assert(2 * BN + D <= 256, "TMEM budget");
+  static constexpr uint32_t S_COL = 0;        // NBUF buffers of BN columns; P_j overwrites columns [0, BN/2) of S_j
+  static constexpr uint32_t O_COL = NBUF * BN;
+  static_assert(NBUF * BN + D <= 256, "TMEM budget");
 };
 
 struct FwdParams {
@@ -83,16 +87,16 @@ __global__ void __launch_bounds__(NTHREADS, 2)
   using C = Cfg<D>;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
+  constexpr int KS = C::KS, NBUF = C::NBUF;
   uint64_t* q_full = bars + 0;
-  uint64_t* k_full = bars + 1;    // [KS]
-  uint64_t* k_empty = bars + 4;   // [KS]
-  uint64_t* v_full = bars + 7;    // [VS]
-  uint64_t* v_empty = bars + 9;   // [VS]
-  uint64_t* s_full = bars + 11;   // [2]  S_t complete (buffer t & 1)
-  uint64_t* p_ready = bars + 13;  // [2]  P_j written by the 128 softmax threads
-  uint64_t* pv_done = bars + 15;  // [2]  P_j V_j complete: buffer j & 1 and V stage j % 2 are free, O holds tile j
-  uint64_t* o_final = bars + 17;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
+  uint64_t* k_full = bars + 1;    // [KS]   (KS <= 4)
+  uint64_t* k_empty = bars + 5;   // [KS]
+  uint64_t* v_full = bars + 9;    // [VS]
+  uint64_t* s_full = bars + 11;   // [NBUF] S_t complete (buffer t % NBUF)
+  uint64_t* p_ready = bars + 14;  // [NBUF] P_j written by the 128 softmax threads
+  uint64_t* pv_done = bars + 17;  // [NBUF] P_j V_j complete: its score buffer and V stage are free, O holds tile j
+  uint64_t* o_final = bars + 20;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 21);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -121,11 +125,8 @@ __global__ void __launch_bounds__(NTHREADS, 2)
       mbar_init(&k_full[s], 1);
       mbar_init(&k_empty[s], 1);
     }
-    for (int s = 0; s < VS; ++s) {
-      mbar_init(&v_full[s], 1);
-      mbar_init(&v_empty[s], 1);
-    }
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < VS; ++s) mbar_init(&v_full[s], 1);
+    for (int s = 0; s < NBUF; ++s) {
       mbar_init(&s_full[s], 1);
       mbar_init(&p_ready[s], 128);
       mbar_init(&pv_done[s], 1);
@@ -148,20 +149,27 @@ __global__ void __launch_bounds__(NTHREADS, 2)
   const int colV = p.colV0 + hkv * D;
 
   if (warp == 0) {
+    // two producer threads: K runs NBUF tiles ahead of the softmax and must not queue behind the V loads, which are
+    // gated by the P V MMAs two tiles back
     if (lane == 0) {
       mbar_arrive_expect_tx(q_full, C::Q_BYTES);
 #pragma unroll
       for (int c = 0; c < D / 64; ++c) tma_load_3d(smem + c * (BM * 128), &tmQ, q_full, colQ + c * 64, q0, b);
       for (int j = 0; j < n_kv; ++j) {
-        // K_j runs two tiles ahead of the softmax, V_j is only needed when P_j exists: separate rings
-        const int ks = j % KS, vs = j % VS;
-        if (!mbar_wait_bounded(&k_empty[ks], ((j / KS) & 1u) ^ 1u, abort_flag, err_word, ERR_WAIT_EMPTY)) break;
+        const int ks = j % KS;
+        if (!mbar_spin_bounded(&k_empty[ks], ((j / KS) & 1u) ^ 1u, abort_flag, err_word, ERR_WAIT_EMPTY)) break;
         uint8_t* sK = smem + C::OFF_K + ks * C::T_BYTES;
         mbar_arrive_expect_tx(&k_full[ks], C::T_BYTES);
 #pragma unroll
         for (int c = 0; c < D / 64; ++c) tma_load_3d(sK + c * (BN * 128), &tmK, &k_full[ks], colK + c * 64, j * BN, b);
-        // V stage j % 2 was read by P_{j-2} V_{j-2} (VS == 2, so it shares its index with the score buffer)
-        if (j >= VS && !mbar_wait_bounded(&pv_done[vs], ((j - VS) >> 1) & 1u, abort_flag, err_word, ERR_WAIT_EMPTY)) break;
+      }
+    } else if (lane == 1) {
+      for (int j = 0; j < n_kv; ++j) {
+        const int vs = j % VS;
+        // V stage j % VS was read by P_{j-VS} V_{j-VS}
+        if (j >= VS && !mbar_spin_bounded(&pv_done[(j - VS) % NBUF], ((j - VS) / NBUF) & 1u, abort_flag, err_word,
+                                          ERR_WAIT_EMPTY))
+          break;
         uint8_t* sV = smem + C::OFF_V + vs * C::T_BYTES;
         mbar_arrive_expect_tx(&v_full[vs], C::T_BYTES);
 #pragma unroll
@@ -179,13 +187,13 @@ __global__ void __launch_bounds__(NTHREADS, 2)
         dV[k] = make_smem_desc_sw128(smem_u32(smem + C::OFF_V) + k * (16 * 128), BN * 128, 1024);
       bool ok = true;
       for (int j = 0; j < n_kv; ++j) {
-        const int bsel = j & 1, vs = j % VS;
+        const int bsel = j % NBUF, vs = j % VS;
         // P_j is in TMEM (over the first half of S_j) once the softmax warps have arrived
-        if (!mbar_wait_bounded(&p_ready[bsel], (j >> 1) & 1u, abort_flag, err_word, ERR_WAIT_AUX)) { ok = false; break; }
-        if (!mbar_wait_bounded(&v_full[vs], (j / VS) & 1u, abort_flag, err_word, ERR_WAIT_FULL)) { ok = false; break; }
+        if (!mbar_spin_bounded(&p_ready[bsel], (j / NBUF) & 1u, abort_flag, err_word, ERR_WAIT_AUX)) { ok = false; break; }
+        if (!mbar_spin_bounded(&v_full[vs], (j / VS) & 1u, abort_flag, err_word, ERR_WAIT_FULL)) { ok = false; break; }
         tc_fence_after_sync();
         const uint64_t stage = static_cast<uint64_t>((vs * C::T_BYTES) >> 4);
-        const uint32_t pcol = tmem_base + C::S_COL + bsel * BN;
+        const uint32_t pcol = tmem_base + C::S_COL + bsel * BN;   // bsel = j % NBUF
         // BN/16 k-steps over keys. A = P from TMEM (16 bf16 of a row = 8 columns per step)
         if (j == 0) {
 #pragma unroll
@@ -210,18 +218,19 @@ __global__ void __launch_bounds__(NTHREADS, 2)
         dQ[k] = make_smem_desc_sw128(smem_u32(smem) + sub * (BM * 128) + kk * 32, 16, 1024);
         dK[k] = make_smem_desc_sw128(smem_u32(smem + C::OFF_K) + sub * (BN * 128) + kk * 32, 16, 1024);
       }
-      bool ok = mbar_wait_bounded(q_full, 0, abort_flag, err_word, ERR_WAIT_FULL);
+      bool ok = mbar_spin_bounded(q_full, 0, abort_flag, err_word, ERR_WAIT_FULL);
       for (int t = 0; ok && t < n_kv; ++t) {
         const int ks = t % KS;
-        // buffer t & 1 held S_{t-2} and then P_{t-2}: it is free when P_{t-2} V_{t-2} has completed
-        if (t >= 2 && !mbar_wait_bounded(&pv_done[t & 1], ((t - 2) >> 1) & 1u, abort_flag, err_word, ERR_WAIT_AUX)) break;
-        if (!mbar_wait_bounded(&k_full[ks], (t / KS) & 1u, abort_flag, err_word, ERR_WAIT_FULL)) break;
+        // buffer t % NBUF held S_{t-NBUF} and then P_{t-NBUF}: it is free when that tile's P V has completed
+        if (t >= NBUF && !mbar_spin_bounded(&pv_done[t % NBUF], ((t - NBUF) / NBUF) & 1u, abort_flag, err_word, ERR_WAIT_AUX))
+          break;
+        if (!mbar_spin_bounded(&k_full[ks], (t / KS) & 1u, abort_flag, err_word, ERR_WAIT_FULL)) break;
         tc_fence_after_sync();
         const uint64_t stage = static_cast<uint64_t>((ks * C::T_BYTES) >> 4);
-        const uint32_t dcol = tmem_base + C::S_COL + (t & 1) * BN;
+        const uint32_t dcol = tmem_base + C::S_COL + (t % NBUF) * BN;
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) umma_f16_ss(dcol, dQ[k], dK[k] + stage, idesc_s, k != 0 ? 1u : 0u);
-        umma_commit(&s_full[t & 1]);
+        umma_commit(&s_full[t % NBUF]);
         umma_commit(&k_empty[ks]);
       }
     }
@@ -272,9 +281,9 @@ __global__ void __launch_bounds__(NTHREADS, 2)
     };
 
     for (int j = 0; j < n_kv; ++j) {
-      const int bsel = j & 1;
+      const int bsel = j % NBUF;
       const uint32_t tS = tmem_base + lane_addr + C::S_COL + bsel * BN;
-      int w = mbar_wait_bounded(&s_full[bsel], (j >> 1) & 1u, abort_flag, err_word, ERR_WAIT_TMEM_FULL) ? 1 : 0;
+      int w = mbar_wait_bounded(&s_full[bsel], (j / NBUF) & 1u, abort_flag, err_word, ERR_WAIT_TMEM_FULL) ? 1 : 0;
       if (!__all_sync(0xffffffffu, w)) { ok = false; break; }
       tc_fence_after_sync();
       const int kv0 = j * BN;
@@ -312,7 +321,7 @@ __global__ void __launch_bounds__(NTHREADS, 2)
         if (need) m_used = mx;
         l *= alpha;
         if (j > 0) {
-          int w2 = mbar_wait_bounded(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1u, abort_flag, err_word, ERR_WAIT_AUX) ? 1 : 0;
+          int w2 = mbar_wait_bounded(&pv_done[(j - 1) % NBUF], ((j - 1) / NBUF) & 1u, abort_flag, err_word, ERR_WAIT_AUX) ? 1 : 0;
           if (!__all_sync(0xffffffffu, w2)) { ok = false; break; }
           tc_fence_after_sync();
 #pragma unroll
