@@ -121,6 +121,7 @@ def set_training_params(student: StudentModel, cfg: DistillConfig) -> None:
     student.grad_accum = cfg.grad_accum_batches
     student.num_grad_accum_batches = math.ceil(student.total_training_steps / student.eff_batch_size)
     student.training_precision_name = cfg.training_precision.lower()
+    student.vocab_parallel_loss = bool(cfg.vocab_parallel_loss) and student.world > 1
     student.decay_start = cfg.decay_start
     student.multi_gpu = cfg.multi_gpu
     student.data_order = cfg.data_order.lower()

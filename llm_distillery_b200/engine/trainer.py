@@ -59,7 +59,7 @@ class DistillEngine:
     def __init__(self, model, *, loss: str = "reference", temperature: float = 1.0, alpha: float = 2.0,
                  crop_to_size: int | None = None, optimizer: str = "adamw", lr: float = 1e-6, betas=(0.9, 0.99),
                  weight_decay: float = 2e-8, grad_accum: int = 1, schedule: LRSchedule | None = None, comm=None,
-                 jsd_renorm: bool = False):
+                 jsd_renorm: bool = False, vocab_parallel: bool = False, max_rows_per_rank: int = 0):
         self.model = model
         self.loss_kind = loss
         self.temperature = float(temperature)
@@ -81,6 +81,16 @@ class DistillEngine:
         if comm is not None:
             comm.attach(self.flat, self.opt)
         self.micro_in_step = 0
+        self.vp_loss = None
+        if vocab_parallel:
+            import torch.distributed as dist
+            if not (dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1):
+                raise ValueError("vocab_parallel_loss needs more than one rank")
+            if getattr(comm, "full_shard", False):
+                raise ValueError("vocab_parallel_loss runs with replicated or optimizer-sharded weights (ddp / fsdp), not zero3")
+            from .vp_loss import VocabParallelLoss
+            self.vp_loss = VocabParallelLoss(model, self.vocab, loss, self.temperature, max_rows_per_rank or 16384,
+                                             jsd_renorm=jsd_renorm)
         self.timer = PhaseTimer(device=self.device)     # B200_TRACE=1 / B200_NVTX=1: device-timed phases, NVTX ranges
 
     # ---- forward of one micro-batch: (sum over conversations of per-conversation loss, logs)
@@ -88,6 +98,8 @@ class DistillEngine:
         hs = self.model.hidden_states(mb.input_ids)
         Hc = hs if mb.rows is None else basic.GatherRowsFn.apply(hs, mb.rows)
         logp = mb.logp if mb.logp.dtype == torch.float32 else mb.logp.float()
+        if self.vp_loss is not None:
+            return self.vp_loss(Hc, self.model.lm_head, mb.ids, logp, mb.seg, mb.n_seg)
         return distill_head_loss(Hc, self.model.lm_head, mb.ids, logp, kind=self.loss_kind,
                                  temperature=self.temperature, vocab=self.vocab, alpha=self.alpha, labels=mb.labels,
                                  avoid=mb.avoid, seg=mb.seg, n_seg=mb.n_seg, jsd_renorm=self.jsd_renorm)

@@ -131,7 +131,8 @@ class StudentModel(BaseModel):
         self.engine = DistillEngine(self.model, loss=self.loss_kind, temperature=self.temperature, alpha=self.alpha,
                                     crop_to_size=self.crop_to_size, optimizer=self.optimizer_name, lr=self.lr,
                                     betas=(0.9, 0.99), weight_decay=2e-8, grad_accum=self.grad_accum, schedule=schedule,
-                                    comm=self.comm)
+                                    comm=self.comm, vocab_parallel=bool(getattr(self, "vocab_parallel_loss", False)),
+                                    max_rows_per_rank=int(self.batch_size) * int(self.context_len))
 
     def memory_note(self) -> str:
         """One line on how the run sits in 180 GB of HBM per GPU under the configured sharding, and what would fit if

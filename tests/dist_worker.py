@@ -281,6 +281,19 @@ def gpu_p2p():
         dist.all_gather(parts, flat)
         assert all(torch.equal(p, parts[0]) for p in parts), "ranks hold different weights"
     _late_rank_step(dev, rank, world, lambda: P2PComm(dev))
+    # training through the vocabulary-parallel head (fused kernels, peer loads) against replicated heads
+    finals = {}
+    for vp in (False, True):
+        model, cfg = tiny(torch.bfloat16, dev)
+        eng = DistillEngine(model, loss="kl", temperature=2.0, optimizer="adamw", lr=1e-3, comm=P2PComm(dev),
+                            crop_to_size=500, vocab_parallel=vp, max_rows_per_rank=256)
+        for s in range(3):
+            eng.train_step([synthetic_batch(cfg.vocab_size, 2, 128 if rank == 0 else 96, 16, seed=100 * s + rank)])
+        finals[vp] = torch.cat([p.detach().float().reshape(-1) for p in model.parameters()])
+    torch.cuda.synchronize()
+    assert _lib.take_device_error() == 0
+    err = (finals[True] - finals[False]).abs().max().item()
+    assert err < 2e-2, ("vocabulary-parallel training", err)
     if rank == 0:
         print("WORKER_OK")
     dist.destroy_process_group()
@@ -370,6 +383,30 @@ def cpu_vp_head():
     dist.init_process_group("gloo")
     _vp_head_check("cpu", torch.float32, dist.get_rank(), dist.get_world_size(), 1e-4)
     if dist.get_rank() == 0:
+        print("WORKER_OK")
+    dist.destroy_process_group()
+
+
+def cpu_vp_training():
+    """Data-parallel training through the vocabulary-parallel head equals training through replicated heads."""
+    dist.init_process_group("gloo")
+    rank, world = dist.get_rank(), dist.get_world_size()
+    finals = {}
+    for vp in (False, True):
+        model, cfg = tiny(torch.float32, "cpu")
+        comm = make_comm("gloo", "cpu", shard_strategy="ddp")
+        eng = DistillEngine(model, loss="jsd", temperature=1.5, optimizer="adamw", lr=1e-3, comm=comm, crop_to_size=500,
+                            vocab_parallel=vp, max_rows_per_rank=512)
+        losses = []
+        for s in range(3):
+            # ranks get different numbers of rows (rank 1 has a shorter batch): the head pads to the step's maximum
+            hb = synthetic_batch(cfg.vocab_size, 2, 128 if rank == 0 else 96, 16, seed=100 * s + rank)
+            losses.append(float(eng.train_step([hb])))
+        finals[vp] = (torch.cat([p.detach().float().reshape(-1) for p in model.parameters()]), losses)
+    err = (finals[True][0] - finals[False][0]).abs().max().item()
+    assert err < 5e-5, err
+    assert all(abs(a - b) < 1e-3 * max(1.0, abs(b)) for a, b in zip(finals[True][1], finals[False][1])), finals
+    if rank == 0:
         print("WORKER_OK")
     dist.destroy_process_group()
 
@@ -878,7 +915,7 @@ def gpu_tp():
 
 if __name__ == "__main__":
     {"cpu_engine": cpu_engine, "gpu_p2p": gpu_p2p, "cpu_tp": cpu_tp, "gpu_tp": gpu_tp, "cpu_cli_tp": cpu_cli_tp,
-     "cpu_vp_head": cpu_vp_head, "cpu_rank_loss": cpu_rank_loss, "cpu_zero3": cpu_zero3, "gpu_zero3": gpu_zero3,
+     "cpu_vp_head": cpu_vp_head, "cpu_vp_training": cpu_vp_training, "cpu_rank_loss": cpu_rank_loss, "cpu_zero3": cpu_zero3, "gpu_zero3": gpu_zero3,
      "cpu_cli_zero3": cpu_cli_zero3, "gpu_cli_zero3": gpu_cli_zero3, "cpu_cli_config3": cpu_cli_config3,
      "cpu_cli_zero3_chunked": cpu_cli_zero3_chunked, "cpu_cli_resume": cpu_cli_resume, "cpu_cli_zero3_three": cpu_cli_zero3_three,
      "cpu_cli_zero3_accum": cpu_cli_zero3_accum, "cpu_cli_zero3_variants": cpu_cli_zero3_variants,

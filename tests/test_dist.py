@@ -29,6 +29,11 @@ def test_cpu_ranks_ddp_and_fsdp_match_single_process():
 
 
 @pytest.mark.parametrize("world", [2, 3])
+def test_cpu_ranks_training_through_the_vocabulary_parallel_head_matches_replicated_heads(world):
+    _launch("cpu_vp_training", world)
+
+
+@pytest.mark.parametrize("world", [2, 3])
 def test_cpu_ranks_full_parameter_sharding_matches_single_process(world):
     _launch("cpu_zero3", world)
 
