@@ -224,3 +224,49 @@ def test_reopen_keeps_the_validation_cycle(tmp_path):
     assert not np.array_equal(again[1]["values"][0], first["values"][0])
     reader.close()
     st.close()
+
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "data", "golden_store.hdf5")
+GOLDEN_SHA256 = "774751dfcc40de7d55c6f62b96068a5a84bc35783a5f21a4e36b33c362c7a0ca"
+
+
+def _write_golden_content(folder):
+    st = H5Store(folder, writers=1)
+    for i in (0, 3, 12):
+        st.write_batch([_rows(i, n=4 + i, K=8, V=100)])
+        st.wait()
+    st.set_vocab_family("llama_3")
+    st.set_topk(8)
+    st.wait()
+    st.close()
+
+
+def test_committed_golden_file_reads_back_and_the_writer_still_emits_its_bytes(tmp_path):
+    """A store file written by an earlier build of the writer is kept in the repository: today's reader (and the
+    independent spec reader) must still read it, and today's writer must still produce it byte for byte (with the zlib
+    the bytes were recorded under; another zlib may deflate differently, then only the content is compared)."""
+    import hashlib
+    import zlib
+    work = str(tmp_path / "golden")
+    os.makedirs(work)
+    shutil.copy(GOLDEN, os.path.join(work, "distributions.hdf5"))
+    st = H5Store(work)
+    assert sorted(st.get_dataset_ids()) == [0, 3, 12] and st.get_vocab_family() == "llama_3" and st.get_topk() == 8
+    for i in (0, 3, 12):
+        r = _rows(i, n=4 + i, K=8, V=100)
+        v, ix = st.load_id(i)
+        assert np.array_equal(v, r.values.astype(np.float16).astype(np.float32)) and np.array_equal(ix, r.indices)
+        assert st.get_sha(i) == r.content_sha
+    st.close()
+    sr = SpecReader(GOLDEN)
+    root = sr.group(sr.root_hdr)
+    assert sorted(root) == ["convo_0", "convo_12", "convo_3"]
+    assert np.array_equal(sr.dataset(sr.group(root["convo_3"])["indices"]), _rows(3, n=7, K=8, V=100).indices.astype(np.uint32))
+    fresh = str(tmp_path / "fresh")
+    _write_golden_content(fresh)
+    with open(os.path.join(fresh, "distributions.hdf5"), "rb") as f:
+        got = hashlib.sha256(f.read()).hexdigest()
+    with open(GOLDEN, "rb") as f:
+        assert hashlib.sha256(f.read()).hexdigest() == GOLDEN_SHA256
+    if zlib.ZLIB_RUNTIME_VERSION == "1.3":
+        assert got == GOLDEN_SHA256
