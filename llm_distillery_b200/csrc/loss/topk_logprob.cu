@@ -48,14 +48,20 @@ __device__ void bitonic_desc(unsigned long long* s, int n) {
 // Vocabulary-shard mode (out_raw != null): the row is one rank's slice of the vocabulary; the kernel writes the raw
 // fp32 logits of the slice's top K, their GLOBAL ids (index + id_offset) and the slice's log-sum-exp, which
 // topk_combine_kernel turns into the exact top-K log-probs of the whole vocabulary.
-__global__ void __launch_bounds__(NT) topk_logprob_kernel(const float* __restrict__ logits, long long ld, int V, int K,
-                                                         __half* __restrict__ out_logp, int* __restrict__ out_idx,
-                                                         float* __restrict__ out_raw, float* __restrict__ out_lse,
-                                                         int id_offset) {
+//
+// STAGE: the row (V <= 50 K fp32 values) is copied into shared memory by the first pass and every later pass reads it
+// from there: the seven passes over a row then cost ONE read of it from DRAM instead of up to five (rows of a
+// collection batch do not all stay in L2), and NTT = 512 threads walk it.
+template <int NTT, bool STAGE>
+__global__ void __launch_bounds__(NTT) topk_logprob_kernel(const float* __restrict__ logits, long long ld, int V, int K,
+                                                          __half* __restrict__ out_logp, int* __restrict__ out_idx,
+                                                          float* __restrict__ out_raw, float* __restrict__ out_lse,
+                                                          int id_offset) {
+  extern __shared__ float srow[];
   __shared__ unsigned long long sel[MAX_K];
   __shared__ unsigned int hist[256];
   __shared__ unsigned int ties[TIE_CAP];
-  __shared__ float redf[NT / 32];
+  __shared__ float redf[NTT / 32];
   __shared__ unsigned int s_prefix, s_remaining, s_nsel, s_nties;
   __shared__ float s_max, s_lse;
   const long long row = blockIdx.x;
@@ -64,22 +70,31 @@ __global__ void __launch_bounds__(NT) topk_logprob_kernel(const float* __restric
 
   // 1. max, sum-exp
   float mx = -INFINITY;
-  for (int i = tid; i < V; i += NT) mx = fmaxf(mx, x[i]);
+  if (STAGE) {
+    for (int i = tid; i < V; i += NTT) {
+      const float v = x[i];
+      srow[i] = v;
+      mx = fmaxf(mx, v);
+    }
+    x = srow;   // the block-wide barrier of the max reduction below orders these stores before every later read
+  } else {
+    for (int i = tid; i < V; i += NTT) mx = fmaxf(mx, x[i]);
+  }
   mx = warp_max(mx);
   if (lane == 0) redf[warp] = mx;
   __syncthreads();
-  if (tid == 0) { float m = redf[0]; for (int w = 1; w < NT / 32; ++w) m = fmaxf(m, redf[w]); s_max = m; }
+  if (tid == 0) { float m = redf[0]; for (int w = 1; w < NTT / 32; ++w) m = fmaxf(m, redf[w]); s_max = m; }
   __syncthreads();
   mx = s_max;
   float sm = 0.f;
-  for (int i = tid; i < V; i += NT) sm += __expf(x[i] - mx);
+  for (int i = tid; i < V; i += NTT) sm += __expf(x[i] - mx);
   sm = warp_sum(sm);
   __syncthreads();
   if (lane == 0) redf[warp] = sm;
   __syncthreads();
   if (tid == 0) {
     float t = 0.f;
-    for (int w = 0; w < NT / 32; ++w) t += redf[w];
+    for (int w = 0; w < NTT / 32; ++w) t += redf[w];
     s_lse = mx + __logf(t);
     s_prefix = 0; s_remaining = (unsigned)K; s_nsel = 0; s_nties = 0;
   }
@@ -91,9 +106,9 @@ __global__ void __launch_bounds__(NT) topk_logprob_kernel(const float* __restric
     const int shift = 24 - 8 * pass;
     const uint32_t mask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
     const uint32_t prefix = s_prefix;
-    hist[tid] = 0;
+    if (tid < 256) hist[tid] = 0;
     __syncthreads();
-    for (int i = tid; i < V; i += NT) {
+    for (int i = tid; i < V; i += NTT) {
       const uint32_t k = fkey(x[i]);
       if ((k & mask) == prefix) atomicAdd(&hist[(k >> shift) & 0xffu], 1u);
     }
@@ -114,7 +129,7 @@ __global__ void __launch_bounds__(NT) topk_logprob_kernel(const float* __restric
   const unsigned need_eq = s_remaining;
 
   // 3. gather
-  for (int i = tid; i < V; i += NT) {
+  for (int i = tid; i < V; i += NTT) {
     const uint32_t k = fkey(x[i]);
     if (k > thr) {
       const unsigned p = atomicAdd(&s_nsel, 1u);
@@ -136,7 +151,7 @@ __global__ void __launch_bounds__(NT) topk_logprob_kernel(const float* __restric
     }
   } else {
     // keep the need_eq lowest indices among the ties: rank each tie by counting smaller indices
-    for (unsigned t = tid; t < nt; t += NT) {
+    for (unsigned t = tid; t < nt; t += NTT) {
       const uint32_t me = ties[t];
       unsigned rank = 0;
       for (unsigned u = 0; u < nt; ++u) rank += (ties[u] < me) ? 1u : 0u;
@@ -148,13 +163,13 @@ __global__ void __launch_bounds__(NT) topk_logprob_kernel(const float* __restric
   // 4. sort (pad to a power of two with zeros, which sort last)
   int n2 = 1;
   while (n2 < K) n2 <<= 1;
-  for (int i = K + tid; i < n2; i += NT) sel[i] = 0ull;
+  for (int i = K + tid; i < n2; i += NTT) sel[i] = 0ull;
   __syncthreads();
   bitonic_desc(sel, n2);
 
   // 5. write
   const float lse = s_lse;
-  for (int i = tid; i < K; i += NT) {
+  for (int i = tid; i < K; i += NTT) {
     const unsigned long long e = sel[i];
     const float z = kfloat((uint32_t)(e >> 32));
     if (out_raw) out_raw[row * K + i] = z;
@@ -262,6 +277,24 @@ __global__ void __launch_bounds__(NT) topk_merge_kernel(const float* __restrict_
   }
 }
 
+static int launch_topk(const float* logits, long long ld, int rows, int V, int K, __half* out_logp, int* out_idx,
+                       float* out_raw, float* out_lse, int id_offset, cudaStream_t st) {
+  const size_t row_bytes = (size_t)V * sizeof(float);
+  if (row_bytes <= 200 * 1024) {
+    auto kern = topk_logprob_kernel<512, true>;
+    static bool attr = false;
+    if (!attr) {
+      B200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+      attr = true;
+    }
+    kern<<<rows, 512, row_bytes, st>>>(logits, ld, V, K, out_logp, out_idx, out_raw, out_lse, id_offset);
+  } else {
+    topk_logprob_kernel<NT, false><<<rows, NT, 0, st>>>(logits, ld, V, K, out_logp, out_idx, out_raw, out_lse, id_offset);
+  }
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200_OK;
+}
+
 }  // namespace topk
 }  // namespace b200
 
@@ -273,9 +306,7 @@ int b200_topk_logprob(const float* logits, long long ld, int rows, int V, int K,
                       cudaStream_t st) {
   if (!logits || !out_logp || !out_idx || rows <= 0 || V <= 0 || K <= 0 || K > topk::MAX_K || K > V)
     return K > topk::MAX_K ? B200_ERR_TOO_BIG : B200_ERR_ARG;
-  topk::topk_logprob_kernel<<<rows, topk::NT, 0, st>>>(logits, ld, V, K, (__half*)out_logp, out_idx, nullptr, nullptr, 0);
-  B200_CUDA_CHECK(cudaGetLastError());
-  return B200_OK;
+  return topk::launch_topk(logits, ld, rows, V, K, (__half*)out_logp, out_idx, nullptr, nullptr, 0, st);
 }
 
 // One vocabulary shard of a vocabulary-parallel LM head: raw top-K logits fp32 [rows, K], global ids, shard lse [rows].
@@ -283,9 +314,7 @@ int b200_topk_partial(const float* logits, long long ld, int rows, int V, int K,
                       int* out_idx, float* out_lse, cudaStream_t st) {
   if (!logits || !out_raw || !out_idx || !out_lse || rows <= 0 || V <= 0 || K <= 0 || K > topk::MAX_K || K > V)
     return K > topk::MAX_K ? B200_ERR_TOO_BIG : B200_ERR_ARG;
-  topk::topk_logprob_kernel<<<rows, topk::NT, 0, st>>>(logits, ld, V, K, nullptr, out_idx, out_raw, out_lse, id_offset);
-  B200_CUDA_CHECK(cudaGetLastError());
-  return B200_OK;
+  return topk::launch_topk(logits, ld, rows, V, K, nullptr, out_idx, out_raw, out_lse, id_offset, st);
 }
 
 // Merge of `parts` shard results (see topk_combine_kernel). zk_stride / lse_stride: elements between parts.
