@@ -11,7 +11,7 @@ stores. The peers' gradients cross NVLink as bf16 (each rank casts its fp32 grad
 first; the owner of a shard adds its own fp32 gradient and the peers' bf16 copies in fp32), which halves the bytes;
 ``B200_WIRE=fp32`` keeps the fp32 exchange.
 
-With ``B200_OVERLAP=1`` (default when several GPUs train) the same kernel runs per finished layer range on a side
+With ``B200_OVERLAP=1`` the same kernel runs per finished layer range on a side
 stream behind the backward of the earlier layers, on a handful of CTAs (``B200_OVERLAP_CTAS``): the exchange needs a
 few tens of GB/s to keep up with backward, so it does not need the SMs the backward GEMMs are using, and only the
 last range (embedding and first layer) is left for after backward. Optimizer state is therefore sharded (ZeRO-1) for ``ddp`` and ``fsdp`` alike. Optimizers other than the
@@ -79,10 +79,10 @@ class P2PComm:
         self.side = torch.cuda.Stream(device=self.device)
         self._ov = None
         import os
-        # the reduction of finished layer ranges runs beside backward on a few CTAs (a full-size grid there took SM
-        # slots and HBM bandwidth from the backward GEMMs and made the step slower); B200_OVERLAP=0 does one
-        # reduction after backward instead
-        self._overlap_enabled = os.environ.get("B200_OVERLAP", "1") == "1"
+        # B200_OVERLAP=1: the reduction of finished layer ranges runs beside backward on a few CTAs (a full-size grid
+        # there took SM slots and HBM bandwidth from the backward GEMMs and made the step slower); default: one
+        # reduction after backward
+        self._overlap_enabled = os.environ.get("B200_OVERLAP", "0") == "1"
         self._buckets = max(1, int(os.environ.get("B200_OVERLAP_BUCKETS", "8")))   # ranges per step handed over early
         self._overlap_ctas = max(1, int(os.environ.get("B200_OVERLAP_CTAS", "24")))
         self._wire16 = os.environ.get("B200_WIRE", "bf16") != "fp32"
