@@ -91,7 +91,8 @@ __global__ void __launch_bounds__(NTHREADS, 1)
   uint64_t* stage_free = bars + 10;  // ... and read out by the TMA reduce
   uint64_t* dq_full1 = bars + 11;    // second dQ accumulator (pipelined variant)
   uint64_t* dq_empty1 = bars + 12;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  uint64_t* sdp_issued = bars + 13;  // the S / dP MMAs of a pair have been handed to the tensor core (not: completed)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -130,6 +131,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     mbar_init(stage_free, 1);
     mbar_init(dq_full1, 3);
     mbar_init(dq_empty1, NWORK);
+    mbar_init(sdp_issued, 1);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -218,6 +220,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
           for (int k = 0; k < D / 16; ++k)
             umma_f16_ss(tmem_base + C::DP_COL, kDO + stage + koff(k), kV + koff(k), idesc_kk, k != 0 ? 1u : 0u);
           umma_commit(sdp_full);
+          mbar_arrive(sdp_issued);
         }
       } else if (warp == 2 || warp == 3) {
         // dV += P^T dO (warp 2) ; dK += dS^T Q (warp 3): reduction over the 128 queries, 16 per step = 2048 B per step
@@ -228,6 +231,12 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         const uint32_t dcol = tmem_base + (warp == 2 ? C::DV_COL : C::DK_COL);
         for (int it = 0; it < n_it; ++it) {
           if (!mbar_spin_bounded(pds_ready, it & 1u, abort_flag, err_word, ERR_WAIT_AUX)) break;
+          // The tensor core takes MMAs in the order they are issued. The next pair's S / dP are what the softmax warps
+          // wait for, this pair's dV / dK / dQ are not needed before the second half of that softmax: let S / dP go
+          // first (its issuer starts at the same barrier).
+          if (C::PIPE && it + 1 < n_it &&
+              !mbar_spin_bounded(sdp_issued, (it + 1) & 1u, abort_flag, err_word, ERR_WAIT_AUX))
+            break;
           tc_fence_after_sync();
           const uint64_t stage = stage_off(it);
           if (it == 0) {
@@ -257,6 +266,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
                                      ERR_WAIT_AUX))
                 break;
             }
+            if (it + 1 < n_it && !mbar_spin_bounded(sdp_issued, (it + 1) & 1u, abort_flag, err_word, ERR_WAIT_AUX)) break;
           }
           tc_fence_after_sync();
 #pragma unroll
