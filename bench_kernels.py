@@ -282,6 +282,7 @@ def main():
     a.add_argument("--batch", type=int, default=8); a.add_argument("--seq", type=int, default=2048)
     a.add_argument("--heads", type=int, default=32); a.add_argument("--kv-heads", type=int, default=4)
     a.add_argument("--dim", type=int, default=64); a.add_argument("--bwd", action="store_true")
+    a.add_argument("--no-library", action="store_true", help="this repository's kernels only (for profiler captures)")
     h = sub.add_parser("head")
     h.add_argument("--rows", type=int, default=16384); h.add_argument("--hidden", type=int, default=2048)
     h.add_argument("--vocab", type=int, default=32000); h.add_argument("--topk", type=int, default=200)
@@ -298,7 +299,8 @@ def main():
     if args.cmd == "gemm":
         bench_gemm(args.m, args.n, args.k, args.layout, args.iters)
     elif args.cmd == "attn":
-        bench_attn(args.batch, args.seq, args.heads, args.kv_heads, args.dim, args.iters, args.bwd)
+        bench_attn(args.batch, args.seq, args.heads, args.kv_heads, args.dim, args.iters, args.bwd,
+                   library=not args.no_library)
     elif args.cmd == "head":
         bench_head(args.rows, args.hidden, args.vocab, args.topk, args.iters)
     elif args.cmd == "elementwise":

@@ -10,7 +10,7 @@
 //                            issuing both groups of a 64-key tile took longer than the softmax of that tile)
 //   warps 3-6 softmax      : thread = query row. Reads S_j from TMEM once (both 32-column loads in flight),
 //                            exponentiates against the maximum known so far (exp2 domain, packed f32x2 arithmetic,
-//                            part of the exponentials on the FMA pipe), writes P_j as bf16 pairs over the first half
+//                            optionally part of the exponentials on the FMA pipe), writes P_j as bf16 pairs over the first half
 //                            of the same score buffer, and only when a score outgrew the maximum by more than 2^8
 //                            moves the maximum, rescales O in TMEM and redoes the tile; final O / l and lse.
 // The score buffers alternate: S_{j+1} is computed while the softmax warps work on S_j, and S_{j+2} goes into S_j's
@@ -32,6 +32,12 @@ constexpr int BN = 64;
 constexpr int NTHREADS = 224;
 constexpr int VS = 2;  // V ring
 constexpr float kRescaleThreshold = 8.0f;  // in log2 units
+// Measured (B200, 1965 MHz): 0.254 ms / 0.264 ms (head dim 64, batch 8 x 2048 / head dim 128, batch 2 x 4096) with every
+// exponential on the MUFU unit, 0.268 / 0.283 with a quarter of them as polynomials, 0.297 / 0.311 with half: with
+// one query row per thread the softmax warps are bound by instruction latency, not by the 16 exponentials per clock
+// of the MUFU unit, so the extra FMA-pipe instructions cost more than they free. The polynomial path stays in the
+// kernel (B200_FA_POLY = 2, 3 or 4 eighths) for shapes where that changes.
+constexpr int kDefaultPoly8 = 0;
 
 template <int D>
 struct Cfg {
@@ -80,7 +86,8 @@ __device__ __forceinline__ float poly_exp2(float x) {
   return __int_as_float(__float_as_int(pl) + (__float_as_int(xr) << 23));
 }
 
-template <int D>
+// POLY8: of every 8 pairs of exponentials, this many are evaluated on the FMA pipe instead of the MUFU unit.
+template <int D, int POLY8>
 __global__ void __launch_bounds__(NTHREADS, 2)
     flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                      const __grid_constant__ CUtensorMap tmV, FwdParams p, unsigned int* err_word) {
@@ -248,8 +255,8 @@ __global__ void __launch_bounds__(NTHREADS, 2)
     bool ok = true;
 
     // One 32-column chunk of scores -> probabilities (bf16 pairs) with the running maximum and the row sum.
-    // `lim`: columns of this chunk with index <= lim are visible (>= 31: all of them). Every fourth pair of
-    // exponentials is evaluated on the FMA pipe.
+    // `lim`: columns of this chunk with index <= lim are visible (>= 31: all of them). POLY8 of every 8 pairs of
+    // exponentials are evaluated on the FMA pipe.
     auto chunk = [&](const uint32_t (&v)[32], const uint64_t nmb, const int lim, float& mx, uint64_t& sum2,
                      uint32_t (&pk)[16]) {
       if (lim >= 31) {
@@ -259,7 +266,7 @@ __global__ void __launch_bounds__(NTHREADS, 2)
           mx = fmax3(mx, s0, s1);
           float x0, x1;
           unpack_f32x2(fma_f32x2(pack_f32x2(s0, s1), c2p, nmb), x0, x1);
-          const bool poly = (t & 6) == 6;
+          const bool poly = ((t >> 1) & 7) < POLY8;
           const float p0 = poly ? poly_exp2(x0) : fast_exp2(x0);
           const float p1 = poly ? poly_exp2(x1) : fast_exp2(x1);
           sum2 = add_f32x2(sum2, pack_f32x2(p0, p1));
@@ -422,7 +429,16 @@ static int launch_fwd(const void* q, long long q_width, int colQ0, const void* k
   rc = make_tmap_3d(&tmV, v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)kv_width, (uint64_t)kv_rows, (uint64_t)B,
                     (uint64_t)kv_width * 2, (uint64_t)kv_rows * kv_width * 2, 64, BN, 1, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != B200_OK) return rc;
-  auto kern = flash_fwd_kernel<D>;
+  // share of the exponentials on the FMA pipe (eighths): B200_FA_POLY overrides the default for experiments
+  static int poly8 = -1;
+  if (poly8 < 0) {
+    const char* e = getenv("B200_FA_POLY");
+    poly8 = e ? atoi(e) : kDefaultPoly8;
+    if (poly8 != 0 && poly8 != 2 && poly8 != 3 && poly8 != 4) poly8 = kDefaultPoly8;
+  }
+  void (*kern)(CUtensorMap, CUtensorMap, CUtensorMap, FwdParams, unsigned int*) =
+      poly8 == 0 ? flash_fwd_kernel<D, 0> : poly8 == 3 ? flash_fwd_kernel<D, 3> : poly8 == 4 ? flash_fwd_kernel<D, 4>
+                                                                                              : flash_fwd_kernel<D, 2>;
   static bool attr = false;
   if (!attr) {
     B200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
