@@ -16,13 +16,17 @@
 // A [q x k] tile written row-per-thread in the 128B-swizzled K-major layout is, byte for byte, also the
 // MN-major layout of its transpose, so P and dS are stored once and read both ways.
 //
-// Roles: warp 0 lane 0 TMA producer (Q_i / dO_i ring); four threads issue the MMA groups, one group each (warp 0 lane 1:
-// S and dP; warps 1-3: dV; dK; dQ):
+// Roles: warp 0 TMA producer (Q_i / dO_i ring); warps 1-4 issue the MMA groups, one group each (S and dP; dV; dK; dQ):
 // every tcgen05 instruction - an MMA, a commit, a completed mbarrier wait - costs its issuing thread on the order of a
 // hundred cycles here, so one thread issuing the 32 MMAs of a pair needed ~3.8 K cycles per pair and was what bound
-// the kernel (the tensor core needs ~1.3 K); warps 4-19 softmax + epilogue: each TMEM lane quadrant is served by four
-// warps that split the tile's columns; warps 20-23 drain the dQ accumulators (TMEM -> staging tile -> TMA reduce-add),
-// which used to take the softmax warps a third of every pair.
+// the kernel (the tensor core needs ~1.3 K); warps 5-20 softmax + dQ drain + epilogue: each TMEM lane quadrant is
+// served by four warps that split the tile's columns.
+// What bounds the kernel now is shared-memory bandwidth: a pair's MMAs read ~224 KB of operands from shared memory
+// (every operand of the five groups lives there) next to ~100 KB of P / dS / dQ-staging traffic from the warps, at
+// ~128 B per clock. Two variants measured no faster and were dropped: the next pair's S / dP MMAs issued ahead of
+// this pair's dV / dK / dQ (0.654 against 0.648 ms at head dim 64), and dedicated dQ drain warps with packed f32x2
+// softmax arithmetic (0.673 ms). Less operand traffic needs P^T / dS^T (and K, V) as TMEM operands, i.e. the
+// transposed S^T = K Q^T formulation.
 #include "../common/ptx.cuh"
 #include "../common/host.cuh"
 
@@ -32,11 +36,10 @@ namespace fab {
 constexpr int BM = 128;  // queries per block
 constexpr int BN = 128;  // keys per block
 constexpr int NSPLIT = 4;        // softmax/drain warps per TMEM lane quadrant: each takes 1/4 of a tile's columns
-constexpr int FIRST_WORK_WARP = 4;               // warp 0: TMA producer (lane 0) and S/dP issuer (lane 1); warps 1-3: dV, dK, dQ
-constexpr int NWORK = 4 * NSPLIT * 32;          // softmax threads (16 warps)
-constexpr int FIRST_DRAIN_WARP = FIRST_WORK_WARP + 4 * NSPLIT;   // then 4 dQ drain warps, one per TMEM lane quadrant
-constexpr int NDRAIN = 4 * 32;
-constexpr int NTHREADS = 32 * FIRST_DRAIN_WARP + NDRAIN;
+constexpr int NISSUE = 4;                        // MMA-issuing warps: S/dP, dV, dK, dQ
+constexpr int FIRST_WORK_WARP = 1 + NISSUE;      // warp 0 is the TMA producer
+constexpr int NTHREADS = 32 * FIRST_WORK_WARP + 4 * NSPLIT * 32;  // + 16 softmax/drain warps
+constexpr int NWORK = 4 * NSPLIT * 32;          // threads that arrive on the softmax/drain barriers
 
 template <int D>
 struct Cfg {
@@ -66,19 +69,6 @@ struct Cfg {
   static constexpr uint32_t TMEM_COLS = 512;
 };
 
-// 2^x for x <= 0 on the FMA pipe (see flash_attn_fwd.cu): relative error 6e-5; -inf and very negative x give ~0.
-__device__ __forceinline__ float poly_exp2(float x) {
-  x = fmaxf(x, -126.f);
-  const float magic = 12582912.f;
-  const float xr = x + magic;
-  const float f = x - (xr - magic);
-  float pl = fmaf(f, 0.0096181291f, 0.0555041087f);
-  pl = fmaf(pl, f, 0.2402265070f);
-  pl = fmaf(pl, f, 0.6931471806f);
-  pl = fmaf(pl, f, 1.0f);
-  return __int_as_float(__float_as_int(pl) + (__float_as_int(xr) << 23));
-}
-
 struct BwdParams {
   const float* lse;    // [H, T]
   const float* delta;  // [H, T]
@@ -107,8 +97,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
   uint64_t* stage_free = bars + 10;  // ... and read out by the TMA reduce
   uint64_t* dq_full1 = bars + 11;    // second dQ accumulator (pipelined variant)
   uint64_t* dq_empty1 = bars + 12;
-  uint64_t* sdp_issued = bars + 13;  // the S / dP MMAs of a pair have been handed to the tensor core (not: completed)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -142,12 +131,11 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     mbar_init(sdp_full, 1);
     mbar_init(pds_ready, NWORK);
     mbar_init(dq_full, 3);     // "pair done": the dV, dK and dQ issuers each commit to it
-    mbar_init(dq_empty, NDRAIN);
-    mbar_init(stage_full, NDRAIN);
+    mbar_init(dq_empty, NWORK);
+    mbar_init(stage_full, NWORK);
     mbar_init(stage_free, 1);
     mbar_init(dq_full1, 3);
-    mbar_init(dq_empty1, NDRAIN);
-    mbar_init(sdp_issued, 1);
+    mbar_init(dq_empty1, NWORK);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -194,40 +182,6 @@ __global__ void __launch_bounds__(NTHREADS, 1)
           tma_load_3d(sDO + c * (BM * 128), &tmDO, &qdo_full[s], hq * D + c * 64, q0, b);
         }
       }
-    } else if (lane == 1) {
-      const uint32_t sK = smem_u32(smem + C::OFF_K);
-      const uint32_t sV = smem_u32(smem + C::OFF_V);
-      const uint32_t sQ0 = smem_u32(smem + C::OFF_QDO), sDO0 = sQ0 + C::QDO_BYTES;
-      auto koff = [](int k) -> uint64_t {
-        return static_cast<uint64_t>(((k >> 2) * (128 * 128) + (k & 3) * 32) >> 4);
-      };
-      auto stage_off = [](int it) -> uint64_t { return static_cast<uint64_t>(((it % ST) * C::STAGE_BYTES) >> 4); };
-      // S = Q K^T and dP = dO V^T (both operands K-major) -> TMEM. Pair it + 1 is issued as soon as the softmax warps
-      // have read S / dP of pair it, i.e. AHEAD of pair it's dV / dK / dQ, which the other issuers handle.
-      const uint32_t idesc_kk = make_idesc_f16(1, BM, BN, 0, 0);
-      const uint64_t kQ = make_smem_desc_sw128(sQ0, 16, 1024), kDO = make_smem_desc_sw128(sDO0, 16, 1024);
-      const uint64_t kK = make_smem_desc_sw128(sK, 16, 1024), kV = make_smem_desc_sw128(sV, 16, 1024);
-      bool ok = mbar_spin_bounded(kv_full, 0, abort_flag, err_word, ERR_WAIT_FULL);
-      for (int it = 0; ok && it < n_it; ++it) {
-        if (!mbar_spin_bounded(&qdo_full[it % ST], (it / ST) & 1u, abort_flag, err_word, ERR_WAIT_FULL)) break;
-        if (it > 0) {
-          if constexpr (C::PIPE) {
-            if (!mbar_spin_bounded(pds_ready, (it - 1) & 1u, abort_flag, err_word, ERR_WAIT_AUX)) break;
-          } else {  // dQ shares its TMEM columns with S: they are free when the drain of pair it - 1 is through
-            if (!mbar_spin_bounded(dq_empty, (it - 1) & 1u, abort_flag, err_word, ERR_WAIT_AUX)) break;
-          }
-        }
-        tc_fence_after_sync();
-        const uint64_t stage = stage_off(it);
-#pragma unroll
-        for (int k = 0; k < D / 16; ++k)
-          umma_f16_ss(tmem_base + C::S_COL, kQ + stage + koff(k), kK + koff(k), idesc_kk, k != 0 ? 1u : 0u);
-#pragma unroll
-        for (int k = 0; k < D / 16; ++k)
-          umma_f16_ss(tmem_base + C::DP_COL, kDO + stage + koff(k), kV + koff(k), idesc_kk, k != 0 ? 1u : 0u);
-        umma_commit(sdp_full);
-        mbar_arrive(sdp_issued);
-      }
     }
   } else if (warp < FIRST_WORK_WARP) {
     // ------------------------------------------------------------------ MMA issuers (one elected thread per warp)
@@ -245,21 +199,41 @@ __global__ void __launch_bounds__(NTHREADS, 1)
       auto stage_off = [](int it) -> uint64_t { return static_cast<uint64_t>(((it % ST) * C::STAGE_BYTES) >> 4); };
       // "pair done" barrier of pair `it` (count 3) and the parity of its phase
       auto pair_bar = [&](int it) -> uint64_t* { return (C::PIPE && (it & 1)) ? dq_full1 : dq_full; };
-      if (warp == 1 || warp == 2) {
-        // dV += P^T dO (warp 1) ; dK += dS^T Q (warp 2): reduction over the 128 queries, 16 per step = 2048 B per step
+      if (warp == 1) {
+        // S = Q K^T and dP = dO V^T (both operands K-major) -> TMEM. Pair it + 1 is issued as soon as the softmax warps
+        // have read S / dP of pair it, i.e. AHEAD of pair it's dV / dK / dQ, which the other issuers handle.
+        const uint32_t idesc_kk = make_idesc_f16(1, BM, BN, 0, 0);
+        const uint64_t kQ = make_smem_desc_sw128(sQ0, 16, 1024), kDO = make_smem_desc_sw128(sDO0, 16, 1024);
+        const uint64_t kK = make_smem_desc_sw128(sK, 16, 1024), kV = make_smem_desc_sw128(sV, 16, 1024);
+        bool ok = mbar_spin_bounded(kv_full, 0, abort_flag, err_word, ERR_WAIT_FULL);
+        for (int it = 0; ok && it < n_it; ++it) {
+          if (!mbar_spin_bounded(&qdo_full[it % ST], (it / ST) & 1u, abort_flag, err_word, ERR_WAIT_FULL)) break;
+          if (it > 0) {
+            if constexpr (C::PIPE) {
+              if (!mbar_spin_bounded(pds_ready, (it - 1) & 1u, abort_flag, err_word, ERR_WAIT_AUX)) break;
+            } else {  // dQ shares its TMEM columns with S: they are free when the drain of pair it - 1 is through
+              if (!mbar_spin_bounded(dq_empty, (it - 1) & 1u, abort_flag, err_word, ERR_WAIT_AUX)) break;
+            }
+          }
+          tc_fence_after_sync();
+          const uint64_t stage = stage_off(it);
+#pragma unroll
+          for (int k = 0; k < D / 16; ++k)
+            umma_f16_ss(tmem_base + C::S_COL, kQ + stage + koff(k), kK + koff(k), idesc_kk, k != 0 ? 1u : 0u);
+#pragma unroll
+          for (int k = 0; k < D / 16; ++k)
+            umma_f16_ss(tmem_base + C::DP_COL, kDO + stage + koff(k), kV + koff(k), idesc_kk, k != 0 ? 1u : 0u);
+          umma_commit(sdp_full);
+        }
+      } else if (warp == 2 || warp == 3) {
+        // dV += P^T dO (warp 2) ; dK += dS^T Q (warp 3): reduction over the 128 queries, 16 per step = 2048 B per step
         // in both tiles, both operands MN-major
         const uint32_t idesc_tt = make_idesc_f16(1, BN, D, 1, 1);
-        const uint64_t tA = make_smem_desc_sw128(warp == 1 ? sP : sDS, BM * 128, 1024);
-        const uint64_t tB = make_smem_desc_sw128(warp == 1 ? sDO0 : sQ0, BM * 128, 1024);
-        const uint32_t dcol = tmem_base + (warp == 1 ? C::DV_COL : C::DK_COL);
+        const uint64_t tA = make_smem_desc_sw128(warp == 2 ? sP : sDS, BM * 128, 1024);
+        const uint64_t tB = make_smem_desc_sw128(warp == 2 ? sDO0 : sQ0, BM * 128, 1024);
+        const uint32_t dcol = tmem_base + (warp == 2 ? C::DV_COL : C::DK_COL);
         for (int it = 0; it < n_it; ++it) {
           if (!mbar_spin_bounded(pds_ready, it & 1u, abort_flag, err_word, ERR_WAIT_AUX)) break;
-          // The tensor core takes MMAs in the order they are issued. The next pair's S / dP are what the softmax warps
-          // wait for, this pair's dV / dK / dQ are not needed before the second half of that softmax: let S / dP go
-          // first (its issuer starts at the same barrier).
-          if (C::PIPE && it + 1 < n_it &&
-              !mbar_spin_bounded(sdp_issued, (it + 1) & 1u, abort_flag, err_word, ERR_WAIT_AUX))
-            break;
           tc_fence_after_sync();
           const uint64_t stage = stage_off(it);
           if (it == 0) {
@@ -289,7 +263,6 @@ __global__ void __launch_bounds__(NTHREADS, 1)
                                      ERR_WAIT_AUX))
                 break;
             }
-            if (it + 1 < n_it && !mbar_spin_bounded(sdp_issued, (it + 1) & 1u, abort_flag, err_word, ERR_WAIT_AUX)) break;
           }
           tc_fence_after_sync();
 #pragma unroll
@@ -299,33 +272,39 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         }
       }
     }
-  } else if (warp >= FIRST_DRAIN_WARP) {
-    // ------------------------------------------------------------------ dQ drain warps
-    // Pair by pair: wait until the pair's MMAs are done, move its dQ accumulator TMEM -> registers -> swizzled staging
-    // tile in shared memory (row r, 128-byte rows of 32 floats, two 32-column sub-tiles per round; D = 128 takes two
-    // rounds) -> TMA reduce-add into the fp32 gradient issued by one thread, then hand the accumulator back.
+  } else {
     const int quad = warp & 3;
+    const int part = (warp - FIRST_WORK_WARP) >> 2;  // which quarter of the columns this warp handles
     const int r = quad * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
-    constexpr int ROUNDS = D / 64;
-    uint8_t* sDQ = smem + C::OFF_DQS;
-    const bool leader = (warp == FIRST_DRAIN_WARP) && lane == 0;
-    uint32_t rd = 0;  // staging rounds so far
+    const float c2 = p.scale * 1.4426950408889634f;
+    uint8_t* sP = smem + C::OFF_P;
+    uint8_t* sDS = smem + C::OFF_DS;
+    constexpr int DW = D / NSPLIT;     // columns of dQ / dK / dV per warp: 16 (D = 64) or 32 (D = 128)
+    constexpr int ROUNDS = D / 64;     // the dQ staging area holds two 32-column sub-tiles per round
+    const int dc0 = part * DW;         // first dQ / dK / dV column of this warp
     bool ok = true;
-    for (int itd = 0; ok && itd < n_it; ++itd) {
+    uint32_t rd = 0;  // staging rounds so far
+    uint8_t* sDQ = smem + C::OFF_DQS;
+    const int st = dc0 >> 5;               // 32-column sub-tile of dQ this warp contributes to
+    const int chunkbase = (dc0 & 31) >> 2;  // first 16-byte chunk (4 floats) inside the 128-byte row
+    // Drain the dQ accumulator of pair `itd` into the fp32 gradient: TMEM -> registers -> swizzled staging tile in
+    // shared memory (row r, 128-byte rows of 32 floats) -> TMA reduce-add issued by one thread. The staging area holds
+    // two 32-column sub-tiles: D = 128 takes two rounds, and in each round only the warps whose columns belong to
+    // that round write (everybody arrives on the barriers). The caller has waited for the pair's dq_full barrier.
+    auto drain = [&](int itd) {
       const int hq = hkv * g + itd / nqi;
       const int q0 = (i_start + itd % nqi) * BM;
-      const bool odd = C::PIPE && (itd & 1);
-      const uint32_t dq_col = odd ? C::DQ_COL1 : C::DQ_COL;
-      {
-        const uint32_t parity = C::PIPE ? ((itd >> 1) & 1u) : (itd & 1u);
-        int w2 = mbar_wait_bounded(odd ? dq_full1 : dq_full, parity, abort_flag, err_word, ERR_WAIT_AUX) ? 1 : 0;
-        if (!__all_sync(0xffffffffu, w2)) { ok = false; break; }
-        tc_fence_after_sync();
-      }
+      const uint32_t dq_col = (C::PIPE && (itd & 1)) ? C::DQ_COL1 : C::DQ_COL;
+      uint32_t v[DW];
+      if constexpr (DW == 32) tmem_ld_32x32b_x32(tmem_base + lane_addr + dq_col + dc0, v);
+      else tmem_ld_32x32b_x16(tmem_base + lane_addr + dq_col + dc0, v);
+      tmem_ld_wait();
+#pragma unroll
       for (int rr = 0; rr < ROUNDS; ++rr) {
-        // the previous round's reduce must have finished READING the staging tile
-        if (leader && rd > 0) {
+        // the previous round's reduce must have finished READING the staging tile. The thread that issued it checks
+        // that only now, a whole softmax phase later, so that the TMA engine's latency is off the critical path.
+        if (warp == FIRST_WORK_WARP && lane == 0 && rd > 0) {
           tma_store_wait_read0();
           mbar_arrive(stage_free);
         }
@@ -334,20 +313,16 @@ __global__ void __launch_bounds__(NTHREADS, 1)
           int w3 = mbar_wait_bounded(stage_free, (rd - 1) & 1u, abort_flag, err_word, ERR_WAIT_AUX) ? 1 : 0;
           if (!__all_sync(0xffffffffu, w3)) { ok = false; break; }
         }
+        if ((st >> 1) == rr) {
+          uint8_t* rowp = sDQ + (st & 1) * (BM * 128) + r * 128;
 #pragma unroll
-        for (int c4 = 0; c4 < 4; ++c4) {   // 16 columns at a time: sub-tile c4 / 2, chunks (c4 % 2) * 4 .. + 3
-          uint32_t v[16];
-          tmem_ld_32x32b_x16(tmem_base + lane_addr + dq_col + rr * 64 + c4 * 16, v);
-          tmem_ld_wait();
-          uint8_t* rowp = sDQ + (c4 >> 1) * (BM * 128) + r * 128;
-#pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4)
-            *reinterpret_cast<uint4*>(rowp + ((((c4 & 1) * 4 + q4) ^ (r & 7)) * 16)) =
+          for (int q4 = 0; q4 < DW / 4; ++q4)
+            *reinterpret_cast<uint4*>(rowp + (((chunkbase + q4) ^ (r & 7)) * 16)) =
                 make_uint4(v[q4 * 4], v[q4 * 4 + 1], v[q4 * 4 + 2], v[q4 * 4 + 3]);
         }
         fence_proxy_async_smem();
         mbar_arrive(stage_full);
-        if (leader) {
+        if (warp == FIRST_WORK_WARP && lane == 0) {
           if (mbar_wait_bounded(stage_full, rd & 1u, abort_flag, err_word, ERR_WAIT_AUX)) {
 #pragma unroll
             for (int hh = 0; hh < 2; ++hh)
@@ -360,23 +335,10 @@ __global__ void __launch_bounds__(NTHREADS, 1)
       }
       if (ok) {
         tc_fence_before_sync();
-        mbar_arrive(odd ? dq_empty1 : dq_empty);
+        mbar_arrive((C::PIPE && (itd & 1)) ? dq_empty1 : dq_empty);
       }
-    }
-    if (leader) tma_store_wait_all0();
-  } else {
-    const int quad = warp & 3;
-    const int part = (warp - FIRST_WORK_WARP) >> 2;  // which quarter of the columns this warp handles
-    const int r = quad * 32 + lane;
-    const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
-    const float c2 = p.scale * 1.4426950408889634f;
-    uint8_t* sP = smem + C::OFF_P;
-    uint8_t* sDS = smem + C::OFF_DS;
-    constexpr int DW = D / NSPLIT;     // columns of dK / dV per warp in the epilogue: 16 (D = 64) or 32 (D = 128)
-    const int dc0 = part * DW;
-    bool ok = true;
-    // "pair done" of pair itd (dV, dK and dQ MMAs complete): one barrier per dQ accumulator, each used by every second
-    // pair in the pipelined variant
+    };
+    // dq_full of pair itd: one barrier per accumulator, each used by every second pair in the pipelined variant
     auto wait_dq_full = [&](int itd) -> bool {
       uint64_t* bar = (C::PIPE && (itd & 1)) ? dq_full1 : dq_full;
       const uint32_t parity = C::PIPE ? ((itd >> 1) & 1u) : (itd & 1u);
@@ -396,8 +358,6 @@ __global__ void __launch_bounds__(NTHREADS, 1)
       const float dlts = row_ok ? p.delta[(long long)hq * T + t] * p.scale : 0.f;
       const bool diag = (kv0 + BN - 1) > q0;
       const int lim = diag ? (qi - kv0) : 0x7fffffff;  // tile columns <= lim are visible to this row
-      const uint64_t c2p = pack_f32x2(c2, c2), nlse2p = pack_f32x2(-lse2, -lse2);
-      const uint64_t scp = pack_f32x2(p.scale, p.scale), ndltsp = pack_f32x2(-dlts, -dlts);
       int w = mbar_wait_bounded(sdp_full, it & 1u, abort_flag, err_word, ERR_WAIT_TMEM_FULL) ? 1 : 0;
       if (!__all_sync(0xffffffffu, w)) { ok = false; break; }
       tc_fence_after_sync();
@@ -411,19 +371,12 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         tmem_ld_wait();
         uint32_t pkP[8], pkS[8];
         if (!diag) {
-          // packed f32x2 arithmetic (one instruction per pair) and every fourth pair of exponentials on the FMA pipe:
-          // the MUFU unit (16 exponentials per clock and SM) and the issue slots are what bound this loop
 #pragma unroll
           for (int e = 0; e < 16; e += 2) {
-            float x0, x1;
-            unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sv[e]), __uint_as_float(sv[e + 1])), c2p, nlse2p), x0, x1);
-            const bool poly = false;   // (e & 6) == 6 puts a quarter of the exponentials on the FMA pipe: slower here, as in the forward
-            const float p0 = poly ? poly_exp2(x0) : fast_exp2(x0);
-            const float p1 = poly ? poly_exp2(x1) : fast_exp2(x1);
-            float d0, d1;
-            unpack_f32x2(mul_f32x2(pack_f32x2(p0, p1),
-                                   fma_f32x2(pack_f32x2(__uint_as_float(dv[e]), __uint_as_float(dv[e + 1])), scp, ndltsp)),
-                         d0, d1);
+            const float p0 = fast_exp2(fmaf(__uint_as_float(sv[e]), c2, -lse2));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(sv[e + 1]), c2, -lse2));
+            const float d0 = p0 * fmaf(__uint_as_float(dv[e]), p.scale, -dlts);
+            const float d1 = p1 * fmaf(__uint_as_float(dv[e + 1]), p.scale, -dlts);
             pkP[e >> 1] = pack_bf16x2(p0, p1);
             pkS[e >> 1] = pack_bf16x2(d0, d1);
           }
@@ -462,10 +415,19 @@ __global__ void __launch_bounds__(NTHREADS, 1)
       fence_proxy_async_smem();
       tc_fence_before_sync();
       mbar_arrive(pds_ready);
+      if constexpr (C::PIPE) {
+        if (it > 0) drain(it - 1);   // its dq_full was waited for above
+      } else {
+        if (!wait_dq_full(it)) { ok = false; break; }
+        drain(it);
+      }
     }
-    // the last pair's "pair done" covers every MMA of the CTA: dK_j and dV_j are complete
-    if (ok && n_it > 0 && !wait_dq_full(n_it - 1)) ok = false;
-    // epilogue: dK_j, dV_j (thread = key row)
+    if (C::PIPE && ok && n_it > 0) {   // the last pair's dQ; this wait also covers every MMA of the CTA
+      if (wait_dq_full(n_it - 1)) drain(n_it - 1);
+      else ok = false;
+    }
+    if (warp == FIRST_WORK_WARP && lane == 0) tma_store_wait_all0();
+    // epilogue: dK_j, dV_j (thread = key row). The last dq_full wait covered every MMA of this CTA.
     if (ok && n_it > 0) {
       const int kvi = kv0 + r;
       const bool row_ok = kvi < p.L;
