@@ -237,6 +237,9 @@ def main() -> int:
     exposed = None
     if args.impl == "ours" and hasattr(runner, "device_step"):
         eng.timer.enabled = True
+        barrier()                       # rank 0 comes late from stopping the clock sampler: without this its peers
+        runner.device_step(dev_pool[0])  # would count that wait as exposed time in their first probe step
+        barrier()
         eng.timer.summary()
         n_probe = 3
         for i in range(n_probe):
