@@ -94,10 +94,12 @@ __device__ __forceinline__ void add_bf16x8(float (&g)[8], const uint4& q) {
   }
 }
 
-// 8 elements per thread. WIRE16 = false: `grads` are the ranks' fp32 gradients (two float4 loads per peer).
-// WIRE16 = true: `grads` are the ranks' bf16 wire copies (one 16-byte load per peer) and this rank's own
-// contribution comes from `own` (its fp32 gradient). One 16-byte bf16 store per peer either way.
-template <bool WIRE16>
+// 8 elements per thread. MODE 0: `grads` are the ranks' fp32 gradients (two float4 loads per peer).
+// MODE 1: `grads` are the ranks' bf16 wire copies (one 16-byte load per peer) and this rank's own contribution comes
+// from `own` (its fp32 gradient). MODE 2: the sum over the ranks is already in `own`, a local fp32 buffer that holds
+// this rank's shard only (indexed like master / m / v) - the reduction ran earlier, behind backward. One 16-byte bf16
+// store per peer in every mode.
+template <int MODE>
 __global__ void __launch_bounds__(256) rs_adamw_ag_kernel(Peers grads, const float* __restrict__ own, Peers models,
                                                          float* __restrict__ master, float* __restrict__ m,
                                                          float* __restrict__ v, long long shard_lo, long long shard_n,
@@ -108,7 +110,12 @@ __global__ void __launch_bounds__(256) rs_adamw_ag_kernel(Peers grads, const flo
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nv;
        i += (long long)gridDim.x * blockDim.x) {
     float g[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    if (WIRE16) {
+    if (MODE == 2) {
+      const float4* src = reinterpret_cast<const float4*>(own + state_off) + 2 * i;
+      const float4 x = src[0], y = src[1];
+      g[0] = x.x; g[1] = x.y; g[2] = x.z; g[3] = x.w;
+      g[4] = y.x; g[5] = y.y; g[6] = y.z; g[7] = y.w;
+    } else if (MODE == 1) {
       uint4 q[MAX_RANKS];
 #pragma unroll
       for (int k = 1; k < MAX_RANKS; ++k)   // all peer loads issued before the first use: their latencies overlap
@@ -223,19 +230,23 @@ __global__ void __launch_bounds__(256) rs_adamw_piece_kernel(Peers grads, long l
   __threadfence_system();
 }
 
-// out[i] = scale * sum_p src_p[lo + i]   (fp32), i < n, n % 4 == 0
+// out[i] = scale * sum_p src_p[lo + i]   (fp32), i < n, n % 4 == 0. All peers' loads of an element are issued before
+// the first addition, so a small grid (the reduction that runs beside backward) still keeps the links busy.
 __global__ void __launch_bounds__(256) reduce_scatter_kernel(Peers src, float* __restrict__ out, long long lo,
                                                             long long n, int rank, int world, float scale) {
   if (poisoned()) return;
   const long long nv = n >> 2;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nv;
        i += (long long)gridDim.x * blockDim.x) {
+    float4 x[MAX_RANKS];
+#pragma unroll
+    for (int k = 0; k < MAX_RANKS; ++k)
+      if (k < world)
+        x[k] = (reinterpret_cast<const float4*>(reinterpret_cast<const float*>(src.p[(rank + k) % world]) + lo))[i];
     float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int k = 0; k < world; ++k) {
-      const int p = (rank + k) % world;
-      const float4 x = (reinterpret_cast<const float4*>(reinterpret_cast<const float*>(src.p[p]) + lo))[i];
-      s.x += x.x; s.y += x.y; s.z += x.z; s.w += x.w;
-    }
+#pragma unroll
+    for (int k = 0; k < MAX_RANKS; ++k)      // fixed order: own copy first, then rank + 1, rank + 2, ...
+      if (k < world) { s.x += x[k].x; s.y += x[k].y; s.z += x[k].z; s.w += x[k].w; }
     s.x *= scale; s.y *= scale; s.z *= scale; s.w *= scale;
     reinterpret_cast<float4*>(out)[i] = s;
   }
@@ -359,36 +370,44 @@ int b200_p2p_cast_wire(const float* grad, void* wire, long long lo, long long n,
 }
 
 // The data-parallel optimizer step on flat offsets [lo, lo + n) (inside this rank's shard):
-//   grad_ptrs[r]   rank r's gradient, fp32 (wire16 = 0) or its bf16 wire copy (wire16 = 1)
-//   own_grad       this rank's fp32 gradient (used with wire16 = 1; its own wire copy is never read)
+//   grad_mode      0: grad_ptrs[r] is rank r's fp32 gradient; 1: grad_ptrs[r] is rank r's bf16 wire copy and own_grad this
+//                  rank's fp32 gradient (its own wire copy is never read); 2: own_grad is a local fp32 buffer of the
+//                  shard's size that already holds the sum over the ranks (grad_ptrs is not read)
 //   model_ptrs[r]  rank r's full bf16 weights
 //   master/m/v     local shard; state_off = lo - shard start
 //   max_ctas       > 0 caps the grid: a launch that runs beside the backward pass takes a few CTAs, not every SM
-int b200_p2p_rs_adamw_ag(const void* const* grad_ptrs, const float* own_grad, int wire16, const void* const* model_ptrs,
+int b200_p2p_rs_adamw_ag(const void* const* grad_ptrs, const float* own_grad, int grad_mode, const void* const* model_ptrs,
                          float* master, float* m, float* v, long long lo, long long n, long long state_off, int rank,
                          int world, float lr, float beta1, float beta2, float eps, float weight_decay, int step,
                          float grad_scale, int decoupled, int max_ctas, cudaStream_t st) {
   Peers G, M;
-  if (!fill(G, grad_ptrs, world) || !fill(M, model_ptrs, world) || !master || !m || !v || n <= 0 || (n & 7) ||
-      (lo & 7) || (state_off & 7) || state_off < 0 || step < 1 || (wire16 && !own_grad))
+  if (grad_mode < 0 || grad_mode > 2 || !fill(M, model_ptrs, world) || !master || !m || !v || n <= 0 || (n & 7) ||
+      (lo & 7) || (state_off & 7) || state_off < 0 || step < 1 || (grad_mode && !own_grad))
     return B200_ERR_ARG;
+  if (grad_mode == 2) G = M;   // the table is not read in this mode
+  else if (!fill(G, grad_ptrs, world)) return B200_ERR_ARG;
   AdamArgs a{lr, beta1, beta2, eps, weight_decay, 1.f - powf(beta1, (float)step), 1.f - powf(beta2, (float)step),
              grad_scale, decoupled};
   int grid = grid_for(n >> 3);
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
-  if (wire16)
-    rs_adamw_ag_kernel<true><<<grid, 256, 0, st>>>(G, own_grad, M, master, m, v, lo, n, state_off, rank, world, a);
+  if (grad_mode == 2)
+    rs_adamw_ag_kernel<2><<<grid, 256, 0, st>>>(G, own_grad, M, master, m, v, lo, n, state_off, rank, world, a);
+  else if (grad_mode == 1)
+    rs_adamw_ag_kernel<1><<<grid, 256, 0, st>>>(G, own_grad, M, master, m, v, lo, n, state_off, rank, world, a);
   else
-    rs_adamw_ag_kernel<false><<<grid, 256, 0, st>>>(G, own_grad, M, master, m, v, lo, n, state_off, rank, world, a);
+    rs_adamw_ag_kernel<0><<<grid, 256, 0, st>>>(G, own_grad, M, master, m, v, lo, n, state_off, rank, world, a);
   B200_CUDA_CHECK(cudaGetLastError());
   return B200_OK;
 }
 
+// max_ctas > 0 caps the grid (a reduction that runs beside the backward pass takes a few CTAs, not every SM)
 int b200_p2p_reduce_scatter_f32(const void* const* src_ptrs, float* out, long long lo, long long n, int rank, int world,
-                                float scale, cudaStream_t st) {
+                                float scale, int max_ctas, cudaStream_t st) {
   Peers S;
   if (!fill(S, src_ptrs, world) || !out || n <= 0 || (n & 3) || (lo & 3)) return B200_ERR_ARG;
-  reduce_scatter_kernel<<<grid_for(n >> 2), 256, 0, st>>>(S, out, lo, n, rank, world, scale);
+  int grid = grid_for(n >> 2);
+  if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
+  reduce_scatter_kernel<<<grid, 256, 0, st>>>(S, out, lo, n, rank, world, scale);
   B200_CUDA_CHECK(cudaGetLastError());
   return B200_OK;
 }

@@ -39,7 +39,7 @@ _lib.register("b200_p2p_rs_adamw_ag", [_VP, _VP, _I, _VP, _VP, _VP, _VP, _LL, _L
 _lib.register("b200_p2p_cast_wire", [_VP, _VP, _LL, _LL, _VP])
 _lib.register("b200_p2p_clear_poison", [_VP])
 _lib.register("b200_p2p_mark_step", [_VP, _VP])
-_lib.register("b200_p2p_reduce_scatter_f32", [_VP, _VP, _LL, _LL, _I, _I, _F, _VP])
+_lib.register("b200_p2p_reduce_scatter_f32", [_VP, _VP, _LL, _LL, _I, _I, _F, _I, _VP])
 _lib.register("b200_p2p_allgather", [_VP, _VP, _LL, _LL, _I, _I, _I, _VP])
 
 
@@ -79,13 +79,17 @@ class P2PComm:
         self.side = torch.cuda.Stream(device=self.device)
         self._ov = None
         import os
-        # B200_OVERLAP=1: the reduction of finished layer ranges runs beside backward on a few CTAs (a full-size grid
-        # there took SM slots and HBM bandwidth from the backward GEMMs and made the step slower); default: one
-        # reduction after backward
+        # B200_OVERLAP=1: the SUM of finished layer ranges over the ranks runs beside backward on a few CTAs, into a
+        # local fp32 buffer of the shard's size; the kernel after backward then only updates and all-gathers. (An
+        # earlier form ran the whole fused kernel there: the AdamW pass moves 30 bytes per parameter through HBM,
+        # which a small grid cannot do in time - 149.5 ms per step against 122.6 on two GPUs.) Default: one fused
+        # kernel after backward.
         self._overlap_enabled = os.environ.get("B200_OVERLAP", "0") == "1"
         self._buckets = max(1, int(os.environ.get("B200_OVERLAP_BUCKETS", "8")))   # ranges per step handed over early
-        self._overlap_ctas = max(1, int(os.environ.get("B200_OVERLAP_CTAS", "24")))
-        self._wire16 = os.environ.get("B200_WIRE", "bf16") != "fp32"
+        self._overlap_ctas = max(1, int(os.environ.get("B200_OVERLAP_CTAS", "16")))
+        # the overlapped reduction reads the peers' fp32 gradients directly: its traffic is hidden, a cast pass is not
+        self._wire16 = os.environ.get("B200_WIRE", "bf16") != "fp32" and not self._overlap_enabled
+        self._reduced = None           # fp32 sum over the ranks of this rank's shard (overlapped reduction only)
         self.grad_buf = None
         self.model_buf = None
         self.wire_buf = None
@@ -173,10 +177,12 @@ class P2PComm:
                 _lib.check(_lib.kernels().b200_p2p_cast_wire(_lib.ptr(f.grad), _lib.ptr(self.wire_buf.tensor), a, b - a,
                                                              _lib.stream()), "b200_p2p_cast_wire")
 
-    def reduce_scatter(self, src: SymmetricBuffer, out: torch.Tensor, lo: int, scale: float = 1.0) -> None:
+    def reduce_scatter(self, src: SymmetricBuffer, out: torch.Tensor, lo: int, scale: float = 1.0,
+                       max_ctas: int = 0) -> None:
         """out[i] = scale * sum over ranks of src[lo + i]; callers bracket this with barriers."""
         _lib.check(_lib.kernels().b200_p2p_reduce_scatter_f32(src.c_ptrs, _lib.ptr(out), lo, out.numel(), self.rank,
-                                                              self.world, float(scale), _lib.stream()), "p2p reduce_scatter")
+                                                              self.world, float(scale), int(max_ctas), _lib.stream()),
+                   "p2p reduce_scatter")
 
     def allgather(self, dst: SymmetricBuffer, local: torch.Tensor, lo_elems: int, skip_self: bool = False) -> None:
         es = local.element_size()
@@ -210,8 +216,9 @@ class P2PComm:
 
     def begin_overlap(self, lr: float, grad_scale: float) -> None:
         """Before the last backward of a step: from now on ``range_ready(lo)`` may hand over finished gradients."""
-        self.opt.step_count += 1
-        self._ov = {"lr": lr, "gs": grad_scale / self.world, "hi": self.flat.total, "met": False}
+        if self._reduced is None:
+            self._reduced = torch.empty(self.flat.shard_size, dtype=torch.float32, device=self.device)
+        self._ov = {"hi": self.flat.total, "met": False}
 
     def range_ready(self, lo: int) -> None:
         """Flat offsets >= lo hold final gradients on THIS rank. Every rank calls this with the same offsets in the
@@ -225,9 +232,8 @@ class P2PComm:
         self._launch_range(lo, hi)
 
     def _launch_range(self, lo: int, hi: int, tail: bool = False) -> None:
-        f, opt, ov = self.flat, self.opt, self._ov
+        f, ov = self.flat, self._ov
         f.zero_untouched_in(lo, hi)
-        self._cast_wire(lo, hi)
         a, b = max(lo, f.shard_lo), min(hi, f.shard_lo + f.shard_size)
         ev = torch.cuda.Event()
         ev.record()                                   # this rank's gradients of the range are complete here
@@ -240,28 +246,31 @@ class P2PComm:
             _lib.check(_lib.kernels().b200_p2p_barrier(self.sig_side.c_ptrs, self.rank, self.world, self.side_epoch,
                                                        _lib.stream()), "b200_p2p_barrier")
             if b > a:
-                b1, b2 = opt.betas
-                st = opt.state
-                gp, own, w16 = self._grad_sources()
                 # ranges that run beside backward take a few CTAs; the last one has the GPU to itself
-                _lib.check(_lib.kernels().b200_p2p_rs_adamw_ag(
-                    gp, own, w16, self.model_buf.c_ptrs, _lib.ptr(f.master), _lib.ptr(st["m"]), _lib.ptr(st["v"]),
-                    a, b - a, a - f.shard_lo, self.rank, self.world, ov["lr"], b1, b2, opt.eps, opt.weight_decay,
-                    opt.step_count, ov["gs"], int(opt.decoupled), 0 if tail else self._overlap_ctas, _lib.stream()),
-                    "b200_p2p_rs_adamw_ag")
+                self.reduce_scatter(self.grad_buf, self._reduced[a - f.shard_lo:b - f.shard_lo], a, 1.0,
+                                    0 if tail else self._overlap_ctas)
 
     # ---- the optimizer step
     def reduce_and_step(self, lr: float, grad_scale: float) -> None:
         f, opt = self.flat, self.opt
         gs = grad_scale / self.world
         if self._ov is not None:
-            # the tail of the flat space (first layers, embedding) and then: everything of the side stream is done,
-            # and every rank's weight stores have landed, before the next forward reads the weights
+            # the tail of the flat space (first layers, embedding); then, with everything of the side stream done, the
+            # update of the shard from the summed gradient and the all-gather of the new weights; the closing barrier
+            # says that every rank's weight stores have landed - and that every rank has finished READING the
+            # gradients - before the next forward and backward run
             self._launch_range(0, self._ov["hi"], tail=True)
             self._ov = None
             done = torch.cuda.Event()
             done.record(self.side)
             torch.cuda.current_stream().wait_event(done)
+            opt.step_count += 1
+            b1, b2 = opt.betas
+            st = opt.state
+            _lib.check(_lib.kernels().b200_p2p_rs_adamw_ag(
+                None, _lib.ptr(self._reduced), 2, self.model_buf.c_ptrs, _lib.ptr(f.master), _lib.ptr(st["m"]),
+                _lib.ptr(st["v"]), f.shard_lo, f.shard_size, 0, self.rank, self.world, lr, b1, b2, opt.eps,
+                opt.weight_decay, opt.step_count, gs, int(opt.decoupled), 0, _lib.stream()), "b200_p2p_rs_adamw_ag")
             self._mark_step()
             self.barrier()
             return

@@ -3,7 +3,9 @@ and the happens-before checker of ``tests/test_zero3_protocol.py``.
 
 Default schedule: backward -> rendezvous + flag barrier -> ONE kernel (peers' gradient shards read, AdamW, new weights
 stored into EVERY rank's weight buffer) -> flag barrier. Overlapped schedule (``B200_OVERLAP=1``): each finished layer
-range is handed to the side stream (own flag words), behind the backward of the earlier layers. Memory is tracked per
+range is handed to the side stream (own flag words), which sums it over the ranks into a local buffer behind the
+backward of the earlier layers; the kernel after backward updates the shard from that buffer and stores the new weights
+into every rank's buffer. Memory is tracked per
 segment of the flat parameter space (cut at parameter and shard boundaries), per rank: the kernel's peer loads of a
 gradient segment must be ordered against the owner's weight-gradient writes of this and of the next step, and its peer
 stores of a weight segment against every rank's compute that reads it. With the bf16 wire format every rank first
@@ -47,8 +49,16 @@ class Segments:
 
 
 class P2PKernels:
-    def __init__(self, seg: Segments, shard_lo: int, shard_size: int):
-        self.seg, self.shard_lo, self.shard_size = seg, shard_lo, shard_size
+    def __init__(self, seg: Segments, shard_lo: int, shard_size: int, comm=None):
+        self.seg, self.shard_lo, self.shard_size, self.comm = seg, shard_lo, shard_size, comm
+
+    def _in_reduced(self, ptr):
+        """Flat offset of a pointer into the communicator's summed-gradient buffer, or None."""
+        red = getattr(self.comm, "_reduced", None)
+        if red is None or ptr is None:
+            return None
+        off = int(getattr(ptr, "value", ptr) or 0) - red.data_ptr()
+        return self.shard_lo + off // 4 if 0 <= off < red.numel() * 4 else None
 
     def b200_p2p_barrier(self, sig, rank, world, epoch, stream):
         zp.SIM.collective(("flag", sig, int(epoch)))
@@ -57,7 +67,10 @@ class P2PKernels:
     def b200_p2p_rs_adamw_ag(self, grads, own, wire16, models, master, m, v, lo, n, state_off, rank, world, *rest):
         segs = list(self.seg.span(lo, lo + n))
         assert state_off == lo - self.shard_lo
-        if wire16:      # own fp32 gradient + the peers' wire copies
+        if wire16 == 2:   # the sum is already in the local buffer
+            assert self._in_reduced(own) == self.shard_lo
+            reads = {("reduced", rank, k) for k in segs}
+        elif wire16:      # own fp32 gradient + the peers' wire copies
             reads = {("grad", rank, k) for k in segs} | {("wire", r, k) for r in range(world) if r != rank for k in segs}
         else:
             reads = {("grad", r, k) for r in range(world) for k in segs}
@@ -74,9 +87,15 @@ class P2PKernels:
         zp.SIM.add("cast wire", reads={("grad", rank, k) for k in segs}, writes={("wire", rank, k) for k in segs})
         return 0
 
-    def b200_p2p_reduce_scatter_f32(self, src, out, lo, n, rank, world, scale, stream):
+    def b200_p2p_reduce_scatter_f32(self, src, out, lo, n, rank, world, scale, max_ctas, stream):
         segs = list(self.seg.span(lo, lo + n))
-        zp.SIM.add("reduce", reads={("grad", r, k) for r in range(world) for k in segs}, writes={("tmp", rank, 0)})
+        where = self._in_reduced(out)
+        if where is not None:
+            assert where == lo          # the buffer is indexed like the shard
+            writes = {("reduced", rank, k) for k in segs}
+        else:
+            writes = {("tmp", rank, 0)}
+        zp.SIM.add("reduce", reads={("grad", r, k) for r in range(world) for k in segs}, writes=writes)
         return 0
 
     def b200_p2p_allgather(self, dst, local, lo_bytes, nbytes, rank, world, skip_self, stream):
@@ -118,7 +137,8 @@ def trace_rank(monkeypatch, rank, world, layers, steps, overlap, optimizer="adam
     if wire:        # the traced model is fp32 (CPU); the schedule of the bf16 wire copy is the same
         comm.wire_buf = zp.FakeSym(flat.total, torch.bfloat16, "cpu")
     comm.segments = seg = Segments(flat)
-    monkeypatch.setattr(zp._lib, "kernels", lambda: P2PKernels(seg, flat.shard_lo, flat.shard_size))
+    monkeypatch.setattr(zp._lib, "kernels", lambda: P2PKernels(seg, flat.shard_lo, flat.shard_size, comm))
+    monkeypatch.setattr(zp._lib, "ptr", lambda t: 0 if t is None else t.data_ptr())   # the recorders tell buffers apart
     real_step = eng.opt.step
 
     def traced_step(lr=None, grad_scale=1.0, grad=None):
@@ -147,7 +167,7 @@ def run(monkeypatch, world, layers, steps, overlap, optimizer="adamw", wire=True
     kinds = {op["kind"] for t in traces for op in t}
     assert "arrive" in kinds and ("reduce+adamw+allgather" in kinds or optimizer != "adamw")
     if overlap and optimizer == "adamw":
-        assert any(op["kind"] == "reduce+adamw+allgather" and op["stream"] == "S" for t in traces for op in t)
+        assert any(op["kind"] == "reduce" and op["stream"] == "S" for t in traces for op in t)
     return zp.find_races(traces)
 
 
