@@ -264,6 +264,9 @@ def load_tp_weights(path: str, rank: int, tp: int, vocab: int | None = None, dty
                          "tensors. Collect with tp_size = 1 (the dequantised model fits one GPU) or export the "
                          "checkpoint to bf16 first.")
     cfg = LlamaConfig.from_pretrained(path)
+    if cfg.num_local_experts:
+        raise NotImplementedError("tensor-parallel collection is built for dense decoders; a mixture-of-experts teacher "
+                                  "runs with tp_size = 1 (ranks become data-parallel replicas)")
     H, Hkv, d, f = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.intermediate_size
     if H % tp or Hkv % tp or f % tp:
         raise ValueError(f"tp={tp} must divide heads ({H}), kv heads ({Hkv}) and the FFN width ({f})")

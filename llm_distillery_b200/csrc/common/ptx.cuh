@@ -119,6 +119,36 @@ __device__ __forceinline__ bool mbar_spin_bounded(uint64_t* bar, uint32_t parity
   }
 }
 
+// ---------------------------------------------------------------- counters in global memory shared by the CTAs of a kernel
+__device__ __forceinline__ unsigned int ld_acquire_gpu_u32(const unsigned int* addr) {
+  unsigned int v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_gpu_u32(unsigned int* addr, unsigned int v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+// Waits until *addr == target (a word that another CTA of the same, fully resident grid sets). Same bound and abort
+// protocol as the mbarrier waits.
+__device__ __forceinline__ bool wait_equal_bounded(const unsigned int* addr, unsigned int target,
+                                                   volatile int* abort_flag, unsigned int* err_word,
+                                                   unsigned int code) {
+  if (ld_acquire_gpu_u32(addr) == target) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    if (ld_acquire_gpu_u32(addr) == target) return true;
+    if (((++spins) & 0xffu) == 0u) {
+      if (*abort_flag) return false;
+      if (globaltimer_ns() - t0 > kWaitTimeoutNs) {
+        *abort_flag = 1;
+        if (err_word) atomicCAS(err_word, 0u, code);
+        return false;
+      }
+    }
+  }
+}
+
 // ---------------------------------------------------------------- fences
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

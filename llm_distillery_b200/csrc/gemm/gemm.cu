@@ -4,6 +4,7 @@
 // GEMMs of a linear layer all run without a transpose pass.
 #include "gemm_pair.cuh"
 #include <stdlib.h>
+#include <atomic>
 #include "../common/host.cuh"
 
 namespace b200 {
@@ -18,12 +19,18 @@ struct StoreParams {
   int out_f32;     // 1: C is fp32, 0: C is 16-bit (bf16 or fp16 according to fmt)
   int accumulate;  // 1: C += result
   int fmt;         // 0 fp16, 1 bf16 (16-bit output type)
-  int atomic;      // 1: fp32 C is updated with red.add (split-K: several CTAs add into one tile)
 };
 
 template <int BN>
 struct EpiStore {
   using Params = StoreParams;
+  static constexpr bool SPLIT_K = true;   // the pair kernel may cut the K loop into slices that are added in order
+  // slice 0 of a tile stores (or adds to what C held, if the caller accumulates); every later slice adds
+  static __device__ __forceinline__ Params slice_params(const Params& p, int slice) {
+    Params q = p;
+    if (slice > 0) q.accumulate = 1;
+    return q;
+  }
   static constexpr int STAGE_BYTES = 32 * 256;              // per epilogue warp: 32 rows x 128 bf16 columns
   static constexpr int SMEM_BYTES = NUM_EPI_WARPS * STAGE_BYTES;
 
@@ -93,11 +100,63 @@ struct EpiStore {
     }
   }
 
+  // fp32 output (weight gradients, with or without accumulation): 64 columns of the warp's 32 rows at a time go
+  // through the same swizzled stage, so that one instruction reads-modifies-writes 256 contiguous bytes of two rows
+  // (whole sectors) instead of 16 bytes of 32 different rows.
+  static __device__ __forceinline__ void tile_staged_f32(const Params& p, uint32_t taddr, int m0, int n0, int M, int N,
+                                                         int quad, int lane, uint8_t* epi_smem) {
+    uint8_t* stage = epi_smem + quad * STAGE_BYTES;
+    const int row0 = m0 + quad * 32;
+    const int rows_valid = min(32, M - row0);
+    float* C = reinterpret_cast<float*>(p.C);
+#pragma unroll 1
+    for (int g = 0; g < BN / 64; ++g) {
+#pragma unroll
+      for (int c2 = 0; c2 < 2; ++c2) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(taddr + g * 64 + c2 * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float4 o = make_float4(__uint_as_float(r[4 * j]) * p.alpha, __uint_as_float(r[4 * j + 1]) * p.alpha,
+                                       __uint_as_float(r[4 * j + 2]) * p.alpha, __uint_as_float(r[4 * j + 3]) * p.alpha);
+          const int chunk = c2 * 8 + j;
+          *reinterpret_cast<float4*>(stage + lane * 256 + ((chunk ^ (lane & 15)) << 4)) = o;
+        }
+      }
+      __syncwarp();
+      const int chunk = lane & 15;
+      const int col = n0 + g * 64 + chunk * 4;
+#pragma unroll 4
+      for (int j = 0; j < 16; ++j) {
+        const int row = 2 * j + (lane >> 4);
+        float4 o = *reinterpret_cast<const float4*>(stage + row * 256 + ((chunk ^ (row & 15)) << 4));
+        if (row < rows_valid && col < N) {
+          float* cp = C + (long long)(row0 + row) * p.ldc + col;
+          if (p.accumulate) {
+            // a reduction, not a load + add + store: the L2 round trip of the load made short K slices epilogue-bound.
+            // The order of the additions into one element is still fixed: the slices of a tile take turns (the
+            // counter protocol of the pair kernel, with a fence before each hand-over) and nothing else adds to C.
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(cp), "f"(o.x), "f"(o.y), "f"(o.z), "f"(o.w)
+                         : "memory");
+          } else {
+            *reinterpret_cast<float4*>(cp) = o;
+          }
+        }
+      }
+      __syncwarp();
+    }
+  }
+
   static __device__ __forceinline__ void tile(const Params& p, uint32_t taddr, int m0, int n0, int M, int N, int quad,
                                               int lane, uint8_t* epi_smem) {
     if (!p.out_f32 && p.fmt == 1 && !p.accumulate && !(N & 7) && !(p.ldc & 7) &&
         !(reinterpret_cast<uintptr_t>(p.C) & 15)) {
       tile_staged(p, taddr, m0, n0, M, N, quad, lane, epi_smem);
+      return;
+    }
+    if (p.out_f32 && !p.resid && !(N & 3) && !(p.ldc & 3) && !(reinterpret_cast<uintptr_t>(p.C) & 15)) {
+      tile_staged_f32(p, taddr, m0, n0, M, N, quad, lane, epi_smem);
       return;
     }
     const int row = m0 + quad * 32 + lane;
@@ -132,20 +191,7 @@ struct EpiStore {
           for (int j = 0; j < ncols; ++j) v[j] += __bfloat162float(rp[j]);
         }
       }
-      if (p.out_f32 && p.atomic) {
-        float* cp = reinterpret_cast<float*>(p.C) + (long long)row * p.ldc + col0;
-        if (ncols == 32 && ((reinterpret_cast<uintptr_t>(cp) & 15) == 0)) {
-#pragma unroll
-          for (int j = 0; j < 8; ++j)
-            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(cp + j * 4), "f"(v[j * 4]),
-                         "f"(v[j * 4 + 1]), "f"(v[j * 4 + 2]), "f"(v[j * 4 + 3])
-                         : "memory");
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (j < ncols) atomicAdd(cp + j, v[j]);
-        }
-      } else if (p.out_f32) {
+      if (p.out_f32) {
         float* cp = reinterpret_cast<float*>(p.C) + (long long)row * p.ldc + col0;
         if (ncols == 32 && ((reinterpret_cast<uintptr_t>(cp) & 15) == 0)) {
 #pragma unroll
@@ -233,6 +279,22 @@ static int launch_store(const void* A, const void* B, int M, int N, int K, long 
   return B200_OK;
 }
 
+// Counters of the ordered split-K epilogue: 8 per tile (one per epilogue warp of a CTA pair), zero between launches.
+constexpr int SPLIT_MAX_TILES = 1024;
+constexpr int SPLIT_MAX_SLICES = 15;
+constexpr int SPLIT_REGIONS = 8;
+__device__ unsigned int g_split_sync[SPLIT_REGIONS * SPLIT_MAX_TILES * 8];
+
+// B200_GEMM_KSPLITS=n forces n slices wherever split-K is possible (experiments); unset: the launcher's estimate
+static int split_k_forced() {
+  static int n = -1;
+  if (n < 0) {
+    const char* e = getenv("B200_GEMM_KSPLITS");
+    n = e ? atoi(e) : 0;
+  }
+  return n;
+}
+
 static bool split_k_enabled() {
   static int on = -1;
   if (on < 0) {
@@ -272,30 +334,42 @@ static int launch_store_pair(const void* A, const void* B, int M, int N, int K, 
   }
   const int tiles = ceil_div(M, PAIR_BM) * ceil_div(N, PAIR_BN);
   const int max_pairs = sm_count() / 2;
-  // split-K for fp32 outputs with a long reduction and too few tiles for even waves (weight-gradient GEMMs):
-  // the slices add atomically into a zeroed (or accumulated-into) C
+  // split-K for fp32 outputs with a long reduction and too few tiles for even waves (weight-gradient GEMMs); the
+  // slices of a tile are added in a fixed order (gemm_pair.cuh)
   int k_splits = 1;
-  StoreParams spl = sp;
-  if (sp.out_f32 && !sp.resid && K >= 4096 && tiles < 3 * max_pairs && split_k_enabled()) {
-    // rounds of the pair grid per unit of tile time: ceil(tiles * s / pairs) / s, plus 8 % per extra slice (measured) for the
-    // atomic epilogues; split only when that buys at least 5 %
-    const int max_s = K / 1024 < 8 ? K / 1024 : 8;   // at least 16 k-blocks per slice
-    double best = (double)((tiles + max_pairs - 1) / max_pairs);
-    const double unsplit = best;
-    for (int s2 = 2; s2 <= max_s; ++s2) {
-      const double c = (double)((tiles * s2 + max_pairs - 1) / max_pairs) / s2 * (1.0 + 0.08 * (s2 - 1));
-      if (c < best) { best = c; k_splits = s2; }
+  const int num_kb = ceil_div(K, BK);
+  if (sp.out_f32 && !sp.resid && !(N & 3) && !(sp.ldc & 3) && tiles <= SPLIT_MAX_TILES && split_k_enabled()) {
+    const int forced = split_k_forced();
+    if (forced > 0) {
+      k_splits = forced;
+    } else {
+      // rounds of the pair grid in units of one whole tile: ceil(tiles * s / pairs) / s, plus 1.5 % per extra slice for
+      // its read-modify-write epilogue; split only when that buys at least 7 %
+      const double unsplit = (double)((tiles + max_pairs - 1) / max_pairs);
+      double best = unsplit;
+      for (int s2 = 2; s2 <= SPLIT_MAX_SLICES && num_kb / s2 >= 16; ++s2) {
+        const double c = (double)((tiles * s2 + max_pairs - 1) / max_pairs) / s2 * (1.0 + 0.015 * (s2 - 1));
+        if (c < best - 1e-9) { best = c; k_splits = s2; }
+      }
+      if (best > 0.93 * unsplit) k_splits = 1;
     }
-    if (best > 0.95 * unsplit) k_splits = 1;
+    if (k_splits > num_kb) k_splits = num_kb;
+    if (k_splits > SPLIT_MAX_SLICES) k_splits = SPLIT_MAX_SLICES;
   }
+  unsigned int* sync = nullptr;
   if (k_splits > 1) {
-    spl.atomic = 1;
-    if (!sp.accumulate)
-      B200_CUDA_CHECK(cudaMemset2DAsync(sp.C, (size_t)sp.ldc * 4, 0, (size_t)N * 4, (size_t)M, stream));
+    // one of 8 counter regions in turn, so that split launches on different streams do not share counters
+    static unsigned int* base[64] = {};        // the array's address on each device of this process
+    static std::atomic<unsigned int> turn{0};
+    int dev = 0;
+    B200_CUDA_CHECK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return B200_ERR_ARG;
+    if (!base[dev]) B200_CUDA_CHECK(cudaGetSymbolAddress(reinterpret_cast<void**>(&base[dev]), g_split_sync));
+    sync = base[dev] + (size_t)(turn.fetch_add(1) % SPLIT_REGIONS) * (SPLIT_MAX_TILES * 8);
   }
   const long long units = (long long)tiles * k_splits;
   const int pairs = units < max_pairs ? (int)units : max_pairs;
-  kern<<<2 * pairs, NUM_THREADS, smem_bytes, stream>>>(tmA, tmB, M, N, K, fmt, spl, device_err_word(), k_splits);
+  kern<<<2 * pairs, NUM_THREADS, smem_bytes, stream>>>(tmA, tmB, M, N, K, fmt, sp, device_err_word(), k_splits, sync);
   B200_CUDA_CHECK(cudaGetLastError());
   return B200_OK;
 }
@@ -345,7 +419,6 @@ int b200_gemm(const void* A, const void* B, void* C, int M, int N, int K, long l
   sp.out_f32 = out_f32;
   sp.accumulate = accumulate;
   sp.fmt = fmt;
-  sp.atomic = 0;
   DescCfg dco;
   const DescCfg* dcp = nullptr;
   if (desc_cfg) {

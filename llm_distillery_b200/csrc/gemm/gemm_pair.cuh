@@ -9,6 +9,14 @@
 // per CTA and are released by tcgen05.commit multicast to both; "accumulator empty" lives in the leader and is
 // arrived on by all 8 epilogue warps (the peer's through its cluster address). Epilogue functors are the same as for
 // the one-SM kernel (gemm_core.cuh).
+//
+// Split-K (k_splits > 1, epilogues with SPLIT_K only): a work unit is (slice of the K loop, tile), slice-major, so
+// the pairs that run side by side work on the same K window of neighbouring tiles. The slices of one tile are added
+// into C in the order of their index: slice s of a tile waits until a counter in global memory says that slice s - 1
+// has been added (8 counters per tile, one per epilogue warp of the pair, because each warp owns its own rows), adds,
+// and releases the counter; the last slice sets it back to zero for the next launch. The order of the additions is
+// therefore fixed and the result repeats bit for bit, which atomic adds did not give. Units are handed out in
+// increasing order and all CTAs of the grid are resident, so the unit a slice waits for is always running or done.
 #pragma once
 #include "gemm_core.cuh"
 
@@ -32,7 +40,8 @@ struct SmemPair {
 template <int STAGES, bool A_MN, bool B_MN, class Epi>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
     gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, int M, int N,
-                     int K, int fmt, typename Epi::Params ep, unsigned int* err_word, int k_splits) {
+                     int K, int fmt, typename Epi::Params ep, unsigned int* err_word, int k_splits,
+                     unsigned int* split_sync) {
   using S = SmemPair<STAGES>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -77,12 +86,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
   const int n_tiles = (N + PAIR_BN - 1) / PAIR_BN;
   const int num_tiles = m_tiles * n_tiles;
   const int num_kb = (K + BK - 1) / BK;
-  // split-K: a work unit is (tile, slice of the K loop); the slices of one tile run on different CTA pairs and the
-  // epilogue (which must add atomically then) combines them. k_splits = 1: one unit per tile.
+  // split-K: a work unit is (slice of the K loop, tile), slice-major. k_splits = 1: one unit per tile.
   const int num_units = num_tiles * k_splits;
   auto unit_range = [&](int unit, int& tile, int& kb0, int& kb1) {
-    tile = unit / k_splits;
-    const int sp = unit - tile * k_splits;
+    const int sp = unit / num_tiles;
+    tile = unit - sp * num_tiles;
     kb0 = (int)((long long)num_kb * sp / k_splits);
     kb1 = (int)((long long)num_kb * (sp + 1) / k_splits);
   };
@@ -195,7 +203,27 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
       if (!ok) break;
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + acc * PAIR_BN + (static_cast<uint32_t>(quad * 32) << 16);
-      Epi::tile(ep, taddr, m_blk * PAIR_BM + (int)cta * BM, n_blk * PAIR_BN, M, N, quad, lane, epi_smem);
+      if constexpr (Epi::SPLIT_K) {
+        if (k_splits > 1) {
+          const int sp = unit / num_tiles;
+          unsigned int* ctr = split_sync + (size_t)tile * 8 + cta * 4 + quad;
+          if (sp > 0) {      // the slices before this one have been added
+            int ok2 = 1;
+            if (lane == 0) ok2 = wait_equal_bounded(ctr, (unsigned)sp, abort_flag, err_word, ERR_WAIT_AUX) ? 1 : 0;
+            ok2 = __all_sync(0xffffffffu, ok2);
+            if (!ok2) break;
+          }
+          Epi::tile(Epi::slice_params(ep, sp), taddr, m_blk * PAIR_BM + (int)cta * BM, n_blk * PAIR_BN, M, N, quad,
+                    lane, epi_smem);
+          __threadfence();
+          __syncwarp();
+          if (lane == 0) st_release_gpu_u32(ctr, sp + 1 == k_splits ? 0u : (unsigned)(sp + 1));
+        } else {
+          Epi::tile(ep, taddr, m_blk * PAIR_BM + (int)cta * BM, n_blk * PAIR_BN, M, N, quad, lane, epi_smem);
+        }
+      } else {
+        Epi::tile(ep, taddr, m_blk * PAIR_BM + (int)cta * BM, n_blk * PAIR_BN, M, N, quad, lane, epi_smem);
+      }
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(leader_tempty0 + acc * 8);

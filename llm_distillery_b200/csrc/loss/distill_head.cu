@@ -34,6 +34,7 @@ struct LseParams {
 };
 
 struct EpiLse {
+  static constexpr bool SPLIT_K = false;
   using Params = LseParams;
   static constexpr int SMEM_BYTES = 0;
   static __device__ __forceinline__ void tile(const Params& p, uint32_t taddr, int m0, int n0, int M, int N, int quad,
@@ -113,6 +114,7 @@ struct DzParams {
 };
 
 struct EpiDz {
+  static constexpr bool SPLIT_K = false;
   using Params = DzParams;
   static constexpr int STAGE_BYTES = 32 * 256;   // per epilogue warp: 32 rows x 128 bf16 columns, chunks XOR-swizzled
   static constexpr int SMEM_BYTES = NUM_EPI_WARPS * STAGE_BYTES;
@@ -233,7 +235,7 @@ static int launch_head(const void* Hc, const void* W, int M, int N, int Kdim, lo
     }
     const int tiles = ceil_div(M, PAIR_BM) * ceil_div(N, PAIR_BN);
     const int pairs = tiles < sm_count() / 2 ? tiles : sm_count() / 2;
-    kern<<<2 * pairs, NUM_THREADS, smem_bytes, stream>>>(tmA, tmB, M, N, Kdim, 1, ep, device_err_word(), 1);
+    kern<<<2 * pairs, NUM_THREADS, smem_bytes, stream>>>(tmA, tmB, M, N, Kdim, 1, ep, device_err_word(), 1, nullptr);
     B200_CUDA_CHECK(cudaGetLastError());
     return B200_OK;
   }

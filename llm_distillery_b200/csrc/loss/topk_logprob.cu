@@ -1,9 +1,10 @@
 // Exact per-row top-K of log_softmax(logits[:, :V]) for teacher collection, and the multi-teacher top-K merge.
 //
 // topk_logprob: one CTA per row over fp32 logits (the row chunk just written by the LM-head GEMM, L2 resident):
-//   1. max and sum-exp                                  -> lse
-//   2. 4-pass 8-bit radix select on order-preserving keys -> exact K-th largest value and how many ties to keep
-//   3. gather: everything above the threshold, plus the lowest-index ties
+//   1. one read: max, sum-exp -> lse, and a histogram of the upper 11 bits of the order-preserving keys
+//   2. second read: everything above the K-th element's bin is selected, the bin itself becomes a candidate list in
+//      shared memory, which three small radix passes narrow to the exact K-th value and the number of ties to keep
+//   3. the lowest-index ties complete the selection
 //   4. bitonic sort in shared memory by (value desc, index asc) - the order torch.topk users expect
 //   5. write fp16 log-probs (value - lse) and int32 ids
 // Output layout matches the HDF5 datasets: [rows, K] fp16 + [rows, K] int32.
@@ -45,103 +46,200 @@ __device__ void bitonic_desc(unsigned long long* s, int n) {
   }
 }
 
+// Block-wide search in a histogram whose bins are ordered by value: the bin that holds the `want`-th largest element
+// (want >= 1, and the histogram holds at least `want` elements). Thread t owns the PER bins just below those of thread
+// t - 1, thread 0 the highest ones; an inclusive scan over the threads gives every thread the number of elements above
+// its bins. Results go to shared memory: the bin, how many elements lie in higher bins, how many in the bin itself.
+// Ends with a block-wide barrier.
+template <int PER>
+__device__ __forceinline__ void find_kth_bin(const unsigned int* hist, unsigned want, unsigned int* redu,
+                                             unsigned int* s_bin, unsigned int* s_above, unsigned int* s_inbin) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int base = NT * PER - PER * (tid + 1);
+  unsigned loc = 0;
+#pragma unroll
+  for (int j = 0; j < PER; ++j) loc += hist[base + j];
+  unsigned inc = loc;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const unsigned n = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += n;
+  }
+  if (lane == 31) redu[warp] = inc;
+  __syncthreads();
+  for (int w = 0; w < warp; ++w) inc += redu[w];
+  const unsigned above = inc - loc;
+  if (above < want && want <= inc) {
+    unsigned cum = above;
+    int bin = base + PER - 1;
+    for (; bin > base; --bin) {
+      if (cum + hist[bin] >= want) break;
+      cum += hist[bin];
+    }
+    *s_bin = (unsigned)bin; *s_above = cum; *s_inbin = hist[bin];
+  }
+  __syncthreads();
+}
+
+// f(value, index) for every index in [lo, hi) of a row, the block's threads striding over it; 16-byte loads when the
+// row pointer allows (lo must be a multiple of 4 then, which the callers' constants are).
+template <class F>
+__device__ __forceinline__ void for_row(const float* __restrict__ x, int lo, int hi, F f) {
+  const int tid = threadIdx.x;
+  if ((reinterpret_cast<uintptr_t>(x) & 15) == 0 && (lo & 3) == 0) {
+    const int hi4 = lo + ((hi - lo) & ~3);
+    const float4* x4 = reinterpret_cast<const float4*>(x);
+    for (int i = (lo >> 2) + tid; i < (hi4 >> 2); i += NT) {
+      const float4 v = x4[i];
+      f(v.x, 4 * i); f(v.y, 4 * i + 1); f(v.z, 4 * i + 2); f(v.w, 4 * i + 3);
+    }
+    for (int i = hi4 + tid; i < hi; i += NT) f(x[i], i);
+  } else {
+    for (int i = lo + tid; i < hi; i += NT) f(x[i], i);
+  }
+}
+
+constexpr int HB = 11;               // bits of the first histogram: sign, exponent, two bits of the mantissa
+constexpr int NBIN = 1 << HB;        // = NT * 8
+constexpr int CAND_CAP = 1024;       // elements of the threshold bin that are kept in shared memory
+constexpr int SAMPLE = 4096;         // leading elements whose K-th largest bounds the row's K-th largest from below
+
+// Two reads of the row. Read 1: running (max, sum-exp) per thread and a histogram of the upper 11 key bits; the first
+// 4096 elements go first, and since the K-th largest of a subset is a lower bound of the K-th largest of the row, the
+// rest of the row only enters the histogram from that bin up (a few per cent of it: the shared-memory atomics were
+// the cost of the one-pass histogram). The histogram gives the bin b of the K-th largest element. Read 2: elements of
+// higher bins are selected, those of bin b (typically 100-200) become candidates in shared memory, and three small
+// radix passes over the candidates' remaining 21 key bits give the exact threshold and the number of ties to keep.
+// A bin with more than CAND_CAP elements falls back to radix passes over the row.
+//
 // Vocabulary-shard mode (out_raw != null): the row is one rank's slice of the vocabulary; the kernel writes the raw
 // fp32 logits of the slice's top K, their GLOBAL ids (index + id_offset) and the slice's log-sum-exp, which
 // topk_combine_kernel turns into the exact top-K log-probs of the whole vocabulary.
-//
-// STAGE: the row (V <= 50 K fp32 values) is copied into shared memory by the first pass and every later pass reads it
-// from there: the seven passes over a row then cost ONE read of it from DRAM instead of up to five (rows of a
-// collection batch do not all stay in L2), and NTT = 512 threads walk it.
-template <int NTT, bool STAGE>
-__global__ void __launch_bounds__(NTT) topk_logprob_kernel(const float* __restrict__ logits, long long ld, int V, int K,
-                                                          __half* __restrict__ out_logp, int* __restrict__ out_idx,
-                                                          float* __restrict__ out_raw, float* __restrict__ out_lse,
-                                                          int id_offset) {
-  extern __shared__ float srow[];
+__global__ void __launch_bounds__(NT) topk_logprob_kernel(const float* __restrict__ logits, long long ld, int V, int K,
+                                                         __half* __restrict__ out_logp, int* __restrict__ out_idx,
+                                                         float* __restrict__ out_raw, float* __restrict__ out_lse,
+                                                         int id_offset) {
+  static_assert(NBIN == NT * 8, "find_kth_bin<8> covers the first histogram");
   __shared__ unsigned long long sel[MAX_K];
-  __shared__ unsigned int hist[256];
+  __shared__ unsigned long long cand[CAND_CAP];
+  __shared__ unsigned int hist[NBIN];
   __shared__ unsigned int ties[TIE_CAP];
-  __shared__ float redf[NTT / 32];
-  __shared__ unsigned int s_prefix, s_remaining, s_nsel, s_nties;
-  __shared__ float s_max, s_lse;
+  __shared__ float redm[NT / 32], reds[NT / 32];
+  __shared__ unsigned int redu[NT / 32];
+  __shared__ unsigned int s_bin, s_above, s_inbin, s_nsel, s_ncand, s_nties;
+  __shared__ float s_lse;
   const long long row = blockIdx.x;
   const float* x = logits + row * ld;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
-  // 1. max, sum-exp
-  float mx = -INFINITY;
-  if (STAGE) {
-    for (int i = tid; i < V; i += NTT) {
-      const float v = x[i];
-      srow[i] = v;
-      mx = fmaxf(mx, v);
-    }
-    x = srow;   // the block-wide barrier of the max reduction below orders these stores before every later read
-  } else {
-    for (int i = tid; i < V; i += NTT) mx = fmaxf(mx, x[i]);
+  for (int i = tid; i < NBIN; i += NT) hist[i] = 0;
+  if (tid == 0) { s_nsel = 0; s_ncand = 0; s_nties = 0; }
+  __syncthreads();
+
+  // ---- read 1: max, sum-exp, histogram
+  float m = -INFINITY, sum = 0.f;
+  auto stat = [&](float v) {
+    if (v > m) { sum *= __expf(m - v); m = v; }
+    if (v > -INFINITY) sum += __expf(v - m);
+  };
+  const int n_sample = V >= 4 * SAMPLE ? SAMPLE : 0;
+  unsigned lb_bin = 0;
+  if (n_sample) {
+    for_row(x, 0, n_sample, [&](float v, int) {
+      stat(v);
+      atomicAdd(&hist[fkey(v) >> (32 - HB)], 1u);
+    });
+    __syncthreads();
+    find_kth_bin<8>(hist, (unsigned)K, redu, &s_bin, &s_above, &s_inbin);
+    lb_bin = s_bin;
+    __syncthreads();
   }
-  mx = warp_max(mx);
-  if (lane == 0) redf[warp] = mx;
-  __syncthreads();
-  if (tid == 0) { float m = redf[0]; for (int w = 1; w < NTT / 32; ++w) m = fmaxf(m, redf[w]); s_max = m; }
-  __syncthreads();
-  mx = s_max;
-  float sm = 0.f;
-  for (int i = tid; i < V; i += NTT) sm += __expf(x[i] - mx);
-  sm = warp_sum(sm);
-  __syncthreads();
-  if (lane == 0) redf[warp] = sm;
+  for_row(x, n_sample, V, [&](float v, int) {
+    stat(v);
+    const unsigned bin = fkey(v) >> (32 - HB);
+    if (bin >= lb_bin) atomicAdd(&hist[bin], 1u);
+  });
+  {
+    const float wm = warp_max(m);
+    const float part = (m > -INFINITY) ? sum * __expf(m - wm) : 0.f;
+    const float ws = warp_sum(part);
+    if (lane == 0) { redm[warp] = wm; reds[warp] = ws; }
+  }
   __syncthreads();
   if (tid == 0) {
+    float M = redm[0];
+    for (int w = 1; w < NT / 32; ++w) M = fmaxf(M, redm[w]);
     float t = 0.f;
-    for (int w = 0; w < NTT / 32; ++w) t += redf[w];
-    s_lse = mx + __logf(t);
-    s_prefix = 0; s_remaining = (unsigned)K; s_nsel = 0; s_nties = 0;
+    for (int w = 0; w < NT / 32; ++w)
+      if (redm[w] > -INFINITY) t += reds[w] * __expf(redm[w] - M);
+    s_lse = M + __logf(t);
   }
+  find_kth_bin<8>(hist, (unsigned)K, redu, &s_bin, &s_above, &s_inbin);
+  const unsigned bstar = s_bin;
+  const unsigned n_inbin = s_inbin;
+  unsigned remaining = (unsigned)K - s_above;       // how many elements of bin bstar belong to the top K (>= 1)
+  const bool in_smem = n_inbin <= (unsigned)CAND_CAP;
+
+  // ---- read 2: higher bins are in; bin bstar becomes the candidate list
+  for_row(x, 0, V, [&](float v, int i) {
+    const uint32_t k = fkey(v);
+    const unsigned bin = k >> (32 - HB);
+    if (bin > bstar) {
+      sel[atomicAdd(&s_nsel, 1u)] = ((unsigned long long)k << 32) | (0xffffffffu - (uint32_t)i);
+    } else if (bin == bstar && in_smem) {
+      cand[atomicAdd(&s_ncand, 1u)] = ((unsigned long long)k << 32) | (0xffffffffu - (uint32_t)i);
+    }
+  });
   __syncthreads();
 
-  // 2. radix select: after the loop s_prefix is the key of the K-th largest element and s_remaining (>= 1) is
-  //    how many elements equal to it belong to the top K
-  for (int pass = 0; pass < 4; ++pass) {
-    const int shift = 24 - 8 * pass;
-    const uint32_t mask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
-    const uint32_t prefix = s_prefix;
-    if (tid < 256) hist[tid] = 0;
-    __syncthreads();
-    for (int i = tid; i < V; i += NTT) {
-      const uint32_t k = fkey(x[i]);
-      if ((k & mask) == prefix) atomicAdd(&hist[(k >> shift) & 0xffu], 1u);
-    }
-    __syncthreads();
-    if (tid == 0) {
-      unsigned rem = s_remaining, cum = 0;
-      int b = 255;
-      for (; b > 0; --b) {
-        if (cum + hist[b] >= rem) break;
-        cum += hist[b];
+  // f(key, index) for every element of bin bstar
+  auto for_bin = [&](auto f) {
+    if (in_smem) {
+      for (unsigned c = tid; c < n_inbin; c += NT) {
+        const unsigned long long e = cand[c];
+        f((uint32_t)(e >> 32), 0xffffffffu - (uint32_t)(e & 0xffffffffu));
       }
-      s_prefix = prefix | ((uint32_t)b << shift);
-      s_remaining = rem - cum;
+    } else {
+      for_row(x, 0, V, [&](float v, int i) {
+        const uint32_t k = fkey(v);
+        if ((k >> (32 - HB)) == bstar) f(k, (uint32_t)i);
+      });
     }
+  };
+
+  // ---- the remaining 21 key bits: 8 + 8 + 5
+  uint32_t prefix = bstar << (32 - HB), mask = 0xffffffffu << (32 - HB);
+#pragma unroll 1
+  for (int pass = 0; pass < 3; ++pass) {
+    const int shift = pass == 0 ? 13 : (pass == 1 ? 5 : 0);
+    const uint32_t digit = pass == 2 ? 0x1fu : 0xffu;
+    hist[tid] = 0;
+    __syncthreads();
+    for_bin([&](uint32_t k, uint32_t) {
+      if ((k & mask) == prefix) atomicAdd(&hist[(k >> shift) & digit], 1u);
+    });
+    __syncthreads();
+    find_kth_bin<1>(hist, remaining, redu, &s_bin, &s_above, &s_inbin);
+    prefix |= s_bin << shift;
+    mask |= digit << shift;
+    remaining -= s_above;
     __syncthreads();
   }
-  const uint32_t thr = s_prefix;
-  const unsigned need_eq = s_remaining;
+  const uint32_t thr = prefix;            // key of the K-th largest element
+  const unsigned need_eq = remaining;     // how many elements equal to it belong to the top K
 
-  // 3. gather
-  for (int i = tid; i < V; i += NTT) {
-    const uint32_t k = fkey(x[i]);
+  // ---- gather from bin bstar
+  for_bin([&](uint32_t k, uint32_t i) {
     if (k > thr) {
-      const unsigned p = atomicAdd(&s_nsel, 1u);
-      if (p < MAX_K) sel[p] = ((unsigned long long)k << 32) | (0xffffffffu - (uint32_t)i);
+      sel[atomicAdd(&s_nsel, 1u)] = ((unsigned long long)k << 32) | (0xffffffffu - i);
     } else if (k == thr) {
       const unsigned p = atomicAdd(&s_nties, 1u);
-      if (p < TIE_CAP) ties[p] = (uint32_t)i;
+      if (p < TIE_CAP) ties[p] = i;
     }
-  }
+  });
   __syncthreads();
   const unsigned ngt = s_nsel;
-  unsigned nt = s_nties;
+  const unsigned nt = s_nties;
   if (nt > TIE_CAP) {
     // pathological row (more than TIE_CAP equal values at the threshold): ordered sequential pick
     if (tid == 0) {
@@ -151,7 +249,7 @@ __global__ void __launch_bounds__(NTT) topk_logprob_kernel(const float* __restri
     }
   } else {
     // keep the need_eq lowest indices among the ties: rank each tie by counting smaller indices
-    for (unsigned t = tid; t < nt; t += NTT) {
+    for (unsigned t = tid; t < nt; t += NT) {
       const uint32_t me = ties[t];
       unsigned rank = 0;
       for (unsigned u = 0; u < nt; ++u) rank += (ties[u] < me) ? 1u : 0u;
@@ -160,16 +258,15 @@ __global__ void __launch_bounds__(NTT) topk_logprob_kernel(const float* __restri
   }
   __syncthreads();
 
-  // 4. sort (pad to a power of two with zeros, which sort last)
+  // ---- sort (pad to a power of two with zeros, which sort last) and write
   int n2 = 1;
   while (n2 < K) n2 <<= 1;
-  for (int i = K + tid; i < n2; i += NTT) sel[i] = 0ull;
+  for (int i = K + tid; i < n2; i += NT) sel[i] = 0ull;
   __syncthreads();
   bitonic_desc(sel, n2);
 
-  // 5. write
   const float lse = s_lse;
-  for (int i = tid; i < K; i += NTT) {
+  for (int i = tid; i < K; i += NT) {
     const unsigned long long e = sel[i];
     const float z = kfloat((uint32_t)(e >> 32));
     if (out_raw) out_raw[row * K + i] = z;
@@ -279,18 +376,7 @@ __global__ void __launch_bounds__(NT) topk_merge_kernel(const float* __restrict_
 
 static int launch_topk(const float* logits, long long ld, int rows, int V, int K, __half* out_logp, int* out_idx,
                        float* out_raw, float* out_lse, int id_offset, cudaStream_t st) {
-  const size_t row_bytes = (size_t)V * sizeof(float);
-  if (row_bytes <= 200 * 1024) {
-    auto kern = topk_logprob_kernel<512, true>;
-    static bool attr = false;
-    if (!attr) {
-      B200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-      attr = true;
-    }
-    kern<<<rows, 512, row_bytes, st>>>(logits, ld, V, K, out_logp, out_idx, out_raw, out_lse, id_offset);
-  } else {
-    topk_logprob_kernel<NT, false><<<rows, NT, 0, st>>>(logits, ld, V, K, out_logp, out_idx, out_raw, out_lse, id_offset);
-  }
+  topk_logprob_kernel<<<rows, NT, 0, st>>>(logits, ld, V, K, out_logp, out_idx, out_raw, out_lse, id_offset);
   B200_CUDA_CHECK(cudaGetLastError());
   return B200_OK;
 }

@@ -1,4 +1,5 @@
-"""Llama-family decoder (Llama 1/2/3, TinyLlama, Mistral: RMSNorm, RoPE, GQA, SwiGLU, optional tied embeddings)
+"""Llama-family decoder (Llama 1/2/3, TinyLlama, Mistral: RMSNorm, RoPE, GQA, SwiGLU, optional tied embeddings;
+Qwen2 with q/k/v bias, Phi-3 with fused projections, Mixtral with sparse experts - models/moe.py)
 for both roles: student training (forward + hand-written backward) and teacher inference.
 
 Design. Each decoder layer is ONE autograd node (``DecoderLayerFn``) whose forward and backward are explicit
@@ -38,6 +39,9 @@ class LlamaConfig:
     bos_token_id: int = 1
     eos_token_id: int = 2
     model_type: str = "llama"         # llama | mistral | qwen2 (q/k/v bias) | phi3 (fused projections in the checkpoint)
+                                      # | mixtral (sparse mixture of experts, models/moe.py)
+    num_local_experts: int = 0        # > 0: every layer's MLP is that many SwiGLU experts behind a linear router
+    num_experts_per_tok: int = 2
     attention_bias: bool = False      # bias on the q/k/v projections (Qwen2 family); o_proj and the MLP have none
     rope_scaling: dict | None = None  # HuggingFace dict; types default / linear / llama3 (ops.basic.rope_tables)
     sliding_window: int | None = None  # attention here is full causal: sequences longer than the window are refused
@@ -58,14 +62,16 @@ class LlamaConfig:
 
     def num_params(self) -> int:
         h, f, V, Lr = self.hidden_size, self.intermediate_size, self.vocab_size, self.num_hidden_layers
-        per_layer = h * (self.q_size + 2 * self.kv_size) + self.q_size * h + 3 * h * f + 2 * h
+        E = self.num_local_experts
+        per_layer = h * (self.q_size + 2 * self.kv_size) + self.q_size * h + 3 * h * f * max(E, 1) + E * h + 2 * h
         if self.attention_bias:
             per_layer += self.q_size + 2 * self.kv_size
         return Lr * per_layer + V * h * (1 if self.tie_word_embeddings else 2) + h
 
     def flops_per_token_fwd(self, seq_len: int) -> float:
         h, f, V, Lr = self.hidden_size, self.intermediate_size, self.vocab_size, self.num_hidden_layers
-        lin = 2 * (Lr * (h * (self.q_size + 2 * self.kv_size) + self.q_size * h + 3 * h * f) + V * h)
+        mlp = 3 * h * f * (self.num_experts_per_tok if self.num_local_experts else 1) + self.num_local_experts * h
+        lin = 2 * (Lr * (h * (self.q_size + 2 * self.kv_size) + self.q_size * h + mlp) + V * h)
         attn = Lr * 4 * self.q_size * seq_len / 2  # causal
         return lin + attn
 
@@ -75,7 +81,13 @@ class LlamaConfig:
         for k in ("rope_scaling", "sliding_window", "pad_token_id"):
             if d[k] is None:
                 d.pop(k)
-        if self.model_type == "phi3":
+        if not self.num_local_experts:
+            d.pop("num_local_experts")
+            d.pop("num_experts_per_tok")
+        if self.model_type == "mixtral":
+            d.pop("attention_bias")
+            d.update(architectures=["MixtralForCausalLM"], hidden_act="silu", torch_dtype="bfloat16")
+        elif self.model_type == "phi3":
             d.pop("attention_bias")
             d.update(architectures=["Phi3ForCausalLM"], hidden_act="silu", torch_dtype="bfloat16")
         elif self.attention_bias:     # q/k/v bias without o_proj bias is the Qwen2 layout in HuggingFace terms
@@ -90,7 +102,7 @@ class LlamaConfig:
                      attention_bias=False, mlp_bias=False)
         return {**extra, **d}
 
-    _KNOWN_TYPES = ("llama", "mistral", "qwen2", "phi3")
+    _KNOWN_TYPES = ("llama", "mistral", "qwen2", "phi3", "mixtral")
 
     @classmethod
     def from_hf_dict(cls, d: dict) -> "LlamaConfig":
@@ -99,6 +111,11 @@ class LlamaConfig:
         mt = d.get("model_type", "llama")
         if mt not in cls._KNOWN_TYPES:
             raise NotImplementedError(f"model_type {mt!r}: only Llama-shaped decoders are built {cls._KNOWN_TYPES}")
+        if mt == "mixtral":
+            if int(kw.get("num_local_experts") or 0) < 1:
+                raise ValueError("a mixtral config needs num_local_experts")
+        elif kw.get("num_local_experts"):
+            raise NotImplementedError(f"experts on model_type {mt!r} are not built (mixtral is)")
         if mt == "qwen2":
             kw["attention_bias"] = True
         elif kw.get("attention_bias"):
@@ -371,8 +388,14 @@ class LlamaDecoderLayer(nn.Module):
             self.qkv_bias = nn.Parameter(torch.zeros(cfg.q_size + 2 * cfg.kv_size, **kw))
         self.o_proj = nn.Parameter(torch.empty(h, cfg.q_size, **kw))
         self.post_attention_layernorm = nn.Parameter(torch.ones(h, **kw))
-        self.gate_up_proj = nn.Parameter(torch.empty(2 * f, h, **kw))
-        self.down_proj = nn.Parameter(torch.empty(h, f, **kw))
+        E = cfg.num_local_experts
+        if E:       # sparse mixture of experts: a router and E stacked expert matrices (models/moe.py)
+            self.router = nn.Parameter(torch.empty(E, h, **kw))
+            self.gate_up_proj = nn.Parameter(torch.empty(E, 2 * f, h, **kw))
+            self.down_proj = nn.Parameter(torch.empty(E, h, f, **kw))
+        else:
+            self.gate_up_proj = nn.Parameter(torch.empty(2 * f, h, **kw))
+            self.down_proj = nn.Parameter(torch.empty(h, f, **kw))
 
 
 class LlamaModel(nn.Module):
@@ -443,6 +466,14 @@ class LlamaModel(nn.Module):
                 pre(layer.input_layernorm, False)
             if LAYER_WEIGHTS_PRE[0] is not None:
                 LAYER_WEIGHTS_PRE[0](layer.input_layernorm)
+            if cfg.num_local_experts:
+                from .moe import AttnBlockFn, MoEBlockFn
+                h = AttnBlockFn.apply(h, pos, cos, sin, layer.input_layernorm, layer.qkv_proj, layer.o_proj, meta,
+                                      getattr(layer, "qkv_bias", None))
+                h = MoEBlockFn.apply(h, layer.post_attention_layernorm, layer.router, layer.gate_up_proj,
+                                     layer.down_proj, (cfg.rms_norm_eps, cfg.num_experts_per_tok, meta[6],
+                                                       layer.input_layernorm))
+                continue
             h = DecoderLayerFn.apply(h, pos, cos, sin, layer.input_layernorm, layer.qkv_proj, layer.o_proj,
                                      layer.post_attention_layernorm, layer.gate_up_proj, layer.down_proj, meta,
                                      getattr(layer, "qkv_bias", None))
@@ -488,6 +519,10 @@ class LlamaModel(nn.Module):
                 att = attention.attention_fwd_cached(qkv, kc, vc, B, n, c0, H, Hkv, d)
                 h1 = basic.linear_fwd(att, layer.o_proj, residual=h)
                 n2, _, _ = basic.rmsnorm_fwd(h1, layer.post_attention_layernorm, cfg.rms_norm_eps)
+                if cfg.num_local_experts:
+                    from .moe import moe_mlp
+                    h = h1 + moe_mlp(n2, layer.router, layer.gate_up_proj, layer.down_proj, cfg.num_experts_per_tok)
+                    continue
                 act = basic.swiglu_fwd(basic.linear_fwd(n2, layer.gate_up_proj))
                 h = basic.linear_fwd(act, layer.down_proj, residual=h1)
             y, _, _ = basic.rmsnorm_fwd(h, self.norm, cfg.rms_norm_eps)
@@ -525,6 +560,14 @@ class LlamaModel(nn.Module):
                 yield pre + "self_attn.v_proj.bias", l.qkv_bias, slice(q + kv, q + 2 * kv)
             yield pre + "self_attn.o_proj.weight", l.o_proj, None
             yield pre + "post_attention_layernorm.weight", l.post_attention_layernorm, None
+            if cfg.num_local_experts:      # Mixtral names: w1 = gate, w3 = up, w2 = down
+                yield pre + "block_sparse_moe.gate.weight", l.router, None
+                for e in range(cfg.num_local_experts):
+                    ex = pre + f"block_sparse_moe.experts.{e}."
+                    yield ex + "w1.weight", l.gate_up_proj, (e, slice(0, f))
+                    yield ex + "w3.weight", l.gate_up_proj, (e, slice(f, 2 * f))
+                    yield ex + "w2.weight", l.down_proj, (e,)
+                continue
             yield pre + "mlp.gate_proj.weight", l.gate_up_proj, slice(0, f)
             yield pre + "mlp.up_proj.weight", l.gate_up_proj, slice(f, 2 * f)
             yield pre + "mlp.down_proj.weight", l.down_proj, None
@@ -550,12 +593,17 @@ class LlamaModel(nn.Module):
         ``training_precision`` 4bit / 8bit do through bitsandbytes (classes/student/model.py:138-148). Embeddings,
         norms and the LM head stay in the compute dtype and keep training."""
         from ..ops.quant import FrozenQuantLinears
+        if self.cfg.num_local_experts:
+            raise NotImplementedError("frozen low-bit weights (training_precision 4bit / 8bit) are not built for "
+                                      "mixture-of-experts models: use bf16")
         self.quant = FrozenQuantLinears(self, kind)
         LAYER_WEIGHTS_PRE[0] = self.quant.before_layer
         return self
 
     @torch.no_grad()
     def load_hf_state_dict(self, sd: dict[str, torch.Tensor], strict: bool = True) -> None:
+        if self.cfg.num_local_experts and any(k.endswith("mlp.experts.gate_up_proj") for k in sd):
+            sd = self._unstack_experts(sd)
         seen = set()
         for n, p, sl in self.named_hf_parameters():
             if n not in sd:
@@ -570,6 +618,28 @@ class LlamaModel(nn.Module):
         extra = [k for k in sd if k not in seen and k != "lm_head.weight" and not k.endswith("rotary_emb.inv_freq")]
         if strict and extra:
             raise KeyError(f"unexpected tensors {extra[:5]}")
+
+    def _unstack_experts(self, sd: dict[str, torch.Tensor]) -> dict[str, torch.Tensor]:
+        """Newer HuggingFace releases keep a Mixtral layer's experts as stacked tensors (``mlp.experts.gate_up_proj``
+        [E, 2f, h], ``mlp.experts.down_proj`` [E, h, f], router ``mlp.gate.weight``); the published checkpoints - and
+        this model's own names - list them per expert under ``block_sparse_moe``."""
+        f = self.cfg.intermediate_size
+        out = {}
+        for k, v in sd.items():
+            if k.endswith("mlp.gate.weight"):
+                out[k.replace("mlp.gate.weight", "block_sparse_moe.gate.weight")] = v
+            elif k.endswith("mlp.experts.gate_up_proj"):
+                pre = k[: -len("mlp.experts.gate_up_proj")] + "block_sparse_moe.experts."
+                for e in range(v.shape[0]):
+                    out[f"{pre}{e}.w1.weight"] = v[e, :f]
+                    out[f"{pre}{e}.w3.weight"] = v[e, f:]
+            elif k.endswith("mlp.experts.down_proj"):
+                pre = k[: -len("mlp.experts.down_proj")] + "block_sparse_moe.experts."
+                for e in range(v.shape[0]):
+                    out[f"{pre}{e}.w2.weight"] = v[e]
+            else:
+                out[k] = v
+        return out
 
     def apply_freeze(self, freeze_layers: list[str]) -> list[str]:
         """requires_grad=False for every parameter one of whose HF names contains a listed substring

@@ -1,6 +1,7 @@
 """Run-twice checks as a race smoke test: kernels whose reduction order is fixed must give bit-identical results on
 identical inputs (a data race between warps, CTAs or pipeline stages shows up as a difference); kernels that add
-with atomics (split-K weight gradients, embedding gradient, dQ accumulation) must agree to rounding."""
+with atomics (embedding gradient, dQ accumulation) must agree to rounding. Split-K weight gradients add their slices
+in a fixed order and repeat exactly (tests/test_gpu_gemm.py)."""
 import pytest
 import torch
 

@@ -59,7 +59,8 @@ def test_gemm_epilogues():
 
 @pytest.mark.parametrize("a_mn,b_mn", [(True, True), (False, False)])
 def test_split_k_fp32_output_overwrite_accumulate_and_strided(a_mn, b_mn):
-    """Long reduction, few tiles, fp32 output: the CTA-pair kernel splits K and adds the slices atomically."""
+    """Long reduction, few tiles, fp32 output: the CTA-pair kernel splits K and adds the slices of a tile in the order
+    of their index, so the result repeats bit for bit."""
     torch.manual_seed(11)
     M, N, K = 1280, 1000, 8192
     a = (torch.randn((K, M) if a_mn else (M, K), device=DEV) * 0.1).bfloat16()
@@ -70,6 +71,10 @@ def test_split_k_fp32_output_overwrite_accumulate_and_strided(a_mn, b_mn):
     basic.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=c)
     assert torch.allclose(c, r, atol=2e-2, rtol=2e-3), (c - r).abs().max()
     assert (wide[:, :8] == 7).all() and (wide[:, 8 + N:] == 7).all()
+    first = c.clone()
+    for _ in range(3):
+        basic.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=c)
+        assert torch.equal(c, first)
     basic.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=c, accumulate=True)
     assert torch.allclose(c, 2 * r, atol=4e-2, rtol=2e-3)
     assert _lib.take_device_error() == 0

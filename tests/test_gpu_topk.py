@@ -26,6 +26,34 @@ def test_topk_logprob_exact(rows, V, Vc, K):
     assert torch.allclose(lp.float().cpu(), ref_lp.float(), atol=2e-3, rtol=1e-3)
 
 
+@pytest.mark.parametrize("case", ["one bin", "masked", "all equal", "few distinct"])
+def test_topk_logprob_rows_that_defeat_the_histogram(case):
+    """Rows whose K-th element shares its 11-bit histogram bin with thousands of others (the candidates no longer fit
+    shared memory and the kernel narrows the threshold over the row instead), rows with masked (-inf) entries, and
+    rows with more equal values at the threshold than the tie list holds."""
+    torch.manual_seed(5)
+    rows, V, K = 9, 20000, 200
+    if case == "one bin":
+        x = 1.0 + 0.1 * torch.rand(rows, V, device=DEV)            # every value in [1.0, 1.1): one bin
+    elif case == "masked":
+        x = torch.randn(rows, V, device=DEV) * 3
+        x[:, 5000:] = float("-inf")
+        x[3, 150:] = float("-inf")                                  # fewer finite values than K
+    elif case == "all equal":
+        x = torch.full((rows, V), 0.25, device=DEV)
+        x[1, 17] = 3.0
+    else:
+        x = torch.randint(0, 3, (rows, V), device=DEV).float()      # ~6700 ties at the threshold
+    lp, ix = topk.topk_logprob(x, V, K)
+    assert _lib.take_device_error() == 0
+    ref_lp, ref_ix = topk.topk_logprob(x.cpu(), V, K)
+    assert torch.equal(ix.cpu(), ref_ix)
+    got, want = lp.float().cpu(), ref_lp.float()
+    finite = torch.isfinite(want)
+    assert torch.equal(torch.isfinite(got), finite)
+    assert torch.allclose(got[finite], want[finite], atol=2e-3, rtol=1e-3)
+
+
 def test_logprob_full_and_merge():
     torch.manual_seed(0)
     x = torch.randn(50, 777, device=DEV) * 3
