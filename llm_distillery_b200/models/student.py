@@ -24,7 +24,7 @@ import torch
 from ..ckpt import hf as ckpt
 from ..engine.schedule import set_lr_scheduler
 from ..engine.trainer import DistillEngine, HostBatch
-from ..obs.console import progress
+from ..obs.console import progress, status
 from ..obs.metrics import Losses, MetricsLogger
 from .base_model import BaseModel
 
@@ -332,18 +332,22 @@ class StudentModel(BaseModel):
                                         group=self.model_name)
         resume = self.saved_state or (self.num_trained_steps == 0 and ckpt.has_trainer_state(self.paths.student_states)
                                       and os.environ.get("B200_RESUME", "1") == "1")
+        self.progress_bar = progress(total=self.total_training_steps, initial=self.num_trained_steps, desc="Training",
+                                     leave=False)
         if resume:
-            self._load_state()
+            with status(self.progress_bar, "Loading state..."):
+                self._load_state()
             self.saved_state = False
+            self.progress_bar.n = self.num_trained_steps      # the saved counters say where the run stands
+            self.progress_bar.refresh()
         else:
-            self._load_model()
+            with status(self.progress_bar, "Loading model..."):
+                self._load_model()
         self._applied = self._counters()
         self._applied_history = [self._applied]      # counters after each of the last few optimizer steps
         self.training_active = True
         if self.losses is None:
             self.losses = Losses(self.logger)
-        self.progress_bar = progress(total=self.total_training_steps, initial=self.num_trained_steps, desc="Training",
-                                     leave=False)
         if self.num_trained_steps == 0:
             self._validate_distillation(validation_data_manager)
         t0 = time.time()
@@ -366,16 +370,20 @@ class StudentModel(BaseModel):
             self._optimizer_step()
         self.train_seconds += time.time() - t0
         if not full_collect:
-            self._save_state()
+            with status(self.progress_bar, "Saving state..."):
+                self._save_state()
             self.saved_state = True
         if self.num_trained_steps >= self.total_training_steps:
-            self._save_model("final")
+            with status(self.progress_bar, "Saving model at step final..."):
+                self._save_model("final")
             if self.save_final_state:
-                self._save_state()
+                with status(self.progress_bar, "Saving state..."):
+                    self._save_state()
                 self.saved_state = True
+        with status(self.progress_bar, "Unloading model..."):
+            self.training_active = False
+            self._unload_model()
         self.progress_bar.close()
-        self.training_active = False
-        self._unload_model()
 
     def _stop_agreed(self) -> bool:
         """A stop request (``stop_requested``, set by the signal handler) reaches the ranks at different moments: they
@@ -476,11 +484,13 @@ class StudentModel(BaseModel):
                 del self._applied_history[:-4]
                 if self._stop_agreed() and self.num_trained_steps < self.total_training_steps:
                     print("Stop requested: saving the trainer state; the same command takes the run up again.", flush=True)
-                    self._save_state()
+                    with status(self.progress_bar, "Saving state..."):
+                        self._save_state()
                     self.training_active = False
                     raise StopRequested()
             if self.num_trained_steps >= self.next_save_step and self.num_trained_steps < self.total_training_steps:
-                self._save_model(self.num_trained_steps)
+                with status(self.progress_bar, f"Saving model at step {self.num_trained_steps}..."):
+                    self._save_model(self.num_trained_steps)
                 self.next_save_step += self.save_every_steps
             if self.num_trained_steps >= self.next_val_step:
                 self._validate_distillation(validation_data_manager)

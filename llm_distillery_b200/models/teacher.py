@@ -21,7 +21,7 @@ import torch
 from ..ckpt.hf import load_hf_model
 from ..collect.collector import TeacherCollector
 from ..data.convo import PARTIAL_SHA_PREFIX
-from ..obs.console import progress
+from ..obs.console import progress, set_status, status
 from .base_model import BaseModel
 
 
@@ -104,6 +104,7 @@ class TeacherModel(BaseModel):
         if not chunk:
             return 0
         aligner = getattr(self, "aligner", None)
+        set_status(None, f"Loading {self.model_name[:20]}...")
         if tp_group is not None:
             from ..collect.collector import TPTeacherCollector
             model = self.load_tp(tp_group)
@@ -118,7 +119,7 @@ class TeacherModel(BaseModel):
         done = 0
         t0 = time.time()
         with progress(total=len(chunk), desc="Convos", leave=False) as bar:
-            bar.set_postfix_str("Generating...")
+            set_status(bar, "Generating...")
             hbt = getattr(self, "heartbeat", None)
             def deliver(rows, convos):
                 nonlocal done
@@ -152,7 +153,8 @@ class TeacherModel(BaseModel):
                     deliver(collector.collect_batch(tokens, convos, aligner=aligner, validation=validation), convos)
             if pending is not None:
                 deliver(collector.rows_of(*pending), pending[1])
-        data_manager.wait()
+            with status(bar, "Writing rows..."):
+                data_manager.wait()
         self.collect_seconds += time.time() - t0
         return done
 

@@ -199,3 +199,15 @@ def test_command_line_with_a_mixtral_student_and_teacher(tmp_path):
     assert all(m == 0.0 for k, m in moved.items() if "block_sparse_moe.gate" in k)
     assert any(m > 0 for k, m in moved.items() if ".experts." in k)
     assert json.load(open(os.path.join(trained, final, "config.json")))["model_type"] == "mixtral"
+
+
+def test_the_console_reports_what_the_workers_are_busy_with():
+    """The status postfixes of the reference's progress bars (classes/student/model.py:81-85 and its call sites,
+    classes/teacher/model.py:81-99): the command-line run above went through all of them."""
+    from llm_distillery_b200.obs import console
+    seen = console.status_history()
+    for text in ("Loading model...", "Generating...", "Writing rows...", "Saving model at step final...",
+                 "Unloading model..."):
+        assert text in seen, (text, seen[-20:])
+    assert any(t.startswith("Loading dense") or t.startswith("Loading sparse") for t in seen)
+    assert console.last_status() == ""
