@@ -137,10 +137,49 @@ def bench_gemms(args, dev, rank, world) -> None:
              frac_of_roofline=round(ideal / ms_f, 3), roofline=f"max(FLOPs/{pk} TF/s of {src}, bytes/{NVLINK_GBS} GB/s)")
 
 
+def bench_collect_replicas(args, dev, rank, world, cfg, full_depth) -> None:
+    """Every rank holds the WHOLE teacher and collects its own batches (what ``tp_size = 0`` picks when the model fits
+    one GPU: a 70 B teacher in bf16 is 131 GiB of 180 GB): no communication, aggregate = sum over the ranks."""
+    import numpy as np
+    from llm_distillery_b200.collect.collector import TeacherCollector
+    from llm_distillery_b200.models.llama import build_model
+    B, L = args.batch, args.seq
+    model = build_model(cfg, dtype=torch.bfloat16, device=dev, seed=None)
+    model.init_weights(seed=rank)
+    collector = TeacherCollector(model, topk=args.topk, crop_to_size=cfg.vocab_size, enable_topk=True)
+
+    class _Convo:      # every position of every sequence is a content row
+        length = L
+
+        @staticmethod
+        def content_indices():
+            return np.arange(L, dtype=np.int64)
+    convos = [_Convo() for _ in range(B)]
+    toks = np.random.default_rng(rank).integers(0, cfg.vocab_size, (B, L)).astype(np.int64)
+
+    def step():
+        with torch.no_grad():
+            collector.fetch(collector.submit(toks, convos))     # rows in pinned host memory when this returns
+
+    n0 = _lib.LAUNCH_COUNT[0]
+    ms = timed_max(step, args.steps, warmup=max(1, args.warmup))
+    launches = (_lib.LAUNCH_COUNT[0] - n0) // (args.steps + max(1, args.warmup))
+    toks_all = B * L * world
+    emit(rank, metric="teacher collect tokens/s", value=round(toks_all / ms * 1e3, 1), unit="tokens/s", n_gpus=world,
+         ms_per_step=round(ms, 3), dtype="bf16", data="synthetic token ids, random-init weights",
+         config={"model": args.model, "layers": cfg.num_hidden_layers, "parallelism": f"{world} replicas (tp1)",
+                 "batch_per_gpu": B, "seq_len": L, "topk": args.topk,
+                 "peak_mem_gb": round(torch.cuda.max_memory_allocated(dev) / 2 ** 30, 1)},
+         smoke_only=bool(cfg.num_hidden_layers != full_depth), gpu_launches_per_step=int(launches),
+         fwd_tflops_per_gpu=round(cfg.flops_per_token_fwd(L) * B * L / ms / 1e9, 1))
+
+
 def bench_collect(args, dev, rank, world) -> None:
     over = {"num_hidden_layers": args.layers} if args.layers else {}
     cfg = preset(args.model, **over)
     full_depth = preset(args.model).num_hidden_layers
+    if args.replicas:
+        return bench_collect_replicas(args, dev, rank, world, cfg, full_depth)
     B = args.batch
     L = padded_seq_len(B, args.seq, world)
     grp = TPGroup(dev, B * L, cfg.hidden_size, topk=args.topk)
@@ -315,6 +354,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=2)
     ap.add_argument("--layers", type=int, default=0)
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--replicas", action="store_true",
+                    help="collect: every rank holds the whole teacher (no tensor parallelism), aggregate over the ranks")
     args = ap.parse_args()
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)

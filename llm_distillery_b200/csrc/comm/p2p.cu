@@ -230,25 +230,42 @@ __global__ void __launch_bounds__(256) rs_adamw_piece_kernel(Peers grads, long l
   __threadfence_system();
 }
 
-// out[i] = scale * sum_p src_p[lo + i]   (fp32), i < n, n % 4 == 0. All peers' loads of an element are issued before
-// the first addition, so a small grid (the reduction that runs beside backward) still keeps the links busy.
+// out[i] = scale * sum_p src_p[lo + i]   (fp32), i < n, n % 4 == 0. A thread works on U 16-byte vectors at a time and
+// issues all world * U loads before the first addition: a peer load takes microseconds, and with one load in flight
+// per thread a small grid (the reduction that runs beside backward) moved 10 GB/s. U is chosen so that world * U
+// vectors (<= 16) are in flight per thread. The order of the additions is fixed: own copy first, then rank + 1, ...
+template <int U>
 __global__ void __launch_bounds__(256) reduce_scatter_kernel(Peers src, float* __restrict__ out, long long lo,
                                                             long long n, int rank, int world, float scale) {
   if (poisoned()) return;
+  constexpr int W = 16 / U;                 // ranks this instantiation serves
   const long long nv = n >> 2;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nv;
-       i += (long long)gridDim.x * blockDim.x) {
-    float4 x[MAX_RANKS];
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i0 = blockIdx.x * (long long)blockDim.x + threadIdx.x; i0 < nv; i0 += stride * U) {
+    float4 x[W][U];
 #pragma unroll
-    for (int k = 0; k < MAX_RANKS; ++k)
-      if (k < world)
-        x[k] = (reinterpret_cast<const float4*>(reinterpret_cast<const float*>(src.p[(rank + k) % world]) + lo))[i];
-    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int k = 0; k < W; ++k) {
+      if (k < world) {
+        const float4* p = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(src.p[(rank + k) % world]) + lo);
 #pragma unroll
-    for (int k = 0; k < MAX_RANKS; ++k)      // fixed order: own copy first, then rank + 1, rank + 2, ...
-      if (k < world) { s.x += x[k].x; s.y += x[k].y; s.z += x[k].z; s.w += x[k].w; }
-    s.x *= scale; s.y *= scale; s.z *= scale; s.w *= scale;
-    reinterpret_cast<float4*>(out)[i] = s;
+        for (int u = 0; u < U; ++u) {
+          const long long i = i0 + u * stride;
+          if (i < nv) x[k][u] = p[i];
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      if (i < nv) {
+        float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int k = 0; k < W; ++k)
+          if (k < world) { s.x += x[k][u].x; s.y += x[k][u].y; s.z += x[k][u].z; s.w += x[k][u].w; }
+        s.x *= scale; s.y *= scale; s.z *= scale; s.w *= scale;
+        reinterpret_cast<float4*>(out)[i] = s;
+      }
+    }
   }
 }
 
@@ -405,9 +422,13 @@ int b200_p2p_reduce_scatter_f32(const void* const* src_ptrs, float* out, long lo
                                 float scale, int max_ctas, cudaStream_t st) {
   Peers S;
   if (!fill(S, src_ptrs, world) || !out || n <= 0 || (n & 3) || (lo & 3)) return B200_ERR_ARG;
-  int grid = grid_for(n >> 2);
+  const int U = world <= 2 ? 8 : (world <= 4 ? 4 : (world <= 8 ? 2 : 1));
+  int grid = grid_for(ceil_div_ll(n >> 2, (long long)U));
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
-  reduce_scatter_kernel<<<grid, 256, 0, st>>>(S, out, lo, n, rank, world, scale);
+  if (U == 8) reduce_scatter_kernel<8><<<grid, 256, 0, st>>>(S, out, lo, n, rank, world, scale);
+  else if (U == 4) reduce_scatter_kernel<4><<<grid, 256, 0, st>>>(S, out, lo, n, rank, world, scale);
+  else if (U == 2) reduce_scatter_kernel<2><<<grid, 256, 0, st>>>(S, out, lo, n, rank, world, scale);
+  else reduce_scatter_kernel<1><<<grid, 256, 0, st>>>(S, out, lo, n, rank, world, scale);
   B200_CUDA_CHECK(cudaGetLastError());
   return B200_OK;
 }

@@ -238,7 +238,8 @@ __device__ __forceinline__ uint4 ld_cg_v4_again(const uint4* p) {
 // Same computation with one WARP per row (h = VPL * 256): no block barriers, 2 * VPL 16-byte loads in flight per
 // lane, the second sweep re-reading the row through the caches, and the warp's running weight-gradient sums
 // in shared memory (h floats per warp, split into two planes so that every access is a conflict-free float4).
-// Each warp owns one row of dw_partial.
+// At the end the CTA's four warps add their sums and the CTA writes ONE row of dw_partial (the column-sum kernel
+// behind it then reads a quarter of the bytes: it has only h / 32 CTAs and was 1.5 % of a training step).
 template <int VPL>
 __global__ void __launch_bounds__(128, 5) rmsnorm_bwd_warp_kernel(const __nv_bfloat16* __restrict__ dy,
                                                               const __nv_bfloat16* __restrict__ x,
@@ -258,9 +259,8 @@ __global__ void __launch_bounds__(128, 5) rmsnorm_bwd_warp_kernel(const __nv_bfl
     lo[lane + 32 * i] = make_float4(0.f, 0.f, 0.f, 0.f);
     hi[lane + 32 * i] = make_float4(0.f, 0.f, 0.f, 0.f);
   }
-  if (gw >= nwarps) return;
   const uint4* wv = reinterpret_cast<const uint4*>(w);
-  for (int row = gw; row < rows; row += nwarps) {
+  for (int row = gw < nwarps ? gw : rows; row < rows; row += nwarps) {
     const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * h);
     const uint4* dr = reinterpret_cast<const uint4*>(dy + (size_t)row * h);
     const float rs = rstd[row];
@@ -306,11 +306,17 @@ __global__ void __launch_bounds__(128, 5) rmsnorm_bwd_warp_kernel(const __nv_bfl
       outr[lane + 32 * i] = pack8(o);
     }
   }
+  __syncthreads();
+  // q < h/8: plane 0 (elements 8q .. 8q+3); q >= h/8: plane 1 (elements 8(q - h/8) + 4 .. + 7)
+  for (int q = threadIdx.x; q < h / 4; q += 128) {
+    float4 s4 = sdw_all[q];
 #pragma unroll
-  for (int i = 0; i < VPL; ++i) {
-    float4* p = reinterpret_cast<float4*>(dw_partial + (size_t)gw * h + (size_t)(lane + 32 * i) * 8);
-    p[0] = lo[lane + 32 * i];
-    p[1] = hi[lane + 32 * i];
+    for (int wi = 1; wi < 4; ++wi) {
+      const float4 t = sdw_all[wi * (h / 4) + q];
+      s4.x += t.x; s4.y += t.y; s4.z += t.z; s4.w += t.w;
+    }
+    const int col = q < h / 8 ? 8 * q : 8 * (q - h / 8) + 4;
+    *reinterpret_cast<float4*>(dw_partial + (size_t)blockIdx.x * h + col) = s4;
   }
 }
 
@@ -614,7 +620,9 @@ int b200_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* 
                                             rstd, (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, dw_partial, rows, h);
 #undef B200_RMS_BWD_WARP
   B200_CUDA_CHECK(cudaGetLastError());
-  colsum_kernel<<<ceil_div(h, 32), 256, 0, st>>>(dw_partial, dw_out, grid, h, dw_accumulate);
+  const bool warp_kernel = h == 2048 || h == 1024 || h == 512 || h == 256;    // one partial row per 4-warp CTA there
+  colsum_kernel<<<ceil_div(h, 32), 256, 0, st>>>(dw_partial, dw_out, warp_kernel ? ceil_div(grid, 4) : grid, h,
+                                                 dw_accumulate);
   B200_CUDA_CHECK(cudaGetLastError());
   return B200_OK;
 }
