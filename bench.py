@@ -131,12 +131,13 @@ def main() -> int:
     from llm_distillery_b200.models.llama import preset
     cfg = preset(args.model)
     B, L, K = args.micro_batch, args.seq_len, args.topk
-    A = max(1, args.grad_accum) if args.impl == "ours" else 1
+    A = max(1, args.grad_accum)
     tokens_per_step = B * L * world * A
 
     if args.impl == "baseline":
         from baseline.hf_baseline import BaselineRunner
-        runner = BaselineRunner(cfg, dev, world, temperature=args.temperature, topk=K, loss=args.loss)
+        runner = BaselineRunner(cfg, dev, world, temperature=args.temperature, topk=K, loss=args.loss, shard=args.shard,
+                                grad_accum=A)
         launches_of = lambda: 0  # noqa: E731
     else:
         from llm_distillery_b200.engine.trainer import DistillEngine

@@ -86,7 +86,7 @@ class P2PComm:
         # kernel after backward.
         self._overlap_enabled = os.environ.get("B200_OVERLAP", "0") == "1"
         self._buckets = max(1, int(os.environ.get("B200_OVERLAP_BUCKETS", "8")))   # ranges per step handed over early
-        self._overlap_ctas = max(1, int(os.environ.get("B200_OVERLAP_CTAS", "16")))
+        self._overlap_ctas = max(1, int(os.environ.get("B200_OVERLAP_CTAS", "32")))
         # the overlapped reduction reads the peers' fp32 gradients directly: its traffic is hidden, a cast pass is not
         self._wire16 = os.environ.get("B200_WIRE", "bf16") != "fp32" and not self._overlap_enabled
         self._reduced = None           # fp32 sum over the ranks of this rank's shard (overlapped reduction only)
