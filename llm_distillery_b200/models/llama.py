@@ -43,14 +43,15 @@ class LlamaConfig:
     num_local_experts: int = 0        # > 0: every layer's MLP is that many SwiGLU experts behind a linear router
     num_experts_per_tok: int = 2
     attention_bias: bool = False      # bias on the q/k/v projections (Qwen2 family); o_proj and the MLP have none
-    rope_scaling: dict | None = None  # HuggingFace dict; types default / linear / llama3 (ops.basic.rope_tables)
+    rope_scaling: dict | None = None  # HuggingFace dict; types default / linear / llama3 / yarn (ops.basic.rope_tables)
+    head_dim_override: int | None = None   # HuggingFace ``head_dim`` when it is not hidden_size / num_attention_heads
     sliding_window: int | None = None  # attention here is full causal: sequences longer than the window are refused
     pad_token_id: int | None = None
     extra: dict = field(default_factory=dict)   # other keys of the source config.json, written back unchanged
 
     @property
     def head_dim(self) -> int:
-        return self.hidden_size // self.num_attention_heads
+        return self.head_dim_override or self.hidden_size // self.num_attention_heads
 
     @property
     def q_size(self) -> int:
@@ -81,6 +82,9 @@ class LlamaConfig:
         for k in ("rope_scaling", "sliding_window", "pad_token_id"):
             if d[k] is None:
                 d.pop(k)
+        hd = d.pop("head_dim_override")
+        if hd:
+            d["head_dim"] = hd
         if not self.num_local_experts:
             d.pop("num_local_experts")
             d.pop("num_experts_per_tok")
@@ -131,14 +135,16 @@ class LlamaConfig:
             kw["num_key_value_heads"] = kw.get("num_attention_heads", 32)
         hd = d.get("head_dim")
         if hd is not None and hd * kw.get("num_attention_heads", 32) != kw.get("hidden_size", 2048):
-            raise NotImplementedError("head_dim different from hidden_size / num_attention_heads is not built")
+            if hd % 16:
+                raise NotImplementedError(f"head_dim {hd}: the rotary and attention kernels need a multiple of 16")
+            kw["head_dim_override"] = int(hd)       # e.g. Mistral-Nemo: 5120 hidden, 32 heads of 128
         if mt == "qwen2" and not d.get("use_sliding_window", False):
             kw["sliding_window"] = None        # Qwen2 configs carry a window that is switched off
         cfg = cls(**kw)
         if cfg.rope_scaling is not None:       # fail at load time, not at the first forward
             kind = cfg.rope_scaling.get("rope_type", cfg.rope_scaling.get("type"))
-            if kind not in (None, "default", "linear", "llama3"):
-                raise NotImplementedError(f"rope_scaling type {kind!r} is not built (default, linear and llama3 are)")
+            if kind not in (None, "default", "linear", "llama3", "yarn"):
+                raise NotImplementedError(f"rope_scaling type {kind!r} is not built (default, linear, llama3 and yarn are)")
         generated = {"architectures", "hidden_act", "torch_dtype", "mlp_bias", "use_sliding_window", "head_dim"}
         cfg.extra = {k: v for k, v in d.items() if k not in keys and k not in generated}
         return cfg
@@ -440,7 +446,8 @@ class LlamaModel(nn.Module):
         need = max_pos or self.cfg.max_position_embeddings
         if self._rope is None or self._rope[0].device != torch.device(device) or self._rope[0].shape[0] < need:
             n = max(need, min(self.cfg.max_position_embeddings, 8192))
-            self._rope = basic.rope_tables(n, self.cfg.head_dim, self.cfg.rope_theta, device, self.cfg.rope_scaling)
+            self._rope = basic.rope_tables(n, self.cfg.head_dim, self.cfg.rope_theta, device, self.cfg.rope_scaling,
+                                           model_max_pos=self.cfg.max_position_embeddings)
         return self._rope
 
     # ---- forward

@@ -158,18 +158,49 @@ def rmsnorm_bwd(dy: torch.Tensor, h: torch.Tensor, w: torch.Tensor, rstd: torch.
 
 
 # ------------------------------------------------------------------------------------------------ RoPE
-def rope_tables(max_pos: int, head_dim: int, theta: float, device, scaling: dict | None = None
-                ) -> tuple[torch.Tensor, torch.Tensor]:
+def rope_tables(max_pos: int, head_dim: int, theta: float, device, scaling: dict | None = None,
+                model_max_pos: int | None = None) -> tuple[torch.Tensor, torch.Tensor]:
     """fp32 cos/sin tables [max_pos, head_dim/2] (HF Llama convention: pairs (i, i + d/2)).
 
     ``scaling`` is a HuggingFace ``rope_scaling`` dict: ``llama3`` (Llama 3.1 / 3.2: low frequencies divided by
     ``factor``, a smooth blend between ``original_max_position_embeddings / low_freq_factor`` and ``/ high_freq_factor``
-    wavelengths) and ``linear`` (every frequency divided by ``factor``) are built; other types are refused."""
+    wavelengths), ``linear`` (every frequency divided by ``factor``) and ``yarn`` (frequencies that turn fewer than
+    ``beta_slow`` times over the original context are interpolated by ``factor``, those that turn more than
+    ``beta_fast`` times are kept, a linear ramp between; cos and sin carry the attention factor 0.1 ln(factor) + 1, or
+    the ``mscale`` / ``mscale_all_dim`` ratio, or an explicit ``attention_factor``) are built; other types are refused.
+    ``model_max_pos`` is the model's ``max_position_embeddings`` (yarn's original context when the dict names none)."""
     import math
     inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32, device=device) / head_dim))
     kind = (scaling or {}).get("rope_type", (scaling or {}).get("type")) if scaling else None
+    amp = 1.0
     if kind in (None, "default"):
         pass
+    elif kind == "yarn":
+        orig = scaling.get("original_max_position_embeddings") or model_max_pos
+        if not orig:
+            raise ValueError("yarn rope scaling needs original_max_position_embeddings")
+        factor = scaling.get("factor")
+        factor = float(factor) if factor is not None else float(model_max_pos) / float(orig)
+
+        def mscale_of(scale, m=1.0):
+            return 1.0 if scale <= 1 else 0.1 * m * math.log(scale) + 1.0
+        amp = scaling.get("attention_factor")
+        if amp is None:
+            ms, ms_all = scaling.get("mscale"), scaling.get("mscale_all_dim")
+            amp = mscale_of(factor, ms) / mscale_of(factor, ms_all) if (ms and ms_all) else mscale_of(factor)
+        amp = float(amp)
+        fast, slow = float(scaling.get("beta_fast") or 32), float(scaling.get("beta_slow") or 1)
+
+        def dim_of(rotations):      # the pair index whose frequency turns `rotations` times over the original context
+            return head_dim * math.log(orig / (rotations * 2 * math.pi)) / (2 * math.log(theta))
+        lo_d, hi_d = dim_of(fast), dim_of(slow)
+        if scaling.get("truncate", True):
+            lo_d, hi_d = math.floor(lo_d), math.ceil(hi_d)
+        lo_d, hi_d = max(lo_d, 0), min(hi_d, head_dim - 1)
+        if lo_d == hi_d:
+            hi_d += 0.001
+        ramp = ((torch.arange(head_dim // 2, dtype=torch.float32, device=device) - lo_d) / (hi_d - lo_d)).clamp(0, 1)
+        inv = (inv / factor) * ramp + inv * (1.0 - ramp)
     elif kind == "linear":
         inv = inv / float(scaling["factor"])
     elif kind == "llama3":
@@ -181,9 +212,9 @@ def rope_tables(max_pos: int, head_dim: int, theta: float, device, scaling: dict
         blended = (1.0 - smooth) * inv / factor + smooth * inv
         inv = torch.where(wavelen > old / lo_f, inv / factor, torch.where(wavelen < old / hi_f, inv, blended))
     else:
-        raise NotImplementedError(f"rope_scaling type {kind!r} is not built (default, linear and llama3 are)")
+        raise NotImplementedError(f"rope_scaling type {kind!r} is not built (default, linear, llama3 and yarn are)")
     ang = torch.arange(max_pos, dtype=torch.float32, device=device)[:, None] * inv[None, :]
-    return ang.cos().contiguous(), ang.sin().contiguous()
+    return (ang.cos() * amp).contiguous(), (ang.sin() * amp).contiguous()
 
 
 def rope_(x: torch.Tensor, pos: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, n_heads: int, head_dim: int,

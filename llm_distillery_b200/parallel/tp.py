@@ -309,7 +309,8 @@ class TPLlama:
     def rope(self, n: int):
         if self._rope is None or self._rope[0].shape[0] < n:
             self._rope = basic.rope_tables(max(n, 2048), self.cfg.head_dim, self.cfg.rope_theta, self.device,
-                                           getattr(self.cfg, "rope_scaling", None))
+                                           getattr(self.cfg, "rope_scaling", None),
+                                           model_max_pos=self.cfg.max_position_embeddings)
         return self._rope
 
     @torch.no_grad()

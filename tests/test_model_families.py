@@ -38,7 +38,7 @@ def test_llama3_rope_scaling_matches_huggingface():
     c0, s0 = basic.rope_tables(128, 16, 10000.0, "cpu")
     assert torch.allclose(c1[4::4], c0[1:8], atol=1e-6) and torch.allclose(s1[4::4], s0[1:8], atol=1e-6)
     with pytest.raises(NotImplementedError):
-        basic.rope_tables(8, 16, 10000.0, "cpu", {"rope_type": "yarn", "factor": 2.0})
+        basic.rope_tables(8, 16, 10000.0, "cpu", {"rope_type": "longrope", "factor": 2.0})
 
 
 def test_phi3_checkpoint_layout_matches_huggingface(tmp_path):
@@ -93,10 +93,45 @@ def test_config_keys_survive_a_round_trip_and_unbuilt_variants_are_refused(tmp_p
     model(torch.randint(0, 320, (1, 128)))                       # up to the window: full causal attention is exact
     with pytest.raises(ValueError, match="attention window"):
         model(torch.randint(0, 320, (1, 129)))
-    for bad in (dict(model_type="gemma2"), dict(hidden_act="gelu_pytorch_tanh"), dict(head_dim=32),
-                dict(partial_rotary_factor=0.5), dict(rope_scaling={"rope_type": "yarn", "factor": 4.0}), dict(mlp_bias=True)):
+    for bad in (dict(model_type="gemma2"), dict(hidden_act="gelu_pytorch_tanh"), dict(head_dim=20),
+                dict(partial_rotary_factor=0.5), dict(rope_scaling={"rope_type": "longrope", "factor": 4.0}), dict(mlp_bias=True)):
         with pytest.raises(NotImplementedError):
             LlamaConfig.from_hf_dict(dict(_base(), **bad))
     # Qwen2 carries a window that is switched off
     q = LlamaConfig.from_hf_dict(dict(_base(), model_type="qwen2", sliding_window=64, use_sliding_window=False))
     assert q.sliding_window is None and q.attention_bias
+
+
+def test_yarn_rope_scaling_and_explicit_head_dim_match_huggingface():
+    yarn = {"rope_type": "yarn", "factor": 4.0, "original_max_position_embeddings": 64, "beta_fast": 32, "beta_slow": 1}
+    cfg = LlamaConfig.from_hf_dict(dict(_base(), model_type="llama", rope_scaling=dict(yarn)))
+    model = build_model(cfg, dtype=torch.float32, device="cpu", seed=3)
+    hf = tr.LlamaForCausalLM(tr.LlamaConfig(**_base(), rope_scaling=dict(yarn), attn_implementation="eager",
+                                            tie_word_embeddings=False)).float()
+    hf.load_state_dict({k: v.clone() for k, v in model.to_hf_state_dict().items()}, strict=False)
+    x = torch.randint(0, 320, (2, 200))
+    ours, ref = model(x), hf(x).logits
+    assert torch.allclose(ours, ref, atol=3e-4, rtol=1e-3), (ours - ref).abs().max()
+    plain = build_model(LlamaConfig(**_base()), dtype=torch.float32, device="cpu", seed=3)
+    assert (plain(x) - ref).abs().max() > 2e-3
+    # the mscale pair of DeepSeek-style configs and an explicit attention factor
+    c1, s1 = basic.rope_tables(16, 16, 10000.0, "cpu", dict(yarn, mscale=1.0, mscale_all_dim=0.5), model_max_pos=256)
+    c0, s0 = basic.rope_tables(16, 16, 10000.0, "cpu", dict(yarn, attention_factor=1.0), model_max_pos=256)
+    import math
+    want = (0.1 * math.log(4.0) + 1.0) / (0.05 * math.log(4.0) + 1.0)
+    assert torch.allclose(c1, c0 * want, atol=1e-6) and torch.allclose(s1, s0 * want, atol=1e-6)
+
+    # head_dim that is not hidden_size / heads (Mistral-Nemo style): 64 hidden, 4 heads of 32
+    d = dict(_base(), model_type="llama", head_dim=32)
+    cfg2 = LlamaConfig.from_hf_dict(d)
+    assert cfg2.head_dim == 32 and cfg2.q_size == 128 and cfg2.to_hf_dict()["head_dim"] == 32
+    m2 = build_model(cfg2, dtype=torch.float32, device="cpu", seed=4)
+    assert m2.layers[0].o_proj.shape == (64, 128)
+    hf2 = tr.LlamaForCausalLM(tr.LlamaConfig(**_base(), head_dim=32, attn_implementation="eager",
+                                             tie_word_embeddings=False)).float()
+    res = hf2.load_state_dict({k: v.clone() for k, v in m2.to_hf_state_dict().items()}, strict=False)
+    assert not res.unexpected_keys
+    x2 = torch.randint(0, 320, (2, 50))
+    assert torch.allclose(m2(x2), hf2(x2).logits, atol=3e-4, rtol=1e-3)
+    with pytest.raises(NotImplementedError):
+        LlamaConfig.from_hf_dict(dict(_base(), model_type="llama", head_dim=20))
