@@ -76,9 +76,15 @@ def cpu_engine():
 
 
 def _tiny3(dtype, device, tied):
+    moe = dict(model_type="mixtral", num_local_experts=4, num_experts_per_tok=2) if os.environ.get("Z3_MOE") == "1" else {}
     cfg = LlamaConfig(vocab_size=512, hidden_size=128, intermediate_size=256, num_hidden_layers=3, num_attention_heads=2,
-                      num_key_value_heads=1, max_position_embeddings=128, tie_word_embeddings=tied)
-    return build_model(cfg, dtype=dtype, device=device, seed=7), cfg
+                      num_key_value_heads=1, max_position_embeddings=128, tie_word_embeddings=tied, **moe)
+    model = build_model(cfg, dtype=dtype, device=device, seed=7)
+    if moe:
+        with torch.no_grad():          # decisive routing: the sharded and the single-process run must pick the same experts
+            for l in model.layers:
+                l.router.mul_(25.0)
+    return model, cfg
 
 
 def _zero3_case(device, dtype, rank, world, tied, freeze, comm_factory, accum=2, steps=3, L=64, close=False):

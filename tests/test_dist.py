@@ -38,6 +38,12 @@ def test_cpu_ranks_full_parameter_sharding_matches_single_process(world):
     _launch("cpu_zero3", world)
 
 
+def test_cpu_ranks_full_parameter_sharding_of_a_mixture_of_experts_student():
+    """The expert half of a Mixtral-style layer is a second autograd node: the unit hooks of the full-shard engine (gather
+    before a layer's backward, reduction after it) must still see the layer as one unit."""
+    _launch("cpu_zero3", 2, env={"Z3_MOE": "1"})
+
+
 def test_cpu_ranks_pipeline_with_fully_sharded_student(tmp_path):
     _launch("cpu_cli_zero3", 2, extra=(str(tmp_path),))
 
