@@ -397,6 +397,17 @@ static bool use_pair(int M, int N, int K) {
 
 extern "C" {
 
+// Zeroes the counters of the ordered split-K epilogue on the current device. A launch leaves them at zero by itself;
+// a kernel that gave up on a bounded wait may not have, so the host calls this when it has taken note of such an error.
+int b200_gemm_reset_split_sync(cudaStream_t stream) {
+  using namespace b200;
+  using namespace b200::gemm;
+  unsigned int* base = nullptr;
+  B200_CUDA_CHECK(cudaGetSymbolAddress(reinterpret_cast<void**>(&base), g_split_sync));
+  B200_CUDA_CHECK(cudaMemsetAsync(base, 0, sizeof(unsigned int) * SPLIT_REGIONS * SPLIT_MAX_TILES * 8, stream));
+  return B200_OK;
+}
+
 // C[M,N] = alpha * op(A) * op(B)^T (+ C if accumulate) (+ residual)
 //   a_mn = 0: A is [M,K] with row stride lda;   a_mn = 1: A is stored [K,M] with row stride lda
 //   b_mn = 0: B is [N,K] with row stride ldb;   b_mn = 1: B is stored [K,N] with row stride ldb

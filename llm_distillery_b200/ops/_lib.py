@@ -55,12 +55,14 @@ _SIGS = {
     "b200_sumsq": [_VP, _LL, _F, _VP, _VP],
     "b200_sm_count": [],
     "b200_segment_reduce": [_VP, _VP, _VP, _LL, _I, _I, _VP],
+    "b200_gemm_reset_split_sync": [_VP],
 }
 
 
 # device kernels launched by one call of each exported launcher (default 1); used to count launches
 KERNELS_PER_CALL = {"b200_rmsnorm_bwd": 2, "b200_flash_attn_bwd": 3, "b200_head_num_tiles": 0, "b200_sm_count": 0,
-                    "b200_rmsnorm_bwd_blocks": 0, "b200_last_cuda_error": 0, "b200_take_device_error": 0}
+                    "b200_rmsnorm_bwd_blocks": 0, "b200_last_cuda_error": 0, "b200_take_device_error": 0,
+                    "b200_gemm_reset_split_sync": 0}
 LAUNCH_COUNT = [0]
 
 
@@ -145,15 +147,22 @@ def check(rc: int, what: str) -> None:
         raise NativeError(f"{what} failed: {_RC.get(rc, rc)} {detail}")
 
 
+def _after_error(err: int) -> int:
+    """A kernel that gave up on a wait may have left the split-K turn counters of the GEMM library non-zero."""
+    if err:
+        kernels().b200_gemm_reset_split_sync(stream())
+    return err
+
+
 def take_device_error() -> int:
     """Synchronise and return (then clear) the in-kernel wait error word of the current device (0 = none)."""
     torch.cuda.synchronize()
-    return int(kernels().b200_take_device_error())
+    return _after_error(int(kernels().b200_take_device_error()))
 
 
 def peek_device_error() -> int:
     """The error word as it stands (pinned host memory), read and cleared WITHOUT synchronising the device."""
-    return int(kernels().b200_take_device_error())
+    return _after_error(int(kernels().b200_take_device_error()))
 
 
 def stream() -> c_void_p:
