@@ -339,6 +339,119 @@ __global__ void __launch_bounds__(256) colsum_kernel(const float* __restrict__ p
   }
 }
 
+// Per-head RMSNorm of the query and key heads of a fused qkv row (Qwen3: q_norm / k_norm, applied before the rotary
+// embedding): y = x * rsqrt(mean_d x^2 + eps) * w, with one weight vector of d elements for all query heads and one
+// for all key heads; value heads are copied. One warp per (token, head), EPL = d / 32 elements per lane, so a head is
+// one 64- or 128-... byte access per lane pair and the reduction over d is a butterfly. rstd [T, H + Hkv] is kept
+// for the backward pass.
+template <int EPL>
+__global__ void __launch_bounds__(256) headnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x,
+                                                          __nv_bfloat16* __restrict__ y,
+                                                          const __nv_bfloat16* __restrict__ wq,
+                                                          const __nv_bfloat16* __restrict__ wk,
+                                                          float* __restrict__ rstd, long long T, int H, int Hkv,
+                                                          long long ld, float eps) {
+  constexpr int d = EPL * 32;
+  const int lane = threadIdx.x & 31;
+  const int nh = H + 2 * Hkv, nn = H + Hkv;
+  const long long items = T * nh;
+  const long long warps = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long it = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5; it < items; it += warps) {
+    const long long t = it / nh;
+    const int hd = (int)(it - t * nh);
+    const __nv_bfloat16* xp = x + t * ld + (long long)hd * d + lane * EPL;
+    __nv_bfloat16* yp = y + t * ld + (long long)hd * d + lane * EPL;
+    float v[EPL];
+#pragma unroll
+    for (int j = 0; j < EPL; j += 2) {
+      const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(xp + j));
+      v[j] = f.x; v[j + 1] = f.y;
+    }
+    if (hd < nn) {
+      float ss = 0.f;
+#pragma unroll
+      for (int j = 0; j < EPL; ++j) ss += v[j] * v[j];
+      ss = warp_sum(ss);
+      const float rs = rsqrtf(ss * (1.f / (float)d) + eps);
+      if (lane == 0) rstd[t * nn + hd] = rs;
+      const __nv_bfloat16* w = (hd < H ? wq : wk) + lane * EPL;
+#pragma unroll
+      for (int j = 0; j < EPL; ++j) v[j] = v[j] * rs * __bfloat162float(w[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < EPL; j += 2)
+      *reinterpret_cast<uint32_t*>(yp + j) = pack_bf16x2(v[j], v[j + 1]);
+  }
+}
+
+// Backward of the above, in place on the gradient g of the normalised (un-rotated) qkv row: for query and key heads
+// g <- rstd * (g w - xhat * mean_d(g w xhat)), xhat = x * rstd; value heads are left alone. The weight gradients
+// sum_{token, head} g * xhat stay in registers over the warp's items (a lane always owns the same EPL elements),
+// the block's warps add theirs through shared memory, and every block writes one row [dwq | dwk] of `partial`.
+template <int EPL>
+__global__ void __launch_bounds__(256) headnorm_bwd_kernel(__nv_bfloat16* __restrict__ g,
+                                                          const __nv_bfloat16* __restrict__ x,
+                                                          const __nv_bfloat16* __restrict__ wq,
+                                                          const __nv_bfloat16* __restrict__ wk,
+                                                          const float* __restrict__ rstd,
+                                                          float* __restrict__ partial, long long T, int H, int Hkv,
+                                                          long long ld) {
+  constexpr int d = EPL * 32;
+  __shared__ float sdw[8][2 * d];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nn = H + Hkv;
+  const long long items = T * nn;
+  const long long warps = ((long long)gridDim.x * blockDim.x) >> 5;
+  float aq[EPL], ak[EPL], wqf[EPL], wkf[EPL];
+#pragma unroll
+  for (int j = 0; j < EPL; ++j) {
+    aq[j] = 0.f; ak[j] = 0.f;
+    wqf[j] = __bfloat162float(wq[lane * EPL + j]);
+    wkf[j] = __bfloat162float(wk[lane * EPL + j]);
+  }
+  for (long long it = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5; it < items; it += warps) {
+    const long long t = it / nn;
+    const int hd = (int)(it - t * nn);
+    const bool isq = hd < H;
+    const __nv_bfloat16* xp = x + t * ld + (long long)hd * d + lane * EPL;
+    __nv_bfloat16* gp = g + t * ld + (long long)hd * d + lane * EPL;
+    const float rs = rstd[it];
+    float xh[EPL], gw[EPL], gy[EPL];
+    float dot = 0.f;
+#pragma unroll
+    for (int j = 0; j < EPL; j += 2) {
+      const float2 fx = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(xp + j));
+      const float2 fg = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(gp + j));
+      xh[j] = fx.x * rs; xh[j + 1] = fx.y * rs;
+      gy[j] = fg.x; gy[j + 1] = fg.y;
+    }
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) {
+      gw[j] = gy[j] * (isq ? wqf[j] : wkf[j]);
+      dot += gw[j] * xh[j];
+      if (isq) aq[j] += gy[j] * xh[j]; else ak[j] += gy[j] * xh[j];
+    }
+    const float c = warp_sum(dot) * (1.f / (float)d);
+    float o[EPL];
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) o[j] = rs * (gw[j] - xh[j] * c);
+#pragma unroll
+    for (int j = 0; j < EPL; j += 2) *reinterpret_cast<uint32_t*>(gp + j) = pack_bf16x2(o[j], o[j + 1]);
+  }
+#pragma unroll
+  for (int j = 0; j < EPL; ++j) {
+    sdw[warp][lane * EPL + j] = aq[j];
+    sdw[warp][d + lane * EPL + j] = ak[j];
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < 2 * d; c += blockDim.x) {
+    float t = 0.f;
+#pragma unroll
+    for (int w8 = 0; w8 < 8; ++w8) t += sdw[w8][c];
+    partial[(size_t)blockIdx.x * (2 * d) + c] = t;
+  }
+}
+
 // Rotary embedding, HF Llama convention (pairs (i, i + d/2)), in place on x[T, nh, d].
 // cos/sin tables are fp32 [max_pos, d/2]; pos[t] gives the position of token t. sign = -1 runs the inverse rotation
 // (the backward pass).
@@ -623,6 +736,52 @@ int b200_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* 
   const bool warp_kernel = h == 2048 || h == 1024 || h == 512 || h == 256;    // one partial row per 4-warp CTA there
   colsum_kernel<<<ceil_div(h, 32), 256, 0, st>>>(dw_partial, dw_out, warp_kernel ? ceil_div(grid, 4) : grid, h,
                                                  dw_accumulate);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200_OK;
+}
+
+// Per-head RMSNorm of the q and k heads of qkv rows [T, (H + 2 Hkv) d] with row stride ld (Qwen3 q_norm / k_norm):
+// y gets the normalised q and k heads and a copy of the v heads, rstd [T, H + Hkv] the inverse norms. d = 64 or 128.
+int b200_headnorm_fwd(const void* x, void* y, const void* wq, const void* wk, float* rstd, long long T, int H, int Hkv,
+                      int d, long long ld, float eps, cudaStream_t st) {
+  if (!x || !y || !wq || !wk || !rstd || T <= 0 || H <= 0 || Hkv <= 0 || (d != 64 && d != 128) || (ld & 7))
+    return B200_ERR_ARG;
+  const long long items = T * (H + 2 * Hkv);
+  const int grid = grid_for(items * 32, 256);
+  if (d == 128)
+    headnorm_fwd_kernel<4><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, (const __nv_bfloat16*)wq,
+                                                 (const __nv_bfloat16*)wk, rstd, T, H, Hkv, ld, eps);
+  else
+    headnorm_fwd_kernel<2><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, (const __nv_bfloat16*)wq,
+                                                 (const __nv_bfloat16*)wk, rstd, T, H, Hkv, ld, eps);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200_OK;
+}
+
+int b200_headnorm_bwd_blocks(long long T, int H, int Hkv) {
+  const long long items = T * (H + Hkv);
+  long long b = (items + 7) / 8;             // 8 warps per block
+  const long long cap = (long long)sm_count() * 8;
+  return (int)(b < cap ? (b < 1 ? 1 : b) : cap);
+}
+
+// In place on g (the gradient of the normalised, un-rotated qkv rows); dw_partial is scratch of
+// b200_headnorm_bwd_blocks(T, H, Hkv) * 2 d floats; dw_out [2 d] = [dwq | dwk] is written or accumulated.
+int b200_headnorm_bwd(void* g, const void* x, const void* wq, const void* wk, const float* rstd, float* dw_partial,
+                      float* dw_out, int dw_accumulate, long long T, int H, int Hkv, int d, long long ld,
+                      cudaStream_t st) {
+  if (!g || !x || !wq || !wk || !rstd || !dw_partial || !dw_out || T <= 0 || H <= 0 || Hkv <= 0 ||
+      (d != 64 && d != 128) || (ld & 7))
+    return B200_ERR_ARG;
+  const int grid = b200_headnorm_bwd_blocks(T, H, Hkv);
+  if (d == 128)
+    headnorm_bwd_kernel<4><<<grid, 256, 0, st>>>((__nv_bfloat16*)g, (const __nv_bfloat16*)x, (const __nv_bfloat16*)wq,
+                                                 (const __nv_bfloat16*)wk, rstd, dw_partial, T, H, Hkv, ld);
+  else
+    headnorm_bwd_kernel<2><<<grid, 256, 0, st>>>((__nv_bfloat16*)g, (const __nv_bfloat16*)x, (const __nv_bfloat16*)wq,
+                                                 (const __nv_bfloat16*)wk, rstd, dw_partial, T, H, Hkv, ld);
+  B200_CUDA_CHECK(cudaGetLastError());
+  colsum_kernel<<<ceil_div(2 * d, 32), 256, 0, st>>>(dw_partial, dw_out, grid, 2 * d, dw_accumulate);
   B200_CUDA_CHECK(cudaGetLastError());
   return B200_OK;
 }

@@ -45,6 +45,7 @@ class LlamaConfig:
     attention_bias: bool = False      # bias on the q/k/v projections (Qwen2 family); o_proj and the MLP have none
     rope_scaling: dict | None = None  # HuggingFace dict; types default / linear / llama3 / yarn (ops.basic.rope_tables)
     head_dim_override: int | None = None   # HuggingFace ``head_dim`` when it is not hidden_size / num_attention_heads
+    qk_norm: bool = False             # Qwen3: RMSNorm over every query and key head (one weight each) before RoPE
     sliding_window: int | None = None  # attention here is full causal: sequences longer than the window are refused
     pad_token_id: int | None = None
     extra: dict = field(default_factory=dict)   # other keys of the source config.json, written back unchanged
@@ -67,6 +68,8 @@ class LlamaConfig:
         per_layer = h * (self.q_size + 2 * self.kv_size) + self.q_size * h + 3 * h * f * max(E, 1) + E * h + 2 * h
         if self.attention_bias:
             per_layer += self.q_size + 2 * self.kv_size
+        if self.qk_norm:
+            per_layer += 2 * self.head_dim
         return Lr * per_layer + V * h * (1 if self.tie_word_embeddings else 2) + h
 
     def flops_per_token_fwd(self, seq_len: int) -> float:
@@ -88,7 +91,11 @@ class LlamaConfig:
         if not self.num_local_experts:
             d.pop("num_local_experts")
             d.pop("num_experts_per_tok")
-        if self.model_type == "mixtral":
+        qk = d.pop("qk_norm")
+        if self.model_type == "qwen3":
+            d.update(architectures=["Qwen3ForCausalLM"], hidden_act="silu", torch_dtype="bfloat16",
+                     use_sliding_window=False, head_dim=self.head_dim)
+        elif self.model_type == "mixtral":
             d.pop("attention_bias")
             d.update(architectures=["MixtralForCausalLM"], hidden_act="silu", torch_dtype="bfloat16")
         elif self.model_type == "phi3":
@@ -106,7 +113,7 @@ class LlamaConfig:
                      attention_bias=False, mlp_bias=False)
         return {**extra, **d}
 
-    _KNOWN_TYPES = ("llama", "mistral", "qwen2", "phi3", "mixtral")
+    _KNOWN_TYPES = ("llama", "mistral", "qwen2", "phi3", "mixtral", "qwen3")
 
     @classmethod
     def from_hf_dict(cls, d: dict) -> "LlamaConfig":
@@ -115,11 +122,19 @@ class LlamaConfig:
         mt = d.get("model_type", "llama")
         if mt not in cls._KNOWN_TYPES:
             raise NotImplementedError(f"model_type {mt!r}: only Llama-shaped decoders are built {cls._KNOWN_TYPES}")
+        if mt == "qwen3" and d.get("num_experts"):
+            raise NotImplementedError("qwen3 mixture-of-experts checkpoints are not built (dense qwen3 and mixtral are)")
         if mt == "mixtral":
             if int(kw.get("num_local_experts") or 0) < 1:
                 raise ValueError("a mixtral config needs num_local_experts")
         elif kw.get("num_local_experts"):
             raise NotImplementedError(f"experts on model_type {mt!r} are not built (mixtral is)")
+        if mt == "qwen3":
+            kw["qk_norm"] = True
+            if kw.get("attention_bias"):
+                raise NotImplementedError("qwen3 with attention_bias also puts a bias on o_proj, which is not built")
+            if not d.get("use_sliding_window", False):
+                kw["sliding_window"] = None
         if mt == "qwen2":
             kw["attention_bias"] = True
         elif kw.get("attention_bias"):
@@ -269,12 +284,17 @@ class DecoderLayerFn(torch.autograd.Function):
     """h_out = h + Attn(RMSNorm(h)) ; then + MLP(RMSNorm(.)) - one node, explicit backward."""
 
     @staticmethod
-    def forward(ctx, h, pos, cos, sin, w_ln1, w_qkv, w_o, w_ln2, w_gu, w_d, meta, b_qkv=None):
+    def forward(ctx, h, pos, cos, sin, w_ln1, w_qkv, w_o, w_ln2, w_gu, w_d, meta, b_qkv=None, w_qn=None, w_kn=None):
         B, L, H, Hkv, d, eps, recompute = meta
         n1, _, rstd1 = basic.rmsnorm_fwd(h, w_ln1, eps)
         qkv = basic.linear_fwd(n1, w_qkv)
         if b_qkv is not None:
             basic.bias_add_(qkv, b_qkv)
+        qk_saved = ()
+        if w_qn is not None:                                  # per-head norm of q and k (Qwen3), before the rotation
+            qkv_raw = qkv
+            qkv, rstd_qk = basic.headnorm_fwd(qkv_raw, w_qn, w_kn, H, Hkv, d, eps)
+            qk_saved = (qkv_raw, rstd_qk)
         basic.rope_(qkv, pos, cos, sin, H + Hkv, d)          # q and k heads are adjacent columns
         att, lse = attention.attention_fwd(qkv, B, L, H, Hkv, d)
         h1 = basic.linear_fwd(att, w_o, residual=h)
@@ -287,10 +307,12 @@ class DecoderLayerFn(torch.autograd.Function):
         ctx.slots = tuple(_slot(w) for w in ctx.weights)
         ctx.b_qkv = b_qkv
         ctx.b_slot = _slot(b_qkv) if b_qkv is not None else None
+        ctx.qk_w = (w_qn, w_kn)
+        ctx.qk_slots = (_slot(w_qn), _slot(w_kn)) if w_qn is not None else (None, None)
         if recompute:   # gradient checkpointing: keep only the layer input
             ctx.save_for_backward(h, pos, cos, sin)
         else:
-            ctx.save_for_backward(h, pos, cos, sin, rstd1, n1, qkv, att, lse, h1, rstd2, n2, gu, act)
+            ctx.save_for_backward(h, pos, cos, sin, rstd1, n1, qkv, att, lse, h1, rstd2, n2, gu, act, *qk_saved)
         return h2
 
     @staticmethod
@@ -302,18 +324,25 @@ class DecoderLayerFn(torch.autograd.Function):
             UNIT_PRE[0](w_ln1, True)
         if LAYER_WEIGHTS_PRE[0] is not None:
             LAYER_WEIGHTS_PRE[0](w_ln1)
+        w_qn, w_kn = ctx.qk_w
+        qkv_raw = rstd_qk = None
         if recompute:
             h, pos, cos, sin = ctx.saved_tensors
             n1, _, rstd1 = basic.rmsnorm_fwd(h, w_ln1, eps)
             qkv = basic.linear_fwd(n1, w_qkv)
             if ctx.b_qkv is not None:
                 basic.bias_add_(qkv, ctx.b_qkv)
+            if w_qn is not None:
+                qkv_raw = qkv
+                qkv, rstd_qk = basic.headnorm_fwd(qkv_raw, w_qn, w_kn, H, Hkv, d, eps)
             basic.rope_(qkv, pos, cos, sin, H + Hkv, d)
             att, lse = attention.attention_fwd(qkv, B, L, H, Hkv, d)
             h1 = basic.linear_fwd(att, w_o, residual=h)
             n2, _, rstd2 = basic.rmsnorm_fwd(h1, w_ln2, eps)
             gu = basic.linear_fwd(n2, w_gu)
             act = basic.swiglu_fwd(gu)
+        elif w_qn is not None:
+            h, pos, cos, sin, rstd1, n1, qkv, att, lse, h1, rstd2, n2, gu, act, qkv_raw, rstd_qk = ctx.saved_tensors
         else:
             h, pos, cos, sin, rstd1, n1, qkv, att, lse, h1, rstd2, n2, gu, act = ctx.saved_tensors
         dh2 = dh2.contiguous()
@@ -334,6 +363,11 @@ class DecoderLayerFn(torch.autograd.Function):
         dqkv = attention.attention_bwd(datt, qkv, att, lse, B, L, H, Hkv, d)
         del datt
         basic.rope_(dqkv, pos, cos, sin, H + Hkv, d, inverse=True)
+        g_qn = g_kn = None
+        if w_qn is not None:
+            dwq, dwk = basic.headnorm_bwd_(dqkv, qkv_raw, w_qn, w_kn, rstd_qk, H, Hkv, d)
+            g_qn = _vec_grad(dwq, w_qn, ctx.qk_slots[0])
+            g_kn = _vec_grad(dwk, w_kn, ctx.qk_slots[1])
         g_b = None
         if ctx.b_qkv is not None and ctx.b_qkv.requires_grad:
             if ctx.b_slot is not None:
@@ -348,7 +382,7 @@ class DecoderLayerFn(torch.autograd.Function):
         g_ln1 = _vec_grad(dw1, w_ln1, s_ln1)
         if LAYER_BACKWARD_DONE[0] is not None:
             LAYER_BACKWARD_DONE[0](w_ln1)
-        return dh, None, None, None, g_ln1, g_qkv, g_o, g_ln2, g_gu, g_d, None, g_b
+        return dh, None, None, None, g_ln1, g_qkv, g_o, g_ln2, g_gu, g_d, None, g_b, g_qn, g_kn
 
 
 class FinalNormFn(torch.autograd.Function):
@@ -392,6 +426,9 @@ class LlamaDecoderLayer(nn.Module):
         self.qkv_proj = nn.Parameter(torch.empty(cfg.q_size + 2 * cfg.kv_size, h, **kw))
         if cfg.attention_bias:
             self.qkv_bias = nn.Parameter(torch.zeros(cfg.q_size + 2 * cfg.kv_size, **kw))
+        if cfg.qk_norm:
+            self.q_norm = nn.Parameter(torch.ones(cfg.head_dim, **kw))
+            self.k_norm = nn.Parameter(torch.ones(cfg.head_dim, **kw))
         self.o_proj = nn.Parameter(torch.empty(h, cfg.q_size, **kw))
         self.post_attention_layernorm = nn.Parameter(torch.ones(h, **kw))
         E = cfg.num_local_experts
@@ -483,7 +520,8 @@ class LlamaModel(nn.Module):
                 continue
             h = DecoderLayerFn.apply(h, pos, cos, sin, layer.input_layernorm, layer.qkv_proj, layer.o_proj,
                                      layer.post_attention_layernorm, layer.gate_up_proj, layer.down_proj, meta,
-                                     getattr(layer, "qkv_bias", None))
+                                     getattr(layer, "qkv_bias", None), getattr(layer, "q_norm", None),
+                                     getattr(layer, "k_norm", None))
         if pre is not None:
             pre(self.norm, False)
         return FinalNormFn.apply(h, self.norm, cfg.rms_norm_eps)
@@ -520,6 +558,8 @@ class LlamaModel(nn.Module):
                 qkv = basic.linear_fwd(n1, layer.qkv_proj)
                 if hasattr(layer, "qkv_bias"):
                     basic.bias_add_(qkv, layer.qkv_bias)
+                if cfg.qk_norm:
+                    qkv, _ = basic.headnorm_fwd(qkv, layer.q_norm, layer.k_norm, H, Hkv, d, cfg.rms_norm_eps)
                 basic.rope_(qkv, pos, cos, sin, H + Hkv, d)
                 kc[:, c0:c0 + n] = qkv[:, H * d:(H + Hkv) * d].reshape(B, n, kv)
                 vc[:, c0:c0 + n] = qkv[:, (H + Hkv) * d:].reshape(B, n, kv)
@@ -565,6 +605,9 @@ class LlamaModel(nn.Module):
                 yield pre + "self_attn.q_proj.bias", l.qkv_bias, slice(0, q)
                 yield pre + "self_attn.k_proj.bias", l.qkv_bias, slice(q, q + kv)
                 yield pre + "self_attn.v_proj.bias", l.qkv_bias, slice(q + kv, q + 2 * kv)
+            if cfg.qk_norm:
+                yield pre + "self_attn.q_norm.weight", l.q_norm, None
+                yield pre + "self_attn.k_norm.weight", l.k_norm, None
             yield pre + "self_attn.o_proj.weight", l.o_proj, None
             yield pre + "post_attention_layernorm.weight", l.post_attention_layernorm, None
             if cfg.num_local_experts:      # Mixtral names: w1 = gate, w3 = up, w2 = down

@@ -56,13 +56,16 @@ _SIGS = {
     "b200_sm_count": [],
     "b200_segment_reduce": [_VP, _VP, _VP, _LL, _I, _I, _VP],
     "b200_gemm_reset_split_sync": [_VP],
+    "b200_headnorm_fwd": [_VP, _VP, _VP, _VP, _VP, _LL, _I, _I, _I, _LL, _F, _VP],
+    "b200_headnorm_bwd_blocks": [_LL, _I, _I],
+    "b200_headnorm_bwd": [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _I, _LL, _I, _I, _I, _LL, _VP],
 }
 
 
 # device kernels launched by one call of each exported launcher (default 1); used to count launches
 KERNELS_PER_CALL = {"b200_rmsnorm_bwd": 2, "b200_flash_attn_bwd": 3, "b200_head_num_tiles": 0, "b200_sm_count": 0,
                     "b200_rmsnorm_bwd_blocks": 0, "b200_last_cuda_error": 0, "b200_take_device_error": 0,
-                    "b200_gemm_reset_split_sync": 0}
+                    "b200_gemm_reset_split_sync": 0, "b200_headnorm_bwd_blocks": 0, "b200_headnorm_bwd": 2}
 LAUNCH_COUNT = [0]
 
 

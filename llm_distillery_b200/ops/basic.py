@@ -157,6 +157,56 @@ def rmsnorm_bwd(dy: torch.Tensor, h: torch.Tensor, w: torch.Tensor, rstd: torch.
     return dh, dw_out
 
 
+# ------------------------------------------------------------------------------------------------ per-head q/k norm
+def headnorm_fwd(qkv: torch.Tensor, wq: torch.Tensor, wk: torch.Tensor, n_q: int, n_kv: int, head_dim: int, eps: float):
+    """Per-head RMSNorm of the query and key heads of fused qkv rows [T, (n_q + 2 n_kv) d] (Qwen3's q_norm / k_norm,
+    applied before the rotary embedding); value heads are copied. Returns (normalised copy, rstd [T, n_q + n_kv])."""
+    T = qkv.shape[0]
+    nn = n_q + n_kv
+    if not _native(qkv):
+        x = qkv.float().view(T, n_q + 2 * n_kv, head_dim)
+        rstd = torch.rsqrt(x[:, :nn].pow(2).mean(-1) + eps)
+        w = torch.cat([wq.float().expand(n_q, -1), wk.float().expand(n_kv, -1)])          # [nn, d]
+        y = x.clone()
+        y[:, :nn] = x[:, :nn] * rstd[..., None] * w
+        return y.view(T, -1).to(qkv.dtype), rstd
+    out = torch.empty_like(qkv)
+    rstd = torch.empty((T, nn), dtype=torch.float32, device=qkv.device)
+    _lib.check(_lib.kernels().b200_headnorm_fwd(_lib.ptr(qkv), _lib.ptr(out), _lib.ptr(wq), _lib.ptr(wk), _lib.ptr(rstd),
+                                                T, n_q, n_kv, head_dim, qkv.stride(0), float(eps), _lib.stream()),
+               "b200_headnorm_fwd")
+    return out, rstd
+
+
+def headnorm_bwd_(g: torch.Tensor, qkv_raw: torch.Tensor, wq: torch.Tensor, wk: torch.Tensor, rstd: torch.Tensor,
+                  n_q: int, n_kv: int, head_dim: int):
+    """Backward of ``headnorm_fwd`` in place on ``g`` (gradient of the normalised rows; value heads untouched).
+    Returns (dwq, dwk) fp32 [d] each."""
+    T = g.shape[0]
+    nn = n_q + n_kv
+    if not _native(g):
+        gv = g.float().view(T, n_q + 2 * n_kv, head_dim)
+        x = qkv_raw.float().view(T, n_q + 2 * n_kv, head_dim)[:, :nn]
+        w = torch.cat([wq.float().expand(n_q, -1), wk.float().expand(n_kv, -1)])
+        xh = x * rstd[..., None]
+        gy = gv[:, :nn]
+        gw = gy * w
+        c = (gw * xh).mean(-1, keepdim=True)
+        dx = rstd[..., None] * (gw - xh * c)
+        dw = (gy * xh).sum(0)                                                             # [nn, d]
+        out = gv.clone()
+        out[:, :nn] = dx
+        g.copy_(out.view(T, -1).to(g.dtype))
+        return dw[:n_q].sum(0), dw[n_q:].sum(0)
+    nblk = _lib.kernels().b200_headnorm_bwd_blocks(T, n_q, n_kv)
+    partial = torch.empty((nblk, 2 * head_dim), dtype=torch.float32, device=g.device)
+    dw = torch.empty(2 * head_dim, dtype=torch.float32, device=g.device)
+    _lib.check(_lib.kernels().b200_headnorm_bwd(_lib.ptr(g), _lib.ptr(qkv_raw), _lib.ptr(wq), _lib.ptr(wk), _lib.ptr(rstd),
+                                                _lib.ptr(partial), _lib.ptr(dw), 0, T, n_q, n_kv, head_dim, g.stride(0),
+                                                _lib.stream()), "b200_headnorm_bwd")
+    return dw[:head_dim], dw[head_dim:]
+
+
 # ------------------------------------------------------------------------------------------------ RoPE
 def rope_tables(max_pos: int, head_dim: int, theta: float, device, scaling: dict | None = None,
                 model_max_pos: int | None = None) -> tuple[torch.Tensor, torch.Tensor]:

@@ -112,3 +112,29 @@ def test_bias_add_and_grad(T, N):
     assert torch.allclose(acc, r + 2.0, atol=2e-3 * T ** 0.5, rtol=1e-3)
     basic.bias_grad(dy, out=acc, accumulate=False)
     assert torch.allclose(acc, r, atol=2e-3 * T ** 0.5, rtol=1e-3)
+
+
+@pytest.mark.parametrize("T,H,Hkv,d", [(37, 4, 2, 64), (1000, 8, 2, 128), (5000, 16, 4, 128), (3, 2, 1, 64)])
+def test_per_head_qk_norm_fwd_bwd(T, H, Hkv, d):
+    """Qwen3's q_norm / k_norm on fused qkv rows: kernels against the fp32 restatement of the same function."""
+    torch.manual_seed(T + d)
+    cols = (H + 2 * Hkv) * d
+    qkv = torch.randn(T, cols, device=DEV).bfloat16()
+    wq = (1 + 0.2 * torch.randn(d, device=DEV)).bfloat16()
+    wk = (1 + 0.2 * torch.randn(d, device=DEV)).bfloat16()
+    y, rstd = basic.headnorm_fwd(qkv, wq, wk, H, Hkv, d, 1e-6)
+    y_ref, rstd_ref = _cpu(basic.headnorm_fwd, qkv.float(), wq.float(), wk.float(), H, Hkv, d, 1e-6)
+    assert torch.allclose(rstd.cpu(), rstd_ref, rtol=1e-4, atol=1e-5)
+    assert torch.allclose(y.float().cpu(), y_ref, atol=3e-2, rtol=2e-2)
+    assert torch.equal(y[:, (H + Hkv) * d:], qkv[:, (H + Hkv) * d:])          # value heads are copied bit for bit
+    g = torch.randn(T, cols, device=DEV).bfloat16()
+    g_ref = g.float().cpu().clone()
+    g_in = g.clone()
+    dwq, dwk = basic.headnorm_bwd_(g, qkv, wq, wk, rstd, H, Hkv, d)
+    dwq_ref, dwk_ref = basic.headnorm_bwd_(g_ref, qkv.float().cpu(), wq.float().cpu(), wk.float().cpu(), rstd.cpu(), H, Hkv, d)
+    assert torch.allclose(g.float().cpu(), g_ref, atol=4e-2, rtol=3e-2)
+    assert torch.equal(g[:, (H + Hkv) * d:], g_in[:, (H + Hkv) * d:])
+    scale = max(1.0, float(dwq_ref.abs().max()))
+    assert torch.allclose(dwq.cpu(), dwq_ref, atol=2e-2 * scale, rtol=2e-2)
+    assert torch.allclose(dwk.cpu(), dwk_ref, atol=2e-2 * scale, rtol=2e-2)
+    assert _lib.take_device_error() == 0

@@ -135,3 +135,51 @@ def test_yarn_rope_scaling_and_explicit_head_dim_match_huggingface():
     assert torch.allclose(m2(x2), hf2(x2).logits, atol=3e-4, rtol=1e-3)
     with pytest.raises(NotImplementedError):
         LlamaConfig.from_hf_dict(dict(_base(), model_type="llama", head_dim=20))
+
+
+def test_qwen3_head_norms_match_huggingface(tmp_path):
+    """Qwen3: no projection bias, RMSNorm over every query and key head before the rotation, explicit head_dim."""
+    d = dict(_base(), model_type="qwen3", head_dim=32, use_sliding_window=False, attention_bias=False)
+    cfg = LlamaConfig.from_hf_dict(d)
+    assert cfg.qk_norm and cfg.head_dim == 32 and not cfg.attention_bias
+    model = build_model(cfg, dtype=torch.float32, device="cpu", seed=6)
+    with torch.no_grad():
+        for l in model.layers:
+            l.q_norm.uniform_(0.5, 1.5)
+            l.k_norm.uniform_(0.5, 1.5)
+    hf = tr.Qwen3ForCausalLM(tr.Qwen3Config(**_base(), head_dim=32, attn_implementation="eager", tie_word_embeddings=False,
+                                            use_sliding_window=False, attention_bias=False)).float()
+    res = hf.load_state_dict({k: v.clone() for k, v in model.to_hf_state_dict().items()}, strict=False)
+    assert not res.unexpected_keys and not [k for k in res.missing_keys if "rotary" not in k], res
+    x = torch.randint(0, 320, (2, 48))
+    ours, ref = model(x), hf(x).logits
+    assert torch.allclose(ours, ref, atol=3e-4, rtol=1e-3), (ours - ref).abs().max()
+    tgt = torch.randint(0, 320, (2 * 48,))
+    torch.nn.functional.cross_entropy(ours.reshape(-1, 320), tgt).backward()
+    torch.nn.functional.cross_entropy(ref.reshape(-1, 320), tgt).backward()
+    hf_grads = {n: p.grad for n, p in hf.named_parameters()}
+    for n, p, sl in model.named_hf_parameters():
+        g = p.grad if sl is None else p.grad[sl]
+        assert torch.allclose(g, hf_grads[n], atol=2e-5, rtol=2e-3), (n, (g - hf_grads[n]).abs().max())
+    # gradient checkpointing and the chunked inference path take the same norms
+    g0 = {n: p.grad.clone() for n, p in model.named_parameters()}
+    model.zero_grad()
+    model.grad_checkpointing = True
+    torch.nn.functional.cross_entropy(model(x).reshape(-1, 320), tgt).backward()
+    for n, p in model.named_parameters():
+        assert torch.allclose(p.grad, g0[n], atol=1e-6, rtol=1e-5), n
+    with torch.no_grad():
+        assert torch.allclose(model.hidden_states(x), model.hidden_states_chunked(x, 16), atol=2e-5, rtol=1e-4)
+    # both checkpoint directions
+    save_hf_model(model, str(tmp_path / "ours"))
+    c = json.load(open(tmp_path / "ours" / "config.json"))
+    assert c["model_type"] == "qwen3" and c["architectures"] == ["Qwen3ForCausalLM"] and c["head_dim"] == 32
+    hf2 = tr.AutoModelForCausalLM.from_pretrained(str(tmp_path / "ours"), dtype=torch.float32, attn_implementation="eager")
+    assert torch.allclose(hf2(x).logits, ref, atol=3e-4, rtol=1e-3)
+    hf.save_pretrained(str(tmp_path / "theirs"), safe_serialization=True)
+    back = load_hf_model(str(tmp_path / "theirs"), dtype=torch.float32)
+    assert back.cfg.qk_norm and torch.allclose(back(x), ref, atol=3e-4, rtol=1e-3)
+    with pytest.raises(NotImplementedError):
+        load_tp_weights(str(tmp_path / "theirs"), 0, 2, dtype=torch.float32)
+    with pytest.raises(NotImplementedError):
+        LlamaConfig.from_hf_dict(dict(d, num_experts=8))
