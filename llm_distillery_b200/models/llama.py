@@ -42,6 +42,7 @@ class LlamaConfig:
                                       # | mixtral (sparse mixture of experts, models/moe.py)
     num_local_experts: int = 0        # > 0: every layer's MLP is that many SwiGLU experts behind a linear router
     num_experts_per_tok: int = 2
+    moe_renormalize: bool = True      # router weights renormalised over the chosen experts (Mixtral; Qwen3-MoE norm_topk_prob)
     attention_bias: bool = False      # bias on the q/k/v projections (Qwen2 family); o_proj and the MLP have none
     rope_scaling: dict | None = None  # HuggingFace dict; types default / linear / llama3 / yarn (ops.basic.rope_tables)
     head_dim_override: int | None = None   # HuggingFace ``head_dim`` when it is not hidden_size / num_attention_heads
@@ -88,11 +89,18 @@ class LlamaConfig:
         hd = d.pop("head_dim_override")
         if hd:
             d["head_dim"] = hd
+        renorm = d.pop("moe_renormalize")
         if not self.num_local_experts:
             d.pop("num_local_experts")
             d.pop("num_experts_per_tok")
         qk = d.pop("qk_norm")
-        if self.model_type == "qwen3":
+        if self.model_type == "qwen3_moe":      # HuggingFace's names: num_experts, moe_intermediate_size, norm_topk_prob
+            d.update(architectures=["Qwen3MoeForCausalLM"], hidden_act="silu", torch_dtype="bfloat16",
+                     use_sliding_window=False, head_dim=self.head_dim, num_experts=d.pop("num_local_experts"),
+                     moe_intermediate_size=self.intermediate_size, norm_topk_prob=bool(renorm), decoder_sparse_step=1,
+                     mlp_only_layers=[])
+            d["intermediate_size"] = extra.pop("dense_intermediate_size", self.intermediate_size)
+        elif self.model_type == "qwen3":
             d.update(architectures=["Qwen3ForCausalLM"], hidden_act="silu", torch_dtype="bfloat16",
                      use_sliding_window=False, head_dim=self.head_dim)
         elif self.model_type == "mixtral":
@@ -113,21 +121,44 @@ class LlamaConfig:
                      attention_bias=False, mlp_bias=False)
         return {**extra, **d}
 
-    _KNOWN_TYPES = ("llama", "mistral", "qwen2", "phi3", "mixtral", "qwen3")
+    _KNOWN_TYPES = ("llama", "mistral", "qwen2", "phi3", "mixtral", "qwen3", "qwen3_moe")
 
     @classmethod
     def from_hf_dict(cls, d: dict) -> "LlamaConfig":
         keys = {f for f in cls.__dataclass_fields__} - {"extra"}
         kw = {k: v for k, v in d.items() if k in keys}
         mt = d.get("model_type", "llama")
+        rp = d.get("rope_parameters")
+        if isinstance(rp, dict):       # newer HuggingFace releases write theta and the scaling keys into one dict
+            if rp.get("rope_theta") is not None and d.get("rope_theta") is None:
+                kw["rope_theta"] = float(rp["rope_theta"])
+            if rp.get("rope_type", rp.get("type")) not in (None, "default") and not d.get("rope_scaling"):
+                kw["rope_scaling"] = {k: v for k, v in rp.items() if k != "rope_theta"}
+        for k in ("bos_token_id", "eos_token_id"):
+            if k in kw and kw[k] is None:
+                kw.pop(k)
         if mt not in cls._KNOWN_TYPES:
             raise NotImplementedError(f"model_type {mt!r}: only Llama-shaped decoders are built {cls._KNOWN_TYPES}")
         if mt == "qwen3" and d.get("num_experts"):
-            raise NotImplementedError("qwen3 mixture-of-experts checkpoints are not built (dense qwen3 and mixtral are)")
+            raise NotImplementedError("experts in a config of model_type qwen3: the mixture-of-experts type is qwen3_moe")
+        dense_ffn = None
+        if mt == "qwen3_moe":
+            if int(d.get("decoder_sparse_step", 1) or 1) != 1 or d.get("mlp_only_layers"):
+                raise NotImplementedError("qwen3_moe with dense layers between the sparse ones is not built")
+            n_exp = int(d.get("num_experts") or d.get("num_local_experts") or 0)
+            if n_exp < 1 or not d.get("moe_intermediate_size"):
+                raise ValueError("a qwen3_moe config needs num_experts and moe_intermediate_size")
+            dense_ffn = d.get("intermediate_size")
+            kw.update(num_local_experts=n_exp, intermediate_size=int(d["moe_intermediate_size"]),
+                      moe_renormalize=bool(d.get("norm_topk_prob", False)), qk_norm=True)
+            if kw.get("attention_bias"):
+                raise NotImplementedError("qwen3_moe with attention_bias also puts a bias on o_proj, which is not built")
+            if not d.get("use_sliding_window", False):
+                kw["sliding_window"] = None
         if mt == "mixtral":
             if int(kw.get("num_local_experts") or 0) < 1:
                 raise ValueError("a mixtral config needs num_local_experts")
-        elif kw.get("num_local_experts"):
+        elif kw.get("num_local_experts") and mt != "qwen3_moe":
             raise NotImplementedError(f"experts on model_type {mt!r} are not built (mixtral is)")
         if mt == "qwen3":
             kw["qk_norm"] = True
@@ -160,8 +191,12 @@ class LlamaConfig:
             kind = cfg.rope_scaling.get("rope_type", cfg.rope_scaling.get("type"))
             if kind not in (None, "default", "linear", "llama3", "yarn"):
                 raise NotImplementedError(f"rope_scaling type {kind!r} is not built (default, linear, llama3 and yarn are)")
-        generated = {"architectures", "hidden_act", "torch_dtype", "mlp_bias", "use_sliding_window", "head_dim"}
+        generated = {"architectures", "hidden_act", "torch_dtype", "mlp_bias", "use_sliding_window", "head_dim",
+                     "num_experts", "moe_intermediate_size", "norm_topk_prob", "decoder_sparse_step", "mlp_only_layers",
+                     "rope_parameters"}
         cfg.extra = {k: v for k, v in d.items() if k not in keys and k not in generated}
+        if dense_ffn is not None:
+            cfg.extra["dense_intermediate_size"] = dense_ffn
         return cfg
 
     @classmethod
@@ -513,10 +548,11 @@ class LlamaModel(nn.Module):
             if cfg.num_local_experts:
                 from .moe import AttnBlockFn, MoEBlockFn
                 h = AttnBlockFn.apply(h, pos, cos, sin, layer.input_layernorm, layer.qkv_proj, layer.o_proj, meta,
-                                      getattr(layer, "qkv_bias", None))
+                                      getattr(layer, "qkv_bias", None), getattr(layer, "q_norm", None),
+                                      getattr(layer, "k_norm", None))
                 h = MoEBlockFn.apply(h, layer.post_attention_layernorm, layer.router, layer.gate_up_proj,
                                      layer.down_proj, (cfg.rms_norm_eps, cfg.num_experts_per_tok, meta[6],
-                                                       layer.input_layernorm))
+                                                       layer.input_layernorm, cfg.moe_renormalize))
                 continue
             h = DecoderLayerFn.apply(h, pos, cos, sin, layer.input_layernorm, layer.qkv_proj, layer.o_proj,
                                      layer.post_attention_layernorm, layer.gate_up_proj, layer.down_proj, meta,
@@ -568,7 +604,8 @@ class LlamaModel(nn.Module):
                 n2, _, _ = basic.rmsnorm_fwd(h1, layer.post_attention_layernorm, cfg.rms_norm_eps)
                 if cfg.num_local_experts:
                     from .moe import moe_mlp
-                    h = h1 + moe_mlp(n2, layer.router, layer.gate_up_proj, layer.down_proj, cfg.num_experts_per_tok)
+                    h = h1 + moe_mlp(n2, layer.router, layer.gate_up_proj, layer.down_proj, cfg.num_experts_per_tok,
+                                     cfg.moe_renormalize)
                     continue
                 act = basic.swiglu_fwd(basic.linear_fwd(n2, layer.gate_up_proj))
                 h = basic.linear_fwd(act, layer.down_proj, residual=h1)
@@ -610,6 +647,14 @@ class LlamaModel(nn.Module):
                 yield pre + "self_attn.k_norm.weight", l.k_norm, None
             yield pre + "self_attn.o_proj.weight", l.o_proj, None
             yield pre + "post_attention_layernorm.weight", l.post_attention_layernorm, None
+            if cfg.num_local_experts and cfg.model_type == "qwen3_moe":
+                yield pre + "mlp.gate.weight", l.router, None
+                for e in range(cfg.num_local_experts):
+                    ex = pre + f"mlp.experts.{e}."
+                    yield ex + "gate_proj.weight", l.gate_up_proj, (e, slice(0, f))
+                    yield ex + "up_proj.weight", l.gate_up_proj, (e, slice(f, 2 * f))
+                    yield ex + "down_proj.weight", l.down_proj, (e,)
+                continue
             if cfg.num_local_experts:      # Mixtral names: w1 = gate, w3 = up, w2 = down
                 yield pre + "block_sparse_moe.gate.weight", l.router, None
                 for e in range(cfg.num_local_experts):
@@ -674,19 +719,22 @@ class LlamaModel(nn.Module):
         [E, 2f, h], ``mlp.experts.down_proj`` [E, h, f], router ``mlp.gate.weight``); the published checkpoints - and
         this model's own names - list them per expert under ``block_sparse_moe``."""
         f = self.cfg.intermediate_size
+        qwen = self.cfg.model_type == "qwen3_moe"
+        block = "mlp." if qwen else "block_sparse_moe."
+        gate_n, up_n, down_n = ("gate_proj", "up_proj", "down_proj") if qwen else ("w1", "w3", "w2")
         out = {}
         for k, v in sd.items():
             if k.endswith("mlp.gate.weight"):
-                out[k.replace("mlp.gate.weight", "block_sparse_moe.gate.weight")] = v
+                out[k.replace("mlp.gate.weight", block + "gate.weight")] = v
             elif k.endswith("mlp.experts.gate_up_proj"):
-                pre = k[: -len("mlp.experts.gate_up_proj")] + "block_sparse_moe.experts."
+                pre = k[: -len("mlp.experts.gate_up_proj")] + block + "experts."
                 for e in range(v.shape[0]):
-                    out[f"{pre}{e}.w1.weight"] = v[e, :f]
-                    out[f"{pre}{e}.w3.weight"] = v[e, f:]
+                    out[f"{pre}{e}.{gate_n}.weight"] = v[e, :f]
+                    out[f"{pre}{e}.{up_n}.weight"] = v[e, f:]
             elif k.endswith("mlp.experts.down_proj"):
-                pre = k[: -len("mlp.experts.down_proj")] + "block_sparse_moe.experts."
+                pre = k[: -len("mlp.experts.down_proj")] + block + "experts."
                 for e in range(v.shape[0]):
-                    out[f"{pre}{e}.w2.weight"] = v[e]
+                    out[f"{pre}{e}.{down_n}.weight"] = v[e]
             else:
                 out[k] = v
         return out

@@ -20,13 +20,14 @@ from . import llama as _ll
 
 
 # ------------------------------------------------------------------------------------------------ routing
-def route(n2: torch.Tensor, w_router: torch.Tensor, k: int):
-    """Router of one layer: (probs [T,E] fp32, chosen experts [T,k] int64, their renormalised weights [T,k] fp32).
-    Logits are computed in the model's dtype and the softmax in fp32, as HuggingFace's Mixtral block does."""
+def route(n2: torch.Tensor, w_router: torch.Tensor, k: int, renorm: bool = True):
+    """Router of one layer: (probs [T,E] fp32, chosen experts [T,k] int64, their weights [T,k] fp32 - renormalised
+    over the chosen experts (Mixtral; Qwen3-MoE with ``norm_topk_prob``) or the plain softmax values).
+    Logits are computed in the model's dtype and the softmax in fp32, as HuggingFace's blocks do."""
     logits = F.linear(n2, w_router)
     probs = torch.softmax(logits.float(), dim=-1)
     top_p, top_e = torch.topk(probs, k, dim=-1)
-    return probs, top_e, top_p / top_p.sum(-1, keepdim=True)
+    return probs, top_e, (top_p / top_p.sum(-1, keepdim=True) if renorm else top_p)
 
 
 def permutation(top_e: torch.Tensor, n_experts: int):
@@ -60,10 +61,11 @@ def experts_forward(x_perm: torch.Tensor, counts: list[int], w_gu: torch.Tensor,
     return gu, act, y
 
 
-def moe_mlp(n2: torch.Tensor, w_router: torch.Tensor, w_gu: torch.Tensor, w_d: torch.Tensor, k: int) -> torch.Tensor:
+def moe_mlp(n2: torch.Tensor, w_router: torch.Tensor, w_gu: torch.Tensor, w_d: torch.Tensor, k: int,
+            renorm: bool = True) -> torch.Tensor:
     """Inference-only expert half: sum_k weight * expert(n2) as [T, h] in n2's dtype."""
     T, h = n2.shape
-    _, top_e, top_w = route(n2, w_router, k)
+    _, top_e, top_w = route(n2, w_router, k, renorm)
     order, inverse, counts = permutation(top_e, w_gu.shape[0])
     x_perm = n2.index_select(0, torch.div(order, k, rounding_mode="floor"))
     _, _, y = experts_forward(x_perm, counts, w_gu, w_d)
@@ -76,12 +78,17 @@ class AttnBlockFn(torch.autograd.Function):
     """h1 = h + Attn(RMSNorm(h)): the attention half of ``llama.DecoderLayerFn`` as a node of its own."""
 
     @staticmethod
-    def forward(ctx, h, pos, cos, sin, w_ln1, w_qkv, w_o, meta, b_qkv=None):
+    def forward(ctx, h, pos, cos, sin, w_ln1, w_qkv, w_o, meta, b_qkv=None, w_qn=None, w_kn=None):
         B, L, H, Hkv, d, eps, recompute = meta
         n1, _, rstd1 = basic.rmsnorm_fwd(h, w_ln1, eps)
         qkv = basic.linear_fwd(n1, w_qkv)
         if b_qkv is not None:
             basic.bias_add_(qkv, b_qkv)
+        qk_saved = ()
+        if w_qn is not None:
+            qkv_raw = qkv
+            qkv, rstd_qk = basic.headnorm_fwd(qkv_raw, w_qn, w_kn, H, Hkv, d, eps)
+            qk_saved = (qkv_raw, rstd_qk)
         basic.rope_(qkv, pos, cos, sin, H + Hkv, d)
         att, lse = attention.attention_fwd(qkv, B, L, H, Hkv, d)
         h1 = basic.linear_fwd(att, w_o, residual=h)
@@ -90,10 +97,12 @@ class AttnBlockFn(torch.autograd.Function):
         ctx.slots = tuple(_ll._slot(w) for w in ctx.weights)
         ctx.b_qkv = b_qkv
         ctx.b_slot = _ll._slot(b_qkv) if b_qkv is not None else None
+        ctx.qk_w = (w_qn, w_kn)
+        ctx.qk_slots = (_ll._slot(w_qn), _ll._slot(w_kn)) if w_qn is not None else (None, None)
         if recompute:
             ctx.save_for_backward(h, pos, cos, sin)
         else:
-            ctx.save_for_backward(h, pos, cos, sin, rstd1, n1, qkv, att, lse)
+            ctx.save_for_backward(h, pos, cos, sin, rstd1, n1, qkv, att, lse, *qk_saved)
         return h1
 
     @staticmethod
@@ -101,14 +110,21 @@ class AttnBlockFn(torch.autograd.Function):
         B, L, H, Hkv, d, eps, recompute = ctx.meta
         w_ln1, w_qkv, w_o = ctx.weights
         s_ln1, s_qkv, s_o = ctx.slots
+        w_qn, w_kn = ctx.qk_w
+        qkv_raw = rstd_qk = None
         if recompute:
             h, pos, cos, sin = ctx.saved_tensors
             n1, _, rstd1 = basic.rmsnorm_fwd(h, w_ln1, eps)
             qkv = basic.linear_fwd(n1, w_qkv)
             if ctx.b_qkv is not None:
                 basic.bias_add_(qkv, ctx.b_qkv)
+            if w_qn is not None:
+                qkv_raw = qkv
+                qkv, rstd_qk = basic.headnorm_fwd(qkv_raw, w_qn, w_kn, H, Hkv, d, eps)
             basic.rope_(qkv, pos, cos, sin, H + Hkv, d)
             att, lse = attention.attention_fwd(qkv, B, L, H, Hkv, d)
+        elif w_qn is not None:
+            h, pos, cos, sin, rstd1, n1, qkv, att, lse, qkv_raw, rstd_qk = ctx.saved_tensors
         else:
             h, pos, cos, sin, rstd1, n1, qkv, att, lse = ctx.saved_tensors
         dh1 = dh1.contiguous()
@@ -117,6 +133,11 @@ class AttnBlockFn(torch.autograd.Function):
         dqkv = attention.attention_bwd(datt, qkv, att, lse, B, L, H, Hkv, d)
         del datt
         basic.rope_(dqkv, pos, cos, sin, H + Hkv, d, inverse=True)
+        g_qn = g_kn = None
+        if w_qn is not None:
+            dwq, dwk = basic.headnorm_bwd_(dqkv, qkv_raw, w_qn, w_kn, rstd_qk, H, Hkv, d)
+            g_qn = _ll._vec_grad(dwq, w_qn, ctx.qk_slots[0])
+            g_kn = _ll._vec_grad(dwk, w_kn, ctx.qk_slots[1])
         g_b = None
         if ctx.b_qkv is not None and ctx.b_qkv.requires_grad:
             if ctx.b_slot is not None:
@@ -131,7 +152,7 @@ class AttnBlockFn(torch.autograd.Function):
         g_ln1 = _ll._vec_grad(dw1, w_ln1, s_ln1)
         if _ll.LAYER_BACKWARD_DONE[0] is not None:      # the layer's first parameter: all of its gradients are final
             _ll.LAYER_BACKWARD_DONE[0](w_ln1)
-        return dh, None, None, None, g_ln1, g_qkv, g_o, None, g_b
+        return dh, None, None, None, g_ln1, g_qkv, g_o, None, g_b, g_qn, g_kn
 
 
 def _expert_wgrad(dy, x, w, slot, e, first):
@@ -150,10 +171,10 @@ class MoEBlockFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, h1, w_ln2, w_router, w_gu, w_d, meta):
-        eps, k, recompute, _first = meta
+        eps, k, recompute, _first, renorm = meta
         T, hdim = h1.shape
         n2, _, rstd2 = basic.rmsnorm_fwd(h1, w_ln2, eps)
-        probs, top_e, top_w = route(n2, w_router, k)
+        probs, top_e, top_w = route(n2, w_router, k, renorm)
         order, inverse, counts = permutation(top_e, w_gu.shape[0])
         tok = torch.div(order, k, rounding_mode="floor")
         x_perm = n2.index_select(0, tok)
@@ -172,7 +193,7 @@ class MoEBlockFn(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dh2):
-        eps, k, recompute, first_param = ctx.meta
+        eps, k, recompute, first_param, renorm = ctx.meta
         counts = ctx.counts
         w_ln2, w_router, w_gu, w_d = ctx.weights
         s_ln2, s_router, s_gu, s_d = ctx.slots
@@ -183,7 +204,7 @@ class MoEBlockFn(torch.autograd.Function):
             n2, _, rstd2 = basic.rmsnorm_fwd(h1, w_ln2, eps)
             probs = torch.softmax(F.linear(n2, w_router).float(), dim=-1)
             top_p = probs.gather(1, top_e)
-            top_w = top_p / top_p.sum(-1, keepdim=True)
+            top_w = top_p / top_p.sum(-1, keepdim=True) if renorm else top_p
             tok = torch.div(order, k, rounding_mode="floor")
             gu, act, y = experts_forward(n2.index_select(0, tok), counts, w_gu, w_d)
         else:
@@ -227,10 +248,12 @@ class MoEBlockFn(torch.autograd.Function):
             o += c
         del dgu
         dn2 = dx_perm.index_select(0, inverse).view(T, k, hdim).float().sum(1)
-        # router: w = p_sel / sum(p_sel), p = softmax(logits)
-        top_p = probs.gather(1, top_e)
-        ssum = top_p.sum(-1, keepdim=True)
-        d_top_p = (d_top_w - (d_top_w * top_w).sum(-1, keepdim=True)) / ssum
+        # router: w = p_sel / sum(p_sel) (or w = p_sel without renormalisation), p = softmax(logits)
+        if renorm:
+            ssum = probs.gather(1, top_e).sum(-1, keepdim=True)
+            d_top_p = (d_top_w - (d_top_w * top_w).sum(-1, keepdim=True)) / ssum
+        else:
+            d_top_p = d_top_w
         d_probs = torch.zeros_like(probs).scatter_(1, top_e, d_top_p)
         d_logits = probs * (d_probs - (d_probs * probs).sum(-1, keepdim=True))         # [T, E] fp32
         dn2 = dn2 + d_logits @ w_router.float()

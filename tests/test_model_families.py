@@ -183,3 +183,17 @@ def test_qwen3_head_norms_match_huggingface(tmp_path):
         load_tp_weights(str(tmp_path / "theirs"), 0, 2, dtype=torch.float32)
     with pytest.raises(NotImplementedError):
         LlamaConfig.from_hf_dict(dict(d, num_experts=8))
+
+
+def test_rope_parameters_dict_of_newer_huggingface_configs_is_read(tmp_path):
+    """transformers 5 writes ``rope_parameters = {rope_theta, rope_type, ...}`` instead of ``rope_theta`` / ``rope_scaling``."""
+    hf_cfg = tr.LlamaConfig(**_base(rope_theta=500000.0), rope_scaling=dict(ROPE3), attn_implementation="eager",
+                            tie_word_embeddings=False)
+    hf = tr.LlamaForCausalLM(hf_cfg).float()
+    hf.save_pretrained(str(tmp_path / "m"), safe_serialization=True)
+    saved = json.load(open(tmp_path / "m" / "config.json"))
+    back = load_hf_model(str(tmp_path / "m"), dtype=torch.float32)
+    assert back.cfg.rope_theta == 500000.0
+    assert (back.cfg.rope_scaling or {}).get("rope_type") == "llama3", (saved, back.cfg.rope_scaling)
+    x = torch.randint(0, 320, (1, 150))
+    assert torch.allclose(back(x), hf(x).logits, atol=3e-4, rtol=1e-3)
