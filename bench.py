@@ -44,7 +44,7 @@ def parse_args():
     ap.add_argument("--temperature", type=float, default=2.0)
     ap.add_argument("--loss", type=str, default="kl")
     ap.add_argument("--comm", type=str, default="p2p", choices=["p2p", "nccl"])
-    ap.add_argument("--grad-accum", type=int, default=1, help="micro-batches per optimizer step (ours only)")
+    ap.add_argument("--grad-accum", type=int, default=1, help="micro-batches per optimizer step")
     ap.add_argument("--shard", type=str, default="ddp", choices=["ddp", "fsdp", "zero3"],
                     help="ddp/fsdp: weights replicated (fsdp shards the optimizer state); zero3: weights and gradients sharded too")
     ap.add_argument("--skip-e2e", action="store_true")

@@ -264,8 +264,6 @@ def load_tp_weights(path: str, rank: int, tp: int, vocab: int | None = None, dty
                          "tensors. Collect with tp_size = 1 (the dequantised model fits one GPU) or export the "
                          "checkpoint to bf16 first.")
     cfg = LlamaConfig.from_pretrained(path)
-    if cfg.qk_norm:
-        raise NotImplementedError("tensor-parallel collection does not apply per-head q/k norms (qwen3): use tp_size = 1")
     if cfg.num_local_experts:
         raise NotImplementedError("tensor-parallel collection is built for dense decoders; a mixture-of-experts teacher "
                                   "runs with tp_size = 1 (ranks become data-parallel replicas)")
@@ -323,6 +321,9 @@ def load_tp_weights(path: str, rank: int, tp: int, vocab: int | None = None, dty
             w[p + "qkv_bias"] = torch.cat([sl(hp + "self_attn.q_proj.bias", rows=(rank * Hl * d, (rank + 1) * Hl * d)),
                                            sl(hp + "self_attn.k_proj.bias", rows=(rank * Hkvl * d, (rank + 1) * Hkvl * d)),
                                            sl(hp + "self_attn.v_proj.bias", rows=(rank * Hkvl * d, (rank + 1) * Hkvl * d))])
+        if cfg.qk_norm:          # one weight vector for all heads: replicated
+            w[p + "q_norm"] = sl(hp + "self_attn.q_norm.weight")
+            w[p + "k_norm"] = sl(hp + "self_attn.k_norm.weight")
         w[p + "o_proj"] = sl(hp + "self_attn.o_proj.weight", cols=(rank * Hl * d, (rank + 1) * Hl * d)).contiguous()
         w[p + "gate_up_proj"] = torch.cat([sl(hp + "mlp.gate_proj.weight", rows=(rank * fl, (rank + 1) * fl)),
                                            sl(hp + "mlp.up_proj.weight", rows=(rank * fl, (rank + 1) * fl))], 0)

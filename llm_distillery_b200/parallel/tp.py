@@ -237,6 +237,9 @@ def shard_llama_weights(cfg, sd: dict, rank: int, tp: int, vocab: int | None = N
             out[p + "qkv_bias"] = torch.cat([bq[: H * d][rank * Hl * d:(rank + 1) * Hl * d],
                                              bq[H * d:(H + Hkv) * d][rank * Hkvl * d:(rank + 1) * Hkvl * d],
                                              bq[(H + Hkv) * d:][rank * Hkvl * d:(rank + 1) * Hkvl * d]]).contiguous()
+        for nm in ("q_norm", "k_norm"):
+            if p + nm in sd:
+                out[p + nm] = sd[p + nm]
         out[p + "o_proj"] = sd[p + "o_proj"][:, rank * Hl * d:(rank + 1) * Hl * d].contiguous()
         gu = sd[p + "gate_up_proj"]
         out[p + "gate_up_proj"] = torch.cat([gu[rank * fl:(rank + 1) * fl], gu[f + rank * fl: f + (rank + 1) * fl]],
@@ -335,6 +338,8 @@ class TPLlama:
             qkv = g.ag_gemm(w[p + "qkv_proj"], T)
             if p + "qkv_bias" in w:
                 basic.bias_add_(qkv, w[p + "qkv_bias"])
+            if p + "q_norm" in w:      # per-head norms act inside a head: local under head sharding
+                qkv, _ = basic.headnorm_fwd(qkv, w[p + "q_norm"], w[p + "k_norm"], Hl, Hkvl, d, eps)
             basic.rope_(qkv, pos, cos, sin, Hl + Hkvl, d)
             att, _ = attention.attention_fwd(qkv, B, L, Hl, Hkvl, d)
             x = g.gemm_rs(att, w[p + "o_proj"], residual=x)

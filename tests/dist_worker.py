@@ -314,7 +314,15 @@ def _tp_model_check(dev, dtype, rank, world, k, atol):
         cfg.num_attention_heads = 2 * world
         cfg.num_key_value_heads = world
         cfg.hidden_size = 64 * cfg.num_attention_heads
+    if os.environ.get("TP_QKNORM") == "1":       # Qwen3-style per-head q/k norms: local to a head, so to a rank
+        cfg.qk_norm, cfg.model_type = True, "qwen3"
     full = build_model(cfg, dtype=dtype, device=dev, seed=11)
+    if cfg.qk_norm:
+        gq = torch.Generator().manual_seed(5)        # the same values on every rank
+        with torch.no_grad():
+            for l in full.layers:
+                l.q_norm.copy_(torch.empty(cfg.head_dim).uniform_(0.5, 1.5, generator=gq).to(dtype))
+                l.k_norm.copy_(torch.empty(cfg.head_dim).uniform_(0.5, 1.5, generator=gq).to(dtype))
     B = 2
     L = padded_seq_len(B, 100, world)
     g = torch.Generator().manual_seed(3)

@@ -148,6 +148,10 @@ def test_cpu_ranks_tensor_parallel_teacher_matches_unsharded():
     _launch("cpu_tp", 2)
 
 
+def test_cpu_ranks_tensor_parallel_teacher_with_per_head_qk_norms():
+    _launch("cpu_tp", 2, env={"TP_QKNORM": "1"})
+
+
 def test_cpu_ranks_vocabulary_parallel_head_matches_unsharded():
     _launch("cpu_vp_head", 2)
 

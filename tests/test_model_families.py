@@ -179,8 +179,8 @@ def test_qwen3_head_norms_match_huggingface(tmp_path):
     hf.save_pretrained(str(tmp_path / "theirs"), safe_serialization=True)
     back = load_hf_model(str(tmp_path / "theirs"), dtype=torch.float32)
     assert back.cfg.qk_norm and torch.allclose(back(x), ref, atol=3e-4, rtol=1e-3)
-    with pytest.raises(NotImplementedError):
-        load_tp_weights(str(tmp_path / "theirs"), 0, 2, dtype=torch.float32)
+    _, w0 = load_tp_weights(str(tmp_path / "theirs"), 0, 2, dtype=torch.float32)      # the norms are replicated
+    assert torch.equal(w0["layers.1.q_norm"], back.layers[1].q_norm.data) and w0["layers.0.k_norm"].shape == (32,)
     with pytest.raises(NotImplementedError):
         LlamaConfig.from_hf_dict(dict(d, num_experts=8))
 
