@@ -235,7 +235,7 @@ def main() -> int:
 
     # ---------------- what the gradient exchange leaves exposed: device time from the end of backward to the end of
     # the step (reduce + optimizer + weight all-gather), a few extra steps with the phase timer on, max over ranks
-    exposed = None
+    exposed = exchange = None
     if args.impl == "ours" and hasattr(runner, "device_step"):
         eng.timer.enabled = True
         barrier()                       # rank 0 comes late from stopping the clock sampler: without this its peers
@@ -243,15 +243,21 @@ def main() -> int:
         barrier()
         eng.timer.summary()
         n_probe = 3
+        if comm is not None and hasattr(comm, "time_exchange"):
+            comm.time_exchange = True
         for i in range(n_probe):
             runner.device_step(dev_pool[i % 2])
         barrier()
         phases = eng.timer.summary()
         eng.timer.enabled = False
-        t = torch.tensor([phases.get("reduce+optimizer", 0.0) / n_probe], device=dev)
+        xms = comm.exchange_ms() if comm is not None and hasattr(comm, "exchange_ms") else None
+        if comm is not None and hasattr(comm, "time_exchange"):
+            comm.time_exchange = False
+        t = torch.tensor([phases.get("reduce+optimizer", 0.0) / n_probe, -1.0 if xms is None else xms], device=dev)
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        exposed = float(t.item())
+        exposed = float(t[0].item())
+        exchange = None if float(t[1].item()) < 0 else float(t[1].item())
 
     # ---------------- teacher collection arm (second half of the metric): tokens in -> top-K rows in pinned host memory
     collect = None
@@ -310,7 +316,7 @@ def main() -> int:
                        "loss": f"{args.loss} T={args.temperature}", "topk": K,
                        "optimizer": "adamw (fp32 master + state)", "comm": args.comm if world > 1 else "none",
                        "l2": "no flush: each step streams ~2.2 GB of weights and >20 GB of activations, far above the 126 MB L2"},
-            "e2e": e2e, "exposed_comm_ms": exposed, "collect": collect, "gpu_launches": launches, "clocks": clocks, "final_loss": final_loss, "device_error": err,
+            "e2e": e2e, "exposed_comm_ms": exposed, "exchange_ms": exchange, "collect": collect, "gpu_launches": launches, "clocks": clocks, "final_loss": final_loss, "device_error": err,
         }
         print(json.dumps(out))
     if world > 1:

@@ -96,6 +96,10 @@ class P2PComm:
         self._rdv = torch.zeros(1, dtype=torch.float32, device=self.device)
         # optimizer steps issued by the host / steps whose reduction kernels really ran (a kernel behind a barrier
         # that gave up does nothing): the difference is what an emergency save must not claim
+        # set by a benchmark: two events per step bracket the exchange proper (from the moment every rank has arrived
+        # to the closing barrier), so that it can be told apart from the wait for the slowest rank before it
+        self.time_exchange = False
+        self._xev = None
         self.steps_issued = 0
         self._steps_applied = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.failed_step = False
@@ -279,6 +283,9 @@ class P2PComm:
             self._cast_wire(0, f.total)
         self.rendezvous()
         self.barrier()
+        if self.time_exchange:
+            self._xev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+            self._xev[0].record()
         if fused:
             opt.step_count += 1
             b1, b2 = opt.betas
@@ -295,3 +302,13 @@ class P2PComm:
             self.allgather(self.model_buf, f.model_shard(), f.shard_lo, skip_self=True)
         self._mark_step()
         self.barrier()
+        if self.time_exchange and self._xev is not None:
+            self._xev[1].record()
+
+    def exchange_ms(self) -> float | None:
+        """Device time of the latest step's exchange proper (reduce-scatter, update, all-gather, closing barrier) when
+        ``time_exchange`` was set; the bf16 wire cast and the wait for the slowest rank come before it. Synchronises."""
+        if self._xev is None:
+            return None
+        torch.cuda.synchronize(self.device)
+        return float(self._xev[0].elapsed_time(self._xev[1]))
