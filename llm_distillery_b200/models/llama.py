@@ -216,6 +216,8 @@ PRESETS = {
     "qwen2.5-0.5b": (24, 896, 14, 2, 4864, 151936, 1000000.0, 1e-6, True, 32768),
     "qwen2.5-1.5b": (28, 1536, 12, 2, 8960, 151936, 1000000.0, 1e-6, True, 32768),
     "qwen2.5-7b": (28, 3584, 28, 4, 18944, 152064, 1000000.0, 1e-6, False, 32768),
+    # Mixtral layout on TinyLlama's dimensions: 8 experts, 2 per token (6.4 B parameters, 1.3 B active per token)
+    "tinymixtral-8x1b": (22, 2048, 32, 4, 5632, 32000, 10000.0, 1e-5, False, 2048),
     "plumbing-teacher": (2, 256, 4, 4, 688, 32000, 10000.0, 1e-6, False, 2048),
     "plumbing-student": (4, 256, 4, 4, 688, 32000, 10000.0, 1e-6, False, 2048),
 }
@@ -226,6 +228,8 @@ def preset(name: str, **over) -> LlamaConfig:
     cfg = LlamaConfig(vocab_size=V, hidden_size=h, intermediate_size=f, num_hidden_layers=Lr, num_attention_heads=H,
                       num_key_value_heads=Hkv, rms_norm_eps=eps, rope_theta=theta, max_position_embeddings=mp,
                       tie_word_embeddings=tied)
+    if name.startswith("tinymixtral"):
+        cfg.model_type, cfg.num_local_experts, cfg.num_experts_per_tok = "mixtral", 8, 2
     if name.startswith("qwen2"):
         cfg.attention_bias, cfg.model_type = True, "qwen2"
     if name.startswith("llama-3.2"):      # the published Llama 3.2 configs scale the low rope frequencies
