@@ -189,8 +189,17 @@ class LlamaConfig:
         cfg = cls(**kw)
         if cfg.rope_scaling is not None:       # fail at load time, not at the first forward
             kind = cfg.rope_scaling.get("rope_type", cfg.rope_scaling.get("type"))
-            if kind not in (None, "default", "linear", "llama3", "yarn"):
-                raise NotImplementedError(f"rope_scaling type {kind!r} is not built (default, linear, llama3 and yarn are)")
+            if kind == "su":                # the name older Phi-3 configs use
+                kind = "longrope"
+                cfg.rope_scaling = {**{k: v for k, v in cfg.rope_scaling.items() if k not in ("type", "rope_type")},
+                                    "rope_type": "longrope"}
+            if kind not in (None, "default", "linear", "llama3", "yarn", "longrope"):
+                raise NotImplementedError(f"rope_scaling type {kind!r} is not built (default, linear, llama3, yarn and "
+                                          "longrope are)")
+            if kind == "longrope" and not cfg.rope_scaling.get("original_max_position_embeddings"):
+                orig = d.get("original_max_position_embeddings")
+                if orig:          # Phi-3 keeps it beside the dict
+                    cfg.rope_scaling = dict(cfg.rope_scaling, original_max_position_embeddings=int(orig))
         generated = {"architectures", "hidden_act", "torch_dtype", "mlp_bias", "use_sliding_window", "head_dim",
                      "num_experts", "moe_intermediate_size", "norm_topk_prob", "decoder_sparse_step", "mlp_only_layers",
                      "rope_parameters"}
@@ -520,10 +529,18 @@ class LlamaModel(nn.Module):
 
     def rope(self, device, max_pos: int | None = None):
         need = max_pos or self.cfg.max_position_embeddings
-        if self._rope is None or self._rope[0].device != torch.device(device) or self._rope[0].shape[0] < need:
+        sc = self.cfg.rope_scaling or {}
+        regime = None
+        if sc.get("rope_type", sc.get("type")) == "longrope":    # the factor set depends on the sequence length
+            regime = need > int(sc.get("original_max_position_embeddings") or self.cfg.max_position_embeddings)
+        if (self._rope is None or self._rope[0].device != torch.device(device) or self._rope[0].shape[0] < need
+                or getattr(self, "_rope_regime", None) != regime):
             n = max(need, min(self.cfg.max_position_embeddings, 8192))
+            if regime is False:
+                n = min(n, int(sc.get("original_max_position_embeddings") or n))
             self._rope = basic.rope_tables(n, self.cfg.head_dim, self.cfg.rope_theta, device, self.cfg.rope_scaling,
-                                           model_max_pos=self.cfg.max_position_embeddings)
+                                           model_max_pos=self.cfg.max_position_embeddings, seq_len=need)
+            self._rope_regime = regime
         return self._rope
 
     # ---- forward

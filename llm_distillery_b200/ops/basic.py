@@ -209,7 +209,7 @@ def headnorm_bwd_(g: torch.Tensor, qkv_raw: torch.Tensor, wq: torch.Tensor, wk: 
 
 # ------------------------------------------------------------------------------------------------ RoPE
 def rope_tables(max_pos: int, head_dim: int, theta: float, device, scaling: dict | None = None,
-                model_max_pos: int | None = None) -> tuple[torch.Tensor, torch.Tensor]:
+                model_max_pos: int | None = None, seq_len: int | None = None) -> tuple[torch.Tensor, torch.Tensor]:
     """fp32 cos/sin tables [max_pos, head_dim/2] (HF Llama convention: pairs (i, i + d/2)).
 
     ``scaling`` is a HuggingFace ``rope_scaling`` dict: ``llama3`` (Llama 3.1 / 3.2: low frequencies divided by
@@ -218,6 +218,9 @@ def rope_tables(max_pos: int, head_dim: int, theta: float, device, scaling: dict
     ``beta_slow`` times over the original context are interpolated by ``factor``, those that turn more than
     ``beta_fast`` times are kept, a linear ramp between; cos and sin carry the attention factor 0.1 ln(factor) + 1, or
     the ``mscale`` / ``mscale_all_dim`` ratio, or an explicit ``attention_factor``) are built; other types are refused.
+    ``longrope`` (Phi-3 long-context checkpoints) divides every frequency by its entry of ``short_factor``, or of
+    ``long_factor`` when the sequence (``seq_len``) is longer than the original context, and scales cos / sin by
+    sqrt(1 + ln(factor) / ln(original context)).
     ``model_max_pos`` is the model's ``max_position_embeddings`` (yarn's original context when the dict names none)."""
     import math
     inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32, device=device) / head_dim))
@@ -251,6 +254,21 @@ def rope_tables(max_pos: int, head_dim: int, theta: float, device, scaling: dict
             hi_d += 0.001
         ramp = ((torch.arange(head_dim // 2, dtype=torch.float32, device=device) - lo_d) / (hi_d - lo_d)).clamp(0, 1)
         inv = (inv / factor) * ramp + inv * (1.0 - ramp)
+    elif kind == "longrope":
+        orig = scaling.get("original_max_position_embeddings") or model_max_pos
+        if not orig or "short_factor" not in scaling or "long_factor" not in scaling:
+            raise ValueError("longrope scaling needs short_factor, long_factor and original_max_position_embeddings")
+        factor = scaling.get("factor")
+        factor = float(factor) if factor is not None else float(model_max_pos or orig) / float(orig)
+        amp = scaling.get("attention_factor")
+        if amp is None:
+            amp = 1.0 if factor <= 1.0 else math.sqrt(1.0 + math.log(factor) / math.log(orig))
+        amp = float(amp)
+        use_long = (seq_len if seq_len is not None else max_pos) > orig
+        ext = torch.tensor(scaling["long_factor" if use_long else "short_factor"], dtype=torch.float32, device=device)
+        if ext.numel() != inv.numel():
+            raise ValueError(f"longrope factors have {ext.numel()} entries, the head has {inv.numel()} frequency pairs")
+        inv = inv / ext
     elif kind == "linear":
         inv = inv / float(scaling["factor"])
     elif kind == "llama3":
@@ -262,7 +280,7 @@ def rope_tables(max_pos: int, head_dim: int, theta: float, device, scaling: dict
         blended = (1.0 - smooth) * inv / factor + smooth * inv
         inv = torch.where(wavelen > old / lo_f, inv / factor, torch.where(wavelen < old / hi_f, inv, blended))
     else:
-        raise NotImplementedError(f"rope_scaling type {kind!r} is not built (default, linear, llama3 and yarn are)")
+        raise NotImplementedError(f"rope_scaling type {kind!r} is not built (default, linear, llama3, yarn and longrope are)")
     ang = torch.arange(max_pos, dtype=torch.float32, device=device)[:, None] * inv[None, :]
     return (ang.cos() * amp).contiguous(), (ang.sin() * amp).contiguous()
 

@@ -310,10 +310,16 @@ class TPLlama:
         return cls(cfg, w, group)
 
     def rope(self, n: int):
+        sc = getattr(self.cfg, "rope_scaling", None) or {}
+        regime = None
+        if sc.get("rope_type", sc.get("type")) == "longrope":    # the factor set depends on the sequence length
+            regime = n > int(sc.get("original_max_position_embeddings") or self.cfg.max_position_embeddings)
+        if regime != getattr(self, "_rope_regime", None):
+            self._rope, self._rope_regime = None, regime
         if self._rope is None or self._rope[0].shape[0] < n:
             self._rope = basic.rope_tables(max(n, 2048), self.cfg.head_dim, self.cfg.rope_theta, self.device,
                                            getattr(self.cfg, "rope_scaling", None),
-                                           model_max_pos=self.cfg.max_position_embeddings)
+                                           model_max_pos=self.cfg.max_position_embeddings, seq_len=n)
         return self._rope
 
     @torch.no_grad()

@@ -38,7 +38,7 @@ def test_llama3_rope_scaling_matches_huggingface():
     c0, s0 = basic.rope_tables(128, 16, 10000.0, "cpu")
     assert torch.allclose(c1[4::4], c0[1:8], atol=1e-6) and torch.allclose(s1[4::4], s0[1:8], atol=1e-6)
     with pytest.raises(NotImplementedError):
-        basic.rope_tables(8, 16, 10000.0, "cpu", {"rope_type": "longrope", "factor": 2.0})
+        basic.rope_tables(8, 16, 10000.0, "cpu", {"rope_type": "dynamic", "factor": 2.0})
 
 
 def test_phi3_checkpoint_layout_matches_huggingface(tmp_path):
@@ -94,7 +94,7 @@ def test_config_keys_survive_a_round_trip_and_unbuilt_variants_are_refused(tmp_p
     with pytest.raises(ValueError, match="attention window"):
         model(torch.randint(0, 320, (1, 129)))
     for bad in (dict(model_type="gemma2"), dict(hidden_act="gelu_pytorch_tanh"), dict(head_dim=20),
-                dict(partial_rotary_factor=0.5), dict(rope_scaling={"rope_type": "longrope", "factor": 4.0}), dict(mlp_bias=True)):
+                dict(partial_rotary_factor=0.5), dict(rope_scaling={"rope_type": "dynamic", "factor": 4.0}), dict(mlp_bias=True)):
         with pytest.raises(NotImplementedError):
             LlamaConfig.from_hf_dict(dict(_base(), **bad))
     # Qwen2 carries a window that is switched off
@@ -197,3 +197,28 @@ def test_rope_parameters_dict_of_newer_huggingface_configs_is_read(tmp_path):
     assert (back.cfg.rope_scaling or {}).get("rope_type") == "llama3", (saved, back.cfg.rope_scaling)
     x = torch.randint(0, 320, (1, 150))
     assert torch.allclose(back(x), hf(x).logits, atol=3e-4, rtol=1e-3)
+
+
+def test_phi3_longrope_matches_huggingface():
+    """Phi-3 long-context checkpoints: per-frequency short / long factors chosen by the sequence length."""
+    torch.manual_seed(0)
+    short = (1.0 + 0.2 * torch.rand(8)).tolist()
+    long = (1.5 + 2.0 * torch.rand(8)).tolist()
+    scaling = {"type": "longrope", "short_factor": short, "long_factor": long}
+    d = dict(_base(max_position_embeddings=256), model_type="phi3", pad_token_id=0, rope_scaling=scaling,
+             original_max_position_embeddings=64)
+    cfg = LlamaConfig.from_hf_dict(d)
+    assert cfg.rope_scaling["original_max_position_embeddings"] == 64
+    model = build_model(cfg, dtype=torch.float32, device="cpu", seed=8)
+    hf_cfg = tr.Phi3Config(**_base(max_position_embeddings=256), pad_token_id=0, attn_implementation="eager",
+                           tie_word_embeddings=False, sliding_window=None, original_max_position_embeddings=64,
+                           rope_scaling=dict(scaling))
+    hf = tr.Phi3ForCausalLM(hf_cfg).float()
+    res = hf.load_state_dict({k: v.clone() for k, v in model.to_hf_state_dict().items()}, strict=False)
+    assert not res.unexpected_keys
+    for L in (48, 200, 40):          # short regime, long regime, short again (the cached tables must follow)
+        x = torch.randint(0, 320, (2, L))
+        ours, ref = model(x), hf(x).logits
+        assert torch.allclose(ours, ref, atol=4e-4, rtol=1e-3), (L, (ours - ref).abs().max())
+    same = LlamaConfig.from_hf_dict(dict(d, rope_scaling=dict(scaling, type="su")))
+    assert same.rope_scaling["rope_type"] == "longrope"
