@@ -26,6 +26,11 @@ CASES = {
     "bf16 on CPU": {"training_precision": "bf16"},
     "4bit: frozen NF4 decoder matrices": {"training_precision": "4bit"},
     "8bit: frozen int8 decoder matrices": {"training_precision": "8bit"},
+    # the combination the reference ships in its config.json (a router entry in freeze_layers matches nothing here)
+    "4bit with the reference's shipped optimizer, schedule and freeze list": {
+        "training_precision": "4bit", "optimizer": "adamw8bit", "lr_scheduler": "wsd", "decay_start": 0.9, "alpha": 2,
+        "freeze_layers": [".block_sparse_moe.gate"], "loss": "reference", "grad_accum_batches": 2,
+        "validate_every_n_epochs": 0.5},
     "shuffled, checkpointing, accumulation of 3": {"data_order": "shuffle", "grad_checkpointing": True, "grad_accum_batches": 3},
     "native order, context 48": {"data_order": "native", "context_len": 48},
     "top-K above the crop": {"save_topK": 600},
