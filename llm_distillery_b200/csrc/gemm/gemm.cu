@@ -245,6 +245,124 @@ struct EpiStore {
   }
 };
 
+// Fused gate / up projection + SwiGLU on the CTA-pair kernel. The accumulator of a tile holds, for 256 rows, the gate
+// (columns 0-127) and the up projection (columns 128-255) of the same 128 features (the B halves come from rows
+// j*128 and f + j*128 of the fused weight, gemm_pair.cuh). The epilogue writes three things per row: gate and up,
+// rounded to bf16, into gu [M, 2f] (the backward pass reads them), and act = silu(gate) * up computed from the ROUNDED
+// values, so that it equals what the stand-alone SwiGLU kernel makes of gu bit for bit. Each leaves through the
+// swizzled stage as 256-byte row segments.
+struct SwigluParams {
+  __nv_bfloat16* gu;    // [M, 2f]
+  long long ld_gu;
+  __nv_bfloat16* act;   // [M, f]
+  long long ld_act;
+  int f;
+};
+
+struct EpiSwiglu {
+  using Params = SwigluParams;
+  static constexpr bool SPLIT_K = false;
+  static constexpr int STAGE_BYTES = 32 * 256;
+  static constexpr int SMEM_BYTES = NUM_EPI_WARPS * STAGE_BYTES;
+
+  static __device__ __forceinline__ void flush(uint8_t* stage, __nv_bfloat16* dst, long long ld, int row0, int rows_valid,
+                                               int col0, int f, int lane) {
+    __syncwarp();
+    const int chunk = lane & 15;
+    const int col = col0 + chunk * 8;
+#pragma unroll 4
+    for (int j = 0; j < 16; ++j) {
+      const int row = 2 * j + (lane >> 4);
+      const uint4 o = *reinterpret_cast<const uint4*>(stage + row * 256 + ((chunk ^ (row & 15)) << 4));
+      if (row < rows_valid && col < f) *reinterpret_cast<uint4*>(dst + (long long)(row0 + row) * ld + col) = o;
+    }
+    __syncwarp();
+  }
+
+  static __device__ __forceinline__ void tile(const Params& p, uint32_t taddr, int m0, int n0, int M, int N, int quad,
+                                              int lane, uint8_t* epi_smem) {
+    uint8_t* stage = epi_smem + quad * STAGE_BYTES;
+    const int row0 = m0 + quad * 32;
+    const int rows_valid = min(32, M - row0);
+    const int col0 = (n0 / PAIR_BN) * PAIR_HALF_N;       // first of the tile's 128 features
+    // gate, then up: rounded copies into gu
+#pragma unroll 1
+    for (int half = 0; half < 2; ++half) {
+#pragma unroll 1
+      for (int c4 = 0; c4 < 4; ++c4) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(taddr + half * 128 + c4 * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint4 o;
+          o.x = pack_bf16x2(__uint_as_float(r[j * 8 + 0]), __uint_as_float(r[j * 8 + 1]));
+          o.y = pack_bf16x2(__uint_as_float(r[j * 8 + 2]), __uint_as_float(r[j * 8 + 3]));
+          o.z = pack_bf16x2(__uint_as_float(r[j * 8 + 4]), __uint_as_float(r[j * 8 + 5]));
+          o.w = pack_bf16x2(__uint_as_float(r[j * 8 + 6]), __uint_as_float(r[j * 8 + 7]));
+          const int chunk = c4 * 4 + j;
+          *reinterpret_cast<uint4*>(stage + lane * 256 + ((chunk ^ (lane & 15)) << 4)) = o;
+        }
+      }
+      flush(stage, p.gu + (half ? p.f : 0), p.ld_gu, row0, rows_valid, col0, p.f, lane);
+    }
+    // act = silu(gate) * up from the rounded values
+#pragma unroll 1
+    for (int c4 = 0; c4 < 4; ++c4) {
+      uint32_t g[32], u[32];
+      tmem_ld_32x32b_x32(taddr + c4 * 32, g);
+      tmem_ld_32x32b_x32(taddr + 128 + c4 * 32, u);
+      tmem_ld_wait();
+      float a[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const float gj = __bfloat162float(__float2bfloat16(__uint_as_float(g[j])));
+        const float uj = __bfloat162float(__float2bfloat16(__uint_as_float(u[j])));
+        a[j] = __fdividef(gj, 1.f + __expf(-gj)) * uj;
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint4 o;
+        o.x = pack_bf16x2(a[j * 8 + 0], a[j * 8 + 1]);
+        o.y = pack_bf16x2(a[j * 8 + 2], a[j * 8 + 3]);
+        o.z = pack_bf16x2(a[j * 8 + 4], a[j * 8 + 5]);
+        o.w = pack_bf16x2(a[j * 8 + 6], a[j * 8 + 7]);
+        const int chunk = c4 * 4 + j;
+        *reinterpret_cast<uint4*>(stage + lane * 256 + ((chunk ^ (lane & 15)) << 4)) = o;
+      }
+    }
+    flush(stage, p.act, p.ld_act, row0, rows_valid, col0, p.f, lane);
+  }
+};
+
+static int launch_swiglu_pair(const void* A, const void* Wgu, int M, int f, int K, long long lda, long long ldb,
+                              const SwigluParams& sp, cudaStream_t stream) {
+  using Epi = EpiSwiglu;
+  constexpr int STAGES = 6;
+  using S = SmemPair<STAGES>;
+  CUtensorMap tmA, tmB;
+  int rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, BK, BM,
+                        CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != B200_OK) return rc;
+  rc = make_tmap_2d(&tmB, Wgu, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)K, (uint64_t)(2 * f), (uint64_t)ldb * 2, BK,
+                    PAIR_HALF_N, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != B200_OK) return rc;
+  auto kern = gemm_pair_kernel<STAGES, false, false, Epi>;
+  const int smem_bytes = S::bytes(Epi::SMEM_BYTES);
+  static bool attr_set = false;
+  if (!attr_set) {
+    B200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+    attr_set = true;
+  }
+  const int N = 2 * f;
+  const int tiles = ceil_div(M, PAIR_BM) * ceil_div(N, PAIR_BN);
+  const int max_pairs = sm_count() / 2;
+  const int pairs = tiles < max_pairs ? tiles : max_pairs;
+  kern<<<2 * pairs, NUM_THREADS, smem_bytes, stream>>>(tmA, tmB, M, N, K, 1, sp, device_err_word(), 1, nullptr, f);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200_OK;
+}
+
 template <int BN, int STAGES, bool A_MN, bool B_MN>
 static int launch_store(const void* A, const void* B, int M, int N, int K, long long lda, long long ldb, int fmt,
                         const StoreParams& sp, const DescCfg* dc_override, cudaStream_t stream) {
@@ -369,7 +487,7 @@ static int launch_store_pair(const void* A, const void* B, int M, int N, int K, 
   }
   const long long units = (long long)tiles * k_splits;
   const int pairs = units < max_pairs ? (int)units : max_pairs;
-  kern<<<2 * pairs, NUM_THREADS, smem_bytes, stream>>>(tmA, tmB, M, N, K, fmt, sp, device_err_word(), k_splits, sync);
+  kern<<<2 * pairs, NUM_THREADS, smem_bytes, stream>>>(tmA, tmB, M, N, K, fmt, sp, device_err_word(), k_splits, sync, 0);
   B200_CUDA_CHECK(cudaGetLastError());
   return B200_OK;
 }
@@ -406,6 +524,20 @@ int b200_gemm_reset_split_sync(cudaStream_t stream) {
   B200_CUDA_CHECK(cudaGetSymbolAddress(reinterpret_cast<void**>(&base), g_split_sync));
   B200_CUDA_CHECK(cudaMemsetAsync(base, 0, sizeof(unsigned int) * SPLIT_REGIONS * SPLIT_MAX_TILES * 8, stream));
   return B200_OK;
+}
+
+// gu[M, 2f] = x[M, K] Wgu[2f, K]^T (rows 0..f-1 of Wgu: gate, f..2f-1: up) and act[M, f] = silu(gate) * up, bf16, in one
+// launch. f must be a multiple of 128; row strides (elements) multiples of 8. Returns B200_ERR_ARG for shapes the fused
+// kernel does not take (the caller then runs the GEMM and the SwiGLU kernel).
+int b200_gemm_swiglu(const void* x, const void* Wgu, void* gu, void* act, int M, int f, int K, long long ldx,
+                     long long ldw, long long ld_gu, long long ld_act, cudaStream_t stream) {
+  using namespace b200;
+  using namespace b200::gemm;
+  if (!x || !Wgu || !gu || !act || M <= 0 || f <= 0 || K <= 0 || (f % PAIR_HALF_N) || (ldx & 7) || (ldw & 7) ||
+      (ld_gu & 7) || (ld_act & 7) || (reinterpret_cast<uintptr_t>(gu) & 15) || (reinterpret_cast<uintptr_t>(act) & 15))
+    return B200_ERR_ARG;
+  SwigluParams sp{reinterpret_cast<__nv_bfloat16*>(gu), ld_gu, reinterpret_cast<__nv_bfloat16*>(act), ld_act, f};
+  return launch_swiglu_pair(x, Wgu, M, f, K, ldx, ldw, sp, stream);
 }
 
 // C[M,N] = alpha * op(A) * op(B)^T (+ C if accumulate) (+ residual)

@@ -41,7 +41,7 @@ template <int STAGES, bool A_MN, bool B_MN, class Epi>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
     gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, int M, int N,
                      int K, int fmt, typename Epi::Params ep, unsigned int* err_word, int k_splits,
-                     unsigned int* split_sync) {
+                     unsigned int* split_sync, int b_half_stride) {
   using S = SmemPair<STAGES>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -117,7 +117,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
         unit_range(unit, tile, kb0, kb1);
         tile_coords(tile, m_blk, n_blk);
         const int m0 = m_blk * PAIR_BM + (int)cta * BM;
-        const int n0 = n_blk * PAIR_BN + (int)cta * PAIR_HALF_N;
+        // B rows of this CTA's half of the tile. b_half_stride > 0 (fused gate / up projection): the leader takes 128
+        // rows of the first half of B and its peer the 128 rows that lie b_half_stride below them, so columns 0-127 of
+        // the accumulator are the gate and columns 128-255 the up projection of the SAME 128 output features.
+        const int n0 = b_half_stride > 0 ? n_blk * PAIR_HALF_N + (int)cta * b_half_stride
+                                         : n_blk * PAIR_BN + (int)cta * PAIR_HALF_N;
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const uint32_t s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;

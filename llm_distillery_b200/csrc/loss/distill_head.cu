@@ -235,7 +235,7 @@ static int launch_head(const void* Hc, const void* W, int M, int N, int Kdim, lo
     }
     const int tiles = ceil_div(M, PAIR_BM) * ceil_div(N, PAIR_BN);
     const int pairs = tiles < sm_count() / 2 ? tiles : sm_count() / 2;
-    kern<<<2 * pairs, NUM_THREADS, smem_bytes, stream>>>(tmA, tmB, M, N, Kdim, 1, ep, device_err_word(), 1, nullptr);
+    kern<<<2 * pairs, NUM_THREADS, smem_bytes, stream>>>(tmA, tmB, M, N, Kdim, 1, ep, device_err_word(), 1, nullptr, 0);
     B200_CUDA_CHECK(cudaGetLastError());
     return B200_OK;
   }

@@ -347,8 +347,7 @@ class DecoderLayerFn(torch.autograd.Function):
         att, lse = attention.attention_fwd(qkv, B, L, H, Hkv, d)
         h1 = basic.linear_fwd(att, w_o, residual=h)
         n2, _, rstd2 = basic.rmsnorm_fwd(h1, w_ln2, eps)
-        gu = basic.linear_fwd(n2, w_gu)
-        act = basic.swiglu_fwd(gu)
+        gu, act = basic.linear_swiglu_fwd(n2, w_gu)
         h2 = basic.linear_fwd(act, w_d, residual=h1)
         ctx.meta = meta
         ctx.weights = (w_ln1, w_qkv, w_o, w_ln2, w_gu, w_d)
@@ -387,8 +386,7 @@ class DecoderLayerFn(torch.autograd.Function):
             att, lse = attention.attention_fwd(qkv, B, L, H, Hkv, d)
             h1 = basic.linear_fwd(att, w_o, residual=h)
             n2, _, rstd2 = basic.rmsnorm_fwd(h1, w_ln2, eps)
-            gu = basic.linear_fwd(n2, w_gu)
-            act = basic.swiglu_fwd(gu)
+            gu, act = basic.linear_swiglu_fwd(n2, w_gu)
         elif w_qn is not None:
             h, pos, cos, sin, rstd1, n1, qkv, att, lse, h1, rstd2, n2, gu, act, qkv_raw, rstd_qk = ctx.saved_tensors
         else:
@@ -628,7 +626,7 @@ class LlamaModel(nn.Module):
                     h = h1 + moe_mlp(n2, layer.router, layer.gate_up_proj, layer.down_proj, cfg.num_experts_per_tok,
                                      cfg.moe_renormalize)
                     continue
-                act = basic.swiglu_fwd(basic.linear_fwd(n2, layer.gate_up_proj))
+                _, act = basic.linear_swiglu_fwd(n2, layer.gate_up_proj)
                 h = basic.linear_fwd(act, layer.down_proj, residual=h1)
             y, _, _ = basic.rmsnorm_fwd(h, self.norm, cfg.rms_norm_eps)
             out[:, c0:c0 + n] = y.reshape(B, n, -1)

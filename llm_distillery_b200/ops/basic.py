@@ -351,6 +351,24 @@ def swiglu_fwd(gu: torch.Tensor) -> torch.Tensor:
     return act
 
 
+def linear_swiglu_fwd(x: torch.Tensor, w_gu: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """(gu, act) with gu[T, 2f] = x w_gu^T (gate rows first, then up rows) and act[T, f] = silu(gate) * up. On the GPU
+    one launch does both when the shape allows (bf16, f a multiple of 128, at least a few hundred rows): the SwiGLU
+    sits in the epilogue of the gate / up GEMM. Same values as ``linear_fwd`` followed by ``swiglu_fwd``."""
+    T = x.shape[0]
+    f = w_gu.shape[0] // 2
+    if (_native(x, w_gu) and x.dtype == _BF16 and w_gu.dtype == _BF16 and f % 128 == 0 and T >= 512
+            and x.stride(-1) == 1 and w_gu.stride(-1) == 1 and x.stride(0) % 8 == 0 and w_gu.stride(0) % 8 == 0):
+        gu = torch.empty((T, 2 * f), dtype=x.dtype, device=x.device)
+        act = torch.empty((T, f), dtype=x.dtype, device=x.device)
+        _lib.check(_lib.kernels().b200_gemm_swiglu(_lib.ptr(x), _lib.ptr(w_gu), _lib.ptr(gu), _lib.ptr(act), T, f,
+                                                   x.shape[1], x.stride(0), w_gu.stride(0), gu.stride(0), act.stride(0),
+                                                   _lib.stream()), "b200_gemm_swiglu")
+        return gu, act
+    gu = linear_fwd(x, w_gu)
+    return gu, swiglu_fwd(gu)
+
+
 def swiglu_bwd(gu: torch.Tensor, dact: torch.Tensor) -> torch.Tensor:
     T, f2 = gu.shape
     f = f2 // 2

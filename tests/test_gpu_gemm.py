@@ -92,3 +92,22 @@ def test_linear_helpers_match_autograd():
     g = torch.zeros(384, 256, device=DEV)
     basic.linear_wgrad(dy, x, out=g, accumulate=True)
     assert torch.allclose(g, wf.grad, atol=0.5, rtol=2e-2)
+
+
+@pytest.mark.parametrize("T,f,K", [(1000, 1408, 512), (4096, 5632, 2048), (513, 128, 64), (2048, 1280, 200)])
+def test_gate_up_gemm_with_swiglu_in_the_epilogue(T, f, K):
+    """One launch writes gu = x W^T and act = silu(gate) * up; both must equal the two-kernel path bit for bit (act is
+    computed from the rounded gate / up values), and nothing may be written outside the outputs."""
+    torch.manual_seed(T + f)
+    x = torch.randn(T, K, device=DEV).bfloat16()
+    w = (torch.randn(2 * f, K, device=DEV) * 0.05).bfloat16()
+    gu, act = basic.linear_swiglu_fwd(x, w)
+    assert _lib.take_device_error() == 0
+    gu_ref = basic.linear_fwd(x, w)
+    act_ref = basic.swiglu_fwd(gu_ref)
+    assert torch.equal(gu, gu_ref)
+    assert torch.equal(act, act_ref)
+    r = x.float() @ w.float().t()
+    assert torch.allclose(gu.float(), r, atol=2e-2 * max(1.0, r.abs().max().item()), rtol=2e-2)
+    want = torch.nn.functional.silu(r[:, :f]) * r[:, f:]
+    assert torch.allclose(act.float(), want, atol=3e-2 * max(1.0, want.abs().max().item()), rtol=3e-2)
