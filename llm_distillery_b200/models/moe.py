@@ -46,12 +46,21 @@ def experts_forward(x_perm: torch.Tensor, counts: list[int], w_gu: torch.Tensor,
     n, h = x_perm.shape
     two_f = w_gu.shape[1]
     gu = torch.empty((n, two_f), dtype=x_perm.dtype, device=x_perm.device)
-    o = 0
-    for e, c in enumerate(counts):
-        if c:
-            basic.gemm(x_perm[o:o + c], w_gu[e], out=gu[o:o + c])
+    offs, o = [], 0
+    for c in counts:
+        offs.append(o)
         o += c
-    act = basic.swiglu_fwd(gu)
+    if all(c == 0 or basic.swiglu_fusable(x_perm[o:o + c], w_gu[e]) for e, (o, c) in enumerate(zip(offs, counts))):
+        # every expert has enough rows for the GEMM that applies SwiGLU in its epilogue
+        act = torch.empty((n, two_f // 2), dtype=x_perm.dtype, device=x_perm.device)
+        for e, (o, c) in enumerate(zip(offs, counts)):
+            if c:
+                basic.linear_swiglu_fwd(x_perm[o:o + c], w_gu[e], gu[o:o + c], act[o:o + c])
+    else:
+        for e, (o, c) in enumerate(zip(offs, counts)):
+            if c:
+                basic.gemm(x_perm[o:o + c], w_gu[e], out=gu[o:o + c])
+        act = basic.swiglu_fwd(gu)
     y = torch.empty((n, h), dtype=x_perm.dtype, device=x_perm.device)
     o = 0
     for e, c in enumerate(counts):

@@ -351,22 +351,34 @@ def swiglu_fwd(gu: torch.Tensor) -> torch.Tensor:
     return act
 
 
-def linear_swiglu_fwd(x: torch.Tensor, w_gu: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+def swiglu_fusable(x: torch.Tensor, w_gu: torch.Tensor) -> bool:
+    """Whether ``linear_swiglu_fwd`` runs as one launch for these operands."""
+    f = w_gu.shape[0] // 2
+    return bool(_native(x, w_gu) and x.dtype == _BF16 and w_gu.dtype == _BF16 and f % 128 == 0 and x.shape[0] >= 512
+                and x.stride(-1) == 1 and w_gu.stride(-1) == 1 and x.stride(0) % 8 == 0 and w_gu.stride(0) % 8 == 0)
+
+
+def linear_swiglu_fwd(x: torch.Tensor, w_gu: torch.Tensor, out_gu: torch.Tensor | None = None,
+                      out_act: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor]:
     """(gu, act) with gu[T, 2f] = x w_gu^T (gate rows first, then up rows) and act[T, f] = silu(gate) * up. On the GPU
     one launch does both when the shape allows (bf16, f a multiple of 128, at least a few hundred rows): the SwiGLU
-    sits in the epilogue of the gate / up GEMM. Same values as ``linear_fwd`` followed by ``swiglu_fwd``."""
+    sits in the epilogue of the gate / up GEMM. Same values as ``linear_fwd`` followed by ``swiglu_fwd``.
+    ``out_gu`` / ``out_act`` (row slices of larger buffers are fine) receive the results when given."""
     T = x.shape[0]
     f = w_gu.shape[0] // 2
-    if (_native(x, w_gu) and x.dtype == _BF16 and w_gu.dtype == _BF16 and f % 128 == 0 and T >= 512
-            and x.stride(-1) == 1 and w_gu.stride(-1) == 1 and x.stride(0) % 8 == 0 and w_gu.stride(0) % 8 == 0):
-        gu = torch.empty((T, 2 * f), dtype=x.dtype, device=x.device)
-        act = torch.empty((T, f), dtype=x.dtype, device=x.device)
+    if swiglu_fusable(x, w_gu):
+        gu = out_gu if out_gu is not None else torch.empty((T, 2 * f), dtype=x.dtype, device=x.device)
+        act = out_act if out_act is not None else torch.empty((T, f), dtype=x.dtype, device=x.device)
         _lib.check(_lib.kernels().b200_gemm_swiglu(_lib.ptr(x), _lib.ptr(w_gu), _lib.ptr(gu), _lib.ptr(act), T, f,
                                                    x.shape[1], x.stride(0), w_gu.stride(0), gu.stride(0), act.stride(0),
                                                    _lib.stream()), "b200_gemm_swiglu")
         return gu, act
-    gu = linear_fwd(x, w_gu)
-    return gu, swiglu_fwd(gu)
+    gu = gemm(x, w_gu, out=out_gu) if out_gu is not None else linear_fwd(x, w_gu)
+    act = swiglu_fwd(gu)
+    if out_act is not None:
+        out_act.copy_(act)
+        act = out_act
+    return gu, act
 
 
 def swiglu_bwd(gu: torch.Tensor, dact: torch.Tensor) -> torch.Tensor:
