@@ -281,6 +281,72 @@ def bench_p2p(args, dev, rank, world) -> None:
         del buf
 
 
+def bench_dpstep(args, dev, rank, world) -> None:
+    """The pieces of the data-parallel optimizer step on a flat parameter space of ``--params`` elements (default: the
+    1.1 B of TinyLlama): bf16 wire cast, the fused reduce-scatter + AdamW + all-gather kernel in its three gradient
+    modes, and reduce-scatter / all-gather alone. Every timed call is bracketed by the flag barriers of a real step."""
+    from llm_distillery_b200.parallel.p2p import P2PComm, SymmetricBuffer
+    comm = P2PComm(dev)
+    n = (int(args.params) // (256 * world)) * (256 * world)
+    per = n // world
+    lo = rank * per
+    grad = SymmetricBuffer(n, torch.float32, dev)
+    wire = SymmetricBuffer(n, torch.bfloat16, dev)
+    model = SymmetricBuffer(n, torch.bfloat16, dev)
+    grad.tensor.normal_(0, 1e-3)
+    master = torch.zeros(per, dtype=torch.float32, device=dev)
+    m = torch.zeros_like(master)
+    v = torch.zeros_like(master)
+    reduced = torch.zeros_like(master)
+    shard16 = torch.zeros(per, dtype=torch.bfloat16, device=dev)
+    K = _lib.kernels()
+    st = _lib.stream
+
+    def cast():
+        for a, b in ((0, lo), (lo + per, n)):
+            if b > a:
+                _lib.check(K.b200_p2p_cast_wire(_lib.ptr(grad.tensor), _lib.ptr(wire.tensor), a, b - a, st()), "cast")
+
+    def fused(mode):
+        def run():
+            comm.barrier()
+            src = wire.c_ptrs if mode == 1 else grad.c_ptrs
+            own = _lib.ptr(grad.tensor) if mode == 1 else (_lib.ptr(reduced) if mode == 2 else None)
+            _lib.check(K.b200_p2p_rs_adamw_ag(src, own, mode, model.c_ptrs, _lib.ptr(master), _lib.ptr(m), _lib.ptr(v), lo,
+                                              per, 0, rank, world, 1e-5, 0.9, 0.99, 1e-8, 0.0, 1, 1.0 / world, 1, 0, st()),
+                       "fused")
+            comm.barrier()
+        return run
+
+    def rs_only():
+        comm.barrier()
+        comm.reduce_scatter(grad, reduced, lo, 1.0)
+        comm.barrier()
+
+    def ag_only():
+        comm.barrier()
+        comm.allgather(model, shard16, lo, skip_self=True)
+        comm.barrier()
+
+    def two_barriers():
+        comm.barrier()
+        comm.barrier()
+
+    gb = lambda b, ms: round(b / ms / 1e6, 1)
+    inbound16, inbound32 = (world - 1) * per * 2, (world - 1) * per * 4
+    for name, fn, note in (
+            ("two flag barriers", two_barriers, {}),
+            ("bf16 wire cast", cast, {"hbm_gbs": None}),
+            ("fused, bf16 wire", fused(1), {"nvlink_in_gbs": inbound16, "nvlink_out_gbs": inbound16}),
+            ("fused, fp32 wire", fused(0), {"nvlink_in_gbs": inbound32, "nvlink_out_gbs": inbound16}),
+            ("fused, gradient already summed (AdamW + all-gather)", fused(2), {"nvlink_out_gbs": inbound16}),
+            ("reduce-scatter alone, fp32", rs_only, {"nvlink_in_gbs": inbound32}),
+            ("all-gather alone, bf16", ag_only, {"nvlink_out_gbs": inbound16})):
+        ms = timed_max(fn, args.iters)
+        extra = {k: (gb(b, ms) if b else None) for k, b in note.items()}
+        emit(rank, case=name, world=world, params=n, ms=round(ms, 4), **extra)
+
+
 def bench_zero3(args, dev, rank, world) -> None:
     """The three kernels of full parameter sharding on one decoder layer's worth of parameters, against the NCCL
     collectives they replace: pull gather (bf16), reduce-scatter-accumulate (fp32), reduce-scatter + AdamW (fp32)."""
@@ -341,7 +407,8 @@ def bench_zero3(args, dev, rank, world) -> None:
 
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
-    ap.add_argument("cmd", choices=["gemms", "collect", "p2p", "head", "zero3"])
+    ap.add_argument("cmd", choices=["gemms", "collect", "p2p", "head", "zero3", "dpstep"])
+    ap.add_argument("--params", type=float, default=1.1e9, help="dpstep: elements of the flat parameter space")
     ap.add_argument("--rows", type=int, default=32768)
     ap.add_argument("--hidden", type=int, default=4096)
     ap.add_argument("--vocab", type=int, default=128256)
@@ -367,7 +434,7 @@ def main() -> None:
     dist.init_process_group("nccl", device_id=dev)
     rank, world = dist.get_rank(), dist.get_world_size()
     {"gemms": bench_gemms, "collect": bench_collect, "p2p": bench_p2p, "head": bench_head,
-     "zero3": bench_zero3}[args.cmd](args, dev, rank, world)
+     "zero3": bench_zero3, "dpstep": bench_dpstep}[args.cmd](args, dev, rank, world)
     torch.cuda.synchronize()
     dist.barrier()
     dist.destroy_process_group()

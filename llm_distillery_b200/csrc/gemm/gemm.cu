@@ -335,6 +335,134 @@ struct EpiSwiglu {
   }
 };
 
+// Backward of SwiGLU in the epilogue of the down projection's dgrad GEMM: the accumulator tile is d(act) for 256 tokens
+// x 256 features; the warp pulls the matching gate and up values (32 rows x 128 columns each, coalesced 256-byte row
+// segments) into two swizzled stages, every lane then works on its own row - d(act) rounded to bf16 first, so that the
+// result equals GEMM + stand-alone kernel bit for bit - and overwrites the stages with d(gate) and d(up), which leave
+// as whole row segments. d(act) itself is never written.
+struct SwigluBwdParams {
+  const __nv_bfloat16* gu;   // [M, 2f] saved by the forward pass
+  long long ld_gu;
+  __nv_bfloat16* dgu;        // [M, 2f]
+  long long ld_dgu;
+  int f;
+};
+
+struct EpiSwigluBwd {
+  using Params = SwigluBwdParams;
+  static constexpr bool SPLIT_K = false;
+  static constexpr int STAGE_BYTES = 2 * 32 * 256;     // gate and up stage per epilogue warp
+  static constexpr int SMEM_BYTES = NUM_EPI_WARPS * STAGE_BYTES;
+
+  static __device__ __forceinline__ void tile(const Params& p, uint32_t taddr, int m0, int n0, int M, int N, int quad,
+                                              int lane, uint8_t* epi_smem) {
+    uint8_t* sg = epi_smem + quad * STAGE_BYTES;
+    uint8_t* su = sg + 32 * 256;
+    const int row0 = m0 + quad * 32;
+    const int rows_valid = min(32, M - row0);
+    const int chunk = lane & 15;
+#pragma unroll 1
+    for (int half = 0; half < 2; ++half) {
+      const int col0 = n0 + half * 128;
+      if (col0 >= N) break;                              // N is a multiple of 128: a half is whole or absent
+      const int col = col0 + chunk * 8;
+      {
+        uint4 t[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int row = 2 * j + (lane >> 4);
+          t[j] = row < rows_valid ? __ldg(reinterpret_cast<const uint4*>(p.gu + (long long)(row0 + row) * p.ld_gu + col))
+                                  : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int row = 2 * j + (lane >> 4);
+          *reinterpret_cast<uint4*>(sg + row * 256 + ((chunk ^ (row & 15)) << 4)) = t[j];
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int row = 2 * j + (lane >> 4);
+          t[j] = row < rows_valid
+                     ? __ldg(reinterpret_cast<const uint4*>(p.gu + (long long)(row0 + row) * p.ld_gu + p.f + col))
+                     : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int row = 2 * j + (lane >> 4);
+          *reinterpret_cast<uint4*>(su + row * 256 + ((chunk ^ (row & 15)) << 4)) = t[j];
+        }
+      }
+      __syncwarp();
+#pragma unroll 1
+      for (int c4 = 0; c4 < 4; ++c4) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(taddr + half * 128 + c4 * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int off = lane * 256 + (((c4 * 4 + j) ^ (lane & 15)) << 4);
+          const uint4 qg = *reinterpret_cast<const uint4*>(sg + off);
+          const uint4 qu = *reinterpret_cast<const uint4*>(su + off);
+          const __nv_bfloat162* hg = reinterpret_cast<const __nv_bfloat162*>(&qg);
+          const __nv_bfloat162* hu = reinterpret_cast<const __nv_bfloat162*>(&qu);
+          float dg[8], du[8];
+#pragma unroll
+          for (int t2 = 0; t2 < 4; ++t2) {
+            const float2 g2 = __bfloat1622float2(hg[t2]);
+            const float2 u2 = __bfloat1622float2(hu[t2]);
+            const float gg[2] = {g2.x, g2.y}, uu[2] = {u2.x, u2.y};
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const float d = __bfloat162float(__float2bfloat16(__uint_as_float(r[j * 8 + t2 * 2 + e])));
+              const float sgm = __fdividef(1.f, 1.f + __expf(-gg[e]));
+              const float silu = gg[e] * sgm;
+              dg[t2 * 2 + e] = d * uu[e] * (sgm + silu * (1.f - sgm));
+              du[t2 * 2 + e] = d * silu;
+            }
+          }
+          uint4 og, ou;
+          og.x = pack_bf16x2(dg[0], dg[1]); og.y = pack_bf16x2(dg[2], dg[3]);
+          og.z = pack_bf16x2(dg[4], dg[5]); og.w = pack_bf16x2(dg[6], dg[7]);
+          ou.x = pack_bf16x2(du[0], du[1]); ou.y = pack_bf16x2(du[2], du[3]);
+          ou.z = pack_bf16x2(du[4], du[5]); ou.w = pack_bf16x2(du[6], du[7]);
+          *reinterpret_cast<uint4*>(sg + off) = og;
+          *reinterpret_cast<uint4*>(su + off) = ou;
+        }
+      }
+      EpiSwiglu::flush(sg, p.dgu, p.ld_dgu, row0, rows_valid, col0, p.f, lane);
+      EpiSwiglu::flush(su, p.dgu + p.f, p.ld_dgu, row0, rows_valid, col0, p.f, lane);
+    }
+  }
+};
+
+static int launch_swiglu_bwd_pair(const void* dY, const void* Wd, int M, int f, int K, long long lda, long long ldb,
+                                  const SwigluBwdParams& sp, cudaStream_t stream) {
+  using Epi = EpiSwigluBwd;
+  constexpr int STAGES = 5;                    // one ring stage less than the store kernel: the epilogue needs 64 KB
+  using S = SmemPair<STAGES>;
+  CUtensorMap tmA, tmB;
+  int rc = make_tmap_2d(&tmA, dY, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, BK, BM,
+                        CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != B200_OK) return rc;
+  // W_d is [K = h, N = f] in memory: an MN-major B operand
+  rc = make_tmap_2d(&tmB, Wd, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)f, (uint64_t)K, (uint64_t)ldb * 2, 64, BK,
+                    CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != B200_OK) return rc;
+  auto kern = gemm_pair_kernel<STAGES, false, true, Epi>;
+  const int smem_bytes = S::bytes(Epi::SMEM_BYTES);
+  static bool attr_set = false;
+  if (!attr_set) {
+    B200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+    attr_set = true;
+  }
+  const int tiles = ceil_div(M, PAIR_BM) * ceil_div(f, PAIR_BN);
+  const int max_pairs = sm_count() / 2;
+  const int pairs = tiles < max_pairs ? tiles : max_pairs;
+  kern<<<2 * pairs, NUM_THREADS, smem_bytes, stream>>>(tmA, tmB, M, f, K, 1, sp, device_err_word(), 1, nullptr, 0);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200_OK;
+}
+
 static int launch_swiglu_pair(const void* A, const void* Wgu, int M, int f, int K, long long lda, long long ldb,
                               const SwigluParams& sp, cudaStream_t stream) {
   using Epi = EpiSwiglu;
@@ -538,6 +666,19 @@ int b200_gemm_swiglu(const void* x, const void* Wgu, void* gu, void* act, int M,
     return B200_ERR_ARG;
   SwigluParams sp{reinterpret_cast<__nv_bfloat16*>(gu), ld_gu, reinterpret_cast<__nv_bfloat16*>(act), ld_act, f};
   return launch_swiglu_pair(x, Wgu, M, f, K, ldx, ldw, sp, stream);
+}
+
+// dgu[M, 2f] = SwiGLU backward of (gu, d(act)) with d(act) = dy[M, K] Wd[K, f] taken straight from the accumulator
+// (never written). f a multiple of 128; strides multiples of 8. B200_ERR_ARG for shapes the fused kernel does not take.
+int b200_gemm_swiglu_bwd(const void* dy, const void* Wd, const void* gu, void* dgu, int M, int f, int K, long long ld_dy,
+                         long long ldw, long long ld_gu, long long ld_dgu, cudaStream_t stream) {
+  using namespace b200;
+  using namespace b200::gemm;
+  if (!dy || !Wd || !gu || !dgu || M <= 0 || f <= 0 || K <= 0 || (f % PAIR_HALF_N) || (ld_dy & 7) || (ldw & 7) ||
+      (ld_gu & 7) || (ld_dgu & 7) || (reinterpret_cast<uintptr_t>(gu) & 15) || (reinterpret_cast<uintptr_t>(dgu) & 15))
+    return B200_ERR_ARG;
+  SwigluBwdParams sp{reinterpret_cast<const __nv_bfloat16*>(gu), ld_gu, reinterpret_cast<__nv_bfloat16*>(dgu), ld_dgu, f};
+  return launch_swiglu_bwd_pair(dy, Wd, M, f, K, ld_dy, ldw, sp, stream);
 }
 
 // C[M,N] = alpha * op(A) * op(B)^T (+ C if accumulate) (+ residual)

@@ -394,10 +394,8 @@ class DecoderLayerFn(torch.autograd.Function):
         dh2 = dh2.contiguous()
         # MLP branch
         g_d = _wgrad(dh2, act, w_d, s_d)
-        dact = basic.linear_dgrad(dh2, w_d)
         del act
-        dgu = basic.swiglu_bwd(gu, dact)
-        del dact
+        dgu = basic.linear_dgrad_swiglu_bwd(dh2, w_d, gu)     # dgrad of the down projection + SwiGLU backward
         g_gu = _wgrad(dgu, n2, w_gu, s_gu)
         dn2 = basic.linear_dgrad(dgu, w_gu)
         del dgu

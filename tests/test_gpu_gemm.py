@@ -111,3 +111,22 @@ def test_gate_up_gemm_with_swiglu_in_the_epilogue(T, f, K):
     assert torch.allclose(gu.float(), r, atol=2e-2 * max(1.0, r.abs().max().item()), rtol=2e-2)
     want = torch.nn.functional.silu(r[:, :f]) * r[:, f:]
     assert torch.allclose(act.float(), want, atol=3e-2 * max(1.0, want.abs().max().item()), rtol=3e-2)
+
+
+@pytest.mark.parametrize("T,f,h", [(1000, 1408, 512), (4096, 5632, 2048), (513, 128, 64), (2048, 1280, 200)])
+def test_down_projection_dgrad_with_swiglu_backward_in_the_epilogue(T, f, h):
+    """dgu from one launch equals dgrad GEMM + SwiGLU backward kernel bit for bit (d(act) is rounded to bf16 before the
+    activation's derivative is applied, exactly as when it is stored in between)."""
+    torch.manual_seed(T + f + 1)
+    dy = torch.randn(T, h, device=DEV).bfloat16()
+    w_d = (torch.randn(h, f, device=DEV) * 0.05).bfloat16()
+    gu = torch.randn(T, 2 * f, device=DEV).bfloat16()
+    dgu = basic.linear_dgrad_swiglu_bwd(dy, w_d, gu)
+    assert _lib.take_device_error() == 0
+    dact = basic.linear_dgrad(dy, w_d)
+    ref = basic.swiglu_bwd(gu, dact)
+    assert torch.equal(dgu, ref)
+    g, u, d = gu[:, :f].float(), gu[:, f:].float(), dy.float() @ w_d.float()
+    sg = torch.sigmoid(g)
+    want = torch.cat([d * u * (sg + g * sg * (1 - sg)), d * g * sg], 1)
+    assert torch.allclose(dgu.float(), want, atol=3e-2 * max(1.0, want.abs().max().item()), rtol=3e-2)
