@@ -335,6 +335,120 @@ struct EpiSwiglu {
   }
 };
 
+// Rotary embedding in the epilogue of the fused q/k/v projection. A head of d = 64 is two 32-column chunks of the
+// accumulator, a head of d = 128 four; the rotation pairs column i with i + d/2, i.e. chunk c with chunk c + 1 (d = 64)
+// or c + 2 (d = 128) of the same 128-column half. Each lane owns one row, fetches the cos / sin entries of that row's
+// position, rounds the two chunks to bf16 first (what the stand-alone kernel reads back from memory) and rotates with
+// the same expressions, so the result is bit-identical to GEMM + rope kernel. Columns from n_rot on (the value heads)
+// are stored unrotated.
+struct RopeParams {
+  __nv_bfloat16* C;     // [M, N]
+  long long ldc;
+  const int* pos;       // [M]
+  const float* cs;      // [max_pos, d/2]
+  const float* sn;
+  int d;                // 64 or 128
+  int n_rot;            // first n_rot columns are rotated ((H + Hkv) * d)
+};
+
+struct EpiRope {
+  using Params = RopeParams;
+  static constexpr bool SPLIT_K = false;
+  static constexpr int STAGE_BYTES = 32 * 256;
+  static constexpr int SMEM_BYTES = NUM_EPI_WARPS * STAGE_BYTES;
+
+  static __device__ __forceinline__ void put(uint8_t* stage, int lane, int c4, const float (&v)[32]) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint4 o;
+      o.x = pack_bf16x2(v[j * 8 + 0], v[j * 8 + 1]);
+      o.y = pack_bf16x2(v[j * 8 + 2], v[j * 8 + 3]);
+      o.z = pack_bf16x2(v[j * 8 + 4], v[j * 8 + 5]);
+      o.w = pack_bf16x2(v[j * 8 + 6], v[j * 8 + 7]);
+      const int chunk = c4 * 4 + j;
+      *reinterpret_cast<uint4*>(stage + lane * 256 + ((chunk ^ (lane & 15)) << 4)) = o;
+    }
+  }
+
+  static __device__ __forceinline__ void tile(const Params& p, uint32_t taddr, int m0, int n0, int M, int N, int quad,
+                                              int lane, uint8_t* epi_smem) {
+    uint8_t* stage = epi_smem + quad * STAGE_BYTES;
+    const int row0 = m0 + quad * 32;
+    const int rows_valid = min(32, M - row0);
+    const int half_d = p.d >> 1;
+    const long long tpos = lane < rows_valid ? (long long)p.pos[row0 + lane] : 0;
+    const int step = p.d == 64 ? 1 : 2;                   // distance, in chunks, between the two halves of a pair
+#pragma unroll 1
+    for (int half = 0; half < 2; ++half) {
+      const int colh = n0 + half * 128;
+      if (colh >= N) break;                               // N is a multiple of 128
+#pragma unroll 1
+      for (int k = 0; k < 2; ++k) {
+        // d = 64: pair (0,1) then (2,3); d = 128: pair (0,2) then (1,3)
+        const int ca = p.d == 64 ? 2 * k : k;
+        const int cb = ca + step;
+        uint32_t ra[32], rb[32];
+        tmem_ld_32x32b_x32(taddr + half * 128 + ca * 32, ra);
+        tmem_ld_32x32b_x32(taddr + half * 128 + cb * 32, rb);
+        tmem_ld_wait();
+        float a[32], b[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          a[j] = __bfloat162float(__float2bfloat16(__uint_as_float(ra[j])));
+          b[j] = __bfloat162float(__float2bfloat16(__uint_as_float(rb[j])));
+        }
+        if (colh + ca * 32 < p.n_rot) {
+          const int j0 = p.d == 64 ? 0 : k * 32;          // first cos / sin entry of chunk ca
+          const float* cp = p.cs + tpos * half_d + j0;
+          const float* sp = p.sn + tpos * half_d + j0;
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            const float4 c4v = *reinterpret_cast<const float4*>(cp + j);
+            const float4 s4v = *reinterpret_cast<const float4*>(sp + j);
+            const float cc[4] = {c4v.x, c4v.y, c4v.z, c4v.w}, ss[4] = {s4v.x, s4v.y, s4v.z, s4v.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float fa = a[j + e], fb = b[j + e];
+              a[j + e] = __fmaf_rn(fa, cc[e], -__fmul_rn(fb, ss[e]));
+              b[j + e] = __fmaf_rn(fb, cc[e], __fmul_rn(fa, ss[e]));
+            }
+          }
+        }
+        put(stage, lane, ca, a);
+        put(stage, lane, cb, b);
+      }
+      EpiSwiglu::flush(stage, p.C, p.ldc, row0, rows_valid, colh, N, lane);
+    }
+  }
+};
+
+static int launch_rope_pair(const void* A, const void* W, int M, int N, int K, long long lda, long long ldb,
+                            const RopeParams& rp, cudaStream_t stream) {
+  using Epi = EpiRope;
+  constexpr int STAGES = 6;
+  using S = SmemPair<STAGES>;
+  CUtensorMap tmA, tmB;
+  int rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, BK, BM,
+                        CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != B200_OK) return rc;
+  rc = make_tmap_2d(&tmB, W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, BK,
+                    PAIR_HALF_N, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != B200_OK) return rc;
+  auto kern = gemm_pair_kernel<STAGES, false, false, Epi>;
+  const int smem_bytes = S::bytes(Epi::SMEM_BYTES);
+  static bool attr_set = false;
+  if (!attr_set) {
+    B200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+    attr_set = true;
+  }
+  const int tiles = ceil_div(M, PAIR_BM) * ceil_div(N, PAIR_BN);
+  const int max_pairs = sm_count() / 2;
+  const int pairs = tiles < max_pairs ? tiles : max_pairs;
+  kern<<<2 * pairs, NUM_THREADS, smem_bytes, stream>>>(tmA, tmB, M, N, K, 1, rp, device_err_word(), 1, nullptr, 0);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200_OK;
+}
+
 // Backward of SwiGLU in the epilogue of the down projection's dgrad GEMM: the accumulator tile is d(act) for 256 tokens
 // x 256 features; the warp pulls the matching gate and up values (32 rows x 128 columns each, coalesced 256-byte row
 // segments) into two swizzled stages, every lane then works on its own row - d(act) rounded to bf16 first, so that the
@@ -666,6 +780,21 @@ int b200_gemm_swiglu(const void* x, const void* Wgu, void* gu, void* act, int M,
     return B200_ERR_ARG;
   SwigluParams sp{reinterpret_cast<__nv_bfloat16*>(gu), ld_gu, reinterpret_cast<__nv_bfloat16*>(act), ld_act, f};
   return launch_swiglu_pair(x, Wgu, M, f, K, ldx, ldw, sp, stream);
+}
+
+// qkv[M, N] = x[M, K] W[N, K]^T with the rotary embedding applied to the first n_rot_heads heads of every row in the
+// epilogue (pos int32 [M]; cos / sin fp32 [max_pos, d/2]). d = 64 or 128, N a multiple of 128.
+int b200_gemm_rope(const void* x, const void* W, void* out, const int* pos, const float* cos_tab, const float* sin_tab,
+                   int M, int N, int K, int n_rot_heads, int d, long long ldx, long long ldw, long long ldo,
+                   cudaStream_t stream) {
+  using namespace b200;
+  using namespace b200::gemm;
+  if (!x || !W || !out || !pos || !cos_tab || !sin_tab || M <= 0 || N <= 0 || K <= 0 || (d != 64 && d != 128) ||
+      (N % PAIR_HALF_N) || n_rot_heads < 0 || n_rot_heads * d > N || (ldx & 7) || (ldw & 7) || (ldo & 7) ||
+      (reinterpret_cast<uintptr_t>(out) & 15))
+    return B200_ERR_ARG;
+  RopeParams rp{reinterpret_cast<__nv_bfloat16*>(out), ldo, pos, cos_tab, sin_tab, d, n_rot_heads * d};
+  return launch_rope_pair(x, W, M, N, K, ldx, ldw, rp, stream);
 }
 
 // dgu[M, 2f] = SwiGLU backward of (gu, d(act)) with d(act) = dy[M, K] Wd[K, f] taken straight from the accumulator

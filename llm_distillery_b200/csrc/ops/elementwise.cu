@@ -482,9 +482,10 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ x, const int* __restrict
     const float sg[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
+      // explicit roundings: the q/k/v GEMM's rotary epilogue (csrc/gemm/gemm.cu) evaluates the same expressions
       const float sk = sg[k] * sign;
-      oa[k] = fa[k] * c[k] - fb[k] * sk;
-      ob[k] = fb[k] * c[k] + fa[k] * sk;
+      oa[k] = __fmaf_rn(fa[k], c[k], -__fmul_rn(fb[k], sk));
+      ob[k] = __fmaf_rn(fb[k], c[k], __fmul_rn(fa[k], sk));
     }
     *reinterpret_cast<uint4*>(base + j) = pack8(oa);
     *reinterpret_cast<uint4*>(base + j + half) = pack8(ob);

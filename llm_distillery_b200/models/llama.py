@@ -335,15 +335,18 @@ class DecoderLayerFn(torch.autograd.Function):
     def forward(ctx, h, pos, cos, sin, w_ln1, w_qkv, w_o, w_ln2, w_gu, w_d, meta, b_qkv=None, w_qn=None, w_kn=None):
         B, L, H, Hkv, d, eps, recompute = meta
         n1, _, rstd1 = basic.rmsnorm_fwd(h, w_ln1, eps)
-        qkv = basic.linear_fwd(n1, w_qkv)
-        if b_qkv is not None:
-            basic.bias_add_(qkv, b_qkv)
         qk_saved = ()
-        if w_qn is not None:                                  # per-head norm of q and k (Qwen3), before the rotation
-            qkv_raw = qkv
-            qkv, rstd_qk = basic.headnorm_fwd(qkv_raw, w_qn, w_kn, H, Hkv, d, eps)
-            qk_saved = (qkv_raw, rstd_qk)
-        basic.rope_(qkv, pos, cos, sin, H + Hkv, d)          # q and k heads are adjacent columns
+        if b_qkv is None and w_qn is None:                    # rotation in the epilogue of the q/k/v GEMM
+            qkv = basic.linear_rope_fwd(n1, w_qkv, pos, cos, sin, H + Hkv, d)
+        else:
+            qkv = basic.linear_fwd(n1, w_qkv)
+            if b_qkv is not None:
+                basic.bias_add_(qkv, b_qkv)
+            if w_qn is not None:                              # per-head norm of q and k (Qwen3), before the rotation
+                qkv_raw = qkv
+                qkv, rstd_qk = basic.headnorm_fwd(qkv_raw, w_qn, w_kn, H, Hkv, d, eps)
+                qk_saved = (qkv_raw, rstd_qk)
+            basic.rope_(qkv, pos, cos, sin, H + Hkv, d)      # q and k heads are adjacent columns
         att, lse = attention.attention_fwd(qkv, B, L, H, Hkv, d)
         h1 = basic.linear_fwd(att, w_o, residual=h)
         n2, _, rstd2 = basic.rmsnorm_fwd(h1, w_ln2, eps)
@@ -376,13 +379,16 @@ class DecoderLayerFn(torch.autograd.Function):
         if recompute:
             h, pos, cos, sin = ctx.saved_tensors
             n1, _, rstd1 = basic.rmsnorm_fwd(h, w_ln1, eps)
-            qkv = basic.linear_fwd(n1, w_qkv)
-            if ctx.b_qkv is not None:
-                basic.bias_add_(qkv, ctx.b_qkv)
-            if w_qn is not None:
-                qkv_raw = qkv
-                qkv, rstd_qk = basic.headnorm_fwd(qkv_raw, w_qn, w_kn, H, Hkv, d, eps)
-            basic.rope_(qkv, pos, cos, sin, H + Hkv, d)
+            if ctx.b_qkv is None and w_qn is None:
+                qkv = basic.linear_rope_fwd(n1, w_qkv, pos, cos, sin, H + Hkv, d)
+            else:
+                qkv = basic.linear_fwd(n1, w_qkv)
+                if ctx.b_qkv is not None:
+                    basic.bias_add_(qkv, ctx.b_qkv)
+                if w_qn is not None:
+                    qkv_raw = qkv
+                    qkv, rstd_qk = basic.headnorm_fwd(qkv_raw, w_qn, w_kn, H, Hkv, d, eps)
+                basic.rope_(qkv, pos, cos, sin, H + Hkv, d)
             att, lse = attention.attention_fwd(qkv, B, L, H, Hkv, d)
             h1 = basic.linear_fwd(att, w_o, residual=h)
             n2, _, rstd2 = basic.rmsnorm_fwd(h1, w_ln2, eps)
@@ -608,12 +614,15 @@ class LlamaModel(nn.Module):
                 if LAYER_WEIGHTS_PRE[0] is not None:
                     LAYER_WEIGHTS_PRE[0](layer.input_layernorm)
                 n1, _, _ = basic.rmsnorm_fwd(h, layer.input_layernorm, cfg.rms_norm_eps)
-                qkv = basic.linear_fwd(n1, layer.qkv_proj)
-                if hasattr(layer, "qkv_bias"):
-                    basic.bias_add_(qkv, layer.qkv_bias)
-                if cfg.qk_norm:
-                    qkv, _ = basic.headnorm_fwd(qkv, layer.q_norm, layer.k_norm, H, Hkv, d, cfg.rms_norm_eps)
-                basic.rope_(qkv, pos, cos, sin, H + Hkv, d)
+                if not hasattr(layer, "qkv_bias") and not cfg.qk_norm:
+                    qkv = basic.linear_rope_fwd(n1, layer.qkv_proj, pos, cos, sin, H + Hkv, d)
+                else:
+                    qkv = basic.linear_fwd(n1, layer.qkv_proj)
+                    if hasattr(layer, "qkv_bias"):
+                        basic.bias_add_(qkv, layer.qkv_bias)
+                    if cfg.qk_norm:
+                        qkv, _ = basic.headnorm_fwd(qkv, layer.q_norm, layer.k_norm, H, Hkv, d, cfg.rms_norm_eps)
+                    basic.rope_(qkv, pos, cos, sin, H + Hkv, d)
                 kc[:, c0:c0 + n] = qkv[:, H * d:(H + Hkv) * d].reshape(B, n, kv)
                 vc[:, c0:c0 + n] = qkv[:, (H + Hkv) * d:].reshape(B, n, kv)
                 att = attention.attention_fwd_cached(qkv, kc, vc, B, n, c0, H, Hkv, d)

@@ -57,6 +57,7 @@ _SIGS = {
     "b200_segment_reduce": [_VP, _VP, _VP, _LL, _I, _I, _VP],
     "b200_gemm_reset_split_sync": [_VP],
     "b200_gemm_swiglu": [_VP, _VP, _VP, _VP, _I, _I, _I, _LL, _LL, _LL, _LL, _VP],
+    "b200_gemm_rope": [_VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _LL, _LL, _LL, _VP],
     "b200_gemm_swiglu_bwd": [_VP, _VP, _VP, _VP, _I, _I, _I, _LL, _LL, _LL, _LL, _VP],
     "b200_headnorm_fwd": [_VP, _VP, _VP, _VP, _VP, _LL, _I, _I, _I, _LL, _F, _VP],
     "b200_headnorm_bwd_blocks": [_LL, _I, _I],

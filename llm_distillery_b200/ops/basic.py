@@ -157,6 +157,24 @@ def rmsnorm_bwd(dy: torch.Tensor, h: torch.Tensor, w: torch.Tensor, rstd: torch.
     return dh, dw_out
 
 
+def linear_rope_fwd(x: torch.Tensor, w: torch.Tensor, pos: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
+                    n_heads: int, head_dim: int) -> torch.Tensor:
+    """qkv[T, N] = x w^T with the rotary embedding applied to the first ``n_heads`` heads of every row. On the GPU one
+    launch when the shape allows (bf16, head_dim 64 or 128, N a multiple of 128, a few hundred rows): the rotation sits
+    in the GEMM's epilogue. Same values as ``linear_fwd`` followed by ``rope_``."""
+    T, N = x.shape[0], w.shape[0]
+    if (_native(x, w) and x.dtype == _BF16 and w.dtype == _BF16 and head_dim in (64, 128) and N % 128 == 0 and T >= 512
+            and x.stride(-1) == 1 and w.stride(-1) == 1 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and pos.dtype == torch.int32 and cos.dtype == torch.float32 and cos.shape[1] == head_dim // 2
+            and cos.is_contiguous() and sin.is_contiguous()):
+        out = torch.empty((T, N), dtype=x.dtype, device=x.device)
+        _lib.check(_lib.kernels().b200_gemm_rope(_lib.ptr(x), _lib.ptr(w), _lib.ptr(out), _lib.ptr(pos), _lib.ptr(cos),
+                                                 _lib.ptr(sin), T, N, x.shape[1], n_heads, head_dim, x.stride(0),
+                                                 w.stride(0), out.stride(0), _lib.stream()), "b200_gemm_rope")
+        return out
+    return rope_(linear_fwd(x, w), pos, cos, sin, n_heads, head_dim)
+
+
 # ------------------------------------------------------------------------------------------------ per-head q/k norm
 def headnorm_fwd(qkv: torch.Tensor, wq: torch.Tensor, wk: torch.Tensor, n_q: int, n_kv: int, head_dim: int, eps: float):
     """Per-head RMSNorm of the query and key heads of fused qkv rows [T, (n_q + 2 n_kv) d] (Qwen3's q_norm / k_norm,

@@ -130,3 +130,23 @@ def test_down_projection_dgrad_with_swiglu_backward_in_the_epilogue(T, f, h):
     sg = torch.sigmoid(g)
     want = torch.cat([d * u * (sg + g * sg * (1 - sg)), d * g * sg], 1)
     assert torch.allclose(dgu.float(), want, atol=3e-2 * max(1.0, want.abs().max().item()), rtol=3e-2)
+
+
+@pytest.mark.parametrize("T,H,Hkv,d,K", [(1000, 8, 2, 64, 512), (4096, 32, 4, 64, 2048), (2048, 8, 2, 128, 1024),
+                                         (513, 2, 1, 128, 64)])
+def test_qkv_gemm_with_rotary_embedding_in_the_epilogue(T, H, Hkv, d, K):
+    """One launch = GEMM + rope kernel, bit for bit; the value heads (the last Hkv) are stored unrotated."""
+    torch.manual_seed(T + d)
+    N = (H + 2 * Hkv) * d
+    x = torch.randn(T, K, device=DEV).bfloat16()
+    w = (torch.randn(N, K, device=DEV) * 0.05).bfloat16()
+    L = 257
+    pos = (torch.arange(T, device=DEV, dtype=torch.int32) * 7) % L
+    cos, sin = basic.rope_tables(L, d, 10000.0, DEV)
+    got = basic.linear_rope_fwd(x, w, pos, cos, sin, H + Hkv, d)
+    assert _lib.take_device_error() == 0
+    plain = basic.linear_fwd(x, w)
+    ref = basic.rope_(plain.clone(), pos, cos, sin, H + Hkv, d)
+    assert torch.equal(got, ref)
+    assert torch.equal(got[:, (H + Hkv) * d:], plain[:, (H + Hkv) * d:])
+    assert not torch.equal(got[:, : H * d], plain[:, : H * d])
