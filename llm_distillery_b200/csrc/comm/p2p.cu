@@ -99,8 +99,10 @@ __device__ __forceinline__ void add_bf16x8(float (&g)[8], const uint4& q) {
 // from `own` (its fp32 gradient). MODE 2: the sum over the ranks is already in `own`, a local fp32 buffer that holds
 // this rank's shard only (indexed like master / m / v) - the reduction ran earlier, behind backward. One 16-byte bf16
 // store per peer in every mode.
-template <int MODE>
-__global__ void __launch_bounds__(256) rs_adamw_ag_kernel(Peers grads, const float* __restrict__ own, Peers models,
+// W: the largest world size this instantiation serves (the peers' vectors of MODE 1 live in W registers-quads; with
+// W = 16 for every world size the kernel needed 128 registers and half the resident warps).
+template <int MODE, int W>
+__global__ void __launch_bounds__(256, (W <= 8 ? 3 : 2)) rs_adamw_ag_kernel(Peers grads, const float* __restrict__ own, Peers models,
                                                          float* __restrict__ master, float* __restrict__ m,
                                                          float* __restrict__ v, long long shard_lo, long long shard_n,
                                                          long long state_off, int rank, int world, AdamArgs a) {
@@ -109,53 +111,46 @@ __global__ void __launch_bounds__(256) rs_adamw_ag_kernel(Peers grads, const flo
   master += state_off; m += state_off; v += state_off;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nv;
        i += (long long)gridDim.x * blockDim.x) {
-    // Every load of this element group is issued before the first use: the peers' gradients (microseconds away over
-    // NVLink) and the local master / moment vectors (HBM) then travel at the same time. With the state loads behind
-    // the additions the kernel took the SUM of the two transfer times (4.6 ms for 0.55 B parameters on two GPUs,
-    // where the HBM traffic alone needs 2.5 ms).
-    float pm[8], mm[8], vv[8];
-    uint4 q[MAX_RANKS];
-    float4 gx[MAX_RANKS], gy[MAX_RANKS];
-    float4 x = make_float4(0.f, 0.f, 0.f, 0.f), y = x;
-    if (MODE == 1) {
+    // (Issuing the master / moment loads BEFORE the peers' gradients are consumed was tried: it costs ~90 more
+    // registers, occupancy drops to one CTA per SM and the kernel takes 7.5 ms instead of 4.6 ms for 0.55 B parameters
+    // on two GPUs. Many resident warps hide the NVLink latency better than a few warps with every load in flight.)
+    float g[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (MODE == 2) {
+      const float4* src = reinterpret_cast<const float4*>(own + state_off) + 2 * i;
+      const float4 x = src[0], y = src[1];
+      g[0] = x.x; g[1] = x.y; g[2] = x.z; g[3] = x.w;
+      g[4] = y.x; g[5] = y.y; g[6] = y.z; g[7] = y.w;
+    } else if (MODE == 1) {
+      uint4 q[W];
 #pragma unroll
-      for (int k = 1; k < MAX_RANKS; ++k)
+      for (int k = 1; k < W; ++k)   // all peer loads issued before the first use: their latencies overlap
         if (k < world)
           q[k] = (reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(grads.p[(rank + k) % world]) +
                                                  shard_lo))[i];
       const float4* src = reinterpret_cast<const float4*>(own + shard_lo) + 2 * i;
-      x = src[0]; y = src[1];
-    } else if (MODE == 2) {
-      const float4* src = reinterpret_cast<const float4*>(own + state_off) + 2 * i;
-      x = src[0]; y = src[1];
-    } else {
+      const float4 x = src[0], y = src[1];
+      g[0] = x.x; g[1] = x.y; g[2] = x.z; g[3] = x.w;
+      g[4] = y.x; g[5] = y.y; g[6] = y.z; g[7] = y.w;
 #pragma unroll
-      for (int k = 0; k < MAX_RANKS; ++k)
-        if (k < world) {
-          const float4* src =
-              reinterpret_cast<const float4*>(reinterpret_cast<const float*>(grads.p[(rank + k) % world]) + shard_lo) + 2 * i;
-          gx[k] = src[0]; gy[k] = src[1];
-        }
+      for (int k = 1; k < W; ++k)
+        if (k < world) add_bf16x8(g, q[k]);
+    } else {
+      for (int k = 0; k < world; ++k) {
+        const int p = (rank + k) % world;  // start with the local copy, spread peers over time
+        const float4* src =
+            reinterpret_cast<const float4*>(reinterpret_cast<const float*>(grads.p[p]) + shard_lo) + 2 * i;
+        const float4 x = src[0], y = src[1];
+        g[0] += x.x; g[1] += x.y; g[2] += x.z; g[3] += x.w;
+        g[4] += y.x; g[5] += y.y; g[6] += y.z; g[7] += y.w;
+      }
     }
+    float pm[8], mm[8], vv[8];
     *reinterpret_cast<float4*>(pm) = reinterpret_cast<float4*>(master)[2 * i];
     *reinterpret_cast<float4*>(pm + 4) = reinterpret_cast<float4*>(master)[2 * i + 1];
     *reinterpret_cast<float4*>(mm) = reinterpret_cast<float4*>(m)[2 * i];
     *reinterpret_cast<float4*>(mm + 4) = reinterpret_cast<float4*>(m)[2 * i + 1];
     *reinterpret_cast<float4*>(vv) = reinterpret_cast<float4*>(v)[2 * i];
     *reinterpret_cast<float4*>(vv + 4) = reinterpret_cast<float4*>(v)[2 * i + 1];
-    float g[8] = {x.x, x.y, x.z, x.w, y.x, y.y, y.z, y.w};
-    if (MODE == 1) {
-#pragma unroll
-      for (int k = 1; k < MAX_RANKS; ++k)
-        if (k < world) add_bf16x8(g, q[k]);
-    } else if (MODE == 0) {
-#pragma unroll
-      for (int k = 0; k < MAX_RANKS; ++k)      // fixed order: own copy first, then rank + 1, rank + 2, ...
-        if (k < world) {
-          g[0] += gx[k].x; g[1] += gx[k].y; g[2] += gx[k].z; g[3] += gx[k].w;
-          g[4] += gy[k].x; g[5] += gy[k].y; g[6] += gy[k].z; g[7] += gy[k].w;
-        }
-    }
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       float gj = g[j] * a.grad_scale;
@@ -417,12 +412,15 @@ int b200_p2p_rs_adamw_ag(const void* const* grad_ptrs, const float* own_grad, in
              grad_scale, decoupled};
   int grid = grid_for(n >> 3);
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
-  if (grad_mode == 2)
-    rs_adamw_ag_kernel<2><<<grid, 256, 0, st>>>(G, own_grad, M, master, m, v, lo, n, state_off, rank, world, a);
-  else if (grad_mode == 1)
-    rs_adamw_ag_kernel<1><<<grid, 256, 0, st>>>(G, own_grad, M, master, m, v, lo, n, state_off, rank, world, a);
-  else
-    rs_adamw_ag_kernel<0><<<grid, 256, 0, st>>>(G, own_grad, M, master, m, v, lo, n, state_off, rank, world, a);
+#define B200_RS_LAUNCH(MODE, WW) \
+  rs_adamw_ag_kernel<MODE, WW><<<grid, 256, 0, st>>>(G, own_grad, M, master, m, v, lo, n, state_off, rank, world, a)
+  if (grad_mode == 2) B200_RS_LAUNCH(2, 2);
+  else if (grad_mode == 0) B200_RS_LAUNCH(0, 2);
+  else if (world <= 2) B200_RS_LAUNCH(1, 2);
+  else if (world <= 4) B200_RS_LAUNCH(1, 4);
+  else if (world <= 8) B200_RS_LAUNCH(1, 8);
+  else B200_RS_LAUNCH(1, 16);
+#undef B200_RS_LAUNCH
   B200_CUDA_CHECK(cudaGetLastError());
   return B200_OK;
 }
