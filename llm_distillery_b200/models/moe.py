@@ -239,15 +239,24 @@ class MoEBlockFn(torch.autograd.Function):
             g_gu = torch.zeros(w_gu.shape, dtype=torch.float32, device=w_gu.device)
         if w_d.requires_grad and s_d is None:
             g_d = torch.zeros(w_d.shape, dtype=torch.float32, device=w_d.device)
-        dact = torch.empty_like(act)
-        o = 0
-        for e, c in enumerate(counts):
+        offs, o = [], 0
+        for c in counts:
+            offs.append(o)
+            o += c
+        fuse = all(c == 0 or basic.swiglu_bwd_fusable(dy_perm[o:o + c], w_d[e], gu[o:o + c])
+                   for e, (o, c) in enumerate(zip(offs, counts)))
+        dgu = torch.empty_like(gu) if fuse else None
+        dact = None if fuse else torch.empty_like(act)
+        for e, (o, c) in enumerate(zip(offs, counts)):
             if c:
                 _expert_wgrad(dy_perm[o:o + c], act[o:o + c], w_d, s_d, e, g_d)
-                basic.gemm(dy_perm[o:o + c], w_d[e], b_mn=True, out=dact[o:o + c])
-            o += c
-        dgu = basic.swiglu_bwd(gu, dact)
-        del dact
+                if fuse:     # dgrad of the expert's down projection with the SwiGLU derivative in its epilogue
+                    basic.linear_dgrad_swiglu_bwd(dy_perm[o:o + c], w_d[e], gu[o:o + c], out=dgu[o:o + c])
+                else:
+                    basic.gemm(dy_perm[o:o + c], w_d[e], b_mn=True, out=dact[o:o + c])
+        if not fuse:
+            dgu = basic.swiglu_bwd(gu, dact)
+            del dact
         dx_perm = torch.empty_like(x_perm)
         o = 0
         for e, c in enumerate(counts):

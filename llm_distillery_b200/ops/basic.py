@@ -399,22 +399,33 @@ def linear_swiglu_fwd(x: torch.Tensor, w_gu: torch.Tensor, out_gu: torch.Tensor 
     return gu, act
 
 
-def linear_dgrad_swiglu_bwd(dy: torch.Tensor, w_d: torch.Tensor, gu: torch.Tensor) -> torch.Tensor:
+def swiglu_bwd_fusable(dy: torch.Tensor, w_d: torch.Tensor, gu: torch.Tensor) -> bool:
+    """Whether ``linear_dgrad_swiglu_bwd`` runs as one launch for these operands."""
+    f = w_d.shape[1]
+    return bool(_native(dy, w_d, gu) and dy.dtype == _BF16 and w_d.dtype == _BF16 and gu.dtype == _BF16 and f % 128 == 0
+                and dy.shape[0] >= 512 and dy.stride(-1) == 1 and w_d.stride(-1) == 1 and gu.stride(-1) == 1
+                and dy.stride(0) % 8 == 0 and w_d.stride(0) % 8 == 0 and gu.stride(0) % 8 == 0)
+
+
+def linear_dgrad_swiglu_bwd(dy: torch.Tensor, w_d: torch.Tensor, gu: torch.Tensor,
+                            out: torch.Tensor | None = None) -> torch.Tensor:
     """dgu[T, 2f] = SwiGLU backward of (gu, dact) with dact = dy[T, h] w_d[h, f] - the gradient through the down
     projection and the activation. On the GPU one launch when the shape allows: the dgrad GEMM's epilogue reads gate /
     up, rounds its accumulator to bf16 and writes d(gate), d(up); dact is never stored. Same values as
-    ``linear_dgrad`` followed by ``swiglu_bwd``."""
+    ``linear_dgrad`` followed by ``swiglu_bwd``. ``out`` (a row slice of a larger buffer is fine) receives the result."""
     T = dy.shape[0]
     f = w_d.shape[1]
-    if (_native(dy, w_d, gu) and dy.dtype == _BF16 and w_d.dtype == _BF16 and gu.dtype == _BF16 and f % 128 == 0
-            and T >= 512 and dy.stride(-1) == 1 and w_d.stride(-1) == 1 and gu.stride(-1) == 1
-            and dy.stride(0) % 8 == 0 and w_d.stride(0) % 8 == 0 and gu.stride(0) % 8 == 0):
-        dgu = torch.empty((T, 2 * f), dtype=gu.dtype, device=gu.device)
+    if swiglu_bwd_fusable(dy, w_d, gu):
+        dgu = out if out is not None else torch.empty((T, 2 * f), dtype=gu.dtype, device=gu.device)
         _lib.check(_lib.kernels().b200_gemm_swiglu_bwd(_lib.ptr(dy), _lib.ptr(w_d), _lib.ptr(gu), _lib.ptr(dgu), T, f,
                                                        dy.shape[1], dy.stride(0), w_d.stride(0), gu.stride(0),
                                                        dgu.stride(0), _lib.stream()), "b200_gemm_swiglu_bwd")
         return dgu
-    return swiglu_bwd(gu, linear_dgrad(dy, w_d))
+    dgu = swiglu_bwd(gu, linear_dgrad(dy, w_d))
+    if out is not None:
+        out.copy_(dgu)
+        return out
+    return dgu
 
 
 def swiglu_bwd(gu: torch.Tensor, dact: torch.Tensor) -> torch.Tensor:
