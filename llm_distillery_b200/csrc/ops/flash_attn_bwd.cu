@@ -521,9 +521,59 @@ __global__ void dq_convert_kernel(const float* __restrict__ acc, __nv_bfloat16* 
   }
 }
 
+// The same with the inverse rotary embedding of the query heads applied on the way: one thread takes the two 8-element
+// vectors that the rotation pairs (i and i + D/2 of a head), rounds them to bf16 first - what the stand-alone rope
+// kernel would read back - and rotates with that kernel's expressions, so the result is bit-identical to convert + rope.
+__global__ void dq_convert_rope_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dqkv,
+                                       const int* __restrict__ pos, const float* __restrict__ cs,
+                                       const float* __restrict__ sn, long long T, int H, int D, long long width) {
+  const int half = D >> 1;
+  const int vph = half >> 3;                 // vector pairs per head
+  const int vpt = H * vph;
+  const long long total = T * vpt;
+  const int HD = H * D;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / vpt;
+    const int r = (int)(i - t * vpt);
+    const int hd = r / vph;
+    const int j = (r - hd * vph) * 8;
+    const float* a = acc + t * HD + (long long)hd * D + j;
+    const float4 a0 = reinterpret_cast<const float4*>(a)[0], a1 = reinterpret_cast<const float4*>(a)[1];
+    const float4 b0 = reinterpret_cast<const float4*>(a + half)[0], b1 = reinterpret_cast<const float4*>(a + half)[1];
+    const float fa_in[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+    const float fb_in[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+    const int p = pos[t];
+    const float4 c0 = *reinterpret_cast<const float4*>(cs + (size_t)p * half + j);
+    const float4 c1 = *reinterpret_cast<const float4*>(cs + (size_t)p * half + j + 4);
+    const float4 s0 = *reinterpret_cast<const float4*>(sn + (size_t)p * half + j);
+    const float4 s1 = *reinterpret_cast<const float4*>(sn + (size_t)p * half + j + 4);
+    const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    const float sg[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+    float oa[8], ob[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float fa = __bfloat162float(__float2bfloat16(fa_in[k]));
+      const float fb = __bfloat162float(__float2bfloat16(fb_in[k]));
+      const float sk = sg[k] * -1.f;                       // the transposed rotation
+      oa[k] = __fmaf_rn(fa, c[k], -__fmul_rn(fb, sk));
+      ob[k] = __fmaf_rn(fb, c[k], __fmul_rn(fa, sk));
+    }
+    uint4 o1, o2;
+    o1.x = pack_bf16x2(oa[0], oa[1]); o1.y = pack_bf16x2(oa[2], oa[3]);
+    o1.z = pack_bf16x2(oa[4], oa[5]); o1.w = pack_bf16x2(oa[6], oa[7]);
+    o2.x = pack_bf16x2(ob[0], ob[1]); o2.y = pack_bf16x2(ob[2], ob[3]);
+    o2.z = pack_bf16x2(ob[4], ob[5]); o2.w = pack_bf16x2(ob[6], ob[7]);
+    __nv_bfloat16* dst = dqkv + t * width + (long long)hd * D + j;
+    *reinterpret_cast<uint4*>(dst) = o1;
+    *reinterpret_cast<uint4*>(dst + half) = o2;
+  }
+}
+
 template <int D>
 static int launch_bwd(const void* dout, const void* qkv, const void* out, const float* lse, float* delta, void* dqkv,
-                      float* dq_acc, int B, int L, int H, int Hkv, cudaStream_t st) {
+                      float* dq_acc, int B, int L, int H, int Hkv, const int* pos, const float* cos_tab,
+                      const float* sin_tab, cudaStream_t st) {
   using C = Cfg<D>;
   const long long width = (long long)(H + 2 * Hkv) * D;
   const long long T = (long long)B * L;
@@ -557,11 +607,16 @@ static int launch_bwd(const void* dout, const void* qkv, const void* out, const 
   kern<<<grid, NTHREADS, C::SMEM_BYTES, st>>>(tmQKV, tmDO, tmDQ, p, device_err_word());
   B200_CUDA_CHECK(cudaGetLastError());
   {
-    long long work = T * (HD >> 3);
+    const bool rot = pos != nullptr;
+    long long work = rot ? T * (HD >> 4) : T * (HD >> 3);
     long long blocks = (work + 255) / 256;
     const long long cap = (long long)sm_count() * 8;
     if (blocks > cap) blocks = cap;
-    dq_convert_kernel<<<(unsigned)blocks, 256, 0, st>>>(dq_acc, (__nv_bfloat16*)dqkv, T, (int)HD, width);
+    if (rot)
+      dq_convert_rope_kernel<<<(unsigned)blocks, 256, 0, st>>>(dq_acc, (__nv_bfloat16*)dqkv, pos, cos_tab, sin_tab, T, H,
+                                                              D, width);
+    else
+      dq_convert_kernel<<<(unsigned)blocks, 256, 0, st>>>(dq_acc, (__nv_bfloat16*)dqkv, T, (int)HD, width);
     B200_CUDA_CHECK(cudaGetLastError());
   }
   return B200_OK;
@@ -577,7 +632,40 @@ extern "C" int b200_flash_attn_bwd(const void* dout, const void* qkv, const void
   if (!dout || !qkv || !out || !lse || !delta || !dqkv || !dq_acc || B <= 0 || L <= 0 || H <= 0 || Hkv <= 0 ||
       (H % Hkv) != 0)
     return B200_ERR_ARG;
-  if (D == 64) return fab::launch_bwd<64>(dout, qkv, out, lse, delta, dqkv, dq_acc, B, L, H, Hkv, st);
-  if (D == 128) return fab::launch_bwd<128>(dout, qkv, out, lse, delta, dqkv, dq_acc, B, L, H, Hkv, st);
+  if (D == 64) return fab::launch_bwd<64>(dout, qkv, out, lse, delta, dqkv, dq_acc, B, L, H, Hkv, nullptr, nullptr, nullptr, st);
+  if (D == 128)
+    return fab::launch_bwd<128>(dout, qkv, out, lse, delta, dqkv, dq_acc, B, L, H, Hkv, nullptr, nullptr, nullptr, st);
   return B200_ERR_ARG;
+}
+
+// The same, with the inverse rotary embedding of the QUERY heads applied where the fp32 dQ accumulator is converted to
+// bf16 (pos int32 [B*L]; cos / sin fp32 [max_pos, D/2]). The key heads' gradient comes out of the main kernel's epilogue
+// and is rotated by the caller.
+extern "C" int b200_flash_attn_bwd_rope(const void* dout, const void* qkv, const void* out, const float* lse,
+                                        float* delta, void* dqkv, float* dq_acc, const int* pos, const float* cos_tab,
+                                        const float* sin_tab, int B, int L, int H, int Hkv, int D, cudaStream_t st) {
+  using namespace b200;
+  if (!dout || !qkv || !out || !lse || !delta || !dqkv || !dq_acc || !pos || !cos_tab || !sin_tab || B <= 0 || L <= 0 ||
+      H <= 0 || Hkv <= 0 || (H % Hkv) != 0)
+    return B200_ERR_ARG;
+  if (D == 64) return fab::launch_bwd<64>(dout, qkv, out, lse, delta, dqkv, dq_acc, B, L, H, Hkv, pos, cos_tab, sin_tab, st);
+  if (D == 128)
+    return fab::launch_bwd<128>(dout, qkv, out, lse, delta, dqkv, dq_acc, B, L, H, Hkv, pos, cos_tab, sin_tab, st);
+  return B200_ERR_ARG;
+}
+
+// The conversion pass alone (fp32 dQ accumulator -> bf16 query columns of dqkv with the inverse rotation): exported so
+// that its bit-exactness against convert + rope kernel can be tested on a given accumulator.
+extern "C" int b200_dq_convert_rope(const float* acc, void* dqkv, const int* pos, const float* cos_tab,
+                                    const float* sin_tab, long long T, int H, int D, long long width, cudaStream_t st) {
+  using namespace b200;
+  if (!acc || !dqkv || !pos || !cos_tab || !sin_tab || T <= 0 || H <= 0 || (D != 64 && D != 128)) return B200_ERR_ARG;
+  long long work = T * ((long long)H * D >> 4);
+  long long blocks = (work + 255) / 256;
+  const long long cap = (long long)sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  fab::dq_convert_rope_kernel<<<(unsigned)blocks, 256, 0, st>>>(acc, (__nv_bfloat16*)dqkv, pos, cos_tab, sin_tab, T, H, D,
+                                                              width);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200_OK;
 }

@@ -139,9 +139,8 @@ class AttnBlockFn(torch.autograd.Function):
         dh1 = dh1.contiguous()
         g_o = _ll._wgrad(dh1, att, w_o, s_o)
         datt = basic.linear_dgrad(dh1, w_o)
-        dqkv = attention.attention_bwd(datt, qkv, att, lse, B, L, H, Hkv, d)
+        dqkv = attention.attention_bwd_unrotated(datt, qkv, att, lse, B, L, H, Hkv, d, pos, cos, sin)
         del datt
-        basic.rope_(dqkv, pos, cos, sin, H + Hkv, d, inverse=True)
         g_qn = g_kn = None
         if w_qn is not None:
             dwq, dwk = basic.headnorm_bwd_(dqkv, qkv_raw, w_qn, w_kn, rstd_qk, H, Hkv, d)

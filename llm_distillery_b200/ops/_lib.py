@@ -66,7 +66,7 @@ _SIGS = {
 
 
 # device kernels launched by one call of each exported launcher (default 1); used to count launches
-KERNELS_PER_CALL = {"b200_rmsnorm_bwd": 2, "b200_flash_attn_bwd": 3, "b200_head_num_tiles": 0, "b200_sm_count": 0,
+KERNELS_PER_CALL = {"b200_rmsnorm_bwd": 2, "b200_flash_attn_bwd": 3, "b200_flash_attn_bwd_rope": 3, "b200_head_num_tiles": 0, "b200_sm_count": 0,
                     "b200_rmsnorm_bwd_blocks": 0, "b200_last_cuda_error": 0, "b200_take_device_error": 0,
                     "b200_gemm_reset_split_sync": 0, "b200_headnorm_bwd_blocks": 0, "b200_headnorm_bwd": 2}
 LAUNCH_COUNT = [0]

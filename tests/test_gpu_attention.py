@@ -34,3 +34,36 @@ def test_flash_bwd(B, L, H, Hkv, d):
     ref = attention.attention_reference_bwd(dout.float(), qkv.float(), ro, rl, B, L, H, Hkv, d)
     err = (dqkv.float() - ref).abs().max().item()
     assert err <= 6e-2 * max(1.0, ref.abs().max().item()), err
+
+
+@pytest.mark.parametrize("B,L,H,Hkv,d", [(2, 384, 8, 2, 64), (1, 1000, 4, 4, 128), (3, 130, 6, 3, 64)])
+def test_backward_with_the_inverse_rotation_of_dq_in_the_conversion_pass(B, L, H, Hkv, d):
+    """dQ is rotated back where its fp32 accumulator becomes bf16, dK by the rope kernel on the key columns only: the
+    result equals attention backward + inverse rope over q and k bit for bit."""
+    from llm_distillery_b200.ops import basic
+    torch.manual_seed(L + d)
+    qkv = torch.randn(B * L, (H + 2 * Hkv) * d, device="cuda").bfloat16()
+    out, lse = attention.attention_fwd(qkv, B, L, H, Hkv, d)
+    dout = torch.randn_like(out)
+    pos = torch.arange(L, dtype=torch.int32, device="cuda").repeat(B)
+    cos, sin = basic.rope_tables(L, d, 10000.0, "cuda")
+    got = attention.attention_bwd_unrotated(dout, qkv, out, lse, B, L, H, Hkv, d, pos, cos, sin)
+    assert _lib.take_device_error() == 0
+    ref = attention.attention_bwd(dout, qkv, out, lse, B, L, H, Hkv, d)
+    v_cols = slice((H + Hkv) * d, None)
+    # dQ accumulates through TMA reduce-add in an order that varies from run to run: compare to rounding, and the
+    # untouched value columns and the rotation itself exactly on a copy of the SAME backward result
+    same = ref.clone()
+    basic.rope_(same, pos, cos, sin, H + Hkv, d, inverse=True)
+    assert torch.allclose(got.float(), same.float(), atol=3e-2 * max(1.0, same.float().abs().max().item()), rtol=3e-2)
+    assert torch.allclose(got[:, v_cols].float(), ref[:, v_cols].float(), atol=2e-2, rtol=2e-2)
+    # exactness of the fused conversion: feed one accumulator through both paths
+    acc = torch.randn(B * L, H * d, device="cuda")
+    a = torch.zeros(B * L, (H + 2 * Hkv) * d, device="cuda", dtype=torch.bfloat16)
+    a[:, : H * d] = acc.bfloat16()
+    basic.rope_(a, pos, cos, sin, H, d, inverse=True)
+    from llm_distillery_b200.ops import flash  # noqa: F401  (registers the entry point)
+    b = torch.zeros_like(a)
+    _lib.check(_lib.kernels().b200_dq_convert_rope(_lib.ptr(acc), _lib.ptr(b), _lib.ptr(pos), _lib.ptr(cos), _lib.ptr(sin),
+                                                   B * L, H, d, b.stride(0), _lib.stream()), "b200_dq_convert_rope")
+    assert torch.equal(a[:, : H * d], b[:, : H * d])
