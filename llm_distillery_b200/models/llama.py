@@ -43,7 +43,9 @@ class LlamaConfig:
     num_local_experts: int = 0        # > 0: every layer's MLP is that many SwiGLU experts behind a linear router
     num_experts_per_tok: int = 2
     moe_renormalize: bool = True      # router weights renormalised over the chosen experts (Mixtral; Qwen3-MoE norm_topk_prob)
-    attention_bias: bool = False      # bias on the q/k/v projections (Qwen2 family); o_proj and the MLP have none
+    attention_bias: bool = False      # bias on the q/k/v projections (Qwen2 family; Llama configs with attention_bias)
+    o_bias: bool = False              # bias on o_proj as well (HuggingFace Llama's attention_bias = true, e.g. Granite code)
+    mlp_bias: bool = False            # bias on gate / up / down projections (HuggingFace Llama's mlp_bias)
     rope_scaling: dict | None = None  # HuggingFace dict; types default / linear / llama3 / yarn (ops.basic.rope_tables)
     head_dim_override: int | None = None   # HuggingFace ``head_dim`` when it is not hidden_size / num_attention_heads
     qk_norm: bool = False             # Qwen3: RMSNorm over every query and key head (one weight each) before RoPE
@@ -71,6 +73,10 @@ class LlamaConfig:
             per_layer += self.q_size + 2 * self.kv_size
         if self.qk_norm:
             per_layer += 2 * self.head_dim
+        if self.o_bias:
+            per_layer += h
+        if self.mlp_bias:
+            per_layer += 2 * f + h
         return Lr * per_layer + V * h * (1 if self.tie_word_embeddings else 2) + h
 
     def flops_per_token_fwd(self, seq_len: int) -> float:
@@ -109,7 +115,7 @@ class LlamaConfig:
         elif self.model_type == "phi3":
             d.pop("attention_bias")
             d.update(architectures=["Phi3ForCausalLM"], hidden_act="silu", torch_dtype="bfloat16")
-        elif self.attention_bias:     # q/k/v bias without o_proj bias is the Qwen2 layout in HuggingFace terms
+        elif self.attention_bias and not self.o_bias:     # q/k/v bias without o_proj bias is the Qwen2 layout in HuggingFace terms
             d.pop("attention_bias")
             d.update(architectures=["Qwen2ForCausalLM"], model_type="qwen2", hidden_act="silu", torch_dtype="bfloat16",
                      use_sliding_window=False)
@@ -119,6 +125,11 @@ class LlamaConfig:
         else:
             d.update(architectures=["LlamaForCausalLM"], hidden_act="silu", torch_dtype="bfloat16",
                      attention_bias=False, mlp_bias=False)
+        d.pop("o_bias")
+        d.pop("mlp_bias", None)
+        ob, mb = self.o_bias, self.mlp_bias
+        if ob or mb:          # HuggingFace's Llama: attention_bias covers q, k, v AND o
+            d.update(architectures=["LlamaForCausalLM"], model_type="llama", attention_bias=bool(ob), mlp_bias=bool(mb))
         return {**extra, **d}
 
     _KNOWN_TYPES = ("llama", "mistral", "qwen2", "phi3", "mixtral", "qwen3", "qwen3_moe")
@@ -169,10 +180,13 @@ class LlamaConfig:
         if mt == "qwen2":
             kw["attention_bias"] = True
         elif kw.get("attention_bias"):
-            raise NotImplementedError("attention_bias on a Llama config also puts a bias on o_proj, which is not built; "
-                                      "q/k/v-only bias (model_type qwen2) is")
+            if mt not in ("llama", "mistral"):
+                raise NotImplementedError(f"attention_bias on model_type {mt!r} is not built")
+            kw["o_bias"] = True            # HuggingFace's Llama puts the bias on q, k, v and o
         if d.get("mlp_bias"):
-            raise NotImplementedError("mlp_bias is not supported")
+            if mt not in ("llama", "mistral"):
+                raise NotImplementedError(f"mlp_bias on model_type {mt!r} is not built")
+            kw["mlp_bias"] = True
         if d.get("hidden_act", "silu") not in ("silu", "swish"):
             raise NotImplementedError(f"hidden_act {d['hidden_act']!r}: only SwiGLU (silu) is built")
         if float(d.get("partial_rotary_factor", 1.0) or 1.0) != 1.0:
@@ -275,6 +289,17 @@ def _wgrad(dy: torch.Tensor, x: torch.Tensor, w: torch.Tensor, slot):
     return basic.linear_wgrad(dy, x, out_dtype=w.dtype)
 
 
+def _bias_grad(dy: torch.Tensor, b: torch.Tensor | None, slot):
+    """Gradient of a bias added to every row of a GEMM output: the column sums of dy."""
+    if b is None or not b.requires_grad:
+        return None
+    if slot is not None:
+        basic.bias_grad(dy, out=slot.buf, accumulate=not slot.fresh)
+        slot.fresh = False
+        return None
+    return basic.bias_grad(dy).to(b.dtype)
+
+
 def _vec_grad(dw: torch.Tensor, w: torch.Tensor, slot):
     if not w.requires_grad:
         return None
@@ -332,7 +357,8 @@ class DecoderLayerFn(torch.autograd.Function):
     """h_out = h + Attn(RMSNorm(h)) ; then + MLP(RMSNorm(.)) - one node, explicit backward."""
 
     @staticmethod
-    def forward(ctx, h, pos, cos, sin, w_ln1, w_qkv, w_o, w_ln2, w_gu, w_d, meta, b_qkv=None, w_qn=None, w_kn=None):
+    def forward(ctx, h, pos, cos, sin, w_ln1, w_qkv, w_o, w_ln2, w_gu, w_d, meta, b_qkv=None, w_qn=None, w_kn=None,
+                b_o=None, b_gu=None, b_d=None):
         B, L, H, Hkv, d, eps, recompute = meta
         n1, _, rstd1 = basic.rmsnorm_fwd(h, w_ln1, eps)
         qk_saved = ()
@@ -349,9 +375,19 @@ class DecoderLayerFn(torch.autograd.Function):
             basic.rope_(qkv, pos, cos, sin, H + Hkv, d)      # q and k heads are adjacent columns
         att, lse = attention.attention_fwd(qkv, B, L, H, Hkv, d)
         h1 = basic.linear_fwd(att, w_o, residual=h)
+        if b_o is not None:
+            basic.bias_add_(h1, b_o)
         n2, _, rstd2 = basic.rmsnorm_fwd(h1, w_ln2, eps)
-        gu, act = basic.linear_swiglu_fwd(n2, w_gu)
+        if b_gu is None:
+            gu, act = basic.linear_swiglu_fwd(n2, w_gu)
+        else:
+            gu = basic.bias_add_(basic.linear_fwd(n2, w_gu), b_gu)
+            act = basic.swiglu_fwd(gu)
         h2 = basic.linear_fwd(act, w_d, residual=h1)
+        if b_d is not None:
+            basic.bias_add_(h2, b_d)
+        ctx.more_b = (b_o, b_gu, b_d)
+        ctx.more_b_slots = tuple(_slot(b) if b is not None else None for b in ctx.more_b)
         ctx.meta = meta
         ctx.weights = (w_ln1, w_qkv, w_o, w_ln2, w_gu, w_d)
         ctx.slots = tuple(_slot(w) for w in ctx.weights)
@@ -391,23 +427,34 @@ class DecoderLayerFn(torch.autograd.Function):
                 basic.rope_(qkv, pos, cos, sin, H + Hkv, d)
             att, lse = attention.attention_fwd(qkv, B, L, H, Hkv, d)
             h1 = basic.linear_fwd(att, w_o, residual=h)
+            if ctx.more_b[0] is not None:
+                basic.bias_add_(h1, ctx.more_b[0])
             n2, _, rstd2 = basic.rmsnorm_fwd(h1, w_ln2, eps)
-            gu, act = basic.linear_swiglu_fwd(n2, w_gu)
+            if ctx.more_b[1] is None:
+                gu, act = basic.linear_swiglu_fwd(n2, w_gu)
+            else:
+                gu = basic.bias_add_(basic.linear_fwd(n2, w_gu), ctx.more_b[1])
+                act = basic.swiglu_fwd(gu)
         elif w_qn is not None:
             h, pos, cos, sin, rstd1, n1, qkv, att, lse, h1, rstd2, n2, gu, act, qkv_raw, rstd_qk = ctx.saved_tensors
         else:
             h, pos, cos, sin, rstd1, n1, qkv, att, lse, h1, rstd2, n2, gu, act = ctx.saved_tensors
         dh2 = dh2.contiguous()
+        b_o, b_gu, b_d = ctx.more_b
+        sb_o, sb_gu, sb_d = ctx.more_b_slots
         # MLP branch
+        g_bd = _bias_grad(dh2, b_d, sb_d)
         g_d = _wgrad(dh2, act, w_d, s_d)
         del act
         dgu = basic.linear_dgrad_swiglu_bwd(dh2, w_d, gu)     # dgrad of the down projection + SwiGLU backward
+        g_bgu = _bias_grad(dgu, b_gu, sb_gu)
         g_gu = _wgrad(dgu, n2, w_gu, s_gu)
         dn2 = basic.linear_dgrad(dgu, w_gu)
         del dgu
         dh1, dw2 = basic.rmsnorm_bwd(dn2, h1, w_ln2, rstd2, dres=dh2)
         g_ln2 = _vec_grad(dw2, w_ln2, s_ln2)
         # attention branch
+        g_bo = _bias_grad(dh1, b_o, sb_o)
         g_o = _wgrad(dh1, att, w_o, s_o)
         datt = basic.linear_dgrad(dh1, w_o)
         dqkv = attention.attention_bwd_unrotated(datt, qkv, att, lse, B, L, H, Hkv, d, pos, cos, sin)
@@ -431,7 +478,7 @@ class DecoderLayerFn(torch.autograd.Function):
         g_ln1 = _vec_grad(dw1, w_ln1, s_ln1)
         if LAYER_BACKWARD_DONE[0] is not None:
             LAYER_BACKWARD_DONE[0](w_ln1)
-        return dh, None, None, None, g_ln1, g_qkv, g_o, g_ln2, g_gu, g_d, None, g_b, g_qn, g_kn
+        return dh, None, None, None, g_ln1, g_qkv, g_o, g_ln2, g_gu, g_d, None, g_b, g_qn, g_kn, g_bo, g_bgu, g_bd
 
 
 class FinalNormFn(torch.autograd.Function):
@@ -479,6 +526,13 @@ class LlamaDecoderLayer(nn.Module):
             self.q_norm = nn.Parameter(torch.ones(cfg.head_dim, **kw))
             self.k_norm = nn.Parameter(torch.ones(cfg.head_dim, **kw))
         self.o_proj = nn.Parameter(torch.empty(h, cfg.q_size, **kw))
+        if cfg.o_bias:
+            self.o_bias = nn.Parameter(torch.zeros(h, **kw))
+        if cfg.mlp_bias:
+            if cfg.num_local_experts:
+                raise NotImplementedError("mlp_bias with experts is not built")
+            self.gate_up_bias = nn.Parameter(torch.zeros(2 * f, **kw))
+            self.down_bias = nn.Parameter(torch.zeros(h, **kw))
         self.post_attention_layernorm = nn.Parameter(torch.ones(h, **kw))
         E = cfg.num_local_experts
         if E:       # sparse mixture of experts: a router and E stacked expert matrices (models/moe.py)
@@ -514,7 +568,7 @@ class LlamaModel(nn.Module):
     def init_weights(self, seed: int = 0, std: float = 0.02) -> "LlamaModel":
         gens: dict = {}
         for name, p in self.named_parameters():
-            if name.endswith("qkv_bias"):
+            if name.endswith("_bias"):
                 dev = p.device
                 if dev not in gens:
                     gens[dev] = torch.Generator(device=dev).manual_seed(seed)
@@ -579,7 +633,8 @@ class LlamaModel(nn.Module):
             h = DecoderLayerFn.apply(h, pos, cos, sin, layer.input_layernorm, layer.qkv_proj, layer.o_proj,
                                      layer.post_attention_layernorm, layer.gate_up_proj, layer.down_proj, meta,
                                      getattr(layer, "qkv_bias", None), getattr(layer, "q_norm", None),
-                                     getattr(layer, "k_norm", None))
+                                     getattr(layer, "k_norm", None), getattr(layer, "o_bias", None),
+                                     getattr(layer, "gate_up_bias", None), getattr(layer, "down_bias", None))
         if pre is not None:
             pre(self.norm, False)
         return FinalNormFn.apply(h, self.norm, cfg.rms_norm_eps)
@@ -626,11 +681,17 @@ class LlamaModel(nn.Module):
                 vc[:, c0:c0 + n] = qkv[:, (H + Hkv) * d:].reshape(B, n, kv)
                 att = attention.attention_fwd_cached(qkv, kc, vc, B, n, c0, H, Hkv, d)
                 h1 = basic.linear_fwd(att, layer.o_proj, residual=h)
+                if cfg.o_bias:
+                    basic.bias_add_(h1, layer.o_bias)
                 n2, _, _ = basic.rmsnorm_fwd(h1, layer.post_attention_layernorm, cfg.rms_norm_eps)
                 if cfg.num_local_experts:
                     from .moe import moe_mlp
                     h = h1 + moe_mlp(n2, layer.router, layer.gate_up_proj, layer.down_proj, cfg.num_experts_per_tok,
                                      cfg.moe_renormalize)
+                    continue
+                if cfg.mlp_bias:
+                    act = basic.swiglu_fwd(basic.bias_add_(basic.linear_fwd(n2, layer.gate_up_proj), layer.gate_up_bias))
+                    h = basic.bias_add_(basic.linear_fwd(act, layer.down_proj, residual=h1), layer.down_bias)
                     continue
                 _, act = basic.linear_swiglu_fwd(n2, layer.gate_up_proj)
                 h = basic.linear_fwd(act, layer.down_proj, residual=h1)
@@ -671,7 +732,13 @@ class LlamaModel(nn.Module):
                 yield pre + "self_attn.q_norm.weight", l.q_norm, None
                 yield pre + "self_attn.k_norm.weight", l.k_norm, None
             yield pre + "self_attn.o_proj.weight", l.o_proj, None
+            if cfg.o_bias:
+                yield pre + "self_attn.o_proj.bias", l.o_bias, None
             yield pre + "post_attention_layernorm.weight", l.post_attention_layernorm, None
+            if cfg.mlp_bias:
+                yield pre + "mlp.gate_proj.bias", l.gate_up_bias, slice(0, f)
+                yield pre + "mlp.up_proj.bias", l.gate_up_bias, slice(f, 2 * f)
+                yield pre + "mlp.down_proj.bias", l.down_bias, None
             if cfg.num_local_experts and cfg.model_type == "qwen3_moe":
                 yield pre + "mlp.gate.weight", l.router, None
                 for e in range(cfg.num_local_experts):

@@ -94,7 +94,7 @@ def test_config_keys_survive_a_round_trip_and_unbuilt_variants_are_refused(tmp_p
     with pytest.raises(ValueError, match="attention window"):
         model(torch.randint(0, 320, (1, 129)))
     for bad in (dict(model_type="gemma2"), dict(hidden_act="gelu_pytorch_tanh"), dict(head_dim=20),
-                dict(partial_rotary_factor=0.5), dict(rope_scaling={"rope_type": "dynamic", "factor": 4.0}), dict(mlp_bias=True)):
+                dict(partial_rotary_factor=0.5), dict(rope_scaling={"rope_type": "dynamic", "factor": 4.0})):
         with pytest.raises(NotImplementedError):
             LlamaConfig.from_hf_dict(dict(_base(), **bad))
     # Qwen2 carries a window that is switched off
@@ -222,3 +222,50 @@ def test_phi3_longrope_matches_huggingface():
         assert torch.allclose(ours, ref, atol=4e-4, rtol=1e-3), (L, (ours - ref).abs().max())
     same = LlamaConfig.from_hf_dict(dict(d, rope_scaling=dict(scaling, type="su")))
     assert same.rope_scaling["rope_type"] == "longrope"
+
+
+def test_llama_with_attention_and_mlp_biases_matches_huggingface(tmp_path):
+    """HuggingFace's Llama with attention_bias (q, k, v and o) and mlp_bias (gate, up, down) - the Granite code models."""
+    d = dict(_base(), model_type="llama", attention_bias=True, mlp_bias=True)
+    cfg = LlamaConfig.from_hf_dict(d)
+    assert cfg.attention_bias and cfg.o_bias and cfg.mlp_bias
+    model = build_model(cfg, dtype=torch.float32, device="cpu", seed=12)
+    hf = tr.LlamaForCausalLM(tr.LlamaConfig(**_base(), attention_bias=True, mlp_bias=True, attn_implementation="eager",
+                                            tie_word_embeddings=False)).float()
+    res = hf.load_state_dict({k: v.clone() for k, v in model.to_hf_state_dict().items()}, strict=False)
+    assert not res.unexpected_keys and not [k for k in res.missing_keys if "rotary" not in k], res
+    x = torch.randint(0, 320, (2, 48))
+    ours, ref = model(x), hf(x).logits
+    assert torch.allclose(ours, ref, atol=3e-4, rtol=1e-3), (ours - ref).abs().max()
+    tgt = torch.randint(0, 320, (2 * 48,))
+    torch.nn.functional.cross_entropy(ours.reshape(-1, 320), tgt).backward()
+    torch.nn.functional.cross_entropy(ref.reshape(-1, 320), tgt).backward()
+    hf_grads = {n: p.grad for n, p in hf.named_parameters()}
+    seen = 0
+    for n, p, sl in model.named_hf_parameters():
+        g = p.grad if sl is None else p.grad[sl]
+        assert torch.allclose(g, hf_grads[n], atol=2e-5, rtol=2e-3), (n, (g - hf_grads[n]).abs().max())
+        seen += n.endswith(".bias")
+    assert seen == 2 * 7                                   # q, k, v, o, gate, up, down per layer
+    g0 = {n: p.grad.clone() for n, p in model.named_parameters()}
+    model.zero_grad()
+    model.grad_checkpointing = True
+    torch.nn.functional.cross_entropy(model(x).reshape(-1, 320), tgt).backward()
+    for n, p in model.named_parameters():
+        assert torch.allclose(p.grad, g0[n], atol=1e-6, rtol=1e-5), n
+    with torch.no_grad():
+        assert torch.allclose(model.hidden_states(x), model.hidden_states_chunked(x, 16), atol=2e-5, rtol=1e-4)
+    save_hf_model(model, str(tmp_path / "ours"))
+    c = json.load(open(tmp_path / "ours" / "config.json"))
+    assert c["model_type"] == "llama" and c["attention_bias"] is True and c["mlp_bias"] is True
+    back = load_hf_model(str(tmp_path / "ours"), dtype=torch.float32)
+    assert torch.equal(back(x), model(x))
+    with pytest.raises(NotImplementedError):
+        load_tp_weights(str(tmp_path / "ours"), 0, 2, dtype=torch.float32)
+    # the engine's flat gradient slots take the bias gradients too
+    from llm_distillery_b200.engine.trainer import DistillEngine, synthetic_batch
+    eng = DistillEngine(back, loss="kl", temperature=1.0, optimizer="adamw", lr=1e-2)
+    b0 = back.layers[0].down_bias.detach().clone()
+    hb = synthetic_batch(cfg.vocab_size, 2, 32, 8, seed=0)
+    l0 = eng.train_step([hb]); l1 = eng.train_step([hb])
+    assert l1 < l0 and not torch.equal(back.layers[0].down_bias, b0)
