@@ -69,23 +69,40 @@ def test_engine_trains_the_bias():
 
 
 @pytest.mark.gpu
-def test_gpu_kernels_follow_the_cpu_model():
-    """bf16 kernels (GEMM + bias add + RoPE + flash attention ...) against the fp32 CPU statement of the same model."""
-    cfg = LlamaConfig(vocab_size=512, hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=4,
-                      num_key_value_heads=2, max_position_embeddings=256, rope_theta=1e6, rms_norm_eps=1e-6,
-                      attention_bias=True, model_type="qwen2")
+@pytest.mark.parametrize("variant", ["qwen2", "qwen3", "llama with biases", "plain llama, long batch"])
+def test_gpu_kernels_follow_the_cpu_model(variant):
+    """bf16 kernels (GEMMs with their epilogues, bias add, per-head norms, RoPE, flash attention ...) against the fp32 CPU
+    statement of the same model, for the layer variants: q/k/v bias (Qwen2), per-head q/k norms (Qwen3), biases on every
+    projection (Llama with attention_bias / mlp_bias), and a plain layer with enough rows for the fused epilogues."""
+    kw = dict(vocab_size=512, hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=4,
+              num_key_value_heads=2, max_position_embeddings=1024, rope_theta=1e6, rms_norm_eps=1e-6)
+    if variant == "qwen2":
+        kw.update(attention_bias=True, model_type="qwen2")
+    elif variant == "qwen3":
+        kw.update(qk_norm=True, model_type="qwen3")
+    elif variant == "llama with biases":
+        kw.update(attention_bias=True, o_bias=True, mlp_bias=True)
+    cfg = LlamaConfig(**kw)
     cpu = build_model(cfg, dtype=torch.float32, device="cpu", seed=7)
+    with torch.no_grad():
+        g = torch.Generator().manual_seed(3)
+        for n, p in cpu.named_parameters():
+            if n.endswith("_bias"):
+                p.copy_(torch.randn(p.shape, generator=g) * 0.05)
+            elif n.endswith("q_norm") or n.endswith("k_norm"):
+                p.copy_(torch.empty(p.shape).uniform_(0.5, 1.5, generator=g))
     gpu = build_model(cfg, dtype=torch.bfloat16, device="cuda", seed=7)
     with torch.no_grad():
         for a, b in zip(gpu.parameters(), cpu.parameters()):
             a.copy_(b.to(torch.bfloat16))
             b.copy_(a.float().cpu())          # both sides hold the bf16-rounded weights
-    x = torch.randint(0, cfg.vocab_size, (2, 128))
+    x = torch.randint(0, cfg.vocab_size, (2, 640 if variant.startswith("plain") else 128))
     lc = cpu(x)
     lg = gpu(x.cuda())
     assert torch.allclose(lg.float().cpu(), lc, atol=6e-2, rtol=5e-2), (lg.float().cpu() - lc).abs().max()
     lc.square().mean().backward()
     lg.float().square().mean().backward()
-    gb_c = cpu.layers[0].qkv_bias.grad
-    gb_g = gpu.layers[0].qkv_bias.grad.float().cpu()
-    assert (gb_g - gb_c).abs().max() <= 0.05 * gb_c.abs().max() + 1e-4
+    for (n, pg), (_, pc) in zip(gpu.named_parameters(), cpu.named_parameters()):
+        gg, gc = pg.grad.float().cpu(), pc.grad
+        assert torch.isfinite(gg).all(), n
+        assert (gg - gc).abs().max() <= 0.06 * gc.abs().max() + 2e-4, (n, (gg - gc).abs().max(), gc.abs().max())
