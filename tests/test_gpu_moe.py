@@ -9,7 +9,7 @@ pytestmark = pytest.mark.gpu
 
 
 def _cos(a, b):
-    a, b = a.double().flatten().cpu(), b.double().flatten().cpu()
+    a, b = a.detach().double().flatten().cpu(), b.detach().double().flatten().cpu()
     return float((a @ b) / (a.norm() * b.norm() + 1e-30))
 
 
