@@ -96,6 +96,31 @@ def bench_gemm(M, N, K, layout, iters, compare=True):
     report(f"gemm_{layout}", ms, flops=2.0 * M * N * K, shape=[M, N, K], **extra)
 
 
+def bench_fused(rows, hidden, ffn, heads, kv_heads, dim, iters):
+    """The GEMMs whose epilogues absorb an elementwise kernel, each against its two-kernel path on the same operands:
+    gate / up projection + SwiGLU, down-projection dgrad + SwiGLU backward, q/k/v projection + rotary embedding."""
+    x = torch.randn(rows, hidden, device="cuda").bfloat16()
+    w_gu = (torch.randn(2 * ffn, hidden, device="cuda") * 0.02).bfloat16()
+    w_d = (torch.randn(hidden, ffn, device="cuda") * 0.02).bfloat16()
+    dy = torch.randn(rows, hidden, device="cuda").bfloat16()
+    gu, _ = basic.linear_swiglu_fwd(x, w_gu)
+    fl = 2.0 * rows * hidden * 2 * ffn
+    ms = timed(lambda: basic.linear_swiglu_fwd(x, w_gu), iters)
+    ms2 = timed(lambda: basic.swiglu_fwd(basic.linear_fwd(x, w_gu)), iters)
+    report("gate_up_gemm+swiglu", ms, flops=fl, shape=[rows, 2 * ffn, hidden], two_kernels_ms=round(ms2, 4))
+    ms = timed(lambda: basic.linear_dgrad_swiglu_bwd(dy, w_d, gu), iters)
+    ms2 = timed(lambda: basic.swiglu_bwd(gu, basic.linear_dgrad(dy, w_d)), iters)
+    report("down_dgrad+swiglu_bwd", ms, flops=2.0 * rows * hidden * ffn, shape=[rows, ffn, hidden],
+           two_kernels_ms=round(ms2, 4))
+    n = (heads + 2 * kv_heads) * dim
+    w_qkv = (torch.randn(n, hidden, device="cuda") * 0.02).bfloat16()
+    pos = (torch.arange(rows, device="cuda", dtype=torch.int32) % 2048)
+    cos, sin = basic.rope_tables(2048, dim, 10000.0, "cuda")
+    ms = timed(lambda: basic.linear_rope_fwd(x, w_qkv, pos, cos, sin, heads + kv_heads, dim), iters)
+    ms2 = timed(lambda: basic.rope_(basic.linear_fwd(x, w_qkv), pos, cos, sin, heads + kv_heads, dim), iters)
+    report("qkv_gemm+rope", ms, flops=2.0 * rows * hidden * n, shape=[rows, n, hidden], two_kernels_ms=round(ms2, 4))
+
+
 def _sm_clock_mhz():
     """SM clock right now (read through NVML; None when it is not available)."""
     try:
@@ -292,8 +317,12 @@ def main():
     t = sub.add_parser("topk")
     t.add_argument("--rows", type=int, default=4096); t.add_argument("--vocab", type=int, default=32000)
     t.add_argument("--topk", type=int, default=200)
+    fu = sub.add_parser("fused")
+    fu.add_argument("--rows", type=int, default=16384); fu.add_argument("--hidden", type=int, default=2048)
+    fu.add_argument("--ffn", type=int, default=5632); fu.add_argument("--heads", type=int, default=32)
+    fu.add_argument("--kv-heads", type=int, default=4); fu.add_argument("--dim", type=int, default=64)
     sub.add_parser("all")
-    for s in (g, a, h, e, t, sub.choices["all"]):
+    for s in (g, a, h, e, t, fu, sub.choices["all"]):
         s.add_argument("--iters", type=int, default=20)
     args = ap.parse_args()
     if args.cmd == "gemm":
@@ -308,6 +337,8 @@ def main():
     elif args.cmd == "topk":
         bench_topk_family(args.rows, args.vocab, args.topk, args.iters)
         bench_trie_walk(args.iters)
+    elif args.cmd == "fused":
+        bench_fused(args.rows, args.hidden, args.ffn, args.heads, args.kv_heads, args.dim, args.iters)
     else:
         for shp, lay in [((8192, 8192, 8192), "nt"), ((16384, 2560, 2048), "nt"), ((16384, 2048, 2048), "nt"),
                          ((16384, 11264, 2048), "nt"), ((16384, 2048, 5632), "nt"), ((16384, 2048, 2560), "nn"),
@@ -318,6 +349,7 @@ def main():
         bench_attn(2, 4096, 32, 8, 128, args.iters, True)
         bench_head(16384, 2048, 32000, 200, max(3, args.iters // 4))
         bench_elementwise(16384, 2048, 5632, args.iters)
+        bench_fused(16384, 2048, 5632, 32, 4, 64, args.iters)
         bench_topk_family(4096, 32000, 200, max(3, args.iters // 2))
         bench_trie_walk(max(3, args.iters // 2))
 
