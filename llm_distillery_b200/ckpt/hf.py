@@ -264,6 +264,8 @@ def load_tp_weights(path: str, rank: int, tp: int, vocab: int | None = None, dty
                          "tensors. Collect with tp_size = 1 (the dequantised model fits one GPU) or export the "
                          "checkpoint to bf16 first.")
     cfg = LlamaConfig.from_pretrained(path)
+    if cfg.model_type == "granite":
+        raise NotImplementedError("tensor-parallel collection does not apply Granite's multipliers: use tp_size = 1")
     if cfg.o_bias or cfg.mlp_bias:
         raise NotImplementedError("tensor-parallel collection does not carry o_proj / MLP biases: use tp_size = 1")
     if cfg.num_local_experts:

@@ -46,6 +46,12 @@ class LlamaConfig:
     attention_bias: bool = False      # bias on the q/k/v projections (Qwen2 family; Llama configs with attention_bias)
     o_bias: bool = False              # bias on o_proj as well (HuggingFace Llama's attention_bias = true, e.g. Granite code)
     mlp_bias: bool = False            # bias on gate / up / down projections (HuggingFace Llama's mlp_bias)
+    # Granite: the embedding output, the attention scores, each branch before it joins the residual stream and the
+    # logits carry fixed multipliers
+    embedding_multiplier: float = 1.0
+    attention_multiplier: float | None = None      # replaces 1 / sqrt(head_dim)
+    residual_multiplier: float = 1.0
+    logits_scaling: float = 1.0                    # logits are DIVIDED by this
     rope_scaling: dict | None = None  # HuggingFace dict; types default / linear / llama3 / yarn (ops.basic.rope_tables)
     head_dim_override: int | None = None   # HuggingFace ``head_dim`` when it is not hidden_size / num_attention_heads
     qk_norm: bool = False             # Qwen3: RMSNorm over every query and key head (one weight each) before RoPE
@@ -100,6 +106,7 @@ class LlamaConfig:
             d.pop("num_local_experts")
             d.pop("num_experts_per_tok")
         qk = d.pop("qk_norm")
+        gran = {k: d.pop(k) for k in ("embedding_multiplier", "attention_multiplier", "residual_multiplier", "logits_scaling")}
         if self.model_type == "qwen3_moe":      # HuggingFace's names: num_experts, moe_intermediate_size, norm_topk_prob
             d.update(architectures=["Qwen3MoeForCausalLM"], hidden_act="silu", torch_dtype="bfloat16",
                      use_sliding_window=False, head_dim=self.head_dim, num_experts=d.pop("num_local_experts"),
@@ -130,9 +137,13 @@ class LlamaConfig:
         ob, mb = self.o_bias, self.mlp_bias
         if ob or mb:          # HuggingFace's Llama: attention_bias covers q, k, v AND o
             d.update(architectures=["LlamaForCausalLM"], model_type="llama", attention_bias=bool(ob), mlp_bias=bool(mb))
+        if self.model_type == "granite":
+            d.update(architectures=["GraniteForCausalLM"], model_type="granite", **gran)
+            if d.get("attention_multiplier") is None:
+                d["attention_multiplier"] = 1.0 / math.sqrt(self.head_dim)
         return {**extra, **d}
 
-    _KNOWN_TYPES = ("llama", "mistral", "qwen2", "phi3", "mixtral", "qwen3", "qwen3_moe")
+    _KNOWN_TYPES = ("llama", "mistral", "qwen2", "phi3", "mixtral", "qwen3", "qwen3_moe", "granite")
 
     @classmethod
     def from_hf_dict(cls, d: dict) -> "LlamaConfig":
@@ -180,11 +191,11 @@ class LlamaConfig:
         if mt == "qwen2":
             kw["attention_bias"] = True
         elif kw.get("attention_bias"):
-            if mt not in ("llama", "mistral"):
+            if mt not in ("llama", "mistral", "granite"):
                 raise NotImplementedError(f"attention_bias on model_type {mt!r} is not built")
             kw["o_bias"] = True            # HuggingFace's Llama puts the bias on q, k, v and o
         if d.get("mlp_bias"):
-            if mt not in ("llama", "mistral"):
+            if mt not in ("llama", "mistral", "granite"):
                 raise NotImplementedError(f"mlp_bias on model_type {mt!r} is not built")
             kw["mlp_bias"] = True
         if d.get("hidden_act", "silu") not in ("silu", "swish"):
@@ -200,6 +211,9 @@ class LlamaConfig:
             kw["head_dim_override"] = int(hd)       # e.g. Mistral-Nemo: 5120 hidden, 32 heads of 128
         if mt == "qwen2" and not d.get("use_sliding_window", False):
             kw["sliding_window"] = None        # Qwen2 configs carry a window that is switched off
+        if mt != "granite":
+            for k in ("embedding_multiplier", "attention_multiplier", "residual_multiplier", "logits_scaling"):
+                kw.pop(k, None)           # other families may carry such keys with another meaning
         cfg = cls(**kw)
         if cfg.rope_scaling is not None:       # fail at load time, not at the first forward
             kind = cfg.rope_scaling.get("rope_type", cfg.rope_scaling.get("type"))
@@ -358,7 +372,7 @@ class DecoderLayerFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, h, pos, cos, sin, w_ln1, w_qkv, w_o, w_ln2, w_gu, w_d, meta, b_qkv=None, w_qn=None, w_kn=None,
-                b_o=None, b_gu=None, b_d=None):
+                b_o=None, b_gu=None, b_d=None, rmul=1.0):
         B, L, H, Hkv, d, eps, recompute = meta
         n1, _, rstd1 = basic.rmsnorm_fwd(h, w_ln1, eps)
         qk_saved = ()
@@ -374,18 +388,21 @@ class DecoderLayerFn(torch.autograd.Function):
                 qk_saved = (qkv_raw, rstd_qk)
             basic.rope_(qkv, pos, cos, sin, H + Hkv, d)      # q and k heads are adjacent columns
         att, lse = attention.attention_fwd(qkv, B, L, H, Hkv, d)
-        h1 = basic.linear_fwd(att, w_o, residual=h)
+        # rmul (Granite's residual_multiplier) scales a branch, bias included, before it joins the residual stream: it is
+        # the alpha of the GEMM whose epilogue adds the residual
+        h1 = basic.gemm(att, w_o, residual=h, alpha=rmul)
         if b_o is not None:
-            basic.bias_add_(h1, b_o)
+            basic.bias_add_(h1, b_o if rmul == 1.0 else b_o * rmul)
         n2, _, rstd2 = basic.rmsnorm_fwd(h1, w_ln2, eps)
         if b_gu is None:
             gu, act = basic.linear_swiglu_fwd(n2, w_gu)
         else:
             gu = basic.bias_add_(basic.linear_fwd(n2, w_gu), b_gu)
             act = basic.swiglu_fwd(gu)
-        h2 = basic.linear_fwd(act, w_d, residual=h1)
+        h2 = basic.gemm(act, w_d, residual=h1, alpha=rmul)
         if b_d is not None:
-            basic.bias_add_(h2, b_d)
+            basic.bias_add_(h2, b_d if rmul == 1.0 else b_d * rmul)
+        ctx.rmul = rmul
         ctx.more_b = (b_o, b_gu, b_d)
         ctx.more_b_slots = tuple(_slot(b) if b is not None else None for b in ctx.more_b)
         ctx.meta = meta
@@ -426,9 +443,9 @@ class DecoderLayerFn(torch.autograd.Function):
                     qkv, rstd_qk = basic.headnorm_fwd(qkv_raw, w_qn, w_kn, H, Hkv, d, eps)
                 basic.rope_(qkv, pos, cos, sin, H + Hkv, d)
             att, lse = attention.attention_fwd(qkv, B, L, H, Hkv, d)
-            h1 = basic.linear_fwd(att, w_o, residual=h)
+            h1 = basic.gemm(att, w_o, residual=h, alpha=ctx.rmul)
             if ctx.more_b[0] is not None:
-                basic.bias_add_(h1, ctx.more_b[0])
+                basic.bias_add_(h1, ctx.more_b[0] if ctx.rmul == 1.0 else ctx.more_b[0] * ctx.rmul)
             n2, _, rstd2 = basic.rmsnorm_fwd(h1, w_ln2, eps)
             if ctx.more_b[1] is None:
                 gu, act = basic.linear_swiglu_fwd(n2, w_gu)
@@ -442,11 +459,14 @@ class DecoderLayerFn(torch.autograd.Function):
         dh2 = dh2.contiguous()
         b_o, b_gu, b_d = ctx.more_b
         sb_o, sb_gu, sb_d = ctx.more_b_slots
-        # MLP branch
-        g_bd = _bias_grad(dh2, b_d, sb_d)
-        g_d = _wgrad(dh2, act, w_d, s_d)
+        # MLP branch (its gradient is the stream's gradient times the branch multiplier)
+        rmul = ctx.rmul
+        db2 = dh2 if rmul == 1.0 else dh2 * rmul
+        g_bd = _bias_grad(db2, b_d, sb_d)
+        g_d = _wgrad(db2, act, w_d, s_d)
         del act
-        dgu = basic.linear_dgrad_swiglu_bwd(dh2, w_d, gu)     # dgrad of the down projection + SwiGLU backward
+        dgu = basic.linear_dgrad_swiglu_bwd(db2, w_d, gu)     # dgrad of the down projection + SwiGLU backward
+        del db2
         g_bgu = _bias_grad(dgu, b_gu, sb_gu)
         g_gu = _wgrad(dgu, n2, w_gu, s_gu)
         dn2 = basic.linear_dgrad(dgu, w_gu)
@@ -454,9 +474,11 @@ class DecoderLayerFn(torch.autograd.Function):
         dh1, dw2 = basic.rmsnorm_bwd(dn2, h1, w_ln2, rstd2, dres=dh2)
         g_ln2 = _vec_grad(dw2, w_ln2, s_ln2)
         # attention branch
-        g_bo = _bias_grad(dh1, b_o, sb_o)
-        g_o = _wgrad(dh1, att, w_o, s_o)
-        datt = basic.linear_dgrad(dh1, w_o)
+        db1 = dh1 if rmul == 1.0 else dh1 * rmul
+        g_bo = _bias_grad(db1, b_o, sb_o)
+        g_o = _wgrad(db1, att, w_o, s_o)
+        datt = basic.linear_dgrad(db1, w_o)
+        del db1
         dqkv = attention.attention_bwd_unrotated(datt, qkv, att, lse, B, L, H, Hkv, d, pos, cos, sin)
         del datt
         g_qn = g_kn = None
@@ -478,7 +500,8 @@ class DecoderLayerFn(torch.autograd.Function):
         g_ln1 = _vec_grad(dw1, w_ln1, s_ln1)
         if LAYER_BACKWARD_DONE[0] is not None:
             LAYER_BACKWARD_DONE[0](w_ln1)
-        return dh, None, None, None, g_ln1, g_qkv, g_o, g_ln2, g_gu, g_d, None, g_b, g_qn, g_kn, g_bo, g_bgu, g_bd
+        return (dh, None, None, None, g_ln1, g_qkv, g_o, g_ln2, g_gu, g_d, None, g_b, g_qn, g_kn, g_bo, g_bgu, g_bd,
+                None)
 
 
 class FinalNormFn(torch.autograd.Function):
@@ -595,6 +618,12 @@ class LlamaModel(nn.Module):
                 n = min(n, int(sc.get("original_max_position_embeddings") or n))
             self._rope = basic.rope_tables(n, self.cfg.head_dim, self.cfg.rope_theta, device, self.cfg.rope_scaling,
                                            model_max_pos=self.cfg.max_position_embeddings, seq_len=need)
+            am = self.cfg.attention_multiplier
+            if am is not None and abs(am * math.sqrt(self.cfg.head_dim) - 1.0) > 1e-9:
+                # the attention kernels scale the scores by 1 / sqrt(d); a different multiplier rides on the rotation:
+                # queries and keys each take sqrt(multiplier * sqrt(d)), their products the multiplier over 1 / sqrt(d)
+                amp = math.sqrt(am * math.sqrt(self.cfg.head_dim))
+                self._rope = ((self._rope[0] * amp).contiguous(), (self._rope[1] * amp).contiguous())
             self._rope_regime = regime
         return self._rope
 
@@ -614,8 +643,11 @@ class LlamaModel(nn.Module):
         if pre is not None:
             pre(self.embed_tokens, False)
         h = EmbeddingFn.apply(ids, self.embed_tokens)
+        if cfg.embedding_multiplier != 1.0:
+            h = h * cfg.embedding_multiplier
         meta = (B, L, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.rms_norm_eps,
                 bool(self.grad_checkpointing and torch.is_grad_enabled()))
+        rmul = float(cfg.residual_multiplier)
         for layer in self.layers:
             if pre is not None:
                 pre(layer.input_layernorm, False)
@@ -634,10 +666,13 @@ class LlamaModel(nn.Module):
                                      layer.post_attention_layernorm, layer.gate_up_proj, layer.down_proj, meta,
                                      getattr(layer, "qkv_bias", None), getattr(layer, "q_norm", None),
                                      getattr(layer, "k_norm", None), getattr(layer, "o_bias", None),
-                                     getattr(layer, "gate_up_bias", None), getattr(layer, "down_bias", None))
+                                     getattr(layer, "gate_up_bias", None), getattr(layer, "down_bias", None), rmul)
         if pre is not None:
             pre(self.norm, False)
-        return FinalNormFn.apply(h, self.norm, cfg.rms_norm_eps)
+        y = FinalNormFn.apply(h, self.norm, cfg.rms_norm_eps)
+        # logits = y W^T / logits_scaling: the division rides on the hidden rows, which every head (fused loss, top-K
+        # collection, full logits) multiplies by the same matrix
+        return y if cfg.logits_scaling == 1.0 else y * (1.0 / cfg.logits_scaling)
 
     @torch.no_grad()
     def hidden_states_chunked(self, input_ids: torch.Tensor, chunk_len: int) -> torch.Tensor:
@@ -664,6 +699,8 @@ class LlamaModel(nn.Module):
             n = min(chunk_len, L - c0)
             pos = torch.arange(c0, c0 + n, dtype=torch.int32, device=dev).repeat(B)
             h = basic.embed_fwd(ids[:, c0:c0 + n].reshape(-1), self.embed_tokens)
+            if cfg.embedding_multiplier != 1.0:
+                h = h * cfg.embedding_multiplier
             for layer, (kc, vc) in zip(self.layers, caches):
                 if LAYER_WEIGHTS_PRE[0] is not None:
                     LAYER_WEIGHTS_PRE[0](layer.input_layernorm)
@@ -680,9 +717,10 @@ class LlamaModel(nn.Module):
                 kc[:, c0:c0 + n] = qkv[:, H * d:(H + Hkv) * d].reshape(B, n, kv)
                 vc[:, c0:c0 + n] = qkv[:, (H + Hkv) * d:].reshape(B, n, kv)
                 att = attention.attention_fwd_cached(qkv, kc, vc, B, n, c0, H, Hkv, d)
-                h1 = basic.linear_fwd(att, layer.o_proj, residual=h)
+                rm = float(cfg.residual_multiplier)
+                h1 = basic.gemm(att, layer.o_proj, residual=h, alpha=rm)
                 if cfg.o_bias:
-                    basic.bias_add_(h1, layer.o_bias)
+                    basic.bias_add_(h1, layer.o_bias if rm == 1.0 else layer.o_bias * rm)
                 n2, _, _ = basic.rmsnorm_fwd(h1, layer.post_attention_layernorm, cfg.rms_norm_eps)
                 if cfg.num_local_experts:
                     from .moe import moe_mlp
@@ -691,11 +729,14 @@ class LlamaModel(nn.Module):
                     continue
                 if cfg.mlp_bias:
                     act = basic.swiglu_fwd(basic.bias_add_(basic.linear_fwd(n2, layer.gate_up_proj), layer.gate_up_bias))
-                    h = basic.bias_add_(basic.linear_fwd(act, layer.down_proj, residual=h1), layer.down_bias)
+                    h = basic.bias_add_(basic.gemm(act, layer.down_proj, residual=h1, alpha=rm),
+                                        layer.down_bias if rm == 1.0 else layer.down_bias * rm)
                     continue
                 _, act = basic.linear_swiglu_fwd(n2, layer.gate_up_proj)
-                h = basic.linear_fwd(act, layer.down_proj, residual=h1)
+                h = basic.gemm(act, layer.down_proj, residual=h1, alpha=rm)
             y, _, _ = basic.rmsnorm_fwd(h, self.norm, cfg.rms_norm_eps)
+            if cfg.logits_scaling != 1.0:
+                y = y * (1.0 / cfg.logits_scaling)
             out[:, c0:c0 + n] = y.reshape(B, n, -1)
         return out.reshape(B * L, -1)
 

@@ -269,3 +269,49 @@ def test_llama_with_attention_and_mlp_biases_matches_huggingface(tmp_path):
     hb = synthetic_batch(cfg.vocab_size, 2, 32, 8, seed=0)
     l0 = eng.train_step([hb]); l1 = eng.train_step([hb])
     assert l1 < l0 and not torch.equal(back.layers[0].down_bias, b0)
+
+
+def test_granite_multipliers_match_huggingface(tmp_path):
+    """Granite: fixed multipliers on the embedding output, the attention scores, each branch and the logits (and
+    optionally biases on every projection)."""
+    mult = dict(embedding_multiplier=6.0, attention_multiplier=0.09, residual_multiplier=0.3, logits_scaling=4.0)
+    d = dict(_base(), model_type="granite", attention_bias=True, mlp_bias=True, **mult)
+    cfg = LlamaConfig.from_hf_dict(d)
+    assert cfg.residual_multiplier == 0.3 and cfg.logits_scaling == 4.0 and cfg.o_bias and cfg.mlp_bias
+    model = build_model(cfg, dtype=torch.float32, device="cpu", seed=13)
+    hf = tr.GraniteForCausalLM(tr.GraniteConfig(**_base(), attention_bias=True, mlp_bias=True, **mult,
+                                                attn_implementation="eager", tie_word_embeddings=False)).float()
+    res = hf.load_state_dict({k: v.clone() for k, v in model.to_hf_state_dict().items()}, strict=False)
+    assert not res.unexpected_keys and not [k for k in res.missing_keys if "rotary" not in k], res
+    x = torch.randint(0, 320, (2, 48))
+    ours, ref = model(x), hf(x).logits
+    assert torch.allclose(ours, ref, atol=3e-4, rtol=1e-3), (ours - ref).abs().max()
+    plain = build_model(LlamaConfig.from_hf_dict(dict(_base(), model_type="llama", attention_bias=True, mlp_bias=True)),
+                        dtype=torch.float32, device="cpu", seed=13)
+    assert (plain(x) - ref).abs().max() > 1e-2            # the multipliers matter
+    tgt = torch.randint(0, 320, (2 * 48,))
+    torch.nn.functional.cross_entropy(ours.reshape(-1, 320), tgt).backward()
+    torch.nn.functional.cross_entropy(ref.reshape(-1, 320), tgt).backward()
+    hf_grads = {n: p.grad for n, p in hf.named_parameters()}
+    for n, p, sl in model.named_hf_parameters():
+        g = p.grad if sl is None else p.grad[sl]
+        assert torch.allclose(g, hf_grads[n], atol=3e-5, rtol=3e-3), (n, (g - hf_grads[n]).abs().max())
+    g0 = {n: p.grad.clone() for n, p in model.named_parameters()}
+    model.zero_grad()
+    model.grad_checkpointing = True
+    torch.nn.functional.cross_entropy(model(x).reshape(-1, 320), tgt).backward()
+    for n, p in model.named_parameters():
+        assert torch.allclose(p.grad, g0[n], atol=1e-6, rtol=1e-5), n
+    with torch.no_grad():
+        assert torch.allclose(model.hidden_states(x), model.hidden_states_chunked(x, 16), atol=2e-5, rtol=1e-4)
+    save_hf_model(model, str(tmp_path / "ours"))
+    c = json.load(open(tmp_path / "ours" / "config.json"))
+    assert c["model_type"] == "granite" and c["residual_multiplier"] == 0.3 and c["logits_scaling"] == 4.0
+    hf2 = tr.AutoModelForCausalLM.from_pretrained(str(tmp_path / "ours"), dtype=torch.float32, attn_implementation="eager")
+    assert torch.allclose(hf2(x).logits, ref, atol=3e-4, rtol=1e-3)
+    back = load_hf_model(str(tmp_path / "ours"), dtype=torch.float32)
+    assert torch.equal(back(x), model(x))
+    with pytest.raises(NotImplementedError):
+        load_tp_weights(str(tmp_path / "ours"), 0, 2, dtype=torch.float32)
+    # a Llama config that happens to carry such keys is not affected by them
+    assert LlamaConfig.from_hf_dict(dict(_base(), model_type="llama", residual_multiplier=0.5)).residual_multiplier == 1.0
