@@ -453,13 +453,14 @@ __global__ void __launch_bounds__(256) headnorm_bwd_kernel(__nv_bfloat16* __rest
 }
 
 // Rotary embedding, HF Llama convention (pairs (i, i + d/2)), in place on x[T, nh, d].
-// cos/sin tables are fp32 [max_pos, d/2]; pos[t] gives the position of token t. sign = -1 runs the inverse rotation
-// (the backward pass).
+// cos/sin tables are fp32 [max_pos, rot/2]; pos[t] gives the position of token t. sign = -1 runs the inverse rotation
+// (the backward pass). rot <= d: only the first rot elements of a head rotate (partial rotary embeddings), element j
+// pairing with j + rot/2; the rest of the head is left as it is.
 __global__ void rope_kernel(__nv_bfloat16* __restrict__ x, const int* __restrict__ pos, const float* __restrict__ cs,
-                            const float* __restrict__ sn, long long T, int nh, int d, long long row_stride,
+                            const float* __restrict__ sn, long long T, int nh, int d, int rot, long long row_stride,
                             float sign) {
-  // one thread rotates 8 pairs: a 16-byte vector from each half of the head
-  const int half = d >> 1;
+  // one thread rotates 8 pairs: a 16-byte vector from each half of the rotated part
+  const int half = rot >> 1;
   const int vecs_per_head = half >> 3;
   const int vecs_per_tok = nh * vecs_per_head;
   const long long total = T * vecs_per_tok;
@@ -787,14 +788,22 @@ int b200_headnorm_bwd(void* g, const void* x, const void* wq, const void* wk, co
   return B200_OK;
 }
 
-int b200_rope(void* x, const int* pos, const float* cos_tab, const float* sin_tab, long long T, int nh, int d,
-              long long row_stride, int inverse, cudaStream_t st) {
-  if (!x || !pos || !cos_tab || !sin_tab || T <= 0 || (d & 15) || (row_stride & 7)) return B200_ERR_ARG;
-  const long long total = T * nh * (d >> 4);
-  rope_kernel<<<grid_for(total, 256), 256, 0, st>>>((__nv_bfloat16*)x, pos, cos_tab, sin_tab, T, nh, d, row_stride,
-                                                   inverse ? -1.f : 1.f);
+// rot: how many leading elements of each head rotate (a multiple of 16, at most d); the tables are [max_pos, rot/2]
+int b200_rope_partial(void* x, const int* pos, const float* cos_tab, const float* sin_tab, long long T, int nh, int d,
+                      int rot, long long row_stride, int inverse, cudaStream_t st) {
+  if (!x || !pos || !cos_tab || !sin_tab || T <= 0 || nh <= 0 || (d & 7) || rot <= 0 || rot > d || (rot & 15) ||
+      (row_stride & 7))
+    return B200_ERR_ARG;
+  const long long total = T * nh * (rot >> 4);
+  rope_kernel<<<grid_for(total, 256), 256, 0, st>>>((__nv_bfloat16*)x, pos, cos_tab, sin_tab, T, nh, d, rot,
+                                                   row_stride, inverse ? -1.f : 1.f);
   B200_CUDA_CHECK(cudaGetLastError());
   return B200_OK;
+}
+
+int b200_rope(void* x, const int* pos, const float* cos_tab, const float* sin_tab, long long T, int nh, int d,
+              long long row_stride, int inverse, cudaStream_t st) {
+  return b200_rope_partial(x, pos, cos_tab, sin_tab, T, nh, d, d, row_stride, inverse, st);
 }
 
 int b200_bias_add(void* x, const void* bias, long long T, int N, long long ld, cudaStream_t st) {

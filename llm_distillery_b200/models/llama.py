@@ -54,6 +54,7 @@ class LlamaConfig:
     logits_scaling: float = 1.0                    # logits are DIVIDED by this
     rope_scaling: dict | None = None  # HuggingFace dict; types default / linear / llama3 / yarn (ops.basic.rope_tables)
     head_dim_override: int | None = None   # HuggingFace ``head_dim`` when it is not hidden_size / num_attention_heads
+    partial_rotary_factor: float = 1.0     # < 1: only the first int(head_dim * factor) elements of a head rotate (Phi-4-mini)
     qk_norm: bool = False             # Qwen3: RMSNorm over every query and key head (one weight each) before RoPE
     sliding_window: int | None = None  # attention here is full causal: sequences longer than the window are refused
     pad_token_id: int | None = None
@@ -62,6 +63,10 @@ class LlamaConfig:
     @property
     def head_dim(self) -> int:
         return self.head_dim_override or self.hidden_size // self.num_attention_heads
+
+    @property
+    def rotary_dim(self) -> int:
+        return int(self.head_dim * self.partial_rotary_factor)
 
     @property
     def q_size(self) -> int:
@@ -101,6 +106,8 @@ class LlamaConfig:
         hd = d.pop("head_dim_override")
         if hd:
             d["head_dim"] = hd
+        if d["partial_rotary_factor"] == 1.0:
+            d.pop("partial_rotary_factor")
         renorm = d.pop("moe_renormalize")
         if not self.num_local_experts:
             d.pop("num_local_experts")
@@ -155,7 +162,9 @@ class LlamaConfig:
             if rp.get("rope_theta") is not None and d.get("rope_theta") is None:
                 kw["rope_theta"] = float(rp["rope_theta"])
             if rp.get("rope_type", rp.get("type")) not in (None, "default") and not d.get("rope_scaling"):
-                kw["rope_scaling"] = {k: v for k, v in rp.items() if k != "rope_theta"}
+                kw["rope_scaling"] = {k: v for k, v in rp.items() if k not in ("rope_theta", "partial_rotary_factor")}
+            if rp.get("partial_rotary_factor") is not None and d.get("partial_rotary_factor") is None:
+                kw["partial_rotary_factor"] = float(rp["partial_rotary_factor"])
         for k in ("bos_token_id", "eos_token_id"):
             if k in kw and kw[k] is None:
                 kw.pop(k)
@@ -200,8 +209,9 @@ class LlamaConfig:
             kw["mlp_bias"] = True
         if d.get("hidden_act", "silu") not in ("silu", "swish"):
             raise NotImplementedError(f"hidden_act {d['hidden_act']!r}: only SwiGLU (silu) is built")
-        if float(d.get("partial_rotary_factor", 1.0) or 1.0) != 1.0:
-            raise NotImplementedError("partial rotary embeddings are not built")
+        kw["partial_rotary_factor"] = float(kw.get("partial_rotary_factor") or 1.0)
+        if not 0.0 < kw["partial_rotary_factor"] <= 1.0:
+            raise ValueError(f"partial_rotary_factor {kw['partial_rotary_factor']} is outside (0, 1]")
         if "num_key_value_heads" not in kw or kw["num_key_value_heads"] is None:
             kw["num_key_value_heads"] = kw.get("num_attention_heads", 32)
         hd = d.get("head_dim")
@@ -616,7 +626,7 @@ class LlamaModel(nn.Module):
             n = max(need, min(self.cfg.max_position_embeddings, 8192))
             if regime is False:
                 n = min(n, int(sc.get("original_max_position_embeddings") or n))
-            self._rope = basic.rope_tables(n, self.cfg.head_dim, self.cfg.rope_theta, device, self.cfg.rope_scaling,
+            self._rope = basic.rope_tables(n, self.cfg.rotary_dim, self.cfg.rope_theta, device, self.cfg.rope_scaling,
                                            model_max_pos=self.cfg.max_position_embeddings, seq_len=need)
             am = self.cfg.attention_multiplier
             if am is not None and abs(am * math.sqrt(self.cfg.head_dim) - 1.0) > 1e-9:

@@ -42,6 +42,7 @@ _SIGS = {
     "b200_rmsnorm_bwd": [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _I, _VP],
     "b200_rmsnorm_bwd_blocks": [_I],
     "b200_rope": [_VP, _VP, _VP, _VP, _LL, _I, _I, _LL, _I, _VP],
+    "b200_rope_partial": [_VP, _VP, _VP, _VP, _LL, _I, _I, _I, _LL, _I, _VP],
     "b200_swiglu_fwd": [_VP, _VP, _LL, _I, _VP],
     "b200_swiglu_bwd": [_VP, _VP, _VP, _LL, _I, _VP],
     "b200_embed_fwd": [_VP, _VP, _VP, _LL, _I, _I, _VP],

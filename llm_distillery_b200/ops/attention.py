@@ -82,7 +82,8 @@ def attention_bwd_unrotated(dout, qkv, out, lse, B, L, H, Hkv, d, pos, cos, sin)
     inverse rotation of the query and key heads. On the GPU the query heads are rotated where their fp32 accumulator is
     converted to bf16 (one pass less over 8/9 of the rotated columns); same values as ``attention_bwd`` + ``rope_``."""
     from . import basic
-    if qkv.is_cuda and qkv.dtype == torch.bfloat16 and pos.dtype == torch.int32 and cos.is_contiguous() and sin.is_contiguous():
+    if (qkv.is_cuda and qkv.dtype == torch.bfloat16 and pos.dtype == torch.int32 and cos.is_contiguous()
+            and sin.is_contiguous() and 2 * cos.shape[1] == d):      # partial rotary: the separate kernel below
         from . import flash
         dqkv = flash.flash_attn_bwd(dout, qkv, out, lse, B, L, H, Hkv, d, rope=(pos, cos, sin))
         basic.rope_(dqkv[:, H * d:], pos, cos, sin, Hkv, d, inverse=True)      # the key heads

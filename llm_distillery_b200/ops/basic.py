@@ -306,22 +306,29 @@ def rope_tables(max_pos: int, head_dim: int, theta: float, device, scaling: dict
 def rope_(x: torch.Tensor, pos: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, n_heads: int, head_dim: int,
           inverse: bool = False) -> torch.Tensor:
     """Rotate x[T, >= n_heads*head_dim] in place (only the first n_heads*head_dim columns of each row).
-    ``pos`` is int32 [T]. ``inverse=True`` applies the transposed rotation (the backward pass)."""
+    ``pos`` is int32 [T]. ``inverse=True`` applies the transposed rotation (the backward pass). The tables' width sets
+    how much of a head rotates: [max_pos, rot/2] with rot <= head_dim (partial rotary embeddings, e.g. Phi-4-mini's
+    0.75); the other head_dim - rot elements of each head stay as they are."""
     T = x.shape[0]
+    rot = 2 * cos.shape[1]
+    if rot > head_dim:
+        raise ValueError(f"rope_: tables of width {cos.shape[1]} for heads of {head_dim}")
     if not _native(x):
-        half = head_dim // 2
+        half = rot // 2
         v = x[:, : n_heads * head_dim].reshape(T, n_heads, head_dim).float()
         c = cos[pos.long()][:, None, :]
         s = sin[pos.long()][:, None, :] * (-1.0 if inverse else 1.0)
-        a, b = v[..., :half], v[..., half:]
-        out = torch.cat([a * c - b * s, b * c + a * s], dim=-1)
+        a, b = v[..., :half], v[..., half:rot]
+        out = torch.cat([a * c - b * s, b * c + a * s, v[..., rot:]], dim=-1)
         x[:, : n_heads * head_dim] = out.reshape(T, n_heads * head_dim).to(x.dtype)
         return x
     if x.stride(-1) != 1 or pos.dtype != torch.int32:
         raise ValueError("rope_: x rows must be contiguous and pos int32")
-    rc = _lib.kernels().b200_rope(_lib.ptr(x), _lib.ptr(pos), _lib.ptr(cos), _lib.ptr(sin), T, n_heads, head_dim,
-                                  x.stride(0), int(inverse), _lib.stream())
-    _lib.check(rc, "b200_rope")
+    if rot % 16:
+        raise ValueError(f"rope_: the kernel rotates 16-byte vectors - rotary width {rot} is not a multiple of 16")
+    rc = _lib.kernels().b200_rope_partial(_lib.ptr(x), _lib.ptr(pos), _lib.ptr(cos), _lib.ptr(sin), T, n_heads,
+                                          head_dim, rot, x.stride(0), int(inverse), _lib.stream())
+    _lib.check(rc, "b200_rope_partial")
     return x
 
 

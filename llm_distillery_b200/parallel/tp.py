@@ -317,7 +317,8 @@ class TPLlama:
         if regime != getattr(self, "_rope_regime", None):
             self._rope, self._rope_regime = None, regime
         if self._rope is None or self._rope[0].shape[0] < n:
-            self._rope = basic.rope_tables(max(n, 2048), self.cfg.head_dim, self.cfg.rope_theta, self.device,
+            self._rope = basic.rope_tables(max(n, 2048), getattr(self.cfg, "rotary_dim", self.cfg.head_dim),
+                                           self.cfg.rope_theta, self.device,
                                            getattr(self.cfg, "rope_scaling", None),
                                            model_max_pos=self.cfg.max_position_embeddings, seq_len=n)
         return self._rope

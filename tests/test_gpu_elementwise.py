@@ -55,6 +55,25 @@ def test_rope_roundtrip_and_reference(T, nh, d):
     assert torch.allclose(back.float(), x.float(), atol=5e-2, rtol=5e-2)
 
 
+@pytest.mark.parametrize("T,nh,d,rot", [(33, 6, 128, 96), (300, 8, 64, 32), (17, 3, 80, 16)])
+def test_partial_rope(T, nh, d, rot):
+    """Only the first ``rot`` elements of a head rotate; the rest of the head and the columns past the heads stay."""
+    torch.manual_seed(11)
+    x = torch.randn(T, nh * d + 24, device=DEV).bfloat16()
+    pos = torch.randint(0, 500, (T,), device=DEV, dtype=torch.int32)
+    cos, sin = basic.rope_tables(512, rot, 10000.0, DEV)
+    ref = _cpu(basic.rope_, x.clone(), pos, cos, sin, nh, d)
+    y = basic.rope_(x.clone(), pos, cos, sin, nh, d)
+    assert torch.allclose(y.float().cpu(), ref.float(), atol=2e-2, rtol=2e-2)
+    heads = y[:, : nh * d].view(T, nh, d)
+    assert torch.equal(heads[..., rot:], x[:, : nh * d].view(T, nh, d)[..., rot:])
+    assert torch.equal(y[:, nh * d:], x[:, nh * d:])
+    back = basic.rope_(y.clone(), pos, cos, sin, nh, d, inverse=True)
+    assert torch.allclose(back.float(), x.float(), atol=5e-2, rtol=5e-2)
+    with pytest.raises(ValueError, match="multiple of 16"):
+        basic.rope_(x.clone(), pos, *basic.rope_tables(512, 24, 10000.0, DEV), nh, d)
+
+
 @pytest.mark.parametrize("T,f", [(5, 64), (257, 5632), (1024, 8192)])
 def test_swiglu(T, f):
     torch.manual_seed(2)

@@ -94,7 +94,7 @@ def test_config_keys_survive_a_round_trip_and_unbuilt_variants_are_refused(tmp_p
     with pytest.raises(ValueError, match="attention window"):
         model(torch.randint(0, 320, (1, 129)))
     for bad in (dict(model_type="gemma2"), dict(hidden_act="gelu_pytorch_tanh"), dict(head_dim=20),
-                dict(partial_rotary_factor=0.5), dict(rope_scaling={"rope_type": "dynamic", "factor": 4.0})):
+                dict(rope_scaling={"rope_type": "dynamic", "factor": 4.0})):
         with pytest.raises(NotImplementedError):
             LlamaConfig.from_hf_dict(dict(_base(), **bad))
     # Qwen2 carries a window that is switched off
@@ -222,6 +222,52 @@ def test_phi3_longrope_matches_huggingface():
         assert torch.allclose(ours, ref, atol=4e-4, rtol=1e-3), (L, (ours - ref).abs().max())
     same = LlamaConfig.from_hf_dict(dict(d, rope_scaling=dict(scaling, type="su")))
     assert same.rope_scaling["rope_type"] == "longrope"
+
+
+def test_partial_rotary_matches_huggingface(tmp_path):
+    """Phi-4-mini's layout: three quarters of every head rotate, the rest passes through; longrope factors cover the
+    rotated part only; tied embeddings."""
+    torch.manual_seed(1)
+    base = _base(max_position_embeddings=256)
+    rot_half = int(base["hidden_size"] // base["num_attention_heads"] * 0.75) // 2
+    scaling = {"type": "longrope", "short_factor": (1.0 + 0.2 * torch.rand(rot_half)).tolist(),
+               "long_factor": (1.5 + 2.0 * torch.rand(rot_half)).tolist()}
+    hf_cfg = tr.Phi3Config(**base, pad_token_id=0, attn_implementation="eager", tie_word_embeddings=True,
+                           sliding_window=None, original_max_position_embeddings=64, partial_rotary_factor=0.75,
+                           rope_scaling=dict(scaling))
+    hf = tr.Phi3ForCausalLM(hf_cfg).float()
+    hf.save_pretrained(str(tmp_path / "hf"), safe_serialization=True)
+    model = load_hf_model(str(tmp_path / "hf"), dtype=torch.float32)
+    cfg = model.cfg
+    assert cfg.partial_rotary_factor == 0.75 and cfg.rotary_dim == 2 * rot_half < cfg.head_dim
+    assert model.rope("cpu", 48)[0].shape[1] == rot_half
+    for L in (48, 200):
+        x = torch.randint(0, 320, (2, L))
+        ours, ref = model(x), hf(x).logits
+        assert torch.allclose(ours, ref, atol=4e-4, rtol=1e-3), (L, (ours - ref).abs().max())
+    full = build_model(LlamaConfig.from_hf_dict(dict(cfg.to_hf_dict(), partial_rotary_factor=1.0, rope_scaling=None)),
+                       dtype=torch.float32, device="cpu", seed=0)
+    full.load_state_dict(model.state_dict())
+    assert (full(x) - ref).abs().max() > 4e-3             # the factor is not a no-op
+    # gradients through the inverse rotation of the rotated part only
+    tgt = torch.randint(0, 320, (2 * 200,))
+    torch.nn.functional.cross_entropy(model(x).view(-1, 320), tgt).backward()
+    torch.nn.functional.cross_entropy(hf(x).logits.view(-1, 320), tgt).backward()
+    g_hf = hf.model.layers[0].self_attn.qkv_proj.weight.grad
+    assert torch.allclose(model.layers[0].qkv_proj.grad, g_hf, atol=2e-5, rtol=2e-3)
+    # the factor survives a save and HuggingFace reads it back
+    save_hf_model(model, str(tmp_path / "ours"))
+    hf2 = tr.AutoModelForCausalLM.from_pretrained(str(tmp_path / "ours"), torch_dtype=torch.float32,
+                                                  attn_implementation="eager")
+    assert torch.allclose(hf2(x).logits, ref, atol=4e-4, rtol=1e-3)
+    # the standalone op: elements past the rotary width are untouched, and the inverse undoes the rotation
+    cos, sin = basic.rope_tables(64, 24, 10000.0, "cpu")
+    v = torch.randn(10, 3 * 32)
+    pos = torch.arange(10, dtype=torch.int32)
+    r = basic.rope_(v.clone(), pos, cos, sin, 3, 32)
+    assert torch.equal(r.view(10, 3, 32)[..., 24:], v.view(10, 3, 32)[..., 24:])
+    assert not torch.allclose(r.view(10, 3, 32)[1:, :, :24], v.view(10, 3, 32)[1:, :, :24])
+    assert torch.allclose(basic.rope_(r, pos, cos, sin, 3, 32, inverse=True), v, atol=1e-5)
 
 
 def test_llama_with_attention_and_mlp_biases_matches_huggingface(tmp_path):

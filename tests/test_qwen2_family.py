@@ -69,11 +69,13 @@ def test_engine_trains_the_bias():
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("variant", ["qwen2", "qwen3", "llama with biases", "plain llama, long batch", "granite"])
+@pytest.mark.parametrize("variant", ["qwen2", "qwen3", "llama with biases", "plain llama, long batch", "granite",
+                                     "plain partial rotary, long batch"])
 def test_gpu_kernels_follow_the_cpu_model(variant):
     """bf16 kernels (GEMMs with their epilogues, bias add, per-head norms, RoPE, flash attention ...) against the fp32 CPU
     statement of the same model, for the layer variants: q/k/v bias (Qwen2), per-head q/k norms (Qwen3), biases on every
-    projection (Llama with attention_bias / mlp_bias), a plain layer with enough rows for the fused epilogues, and Granite's multipliers."""
+    projection (Llama with attention_bias / mlp_bias), a plain layer with enough rows for the fused epilogues, Granite's
+    multipliers, and heads of which three quarters rotate (the fused rotary epilogues must step aside)."""
     kw = dict(vocab_size=512, hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=4,
               num_key_value_heads=2, max_position_embeddings=1024, rope_theta=1e6, rms_norm_eps=1e-6)
     if variant == "qwen2":
@@ -82,6 +84,8 @@ def test_gpu_kernels_follow_the_cpu_model(variant):
         kw.update(qk_norm=True, model_type="qwen3")
     elif variant == "llama with biases":
         kw.update(attention_bias=True, o_bias=True, mlp_bias=True)
+    elif "partial rotary" in variant:
+        kw.update(partial_rotary_factor=0.75)
     elif variant == "granite":
         kw.update(model_type="granite", embedding_multiplier=6.0, attention_multiplier=0.09, residual_multiplier=0.3,
                   logits_scaling=4.0, attention_bias=True, o_bias=True, mlp_bias=True)
