@@ -39,10 +39,12 @@ class LlamaConfig:
     bos_token_id: int = 1
     eos_token_id: int = 2
     model_type: str = "llama"         # llama | mistral | qwen2 (q/k/v bias) | phi3 (fused projections in the checkpoint)
-                                      # | mixtral (sparse mixture of experts, models/moe.py)
+                                      # | mixtral, qwen3_moe, qwen2_moe (sparse mixtures of experts, models/moe.py) | qwen3 | granite
     num_local_experts: int = 0        # > 0: every layer's MLP is that many SwiGLU experts behind a linear router
     num_experts_per_tok: int = 2
     moe_renormalize: bool = True      # router weights renormalised over the chosen experts (Mixtral; Qwen3-MoE norm_topk_prob)
+    shared_expert_intermediate_size: int = 0   # > 0 (Qwen2-MoE): a dense SwiGLU expert of this width for every token,
+                                               # scaled by a per-token sigmoid gate, beside the routed experts
     attention_bias: bool = False      # bias on the q/k/v projections (Qwen2 family; Llama configs with attention_bias)
     o_bias: bool = False              # bias on o_proj as well (HuggingFace Llama's attention_bias = true, e.g. Granite code)
     mlp_bias: bool = False            # bias on gate / up / down projections (HuggingFace Llama's mlp_bias)
@@ -80,6 +82,8 @@ class LlamaConfig:
         h, f, V, Lr = self.hidden_size, self.intermediate_size, self.vocab_size, self.num_hidden_layers
         E = self.num_local_experts
         per_layer = h * (self.q_size + 2 * self.kv_size) + self.q_size * h + 3 * h * f * max(E, 1) + E * h + 2 * h
+        if self.shared_expert_intermediate_size:
+            per_layer += 3 * h * self.shared_expert_intermediate_size + h
         if self.attention_bias:
             per_layer += self.q_size + 2 * self.kv_size
         if self.qk_norm:
@@ -93,6 +97,8 @@ class LlamaConfig:
     def flops_per_token_fwd(self, seq_len: int) -> float:
         h, f, V, Lr = self.hidden_size, self.intermediate_size, self.vocab_size, self.num_hidden_layers
         mlp = 3 * h * f * (self.num_experts_per_tok if self.num_local_experts else 1) + self.num_local_experts * h
+        if self.shared_expert_intermediate_size:
+            mlp += 3 * h * self.shared_expert_intermediate_size + h
         lin = 2 * (Lr * (h * (self.q_size + 2 * self.kv_size) + self.q_size * h + mlp) + V * h)
         attn = Lr * 4 * self.q_size * seq_len / 2  # causal
         return lin + attn
@@ -113,12 +119,20 @@ class LlamaConfig:
             d.pop("num_local_experts")
             d.pop("num_experts_per_tok")
         qk = d.pop("qk_norm")
+        shared_f = d.pop("shared_expert_intermediate_size")
         gran = {k: d.pop(k) for k in ("embedding_multiplier", "attention_multiplier", "residual_multiplier", "logits_scaling")}
         if self.model_type == "qwen3_moe":      # HuggingFace's names: num_experts, moe_intermediate_size, norm_topk_prob
             d.update(architectures=["Qwen3MoeForCausalLM"], hidden_act="silu", torch_dtype="bfloat16",
                      use_sliding_window=False, head_dim=self.head_dim, num_experts=d.pop("num_local_experts"),
                      moe_intermediate_size=self.intermediate_size, norm_topk_prob=bool(renorm), decoder_sparse_step=1,
                      mlp_only_layers=[])
+            d["intermediate_size"] = extra.pop("dense_intermediate_size", self.intermediate_size)
+        elif self.model_type == "qwen2_moe":
+            d.pop("attention_bias")
+            d.update(architectures=["Qwen2MoeForCausalLM"], hidden_act="silu", torch_dtype="bfloat16",
+                     use_sliding_window=False, num_experts=d.pop("num_local_experts"), qkv_bias=True,
+                     moe_intermediate_size=self.intermediate_size, shared_expert_intermediate_size=shared_f,
+                     norm_topk_prob=bool(renorm), decoder_sparse_step=1, mlp_only_layers=[])
             d["intermediate_size"] = extra.pop("dense_intermediate_size", self.intermediate_size)
         elif self.model_type == "qwen3":
             d.update(architectures=["Qwen3ForCausalLM"], hidden_act="silu", torch_dtype="bfloat16",
@@ -150,7 +164,7 @@ class LlamaConfig:
                 d["attention_multiplier"] = 1.0 / math.sqrt(self.head_dim)
         return {**extra, **d}
 
-    _KNOWN_TYPES = ("llama", "mistral", "qwen2", "phi3", "mixtral", "qwen3", "qwen3_moe", "granite")
+    _KNOWN_TYPES = ("llama", "mistral", "qwen2", "phi3", "mixtral", "qwen3", "qwen3_moe", "qwen2_moe", "granite")
 
     @classmethod
     def from_hf_dict(cls, d: dict) -> "LlamaConfig":
@@ -186,10 +200,27 @@ class LlamaConfig:
                 raise NotImplementedError("qwen3_moe with attention_bias also puts a bias on o_proj, which is not built")
             if not d.get("use_sliding_window", False):
                 kw["sliding_window"] = None
+        if mt == "qwen2_moe":        # Qwen2 attention (bias on q, k, v), routed experts plus a gated shared expert
+            if int(d.get("decoder_sparse_step", 1) or 1) != 1 or d.get("mlp_only_layers"):
+                raise NotImplementedError("qwen2_moe with dense layers between the sparse ones is not built")
+            n_exp = int(d.get("num_experts") or d.get("num_local_experts") or 0)
+            if n_exp < 1 or not d.get("moe_intermediate_size") or not d.get("shared_expert_intermediate_size"):
+                raise ValueError("a qwen2_moe config needs num_experts, moe_intermediate_size and "
+                                 "shared_expert_intermediate_size")
+            if not d.get("qkv_bias", True):
+                raise NotImplementedError("qwen2_moe without the q/k/v bias is not built")
+            dense_ffn = d.get("intermediate_size")
+            kw.update(num_local_experts=n_exp, intermediate_size=int(d["moe_intermediate_size"]),
+                      shared_expert_intermediate_size=int(d["shared_expert_intermediate_size"]),
+                      moe_renormalize=bool(d.get("norm_topk_prob", False)), attention_bias=True)
+            if not d.get("use_sliding_window", False):
+                kw["sliding_window"] = None
+        elif kw.get("shared_expert_intermediate_size"):
+            raise NotImplementedError(f"a shared expert on model_type {mt!r} is not built (qwen2_moe is)")
         if mt == "mixtral":
             if int(kw.get("num_local_experts") or 0) < 1:
                 raise ValueError("a mixtral config needs num_local_experts")
-        elif kw.get("num_local_experts") and mt != "qwen3_moe":
+        elif kw.get("num_local_experts") and mt not in ("qwen3_moe", "qwen2_moe"):
             raise NotImplementedError(f"experts on model_type {mt!r} are not built (mixtral is)")
         if mt == "qwen3":
             kw["qk_norm"] = True
@@ -197,7 +228,7 @@ class LlamaConfig:
                 raise NotImplementedError("qwen3 with attention_bias also puts a bias on o_proj, which is not built")
             if not d.get("use_sliding_window", False):
                 kw["sliding_window"] = None
-        if mt == "qwen2":
+        if mt in ("qwen2", "qwen2_moe"):
             kw["attention_bias"] = True
         elif kw.get("attention_bias"):
             if mt not in ("llama", "mistral", "granite"):
@@ -572,6 +603,11 @@ class LlamaDecoderLayer(nn.Module):
             self.router = nn.Parameter(torch.empty(E, h, **kw))
             self.gate_up_proj = nn.Parameter(torch.empty(E, 2 * f, h, **kw))
             self.down_proj = nn.Parameter(torch.empty(E, h, f, **kw))
+            fs = cfg.shared_expert_intermediate_size
+            if fs:
+                self.shared_gate_up_proj = nn.Parameter(torch.empty(2 * fs, h, **kw))
+                self.shared_down_proj = nn.Parameter(torch.empty(h, fs, **kw))
+                self.shared_expert_gate = nn.Parameter(torch.empty(1, h, **kw))
         else:
             self.gate_up_proj = nn.Parameter(torch.empty(2 * f, h, **kw))
             self.down_proj = nn.Parameter(torch.empty(h, f, **kw))
@@ -670,7 +706,10 @@ class LlamaModel(nn.Module):
                                       getattr(layer, "k_norm", None))
                 h = MoEBlockFn.apply(h, layer.post_attention_layernorm, layer.router, layer.gate_up_proj,
                                      layer.down_proj, (cfg.rms_norm_eps, cfg.num_experts_per_tok, meta[6],
-                                                       layer.input_layernorm, cfg.moe_renormalize))
+                                                       layer.input_layernorm, cfg.moe_renormalize),
+                                     getattr(layer, "shared_gate_up_proj", None),
+                                     getattr(layer, "shared_down_proj", None),
+                                     getattr(layer, "shared_expert_gate", None))
                 continue
             h = DecoderLayerFn.apply(h, pos, cos, sin, layer.input_layernorm, layer.qkv_proj, layer.o_proj,
                                      layer.post_attention_layernorm, layer.gate_up_proj, layer.down_proj, meta,
@@ -734,8 +773,10 @@ class LlamaModel(nn.Module):
                 n2, _, _ = basic.rmsnorm_fwd(h1, layer.post_attention_layernorm, cfg.rms_norm_eps)
                 if cfg.num_local_experts:
                     from .moe import moe_mlp
+                    shared = ((layer.shared_gate_up_proj, layer.shared_down_proj, layer.shared_expert_gate)
+                              if cfg.shared_expert_intermediate_size else None)
                     h = h1 + moe_mlp(n2, layer.router, layer.gate_up_proj, layer.down_proj, cfg.num_experts_per_tok,
-                                     cfg.moe_renormalize)
+                                     cfg.moe_renormalize, shared)
                     continue
                 if cfg.mlp_bias:
                     act = basic.swiglu_fwd(basic.bias_add_(basic.linear_fwd(n2, layer.gate_up_proj), layer.gate_up_bias))
@@ -790,7 +831,13 @@ class LlamaModel(nn.Module):
                 yield pre + "mlp.gate_proj.bias", l.gate_up_bias, slice(0, f)
                 yield pre + "mlp.up_proj.bias", l.gate_up_bias, slice(f, 2 * f)
                 yield pre + "mlp.down_proj.bias", l.down_bias, None
-            if cfg.num_local_experts and cfg.model_type == "qwen3_moe":
+            if cfg.shared_expert_intermediate_size:
+                fs = cfg.shared_expert_intermediate_size
+                yield pre + "mlp.shared_expert.gate_proj.weight", l.shared_gate_up_proj, slice(0, fs)
+                yield pre + "mlp.shared_expert.up_proj.weight", l.shared_gate_up_proj, slice(fs, 2 * fs)
+                yield pre + "mlp.shared_expert.down_proj.weight", l.shared_down_proj, None
+                yield pre + "mlp.shared_expert_gate.weight", l.shared_expert_gate, None
+            if cfg.num_local_experts and cfg.model_type in ("qwen3_moe", "qwen2_moe"):
                 yield pre + "mlp.gate.weight", l.router, None
                 for e in range(cfg.num_local_experts):
                     ex = pre + f"mlp.experts.{e}."
@@ -862,7 +909,7 @@ class LlamaModel(nn.Module):
         [E, 2f, h], ``mlp.experts.down_proj`` [E, h, f], router ``mlp.gate.weight``); the published checkpoints - and
         this model's own names - list them per expert under ``block_sparse_moe``."""
         f = self.cfg.intermediate_size
-        qwen = self.cfg.model_type == "qwen3_moe"
+        qwen = self.cfg.model_type in ("qwen3_moe", "qwen2_moe")
         block = "mlp." if qwen else "block_sparse_moe."
         gate_n, up_n, down_n = ("gate_proj", "up_proj", "down_proj") if qwen else ("w1", "w3", "w2")
         out = {}

@@ -1,5 +1,6 @@
 """Sparse mixture-of-experts decoder blocks (Mixtral layout: a linear router, top-k of the softmax renormalised over
-the chosen experts, SwiGLU experts) for both roles, student training and teacher inference.
+the chosen experts, SwiGLU experts; Qwen2-MoE adds a dense "shared" expert behind a sigmoid gate to every token) for
+both roles, student training and teacher inference.
 
 The reference loads such students through ``AutoModelForCausalLM`` (classes/student/model.py:194-201) and its shipped
 ``freeze_layers`` default names Mixtral's router (config.json: ``block_sparse_moe.gate``). Here a decoder layer with
@@ -70,16 +71,30 @@ def experts_forward(x_perm: torch.Tensor, counts: list[int], w_gu: torch.Tensor,
     return gu, act, y
 
 
+def shared_expert_forward(n2: torch.Tensor, w_sgu: torch.Tensor, w_sd: torch.Tensor, w_sg: torch.Tensor):
+    """Qwen2-MoE's shared expert: a dense SwiGLU MLP every token passes through, scaled per token by
+    sigmoid(n2 . w_sg). Returns (gu_s [T, 2fs], act_s [T, fs], y_s [T, h], gate [T, 1] fp32)."""
+    gu_s, act_s = basic.linear_swiglu_fwd(n2, w_sgu)
+    y_s = basic.linear_fwd(act_s, w_sd)
+    gate = torch.sigmoid(F.linear(n2, w_sg).float())
+    return gu_s, act_s, y_s, gate
+
+
 def moe_mlp(n2: torch.Tensor, w_router: torch.Tensor, w_gu: torch.Tensor, w_d: torch.Tensor, k: int,
-            renorm: bool = True) -> torch.Tensor:
-    """Inference-only expert half: sum_k weight * expert(n2) as [T, h] in n2's dtype."""
+            renorm: bool = True, shared=None) -> torch.Tensor:
+    """Inference-only expert half: sum_k weight * expert(n2) as [T, h] in n2's dtype. ``shared`` = (gate/up matrix,
+    down matrix, gate vector) of a shared expert, or None."""
     T, h = n2.shape
     _, top_e, top_w = route(n2, w_router, k, renorm)
     order, inverse, counts = permutation(top_e, w_gu.shape[0])
     x_perm = n2.index_select(0, torch.div(order, k, rounding_mode="floor"))
     _, _, y = experts_forward(x_perm, counts, w_gu, w_d)
     y_tok = y.index_select(0, inverse).view(T, k, h)
-    return (y_tok.float() * top_w.unsqueeze(-1)).sum(1).to(n2.dtype)
+    out = (y_tok.float() * top_w.unsqueeze(-1)).sum(1)
+    if shared is not None:
+        _, _, y_s, gate = shared_expert_forward(n2, *shared)
+        out = out + gate * y_s.float()
+    return out.to(n2.dtype)
 
 
 # ------------------------------------------------------------------------------------------------ autograd nodes
@@ -175,10 +190,11 @@ def _expert_wgrad(dy, x, w, slot, e, first):
 
 
 class MoEBlockFn(torch.autograd.Function):
-    """h2 = h1 + sum_k weight_k * Expert_k(RMSNorm(h1)) with the router's top-k experts per token."""
+    """h2 = h1 + sum_k weight_k * Expert_k(n2) [+ sigmoid(n2 . w_sg) * SharedExpert(n2)], n2 = RMSNorm(h1), with the
+    router's top-k experts per token. The shared expert's three tensors are optional (Qwen2-MoE has them)."""
 
     @staticmethod
-    def forward(ctx, h1, w_ln2, w_router, w_gu, w_d, meta):
+    def forward(ctx, h1, w_ln2, w_router, w_gu, w_d, meta, w_sgu=None, w_sd=None, w_sg=None):
         eps, k, recompute, _first, renorm = meta
         T, hdim = h1.shape
         n2, _, rstd2 = basic.rmsnorm_fwd(h1, w_ln2, eps)
@@ -188,15 +204,23 @@ class MoEBlockFn(torch.autograd.Function):
         x_perm = n2.index_select(0, tok)
         gu, act, y = experts_forward(x_perm, counts, w_gu, w_d)
         y_tok = y.index_select(0, inverse).view(T, k, hdim)
-        h2 = (h1.float() + (y_tok.float() * top_w.unsqueeze(-1)).sum(1)).to(h1.dtype)
+        h2 = h1.float() + (y_tok.float() * top_w.unsqueeze(-1)).sum(1)
+        shared_saved = ()
+        if w_sgu is not None:
+            gu_s, act_s, y_s, gate = shared_expert_forward(n2, w_sgu, w_sd, w_sg)
+            h2 = h2 + gate * y_s.float()
+            shared_saved = (gu_s, act_s, y_s, gate)
+        h2 = h2.to(h1.dtype)
         ctx.meta = meta
         ctx.counts = counts
         ctx.weights = (w_ln2, w_router, w_gu, w_d)
         ctx.slots = tuple(_ll._slot(w) for w in ctx.weights)
+        ctx.shared = (w_sgu, w_sd, w_sg)
+        ctx.shared_slots = tuple(_ll._slot(w) for w in ctx.shared) if w_sgu is not None else (None, None, None)
         if recompute:
             ctx.save_for_backward(h1, top_e, order, inverse)
         else:
-            ctx.save_for_backward(h1, top_e, order, inverse, rstd2, n2, probs, top_w, gu, act, y)
+            ctx.save_for_backward(h1, top_e, order, inverse, rstd2, n2, probs, top_w, gu, act, y, *shared_saved)
         return h2
 
     @staticmethod
@@ -205,6 +229,8 @@ class MoEBlockFn(torch.autograd.Function):
         counts = ctx.counts
         w_ln2, w_router, w_gu, w_d = ctx.weights
         s_ln2, s_router, s_gu, s_d = ctx.slots
+        w_sgu, w_sd, w_sg = ctx.shared
+        s_sgu, s_sd, s_sg = ctx.shared_slots
         if _ll.UNIT_PRE[0] is not None:                 # the layer's backward starts here
             _ll.UNIT_PRE[0](first_param, True)
         if recompute:
@@ -215,8 +241,12 @@ class MoEBlockFn(torch.autograd.Function):
             top_w = top_p / top_p.sum(-1, keepdim=True) if renorm else top_p
             tok = torch.div(order, k, rounding_mode="floor")
             gu, act, y = experts_forward(n2.index_select(0, tok), counts, w_gu, w_d)
+            if w_sgu is not None:
+                gu_s, act_s, y_s, gate = shared_expert_forward(n2, w_sgu, w_sd, w_sg)
         else:
-            h1, top_e, order, inverse, rstd2, n2, probs, top_w, gu, act, y = ctx.saved_tensors
+            h1, top_e, order, inverse, rstd2, n2, probs, top_w, gu, act, y, *rest = ctx.saved_tensors
+            if w_sgu is not None:
+                gu_s, act_s, y_s, gate = rest
             tok = torch.div(order, k, rounding_mode="floor")
         T, hdim = h1.shape
         E = w_gu.shape[0]
@@ -278,10 +308,22 @@ class MoEBlockFn(torch.autograd.Function):
         if w_router.requires_grad:
             dwr = d_logits.t() @ n2.float()                                              # [E, h]
             g_router = _ll._vec_grad(dwr, w_router, s_router)
+        g_sgu = g_sd = g_sg = None
+        if w_sgu is not None:
+            # h2 += gate * y_s with gate = sigmoid(n2 . w_sg), y_s = act_s w_sd^T, act_s = SwiGLU(n2 w_sgu^T)
+            d_gate = (y_s.float() * dh2f).sum(-1, keepdim=True)                          # [T, 1]
+            d_glogit = d_gate * gate * (1.0 - gate)
+            dy_s = (dh2f * gate).to(y_s.dtype)
+            g_sd = _ll._wgrad(dy_s, act_s, w_sd, s_sd)
+            dgu_s = basic.linear_dgrad_swiglu_bwd(dy_s, w_sd, gu_s)
+            g_sgu = _ll._wgrad(dgu_s, n2, w_sgu, s_sgu)
+            dn2 = dn2 + basic.linear_dgrad(dgu_s, w_sgu).float() + d_glogit * w_sg.float()
+            if w_sg.requires_grad:
+                g_sg = _ll._vec_grad(d_glogit.t() @ n2.float(), w_sg, s_sg)              # [1, h]
         dh1, dw2 = basic.rmsnorm_bwd(dn2.to(h1.dtype), h1, w_ln2, rstd2, dres=dh2)
         g_ln2 = _ll._vec_grad(dw2, w_ln2, s_ln2)
         if g_gu is not None:
             g_gu = g_gu.to(w_gu.dtype)
         if g_d is not None:
             g_d = g_d.to(w_d.dtype)
-        return dh1, g_ln2, g_router, g_gu, g_d, None
+        return dh1, g_ln2, g_router, g_gu, g_d, None, g_sgu, g_sd, g_sg

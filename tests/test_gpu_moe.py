@@ -13,14 +13,21 @@ def _cos(a, b):
     return float((a @ b) / (a.norm() * b.norm() + 1e-30))
 
 
-def test_mixtral_forward_and_backward_match_the_fp32_restatement():
+@pytest.mark.parametrize("family", ["mixtral", "qwen2_moe"])
+def test_experts_forward_and_backward_match_the_fp32_restatement(family):
+    """Mixtral's routed experts; Qwen2-MoE adds the q/k/v bias and the gated shared expert (a dense MLP on the fused
+    SwiGLU GEMMs)."""
     cfg = LlamaConfig(vocab_size=1024, hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=4,
-                      num_key_value_heads=2, max_position_embeddings=512, model_type="mixtral", num_local_experts=4,
-                      num_experts_per_tok=2)
+                      num_key_value_heads=2, max_position_embeddings=512, model_type=family, num_local_experts=4,
+                      num_experts_per_tok=2,
+                      **(dict(shared_expert_intermediate_size=384, attention_bias=True, moe_renormalize=False)
+                         if family == "qwen2_moe" else {}))
     ref = build_model(cfg, dtype=torch.float32, device="cpu", seed=4)
     with torch.no_grad():
         for l in ref.layers:
             l.router.mul_(20.0)          # clear routing decisions: bf16 rounding must not flip many of them
+            if family == "qwen2_moe":
+                l.shared_expert_gate.mul_(20.0)
     gpu = build_model(cfg, dtype=torch.bfloat16, device="cuda", seed=None)
     with torch.no_grad():
         for (n, p), (_, q) in zip(gpu.named_parameters(), ref.named_parameters()):
@@ -37,7 +44,8 @@ def test_mixtral_forward_and_backward_match_the_fp32_restatement():
     assert _lib.take_device_error() == 0
     for (n, p), (_, q) in zip(gpu.named_parameters(), ref.named_parameters()):
         assert torch.isfinite(p.grad).all(), n
-        assert _cos(p.grad.float(), q.grad) > (0.95 if "router" in n else 0.985), (n, _cos(p.grad.float(), q.grad))
+        loose = "router" in n or "shared_expert_gate" in n
+        assert _cos(p.grad.float(), q.grad) > (0.95 if loose else 0.985), (n, _cos(p.grad.float(), q.grad))
     # inference in chunks against the K/V cache takes the same expert path
     with torch.no_grad():
         full = gpu.hidden_states(x.cuda())

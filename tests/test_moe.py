@@ -273,3 +273,80 @@ def test_qwen3_moe_matches_huggingface(tmp_path, renorm):
     assert back.cfg.model_type == "qwen3_moe" and torch.allclose(back(x), ref, atol=3e-4, rtol=1e-3)
     with pytest.raises(NotImplementedError):
         LlamaConfig.from_hf_dict(dict(d, mlp_only_layers=[0]))
+
+
+@pytest.mark.parametrize("renorm,recompute", [(False, False), (True, True)])
+def test_qwen2_moe_matches_huggingface(tmp_path, renorm, recompute):
+    """Qwen2-MoE: Qwen2's attention (bias on q, k, v), routed experts and a dense shared expert whose output is scaled
+    per token by a sigmoid gate - logits and every gradient against HuggingFace, with and without recomputation."""
+    d = dict(_base(), model_type="qwen2_moe", num_experts=4, num_experts_per_tok=2, moe_intermediate_size=48,
+             shared_expert_intermediate_size=80, norm_topk_prob=renorm, decoder_sparse_step=1, mlp_only_layers=[],
+             use_sliding_window=False)
+    cfg = LlamaConfig.from_hf_dict(d)
+    assert cfg.num_local_experts == 4 and cfg.intermediate_size == 48 and cfg.shared_expert_intermediate_size == 80
+    assert cfg.attention_bias and not cfg.qk_norm and cfg.moe_renormalize == renorm
+    model = build_model(cfg, dtype=torch.float32, device="cpu", seed=10)
+    assert sum(p.numel() for p in model.parameters()) == cfg.num_params()
+    with torch.no_grad():
+        for l in model.layers:
+            l.router.mul_(30.0)
+            l.shared_expert_gate.mul_(40.0)        # gates away from one half
+    model.grad_checkpointing = recompute
+    hf_kw = {k: v for k, v in d.items() if k != "model_type"}
+    hf = tr.Qwen2MoeForCausalLM(tr.Qwen2MoeConfig(**hf_kw, attn_implementation="eager", tie_word_embeddings=False)).float()
+    sd = model.to_hf_state_dict()
+    own = hf.state_dict()
+    if not all(k in own for k in sd):          # newer releases stack the experts
+        packed = {k: v for k, v in sd.items() if ".experts." not in k}
+        for li in range(cfg.num_hidden_layers):
+            pre = f"model.layers.{li}.mlp.experts."
+            packed[pre + "gate_up_proj"] = torch.stack([torch.cat([sd[f"{pre}{e}.gate_proj.weight"],
+                                                                   sd[f"{pre}{e}.up_proj.weight"]]) for e in range(4)])
+            packed[pre + "down_proj"] = torch.stack([sd[f"{pre}{e}.down_proj.weight"] for e in range(4)])
+        sd = packed
+    res = hf.load_state_dict({k: v.clone() for k, v in sd.items()}, strict=False)
+    assert not res.unexpected_keys and not [k for k in res.missing_keys if "rotary" not in k], res
+    x = torch.randint(0, 320, (2, 48))
+    ours, ref = model(x), hf(x).logits
+    assert torch.allclose(ours, ref, atol=3e-4, rtol=1e-3), (ours - ref).abs().max()
+    tgt = torch.randint(0, 320, (2 * 48,))
+    torch.nn.functional.cross_entropy(ours.reshape(-1, 320), tgt).backward()
+    torch.nn.functional.cross_entropy(ref.reshape(-1, 320), tgt).backward()
+    hf_grads = {n: p.grad for n, p in hf.named_parameters()}
+    f = cfg.intermediate_size
+    seen_shared = 0
+    for n, p, sl in model.named_hf_parameters():
+        g = p.grad if sl is None else p.grad[sl]
+        if n in hf_grads:
+            want = hf_grads[n]
+            seen_shared += "shared_expert" in n
+        else:
+            pre, rest = n.split("mlp.experts.")
+            e, which = int(rest.split(".")[0]), rest.split(".")[1]
+            if which == "down_proj":
+                want = hf_grads[pre + "mlp.experts.down_proj"][e]
+            else:
+                gu = hf_grads[pre + "mlp.experts.gate_up_proj"][e]
+                want = gu[:f] if which == "gate_proj" else gu[f:]
+        assert torch.allclose(g, want, atol=2e-5, rtol=2e-3), (n, (g - want).abs().max())
+    assert seen_shared == 4 * cfg.num_hidden_layers
+    # the inference path (chunked prefill) runs the shared expert too
+    model.grad_checkpointing = False
+    with torch.no_grad():
+        hs = model.hidden_states_chunked(x, 16)
+        assert torch.allclose(torch.nn.functional.linear(hs, model.lm_head).view(2, 48, -1), ref, atol=3e-4, rtol=1e-3)
+    # checkpoints both ways
+    save_hf_model(model, str(tmp_path / "ours"))
+    c = json.load(open(tmp_path / "ours" / "config.json"))
+    assert c["model_type"] == "qwen2_moe" and c["num_experts"] == 4 and c["shared_expert_intermediate_size"] == 80
+    assert c["intermediate_size"] == 136 and c["moe_intermediate_size"] == 48 and "num_local_experts" not in c
+    hf2 = tr.AutoModelForCausalLM.from_pretrained(str(tmp_path / "ours"), dtype=torch.float32, attn_implementation="eager")
+    assert torch.allclose(hf2(x).logits, ref, atol=3e-4, rtol=1e-3)
+    hf.save_pretrained(str(tmp_path / "theirs"), safe_serialization=True)
+    back = load_hf_model(str(tmp_path / "theirs"), dtype=torch.float32)
+    assert back.cfg.model_type == "qwen2_moe" and torch.allclose(back(x), ref, atol=3e-4, rtol=1e-3)
+    for bad in (dict(mlp_only_layers=[0]), dict(decoder_sparse_step=2), dict(qkv_bias=False)):
+        with pytest.raises(NotImplementedError):
+            LlamaConfig.from_hf_dict(dict(d, **bad))
+    with pytest.raises(NotImplementedError):
+        LlamaConfig.from_hf_dict(dict(_base(), model_type="llama", shared_expert_intermediate_size=64))
