@@ -56,6 +56,7 @@ class LlamaConfig:
     logits_scaling: float = 1.0                    # logits are DIVIDED by this
     rope_scaling: dict | None = None  # HuggingFace dict; types default / linear / llama3 / yarn (ops.basic.rope_tables)
     head_dim_override: int | None = None   # HuggingFace ``head_dim`` when it is not hidden_size / num_attention_heads
+    no_rope_layers: list | None = None     # SmolLM3: one flag per layer, 1 = rotary embedding, 0 = no positional rotation
     partial_rotary_factor: float = 1.0     # < 1: only the first int(head_dim * factor) elements of a head rotate (Phi-4-mini)
     qk_norm: bool = False             # Qwen3: RMSNorm over every query and key head (one weight each) before RoPE
     sliding_window: int | None = None  # attention here is full causal: sequences longer than the window are refused
@@ -114,6 +115,7 @@ class LlamaConfig:
             d["head_dim"] = hd
         if d["partial_rotary_factor"] == 1.0:
             d.pop("partial_rotary_factor")
+        nope = d.pop("no_rope_layers")
         renorm = d.pop("moe_renormalize")
         if not self.num_local_experts:
             d.pop("num_local_experts")
@@ -134,6 +136,9 @@ class LlamaConfig:
                      moe_intermediate_size=self.intermediate_size, shared_expert_intermediate_size=shared_f,
                      norm_topk_prob=bool(renorm), decoder_sparse_step=1, mlp_only_layers=[])
             d["intermediate_size"] = extra.pop("dense_intermediate_size", self.intermediate_size)
+        elif self.model_type == "smollm3":
+            d.update(architectures=["SmolLM3ForCausalLM"], hidden_act="silu", torch_dtype="bfloat16", mlp_bias=False,
+                     use_sliding_window=False, no_rope_layers=list(nope or [1] * self.num_hidden_layers))
         elif self.model_type == "qwen3":
             d.update(architectures=["Qwen3ForCausalLM"], hidden_act="silu", torch_dtype="bfloat16",
                      use_sliding_window=False, head_dim=self.head_dim)
@@ -164,7 +169,8 @@ class LlamaConfig:
                 d["attention_multiplier"] = 1.0 / math.sqrt(self.head_dim)
         return {**extra, **d}
 
-    _KNOWN_TYPES = ("llama", "mistral", "qwen2", "phi3", "mixtral", "qwen3", "qwen3_moe", "qwen2_moe", "granite")
+    _KNOWN_TYPES = ("llama", "mistral", "qwen2", "phi3", "mixtral", "qwen3", "qwen3_moe", "qwen2_moe", "granite",
+                    "smollm3")
 
     @classmethod
     def from_hf_dict(cls, d: dict) -> "LlamaConfig":
@@ -184,6 +190,21 @@ class LlamaConfig:
                 kw.pop(k)
         if mt not in cls._KNOWN_TYPES:
             raise NotImplementedError(f"model_type {mt!r}: only Llama-shaped decoders are built {cls._KNOWN_TYPES}")
+        if mt == "smollm3":          # Llama blocks; every n-th layer applies no rotary embedding
+            n_layers = int(kw.get("num_hidden_layers", 32))
+            flags = d.get("no_rope_layers")
+            if flags is None:
+                step = int(d.get("no_rope_layer_interval", 4) or 4)
+                flags = [int((i + 1) % step != 0) for i in range(n_layers)]
+            if len(flags) != n_layers:
+                raise ValueError(f"no_rope_layers lists {len(flags)} layers, the model has {n_layers}")
+            kw["no_rope_layers"] = [int(bool(v)) for v in flags]
+            if kw.get("attention_bias") or d.get("mlp_bias"):
+                raise NotImplementedError("smollm3 with projection biases is not built")
+            if not d.get("use_sliding_window", False):
+                kw["sliding_window"] = None
+        else:
+            kw.pop("no_rope_layers", None)
         if mt == "qwen3" and d.get("num_experts"):
             raise NotImplementedError("experts in a config of model_type qwen3: the mixture-of-experts type is qwen3_moe")
         dense_ffn = None
@@ -673,6 +694,18 @@ class LlamaModel(nn.Module):
             self._rope_regime = regime
         return self._rope
 
+    def layer_rope(self, cos: torch.Tensor, sin: torch.Tensor) -> list:
+        """One (cos, sin) pair per layer: the tables, or the identity rotation (cos 1, sin 0) for layers that apply no
+        positional rotation. The same kernels run either way."""
+        flags = self.cfg.no_rope_layers
+        n = len(self.layers)
+        if not flags or all(flags):
+            return [(cos, sin)] * n
+        ident = getattr(self, "_rope_ident", None)
+        if ident is None or ident[0].shape != cos.shape or ident[0].device != cos.device:
+            ident = self._rope_ident = (torch.ones_like(cos), torch.zeros_like(sin))
+        return [(cos, sin) if flags[i] else ident for i in range(n)]
+
     # ---- forward
     def hidden_states(self, input_ids: torch.Tensor) -> torch.Tensor:
         """input_ids [B, L] int64 -> final-norm hidden states [B*L, h]."""
@@ -694,7 +727,8 @@ class LlamaModel(nn.Module):
         meta = (B, L, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.rms_norm_eps,
                 bool(self.grad_checkpointing and torch.is_grad_enabled()))
         rmul = float(cfg.residual_multiplier)
-        for layer in self.layers:
+        tables = self.layer_rope(cos, sin)
+        for layer, (cos, sin) in zip(self.layers, tables):
             if pre is not None:
                 pre(layer.input_layernorm, False)
             if LAYER_WEIGHTS_PRE[0] is not None:
@@ -738,7 +772,7 @@ class LlamaModel(nn.Module):
             raise ValueError(f"sequence length {L} exceeds the model's attention window ({cfg.sliding_window})")
         dev = self.embed_tokens.device
         H, Hkv, d = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
-        cos, sin = self.rope(dev, L)
+        tables = self.layer_rope(*self.rope(dev, L))
         kv = Hkv * d
         caches = [(torch.zeros((B, L, kv), dtype=self.embed_tokens.dtype, device=dev),
                    torch.zeros((B, L, kv), dtype=self.embed_tokens.dtype, device=dev)) for _ in self.layers]
@@ -750,7 +784,7 @@ class LlamaModel(nn.Module):
             h = basic.embed_fwd(ids[:, c0:c0 + n].reshape(-1), self.embed_tokens)
             if cfg.embedding_multiplier != 1.0:
                 h = h * cfg.embedding_multiplier
-            for layer, (kc, vc) in zip(self.layers, caches):
+            for layer, (kc, vc), (cos, sin) in zip(self.layers, caches, tables):
                 if LAYER_WEIGHTS_PRE[0] is not None:
                     LAYER_WEIGHTS_PRE[0](layer.input_layernorm)
                 n1, _, _ = basic.rmsnorm_fwd(h, layer.input_layernorm, cfg.rms_norm_eps)

@@ -336,7 +336,8 @@ class TPLlama:
         Hl, Hkvl, d, h, eps = cfg.num_attention_heads // tp, cfg.num_key_value_heads // tp, cfg.head_dim, cfg.hidden_size, cfg.rms_norm_eps
         ids = input_ids.reshape(-1).to(self.device)
         pos = torch.arange(L, dtype=torch.int32, device=self.device).repeat(B)
-        cos, sin = self.rope(L)
+        cos_t, sin_t = self.rope(L)
+        nope = getattr(cfg, "no_rope_layers", None) or []       # 0 = the layer applies no positional rotation
         g.rendezvous()
         x = basic.embed_fwd(ids[r * Ts:(r + 1) * Ts].contiguous(), w["embed_tokens"])
         for i in range(cfg.num_hidden_layers):
@@ -347,7 +348,8 @@ class TPLlama:
                 basic.bias_add_(qkv, w[p + "qkv_bias"])
             if p + "q_norm" in w:      # per-head norms act inside a head: local under head sharding
                 qkv, _ = basic.headnorm_fwd(qkv, w[p + "q_norm"], w[p + "k_norm"], Hl, Hkvl, d, eps)
-            basic.rope_(qkv, pos, cos, sin, Hl + Hkvl, d)
+            if not nope or nope[i]:
+                basic.rope_(qkv, pos, cos_t, sin_t, Hl + Hkvl, d)
             att, _ = attention.attention_fwd(qkv, B, L, Hl, Hkvl, d)
             x = g.gemm_rs(att, w[p + "o_proj"], residual=x)
             basic.rmsnorm_fwd(x, w[p + "post_attention_layernorm"], eps, out=g.slab(T, h))

@@ -316,6 +316,8 @@ def _tp_model_check(dev, dtype, rank, world, k, atol):
         cfg.hidden_size = 64 * cfg.num_attention_heads
     if os.environ.get("TP_QKNORM") == "1":       # Qwen3-style per-head q/k norms: local to a head, so to a rank
         cfg.qk_norm, cfg.model_type = True, "qwen3"
+    if os.environ.get("TP_VARIANT") == "partial_nope":     # three quarters of a head rotate; the second layer not at all
+        cfg.partial_rotary_factor, cfg.no_rope_layers, cfg.model_type = 0.75, [1, 0], "smollm3"
     full = build_model(cfg, dtype=dtype, device=dev, seed=11)
     if cfg.qk_norm:
         gq = torch.Generator().manual_seed(5)        # the same values on every rank

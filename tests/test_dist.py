@@ -152,6 +152,10 @@ def test_cpu_ranks_tensor_parallel_teacher_with_per_head_qk_norms():
     _launch("cpu_tp", 2, env={"TP_QKNORM": "1"})
 
 
+def test_cpu_ranks_tensor_parallel_teacher_with_partial_rotation_and_a_layer_without():
+    _launch("cpu_tp", 2, env={"TP_VARIANT": "partial_nope"})
+
+
 def test_cpu_ranks_vocabulary_parallel_head_matches_unsharded():
     _launch("cpu_vp_head", 2)
 

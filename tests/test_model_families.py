@@ -270,6 +270,49 @@ def test_partial_rotary_matches_huggingface(tmp_path):
     assert torch.allclose(basic.rope_(r, pos, cos, sin, 3, 32, inverse=True), v, atol=1e-5)
 
 
+def test_smollm3_layers_without_rotation_match_huggingface(tmp_path):
+    """SmolLM3: Llama blocks of which every n-th applies no rotary embedding (the flags come from the interval when
+    the config does not list them)."""
+    base = _base(num_hidden_layers=4)
+    hf_cfg = tr.SmolLM3Config(**base, pad_token_id=0, attn_implementation="eager", tie_word_embeddings=True,
+                              no_rope_layer_interval=2)
+    assert hf_cfg.no_rope_layers == [1, 0, 1, 0]
+    hf = tr.SmolLM3ForCausalLM(hf_cfg).float()
+    hf.save_pretrained(str(tmp_path / "hf"), safe_serialization=True)
+    model = load_hf_model(str(tmp_path / "hf"), dtype=torch.float32)
+    assert model.cfg.model_type == "smollm3" and model.cfg.no_rope_layers == [1, 0, 1, 0]
+    x = torch.randint(0, 320, (2, 64))
+    ours, ref = model(x), hf(x).logits
+    assert torch.allclose(ours, ref, atol=3e-4, rtol=1e-3), (ours - ref).abs().max()
+    every = build_model(LlamaConfig.from_hf_dict(dict(model.cfg.to_hf_dict(), no_rope_layers=[1, 1, 1, 1])),
+                        dtype=torch.float32, device="cpu", seed=0)
+    every.load_state_dict(model.state_dict())
+    assert (every(x) - ref).abs().max() > 3e-3                  # the flags matter
+    # from the interval alone
+    d = dict(model.cfg.to_hf_dict())
+    d.pop("no_rope_layers")
+    assert LlamaConfig.from_hf_dict(dict(d, no_rope_layer_interval=3)).no_rope_layers == [1, 1, 0, 1]
+    # gradients, with recomputation in backward, and the chunked inference path
+    model.grad_checkpointing = True
+    tgt = torch.randint(0, 320, (2 * 64,))
+    torch.nn.functional.cross_entropy(model(x).view(-1, 320), tgt).backward()
+    torch.nn.functional.cross_entropy(hf(x).logits.view(-1, 320), tgt).backward()
+    for li in (0, 1):
+        want = torch.cat([getattr(hf.model.layers[li].self_attn, n).weight.grad for n in ("q_proj", "k_proj", "v_proj")])
+        assert torch.allclose(model.layers[li].qkv_proj.grad, want, atol=2e-5, rtol=2e-3), li
+    with torch.no_grad():
+        hs = model.hidden_states_chunked(x, 16)
+        assert torch.allclose(torch.nn.functional.linear(hs, model.lm_head).view(2, 64, -1), ref, atol=3e-4, rtol=1e-3)
+    save_hf_model(model, str(tmp_path / "ours"))
+    hf2 = tr.AutoModelForCausalLM.from_pretrained(str(tmp_path / "ours"), torch_dtype=torch.float32,
+                                                  attn_implementation="eager")
+    assert hf2.config.no_rope_layers == [1, 0, 1, 0] and torch.allclose(hf2(x).logits, ref, atol=3e-4, rtol=1e-3)
+    with pytest.raises(ValueError, match="lists 3 layers"):
+        LlamaConfig.from_hf_dict(dict(model.cfg.to_hf_dict(), no_rope_layers=[1, 0, 1]))
+    # other model types ignore the key
+    assert LlamaConfig.from_hf_dict(dict(_base(), model_type="llama", no_rope_layers=[0, 0])).no_rope_layers is None
+
+
 def test_llama_with_attention_and_mlp_biases_matches_huggingface(tmp_path):
     """HuggingFace's Llama with attention_bias (q, k, v and o) and mlp_bias (gate, up, down) - the Granite code models."""
     d = dict(_base(), model_type="llama", attention_bias=True, mlp_bias=True)
