@@ -109,3 +109,60 @@ def test_cli_case(world, name):
         assert len(os.listdir(trained)) == 2                              # the epoch-1 checkpoint and the final one
         assert {"model_state.pt", "optimizer_state.pt", "scheduler_state.pt", "trainer_state.json"} <= set(
             os.listdir(os.path.join(cache, "student", "states")))
+
+
+FAMILIES = {
+    "qwen2_moe": dict(model_type="qwen2_moe", num_local_experts=4, num_experts_per_tok=2, intermediate_size=48,
+                      shared_expert_intermediate_size=80, attention_bias=True, moe_renormalize=False),
+    "qwen3_moe": dict(model_type="qwen3_moe", num_local_experts=4, num_experts_per_tok=2, intermediate_size=48,
+                      qk_norm=True, head_dim_override=32),
+    "smollm3": dict(model_type="smollm3", no_rope_layers=[1, 0]),
+    "phi3, three quarters of a head rotate": dict(model_type="phi3", partial_rotary_factor=0.75),
+    "granite": dict(model_type="granite", embedding_multiplier=6.0, attention_multiplier=0.2, residual_multiplier=0.4,
+                    logits_scaling=3.0),
+    "qwen3": dict(model_type="qwen3", qk_norm=True),
+}
+
+
+@pytest.mark.parametrize("family", list(FAMILIES))
+def test_cli_with_teacher_and_student_of_a_model_family(tmp_path, family):
+    """Collection, training, validation and the saved checkpoint with both models of one family; the saved student
+    loads again and HuggingFace's config class for the family accepts its config.json."""
+    import dataclasses
+    import transformers as tr
+    from llm_distillery_b200.ckpt.hf import load_hf_model
+    root = str(tmp_path)
+    os.environ["B200_NO_PROGRESS"] = "1"
+    tok = os.path.join(root, "tok")
+    synthetic.make_tokenizer(tok, 400)
+    kw = dict(vocab_size=512, hidden_size=64, intermediate_size=176, max_position_embeddings=512, num_hidden_layers=2)
+    fam = FAMILIES[family]
+    t_cfg = dataclasses.replace(preset("plumbing-teacher", **kw), **fam)
+    s_cfg = dataclasses.replace(preset("plumbing-student", **kw), **fam)
+    synthetic.make_model_dir(os.path.join(root, "teachers", "teacher_a"), t_cfg, tok, seed=1, batch_size=4)
+    synthetic.make_model_dir(os.path.join(root, "student"), s_cfg, tok, seed=2)
+    synthetic.make_dataset(os.path.join(root, "train.jsonl"), 6, seed=3)
+    synthetic.make_dataset(os.path.join(root, "val.jsonl"), 2, seed=4)
+    cache = os.path.join(root, "cache")
+    conf = {"dataset_path": os.path.join(root, "train.jsonl"), "validation_dataset_path": os.path.join(root, "val.jsonl"),
+            "teacher_models_folder": os.path.join(root, "teachers"), "student_path": os.path.join(root, "student"),
+            "context_len": 96, "crop_distr_to_size": 400, "save_topK": 20, "enable_topK": True, "device": "cpu",
+            "num_epochs": 1, "num_warmup_steps": 1, "batch_size": 2, "grad_accum_batches": 1, "lr": 1e-3,
+            "optimizer": "adamw", "data_order": "sorted", "training_precision": "fp32", "freeze_layers": [], "loss": "kl",
+            "max_cache_size_gb": 320, "cache_folder": cache}
+    path = os.path.join(root, "config.json")
+    with open(path, "w") as f:
+        json.dump(conf, f)
+    out = cli.main(["--config", path])
+    assert out["trained_samples"] == 6 and out["tokens_collected"] > 0
+    assert all(math.isfinite(v) for v in out["last_validation"].values())
+    trained = os.path.join(cache, "student", "trained")
+    final = os.path.join(trained, [d for d in os.listdir(trained) if d.endswith("final")][0])
+    back = load_hf_model(final, dtype=None)
+    for k, v in fam.items():
+        assert getattr(back.cfg, k) == v, (k, getattr(back.cfg, k))
+    init = load_hf_state_dict(os.path.join(root, "student"))
+    sd = load_hf_state_dict(final)
+    assert set(sd) == set(init) and max(float((sd[k].float() - init[k].float()).abs().max()) for k in init) > 1e-5
+    hf_cfg = tr.AutoConfig.from_pretrained(final)
+    assert hf_cfg.model_type == fam["model_type"]
