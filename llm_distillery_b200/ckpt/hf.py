@@ -268,6 +268,9 @@ def load_tp_weights(path: str, rank: int, tp: int, vocab: int | None = None, dty
         raise NotImplementedError("tensor-parallel collection does not apply Granite's multipliers: use tp_size = 1")
     if cfg.o_bias or cfg.mlp_bias:
         raise NotImplementedError("tensor-parallel collection does not carry o_proj / MLP biases: use tp_size = 1")
+    if cfg.sandwich or cfg.rope_interleaved:
+        raise NotImplementedError(f"tensor-parallel collection is built for Llama-style pre-norm layers; a "
+                                  f"{cfg.model_type} teacher runs with tp_size = 1 (ranks become data-parallel replicas)")
     if cfg.num_local_experts:
         raise NotImplementedError("tensor-parallel collection is built for dense decoders; a mixture-of-experts teacher "
                                   "runs with tp_size = 1 (ranks become data-parallel replicas)")

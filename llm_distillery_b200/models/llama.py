@@ -1,5 +1,6 @@
 """Llama-family decoder (Llama 1/2/3, TinyLlama, Mistral: RMSNorm, RoPE, GQA, SwiGLU, optional tied embeddings;
-Qwen2 with q/k/v bias, Phi-3 with fused projections, Mixtral with sparse experts - models/moe.py)
+Qwen2 with q/k/v bias, Phi-3 with fused projections, Mixtral with sparse experts - models/moe.py; OLMo 2 and GLM-4
+with norms behind the branches - models/sandwich.py)
 for both roles: student training (forward + hand-written backward) and teacher inference.
 
 Design. Each decoder layer is ONE autograd node (``DecoderLayerFn``) whose forward and backward are explicit
@@ -59,6 +60,10 @@ class LlamaConfig:
     no_rope_layers: list | None = None     # SmolLM3: one flag per layer, 1 = rotary embedding, 0 = no positional rotation
     partial_rotary_factor: float = 1.0     # < 1: only the first int(head_dim * factor) elements of a head rotate (Phi-4-mini)
     qk_norm: bool = False             # Qwen3: RMSNorm over every query and key head (one weight each) before RoPE
+    qk_norm_full: bool = False        # OLMo 2: one RMSNorm over the whole query projection, one over the key projection
+    pre_norm: bool = True             # RMSNorm on the way into the attention and MLP branches (false: OLMo 2)
+    post_norm: bool = False           # RMSNorm on the way out of both branches (OLMo 2, GLM-4 0414; models/sandwich.py)
+    rope_interleaved: bool = False    # checkpoint layout: rotary pairs are neighbours (GLM); rows are permuted at load / save
     sliding_window: int | None = None  # attention here is full causal: sequences longer than the window are refused
     pad_token_id: int | None = None
     extra: dict = field(default_factory=dict)   # other keys of the source config.json, written back unchanged
@@ -66,6 +71,11 @@ class LlamaConfig:
     @property
     def head_dim(self) -> int:
         return self.head_dim_override or self.hidden_size // self.num_attention_heads
+
+    @property
+    def sandwich(self) -> bool:
+        """Whether the layers take the general node of models/sandwich.py instead of the fused pre-norm layer."""
+        return self.post_norm or not self.pre_norm or self.qk_norm_full
 
     @property
     def rotary_dim(self) -> int:
@@ -89,6 +99,12 @@ class LlamaConfig:
             per_layer += self.q_size + 2 * self.kv_size
         if self.qk_norm:
             per_layer += 2 * self.head_dim
+        if self.qk_norm_full:
+            per_layer += self.q_size + self.kv_size
+        if not self.pre_norm:
+            per_layer -= 2 * h
+        if self.post_norm:
+            per_layer += 2 * h
         if self.o_bias:
             per_layer += h
         if self.mlp_bias:
@@ -121,6 +137,8 @@ class LlamaConfig:
             d.pop("num_local_experts")
             d.pop("num_experts_per_tok")
         qk = d.pop("qk_norm")
+        for k in ("qk_norm_full", "pre_norm", "post_norm", "rope_interleaved"):      # implied by the model type
+            d.pop(k)
         shared_f = d.pop("shared_expert_intermediate_size")
         gran = {k: d.pop(k) for k in ("embedding_multiplier", "attention_multiplier", "residual_multiplier", "logits_scaling")}
         if self.model_type == "qwen3_moe":      # HuggingFace's names: num_experts, moe_intermediate_size, norm_topk_prob
@@ -136,6 +154,12 @@ class LlamaConfig:
                      moe_intermediate_size=self.intermediate_size, shared_expert_intermediate_size=shared_f,
                      norm_topk_prob=bool(renorm), decoder_sparse_step=1, mlp_only_layers=[])
             d["intermediate_size"] = extra.pop("dense_intermediate_size", self.intermediate_size)
+        elif self.model_type == "olmo2":
+            d.update(architectures=["Olmo2ForCausalLM"], hidden_act="silu", torch_dtype="bfloat16", attention_bias=False)
+        elif self.model_type in ("glm", "glm4"):
+            d.update(architectures=["GlmForCausalLM" if self.model_type == "glm" else "Glm4ForCausalLM"],
+                     hidden_act="silu", torch_dtype="bfloat16", head_dim=self.head_dim,
+                     partial_rotary_factor=self.partial_rotary_factor)
         elif self.model_type == "smollm3":
             d.update(architectures=["SmolLM3ForCausalLM"], hidden_act="silu", torch_dtype="bfloat16", mlp_bias=False,
                      use_sliding_window=False, no_rope_layers=list(nope or [1] * self.num_hidden_layers))
@@ -170,7 +194,7 @@ class LlamaConfig:
         return {**extra, **d}
 
     _KNOWN_TYPES = ("llama", "mistral", "qwen2", "phi3", "mixtral", "qwen3", "qwen3_moe", "qwen2_moe", "granite",
-                    "smollm3")
+                    "smollm3", "olmo2", "glm", "glm4")
 
     @classmethod
     def from_hf_dict(cls, d: dict) -> "LlamaConfig":
@@ -249,7 +273,18 @@ class LlamaConfig:
                 raise NotImplementedError("qwen3 with attention_bias also puts a bias on o_proj, which is not built")
             if not d.get("use_sliding_window", False):
                 kw["sliding_window"] = None
-        if mt in ("qwen2", "qwen2_moe"):
+        for k in ("qk_norm_full", "pre_norm", "post_norm", "rope_interleaved"):      # set by the model type alone
+            kw.pop(k, None)
+        if mt == "olmo2":            # no norms in front of the branches, norms behind them, q/k norms over all heads
+            if kw.get("attention_bias"):
+                raise NotImplementedError("olmo2 with attention_bias also puts a bias on o_proj, which is not built")
+            kw.update(pre_norm=False, post_norm=True, qk_norm_full=True)
+        if mt in ("glm", "glm4"):    # rotary pairs are neighbours in the checkpoint; half of each head rotates
+            kw.update(rope_interleaved=True, post_norm=(mt == "glm4"),
+                      attention_bias=bool(d.get("attention_bias", True)))
+            if d.get("partial_rotary_factor") is None and not (isinstance(rp, dict) and rp.get("partial_rotary_factor")):
+                kw["partial_rotary_factor"] = 0.5
+        elif mt in ("qwen2", "qwen2_moe"):
             kw["attention_bias"] = True
         elif kw.get("attention_bias"):
             if mt not in ("llama", "mistral", "granite"):
@@ -603,22 +638,29 @@ class LlamaDecoderLayer(nn.Module):
         super().__init__()
         h, f = cfg.hidden_size, cfg.intermediate_size
         kw = dict(dtype=dtype, device=device)
-        self.input_layernorm = nn.Parameter(torch.ones(h, **kw))
+        if cfg.pre_norm:
+            self.input_layernorm = nn.Parameter(torch.ones(h, **kw))
         self.qkv_proj = nn.Parameter(torch.empty(cfg.q_size + 2 * cfg.kv_size, h, **kw))
         if cfg.attention_bias:
             self.qkv_bias = nn.Parameter(torch.zeros(cfg.q_size + 2 * cfg.kv_size, **kw))
         if cfg.qk_norm:
             self.q_norm = nn.Parameter(torch.ones(cfg.head_dim, **kw))
             self.k_norm = nn.Parameter(torch.ones(cfg.head_dim, **kw))
+        elif cfg.qk_norm_full:
+            self.q_norm = nn.Parameter(torch.ones(cfg.q_size, **kw))
+            self.k_norm = nn.Parameter(torch.ones(cfg.kv_size, **kw))
         self.o_proj = nn.Parameter(torch.empty(h, cfg.q_size, **kw))
         if cfg.o_bias:
             self.o_bias = nn.Parameter(torch.zeros(h, **kw))
+        if cfg.post_norm:
+            self.attn_out_norm = nn.Parameter(torch.ones(h, **kw))
         if cfg.mlp_bias:
             if cfg.num_local_experts:
                 raise NotImplementedError("mlp_bias with experts is not built")
             self.gate_up_bias = nn.Parameter(torch.zeros(2 * f, **kw))
             self.down_bias = nn.Parameter(torch.zeros(h, **kw))
-        self.post_attention_layernorm = nn.Parameter(torch.ones(h, **kw))
+        if cfg.pre_norm:
+            self.post_attention_layernorm = nn.Parameter(torch.ones(h, **kw))
         E = cfg.num_local_experts
         if E:       # sparse mixture of experts: a router and E stacked expert matrices (models/moe.py)
             self.router = nn.Parameter(torch.empty(E, h, **kw))
@@ -632,6 +674,17 @@ class LlamaDecoderLayer(nn.Module):
         else:
             self.gate_up_proj = nn.Parameter(torch.empty(2 * f, h, **kw))
             self.down_proj = nn.Parameter(torch.empty(h, f, **kw))
+        if cfg.post_norm:
+            self.mlp_out_norm = nn.Parameter(torch.ones(h, **kw))
+        if cfg.sandwich and (E or cfg.o_bias or cfg.mlp_bias or cfg.residual_multiplier != 1.0):
+            raise NotImplementedError("output norms / whole-projection q-k norms together with experts, o_proj or MLP "
+                                      "biases or a residual multiplier are not built")
+
+    @property
+    def first_param(self) -> torch.Tensor:
+        """The layer's first registered parameter: the key under which the engines' per-layer hooks know the layer
+        (lowest offset of the layer in a flat parameter buffer)."""
+        return next(iter(self.parameters()))
 
 
 class LlamaModel(nn.Module):
@@ -730,9 +783,18 @@ class LlamaModel(nn.Module):
         tables = self.layer_rope(cos, sin)
         for layer, (cos, sin) in zip(self.layers, tables):
             if pre is not None:
-                pre(layer.input_layernorm, False)
+                pre(layer.first_param, False)
             if LAYER_WEIGHTS_PRE[0] is not None:
-                LAYER_WEIGHTS_PRE[0](layer.input_layernorm)
+                LAYER_WEIGHTS_PRE[0](layer.first_param)
+            if cfg.sandwich:
+                from .sandwich import SandwichLayerFn
+                g = lambda n: getattr(layer, n, None)
+                h = SandwichLayerFn.apply(h, pos, cos, sin,
+                                          meta + (2 if cfg.qk_norm_full else int(cfg.qk_norm), layer.first_param),
+                                          layer.qkv_proj, layer.o_proj, layer.gate_up_proj, layer.down_proj,
+                                          g("input_layernorm"), g("post_attention_layernorm"), g("attn_out_norm"),
+                                          g("mlp_out_norm"), g("qkv_bias"), g("q_norm"), g("k_norm"))
+                continue
             if cfg.num_local_experts:
                 from .moe import AttnBlockFn, MoEBlockFn
                 h = AttnBlockFn.apply(h, pos, cos, sin, layer.input_layernorm, layer.qkv_proj, layer.o_proj, meta,
@@ -786,7 +848,17 @@ class LlamaModel(nn.Module):
                 h = h * cfg.embedding_multiplier
             for layer, (kc, vc), (cos, sin) in zip(self.layers, caches, tables):
                 if LAYER_WEIGHTS_PRE[0] is not None:
-                    LAYER_WEIGHTS_PRE[0](layer.input_layernorm)
+                    LAYER_WEIGHTS_PRE[0](layer.first_param)
+                if cfg.sandwich:
+                    from .sandwich import layer_inference
+
+                    def attend(qkv, kc=kc, vc=vc, cos=cos, sin=sin):
+                        basic.rope_(qkv, pos, cos, sin, H + Hkv, d)
+                        kc[:, c0:c0 + n] = qkv[:, H * d:(H + Hkv) * d].reshape(B, n, kv)
+                        vc[:, c0:c0 + n] = qkv[:, (H + Hkv) * d:].reshape(B, n, kv)
+                        return attention.attention_fwd_cached(qkv, kc, vc, B, n, c0, H, Hkv, d)
+                    h = layer_inference(layer, cfg, h, attend, cfg.rms_norm_eps)
+                    continue
                 n1, _, _ = basic.rmsnorm_fwd(h, layer.input_layernorm, cfg.rms_norm_eps)
                 if not hasattr(layer, "qkv_bias") and not cfg.qk_norm:
                     qkv = basic.linear_rope_fwd(n1, layer.qkv_proj, pos, cos, sin, H + Hkv, d)
@@ -839,6 +911,36 @@ class LlamaModel(nn.Module):
         q, kv, f = cfg.q_size, cfg.kv_size, cfg.intermediate_size
         for i, l in enumerate(self.layers):
             pre = f"model.layers.{i}."
+            if cfg.model_type in ("olmo2", "glm", "glm4"):
+                glm = cfg.model_type != "olmo2"
+                if glm:
+                    yield pre + "input_layernorm.weight", l.input_layernorm, None
+                yield pre + "self_attn.q_proj.weight", l.qkv_proj, slice(0, q)
+                yield pre + "self_attn.k_proj.weight", l.qkv_proj, slice(q, q + kv)
+                yield pre + "self_attn.v_proj.weight", l.qkv_proj, slice(q + kv, q + 2 * kv)
+                if cfg.attention_bias:
+                    yield pre + "self_attn.q_proj.bias", l.qkv_bias, slice(0, q)
+                    yield pre + "self_attn.k_proj.bias", l.qkv_bias, slice(q, q + kv)
+                    yield pre + "self_attn.v_proj.bias", l.qkv_bias, slice(q + kv, q + 2 * kv)
+                if cfg.qk_norm_full:
+                    yield pre + "self_attn.q_norm.weight", l.q_norm, None
+                    yield pre + "self_attn.k_norm.weight", l.k_norm, None
+                yield pre + "self_attn.o_proj.weight", l.o_proj, None
+                if glm:      # GLM keeps Llama's name for the norm in front of the MLP and stores gate / up fused
+                    if cfg.post_norm:
+                        yield pre + "post_self_attn_layernorm.weight", l.attn_out_norm, None
+                    yield pre + "post_attention_layernorm.weight", l.post_attention_layernorm, None
+                    yield pre + "mlp.gate_up_proj.weight", l.gate_up_proj, None
+                    yield pre + "mlp.down_proj.weight", l.down_proj, None
+                    if cfg.post_norm:
+                        yield pre + "post_mlp_layernorm.weight", l.mlp_out_norm, None
+                else:        # OLMo 2 uses that name for the norm BEHIND the attention
+                    yield pre + "post_attention_layernorm.weight", l.attn_out_norm, None
+                    yield pre + "mlp.gate_proj.weight", l.gate_up_proj, slice(0, f)
+                    yield pre + "mlp.up_proj.weight", l.gate_up_proj, slice(f, 2 * f)
+                    yield pre + "mlp.down_proj.weight", l.down_proj, None
+                    yield pre + "post_feedforward_layernorm.weight", l.mlp_out_norm, None
+                continue
             yield pre + "input_layernorm.weight", l.input_layernorm, None
             if cfg.model_type == "phi3":     # the checkpoint stores the fused projections, in this model's own order
                 yield pre + "self_attn.qkv_proj.weight", l.qkv_proj, None
@@ -894,7 +996,35 @@ class LlamaModel(nn.Module):
         if not cfg.tie_word_embeddings:
             yield "lm_head.weight", self.lm_head, None
 
+    def _rotary_row_order(self) -> torch.Tensor:
+        """Row order inside one head that turns a checkpoint whose rotary pairs are neighbours (2i, 2i+1) into this
+        model's layout, where element i pairs with i + rot/2: q . k is unchanged when both are permuted alike."""
+        d, rot = self.cfg.head_dim, self.cfg.rotary_dim
+        return torch.cat([torch.arange(0, rot, 2), torch.arange(1, rot, 2), torch.arange(rot, d)])
+
+    def _permute_rotary_rows(self, sd: dict, to_checkpoint: bool) -> dict:
+        order = self._rotary_row_order()
+        d = self.cfg.head_dim
+        out = dict(sd)
+        for k, v in sd.items():
+            if k.endswith(("self_attn.q_proj.weight", "self_attn.k_proj.weight", "self_attn.q_proj.bias",
+                           "self_attn.k_proj.bias")):
+                heads = v.reshape(v.shape[0] // d, d, *v.shape[1:])
+                idx = order.to(v.device)
+                if to_checkpoint:
+                    t = torch.empty_like(heads)
+                    t[:, idx] = heads
+                else:
+                    t = heads[:, idx]
+                out[k] = t.reshape(v.shape)
+        return out
+
     def to_hf_state_dict(self) -> dict[str, torch.Tensor]:
+        if self.cfg.rope_interleaved:
+            return self._permute_rotary_rows(self._to_hf_state_dict(), to_checkpoint=True)
+        return self._to_hf_state_dict()
+
+    def _to_hf_state_dict(self) -> dict[str, torch.Tensor]:
         if self.quant is None:
             return {n: (p.data if sl is None else p.data[sl]) for n, p, sl in self.named_hf_parameters()}
         # frozen low-bit matrices live packed; their parameters are views of a rotating buffer: export dequantised copies
@@ -923,6 +1053,8 @@ class LlamaModel(nn.Module):
     def load_hf_state_dict(self, sd: dict[str, torch.Tensor], strict: bool = True) -> None:
         if self.cfg.num_local_experts and any(k.endswith("mlp.experts.gate_up_proj") for k in sd):
             sd = self._unstack_experts(sd)
+        if self.cfg.rope_interleaved:
+            sd = self._permute_rotary_rows(sd, to_checkpoint=False)
         seen = set()
         for n, p, sl in self.named_hf_parameters():
             if n not in sd:

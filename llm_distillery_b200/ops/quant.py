@@ -122,7 +122,7 @@ class FrozenQuantLinears:
                     p.requires_grad = False
                     p.data = self._buffers[i & 1][off:off + p.numel()].view(p.shape)
                 self.layers.append(packed)
-                self._layer_of[id(layer.input_layernorm)] = i
+                self._layer_of[id(layer.first_param)] = i
 
     def materialize(self, layer_index: int) -> None:
         layer = self.model.layers[layer_index]

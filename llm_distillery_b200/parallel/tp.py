@@ -224,6 +224,8 @@ def shard_llama_weights(cfg, sd: dict, rank: int, tp: int, vocab: int | None = N
     H, Hkv, d, f = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.intermediate_size
     if H % tp or Hkv % tp or f % tp:
         raise ValueError(f"tp={tp} must divide heads ({H}), kv heads ({Hkv}) and the FFN width ({f})")
+    if getattr(cfg, "sandwich", False):
+        raise NotImplementedError("tensor-parallel collection is built for Llama-style pre-norm layers")
     Hl, Hkvl, fl = H // tp, Hkv // tp, f // tp
     out = {"embed_tokens": sd["embed_tokens"], "norm": sd["norm"]}
     for i in range(cfg.num_hidden_layers):

@@ -77,10 +77,19 @@ def cpu_engine():
 
 def _tiny3(dtype, device, tied):
     moe = dict(model_type="mixtral", num_local_experts=4, num_experts_per_tok=2) if os.environ.get("Z3_MOE") == "1" else {}
+    if os.environ.get("Z3_FAMILY") == "olmo2":       # norms behind the branches, none in front: models/sandwich.py
+        moe = {}
+        tied = False
+        extra = dict(model_type="olmo2", pre_norm=False, post_norm=True, qk_norm_full=True)
+    elif os.environ.get("Z3_FAMILY") == "glm4":
+        extra = dict(model_type="glm4", post_norm=True, attention_bias=True, partial_rotary_factor=0.5, rope_interleaved=True)
+    else:
+        extra = {}
+    moe = dict(moe, **extra)
     cfg = LlamaConfig(vocab_size=512, hidden_size=128, intermediate_size=256, num_hidden_layers=3, num_attention_heads=2,
                       num_key_value_heads=1, max_position_embeddings=128, tie_word_embeddings=tied, **moe)
     model = build_model(cfg, dtype=dtype, device=device, seed=7)
-    if moe:
+    if cfg.num_local_experts:
         with torch.no_grad():          # decisive routing: the sharded and the single-process run must pick the same experts
             for l in model.layers:
                 l.router.mul_(25.0)

@@ -121,6 +121,10 @@ FAMILIES = {
     "granite": dict(model_type="granite", embedding_multiplier=6.0, attention_multiplier=0.2, residual_multiplier=0.4,
                     logits_scaling=3.0),
     "qwen3": dict(model_type="qwen3", qk_norm=True),
+    "olmo2": dict(model_type="olmo2", pre_norm=False, post_norm=True, qk_norm_full=True),
+    "glm4": dict(model_type="glm4", post_norm=True, attention_bias=True, partial_rotary_factor=0.5, rope_interleaved=True,
+                 head_dim_override=32),
+    "glm": dict(model_type="glm", attention_bias=True, partial_rotary_factor=0.5, rope_interleaved=True),
 }
 
 

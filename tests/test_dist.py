@@ -44,6 +44,12 @@ def test_cpu_ranks_full_parameter_sharding_of_a_mixture_of_experts_student():
     _launch("cpu_zero3", 2, env={"Z3_MOE": "1"})
 
 
+@pytest.mark.parametrize("family", ["olmo2", "glm4"])
+def test_cpu_ranks_full_sharding_with_layers_that_have_output_norms(family):
+    """The general layer node (models/sandwich.py) calls the engines' per-layer hooks like the fused layer does."""
+    _launch("cpu_zero3", 2, env={"Z3_FAMILY": family})
+
+
 def test_cpu_ranks_pipeline_with_fully_sharded_student(tmp_path):
     _launch("cpu_cli_zero3", 2, extra=(str(tmp_path),))
 

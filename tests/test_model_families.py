@@ -313,6 +313,60 @@ def test_smollm3_layers_without_rotation_match_huggingface(tmp_path):
     assert LlamaConfig.from_hf_dict(dict(_base(), model_type="llama", no_rope_layers=[0, 0])).no_rope_layers is None
 
 
+@pytest.mark.parametrize("family,recompute", [("olmo2", False), ("olmo2", True), ("glm", False), ("glm4", False),
+                                              ("glm4", True)])
+def test_layers_with_output_norms_match_huggingface(tmp_path, family, recompute):
+    """OLMo 2 (norms behind the branches only, q/k norms over the whole projections), GLM (half of each head rotates,
+    rotary pairs neighbours in the checkpoint, fused gate/up tensor, q/k/v bias) and GLM-4 0414 (GLM with norms behind
+    the branches as well): logits, every gradient, the chunked inference path and checkpoints both ways."""
+    cls, ccls, extra = {"olmo2": (tr.Olmo2ForCausalLM, tr.Olmo2Config, {}),
+                        "glm": (tr.GlmForCausalLM, tr.GlmConfig, dict(head_dim=16)),
+                        "glm4": (tr.Glm4ForCausalLM, tr.Glm4Config, dict(head_dim=16))}[family]
+    torch.manual_seed(4)
+    hf = cls(ccls(**{k: v for k, v in _base().items() if k != "rope_theta"}, **extra, pad_token_id=0,
+                  attn_implementation="eager", tie_word_embeddings=False)).float()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if "norm" in n:
+                p.uniform_(0.5, 1.5)
+            elif n.endswith("bias"):
+                p.normal_(0, 0.05)
+    hf.save_pretrained(str(tmp_path / "hf"), safe_serialization=True)
+    model = load_hf_model(str(tmp_path / "hf"), dtype=torch.float32)
+    cfg = model.cfg
+    assert cfg.model_type == family and cfg.sandwich == (family != "glm")
+    assert (cfg.pre_norm, cfg.post_norm, cfg.qk_norm_full) == {"olmo2": (False, True, True), "glm": (True, False, False),
+                                                                "glm4": (True, True, False)}[family]
+    if family != "olmo2":
+        assert cfg.rope_interleaved and cfg.partial_rotary_factor == 0.5 and cfg.attention_bias and not cfg.o_bias
+    assert sum(p.numel() for p in model.parameters()) == cfg.num_params() == sum(p.numel() for p in hf.parameters())
+    model.grad_checkpointing = recompute
+    x = torch.randint(1, 320, (2, 48))          # not the padding id: HuggingFace's embedding gives it no gradient
+    ours, ref = model(x), hf(x).logits
+    assert torch.allclose(ours, ref, atol=3e-4, rtol=1e-3), (ours - ref).abs().max()
+    tgt = torch.randint(0, 320, (2 * 48,))
+    torch.nn.functional.cross_entropy(ours.reshape(-1, 320), tgt).backward()
+    torch.nn.functional.cross_entropy(ref.reshape(-1, 320), tgt).backward()
+    ours_g = {n: (p.grad if sl is None else p.grad[sl]) for n, p, sl in model.named_hf_parameters()}
+    if cfg.rope_interleaved:
+        ours_g = model._permute_rotary_rows(ours_g, to_checkpoint=True)
+    hf_g = {n: p.grad for n, p in hf.named_parameters()}
+    assert set(ours_g) == set(hf_g)
+    for n, g in ours_g.items():
+        assert torch.allclose(g, hf_g[n], atol=2e-5, rtol=2e-3), (n, (g - hf_g[n]).abs().max())
+    model.grad_checkpointing = False
+    with torch.no_grad():
+        hs = model.hidden_states_chunked(x, 16)
+        assert torch.allclose(torch.nn.functional.linear(hs, model.lm_head).view(2, 48, -1), ref, atol=3e-4, rtol=1e-3)
+    save_hf_model(model, str(tmp_path / "ours"))
+    hf2 = tr.AutoModelForCausalLM.from_pretrained(str(tmp_path / "ours"), torch_dtype=torch.float32,
+                                                  attn_implementation="eager")
+    assert type(hf2) is cls and torch.allclose(hf2(x).logits, ref, atol=3e-4, rtol=1e-3)
+    if family == "olmo2":
+        with pytest.raises(NotImplementedError, match="o_proj"):
+            LlamaConfig.from_hf_dict(dict(cfg.to_hf_dict(), attention_bias=True))
+
+
 def test_llama_with_attention_and_mlp_biases_matches_huggingface(tmp_path):
     """HuggingFace's Llama with attention_bias (q, k, v and o) and mlp_bias (gate, up, down) - the Granite code models."""
     d = dict(_base(), model_type="llama", attention_bias=True, mlp_bias=True)

@@ -70,12 +70,13 @@ def test_engine_trains_the_bias():
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("variant", ["qwen2", "qwen3", "llama with biases", "plain llama, long batch", "granite",
-                                     "plain partial rotary, long batch"])
+                                     "plain partial rotary, long batch", "olmo2", "glm4, long batch"])
 def test_gpu_kernels_follow_the_cpu_model(variant):
     """bf16 kernels (GEMMs with their epilogues, bias add, per-head norms, RoPE, flash attention ...) against the fp32 CPU
     statement of the same model, for the layer variants: q/k/v bias (Qwen2), per-head q/k norms (Qwen3), biases on every
     projection (Llama with attention_bias / mlp_bias), a plain layer with enough rows for the fused epilogues, Granite's
-    multipliers, and heads of which three quarters rotate (the fused rotary epilogues must step aside)."""
+    multipliers, heads of which three quarters rotate (the fused rotary epilogues must step aside), and the general
+    layer node with norms behind the branches (OLMo 2 with q/k norms over the whole projections; GLM-4)."""
     kw = dict(vocab_size=512, hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=4,
               num_key_value_heads=2, max_position_embeddings=1024, rope_theta=1e6, rms_norm_eps=1e-6)
     if variant == "qwen2":
@@ -86,6 +87,10 @@ def test_gpu_kernels_follow_the_cpu_model(variant):
         kw.update(attention_bias=True, o_bias=True, mlp_bias=True)
     elif "partial rotary" in variant:
         kw.update(partial_rotary_factor=0.75)
+    elif variant == "olmo2":
+        kw.update(model_type="olmo2", pre_norm=False, post_norm=True, qk_norm_full=True)
+    elif variant.startswith("glm4"):
+        kw.update(model_type="glm4", post_norm=True, attention_bias=True, partial_rotary_factor=0.5, rope_interleaved=True)
     elif variant == "granite":
         kw.update(model_type="granite", embedding_multiplier=6.0, attention_multiplier=0.09, residual_multiplier=0.3,
                   logits_scaling=4.0, attention_bias=True, o_bias=True, mlp_bias=True)
@@ -96,14 +101,14 @@ def test_gpu_kernels_follow_the_cpu_model(variant):
         for n, p in cpu.named_parameters():
             if n.endswith("_bias"):
                 p.copy_(torch.randn(p.shape, generator=g) * 0.05)
-            elif n.endswith("q_norm") or n.endswith("k_norm"):
+            elif n.endswith("q_norm") or n.endswith("k_norm") or n.endswith("_out_norm"):
                 p.copy_(torch.empty(p.shape).uniform_(0.5, 1.5, generator=g))
     gpu = build_model(cfg, dtype=torch.bfloat16, device="cuda", seed=7)
     with torch.no_grad():
         for a, b in zip(gpu.parameters(), cpu.parameters()):
             a.copy_(b.to(torch.bfloat16))
             b.copy_(a.float().cpu())          # both sides hold the bf16-rounded weights
-    x = torch.randint(0, cfg.vocab_size, (2, 640 if variant.startswith("plain") else 128))
+    x = torch.randint(0, cfg.vocab_size, (2, 640 if "long batch" in variant else 128))
     lc = cpu(x)
     lg = gpu(x.cuda())
     assert torch.allclose(lg.float().cpu(), lc, atol=6e-2, rtol=5e-2), (lg.float().cpu() - lc).abs().max()
