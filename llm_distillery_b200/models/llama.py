@@ -156,6 +156,22 @@ class LlamaConfig:
             d["intermediate_size"] = extra.pop("dense_intermediate_size", self.intermediate_size)
         elif self.model_type == "olmo2":
             d.update(architectures=["Olmo2ForCausalLM"], hidden_act="silu", torch_dtype="bfloat16", attention_bias=False)
+        elif self.model_type == "exaone4":
+            d.pop("attention_bias")
+            d.update(architectures=["Exaone4ForCausalLM"], hidden_act="silu", torch_dtype="bfloat16",
+                     sliding_window=self.sliding_window,
+                     layer_types=["sliding_attention" if (nope and nope[i]) else "full_attention"
+                                  for i in range(self.num_hidden_layers)])
+        elif self.model_type == "helium":
+            d.update(architectures=["HeliumForCausalLM"], hidden_act="silu", torch_dtype="bfloat16", mlp_bias=False,
+                     head_dim=self.head_dim)
+        elif self.model_type == "ernie4_5":
+            d.pop("attention_bias")
+            d.update(architectures=["Ernie4_5ForCausalLM"], hidden_act="silu", torch_dtype="bfloat16", use_bias=False,
+                     head_dim=self.head_dim)
+        elif self.model_type == "seed_oss":
+            d.update(architectures=["SeedOssForCausalLM"], hidden_act="silu", torch_dtype="bfloat16", mlp_bias=False,
+                     attention_out_bias=False, head_dim=self.head_dim)
         elif self.model_type in ("glm", "glm4"):
             d.update(architectures=["GlmForCausalLM" if self.model_type == "glm" else "Glm4ForCausalLM"],
                      hidden_act="silu", torch_dtype="bfloat16", head_dim=self.head_dim,
@@ -194,7 +210,7 @@ class LlamaConfig:
         return {**extra, **d}
 
     _KNOWN_TYPES = ("llama", "mistral", "qwen2", "phi3", "mixtral", "qwen3", "qwen3_moe", "qwen2_moe", "granite",
-                    "smollm3", "olmo2", "glm", "glm4")
+                    "smollm3", "olmo2", "glm", "glm4", "exaone4", "helium", "ernie4_5", "seed_oss")
 
     @classmethod
     def from_hf_dict(cls, d: dict) -> "LlamaConfig":
@@ -227,7 +243,7 @@ class LlamaConfig:
                 raise NotImplementedError("smollm3 with projection biases is not built")
             if not d.get("use_sliding_window", False):
                 kw["sliding_window"] = None
-        else:
+        elif mt != "exaone4":
             kw.pop("no_rope_layers", None)
         if mt == "qwen3" and d.get("num_experts"):
             raise NotImplementedError("experts in a config of model_type qwen3: the mixture-of-experts type is qwen3_moe")
@@ -279,6 +295,32 @@ class LlamaConfig:
             if kw.get("attention_bias"):
                 raise NotImplementedError("olmo2 with attention_bias also puts a bias on o_proj, which is not built")
             kw.update(pre_norm=False, post_norm=True, qk_norm_full=True)
+        if mt == "exaone4":          # OLMo 2's placement of the norms with per-head q/k norms
+            kw.update(pre_norm=False, post_norm=True, qk_norm=True)
+            n_layers = int(kw.get("num_hidden_layers", 32))
+            window = d.get("sliding_window")
+            types = d.get("layer_types")
+            if types is None and window is not None:
+                pat = d.get("sliding_window_pattern", 4)
+                if isinstance(pat, str):         # e.g. "LLLG": local (windowed) and global layers in turn
+                    types = ["sliding_attention" if pat[i % len(pat)].upper() == "L" else "full_attention"
+                             for i in range(n_layers)]
+                else:
+                    types = ["sliding_attention" if (i + 1) % int(pat) else "full_attention" for i in range(n_layers)]
+            if window is not None and types and "sliding_attention" in types:
+                # hybrid checkpoints: windowed layers rotate, global layers apply no rotation; sequences up to the window
+                # are exact under full causal attention, longer ones are refused
+                kw["no_rope_layers"] = [int(t == "sliding_attention") for t in types]
+            else:
+                kw["sliding_window"] = None
+        if mt in ("helium", "ernie4_5"):     # rotary pairs are neighbours in the checkpoint
+            kw["rope_interleaved"] = True
+            if d.get("use_bias"):
+                raise NotImplementedError("ernie4_5 with use_bias puts a bias on every projection, which is not built")
+        if mt == "seed_oss":
+            if d.get("attention_out_bias"):
+                raise NotImplementedError("seed_oss with a bias on o_proj is not built")
+            kw["attention_bias"] = bool(d.get("attention_bias", True))
         if mt in ("glm", "glm4"):    # rotary pairs are neighbours in the checkpoint; half of each head rotates
             kw.update(rope_interleaved=True, post_norm=(mt == "glm4"),
                       attention_bias=bool(d.get("attention_bias", True)))
@@ -286,6 +328,8 @@ class LlamaConfig:
                 kw["partial_rotary_factor"] = 0.5
         elif mt in ("qwen2", "qwen2_moe"):
             kw["attention_bias"] = True
+        elif mt in ("seed_oss", "helium"):
+            pass                         # their attention_bias covers q, k and v only
         elif kw.get("attention_bias"):
             if mt not in ("llama", "mistral", "granite"):
                 raise NotImplementedError(f"attention_bias on model_type {mt!r} is not built")
@@ -911,8 +955,8 @@ class LlamaModel(nn.Module):
         q, kv, f = cfg.q_size, cfg.kv_size, cfg.intermediate_size
         for i, l in enumerate(self.layers):
             pre = f"model.layers.{i}."
-            if cfg.model_type in ("olmo2", "glm", "glm4"):
-                glm = cfg.model_type != "olmo2"
+            if cfg.model_type in ("olmo2", "exaone4", "glm", "glm4"):
+                glm = cfg.model_type in ("glm", "glm4")
                 if glm:
                     yield pre + "input_layernorm.weight", l.input_layernorm, None
                 yield pre + "self_attn.q_proj.weight", l.qkv_proj, slice(0, q)
@@ -922,7 +966,7 @@ class LlamaModel(nn.Module):
                     yield pre + "self_attn.q_proj.bias", l.qkv_bias, slice(0, q)
                     yield pre + "self_attn.k_proj.bias", l.qkv_bias, slice(q, q + kv)
                     yield pre + "self_attn.v_proj.bias", l.qkv_bias, slice(q + kv, q + 2 * kv)
-                if cfg.qk_norm_full:
+                if cfg.qk_norm_full or cfg.qk_norm:
                     yield pre + "self_attn.q_norm.weight", l.q_norm, None
                     yield pre + "self_attn.k_norm.weight", l.k_norm, None
                 yield pre + "self_attn.o_proj.weight", l.o_proj, None

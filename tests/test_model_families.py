@@ -313,15 +313,33 @@ def test_smollm3_layers_without_rotation_match_huggingface(tmp_path):
     assert LlamaConfig.from_hf_dict(dict(_base(), model_type="llama", no_rope_layers=[0, 0])).no_rope_layers is None
 
 
+_MORE = {   # family: (HuggingFace model, config, extra config keys, (pre_norm, post_norm, qk_norm_full, qk_norm), general node)
+    "olmo2": ("Olmo2ForCausalLM", "Olmo2Config", {}, (False, True, True, False), True),
+    "glm": ("GlmForCausalLM", "GlmConfig", dict(head_dim=16), (True, False, False, False), False),
+    "glm4": ("Glm4ForCausalLM", "Glm4Config", dict(head_dim=16), (True, True, False, False), True),
+    "exaone4": ("Exaone4ForCausalLM", "Exaone4Config", dict(sliding_window=None, layer_types=["full_attention"] * 2),
+                (False, True, False, True), True),
+    "exaone4 hybrid": ("Exaone4ForCausalLM", "Exaone4Config", dict(sliding_window=64, sliding_window_pattern=2),
+                       (False, True, False, True), True),
+    "helium": ("HeliumForCausalLM", "HeliumConfig", dict(head_dim=16), (True, False, False, False), False),
+    "ernie4_5": ("Ernie4_5ForCausalLM", "Ernie4_5Config", dict(head_dim=32), (True, False, False, False), False),
+    "seed_oss": ("SeedOssForCausalLM", "SeedOssConfig", dict(head_dim=32, attention_dropout=0.0, residual_dropout=0.0),
+                 (True, False, False, False), False),
+}
+
+
 @pytest.mark.parametrize("family,recompute", [("olmo2", False), ("olmo2", True), ("glm", False), ("glm4", False),
-                                              ("glm4", True)])
-def test_layers_with_output_norms_match_huggingface(tmp_path, family, recompute):
-    """OLMo 2 (norms behind the branches only, q/k norms over the whole projections), GLM (half of each head rotates,
-    rotary pairs neighbours in the checkpoint, fused gate/up tensor, q/k/v bias) and GLM-4 0414 (GLM with norms behind
-    the branches as well): logits, every gradient, the chunked inference path and checkpoints both ways."""
-    cls, ccls, extra = {"olmo2": (tr.Olmo2ForCausalLM, tr.Olmo2Config, {}),
-                        "glm": (tr.GlmForCausalLM, tr.GlmConfig, dict(head_dim=16)),
-                        "glm4": (tr.Glm4ForCausalLM, tr.Glm4Config, dict(head_dim=16))}[family]
+                                              ("glm4", True), ("exaone4", False), ("exaone4 hybrid", True),
+                                              ("helium", False), ("ernie4_5", False), ("seed_oss", False)])
+def test_more_decoder_families_match_huggingface(tmp_path, family, recompute):
+    """OLMo 2 (norms behind the branches only, q/k norms over the whole projections), EXAONE 4 (the same placement with
+    per-head q/k norms; hybrid checkpoints: windowed layers rotate, global ones do not), GLM (half of each head rotates,
+    rotary pairs neighbours in the checkpoint, fused gate/up tensor, q/k/v bias), GLM-4 0414 (GLM with norms behind
+    the branches as well), Helium and ERNIE 4.5 (Llama layers, rotary pairs neighbours), Seed-OSS (q/k/v bias and an
+    explicit head_dim): logits, every gradient, the chunked inference path and checkpoints both ways."""
+    cls_n, ccls_n, extra, flags, general = _MORE[family]
+    cls, ccls = getattr(tr, cls_n), getattr(tr, ccls_n)
+    mt = family.split()[0]
     torch.manual_seed(4)
     hf = cls(ccls(**{k: v for k, v in _base().items() if k != "rope_theta"}, **extra, pad_token_id=0,
                   attn_implementation="eager", tie_word_embeddings=False)).float()
@@ -334,11 +352,18 @@ def test_layers_with_output_norms_match_huggingface(tmp_path, family, recompute)
     hf.save_pretrained(str(tmp_path / "hf"), safe_serialization=True)
     model = load_hf_model(str(tmp_path / "hf"), dtype=torch.float32)
     cfg = model.cfg
-    assert cfg.model_type == family and cfg.sandwich == (family != "glm")
-    assert (cfg.pre_norm, cfg.post_norm, cfg.qk_norm_full) == {"olmo2": (False, True, True), "glm": (True, False, False),
-                                                                "glm4": (True, True, False)}[family]
-    if family != "olmo2":
+    assert cfg.model_type == mt and cfg.sandwich == general
+    assert (cfg.pre_norm, cfg.post_norm, cfg.qk_norm_full, cfg.qk_norm) == flags
+    if mt in ("glm", "glm4"):
         assert cfg.rope_interleaved and cfg.partial_rotary_factor == 0.5 and cfg.attention_bias and not cfg.o_bias
+    if mt in ("helium", "ernie4_5"):
+        assert cfg.rope_interleaved and cfg.partial_rotary_factor == 1.0 and not cfg.attention_bias
+    if mt == "seed_oss":
+        assert cfg.attention_bias and not cfg.o_bias and cfg.head_dim == 32 and not cfg.rope_interleaved
+    if family == "exaone4 hybrid":
+        assert cfg.no_rope_layers == [1, 0] and cfg.sliding_window == 64
+    elif mt == "exaone4":
+        assert cfg.no_rope_layers is None and cfg.sliding_window is None
     assert sum(p.numel() for p in model.parameters()) == cfg.num_params() == sum(p.numel() for p in hf.parameters())
     model.grad_checkpointing = recompute
     x = torch.randint(1, 320, (2, 48))          # not the padding id: HuggingFace's embedding gives it no gradient
@@ -365,6 +390,9 @@ def test_layers_with_output_norms_match_huggingface(tmp_path, family, recompute)
     if family == "olmo2":
         with pytest.raises(NotImplementedError, match="o_proj"):
             LlamaConfig.from_hf_dict(dict(cfg.to_hf_dict(), attention_bias=True))
+    if family == "exaone4 hybrid":           # beyond the window the windowed layers would differ: refused
+        with pytest.raises(ValueError, match="attention window"):
+            model(torch.randint(1, 320, (1, 65)))
 
 
 def test_llama_with_attention_and_mlp_biases_matches_huggingface(tmp_path):
