@@ -87,7 +87,7 @@ def load_hf_state_dict(path: str) -> dict[str, torch.Tensor]:
     for f in files:
         sd.update(load_file(os.path.join(path, f)))
     if any(k.endswith((".qweight", ".q_weight")) for k in sd):
-        # a quantised export (GPTQ): expanded to bf16 here, once (ckpt/gptq.py says why and which layouts are read)
+        # a quantised export (GPTQ, AWQ): expanded to bf16 here, once (ckpt/gptq.py says why and which layouts are read)
         from . import gptq
         sd = gptq.dequantize_state_dict(sd, gptq.quantization_config(path) or {})
     return sd
@@ -259,7 +259,7 @@ def load_tp_weights(path: str, rank: int, tp: int, vocab: int | None = None, dty
     replicated embedding and norms. Returns (config, weights) in the layout of ``parallel.tp.shard_llama_weights``."""
     from safetensors import safe_open
     from . import gptq
-    if (gptq.quantization_config(path) or {}).get("quant_method") in ("gptq", "exl2"):
+    if (gptq.quantization_config(path) or {}).get("quant_method") in ("gptq", "awq", "exl2"):
         raise ValueError(f"{path} is a quantised checkpoint: the tensor-parallel loader reads slices of plain 16-bit "
                          "tensors. Collect with tp_size = 1 (the dequantised model fits one GPU) or export the "
                          "checkpoint to bf16 first.")
