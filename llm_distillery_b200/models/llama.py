@@ -55,11 +55,12 @@ class LlamaConfig:
     attention_multiplier: float | None = None      # replaces 1 / sqrt(head_dim)
     residual_multiplier: float = 1.0
     logits_scaling: float = 1.0                    # logits are DIVIDED by this
-    rope_scaling: dict | None = None  # HuggingFace dict; types default / linear / llama3 / yarn (ops.basic.rope_tables)
+    rope_scaling: dict | None = None  # HuggingFace dict; types default / linear / dynamic / llama3 / yarn / longrope (ops.basic.rope_tables)
     head_dim_override: int | None = None   # HuggingFace ``head_dim`` when it is not hidden_size / num_attention_heads
     no_rope_layers: list | None = None     # SmolLM3: one flag per layer, 1 = rotary embedding, 0 = no positional rotation
     partial_rotary_factor: float = 1.0     # < 1: only the first int(head_dim * factor) elements of a head rotate (Phi-4-mini)
     qk_norm: bool = False             # Qwen3: RMSNorm over every query and key head (one weight each) before RoPE
+    qk_norm_after_rope: bool = False  # HunYuan: the per-head q/k norms act on the rotated queries and keys
     qk_norm_full: bool = False        # OLMo 2: one RMSNorm over the whole query projection, one over the key projection
     pre_norm: bool = True             # RMSNorm on the way into the attention and MLP branches (false: OLMo 2)
     post_norm: bool = False           # RMSNorm on the way out of both branches (OLMo 2, GLM-4 0414; models/sandwich.py)
@@ -75,7 +76,7 @@ class LlamaConfig:
     @property
     def sandwich(self) -> bool:
         """Whether the layers take the general node of models/sandwich.py instead of the fused pre-norm layer."""
-        return self.post_norm or not self.pre_norm or self.qk_norm_full
+        return self.post_norm or not self.pre_norm or self.qk_norm_full or self.qk_norm_after_rope
 
     @property
     def rotary_dim(self) -> int:
@@ -137,7 +138,7 @@ class LlamaConfig:
             d.pop("num_local_experts")
             d.pop("num_experts_per_tok")
         qk = d.pop("qk_norm")
-        for k in ("qk_norm_full", "pre_norm", "post_norm", "rope_interleaved"):      # implied by the model type
+        for k in ("qk_norm_full", "qk_norm_after_rope", "pre_norm", "post_norm", "rope_interleaved"):      # implied by the model type
             d.pop(k)
         shared_f = d.pop("shared_expert_intermediate_size")
         gran = {k: d.pop(k) for k in ("embedding_multiplier", "attention_multiplier", "residual_multiplier", "logits_scaling")}
@@ -162,6 +163,9 @@ class LlamaConfig:
                      sliding_window=self.sliding_window,
                      layer_types=["sliding_attention" if (nope and nope[i]) else "full_attention"
                                   for i in range(self.num_hidden_layers)])
+        elif self.model_type == "hunyuan_v1_dense":
+            d.update(architectures=["HunYuanDenseV1ForCausalLM"], hidden_act="silu", torch_dtype="bfloat16",
+                     attention_bias=False, head_dim=self.head_dim)
         elif self.model_type == "helium":
             d.update(architectures=["HeliumForCausalLM"], hidden_act="silu", torch_dtype="bfloat16", mlp_bias=False,
                      head_dim=self.head_dim)
@@ -210,7 +214,7 @@ class LlamaConfig:
         return {**extra, **d}
 
     _KNOWN_TYPES = ("llama", "mistral", "qwen2", "phi3", "mixtral", "qwen3", "qwen3_moe", "qwen2_moe", "granite",
-                    "smollm3", "olmo2", "glm", "glm4", "exaone4", "helium", "ernie4_5", "seed_oss")
+                    "smollm3", "olmo2", "glm", "glm4", "exaone4", "helium", "ernie4_5", "seed_oss", "hunyuan_v1_dense")
 
     @classmethod
     def from_hf_dict(cls, d: dict) -> "LlamaConfig":
@@ -289,8 +293,12 @@ class LlamaConfig:
                 raise NotImplementedError("qwen3 with attention_bias also puts a bias on o_proj, which is not built")
             if not d.get("use_sliding_window", False):
                 kw["sliding_window"] = None
-        for k in ("qk_norm_full", "pre_norm", "post_norm", "rope_interleaved"):      # set by the model type alone
+        for k in ("qk_norm_full", "qk_norm_after_rope", "pre_norm", "post_norm", "rope_interleaved"):      # set by the model type alone
             kw.pop(k, None)
+        if mt == "hunyuan_v1_dense":         # Llama layers with per-head q/k norms behind the rotation
+            kw.update(qk_norm=True, qk_norm_after_rope=True)
+            if kw.get("attention_bias"):
+                raise NotImplementedError("hunyuan_v1_dense with attention_bias also puts a bias on o_proj, which is not built")
         if mt == "olmo2":            # no norms in front of the branches, norms behind them, q/k norms over all heads
             if kw.get("attention_bias"):
                 raise NotImplementedError("olmo2 with attention_bias also puts a bias on o_proj, which is not built")
@@ -362,9 +370,9 @@ class LlamaConfig:
                 kind = "longrope"
                 cfg.rope_scaling = {**{k: v for k, v in cfg.rope_scaling.items() if k not in ("type", "rope_type")},
                                     "rope_type": "longrope"}
-            if kind not in (None, "default", "linear", "llama3", "yarn", "longrope"):
-                raise NotImplementedError(f"rope_scaling type {kind!r} is not built (default, linear, llama3, yarn and "
-                                          "longrope are)")
+            if kind not in (None, "default", "linear", "dynamic", "llama3", "yarn", "longrope"):
+                raise NotImplementedError(f"rope_scaling type {kind!r} is not built (default, linear, dynamic, llama3, "
+                                          "yarn and longrope are)")
             if kind == "longrope" and not cfg.rope_scaling.get("original_max_position_embeddings"):
                 orig = d.get("original_max_position_embeddings")
                 if orig:          # Phi-3 keeps it beside the dict
@@ -775,10 +783,12 @@ class LlamaModel(nn.Module):
         regime = None
         if sc.get("rope_type", sc.get("type")) == "longrope":    # the factor set depends on the sequence length
             regime = need > int(sc.get("original_max_position_embeddings") or self.cfg.max_position_embeddings)
+        elif sc.get("rope_type", sc.get("type")) == "dynamic" and not sc.get("alpha"):
+            regime = need if need > self.cfg.max_position_embeddings else False      # the base follows the length
         if (self._rope is None or self._rope[0].device != torch.device(device) or self._rope[0].shape[0] < need
                 or getattr(self, "_rope_regime", None) != regime):
             n = max(need, min(self.cfg.max_position_embeddings, 8192))
-            if regime is False:
+            if regime is False and sc.get("rope_type", sc.get("type")) == "longrope":
                 n = min(n, int(sc.get("original_max_position_embeddings") or n))
             self._rope = basic.rope_tables(n, self.cfg.rotary_dim, self.cfg.rope_theta, device, self.cfg.rope_scaling,
                                            model_max_pos=self.cfg.max_position_embeddings, seq_len=need)
@@ -834,7 +844,8 @@ class LlamaModel(nn.Module):
                 from .sandwich import SandwichLayerFn
                 g = lambda n: getattr(layer, n, None)
                 h = SandwichLayerFn.apply(h, pos, cos, sin,
-                                          meta + (2 if cfg.qk_norm_full else int(cfg.qk_norm), layer.first_param),
+                                          meta + (2 if cfg.qk_norm_full else 3 if cfg.qk_norm_after_rope
+                                                  else int(cfg.qk_norm), layer.first_param),
                                           layer.qkv_proj, layer.o_proj, layer.gate_up_proj, layer.down_proj,
                                           g("input_layernorm"), g("post_attention_layernorm"), g("attn_out_norm"),
                                           g("mlp_out_norm"), g("qkv_bias"), g("q_norm"), g("k_norm"))
@@ -896,8 +907,10 @@ class LlamaModel(nn.Module):
                 if cfg.sandwich:
                     from .sandwich import layer_inference
 
-                    def attend(qkv, kc=kc, vc=vc, cos=cos, sin=sin):
+                    def attend(qkv, after_rotation=None, kc=kc, vc=vc, cos=cos, sin=sin):
                         basic.rope_(qkv, pos, cos, sin, H + Hkv, d)
+                        if after_rotation is not None:
+                            qkv = after_rotation(qkv)
                         kc[:, c0:c0 + n] = qkv[:, H * d:(H + Hkv) * d].reshape(B, n, kv)
                         vc[:, c0:c0 + n] = qkv[:, (H + Hkv) * d:].reshape(B, n, kv)
                         return attention.attention_fwd_cached(qkv, kc, vc, B, n, c0, H, Hkv, d)
@@ -1000,7 +1013,10 @@ class LlamaModel(nn.Module):
                 yield pre + "self_attn.q_proj.bias", l.qkv_bias, slice(0, q)
                 yield pre + "self_attn.k_proj.bias", l.qkv_bias, slice(q, q + kv)
                 yield pre + "self_attn.v_proj.bias", l.qkv_bias, slice(q + kv, q + 2 * kv)
-            if cfg.qk_norm:
+            if cfg.qk_norm and cfg.model_type == "hunyuan_v1_dense":
+                yield pre + "self_attn.query_layernorm.weight", l.q_norm, None
+                yield pre + "self_attn.key_layernorm.weight", l.k_norm, None
+            elif cfg.qk_norm:
                 yield pre + "self_attn.q_norm.weight", l.q_norm, None
                 yield pre + "self_attn.k_norm.weight", l.k_norm, None
             yield pre + "self_attn.o_proj.weight", l.o_proj, None

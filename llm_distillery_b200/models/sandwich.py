@@ -4,8 +4,9 @@
     h2 = h1 + [OutNorm_m]( MLP(  [InNorm_2](h1) ) )
 
 OLMo 2 has only the output norms and normalises the whole query / key projections (one RMSNorm over all heads) before
-the rotation; GLM-4 (0414) has all four norms. The reference trains such students through ``AutoModelForCausalLM``
-(classes/student/model.py:194-201). One autograd node with an explicit backward, built from the same kernels as
+the rotation; GLM-4 (0414) has all four norms; HunYuan is a plain pre-norm layer whose per-head q/k norms come AFTER
+the rotation (the norm's weight does not commute with it), which the fused layer of ``llama.py`` does not do. The
+reference trains such students through ``AutoModelForCausalLM`` (classes/student/model.py:194-201). One autograd node with an explicit backward, built from the same kernels as
 ``llama.DecoderLayerFn`` (tcgen05 GEMMs with the SwiGLU epilogues, RMSNorm, RoPE, flash attention); the residual adds
 that the plain layer folds into GEMM epilogues are separate here because a norm sits between the GEMM and the add.
 """
@@ -44,6 +45,10 @@ def _forward(h, pos, cos, sin, meta, w_qkv, w_o, w_gu, w_d, w_ln1, w_ln2, w_pa, 
         qkv, rstd_qk = basic.headnorm_fwd(qkv_raw, w_qn, w_kn, H, Hkv, d, eps)
         qk_saved = (qkv_raw, rstd_qk)
     basic.rope_(qkv, pos, cos, sin, H + Hkv, d)
+    if qk_mode == 3:                       # per-head norms of the ROTATED queries and keys
+        qkv_rot = qkv
+        qkv, rstd_qk = basic.headnorm_fwd(qkv_rot, w_qn, w_kn, H, Hkv, d, eps)
+        qk_saved = (qkv_rot, rstd_qk)
     att, lse = attention.attention_fwd(qkv, B, L, H, Hkv, d)
     if w_pa is None:
         a = None
@@ -68,7 +73,8 @@ def _forward(h, pos, cos, sin, meta, w_qkv, w_o, w_gu, w_d, w_ln1, w_ln2, w_pa, 
 
 class SandwichLayerFn(torch.autograd.Function):
     """meta = (B, L, heads, kv heads, head dim, eps, recompute in backward, q/k norm: 0 none / 1 per head / 2 over the
-    whole projection, the layer's first parameter). Norm weights that the family does not have are None."""
+    whole projection / 3 per head after the rotation, the layer's first parameter). Norm weights that the family does
+    not have are None."""
 
     @staticmethod
     def forward(ctx, h, pos, cos, sin, meta, w_qkv, w_o, w_gu, w_d, w_ln1=None, w_ln2=None, w_pa=None, w_pm=None,
@@ -133,9 +139,17 @@ class SandwichLayerFn(torch.autograd.Function):
             g_pa = _ll._vec_grad(dw, w_pa, s_pa)
         g_o = _ll._wgrad(da, att, w_o, s_o)
         datt = basic.linear_dgrad(da, w_o)
-        dqkv = attention.attention_bwd_unrotated(datt, qkv, att, lse, B, L, H, Hkv, d, pos, cos, sin)
-        del datt
         g_qn = g_kn = None
+        if qk_mode == 3:
+            qkv_rot, rstd_qk = qk_saved
+            dqkv = attention.attention_bwd(datt, qkv, att, lse, B, L, H, Hkv, d)
+            dwq, dwk = basic.headnorm_bwd_(dqkv, qkv_rot, w_qn, w_kn, rstd_qk, H, Hkv, d)
+            basic.rope_(dqkv, pos, cos, sin, H + Hkv, d, inverse=True)
+            g_qn = _ll._vec_grad(dwq, w_qn, s_qn)
+            g_kn = _ll._vec_grad(dwk, w_kn, s_kn)
+        else:
+            dqkv = attention.attention_bwd_unrotated(datt, qkv, att, lse, B, L, H, Hkv, d, pos, cos, sin)
+        del datt
         if qk_mode == 2:
             q_raw, k_raw, rq, rk = qk_saved
             dq, dwq = basic.rmsnorm_bwd(dqkv[:, :q].contiguous(), q_raw, w_qn, rq)
@@ -165,9 +179,10 @@ class SandwichLayerFn(torch.autograd.Function):
 
 @torch.no_grad()
 def layer_inference(layer, cfg, h, qkv_hook, eps):
-    """Forward of one such layer for the chunked-prefill path. ``qkv_hook(qkv) -> att`` receives the projected (bias
-    added, normalised) rows before the rotation and returns the attention output (it rotates, fills the key / value
-    cache and runs attention against it)."""
+    """Forward of one such layer for the chunked-prefill path. ``qkv_hook(qkv, after_rotation) -> att`` receives the
+    projected (bias added, normalised) rows before the rotation and returns the attention output: it rotates, applies
+    ``after_rotation`` (None, or a function of the rotated rows), fills the key / value cache and runs attention
+    against it."""
     H, Hkv, d = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
     x1 = h
     if cfg.pre_norm:
@@ -177,9 +192,12 @@ def layer_inference(layer, cfg, h, qkv_hook, eps):
         basic.bias_add_(qkv, layer.qkv_bias)
     if cfg.qk_norm_full:
         qkv, _ = _qk_full_fwd(qkv, layer.q_norm, layer.k_norm, H * d, Hkv * d, eps)
-    elif cfg.qk_norm:
+    elif cfg.qk_norm and not cfg.qk_norm_after_rope:
         qkv, _ = basic.headnorm_fwd(qkv, layer.q_norm, layer.k_norm, H, Hkv, d, eps)
-    att = qkv_hook(qkv)
+    after = None
+    if cfg.qk_norm_after_rope:
+        after = lambda rows: basic.headnorm_fwd(rows, layer.q_norm, layer.k_norm, H, Hkv, d, eps)[0]
+    att = qkv_hook(qkv, after)
     if cfg.post_norm:
         a, _, _ = basic.rmsnorm_fwd(basic.linear_fwd(att, layer.o_proj), layer.attn_out_norm, eps)
         h1 = h + a

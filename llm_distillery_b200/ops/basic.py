@@ -239,6 +239,9 @@ def rope_tables(max_pos: int, head_dim: int, theta: float, device, scaling: dict
     ``longrope`` (Phi-3 long-context checkpoints) divides every frequency by its entry of ``short_factor``, or of
     ``long_factor`` when the sequence (``seq_len``) is longer than the original context, and scales cos / sin by
     sqrt(1 + ln(factor) / ln(original context)).
+    ``dynamic`` (NTK-aware): beyond the model's context the base grows with the sequence length,
+    theta * (factor * seq_len / context - (factor - 1)) ^ (d / (d - 2)), inside it nothing changes; with an ``alpha`` key
+    (HunYuan) the base is theta * alpha ^ (d / (d - 2)) at every length.
     ``model_max_pos`` is the model's ``max_position_embeddings`` (yarn's original context when the dict names none)."""
     import math
     inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32, device=device) / head_dim))
@@ -289,6 +292,17 @@ def rope_tables(max_pos: int, head_dim: int, theta: float, device, scaling: dict
         inv = inv / ext
     elif kind == "linear":
         inv = inv / float(scaling["factor"])
+    elif kind == "dynamic":
+        if scaling.get("alpha"):
+            base = theta * float(scaling["alpha"]) ** (head_dim / (head_dim - 2))
+        else:
+            orig = model_max_pos or scaling.get("original_max_position_embeddings")
+            if not orig:
+                raise ValueError("dynamic rope scaling needs the model's max_position_embeddings")
+            factor = float(scaling["factor"])
+            length = max(int(seq_len if seq_len is not None else max_pos), int(orig))
+            base = theta * (factor * length / float(orig) - (factor - 1.0)) ** (head_dim / (head_dim - 2))
+        inv = 1.0 / (base ** (torch.arange(0, head_dim, 2, dtype=torch.float32, device=device) / head_dim))
     elif kind == "llama3":
         factor = float(scaling["factor"])
         lo_f, hi_f = float(scaling.get("low_freq_factor", 1.0)), float(scaling.get("high_freq_factor", 4.0))
@@ -298,7 +312,8 @@ def rope_tables(max_pos: int, head_dim: int, theta: float, device, scaling: dict
         blended = (1.0 - smooth) * inv / factor + smooth * inv
         inv = torch.where(wavelen > old / lo_f, inv / factor, torch.where(wavelen < old / hi_f, inv, blended))
     else:
-        raise NotImplementedError(f"rope_scaling type {kind!r} is not built (default, linear, llama3, yarn and longrope are)")
+        raise NotImplementedError(f"rope_scaling type {kind!r} is not built (default, linear, dynamic, llama3, yarn and "
+                                  "longrope are)")
     ang = torch.arange(max_pos, dtype=torch.float32, device=device)[:, None] * inv[None, :]
     return (ang.cos() * amp).contiguous(), (ang.sin() * amp).contiguous()
 

@@ -316,6 +316,8 @@ class TPLlama:
         regime = None
         if sc.get("rope_type", sc.get("type")) == "longrope":    # the factor set depends on the sequence length
             regime = n > int(sc.get("original_max_position_embeddings") or self.cfg.max_position_embeddings)
+        elif sc.get("rope_type", sc.get("type")) == "dynamic" and not sc.get("alpha"):
+            regime = n if n > self.cfg.max_position_embeddings else False            # the base follows the length
         if regime != getattr(self, "_rope_regime", None):
             self._rope, self._rope_regime = None, regime
         if self._rope is None or self._rope[0].shape[0] < n:

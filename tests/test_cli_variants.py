@@ -130,6 +130,8 @@ FAMILIES = {
     "helium": dict(model_type="helium", rope_interleaved=True),
     "ernie4_5": dict(model_type="ernie4_5", rope_interleaved=True),
     "seed_oss": dict(model_type="seed_oss", attention_bias=True, head_dim_override=32),
+    "hunyuan_v1_dense": dict(model_type="hunyuan_v1_dense", qk_norm=True, qk_norm_after_rope=True,
+                             rope_scaling={"rope_type": "dynamic", "alpha": 1000.0, "factor": 1.0}),
 }
 
 

@@ -38,7 +38,7 @@ def test_llama3_rope_scaling_matches_huggingface():
     c0, s0 = basic.rope_tables(128, 16, 10000.0, "cpu")
     assert torch.allclose(c1[4::4], c0[1:8], atol=1e-6) and torch.allclose(s1[4::4], s0[1:8], atol=1e-6)
     with pytest.raises(NotImplementedError):
-        basic.rope_tables(8, 16, 10000.0, "cpu", {"rope_type": "dynamic", "factor": 2.0})
+        basic.rope_tables(8, 16, 10000.0, "cpu", {"rope_type": "ntk-by-parts", "factor": 2.0})
 
 
 def test_phi3_checkpoint_layout_matches_huggingface(tmp_path):
@@ -94,7 +94,7 @@ def test_config_keys_survive_a_round_trip_and_unbuilt_variants_are_refused(tmp_p
     with pytest.raises(ValueError, match="attention window"):
         model(torch.randint(0, 320, (1, 129)))
     for bad in (dict(model_type="gemma2"), dict(hidden_act="gelu_pytorch_tanh"), dict(head_dim=20),
-                dict(rope_scaling={"rope_type": "dynamic", "factor": 4.0})):
+                dict(rope_scaling={"rope_type": "ntk-by-parts", "factor": 4.0})):
         with pytest.raises(NotImplementedError):
             LlamaConfig.from_hf_dict(dict(_base(), **bad))
     # Qwen2 carries a window that is switched off
@@ -270,6 +270,26 @@ def test_partial_rotary_matches_huggingface(tmp_path):
     assert torch.allclose(basic.rope_(r, pos, cos, sin, 3, 32, inverse=True), v, atol=1e-5)
 
 
+def test_dynamic_ntk_rope_scaling_matches_huggingface():
+    """Inside the model's context nothing changes; beyond it the base follows the sequence length."""
+    sc = {"rope_type": "dynamic", "factor": 3.0}
+    cfg = LlamaConfig.from_hf_dict(dict(_base(max_position_embeddings=64), model_type="llama", rope_scaling=dict(sc)))
+    model = build_model(cfg, dtype=torch.float32, device="cpu", seed=6)
+    plain = build_model(LlamaConfig(**_base(max_position_embeddings=64)), dtype=torch.float32, device="cpu", seed=6)
+    for L in (48, 200, 120, 40):          # a fresh HuggingFace model per length: its tables remember earlier lengths
+        hf = tr.LlamaForCausalLM(tr.LlamaConfig(**_base(max_position_embeddings=64), rope_scaling=dict(sc),
+                                                attn_implementation="eager", tie_word_embeddings=False)).float()
+        hf.load_state_dict({k: v.clone() for k, v in model.to_hf_state_dict().items()}, strict=False)
+        x = torch.randint(0, 320, (2, L))
+        ours, ref = model(x), hf(x).logits
+        assert torch.allclose(ours, ref, atol=4e-4, rtol=1e-3), (L, (ours - ref).abs().max())
+        assert ((plain(x) - ref).abs().max() > 3e-3) == (L > 64), L
+    # HunYuan's form: a fixed alpha instead of the length
+    c, s_ = basic.rope_tables(16, 16, 10000.0, "cpu", {"rope_type": "dynamic", "alpha": 1000.0, "factor": 1.0})
+    c2, s2 = basic.rope_tables(16, 16, 10000.0 * 1000.0 ** (16 / 14), "cpu")
+    assert torch.allclose(c, c2) and torch.allclose(s_, s2)
+
+
 def test_smollm3_layers_without_rotation_match_huggingface(tmp_path):
     """SmolLM3: Llama blocks of which every n-th applies no rotary embedding (the flags come from the interval when
     the config does not list them)."""
@@ -323,6 +343,10 @@ _MORE = {   # family: (HuggingFace model, config, extra config keys, (pre_norm, 
                        (False, True, False, True), True),
     "helium": ("HeliumForCausalLM", "HeliumConfig", dict(head_dim=16), (True, False, False, False), False),
     "ernie4_5": ("Ernie4_5ForCausalLM", "Ernie4_5Config", dict(head_dim=32), (True, False, False, False), False),
+    "hunyuan_v1_dense": ("HunYuanDenseV1ForCausalLM", "HunYuanDenseV1Config",
+                         dict(head_dim=16, rope_parameters={"rope_type": "dynamic", "alpha": 50.0, "factor": 1.0,
+                                                            "rope_theta": 10000.0}),
+                         (True, False, False, True), True),
     "seed_oss": ("SeedOssForCausalLM", "SeedOssConfig", dict(head_dim=32, attention_dropout=0.0, residual_dropout=0.0),
                  (True, False, False, False), False),
 }
@@ -330,13 +354,14 @@ _MORE = {   # family: (HuggingFace model, config, extra config keys, (pre_norm, 
 
 @pytest.mark.parametrize("family,recompute", [("olmo2", False), ("olmo2", True), ("glm", False), ("glm4", False),
                                               ("glm4", True), ("exaone4", False), ("exaone4 hybrid", True),
-                                              ("helium", False), ("ernie4_5", False), ("seed_oss", False)])
+                                              ("helium", False), ("ernie4_5", False), ("seed_oss", False),
+                                              ("hunyuan_v1_dense", False), ("hunyuan_v1_dense", True)])
 def test_more_decoder_families_match_huggingface(tmp_path, family, recompute):
     """OLMo 2 (norms behind the branches only, q/k norms over the whole projections), EXAONE 4 (the same placement with
     per-head q/k norms; hybrid checkpoints: windowed layers rotate, global ones do not), GLM (half of each head rotates,
     rotary pairs neighbours in the checkpoint, fused gate/up tensor, q/k/v bias), GLM-4 0414 (GLM with norms behind
     the branches as well), Helium and ERNIE 4.5 (Llama layers, rotary pairs neighbours), Seed-OSS (q/k/v bias and an
-    explicit head_dim): logits, every gradient, the chunked inference path and checkpoints both ways."""
+    explicit head_dim), HunYuan (per-head q/k norms behind the rotation, a base scaled by a fixed alpha): logits, every gradient, the chunked inference path and checkpoints both ways."""
     cls_n, ccls_n, extra, flags, general = _MORE[family]
     cls, ccls = getattr(tr, cls_n), getattr(tr, ccls_n)
     mt = family.split()[0]

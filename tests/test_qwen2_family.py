@@ -70,7 +70,8 @@ def test_engine_trains_the_bias():
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("variant", ["qwen2", "qwen3", "llama with biases", "plain llama, long batch", "granite",
-                                     "plain partial rotary, long batch", "olmo2", "glm4, long batch"])
+                                     "plain partial rotary, long batch", "olmo2", "glm4, long batch",
+                                     "hunyuan"])
 def test_gpu_kernels_follow_the_cpu_model(variant):
     """bf16 kernels (GEMMs with their epilogues, bias add, per-head norms, RoPE, flash attention ...) against the fp32 CPU
     statement of the same model, for the layer variants: q/k/v bias (Qwen2), per-head q/k norms (Qwen3), biases on every
@@ -87,6 +88,8 @@ def test_gpu_kernels_follow_the_cpu_model(variant):
         kw.update(attention_bias=True, o_bias=True, mlp_bias=True)
     elif "partial rotary" in variant:
         kw.update(partial_rotary_factor=0.75)
+    elif variant == "hunyuan":
+        kw.update(model_type="hunyuan_v1_dense", qk_norm=True, qk_norm_after_rope=True)
     elif variant == "olmo2":
         kw.update(model_type="olmo2", pre_norm=False, post_norm=True, qk_norm_full=True)
     elif variant.startswith("glm4"):
