@@ -76,6 +76,8 @@ class LlamaConfig:
     @property
     def sandwich(self) -> bool:
         """Whether the layers take the general node of models/sandwich.py instead of the fused pre-norm layer."""
+        if self.num_local_experts and self.pre_norm and not self.post_norm and not self.qk_norm_after_rope:
+            return False         # experts: the two nodes of models/moe.py (their attention half takes either q/k norm)
         return self.post_norm or not self.pre_norm or self.qk_norm_full or self.qk_norm_after_rope
 
     @property
@@ -155,6 +157,9 @@ class LlamaConfig:
                      moe_intermediate_size=self.intermediate_size, shared_expert_intermediate_size=shared_f,
                      norm_topk_prob=bool(renorm), decoder_sparse_step=1, mlp_only_layers=[])
             d["intermediate_size"] = extra.pop("dense_intermediate_size", self.intermediate_size)
+        elif self.model_type == "olmoe":
+            d.update(architectures=["OlmoeForCausalLM"], hidden_act="silu", torch_dtype="bfloat16", attention_bias=False,
+                     num_experts=d.pop("num_local_experts"), norm_topk_prob=bool(renorm), clip_qkv=None)
         elif self.model_type == "olmo2":
             d.update(architectures=["Olmo2ForCausalLM"], hidden_act="silu", torch_dtype="bfloat16", attention_bias=False)
         elif self.model_type == "exaone4":
@@ -214,7 +219,8 @@ class LlamaConfig:
         return {**extra, **d}
 
     _KNOWN_TYPES = ("llama", "mistral", "qwen2", "phi3", "mixtral", "qwen3", "qwen3_moe", "qwen2_moe", "granite",
-                    "smollm3", "olmo2", "glm", "glm4", "exaone4", "helium", "ernie4_5", "seed_oss", "hunyuan_v1_dense")
+                    "smollm3", "olmo2", "glm", "glm4", "exaone4", "helium", "ernie4_5", "seed_oss", "hunyuan_v1_dense",
+                    "olmoe")
 
     @classmethod
     def from_hf_dict(cls, d: dict) -> "LlamaConfig":
@@ -285,7 +291,7 @@ class LlamaConfig:
         if mt == "mixtral":
             if int(kw.get("num_local_experts") or 0) < 1:
                 raise ValueError("a mixtral config needs num_local_experts")
-        elif kw.get("num_local_experts") and mt not in ("qwen3_moe", "qwen2_moe"):
+        elif kw.get("num_local_experts") and mt not in ("qwen3_moe", "qwen2_moe", "olmoe"):
             raise NotImplementedError(f"experts on model_type {mt!r} are not built (mixtral is)")
         if mt == "qwen3":
             kw["qk_norm"] = True
@@ -295,6 +301,15 @@ class LlamaConfig:
                 kw["sliding_window"] = None
         for k in ("qk_norm_full", "qk_norm_after_rope", "pre_norm", "post_norm", "rope_interleaved"):      # set by the model type alone
             kw.pop(k, None)
+        if mt == "olmoe":            # Llama layers, q/k norms over the whole projections, every MLP a mixture of experts
+            n_exp = int(d.get("num_experts") or d.get("num_local_experts") or 0)
+            if n_exp < 1:
+                raise ValueError("an olmoe config needs num_experts")
+            if kw.get("attention_bias"):
+                raise NotImplementedError("olmoe with attention_bias also puts a bias on o_proj, which is not built")
+            if d.get("clip_qkv"):
+                raise NotImplementedError("olmoe with clip_qkv is not built")
+            kw.update(num_local_experts=n_exp, qk_norm_full=True, moe_renormalize=bool(d.get("norm_topk_prob", False)))
         if mt == "hunyuan_v1_dense":         # Llama layers with per-head q/k norms behind the rotation
             kw.update(qk_norm=True, qk_norm_after_rope=True)
             if kw.get("attention_bias"):
@@ -917,13 +932,16 @@ class LlamaModel(nn.Module):
                     h = layer_inference(layer, cfg, h, attend, cfg.rms_norm_eps)
                     continue
                 n1, _, _ = basic.rmsnorm_fwd(h, layer.input_layernorm, cfg.rms_norm_eps)
-                if not hasattr(layer, "qkv_bias") and not cfg.qk_norm:
+                if not hasattr(layer, "qkv_bias") and not cfg.qk_norm and not cfg.qk_norm_full:
                     qkv = basic.linear_rope_fwd(n1, layer.qkv_proj, pos, cos, sin, H + Hkv, d)
                 else:
                     qkv = basic.linear_fwd(n1, layer.qkv_proj)
                     if hasattr(layer, "qkv_bias"):
                         basic.bias_add_(qkv, layer.qkv_bias)
-                    if cfg.qk_norm:
+                    if cfg.qk_norm_full:
+                        from .sandwich import _qk_full_fwd
+                        qkv, _ = _qk_full_fwd(qkv, layer.q_norm, layer.k_norm, H * d, Hkv * d, cfg.rms_norm_eps)
+                    elif cfg.qk_norm:
                         qkv, _ = basic.headnorm_fwd(qkv, layer.q_norm, layer.k_norm, H, Hkv, d, cfg.rms_norm_eps)
                     basic.rope_(qkv, pos, cos, sin, H + Hkv, d)
                 kc[:, c0:c0 + n] = qkv[:, H * d:(H + Hkv) * d].reshape(B, n, kv)
@@ -1016,7 +1034,7 @@ class LlamaModel(nn.Module):
             if cfg.qk_norm and cfg.model_type == "hunyuan_v1_dense":
                 yield pre + "self_attn.query_layernorm.weight", l.q_norm, None
                 yield pre + "self_attn.key_layernorm.weight", l.k_norm, None
-            elif cfg.qk_norm:
+            elif cfg.qk_norm or cfg.qk_norm_full:
                 yield pre + "self_attn.q_norm.weight", l.q_norm, None
                 yield pre + "self_attn.k_norm.weight", l.k_norm, None
             yield pre + "self_attn.o_proj.weight", l.o_proj, None
@@ -1033,7 +1051,7 @@ class LlamaModel(nn.Module):
                 yield pre + "mlp.shared_expert.up_proj.weight", l.shared_gate_up_proj, slice(fs, 2 * fs)
                 yield pre + "mlp.shared_expert.down_proj.weight", l.shared_down_proj, None
                 yield pre + "mlp.shared_expert_gate.weight", l.shared_expert_gate, None
-            if cfg.num_local_experts and cfg.model_type in ("qwen3_moe", "qwen2_moe"):
+            if cfg.num_local_experts and cfg.model_type in ("qwen3_moe", "qwen2_moe", "olmoe"):
                 yield pre + "mlp.gate.weight", l.router, None
                 for e in range(cfg.num_local_experts):
                     ex = pre + f"mlp.experts.{e}."
@@ -1135,7 +1153,7 @@ class LlamaModel(nn.Module):
         [E, 2f, h], ``mlp.experts.down_proj`` [E, h, f], router ``mlp.gate.weight``); the published checkpoints - and
         this model's own names - list them per expert under ``block_sparse_moe``."""
         f = self.cfg.intermediate_size
-        qwen = self.cfg.model_type in ("qwen3_moe", "qwen2_moe")
+        qwen = self.cfg.model_type in ("qwen3_moe", "qwen2_moe", "olmoe")
         block = "mlp." if qwen else "block_sparse_moe."
         gate_n, up_n, down_n = ("gate_proj", "up_proj", "down_proj") if qwen else ("w1", "w3", "w2")
         out = {}

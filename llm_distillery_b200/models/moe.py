@@ -109,7 +109,10 @@ class AttnBlockFn(torch.autograd.Function):
         if b_qkv is not None:
             basic.bias_add_(qkv, b_qkv)
         qk_saved = ()
-        if w_qn is not None:
+        if w_qn is not None and w_qn.numel() != d:       # one norm over the whole projection (OLMoE)
+            from .sandwich import _qk_full_fwd
+            qkv, qk_saved = _qk_full_fwd(qkv, w_qn, w_kn, H * d, Hkv * d, eps)
+        elif w_qn is not None:
             qkv_raw = qkv
             qkv, rstd_qk = basic.headnorm_fwd(qkv_raw, w_qn, w_kn, H, Hkv, d, eps)
             qk_saved = (qkv_raw, rstd_qk)
@@ -136,17 +139,24 @@ class AttnBlockFn(torch.autograd.Function):
         s_ln1, s_qkv, s_o = ctx.slots
         w_qn, w_kn = ctx.qk_w
         qkv_raw = rstd_qk = None
+        full = w_qn is not None and w_qn.numel() != d
+        qk_full = ()
         if recompute:
             h, pos, cos, sin = ctx.saved_tensors
             n1, _, rstd1 = basic.rmsnorm_fwd(h, w_ln1, eps)
             qkv = basic.linear_fwd(n1, w_qkv)
             if ctx.b_qkv is not None:
                 basic.bias_add_(qkv, ctx.b_qkv)
-            if w_qn is not None:
+            if full:
+                from .sandwich import _qk_full_fwd
+                qkv, qk_full = _qk_full_fwd(qkv, w_qn, w_kn, H * d, Hkv * d, eps)
+            elif w_qn is not None:
                 qkv_raw = qkv
                 qkv, rstd_qk = basic.headnorm_fwd(qkv_raw, w_qn, w_kn, H, Hkv, d, eps)
             basic.rope_(qkv, pos, cos, sin, H + Hkv, d)
             att, lse = attention.attention_fwd(qkv, B, L, H, Hkv, d)
+        elif full:
+            h, pos, cos, sin, rstd1, n1, qkv, att, lse, *qk_full = ctx.saved_tensors
         elif w_qn is not None:
             h, pos, cos, sin, rstd1, n1, qkv, att, lse, qkv_raw, rstd_qk = ctx.saved_tensors
         else:
@@ -157,8 +167,15 @@ class AttnBlockFn(torch.autograd.Function):
         dqkv = attention.attention_bwd_unrotated(datt, qkv, att, lse, B, L, H, Hkv, d, pos, cos, sin)
         del datt
         g_qn = g_kn = None
-        if w_qn is not None:
+        if full:
+            q_raw, k_raw, rq, rk = qk_full
+            qw, kvw = H * d, Hkv * d
+            dq, dwq = basic.rmsnorm_bwd(dqkv[:, :qw].contiguous(), q_raw, w_qn, rq)
+            dk, dwk = basic.rmsnorm_bwd(dqkv[:, qw:qw + kvw].contiguous(), k_raw, w_kn, rk)
+            dqkv = torch.cat([dq, dk, dqkv[:, qw + kvw:]], dim=1)
+        elif w_qn is not None:
             dwq, dwk = basic.headnorm_bwd_(dqkv, qkv_raw, w_qn, w_kn, rstd_qk, H, Hkv, d)
+        if w_qn is not None:
             g_qn = _ll._vec_grad(dwq, w_qn, ctx.qk_slots[0])
             g_kn = _ll._vec_grad(dwk, w_kn, ctx.qk_slots[1])
         g_b = None

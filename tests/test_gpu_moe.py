@@ -13,21 +13,25 @@ def _cos(a, b):
     return float((a @ b) / (a.norm() * b.norm() + 1e-30))
 
 
-@pytest.mark.parametrize("family", ["mixtral", "qwen2_moe"])
+@pytest.mark.parametrize("family", ["mixtral", "qwen2_moe", "olmoe"])
 def test_experts_forward_and_backward_match_the_fp32_restatement(family):
     """Mixtral's routed experts; Qwen2-MoE adds the q/k/v bias and the gated shared expert (a dense MLP on the fused
-    SwiGLU GEMMs)."""
+    SwiGLU GEMMs); OLMoE normalises the whole query / key projections."""
     cfg = LlamaConfig(vocab_size=1024, hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=4,
                       num_key_value_heads=2, max_position_embeddings=512, model_type=family, num_local_experts=4,
                       num_experts_per_tok=2,
                       **(dict(shared_expert_intermediate_size=384, attention_bias=True, moe_renormalize=False)
-                         if family == "qwen2_moe" else {}))
+                         if family == "qwen2_moe" else dict(qk_norm_full=True, moe_renormalize=False)
+                         if family == "olmoe" else {}))
     ref = build_model(cfg, dtype=torch.float32, device="cpu", seed=4)
     with torch.no_grad():
         for l in ref.layers:
             l.router.mul_(20.0)          # clear routing decisions: bf16 rounding must not flip many of them
             if family == "qwen2_moe":
                 l.shared_expert_gate.mul_(20.0)
+            if family == "olmoe":
+                l.q_norm.uniform_(0.5, 1.5)
+                l.k_norm.uniform_(0.5, 1.5)
     gpu = build_model(cfg, dtype=torch.bfloat16, device="cuda", seed=None)
     with torch.no_grad():
         for (n, p), (_, q) in zip(gpu.named_parameters(), ref.named_parameters()):

@@ -350,3 +350,54 @@ def test_qwen2_moe_matches_huggingface(tmp_path, renorm, recompute):
             LlamaConfig.from_hf_dict(dict(d, **bad))
     with pytest.raises(NotImplementedError):
         LlamaConfig.from_hf_dict(dict(_base(), model_type="llama", shared_expert_intermediate_size=64))
+
+
+@pytest.mark.parametrize("recompute", [False, True])
+def test_olmoe_matches_huggingface(tmp_path, recompute):
+    """OLMoE: Llama layers whose q/k norms cover the whole projections, every MLP a mixture of experts without
+    renormalised router weights."""
+    torch.manual_seed(3)
+    hf = tr.OlmoeForCausalLM(tr.OlmoeConfig(**{k: v for k, v in _base().items() if k != "rope_theta"}, num_experts=4,
+                                            num_experts_per_tok=2, pad_token_id=0, attn_implementation="eager",
+                                            tie_word_embeddings=False)).float()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if "norm" in n:
+                p.uniform_(0.5, 1.5)
+            elif n.endswith("mlp.gate.weight"):
+                p.mul_(30.0)
+    hf.save_pretrained(str(tmp_path / "hf"), safe_serialization=True)
+    model = load_hf_model(str(tmp_path / "hf"), dtype=torch.float32)
+    cfg = model.cfg
+    assert cfg.model_type == "olmoe" and cfg.qk_norm_full and not cfg.sandwich and cfg.num_local_experts == 4
+    assert not cfg.moe_renormalize
+    assert sum(p.numel() for p in model.parameters()) == cfg.num_params() == sum(p.numel() for p in hf.parameters())
+    model.grad_checkpointing = recompute
+    x = torch.randint(1, 320, (2, 48))
+    ours, ref = model(x), hf(x).logits
+    assert torch.allclose(ours, ref, atol=3e-4, rtol=1e-3), (ours - ref).abs().max()
+    tgt = torch.randint(0, 320, (2 * 48,))
+    torch.nn.functional.cross_entropy(ours.reshape(-1, 320), tgt).backward()
+    torch.nn.functional.cross_entropy(ref.reshape(-1, 320), tgt).backward()
+    hf_grads = {n: p.grad for n, p in hf.named_parameters()}
+    f = cfg.intermediate_size
+    for n, p, sl in model.named_hf_parameters():
+        g = p.grad if sl is None else p.grad[sl]
+        if n in hf_grads:
+            want = hf_grads[n]
+        else:
+            pre, rest = n.split("mlp.experts.")
+            e, which = int(rest.split(".")[0]), rest.split(".")[1]
+            if which == "down_proj":
+                want = hf_grads[pre + "mlp.experts.down_proj"][e]
+            else:
+                gu = hf_grads[pre + "mlp.experts.gate_up_proj"][e]
+                want = gu[:f] if which == "gate_proj" else gu[f:]
+        assert torch.allclose(g, want, atol=2e-5, rtol=2e-3), (n, (g - want).abs().max())
+    model.grad_checkpointing = False
+    with torch.no_grad():
+        hs = model.hidden_states_chunked(x, 16)
+        assert torch.allclose(torch.nn.functional.linear(hs, model.lm_head).view(2, 48, -1), ref, atol=3e-4, rtol=1e-3)
+    save_hf_model(model, str(tmp_path / "ours"))
+    hf2 = tr.AutoModelForCausalLM.from_pretrained(str(tmp_path / "ours"), dtype=torch.float32, attn_implementation="eager")
+    assert type(hf2) is tr.OlmoeForCausalLM and torch.allclose(hf2(x).logits, ref, atol=3e-4, rtol=1e-3)
