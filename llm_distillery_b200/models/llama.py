@@ -46,6 +46,7 @@ class LlamaConfig:
     moe_renormalize: bool = True      # router weights renormalised over the chosen experts (Mixtral; Qwen3-MoE norm_topk_prob)
     shared_expert_intermediate_size: int = 0   # > 0 (Qwen2-MoE): a dense SwiGLU expert of this width for every token,
                                                # scaled by a per-token sigmoid gate, beside the routed experts
+    shared_expert_gated: bool = True           # false: the shared expert's output is added as it is (Granite MoE)
     attention_bias: bool = False      # bias on the q/k/v projections (Qwen2 family; Llama configs with attention_bias)
     o_bias: bool = False              # bias on o_proj as well (HuggingFace Llama's attention_bias = true, e.g. Granite code)
     mlp_bias: bool = False            # bias on gate / up / down projections (HuggingFace Llama's mlp_bias)
@@ -97,7 +98,7 @@ class LlamaConfig:
         E = self.num_local_experts
         per_layer = h * (self.q_size + 2 * self.kv_size) + self.q_size * h + 3 * h * f * max(E, 1) + E * h + 2 * h
         if self.shared_expert_intermediate_size:
-            per_layer += 3 * h * self.shared_expert_intermediate_size + h
+            per_layer += 3 * h * self.shared_expert_intermediate_size + (h if self.shared_expert_gated else 0)
         if self.attention_bias:
             per_layer += self.q_size + 2 * self.kv_size
         if self.qk_norm:
@@ -143,6 +144,7 @@ class LlamaConfig:
         for k in ("qk_norm_full", "qk_norm_after_rope", "pre_norm", "post_norm", "rope_interleaved"):      # implied by the model type
             d.pop(k)
         shared_f = d.pop("shared_expert_intermediate_size")
+        d.pop("shared_expert_gated")
         gran = {k: d.pop(k) for k in ("embedding_multiplier", "attention_multiplier", "residual_multiplier", "logits_scaling")}
         if self.model_type == "qwen3_moe":      # HuggingFace's names: num_experts, moe_intermediate_size, norm_topk_prob
             d.update(architectures=["Qwen3MoeForCausalLM"], hidden_act="silu", torch_dtype="bfloat16",
@@ -212,6 +214,14 @@ class LlamaConfig:
         ob, mb = self.o_bias, self.mlp_bias
         if ob or mb:          # HuggingFace's Llama: attention_bias covers q, k, v AND o
             d.update(architectures=["LlamaForCausalLM"], model_type="llama", attention_bias=bool(ob), mlp_bias=bool(mb))
+        if self.model_type in ("granitemoe", "granitemoeshared"):
+            d.update(architectures=["GraniteMoeForCausalLM" if self.model_type == "granitemoe"
+                                    else "GraniteMoeSharedForCausalLM"], model_type=self.model_type,
+                     num_local_experts=self.num_local_experts, num_experts_per_tok=self.num_experts_per_tok, **gran)
+            if self.model_type == "granitemoeshared":
+                d["shared_intermediate_size"] = shared_f
+            if d.get("attention_multiplier") is None:
+                d["attention_multiplier"] = 1.0 / math.sqrt(self.head_dim)
         if self.model_type == "granite":
             d.update(architectures=["GraniteForCausalLM"], model_type="granite", **gran)
             if d.get("attention_multiplier") is None:
@@ -220,7 +230,7 @@ class LlamaConfig:
 
     _KNOWN_TYPES = ("llama", "mistral", "qwen2", "phi3", "mixtral", "qwen3", "qwen3_moe", "qwen2_moe", "granite",
                     "smollm3", "olmo2", "glm", "glm4", "exaone4", "helium", "ernie4_5", "seed_oss", "hunyuan_v1_dense",
-                    "olmoe")
+                    "olmoe", "granitemoe", "granitemoeshared")
 
     @classmethod
     def from_hf_dict(cls, d: dict) -> "LlamaConfig":
@@ -286,12 +296,12 @@ class LlamaConfig:
                       moe_renormalize=bool(d.get("norm_topk_prob", False)), attention_bias=True)
             if not d.get("use_sliding_window", False):
                 kw["sliding_window"] = None
-        elif kw.get("shared_expert_intermediate_size"):
+        elif kw.get("shared_expert_intermediate_size") and mt != "granitemoeshared":
             raise NotImplementedError(f"a shared expert on model_type {mt!r} is not built (qwen2_moe is)")
         if mt == "mixtral":
             if int(kw.get("num_local_experts") or 0) < 1:
                 raise ValueError("a mixtral config needs num_local_experts")
-        elif kw.get("num_local_experts") and mt not in ("qwen3_moe", "qwen2_moe", "olmoe"):
+        elif kw.get("num_local_experts") and mt not in ("qwen3_moe", "qwen2_moe", "olmoe", "granitemoe", "granitemoeshared"):
             raise NotImplementedError(f"experts on model_type {mt!r} are not built (mixtral is)")
         if mt == "qwen3":
             kw["qk_norm"] = True
@@ -301,6 +311,14 @@ class LlamaConfig:
                 kw["sliding_window"] = None
         for k in ("qk_norm_full", "qk_norm_after_rope", "pre_norm", "post_norm", "rope_interleaved"):      # set by the model type alone
             kw.pop(k, None)
+        if mt in ("granitemoe", "granitemoeshared"):     # Granite's multipliers around Mixtral-style experts
+            if int(kw.get("num_local_experts") or 0) < 1:
+                raise ValueError(f"a {mt} config needs num_local_experts")
+            if kw.get("attention_bias"):
+                raise NotImplementedError(f"{mt} with attention_bias also puts a bias on o_proj, which is not built")
+            kw.update(moe_renormalize=True, shared_expert_gated=False,
+                      shared_expert_intermediate_size=int(d.get("shared_intermediate_size") or 0)
+                      if mt == "granitemoeshared" else 0)
         if mt == "olmoe":            # Llama layers, q/k norms over the whole projections, every MLP a mixture of experts
             n_exp = int(d.get("num_experts") or d.get("num_local_experts") or 0)
             if n_exp < 1:
@@ -375,7 +393,7 @@ class LlamaConfig:
             kw["head_dim_override"] = int(hd)       # e.g. Mistral-Nemo: 5120 hidden, 32 heads of 128
         if mt == "qwen2" and not d.get("use_sliding_window", False):
             kw["sliding_window"] = None        # Qwen2 configs carry a window that is switched off
-        if mt != "granite":
+        if mt not in ("granite", "granitemoe", "granitemoeshared"):
             for k in ("embedding_multiplier", "attention_multiplier", "residual_multiplier", "logits_scaling"):
                 kw.pop(k, None)           # other families may carry such keys with another meaning
         cfg = cls(**kw)
@@ -737,7 +755,8 @@ class LlamaDecoderLayer(nn.Module):
             if fs:
                 self.shared_gate_up_proj = nn.Parameter(torch.empty(2 * fs, h, **kw))
                 self.shared_down_proj = nn.Parameter(torch.empty(h, fs, **kw))
-                self.shared_expert_gate = nn.Parameter(torch.empty(1, h, **kw))
+                if cfg.shared_expert_gated:
+                    self.shared_expert_gate = nn.Parameter(torch.empty(1, h, **kw))
         else:
             self.gate_up_proj = nn.Parameter(torch.empty(2 * f, h, **kw))
             self.down_proj = nn.Parameter(torch.empty(h, f, **kw))
@@ -869,10 +888,10 @@ class LlamaModel(nn.Module):
                 from .moe import AttnBlockFn, MoEBlockFn
                 h = AttnBlockFn.apply(h, pos, cos, sin, layer.input_layernorm, layer.qkv_proj, layer.o_proj, meta,
                                       getattr(layer, "qkv_bias", None), getattr(layer, "q_norm", None),
-                                      getattr(layer, "k_norm", None))
+                                      getattr(layer, "k_norm", None), rmul)
                 h = MoEBlockFn.apply(h, layer.post_attention_layernorm, layer.router, layer.gate_up_proj,
                                      layer.down_proj, (cfg.rms_norm_eps, cfg.num_experts_per_tok, meta[6],
-                                                       layer.input_layernorm, cfg.moe_renormalize),
+                                                       layer.input_layernorm, cfg.moe_renormalize, rmul),
                                      getattr(layer, "shared_gate_up_proj", None),
                                      getattr(layer, "shared_down_proj", None),
                                      getattr(layer, "shared_expert_gate", None))
@@ -954,10 +973,11 @@ class LlamaModel(nn.Module):
                 n2, _, _ = basic.rmsnorm_fwd(h1, layer.post_attention_layernorm, cfg.rms_norm_eps)
                 if cfg.num_local_experts:
                     from .moe import moe_mlp
-                    shared = ((layer.shared_gate_up_proj, layer.shared_down_proj, layer.shared_expert_gate)
+                    shared = ((layer.shared_gate_up_proj, layer.shared_down_proj, getattr(layer, "shared_expert_gate", None))
                               if cfg.shared_expert_intermediate_size else None)
-                    h = h1 + moe_mlp(n2, layer.router, layer.gate_up_proj, layer.down_proj, cfg.num_experts_per_tok,
+                    branch = moe_mlp(n2, layer.router, layer.gate_up_proj, layer.down_proj, cfg.num_experts_per_tok,
                                      cfg.moe_renormalize, shared)
+                    h = h1 + (branch if rm == 1.0 else branch * rm)
                     continue
                 if cfg.mlp_bias:
                     act = basic.swiglu_fwd(basic.bias_add_(basic.linear_fwd(n2, layer.gate_up_proj), layer.gate_up_bias))
@@ -1045,6 +1065,14 @@ class LlamaModel(nn.Module):
                 yield pre + "mlp.gate_proj.bias", l.gate_up_bias, slice(0, f)
                 yield pre + "mlp.up_proj.bias", l.gate_up_bias, slice(f, 2 * f)
                 yield pre + "mlp.down_proj.bias", l.down_bias, None
+            if cfg.model_type in ("granitemoe", "granitemoeshared"):      # stacked tensors, in this model's own order
+                yield pre + "block_sparse_moe.router.layer.weight", l.router, None
+                yield pre + "block_sparse_moe.input_linear.weight", l.gate_up_proj, None
+                yield pre + "block_sparse_moe.output_linear.weight", l.down_proj, None
+                if cfg.shared_expert_intermediate_size:
+                    yield pre + "shared_mlp.input_linear.weight", l.shared_gate_up_proj, None
+                    yield pre + "shared_mlp.output_linear.weight", l.shared_down_proj, None
+                continue
             if cfg.shared_expert_intermediate_size:
                 fs = cfg.shared_expert_intermediate_size
                 yield pre + "mlp.shared_expert.gate_proj.weight", l.shared_gate_up_proj, slice(0, fs)

@@ -73,10 +73,14 @@ def experts_forward(x_perm: torch.Tensor, counts: list[int], w_gu: torch.Tensor,
 
 def shared_expert_forward(n2: torch.Tensor, w_sgu: torch.Tensor, w_sd: torch.Tensor, w_sg: torch.Tensor):
     """Qwen2-MoE's shared expert: a dense SwiGLU MLP every token passes through, scaled per token by
-    sigmoid(n2 . w_sg). Returns (gu_s [T, 2fs], act_s [T, fs], y_s [T, h], gate [T, 1] fp32)."""
+    sigmoid(n2 . w_sg) (Qwen2-MoE) or added as it is (``w_sg`` None: Granite's shared MLP).
+    Returns (gu_s [T, 2fs], act_s [T, fs], y_s [T, h], gate [T, 1] fp32)."""
     gu_s, act_s = basic.linear_swiglu_fwd(n2, w_sgu)
     y_s = basic.linear_fwd(act_s, w_sd)
-    gate = torch.sigmoid(F.linear(n2, w_sg).float())
+    if w_sg is None:         # Granite's shared MLP joins ungated
+        gate = torch.ones((n2.shape[0], 1), dtype=torch.float32, device=n2.device)
+    else:
+        gate = torch.sigmoid(F.linear(n2, w_sg).float())
     return gu_s, act_s, y_s, gate
 
 
@@ -102,8 +106,9 @@ class AttnBlockFn(torch.autograd.Function):
     """h1 = h + Attn(RMSNorm(h)): the attention half of ``llama.DecoderLayerFn`` as a node of its own."""
 
     @staticmethod
-    def forward(ctx, h, pos, cos, sin, w_ln1, w_qkv, w_o, meta, b_qkv=None, w_qn=None, w_kn=None):
+    def forward(ctx, h, pos, cos, sin, w_ln1, w_qkv, w_o, meta, b_qkv=None, w_qn=None, w_kn=None, rmul=1.0):
         B, L, H, Hkv, d, eps, recompute = meta
+        ctx.rmul = rmul          # Granite's residual multiplier: the branch is scaled before it joins the stream
         n1, _, rstd1 = basic.rmsnorm_fwd(h, w_ln1, eps)
         qkv = basic.linear_fwd(n1, w_qkv)
         if b_qkv is not None:
@@ -118,7 +123,7 @@ class AttnBlockFn(torch.autograd.Function):
             qk_saved = (qkv_raw, rstd_qk)
         basic.rope_(qkv, pos, cos, sin, H + Hkv, d)
         att, lse = attention.attention_fwd(qkv, B, L, H, Hkv, d)
-        h1 = basic.linear_fwd(att, w_o, residual=h)
+        h1 = basic.gemm(att, w_o, residual=h, alpha=rmul)
         ctx.meta = meta
         ctx.weights = (w_ln1, w_qkv, w_o)
         ctx.slots = tuple(_ll._slot(w) for w in ctx.weights)
@@ -162,8 +167,10 @@ class AttnBlockFn(torch.autograd.Function):
         else:
             h, pos, cos, sin, rstd1, n1, qkv, att, lse = ctx.saved_tensors
         dh1 = dh1.contiguous()
-        g_o = _ll._wgrad(dh1, att, w_o, s_o)
-        datt = basic.linear_dgrad(dh1, w_o)
+        da = dh1 if ctx.rmul == 1.0 else dh1 * ctx.rmul
+        g_o = _ll._wgrad(da, att, w_o, s_o)
+        datt = basic.linear_dgrad(da, w_o)
+        del da
         dqkv = attention.attention_bwd_unrotated(datt, qkv, att, lse, B, L, H, Hkv, d, pos, cos, sin)
         del datt
         g_qn = g_kn = None
@@ -192,7 +199,7 @@ class AttnBlockFn(torch.autograd.Function):
         g_ln1 = _ll._vec_grad(dw1, w_ln1, s_ln1)
         if _ll.LAYER_BACKWARD_DONE[0] is not None:      # the layer's first parameter: all of its gradients are final
             _ll.LAYER_BACKWARD_DONE[0](w_ln1)
-        return dh, None, None, None, g_ln1, g_qkv, g_o, None, g_b, g_qn, g_kn
+        return dh, None, None, None, g_ln1, g_qkv, g_o, None, g_b, g_qn, g_kn, None
 
 
 def _expert_wgrad(dy, x, w, slot, e, first):
@@ -212,7 +219,8 @@ class MoEBlockFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, h1, w_ln2, w_router, w_gu, w_d, meta, w_sgu=None, w_sd=None, w_sg=None):
-        eps, k, recompute, _first, renorm = meta
+        eps, k, recompute, _first, renorm = meta[:5]
+        rmul = meta[5] if len(meta) > 5 else 1.0         # Granite's residual multiplier on the whole expert branch
         T, hdim = h1.shape
         n2, _, rstd2 = basic.rmsnorm_fwd(h1, w_ln2, eps)
         probs, top_e, top_w = route(n2, w_router, k, renorm)
@@ -221,19 +229,20 @@ class MoEBlockFn(torch.autograd.Function):
         x_perm = n2.index_select(0, tok)
         gu, act, y = experts_forward(x_perm, counts, w_gu, w_d)
         y_tok = y.index_select(0, inverse).view(T, k, hdim)
-        h2 = h1.float() + (y_tok.float() * top_w.unsqueeze(-1)).sum(1)
+        branch = (y_tok.float() * top_w.unsqueeze(-1)).sum(1)
         shared_saved = ()
         if w_sgu is not None:
             gu_s, act_s, y_s, gate = shared_expert_forward(n2, w_sgu, w_sd, w_sg)
-            h2 = h2 + gate * y_s.float()
+            branch = branch + gate * y_s.float()
             shared_saved = (gu_s, act_s, y_s, gate)
-        h2 = h2.to(h1.dtype)
+        h2 = (h1.float() + (branch if rmul == 1.0 else branch * rmul)).to(h1.dtype)
         ctx.meta = meta
         ctx.counts = counts
         ctx.weights = (w_ln2, w_router, w_gu, w_d)
         ctx.slots = tuple(_ll._slot(w) for w in ctx.weights)
         ctx.shared = (w_sgu, w_sd, w_sg)
-        ctx.shared_slots = tuple(_ll._slot(w) for w in ctx.shared) if w_sgu is not None else (None, None, None)
+        ctx.shared_slots = (tuple(_ll._slot(w) if w is not None else None for w in ctx.shared) if w_sgu is not None
+                            else (None, None, None))
         if recompute:
             ctx.save_for_backward(h1, top_e, order, inverse)
         else:
@@ -242,7 +251,8 @@ class MoEBlockFn(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dh2):
-        eps, k, recompute, first_param, renorm = ctx.meta
+        eps, k, recompute, first_param, renorm = ctx.meta[:5]
+        rmul = ctx.meta[5] if len(ctx.meta) > 5 else 1.0
         counts = ctx.counts
         w_ln2, w_router, w_gu, w_d = ctx.weights
         s_ln2, s_router, s_gu, s_d = ctx.slots
@@ -268,8 +278,10 @@ class MoEBlockFn(torch.autograd.Function):
         T, hdim = h1.shape
         E = w_gu.shape[0]
         dh2 = dh2.contiguous()
-        dh2f = dh2.float()
-        # combine: h2 = h1 + sum_k w_k y_k
+        dh2f = dh2.float()              # from here on the gradient of the BRANCH (the residual path keeps dh2)
+        if rmul != 1.0:
+            dh2f = dh2f * rmul
+        # combine: h2 = h1 + rmul * sum_k w_k y_k
         y_tok = y.index_select(0, inverse).view(T, k, hdim)
         d_top_w = (y_tok.float() * dh2f.unsqueeze(1)).sum(-1)                        # [T, k]
         dy_perm = (dh2f.unsqueeze(1) * top_w.unsqueeze(-1)).to(y.dtype).view(T * k, hdim).index_select(0, order)
@@ -334,9 +346,11 @@ class MoEBlockFn(torch.autograd.Function):
             g_sd = _ll._wgrad(dy_s, act_s, w_sd, s_sd)
             dgu_s = basic.linear_dgrad_swiglu_bwd(dy_s, w_sd, gu_s)
             g_sgu = _ll._wgrad(dgu_s, n2, w_sgu, s_sgu)
-            dn2 = dn2 + basic.linear_dgrad(dgu_s, w_sgu).float() + d_glogit * w_sg.float()
-            if w_sg.requires_grad:
-                g_sg = _ll._vec_grad(d_glogit.t() @ n2.float(), w_sg, s_sg)              # [1, h]
+            dn2 = dn2 + basic.linear_dgrad(dgu_s, w_sgu).float()
+            if w_sg is not None:
+                dn2 = dn2 + d_glogit * w_sg.float()
+                if w_sg.requires_grad:
+                    g_sg = _ll._vec_grad(d_glogit.t() @ n2.float(), w_sg, s_sg)          # [1, h]
         dh1, dw2 = basic.rmsnorm_bwd(dn2.to(h1.dtype), h1, w_ln2, rstd2, dres=dh2)
         g_ln2 = _ll._vec_grad(dw2, w_ln2, s_ln2)
         if g_gu is not None:

@@ -118,6 +118,9 @@ FAMILIES = {
                       qk_norm=True, head_dim_override=32),
     "olmoe": dict(model_type="olmoe", num_local_experts=4, num_experts_per_tok=2, intermediate_size=48,
                   qk_norm_full=True, moe_renormalize=False),
+    "granitemoeshared": dict(model_type="granitemoeshared", num_local_experts=4, num_experts_per_tok=2,
+                             intermediate_size=48, shared_expert_intermediate_size=80, shared_expert_gated=False,
+                             embedding_multiplier=6.0, attention_multiplier=0.2, residual_multiplier=0.4, logits_scaling=3.0),
     "smollm3": dict(model_type="smollm3", no_rope_layers=[1, 0]),
     "phi3, three quarters of a head rotate": dict(model_type="phi3", partial_rotary_factor=0.75),
     "granite": dict(model_type="granite", embedding_multiplier=6.0, attention_multiplier=0.2, residual_multiplier=0.4,

@@ -13,16 +13,20 @@ def _cos(a, b):
     return float((a @ b) / (a.norm() * b.norm() + 1e-30))
 
 
-@pytest.mark.parametrize("family", ["mixtral", "qwen2_moe", "olmoe"])
+@pytest.mark.parametrize("family", ["mixtral", "qwen2_moe", "olmoe", "granitemoeshared"])
 def test_experts_forward_and_backward_match_the_fp32_restatement(family):
     """Mixtral's routed experts; Qwen2-MoE adds the q/k/v bias and the gated shared expert (a dense MLP on the fused
-    SwiGLU GEMMs); OLMoE normalises the whole query / key projections."""
+    SwiGLU GEMMs); OLMoE normalises the whole query / key projections; Granite MoE scales both branches by a residual
+    multiplier and adds an ungated shared MLP."""
     cfg = LlamaConfig(vocab_size=1024, hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=4,
                       num_key_value_heads=2, max_position_embeddings=512, model_type=family, num_local_experts=4,
                       num_experts_per_tok=2,
                       **(dict(shared_expert_intermediate_size=384, attention_bias=True, moe_renormalize=False)
                          if family == "qwen2_moe" else dict(qk_norm_full=True, moe_renormalize=False)
-                         if family == "olmoe" else {}))
+                         if family == "olmoe" else
+                         dict(shared_expert_intermediate_size=384, shared_expert_gated=False, residual_multiplier=0.3,
+                              embedding_multiplier=6.0, attention_multiplier=0.1, logits_scaling=4.0)
+                         if family == "granitemoeshared" else {}))
     ref = build_model(cfg, dtype=torch.float32, device="cpu", seed=4)
     with torch.no_grad():
         for l in ref.layers:

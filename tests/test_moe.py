@@ -401,3 +401,47 @@ def test_olmoe_matches_huggingface(tmp_path, recompute):
     save_hf_model(model, str(tmp_path / "ours"))
     hf2 = tr.AutoModelForCausalLM.from_pretrained(str(tmp_path / "ours"), dtype=torch.float32, attn_implementation="eager")
     assert type(hf2) is tr.OlmoeForCausalLM and torch.allclose(hf2(x).logits, ref, atol=3e-4, rtol=1e-3)
+
+
+@pytest.mark.parametrize("family,recompute", [("granitemoe", False), ("granitemoeshared", False), ("granitemoeshared", True)])
+def test_granite_moe_matches_huggingface(tmp_path, family, recompute):
+    """Granite MoE: Granite's four multipliers around Mixtral-style experts (stacked tensors in the checkpoint); the
+    shared variant adds a dense MLP to every token's expert output, ungated."""
+    cls, ccls = ((tr.GraniteMoeForCausalLM, tr.GraniteMoeConfig) if family == "granitemoe"
+                 else (tr.GraniteMoeSharedForCausalLM, tr.GraniteMoeSharedConfig))
+    extra = dict(shared_intermediate_size=80) if family == "granitemoeshared" else {}
+    torch.manual_seed(5)
+    hf = cls(ccls(**{k: v for k, v in _base().items() if k != "rope_theta"}, num_local_experts=4, num_experts_per_tok=2,
+                  embedding_multiplier=6.0, attention_multiplier=0.2, residual_multiplier=0.4, logits_scaling=3.0,
+                  pad_token_id=0, attn_implementation="eager", tie_word_embeddings=False, **extra)).float()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if "norm" in n:
+                p.uniform_(0.5, 1.5)
+            elif "router" in n:
+                p.mul_(30.0)
+    hf.save_pretrained(str(tmp_path / "hf"), safe_serialization=True)
+    model = load_hf_model(str(tmp_path / "hf"), dtype=torch.float32)
+    cfg = model.cfg
+    assert cfg.model_type == family and cfg.num_local_experts == 4 and cfg.residual_multiplier == 0.4
+    assert cfg.shared_expert_intermediate_size == (80 if extra else 0) and not cfg.shared_expert_gated
+    assert sum(p.numel() for p in model.parameters()) == cfg.num_params() == sum(p.numel() for p in hf.parameters())
+    model.grad_checkpointing = recompute
+    x = torch.randint(1, 320, (2, 48))
+    ours, ref = model(x), hf(x).logits
+    assert torch.allclose(ours, ref, atol=3e-4, rtol=1e-3), (ours - ref).abs().max()
+    tgt = torch.randint(0, 320, (2 * 48,))
+    torch.nn.functional.cross_entropy(ours.reshape(-1, 320), tgt).backward()
+    torch.nn.functional.cross_entropy(ref.reshape(-1, 320), tgt).backward()
+    hf_grads = {n: p.grad for n, p in hf.named_parameters()}
+    ours_g = {n: (p.grad if sl is None else p.grad[sl]) for n, p, sl in model.named_hf_parameters()}
+    assert set(ours_g) == set(hf_grads)
+    for n, g in ours_g.items():
+        assert torch.allclose(g, hf_grads[n], atol=2e-5, rtol=2e-3), (n, (g - hf_grads[n]).abs().max())
+    model.grad_checkpointing = False
+    with torch.no_grad():
+        hs = model.hidden_states_chunked(x, 16)
+        assert torch.allclose(torch.nn.functional.linear(hs, model.lm_head).view(2, 48, -1), ref, atol=3e-4, rtol=1e-3)
+    save_hf_model(model, str(tmp_path / "ours"))
+    hf2 = tr.AutoModelForCausalLM.from_pretrained(str(tmp_path / "ours"), dtype=torch.float32, attn_implementation="eager")
+    assert type(hf2) is cls and torch.allclose(hf2(x).logits, ref, atol=3e-4, rtol=1e-3)
