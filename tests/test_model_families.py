@@ -511,3 +511,43 @@ def test_granite_multipliers_match_huggingface(tmp_path):
         load_tp_weights(str(tmp_path / "ours"), 0, 2, dtype=torch.float32)
     # a Llama config that happens to carry such keys is not affected by them
     assert LlamaConfig.from_hf_dict(dict(_base(), model_type="llama", residual_multiplier=0.5)).residual_multiplier == 1.0
+
+
+def test_every_model_type_survives_config_round_trips():
+    """to_hf_dict -> from_hf_dict gives the same configuration for every model type that is read, and every type in
+    the list of known types is exercised here."""
+    import dataclasses
+    moe = dict(num_local_experts=4, num_experts_per_tok=2)
+    cases = {
+        "llama": {}, "mistral": dict(sliding_window=128), "qwen2": dict(attention_bias=True),
+        "phi3": dict(partial_rotary_factor=0.75), "mixtral": moe,
+        "qwen3": dict(qk_norm=True, head_dim_override=32),
+        "qwen3_moe": dict(moe, qk_norm=True, moe_renormalize=False),
+        "qwen2_moe": dict(moe, attention_bias=True, shared_expert_intermediate_size=80, moe_renormalize=False),
+        "granite": dict(embedding_multiplier=6.0, attention_multiplier=0.2, residual_multiplier=0.4, logits_scaling=3.0),
+        "granitemoe": dict(moe, residual_multiplier=0.4, attention_multiplier=0.2, shared_expert_gated=False),
+        "granitemoeshared": dict(moe, residual_multiplier=0.4, attention_multiplier=0.2, shared_expert_gated=False,
+                                 shared_expert_intermediate_size=80),
+        "smollm3": dict(no_rope_layers=[1, 0]),
+        "olmo2": dict(pre_norm=False, post_norm=True, qk_norm_full=True),
+        "olmoe": dict(moe, qk_norm_full=True, moe_renormalize=False),
+        "glm": dict(attention_bias=True, partial_rotary_factor=0.5, rope_interleaved=True),
+        "glm4": dict(attention_bias=True, partial_rotary_factor=0.5, rope_interleaved=True, post_norm=True),
+        "exaone4": dict(pre_norm=False, post_norm=True, qk_norm=True, no_rope_layers=[1, 0], sliding_window=128),
+        "helium": dict(rope_interleaved=True), "ernie4_5": dict(rope_interleaved=True),
+        "seed_oss": dict(attention_bias=True, head_dim_override=32),
+        "hunyuan_v1_dense": dict(qk_norm=True, qk_norm_after_rope=True,
+                                 rope_scaling={"rope_type": "dynamic", "alpha": 1000.0, "factor": 1.0}),
+    }
+    assert set(cases) == set(LlamaConfig._KNOWN_TYPES)
+    for mt, kw in cases.items():
+        cfg = LlamaConfig(**_base(), model_type=mt, **kw)
+        back = LlamaConfig.from_hf_dict(cfg.to_hf_dict())
+        a, b = dataclasses.asdict(cfg), dataclasses.asdict(back)
+        a.pop("extra"), b.pop("extra")
+        if a["attention_multiplier"] is None and b["attention_multiplier"] is not None:     # written out as 1 / sqrt(d)
+            assert abs(b["attention_multiplier"] - cfg.head_dim ** -0.5) < 1e-12
+            b["attention_multiplier"] = None
+        assert a == b, (mt, {k: (a[k], b[k]) for k in a if a[k] != b[k]})
+        again = LlamaConfig.from_hf_dict(back.to_hf_dict())
+        assert dataclasses.asdict(again) == dataclasses.asdict(back), mt
