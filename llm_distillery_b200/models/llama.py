@@ -14,449 +14,13 @@ The same code runs on CPU tensors through the PyTorch restatements in ``ops`` (f
 """
 from __future__ import annotations
 
-import json
 import math
-import os
-from dataclasses import asdict, dataclass, field
 
 import torch
 import torch.nn as nn
 
-from ..ops import basic, attention
-
-
-@dataclass
-class LlamaConfig:
-    vocab_size: int = 32000
-    hidden_size: int = 2048
-    intermediate_size: int = 5632
-    num_hidden_layers: int = 22
-    num_attention_heads: int = 32
-    num_key_value_heads: int = 4
-    rms_norm_eps: float = 1e-5
-    rope_theta: float = 10000.0
-    max_position_embeddings: int = 2048
-    tie_word_embeddings: bool = False
-    bos_token_id: int = 1
-    eos_token_id: int = 2
-    model_type: str = "llama"         # llama | mistral | qwen2 (q/k/v bias) | phi3 (fused projections in the checkpoint)
-                                      # | mixtral, qwen3_moe, qwen2_moe (sparse mixtures of experts, models/moe.py) | qwen3 | granite
-    num_local_experts: int = 0        # > 0: every layer's MLP is that many SwiGLU experts behind a linear router
-    num_experts_per_tok: int = 2
-    moe_renormalize: bool = True      # router weights renormalised over the chosen experts (Mixtral; Qwen3-MoE norm_topk_prob)
-    shared_expert_intermediate_size: int = 0   # > 0 (Qwen2-MoE): a dense SwiGLU expert of this width for every token,
-                                               # scaled by a per-token sigmoid gate, beside the routed experts
-    shared_expert_gated: bool = True           # false: the shared expert's output is added as it is (Granite MoE)
-    attention_bias: bool = False      # bias on the q/k/v projections (Qwen2 family; Llama configs with attention_bias)
-    o_bias: bool = False              # bias on o_proj as well (HuggingFace Llama's attention_bias = true, e.g. Granite code)
-    mlp_bias: bool = False            # bias on gate / up / down projections (HuggingFace Llama's mlp_bias)
-    # Granite: the embedding output, the attention scores, each branch before it joins the residual stream and the
-    # logits carry fixed multipliers
-    embedding_multiplier: float = 1.0
-    attention_multiplier: float | None = None      # replaces 1 / sqrt(head_dim)
-    residual_multiplier: float = 1.0
-    logits_scaling: float = 1.0                    # logits are DIVIDED by this
-    rope_scaling: dict | None = None  # HuggingFace dict; types default / linear / dynamic / llama3 / yarn / longrope (ops.basic.rope_tables)
-    head_dim_override: int | None = None   # HuggingFace ``head_dim`` when it is not hidden_size / num_attention_heads
-    no_rope_layers: list | None = None     # SmolLM3: one flag per layer, 1 = rotary embedding, 0 = no positional rotation
-    partial_rotary_factor: float = 1.0     # < 1: only the first int(head_dim * factor) elements of a head rotate (Phi-4-mini)
-    qk_norm: bool = False             # Qwen3: RMSNorm over every query and key head (one weight each) before RoPE
-    qk_norm_after_rope: bool = False  # HunYuan: the per-head q/k norms act on the rotated queries and keys
-    qk_norm_full: bool = False        # OLMo 2: one RMSNorm over the whole query projection, one over the key projection
-    pre_norm: bool = True             # RMSNorm on the way into the attention and MLP branches (false: OLMo 2)
-    post_norm: bool = False           # RMSNorm on the way out of both branches (OLMo 2, GLM-4 0414; models/sandwich.py)
-    rope_interleaved: bool = False    # checkpoint layout: rotary pairs are neighbours (GLM); rows are permuted at load / save
-    sliding_window: int | None = None  # attention here is full causal: sequences longer than the window are refused
-    pad_token_id: int | None = None
-    extra: dict = field(default_factory=dict)   # other keys of the source config.json, written back unchanged
-
-    @property
-    def head_dim(self) -> int:
-        return self.head_dim_override or self.hidden_size // self.num_attention_heads
-
-    @property
-    def sandwich(self) -> bool:
-        """Whether the layers take the general node of models/sandwich.py instead of the fused pre-norm layer."""
-        if self.num_local_experts and self.pre_norm and not self.post_norm and not self.qk_norm_after_rope:
-            return False         # experts: the two nodes of models/moe.py (their attention half takes either q/k norm)
-        return self.post_norm or not self.pre_norm or self.qk_norm_full or self.qk_norm_after_rope
-
-    @property
-    def rotary_dim(self) -> int:
-        return int(self.head_dim * self.partial_rotary_factor)
-
-    @property
-    def q_size(self) -> int:
-        return self.num_attention_heads * self.head_dim
-
-    @property
-    def kv_size(self) -> int:
-        return self.num_key_value_heads * self.head_dim
-
-    def num_params(self) -> int:
-        h, f, V, Lr = self.hidden_size, self.intermediate_size, self.vocab_size, self.num_hidden_layers
-        E = self.num_local_experts
-        per_layer = h * (self.q_size + 2 * self.kv_size) + self.q_size * h + 3 * h * f * max(E, 1) + E * h + 2 * h
-        if self.shared_expert_intermediate_size:
-            per_layer += 3 * h * self.shared_expert_intermediate_size + (h if self.shared_expert_gated else 0)
-        if self.attention_bias:
-            per_layer += self.q_size + 2 * self.kv_size
-        if self.qk_norm:
-            per_layer += 2 * self.head_dim
-        if self.qk_norm_full:
-            per_layer += self.q_size + self.kv_size
-        if not self.pre_norm:
-            per_layer -= 2 * h
-        if self.post_norm:
-            per_layer += 2 * h
-        if self.o_bias:
-            per_layer += h
-        if self.mlp_bias:
-            per_layer += 2 * f + h
-        return Lr * per_layer + V * h * (1 if self.tie_word_embeddings else 2) + h
-
-    def flops_per_token_fwd(self, seq_len: int) -> float:
-        h, f, V, Lr = self.hidden_size, self.intermediate_size, self.vocab_size, self.num_hidden_layers
-        mlp = 3 * h * f * (self.num_experts_per_tok if self.num_local_experts else 1) + self.num_local_experts * h
-        if self.shared_expert_intermediate_size:
-            mlp += 3 * h * self.shared_expert_intermediate_size + h
-        lin = 2 * (Lr * (h * (self.q_size + 2 * self.kv_size) + self.q_size * h + mlp) + V * h)
-        attn = Lr * 4 * self.q_size * seq_len / 2  # causal
-        return lin + attn
-
-    def to_hf_dict(self) -> dict:
-        d = asdict(self)
-        extra = d.pop("extra") or {}
-        for k in ("rope_scaling", "sliding_window", "pad_token_id"):
-            if d[k] is None:
-                d.pop(k)
-        hd = d.pop("head_dim_override")
-        if hd:
-            d["head_dim"] = hd
-        if d["partial_rotary_factor"] == 1.0:
-            d.pop("partial_rotary_factor")
-        nope = d.pop("no_rope_layers")
-        renorm = d.pop("moe_renormalize")
-        if not self.num_local_experts:
-            d.pop("num_local_experts")
-            d.pop("num_experts_per_tok")
-        qk = d.pop("qk_norm")
-        for k in ("qk_norm_full", "qk_norm_after_rope", "pre_norm", "post_norm", "rope_interleaved"):      # implied by the model type
-            d.pop(k)
-        shared_f = d.pop("shared_expert_intermediate_size")
-        d.pop("shared_expert_gated")
-        gran = {k: d.pop(k) for k in ("embedding_multiplier", "attention_multiplier", "residual_multiplier", "logits_scaling")}
-        if self.model_type == "qwen3_moe":      # HuggingFace's names: num_experts, moe_intermediate_size, norm_topk_prob
-            d.update(architectures=["Qwen3MoeForCausalLM"], hidden_act="silu", torch_dtype="bfloat16",
-                     use_sliding_window=False, head_dim=self.head_dim, num_experts=d.pop("num_local_experts"),
-                     moe_intermediate_size=self.intermediate_size, norm_topk_prob=bool(renorm), decoder_sparse_step=1,
-                     mlp_only_layers=[])
-            d["intermediate_size"] = extra.pop("dense_intermediate_size", self.intermediate_size)
-        elif self.model_type == "qwen2_moe":
-            d.pop("attention_bias")
-            d.update(architectures=["Qwen2MoeForCausalLM"], hidden_act="silu", torch_dtype="bfloat16",
-                     use_sliding_window=False, num_experts=d.pop("num_local_experts"), qkv_bias=True,
-                     moe_intermediate_size=self.intermediate_size, shared_expert_intermediate_size=shared_f,
-                     norm_topk_prob=bool(renorm), decoder_sparse_step=1, mlp_only_layers=[])
-            d["intermediate_size"] = extra.pop("dense_intermediate_size", self.intermediate_size)
-        elif self.model_type == "olmoe":
-            d.update(architectures=["OlmoeForCausalLM"], hidden_act="silu", torch_dtype="bfloat16", attention_bias=False,
-                     num_experts=d.pop("num_local_experts"), norm_topk_prob=bool(renorm), clip_qkv=None)
-        elif self.model_type == "olmo2":
-            d.update(architectures=["Olmo2ForCausalLM"], hidden_act="silu", torch_dtype="bfloat16", attention_bias=False)
-        elif self.model_type == "exaone4":
-            d.pop("attention_bias")
-            d.update(architectures=["Exaone4ForCausalLM"], hidden_act="silu", torch_dtype="bfloat16",
-                     sliding_window=self.sliding_window,
-                     layer_types=["sliding_attention" if (nope and nope[i]) else "full_attention"
-                                  for i in range(self.num_hidden_layers)])
-        elif self.model_type == "hunyuan_v1_dense":
-            d.update(architectures=["HunYuanDenseV1ForCausalLM"], hidden_act="silu", torch_dtype="bfloat16",
-                     attention_bias=False, head_dim=self.head_dim)
-        elif self.model_type == "helium":
-            d.update(architectures=["HeliumForCausalLM"], hidden_act="silu", torch_dtype="bfloat16", mlp_bias=False,
-                     head_dim=self.head_dim)
-        elif self.model_type == "ernie4_5":
-            d.pop("attention_bias")
-            d.update(architectures=["Ernie4_5ForCausalLM"], hidden_act="silu", torch_dtype="bfloat16", use_bias=False,
-                     head_dim=self.head_dim)
-        elif self.model_type == "seed_oss":
-            d.update(architectures=["SeedOssForCausalLM"], hidden_act="silu", torch_dtype="bfloat16", mlp_bias=False,
-                     attention_out_bias=False, head_dim=self.head_dim)
-        elif self.model_type in ("glm", "glm4"):
-            d.update(architectures=["GlmForCausalLM" if self.model_type == "glm" else "Glm4ForCausalLM"],
-                     hidden_act="silu", torch_dtype="bfloat16", head_dim=self.head_dim,
-                     partial_rotary_factor=self.partial_rotary_factor)
-        elif self.model_type == "smollm3":
-            d.update(architectures=["SmolLM3ForCausalLM"], hidden_act="silu", torch_dtype="bfloat16", mlp_bias=False,
-                     use_sliding_window=False, no_rope_layers=list(nope or [1] * self.num_hidden_layers))
-        elif self.model_type == "qwen3":
-            d.update(architectures=["Qwen3ForCausalLM"], hidden_act="silu", torch_dtype="bfloat16",
-                     use_sliding_window=False, head_dim=self.head_dim)
-        elif self.model_type == "mixtral":
-            d.pop("attention_bias")
-            d.update(architectures=["MixtralForCausalLM"], hidden_act="silu", torch_dtype="bfloat16")
-        elif self.model_type == "phi3":
-            d.pop("attention_bias")
-            d.update(architectures=["Phi3ForCausalLM"], hidden_act="silu", torch_dtype="bfloat16")
-        elif self.attention_bias and not self.o_bias:     # q/k/v bias without o_proj bias is the Qwen2 layout in HuggingFace terms
-            d.pop("attention_bias")
-            d.update(architectures=["Qwen2ForCausalLM"], model_type="qwen2", hidden_act="silu", torch_dtype="bfloat16",
-                     use_sliding_window=False)
-        elif self.model_type == "mistral":
-            d.pop("attention_bias")
-            d.update(architectures=["MistralForCausalLM"], hidden_act="silu", torch_dtype="bfloat16")
-        else:
-            d.update(architectures=["LlamaForCausalLM"], hidden_act="silu", torch_dtype="bfloat16",
-                     attention_bias=False, mlp_bias=False)
-        d.pop("o_bias")
-        d.pop("mlp_bias", None)
-        ob, mb = self.o_bias, self.mlp_bias
-        if ob or mb:          # HuggingFace's Llama: attention_bias covers q, k, v AND o
-            d.update(architectures=["LlamaForCausalLM"], model_type="llama", attention_bias=bool(ob), mlp_bias=bool(mb))
-        if self.model_type in ("granitemoe", "granitemoeshared"):
-            d.update(architectures=["GraniteMoeForCausalLM" if self.model_type == "granitemoe"
-                                    else "GraniteMoeSharedForCausalLM"], model_type=self.model_type,
-                     num_local_experts=self.num_local_experts, num_experts_per_tok=self.num_experts_per_tok, **gran)
-            if self.model_type == "granitemoeshared":
-                d["shared_intermediate_size"] = shared_f
-            if d.get("attention_multiplier") is None:
-                d["attention_multiplier"] = 1.0 / math.sqrt(self.head_dim)
-        if self.model_type == "granite":
-            d.update(architectures=["GraniteForCausalLM"], model_type="granite", **gran)
-            if d.get("attention_multiplier") is None:
-                d["attention_multiplier"] = 1.0 / math.sqrt(self.head_dim)
-        return {**extra, **d}
-
-    _KNOWN_TYPES = ("llama", "mistral", "qwen2", "phi3", "mixtral", "qwen3", "qwen3_moe", "qwen2_moe", "granite",
-                    "smollm3", "olmo2", "glm", "glm4", "exaone4", "helium", "ernie4_5", "seed_oss", "hunyuan_v1_dense",
-                    "olmoe", "granitemoe", "granitemoeshared")
-
-    @classmethod
-    def from_hf_dict(cls, d: dict) -> "LlamaConfig":
-        keys = {f for f in cls.__dataclass_fields__} - {"extra"}
-        kw = {k: v for k, v in d.items() if k in keys}
-        mt = d.get("model_type", "llama")
-        rp = d.get("rope_parameters")
-        if isinstance(rp, dict):       # newer HuggingFace releases write theta and the scaling keys into one dict
-            if rp.get("rope_theta") is not None and d.get("rope_theta") is None:
-                kw["rope_theta"] = float(rp["rope_theta"])
-            if rp.get("rope_type", rp.get("type")) not in (None, "default") and not d.get("rope_scaling"):
-                kw["rope_scaling"] = {k: v for k, v in rp.items() if k not in ("rope_theta", "partial_rotary_factor")}
-            if rp.get("partial_rotary_factor") is not None and d.get("partial_rotary_factor") is None:
-                kw["partial_rotary_factor"] = float(rp["partial_rotary_factor"])
-        for k in ("bos_token_id", "eos_token_id"):
-            if k in kw and kw[k] is None:
-                kw.pop(k)
-        if mt not in cls._KNOWN_TYPES:
-            raise NotImplementedError(f"model_type {mt!r}: only Llama-shaped decoders are built {cls._KNOWN_TYPES}")
-        if mt == "smollm3":          # Llama blocks; every n-th layer applies no rotary embedding
-            n_layers = int(kw.get("num_hidden_layers", 32))
-            flags = d.get("no_rope_layers")
-            if flags is None:
-                step = int(d.get("no_rope_layer_interval", 4) or 4)
-                flags = [int((i + 1) % step != 0) for i in range(n_layers)]
-            if len(flags) != n_layers:
-                raise ValueError(f"no_rope_layers lists {len(flags)} layers, the model has {n_layers}")
-            kw["no_rope_layers"] = [int(bool(v)) for v in flags]
-            if kw.get("attention_bias") or d.get("mlp_bias"):
-                raise NotImplementedError("smollm3 with projection biases is not built")
-            if not d.get("use_sliding_window", False):
-                kw["sliding_window"] = None
-        elif mt != "exaone4":
-            kw.pop("no_rope_layers", None)
-        if mt == "qwen3" and d.get("num_experts"):
-            raise NotImplementedError("experts in a config of model_type qwen3: the mixture-of-experts type is qwen3_moe")
-        dense_ffn = None
-        if mt == "qwen3_moe":
-            if int(d.get("decoder_sparse_step", 1) or 1) != 1 or d.get("mlp_only_layers"):
-                raise NotImplementedError("qwen3_moe with dense layers between the sparse ones is not built")
-            n_exp = int(d.get("num_experts") or d.get("num_local_experts") or 0)
-            if n_exp < 1 or not d.get("moe_intermediate_size"):
-                raise ValueError("a qwen3_moe config needs num_experts and moe_intermediate_size")
-            dense_ffn = d.get("intermediate_size")
-            kw.update(num_local_experts=n_exp, intermediate_size=int(d["moe_intermediate_size"]),
-                      moe_renormalize=bool(d.get("norm_topk_prob", False)), qk_norm=True)
-            if kw.get("attention_bias"):
-                raise NotImplementedError("qwen3_moe with attention_bias also puts a bias on o_proj, which is not built")
-            if not d.get("use_sliding_window", False):
-                kw["sliding_window"] = None
-        if mt == "qwen2_moe":        # Qwen2 attention (bias on q, k, v), routed experts plus a gated shared expert
-            if int(d.get("decoder_sparse_step", 1) or 1) != 1 or d.get("mlp_only_layers"):
-                raise NotImplementedError("qwen2_moe with dense layers between the sparse ones is not built")
-            n_exp = int(d.get("num_experts") or d.get("num_local_experts") or 0)
-            if n_exp < 1 or not d.get("moe_intermediate_size") or not d.get("shared_expert_intermediate_size"):
-                raise ValueError("a qwen2_moe config needs num_experts, moe_intermediate_size and "
-                                 "shared_expert_intermediate_size")
-            if not d.get("qkv_bias", True):
-                raise NotImplementedError("qwen2_moe without the q/k/v bias is not built")
-            dense_ffn = d.get("intermediate_size")
-            kw.update(num_local_experts=n_exp, intermediate_size=int(d["moe_intermediate_size"]),
-                      shared_expert_intermediate_size=int(d["shared_expert_intermediate_size"]),
-                      moe_renormalize=bool(d.get("norm_topk_prob", False)), attention_bias=True)
-            if not d.get("use_sliding_window", False):
-                kw["sliding_window"] = None
-        elif kw.get("shared_expert_intermediate_size") and mt != "granitemoeshared":
-            raise NotImplementedError(f"a shared expert on model_type {mt!r} is not built (qwen2_moe is)")
-        if mt == "mixtral":
-            if int(kw.get("num_local_experts") or 0) < 1:
-                raise ValueError("a mixtral config needs num_local_experts")
-        elif kw.get("num_local_experts") and mt not in ("qwen3_moe", "qwen2_moe", "olmoe", "granitemoe", "granitemoeshared"):
-            raise NotImplementedError(f"experts on model_type {mt!r} are not built (mixtral is)")
-        if mt == "qwen3":
-            kw["qk_norm"] = True
-            if kw.get("attention_bias"):
-                raise NotImplementedError("qwen3 with attention_bias also puts a bias on o_proj, which is not built")
-            if not d.get("use_sliding_window", False):
-                kw["sliding_window"] = None
-        for k in ("qk_norm_full", "qk_norm_after_rope", "pre_norm", "post_norm", "rope_interleaved"):      # set by the model type alone
-            kw.pop(k, None)
-        if mt in ("granitemoe", "granitemoeshared"):     # Granite's multipliers around Mixtral-style experts
-            if int(kw.get("num_local_experts") or 0) < 1:
-                raise ValueError(f"a {mt} config needs num_local_experts")
-            if kw.get("attention_bias"):
-                raise NotImplementedError(f"{mt} with attention_bias also puts a bias on o_proj, which is not built")
-            kw.update(moe_renormalize=True, shared_expert_gated=False,
-                      shared_expert_intermediate_size=int(d.get("shared_intermediate_size") or 0)
-                      if mt == "granitemoeshared" else 0)
-        if mt == "olmoe":            # Llama layers, q/k norms over the whole projections, every MLP a mixture of experts
-            n_exp = int(d.get("num_experts") or d.get("num_local_experts") or 0)
-            if n_exp < 1:
-                raise ValueError("an olmoe config needs num_experts")
-            if kw.get("attention_bias"):
-                raise NotImplementedError("olmoe with attention_bias also puts a bias on o_proj, which is not built")
-            if d.get("clip_qkv"):
-                raise NotImplementedError("olmoe with clip_qkv is not built")
-            kw.update(num_local_experts=n_exp, qk_norm_full=True, moe_renormalize=bool(d.get("norm_topk_prob", False)))
-        if mt == "hunyuan_v1_dense":         # Llama layers with per-head q/k norms behind the rotation
-            kw.update(qk_norm=True, qk_norm_after_rope=True)
-            if kw.get("attention_bias"):
-                raise NotImplementedError("hunyuan_v1_dense with attention_bias also puts a bias on o_proj, which is not built")
-        if mt == "olmo2":            # no norms in front of the branches, norms behind them, q/k norms over all heads
-            if kw.get("attention_bias"):
-                raise NotImplementedError("olmo2 with attention_bias also puts a bias on o_proj, which is not built")
-            kw.update(pre_norm=False, post_norm=True, qk_norm_full=True)
-        if mt == "exaone4":          # OLMo 2's placement of the norms with per-head q/k norms
-            kw.update(pre_norm=False, post_norm=True, qk_norm=True)
-            n_layers = int(kw.get("num_hidden_layers", 32))
-            window = d.get("sliding_window")
-            types = d.get("layer_types")
-            if types is None and window is not None:
-                pat = d.get("sliding_window_pattern", 4)
-                if isinstance(pat, str):         # e.g. "LLLG": local (windowed) and global layers in turn
-                    types = ["sliding_attention" if pat[i % len(pat)].upper() == "L" else "full_attention"
-                             for i in range(n_layers)]
-                else:
-                    types = ["sliding_attention" if (i + 1) % int(pat) else "full_attention" for i in range(n_layers)]
-            if window is not None and types and "sliding_attention" in types:
-                # hybrid checkpoints: windowed layers rotate, global layers apply no rotation; sequences up to the window
-                # are exact under full causal attention, longer ones are refused
-                kw["no_rope_layers"] = [int(t == "sliding_attention") for t in types]
-            else:
-                kw["sliding_window"] = None
-        if mt in ("helium", "ernie4_5"):     # rotary pairs are neighbours in the checkpoint
-            kw["rope_interleaved"] = True
-            if d.get("use_bias"):
-                raise NotImplementedError("ernie4_5 with use_bias puts a bias on every projection, which is not built")
-        if mt == "seed_oss":
-            if d.get("attention_out_bias"):
-                raise NotImplementedError("seed_oss with a bias on o_proj is not built")
-            kw["attention_bias"] = bool(d.get("attention_bias", True))
-        if mt in ("glm", "glm4"):    # rotary pairs are neighbours in the checkpoint; half of each head rotates
-            kw.update(rope_interleaved=True, post_norm=(mt == "glm4"),
-                      attention_bias=bool(d.get("attention_bias", True)))
-            if d.get("partial_rotary_factor") is None and not (isinstance(rp, dict) and rp.get("partial_rotary_factor")):
-                kw["partial_rotary_factor"] = 0.5
-        elif mt in ("qwen2", "qwen2_moe"):
-            kw["attention_bias"] = True
-        elif mt in ("seed_oss", "helium"):
-            pass                         # their attention_bias covers q, k and v only
-        elif kw.get("attention_bias"):
-            if mt not in ("llama", "mistral", "granite"):
-                raise NotImplementedError(f"attention_bias on model_type {mt!r} is not built")
-            kw["o_bias"] = True            # HuggingFace's Llama puts the bias on q, k, v and o
-        if d.get("mlp_bias"):
-            if mt not in ("llama", "mistral", "granite"):
-                raise NotImplementedError(f"mlp_bias on model_type {mt!r} is not built")
-            kw["mlp_bias"] = True
-        if d.get("hidden_act", "silu") not in ("silu", "swish"):
-            raise NotImplementedError(f"hidden_act {d['hidden_act']!r}: only SwiGLU (silu) is built")
-        kw["partial_rotary_factor"] = float(kw.get("partial_rotary_factor") or 1.0)
-        if not 0.0 < kw["partial_rotary_factor"] <= 1.0:
-            raise ValueError(f"partial_rotary_factor {kw['partial_rotary_factor']} is outside (0, 1]")
-        if "num_key_value_heads" not in kw or kw["num_key_value_heads"] is None:
-            kw["num_key_value_heads"] = kw.get("num_attention_heads", 32)
-        hd = d.get("head_dim")
-        if hd is not None and hd * kw.get("num_attention_heads", 32) != kw.get("hidden_size", 2048):
-            if hd % 16:
-                raise NotImplementedError(f"head_dim {hd}: the rotary and attention kernels need a multiple of 16")
-            kw["head_dim_override"] = int(hd)       # e.g. Mistral-Nemo: 5120 hidden, 32 heads of 128
-        if mt == "qwen2" and not d.get("use_sliding_window", False):
-            kw["sliding_window"] = None        # Qwen2 configs carry a window that is switched off
-        if mt not in ("granite", "granitemoe", "granitemoeshared"):
-            for k in ("embedding_multiplier", "attention_multiplier", "residual_multiplier", "logits_scaling"):
-                kw.pop(k, None)           # other families may carry such keys with another meaning
-        cfg = cls(**kw)
-        if cfg.rope_scaling is not None:       # fail at load time, not at the first forward
-            kind = cfg.rope_scaling.get("rope_type", cfg.rope_scaling.get("type"))
-            if kind == "su":                # the name older Phi-3 configs use
-                kind = "longrope"
-                cfg.rope_scaling = {**{k: v for k, v in cfg.rope_scaling.items() if k not in ("type", "rope_type")},
-                                    "rope_type": "longrope"}
-            if kind not in (None, "default", "linear", "dynamic", "llama3", "yarn", "longrope"):
-                raise NotImplementedError(f"rope_scaling type {kind!r} is not built (default, linear, dynamic, llama3, "
-                                          "yarn and longrope are)")
-            if kind == "longrope" and not cfg.rope_scaling.get("original_max_position_embeddings"):
-                orig = d.get("original_max_position_embeddings")
-                if orig:          # Phi-3 keeps it beside the dict
-                    cfg.rope_scaling = dict(cfg.rope_scaling, original_max_position_embeddings=int(orig))
-        generated = {"architectures", "hidden_act", "torch_dtype", "mlp_bias", "use_sliding_window", "head_dim",
-                     "num_experts", "moe_intermediate_size", "norm_topk_prob", "decoder_sparse_step", "mlp_only_layers",
-                     "rope_parameters"}
-        cfg.extra = {k: v for k, v in d.items() if k not in keys and k not in generated}
-        if dense_ffn is not None:
-            cfg.extra["dense_intermediate_size"] = dense_ffn
-        return cfg
-
-    @classmethod
-    def from_pretrained(cls, path: str) -> "LlamaConfig":
-        with open(os.path.join(path, "config.json"), "r", encoding="utf-8") as f:
-            return cls.from_hf_dict(json.load(f))
-
-
-PRESETS = {
-    # name: (layers, hidden, heads, kv_heads, ffn, vocab, theta, eps, tied, max_pos)
-    "tinyllama-1.1b": (22, 2048, 32, 4, 5632, 32000, 10000.0, 1e-5, False, 2048),
-    "llama-3.2-1b": (16, 2048, 32, 8, 8192, 128256, 500000.0, 1e-5, True, 131072),
-    "llama-3-8b": (32, 4096, 32, 8, 14336, 128256, 500000.0, 1e-5, False, 8192),
-    "mistral-7b": (32, 4096, 32, 8, 14336, 32000, 10000.0, 1e-5, False, 32768),
-    "llama-3-70b": (80, 8192, 64, 8, 28672, 128256, 500000.0, 1e-5, False, 8192),
-    # Qwen2 family: the same blocks with a bias on the q/k/v projections (attention_bias, set by preset())
-    "qwen2.5-0.5b": (24, 896, 14, 2, 4864, 151936, 1000000.0, 1e-6, True, 32768),
-    "qwen2.5-1.5b": (28, 1536, 12, 2, 8960, 151936, 1000000.0, 1e-6, True, 32768),
-    "qwen2.5-7b": (28, 3584, 28, 4, 18944, 152064, 1000000.0, 1e-6, False, 32768),
-    # Mixtral layout on TinyLlama's dimensions: 8 experts, 2 per token (6.4 B parameters, 1.3 B active per token)
-    "tinymixtral-8x1b": (22, 2048, 32, 4, 5632, 32000, 10000.0, 1e-5, False, 2048),
-    "plumbing-teacher": (2, 256, 4, 4, 688, 32000, 10000.0, 1e-6, False, 2048),
-    "plumbing-student": (4, 256, 4, 4, 688, 32000, 10000.0, 1e-6, False, 2048),
-}
-
-
-def preset(name: str, **over) -> LlamaConfig:
-    Lr, h, H, Hkv, f, V, theta, eps, tied, mp = PRESETS[name]
-    cfg = LlamaConfig(vocab_size=V, hidden_size=h, intermediate_size=f, num_hidden_layers=Lr, num_attention_heads=H,
-                      num_key_value_heads=Hkv, rms_norm_eps=eps, rope_theta=theta, max_position_embeddings=mp,
-                      tie_word_embeddings=tied)
-    if name.startswith("tinymixtral"):
-        cfg.model_type, cfg.num_local_experts, cfg.num_experts_per_tok = "mixtral", 8, 2
-    if name.startswith("qwen2"):
-        cfg.attention_bias, cfg.model_type = True, "qwen2"
-    if name.startswith("llama-3.2"):      # the published Llama 3.2 configs scale the low rope frequencies
-        cfg.rope_scaling = {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
-                            "original_max_position_embeddings": 8192}
-    for k, v in over.items():
-        setattr(cfg, k, v)
-    return cfg
+from ..ops import attention, basic
+from .config import PRESETS, LlamaConfig, preset  # noqa: F401  (re-exported: the models' public names live here)
 
 
 # ---------------------------------------------------------------------------------------------- gradient slots
