@@ -551,3 +551,39 @@ def test_every_model_type_survives_config_round_trips():
         assert a == b, (mt, {k: (a[k], b[k]) for k in a if a[k] != b[k]})
         again = LlamaConfig.from_hf_dict(back.to_hf_dict())
         assert dataclasses.asdict(again) == dataclasses.asdict(back), mt
+
+
+# config.json contents as published for these checkpoints (keys that matter here; long factor lists shortened)
+_PUBLISHED = {
+ "llama-3.1-8b": {"architectures":["LlamaForCausalLM"],"attention_bias":False,"attention_dropout":0.0,"bos_token_id":128000,"eos_token_id":[128001,128008,128009],"hidden_act":"silu","hidden_size":4096,"initializer_range":0.02,"intermediate_size":14336,"max_position_embeddings":131072,"mlp_bias":False,"model_type":"llama","num_attention_heads":32,"num_hidden_layers":32,"num_key_value_heads":8,"pretraining_tp":1,"rms_norm_eps":1e-05,"rope_scaling":{"factor":8.0,"low_freq_factor":1.0,"high_freq_factor":4.0,"original_max_position_embeddings":8192,"rope_type":"llama3"},"rope_theta":500000.0,"tie_word_embeddings":False,"torch_dtype":"bfloat16","use_cache":True,"vocab_size":128256},
+ "qwen2.5-7b": {"architectures":["Qwen2ForCausalLM"],"attention_dropout":0.0,"bos_token_id":151643,"eos_token_id":151645,"hidden_act":"silu","hidden_size":3584,"initializer_range":0.02,"intermediate_size":18944,"max_position_embeddings":32768,"max_window_layers":28,"model_type":"qwen2","num_attention_heads":28,"num_hidden_layers":28,"num_key_value_heads":4,"rms_norm_eps":1e-06,"rope_theta":1000000.0,"sliding_window":131072,"tie_word_embeddings":False,"torch_dtype":"bfloat16","use_cache":True,"use_sliding_window":False,"vocab_size":152064},
+ "qwen3-8b": {"architectures":["Qwen3ForCausalLM"],"attention_bias":False,"attention_dropout":0.0,"head_dim":128,"hidden_act":"silu","hidden_size":4096,"intermediate_size":12288,"max_position_embeddings":40960,"max_window_layers":36,"model_type":"qwen3","num_attention_heads":32,"num_hidden_layers":36,"num_key_value_heads":8,"rms_norm_eps":1e-06,"rope_scaling":None,"rope_theta":1000000,"sliding_window":None,"tie_word_embeddings":False,"use_sliding_window":False,"vocab_size":151936},
+ "mistral-7b-v0.1": {"architectures":["MistralForCausalLM"],"bos_token_id":1,"eos_token_id":2,"hidden_act":"silu","hidden_size":4096,"initializer_range":0.02,"intermediate_size":14336,"max_position_embeddings":32768,"model_type":"mistral","num_attention_heads":32,"num_hidden_layers":32,"num_key_value_heads":8,"rms_norm_eps":1e-05,"rope_theta":10000.0,"sliding_window":4096,"tie_word_embeddings":False,"vocab_size":32000},
+ "mistral-nemo": {"architectures":["MistralForCausalLM"],"head_dim":128,"hidden_act":"silu","hidden_size":5120,"intermediate_size":14336,"max_position_embeddings":1024000,"model_type":"mistral","num_attention_heads":32,"num_hidden_layers":40,"num_key_value_heads":8,"rms_norm_eps":1e-05,"rope_theta":1000000.0,"sliding_window":None,"vocab_size":131072},
+ "phi-4-mini": {"architectures":["Phi3ForCausalLM"],"attention_bias":False,"bos_token_id":199999,"embd_pdrop":0.0,"eos_token_id":199999,"full_attn_mod":1,"hidden_act":"silu","hidden_size":3072,"intermediate_size":8192,"interpolate_factor":1,"lm_head_bias":False,"max_position_embeddings":131072,"mlp_bias":False,"model_type":"phi3","num_attention_heads":24,"num_hidden_layers":32,"num_key_value_heads":8,"original_max_position_embeddings":4096,"pad_token_id":199999,"partial_rotary_factor":0.75,"resid_pdrop":0.0,"rms_norm_eps":1e-05,"rope_scaling":{"long_factor":[1.0]*48,"short_factor":[1.0]*48,"type":"longrope"},"rope_theta":10000.0,"sliding_window":262144,"tie_word_embeddings":True,"vocab_size":200064},
+ "mixtral-8x7b": {"architectures":["MixtralForCausalLM"],"hidden_act":"silu","hidden_size":4096,"intermediate_size":14336,"max_position_embeddings":32768,"model_type":"mixtral","num_attention_heads":32,"num_experts_per_tok":2,"num_hidden_layers":32,"num_key_value_heads":8,"num_local_experts":8,"output_router_logits":False,"rms_norm_eps":1e-05,"rope_theta":1000000.0,"router_aux_loss_coef":0.02,"sliding_window":None,"vocab_size":32000},
+ "olmo2-7b": {"architectures":["Olmo2ForCausalLM"],"attention_bias":False,"hidden_act":"silu","hidden_size":4096,"intermediate_size":11008,"max_position_embeddings":4096,"model_type":"olmo2","num_attention_heads":32,"num_hidden_layers":32,"num_key_value_heads":32,"rms_norm_eps":1e-06,"rope_scaling":None,"rope_theta":500000,"tie_word_embeddings":False,"vocab_size":100352},
+ "glm-4-9b-chat-hf": {"architectures":["GlmForCausalLM"],"attention_bias":True,"head_dim":128,"hidden_act":"silu","hidden_size":4096,"intermediate_size":13696,"max_position_embeddings":131072,"model_type":"glm","num_attention_heads":32,"num_hidden_layers":40,"num_key_value_heads":2,"partial_rotary_factor":0.5,"rms_norm_eps":1.5625e-07,"rope_theta":10000.0,"tie_word_embeddings":False,"vocab_size":151552},
+ "smollm3-3b": {"architectures":["SmolLM3ForCausalLM"],"attention_bias":False,"hidden_act":"silu","hidden_size":2048,"intermediate_size":11008,"max_position_embeddings":65536,"mlp_bias":False,"model_type":"smollm3","no_rope_layer_interval":4,"no_rope_layers":[1,1,1,0]*9,"num_attention_heads":16,"num_hidden_layers":36,"num_key_value_heads":4,"rms_norm_eps":1e-06,"rope_scaling":None,"rope_theta":5000000.0,"sliding_window":None,"use_sliding_window":False,"tie_word_embeddings":True,"vocab_size":128256},
+ "granite-3.1-1b-a400m": {"architectures":["GraniteMoeForCausalLM"],"attention_bias":False,"attention_multiplier":0.015625,"embedding_multiplier":12.0,"hidden_act":"silu","hidden_size":1024,"intermediate_size":512,"logits_scaling":6.0,"max_position_embeddings":131072,"model_type":"granitemoe","num_attention_heads":16,"num_experts_per_tok":8,"num_hidden_layers":24,"num_key_value_heads":8,"num_local_experts":32,"output_router_logits":False,"residual_multiplier":0.22,"rms_norm_eps":1e-06,"rope_scaling":None,"rope_theta":10000000.0,"router_aux_loss_coef":0.0,"tie_word_embeddings":True,"vocab_size":49155},
+ "gemma-2": {"model_type":"gemma2","hidden_size":2304},
+}
+
+
+def test_published_configs_parse_to_the_published_sizes():
+    want = {"llama-3.1-8b": 8.03, "qwen2.5-7b": 7.62, "qwen3-8b": 8.19, "mistral-7b-v0.1": 7.24, "mistral-nemo": 12.25,
+            "phi-4-mini": 3.84, "mixtral-8x7b": 46.70, "olmo2-7b": 7.30, "glm-4-9b-chat-hf": 9.40, "smollm3-3b": 3.08,
+            "granite-3.1-1b-a400m": 1.33}
+    for name, d in _PUBLISHED.items():
+        if name not in want:
+            with pytest.raises(NotImplementedError, match="model_type"):
+                LlamaConfig.from_hf_dict(d)
+            continue
+        cfg = LlamaConfig.from_hf_dict(d)
+        assert abs(cfg.num_params() / 1e9 - want[name]) < 0.006, (name, cfg.num_params())
+        assert cfg.head_dim in (64, 128) and cfg.rotary_dim % 16 == 0, name       # what the GPU kernels take
+        assert LlamaConfig.from_hf_dict(cfg.to_hf_dict()).num_params() == cfg.num_params()
+    assert LlamaConfig.from_hf_dict(_PUBLISHED["phi-4-mini"]).rotary_dim == 96
+    assert LlamaConfig.from_hf_dict(_PUBLISHED["mistral-7b-v0.1"]).sliding_window == 4096
+    assert LlamaConfig.from_hf_dict(_PUBLISHED["qwen2.5-7b"]).sliding_window is None
+    assert LlamaConfig.from_hf_dict(_PUBLISHED["smollm3-3b"]).no_rope_layers.count(0) == 9
