@@ -65,6 +65,20 @@ class LlamaConfig:
     def head_dim(self) -> int:
         return self.head_dim_override or self.hidden_size // self.num_attention_heads
 
+    def check_gpu_kernels(self) -> None:
+        """Raises when a shape is outside what the sm_100a kernels take, in words, before any kernel is launched."""
+        problems = []
+        if self.head_dim not in (64, 128):
+            problems.append(f"head_dim {self.head_dim}: the flash-attention kernels take 64 and 128")
+        if self.rotary_dim % 16:
+            problems.append(f"rotary width {self.rotary_dim}: the rotary kernel moves 16-byte vectors (a multiple of 16)")
+        for name, v in (("hidden_size", self.hidden_size), ("intermediate_size", self.intermediate_size),
+                        ("shared_expert_intermediate_size", self.shared_expert_intermediate_size)):
+            if v % 8:
+                problems.append(f"{name} {v}: rows of the GEMM operands must be multiples of 16 bytes (8 elements)")
+        if problems:
+            raise NotImplementedError("this model does not fit the GPU kernels - " + "; ".join(problems))
+
     @property
     def sandwich(self) -> bool:
         """Whether the layers take the general node of models/sandwich.py instead of the fused pre-norm layer."""

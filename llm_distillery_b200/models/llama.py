@@ -344,6 +344,8 @@ class LlamaModel(nn.Module):
     def __init__(self, cfg: LlamaConfig, dtype=torch.bfloat16, device="cpu"):
         super().__init__()
         self.cfg = cfg
+        if torch.device(device).type == "cuda":
+            cfg.check_gpu_kernels()
         kw = dict(dtype=dtype, device=device)
         self.embed_tokens = nn.Parameter(torch.empty(cfg.vocab_size, cfg.hidden_size, **kw))
         self.layers = nn.ModuleList([LlamaDecoderLayer(cfg, dtype, device) for _ in range(cfg.num_hidden_layers)])

@@ -587,3 +587,12 @@ def test_published_configs_parse_to_the_published_sizes():
     assert LlamaConfig.from_hf_dict(_PUBLISHED["mistral-7b-v0.1"]).sliding_window == 4096
     assert LlamaConfig.from_hf_dict(_PUBLISHED["qwen2.5-7b"]).sliding_window is None
     assert LlamaConfig.from_hf_dict(_PUBLISHED["smollm3-3b"]).no_rope_layers.count(0) == 9
+
+
+def test_shapes_outside_the_gpu_kernels_are_named_before_any_launch():
+    LlamaConfig(**_base(hidden_size=256, num_attention_heads=4)).check_gpu_kernels()                  # head_dim 64
+    LlamaConfig(**_base(hidden_size=256, num_attention_heads=2, partial_rotary_factor=0.75)).check_gpu_kernels()
+    with pytest.raises(NotImplementedError, match="head_dim 16.*rotary width 8"):
+        LlamaConfig(**_base(partial_rotary_factor=0.5)).check_gpu_kernels()
+    with pytest.raises(NotImplementedError, match="intermediate_size 100"):
+        LlamaConfig(**_base(hidden_size=256, num_attention_heads=4, intermediate_size=100)).check_gpu_kernels()
