@@ -275,11 +275,11 @@ def main() -> int:
         with torch.no_grad():
             runner.collect_topk = K
             runner.collect_setup()
-            for i in range(2):
+            for i in range(4):          # pinned buffers, the copy stream and the top-K workspace are first touched here
                 runner.collect_step(toks[i % 2], convos)
             barrier()
             t0 = time.perf_counter()
-            n_col = max(3, args.steps // 2)
+            n_col = max(8, args.steps // 2)
             d2h = 0
             if hasattr(runner, "collect_many"):
                 hv, hi, _ = runner.collect_many(toks, convos, n_col)
