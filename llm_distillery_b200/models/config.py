@@ -236,6 +236,14 @@ class LlamaConfig:
     _KNOWN_TYPES = ("llama", "mistral", "qwen2", "phi3", "mixtral", "qwen3", "qwen3_moe", "qwen2_moe", "granite",
                     "smollm3", "olmo2", "glm", "glm4", "exaone4", "helium", "ernie4_5", "seed_oss", "hunyuan_v1_dense",
                     "olmoe", "granitemoe", "granitemoeshared")
+    # what HuggingFace's attention_bias puts a bias on, per family: q, k and v only / the o projection as well (built for
+    # the second group, refused for every other family); families whose MLP may carry biases; families with experts
+    _QKV_BIAS_TYPES = ("qwen2", "qwen2_moe", "glm", "glm4", "seed_oss", "helium")
+    _QKVO_BIAS_TYPES = ("llama", "mistral", "granite")
+    _MLP_BIAS_TYPES = ("llama", "mistral", "granite")
+    _EXPERT_TYPES = ("mixtral", "qwen3_moe", "qwen2_moe", "olmoe", "granitemoe", "granitemoeshared")
+    _MULTIPLIER_TYPES = ("granite", "granitemoe", "granitemoeshared")
+    _SWITCHES = ("qk_norm_full", "qk_norm_after_rope", "pre_norm", "post_norm", "rope_interleaved")   # set by the type alone
 
     @classmethod
     def from_hf_dict(cls, d: dict) -> "LlamaConfig":
@@ -255,137 +263,38 @@ class LlamaConfig:
                 kw.pop(k)
         if mt not in cls._KNOWN_TYPES:
             raise NotImplementedError(f"model_type {mt!r}: only Llama-shaped decoders are built {cls._KNOWN_TYPES}")
-        if mt == "smollm3":          # Llama blocks; every n-th layer applies no rotary embedding
-            n_layers = int(kw.get("num_hidden_layers", 32))
-            flags = d.get("no_rope_layers")
-            if flags is None:
-                step = int(d.get("no_rope_layer_interval", 4) or 4)
-                flags = [int((i + 1) % step != 0) for i in range(n_layers)]
-            if len(flags) != n_layers:
-                raise ValueError(f"no_rope_layers lists {len(flags)} layers, the model has {n_layers}")
-            kw["no_rope_layers"] = [int(bool(v)) for v in flags]
-            if kw.get("attention_bias") or d.get("mlp_bias"):
-                raise NotImplementedError("smollm3 with projection biases is not built")
-            if not d.get("use_sliding_window", False):
-                kw["sliding_window"] = None
-        elif mt != "exaone4":
+        # keys that only some families may carry
+        for k in cls._SWITCHES:
+            kw.pop(k, None)
+        if mt not in ("smollm3", "exaone4"):
             kw.pop("no_rope_layers", None)
+        if kw.get("shared_expert_intermediate_size") and mt != "qwen2_moe":
+            raise NotImplementedError(f"a shared expert on model_type {mt!r} is not built (qwen2_moe is)")
         if mt == "qwen3" and d.get("num_experts"):
             raise NotImplementedError("experts in a config of model_type qwen3: the mixture-of-experts type is qwen3_moe")
-        dense_ffn = None
-        if mt == "qwen3_moe":
-            if int(d.get("decoder_sparse_step", 1) or 1) != 1 or d.get("mlp_only_layers"):
-                raise NotImplementedError("qwen3_moe with dense layers between the sparse ones is not built")
-            n_exp = int(d.get("num_experts") or d.get("num_local_experts") or 0)
-            if n_exp < 1 or not d.get("moe_intermediate_size"):
-                raise ValueError("a qwen3_moe config needs num_experts and moe_intermediate_size")
-            dense_ffn = d.get("intermediate_size")
-            kw.update(num_local_experts=n_exp, intermediate_size=int(d["moe_intermediate_size"]),
-                      moe_renormalize=bool(d.get("norm_topk_prob", False)), qk_norm=True)
-            if kw.get("attention_bias"):
-                raise NotImplementedError("qwen3_moe with attention_bias also puts a bias on o_proj, which is not built")
-            if not d.get("use_sliding_window", False):
-                kw["sliding_window"] = None
-        if mt == "qwen2_moe":        # Qwen2 attention (bias on q, k, v), routed experts plus a gated shared expert
-            if int(d.get("decoder_sparse_step", 1) or 1) != 1 or d.get("mlp_only_layers"):
-                raise NotImplementedError("qwen2_moe with dense layers between the sparse ones is not built")
-            n_exp = int(d.get("num_experts") or d.get("num_local_experts") or 0)
-            if n_exp < 1 or not d.get("moe_intermediate_size") or not d.get("shared_expert_intermediate_size"):
-                raise ValueError("a qwen2_moe config needs num_experts, moe_intermediate_size and "
-                                 "shared_expert_intermediate_size")
-            if not d.get("qkv_bias", True):
-                raise NotImplementedError("qwen2_moe without the q/k/v bias is not built")
-            dense_ffn = d.get("intermediate_size")
-            kw.update(num_local_experts=n_exp, intermediate_size=int(d["moe_intermediate_size"]),
-                      shared_expert_intermediate_size=int(d["shared_expert_intermediate_size"]),
-                      moe_renormalize=bool(d.get("norm_topk_prob", False)), attention_bias=True)
-            if not d.get("use_sliding_window", False):
-                kw["sliding_window"] = None
-        elif kw.get("shared_expert_intermediate_size") and mt != "granitemoeshared":
-            raise NotImplementedError(f"a shared expert on model_type {mt!r} is not built (qwen2_moe is)")
-        if mt == "mixtral":
-            if int(kw.get("num_local_experts") or 0) < 1:
-                raise ValueError("a mixtral config needs num_local_experts")
-        elif kw.get("num_local_experts") and mt not in ("qwen3_moe", "qwen2_moe", "olmoe", "granitemoe", "granitemoeshared"):
+        if kw.get("num_local_experts") and mt not in cls._EXPERT_TYPES:
             raise NotImplementedError(f"experts on model_type {mt!r} are not built (mixtral is)")
-        if mt == "qwen3":
-            kw["qk_norm"] = True
-            if kw.get("attention_bias"):
-                raise NotImplementedError("qwen3 with attention_bias also puts a bias on o_proj, which is not built")
-            if not d.get("use_sliding_window", False):
-                kw["sliding_window"] = None
-        for k in ("qk_norm_full", "qk_norm_after_rope", "pre_norm", "post_norm", "rope_interleaved"):      # set by the model type alone
-            kw.pop(k, None)
-        if mt in ("granitemoe", "granitemoeshared"):     # Granite's multipliers around Mixtral-style experts
-            if int(kw.get("num_local_experts") or 0) < 1:
-                raise ValueError(f"a {mt} config needs num_local_experts")
-            if kw.get("attention_bias"):
-                raise NotImplementedError(f"{mt} with attention_bias also puts a bias on o_proj, which is not built")
-            kw.update(moe_renormalize=True, shared_expert_gated=False,
-                      shared_expert_intermediate_size=int(d.get("shared_intermediate_size") or 0)
-                      if mt == "granitemoeshared" else 0)
-        if mt == "olmoe":            # Llama layers, q/k norms over the whole projections, every MLP a mixture of experts
-            n_exp = int(d.get("num_experts") or d.get("num_local_experts") or 0)
-            if n_exp < 1:
-                raise ValueError("an olmoe config needs num_experts")
-            if kw.get("attention_bias"):
-                raise NotImplementedError("olmoe with attention_bias also puts a bias on o_proj, which is not built")
-            if d.get("clip_qkv"):
-                raise NotImplementedError("olmoe with clip_qkv is not built")
-            kw.update(num_local_experts=n_exp, qk_norm_full=True, moe_renormalize=bool(d.get("norm_topk_prob", False)))
-        if mt == "hunyuan_v1_dense":         # Llama layers with per-head q/k norms behind the rotation
-            kw.update(qk_norm=True, qk_norm_after_rope=True)
-            if kw.get("attention_bias"):
-                raise NotImplementedError("hunyuan_v1_dense with attention_bias also puts a bias on o_proj, which is not built")
-        if mt == "olmo2":            # no norms in front of the branches, norms behind them, q/k norms over all heads
-            if kw.get("attention_bias"):
-                raise NotImplementedError("olmo2 with attention_bias also puts a bias on o_proj, which is not built")
-            kw.update(pre_norm=False, post_norm=True, qk_norm_full=True)
-        if mt == "exaone4":          # OLMo 2's placement of the norms with per-head q/k norms
-            kw.update(pre_norm=False, post_norm=True, qk_norm=True)
-            n_layers = int(kw.get("num_hidden_layers", 32))
-            window = d.get("sliding_window")
-            types = d.get("layer_types")
-            if types is None and window is not None:
-                pat = d.get("sliding_window_pattern", 4)
-                if isinstance(pat, str):         # e.g. "LLLG": local (windowed) and global layers in turn
-                    types = ["sliding_attention" if pat[i % len(pat)].upper() == "L" else "full_attention"
-                             for i in range(n_layers)]
-                else:
-                    types = ["sliding_attention" if (i + 1) % int(pat) else "full_attention" for i in range(n_layers)]
-            if window is not None and types and "sliding_attention" in types:
-                # hybrid checkpoints: windowed layers rotate, global layers apply no rotation; sequences up to the window
-                # are exact under full causal attention, longer ones are refused
-                kw["no_rope_layers"] = [int(t == "sliding_attention") for t in types]
-            else:
-                kw["sliding_window"] = None
-        if mt in ("helium", "ernie4_5"):     # rotary pairs are neighbours in the checkpoint
-            kw["rope_interleaved"] = True
-            if d.get("use_bias"):
-                raise NotImplementedError("ernie4_5 with use_bias puts a bias on every projection, which is not built")
-        if mt == "seed_oss":
-            if d.get("attention_out_bias"):
-                raise NotImplementedError("seed_oss with a bias on o_proj is not built")
-            kw["attention_bias"] = bool(d.get("attention_bias", True))
-        if mt in ("glm", "glm4"):    # rotary pairs are neighbours in the checkpoint; half of each head rotates
-            kw.update(rope_interleaved=True, post_norm=(mt == "glm4"),
-                      attention_bias=bool(d.get("attention_bias", True)))
-            if d.get("partial_rotary_factor") is None and not (isinstance(rp, dict) and rp.get("partial_rotary_factor")):
-                kw["partial_rotary_factor"] = 0.5
-        elif mt in ("qwen2", "qwen2_moe"):
-            kw["attention_bias"] = True
-        elif mt in ("seed_oss", "helium"):
-            pass                         # their attention_bias covers q, k and v only
+        if mt not in cls._MULTIPLIER_TYPES:
+            for k in ("embedding_multiplier", "attention_multiplier", "residual_multiplier", "logits_scaling"):
+                kw.pop(k, None)           # other families may carry such keys with another meaning
+        # the family's own keys and switches
+        reader = _FAMILY_READERS.get(mt)
+        if reader is not None:
+            reader(mt, d, kw)
+        # biases
+        if mt in cls._QKV_BIAS_TYPES:
+            pass                           # the family's reader has set attention_bias: q, k and v only
         elif kw.get("attention_bias"):
-            if mt not in ("llama", "mistral", "granite"):
-                raise NotImplementedError(f"attention_bias on model_type {mt!r} is not built")
+            if mt not in cls._QKVO_BIAS_TYPES:
+                raise NotImplementedError(f"{mt} with attention_bias also puts a bias on o_proj, which is not built")
             kw["o_bias"] = True            # HuggingFace's Llama puts the bias on q, k, v and o
         if d.get("mlp_bias"):
-            if mt not in ("llama", "mistral", "granite"):
+            if mt not in cls._MLP_BIAS_TYPES:
                 raise NotImplementedError(f"mlp_bias on model_type {mt!r} is not built")
             kw["mlp_bias"] = True
         if d.get("hidden_act", "silu") not in ("silu", "swish"):
             raise NotImplementedError(f"hidden_act {d['hidden_act']!r}: only SwiGLU (silu) is built")
+        # heads
         kw["partial_rotary_factor"] = float(kw.get("partial_rotary_factor") or 1.0)
         if not 0.0 < kw["partial_rotary_factor"] <= 1.0:
             raise ValueError(f"partial_rotary_factor {kw['partial_rotary_factor']} is outside (0, 1]")
@@ -396,11 +305,7 @@ class LlamaConfig:
             if hd % 16:
                 raise NotImplementedError(f"head_dim {hd}: the rotary and attention kernels need a multiple of 16")
             kw["head_dim_override"] = int(hd)       # e.g. Mistral-Nemo: 5120 hidden, 32 heads of 128
-        if mt == "qwen2" and not d.get("use_sliding_window", False):
-            kw["sliding_window"] = None        # Qwen2 configs carry a window that is switched off
-        if mt not in ("granite", "granitemoe", "granitemoeshared"):
-            for k in ("embedding_multiplier", "attention_multiplier", "residual_multiplier", "logits_scaling"):
-                kw.pop(k, None)           # other families may carry such keys with another meaning
+        dense_ffn = kw.pop("_dense_intermediate_size", None)
         cfg = cls(**kw)
         if cfg.rope_scaling is not None:       # fail at load time, not at the first forward
             kind = cfg.rope_scaling.get("rope_type", cfg.rope_scaling.get("type"))
@@ -427,6 +332,140 @@ class LlamaConfig:
     def from_pretrained(cls, path: str) -> "LlamaConfig":
         with open(os.path.join(path, "config.json"), "r", encoding="utf-8") as f:
             return cls.from_hf_dict(json.load(f))
+
+
+# ---------------------------------------------------------------------------------------------- per-family readers
+# Each takes (model_type, the config.json dict, the keyword arguments collected so far) and sets the family's switches.
+def _window_off_unless_used(d: dict, kw: dict) -> None:
+    if not d.get("use_sliding_window", False):
+        kw["sliding_window"] = None        # Qwen-style configs carry a window that is switched off
+
+
+def _every_layer_sparse(mt: str, d: dict) -> None:
+    if int(d.get("decoder_sparse_step", 1) or 1) != 1 or d.get("mlp_only_layers"):
+        raise NotImplementedError(f"{mt} with dense layers between the sparse ones is not built")
+
+
+def _read_qwen2(mt, d, kw):
+    kw["attention_bias"] = True
+    _window_off_unless_used(d, kw)
+
+
+def _read_qwen3(mt, d, kw):
+    kw["qk_norm"] = True
+    _window_off_unless_used(d, kw)
+
+
+def _read_qwen3_moe(mt, d, kw):
+    _every_layer_sparse(mt, d)
+    n_exp = int(d.get("num_experts") or d.get("num_local_experts") or 0)
+    if n_exp < 1 or not d.get("moe_intermediate_size"):
+        raise ValueError("a qwen3_moe config needs num_experts and moe_intermediate_size")
+    kw.update(num_local_experts=n_exp, intermediate_size=int(d["moe_intermediate_size"]),
+              moe_renormalize=bool(d.get("norm_topk_prob", False)), qk_norm=True,
+              _dense_intermediate_size=d.get("intermediate_size"))
+    _window_off_unless_used(d, kw)
+
+
+def _read_qwen2_moe(mt, d, kw):        # Qwen2 attention (bias on q, k, v), routed experts plus a gated shared expert
+    _every_layer_sparse(mt, d)
+    n_exp = int(d.get("num_experts") or d.get("num_local_experts") or 0)
+    if n_exp < 1 or not d.get("moe_intermediate_size") or not d.get("shared_expert_intermediate_size"):
+        raise ValueError("a qwen2_moe config needs num_experts, moe_intermediate_size and shared_expert_intermediate_size")
+    if not d.get("qkv_bias", True):
+        raise NotImplementedError("qwen2_moe without the q/k/v bias is not built")
+    kw.update(num_local_experts=n_exp, intermediate_size=int(d["moe_intermediate_size"]),
+              shared_expert_intermediate_size=int(d["shared_expert_intermediate_size"]),
+              moe_renormalize=bool(d.get("norm_topk_prob", False)), attention_bias=True,
+              _dense_intermediate_size=d.get("intermediate_size"))
+    _window_off_unless_used(d, kw)
+
+
+def _read_mixtral(mt, d, kw):
+    if int(kw.get("num_local_experts") or 0) < 1:
+        raise ValueError(f"a {mt} config needs num_local_experts")
+
+
+def _read_granite_moe(mt, d, kw):      # Granite's multipliers around Mixtral-style experts
+    _read_mixtral(mt, d, kw)
+    kw.update(moe_renormalize=True, shared_expert_gated=False,
+              shared_expert_intermediate_size=int(d.get("shared_intermediate_size") or 0) if mt == "granitemoeshared" else 0)
+
+
+def _read_olmoe(mt, d, kw):            # Llama layers, q/k norms over the whole projections, every MLP a mixture of experts
+    n_exp = int(d.get("num_experts") or d.get("num_local_experts") or 0)
+    if n_exp < 1:
+        raise ValueError("an olmoe config needs num_experts")
+    if d.get("clip_qkv"):
+        raise NotImplementedError("olmoe with clip_qkv is not built")
+    kw.update(num_local_experts=n_exp, qk_norm_full=True, moe_renormalize=bool(d.get("norm_topk_prob", False)))
+
+
+def _read_smollm3(mt, d, kw):          # Llama blocks; every n-th layer applies no rotary embedding
+    n_layers = int(kw.get("num_hidden_layers", 32))
+    flags = d.get("no_rope_layers")
+    if flags is None:
+        step = int(d.get("no_rope_layer_interval", 4) or 4)
+        flags = [int((i + 1) % step != 0) for i in range(n_layers)]
+    if len(flags) != n_layers:
+        raise ValueError(f"no_rope_layers lists {len(flags)} layers, the model has {n_layers}")
+    kw["no_rope_layers"] = [int(bool(v)) for v in flags]
+    _window_off_unless_used(d, kw)
+
+
+def _read_olmo2(mt, d, kw):            # no norms in front of the branches, norms behind them, q/k norms over all heads
+    kw.update(pre_norm=False, post_norm=True, qk_norm_full=True)
+
+
+def _read_exaone4(mt, d, kw):          # OLMo 2's placement of the norms with per-head q/k norms
+    kw.update(pre_norm=False, post_norm=True, qk_norm=True)
+    n_layers = int(kw.get("num_hidden_layers", 32))
+    window = d.get("sliding_window")
+    types = d.get("layer_types")
+    if types is None and window is not None:
+        pat = d.get("sliding_window_pattern", 4)
+        if isinstance(pat, str):         # e.g. "LLLG": local (windowed) and global layers in turn
+            types = ["sliding_attention" if pat[i % len(pat)].upper() == "L" else "full_attention" for i in range(n_layers)]
+        else:
+            types = ["sliding_attention" if (i + 1) % int(pat) else "full_attention" for i in range(n_layers)]
+    if window is not None and types and "sliding_attention" in types:
+        # hybrid checkpoints: windowed layers rotate, global layers apply no rotation; sequences up to the window are
+        # exact under full causal attention, longer ones are refused
+        kw["no_rope_layers"] = [int(t == "sliding_attention") for t in types]
+    else:
+        kw["sliding_window"] = None
+        kw.pop("no_rope_layers", None)
+
+
+def _read_interleaved(mt, d, kw):      # Helium, ERNIE 4.5: rotary pairs are neighbours in the checkpoint
+    kw["rope_interleaved"] = True
+    if d.get("use_bias"):
+        raise NotImplementedError("ernie4_5 with use_bias puts a bias on every projection, which is not built")
+
+
+def _read_seed_oss(mt, d, kw):
+    if d.get("attention_out_bias"):
+        raise NotImplementedError("seed_oss with a bias on o_proj is not built")
+    kw["attention_bias"] = bool(d.get("attention_bias", True))
+
+
+def _read_glm(mt, d, kw):              # rotary pairs are neighbours in the checkpoint; half of each head rotates
+    kw.update(rope_interleaved=True, post_norm=(mt == "glm4"), attention_bias=bool(d.get("attention_bias", True)))
+    if kw.get("partial_rotary_factor") is None:
+        kw["partial_rotary_factor"] = 0.5
+
+
+def _read_hunyuan(mt, d, kw):          # Llama layers with per-head q/k norms behind the rotation
+    kw.update(qk_norm=True, qk_norm_after_rope=True)
+
+
+_FAMILY_READERS = {
+    "qwen2": _read_qwen2, "qwen3": _read_qwen3, "qwen3_moe": _read_qwen3_moe, "qwen2_moe": _read_qwen2_moe,
+    "mixtral": _read_mixtral, "granitemoe": _read_granite_moe, "granitemoeshared": _read_granite_moe,
+    "olmoe": _read_olmoe, "smollm3": _read_smollm3, "olmo2": _read_olmo2, "exaone4": _read_exaone4,
+    "helium": _read_interleaved, "ernie4_5": _read_interleaved, "seed_oss": _read_seed_oss, "glm": _read_glm,
+    "glm4": _read_glm, "hunyuan_v1_dense": _read_hunyuan,
+}
 
 
 PRESETS = {
