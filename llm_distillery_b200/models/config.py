@@ -57,13 +57,22 @@ class LlamaConfig:
     pre_norm: bool = True             # RMSNorm on the way into the attention and MLP branches (false: OLMo 2)
     post_norm: bool = False           # RMSNorm on the way out of both branches (OLMo 2, GLM-4 0414; models/sandwich.py)
     rope_interleaved: bool = False    # checkpoint layout: rotary pairs are neighbours (GLM); rows are permuted at load / save
-    sliding_window: int | None = None  # attention here is full causal: sequences longer than the window are refused
+    sliding_window: int | None = None  # a query sees the last ``sliding_window`` positions; matters for longer sequences only
+    window_layers: list | None = None  # one flag per layer, 1 = windowed; None: every layer (when sliding_window is set)
     pad_token_id: int | None = None
     extra: dict = field(default_factory=dict)   # other keys of the source config.json, written back unchanged
 
     @property
     def head_dim(self) -> int:
         return self.head_dim_override or self.hidden_size // self.num_attention_heads
+
+    def layer_window(self, layer: int, seq_len: int) -> int | None:
+        """The sliding window that layer's attention must apply to sequences of ``seq_len``, or None when plain causal
+        attention is exact (no window, a layer that attends to everything, a sequence inside the window)."""
+        w = self.sliding_window
+        if not w or seq_len <= w or (self.window_layers is not None and not self.window_layers[layer]):
+            return None
+        return int(w)
 
     def check_gpu_kernels(self) -> None:
         """Raises when a shape is outside what the sm_100a kernels take, in words, before any kernel is launched."""
@@ -141,6 +150,7 @@ class LlamaConfig:
         if d["partial_rotary_factor"] == 1.0:
             d.pop("partial_rotary_factor")
         nope = d.pop("no_rope_layers")
+        win_layers = d.pop("window_layers")
         renorm = d.pop("moe_renormalize")
         if not self.num_local_experts:
             d.pop("num_local_experts")
@@ -153,14 +163,14 @@ class LlamaConfig:
         gran = {k: d.pop(k) for k in ("embedding_multiplier", "attention_multiplier", "residual_multiplier", "logits_scaling")}
         if self.model_type == "qwen3_moe":      # HuggingFace's names: num_experts, moe_intermediate_size, norm_topk_prob
             d.update(architectures=["Qwen3MoeForCausalLM"], hidden_act="silu", torch_dtype="bfloat16",
-                     use_sliding_window=False, head_dim=self.head_dim, num_experts=d.pop("num_local_experts"),
+                     use_sliding_window=self.sliding_window is not None, head_dim=self.head_dim, num_experts=d.pop("num_local_experts"),
                      moe_intermediate_size=self.intermediate_size, norm_topk_prob=bool(renorm), decoder_sparse_step=1,
                      mlp_only_layers=[])
             d["intermediate_size"] = extra.pop("dense_intermediate_size", self.intermediate_size)
         elif self.model_type == "qwen2_moe":
             d.pop("attention_bias")
             d.update(architectures=["Qwen2MoeForCausalLM"], hidden_act="silu", torch_dtype="bfloat16",
-                     use_sliding_window=False, num_experts=d.pop("num_local_experts"), qkv_bias=True,
+                     use_sliding_window=self.sliding_window is not None, num_experts=d.pop("num_local_experts"), qkv_bias=True,
                      moe_intermediate_size=self.intermediate_size, shared_expert_intermediate_size=shared_f,
                      norm_topk_prob=bool(renorm), decoder_sparse_step=1, mlp_only_layers=[])
             d["intermediate_size"] = extra.pop("dense_intermediate_size", self.intermediate_size)
@@ -194,10 +204,10 @@ class LlamaConfig:
                      partial_rotary_factor=self.partial_rotary_factor)
         elif self.model_type == "smollm3":
             d.update(architectures=["SmolLM3ForCausalLM"], hidden_act="silu", torch_dtype="bfloat16", mlp_bias=False,
-                     use_sliding_window=False, no_rope_layers=list(nope or [1] * self.num_hidden_layers))
+                     use_sliding_window=self.sliding_window is not None, no_rope_layers=list(nope or [1] * self.num_hidden_layers))
         elif self.model_type == "qwen3":
             d.update(architectures=["Qwen3ForCausalLM"], hidden_act="silu", torch_dtype="bfloat16",
-                     use_sliding_window=False, head_dim=self.head_dim)
+                     use_sliding_window=self.sliding_window is not None, head_dim=self.head_dim)
         elif self.model_type == "mixtral":
             d.pop("attention_bias")
             d.update(architectures=["MixtralForCausalLM"], hidden_act="silu", torch_dtype="bfloat16")
@@ -207,13 +217,15 @@ class LlamaConfig:
         elif self.attention_bias and not self.o_bias:     # q/k/v bias without o_proj bias is the Qwen2 layout in HuggingFace terms
             d.pop("attention_bias")
             d.update(architectures=["Qwen2ForCausalLM"], model_type="qwen2", hidden_act="silu", torch_dtype="bfloat16",
-                     use_sliding_window=False)
+                     use_sliding_window=self.sliding_window is not None)
         elif self.model_type == "mistral":
             d.pop("attention_bias")
             d.update(architectures=["MistralForCausalLM"], hidden_act="silu", torch_dtype="bfloat16")
         else:
             d.update(architectures=["LlamaForCausalLM"], hidden_act="silu", torch_dtype="bfloat16",
                      attention_bias=False, mlp_bias=False)
+        if win_layers is not None and self.sliding_window is not None and self.model_type != "exaone4":
+            d["layer_types"] = ["sliding_attention" if f else "full_attention" for f in win_layers]
         d.pop("o_bias")
         d.pop("mlp_bias", None)
         ob, mb = self.o_bias, self.mlp_bias
@@ -264,7 +276,7 @@ class LlamaConfig:
         if mt not in cls._KNOWN_TYPES:
             raise NotImplementedError(f"model_type {mt!r}: only Llama-shaped decoders are built {cls._KNOWN_TYPES}")
         # keys that only some families may carry
-        for k in cls._SWITCHES:
+        for k in cls._SWITCHES + ("window_layers",):
             kw.pop(k, None)
         if mt not in ("smollm3", "exaone4"):
             kw.pop("no_rope_layers", None)
@@ -322,7 +334,7 @@ class LlamaConfig:
                     cfg.rope_scaling = dict(cfg.rope_scaling, original_max_position_embeddings=int(orig))
         generated = {"architectures", "hidden_act", "torch_dtype", "mlp_bias", "use_sliding_window", "head_dim",
                      "num_experts", "moe_intermediate_size", "norm_topk_prob", "decoder_sparse_step", "mlp_only_layers",
-                     "rope_parameters"}
+                     "rope_parameters", "layer_types"}
         cfg.extra = {k: v for k, v in d.items() if k not in keys and k not in generated}
         if dense_ffn is not None:
             cfg.extra["dense_intermediate_size"] = dense_ffn
@@ -337,8 +349,17 @@ class LlamaConfig:
 # ---------------------------------------------------------------------------------------------- per-family readers
 # Each takes (model_type, the config.json dict, the keyword arguments collected so far) and sets the family's switches.
 def _window_off_unless_used(d: dict, kw: dict) -> None:
-    if not d.get("use_sliding_window", False):
+    if not d.get("use_sliding_window", False) or kw.get("sliding_window") is None:
         kw["sliding_window"] = None        # Qwen-style configs carry a window that is switched off
+        return
+    n_layers = int(kw.get("num_hidden_layers", 32))
+    types = d.get("layer_types")
+    if types is not None:
+        kw["window_layers"] = [int(t == "sliding_attention") for t in types]
+    elif d.get("max_window_layers") is not None:       # the first ``max_window_layers`` layers attend to everything
+        kw["window_layers"] = [int(i >= int(d["max_window_layers"])) for i in range(n_layers)]
+    if kw.get("window_layers") is not None and not any(kw["window_layers"]):
+        kw["sliding_window"], kw["window_layers"] = None, None
 
 
 def _every_layer_sparse(mt: str, d: dict) -> None:
@@ -429,9 +450,9 @@ def _read_exaone4(mt, d, kw):          # OLMo 2's placement of the norms with pe
         else:
             types = ["sliding_attention" if (i + 1) % int(pat) else "full_attention" for i in range(n_layers)]
     if window is not None and types and "sliding_attention" in types:
-        # hybrid checkpoints: windowed layers rotate, global layers apply no rotation; sequences up to the window are
-        # exact under full causal attention, longer ones are refused
+        # hybrid checkpoints: windowed layers rotate, global layers apply no rotation
         kw["no_rope_layers"] = [int(t == "sliding_attention") for t in types]
+        kw["window_layers"] = list(kw["no_rope_layers"])
     else:
         kw["sliding_window"] = None
         kw.pop("no_rope_layers", None)

@@ -119,7 +119,7 @@ class DecoderLayerFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, h, pos, cos, sin, w_ln1, w_qkv, w_o, w_ln2, w_gu, w_d, meta, b_qkv=None, w_qn=None, w_kn=None,
                 b_o=None, b_gu=None, b_d=None, rmul=1.0):
-        B, L, H, Hkv, d, eps, recompute = meta
+        B, L, H, Hkv, d, eps, recompute, window = meta
         n1, _, rstd1 = basic.rmsnorm_fwd(h, w_ln1, eps)
         qk_saved = ()
         if b_qkv is None and w_qn is None:                    # rotation in the epilogue of the q/k/v GEMM
@@ -133,7 +133,7 @@ class DecoderLayerFn(torch.autograd.Function):
                 qkv, rstd_qk = basic.headnorm_fwd(qkv_raw, w_qn, w_kn, H, Hkv, d, eps)
                 qk_saved = (qkv_raw, rstd_qk)
             basic.rope_(qkv, pos, cos, sin, H + Hkv, d)      # q and k heads are adjacent columns
-        att, lse = attention.attention_fwd(qkv, B, L, H, Hkv, d)
+        att, lse = attention.attention_fwd(qkv, B, L, H, Hkv, d, window)
         # rmul (Granite's residual_multiplier) scales a branch, bias included, before it joins the residual stream: it is
         # the alpha of the GEMM whose epilogue adds the residual
         h1 = basic.gemm(att, w_o, residual=h, alpha=rmul)
@@ -166,7 +166,7 @@ class DecoderLayerFn(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dh2):
-        B, L, H, Hkv, d, eps, recompute = ctx.meta
+        B, L, H, Hkv, d, eps, recompute, window = ctx.meta
         w_ln1, w_qkv, w_o, w_ln2, w_gu, w_d = ctx.weights
         s_ln1, s_qkv, s_o, s_ln2, s_gu, s_d = ctx.slots
         if UNIT_PRE[0] is not None:
@@ -188,7 +188,7 @@ class DecoderLayerFn(torch.autograd.Function):
                     qkv_raw = qkv
                     qkv, rstd_qk = basic.headnorm_fwd(qkv_raw, w_qn, w_kn, H, Hkv, d, eps)
                 basic.rope_(qkv, pos, cos, sin, H + Hkv, d)
-            att, lse = attention.attention_fwd(qkv, B, L, H, Hkv, d)
+            att, lse = attention.attention_fwd(qkv, B, L, H, Hkv, d, window)
             h1 = basic.gemm(att, w_o, residual=h, alpha=ctx.rmul)
             if ctx.more_b[0] is not None:
                 basic.bias_add_(h1, ctx.more_b[0] if ctx.rmul == 1.0 else ctx.more_b[0] * ctx.rmul)
@@ -225,7 +225,7 @@ class DecoderLayerFn(torch.autograd.Function):
         g_o = _wgrad(db1, att, w_o, s_o)
         datt = basic.linear_dgrad(db1, w_o)
         del db1
-        dqkv = attention.attention_bwd_unrotated(datt, qkv, att, lse, B, L, H, Hkv, d, pos, cos, sin)
+        dqkv = attention.attention_bwd_unrotated(datt, qkv, att, lse, B, L, H, Hkv, d, pos, cos, sin, window)
         del datt
         g_qn = g_kn = None
         if w_qn is not None:
@@ -418,9 +418,6 @@ class LlamaModel(nn.Module):
         """input_ids [B, L] int64 -> final-norm hidden states [B*L, h]."""
         cfg = self.cfg
         B, L = input_ids.shape
-        if cfg.sliding_window and L > cfg.sliding_window:
-            raise ValueError(f"sequence length {L} exceeds the model's attention window ({cfg.sliding_window}); windowed "
-                             "attention is not built - lower context_len")
         dev = self.embed_tokens.device
         ids = input_ids.reshape(-1).to(dev)
         pos = torch.arange(L, dtype=torch.int32, device=dev).repeat(B)
@@ -435,7 +432,9 @@ class LlamaModel(nn.Module):
                 bool(self.grad_checkpointing and torch.is_grad_enabled()))
         rmul = float(cfg.residual_multiplier)
         tables = self.layer_rope(cos, sin)
-        for layer, (cos, sin) in zip(self.layers, tables):
+        meta7 = meta
+        for li, (layer, (cos, sin)) in enumerate(zip(self.layers, tables)):
+            meta = meta7 + (cfg.layer_window(li, L),)       # the layer's sliding window when the sequence is longer
             if pre is not None:
                 pre(layer.first_param, False)
             if LAYER_WEIGHTS_PRE[0] is not None:
@@ -485,8 +484,6 @@ class LlamaModel(nn.Module):
         B, L = input_ids.shape
         if chunk_len <= 0 or chunk_len >= L:
             return self.hidden_states(input_ids)
-        if cfg.sliding_window and L > cfg.sliding_window:
-            raise ValueError(f"sequence length {L} exceeds the model's attention window ({cfg.sliding_window})")
         dev = self.embed_tokens.device
         H, Hkv, d = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
         tables = self.layer_rope(*self.rope(dev, L))
@@ -501,19 +498,20 @@ class LlamaModel(nn.Module):
             h = basic.embed_fwd(ids[:, c0:c0 + n].reshape(-1), self.embed_tokens)
             if cfg.embedding_multiplier != 1.0:
                 h = h * cfg.embedding_multiplier
-            for layer, (kc, vc), (cos, sin) in zip(self.layers, caches, tables):
+            for li, (layer, (kc, vc), (cos, sin)) in enumerate(zip(self.layers, caches, tables)):
+                window = cfg.layer_window(li, L)
                 if LAYER_WEIGHTS_PRE[0] is not None:
                     LAYER_WEIGHTS_PRE[0](layer.first_param)
                 if cfg.sandwich:
                     from .sandwich import layer_inference
 
-                    def attend(qkv, after_rotation=None, kc=kc, vc=vc, cos=cos, sin=sin):
+                    def attend(qkv, after_rotation=None, kc=kc, vc=vc, cos=cos, sin=sin, window=window):
                         basic.rope_(qkv, pos, cos, sin, H + Hkv, d)
                         if after_rotation is not None:
                             qkv = after_rotation(qkv)
                         kc[:, c0:c0 + n] = qkv[:, H * d:(H + Hkv) * d].reshape(B, n, kv)
                         vc[:, c0:c0 + n] = qkv[:, (H + Hkv) * d:].reshape(B, n, kv)
-                        return attention.attention_fwd_cached(qkv, kc, vc, B, n, c0, H, Hkv, d)
+                        return attention.attention_fwd_cached(qkv, kc, vc, B, n, c0, H, Hkv, d, window)
                     h = layer_inference(layer, cfg, h, attend, cfg.rms_norm_eps)
                     continue
                 n1, _, _ = basic.rmsnorm_fwd(h, layer.input_layernorm, cfg.rms_norm_eps)
@@ -531,7 +529,7 @@ class LlamaModel(nn.Module):
                     basic.rope_(qkv, pos, cos, sin, H + Hkv, d)
                 kc[:, c0:c0 + n] = qkv[:, H * d:(H + Hkv) * d].reshape(B, n, kv)
                 vc[:, c0:c0 + n] = qkv[:, (H + Hkv) * d:].reshape(B, n, kv)
-                att = attention.attention_fwd_cached(qkv, kc, vc, B, n, c0, H, Hkv, d)
+                att = attention.attention_fwd_cached(qkv, kc, vc, B, n, c0, H, Hkv, d, window)
                 rm = float(cfg.residual_multiplier)
                 h1 = basic.gemm(att, layer.o_proj, residual=h, alpha=rm)
                 if cfg.o_bias:

@@ -107,7 +107,7 @@ class AttnBlockFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, h, pos, cos, sin, w_ln1, w_qkv, w_o, meta, b_qkv=None, w_qn=None, w_kn=None, rmul=1.0):
-        B, L, H, Hkv, d, eps, recompute = meta
+        B, L, H, Hkv, d, eps, recompute, window = meta
         ctx.rmul = rmul          # Granite's residual multiplier: the branch is scaled before it joins the stream
         n1, _, rstd1 = basic.rmsnorm_fwd(h, w_ln1, eps)
         qkv = basic.linear_fwd(n1, w_qkv)
@@ -122,7 +122,7 @@ class AttnBlockFn(torch.autograd.Function):
             qkv, rstd_qk = basic.headnorm_fwd(qkv_raw, w_qn, w_kn, H, Hkv, d, eps)
             qk_saved = (qkv_raw, rstd_qk)
         basic.rope_(qkv, pos, cos, sin, H + Hkv, d)
-        att, lse = attention.attention_fwd(qkv, B, L, H, Hkv, d)
+        att, lse = attention.attention_fwd(qkv, B, L, H, Hkv, d, window)
         h1 = basic.gemm(att, w_o, residual=h, alpha=rmul)
         ctx.meta = meta
         ctx.weights = (w_ln1, w_qkv, w_o)
@@ -139,7 +139,7 @@ class AttnBlockFn(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dh1):
-        B, L, H, Hkv, d, eps, recompute = ctx.meta
+        B, L, H, Hkv, d, eps, recompute, window = ctx.meta
         w_ln1, w_qkv, w_o = ctx.weights
         s_ln1, s_qkv, s_o = ctx.slots
         w_qn, w_kn = ctx.qk_w
@@ -159,7 +159,7 @@ class AttnBlockFn(torch.autograd.Function):
                 qkv_raw = qkv
                 qkv, rstd_qk = basic.headnorm_fwd(qkv_raw, w_qn, w_kn, H, Hkv, d, eps)
             basic.rope_(qkv, pos, cos, sin, H + Hkv, d)
-            att, lse = attention.attention_fwd(qkv, B, L, H, Hkv, d)
+            att, lse = attention.attention_fwd(qkv, B, L, H, Hkv, d, window)
         elif full:
             h, pos, cos, sin, rstd1, n1, qkv, att, lse, *qk_full = ctx.saved_tensors
         elif w_qn is not None:
@@ -171,7 +171,7 @@ class AttnBlockFn(torch.autograd.Function):
         g_o = _ll._wgrad(da, att, w_o, s_o)
         datt = basic.linear_dgrad(da, w_o)
         del da
-        dqkv = attention.attention_bwd_unrotated(datt, qkv, att, lse, B, L, H, Hkv, d, pos, cos, sin)
+        dqkv = attention.attention_bwd_unrotated(datt, qkv, att, lse, B, L, H, Hkv, d, pos, cos, sin, window)
         del datt
         g_qn = g_kn = None
         if full:

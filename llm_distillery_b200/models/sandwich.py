@@ -28,7 +28,7 @@ def _qk_full_fwd(qkv, w_qn, w_kn, q, kv, eps):
 
 
 def _forward(h, pos, cos, sin, meta, w_qkv, w_o, w_gu, w_d, w_ln1, w_ln2, w_pa, w_pm, b_qkv, w_qn, w_kn):
-    B, L, H, Hkv, d, eps, _recompute, qk_mode, _first = meta
+    B, L, H, Hkv, d, eps, _recompute, window, qk_mode, _first = meta
     q, kv = H * d, Hkv * d
     r1 = r2 = ra = rm = None
     x1 = h
@@ -49,7 +49,7 @@ def _forward(h, pos, cos, sin, meta, w_qkv, w_o, w_gu, w_d, w_ln1, w_ln2, w_pa, 
         qkv_rot = qkv
         qkv, rstd_qk = basic.headnorm_fwd(qkv_rot, w_qn, w_kn, H, Hkv, d, eps)
         qk_saved = (qkv_rot, rstd_qk)
-    att, lse = attention.attention_fwd(qkv, B, L, H, Hkv, d)
+    att, lse = attention.attention_fwd(qkv, B, L, H, Hkv, d, window)
     if w_pa is None:
         a = None
         h1 = basic.linear_fwd(att, w_o, residual=h)
@@ -72,7 +72,7 @@ def _forward(h, pos, cos, sin, meta, w_qkv, w_o, w_gu, w_d, w_ln1, w_ln2, w_pa, 
 
 
 class SandwichLayerFn(torch.autograd.Function):
-    """meta = (B, L, heads, kv heads, head dim, eps, recompute in backward, q/k norm: 0 none / 1 per head / 2 over the
+    """meta = (B, L, heads, kv heads, head dim, eps, recompute in backward, sliding window or None, q/k norm: 0 none / 1 per head / 2 over the
     whole projection / 3 per head after the rotation, the layer's first parameter). Norm weights that the family does
     not have are None."""
 
@@ -96,7 +96,7 @@ class SandwichLayerFn(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dh2):
-        B, L, H, Hkv, d, eps, recompute, qk_mode, first = ctx.meta
+        B, L, H, Hkv, d, eps, recompute, window, qk_mode, first = ctx.meta
         w_qkv, w_o, w_gu, w_d, w_ln1, w_ln2, w_pa, w_pm, b_qkv, w_qn, w_kn = ctx.weights
         s_qkv, s_o, s_gu, s_d, s_ln1, s_ln2, s_pa, s_pm, s_b, s_qn, s_kn = ctx.slots
         q, kv = H * d, Hkv * d
@@ -142,13 +142,13 @@ class SandwichLayerFn(torch.autograd.Function):
         g_qn = g_kn = None
         if qk_mode == 3:
             qkv_rot, rstd_qk = qk_saved
-            dqkv = attention.attention_bwd(datt, qkv, att, lse, B, L, H, Hkv, d)
+            dqkv = attention.attention_bwd(datt, qkv, att, lse, B, L, H, Hkv, d, window)
             dwq, dwk = basic.headnorm_bwd_(dqkv, qkv_rot, w_qn, w_kn, rstd_qk, H, Hkv, d)
             basic.rope_(dqkv, pos, cos, sin, H + Hkv, d, inverse=True)
             g_qn = _ll._vec_grad(dwq, w_qn, s_qn)
             g_kn = _ll._vec_grad(dwk, w_kn, s_kn)
         else:
-            dqkv = attention.attention_bwd_unrotated(datt, qkv, att, lse, B, L, H, Hkv, d, pos, cos, sin)
+            dqkv = attention.attention_bwd_unrotated(datt, qkv, att, lse, B, L, H, Hkv, d, pos, cos, sin, window)
         del datt
         if qk_mode == 2:
             q_raw, k_raw, rq, rk = qk_saved

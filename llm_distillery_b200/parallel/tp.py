@@ -354,7 +354,7 @@ class TPLlama:
                 qkv, _ = basic.headnorm_fwd(qkv, w[p + "q_norm"], w[p + "k_norm"], Hl, Hkvl, d, eps)
             if not nope or nope[i]:
                 basic.rope_(qkv, pos, cos_t, sin_t, Hl + Hkvl, d)
-            att, _ = attention.attention_fwd(qkv, B, L, Hl, Hkvl, d)
+            att, _ = attention.attention_fwd(qkv, B, L, Hl, Hkvl, d, cfg.layer_window(i, L) if hasattr(cfg, "layer_window") else None)
             x = g.gemm_rs(att, w[p + "o_proj"], residual=x)
             basic.rmsnorm_fwd(x, w[p + "post_attention_layernorm"], eps, out=g.slab(T, h))
             gu = g.ag_gemm(w[p + "gate_up_proj"], T)

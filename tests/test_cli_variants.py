@@ -131,7 +131,8 @@ FAMILIES = {
                  head_dim_override=32),
     "glm": dict(model_type="glm", attention_bias=True, partial_rotary_factor=0.5, rope_interleaved=True),
     "exaone4, windowed and global layers": dict(model_type="exaone4", pre_norm=False, post_norm=True, qk_norm=True,
-                                                no_rope_layers=[1, 0], sliding_window=256),
+                                                no_rope_layers=[1, 0], window_layers=[1, 0], sliding_window=48),
+    "mistral, window shorter than the context": dict(model_type="mistral", sliding_window=40),
     "helium": dict(model_type="helium", rope_interleaved=True),
     "ernie4_5": dict(model_type="ernie4_5", rope_interleaved=True),
     "seed_oss": dict(model_type="seed_oss", attention_bias=True, head_dim_override=32),

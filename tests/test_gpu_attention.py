@@ -67,3 +67,35 @@ def test_backward_with_the_inverse_rotation_of_dq_in_the_conversion_pass(B, L, H
     _lib.check(_lib.kernels().b200_dq_convert_rope(_lib.ptr(acc), _lib.ptr(b), _lib.ptr(pos), _lib.ptr(cos), _lib.ptr(sin),
                                                    B * L, H, d, b.stride(0), _lib.stream()), "b200_dq_convert_rope")
     assert torch.equal(a[:, : H * d], b[:, : H * d])
+
+
+@pytest.mark.parametrize("B,L,H,Hkv,d,window", [(2, 300, 4, 2, 64, 128), (1, 1000, 8, 8, 128, 256)])
+def test_sequences_longer_than_a_sliding_window(B, L, H, Hkv, d, window):
+    """Beyond the window the flash kernels step aside for the band-masked library path: forward and backward on the
+    GPU (bf16) against the same path in fp32 on the CPU; inside the window the flash kernels still run."""
+    torch.manual_seed(L + window)
+    qkv = torch.randn(B * L, (H + 2 * Hkv) * d, device=DEV).bfloat16()
+    dout = torch.randn(B * L, H * d, device=DEV).bfloat16()
+    out, lse = attention.attention_fwd(qkv, B, L, H, Hkv, d, window)
+    dqkv = attention.attention_bwd(dout, qkv, out, lse, B, L, H, Hkv, d, window)
+    assert out.dtype == torch.bfloat16 and dqkv.shape == qkv.shape
+    ro, _ = attention.attention_fwd(qkv.float().cpu(), B, L, H, Hkv, d, window)
+    rd = attention.attention_bwd(dout.float().cpu(), qkv.float().cpu(), ro, None, B, L, H, Hkv, d, window)
+    assert torch.allclose(out.float().cpu(), ro, atol=3e-2, rtol=3e-2), (out.float().cpu() - ro).abs().max()
+    err = (dqkv.float().cpu() - rd).abs().max().item()
+    assert err <= 6e-2 * max(1.0, rd.abs().max().item()), err
+    causal, _ = attention.attention_reference_fwd(qkv.float().cpu(), B, L, H, Hkv, d)
+    assert (causal - ro).abs().max() > 0.1                    # the window matters at this length
+    # a chunk against the key / value cache
+    kv = Hkv * d
+    kc = qkv[:, H * d:H * d + kv].reshape(B, L, kv).contiguous()
+    vc = qkv[:, H * d + kv:].reshape(B, L, kv).contiguous()
+    n, c0 = 128, L - 128 - (L - 128) % 8
+    rows = torch.cat([qkv[b * L + c0: b * L + c0 + n] for b in range(B)])
+    got = attention.attention_fwd_cached(rows.contiguous(), kc, vc, B, n, c0, H, Hkv, d, window)
+    want = torch.cat([ro[b * L + c0: b * L + c0 + n] for b in range(B)])
+    assert torch.allclose(got.float().cpu(), want, atol=3e-2, rtol=3e-2)
+    # a window that covers the sequence: the flash kernels, bit for bit what they give without one
+    a, _ = attention.attention_fwd(qkv, B, L, H, Hkv, d, L)
+    b, _ = attention.attention_fwd(qkv, B, L, H, Hkv, d)
+    assert torch.equal(a, b) and _lib.take_device_error() == 0

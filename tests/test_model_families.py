@@ -89,10 +89,7 @@ def test_config_keys_survive_a_round_trip_and_unbuilt_variants_are_refused(tmp_p
               "some_future_key", "model_type"):
         assert out[k] == src[k], k
     assert out["architectures"] == ["MistralForCausalLM"]
-    model = build_model(cfg, dtype=torch.float32, device="cpu", seed=0)
-    model(torch.randint(0, 320, (1, 128)))                       # up to the window: full causal attention is exact
-    with pytest.raises(ValueError, match="attention window"):
-        model(torch.randint(0, 320, (1, 129)))
+    assert cfg.layer_window(0, 128) is None and cfg.layer_window(1, 129) == 128    # inside the window: plain causal
     for bad in (dict(model_type="gemma2"), dict(hidden_act="gelu_pytorch_tanh"), dict(head_dim=20),
                 dict(rope_scaling={"rope_type": "ntk-by-parts", "factor": 4.0})):
         with pytest.raises(NotImplementedError):
@@ -270,6 +267,56 @@ def test_partial_rotary_matches_huggingface(tmp_path):
     assert torch.allclose(basic.rope_(r, pos, cos, sin, 3, 32, inverse=True), v, atol=1e-5)
 
 
+@pytest.mark.parametrize("family", ["mistral", "qwen2 with windowed upper layers", "phi3"])
+def test_sliding_window_attention_matches_huggingface(tmp_path, family):
+    """Sequences longer than the window: a query sees the last ``sliding_window`` positions - logits, gradients (with and
+    without recomputation) and the chunked inference path against HuggingFace; inside the window nothing changes."""
+    torch.manual_seed(7)
+    if family == "mistral":
+        hf = tr.MistralForCausalLM(tr.MistralConfig(**_base(), sliding_window=32, attn_implementation="eager",
+                                                    tie_word_embeddings=False)).float()
+        flags = None
+    elif family == "phi3":
+        hf = tr.Phi3ForCausalLM(tr.Phi3Config(**_base(), sliding_window=32, pad_token_id=0, attn_implementation="eager",
+                                              tie_word_embeddings=False)).float()
+        flags = None
+    else:
+        hf = tr.Qwen2ForCausalLM(tr.Qwen2Config(**_base(num_hidden_layers=3), sliding_window=32, use_sliding_window=True,
+                                                max_window_layers=1, attn_implementation="eager",
+                                                tie_word_embeddings=False)).float()
+        flags = [0, 1, 1]
+    hf.save_pretrained(str(tmp_path / "hf"), safe_serialization=True)
+    model = load_hf_model(str(tmp_path / "hf"), dtype=torch.float32)
+    cfg = model.cfg
+    assert cfg.sliding_window == 32 and cfg.window_layers == flags
+    for L, recompute in ((24, False), (100, False), (100, True)):
+        model.grad_checkpointing = recompute
+        model.zero_grad()
+        hf.zero_grad()
+        x = torch.randint(1, 320, (2, L))
+        ours, ref = model(x), hf(x).logits
+        assert torch.allclose(ours, ref, atol=3e-4, rtol=1e-3), (L, (ours - ref).abs().max())
+        tgt = torch.randint(0, 320, (2 * L,))
+        torch.nn.functional.cross_entropy(ours.reshape(-1, 320), tgt).backward()
+        torch.nn.functional.cross_entropy(ref.reshape(-1, 320), tgt).backward()
+        hf_g = {n: p.grad for n, p in hf.named_parameters()}
+        for n, p, sl in model.named_hf_parameters():
+            g = p.grad if sl is None else p.grad[sl]
+            assert torch.allclose(g, hf_g[n], atol=2e-5, rtol=2e-3), (L, n, (g - hf_g[n]).abs().max())
+    model.grad_checkpointing = False
+    with torch.no_grad():
+        hs = model.hidden_states_chunked(x, 16)
+        assert torch.allclose(torch.nn.functional.linear(hs, model.lm_head).view(2, 100, -1), ref, atol=3e-4, rtol=1e-3)
+        plain = build_model(LlamaConfig.from_hf_dict(dict(cfg.to_hf_dict(), sliding_window=None, use_sliding_window=False)),
+                            dtype=torch.float32, device="cpu", seed=0)
+        plain.load_state_dict(model.state_dict())
+        assert (plain(x) - ref).abs().max() > 3e-3            # the window is not a no-op at this length
+    save_hf_model(model, str(tmp_path / "ours"))
+    hf2 = tr.AutoModelForCausalLM.from_pretrained(str(tmp_path / "ours"), torch_dtype=torch.float32,
+                                                  attn_implementation="eager")
+    assert torch.allclose(hf2(x).logits, ref, atol=3e-4, rtol=1e-3)
+
+
 def test_dynamic_ntk_rope_scaling_matches_huggingface():
     """Inside the model's context nothing changes; beyond it the base follows the sequence length."""
     sc = {"rope_type": "dynamic", "factor": 3.0}
@@ -415,9 +462,10 @@ def test_more_decoder_families_match_huggingface(tmp_path, family, recompute):
     if family == "olmo2":
         with pytest.raises(NotImplementedError, match="o_proj"):
             LlamaConfig.from_hf_dict(dict(cfg.to_hf_dict(), attention_bias=True))
-    if family == "exaone4 hybrid":           # beyond the window the windowed layers would differ: refused
-        with pytest.raises(ValueError, match="attention window"):
-            model(torch.randint(1, 320, (1, 65)))
+    if family == "exaone4 hybrid":           # beyond the window the windowed layer sees the last 64 positions only
+        assert cfg.window_layers == [1, 0] and cfg.layer_window(0, 100) == 64 and cfg.layer_window(1, 100) is None
+        x = torch.randint(1, 320, (2, 100))
+        assert torch.allclose(model(x), hf(x).logits, atol=3e-4, rtol=1e-3)
 
 
 def test_llama_with_attention_and_mlp_biases_matches_huggingface(tmp_path):
@@ -519,7 +567,8 @@ def test_every_model_type_survives_config_round_trips():
     import dataclasses
     moe = dict(num_local_experts=4, num_experts_per_tok=2)
     cases = {
-        "llama": {}, "mistral": dict(sliding_window=128), "qwen2": dict(attention_bias=True),
+        "llama": {}, "mistral": dict(sliding_window=128),
+        "qwen2": dict(attention_bias=True, sliding_window=64, window_layers=[0, 1]),
         "phi3": dict(partial_rotary_factor=0.75), "mixtral": moe,
         "qwen3": dict(qk_norm=True, head_dim_override=32),
         "qwen3_moe": dict(moe, qk_norm=True, moe_renormalize=False),
@@ -533,7 +582,8 @@ def test_every_model_type_survives_config_round_trips():
         "olmoe": dict(moe, qk_norm_full=True, moe_renormalize=False),
         "glm": dict(attention_bias=True, partial_rotary_factor=0.5, rope_interleaved=True),
         "glm4": dict(attention_bias=True, partial_rotary_factor=0.5, rope_interleaved=True, post_norm=True),
-        "exaone4": dict(pre_norm=False, post_norm=True, qk_norm=True, no_rope_layers=[1, 0], sliding_window=128),
+        "exaone4": dict(pre_norm=False, post_norm=True, qk_norm=True, no_rope_layers=[1, 0], window_layers=[1, 0],
+                        sliding_window=128),
         "helium": dict(rope_interleaved=True), "ernie4_5": dict(rope_interleaved=True),
         "seed_oss": dict(attention_bias=True, head_dim_override=32),
         "hunyuan_v1_dense": dict(qk_norm=True, qk_norm_after_rope=True,
