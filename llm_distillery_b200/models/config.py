@@ -56,6 +56,10 @@ class LlamaConfig:
     qk_norm_full: bool = False        # OLMo 2: one RMSNorm over the whole query projection, one over the key projection
     pre_norm: bool = True             # RMSNorm on the way into the attention and MLP branches (false: OLMo 2)
     post_norm: bool = False           # RMSNorm on the way out of both branches (OLMo 2, GLM-4 0414; models/sandwich.py)
+    mlp_act: str = "silu"             # the gate's activation: silu (SwiGLU) or gelu_tanh (Gemma's GeGLU; PyTorch ops)
+    norm_plus_one: bool = False       # checkpoint layout: RMSNorm weights are stored minus one (Gemma); converted at load / save
+    rope_local_theta: float | None = None      # Gemma 3: the windowed layers rotate with this base, without scaling
+    embedding_multiplier_rounded: bool = False # Gemma: the embedding multiplier is rounded to the model's dtype first
     rope_interleaved: bool = False    # checkpoint layout: rotary pairs are neighbours (GLM); rows are permuted at load / save
     sliding_window: int | None = None  # a query sees the last ``sliding_window`` positions; matters for longer sequences only
     window_layers: list | None = None  # one flag per layer, 1 = windowed; None: every layer (when sliding_window is set)
@@ -77,8 +81,9 @@ class LlamaConfig:
     def check_gpu_kernels(self) -> None:
         """Raises when a shape is outside what the sm_100a kernels take, in words, before any kernel is launched."""
         problems = []
-        if self.head_dim not in (64, 128):
-            problems.append(f"head_dim {self.head_dim}: the flash-attention kernels take 64 and 128")
+        if self.head_dim % 16:
+            problems.append(f"head_dim {self.head_dim}: a multiple of 16 is needed (64 and 128 run the flash-attention "
+                            "kernels, other sizes PyTorch's attention)")
         if self.rotary_dim % 16:
             problems.append(f"rotary width {self.rotary_dim}: the rotary kernel moves 16-byte vectors (a multiple of 16)")
         for name, v in (("hidden_size", self.hidden_size), ("intermediate_size", self.intermediate_size),
@@ -93,7 +98,8 @@ class LlamaConfig:
         """Whether the layers take the general node of models/sandwich.py instead of the fused pre-norm layer."""
         if self.num_local_experts and self.pre_norm and not self.post_norm and not self.qk_norm_after_rope:
             return False         # experts: the two nodes of models/moe.py (their attention half takes either q/k norm)
-        return self.post_norm or not self.pre_norm or self.qk_norm_full or self.qk_norm_after_rope
+        return (self.post_norm or not self.pre_norm or self.qk_norm_full or self.qk_norm_after_rope
+                or self.mlp_act != "silu")
 
     @property
     def rotary_dim(self) -> int:
@@ -156,7 +162,7 @@ class LlamaConfig:
             d.pop("num_local_experts")
             d.pop("num_experts_per_tok")
         qk = d.pop("qk_norm")
-        for k in ("qk_norm_full", "qk_norm_after_rope", "pre_norm", "post_norm", "rope_interleaved"):      # implied by the model type
+        for k in self._SWITCHES:      # implied by the model type
             d.pop(k)
         shared_f = d.pop("shared_expert_intermediate_size")
         d.pop("shared_expert_gated")
@@ -174,6 +180,23 @@ class LlamaConfig:
                      moe_intermediate_size=self.intermediate_size, shared_expert_intermediate_size=shared_f,
                      norm_topk_prob=bool(renorm), decoder_sparse_step=1, mlp_only_layers=[])
             d["intermediate_size"] = extra.pop("dense_intermediate_size", self.intermediate_size)
+        elif self.model_type == "gemma":
+            d.update(architectures=["GemmaForCausalLM"], hidden_act="gelu_pytorch_tanh", hidden_activation="gelu_pytorch_tanh",
+                     torch_dtype="bfloat16", attention_bias=False, head_dim=self.head_dim)
+        elif self.model_type == "gemma3_text":
+            d.pop("attention_bias")
+            d.pop("rope_theta")
+            rope_full = dict(self.rope_scaling or {"rope_type": "default"}, rope_theta=self.rope_theta)
+            d.pop("rope_scaling", None)
+            d.update(architectures=["Gemma3ForCausalLM"], hidden_activation="gelu_pytorch_tanh", torch_dtype="bfloat16",
+                     head_dim=self.head_dim, query_pre_attn_scalar=_whole_if_close(1.0 / gran["attention_multiplier"] ** 2)
+                     if gran["attention_multiplier"] else self.head_dim,
+                     layer_types=["sliding_attention" if (win_layers is None or win_layers[i]) and self.sliding_window
+                                  else "full_attention" for i in range(self.num_hidden_layers)],
+                     rope_parameters={"full_attention": rope_full,
+                                      "sliding_attention": {"rope_type": "default",
+                                                            "rope_theta": self.rope_local_theta or self.rope_theta}},
+                     final_logit_softcapping=None, attn_logit_softcapping=None)
         elif self.model_type == "olmoe":
             d.update(architectures=["OlmoeForCausalLM"], hidden_act="silu", torch_dtype="bfloat16", attention_bias=False,
                      num_experts=d.pop("num_local_experts"), norm_topk_prob=bool(renorm), clip_qkv=None)
@@ -224,7 +247,7 @@ class LlamaConfig:
         else:
             d.update(architectures=["LlamaForCausalLM"], hidden_act="silu", torch_dtype="bfloat16",
                      attention_bias=False, mlp_bias=False)
-        if win_layers is not None and self.sliding_window is not None and self.model_type != "exaone4":
+        if win_layers is not None and self.sliding_window is not None and self.model_type not in ("exaone4", "gemma3_text"):
             d["layer_types"] = ["sliding_attention" if f else "full_attention" for f in win_layers]
         d.pop("o_bias")
         d.pop("mlp_bias", None)
@@ -247,7 +270,7 @@ class LlamaConfig:
 
     _KNOWN_TYPES = ("llama", "mistral", "qwen2", "phi3", "mixtral", "qwen3", "qwen3_moe", "qwen2_moe", "granite",
                     "smollm3", "olmo2", "glm", "glm4", "exaone4", "helium", "ernie4_5", "seed_oss", "hunyuan_v1_dense",
-                    "olmoe", "granitemoe", "granitemoeshared")
+                    "olmoe", "granitemoe", "granitemoeshared", "gemma", "gemma3_text")
     # what HuggingFace's attention_bias puts a bias on, per family: q, k and v only / the o projection as well (built for
     # the second group, refused for every other family); families whose MLP may carry biases; families with experts
     _QKV_BIAS_TYPES = ("qwen2", "qwen2_moe", "glm", "glm4", "seed_oss", "helium")
@@ -255,10 +278,16 @@ class LlamaConfig:
     _MLP_BIAS_TYPES = ("llama", "mistral", "granite")
     _EXPERT_TYPES = ("mixtral", "qwen3_moe", "qwen2_moe", "olmoe", "granitemoe", "granitemoeshared")
     _MULTIPLIER_TYPES = ("granite", "granitemoe", "granitemoeshared")
-    _SWITCHES = ("qk_norm_full", "qk_norm_after_rope", "pre_norm", "post_norm", "rope_interleaved")   # set by the type alone
+    _GELU_TYPES = ("gemma", "gemma3_text")
+    _SWITCHES = ("qk_norm_full", "qk_norm_after_rope", "pre_norm", "post_norm", "rope_interleaved", "mlp_act",
+                 "norm_plus_one", "rope_local_theta", "embedding_multiplier_rounded")      # set by the type alone
 
     @classmethod
     def from_hf_dict(cls, d: dict) -> "LlamaConfig":
+        d = dict(d)
+        if d.get("model_type") == "gemma3" and isinstance(d.get("text_config"), dict):
+            # the multimodal wrapper: its language model is read (and saved) as a text-only Gemma 3
+            d = dict(d["text_config"], model_type="gemma3_text")
         keys = {f for f in cls.__dataclass_fields__} - {"extra"}
         kw = {k: v for k, v in d.items() if k in keys}
         mt = d.get("model_type", "llama")
@@ -304,8 +333,12 @@ class LlamaConfig:
             if mt not in cls._MLP_BIAS_TYPES:
                 raise NotImplementedError(f"mlp_bias on model_type {mt!r} is not built")
             kw["mlp_bias"] = True
-        if d.get("hidden_act", "silu") not in ("silu", "swish"):
-            raise NotImplementedError(f"hidden_act {d['hidden_act']!r}: only SwiGLU (silu) is built")
+        act = d.get("hidden_activation") or d.get("hidden_act") or ("gelu_pytorch_tanh" if mt in cls._GELU_TYPES else "silu")
+        if mt in cls._GELU_TYPES:
+            if act not in ("gelu_pytorch_tanh", "gelu_tanh"):
+                raise NotImplementedError(f"{mt} with hidden activation {act!r} is not built (gelu_pytorch_tanh is)")
+        elif act not in ("silu", "swish"):
+            raise NotImplementedError(f"hidden_act {act!r}: only SwiGLU (silu) is built for model_type {mt!r}")
         # heads
         kw["partial_rotary_factor"] = float(kw.get("partial_rotary_factor") or 1.0)
         if not 0.0 < kw["partial_rotary_factor"] <= 1.0:
@@ -334,7 +367,8 @@ class LlamaConfig:
                     cfg.rope_scaling = dict(cfg.rope_scaling, original_max_position_embeddings=int(orig))
         generated = {"architectures", "hidden_act", "torch_dtype", "mlp_bias", "use_sliding_window", "head_dim",
                      "num_experts", "moe_intermediate_size", "norm_topk_prob", "decoder_sparse_step", "mlp_only_layers",
-                     "rope_parameters", "layer_types"}
+                     "rope_parameters", "layer_types", "hidden_activation", "query_pre_attn_scalar",
+                     "rope_local_base_freq", "final_logit_softcapping", "attn_logit_softcapping"}
         cfg.extra = {k: v for k, v in d.items() if k not in keys and k not in generated}
         if dense_ffn is not None:
             cfg.extra["dense_intermediate_size"] = dense_ffn
@@ -344,6 +378,11 @@ class LlamaConfig:
     def from_pretrained(cls, path: str) -> "LlamaConfig":
         with open(os.path.join(path, "config.json"), "r", encoding="utf-8") as f:
             return cls.from_hf_dict(json.load(f))
+
+
+def _whole_if_close(x: float):
+    """HuggingFace's Gemma 3 config types query_pre_attn_scalar as an integer."""
+    return int(round(x)) if abs(x - round(x)) < 1e-6 else x
 
 
 # ---------------------------------------------------------------------------------------------- per-family readers
@@ -480,7 +519,56 @@ def _read_hunyuan(mt, d, kw):          # Llama layers with per-head q/k norms be
     kw.update(qk_norm=True, qk_norm_after_rope=True)
 
 
+def _read_gemma(mt, d, kw):            # Llama layers with GeGLU, norm weights stored minus one, scaled embeddings
+    kw.update(mlp_act="gelu_tanh", norm_plus_one=True, embedding_multiplier_rounded=True,
+              embedding_multiplier=float(kw.get("hidden_size", 2048)) ** 0.5)
+    for k in ("final_logit_softcapping", "attn_logit_softcapping"):
+        if d.get(k):
+            raise NotImplementedError(f"{mt} with {k} is not built")
+    if d.get("use_bidirectional_attention"):
+        raise NotImplementedError(f"{mt} with bidirectional attention is not built")
+
+
+# HuggingFace's defaults for Gemma 3 text configs: published text_config blocks list only what differs from them
+_GEMMA3_TEXT_DEFAULTS = dict(vocab_size=262208, hidden_size=2304, intermediate_size=9216, num_hidden_layers=26,
+                             num_attention_heads=8, num_key_value_heads=4, max_position_embeddings=131072,
+                             rms_norm_eps=1e-6, tie_word_embeddings=True, sliding_window=4096, head_dim=256)
+
+
+def _read_gemma3_text(mt, d, kw):      # Gemma with norms behind the branches, per-head q/k norms, windowed layers
+    for k, v in _GEMMA3_TEXT_DEFAULTS.items():
+        if d.get(k) is None:
+            d[k] = v
+            if k != "head_dim":
+                kw[k] = v
+    _read_gemma(mt, d, kw)
+    kw.update(post_norm=True, qk_norm=True)
+    n_layers = int(kw.get("num_hidden_layers", 26))
+    q_scalar = d.get("query_pre_attn_scalar")
+    if q_scalar:
+        kw["attention_multiplier"] = float(q_scalar) ** -0.5
+    types = d.get("layer_types")
+    if types is None:
+        pat = int(d.get("sliding_window_pattern", 6) or 6)
+        types = ["sliding_attention" if (i + 1) % pat else "full_attention" for i in range(n_layers)]
+    if kw.get("sliding_window") is None:
+        kw["sliding_window"] = int(d.get("sliding_window", 4096) or 4096)
+    kw["window_layers"] = [int(t == "sliding_attention") for t in types]
+    rp = d.get("rope_parameters")
+    if isinstance(rp, dict) and ("full_attention" in rp or "sliding_attention" in rp):
+        full, local = dict(rp.get("full_attention") or {}), dict(rp.get("sliding_attention") or {})
+        kw["rope_theta"] = float(full.pop("rope_theta", d.get("rope_theta") or 1_000_000.0))
+        kw["rope_local_theta"] = float(local.get("rope_theta", d.get("rope_local_base_freq") or 10_000.0))
+        kw["rope_scaling"] = full if full.get("rope_type", full.get("type")) not in (None, "default") else None
+        if local.get("rope_type", "default") != "default":
+            raise NotImplementedError("gemma3_text with rope scaling on the windowed layers is not built")
+    else:            # older configs: rope_theta, rope_local_base_freq and rope_scaling (for the global layers) side by side
+        kw["rope_theta"] = float(d.get("rope_theta") or 1_000_000.0)
+        kw["rope_local_theta"] = float(d.get("rope_local_base_freq") or 10_000.0)
+
+
 _FAMILY_READERS = {
+    "gemma": _read_gemma, "gemma3_text": _read_gemma3_text,
     "qwen2": _read_qwen2, "qwen3": _read_qwen3, "qwen3_moe": _read_qwen3_moe, "qwen2_moe": _read_qwen2_moe,
     "mixtral": _read_mixtral, "granitemoe": _read_granite_moe, "granitemoeshared": _read_granite_moe,
     "olmoe": _read_olmoe, "smollm3": _read_smollm3, "olmo2": _read_olmo2, "exaone4": _read_exaone4,

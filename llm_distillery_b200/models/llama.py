@@ -401,11 +401,28 @@ class LlamaModel(nn.Module):
             self._rope_regime = regime
         return self._rope
 
+    def _embedding_scale(self, dtype):
+        m = self.cfg.embedding_multiplier
+        if self.cfg.embedding_multiplier_rounded:       # Gemma keeps the multiplier as a tensor of the model's dtype
+            return torch.tensor(m, dtype=torch.float32).to(dtype).item()
+        return m
+
     def layer_rope(self, cos: torch.Tensor, sin: torch.Tensor) -> list:
         """One (cos, sin) pair per layer: the tables, or the identity rotation (cos 1, sin 0) for layers that apply no
-        positional rotation. The same kernels run either way."""
+        positional rotation, or (Gemma 3) tables of another base for the windowed layers. The same kernels run either
+        way."""
         flags = self.cfg.no_rope_layers
         n = len(self.layers)
+        if self.cfg.rope_local_theta and self.cfg.window_layers:
+            local = getattr(self, "_rope_local", None)
+            if local is None or local[0].shape[0] < cos.shape[0] or local[0].device != cos.device:
+                local = basic.rope_tables(cos.shape[0], self.cfg.rotary_dim, self.cfg.rope_local_theta, cos.device)
+                am = self.cfg.attention_multiplier
+                if am is not None and abs(am * math.sqrt(self.cfg.head_dim) - 1.0) > 1e-9:
+                    amp = math.sqrt(am * math.sqrt(self.cfg.head_dim))       # as for the global tables (``rope``)
+                    local = ((local[0] * amp).contiguous(), (local[1] * amp).contiguous())
+                self._rope_local = local
+            return [local if self.cfg.window_layers[i] else (cos, sin) for i in range(n)]
         if not flags or all(flags):
             return [(cos, sin)] * n
         ident = getattr(self, "_rope_ident", None)
@@ -427,7 +444,7 @@ class LlamaModel(nn.Module):
             pre(self.embed_tokens, False)
         h = EmbeddingFn.apply(ids, self.embed_tokens)
         if cfg.embedding_multiplier != 1.0:
-            h = h * cfg.embedding_multiplier
+            h = h * self._embedding_scale(h.dtype)
         meta = (B, L, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.rms_norm_eps,
                 bool(self.grad_checkpointing and torch.is_grad_enabled()))
         rmul = float(cfg.residual_multiplier)
@@ -444,7 +461,7 @@ class LlamaModel(nn.Module):
                 g = lambda n: getattr(layer, n, None)
                 h = SandwichLayerFn.apply(h, pos, cos, sin,
                                           meta + (2 if cfg.qk_norm_full else 3 if cfg.qk_norm_after_rope
-                                                  else int(cfg.qk_norm), layer.first_param),
+                                                  else int(cfg.qk_norm), layer.first_param, cfg.mlp_act),
                                           layer.qkv_proj, layer.o_proj, layer.gate_up_proj, layer.down_proj,
                                           g("input_layernorm"), g("post_attention_layernorm"), g("attn_out_norm"),
                                           g("mlp_out_norm"), g("qkv_bias"), g("q_norm"), g("k_norm"))
@@ -497,7 +514,7 @@ class LlamaModel(nn.Module):
             pos = torch.arange(c0, c0 + n, dtype=torch.int32, device=dev).repeat(B)
             h = basic.embed_fwd(ids[:, c0:c0 + n].reshape(-1), self.embed_tokens)
             if cfg.embedding_multiplier != 1.0:
-                h = h * cfg.embedding_multiplier
+                h = h * self._embedding_scale(h.dtype)
             for li, (layer, (kc, vc), (cos, sin)) in enumerate(zip(self.layers, caches, tables)):
                 window = cfg.layer_window(li, L)
                 if LAYER_WEIGHTS_PRE[0] is not None:
@@ -570,6 +587,21 @@ class LlamaModel(nn.Module):
         q, kv, f = cfg.q_size, cfg.kv_size, cfg.intermediate_size
         for i, l in enumerate(self.layers):
             pre = f"model.layers.{i}."
+            if cfg.model_type == "gemma3_text":      # Llama's name for the norm in front of the MLP means the one behind attention
+                yield pre + "input_layernorm.weight", l.input_layernorm, None
+                yield pre + "self_attn.q_proj.weight", l.qkv_proj, slice(0, q)
+                yield pre + "self_attn.k_proj.weight", l.qkv_proj, slice(q, q + kv)
+                yield pre + "self_attn.v_proj.weight", l.qkv_proj, slice(q + kv, q + 2 * kv)
+                yield pre + "self_attn.q_norm.weight", l.q_norm, None
+                yield pre + "self_attn.k_norm.weight", l.k_norm, None
+                yield pre + "self_attn.o_proj.weight", l.o_proj, None
+                yield pre + "post_attention_layernorm.weight", l.attn_out_norm, None
+                yield pre + "pre_feedforward_layernorm.weight", l.post_attention_layernorm, None
+                yield pre + "mlp.gate_proj.weight", l.gate_up_proj, slice(0, f)
+                yield pre + "mlp.up_proj.weight", l.gate_up_proj, slice(f, 2 * f)
+                yield pre + "mlp.down_proj.weight", l.down_proj, None
+                yield pre + "post_feedforward_layernorm.weight", l.mlp_out_norm, None
+                continue
             if cfg.model_type in ("olmo2", "exaone4", "glm", "glm4"):
                 glm = cfg.model_type in ("glm", "glm4")
                 if glm:
@@ -689,10 +721,18 @@ class LlamaModel(nn.Module):
                 out[k] = t.reshape(v.shape)
         return out
 
+    @staticmethod
+    def _shift_norm_weights(sd: dict, by: float) -> dict:
+        """Gemma stores every RMSNorm weight minus one (the module multiplies by 1 + w): this model keeps the factor."""
+        return {k: (v + by if k.endswith("norm.weight") else v) for k, v in sd.items()}
+
     def to_hf_state_dict(self) -> dict[str, torch.Tensor]:
+        sd = self._to_hf_state_dict()
         if self.cfg.rope_interleaved:
-            return self._permute_rotary_rows(self._to_hf_state_dict(), to_checkpoint=True)
-        return self._to_hf_state_dict()
+            sd = self._permute_rotary_rows(sd, to_checkpoint=True)
+        if self.cfg.norm_plus_one:
+            sd = self._shift_norm_weights(sd, -1.0)
+        return sd
 
     def _to_hf_state_dict(self) -> dict[str, torch.Tensor]:
         if self.quant is None:
@@ -723,8 +763,18 @@ class LlamaModel(nn.Module):
     def load_hf_state_dict(self, sd: dict[str, torch.Tensor], strict: bool = True) -> None:
         if self.cfg.num_local_experts and any(k.endswith("mlp.experts.gate_up_proj") for k in sd):
             sd = self._unstack_experts(sd)
+        wrapped = [k for k in sd if "language_model" in k and k.endswith("embed_tokens.weight")]
+        if wrapped:
+            # a multimodal wrapper (Gemma 3): the language model's tensors under their plain names, the rest left out.
+            # Releases of the wrapper differ in the prefix (language_model.model. / model.language_model. / ...)
+            prefix = wrapped[0][: -len("embed_tokens.weight")]
+            plain = {"model." + k[len(prefix):]: v for k, v in sd.items() if k.startswith(prefix)}
+            plain.update({"lm_head.weight": v for k, v in sd.items() if k.endswith("lm_head.weight")})
+            sd = plain
         if self.cfg.rope_interleaved:
             sd = self._permute_rotary_rows(sd, to_checkpoint=False)
+        if self.cfg.norm_plus_one:
+            sd = self._shift_norm_weights(sd, 1.0)
         seen = set()
         for n, p, sl in self.named_hf_parameters():
             if n not in sd:

@@ -5,7 +5,8 @@
 
 OLMo 2 has only the output norms and normalises the whole query / key projections (one RMSNorm over all heads) before
 the rotation; GLM-4 (0414) has all four norms; HunYuan is a plain pre-norm layer whose per-head q/k norms come AFTER
-the rotation (the norm's weight does not commute with it), which the fused layer of ``llama.py`` does not do. The
+the rotation (the norm's weight does not commute with it), which the fused layer of ``llama.py`` does not do; Gemma's
+gate activation is GELU. The
 reference trains such students through ``AutoModelForCausalLM`` (classes/student/model.py:194-201). One autograd node with an explicit backward, built from the same kernels as
 ``llama.DecoderLayerFn`` (tcgen05 GEMMs with the SwiGLU epilogues, RMSNorm, RoPE, flash attention); the residual adds
 that the plain layer folds into GEMM epilogues are separate here because a norm sits between the GEMM and the add.
@@ -28,7 +29,7 @@ def _qk_full_fwd(qkv, w_qn, w_kn, q, kv, eps):
 
 
 def _forward(h, pos, cos, sin, meta, w_qkv, w_o, w_gu, w_d, w_ln1, w_ln2, w_pa, w_pm, b_qkv, w_qn, w_kn):
-    B, L, H, Hkv, d, eps, _recompute, window, qk_mode, _first = meta
+    B, L, H, Hkv, d, eps, _recompute, window, qk_mode, _first, act_fn = meta
     q, kv = H * d, Hkv * d
     r1 = r2 = ra = rm = None
     x1 = h
@@ -60,7 +61,7 @@ def _forward(h, pos, cos, sin, meta, w_qkv, w_o, w_gu, w_d, w_ln1, w_ln2, w_pa, 
     x2 = h1
     if w_ln2 is not None:
         x2, _, r2 = basic.rmsnorm_fwd(h1, w_ln2, eps)
-    gu, act = basic.linear_swiglu_fwd(x2, w_gu)
+    gu, act = basic.linear_glu_fwd(x2, w_gu, act_fn)
     if w_pm is None:
         m = None
         h2 = basic.linear_fwd(act, w_d, residual=h1)
@@ -73,8 +74,8 @@ def _forward(h, pos, cos, sin, meta, w_qkv, w_o, w_gu, w_d, w_ln1, w_ln2, w_pa, 
 
 class SandwichLayerFn(torch.autograd.Function):
     """meta = (B, L, heads, kv heads, head dim, eps, recompute in backward, sliding window or None, q/k norm: 0 none / 1 per head / 2 over the
-    whole projection / 3 per head after the rotation, the layer's first parameter). Norm weights that the family does
-    not have are None."""
+    whole projection / 3 per head after the rotation, the layer's first parameter, the gate's activation). Norm weights
+    that the family does not have are None."""
 
     @staticmethod
     def forward(ctx, h, pos, cos, sin, meta, w_qkv, w_o, w_gu, w_d, w_ln1=None, w_ln2=None, w_pa=None, w_pm=None,
@@ -96,7 +97,7 @@ class SandwichLayerFn(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dh2):
-        B, L, H, Hkv, d, eps, recompute, window, qk_mode, first = ctx.meta
+        B, L, H, Hkv, d, eps, recompute, window, qk_mode, first, act_fn = ctx.meta
         w_qkv, w_o, w_gu, w_d, w_ln1, w_ln2, w_pa, w_pm, b_qkv, w_qn, w_kn = ctx.weights
         s_qkv, s_o, s_gu, s_d, s_ln1, s_ln2, s_pa, s_pm, s_b, s_qn, s_kn = ctx.slots
         q, kv = H * d, Hkv * d
@@ -121,7 +122,7 @@ class SandwichLayerFn(torch.autograd.Function):
             dm, dw = basic.rmsnorm_bwd(dh2, m, w_pm, rm)
             g_pm = _ll._vec_grad(dw, w_pm, s_pm)
         g_d = _ll._wgrad(dm, act, w_d, s_d)
-        dgu = basic.linear_dgrad_swiglu_bwd(dm, w_d, gu)
+        dgu = basic.linear_dgrad_glu_bwd(dm, w_d, gu, act_fn)
         g_gu = _ll._wgrad(dgu, x2, w_gu, s_gu)
         dx2 = basic.linear_dgrad(dgu, w_gu)
         del dgu
@@ -206,7 +207,7 @@ def layer_inference(layer, cfg, h, qkv_hook, eps):
     x2 = h1
     if cfg.pre_norm:
         x2, _, _ = basic.rmsnorm_fwd(h1, layer.post_attention_layernorm, eps)
-    _, act = basic.linear_swiglu_fwd(x2, layer.gate_up_proj)
+    _, act = basic.linear_glu_fwd(x2, layer.gate_up_proj, cfg.mlp_act)
     if cfg.post_norm:
         m, _, _ = basic.rmsnorm_fwd(basic.linear_fwd(act, layer.down_proj), layer.mlp_out_norm, eps)
         return h1 + m

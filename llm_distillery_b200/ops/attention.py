@@ -10,7 +10,8 @@ restatement below, which is also the oracle of the GPU tests.
 Sliding-window layers (Mistral v0.1, Phi-3, the windowed layers of hybrid models): a query at position i sees the
 keys j with i - window < j <= i. Up to ``window`` positions that IS causal attention and the paths above run. Longer
 sequences take ``windowed_fwd`` / ``windowed_bwd`` below: PyTorch's scaled-dot-product attention under a band mask, on
-either device - the flash kernels have no window, so this case is exact but runs at the library's speed.
+either device - the flash kernels have no window, so this case is exact but runs at the library's speed. The same
+path, without a window, serves heads of other sizes than 64 and 128 on a GPU (Gemma's 256).
 """
 from __future__ import annotations
 
@@ -66,6 +67,11 @@ def attention_reference_bwd(dout, qkv, out, lse, B, L, H, Hkv, d):
     return dqkv.to(qkv.dtype)
 
 
+def _library_path(qkv: torch.Tensor, d: int) -> bool:
+    """Heads the flash kernels do not take (they take 64 and 128) go to the library path on a GPU, e.g. Gemma's 256."""
+    return qkv.is_cuda and d not in (64, 128)
+
+
 def _band_mask(n_q: int, n_k: int, q_off: int, window: int, device) -> torch.Tensor:
     """[n_q, n_k] bool: key j visible to the query at position q_off + i."""
     qi = torch.arange(q_off, q_off + n_q, device=device)[:, None]
@@ -73,18 +79,19 @@ def _band_mask(n_q: int, n_k: int, q_off: int, window: int, device) -> torch.Ten
     return (kj <= qi) & (kj > qi - window)
 
 
-def _sdpa_banded(q, k, v, q_off: int, window: int):
-    """q [B, n_q, H, d], k / v [B, n_k, Hkv, d] -> [B, n_q, H, d]."""
-    mask = _band_mask(q.shape[1], k.shape[1], q_off, window, q.device)
+def _sdpa_banded(q, k, v, q_off: int, window: int | None):
+    """q [B, n_q, H, d], k / v [B, n_k, Hkv, d] -> [B, n_q, H, d]; ``window`` None: causal without a window."""
+    causal = window is None and q_off == 0 and q.shape[1] == k.shape[1]       # plain causal: no mask tensor needed
+    mask = None if causal else _band_mask(q.shape[1], k.shape[1], q_off, window or (q_off + q.shape[1]), q.device)
     g = q.shape[2] // k.shape[2]
     if g > 1:          # grouped queries: the key / value heads are repeated (differentiated through, in the backward)
         k, v = k.repeat_interleave(g, dim=2), v.repeat_interleave(g, dim=2)
     o = torch.nn.functional.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
-                                                         attn_mask=mask)
+                                                         attn_mask=mask, is_causal=causal)
     return o.transpose(1, 2)
 
 
-def windowed_fwd(qkv, B, L, H, Hkv, d, window: int):
+def windowed_fwd(qkv, B, L, H, Hkv, d, window: int | None):
     """Sliding-window attention of sequences longer than the window. Returns (out, lse placeholder): the backward
     below recomputes instead of using the log-sum-exp."""
     q, k, v = _split(qkv, B, L, H, Hkv, d)
@@ -92,7 +99,7 @@ def windowed_fwd(qkv, B, L, H, Hkv, d, window: int):
     return o, torch.zeros((H, B * L), dtype=torch.float32, device=qkv.device)
 
 
-def windowed_bwd(dout, qkv, B, L, H, Hkv, d, window: int):
+def windowed_bwd(dout, qkv, B, L, H, Hkv, d, window: int | None):
     """dqkv of ``windowed_fwd`` by differentiating its recomputation."""
     with torch.enable_grad():
         q, k, v = (t.detach().requires_grad_(True) for t in _split(qkv, B, L, H, Hkv, d))
@@ -103,7 +110,9 @@ def windowed_bwd(dout, qkv, B, L, H, Hkv, d, window: int):
 
 def attention_fwd(qkv: torch.Tensor, B: int, L: int, H: int, Hkv: int, d: int, window: int | None = None):
     """Returns (out [T, H*d], lse [H, T] fp32). ``window``: the layer's sliding window, or None."""
-    if window is not None and L > window:
+    if window is not None and L <= window:
+        window = None
+    if window is not None or _library_path(qkv, d):
         return windowed_fwd(qkv, B, L, H, Hkv, d, window)
     if not qkv.is_cuda:
         return attention_reference_fwd(qkv, B, L, H, Hkv, d)
@@ -113,7 +122,9 @@ def attention_fwd(qkv: torch.Tensor, B: int, L: int, H: int, Hkv: int, d: int, w
 
 def attention_bwd(dout, qkv, out, lse, B, L, H, Hkv, d, window: int | None = None):
     """Returns dqkv with the layout of qkv."""
-    if window is not None and L > window:
+    if window is not None and L <= window:
+        window = None
+    if window is not None or _library_path(qkv, d):
         return windowed_bwd(dout, qkv, B, L, H, Hkv, d, window)
     if not qkv.is_cuda:
         return attention_reference_bwd(dout, qkv, out, lse, B, L, H, Hkv, d)
@@ -126,7 +137,9 @@ def attention_bwd_unrotated(dout, qkv, out, lse, B, L, H, Hkv, d, pos, cos, sin,
     inverse rotation of the query and key heads. On the GPU the query heads are rotated where their fp32 accumulator is
     converted to bf16 (one pass less over 8/9 of the rotated columns); same values as ``attention_bwd`` + ``rope_``."""
     from . import basic
-    if window is not None and L > window:
+    if window is not None and L <= window:
+        window = None
+    if window is not None or _library_path(qkv, d):
         return basic.rope_(windowed_bwd(dout, qkv, B, L, H, Hkv, d, window), pos, cos, sin, H + Hkv, d, inverse=True)
     if (qkv.is_cuda and qkv.dtype == torch.bfloat16 and pos.dtype == torch.int32 and cos.is_contiguous()
             and sin.is_contiguous() and 2 * cos.shape[1] == d):      # partial rotary: the separate kernel below
@@ -157,7 +170,9 @@ def attention_fwd_cached(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
                          H: int, Hkv: int, d: int, window: int | None = None) -> torch.Tensor:
     """Attention of one prefill chunk against the key / value caches (which already contain the chunk's own keys and
     values at rows q_off .. q_off+L-1). Inference only: no log-sum-exp is kept."""
-    if window is not None and q_off + L > window:
+    if window is not None and q_off + L <= window:
+        window = None
+    if window is not None or _library_path(qkv, d):
         n = q_off + L
         q = qkv[:, : H * d].reshape(B, L, H, d)
         k = k_cache[:, :n].reshape(B, n, Hkv, d)

@@ -181,7 +181,7 @@ def headnorm_fwd(qkv: torch.Tensor, wq: torch.Tensor, wk: torch.Tensor, n_q: int
     applied before the rotary embedding); value heads are copied. Returns (normalised copy, rstd [T, n_q + n_kv])."""
     T = qkv.shape[0]
     nn = n_q + n_kv
-    if not _native(qkv):
+    if not _native(qkv) or head_dim not in (64, 128):        # the kernels take heads of 64 and 128; others: PyTorch ops
         x = qkv.float().view(T, n_q + 2 * n_kv, head_dim)
         rstd = torch.rsqrt(x[:, :nn].pow(2).mean(-1) + eps)
         w = torch.cat([wq.float().expand(n_q, -1), wk.float().expand(n_kv, -1)])          # [nn, d]
@@ -202,7 +202,7 @@ def headnorm_bwd_(g: torch.Tensor, qkv_raw: torch.Tensor, wq: torch.Tensor, wk: 
     Returns (dwq, dwk) fp32 [d] each."""
     T = g.shape[0]
     nn = n_q + n_kv
-    if not _native(g):
+    if not _native(g) or head_dim not in (64, 128):
         gv = g.float().view(T, n_q + 2 * n_kv, head_dim)
         x = qkv_raw.float().view(T, n_q + 2 * n_kv, head_dim)[:, :nn]
         w = torch.cat([wq.float().expand(n_q, -1), wk.float().expand(n_kv, -1)])
@@ -462,6 +462,48 @@ def swiglu_bwd(gu: torch.Tensor, dact: torch.Tensor) -> torch.Tensor:
     _lib.check(_lib.kernels().b200_swiglu_bwd(_lib.ptr(gu), _lib.ptr(dact), _lib.ptr(dgu), T, f, _lib.stream()),
                "b200_swiglu_bwd")
     return dgu
+
+
+# ------------------------------------------------------------------------------------------------ GeGLU (Gemma)
+def glu_fwd(gu: torch.Tensor, act: str = "silu") -> torch.Tensor:
+    """act(gate) * up of fused rows [T, 2f]. ``silu``: the SwiGLU kernel; ``gelu_tanh`` (Gemma's GeGLU): PyTorch's
+    elementwise ops on either device - no kernel of this library covers it."""
+    if act == "silu":
+        return swiglu_fwd(gu)
+    if act != "gelu_tanh":
+        raise NotImplementedError(f"gated activation {act!r} is not built (silu and gelu_tanh are)")
+    f = gu.shape[1] // 2
+    return (F.gelu(gu[:, :f].float(), approximate="tanh") * gu[:, f:].float()).to(gu.dtype)
+
+
+def glu_bwd(gu: torch.Tensor, dact: torch.Tensor, act: str = "silu") -> torch.Tensor:
+    """Gradient of ``glu_fwd`` with respect to the fused rows."""
+    if act == "silu":
+        return swiglu_bwd(gu, dact)
+    if act != "gelu_tanh":
+        raise NotImplementedError(f"gated activation {act!r} is not built (silu and gelu_tanh are)")
+    f = gu.shape[1] // 2
+    up, d = gu[:, f:].float(), dact.float()
+    with torch.enable_grad():
+        g = gu[:, :f].detach().float().requires_grad_(True)
+        y = F.gelu(g, approximate="tanh")
+        (dg,) = torch.autograd.grad(y, g, d * up)
+    return torch.cat([dg, d * y.detach()], dim=1).to(gu.dtype)
+
+
+def linear_glu_fwd(x: torch.Tensor, w_gu: torch.Tensor, act: str = "silu"):
+    """(gu, act(gate) * up) of x w_gu^T: ``linear_swiglu_fwd`` for silu, projection + ``glu_fwd`` otherwise."""
+    if act == "silu":
+        return linear_swiglu_fwd(x, w_gu)
+    gu = linear_fwd(x, w_gu)
+    return gu, glu_fwd(gu, act)
+
+
+def linear_dgrad_glu_bwd(dy: torch.Tensor, w_d: torch.Tensor, gu: torch.Tensor, act: str = "silu") -> torch.Tensor:
+    """dgu through the down projection and the gated activation: ``linear_dgrad_swiglu_bwd`` for silu."""
+    if act == "silu":
+        return linear_dgrad_swiglu_bwd(dy, w_d, gu)
+    return glu_bwd(gu, linear_dgrad(dy, w_d), act)
 
 
 # ------------------------------------------------------------------------------------------------ embedding

@@ -133,6 +133,9 @@ FAMILIES = {
     "exaone4, windowed and global layers": dict(model_type="exaone4", pre_norm=False, post_norm=True, qk_norm=True,
                                                 no_rope_layers=[1, 0], window_layers=[1, 0], sliding_window=48),
     "mistral, window shorter than the context": dict(model_type="mistral", sliding_window=40),
+    "gemma3_text": dict(model_type="gemma3_text", mlp_act="gelu_tanh", norm_plus_one=True, embedding_multiplier=8.0,
+                        embedding_multiplier_rounded=True, post_norm=True, qk_norm=True, sliding_window=40,
+                        window_layers=[1, 0], rope_local_theta=10000.0, head_dim_override=32, tie_word_embeddings=True),
     "helium": dict(model_type="helium", rope_interleaved=True),
     "ernie4_5": dict(model_type="ernie4_5", rope_interleaved=True),
     "seed_oss": dict(model_type="seed_oss", attention_bias=True, head_dim_override=32),

@@ -394,6 +394,10 @@ _MORE = {   # family: (HuggingFace model, config, extra config keys, (pre_norm, 
                          dict(head_dim=16, rope_parameters={"rope_type": "dynamic", "alpha": 50.0, "factor": 1.0,
                                                             "rope_theta": 10000.0}),
                          (True, False, False, True), True),
+    "gemma": ("GemmaForCausalLM", "GemmaConfig", dict(head_dim=32), (True, False, False, False), True),
+    "gemma3_text": ("Gemma3ForCausalLM", "Gemma3TextConfig",
+                    dict(head_dim=32, sliding_window=24, sliding_window_pattern=2, query_pre_attn_scalar=48),
+                    (True, True, False, True), True),
     "seed_oss": ("SeedOssForCausalLM", "SeedOssConfig", dict(head_dim=32, attention_dropout=0.0, residual_dropout=0.0),
                  (True, False, False, False), False),
 }
@@ -402,13 +406,16 @@ _MORE = {   # family: (HuggingFace model, config, extra config keys, (pre_norm, 
 @pytest.mark.parametrize("family,recompute", [("olmo2", False), ("olmo2", True), ("glm", False), ("glm4", False),
                                               ("glm4", True), ("exaone4", False), ("exaone4 hybrid", True),
                                               ("helium", False), ("ernie4_5", False), ("seed_oss", False),
-                                              ("hunyuan_v1_dense", False), ("hunyuan_v1_dense", True)])
+                                              ("hunyuan_v1_dense", False), ("hunyuan_v1_dense", True),
+                                              ("gemma", False), ("gemma3_text", False), ("gemma3_text", True)])
 def test_more_decoder_families_match_huggingface(tmp_path, family, recompute):
     """OLMo 2 (norms behind the branches only, q/k norms over the whole projections), EXAONE 4 (the same placement with
     per-head q/k norms; hybrid checkpoints: windowed layers rotate, global ones do not), GLM (half of each head rotates,
     rotary pairs neighbours in the checkpoint, fused gate/up tensor, q/k/v bias), GLM-4 0414 (GLM with norms behind
     the branches as well), Helium and ERNIE 4.5 (Llama layers, rotary pairs neighbours), Seed-OSS (q/k/v bias and an
-    explicit head_dim), HunYuan (per-head q/k norms behind the rotation, a base scaled by a fixed alpha): logits, every gradient, the chunked inference path and checkpoints both ways."""
+    explicit head_dim), HunYuan (per-head q/k norms behind the rotation, a base scaled by a fixed alpha), Gemma (GeGLU,
+    norm weights stored minus one, scaled embeddings) and Gemma 3 text (Gemma with four norms per layer, per-head q/k
+    norms, windowed layers with a rotary base of their own - the 48 positions are twice its window): logits, every gradient, the chunked inference path and checkpoints both ways."""
     cls_n, ccls_n, extra, flags, general = _MORE[family]
     cls, ccls = getattr(tr, cls_n), getattr(tr, ccls_n)
     mt = family.split()[0]
@@ -432,6 +439,11 @@ def test_more_decoder_families_match_huggingface(tmp_path, family, recompute):
         assert cfg.rope_interleaved and cfg.partial_rotary_factor == 1.0 and not cfg.attention_bias
     if mt == "seed_oss":
         assert cfg.attention_bias and not cfg.o_bias and cfg.head_dim == 32 and not cfg.rope_interleaved
+    if mt == "gemma3_text":
+        assert cfg.window_layers == [1, 0] and cfg.sliding_window == 24 and cfg.rope_local_theta == 10000.0
+        assert cfg.rope_theta == 1e6 and abs(cfg.attention_multiplier - 48 ** -0.5) < 1e-12
+    if mt in ("gemma", "gemma3_text"):
+        assert cfg.mlp_act == "gelu_tanh" and cfg.norm_plus_one and cfg.embedding_multiplier == 8.0
     if family == "exaone4 hybrid":
         assert cfg.no_rope_layers == [1, 0] and cfg.sliding_window == 64
     elif mt == "exaone4":
@@ -586,6 +598,12 @@ def test_every_model_type_survives_config_round_trips():
                         sliding_window=128),
         "helium": dict(rope_interleaved=True), "ernie4_5": dict(rope_interleaved=True),
         "seed_oss": dict(attention_bias=True, head_dim_override=32),
+        "gemma": dict(mlp_act="gelu_tanh", norm_plus_one=True, embedding_multiplier_rounded=True, embedding_multiplier=8.0,
+                      head_dim_override=32),
+        "gemma3_text": dict(mlp_act="gelu_tanh", norm_plus_one=True, embedding_multiplier_rounded=True,
+                            embedding_multiplier=8.0, head_dim_override=32, post_norm=True, qk_norm=True,
+                            sliding_window=24, window_layers=[1, 0], rope_local_theta=10000.0,
+                            attention_multiplier=48 ** -0.5),
         "hunyuan_v1_dense": dict(qk_norm=True, qk_norm_after_rope=True,
                                  rope_scaling={"rope_type": "dynamic", "alpha": 1000.0, "factor": 1.0}),
     }
@@ -631,8 +649,17 @@ def test_published_configs_parse_to_the_published_sizes():
             continue
         cfg = LlamaConfig.from_hf_dict(d)
         assert abs(cfg.num_params() / 1e9 - want[name]) < 0.006, (name, cfg.num_params())
-        assert cfg.head_dim in (64, 128) and cfg.rotary_dim % 16 == 0, name       # what the GPU kernels take
+        assert cfg.head_dim in (64, 128) and cfg.rotary_dim % 16 == 0, name       # what the flash kernels take
         assert LlamaConfig.from_hf_dict(cfg.to_hf_dict()).num_params() == cfg.num_params()
+    g = LlamaConfig.from_hf_dict({"architectures": ["Gemma3ForCausalLM"], "attention_bias": False, "head_dim": 256,
+                                  "hidden_activation": "gelu_pytorch_tanh", "hidden_size": 1152, "intermediate_size": 6912,
+                                  "max_position_embeddings": 32768, "model_type": "gemma3_text", "num_attention_heads": 4,
+                                  "num_hidden_layers": 26, "num_key_value_heads": 1, "query_pre_attn_scalar": 256,
+                                  "rms_norm_eps": 1e-06, "rope_local_base_freq": 10000, "rope_scaling": None,
+                                  "rope_theta": 1000000, "sliding_window": 512, "sliding_window_pattern": 6,
+                                  "vocab_size": 262144, "final_logit_softcapping": None, "attn_logit_softcapping": None})
+    assert abs(g.num_params() / 1e9 - 1.00) < 0.006 and g.window_layers.count(0) == 4 and g.rope_local_theta == 10000.0
+    g.check_gpu_kernels()                                        # heads of 256 run, on PyTorch's attention
     assert LlamaConfig.from_hf_dict(_PUBLISHED["phi-4-mini"]).rotary_dim == 96
     assert LlamaConfig.from_hf_dict(_PUBLISHED["mistral-7b-v0.1"]).sliding_window == 4096
     assert LlamaConfig.from_hf_dict(_PUBLISHED["qwen2.5-7b"]).sliding_window is None
@@ -642,7 +669,48 @@ def test_published_configs_parse_to_the_published_sizes():
 def test_shapes_outside_the_gpu_kernels_are_named_before_any_launch():
     LlamaConfig(**_base(hidden_size=256, num_attention_heads=4)).check_gpu_kernels()                  # head_dim 64
     LlamaConfig(**_base(hidden_size=256, num_attention_heads=2, partial_rotary_factor=0.75)).check_gpu_kernels()
-    with pytest.raises(NotImplementedError, match="head_dim 16.*rotary width 8"):
+    with pytest.raises(NotImplementedError, match="rotary width 8"):
         LlamaConfig(**_base(partial_rotary_factor=0.5)).check_gpu_kernels()
+    with pytest.raises(NotImplementedError, match="head_dim 24.*rotary width 24"):
+        LlamaConfig(**_base(hidden_size=96)).check_gpu_kernels()
+    LlamaConfig(**_base(hidden_size=1024, head_dim_override=256)).check_gpu_kernels()     # PyTorch's attention
     with pytest.raises(NotImplementedError, match="intermediate_size 100"):
         LlamaConfig(**_base(hidden_size=256, num_attention_heads=4, intermediate_size=100)).check_gpu_kernels()
+
+
+def test_gemma3_multimodal_wrapper_loads_as_its_language_model(tmp_path):
+    """A Gemma 3 checkpoint with a vision tower: the text_config block (which lists only what differs from
+    HuggingFace's defaults) and the language model's tensors are read; the result is a text-only Gemma 3."""
+    text = dict(hidden_size=64, intermediate_size=136, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                head_dim=32, vocab_size=320, sliding_window=24, sliding_window_pattern=2, max_position_embeddings=256,
+                rope_scaling={"rope_type": "linear", "factor": 8.0})
+    vision = dict(hidden_size=32, intermediate_size=64, num_hidden_layers=1, num_attention_heads=2, image_size=28,
+                  patch_size=14)
+    torch.manual_seed(9)
+    hf = tr.Gemma3ForConditionalGeneration(tr.Gemma3Config(text_config=text, vision_config=vision, mm_tokens_per_image=4,
+                                                           attn_implementation="eager")).float()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if "norm" in n:
+                p.uniform_(-0.3, 0.3)
+    hf.save_pretrained(str(tmp_path / "hf"), safe_serialization=True)
+    hf.eval()
+    model = load_hf_model(str(tmp_path / "hf"), dtype=torch.float32)
+    cfg = model.cfg
+    assert cfg.model_type == "gemma3_text" and cfg.head_dim == 32 and cfg.window_layers == [1, 0]
+    assert cfg.rope_scaling["factor"] == 8.0 and cfg.rope_local_theta == 10000.0 and cfg.rope_theta == 1e6
+    x = torch.randint(1, 320, (2, 60))
+    with torch.no_grad():
+        ref = hf(input_ids=x).logits
+        assert torch.allclose(model(x), ref, atol=4e-4, rtol=1e-3), (model(x) - ref).abs().max()
+    # a published text_config names only a few keys: the rest are HuggingFace's defaults, not this model's
+    big = LlamaConfig.from_hf_dict({"model_type": "gemma3", "text_config": {
+        "hidden_size": 2560, "intermediate_size": 10240, "model_type": "gemma3_text", "num_hidden_layers": 34,
+        "rope_scaling": {"factor": 8.0, "rope_type": "linear"}, "sliding_window": 1024}})
+    assert (big.vocab_size, big.num_attention_heads, big.num_key_value_heads, big.head_dim) == (262208, 8, 4, 256)
+    assert big.window_layers.count(0) == 5 and big.embedding_multiplier == 2560 ** 0.5 and big.tie_word_embeddings
+    assert abs(big.num_params() / 1e9 - 3.88) < 0.01             # the 4B checkpoint's language model
+    save_hf_model(model, str(tmp_path / "ours"))
+    hf2 = tr.AutoModelForCausalLM.from_pretrained(str(tmp_path / "ours"), torch_dtype=torch.float32,
+                                                  attn_implementation="eager")
+    assert type(hf2) is tr.Gemma3ForCausalLM and torch.allclose(hf2(x).logits, ref, atol=4e-4, rtol=1e-3)

@@ -71,7 +71,7 @@ def test_engine_trains_the_bias():
 @pytest.mark.gpu
 @pytest.mark.parametrize("variant", ["qwen2", "qwen3", "llama with biases", "plain llama, long batch", "granite",
                                      "plain partial rotary, long batch", "olmo2", "glm4, long batch",
-                                     "hunyuan"])
+                                     "hunyuan", "gemma3, heads of 256", "mistral beyond its window"])
 def test_gpu_kernels_follow_the_cpu_model(variant):
     """bf16 kernels (GEMMs with their epilogues, bias add, per-head norms, RoPE, flash attention ...) against the fp32 CPU
     statement of the same model, for the layer variants: q/k/v bias (Qwen2), per-head q/k norms (Qwen3), biases on every
@@ -88,6 +88,13 @@ def test_gpu_kernels_follow_the_cpu_model(variant):
         kw.update(attention_bias=True, o_bias=True, mlp_bias=True)
     elif "partial rotary" in variant:
         kw.update(partial_rotary_factor=0.75)
+    elif variant.startswith("gemma3"):        # heads of 256: PyTorch's attention and per-head norms; GeGLU; two rotary bases
+        kw.update(model_type="gemma3_text", num_attention_heads=2, num_key_value_heads=1, head_dim_override=256,
+                  hidden_size=256, mlp_act="gelu_tanh", norm_plus_one=True, embedding_multiplier=16.0,
+                  embedding_multiplier_rounded=True, post_norm=True, qk_norm=True, sliding_window=64,
+                  window_layers=[1, 0], rope_local_theta=10000.0, tie_word_embeddings=True)
+    elif variant.startswith("mistral"):
+        kw.update(model_type="mistral", sliding_window=48)
     elif variant == "hunyuan":
         kw.update(model_type="hunyuan_v1_dense", qk_norm=True, qk_norm_after_rope=True)
     elif variant == "olmo2":
