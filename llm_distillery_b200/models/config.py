@@ -167,103 +167,23 @@ class LlamaConfig:
         shared_f = d.pop("shared_expert_intermediate_size")
         d.pop("shared_expert_gated")
         gran = {k: d.pop(k) for k in ("embedding_multiplier", "attention_multiplier", "residual_multiplier", "logits_scaling")}
-        if self.model_type == "qwen3_moe":      # HuggingFace's names: num_experts, moe_intermediate_size, norm_topk_prob
-            d.update(architectures=["Qwen3MoeForCausalLM"], hidden_act="silu", torch_dtype="bfloat16",
-                     use_sliding_window=self.sliding_window is not None, head_dim=self.head_dim, num_experts=d.pop("num_local_experts"),
-                     moe_intermediate_size=self.intermediate_size, norm_topk_prob=bool(renorm), decoder_sparse_step=1,
-                     mlp_only_layers=[])
-            d["intermediate_size"] = extra.pop("dense_intermediate_size", self.intermediate_size)
-        elif self.model_type == "qwen2_moe":
-            d.pop("attention_bias")
-            d.update(architectures=["Qwen2MoeForCausalLM"], hidden_act="silu", torch_dtype="bfloat16",
-                     use_sliding_window=self.sliding_window is not None, num_experts=d.pop("num_local_experts"), qkv_bias=True,
-                     moe_intermediate_size=self.intermediate_size, shared_expert_intermediate_size=shared_f,
-                     norm_topk_prob=bool(renorm), decoder_sparse_step=1, mlp_only_layers=[])
-            d["intermediate_size"] = extra.pop("dense_intermediate_size", self.intermediate_size)
-        elif self.model_type == "gemma":
-            d.update(architectures=["GemmaForCausalLM"], hidden_act="gelu_pytorch_tanh", hidden_activation="gelu_pytorch_tanh",
-                     torch_dtype="bfloat16", attention_bias=False, head_dim=self.head_dim)
-        elif self.model_type == "gemma3_text":
-            d.pop("attention_bias")
-            d.pop("rope_theta")
-            rope_full = dict(self.rope_scaling or {"rope_type": "default"}, rope_theta=self.rope_theta)
-            d.pop("rope_scaling", None)
-            d.update(architectures=["Gemma3ForCausalLM"], hidden_activation="gelu_pytorch_tanh", torch_dtype="bfloat16",
-                     head_dim=self.head_dim, query_pre_attn_scalar=_whole_if_close(1.0 / gran["attention_multiplier"] ** 2)
-                     if gran["attention_multiplier"] else self.head_dim,
-                     layer_types=["sliding_attention" if (win_layers is None or win_layers[i]) and self.sliding_window
-                                  else "full_attention" for i in range(self.num_hidden_layers)],
-                     rope_parameters={"full_attention": rope_full,
-                                      "sliding_attention": {"rope_type": "default",
-                                                            "rope_theta": self.rope_local_theta or self.rope_theta}},
-                     final_logit_softcapping=None, attn_logit_softcapping=None)
-        elif self.model_type == "olmoe":
-            d.update(architectures=["OlmoeForCausalLM"], hidden_act="silu", torch_dtype="bfloat16", attention_bias=False,
-                     num_experts=d.pop("num_local_experts"), norm_topk_prob=bool(renorm), clip_qkv=None)
-        elif self.model_type == "olmo2":
-            d.update(architectures=["Olmo2ForCausalLM"], hidden_act="silu", torch_dtype="bfloat16", attention_bias=False)
-        elif self.model_type == "exaone4":
-            d.pop("attention_bias")
-            d.update(architectures=["Exaone4ForCausalLM"], hidden_act="silu", torch_dtype="bfloat16",
-                     sliding_window=self.sliding_window,
-                     layer_types=["sliding_attention" if (nope and nope[i]) else "full_attention"
-                                  for i in range(self.num_hidden_layers)])
-        elif self.model_type == "hunyuan_v1_dense":
-            d.update(architectures=["HunYuanDenseV1ForCausalLM"], hidden_act="silu", torch_dtype="bfloat16",
-                     attention_bias=False, head_dim=self.head_dim)
-        elif self.model_type == "helium":
-            d.update(architectures=["HeliumForCausalLM"], hidden_act="silu", torch_dtype="bfloat16", mlp_bias=False,
-                     head_dim=self.head_dim)
-        elif self.model_type == "ernie4_5":
-            d.pop("attention_bias")
-            d.update(architectures=["Ernie4_5ForCausalLM"], hidden_act="silu", torch_dtype="bfloat16", use_bias=False,
-                     head_dim=self.head_dim)
-        elif self.model_type == "seed_oss":
-            d.update(architectures=["SeedOssForCausalLM"], hidden_act="silu", torch_dtype="bfloat16", mlp_bias=False,
-                     attention_out_bias=False, head_dim=self.head_dim)
-        elif self.model_type in ("glm", "glm4"):
-            d.update(architectures=["GlmForCausalLM" if self.model_type == "glm" else "Glm4ForCausalLM"],
-                     hidden_act="silu", torch_dtype="bfloat16", head_dim=self.head_dim,
-                     partial_rotary_factor=self.partial_rotary_factor)
-        elif self.model_type == "smollm3":
-            d.update(architectures=["SmolLM3ForCausalLM"], hidden_act="silu", torch_dtype="bfloat16", mlp_bias=False,
-                     use_sliding_window=self.sliding_window is not None, no_rope_layers=list(nope or [1] * self.num_hidden_layers))
-        elif self.model_type == "qwen3":
-            d.update(architectures=["Qwen3ForCausalLM"], hidden_act="silu", torch_dtype="bfloat16",
-                     use_sliding_window=self.sliding_window is not None, head_dim=self.head_dim)
-        elif self.model_type == "mixtral":
-            d.pop("attention_bias")
-            d.update(architectures=["MixtralForCausalLM"], hidden_act="silu", torch_dtype="bfloat16")
-        elif self.model_type == "phi3":
-            d.pop("attention_bias")
-            d.update(architectures=["Phi3ForCausalLM"], hidden_act="silu", torch_dtype="bfloat16")
-        elif self.attention_bias and not self.o_bias:     # q/k/v bias without o_proj bias is the Qwen2 layout in HuggingFace terms
-            d.pop("attention_bias")
-            d.update(architectures=["Qwen2ForCausalLM"], model_type="qwen2", hidden_act="silu", torch_dtype="bfloat16",
-                     use_sliding_window=self.sliding_window is not None)
-        elif self.model_type == "mistral":
-            d.pop("attention_bias")
-            d.update(architectures=["MistralForCausalLM"], hidden_act="silu", torch_dtype="bfloat16")
-        else:
-            d.update(architectures=["LlamaForCausalLM"], hidden_act="silu", torch_dtype="bfloat16",
-                     attention_bias=False, mlp_bias=False)
-        if win_layers is not None and self.sliding_window is not None and self.model_type not in ("exaone4", "gemma3_text"):
+        held = dict(nope=nope, win_layers=win_layers, renorm=renorm, shared_f=shared_f, gran=gran, extra=extra)
+        d.update(hidden_act="silu", torch_dtype="bfloat16")
+        mt = self.model_type
+        if mt in ("llama", "mistral", "qwen2", "granite") and self.attention_bias and not self.o_bias:
+            mt = "qwen2"          # q/k/v bias without o_proj bias is the Qwen2 layout in HuggingFace terms
+            d["model_type"] = "qwen2"
+        d["architectures"] = [_ARCHITECTURES[mt]]
+        _FAMILY_WRITERS.get(mt, _write_plain)(self, d, held)
+        if win_layers is not None and self.sliding_window is not None and mt not in ("exaone4", "gemma3_text"):
             d["layer_types"] = ["sliding_attention" if f else "full_attention" for f in win_layers]
         d.pop("o_bias")
         d.pop("mlp_bias", None)
-        ob, mb = self.o_bias, self.mlp_bias
-        if ob or mb:          # HuggingFace's Llama: attention_bias covers q, k, v AND o
-            d.update(architectures=["LlamaForCausalLM"], model_type="llama", attention_bias=bool(ob), mlp_bias=bool(mb))
-        if self.model_type in ("granitemoe", "granitemoeshared"):
-            d.update(architectures=["GraniteMoeForCausalLM" if self.model_type == "granitemoe"
-                                    else "GraniteMoeSharedForCausalLM"], model_type=self.model_type,
-                     num_local_experts=self.num_local_experts, num_experts_per_tok=self.num_experts_per_tok, **gran)
-            if self.model_type == "granitemoeshared":
-                d["shared_intermediate_size"] = shared_f
-            if d.get("attention_multiplier") is None:
-                d["attention_multiplier"] = 1.0 / math.sqrt(self.head_dim)
-        if self.model_type == "granite":
-            d.update(architectures=["GraniteForCausalLM"], model_type="granite", **gran)
+        if self.o_bias or self.mlp_bias:          # HuggingFace's Llama: attention_bias covers q, k, v AND o
+            d.update(architectures=["LlamaForCausalLM"], model_type="llama", attention_bias=bool(self.o_bias),
+                     mlp_bias=bool(self.mlp_bias))
+        if self.model_type in self._MULTIPLIER_TYPES:
+            d.update(architectures=[_ARCHITECTURES[self.model_type]], model_type=self.model_type, **gran)
             if d.get("attention_multiplier") is None:
                 d["attention_multiplier"] = 1.0 / math.sqrt(self.head_dim)
         return {**extra, **d}
@@ -574,6 +494,125 @@ _FAMILY_READERS = {
     "olmoe": _read_olmoe, "smollm3": _read_smollm3, "olmo2": _read_olmo2, "exaone4": _read_exaone4,
     "helium": _read_interleaved, "ernie4_5": _read_interleaved, "seed_oss": _read_seed_oss, "glm": _read_glm,
     "glm4": _read_glm, "hunyuan_v1_dense": _read_hunyuan,
+}
+
+
+# ---------------------------------------------------------------------------------------------- per-family writers
+# The inverse direction: each takes (the configuration, the config.json dict so far, what was taken out of it) and puts
+# the family's own keys in. ``d`` arrives with the shared keys, hidden_act = silu and the architecture name.
+_ARCHITECTURES = {
+    "llama": "LlamaForCausalLM", "mistral": "MistralForCausalLM", "qwen2": "Qwen2ForCausalLM", "phi3": "Phi3ForCausalLM",
+    "mixtral": "MixtralForCausalLM", "qwen3": "Qwen3ForCausalLM", "qwen3_moe": "Qwen3MoeForCausalLM",
+    "qwen2_moe": "Qwen2MoeForCausalLM", "granite": "GraniteForCausalLM", "granitemoe": "GraniteMoeForCausalLM",
+    "granitemoeshared": "GraniteMoeSharedForCausalLM", "smollm3": "SmolLM3ForCausalLM", "olmo2": "Olmo2ForCausalLM",
+    "olmoe": "OlmoeForCausalLM", "glm": "GlmForCausalLM", "glm4": "Glm4ForCausalLM", "exaone4": "Exaone4ForCausalLM",
+    "helium": "HeliumForCausalLM", "ernie4_5": "Ernie4_5ForCausalLM", "seed_oss": "SeedOssForCausalLM",
+    "hunyuan_v1_dense": "HunYuanDenseV1ForCausalLM", "gemma": "GemmaForCausalLM", "gemma3_text": "Gemma3ForCausalLM",
+}
+
+
+def _write_plain(cfg, d, held):          # llama, granite (and any type without keys of its own)
+    d.update(attention_bias=False, mlp_bias=False)
+
+
+def _write_granite_moe_shared(cfg, d, held):
+    _write_plain(cfg, d, held)
+    d["shared_intermediate_size"] = held["shared_f"]
+
+
+def _write_no_attention_bias_key(cfg, d, held):      # mistral, mixtral, phi3: their configs have no such key
+    d.pop("attention_bias")
+
+
+def _write_qwen2(cfg, d, held):
+    d.pop("attention_bias")
+    d["use_sliding_window"] = cfg.sliding_window is not None
+
+
+def _write_qwen3(cfg, d, held):
+    d.update(use_sliding_window=cfg.sliding_window is not None, head_dim=cfg.head_dim)
+
+
+def _write_qwen_moe(cfg, d, held):       # HuggingFace's names: num_experts, moe_intermediate_size, norm_topk_prob
+    d.update(use_sliding_window=cfg.sliding_window is not None, num_experts=d.pop("num_local_experts"),
+             moe_intermediate_size=cfg.intermediate_size, norm_topk_prob=bool(held["renorm"]), decoder_sparse_step=1,
+             mlp_only_layers=[])
+    d["intermediate_size"] = held["extra"].pop("dense_intermediate_size", cfg.intermediate_size)
+    if cfg.model_type == "qwen3_moe":
+        d["head_dim"] = cfg.head_dim
+    else:
+        d.pop("attention_bias")
+        d.update(qkv_bias=True, shared_expert_intermediate_size=held["shared_f"])
+
+
+def _write_olmoe(cfg, d, held):
+    d.update(attention_bias=False, num_experts=d.pop("num_local_experts"), norm_topk_prob=bool(held["renorm"]),
+             clip_qkv=None)
+
+
+def _write_olmo2(cfg, d, held):
+    d["attention_bias"] = False
+
+
+def _write_exaone4(cfg, d, held):
+    d.pop("attention_bias")
+    nope = held["nope"]
+    d.update(sliding_window=cfg.sliding_window,
+             layer_types=["sliding_attention" if (nope and nope[i]) else "full_attention"
+                          for i in range(cfg.num_hidden_layers)])
+
+
+def _write_head_dim(cfg, d, held):       # hunyuan, helium, seed_oss, ernie4_5: an explicit head_dim and their bias keys
+    d["head_dim"] = cfg.head_dim
+    if cfg.model_type == "hunyuan_v1_dense":
+        d["attention_bias"] = False
+    elif cfg.model_type == "helium":
+        d["mlp_bias"] = False
+    elif cfg.model_type == "seed_oss":
+        d.update(mlp_bias=False, attention_out_bias=False)
+    else:
+        d.pop("attention_bias")
+        d["use_bias"] = False
+
+
+def _write_glm(cfg, d, held):
+    d.update(head_dim=cfg.head_dim, partial_rotary_factor=cfg.partial_rotary_factor)
+
+
+def _write_smollm3(cfg, d, held):
+    d.update(mlp_bias=False, use_sliding_window=cfg.sliding_window is not None,
+             no_rope_layers=list(held["nope"] or [1] * cfg.num_hidden_layers))
+
+
+def _write_gemma(cfg, d, held):
+    d.update(hidden_act="gelu_pytorch_tanh", hidden_activation="gelu_pytorch_tanh", attention_bias=False,
+             head_dim=cfg.head_dim)
+
+
+def _write_gemma3_text(cfg, d, held):
+    d.pop("attention_bias")
+    d.pop("hidden_act")
+    d.pop("rope_theta")
+    d.pop("rope_scaling", None)
+    am, win = held["gran"]["attention_multiplier"], held["win_layers"]
+    rope_full = dict(cfg.rope_scaling or {"rope_type": "default"}, rope_theta=cfg.rope_theta)
+    d.update(hidden_activation="gelu_pytorch_tanh", head_dim=cfg.head_dim,
+             query_pre_attn_scalar=_whole_if_close(1.0 / am ** 2) if am else cfg.head_dim,
+             layer_types=["sliding_attention" if (win is None or win[i]) and cfg.sliding_window else "full_attention"
+                          for i in range(cfg.num_hidden_layers)],
+             rope_parameters={"full_attention": rope_full,
+                              "sliding_attention": {"rope_type": "default",
+                                                    "rope_theta": cfg.rope_local_theta or cfg.rope_theta}},
+             final_logit_softcapping=None, attn_logit_softcapping=None)
+
+
+_FAMILY_WRITERS = {
+    "granitemoeshared": _write_granite_moe_shared, "mistral": _write_no_attention_bias_key, "mixtral": _write_no_attention_bias_key,
+    "phi3": _write_no_attention_bias_key, "qwen2": _write_qwen2, "qwen3": _write_qwen3, "qwen3_moe": _write_qwen_moe,
+    "qwen2_moe": _write_qwen_moe, "olmoe": _write_olmoe, "olmo2": _write_olmo2, "exaone4": _write_exaone4,
+    "hunyuan_v1_dense": _write_head_dim, "helium": _write_head_dim, "seed_oss": _write_head_dim,
+    "ernie4_5": _write_head_dim, "glm": _write_glm, "glm4": _write_glm, "smollm3": _write_smollm3,
+    "gemma": _write_gemma, "gemma3_text": _write_gemma3_text,
 }
 
 
