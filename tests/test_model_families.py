@@ -714,3 +714,35 @@ def test_gemma3_multimodal_wrapper_loads_as_its_language_model(tmp_path):
     hf2 = tr.AutoModelForCausalLM.from_pretrained(str(tmp_path / "ours"), torch_dtype=torch.float32,
                                                   attn_implementation="eager")
     assert type(hf2) is tr.Gemma3ForCausalLM and torch.allclose(hf2(x).logits, ref, atol=4e-4, rtol=1e-3)
+
+
+@pytest.mark.parametrize("family", ["seed_oss", "smollm3", "qwen3", "phi3 with partial rotation"])
+def test_tensor_parallel_slice_loader_agrees_with_slicing_the_whole_model(tmp_path, family):
+    """The types the tensor-parallel teacher takes: what ``load_tp_weights`` reads from a saved folder rank by rank is
+    what ``shard_llama_weights`` cuts out of the whole model; the types it does not take are refused by name."""
+    from llm_distillery_b200.parallel.tp import shard_llama_weights
+    kw = {"seed_oss": dict(model_type="seed_oss", attention_bias=True, head_dim_override=32),
+          "smollm3": dict(model_type="smollm3", no_rope_layers=[1, 0]), "qwen3": dict(model_type="qwen3", qk_norm=True),
+          "phi3 with partial rotation": dict(model_type="phi3", partial_rotary_factor=0.5)}[family]
+    cfg = LlamaConfig(**_base(), **kw)
+    model = build_model(cfg, dtype=torch.float32, device="cpu", seed=1)
+    with torch.no_grad():
+        for n, p in model.named_parameters():
+            if n.endswith("_bias"):
+                p.normal_(0, 0.1)
+    save_hf_model(model, str(tmp_path / "m"))
+    sd = {k: v.detach() for k, v in model.state_dict().items()}
+    for rank in range(2):
+        got_cfg, got = load_tp_weights(str(tmp_path / "m"), rank, 2, dtype=torch.float32)
+        want = shard_llama_weights(cfg, sd, rank, 2, None)
+        assert got_cfg.model_type == cfg.model_type and got_cfg.rotary_dim == cfg.rotary_dim
+        for k, v in want.items():
+            if torch.is_tensor(v):
+                assert torch.equal(v, got[k]), (rank, k)
+    for other in (dict(model_type="olmo2", pre_norm=False, post_norm=True, qk_norm_full=True),
+                  dict(model_type="glm", attention_bias=True, partial_rotary_factor=0.5, rope_interleaved=True),
+                  dict(model_type="gemma", mlp_act="gelu_tanh", norm_plus_one=True, head_dim_override=32)):
+        save_hf_model(build_model(LlamaConfig(**_base(), **other), dtype=torch.float32, device="cpu", seed=1),
+                      str(tmp_path / other["model_type"]))
+        with pytest.raises(NotImplementedError, match="tp_size = 1"):
+            load_tp_weights(str(tmp_path / other["model_type"]), 0, 2)
