@@ -205,9 +205,20 @@ class LlamaConfig:
     @classmethod
     def from_hf_dict(cls, d: dict) -> "LlamaConfig":
         d = dict(d)
-        if d.get("model_type") == "gemma3" and isinstance(d.get("text_config"), dict):
-            # the multimodal wrapper: its language model is read (and saved) as a text-only Gemma 3
-            d = dict(d["text_config"], model_type="gemma3_text")
+        if d.get("model_type") not in cls._KNOWN_TYPES and isinstance(d.get("text_config"), dict):
+            # a multimodal wrapper (gemma3, mistral3, llava ...): its language model is read, and saved, as a text model
+            text = dict(d["text_config"])
+            if d.get("model_type") == "gemma3":
+                text["model_type"] = "gemma3_text"
+            elif text.get("model_type") in cls._KNOWN_TYPES:
+                missing = [k for k in ("vocab_size", "hidden_size", "intermediate_size", "num_hidden_layers",
+                                       "num_attention_heads") if text.get(k) is None]
+                if missing:      # such blocks list only what differs from HuggingFace's defaults for that text model
+                    raise ValueError(f"the text_config of this {d.get('model_type')} checkpoint does not name {missing}")
+            else:
+                raise NotImplementedError(f"model_type {d.get('model_type')!r} with a {text.get('model_type')!r} language "
+                                          f"model: only Llama-shaped decoders are built {cls._KNOWN_TYPES}")
+            d = text
         keys = {f for f in cls.__dataclass_fields__} - {"extra"}
         kw = {k: v for k, v in d.items() if k in keys}
         mt = d.get("model_type", "llama")

@@ -746,3 +746,24 @@ def test_tensor_parallel_slice_loader_agrees_with_slicing_the_whole_model(tmp_pa
                       str(tmp_path / other["model_type"]))
         with pytest.raises(NotImplementedError, match="tp_size = 1"):
             load_tp_weights(str(tmp_path / other["model_type"]), 0, 2)
+
+
+def test_mistral3_wrapper_loads_as_its_language_model(tmp_path):
+    """Mistral Small 3.1 style checkpoints: a vision tower around a Mistral text model."""
+    text = dict(_base(), model_type="mistral", head_dim=32, sliding_window=None)
+    vision = dict(hidden_size=32, intermediate_size=64, num_hidden_layers=1, num_attention_heads=2, image_size=28,
+                  patch_size=14, head_dim=16)
+    torch.manual_seed(11)
+    hf = tr.Mistral3ForConditionalGeneration(tr.Mistral3Config(text_config=text, vision_config=vision,
+                                                               attn_implementation="eager")).float().eval()
+    hf.save_pretrained(str(tmp_path / "hf"), safe_serialization=True)
+    model = load_hf_model(str(tmp_path / "hf"), dtype=torch.float32)
+    assert model.cfg.model_type == "mistral" and model.cfg.head_dim == 32
+    x = torch.randint(1, 320, (2, 40))
+    with torch.no_grad():
+        ref = hf(input_ids=x).logits
+        assert torch.allclose(model(x), ref, atol=3e-4, rtol=1e-3), (model(x) - ref).abs().max()
+    with pytest.raises(ValueError, match="does not name"):
+        LlamaConfig.from_hf_dict({"model_type": "mistral3", "text_config": {"model_type": "mistral", "hidden_size": 64}})
+    with pytest.raises(NotImplementedError, match="language model"):
+        LlamaConfig.from_hf_dict({"model_type": "qwen2_vl", "text_config": {"model_type": "qwen2_vl_text"}})
