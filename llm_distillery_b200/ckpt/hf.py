@@ -289,8 +289,18 @@ def load_tp_weights(path: str, rank: int, tp: int, vocab: int | None = None, dty
                 for k in sf.keys():
                     where[k] = fn
     handles: dict = {}
+    # a multimodal wrapper keeps its language model under a prefix: the plain names point at the prefixed tensors
+    stored = {k: k for k in where}
+    wrapped = [k for k in where if "language_model" in k and k.endswith("embed_tokens.weight")]
+    if wrapped:
+        prefix = wrapped[0][: -len("embed_tokens.weight")]
+        stored.update({"model." + k[len(prefix):]: k for k in where if k.startswith(prefix)})
+        stored.update({"lm_head.weight": k for k in where if k.endswith("lm_head.weight")})
 
     def sl(name: str, rows=None, cols=None) -> torch.Tensor:
+        if name not in stored:
+            raise KeyError(f"tensor {name} is not in the checkpoint at {path}")
+        name = stored[name]
         fn = where[name]
         if fn not in handles:
             handles[fn] = safe_open(os.path.join(path, fn), "pt")
@@ -337,7 +347,7 @@ def load_tp_weights(path: str, rank: int, tp: int, vocab: int | None = None, dty
         w[p + "down_proj"] = sl(hp + "mlp.down_proj.weight", cols=(rank * fl, (rank + 1) * fl)).contiguous()
         w[p + "input_layernorm"] = sl(hp + "input_layernorm.weight")
         w[p + "post_attention_layernorm"] = sl(hp + "post_attention_layernorm.weight")
-    head_name = "lm_head.weight" if "lm_head.weight" in where else "model.embed_tokens.weight"
+    head_name = "lm_head.weight" if "lm_head.weight" in stored else "model.embed_tokens.weight"
     V = min(vocab or cfg.vocab_size, cfg.vocab_size)
     Vl = -(-(-(-V // tp)) // 8) * 8
     lo, hi = min(rank * Vl, V), min((rank + 1) * Vl, V)

@@ -763,6 +763,13 @@ def test_mistral3_wrapper_loads_as_its_language_model(tmp_path):
     with torch.no_grad():
         ref = hf(input_ids=x).logits
         assert torch.allclose(model(x), ref, atol=3e-4, rtol=1e-3), (model(x) - ref).abs().max()
+    # the tensor-parallel loader reads the wrapped tensors through the same names
+    from llm_distillery_b200.parallel.tp import shard_llama_weights
+    sd = {k: v.detach() for k, v in model.state_dict().items()}
+    for rank in range(2):
+        _, got = load_tp_weights(str(tmp_path / "hf"), rank, 2, dtype=torch.float32)
+        want = shard_llama_weights(model.cfg, sd, rank, 2, None)
+        assert all(torch.equal(v, got[k]) for k, v in want.items() if torch.is_tensor(v))
     with pytest.raises(ValueError, match="does not name"):
         LlamaConfig.from_hf_dict({"model_type": "mistral3", "text_config": {"model_type": "mistral", "hidden_size": 64}})
     with pytest.raises(NotImplementedError, match="language model"):
