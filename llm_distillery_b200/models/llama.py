@@ -602,7 +602,7 @@ class LlamaModel(nn.Module):
                 yield pre + "mlp.down_proj.weight", l.down_proj, None
                 yield pre + "post_feedforward_layernorm.weight", l.mlp_out_norm, None
                 continue
-            if cfg.model_type in ("olmo2", "exaone4", "glm", "glm4"):
+            if cfg.model_type in ("olmo2", "olmo3", "exaone4", "glm", "glm4"):
                 glm = cfg.model_type in ("glm", "glm4")
                 if glm:
                     yield pre + "input_layernorm.weight", l.input_layernorm, None

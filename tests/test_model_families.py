@@ -382,6 +382,8 @@ def test_smollm3_layers_without_rotation_match_huggingface(tmp_path):
 
 _MORE = {   # family: (HuggingFace model, config, extra config keys, (pre_norm, post_norm, qk_norm_full, qk_norm), general node)
     "olmo2": ("Olmo2ForCausalLM", "Olmo2Config", {}, (False, True, True, False), True),
+    "olmo3": ("Olmo3ForCausalLM", "Olmo3Config", dict(sliding_window=24, layer_types=["sliding_attention", "full_attention"]),
+              (False, True, True, False), True),
     "glm": ("GlmForCausalLM", "GlmConfig", dict(head_dim=16), (True, False, False, False), False),
     "glm4": ("Glm4ForCausalLM", "Glm4Config", dict(head_dim=16), (True, True, False, False), True),
     "exaone4": ("Exaone4ForCausalLM", "Exaone4Config", dict(sliding_window=None, layer_types=["full_attention"] * 2),
@@ -407,7 +409,8 @@ _MORE = {   # family: (HuggingFace model, config, extra config keys, (pre_norm, 
                                               ("glm4", True), ("exaone4", False), ("exaone4 hybrid", True),
                                               ("helium", False), ("ernie4_5", False), ("seed_oss", False),
                                               ("hunyuan_v1_dense", False), ("hunyuan_v1_dense", True),
-                                              ("gemma", False), ("gemma3_text", False), ("gemma3_text", True)])
+                                              ("gemma", False), ("gemma3_text", False), ("gemma3_text", True),
+                                              ("olmo3", False), ("olmo3", True)])
 def test_more_decoder_families_match_huggingface(tmp_path, family, recompute):
     """OLMo 2 (norms behind the branches only, q/k norms over the whole projections), EXAONE 4 (the same placement with
     per-head q/k norms; hybrid checkpoints: windowed layers rotate, global ones do not), GLM (half of each head rotates,
@@ -592,6 +595,7 @@ def test_every_model_type_survives_config_round_trips():
         "smollm3": dict(no_rope_layers=[1, 0]),
         "olmo2": dict(pre_norm=False, post_norm=True, qk_norm_full=True),
         "olmoe": dict(moe, qk_norm_full=True, moe_renormalize=False),
+        "olmo3": dict(pre_norm=False, post_norm=True, qk_norm_full=True, sliding_window=24, window_layers=[1, 0]),
         "glm": dict(attention_bias=True, partial_rotary_factor=0.5, rope_interleaved=True),
         "glm4": dict(attention_bias=True, partial_rotary_factor=0.5, rope_interleaved=True, post_norm=True),
         "exaone4": dict(pre_norm=False, post_norm=True, qk_norm=True, no_rope_layers=[1, 0], window_layers=[1, 0],
