@@ -190,7 +190,7 @@ class LlamaConfig:
 
     _KNOWN_TYPES = ("llama", "mistral", "qwen2", "phi3", "mixtral", "qwen3", "qwen3_moe", "qwen2_moe", "granite",
                     "smollm3", "olmo2", "glm", "glm4", "exaone4", "helium", "ernie4_5", "seed_oss", "hunyuan_v1_dense",
-                    "olmoe", "granitemoe", "granitemoeshared", "gemma", "gemma3_text", "olmo3")
+                    "olmoe", "granitemoe", "granitemoeshared", "gemma", "gemma3_text", "olmo3", "ministral")
     # what HuggingFace's attention_bias puts a bias on, per family: q, k and v only / the o projection as well (built for
     # the second group, refused for every other family); families whose MLP may carry biases; families with experts
     _QKV_BIAS_TYPES = ("qwen2", "qwen2_moe", "glm", "glm4", "seed_oss", "helium")
@@ -408,6 +408,14 @@ def _read_olmo2(mt, d, kw):            # no norms in front of the branches, norm
     kw.update(pre_norm=False, post_norm=True, qk_norm_full=True)
 
 
+def _read_ministral(mt, d, kw):        # Mistral layers; the config says which of them are windowed
+    types = d.get("layer_types")
+    if kw.get("sliding_window") and types is not None and "sliding_attention" in types:
+        kw["window_layers"] = [int(t == "sliding_attention") for t in types]
+    elif types is not None:
+        kw["sliding_window"] = None
+
+
 def _read_olmo3(mt, d, kw):            # OLMo 2 layers, three of every four with a sliding window
     _read_olmo2(mt, d, kw)
     n_layers = int(kw.get("num_hidden_layers", 32))
@@ -514,7 +522,7 @@ _FAMILY_READERS = {
     "gemma": _read_gemma, "gemma3_text": _read_gemma3_text,
     "qwen2": _read_qwen2, "qwen3": _read_qwen3, "qwen3_moe": _read_qwen3_moe, "qwen2_moe": _read_qwen2_moe,
     "mixtral": _read_mixtral, "granitemoe": _read_granite_moe, "granitemoeshared": _read_granite_moe,
-    "olmoe": _read_olmoe, "smollm3": _read_smollm3, "olmo2": _read_olmo2, "olmo3": _read_olmo3, "exaone4": _read_exaone4,
+    "olmoe": _read_olmoe, "smollm3": _read_smollm3, "olmo2": _read_olmo2, "olmo3": _read_olmo3, "ministral": _read_ministral, "exaone4": _read_exaone4,
     "helium": _read_interleaved, "ernie4_5": _read_interleaved, "seed_oss": _read_seed_oss, "glm": _read_glm,
     "glm4": _read_glm, "hunyuan_v1_dense": _read_hunyuan,
 }
@@ -524,7 +532,7 @@ _FAMILY_READERS = {
 # The inverse direction: each takes (the configuration, the config.json dict so far, what was taken out of it) and puts
 # the family's own keys in. ``d`` arrives with the shared keys, hidden_act = silu and the architecture name.
 _ARCHITECTURES = {
-    "llama": "LlamaForCausalLM", "mistral": "MistralForCausalLM", "qwen2": "Qwen2ForCausalLM", "phi3": "Phi3ForCausalLM",
+    "llama": "LlamaForCausalLM", "mistral": "MistralForCausalLM", "ministral": "MinistralForCausalLM", "qwen2": "Qwen2ForCausalLM", "phi3": "Phi3ForCausalLM",
     "mixtral": "MixtralForCausalLM", "qwen3": "Qwen3ForCausalLM", "qwen3_moe": "Qwen3MoeForCausalLM",
     "qwen2_moe": "Qwen2MoeForCausalLM", "granite": "GraniteForCausalLM", "granitemoe": "GraniteMoeForCausalLM",
     "granitemoeshared": "GraniteMoeSharedForCausalLM", "smollm3": "SmolLM3ForCausalLM", "olmo2": "Olmo2ForCausalLM", "olmo3": "Olmo3ForCausalLM",
@@ -545,6 +553,11 @@ def _write_granite_moe_shared(cfg, d, held):
 
 def _write_no_attention_bias_key(cfg, d, held):      # mistral, mixtral, phi3: their configs have no such key
     d.pop("attention_bias")
+
+
+def _write_ministral(cfg, d, held):      # HuggingFace's module needs the head size spelled out
+    d.pop("attention_bias")
+    d["head_dim"] = cfg.head_dim
 
 
 def _write_qwen2(cfg, d, held):
@@ -630,7 +643,8 @@ def _write_gemma3_text(cfg, d, held):
 
 
 _FAMILY_WRITERS = {
-    "granitemoeshared": _write_granite_moe_shared, "mistral": _write_no_attention_bias_key, "mixtral": _write_no_attention_bias_key,
+    "granitemoeshared": _write_granite_moe_shared, "mistral": _write_no_attention_bias_key,
+    "ministral": _write_ministral, "mixtral": _write_no_attention_bias_key,
     "phi3": _write_no_attention_bias_key, "qwen2": _write_qwen2, "qwen3": _write_qwen3, "qwen3_moe": _write_qwen_moe,
     "qwen2_moe": _write_qwen_moe, "olmoe": _write_olmoe, "olmo2": _write_olmo2, "olmo3": _write_olmo2, "exaone4": _write_exaone4,
     "hunyuan_v1_dense": _write_head_dim, "helium": _write_head_dim, "seed_oss": _write_head_dim,

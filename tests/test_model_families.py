@@ -384,6 +384,9 @@ _MORE = {   # family: (HuggingFace model, config, extra config keys, (pre_norm, 
     "olmo2": ("Olmo2ForCausalLM", "Olmo2Config", {}, (False, True, True, False), True),
     "olmo3": ("Olmo3ForCausalLM", "Olmo3Config", dict(sliding_window=24, layer_types=["sliding_attention", "full_attention"]),
               (False, True, True, False), True),
+    "ministral": ("MinistralForCausalLM", "MinistralConfig",
+                  dict(head_dim=16, sliding_window=24, layer_types=["sliding_attention", "full_attention"]),
+                  (True, False, False, False), False),
     "glm": ("GlmForCausalLM", "GlmConfig", dict(head_dim=16), (True, False, False, False), False),
     "glm4": ("Glm4ForCausalLM", "Glm4Config", dict(head_dim=16), (True, True, False, False), True),
     "exaone4": ("Exaone4ForCausalLM", "Exaone4Config", dict(sliding_window=None, layer_types=["full_attention"] * 2),
@@ -410,7 +413,7 @@ _MORE = {   # family: (HuggingFace model, config, extra config keys, (pre_norm, 
                                               ("helium", False), ("ernie4_5", False), ("seed_oss", False),
                                               ("hunyuan_v1_dense", False), ("hunyuan_v1_dense", True),
                                               ("gemma", False), ("gemma3_text", False), ("gemma3_text", True),
-                                              ("olmo3", False), ("olmo3", True)])
+                                              ("olmo3", False), ("olmo3", True), ("ministral", False)])
 def test_more_decoder_families_match_huggingface(tmp_path, family, recompute):
     """OLMo 2 (norms behind the branches only, q/k norms over the whole projections), EXAONE 4 (the same placement with
     per-head q/k norms; hybrid checkpoints: windowed layers rotate, global ones do not), GLM (half of each head rotates,
@@ -595,6 +598,7 @@ def test_every_model_type_survives_config_round_trips():
         "smollm3": dict(no_rope_layers=[1, 0]),
         "olmo2": dict(pre_norm=False, post_norm=True, qk_norm_full=True),
         "olmoe": dict(moe, qk_norm_full=True, moe_renormalize=False),
+        "ministral": dict(sliding_window=24, window_layers=[1, 0]),
         "olmo3": dict(pre_norm=False, post_norm=True, qk_norm_full=True, sliding_window=24, window_layers=[1, 0]),
         "glm": dict(attention_bias=True, partial_rotary_factor=0.5, rope_interleaved=True),
         "glm4": dict(attention_bias=True, partial_rotary_factor=0.5, rope_interleaved=True, post_norm=True),
